@@ -1,0 +1,164 @@
+"""End-to-end CPU fp32 checks of the engine plumbing (scheduler, paged cache,
+model runner) against independent oracles: HF transformers for the dense
+families and a cache-free recomputation for every family."""
+import numpy as np
+import pytest
+import torch
+
+from vllm_ascend_b200.config import get_model_config
+from vllm_ascend_b200.engine.llm import LLM
+from vllm_ascend_b200.engine.request import SamplingParams
+from vllm_ascend_b200.models.transformer import export_hf_state_dict
+
+
+def _prompts(n, length, vocab, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, vocab, size=length).tolist() for _ in range(n)]
+
+
+def _hf_greedy(hf_model, prompt, n_new):
+    ids = torch.tensor([prompt])
+    out = []
+    with torch.no_grad():
+        for _ in range(n_new):
+            logits = hf_model(ids).logits[0, -1]
+            t = int(logits.argmax())
+            out.append(t)
+            ids = torch.cat([ids, torch.tensor([[t]])], dim=1)
+    return out
+
+
+def _make_hf(cfg, sd):
+    import transformers
+    common = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+                  intermediate_size=cfg.intermediate_size, num_hidden_layers=cfg.num_hidden_layers,
+                  num_attention_heads=cfg.num_attention_heads,
+                  num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
+                  rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta,
+                  max_position_embeddings=4096, tie_word_embeddings=False,
+                  attention_bias=False, torch_dtype=torch.float32)
+    if cfg.architecture == "Qwen3ForCausalLM":
+        hc = transformers.Qwen3Config(**common)
+        hc.rope_parameters = {"rope_type": "default", "rope_theta": cfg.rope_theta}
+        m = transformers.Qwen3ForCausalLM(hc)
+    else:
+        hc = transformers.LlamaConfig(**common)
+        hc.rope_parameters = {"rope_type": "default", "rope_theta": cfg.rope_theta}
+        m = transformers.LlamaForCausalLM(hc)
+    missing, unexpected = m.load_state_dict(sd, strict=False)
+    assert not [k for k in missing if "rotary" not in k], missing
+    assert not unexpected, unexpected
+    return m.eval().float()
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen", "tiny-llama"])
+def test_greedy_matches_hf(preset):
+    """Config 1 of the benchmark list: 4 prompts x 32 tokens, 16 greedy tokens, block 16."""
+    cfg = get_model_config(preset)
+    llm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=48,
+              block_size=16)
+    prompts = _prompts(4, 32, cfg.vocab_size)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    hf = _make_hf(cfg, export_hf_state_dict(llm.engine.runner.model))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == _hf_greedy(hf, p, 16)
+        assert o.outputs[0].finish_reason == "length"
+
+
+def _recompute_greedy(model, prompt, n_new, block_size=16):
+    """Cache-free oracle: every step re-runs the whole sequence as one prefill."""
+    from vllm_ascend_b200.attention.metadata import AttentionMetadata
+    cfg = model.cfg
+    out = []
+    ids = list(prompt)
+    for _ in range(n_new):
+        T = len(ids)
+        nblk = (T + block_size - 1) // block_size + 1
+        caches = []
+        for L in model.layers:
+            if cfg.use_mla:
+                shapes = [(nblk, block_size, 1, cfg.kv_lora_rank), (nblk, block_size, 1, cfg.qk_rope_head_dim)]
+            else:
+                a = L.self_attn
+                shapes = [(nblk, block_size, a.Hkv, a.D)] * 2
+            caches.append(tuple(torch.zeros(s) for s in shapes))
+        pos = torch.arange(T)
+        meta = AttentionMetadata(
+            num_reqs=1, num_actual_tokens=T, max_query_len=T, max_seq_len=T,
+            query_start_loc=torch.tensor([0, T], dtype=torch.int32),
+            seq_lens=torch.tensor([T], dtype=torch.int32),
+            block_table=torch.arange(1, nblk, dtype=torch.int32).unsqueeze(0),
+            slot_mapping=pos + block_size, positions=pos,
+            query_start_loc_cpu=np.array([0, T]), seq_lens_cpu=np.array([T]))
+        with torch.no_grad():
+            h = model.forward(torch.tensor(ids), meta, caches)
+            t = int(model.compute_logits(h[-1:]).argmax())
+        out.append(t)
+        ids.append(t)
+    return out
+
+
+@pytest.mark.parametrize("preset", ["tiny-moe", "tiny-deepseek"])
+def test_greedy_matches_recompute(preset):
+    cfg = get_model_config(preset)
+    llm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=24,
+              block_size=16)
+    prompts = _prompts(3, 20, cfg.vocab_size, seed=1)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == _recompute_greedy(llm.engine.runner.model, p, 8)
+
+
+def test_chunked_prefill_and_preemption_are_transparent():
+    cfg = get_model_config("tiny-qwen")
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    prompts = _prompts(6, 40, cfg.vocab_size, seed=3)
+    big = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=512, block_size=16)
+    ref = [o.outputs[0].token_ids for o in big.generate(prompts, sp)]
+    # tiny token budget -> chunked prefill; tiny pool -> recompute preemption
+    small = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=16,
+                block_size=16, num_gpu_blocks_override=14)
+    got = [o.outputs[0].token_ids for o in small.generate(prompts, sp)]
+    assert got == ref
+    assert small.engine.scheduler.num_preemptions > 0
+
+
+def test_prefix_caching_reuses_blocks_and_keeps_outputs():
+    cfg = get_model_config("tiny-qwen")
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    shared = _prompts(1, 48, cfg.vocab_size, seed=5)[0]
+    prompts = [shared + t for t in _prompts(3, 8, cfg.vocab_size, seed=6)]
+    plain = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, block_size=16)
+    ref = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    pc = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, block_size=16,
+             enable_prefix_caching=True)
+    first = pc.generate(prompts[:1], sp)
+    rest = pc.generate(prompts[1:], sp)
+    assert [o.outputs[0].token_ids for o in first + rest] == ref
+    assert all(o.num_cached_tokens == 48 for o in rest)
+
+
+def test_stop_token_and_sampling_params_validation():
+    cfg = get_model_config("tiny-qwen")
+    llm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, block_size=16)
+    p = _prompts(1, 16, cfg.vocab_size, seed=9)
+    full = llm.generate(p, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))[0].outputs[0].token_ids
+    stop_at = full[3]
+    out = llm.generate(p, SamplingParams(temperature=0.0, max_tokens=10, stop_token_ids=[stop_at]))[0]
+    assert out.outputs[0].token_ids == full[:full.index(stop_at) + 1]
+    assert out.outputs[0].finish_reason == "stop"
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0.0)
+    with pytest.raises(ValueError):
+        SamplingParams(temperature=-1)
+
+
+def test_random_sampling_is_seeded_and_respects_top_k():
+    cfg = get_model_config("tiny-qwen")
+    llm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, block_size=16, seed=7)
+    p = _prompts(2, 16, cfg.vocab_size, seed=11)
+    sp = SamplingParams(temperature=1.0, top_k=1, max_tokens=6, ignore_eos=True)
+    greedy = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    a = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
+    g = [o.outputs[0].token_ids for o in llm.generate(p, greedy)]
+    assert a == g          # top_k=1 is greedy whatever the noise

@@ -1,0 +1,87 @@
+"""Per-step attention metadata.
+
+Field set follows the contract of ``AscendCommonAttentionMetadata``
+(vllm_ascend/attention/utils.py:214-320): query_start_loc / seq_lens on host and
+device, block table, slot mapping, positions, attention state and the
+decodes-first split.  Device tensors are views of persistent buffers so captured
+CUDA graphs replay without host-side patching.
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+
+class AttentionState(enum.IntEnum):
+    """States of vllm_ascend/attention/attention_v1.py:152-157."""
+    PrefillNoCache = 0
+    PrefillCacheHit = 1
+    DecodeOnly = 2
+    ChunkedPrefill = 3
+    SpecDecoding = 4
+
+
+@dataclass
+class AttentionMetadata:
+    num_reqs: int
+    num_actual_tokens: int
+    max_query_len: int
+    max_seq_len: int
+    query_start_loc: torch.Tensor          # int32 [B+1] device
+    seq_lens: torch.Tensor                 # int32 [B] device
+    block_table: torch.Tensor              # int32 [B, max_blocks] device
+    slot_mapping: torch.Tensor             # int64 [T] device
+    positions: torch.Tensor                # int64 [T] device
+    query_start_loc_cpu: np.ndarray
+    seq_lens_cpu: np.ndarray
+    attn_state: AttentionState = AttentionState.ChunkedPrefill
+    num_decodes: int = 0
+    num_decode_tokens: int = 0
+    num_prefills: int = 0
+    # work list of the tensor-core attention kernel (one entry per 128-row tile)
+    tile_seq: Optional[torch.Tensor] = None
+    tile_qoff: Optional[torch.Tensor] = None
+    num_tiles: int = 0
+    num_splits: int = 1
+    num_input_tokens: int = 0              # padded token count (graph replay)
+    # decode-context-parallel / extras
+    dcp_world_size: int = 1
+    dcp_rank: int = 0
+    extra: Optional[dict] = None
+
+
+def split_decodes_and_prefills(query_lens: np.ndarray, decode_threshold: int = 1) -> tuple[int, int, int, int]:
+    """Batches are ordered decodes-first; split at the first request whose query
+    is longer than the threshold (vllm_ascend/attention/utils.py:346-435).
+    Returns (num_decodes, num_prefills, num_decode_tokens, num_prefill_tokens)."""
+    n = len(query_lens)
+    if n == 0:
+        return 0, 0, 0, 0
+    is_prefill = query_lens > decode_threshold
+    if not is_prefill.any():
+        return n, 0, int(query_lens.sum()), 0
+    first = int(np.argmax(is_prefill))
+    nd_tokens = int(query_lens[:first].sum())
+    return first, n - first, nd_tokens, int(query_lens.sum()) - nd_tokens
+
+
+def build_tile_worklist(query_lens: np.ndarray, tok_per_tile: int,
+                        seq_lens: Optional[np.ndarray] = None) -> tuple[np.ndarray, np.ndarray]:
+    """(tile_seq, tile_qoff) for the tensor-core kernel.  Tiles of long-context
+    sequences are placed first so the heaviest CTAs start early."""
+    n_tiles = (query_lens + tok_per_tile - 1) // tok_per_tile
+    total = int(n_tiles.sum())
+    tile_seq = np.repeat(np.arange(len(query_lens), dtype=np.int32), n_tiles)
+    starts = np.cumsum(n_tiles) - n_tiles
+    tile_idx = np.arange(total, dtype=np.int32) - np.repeat(starts, n_tiles).astype(np.int32)
+    tile_qoff = (tile_idx * tok_per_tile).astype(np.int32)
+    if seq_lens is not None and total > 1:
+        ctx = (seq_lens - query_lens)[tile_seq]
+        work = ctx + tile_qoff                      # keys visible to the tile's first row
+        order = np.argsort(-work, kind="stable")
+        tile_seq, tile_qoff = tile_seq[order], tile_qoff[order]
+    return np.ascontiguousarray(tile_seq), np.ascontiguousarray(tile_qoff)

@@ -1,0 +1,289 @@
+"""Engine configuration objects and the model presets named by the benchmarks.
+
+``ModelConfig`` is an HF-``config.json``-shaped description of a decoder; it can
+be built from a checkpoint directory (``from_pretrained``) or from a preset
+(random-init weights).  ``EngineConfig`` groups the cache / scheduler /
+parallel knobs, mirroring the fields of upstream ``VllmConfig`` that the
+reference reads in ``vllm_ascend/platform.py:343-395``.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field, asdict
+from typing import Any, Optional
+
+import torch
+
+
+@dataclass
+class ModelConfig:
+    architecture: str = "Qwen3ForCausalLM"
+    vocab_size: int = 1024
+    hidden_size: int = 256
+    intermediate_size: int = 512
+    num_hidden_layers: int = 2
+    num_attention_heads: int = 4
+    num_key_value_heads: int = 2
+    head_dim: int = 64
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    rope_scaling: Optional[dict] = None
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = False
+    qk_norm: bool = False            # Qwen3 per-head q/k RMSNorm
+    attention_bias: bool = False     # Qwen2 style qkv bias
+    sliding_window: Optional[int] = None
+    hidden_act: str = "silu"
+    # ---- MoE ----
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    n_shared_experts: int = 0
+    norm_topk_prob: bool = True
+    scoring_func: str = "softmax"    # "softmax" | "sigmoid"
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    first_k_dense_replace: int = 0   # leading dense layers (DeepSeek)
+    e_score_correction_bias: bool = False
+    # ---- MLA ----
+    use_mla: bool = False
+    q_lora_rank: Optional[int] = None
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    # ---- numerics / quantization ----
+    dtype: str = "bfloat16"
+    quantization: Optional[str] = None   # None | "fp8" (128x128 block) | "w8a8_dynamic"
+    weight_block_size: tuple = (128, 128)
+    init_std: float = 0.02
+    seed: int = 0
+    name: str = "tiny-qwen"
+    model_path: Optional[str] = None
+
+    @property
+    def torch_dtype(self) -> torch.dtype:
+        return {"bfloat16": torch.bfloat16, "float16": torch.float16,
+                "float32": torch.float32}[self.dtype]
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def is_moe_layer(self, layer_idx: int) -> bool:
+        return self.is_moe and layer_idx >= self.first_k_dense_replace
+
+    @property
+    def q_head_dim(self) -> int:
+        return (self.qk_nope_head_dim + self.qk_rope_head_dim) if self.use_mla else self.head_dim
+
+    @property
+    def kv_cache_entry_dims(self) -> tuple[int, int]:
+        """Per-token per-layer widths of the two cache tensors.
+
+        GQA: (kv_heads*head_dim, kv_heads*head_dim); MLA: (kv_lora_rank, rope_dim)
+        — the layout contract of vllm_ascend/worker/model_runner_v1.py:3994-4069.
+        """
+        if self.use_mla:
+            return (self.kv_lora_rank, self.qk_rope_head_dim)
+        w = self.num_key_value_heads * self.head_dim
+        return (w, w)
+
+    # ------------------------------------------------------------------
+    @classmethod
+    def from_hf_dict(cls, d: dict, **over) -> "ModelConfig":
+        arch = (d.get("architectures") or ["LlamaForCausalLM"])[0]
+        hs = d["hidden_size"]
+        nh = d["num_attention_heads"]
+        kw: dict[str, Any] = dict(
+            architecture=arch,
+            vocab_size=d["vocab_size"], hidden_size=hs,
+            intermediate_size=d.get("intermediate_size", 4 * hs),
+            num_hidden_layers=d["num_hidden_layers"], num_attention_heads=nh,
+            num_key_value_heads=d.get("num_key_value_heads", nh),
+            head_dim=d.get("head_dim") or hs // nh,
+            rms_norm_eps=d.get("rms_norm_eps", 1e-6),
+            rope_theta=d.get("rope_theta", 10000.0),
+            rope_scaling=d.get("rope_scaling"),
+            max_position_embeddings=d.get("max_position_embeddings", 32768),
+            tie_word_embeddings=d.get("tie_word_embeddings", False),
+            qk_norm=arch.startswith("Qwen3"),
+            attention_bias=d.get("attention_bias", arch.startswith("Qwen2")),
+            sliding_window=d.get("sliding_window") if d.get("use_sliding_window", False) else None,
+            hidden_act=d.get("hidden_act", "silu"),
+            dtype=str(d.get("torch_dtype", "bfloat16")).replace("torch.", ""),
+        )
+        if "num_experts" in d or "n_routed_experts" in d:
+            kw.update(
+                num_experts=d.get("num_experts", d.get("n_routed_experts", 0)),
+                num_experts_per_tok=d.get("num_experts_per_tok", 0),
+                moe_intermediate_size=d.get("moe_intermediate_size", 0),
+                n_shared_experts=d.get("n_shared_experts", 0) or 0,
+                norm_topk_prob=d.get("norm_topk_prob", True),
+                scoring_func=d.get("scoring_func", "softmax"),
+                n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1,
+                routed_scaling_factor=d.get("routed_scaling_factor", 1.0),
+                first_k_dense_replace=d.get("first_k_dense_replace", 0),
+                e_score_correction_bias=d.get("topk_method", "") == "noaux_tc",
+            )
+        if "kv_lora_rank" in d:
+            kw.update(use_mla=True, q_lora_rank=d.get("q_lora_rank"),
+                      kv_lora_rank=d["kv_lora_rank"],
+                      qk_nope_head_dim=d["qk_nope_head_dim"],
+                      qk_rope_head_dim=d["qk_rope_head_dim"], v_head_dim=d["v_head_dim"])
+        qc = d.get("quantization_config")
+        if qc:
+            method = qc.get("quant_method", "")
+            if method == "fp8" and qc.get("weight_block_size"):
+                kw.update(quantization="fp8", weight_block_size=tuple(qc["weight_block_size"]))
+            elif method == "compressed-tensors":
+                kw.update(quantization="compressed-tensors")
+            elif method:
+                kw.update(quantization=method)
+        kw.update(over)
+        return cls(**kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, **over) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            d = json.load(f)
+        cfg = cls.from_hf_dict(d, **over)
+        cfg.model_path = path
+        cfg.name = os.path.basename(os.path.normpath(path))
+        return cfg
+
+    def to_hf_dict(self) -> dict:
+        d = asdict(self)
+        d["architectures"] = [self.architecture]
+        d["torch_dtype"] = self.dtype
+        if self.is_moe:
+            d["n_routed_experts"] = self.num_experts
+        return d
+
+
+def _preset(**kw) -> ModelConfig:
+    return ModelConfig(**kw)
+
+
+#: Architectures named by the benchmark configs (random-init, synthetic prompts).
+PRESETS: dict[str, Any] = {
+    "tiny-qwen": lambda: _preset(
+        name="tiny-qwen", architecture="Qwen3ForCausalLM", vocab_size=1024, hidden_size=256,
+        intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=64, rope_theta=1e6, qk_norm=True, dtype="float32"),
+    "qwen3-8b": lambda: _preset(
+        name="qwen3-8b", architecture="Qwen3ForCausalLM", vocab_size=151936, hidden_size=4096,
+        intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+        num_key_value_heads=8, head_dim=128, rope_theta=1e6, qk_norm=True,
+        max_position_embeddings=40960),
+    "llama-3.1-70b": lambda: _preset(
+        name="llama-3.1-70b", architecture="LlamaForCausalLM", vocab_size=128256,
+        hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+        num_attention_heads=64, num_key_value_heads=8, head_dim=128, rope_theta=5e5,
+        rms_norm_eps=1e-5, max_position_embeddings=131072),
+    "qwen3-30b-a3b": lambda: _preset(
+        name="qwen3-30b-a3b", architecture="Qwen3MoeForCausalLM", vocab_size=151936,
+        hidden_size=2048, intermediate_size=6144, num_hidden_layers=48,
+        num_attention_heads=32, num_key_value_heads=4, head_dim=128, rope_theta=1e6,
+        qk_norm=True, num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768,
+        norm_topk_prob=True, max_position_embeddings=40960),
+    "deepseek-v3": lambda: _preset(
+        name="deepseek-v3", architecture="DeepseekV3ForCausalLM", vocab_size=129280,
+        hidden_size=7168, intermediate_size=18432, num_hidden_layers=61,
+        num_attention_heads=128, num_key_value_heads=128, head_dim=192, rope_theta=1e4,
+        num_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048,
+        n_shared_experts=1, scoring_func="sigmoid", n_group=8, topk_group=4,
+        routed_scaling_factor=2.5, first_k_dense_replace=3, e_score_correction_bias=True,
+        use_mla=True, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+        qk_rope_head_dim=64, v_head_dim=128, quantization="fp8",
+        max_position_embeddings=163840),
+    # small shapes of each family for tests
+    "tiny-llama": lambda: _preset(
+        name="tiny-llama", architecture="LlamaForCausalLM", vocab_size=512, hidden_size=128,
+        intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, rope_theta=1e4, dtype="float32"),
+    "tiny-moe": lambda: _preset(
+        name="tiny-moe", architecture="Qwen3MoeForCausalLM", vocab_size=512, hidden_size=128,
+        intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, rope_theta=1e6, qk_norm=True, num_experts=8,
+        num_experts_per_tok=2, moe_intermediate_size=64, dtype="float32"),
+    "tiny-deepseek": lambda: _preset(
+        name="tiny-deepseek", architecture="DeepseekV3ForCausalLM", vocab_size=512,
+        hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+        num_key_value_heads=4, head_dim=48, rope_theta=1e4, num_experts=8,
+        num_experts_per_tok=2, moe_intermediate_size=64, n_shared_experts=1,
+        scoring_func="sigmoid", n_group=4, topk_group=2, routed_scaling_factor=2.5,
+        first_k_dense_replace=1, e_score_correction_bias=True, use_mla=True, q_lora_rank=64,
+        kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+        dtype="float32"),
+}
+
+
+def get_model_config(name_or_path: str, **over) -> ModelConfig:
+    if name_or_path in PRESETS:
+        cfg = PRESETS[name_or_path]()
+        for k, v in over.items():
+            setattr(cfg, k, v)
+        return cfg
+    if os.path.isdir(name_or_path):
+        return ModelConfig.from_pretrained(name_or_path, **over)
+    raise ValueError(f"unknown model {name_or_path!r}: not a preset {sorted(PRESETS)} nor a directory")
+
+
+@dataclass
+class CacheConfig:
+    block_size: int = 128              # reference default (vllm_ascend/utils.py:1162-1212)
+    gpu_memory_utilization: float = 0.92
+    num_gpu_blocks: Optional[int] = None   # override; else profiled
+    enable_prefix_caching: bool = False
+    kv_cache_dtype: str = "auto"
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_seqs: int = 1024
+    max_num_batched_tokens: int = 8192
+    max_model_len: int = 4096
+    enable_chunked_prefill: bool = True
+    policy: str = "fcfs"               # fcfs | short_request_first | batch_job | recompute
+    async_scheduling: bool = False
+
+
+@dataclass
+class ParallelConfig:
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    decode_context_parallel_size: int = 1
+    enable_sequence_parallel: bool = False
+    rank: int = 0
+    local_rank: int = 0
+    world_size: int = 1
+    backend: str = "nccl"
+
+
+@dataclass
+class CompilationConfig:
+    """CUDA-graph settings (modes of vllm_ascend/platform.py:937-1008)."""
+    cudagraph_mode: str = "FULL_DECODE_ONLY"   # NONE|PIECEWISE|FULL|FULL_DECODE_ONLY|FULL_AND_PIECEWISE
+    cudagraph_capture_sizes: Optional[list] = None
+    max_cudagraph_capture_size: Optional[int] = None
+
+
+@dataclass
+class EngineConfig:
+    model: ModelConfig = field(default_factory=ModelConfig)
+    cache: CacheConfig = field(default_factory=CacheConfig)
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    compilation: CompilationConfig = field(default_factory=CompilationConfig)
+    additional_config: dict = field(default_factory=dict)
+    device: str = "cuda"
+    seed: int = 0
+    kv_transfer_config: Optional[dict] = None
+    speculative_config: Optional[dict] = None
+    enable_sleep_mode: bool = False
+    enable_lora: bool = False

@@ -1,0 +1,217 @@
+"""Public offline entry point: ``LLM(...).generate(prompts, sampling_params)``.
+
+The class keeps the upstream vLLM ``LLM`` call shape (the reference exposes no
+entry point of its own; its users call ``vllm.LLM`` / ``vllm serve``).  One
+process drives one GPU; under ``torchrun`` every rank constructs the same ``LLM``
+and calls ``generate`` with the same prompts (SPMD), the ranks meeting in the
+model's collectives.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from .. import _native, envs
+from ..config import (CacheConfig, CompilationConfig, EngineConfig, ModelConfig, ParallelConfig,
+                      SchedulerConfig, get_model_config)
+from ..parallel import state as pstate
+from .model_runner import ModelRunner
+from .request import (CompletionOutput, Request, RequestMetrics, RequestOutput, RequestStatus,
+                      SamplingParams)
+from .scheduler import Scheduler
+
+_FINISH_REASON = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
+                  RequestStatus.FINISHED_ABORTED: "abort"}
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig):
+        self.cfg = cfg
+        rank, local, world = pstate.init_distributed(
+            backend=None if cfg.device == "cuda" else "gloo")
+        pc = cfg.parallel
+        pc.rank, pc.local_rank, pc.world_size = rank, local, world
+        if cfg.device == "cuda":
+            if not torch.cuda.is_available():
+                raise RuntimeError("device='cuda' requested but no GPU is visible")
+            self.device = torch.device("cuda", local)
+            torch.cuda.set_device(self.device)
+            _native.load(required=True)
+        else:
+            self.device = torch.device("cpu")
+        if world > 1:
+            dp = max(1, world // (pc.tensor_parallel_size * pc.pipeline_parallel_size))
+            pc.data_parallel_size = dp
+            from ..platform_config import finegrained_sizes
+            pstate.initialize_model_parallel(pc.tensor_parallel_size, pc.pipeline_parallel_size, dp,
+                                             pc.decode_context_parallel_size,
+                                             finegrained=finegrained_sizes(cfg.additional_config))
+        else:
+            pstate.initialize_model_parallel()
+        self.runner = ModelRunner(cfg, self.device)
+        moe_runtime = None
+        if cfg.model.is_moe and pc.enable_expert_parallel and world > 1:
+            from ..ops.moe_comm import MoERuntime
+            moe_runtime = MoERuntime(cfg, self.device)
+        self.runner.load_model(moe_runtime=moe_runtime)
+        if world > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM == "fused" \
+                and pc.tensor_parallel_size > 1:
+            from ..parallel import fused_linear
+            fused_linear.attach(self.runner.model, cfg, self.device)
+        self.runner.warmup()
+        num_blocks = self.runner.determine_num_blocks()
+        if world > 1:   # every rank must agree
+            num_blocks = min(pstate.get_world_group().all_gather_object(num_blocks))
+        self.runner.init_kv_cache(num_blocks)
+        self.kv_connector = None
+        if cfg.kv_transfer_config:
+            from ..distributed.kv_transfer import create_connector
+            self.kv_connector = create_connector(cfg, self.runner)
+        self.scheduler = self._make_scheduler(num_blocks)
+        self.runner.capture_graphs()
+        self._req_counter = itertools.count()
+        self.eos_token_id: Optional[int] = None
+        self.step_times: list[float] = []
+
+    def _make_scheduler(self, num_blocks: int) -> Scheduler:
+        from ..core import make_scheduler
+        return make_scheduler(self.cfg, num_blocks, self.kv_connector)
+
+    # ------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int], sampling_params: SamplingParams,
+                    request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None,
+                    job_id: Optional[str] = None) -> str:
+        rid = request_id or f"req-{next(self._req_counter)}"
+        req = Request(rid, np.asarray(prompt_token_ids, dtype=np.int32), sampling_params,
+                      eos_token_id=self.eos_token_id, kv_transfer_params=kv_transfer_params,
+                      job_id=job_id)
+        self.scheduler.add_request(req)
+        return rid
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def step(self) -> list[Request]:
+        so = self.scheduler.schedule()
+        if self.kv_connector is not None:
+            self.kv_connector.start_load_kv(so)
+        sampled = self.runner.execute(so)
+        now = time.monotonic()
+        for req, _ in so.scheduled:
+            if req.first_token_time is None and req.request_id in sampled:
+                req.first_token_time = now
+        finished = self.scheduler.update_from_output(so, sampled)
+        if self.kv_connector is not None:
+            self.kv_connector.step_finished(so, self.scheduler)
+        return finished
+
+    def check_health(self) -> None:
+        if self.device.type == "cuda":
+            _native.check_status(self.device)
+
+
+class LLM:
+    """vLLM-style offline interface.
+
+    ``model`` is a preset name (random-init weights of that architecture), an HF
+    checkpoint directory, or a ``ModelConfig``.
+    """
+
+    def __init__(self, model: Union[str, ModelConfig], tensor_parallel_size: int = 1,
+                 pipeline_parallel_size: int = 1, enable_expert_parallel: bool = False,
+                 dtype: Optional[str] = None, device: Optional[str] = None,
+                 max_model_len: int = 4096, max_num_seqs: int = 1024,
+                 max_num_batched_tokens: int = 8192, block_size: Optional[int] = None,
+                 gpu_memory_utilization: float = 0.92, num_gpu_blocks_override: Optional[int] = None,
+                 enable_prefix_caching: bool = False, enforce_eager: bool = False,
+                 enable_chunked_prefill: bool = True, quantization: Optional[str] = None,
+                 seed: int = 0, additional_config: Optional[dict] = None,
+                 kv_transfer_config: Optional[dict] = None,
+                 speculative_config: Optional[dict] = None, enable_sleep_mode: bool = False,
+                 cudagraph_capture_sizes: Optional[list] = None,
+                 decode_context_parallel_size: int = 1, **unused):
+        mcfg = model if isinstance(model, ModelConfig) else get_model_config(model)
+        if dtype:
+            mcfg.dtype = dtype
+        if quantization:
+            mcfg.quantization = quantization
+        mcfg.seed = seed
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        if block_size is None:
+            block_size = 128 if device == "cuda" else 16
+        cfg = EngineConfig(
+            model=mcfg,
+            cache=CacheConfig(block_size=block_size, gpu_memory_utilization=gpu_memory_utilization,
+                              num_gpu_blocks=num_gpu_blocks_override,
+                              enable_prefix_caching=enable_prefix_caching),
+            scheduler=SchedulerConfig(max_num_seqs=max_num_seqs,
+                                      max_num_batched_tokens=max(max_num_batched_tokens, 1),
+                                      max_model_len=max_model_len,
+                                      enable_chunked_prefill=enable_chunked_prefill),
+            parallel=ParallelConfig(tensor_parallel_size=tensor_parallel_size,
+                                    pipeline_parallel_size=pipeline_parallel_size,
+                                    enable_expert_parallel=enable_expert_parallel,
+                                    decode_context_parallel_size=decode_context_parallel_size),
+            compilation=CompilationConfig(
+                cudagraph_mode="NONE" if enforce_eager else "FULL_DECODE_ONLY",
+                cudagraph_capture_sizes=cudagraph_capture_sizes),
+            additional_config=additional_config or {}, device=device, seed=seed,
+            kv_transfer_config=kv_transfer_config, speculative_config=speculative_config,
+            enable_sleep_mode=enable_sleep_mode)
+        from ..platform_config import check_and_update_config
+        check_and_update_config(cfg)
+        self.cfg = cfg
+        self.engine = LLMEngine(cfg)
+
+    # ------------------------------------------------------------------
+    def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 use_tqdm: bool = False) -> list[RequestOutput]:
+        """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``)."""
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        eng = self.engine
+        order: list[str] = []
+        reqs: dict[str, Request] = {}
+        for i, p in enumerate(prompts):
+            ids = p["prompt_token_ids"] if isinstance(p, dict) else p
+            sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
+            ktp = p.get("kv_transfer_params") if isinstance(p, dict) else None
+            rid = eng.add_request(ids, sp, kv_transfer_params=ktp)
+            order.append(rid)
+            reqs[rid] = eng.scheduler.requests[rid]
+        while eng.has_unfinished():
+            eng.step()
+        eng.check_health()
+        outs = []
+        for rid in order:
+            r = reqs[rid]
+            outs.append(RequestOutput(
+                request_id=rid, prompt_token_ids=r.prompt_token_ids.tolist(),
+                outputs=[CompletionOutput(0, list(r.output_token_ids or []),
+                                          finish_reason=_FINISH_REASON.get(r.status))],
+                finished=True,
+                metrics=RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time),
+                kv_transfer_params=r.kv_transfer_params, num_cached_tokens=r.num_cached_tokens))
+            eng.scheduler.requests.pop(rid, None)
+        return outs
+
+    # -- RL / lifecycle passthroughs (implemented by the worker-level mixins) ------
+    def sleep(self, level: int = 1) -> None:
+        from ..device_allocator.sleep import sleep as _sleep
+        _sleep(self.engine, level)
+
+    def wake_up(self, tags: Optional[list[str]] = None) -> None:
+        from ..device_allocator.sleep import wake_up as _wake
+        _wake(self.engine, tags)
+
+    def reset_prefix_cache(self) -> bool:
+        return self.engine.scheduler.pool.reset_prefix_cache()
+
+    def get_metrics(self) -> dict:
+        from ..observability.metrics import collect
+        return collect(self.engine)

@@ -1,0 +1,409 @@
+"""Model runner: persistent input batch, input preparation, forward (eager or
+CUDA-graph replay), logits and sampling.
+
+Responsibilities mirror ``NPUModelRunner`` (vllm_ascend/worker/model_runner_v1.py):
+``_prepare_inputs`` (:850-1285), attention metadata (:2813-3122), batch padding and
+graph dispatch (:2714-2811), KV-cache allocation as separate K and V tensors per
+layer (:3863-4069), ``capture_model`` (:4852-4862).  Device-side metadata lives in
+persistent buffers so graph replay needs no host-side argument refresh.
+"""
+from __future__ import annotations
+
+import math
+import time
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import _native, envs, ops
+from ..attention.metadata import (AttentionMetadata, AttentionState, build_tile_worklist,
+                                  split_decodes_and_prefills)
+from ..config import EngineConfig
+from ..parallel import state as pstate
+from ..sample.sampler import Sampler, SamplingMetadata
+from .request import Request
+from .scheduler import SchedulerOutput
+
+
+def default_capture_sizes(max_size: int) -> list[int]:
+    """1, 2, 4, 8, then multiples of 8 up to 64, of 16 up to 256, of 32 beyond."""
+    sizes = [1, 2, 4]
+    s = 8
+    while s <= max_size:
+        sizes.append(s)
+        s += 8 if s < 64 else (16 if s < 256 else 32)
+    if sizes[-1] != max_size and max_size > sizes[-1]:
+        sizes.append(max_size)
+    return [x for x in sizes if x <= max_size]
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig, device: torch.device):
+        self.cfg = cfg
+        self.device = device
+        self.mcfg = cfg.model
+        self.block_size = cfg.cache.block_size
+        self.max_seqs = cfg.scheduler.max_num_seqs
+        self.max_tokens = cfg.scheduler.max_num_batched_tokens
+        self.max_model_len = cfg.scheduler.max_model_len
+        self.max_blocks_per_seq = (self.max_model_len + self.block_size - 1) // self.block_size
+        self.model = None
+        self.kv_caches: list = []
+        self.num_blocks = 0
+        self.sampler = Sampler()
+        self.is_cuda = device.type == "cuda"
+        # ---- persistent host state (one row per live request)
+        self.token_ids_cpu = np.zeros((self.max_seqs, self.max_model_len), dtype=np.int32)
+        self.block_table_cpu = np.zeros((self.max_seqs, self.max_blocks_per_seq), dtype=np.int32)
+        self.row_owner: list[Optional[str]] = [None] * self.max_seqs
+        self.row_num_blocks = np.zeros(self.max_seqs, dtype=np.int32)
+        self.row_num_tokens = np.zeros(self.max_seqs, dtype=np.int32)
+        # ---- persistent device inputs
+        T, B = self.max_tokens, self.max_seqs
+        i64, i32 = torch.int64, torch.int32
+        self.input_ids = torch.zeros(T, dtype=i64, device=device)
+        self.positions = torch.zeros(T, dtype=i64, device=device)
+        self.slot_mapping = torch.full((T,), -1, dtype=i64, device=device)
+        self.query_start_loc = torch.zeros(B + 1, dtype=i32, device=device)
+        self.seq_lens = torch.ones(B, dtype=i32, device=device)
+        self.block_table = torch.zeros((B, self.max_blocks_per_seq), dtype=i32, device=device)
+        max_tiles = T + B
+        self.tile_seq = torch.zeros(max_tiles, dtype=i32, device=device)
+        self.tile_qoff = torch.zeros(max_tiles, dtype=i32, device=device)
+        pin = self.is_cuda
+        self._h_ids = torch.zeros(T, dtype=i64, pin_memory=pin)
+        self._h_pos = torch.zeros(T, dtype=i64, pin_memory=pin)
+        self._h_slot = torch.zeros(T, dtype=i64, pin_memory=pin)
+        self._h_qsl = torch.zeros(B + 1, dtype=i32, pin_memory=pin)
+        self._h_sl = torch.zeros(B, dtype=i32, pin_memory=pin)
+        self._h_bt = torch.zeros((B, self.max_blocks_per_seq), dtype=i32, pin_memory=pin)
+        self._h_tile = torch.zeros((2, max_tiles), dtype=i32, pin_memory=pin)
+        self._h_sampled = torch.zeros(B, dtype=i64, pin_memory=pin)
+        # ---- CUDA graphs
+        self.graphs: dict[int, tuple] = {}
+        self.graph_pool = None
+        self.capture_sizes: list[int] = []
+        self.stats = {"graph_replays": 0, "eager_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0,
+                      "steps": 0}
+        self.sm_count = (torch.cuda.get_device_properties(device).multi_processor_count
+                         if self.is_cuda else 1)
+
+    # ------------------------------------------------------------------ model / memory
+    def load_model(self, moe_runtime=None) -> None:
+        from ..models import build_model
+        t0 = time.time()
+        self.model = build_model(self.cfg, self.device, moe_runtime=moe_runtime)
+        if self.mcfg.model_path:
+            from ..models.transformer import iterate_safetensors
+            self.model.load_weights(iterate_safetensors(self.mcfg.model_path))
+        self.load_time = time.time() - t0
+
+    def kv_bytes_per_block(self) -> int:
+        m = self.model
+        n_layers = len(m.layers)
+        itemsize = torch.tensor([], dtype=self.kv_dtype).element_size()
+        per_tok = sum(self._cache_widths()) * itemsize
+        return n_layers * self.block_size * per_tok
+
+    @property
+    def kv_dtype(self) -> torch.dtype:
+        return self.mcfg.torch_dtype
+
+    def _cache_widths(self) -> tuple[int, int]:
+        c = self.mcfg
+        if c.use_mla:
+            return (c.kv_lora_rank, c.qk_rope_head_dim)
+        a = self.model.layers[0].self_attn
+        return (a.Hkv * a.D, a.Hkv * a.D)
+
+    def activation_bytes_estimate(self) -> int:
+        c = self.mcfg
+        tp = self.cfg.parallel.tensor_parallel_size
+        T = self.max_tokens
+        inter = max(c.intermediate_size, c.moe_intermediate_size * max(1, c.num_experts_per_tok))
+        per_tok = (6 * c.hidden_size + 3 * (c.num_attention_heads * c.q_head_dim) // tp
+                   + 3 * inter // tp) * 2
+        logits = self.max_seqs * c.vocab_size * 6
+        return int(1.3 * (T * per_tok + logits)) + (1 << 30)
+
+    def determine_num_blocks(self) -> int:
+        cc = self.cfg.cache
+        if cc.num_gpu_blocks:
+            return cc.num_gpu_blocks
+        if not self.is_cuda:
+            return max(64, 4 * self.max_seqs)
+        torch.cuda.synchronize()
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = total * cc.gpu_memory_utilization - (total - free) - self.activation_bytes_estimate()
+        n = int(budget // self.kv_bytes_per_block())
+        if n < 8:
+            raise RuntimeError(f"not enough memory for the KV cache ({budget / 2**30:.1f} GiB left)")
+        # a block beyond what max_num_seqs full-length sequences can use is wasted
+        return min(n, self.max_seqs * self.max_blocks_per_seq + 1)
+
+    def init_kv_cache(self, num_blocks: int) -> None:
+        """Per layer two tensors (K, V) or (latent, rope), zero-filled so masked key
+        positions never hold NaN bit patterns."""
+        self.num_blocks = num_blocks
+        c = self.mcfg
+        self.kv_caches = []
+        for layer in self.model.layers:
+            if c.use_mla:
+                shapes = [(num_blocks, self.block_size, 1, c.kv_lora_rank),
+                          (num_blocks, self.block_size, 1, c.qk_rope_head_dim)]
+            else:
+                a = layer.self_attn
+                shapes = [(num_blocks, self.block_size, a.Hkv, a.D)] * 2
+            self.kv_caches.append(tuple(torch.zeros(s, dtype=self.kv_dtype, device=self.device)
+                                        for s in shapes))
+
+    # ------------------------------------------------------------------ persistent batch
+    def _sync_rows(self, so: SchedulerOutput) -> None:
+        for req in so.new_block_rows:
+            row = req.row
+            if row < 0:
+                continue
+            if self.row_owner[row] != req.request_id:
+                self.row_owner[row] = req.request_id
+                self.row_num_blocks[row] = 0
+                n = req.num_prompt_tokens
+                self.token_ids_cpu[row, :n] = req.prompt_token_ids
+                if req.output_token_ids:
+                    k = len(req.output_token_ids)
+                    self.token_ids_cpu[row, n:n + k] = req.output_token_ids
+                self.row_num_tokens[row] = req.num_tokens
+            have = self.row_num_blocks[row]
+            nb = len(req.block_ids)
+            if nb > have:
+                self.block_table_cpu[row, have:nb] = req.block_ids[have:nb]
+                self.row_num_blocks[row] = nb
+            elif nb < have:          # preempted and re-admitted with fewer blocks
+                self.block_table_cpu[row, :nb] = req.block_ids
+                self.row_num_blocks[row] = nb
+
+    def _prepare_inputs(self, so: SchedulerOutput, pad_to: Optional[int] = None):
+        reqs = [r for r, _ in so.scheduled]
+        B = len(reqs)
+        q_lens = np.fromiter((n for _, n in so.scheduled), dtype=np.int32, count=B)
+        rows = np.fromiter((r.row for r in reqs), dtype=np.int64, count=B)
+        starts = np.fromiter((r.num_computed_tokens for r in reqs), dtype=np.int32, count=B)
+        T = int(q_lens.sum())
+        cu = np.zeros(B + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=cu[1:])
+        req_idx = np.repeat(np.arange(B, dtype=np.int64), q_lens)
+        pos = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1].astype(np.int64), q_lens) \
+            + np.repeat(starts.astype(np.int64), q_lens)
+        tok_rows = rows[req_idx]
+        ids = self.token_ids_cpu[tok_rows, pos]
+        blk = self.block_table_cpu[tok_rows, pos // self.block_size].astype(np.int64)
+        slots = blk * self.block_size + pos % self.block_size
+        seq_lens = starts + q_lens
+        Bp = pad_to or B
+        Tp = T + (Bp - B)                       # padded rows carry one dummy token each
+        h = self
+        h._h_ids[:T] = torch.from_numpy(ids.astype(np.int64))
+        h._h_pos[:T] = torch.from_numpy(pos)
+        h._h_slot[:T] = torch.from_numpy(slots)
+        h._h_qsl[:B + 1] = torch.from_numpy(cu)
+        h._h_sl[:B] = torch.from_numpy(seq_lens)
+        h._h_bt[:B] = torch.from_numpy(self.block_table_cpu[rows])
+        if Bp > B:
+            h._h_ids[T:Tp] = 0
+            h._h_pos[T:Tp] = 0
+            h._h_slot[T:Tp] = -1
+            h._h_qsl[B + 1:Bp + 1] = torch.arange(T + 1, Tp + 1, dtype=torch.int32)
+            h._h_sl[B:Bp] = 1
+            h._h_bt[B:Bp] = 0
+        nb = True
+        self.input_ids[:Tp].copy_(h._h_ids[:Tp], non_blocking=nb)
+        self.positions[:Tp].copy_(h._h_pos[:Tp], non_blocking=nb)
+        self.slot_mapping[:Tp].copy_(h._h_slot[:Tp], non_blocking=nb)
+        self.query_start_loc[:Bp + 1].copy_(h._h_qsl[:Bp + 1], non_blocking=nb)
+        self.seq_lens[:Bp].copy_(h._h_sl[:Bp], non_blocking=nb)
+        self.block_table[:Bp].copy_(h._h_bt[:Bp], non_blocking=nb)
+        self.stats["h2d_bytes"] += Tp * 24 + (Bp + 1) * 4 + Bp * 4 + Bp * self.max_blocks_per_seq * 4
+
+        max_q = int(q_lens.max()) if B else 0
+        max_s = int(seq_lens.max()) if B else 0
+        nd, npf, ndt, _ = split_decodes_and_prefills(q_lens)
+        if max_q == 1:
+            state = AttentionState.DecodeOnly
+        elif (starts == 0).all():
+            state = AttentionState.PrefillNoCache
+        else:
+            state = AttentionState.ChunkedPrefill
+        qsl_cpu = cu if Bp == B else np.concatenate([cu, np.arange(T + 1, Tp + 1, dtype=np.int32)])
+        sl_cpu = seq_lens if Bp == B else np.concatenate([seq_lens, np.ones(Bp - B, dtype=np.int32)])
+        meta = AttentionMetadata(
+            num_reqs=Bp, num_actual_tokens=T, max_query_len=max_q, max_seq_len=max_s,
+            query_start_loc=self.query_start_loc[:Bp + 1], seq_lens=self.seq_lens[:Bp],
+            block_table=self.block_table[:Bp], slot_mapping=self.slot_mapping[:Tp],
+            positions=self.positions[:Tp], query_start_loc_cpu=qsl_cpu, seq_lens_cpu=sl_cpu,
+            attn_state=state, num_decodes=nd, num_decode_tokens=ndt, num_prefills=npf,
+            num_input_tokens=Tp)
+        if self.is_cuda and not self.mcfg.use_mla:
+            a = self.model.layers[0].self_attn
+            G = a.Hq // a.Hkv
+            tok_per_tile = max(1, 128 // G)
+            if max_q > 1:
+                ts, tq = build_tile_worklist(q_lens, tok_per_tile, seq_lens)
+                nt = len(ts)
+                h._h_tile[0, :nt] = torch.from_numpy(ts)
+                h._h_tile[1, :nt] = torch.from_numpy(tq)
+                self.tile_seq[:nt].copy_(h._h_tile[0, :nt], non_blocking=True)
+                self.tile_qoff[:nt].copy_(h._h_tile[1, :nt], non_blocking=True)
+                meta.tile_seq, meta.tile_qoff, meta.num_tiles = self.tile_seq[:nt], self.tile_qoff[:nt], nt
+                self.stats["h2d_bytes"] += nt * 8
+            else:
+                meta.num_splits = self._decode_splits(Bp, a.Hkv)
+        logits_idx = None
+        sample_reqs = []
+        sel = []
+        for i, r in enumerate(reqs):
+            if starts[i] + q_lens[i] >= r.num_tokens:
+                sel.append(int(cu[i + 1]) - 1)
+                sample_reqs.append(r)
+        return meta, T, Tp, sel, sample_reqs
+
+    def _decode_splits(self, batch: int, Hkv: int) -> int:
+        """Split factor depends only on the (padded) batch size so that it is a
+        compile-time constant of the captured graph."""
+        return ops.choose_num_splits(batch, Hkv, self.max_model_len, self.sm_count)
+
+    # ------------------------------------------------------------------ execution
+    def _forward(self, T: int, meta: AttentionMetadata) -> torch.Tensor:
+        return self.model.forward(self.input_ids[:T], meta, self.kv_caches)
+
+    def _graph_size_for(self, B: int) -> Optional[int]:
+        if not self.capture_sizes or B > self.capture_sizes[-1]:
+            return None
+        for s in self.capture_sizes:
+            if s >= B:
+                return s
+        return None
+
+    @torch.inference_mode()
+    def execute(self, so: SchedulerOutput) -> dict:
+        """Runs one step; returns {request_id: [sampled token ids]}."""
+        if so.is_empty:
+            return {}
+        self.stats["steps"] += 1
+        self._sync_rows(so)
+        B = len(so.scheduled)
+        decode_only = all(n == 1 for _, n in so.scheduled)
+        gsize = self._graph_size_for(B) if decode_only else None
+        meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
+        if gsize is not None:
+            graph, hidden_out = self.graphs[gsize]
+            graph.replay()
+            self.stats["graph_replays"] += 1
+            logits = self.model.compute_logits(hidden_out[:B])
+        else:
+            hidden = self._forward(Tp, meta)
+            self.stats["eager_steps"] += 1
+            if not sel:
+                return {}
+            if len(sel) == T:
+                h_sel = hidden[:T]
+            else:
+                h_sel = hidden[torch.tensor(sel, dtype=torch.int64, device=self.device)]
+            logits = self.model.compute_logits(h_sel)
+        md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
+        if not md.all_greedy and not self.is_cuda:
+            md.generator = self._cpu_generator()
+        tokens = self.sampler(logits, md)
+        n = tokens.shape[0]
+        if self.is_cuda:
+            self._h_sampled[:n].copy_(tokens, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            toks = self._h_sampled[:n].numpy()
+        else:
+            toks = tokens.numpy()
+        self.stats["d2h_bytes"] += n * 8
+        out = {}
+        for r, t in zip(sample_reqs, toks):
+            t = int(t)
+            row = r.row
+            self.token_ids_cpu[row, r.num_tokens] = t
+            out[r.request_id] = [t]
+        return out
+
+    def _cpu_generator(self) -> torch.Generator:
+        g = getattr(self, "_gen", None)
+        if g is None:
+            g = torch.Generator()
+            g.manual_seed(self.cfg.seed)
+            self._gen = g
+        return g
+
+    # ------------------------------------------------------------------ warm-up / capture
+    def _dummy_meta(self, B: int, q_len: int, pad_to: Optional[int] = None):
+        """Synthetic batch of B sequences of q_len tokens over block 0."""
+        class _R:  # minimal request stand-in
+            pass
+        sched = []
+        for i in range(B):
+            r = _R()
+            r.row, r.num_computed_tokens, r.num_tokens = i, 0, q_len + 1
+            r.request_id = f"_dummy{i}"
+            sched.append((r, q_len))
+        so = SchedulerOutput(scheduled=sched)
+        saved = self.block_table_cpu[:B].copy()
+        self.block_table_cpu[:B] = 0
+        try:
+            return self._prepare_inputs(so, pad_to=pad_to)
+        finally:
+            self.block_table_cpu[:B] = saved
+
+    @torch.inference_mode()
+    def warmup(self) -> None:
+        """One prefill-shaped and one decode-shaped eager pass (kernel attribute setup,
+        allocator warm-up) before any capture."""
+        B = min(self.max_seqs, 8)
+        q = max(1, min(self.max_tokens // B, self.max_model_len - 1, 256))
+        meta, T, Tp, _, _ = self._dummy_meta(B, q)
+        meta.slot_mapping.fill_(-1)
+        h = self._forward(Tp, meta)
+        self.model.compute_logits(h[:B])
+        meta, T, Tp, _, _ = self._dummy_meta(B, 1)
+        meta.slot_mapping.fill_(-1)
+        self._forward(Tp, meta)
+        if self.is_cuda:
+            torch.cuda.synchronize()
+
+    @torch.inference_mode()
+    def capture_graphs(self) -> None:
+        cc = self.cfg.compilation
+        if not self.is_cuda or cc.cudagraph_mode == "NONE" or not envs.VLLM_B200_CUDA_GRAPH:
+            return
+        max_size = cc.max_cudagraph_capture_size or min(self.max_seqs, 1024)
+        sizes = cc.cudagraph_capture_sizes or default_capture_sizes(max_size)
+        self.capture_sizes = sorted(set(int(s) for s in sizes if s <= self.max_seqs))
+        # scratch for split-KV partials must exist before capture
+        if not self.mcfg.use_mla:
+            a = self.model.layers[0].self_attn
+            worst = 0
+            for s in self.capture_sizes:
+                ns = self._decode_splits(s, a.Hkv)
+                if ns > 1:
+                    worst = max(worst, s * a.Hq * ns * (a.D + 1) * 4)
+            if worst:
+                ops.reserve_attention_scratch(self.device, worst)
+        self.graph_pool = torch.cuda.graph_pool_handle()
+        for size in sorted(self.capture_sizes, reverse=True):
+            meta, T, Tp, _, _ = self._dummy_meta(size, 1)
+            meta.slot_mapping.fill_(-1)
+            # warm-up run on the side stream, then capture
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                h = self._forward(Tp, meta)
+                self.model.compute_logits(h)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self.graph_pool):
+                hidden = self._forward(Tp, meta)
+            self.graphs[size] = (g, hidden)
+        torch.cuda.synchronize()

@@ -1,0 +1,133 @@
+"""Request-level data types of the public API (vLLM-compatible names)."""
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import numpy as np
+
+
+@dataclass
+class SamplingParams:
+    n: int = 1
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = 0                       # 0 / -1: disabled
+    min_p: float = 0.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    max_tokens: int = 16
+    min_tokens: int = 0
+    stop_token_ids: Optional[list[int]] = None
+    ignore_eos: bool = False
+    seed: Optional[int] = None
+    logprobs: Optional[int] = None
+    extra_args: Optional[dict] = None
+
+    def __post_init__(self):
+        if self.top_k is None or self.top_k < 0:
+            self.top_k = 0
+        if self.temperature < 0:
+            raise ValueError("temperature must be non-negative")
+        if not (0.0 < self.top_p <= 1.0):
+            raise ValueError("top_p must be in (0, 1]")
+        if self.max_tokens is not None and self.max_tokens < 1:
+            raise ValueError("max_tokens must be at least 1")
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature < 1e-5
+
+    @property
+    def has_penalties(self) -> bool:
+        return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+                or self.repetition_penalty != 1.0)
+
+
+class RequestStatus(enum.IntEnum):
+    WAITING = 0
+    WAITING_FOR_REMOTE_KVS = 1
+    RUNNING = 2
+    PREEMPTED = 3
+    FINISHED_STOPPED = 4
+    FINISHED_LENGTH = 5
+    FINISHED_ABORTED = 6
+
+    @property
+    def finished(self) -> bool:
+        return self >= RequestStatus.FINISHED_STOPPED
+
+
+@dataclass
+class Request:
+    request_id: str
+    prompt_token_ids: np.ndarray
+    sampling_params: SamplingParams
+    eos_token_id: Optional[int] = None
+    arrival_time: float = field(default_factory=time.monotonic)
+    priority: int = 0
+    kv_transfer_params: Optional[dict] = None
+    lora_request: Optional[Any] = None
+    # ---- engine state ----
+    status: RequestStatus = RequestStatus.WAITING
+    row: int = -1                         # persistent batch row
+    num_computed_tokens: int = 0
+    num_output_tokens: int = 0
+    block_ids: list = field(default_factory=list)
+    num_cached_tokens: int = 0            # prefix-cache hit length
+    num_preemptions: int = 0
+    output_token_ids: Optional[list[int]] = None
+    first_token_time: Optional[float] = None
+    finish_time: Optional[float] = None
+    spec_token_ids: list = field(default_factory=list)
+    job_id: Optional[str] = None
+
+    @property
+    def num_prompt_tokens(self) -> int:
+        return len(self.prompt_token_ids)
+
+    @property
+    def num_tokens(self) -> int:
+        return self.num_prompt_tokens + self.num_output_tokens
+
+    @property
+    def is_finished(self) -> bool:
+        return self.status.finished
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    token_ids: list[int]
+    text: str = ""
+    finish_reason: Optional[str] = None
+    logprobs: Optional[list] = None
+
+
+@dataclass
+class RequestMetrics:
+    arrival_time: float
+    first_token_time: Optional[float]
+    finish_time: Optional[float]
+
+    @property
+    def ttft(self) -> Optional[float]:
+        return None if self.first_token_time is None else self.first_token_time - self.arrival_time
+
+    @property
+    def tpot(self) -> Optional[float]:
+        return None
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: list[int]
+    outputs: list[CompletionOutput]
+    finished: bool
+    metrics: Optional[RequestMetrics] = None
+    kv_transfer_params: Optional[dict] = None
+    num_cached_tokens: int = 0

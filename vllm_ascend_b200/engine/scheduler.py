@@ -1,0 +1,299 @@
+"""Continuous-batching scheduler with chunked prefill, prefix caching and
+recompute preemption.
+
+Running requests are served first (one decode token, or the next prompt chunk),
+then waiting requests are admitted while the token budget and the KV pool allow.
+The waiting-queue order is a pluggable policy — the scheduler extensions of
+``vllm_ascend/core`` (short-request-first, batch-job-aware, recompute, balance)
+subclass this and override ``_pick_waiting`` / the admission hooks.
+KV-connector hooks follow the scheduler-side contract of
+vllm_ascend/distributed/kv_transfer/kv_p2p/mooncake_connector.py:1843-2001.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+
+from ..config import CacheConfig, SchedulerConfig
+from .block_pool import BlockPool
+from .request import Request, RequestStatus
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled: list                      # [(Request, num_new_tokens)], decodes first
+    num_scheduled_tokens: int = 0
+    preempted: list = field(default_factory=list)
+    finished_ids: list = field(default_factory=list)
+    new_block_rows: list = field(default_factory=list)   # requests whose block list grew
+    kv_connector_metadata: Optional[object] = None
+    step_id: int = 0
+
+    @property
+    def is_empty(self) -> bool:
+        return not self.scheduled
+
+
+class Scheduler:
+    def __init__(self, sched_cfg: SchedulerConfig, cache_cfg: CacheConfig, num_blocks: int,
+                 kv_connector=None):
+        self.cfg = sched_cfg
+        self.block_size = cache_cfg.block_size
+        self.pool = BlockPool(num_blocks, cache_cfg.block_size, cache_cfg.enable_prefix_caching)
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.requests: dict[str, Request] = {}
+        self.finished_since_last: list[str] = []
+        self.kv_connector = kv_connector
+        self.step_id = 0
+        self._free_rows = list(range(sched_cfg.max_num_seqs - 1, -1, -1))
+        self._hashes: dict[str, list[bytes]] = {}
+        # stats
+        self.num_preemptions = 0
+
+    # ------------------------------------------------------------------ API
+    def add_request(self, req: Request) -> None:
+        if req.num_prompt_tokens + 1 > self.cfg.max_model_len:
+            raise ValueError(f"prompt of {req.num_prompt_tokens} tokens exceeds max_model_len "
+                             f"{self.cfg.max_model_len}")
+        self.requests[req.request_id] = req
+        req.status = RequestStatus.WAITING
+        self.waiting.append(req)
+
+    def abort_request(self, request_id: str) -> None:
+        req = self.requests.get(request_id)
+        if req is None or req.is_finished:
+            return
+        if req in self.running:
+            self.running.remove(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)
+        self._finish(req, RequestStatus.FINISHED_ABORTED)
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    @property
+    def num_unfinished(self) -> int:
+        return len(self.waiting) + len(self.running)
+
+    # ------------------------------------------------------------------ policy hooks
+    def _pick_waiting(self) -> Optional[Request]:
+        """Next candidate from the waiting queue (FCFS)."""
+        return self.waiting[0] if self.waiting else None
+
+    def _pop_waiting(self, req: Request) -> None:
+        if self.waiting and self.waiting[0] is req:
+            self.waiting.popleft()
+        else:
+            self.waiting.remove(req)
+
+    def _can_admit(self, req: Request, num_new_blocks: int) -> bool:
+        return self.pool.can_allocate(num_new_blocks)
+
+    def _select_preemption_victim(self) -> Optional[Request]:
+        return self.running[-1] if self.running else None
+
+    # ------------------------------------------------------------------ core
+    def _blocks_needed(self, req: Request, num_tokens_after: int) -> int:
+        need = (num_tokens_after + self.block_size - 1) // self.block_size
+        return max(0, need - len(req.block_ids))
+
+    def _preempt(self, req: Request, out: SchedulerOutput) -> None:
+        self.running.remove(req)
+        self.pool.free(req.block_ids)
+        req.block_ids = []
+        req.num_computed_tokens = 0
+        req.status = RequestStatus.PREEMPTED
+        req.num_preemptions += 1
+        self.num_preemptions += 1
+        self._release_row(req)
+        self.waiting.appendleft(req)
+        out.preempted.append(req)
+
+    def _release_row(self, req: Request) -> None:
+        if req.row >= 0:
+            self._free_rows.append(req.row)
+            req.row = -1
+
+    def schedule(self) -> SchedulerOutput:
+        self.step_id += 1
+        out = SchedulerOutput(scheduled=[], step_id=self.step_id)
+        out.finished_ids, self.finished_since_last = self.finished_since_last, []
+        budget = self.cfg.max_num_batched_tokens
+        decodes: list = []
+        prefills: list = []
+
+        # ---- running requests
+        i = 0
+        while i < len(self.running) and budget > 0:
+            req = self.running[i]
+            remaining = req.num_tokens + len(req.spec_token_ids) - req.num_computed_tokens
+            n = min(remaining, budget)
+            if n <= 0:
+                i += 1
+                continue
+            if not self.cfg.enable_chunked_prefill and n < remaining:
+                i += 1
+                continue
+            need = self._blocks_needed(req, req.num_computed_tokens + n)
+            preempted_self = False
+            while need > self.pool.num_free_blocks:
+                victim = self._select_preemption_victim()
+                if victim is None:
+                    break
+                # victims scheduled earlier in this step must be dropped from the batch
+                decodes = [(r, k) for r, k in decodes if r is not victim]
+                prefills = [(r, k) for r, k in prefills if r is not victim]
+                vi = self.running.index(victim)
+                self._preempt(victim, out)
+                if victim is req:
+                    preempted_self = True
+                    break
+                if vi < i:
+                    i -= 1
+            if preempted_self:
+                continue
+            if need > self.pool.num_free_blocks:
+                break
+            if need:
+                req.block_ids.extend(self.pool.allocate(need))
+                out.new_block_rows.append(req)
+            (decodes if n == 1 and req.num_computed_tokens >= req.num_prompt_tokens
+             else prefills).append((req, n))
+            budget -= n
+            i += 1
+
+        # ---- admit waiting requests
+        while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs \
+                and not out.preempted:
+            req = self._pick_waiting()
+            if req is None:
+                break
+            if req.status == RequestStatus.WAITING_FOR_REMOTE_KVS:
+                if self.kv_connector is None or not self.kv_connector.is_ready(req):
+                    # rotate so it does not block the queue head
+                    self._pop_waiting(req)
+                    self.waiting.append(req)
+                    if all(r.status == RequestStatus.WAITING_FOR_REMOTE_KVS for r in self.waiting):
+                        break
+                    continue
+                req.status = RequestStatus.WAITING
+            # prefix cache
+            cached_blocks: list[int] = []
+            if self.pool.enable_prefix_caching and req.num_computed_tokens == 0 and not req.block_ids:
+                hashes = self._hashes.get(req.request_id)
+                if hashes is None:
+                    hashes = self.pool.block_hashes(req.prompt_token_ids)
+                    self._hashes[req.request_id] = hashes
+                # never treat the whole prompt as cached: the last token must be computed
+                max_hit = (req.num_prompt_tokens - 1) // self.block_size
+                cached_blocks = self.pool.find_cached_prefix(hashes[:max_hit])
+            num_cached = len(cached_blocks) * self.block_size
+            # external KV (disaggregated prefill): tokens the connector will load
+            num_external, load_async = 0, False
+            if self.kv_connector is not None and req.num_computed_tokens == 0:
+                num_external, load_async = self.kv_connector.get_num_new_matched_tokens(req, num_cached)
+            computed = max(req.num_computed_tokens, num_cached + num_external)
+            remaining = req.num_tokens - computed
+            n = min(remaining, budget) if not load_async else 0
+            if not self.cfg.enable_chunked_prefill and n < remaining and not load_async:
+                break
+            total_after = computed + n
+            need = (total_after + self.block_size - 1) // self.block_size - len(cached_blocks) \
+                - len(req.block_ids)
+            need = max(need, 0)
+            if not self._can_admit(req, need):
+                break
+            self._pop_waiting(req)
+            if cached_blocks:
+                self.pool.touch(cached_blocks)
+                req.block_ids = list(cached_blocks)
+                req.num_cached_tokens = num_cached
+            if need:
+                req.block_ids.extend(self.pool.allocate(need))
+            req.num_computed_tokens = computed
+            if req.row < 0:
+                req.row = self._free_rows.pop()
+            out.new_block_rows.append(req)
+            if self.kv_connector is not None:
+                self.kv_connector.update_state_after_alloc(req, req.block_ids, num_external)
+            if load_async:
+                req.status = RequestStatus.WAITING_FOR_REMOTE_KVS
+                self.waiting.append(req)
+                continue
+            req.status = RequestStatus.RUNNING
+            self.running.append(req)
+            if n > 0:
+                prefills.append((req, n))
+                budget -= n
+
+        out.scheduled = decodes + prefills
+        out.num_scheduled_tokens = sum(n for _, n in out.scheduled)
+        if self.kv_connector is not None:
+            out.kv_connector_metadata = self.kv_connector.build_connector_meta(out)
+        return out
+
+    # ------------------------------------------------------------------ results
+    def update_from_output(self, out: SchedulerOutput, sampled: dict) -> list[Request]:
+        """``sampled`` maps request_id -> list of new token ids (empty for a partial
+        prefill chunk).  Returns the requests that finished in this step."""
+        finished: list[Request] = []
+        for req, n in out.scheduled:
+            if req.status != RequestStatus.RUNNING:
+                continue
+            req.num_computed_tokens += n
+            if self.pool.enable_prefix_caching:
+                hashes = self._hashes.get(req.request_id)
+                if hashes:
+                    full = min(req.num_computed_tokens, req.num_prompt_tokens) // self.block_size
+                    self.pool.cache_full_blocks(req.block_ids, hashes, full)
+            toks = sampled.get(req.request_id)
+            if not toks:
+                continue
+            if req.output_token_ids is None:
+                req.output_token_ids = []
+            sp = req.sampling_params
+            for t in toks:
+                req.output_token_ids.append(int(t))
+                req.num_output_tokens += 1
+                stop = None
+                if req.num_output_tokens >= sp.max_tokens or req.num_tokens >= self.cfg.max_model_len:
+                    stop = RequestStatus.FINISHED_LENGTH
+                if req.num_output_tokens >= sp.min_tokens:
+                    if (not sp.ignore_eos and req.eos_token_id is not None and t == req.eos_token_id) \
+                            or (sp.stop_token_ids and t in sp.stop_token_ids):
+                        stop = RequestStatus.FINISHED_STOPPED
+                if stop is not None:
+                    self.running.remove(req)
+                    self._finish(req, stop)
+                    finished.append(req)
+                    break
+        return finished
+
+    def _finish(self, req: Request, status: RequestStatus) -> None:
+        import time
+        req.status = status
+        req.finish_time = time.monotonic()
+        delay_free = False
+        if self.kv_connector is not None:
+            delay_free, params = self.kv_connector.request_finished(req, req.block_ids)
+            if params is not None:
+                req.kv_transfer_params = params
+        if not delay_free:
+            self.free_blocks(req)
+        self._release_row(req)
+        self._hashes.pop(req.request_id, None)
+        self.finished_since_last.append(req.request_id)
+
+    def free_blocks(self, req: Request) -> None:
+        self.pool.free(req.block_ids)
+        req.block_ids = []
+
+    def finish_decode_fast(self, req: Request, status: RequestStatus) -> None:
+        """Used by the vectorised decode loop of the engine."""
+        self.running.remove(req)
+        self._finish(req, status)

@@ -1,0 +1,65 @@
+"""Lazily evaluated environment-variable table.
+
+Every variable is read at attribute access time (not import time) so tests can
+monkeypatch ``os.environ``.  Parity: vllm_ascend/envs.py:30-108 (same lazy
+``__getattr__`` contract, B200-relevant names).
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Callable
+
+
+def _bool(name: str, default: str = "0") -> Callable[[], bool]:
+    return lambda: os.getenv(name, default).strip().lower() in ("1", "true", "yes", "on")
+
+
+def _int(name: str, default: int) -> Callable[[], int]:
+    return lambda: int(os.getenv(name, str(default)))
+
+
+def _str(name: str, default: str | None = None) -> Callable[[], str | None]:
+    return lambda: os.getenv(name, default)
+
+
+env_variables: dict[str, Callable[[], Any]] = {
+    # ---- build ----
+    "MAX_JOBS": _int("MAX_JOBS", 8),
+    "CMAKE_BUILD_TYPE": _str("CMAKE_BUILD_TYPE", "Release"),
+    "COMPILE_CUSTOM_KERNELS": _bool("COMPILE_CUSTOM_KERNELS", "1"),
+    # ---- kernel selection (one native path per op; these only exist to fall
+    # back to the library path while a kernel is being validated) ----
+    # bf16 GEMM: "tcgen05" (hand-written) or "cublas" (plain library GEMM)
+    "VLLM_B200_GEMM": _str("VLLM_B200_GEMM", "tcgen05"),
+    # prefill attention: "tcgen05" or "sdpa" (torch fallback/oracle)
+    "VLLM_B200_PREFILL_ATTN": _str("VLLM_B200_PREFILL_ATTN", "tcgen05"),
+    "VLLM_B200_DECODE_ATTN": _str("VLLM_B200_DECODE_ATTN", "native"),
+    # fused TP collectives over peer memory: "fused" or "nccl"
+    "VLLM_B200_TP_COMM": _str("VLLM_B200_TP_COMM", "fused"),
+    # MoE path override: "", "allgather", "alltoall", "fused"
+    "VLLM_B200_MOE_COMM": _str("VLLM_B200_MOE_COMM", ""),
+    "VLLM_B200_ENABLE_NVLS": _bool("VLLM_B200_ENABLE_NVLS", "0"),
+    "VLLM_B200_DEBUG_BOUNDS": _bool("VLLM_B200_DEBUG_BOUNDS", "0"),
+    # device-side bounded wait, in microseconds of globaltimer
+    "VLLM_B200_WAIT_TIMEOUT_US": _int("VLLM_B200_WAIT_TIMEOUT_US", 1_000_000),
+    # ---- runtime features (names follow the reference where they make sense) ----
+    "DYNAMIC_EPLB": _bool("DYNAMIC_EPLB", "0"),
+    "VLLM_B200_ENABLE_FUSED_MOE_COMM": _bool("VLLM_B200_ENABLE_FUSED_MOE_COMM", "1"),
+    "VLLM_B200_BALANCE_SCHEDULING": _bool("VLLM_B200_BALANCE_SCHEDULING", "0"),
+    "VLLM_B200_ENABLE_BATCH_MEMCPY": _bool("VLLM_B200_ENABLE_BATCH_MEMCPY", "1"),
+    "VLLM_B200_TRANSPOSE_KV_CACHE_BY_BLOCK": _bool("VLLM_B200_TRANSPOSE_KV_CACHE_BY_BLOCK", "1"),
+    "VLLM_B200_KV_ABORT_REQUEST_TIMEOUT": _int("VLLM_B200_KV_ABORT_REQUEST_TIMEOUT", 480),
+    "VLLM_B200_LOG_PATH": _str("VLLM_B200_LOG_PATH", None),
+    "VLLM_B200_ENABLE_CPU_BINDING": _bool("VLLM_B200_ENABLE_CPU_BINDING", "1"),
+    "VLLM_B200_CUDA_GRAPH": _bool("VLLM_B200_CUDA_GRAPH", "1"),
+}
+
+
+def __getattr__(name: str) -> Any:
+    if name in env_variables:
+        return env_variables[name]()
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def __dir__() -> list[str]:
+    return list(env_variables.keys())

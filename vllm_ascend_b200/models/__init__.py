@@ -1,0 +1,48 @@
+"""Model registry: architecture name -> constructor (the role of
+``register_model`` in vllm_ascend/models/__init__.py:4-29)."""
+from __future__ import annotations
+
+from typing import Callable
+
+from ..parallel import state as pstate
+
+_REGISTRY: dict[str, Callable] = {}
+
+
+def register_model(arch: str, ctor: Callable) -> None:
+    _REGISTRY[arch] = ctor
+
+
+def _causal_lm(cfg, device, **kw):
+    from .transformer import CausalLM
+    return CausalLM(cfg, device, **kw)
+
+
+for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwen3ForCausalLM",
+              "Qwen2MoeForCausalLM", "Qwen3MoeForCausalLM", "DeepseekV2ForCausalLM",
+              "DeepseekV3ForCausalLM", "InternLM2ForCausalLM", "Phi3ForCausalLM",
+              "GemmaForCausalLM", "MiniCPMForCausalLM"):
+    register_model(_arch, _causal_lm)
+
+
+def supported_architectures() -> list[str]:
+    return sorted(_REGISTRY)
+
+
+def build_model(engine_cfg, device, moe_runtime=None):
+    cfg = engine_cfg.model
+    ctor = _REGISTRY.get(cfg.architecture)
+    if ctor is None:
+        raise ValueError(f"unsupported architecture {cfg.architecture}; known: {supported_architectures()}")
+    st = pstate.get_state()
+    ep_group = st.ep if (engine_cfg.parallel.enable_expert_parallel and st.ep is not None) else None
+    pp = st.pp
+    layer_range = None
+    if pp is not None and pp.world_size > 1:
+        n = cfg.num_hidden_layers
+        per = (n + pp.world_size - 1) // pp.world_size
+        lo = pp.rank_in_group * per
+        layer_range = (lo, min(n, lo + per))
+    return ctor(cfg, device, max_model_len=engine_cfg.scheduler.max_model_len,
+                tp_group=st.tp, ep_group=ep_group, moe_runtime=moe_runtime,
+                layer_range=layer_range)

@@ -1,0 +1,283 @@
+"""Building blocks shared by every decoder family: TP-sharded linears, norms,
+rotary tables, the paged GQA attention layer and the SwiGLU MLP.
+
+Parity notes: the linear classes mirror the reference's per-layer communication
+group selection (vllm_ascend/ops/linear.py:114-575, ops/linear_op.py:152-357):
+column-parallel layers may all-gather their input and row-parallel layers end in
+all-reduce or reduce-scatter, chosen by the layer's ``TPComm``.
+"""
+from __future__ import annotations
+
+import hashlib
+import math
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import reference as ref
+from ..parallel import state as pstate
+
+
+# ---------------------------------------------------------------- parameters
+class ParamFactory:
+    """Creates (shards of) parameters.  Random init is seeded per parameter name so
+    every TP rank slices the same full tensor; small tensors are drawn on the CPU so
+    CPU and GPU instances of a test model hold identical weights."""
+
+    def __init__(self, cfg: ModelConfig, device: torch.device, dtype: torch.dtype):
+        self.cfg, self.device, self.dtype = cfg, device, dtype
+        self.meta_only = False
+
+    def _gen(self, name: str, dev) -> torch.Generator:
+        h = int.from_bytes(hashlib.sha256(f"{self.cfg.seed}:{name}".encode()).digest()[:7], "little")
+        g = torch.Generator(device=dev)
+        g.manual_seed(h)
+        return g
+
+    def normal(self, name: str, shape, shard_dim: Optional[int] = None, shard_rank: int = 0,
+               shard_world: int = 1, std: Optional[float] = None, dtype=None) -> torch.Tensor:
+        std = self.cfg.init_std if std is None else std
+        dtype = dtype or self.dtype
+        numel = math.prod(shape)
+        dev = torch.device("cpu") if numel <= (1 << 26) else self.device
+        full = torch.empty(shape, dtype=torch.float32 if dev.type == "cpu" else dtype, device=dev)
+        full.normal_(0.0, std, generator=self._gen(name, dev))
+        if shard_dim is not None and shard_world > 1:
+            size = shape[shard_dim] // shard_world
+            full = full.narrow(shard_dim, shard_rank * size, size)
+        return full.to(device=self.device, dtype=dtype).contiguous()
+
+    def ones(self, shape, dtype=None) -> torch.Tensor:
+        return torch.ones(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def zeros(self, shape, dtype=None) -> torch.Tensor:
+        return torch.zeros(shape, dtype=dtype or self.dtype, device=self.device)
+
+
+# ---------------------------------------------------------------- TP communication
+class TPComm:
+    """Collective that follows a row-parallel GEMM / precedes a column-parallel one.
+
+    ``mode``: "allreduce" (upstream default), or "sp" — sequence-parallel residual
+    stream where row-parallel ends in reduce-scatter and column-parallel starts with
+    all-gather (the reference's MLP/O-proj fine-grained TP ops).  The fused
+    GEMM+collective kernels plug in through ``parallel.fused_linear``.
+    """
+
+    def __init__(self, group: Optional[pstate.GroupCoordinator] = None, mode: str = "allreduce"):
+        self.group = group or pstate.get_tp_group()
+        self.mode = mode
+        self.fused = None          # set by parallel.fused_linear.attach()
+
+    @property
+    def size(self) -> int:
+        return self.group.world_size
+
+    @property
+    def rank(self) -> int:
+        return self.group.rank_in_group
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size == 1:
+            return t
+        if self.fused is not None and t.is_cuda:
+            return self.fused.all_reduce(t)
+        return self.group.all_reduce(t)
+
+    def all_gather(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
+        return self.group.all_gather(t, dim)
+
+    def reduce_scatter(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
+        return self.group.reduce_scatter(t, dim)
+
+
+# ---------------------------------------------------------------- linear layers
+class Linear:
+    """y = x W^T (+b).  ``weight`` is [N_local, K_local]."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, name: str = ""):
+        self.weight = weight
+        self.bias = bias
+        self.name = name
+        self.quant = None           # quantization.LinearMethod or None
+
+    def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.quant is not None:
+            return self.quant.apply(self, x, residual)
+        return ops.linear(x, self.weight, self.bias, residual)
+
+    def named_tensors(self):
+        yield "weight", self.weight
+        if self.bias is not None:
+            yield "bias", self.bias
+        if self.quant is not None:
+            yield from self.quant.named_tensors(self)
+
+
+class ColumnParallelLinear(Linear):
+    """Output dim sharded over TP.  ``output_sizes`` lists merged sub-matrices
+    (qkv, gate_up) so checkpoint shards land in the right rows."""
+
+    def __init__(self, pf: ParamFactory, name: str, in_size: int, output_sizes: list[int],
+                 comm: TPComm, bias: bool = False, gather_output: bool = False):
+        tp, r = comm.size, comm.rank
+        parts = [pf.normal(f"{name}.{i}", (n, in_size), 0, r, tp) for i, n in enumerate(output_sizes)]
+        w = torch.cat(parts, dim=0) if len(parts) > 1 else parts[0]
+        b = pf.zeros((w.shape[0],)) if bias else None
+        super().__init__(w, b, name)
+        self.comm = comm
+        self.output_sizes = output_sizes
+        self.local_sizes = [n // tp for n in output_sizes]
+        self.gather_output = gather_output
+
+    def __call__(self, x, residual=None):
+        y = super().__call__(x, residual)
+        if self.gather_output and self.comm.size > 1:
+            y = self.comm.all_gather(y, dim=-1)
+        return y
+
+
+class RowParallelLinear(Linear):
+    """Input dim sharded over TP; the partial sums are reduced by ``comm``."""
+
+    def __init__(self, pf: ParamFactory, name: str, in_size: int, out_size: int, comm: TPComm,
+                 bias: bool = False, reduce_results: bool = True):
+        w = pf.normal(name, (out_size, in_size), 1, comm.rank, comm.size)
+        b = pf.zeros((out_size,)) if bias else None
+        super().__init__(w, b, name)
+        self.comm = comm
+        self.reduce_results = reduce_results
+
+    def __call__(self, x, residual=None):
+        if self.comm.size == 1:
+            return super().__call__(x, residual)
+        # residual/bias must be added once, not per rank
+        if self.quant is not None:
+            y = self.quant.apply(self, x, None, skip_bias=self.comm.rank != 0)
+        else:
+            y = ops.linear(x, self.weight, self.bias if self.comm.rank == 0 else None)
+        if self.reduce_results:
+            y = self.comm.all_reduce(y)
+        if residual is not None:
+            y = y + residual
+        return y
+
+
+class RMSNorm:
+    def __init__(self, pf: ParamFactory, size: int, eps: float, gemma: bool = False):
+        self.weight = pf.ones((size,))
+        self.eps = eps
+        self.gemma = gemma
+
+    def __call__(self, x, residual=None):
+        return ops.rms_norm(x, self.weight, self.eps, residual, self.gemma)
+
+
+class VocabParallelEmbedding:
+    """Vocab sharded over TP, masked lookup + all-reduce
+    (vllm_ascend/ops/vocab_parallel_embedding.py:229-257)."""
+
+    def __init__(self, pf: ParamFactory, name: str, vocab: int, hidden: int, comm: TPComm):
+        self.comm = comm
+        self.vocab = vocab
+        pad = (-vocab) % (comm.size * 8)
+        self.padded_vocab = vocab + pad
+        self.shard = self.padded_vocab // comm.size
+        self.start = comm.rank * self.shard
+        full_rows = min(max(vocab - self.start, 0), self.shard)
+        w = pf.zeros((self.shard, hidden))
+        if full_rows > 0:
+            src = pf.normal(name, (self.padded_vocab, hidden), 0, comm.rank, comm.size)
+            w[:full_rows] = src[:full_rows]
+        self.weight = w
+
+    def __call__(self, ids: torch.Tensor) -> torch.Tensor:
+        out = ops.embedding(ids, self.weight, self.start, self.start + self.shard)
+        if self.comm.size > 1:
+            out = self.comm.all_reduce(out)
+        return out
+
+
+class ParallelLMHead:
+    """Logits = hidden @ W^T with the vocab sharded over TP and gathered."""
+
+    def __init__(self, embed: VocabParallelEmbedding, weight: Optional[torch.Tensor] = None):
+        self.embed = embed
+        self.weight = weight if weight is not None else embed.weight
+        self.comm = embed.comm
+
+    def __call__(self, hidden: torch.Tensor) -> torch.Tensor:
+        logits = ops.linear(hidden, self.weight)
+        if self.comm.size > 1:
+            logits = self.comm.all_gather(logits, dim=-1)
+        return logits[..., :self.embed.vocab]
+
+
+# ---------------------------------------------------------------- rotary tables
+_ROPE_CACHE: dict = {}
+
+
+def get_cos_sin_cache(rot_dim: int, max_pos: int, theta: float, scaling, device) -> torch.Tensor:
+    key = (rot_dim, max_pos, theta, str(scaling), str(device))
+    t = _ROPE_CACHE.get(key)
+    if t is None:
+        t = ref.build_cos_sin_cache(rot_dim, max_pos, theta, scaling, device)
+        _ROPE_CACHE[key] = t
+    return t
+
+
+# ---------------------------------------------------------------- attention + MLP
+class GQAAttention:
+    """qkv proj -> fused (q/k RMSNorm + RoPE + paged KV write) -> paged attention -> o proj."""
+
+    def __init__(self, pf: ParamFactory, cfg: ModelConfig, layer_idx: int, comm: TPComm,
+                 max_pos: int):
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        tp = comm.size
+        self.D = cfg.head_dim
+        self.Hq = cfg.num_attention_heads // tp
+        self.total_kv = cfg.num_key_value_heads
+        # kv heads are replicated when there are fewer of them than TP ranks
+        self.Hkv = max(1, self.total_kv // tp)
+        prefix = f"model.layers.{layer_idx}.self_attn"
+        kv_out = self.total_kv * self.D if self.total_kv >= tp else tp * self.D
+        self.kv_replicas = 1 if self.total_kv >= tp else tp // self.total_kv
+        self.qkv_proj = ColumnParallelLinear(
+            pf, f"{prefix}.qkv_proj", cfg.hidden_size,
+            [cfg.num_attention_heads * self.D, kv_out, kv_out], comm, bias=cfg.attention_bias)
+        self.o_proj = RowParallelLinear(pf, f"{prefix}.o_proj", cfg.num_attention_heads * self.D,
+                                        cfg.hidden_size, comm)
+        self.q_norm = pf.ones((self.D,)) if cfg.qk_norm else None
+        self.k_norm = pf.ones((self.D,)) if cfg.qk_norm else None
+        self.scale = self.D ** -0.5
+        self.rot_dim = self.D
+        self.cos_sin = get_cos_sin_cache(self.rot_dim, max_pos, cfg.rope_theta, cfg.rope_scaling,
+                                         pf.device)
+        self.window = cfg.sliding_window or 0
+
+    def __call__(self, x: torch.Tensor, meta, kv_cache) -> torch.Tensor:
+        qkv = self.qkv_proj(x)
+        k_cache, v_cache = kv_cache
+        ops.qknorm_rope_kvwrite(qkv, meta.positions, self.cos_sin, self.rot_dim, self.q_norm,
+                                self.k_norm, self.cfg.rms_norm_eps, k_cache, v_cache,
+                                meta.slot_mapping, self.Hq, self.Hkv, self.D)
+        T = qkv.shape[0]
+        q = qkv[:, :self.Hq * self.D].view(T, self.Hq, self.D)
+        o = ops.paged_attention(q, k_cache, v_cache, meta, self.scale, causal=True,
+                                window=self.window)
+        return self.o_proj(o.view(T, self.Hq * self.D))
+
+
+class SwiGLUMLP:
+    def __init__(self, pf: ParamFactory, prefix: str, hidden: int, inter: int, comm: TPComm,
+                 reduce_results: bool = True):
+        self.gate_up_proj = ColumnParallelLinear(pf, f"{prefix}.gate_up_proj", hidden,
+                                                 [inter, inter], comm)
+        self.down_proj = RowParallelLinear(pf, f"{prefix}.down_proj", inter, hidden, comm,
+                                           reduce_results=reduce_results)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(ops.silu_and_mul(self.gate_up_proj(x)))

@@ -1,0 +1,449 @@
+"""Decoder-only transformer covering the model families the benchmarks name:
+Llama / Qwen2 / Qwen3 (dense, GQA), Qwen3-MoE (routed experts) and
+DeepSeek-V2/V3 (MLA attention + shared/routed experts, leading dense layers).
+
+The reference takes model definitions from upstream vLLM and overrides layers
+through its OOT op table (vllm_ascend/utils.py:703-732); here the definitions
+live in the framework and call the op entry points directly.  Checkpoints use the
+HF parameter names (``load_weights``), so the same safetensors files load.
+"""
+from __future__ import annotations
+
+import re
+from typing import Iterable, Optional
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import fused_moe, reference as ref
+from ..parallel import state as pstate
+from .layers import (ColumnParallelLinear, GQAAttention, Linear, ParallelLMHead, ParamFactory,
+                     RMSNorm, RowParallelLinear, SwiGLUMLP, TPComm, VocabParallelEmbedding,
+                     get_cos_sin_cache)
+
+
+# ---------------------------------------------------------------- MoE block
+class SparseMoeBlock:
+    """Router + routed experts (+ shared experts).  Experts are sharded over the EP
+    group when expert parallelism is on, else over TP along the intermediate dim."""
+
+    def __init__(self, pf: ParamFactory, cfg: ModelConfig, layer_idx: int, comm: TPComm,
+                 ep_group: Optional[pstate.GroupCoordinator], moe_runtime=None):
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        self.comm = comm
+        prefix = f"model.layers.{layer_idx}.mlp"
+        E, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
+        self.gate_weight = pf.normal(f"{prefix}.gate", (E, H), dtype=torch.float32)
+        self.e_bias = pf.zeros((E,), dtype=torch.float32) if cfg.e_score_correction_bias else None
+        self.ep = ep_group if (ep_group is not None and ep_group.world_size > 1) else None
+        self.runtime = moe_runtime
+        if self.ep is not None:
+            ep, r = self.ep.world_size, self.ep.rank_in_group
+            assert E % ep == 0
+            self.E_local = E // ep
+            self.expert_start = r * self.E_local
+            self.w13 = pf.normal(f"{prefix}.experts.w13", (E, 2 * I, H), 0, r, ep)
+            self.w2 = pf.normal(f"{prefix}.experts.w2", (E, H, I), 0, r, ep)
+            emap = torch.full((E,), -1, dtype=torch.int32)
+            emap[self.expert_start:self.expert_start + self.E_local] = torch.arange(self.E_local, dtype=torch.int32)
+            self.expert_map = emap.to(pf.device)
+        else:
+            tp, r = comm.size, comm.rank
+            self.E_local = E
+            self.expert_start = 0
+            g = pf.normal(f"{prefix}.experts.w1", (E, I, H), 1, r, tp)
+            u = pf.normal(f"{prefix}.experts.w3", (E, I, H), 1, r, tp)
+            self.w13 = torch.cat([g, u], dim=1).contiguous()
+            self.w2 = pf.normal(f"{prefix}.experts.w2", (E, H, I), 2, r, tp)
+            self.expert_map = None
+        self.quant = None
+        self.shared = None
+        if cfg.n_shared_experts > 0:
+            self.shared = SwiGLUMLP(pf, f"{prefix}.shared_experts", H, I * cfg.n_shared_experts,
+                                    comm, reduce_results=False)
+        # logical -> physical redirect for redundant experts (EPLB); identity by default
+        self.log2phy: Optional[torch.Tensor] = None
+        self.expert_load: Optional[torch.Tensor] = None      # per-physical-expert hit counter
+
+    def route(self, x: torch.Tensor):
+        cfg = self.cfg
+        logits = torch.nn.functional.linear(x.float(), self.gate_weight)
+        w, ids = fused_moe.gating_topk(logits, cfg.num_experts_per_tok, cfg.scoring_func,
+                                       cfg.norm_topk_prob, cfg.n_group, cfg.topk_group,
+                                       self.e_bias, cfg.routed_scaling_factor)
+        if self.log2phy is not None:
+            ids = self.log2phy[ids.long()].to(torch.int32)
+        if self.expert_load is not None:
+            self.expert_load.scatter_add_(0, ids.flatten().long(),
+                                          torch.ones(ids.numel(), dtype=self.expert_load.dtype,
+                                                     device=ids.device))
+        return w, ids
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        w, ids = self.route(x)
+        if self.runtime is not None and self.ep is not None:
+            y = self.runtime.forward(self, x, w, ids)          # EP dispatch/combine paths
+        else:
+            y = fused_moe.fused_experts(x, self.w13, self.w2, w, ids, self.expert_map, self.quant)
+        if self.ep is None:
+            # TP-sharded experts (and shared experts) hold partial sums: one reduction
+            if self.shared is not None:
+                y = y + self.shared(x)
+            if self.comm.size > 1:
+                y = self.comm.all_reduce(y)
+            return y
+        if self.shared is not None:
+            s = self.shared(x)
+            if self.comm.size > 1:
+                s = self.comm.all_reduce(s)
+            y = y + s
+        return y
+
+
+# ---------------------------------------------------------------- MLA attention
+class MLAAttention:
+    """Multi-head latent attention with absorbed weights.
+
+    Cache contract (vllm_ascend/attention/mla_v1.py:1296-1326): per token one
+    normalised latent vector (kv_lora_rank) and one RoPE'd key slice
+    (qk_rope_head_dim), in two paged tensors.  Scores are
+    q_nope·W_UK·latent + q_pe·k_pe; the value path is latent·W_UV — i.e. MQA over a
+    576-wide key with the up-projections folded into q and the output
+    (``W_UK_T`` / ``W_UV`` of mla_v1.py:907-971).
+    """
+
+    def __init__(self, pf: ParamFactory, cfg: ModelConfig, layer_idx: int, comm: TPComm,
+                 max_pos: int):
+        self.cfg = cfg
+        tp = comm.size
+        self.H = cfg.num_attention_heads // tp
+        self.dn, self.dr, self.dv, self.dc = (cfg.qk_nope_head_dim, cfg.qk_rope_head_dim,
+                                              cfg.v_head_dim, cfg.kv_lora_rank)
+        hid = cfg.hidden_size
+        p = f"model.layers.{layer_idx}.self_attn"
+        rep = TPComm(pstate.GroupCoordinator("single", [0], 0))   # replicated (not sharded)
+        qd = cfg.num_attention_heads * (self.dn + self.dr)
+        if cfg.q_lora_rank:
+            self.q_a_proj = ColumnParallelLinear(pf, f"{p}.q_a_proj", hid, [cfg.q_lora_rank], rep)
+            self.q_a_norm = RMSNorm(pf, cfg.q_lora_rank, cfg.rms_norm_eps)
+            self.q_b_proj = ColumnParallelLinear(pf, f"{p}.q_b_proj", cfg.q_lora_rank, [qd], comm)
+            self.q_proj = None
+        else:
+            self.q_proj = ColumnParallelLinear(pf, f"{p}.q_proj", hid, [qd], comm)
+        self.kv_a_proj = ColumnParallelLinear(pf, f"{p}.kv_a_proj_with_mqa", hid,
+                                              [self.dc + self.dr], rep)
+        self.kv_a_norm = RMSNorm(pf, self.dc, cfg.rms_norm_eps)
+        # kv_b_proj [H*(dn+dv), dc] kept for checkpoint parity, used through the absorbed views
+        self.kv_b_proj = ColumnParallelLinear(pf, f"{p}.kv_b_proj", self.dc,
+                                              [cfg.num_attention_heads * (self.dn + self.dv)], comm)
+        self.o_proj = RowParallelLinear(pf, f"{p}.o_proj", cfg.num_attention_heads * self.dv, hid,
+                                        comm)
+        self.scale = (self.dn + self.dr) ** -0.5
+        sc = cfg.rope_scaling
+        if sc and sc.get("mscale_all_dim"):
+            import math
+            m = 0.1 * sc["mscale_all_dim"] * math.log(sc.get("factor", 1.0)) + 1.0
+            self.scale *= m * m
+        self.cos_sin = get_cos_sin_cache(self.dr, max_pos, cfg.rope_theta,
+                                         dict(sc, rope_type="deepseek_yarn") if sc else None,
+                                         pf.device)
+        self.process_weights_after_loading()
+
+    def process_weights_after_loading(self) -> None:
+        w = self.kv_b_proj.weight.view(self.H, self.dn + self.dv, self.dc)
+        self.W_UK = w[:, :self.dn, :].contiguous()                        # [H, dn, dc]
+        self.W_UV = w[:, self.dn:, :].transpose(1, 2).contiguous()        # [H, dc, dv]
+
+    def __call__(self, x: torch.Tensor, meta, kv_cache) -> torch.Tensor:
+        T = x.shape[0]
+        if self.q_proj is None:
+            q = self.q_b_proj(self.q_a_norm(self.q_a_proj(x))[0])
+        else:
+            q = self.q_proj(x)
+        q = q.view(T, self.H, self.dn + self.dr)
+        kv = self.kv_a_proj(x)
+        latent = self.kv_a_norm(kv[:, :self.dc].contiguous())[0]
+        k_pe = kv[:, self.dc:].reshape(T, 1, self.dr)
+        q_pe = ref.apply_rope_interleaved(q[..., self.dn:], meta.positions, self.cos_sin, self.dr)
+        k_pe = ref.apply_rope_interleaved(k_pe, meta.positions, self.cos_sin, self.dr)
+        lat_cache, pe_cache = kv_cache
+        from ..attention import mla as mla_ops
+        mla_ops.write_latent_cache(latent, k_pe.view(T, self.dr), lat_cache, pe_cache,
+                                   meta.slot_mapping)
+        # absorb W_UK into q: [T,H,dn] x [H,dn,dc] -> [T,H,dc]
+        q_lat = torch.einsum("thd,hdc->thc", q[..., :self.dn], self.W_UK.to(q.dtype))
+        o_lat = mla_ops.mla_paged_attention(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale)
+        o = torch.einsum("thc,hcv->thv", o_lat, self.W_UV.to(o_lat.dtype))
+        return self.o_proj(o.reshape(T, self.H * self.dv))
+
+
+# ---------------------------------------------------------------- decoder layer / model
+class DecoderLayer:
+    def __init__(self, pf: ParamFactory, cfg: ModelConfig, idx: int, comm: TPComm, max_pos: int,
+                 ep_group=None, moe_runtime=None):
+        p = f"model.layers.{idx}"
+        self.idx = idx
+        self.input_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
+        self.self_attn = (MLAAttention if cfg.use_mla else GQAAttention)(pf, cfg, idx, comm, max_pos)
+        if cfg.is_moe_layer(idx):
+            self.mlp = SparseMoeBlock(pf, cfg, idx, comm, ep_group, moe_runtime)
+        else:
+            self.mlp = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm)
+
+    def __call__(self, h, residual, meta, kv_cache):
+        if residual is None:
+            residual = h
+            x, _ = self.input_layernorm(h)
+        else:
+            x, residual = self.input_layernorm(h, residual)
+        h = self.self_attn(x, meta, kv_cache)
+        x, residual = self.post_attention_layernorm(h, residual)
+        h = self.mlp(x)
+        return h, residual
+
+
+class CausalLM:
+    """Model object the runner drives: ``forward`` -> hidden states, ``compute_logits``."""
+
+    def __init__(self, cfg: ModelConfig, device, max_model_len: int = 4096,
+                 tp_group: Optional[pstate.GroupCoordinator] = None,
+                 ep_group: Optional[pstate.GroupCoordinator] = None, moe_runtime=None,
+                 layer_range: Optional[tuple[int, int]] = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = cfg.torch_dtype
+        pf = ParamFactory(cfg, self.device, self.dtype)
+        self.comm = TPComm(tp_group or pstate.get_tp_group())
+        max_pos = max(max_model_len, 16)
+        lo, hi = layer_range or (0, cfg.num_hidden_layers)
+        self.layer_range = (lo, hi)
+        self.is_first = lo == 0
+        self.is_last = hi == cfg.num_hidden_layers
+        self.embed_tokens = VocabParallelEmbedding(pf, "model.embed_tokens", cfg.vocab_size,
+                                                   cfg.hidden_size, self.comm)
+        self.layers = [DecoderLayer(pf, cfg, i, self.comm, max_pos, ep_group, moe_runtime)
+                       for i in range(lo, hi)]
+        self.norm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
+        if cfg.tie_word_embeddings:
+            self.lm_head = ParallelLMHead(self.embed_tokens)
+        else:
+            head = VocabParallelEmbedding(pf, "lm_head", cfg.vocab_size, cfg.hidden_size, self.comm)
+            self.lm_head = ParallelLMHead(head)
+        if cfg.quantization:
+            from ..quantization import apply_quantization
+            apply_quantization(self, cfg)
+
+    # -- forward ---------------------------------------------------------
+    def forward(self, input_ids: torch.Tensor, meta, kv_caches: list,
+                intermediate: Optional[tuple] = None):
+        if self.is_first:
+            h = self.embed_tokens(input_ids)
+            residual = None
+        else:
+            h, residual = intermediate
+        for layer, cache in zip(self.layers, kv_caches):
+            h, residual = layer(h, residual, meta, cache)
+        if not self.is_last:
+            return h, residual
+        h, _ = self.norm(h, residual)
+        return h
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.lm_head(hidden)
+
+    __call__ = forward
+
+    # -- parameters --------------------------------------------------------
+    def named_parameters(self):
+        yield "model.embed_tokens.weight", self.embed_tokens.weight
+        for L in self.layers:
+            p = f"model.layers.{L.idx}"
+            yield f"{p}.input_layernorm.weight", L.input_layernorm.weight
+            yield f"{p}.post_attention_layernorm.weight", L.post_attention_layernorm.weight
+            a = L.self_attn
+            for attr in ("qkv_proj", "o_proj", "q_a_proj", "q_b_proj", "q_proj", "kv_a_proj",
+                         "kv_b_proj"):
+                lin = getattr(a, attr, None)
+                if isinstance(lin, Linear):
+                    for n, t in lin.named_tensors():
+                        yield f"{p}.self_attn.{attr}.{n}", t
+            for attr in ("q_norm", "k_norm"):
+                t = getattr(a, attr, None)
+                if isinstance(t, torch.Tensor):
+                    yield f"{p}.self_attn.{attr}.weight", t
+            for attr in ("q_a_norm", "kv_a_norm"):
+                n = getattr(a, attr, None)
+                if n is not None:
+                    yield f"{p}.self_attn.{attr}.weight", n.weight
+            m = L.mlp
+            if isinstance(m, SparseMoeBlock):
+                yield f"{p}.mlp.gate.weight", m.gate_weight
+                if m.e_bias is not None:
+                    yield f"{p}.mlp.gate.e_score_correction_bias", m.e_bias
+                yield f"{p}.mlp.experts.w13", m.w13
+                yield f"{p}.mlp.experts.w2", m.w2
+                if m.shared is not None:
+                    for n, t in m.shared.gate_up_proj.named_tensors():
+                        yield f"{p}.mlp.shared_experts.gate_up_proj.{n}", t
+                    for n, t in m.shared.down_proj.named_tensors():
+                        yield f"{p}.mlp.shared_experts.down_proj.{n}", t
+            else:
+                for n, t in m.gate_up_proj.named_tensors():
+                    yield f"{p}.mlp.gate_up_proj.{n}", t
+                for n, t in m.down_proj.named_tensors():
+                    yield f"{p}.mlp.down_proj.{n}", t
+        yield "model.norm.weight", self.norm.weight
+        if not self.cfg.tie_word_embeddings:
+            yield "lm_head.weight", self.lm_head.weight
+
+    def num_parameters(self) -> int:
+        return sum(t.numel() for _, t in self.named_parameters())
+
+    # -- checkpoint loading ------------------------------------------------
+    _STACKED = {"q_proj": ("qkv_proj", 0), "k_proj": ("qkv_proj", 1), "v_proj": ("qkv_proj", 2),
+                "gate_proj": ("gate_up_proj", 0), "up_proj": ("gate_up_proj", 1)}
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        """Loads HF-named tensors, slicing each to this rank's TP/EP shard."""
+        loaded: set[str] = set()
+        params = dict(self.named_parameters())
+        layers = {L.idx: L for L in self.layers}
+        tp, r = self.comm.size, self.comm.rank
+        for name, w in weights:
+            if name.endswith("rotary_emb.inv_freq"):
+                continue
+            m = re.match(r"model\.layers\.(\d+)\.(.*)", name)
+            if m and int(m.group(1)) not in layers:
+                continue
+            # routed experts
+            me = re.match(r"model\.layers\.(\d+)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight", name)
+            if me:
+                L = layers[int(me.group(1))].mlp
+                e = int(me.group(2))
+                I = self.cfg.moe_intermediate_size
+                if L.ep is not None:
+                    le = e - L.expert_start
+                    if not (0 <= le < L.E_local):
+                        continue
+                    if me.group(3) == "gate_proj":
+                        L.w13[le, :I].copy_(w)
+                    elif me.group(3) == "up_proj":
+                        L.w13[le, I:].copy_(w)
+                    else:
+                        L.w2[le].copy_(w)
+                else:
+                    Il = I // tp
+                    if me.group(3) == "gate_proj":
+                        L.w13[e, :Il].copy_(w[r * Il:(r + 1) * Il])
+                    elif me.group(3) == "up_proj":
+                        L.w13[e, Il:].copy_(w[r * Il:(r + 1) * Il])
+                    else:
+                        L.w2[e].copy_(w[:, r * Il:(r + 1) * Il])
+                loaded.add(name)
+                continue
+            target, shard_id = name, None
+            for hf, (merged, sid) in self._STACKED.items():
+                if f".{hf}." in name:
+                    target, shard_id = name.replace(hf, merged), sid
+                    break
+            target = target.replace("kv_a_proj_with_mqa", "kv_a_proj") \
+                           .replace("q_a_layernorm", "q_a_norm").replace("kv_a_layernorm", "kv_a_norm")
+            if target not in params:
+                continue
+            dst = params[target]
+            self._copy_shard(target, dst, w, shard_id, tp, r)
+            loaded.add(name)
+        for L in self.layers:
+            if isinstance(L.self_attn, MLAAttention):
+                L.self_attn.process_weights_after_loading()
+        return loaded
+
+    def _copy_shard(self, target: str, dst: torch.Tensor, w: torch.Tensor, shard_id, tp: int, r: int):
+        cfg = self.cfg
+        if shard_id is not None and "qkv_proj" in target:
+            D = cfg.head_dim
+            Hq_l = cfg.num_attention_heads // tp
+            Hkv = cfg.num_key_value_heads
+            Hkv_l = max(1, Hkv // tp)
+            if shard_id == 0:
+                rows = slice(0, Hq_l * D)
+                src = w[r * Hq_l * D:(r + 1) * Hq_l * D]
+            else:
+                kv_rank = r if Hkv >= tp else r // (tp // Hkv)
+                base = Hq_l * D + (shard_id - 1) * Hkv_l * D
+                rows = slice(base, base + Hkv_l * D)
+                src = w[kv_rank * Hkv_l * D:(kv_rank + 1) * Hkv_l * D]
+            dst[rows].copy_(src)
+            return
+        if shard_id is not None:       # gate_up
+            n = dst.shape[0] // 2
+            dst[shard_id * n:(shard_id + 1) * n].copy_(w[r * n:(r + 1) * n])
+            return
+        if tuple(dst.shape) == tuple(w.shape):
+            dst.copy_(w)
+            return
+        # TP-sharded single matrices: find the dim that differs
+        for d in range(w.dim()):
+            if dst.shape[d] != w.shape[d]:
+                if d == 0 and ("embed_tokens" in target or "lm_head" in target):
+                    n = dst.shape[0]
+                    rows = min(max(w.shape[0] - r * n, 0), n)
+                    dst[:rows].copy_(w[r * n:r * n + rows])
+                else:
+                    n = dst.shape[d]
+                    dst.copy_(w.narrow(d, r * n, n))
+                return
+        raise ValueError(f"cannot place {target}: {tuple(w.shape)} -> {tuple(dst.shape)}")
+
+
+def iterate_safetensors(path: str):
+    """Yields (name, tensor) from every *.safetensors file of an HF checkpoint dir."""
+    import glob
+    import os
+    from safetensors import safe_open
+    files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    if not files:
+        raise FileNotFoundError(f"no safetensors files under {path}")
+    for f in files:
+        with safe_open(f, framework="pt", device="cpu") as sf:
+            for k in sf.keys():
+                yield k, sf.get_tensor(k)
+
+
+def export_hf_state_dict(model: CausalLM) -> dict[str, torch.Tensor]:
+    """Inverse of ``load_weights`` for single-rank models (tests, save_sharded_state)."""
+    cfg = model.cfg
+    out: dict[str, torch.Tensor] = {}
+    D = cfg.head_dim
+    for name, t in model.named_parameters():
+        t = t.detach().cpu()
+        if name.endswith("qkv_proj.weight") or name.endswith("qkv_proj.bias"):
+            nq, nkv = cfg.num_attention_heads * D, cfg.num_key_value_heads * D
+            suffix = name.rsplit(".", 1)[1]
+            base = name[: -len("qkv_proj." + suffix)]
+            out[f"{base}q_proj.{suffix}"] = t[:nq].clone()
+            out[f"{base}k_proj.{suffix}"] = t[nq:nq + nkv].clone()
+            out[f"{base}v_proj.{suffix}"] = t[nq + nkv:].clone()
+        elif name.endswith("gate_up_proj.weight"):
+            n = t.shape[0] // 2
+            base = name[: -len("gate_up_proj.weight")]
+            out[f"{base}gate_proj.weight"] = t[:n].clone()
+            out[f"{base}up_proj.weight"] = t[n:].clone()
+        elif name.endswith("experts.w13"):
+            base = name[: -len("w13")]
+            I = cfg.moe_intermediate_size
+            for e in range(t.shape[0]):
+                out[f"{base}{e}.gate_proj.weight"] = t[e, :I].clone()
+                out[f"{base}{e}.up_proj.weight"] = t[e, I:].clone()
+        elif name.endswith("experts.w2"):
+            base = name[: -len("w2")]
+            for e in range(t.shape[0]):
+                out[f"{base}{e}.down_proj.weight"] = t[e].clone()
+        else:
+            name = name.replace("kv_a_proj.", "kv_a_proj_with_mqa.") \
+                       .replace("q_a_norm", "q_a_layernorm").replace("kv_a_norm", "kv_a_layernorm")
+            out[name] = t.clone()
+    return out

@@ -1,0 +1,326 @@
+"""Op entry points.  CUDA bf16 tensors go to the hand-written sm_100a kernels;
+CPU (and non-bf16) tensors run the PyTorch restatement in ``reference``.
+
+A CUDA bf16 tensor never falls back silently: if the native library is missing
+the call raises.  The only library paths are explicit opt-outs through
+``envs.VLLM_B200_GEMM`` / ``VLLM_B200_PREFILL_ATTN`` (kept for validation).
+
+The op set corresponds to the reference's OOT custom-op table
+(vllm_ascend/utils.py:703-732) and ``DeviceOperator`` routes
+(vllm_ascend/device/device_op.py:43-965).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native, envs
+from . import reference as ref
+
+_BF16 = torch.bfloat16
+
+#: number of launches of this package's own kernels (bench.py reports it)
+launch_counter = [0]
+
+
+def _use_native(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == _BF16
+
+
+# ---------------------------------------------------------------- norms / activations
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+             residual: Optional[torch.Tensor] = None, gemma: bool = False,
+             out: Optional[torch.Tensor] = None):
+    """Returns (normed, residual_out).  With ``residual`` the sum x+residual is
+    written back into ``residual`` (in place) — the fused add+RMSNorm of
+    vllm_ascend/ops/layernorm.py:63-85."""
+    if not _use_native(x):
+        return ref.rms_norm(x, weight, eps, residual, gemma)
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H) if x.stride(-1) == 1 else x.contiguous().view(-1, H)
+    T = x2.shape[0]
+    if out is None:
+        out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    if residual is not None:
+        assert residual.is_contiguous()
+    rc = _native.lib().b200_rms_norm(x2.data_ptr(), _native.ptr(residual), weight.data_ptr(),
+                                     out.data_ptr(), T, H, eps, int(gemma), x2.stride(0),
+                                     out.stride(0), _native.stream_ptr())
+    _native.check(rc, "rms_norm")
+    launch_counter[0] += 1
+    return out.view(x.shape), residual
+
+
+def silu_and_mul(x: torch.Tensor, limit: float = 0.0,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if not _use_native(x):
+        return ref.silu_and_mul(x, limit)
+    I = x.shape[-1] // 2
+    x2 = x.view(-1, 2 * I)
+    T = x2.shape[0]
+    if out is None:
+        out = torch.empty((T, I), dtype=x.dtype, device=x.device)
+    rc = _native.lib().b200_silu_and_mul(x2.data_ptr(), out.data_ptr(), T, I, limit,
+                                         _native.stream_ptr())
+    _native.check(rc, "silu_and_mul")
+    launch_counter[0] += 1
+    return out.view(*x.shape[:-1], I)
+
+
+def embedding(ids: torch.Tensor, weight: torch.Tensor, vocab_start: int = 0,
+              vocab_end: Optional[int] = None, out: Optional[torch.Tensor] = None):
+    if vocab_end is None:
+        vocab_end = vocab_start + weight.shape[0]
+    if not _use_native(weight):
+        return ref.embedding(ids, weight, vocab_start, vocab_end)
+    T, H = ids.numel(), weight.shape[1]
+    if out is None:
+        out = torch.empty((T, H), dtype=weight.dtype, device=weight.device)
+    ids = ids.to(torch.int64)
+    rc = _native.lib().b200_embedding(ids.data_ptr(), weight.data_ptr(), out.data_ptr(), T, H,
+                                      vocab_start, vocab_end, _native.stream_ptr())
+    _native.check(rc, "embedding")
+    launch_counter[0] += 1
+    return out
+
+
+def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                        rot_dim: int, q_norm_w, k_norm_w, eps: float,
+                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                        slot_mapping: Optional[torch.Tensor], Hq: int, Hkv: int, D: int) -> None:
+    """Split-QKV + per-head q/k RMSNorm + neox RoPE + paged KV-cache write, one pass, in place."""
+    native_ok = (_use_native(qkv) and D in (32, 64, 96, 128, 256) and rot_dim <= D
+                 and (rot_dim == 0 or (rot_dim // 2) % 32 == 0)
+                 and (k_cache is None or k_cache.dtype == _BF16))
+    if not native_ok:
+        if qkv.is_cuda and qkv.dtype == _BF16 and D in (64, 128):
+            raise RuntimeError("qknorm_rope_kvwrite: unsupported rotary shape for the native kernel")
+        return ref.qknorm_rope_kvwrite(qkv, positions, cos_sin, rot_dim, q_norm_w, k_norm_w, eps,
+                                       k_cache, v_cache, slot_mapping, Hq, Hkv, D)
+    T = qkv.shape[0]
+    num_slots = 0 if k_cache is None else k_cache.shape[0] * k_cache.shape[1]
+    rc = _native.lib().b200_qknorm_rope_kvwrite(
+        qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), cos_sin.data_ptr(), rot_dim,
+        _native.ptr(q_norm_w), _native.ptr(k_norm_w), eps, _native.ptr(k_cache),
+        _native.ptr(v_cache), _native.ptr(slot_mapping), T, Hq, Hkv, D, num_slots,
+        _native.status_word(qkv.device).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "qknorm_rope_kvwrite")
+    launch_counter[0] += 1
+
+
+# ---------------------------------------------------------------- GEMM
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+           bn: int = 0) -> torch.Tensor:
+    """y = x @ weight.T (+bias) (+residual).  x [..., K], weight [N, K]."""
+    K = x.shape[-1]
+    N = weight.shape[0]
+    if (not _use_native(x)) or weight.dtype != _BF16:
+        y = torch.nn.functional.linear(x, weight.to(x.dtype), bias)
+        if residual is not None:
+            y = y + residual
+        return y
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) != 0:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    if envs.VLLM_B200_GEMM == "cublas" or (K % 8) or (N % 8):
+        y = torch.nn.functional.linear(x2, weight, bias)
+        if residual is not None:
+            y = y + residual.view(M, N)
+        return y.view(*x.shape[:-1], N)
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return out.view(*x.shape[:-1], N)
+    res2 = None
+    if residual is not None:
+        res2 = residual.view(M, N)
+        assert res2.stride(0) == out.stride(0) and res2.stride(1) == 1
+    rc = _native.lib().b200_gemm_bf16(
+        x2.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias), _native.ptr(res2),
+        M, N, K, x2.stride(0), weight.stride(0), out.stride(0), bn,
+        _native.status_word(x.device).data_ptr(), 0, _native.stream_ptr())
+    _native.check(rc, "gemm_bf16")
+    launch_counter[0] += 1
+    return out.view(*x.shape[:-1], N)
+
+
+# ---------------------------------------------------------------- attention
+_scratch: dict = {}
+
+
+def _get_scratch(device, nbytes: int) -> torch.Tensor:
+    """Grow-only per-device scratch (split-KV partials)."""
+    key = (device.type, device.index)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def reserve_attention_scratch(device, nbytes: int) -> None:
+    """Pre-size the split-KV scratch (must happen before CUDA-graph capture)."""
+    _get_scratch(torch.device(device), nbytes)
+
+
+def paged_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
+                       scale: float, out: torch.Tensor, causal: bool = True, window: int = 0,
+                       num_splits: int = 1, rescale_threshold: float = 8.0,
+                       v_lbo: int = 0, v_sbo: int = 0) -> torch.Tensor:
+    """tcgen05 kernel over all query tokens of the batch (prefill, decode or mixed)."""
+    T, Hq, D = q.shape
+    NB, BS, Hkv, _ = k_cache.shape
+    G = Hq // Hkv
+    if meta.tile_seq is None and meta.max_query_len > 128 // G:
+        raise ValueError("attention work list required when a sequence has more than 128/G query tokens")
+    num_tiles = meta.num_tiles if meta.tile_seq is not None else meta.num_reqs
+    scratch = None
+    if num_splits > 1:
+        nbytes = T * Hq * num_splits * (D + 1) * 4
+        scratch = _get_scratch(q.device, nbytes)
+    rc = _native.lib().b200_attn_fwd_tc(
+        q.data_ptr(), q.stride(0), T, k_cache.data_ptr(), v_cache.data_ptr(), NB, BS,
+        meta.query_start_loc.data_ptr(), meta.seq_lens.data_ptr(), meta.block_table.data_ptr(),
+        meta.block_table.stride(0), _native.ptr(meta.tile_seq), _native.ptr(meta.tile_qoff),
+        num_tiles, Hq, Hkv, D, scale, int(causal), int(window), num_splits, out.data_ptr(),
+        out.stride(0), _native.ptr(scratch), rescale_threshold, v_lbo, v_sbo,
+        _native.status_word(q.device).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "attn_fwd_tc")
+    launch_counter[0] += 1 + (1 if num_splits > 1 else 0)
+    return out
+
+
+def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 block_table: torch.Tensor, seq_lens: torch.Tensor, scale: float,
+                 out: torch.Tensor, window: int = 0, num_splits: int = 1) -> torch.Tensor:
+    """CUDA-core flash-decode: one query token per sequence (q [B, Hq, D])."""
+    B, Hq, D = q.shape
+    NB, BS, Hkv, _ = k_cache.shape
+    scratch = None
+    if num_splits > 1:
+        scratch = _get_scratch(q.device, B * Hq * num_splits * (D + 1) * 4)
+    rc = _native.lib().b200_paged_decode(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), seq_lens.data_ptr(), B, Hq, Hkv, D, BS, scale, int(window),
+        num_splits, out.data_ptr(), out.stride(0), _native.ptr(scratch), NB,
+        _native.status_word(q.device).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "paged_decode")
+    launch_counter[0] += 1 + (1 if num_splits > 1 else 0)
+    return out
+
+
+def choose_num_splits(num_seqs: int, Hkv: int, max_seq_len: int, sm_count: int = 148,
+                      tile: int = 128) -> int:
+    """Split-KV factor: enough CTAs to fill the GPU, never more splits than KV tiles."""
+    ctas = max(1, num_seqs * Hkv)
+    if ctas >= 2 * sm_count:
+        return 1
+    want = (2 * sm_count + ctas - 1) // ctas
+    max_tiles = max(1, (max_seq_len + tile - 1) // tile)
+    return max(1, min(want, max_tiles, 32))
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
+                    scale: float, out: Optional[torch.Tensor] = None, causal: bool = True,
+                    window: int = 0) -> torch.Tensor:
+    """Attention of every scheduled token over its sequence's paged KV."""
+    T, Hq, D = q.shape
+    if out is None:
+        out = torch.empty((T, Hq, v_cache.shape[-1]), dtype=q.dtype, device=q.device)
+    if not _use_native(q):
+        return ref.paged_attention(q, k_cache, v_cache, meta.query_start_loc_cpu,
+                                   meta.seq_lens_cpu, meta.block_table, scale, causal, window,
+                                   out=out)
+    Hkv = k_cache.shape[2]
+    G = Hq // Hkv
+    is_decode = meta.max_query_len == 1
+    tc_ok = D in (64, 128) and 128 % G == 0 and v_cache.shape[-1] == D
+    if is_decode:
+        mode = envs.VLLM_B200_DECODE_ATTN
+        if mode == "tcgen05" and tc_ok:
+            return paged_attention_tc(q, k_cache, v_cache, meta, scale, out, causal, window,
+                                      num_splits=meta.num_splits)
+        if D in (64, 128) and G in (1, 2, 4, 8):
+            return paged_decode(q, k_cache, v_cache, meta.block_table, meta.seq_lens, scale, out,
+                                window, num_splits=meta.num_splits)
+        if tc_ok:
+            return paged_attention_tc(q, k_cache, v_cache, meta, scale, out, causal, window,
+                                      num_splits=meta.num_splits)
+    if envs.VLLM_B200_PREFILL_ATTN == "tcgen05" and tc_ok:
+        return paged_attention_tc(q, k_cache, v_cache, meta, scale, out, causal, window)
+    # explicit opt-out: PyTorch path (validation only)
+    return ref.paged_attention(q, k_cache, v_cache, meta.query_start_loc_cpu, meta.seq_lens_cpu,
+                               meta.block_table, scale, causal, window, out=out)
+
+
+# ---------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    if not logits.is_cuda or logits.dtype not in (_BF16, torch.float32):
+        return logits.argmax(dim=-1)
+    B, V = logits.shape
+    out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    rc = _native.lib().b200_argmax(logits.data_ptr(), 0 if logits.dtype == _BF16 else 1,
+                                   logits.stride(0), B, V, out.data_ptr(), _native.stream_ptr())
+    _native.check(rc, "argmax")
+    launch_counter[0] += 1
+    return out
+
+
+def to_float_logits(logits: torch.Tensor) -> torch.Tensor:
+    if logits.dtype == torch.float32:
+        return logits
+    if not (logits.is_cuda and logits.dtype == _BF16):
+        return logits.float()
+    B, V = logits.shape
+    out = torch.empty((B, V), dtype=torch.float32, device=logits.device)
+    rc = _native.lib().b200_cast_bf16_f32(logits.data_ptr(), logits.stride(0), out.data_ptr(),
+                                          out.stride(0), B, V, _native.stream_ptr())
+    _native.check(rc, "cast")
+    launch_counter[0] += 1
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, prompt_ids, output_ids, rep, freq, pres) -> torch.Tensor:
+    """fp32 logits [B, V], in place on CUDA."""
+    if not logits.is_cuda:
+        return ref.apply_penalties(logits, prompt_ids, output_ids, rep, freq, pres)
+    B, V = logits.shape
+    rc = _native.lib().b200_apply_penalties(
+        logits.data_ptr(), logits.stride(0), B, V, prompt_ids.data_ptr(), prompt_ids.shape[1],
+        output_ids.data_ptr(), output_ids.shape[1], rep.data_ptr(), freq.data_ptr(),
+        pres.data_ptr(), _native.stream_ptr())
+    _native.check(rc, "apply_penalties")
+    launch_counter[0] += 1
+    return logits
+
+
+def sample(logits_f32: torch.Tensor, temperature, top_k, top_p, min_p=None, seeds=None,
+           offsets=None, generator=None) -> torch.Tensor:
+    """Top-k/top-p/min-p + exponential-race sampling (destroys ``logits_f32`` on CUDA)."""
+    if not logits_f32.is_cuda:
+        return ref.sample(logits_f32, temperature, top_k.to(torch.int64), top_p, min_p, generator)
+    B, V = logits_f32.shape
+    out = torch.empty(B, dtype=torch.int64, device=logits_f32.device)
+    rc = _native.lib().b200_sample(
+        logits_f32.data_ptr(), logits_f32.stride(0), B, V, _native.ptr(temperature),
+        _native.ptr(top_k), _native.ptr(top_p), _native.ptr(min_p), _native.ptr(seeds),
+        _native.ptr(offsets), out.data_ptr(), _native.stream_ptr())
+    _native.check(rc, "sample")
+    launch_counter[0] += 1
+    return out
+
+
+def quant_fp8_group128(x: torch.Tensor, pow2_scale: bool = False):
+    if not _use_native(x):
+        return ref.quant_fp8_group128(x, pow2_scale)
+    T, H = x.shape
+    q = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((T, H // 128), dtype=torch.float32, device=x.device)
+    rc = _native.lib().b200_quant_fp8_group128(x.data_ptr(), q.data_ptr(), s.data_ptr(), T, H,
+                                               int(pow2_scale), _native.stream_ptr())
+    _native.check(rc, "quant_fp8_group128")
+    launch_counter[0] += 1
+    return q, s
