@@ -1,0 +1,91 @@
+"""Paged attention kernels (tcgen05 unified kernel, CUDA-core decode) vs fp32 reference."""
+import numpy as np
+import pytest
+import torch
+
+from vllm_ascend_b200 import _native, ops
+from vllm_ascend_b200.ops import reference as ref
+from gpu_utils import make_paged_case
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ref(q, kc, vc, meta, scale, causal=True, window=0):
+    return ref.paged_attention(q.float().cpu(), kc.float().cpu(), vc.float().cpu(),
+                               meta.query_start_loc_cpu, meta.seq_lens_cpu, meta.block_table.cpu(),
+                               scale, causal, window)
+
+
+def _run_tc(q, kc, vc, meta, scale, window=0, num_splits=1, thr=8.0):
+    out = torch.full_like(q, float("nan"))
+    ops.paged_attention_tc(q, kc, vc, meta, scale, out, True, window, num_splits, thr)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    return out
+
+
+CASES = [
+    # q_lens, ctx_lens, Hq, Hkv, D, block_size
+    ([128], [0], 4, 4, 128, 128),                # one tile, MHA
+    ([32], [0], 4, 1, 128, 128),                 # one packed-GQA tile
+    ([200, 77, 1024], [0, 0, 0], 8, 2, 128, 128),  # varlen causal prefill
+    ([64, 300], [500, 37], 8, 2, 128, 128),      # chunked prefill with context
+    ([1, 1, 1, 1, 1], [5, 127, 128, 700, 1300], 8, 2, 128, 128),  # decode
+    ([3, 2, 4], [100, 260, 9], 8, 2, 128, 128),  # spec-decode style short queries
+    ([150, 90], [0, 40], 4, 2, 128, 16),         # small pages (several TMA loads per tile)
+    ([150, 1], [10, 333], 4, 2, 64, 32),         # head_dim 64
+    ([96], [64], 32, 8, 128, 256),               # pages larger than a tile
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_attn_tc_matches_reference(case):
+    q_lens, ctx, Hq, Hkv, D, bs = case
+    q, kc, vc, meta = make_paged_case(q_lens, ctx, Hq, Hkv, D, bs, seed=len(q_lens))
+    scale = D ** -0.5
+    out = _run_tc(q, kc, vc, meta, scale)
+    exp = _ref(q, kc, vc, meta, scale)
+    err = (out.float().cpu() - exp).abs().max().item()
+    assert err < 2e-2, f"max abs err {err}"
+
+
+def test_attn_tc_exact_rescale_and_lazy_rescale_agree():
+    q, kc, vc, meta = make_paged_case([256, 64], [900, 0], 8, 2, 128, 128, seed=3)
+    q = q * 4        # large score spread so the running max moves a lot
+    scale = 128 ** -0.5
+    exp = _ref(q, kc, vc, meta, scale)
+    for thr in (0.0, 8.0):
+        out = _run_tc(q, kc, vc, meta, scale, thr=thr)
+        assert (out.float().cpu() - exp).abs().max().item() < 3e-2
+
+
+def test_attn_tc_split_kv_decode():
+    q, kc, vc, meta = make_paged_case([1] * 6, [40, 1000, 2047, 129, 3000, 5], 8, 2, 128, 128, seed=4)
+    scale = 128 ** -0.5
+    exp = _ref(q, kc, vc, meta, scale)
+    for ns in (2, 4, 7):
+        out = _run_tc(q, kc, vc, meta, scale, num_splits=ns)
+        assert (out.float().cpu() - exp).abs().max().item() < 2e-2
+
+
+def test_attn_tc_sliding_window():
+    q, kc, vc, meta = make_paged_case([300, 1], [200, 700], 4, 2, 128, 128, seed=5)
+    scale = 128 ** -0.5
+    out = _run_tc(q, kc, vc, meta, scale, window=160)
+    exp = _ref(q, kc, vc, meta, scale, window=160)
+    assert (out.float().cpu() - exp).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,bs", [(32, 8, 128, 128), (8, 8, 128, 16), (16, 2, 64, 32), (4, 2, 128, 256)])
+@pytest.mark.parametrize("ns", [1, 3])
+def test_cuda_core_decode(Hq, Hkv, D, bs, ns):
+    ctx = [0, 17, 128, 999, 2500]
+    q, kc, vc, meta = make_paged_case([1] * len(ctx), ctx, Hq, Hkv, D, bs, seed=7)
+    scale = D ** -0.5
+    out = torch.full_like(q, float("nan"))
+    ops.paged_decode(q, kc, vc, meta.block_table, meta.seq_lens, scale, out, 0, ns)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp = _ref(q, kc, vc, meta, scale)
+    assert (out.float().cpu() - exp).abs().max().item() < 2e-2

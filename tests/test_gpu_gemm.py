@@ -1,0 +1,61 @@
+"""tcgen05 bf16 GEMM vs fp32 matmul."""
+import pytest
+import torch
+
+from vllm_ascend_b200 import _native, ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _check(M, N, K, bn=0, bias=False, residual=False, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.5).bfloat16().to(DEV)
+    b = torch.randn(N, generator=g).bfloat16().to(DEV) if bias else None
+    r = torch.randn(M, N, generator=g).bfloat16().to(DEV) if residual else None
+    out = ops.linear(a, w, b, r, bn=bn)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp = a.float() @ w.float().t()
+    if bias:
+        exp += b.float()
+    if residual:
+        exp += r.float()
+    err = (out.float() - exp).abs().max().item()
+    tol = 0.02 * (K ** 0.5) * 0.25 + 0.05
+    assert err < tol, f"M={M} N={N} K={K} bn={bn}: max abs err {err} (tol {tol})"
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (256, 512, 4096),
+                                   (1, 256, 128), (77, 1024, 1024), (1000, 768, 2048),
+                                   (4096, 6144, 4096)])
+def test_gemm_shapes(M, N, K, bn):
+    _check(M, N, K, bn)
+
+
+def test_gemm_ragged_n_and_k_tail():
+    _check(130, 136, 72)         # N % 128 != 0, K % 64 != 0
+    _check(64, 151936 // 8 * 8 // 64 * 8, 256)
+    _check(33, 8, 8)
+
+
+def test_gemm_epilogue_bias_residual():
+    _check(300, 512, 1024, bias=True)
+    _check(300, 512, 1024, residual=True)
+    _check(300, 512, 1024, bias=True, residual=True)
+
+
+def test_gemm_auto_tile_many_waves():
+    _check(8192, 4096, 4096)
+    _check(1024, 12288, 4096)
+
+
+def test_gemm_strided_input():
+    a_full = (torch.randn(256, 2048) * 0.5).bfloat16().to(DEV)
+    a = a_full[:, 512:1536]
+    w = (torch.randn(384, 1024) * 0.5).bfloat16().to(DEV)
+    out = ops.linear(a, w)
+    exp = a.float() @ w.float().t()
+    assert (out.float() - exp).abs().max().item() < 0.5

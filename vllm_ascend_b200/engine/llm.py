@@ -62,11 +62,11 @@ class LLMEngine:
                 and pc.tensor_parallel_size > 1:
             from ..parallel import fused_linear
             fused_linear.attach(self.runner.model, cfg, self.device)
-        self.runner.warmup()
         num_blocks = self.runner.determine_num_blocks()
         if world > 1:   # every rank must agree
             num_blocks = min(pstate.get_world_group().all_gather_object(num_blocks))
         self.runner.init_kv_cache(num_blocks)
+        self.runner.warmup()
         self.kv_connector = None
         if cfg.kv_transfer_config:
             from ..distributed.kv_transfer import create_connector

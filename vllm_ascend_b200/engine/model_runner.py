@@ -85,7 +85,8 @@ class ModelRunner:
         self.graph_pool = None
         self.capture_sizes: list[int] = []
         self.stats = {"graph_replays": 0, "eager_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0,
-                      "steps": 0}
+                      "steps": 0, "graph_kernel_launches": 0}
+        self.graph_launches: dict[int, int] = {}
         self.sm_count = (torch.cuda.get_device_properties(device).multi_processor_count
                          if self.is_cuda else 1)
 
@@ -298,6 +299,7 @@ class ModelRunner:
             graph, hidden_out = self.graphs[gsize]
             graph.replay()
             self.stats["graph_replays"] += 1
+            self.stats["graph_kernel_launches"] += self.graph_launches[gsize]
             logits = self.model.compute_logits(hidden_out[:B])
         else:
             hidden = self._forward(Tp, meta)
@@ -328,6 +330,10 @@ class ModelRunner:
             self.token_ids_cpu[row, r.num_tokens] = t
             out[r.request_id] = [t]
         return out
+
+    def total_launches(self) -> int:
+        """Launches of this package's own kernels so far (eager + inside replayed graphs)."""
+        return ops.launch_counter[0] + self.stats["graph_kernel_launches"]
 
     def _cpu_generator(self) -> torch.Generator:
         g = getattr(self, "_gen", None)
@@ -403,7 +409,11 @@ class ModelRunner:
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            c0 = ops.launch_counter[0]
             with torch.cuda.graph(g, pool=self.graph_pool):
                 hidden = self._forward(Tp, meta)
+            # kernels recorded into the graph run at every replay, not at capture
+            self.graph_launches[size] = ops.launch_counter[0] - c0
+            ops.launch_counter[0] = c0
             self.graphs[size] = (g, hidden)
         torch.cuda.synchronize()
