@@ -1,0 +1,191 @@
+#!/usr/bin/env python
+"""Per-kernel micro-benchmarks with roofline fractions.
+
+    python benchmarks/kernel_bench.py gemm --m 8192 --n 4096 --k 4096
+    python benchmarks/kernel_bench.py attn-decode --batch 256 --ctx 1152
+    python benchmarks/kernel_bench.py attn-prefill --batch 8 --seq 1024
+    python benchmarks/kernel_bench.py norm --tokens 8192 --hidden 4096
+    python benchmarks/kernel_bench.py all
+
+Timing: CUDA events on the launching stream, warm-up first, a buffer larger than
+L2 is rewritten between timed iterations.  Fractions are "of measured": the
+denominators come from MEASURED_PEAKS.json at the repository root (copy bandwidth
+and cuBLAS bf16 throughput measured on this machine type); when the file is absent
+the fallback 6650 GB/s / 1590 TFLOP/s is used and marked "of fallback".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from vllm_ascend_b200 import _native, ops  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+_flush = None
+
+
+def timeit(fn, iters=20, warm=5, flush=True):
+    global _flush
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    if flush and _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(a):
+    M, N, K = a.m, a.n, a.k
+    x = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: ops.linear(x, w, out=out, bn=a.bn), a.iters)
+    ms_lib = timeit(lambda: torch.nn.functional.linear(x, w), a.iters) if a.compare else None
+    hbm, tf, tag = peaks()
+    fl = 2.0 * M * N * K
+    line = (f"gemm M={M} N={N} K={K} bn={a.bn or 'auto'}: {ms:.4f} ms  {fl / ms / 1e9:.0f} TFLOP/s "
+            f"({fl / ms / 1e9 / tf:.2f} {tag})")
+    if ms_lib:
+        line += f"  | cuBLAS {ms_lib:.4f} ms {fl / ms_lib / 1e9:.0f} TFLOP/s"
+    print(line, flush=True)
+
+
+def bench_attn_decode(a):
+    from gpu_utils import make_paged_case
+    B, ctx = a.batch, a.ctx
+    q, kc, vc, meta = make_paged_case([1] * B, [ctx - 1] * B, a.hq, a.hkv, a.d, a.block_size, seed=0)
+    out = torch.empty_like(q)
+    scale = a.d ** -0.5
+    meta.tile_seq = meta.tile_qoff = None
+    bytes_kv = 2.0 * B * ctx * a.hkv * a.d * 2
+    hbm, tf, tag = peaks()
+    for name, fn in (
+        ("cuda-core", lambda ns: ops.paged_decode(q, kc, vc, meta.block_table, meta.seq_lens, scale, out, 0, ns)),
+        ("tcgen05", lambda ns: ops.paged_attention_tc(q, kc, vc, meta, scale, out, True, 0, ns)),
+    ):
+        if a.impl not in ("both", name):
+            continue
+        ns = a.splits or ops.choose_num_splits(B, a.hkv, ctx)
+        ms = timeit(lambda: fn(ns), a.iters)
+        print(f"attn-decode[{name}] B={B} ctx={ctx} Hq={a.hq} Hkv={a.hkv} D={a.d} splits={ns}: "
+              f"{ms:.4f} ms  {bytes_kv / ms / 1e6:.0f} GB/s ({bytes_kv / ms / 1e6 / hbm:.2f} {tag})",
+              flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
+def bench_attn_prefill(a):
+    from gpu_utils import make_paged_case
+    B, S = a.batch, a.seq
+    q, kc, vc, meta = make_paged_case([S] * B, [a.ctx] * B, a.hq, a.hkv, a.d, a.block_size, seed=0)
+    out = torch.empty_like(q)
+    scale = a.d ** -0.5
+    ms = timeit(lambda: ops.paged_attention_tc(q, kc, vc, meta, scale, out, True, 0, 1), a.iters)
+    # causal: each query sees ctx + (i+1) keys
+    pairs = B * (S * a.ctx + S * (S + 1) / 2.0)
+    fl = 4.0 * pairs * a.hq * a.d
+    hbm, tf, tag = peaks()
+    print(f"attn-prefill B={B} S={S} ctx={a.ctx} Hq={a.hq} Hkv={a.hkv} D={a.d}: {ms:.4f} ms  "
+          f"{fl / ms / 1e9:.0f} TFLOP/s ({fl / ms / 1e9 / tf:.2f} {tag})", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
+def bench_norm(a):
+    T, H = a.tokens, a.hidden
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    r = torch.randn(T, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda").bfloat16()
+    out = torch.empty_like(x)
+    hbm, tf, tag = peaks()
+    ms = timeit(lambda: ops.rms_norm(x, w, 1e-6, r, out=out), a.iters)
+    by = 4.0 * T * H * 2
+    print(f"add+rmsnorm T={T} H={H}: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s ({by / ms / 1e6 / hbm:.2f} {tag})")
+    g = torch.randn(T, 2 * a.inter, device="cuda").bfloat16()
+    ms = timeit(lambda: ops.silu_and_mul(g), a.iters)
+    by = 3.0 * T * a.inter * 2
+    print(f"silu_and_mul T={T} I={a.inter}: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s ({by / ms / 1e6 / hbm:.2f} {tag})",
+          flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "norm", "all"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=1152)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--block-size", type=int, default=128)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--impl", default="both")
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--inter", type=int, default=12288)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    if a.what in ("gemm", "all"):
+        if a.what == "all":
+            a.compare = True
+            for (m, n, k) in [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 24576, 4096),
+                              (8192, 4096, 12288), (768, 6144, 4096), (768, 24576, 4096),
+                              (768, 4096, 12288), (768, 151936, 4096)]:
+                a.m, a.n, a.k = m, n, k
+                bench_gemm(a)
+        else:
+            bench_gemm(a)
+    if a.what in ("attn-decode", "all"):
+        if a.what == "all":
+            for b, c in [(768, 1152), (256, 1152), (32, 4096), (4, 32768)]:
+                a.batch, a.ctx = b, c
+                a.ctx = min(a.ctx, 8192) if b * c > 2_000_000 else a.ctx
+                bench_attn_decode(a)
+        else:
+            bench_attn_decode(a)
+    if a.what in ("attn-prefill", "all"):
+        if a.what == "all":
+            a.ctx = 0
+            for b, s in [(8, 1024), (2, 4096), (1, 8192)]:
+                a.batch, a.seq = b, s
+                bench_attn_prefill(a)
+        else:
+            a.ctx = 0 if a.ctx == 1152 else a.ctx
+            bench_attn_prefill(a)
+    if a.what in ("norm", "all"):
+        bench_norm(a)
+
+
+if __name__ == "__main__":
+    main()

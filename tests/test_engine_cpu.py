@@ -118,9 +118,15 @@ def test_chunked_prefill_and_preemption_are_transparent():
     # tiny token budget -> chunked prefill; tiny pool -> recompute preemption
     small = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=16,
                 block_size=16, num_gpu_blocks_override=14)
+    small.engine.scheduler.reserve_full = False      # over-admit so decode must preempt
     got = [o.outputs[0].token_ids for o in small.generate(prompts, sp)]
     assert got == ref
     assert small.engine.scheduler.num_preemptions > 0
+    # with whole-sequence reservation the same pool never preempts
+    calm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=16,
+               block_size=16, num_gpu_blocks_override=14)
+    assert [o.outputs[0].token_ids for o in calm.generate(prompts, sp)] == ref
+    assert calm.engine.scheduler.num_preemptions == 0
 
 
 def test_prefix_caching_reuses_blocks_and_keeps_outputs():

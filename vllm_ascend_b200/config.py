@@ -249,6 +249,7 @@ class SchedulerConfig:
     enable_chunked_prefill: bool = True
     policy: str = "fcfs"               # fcfs | short_request_first | batch_job | recompute
     async_scheduling: bool = False
+    reserve_full_sequence: bool = True   # admit only what can finish without preemption
 
 
 @dataclass

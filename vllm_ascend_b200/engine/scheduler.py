@@ -49,6 +49,11 @@ class Scheduler:
         self.finished_since_last: list[str] = []
         self.kv_connector = kv_connector
         self.step_id = 0
+        # blocks promised to admitted requests for their whole life (prompt + max_tokens);
+        # admission keeps the sum within the pool so decode never has to preempt
+        self.reserve_full = getattr(sched_cfg, "reserve_full_sequence", True)
+        self._committed_blocks = 0
+        self._commit: dict[str, int] = {}
         self._free_rows = list(range(sched_cfg.max_num_seqs - 1, -1, -1))
         self._hashes: dict[str, list[bytes]] = {}
         # stats
@@ -91,8 +96,25 @@ class Scheduler:
         else:
             self.waiting.remove(req)
 
+    def _final_blocks(self, req: Request) -> int:
+        n = min(req.num_prompt_tokens + req.sampling_params.max_tokens, self.cfg.max_model_len)
+        return (n + self.block_size - 1) // self.block_size
+
     def _can_admit(self, req: Request, num_new_blocks: int) -> bool:
-        return self.pool.can_allocate(num_new_blocks)
+        if not self.pool.can_allocate(num_new_blocks):
+            return False
+        if self.reserve_full and self.running:
+            return self._committed_blocks + self._final_blocks(req) <= self.pool.num_blocks - 1
+        return True
+
+    def _commit_blocks(self, req: Request) -> None:
+        if req.request_id not in self._commit:
+            n = self._final_blocks(req)
+            self._commit[req.request_id] = n
+            self._committed_blocks += n
+
+    def _uncommit_blocks(self, req: Request) -> None:
+        self._committed_blocks -= self._commit.pop(req.request_id, 0)
 
     def _select_preemption_victim(self) -> Optional[Request]:
         return self.running[-1] if self.running else None
@@ -110,6 +132,7 @@ class Scheduler:
         req.status = RequestStatus.PREEMPTED
         req.num_preemptions += 1
         self.num_preemptions += 1
+        self._uncommit_blocks(req)
         self._release_row(req)
         self.waiting.appendleft(req)
         out.preempted.append(req)
@@ -227,6 +250,7 @@ class Scheduler:
                 continue
             req.status = RequestStatus.RUNNING
             self.running.append(req)
+            self._commit_blocks(req)
             if n > 0:
                 prefills.append((req, n))
                 budget -= n
@@ -285,6 +309,7 @@ class Scheduler:
                 req.kv_transfer_params = params
         if not delay_free:
             self.free_blocks(req)
+        self._uncommit_blocks(req)
         self._release_row(req)
         self._hashes.pop(req.request_id, None)
         self.finished_since_last.append(req.request_id)
