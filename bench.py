@@ -283,6 +283,9 @@ def main():
             "gpu_launches": launches,
             "graph_replays": runner.stats["graph_replays"] - stats0["graph_replays"],
             "preemptions": llm.engine.scheduler.num_preemptions,
+            "host_breakdown_s": {**{k: round(v, 3) for k, v in llm.engine.host_times.items()},
+                                 **{k: round(runner.stats[k], 3) for k in ("t_prepare", "t_launch", "t_wait")},
+                                 "note": "cumulative over warm-up and timed passes"},
         }))
     if world > 1:
         dist.barrier()

@@ -90,6 +90,7 @@ def bench_attn_decode(a):
     for name, fn in (
         ("cuda-core", lambda ns: ops.paged_decode(q, kc, vc, meta.block_table, meta.seq_lens, scale, out, 0, ns)),
         ("tcgen05", lambda ns: ops.paged_attention_tc(q, kc, vc, meta, scale, out, True, 0, ns)),
+        ("tcgen05-decode", lambda ns: ops.paged_attention_decode_tc(q, kc, vc, meta, scale, out, 0, ns)),
     ):
         if a.impl not in ("both", name):
             continue

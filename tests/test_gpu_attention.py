@@ -89,3 +89,37 @@ def test_cuda_core_decode(Hq, Hkv, D, bs, ns):
     _native.check_status(torch.device(DEV))
     exp = _ref(q, kc, vc, meta, scale)
     assert (out.float().cpu() - exp).abs().max().item() < 2e-2
+
+
+DEC_CASES = [
+    # q_lens, ctx_lens, Hq, Hkv, block_size
+    ([1, 1, 1, 1, 1, 1], [0, 5, 127, 128, 700, 1300], 32, 8, 128),
+    ([1, 1, 1], [31, 1000, 257], 8, 8, 16),          # MHA, small pages
+    ([4, 2, 1, 3], [100, 260, 9, 1151], 8, 2, 128),  # spec-decode style (G=4: up to 4 tokens)
+    ([2, 1], [500, 3], 64, 8, 256),                  # G=8: up to 2 tokens
+    ([1, 1], [2000, 77], 16, 1, 128),                # G=16
+]
+
+
+@pytest.mark.parametrize("case", DEC_CASES)
+@pytest.mark.parametrize("ns", [1, 3])
+def test_attn_decode_tc(case, ns):
+    q_lens, ctx, Hq, Hkv, bs = case
+    q, kc, vc, meta = make_paged_case(q_lens, ctx, Hq, Hkv, 128, bs, seed=11)
+    scale = 128 ** -0.5
+    out = torch.full_like(q, float("nan"))
+    ops.paged_attention_decode_tc(q, kc, vc, meta, scale, out, 0, ns)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp = _ref(q, kc, vc, meta, scale)
+    assert (out.float().cpu() - exp).abs().max().item() < 2e-2
+
+
+def test_attn_decode_tc_sliding_window():
+    q, kc, vc, meta = make_paged_case([1, 2, 1], [900, 300, 40], 8, 2, 128, 128, seed=12)
+    scale = 128 ** -0.5
+    out = torch.full_like(q, float("nan"))
+    ops.paged_attention_decode_tc(q, kc, vc, meta, scale, out, 200, 1)
+    torch.cuda.synchronize()
+    exp = _ref(q, kc, vc, meta, scale, window=200)
+    assert (out.float().cpu() - exp).abs().max().item() < 2e-2

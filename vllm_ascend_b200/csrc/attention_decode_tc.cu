@@ -1,0 +1,491 @@
+// Flash-decode on tcgen05 in "keys on the M axis" form, for sequences with at most
+// 16 / G query tokens (decode and short speculative verification).
+//
+// Decode attention streams the whole KV cache once and is bound by HBM, so the
+// kernel is organised around the K/V stream instead of around query rows:
+//   S^T[128 keys, 16] = K_tile[128 keys, D] . Q^T          (A = K, K-major; B = Q, K-major)
+//   O^T[D, 16]      += V_tile^T[D, 128 keys] . P^T         (A = V, MN-major; B = P, K-major)
+// The 16 columns are the (token, head-of-group) rows that share this KV head.
+// Every softmax thread owns one key of the tile (one TMEM lane): it masks and
+// exponentiates only the valid columns, the per-column max is reduced across the
+// 128 threads, and the running row sums stay thread-local until the end.  K and V
+// pages arrive through a 3-stage TMA pipeline; accumulators live in TMEM
+// (S^T double-buffered, 16 columns each; O^T 16 columns).
+//
+// Parity: the reference's paged decode path (_npu_paged_attention,
+// vllm_ascend/attention/attention_v1.py:1555-1574) incl. split-KV partials merged
+// by log-sum-exp (npu_attention_update).  All waits are bounded.
+#include "attention.h"
+#include "common.cuh"
+
+#include <mutex>
+#include <string.h>
+#include <string>
+#include <unordered_map>
+
+namespace b200 {
+
+constexpr int DEC_THREADS = 192;
+constexpr int DEC_NQ = 16;                 // MMA N: query rows per CTA
+constexpr int DEC_HALF = 128 * 128;        // 128 keys x 64 bf16
+constexpr int DEC_QHALF = DEC_NQ * 128;    // 16 rows x 64 bf16
+
+struct DecParams {
+  const int* query_start_loc;
+  const int* seq_lens;
+  const int* block_table;
+  int max_blocks, block_size, rows_per_load;
+  int G, Hkv, Hq;
+  float scale_log2;
+  int window, num_splits;
+  __nv_bfloat16* out;
+  long out_stride;
+  float* partial_o;
+  float* partial_lse;
+  long num_blocks_total;
+  int* status;
+};
+
+template <int D>
+struct DecCfg {
+  static constexpr int NH = D / 64;
+  static constexpr int STAGES = 3;
+  static constexpr int TILE_BYTES = NH * DEC_HALF;
+  static constexpr int Q_BYTES = NH * DEC_QHALF;
+  static constexpr int P_BYTES = 2 * DEC_QHALF;
+  static constexpr int SMEM_BYTES = 2 * STAGES * TILE_BYTES + Q_BYTES + P_BYTES + 1024 + 1024;
+  static constexpr int TMEM_COLS = 64;
+  static constexpr int O_COL = 32;
+};
+
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                      const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const DecParams p) {
+  using Cfg = DecCfg<D>;
+  constexpr int NH = Cfg::NH, ST = Cfg::STAGES;
+
+  const int seq = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  const int q_start = p.query_start_loc[seq];
+  const int q_len = p.query_start_loc[seq + 1] - q_start;
+  const int seq_len = p.seq_lens[seq];
+  const int ctx = seq_len - q_len;
+  const int G = p.G;
+  const int nv = q_len * G;                 // valid columns (<= 16)
+  if (q_len <= 0) return;
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, ctx - p.window + 1);
+  const int tile_lo = kv_lo >> 7, tile_hi = (seq_len + 127) >> 7;
+  const int n_all = tile_hi - tile_lo;
+  const int per_split = (n_all + p.num_splits - 1) / p.num_splits;
+  const int t0 = tile_lo + split * per_split;
+  const int t1 = min(tile_hi, t0 + per_split);
+  const int n = t1 - t0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (n <= 0) {
+    if (p.num_splits > 1) {
+      for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+        const long pidx =
+            ((long)(q_start + c / G) * p.Hq + (h * G + c % G)) * p.num_splits + split;
+        p.partial_lse[pidx] = -INFINITY;
+        for (int d = 0; d < D; d++) p.partial_o[pidx * D + d] = 0.f;
+      }
+    }
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* Ks = smem;
+  uint8_t* Vs = Ks + ST * Cfg::TILE_BYTES;
+  uint8_t* Qs = Vs + ST * Cfg::TILE_BYTES;
+  uint8_t* Ps = Qs + Cfg::Q_BYTES;
+  uint64_t* bars = (uint64_t*)(Ps + Cfg::P_BYTES);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* k_full = bars + 1;        // ST
+  uint64_t* k_empty = k_full + ST;    // ST
+  uint64_t* v_full = k_empty + ST;    // ST
+  uint64_t* v_empty = v_full + ST;    // ST
+  uint64_t* s_ready = v_empty + ST;   // 2
+  uint64_t* s_free = s_ready + 2;     // 2
+  uint64_t* p_ready = s_free + 2;     // 1
+  uint64_t* pv_done = p_ready + 1;    // 1
+  uint32_t* tmem_ptr = (uint32_t*)(pv_done + 1);
+  volatile int* abort_word = (volatile int*)(tmem_ptr + 1);
+  float* red = (float*)(tmem_ptr + 2);            // [4 warps][16]
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < ST; s++) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(&s_ready[b], 1);
+      mbar_init(&s_free[b], 4);
+    }
+    mbar_init(p_ready, 4);
+    mbar_init(pv_done, 1);
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    const int* bt = p.block_table + (long)seq * p.max_blocks;
+    const int rpl = p.rows_per_load;
+    const int parts = 128 / rpl;
+    if (lane == 0) {
+      mbar_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+      for (int hf = 0; hf < NH; hf++)
+        tma_load_4d(Qs + hf * DEC_QHALF, &tmap_q, q_full, hf * 64, 0, h, q_start);
+    }
+    for (int j = 0; j < n; j++) {
+      const int st = j % ST;
+      const uint32_t ph = (uint32_t)(j / ST) & 1u;
+      const int key_base = (t0 + j) << 7;
+#pragma unroll 1
+      for (int kv = 0; kv < 2; kv++) {
+        uint64_t* fullb = kv == 0 ? &k_full[st] : &v_full[st];
+        uint64_t* emptyb = kv == 0 ? &k_empty[st] : &v_empty[st];
+        if (!mbar_wait(emptyb, ph ^ 1u, abort_word)) goto done;
+        if (lane == 0) {
+          uint8_t* dst = (kv == 0 ? Ks : Vs) + st * Cfg::TILE_BYTES;
+          const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
+          mbar_expect_tx(fullb, Cfg::TILE_BYTES);
+          for (int part = 0; part < parts; part++) {
+            const int key0 = key_base + part * rpl;
+            const int kc = min(key0, seq_len - 1);
+            int blk = bt[kc / p.block_size];
+            if (blk < 0 || blk >= p.num_blocks_total) {
+              *abort_word = B200_BAD_INDEX;
+              blk = 0;
+            }
+            const int off = key0 % p.block_size;
+#pragma unroll
+            for (int hf = 0; hf < NH; hf++)
+              tma_load_4d(dst + hf * DEC_HALF + part * rpl * 128, tm, fullb, hf * 64, h, off, blk);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_s = make_idesc_f16(128, DEC_NQ, true, false, false);
+    constexpr uint32_t idesc_o = make_idesc_f16(D, DEC_NQ, true, true, false);   // A = V, MN-major
+    const uint32_t q_addr = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
+                   p_addr = smem_u32(Ps);
+    if (!mbar_wait(q_full, 0, abort_word)) goto done;
+    auto issue_s = [&](int j) -> bool {
+      const int st = j % ST;
+      const uint32_t ph = (uint32_t)(j / ST) & 1u;
+      const int b = j & 1;
+      if (!mbar_wait(&k_full[st], ph, abort_word)) return false;
+      if (!mbar_wait(&s_free[b], (((uint32_t)j >> 1) & 1u) ^ 1u, abort_word)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; kk++) {
+          const uint64_t da = make_smem_desc(
+              k_addr + st * Cfg::TILE_BYTES + (kk >> 2) * DEC_HALF + (kk & 3) * 32, 16, 1024,
+              kLayoutSw128);
+          const uint64_t db = make_smem_desc(q_addr + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16,
+                                             1024, kLayoutSw128);
+          umma_f16_ss(tmem_base + b * DEC_NQ, da, db, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_ready[b]);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (!issue_s(0)) goto done;
+    for (int j = 0; j < n; j++) {
+      if (j + 1 < n) {
+        if (!issue_s(j + 1)) goto done;
+      }
+      const int st = j % ST;
+      const uint32_t ph = (uint32_t)(j / ST) & 1u;
+      if (!mbar_wait(&v_full[st], ph, abort_word)) goto done;
+      if (!mbar_wait(p_ready, (uint32_t)j & 1u, abort_word)) goto done;
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {
+          // A: 16 keys of V^T (two 64-wide d atoms DEC_HALF apart, 8-key groups 1024 B apart)
+          const uint64_t da = make_smem_desc(v_addr + st * Cfg::TILE_BYTES + kk * 2048, DEC_HALF,
+                                             1024, kLayoutSw128);
+          const uint64_t db = make_smem_desc(p_addr + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16,
+                                             1024, kLayoutSw128);
+          umma_f16_ss(tmem_base + Cfg::O_COL, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(pv_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------ softmax / epilogue
+    const int qd = warp & 3;
+    const int tid = qd * 32 + lane;                 // key inside the tile; d index for O^T
+    const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl2 = p.scale_log2;
+    float m[DEC_NQ], lsum[DEC_NQ];
+#pragma unroll
+    for (int c = 0; c < DEC_NQ; c++) { m[c] = -INFINITY; lsum[c] = 0.f; }
+
+    for (int j = 0; j < n; j++) {
+      const int b = j & 1;
+      if (!mbar_wait(&s_ready[b], ((uint32_t)j >> 1) & 1u, abort_word)) goto done;
+      tc_fence_after();
+      uint32_t r[16];
+      tmem_ld_32x32b_x16(t_lane + b * DEC_NQ, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[b]);
+      const int key = ((t0 + j) << 7) + tid;
+      float s[DEC_NQ];
+      float wmax[DEC_NQ];
+#pragma unroll
+      for (int c = 0; c < DEC_NQ; c++) {
+        if (c < nv) {
+          const int q_pos = ctx + c / G;
+          const bool ok = key < seq_len && key <= q_pos && (p.window <= 0 || key > q_pos - p.window);
+          s[c] = ok ? __uint_as_float(r[c]) : -INFINITY;
+          wmax[c] = warp_reduce_max(s[c]);
+        }
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int c = 0; c < DEC_NQ; c++)
+          if (c < nv) red[qd * DEC_NQ + c] = wmax[c];
+      }
+      softmax_bar();
+      bool any_change = false;
+      float alpha[DEC_NQ];
+#pragma unroll
+      for (int c = 0; c < DEC_NQ; c++) {
+        alpha[c] = 1.f;
+        if (c < nv) {
+          const float tm = fmaxf(fmaxf(red[c], red[DEC_NQ + c]),
+                                 fmaxf(red[2 * DEC_NQ + c], red[3 * DEC_NQ + c]));
+          const float mn = fmaxf(m[c], tm);
+          if (mn > m[c]) {
+            alpha[c] = (m[c] == -INFINITY) ? 0.f : exp2f((m[c] - mn) * sl2);
+            any_change = true;
+            m[c] = mn;
+          }
+          lsum[c] *= alpha[c];
+        }
+      }
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_word)) goto done;
+        tc_fence_after();
+        if (any_change) {           // uniform over the 128 threads
+          uint32_t o[16];
+          tmem_ld_32x32b_x16(t_lane + Cfg::O_COL, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < DEC_NQ; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c]);
+          tmem_st_32x32b_x16(t_lane + Cfg::O_COL, o);
+          tmem_st_wait();
+        }
+      }
+      // probabilities of this key for every valid column -> P[c][key] (K-major, swizzled)
+      uint8_t* pbase = Ps + (tid >> 6) * DEC_QHALF;
+      const int kin = tid & 63;
+#pragma unroll
+      for (int c = 0; c < DEC_NQ; c++) {
+        if (c < nv) {
+          const float mb = (m[c] == -INFINITY) ? 0.f : m[c] * sl2;
+          const float pv = exp2f(s[c] * sl2 - mb);
+          lsum[c] += pv;
+          const int chunk = (kin >> 3) ^ (c & 7);
+          *reinterpret_cast<__nv_bfloat16*>(pbase + c * 128 + (chunk << 4) + (kin & 7) * 2) =
+              __float2bfloat16(pv);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      softmax_bar();            // all red[] reads done before the next tile overwrites it
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    // ---- epilogue: total row sums, normalise, store
+    if (!mbar_wait(pv_done, (uint32_t)(n - 1) & 1u, abort_word)) goto done;
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < DEC_NQ; c++) {
+      if (c < nv) {
+        const float w = warp_reduce_sum(lsum[c]);
+        if (lane == 0) red[qd * DEC_NQ + c] = w;
+      }
+    }
+    softmax_bar();
+    uint32_t o[16];
+    tmem_ld_32x32b_x16(t_lane + Cfg::O_COL, o);
+    tmem_ld_wait();
+    if (tid < D) {
+#pragma unroll
+      for (int c = 0; c < DEC_NQ; c++) {
+        if (c < nv) {
+          const float l = red[c] + red[DEC_NQ + c] + red[2 * DEC_NQ + c] + red[3 * DEC_NQ + c];
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          const long tok = q_start + c / G;
+          const int hq = h * G + c % G;
+          const float val = __uint_as_float(o[c]) * inv;
+          if (p.num_splits == 1) {
+            p.out[tok * p.out_stride + (long)hq * D + tid] = __float2bfloat16(val);
+          } else {
+            const long pidx = (tok * p.Hq + hq) * p.num_splits + split;
+            p.partial_o[pidx * D + tid] = val;
+            if (tid == 0)
+              p.partial_lse[pidx] =
+                  (l > 0.f) ? (m[c] * sl2 * 0.6931471805599453f + logf(l)) : -INFINITY;
+          }
+        }
+      }
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    const uint64_t t_start = globaltimer_ns();
+    while (globaltimer_ns() - t_start < 50000ull) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, *abort_word);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host
+struct DecTmapCache {
+  std::unordered_map<std::string, CUtensorMap> map;
+  std::mutex mu;
+  int get(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+          const uint64_t* strides, const uint32_t* box) {
+    char key[128];
+    memset(key, 0, sizeof(key));
+    memcpy(key, &base, 8);
+    memcpy(key + 8, dims, 8 * rank);
+    memcpy(key + 48, strides, 8 * (rank - 1));
+    memcpy(key + 88, box, 4 * rank);
+    std::string k(key, 120);
+    std::lock_guard<std::mutex> g(mu);
+    auto it = map.find(k);
+    if (it != map.end()) {
+      *out = it->second;
+      return 0;
+    }
+    int rc = make_tmap(out, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, dims, strides, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    if (map.size() > 4096) map.clear();
+    map.emplace(k, *out);
+    return 0;
+  }
+};
+static DecTmapCache g_dec_tmaps;
+
+}  // namespace b200
+
+// Decode / short-query attention: every sequence has q_len <= 16 / (Hq/Hkv) query
+// tokens (query_start_loc gives their positions in q).  Arguments as b200_attn_fwd_tc;
+// scratch needs b200_attn_scratch_bytes(T, Hq, D, num_splits) bytes when num_splits > 1.
+B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const void* k_cache,
+                                 const void* v_cache, long num_blocks, int block_size,
+                                 const void* query_start_loc, const void* seq_lens,
+                                 const void* block_table, int max_blocks, int num_seqs, int Hq,
+                                 int Hkv, int D, float scale, int window, int num_splits,
+                                 void* out, long out_stride, void* scratch, int* status,
+                                 cudaStream_t stream) {
+  using namespace b200;
+  if (num_seqs <= 0 || T <= 0) return 0;
+  const int G = Hq / Hkv;
+  if (G * Hkv != Hq || G > DEC_NQ || (DEC_NQ % G) != 0) return 9120;
+  if (D != 128) return 9121;
+  if (block_size < 8 || (block_size < 128 && (128 % block_size) != 0) ||
+      (block_size > 128 && (block_size % 128) != 0))
+    return 9122;
+  if ((q_stride & 7) || (out_stride & 7)) return 9123;
+  if (num_splits < 1) num_splits = 1;
+  if (num_splits > 1 && !scratch) return 9124;
+  const int rpl = block_size < 128 ? block_size : 128;
+  CUtensorMap tq, tk, tv;
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)G, (uint64_t)Hkv, (uint64_t)T};
+    uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)G * D * 2, (uint64_t)q_stride * 2};
+    uint32_t box[4] = {64, (uint32_t)G, 1, (uint32_t)(DEC_NQ / G)};
+    int rc = g_dec_tmaps.get(&tq, q, 4, dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)block_size, (uint64_t)num_blocks};
+    uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2,
+                       (uint64_t)block_size * Hkv * D * 2};
+    uint32_t box[4] = {64, 1, (uint32_t)rpl, 1};
+    int rc = g_dec_tmaps.get(&tk, k_cache, 4, dims, str, box);
+    if (rc) return rc;
+    rc = g_dec_tmaps.get(&tv, v_cache, 4, dims, str, box);
+    if (rc) return rc;
+  }
+  DecParams p;
+  p.query_start_loc = (const int*)query_start_loc;
+  p.seq_lens = (const int*)seq_lens;
+  p.block_table = (const int*)block_table;
+  p.max_blocks = max_blocks;
+  p.block_size = block_size;
+  p.rows_per_load = rpl;
+  p.G = G; p.Hkv = Hkv; p.Hq = Hq;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
+  p.num_splits = num_splits;
+  p.out = (__nv_bfloat16*)out;
+  p.out_stride = out_stride;
+  p.partial_o = (float*)scratch;
+  p.partial_lse = scratch ? (float*)scratch + T * Hq * (long)num_splits * D : nullptr;
+  p.num_blocks_total = num_blocks;
+  p.status = status;
+  using Cfg = DecCfg<128>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<128>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((unsigned)num_seqs, (unsigned)Hkv, (unsigned)num_splits);
+  attn_decode_tc_kernel<128><<<grid, DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  int rc = B200_CHECK_LAUNCH();
+  if (rc) return rc;
+  if (num_splits > 1)
+    return launch_merge_splits(p.partial_o, p.partial_lse, T, Hq, num_splits, D, out,
+                               out_stride, stream);
+  return 0;
+}

@@ -1,15 +1,28 @@
-// bf16 GEMM for sm_100a:  C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ residual[M,N])
+// bf16 GEMM family for sm_100a:  C[M,N] = A[M,K] * W[N,K]^T  with fused variants.
 //
-// Both operands are K-major (row-major activations, nn.Linear weights), which
-// is the layout every linear layer of the decoder uses (parity with the
-// reference's unquantized GEMM custom op, vllm_ascend/ops/linear.py:53-110).
+// Both operands are K-major (row-major activations, nn.Linear weights) — the
+// layout of every linear layer of the decoder (parity: the reference's
+// unquantized GEMM op, vllm_ascend/ops/linear.py:53-110, and its communication-
+// fused linear ops, vllm_ascend/ops/linear_op.py:152-273).
 //
-// Structure: persistent CTAs (one per SM), warp-specialised:
+// One persistent, warp-specialised kernel (one CTA per SM):
 //   warp 0      TMA producer: 128x64 A tile + BNx64 W tile per stage, 128B swizzle
 //   warp 1      MMA issuer: tcgen05.mma cta_group::1, M=128, N=BN, K=16, f32 accum in TMEM
-//   warps 2..5  epilogue: tcgen05.ld 32x32b -> bf16 -> 16-byte global stores
+//   warps 2..5  epilogue: tcgen05.ld 32x32b -> bf16 -> 16-byte stores
 // Two TMEM accumulator buffers let the epilogue of tile i overlap the main
-// loop of tile i+1.  All waits are bounded (see common.cuh).
+// loop of tile i+1.  Mode bits select the fused behaviour:
+//   AG     all-gather -> GEMM: rows of A are pushed into this GPU's memory by its
+//          peers; the producer waits for the source rank's epoch flag before
+//          loading a tile and starts with the locally produced rows.
+//   RS     GEMM -> reduce-scatter: the epilogue stores each bf16 partial row
+//          straight into the owning rank's staging buffer over NVLink (peer
+//          pointers), and the last CTA publishes this rank's epoch flag.
+//   SWIGLU W holds [gate; up]; the tile pairs 128 gate with 128 up columns and the
+//          epilogue writes silu(gate) * up.
+//   GROUPED rows of A are grouped by expert (prefix offsets on the device) and
+//          each group multiplies its own weight matrix (MoE grouped GEMM).
+// All waits are bounded (see common.cuh / comm.cuh).
+#include "comm.cuh"
 #include "common.cuh"
 
 #include <mutex>
@@ -20,6 +33,9 @@ namespace b200 {
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_MAX_GROUPS = 512;
+
+enum : int { GEMM_AG = 1, GEMM_RS = 2, GEMM_SWIGLU = 4, GEMM_GROUPED = 8 };
 
 template <int BN>
 struct GemmCfg {
@@ -28,24 +44,85 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * GEMM_BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // 256 or 512 (power of two)
-  // tiles + barriers + tmem pointer + abort word, plus 1 KB alignment slack
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  // tiles + barriers + tmem pointer + abort word + group table, plus alignment slack
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + 1024 + 256 + (GEMM_MAX_GROUPS + 1) * 4;
 };
 
 struct GemmParams {
-  int M, N, K;
+  int M, N, K;         // N = output columns (after SwiGLU pairing: columns of the product / 2)
   int ldc;             // row stride of C (elements)
   const __nv_bfloat16* bias;      // [N] or null
   const __nv_bfloat16* residual;  // [M, ldc] or null
   __nv_bfloat16* C;
   int* status;         // device status word (may be null)
   int tiles_m, tiles_n;
+  int mode;
+  // ---- AG
+  const uint32_t* ag_flags;   // local CommCtl.ag_flag
+  const uint32_t* ag_epoch;   // local CommCtl.ag_epoch (epoch to wait for)
+  int rows_per_src;
+  int my_rank, num_ranks;
+  // ---- RS
+  __nv_bfloat16* rs_dst[kMaxRanks];   // staging on owner o: [num_ranks][rows_per_owner][N]
+  uint32_t* rs_flag_dst[kMaxRanks];   // &ctl(o)->rs_flag[my_rank]
+  CommCtl* ctl;
+  int rows_per_owner;
+  // ---- SWIGLU
+  int up_row_offset;          // row of W where the "up" half starts (I), per group
+  // ---- GROUPED
+  const int* group_offsets;   // [num_groups + 1] row offsets into A / C
+  int num_groups;
+  int w_rows_per_group;       // rows of W per group
 };
+
+struct TileCoord {
+  int row0;      // first row of the tile in A / C
+  int row_end;   // rows >= row_end are not stored
+  int tn;        // N tile index
+  int w_row0;    // first row of W for the (gate) part of the tile
+};
+
+template <int BN>
+__device__ __forceinline__ bool tile_coord(const GemmParams& p, const int* grp_tiles, int t,
+                                           TileCoord& c) {
+  constexpr int BN_OUT = BN;  // columns of W consumed per tile
+  if (p.mode & GEMM_GROUPED) {
+    // grp_tiles[e] = first tile (in units of M tiles) of group e
+    int lo = 0, hi = p.num_groups;
+    const int tm_global = t % grp_tiles[p.num_groups];
+    const int tn = t / grp_tiles[p.num_groups];
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (grp_tiles[mid] <= tm_global) lo = mid; else hi = mid;
+    }
+    const int e = lo;
+    const int g0 = p.group_offsets[e], g1 = p.group_offsets[e + 1];
+    c.row0 = g0 + (tm_global - grp_tiles[e]) * GEMM_BM;
+    c.row_end = g1;
+    c.tn = tn;
+    const int ncols = (p.mode & GEMM_SWIGLU) ? BN_OUT / 2 : BN_OUT;
+    c.w_row0 = e * p.w_rows_per_group + tn * ncols;
+    return true;
+  }
+  int tm = t % p.tiles_m;
+  const int tn = t / p.tiles_m;
+  if (p.mode & GEMM_AG) {
+    const int rot = (p.my_rank * p.rows_per_src) / GEMM_BM;
+    tm = (tm + rot) % p.tiles_m;
+  }
+  c.row0 = tm * GEMM_BM;
+  c.row_end = p.M;
+  c.tn = tn;
+  const int ncols = (p.mode & GEMM_SWIGLU) ? BN_OUT / 2 : BN_OUT;
+  c.w_row0 = tn * ncols;
+  return true;
+}
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -56,11 +133,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* tmem_empty = tmem_full + 2;             // [2]
   uint32_t* tmem_ptr = (uint32_t*)(tmem_empty + 2);
   volatile int* abort_word = (volatile int*)(tmem_ptr + 1);
+  int* grp_tiles = (int*)(tmem_ptr + 2);            // [num_groups + 1] (GROUPED only)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const bool swiglu = (p.mode & GEMM_SWIGLU) != 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; s++) {
@@ -73,6 +151,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     *abort_word = 0;
     mbar_fence_init();
+    if (p.mode & GEMM_GROUPED) {
+      int acc = 0;
+      for (int e = 0; e < p.num_groups; e++) {
+        grp_tiles[e] = acc;
+        const int cnt = p.group_offsets[e + 1] - p.group_offsets[e];
+        acc += (cnt + GEMM_BM - 1) / GEMM_BM;
+      }
+      grp_tiles[p.num_groups] = acc;
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr, Cfg::kTmemCols);
@@ -86,23 +173,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
+  const int num_tiles = (p.mode & GEMM_GROUPED) ? grp_tiles[p.num_groups] * p.tiles_n
+                                                : p.tiles_m * p.tiles_n;
 
-  // Tile order: consecutive CTAs take consecutive M tiles of the same N tile so
-  // the W tile is shared through L2.
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     int stage = 0;
     uint32_t phase = 0;
+    uint32_t ag_epoch = 0;
+    if (p.mode & GEMM_AG) ag_epoch = *((volatile const uint32_t*)p.ag_epoch);
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      TileCoord c;
+      tile_coord<BN>(p, grp_tiles, t, c);
+      if (p.mode & GEMM_AG) {
+        // rows of this tile come from source ranks s0..s1: wait for their pushes
+        if (lane == 0) {
+          const int last_row = min(c.row0 + GEMM_BM, p.M) - 1;
+          const int s0 = c.row0 / p.rows_per_src, s1 = last_row / p.rows_per_src;
+          for (int s = s0; s <= s1; s++) {
+            if (s == p.my_rank) continue;
+            if (!wait_flag_ge(&p.ag_flags[s], ag_epoch, p.status)) *abort_word = B200_TIMEOUT;
+          }
+          fence_proxy_async_global();
+        }
+        __syncwarp();
+        if (*abort_word) goto done;
+      }
       for (int kb = 0; kb < num_kb; kb++) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) goto done;
         if (lane == 0) {
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * GEMM_BK, tm * GEMM_BM);
-          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * GEMM_BK, tn * BN);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * GEMM_BK, c.row0);
+          if (swiglu) {
+            // 128 gate rows then 128 up rows (the W tensor map has a 128-row box)
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * GEMM_BK, c.w_row0);
+            tma_load_2d(sb + Cfg::kBBytes / 2, &tmap_b, &full_bar[stage], kb * GEMM_BK,
+                        c.w_row0 + p.up_row_offset);
+          } else {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * GEMM_BK, c.w_row0);
+          }
         }
         __syncwarp();
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
@@ -142,25 +253,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    constexpr int OUT_COLS = BN;             // accumulator columns per tile
+    const int out_per_tile = swiglu ? OUT_COLS / 2 : OUT_COLS;
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, it++) {
-      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      TileCoord c;
+      tile_coord<BN>(p, grp_tiles, t, c);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_word)) goto done;
       tc_fence_after();
-      const int row = tm * GEMM_BM + q * 32 + lane;
+      const int row = c.row0 + q * 32 + lane;
+      const bool row_ok = row < c.row_end;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      __nv_bfloat16* crow = p.C + (size_t)row * p.ldc;
+      __nv_bfloat16* crow;
+      if (p.mode & GEMM_RS) {
+        const int owner = row_ok ? row / p.rows_per_owner : 0;
+        const int local = row - owner * p.rows_per_owner;
+        crow = p.rs_dst[owner] + ((size_t)p.my_rank * p.rows_per_owner + local) * p.ldc;
+      } else {
+        crow = p.C + (size_t)row * p.ldc;
+      }
       const __nv_bfloat16* rrow = p.residual ? p.residual + (size_t)row * p.ldc : nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = tn * BN + c0;
+      for (int c0 = 0; c0 < out_per_tile; c0 += 32) {
+        const int col0 = c.tn * out_per_tile + c0;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (row < p.M) {
+        if (swiglu) {
+          uint32_t u[32];
+          tmem_ld_32x32b_x32(t_row + OUT_COLS / 2 + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const float g = __uint_as_float(r[j]);
+            r[j] = __float_as_uint(g / (1.f + __expf(-g)) * __uint_as_float(u[j]));
+          }
+        } else {
+          tmem_ld_wait();
+        }
+        if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; g++) {
             const int col = col0 + g * 8;
@@ -202,11 +335,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
+    if (p.mode & GEMM_RS) __threadfence_system();   // partial rows visible to their owners
   }
 done:
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_word != 0 && p.status) atomicExch(p.status, *abort_word);
+  if (*abort_word != 0) {
+    const uint64_t t_start = globaltimer_ns();
+    while (globaltimer_ns() - t_start < 50000ull) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, *abort_word);
+    __syncthreads();
+  } else if ((p.mode & GEMM_RS) && threadIdx.x == 0) {
+    // last CTA of the grid publishes this rank's reduce-scatter epoch to every owner
+    const uint32_t prev = atomicAdd(&p.ctl->done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      const uint32_t epoch = p.ctl->rs_epoch + 1;
+      for (int o = 0; o < p.num_ranks; o++) st_release_sys(p.rs_flag_dst[o], epoch);
+      p.ctl->rs_epoch = epoch;
+      p.ctl->done_ctr = 0;
+      __threadfence();
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -259,9 +409,8 @@ static int get_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, ui
 }
 
 template <int BN>
-static int launch_gemm(const void* A, const void* W, void* C, const void* bias,
-                       const void* residual, int M, int N, int K, int lda, int ldw, int ldc,
-                       int* status, int max_ctas, cudaStream_t stream) {
+static int launch_gemm(const void* A, const void* W, GemmParams& p, int lda, int ldw,
+                       long a_rows, long w_rows, int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -272,27 +421,41 @@ static int launch_gemm(const void* A, const void* W, void* C, const void* bias,
     attr_set = true;
   }
   CUtensorMap ta, tb;
-  int rc = get_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GEMM_BM);
+  int rc = get_tmap_2d_bf16(&ta, A, (uint64_t)a_rows, (uint64_t)p.K, (uint64_t)lda, GEMM_BM);
   if (rc) return rc;
-  rc = get_tmap_2d_bf16(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN);
+  const uint32_t b_box = (p.mode & GEMM_SWIGLU) ? BN / 2 : BN;
+  rc = get_tmap_2d_bf16(&tb, W, (uint64_t)w_rows, (uint64_t)p.K, (uint64_t)ldw, b_box);
   if (rc) return rc;
-  GemmParams p;
-  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
-  p.bias = (const __nv_bfloat16*)bias;
-  p.residual = (const __nv_bfloat16*)residual;
-  p.C = (__nv_bfloat16*)C;
-  p.status = status;
-  p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
-  p.tiles_n = (N + BN - 1) / BN;
-  int grid = p.tiles_m * p.tiles_n;
+  const int out_per_tile = (p.mode & GEMM_SWIGLU) ? BN / 2 : BN;
+  p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (p.N + out_per_tile - 1) / out_per_tile;
   int sms = num_sms();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  if (grid > sms) grid = sms;
+  int grid;
+  if (p.mode & GEMM_GROUPED) {
+    grid = sms;   // tile count is only known on the device
+  } else {
+    grid = p.tiles_m * p.tiles_n;
+    if (grid > sms) grid = sms;
+  }
   gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   return B200_CHECK_LAUNCH();
 }
 
+static int pick_bn(int M, int N, int bn) {
+  if (bn == 128 || bn == 256) return bn;
+  // 256-wide tiles halve A re-reads; use them when they still fill the GPU.
+  const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
+  bn = (N >= 256 && tiles256 >= num_sms()) ? 256 : 128;
+  if (N % 256 != 0 && N % 128 == 0) bn = 128;
+  return bn;
+}
+
+static void init_params(GemmParams& p) { memset(&p, 0, sizeof(p)); }
+
 }  // namespace b200
+
+using namespace b200;
 
 // C[M,N] (row stride ldc) = A[M,K] (row stride lda) * W[N,K]^T (row stride ldw)
 // (+bias[N]) (+residual[M,N] with row stride ldc).  Requirements: K, N, lda,
@@ -303,15 +466,113 @@ B200_API int b200_gemm_bf16(const void* A, const void* W, void* C, const void* b
                             int ldc, int bn, int* status, int max_ctas, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
-  if (bn == 0) {
-    // 256-wide tiles halve A re-reads; use them when they still fill the GPU.
-    const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
-    bn = (N >= 256 && tiles256 >= b200::num_sms()) ? 256 : 128;
-    if (N % 256 != 0 && N % 128 == 0) bn = 128;
+  GemmParams p;
+  init_params(p);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  if (pick_bn(M, N, bn) == 256) return launch_gemm<256>(A, W, p, lda, ldw, M, N, max_ctas, stream);
+  return launch_gemm<128>(A, W, p, lda, ldw, M, N, max_ctas, stream);
+}
+
+// out[M, I] = silu(A W_gate^T) * (A W_up^T) with W = [gate (I rows); up (I rows)] of row
+// stride ldw.  I must be a multiple of 128.
+B200_API int b200_gemm_swiglu_bf16(const void* A, const void* W, void* out, int M, int I, int K,
+                                   int lda, int ldw, int ldo, int* status,
+                                   cudaStream_t stream) {
+  if (M <= 0 || I <= 0) return 0;
+  if ((K & 7) || (I % 128) || (lda & 7) || (ldw & 7) || (ldo & 7)) return 9100;
+  GemmParams p;
+  init_params(p);
+  p.M = M; p.N = I; p.K = K; p.ldc = ldo;
+  p.C = (__nv_bfloat16*)out;
+  p.status = status;
+  p.mode = GEMM_SWIGLU;
+  p.up_row_offset = I;
+  return launch_gemm<256>(A, W, p, lda, ldw, M, 2L * I, 0, stream);
+}
+
+// All-gather -> GEMM.  A [M, K] lives in this rank's gather buffer; rows
+// [s*rows_per_src, (s+1)*rows_per_src) are pushed by rank s, which then raises
+// ctl->ag_flag[s] to the current epoch (ctl->ag_epoch).
+B200_API int b200_gemm_ag_bf16(const void* A, const void* W, void* C, const void* bias, int M,
+                               int N, int K, int lda, int ldw, int ldc, void* ctl, int my_rank,
+                               int num_ranks, int rows_per_src, int bn, int* status,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
+  if (num_ranks > kMaxRanks || rows_per_src <= 0) return 9130;
+  GemmParams p;
+  init_params(p);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.mode = GEMM_AG;
+  CommCtl* c = (CommCtl*)ctl;
+  p.ag_flags = c->ag_flag;
+  p.ag_epoch = &c->ag_epoch;
+  p.ctl = c;
+  p.rows_per_src = rows_per_src;
+  p.my_rank = my_rank;
+  p.num_ranks = num_ranks;
+  if (pick_bn(M, N, bn) == 256) return launch_gemm<256>(A, W, p, lda, ldw, M, N, 0, stream);
+  return launch_gemm<128>(A, W, p, lda, ldw, M, N, 0, stream);
+}
+
+// GEMM -> reduce-scatter.  Row r of the bf16 partial product goes to rank
+// o = r / rows_per_owner, at rs_staging[o][my_rank][r % rows_per_owner][0..N).
+// rs_staging / peer_ctl: host arrays of num_ranks device pointers (peer-mapped).
+B200_API int b200_gemm_rs_bf16(const void* A, const void* W, const void* bias, int M, int N,
+                               int K, int lda, int ldw, void* const* rs_staging,
+                               void* const* peer_ctl, int my_rank, int num_ranks,
+                               int rows_per_owner, int bn, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7)) return 9100;
+  if (num_ranks > kMaxRanks || rows_per_owner * num_ranks < M) return 9130;
+  GemmParams p;
+  init_params(p);
+  p.M = M; p.N = N; p.K = K; p.ldc = N;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.status = status;
+  p.mode = GEMM_RS;
+  p.my_rank = my_rank;
+  p.num_ranks = num_ranks;
+  p.rows_per_owner = rows_per_owner;
+  for (int o = 0; o < num_ranks; o++) {
+    p.rs_dst[o] = (__nv_bfloat16*)rs_staging[o];
+    p.rs_flag_dst[o] = &((CommCtl*)peer_ctl[o])->rs_flag[my_rank];
   }
-  if (bn == 256)
-    return b200::launch_gemm<256>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, status,
-                                  max_ctas, stream);
-  return b200::launch_gemm<128>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, status,
-                                max_ctas, stream);
+  p.ctl = (CommCtl*)peer_ctl[my_rank];
+  if (pick_bn(M, N, bn) == 256) return launch_gemm<256>(A, W, p, lda, ldw, M, N, 0, stream);
+  return launch_gemm<128>(A, W, p, lda, ldw, M, N, 0, stream);
+}
+
+// Grouped GEMM (MoE): rows [offsets[e], offsets[e+1]) of A multiply W[e] ([n_per_group, K]);
+// with swiglu != 0, W[e] = [gate (I); up (I)] and C has I columns.  total_rows bounds the
+// rows of A / C; offsets is a device int32 array of num_groups + 1 entries.
+B200_API int b200_grouped_gemm_bf16(const void* A, const void* W, void* C, const void* offsets,
+                                    int num_groups, long total_rows, int N, int K, int lda,
+                                    int ldw, int ldc, int swiglu, int* status,
+                                    cudaStream_t stream) {
+  if (total_rows <= 0 || N <= 0 || num_groups <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
+  if (num_groups > GEMM_MAX_GROUPS) return 9131;
+  if (swiglu && (N % 128)) return 9132;
+  GemmParams p;
+  init_params(p);
+  p.M = (int)total_rows; p.N = N; p.K = K; p.ldc = ldc;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.mode = GEMM_GROUPED | (swiglu ? GEMM_SWIGLU : 0);
+  p.group_offsets = (const int*)offsets;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = swiglu ? 2 * N : N;
+  p.up_row_offset = N;
+  const long w_rows = (long)num_groups * p.w_rows_per_group;
+  if (swiglu || N % 256 == 0)
+    return launch_gemm<256>(A, W, p, lda, ldw, total_rows, w_rows, 0, stream);
+  return launch_gemm<128>(A, W, p, lda, ldw, total_rows, w_rows, 0, stream);
 }

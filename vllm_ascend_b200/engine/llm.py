@@ -76,6 +76,7 @@ class LLMEngine:
         self._req_counter = itertools.count()
         self.eos_token_id: Optional[int] = None
         self.step_times: list[float] = []
+        self.host_times = {"schedule": 0.0, "execute": 0.0, "update": 0.0}
 
     def _make_scheduler(self, num_blocks: int) -> Scheduler:
         from ..core import make_scheduler
@@ -96,10 +97,15 @@ class LLMEngine:
         return self.scheduler.has_unfinished()
 
     def step(self) -> list[Request]:
+        t0 = time.perf_counter()
         so = self.scheduler.schedule()
+        t1 = time.perf_counter()
         if self.kv_connector is not None:
             self.kv_connector.start_load_kv(so)
         sampled = self.runner.execute(so)
+        t2 = time.perf_counter()
+        self.host_times["schedule"] += t1 - t0
+        self.host_times["execute"] += t2 - t1
         now = time.monotonic()
         for req, _ in so.scheduled:
             if req.first_token_time is None and req.request_id in sampled:
@@ -107,6 +113,7 @@ class LLMEngine:
         finished = self.scheduler.update_from_output(so, sampled)
         if self.kv_connector is not None:
             self.kv_connector.step_finished(so, self.scheduler)
+        self.host_times["update"] += time.perf_counter() - t2
         return finished
 
     def check_health(self) -> None:

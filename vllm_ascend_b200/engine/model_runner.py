@@ -85,7 +85,8 @@ class ModelRunner:
         self.graph_pool = None
         self.capture_sizes: list[int] = []
         self.stats = {"graph_replays": 0, "eager_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0,
-                      "steps": 0, "graph_kernel_launches": 0}
+                      "steps": 0, "graph_kernel_launches": 0, "t_prepare": 0.0, "t_launch": 0.0,
+                      "t_wait": 0.0}
         self.graph_launches: dict[int, int] = {}
         self.sm_count = (torch.cuda.get_device_properties(device).multi_processor_count
                          if self.is_cuda else 1)
@@ -248,7 +249,13 @@ class ModelRunner:
             G = a.Hq // a.Hkv
             tok_per_tile = max(1, 128 // G)
             if max_q > 1:
-                ts, tq = build_tile_worklist(q_lens, tok_per_tile, seq_lens)
+                # decode sequences (leading, one token each) go to the decode kernel when it
+                # supports the head layout; the work list then covers the rest
+                skip = nd if (a.D == 128 and 16 % G == 0 and envs.VLLM_B200_DECODE_ATTN == "native") else 0
+                ts, tq = build_tile_worklist(q_lens[skip:], tok_per_tile, seq_lens[skip:])
+                ts = ts + np.int32(skip)
+                if skip == 0:
+                    meta.num_decodes = meta.num_decode_tokens = 0
                 nt = len(ts)
                 h._h_tile[0, :nt] = torch.from_numpy(ts)
                 h._h_tile[1, :nt] = torch.from_numpy(tq)
@@ -289,12 +296,14 @@ class ModelRunner:
         """Runs one step; returns {request_id: [sampled token ids]}."""
         if so.is_empty:
             return {}
+        t_start = time.perf_counter()
         self.stats["steps"] += 1
         self._sync_rows(so)
         B = len(so.scheduled)
         decode_only = all(n == 1 for _, n in so.scheduled)
         gsize = self._graph_size_for(B) if decode_only else None
         meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
+        t_prep = time.perf_counter()
         if gsize is not None:
             graph, hidden_out = self.graphs[gsize]
             graph.replay()
@@ -316,6 +325,7 @@ class ModelRunner:
             md.generator = self._cpu_generator()
         tokens = self.sampler(logits, md)
         n = tokens.shape[0]
+        t_launch = time.perf_counter()
         if self.is_cuda:
             self._h_sampled[:n].copy_(tokens, non_blocking=True)
             torch.cuda.current_stream().synchronize()
@@ -323,6 +333,10 @@ class ModelRunner:
         else:
             toks = tokens.numpy()
         self.stats["d2h_bytes"] += n * 8
+        t_sync = time.perf_counter()
+        self.stats["t_prepare"] += t_prep - t_start
+        self.stats["t_launch"] += t_launch - t_prep
+        self.stats["t_wait"] += t_sync - t_launch
         out = {}
         for r, t in zip(sample_reqs, toks):
             t = int(t)

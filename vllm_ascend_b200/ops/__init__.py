@@ -193,6 +193,29 @@ def paged_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     return out
 
 
+def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
+                              scale: float, out: torch.Tensor, window: int = 0,
+                              num_splits: int = 1, num_seqs: Optional[int] = None) -> torch.Tensor:
+    """tcgen05 flash-decode (keys on the MMA M axis): the first ``num_seqs`` sequences of the
+    batch, each with at most 16/G query tokens; ``q``/``out`` hold exactly their tokens."""
+    T, Hq, D = q.shape
+    if num_seqs is None:
+        num_seqs = meta.num_reqs
+    NB, BS, Hkv, _ = k_cache.shape
+    scratch = None
+    if num_splits > 1:
+        scratch = _get_scratch(q.device, T * Hq * num_splits * (D + 1) * 4)
+    rc = _native.lib().b200_attn_decode_tc(
+        q.data_ptr(), q.stride(0), T, k_cache.data_ptr(), v_cache.data_ptr(), NB, BS,
+        meta.query_start_loc.data_ptr(), meta.seq_lens.data_ptr(), meta.block_table.data_ptr(),
+        meta.block_table.stride(0), num_seqs, Hq, Hkv, D, scale, int(window), num_splits,
+        out.data_ptr(), out.stride(0), _native.ptr(scratch),
+        _native.status_word(q.device).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "attn_decode_tc")
+    launch_counter[0] += 1 + (1 if num_splits > 1 else 0)
+    return out
+
+
 def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  block_table: torch.Tensor, seq_lens: torch.Tensor, scale: float,
                  out: torch.Tensor, window: int = 0, num_splits: int = 1) -> torch.Tensor:
@@ -238,8 +261,23 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     G = Hq // Hkv
     is_decode = meta.max_query_len == 1
     tc_ok = D in (64, 128) and 128 % G == 0 and v_cache.shape[-1] == D
+    mode = envs.VLLM_B200_DECODE_ATTN
+    dec_ok = (mode == "native" and D == 128 and 16 % G == 0 and causal
+              and v_cache.shape[-1] == D)
+    if dec_ok and meta.max_query_len <= 16 // G:
+        return paged_attention_decode_tc(q, k_cache, v_cache, meta, scale, out, window,
+                                         num_splits=meta.num_splits if is_decode else 1)
+    if (dec_ok and tc_ok and meta.num_decodes > 0 and meta.tile_seq is not None
+            and envs.VLLM_B200_PREFILL_ATTN == "tcgen05"):
+        # mixed batch: the leading decode sequences stream their KV through the decode
+        # kernel, the work list of the prefill kernel covers the remaining sequences
+        nd, ndt = meta.num_decodes, meta.num_decode_tokens
+        paged_attention_decode_tc(q[:ndt], k_cache, v_cache, meta, scale, out[:ndt], window,
+                                  num_splits=1, num_seqs=nd)
+        if meta.num_tiles > 0:
+            paged_attention_tc(q, k_cache, v_cache, meta, scale, out, causal, window)
+        return out
     if is_decode:
-        mode = envs.VLLM_B200_DECODE_ATTN
         if mode == "tcgen05" and tc_ok:
             return paged_attention_tc(q, k_cache, v_cache, meta, scale, out, causal, window,
                                       num_splits=meta.num_splits)

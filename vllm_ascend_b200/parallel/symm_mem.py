@@ -1,0 +1,119 @@
+"""Symmetric (peer-mapped) device memory for one process group.
+
+Every rank allocates one buffer of the same size with the native allocator,
+exports it as a CUDA IPC handle, and maps all peers' buffers, so kernels can
+load/store any rank's copy through NVLink.  The buffer starts with the control
+block (epoch flags, see csrc/comm.cuh); the rest is carved into named regions at
+identical offsets on every rank.
+
+This layer replaces the HCCL "window" the reference's device-initiated ops use as
+peer memory (csrc/mc2/*/op_kernel/utils/hccl_shmem.hpp; buffer sizing in
+vllm_ascend/ops/fused_moe/moe_comm_method.py:283-336).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_long, c_void_p, POINTER
+from typing import Optional
+
+import torch
+
+from .. import _native
+from .state import GroupCoordinator
+
+P, I, L, F = c_void_p, c_int, c_long, ctypes.c_float
+_native.register_signature("b200_symm_alloc", [L, POINTER(c_void_p)])
+_native.register_signature("b200_symm_free", [P])
+_native.register_signature("b200_ipc_get_handle", [P, P])
+_native.register_signature("b200_ipc_open", [P, POINTER(c_void_p)])
+_native.register_signature("b200_ipc_close", [P])
+_native.register_signature("b200_comm_ctl_bytes", [])
+_native.register_signature("b200_comm_barrier", [P, I, I, P])
+_native.register_signature("b200_comm_ctl_reset", [P, P])
+_native.register_signature("b200_comm_read_status", [P, POINTER(c_int), P])
+_native.register_signature("b200_allreduce_oneshot", [P, P, P, L, I, I, P])
+_native.register_signature("b200_reduce_add_norm_push", [P, I, P, P, P, F, P, P, I, I, I, I, I, P])
+_native.register_signature("b200_ag_wait", [P, I, I, P])
+_native.register_signature("b200_gemm_ag_bf16", [P, P, P, P, I, I, I, I, I, I, P, I, I, I, I, P, P])
+_native.register_signature("b200_gemm_rs_bf16", [P, P, P, I, I, I, I, I, P, P, I, I, I, I, P, P])
+_native.register_signature("b200_gemm_swiglu_bf16", [P, P, P, I, I, I, I, I, I, P, P])
+_native.register_signature("b200_grouped_gemm_bf16", [P, P, P, P, I, L, I, I, I, I, I, I, P, P])
+
+
+class _RawCudaBuffer:
+    """Exposes a raw device pointer through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class SymmetricMemory:
+    ALIGN = 1024
+
+    def __init__(self, group: GroupCoordinator, device: torch.device, nbytes: int):
+        self.group = group
+        self.device = device
+        self.rank = group.rank_in_group
+        self.world = group.world_size
+        lib = _native.lib()
+        self.ctl_bytes = ((lib.b200_comm_ctl_bytes() + self.ALIGN - 1) // self.ALIGN) * self.ALIGN
+        self.nbytes = self.ctl_bytes + ((nbytes + self.ALIGN - 1) // self.ALIGN) * self.ALIGN
+        p = c_void_p()
+        _native.check(lib.b200_symm_alloc(self.nbytes, ctypes.byref(p)), "symm_alloc")
+        self.local_ptr = p.value
+        handle = (ctypes.c_ubyte * 64)()
+        _native.check(lib.b200_ipc_get_handle(self.local_ptr, handle), "ipc_get_handle")
+        handles = group.all_gather_object(bytes(handle))
+        self.peer_ptrs: list[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.peer_ptrs.append(self.local_ptr)
+                continue
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            q = c_void_p()
+            _native.check(lib.b200_ipc_open(buf, ctypes.byref(q)), f"ipc_open(rank {r})")
+            self.peer_ptrs.append(q.value)
+        self._offset = self.ctl_bytes
+        self._keep = _RawCudaBuffer(self.local_ptr, self.nbytes)
+        self.local = torch.as_tensor(self._keep, device=device)     # uint8 view of the whole buffer
+        self.ctl_ptrs = (c_void_p * self.world)(*self.peer_ptrs)
+        group.barrier()
+
+    def region(self, nbytes: int) -> int:
+        """Reserve a region; returns its byte offset (identical on every rank)."""
+        off = self._offset
+        self._offset += ((nbytes + self.ALIGN - 1) // self.ALIGN) * self.ALIGN
+        if self._offset > self.nbytes:
+            raise RuntimeError("symmetric buffer exhausted")
+        return off
+
+    def tensor(self, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = int(torch.tensor([], dtype=dtype).element_size())
+        numel = 1
+        for s in shape:
+            numel *= s
+        return self.local[offset:offset + numel * n].view(dtype).view(*shape)
+
+    def ptr_array(self, offset: int):
+        """ctypes array of every rank's pointer to the region at ``offset``."""
+        return (c_void_p * self.world)(*[p + offset for p in self.peer_ptrs])
+
+    def barrier(self) -> None:
+        _native.check(_native.lib().b200_comm_barrier(self.ctl_ptrs, self.rank, self.world,
+                                                      _native.stream_ptr()), "comm_barrier")
+
+    def read_status(self) -> int:
+        out = c_int(0)
+        _native.check(_native.lib().b200_comm_read_status(self.local_ptr, ctypes.byref(out),
+                                                          _native.stream_ptr()), "read_status")
+        return out.value
+
+    def close(self) -> None:
+        lib = _native.lib()
+        for r, p in enumerate(self.peer_ptrs):
+            if r != self.rank and p:
+                lib.b200_ipc_close(p)
+        if self.local_ptr:
+            lib.b200_symm_free(self.local_ptr)
+            self.local_ptr = 0
