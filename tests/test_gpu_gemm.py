@@ -59,3 +59,43 @@ def test_gemm_strided_input():
     out = ops.linear(a, w)
     exp = a.float() @ w.float().t()
     assert (out.float() - exp).abs().max().item() < 0.5
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 768, 2048), (1024, 12288, 4096), (5, 256, 512)])
+def test_gemm_swiglu_epilogue(M, I, K):
+    g = torch.Generator(device="cpu").manual_seed(3)
+    a = (torch.randn(M, K, generator=g) * 0.3).bfloat16().to(DEV)
+    w = (torch.randn(2 * I, K, generator=g) * 0.1).bfloat16().to(DEV)
+    out = ops.linear_swiglu(a, w)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    h = a.float() @ w.float().t()
+    exp = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
+    assert (out.float() - exp).abs().max().item() < 0.02 * exp.abs().max().item() + 0.02
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_grouped_gemm(swiglu):
+    torch.manual_seed(4)
+    E, K, N = 8, 512, 256
+    counts = [0, 5, 128, 300, 1, 0, 77, 129]
+    offs = torch.tensor([0] + list(__import__("itertools").accumulate(counts)), dtype=torch.int32, device=DEV)
+    total = int(offs[-1])
+    a = (torch.randn(total, K, device=DEV) * 0.3).bfloat16()
+    wrows = 2 * N if swiglu else N
+    w = (torch.randn(E, wrows, K, device=DEV) * 0.1).bfloat16()
+    out = torch.full((total, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    rc = _native.lib().b200_grouped_gemm_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), offs.data_ptr(),
+                                              E, total, N, K, K, K, N, int(swiglu),
+                                              _native.status_word(torch.device(DEV)).data_ptr(),
+                                              _native.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    for e in range(E):
+        lo, hi = int(offs[e]), int(offs[e + 1])
+        if hi == lo:
+            continue
+        h = a[lo:hi].float() @ w[e].float().t()
+        exp = torch.nn.functional.silu(h[:, :N]) * h[:, N:] if swiglu else h
+        assert (out[lo:hi].float() - exp).abs().max().item() < 0.05, e

@@ -1,0 +1,56 @@
+"""Multi-GPU checks (skipped with fewer than two GPUs): fused tensor parallelism over
+peer memory must reproduce the single-GPU generation and the NCCL path."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _run(n, what, env=None, timeout=600):
+    e = dict(os.environ)
+    e.update(env or {})
+    e.setdefault("NCCL_NVLS_ENABLE", "0")
+    port = 29600 + (os.getpid() + hash(what) % 97) % 300
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           os.path.join(ROOT, "tests", "multi_gpu_worker.py"), what]
+    p = subprocess.run(cmd, capture_output=True, text=True, env=e, timeout=timeout)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_peer_memory_allreduce_matches_nccl():
+    r = _run(2, "symm_allreduce")
+    assert r["status"] == 0
+    assert r["max_err"] < 0.1
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_tp2_matches_single_gpu_and_nccl():
+    single = _run(1, "tp_generate", {"EAGER": "1"})
+    nccl = _run(2, "tp_generate", {"VLLM_B200_TP_COMM": "nccl", "EAGER": "1"})
+    fused = _run(2, "tp_generate", {"VLLM_B200_TP_COMM": "fused", "EAGER": "1"})
+    graph = _run(2, "tp_generate", {"VLLM_B200_TP_COMM": "fused", "EAGER": "0"})
+    assert fused["fused"] and not nccl["fused"]
+    assert graph["replays"] > 0
+
+    def agree(a, b):
+        same = sum(x == y for s, t in zip(a, b) for x, y in zip(s, t))
+        total = sum(len(s) for s in a)
+        return same / total
+    # bf16 partial-sum order differs between the paths: allow rare near-tie flips
+    assert agree(nccl["tokens"], single["tokens"]) > 0.8
+    assert agree(fused["tokens"], nccl["tokens"]) > 0.8
+    assert fused["tokens"] == graph["tokens"]

@@ -52,8 +52,10 @@ struct DecCfg {
   static constexpr int STAGES = 3;
   static constexpr int TILE_BYTES = NH * DEC_HALF;
   static constexpr int Q_BYTES = NH * DEC_QHALF;
-  static constexpr int P_BYTES = 2 * DEC_QHALF;
-  static constexpr int SMEM_BYTES = 2 * STAGES * TILE_BYTES + Q_BYTES + P_BYTES + 1024 + 1024;
+  static constexpr int P_BYTES = 2 * DEC_QHALF;     // one P buffer (two 64-key halves)
+  static constexpr int P_BUFS = 2;                  // double-buffered so P(j+1) overlaps PV(j)
+  static constexpr int SMEM_BYTES =
+      2 * STAGES * TILE_BYTES + Q_BYTES + P_BUFS * P_BYTES + 1024 + 1024;
   static constexpr int TMEM_COLS = 64;
   static constexpr int O_COL = 32;
 };
@@ -104,7 +106,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint8_t* Vs = Ks + ST * Cfg::TILE_BYTES;
   uint8_t* Qs = Vs + ST * Cfg::TILE_BYTES;
   uint8_t* Ps = Qs + Cfg::Q_BYTES;
-  uint64_t* bars = (uint64_t*)(Ps + Cfg::P_BYTES);
+  uint64_t* bars = (uint64_t*)(Ps + Cfg::P_BUFS * Cfg::P_BYTES);
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // ST
   uint64_t* k_empty = k_full + ST;    // ST
@@ -112,9 +114,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint64_t* v_empty = v_full + ST;    // ST
   uint64_t* s_ready = v_empty + ST;   // 2
   uint64_t* s_free = s_ready + 2;     // 2
-  uint64_t* p_ready = s_free + 2;     // 1
-  uint64_t* pv_done = p_ready + 1;    // 1
-  uint32_t* tmem_ptr = (uint32_t*)(pv_done + 1);
+  uint64_t* p_ready = s_free + 2;     // 2 (per P buffer)
+  uint64_t* pv_done = p_ready + 2;    // 2 (per P buffer)
+  uint32_t* tmem_ptr = (uint32_t*)(pv_done + 2);
   volatile int* abort_word = (volatile int*)(tmem_ptr + 1);
   float* red = (float*)(tmem_ptr + 2);            // [4 warps][16]
 
@@ -129,9 +131,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int b = 0; b < 2; b++) {
       mbar_init(&s_ready[b], 1);
       mbar_init(&s_free[b], 4);
+      mbar_init(&p_ready[b], 4);
+      mbar_init(&pv_done[b], 1);
     }
-    mbar_init(p_ready, 4);
-    mbar_init(pv_done, 1);
     *abort_word = 0;
     mbar_fence_init();
   }
@@ -227,8 +229,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       const int st = j % ST;
       const uint32_t ph = (uint32_t)(j / ST) & 1u;
+      const int pb = j & 1;
       if (!mbar_wait(&v_full[st], ph, abort_word)) goto done;
-      if (!mbar_wait(p_ready, (uint32_t)j & 1u, abort_word)) goto done;
+      if (!mbar_wait(&p_ready[pb], ((uint32_t)j >> 1) & 1u, abort_word)) goto done;
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
@@ -236,12 +239,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
           // A: 16 keys of V^T (two 64-wide d atoms DEC_HALF apart, 8-key groups 1024 B apart)
           const uint64_t da = make_smem_desc(v_addr + st * Cfg::TILE_BYTES + kk * 2048, DEC_HALF,
                                              1024, kLayoutSw128);
-          const uint64_t db = make_smem_desc(p_addr + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16,
-                                             1024, kLayoutSw128);
+          const uint64_t db = make_smem_desc(
+              p_addr + pb * Cfg::P_BYTES + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16, 1024,
+              kLayoutSw128);
           umma_f16_ss(tmem_base + Cfg::O_COL, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[st]);
-        umma_commit(pv_done);
+        umma_commit(&pv_done[pb]);
       }
       __syncwarp();
     }
@@ -300,10 +304,14 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
           lsum[c] *= alpha[c];
         }
       }
-      if (j > 0) {
-        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_word)) goto done;
+      // P buffer j&1 was last read by PV(j-2)
+      if (j >= 2) {
+        if (!mbar_wait(&pv_done[j & 1], (((uint32_t)j - 2) >> 1) & 1u, abort_word)) goto done;
+      }
+      if (j > 0 && any_change) {    // uniform over the 128 threads: O^T must be quiescent
+        if (!mbar_wait(&pv_done[(j - 1) & 1], (((uint32_t)j - 1) >> 1) & 1u, abort_word)) goto done;
         tc_fence_after();
-        if (any_change) {           // uniform over the 128 threads
+        {
           uint32_t o[16];
           tmem_ld_32x32b_x16(t_lane + Cfg::O_COL, o);
           tmem_ld_wait();
@@ -314,7 +322,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
       }
       // probabilities of this key for every valid column -> P[c][key] (K-major, swizzled)
-      uint8_t* pbase = Ps + (tid >> 6) * DEC_QHALF;
+      uint8_t* pbase = Ps + (j & 1) * Cfg::P_BYTES + (tid >> 6) * DEC_QHALF;
       const int kin = tid & 63;
 #pragma unroll
       for (int c = 0; c < DEC_NQ; c++) {
@@ -330,10 +338,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       tc_fence_before();
       fence_proxy_async_smem();
       softmax_bar();            // all red[] reads done before the next tile overwrites it
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
     }
     // ---- epilogue: total row sums, normalise, store
-    if (!mbar_wait(pv_done, (uint32_t)(n - 1) & 1u, abort_word)) goto done;
+    if (!mbar_wait(&pv_done[(n - 1) & 1], (((uint32_t)n - 1) >> 1) & 1u, abort_word)) goto done;
     tc_fence_after();
 #pragma unroll
     for (int c = 0; c < DEC_NQ; c++) {

@@ -280,4 +280,7 @@ class SwiGLUMLP:
                                            reduce_results=reduce_results)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(ops.silu_and_mul(self.gate_up_proj(x)))
+        gu = self.gate_up_proj
+        if gu.quant is None and gu.bias is None and not gu.gather_output:
+            return self.down_proj(ops.linear_swiglu(x, gu.weight))
+        return self.down_proj(ops.silu_and_mul(gu(x)))

@@ -217,6 +217,8 @@ class CausalLM:
         self.dtype = cfg.torch_dtype
         pf = ParamFactory(cfg, self.device, self.dtype)
         self.comm = TPComm(tp_group or pstate.get_tp_group())
+        self.sp_ctx = None             # set by parallel.fused_linear.attach()
+        self.full_embedding = None
         max_pos = max(max_model_len, 16)
         lo, hi = layer_range or (0, cfg.num_hidden_layers)
         self.layer_range = (lo, hi)
@@ -239,6 +241,9 @@ class CausalLM:
     # -- forward ---------------------------------------------------------
     def forward(self, input_ids: torch.Tensor, meta, kv_caches: list,
                 intermediate: Optional[tuple] = None):
+        if self.sp_ctx is not None and input_ids.is_cuda:
+            from ..parallel.fused_linear import forward_sp
+            return forward_sp(self, self.sp_ctx, input_ids, meta, kv_caches)
         if self.is_first:
             h = self.embed_tokens(input_ids)
             residual = None

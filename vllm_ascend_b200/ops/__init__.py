@@ -147,6 +147,31 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return out.view(*x.shape[:-1], N)
 
 
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x @ Wg^T) * (x @ Wu^T) with weight = [Wg; Wu] ([2I, K]) in one GEMM: the tile pairs
+    128 gate columns with the matching 128 up columns and the epilogue applies SiLU-mul
+    (the reference fuses the same pair in its grouped-matmul+swiglu op, csrc/gmm)."""
+    I = weight.shape[0] // 2
+    K = x.shape[-1]
+    if not (_use_native(x) and weight.dtype == _BF16 and I % 128 == 0 and K % 8 == 0
+            and envs.VLLM_B200_GEMM != "cublas"):
+        return silu_and_mul(linear(x, weight))
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) != 0:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    if out is None:
+        out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+    if M > 0:
+        rc = _native.lib().b200_gemm_swiglu_bf16(
+            x2.data_ptr(), weight.data_ptr(), out.data_ptr(), M, I, K, x2.stride(0),
+            weight.stride(0), out.stride(0), _native.status_word(x.device).data_ptr(),
+            _native.stream_ptr())
+        _native.check(rc, "gemm_swiglu")
+        launch_counter[0] += 1
+    return out.view(*x.shape[:-1], I)
+
+
 # ---------------------------------------------------------------- attention
 _scratch: dict = {}
 

@@ -50,8 +50,12 @@ class GroupCoordinator:
         if self.world_size == 1:
             return t
         t = t.contiguous()
-        out = torch.empty((self.world_size,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-        dist.all_gather_into_tensor(out, t, group=self.device_group)
+        if t.dim() == 0:
+            t = t.view(1)
+        flat = torch.empty((self.world_size * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype,
+                           device=t.device)
+        dist.all_gather_into_tensor(flat, t, group=self.device_group)
+        out = flat.view((self.world_size,) + tuple(t.shape))
         if dim < 0:
             dim += t.dim()
         out = out.movedim(0, dim)
