@@ -53,10 +53,13 @@ class LLMEngine:
         else:
             pstate.initialize_model_parallel()
         self.runner = ModelRunner(cfg, self.device)
+        self.dp = pstate.get_dp_group()
+        self.moe_runtime = None
         moe_runtime = None
         if cfg.model.is_moe and pc.enable_expert_parallel and world > 1:
             from ..ops.moe_comm import MoERuntime
             moe_runtime = MoERuntime(cfg, self.device)
+            self.moe_runtime = moe_runtime
         self.runner.load_model(moe_runtime=moe_runtime)
         if world > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM == "fused" \
                 and pc.tensor_parallel_size > 1:
@@ -115,6 +118,44 @@ class LLMEngine:
             self.kv_connector.step_finished(so, self.scheduler)
         self.host_times["update"] += time.perf_counter() - t2
         return finished
+
+    def step_dp(self) -> bool:
+        """One lock-step iteration of a data-parallel engine: the DP ranks agree on whether
+        anyone still has work and on the largest token count (the per-step CPU all-reduce of
+        vllm_ascend/worker/model_runner_v1.py:669-707); ranks without work run a dummy batch
+        so they still meet the others in the expert-parallel collectives
+        (vllm_ascend/worker/worker.py:1048-1051).  Returns False when every rank is done."""
+        import torch.distributed as dist
+        t0 = time.perf_counter()
+        busy = self.scheduler.has_unfinished()
+        so = self.scheduler.schedule() if busy else None
+        ntok = so.num_scheduled_tokens if so is not None else 0
+        sync = torch.tensor([int(busy), max(ntok, 1)], dtype=torch.int32)
+        dist.all_reduce(sync, op=dist.ReduceOp.MAX, group=self.dp.cpu_group)
+        if int(sync[0]) == 0:
+            return False
+        if self.moe_runtime is not None:
+            self.moe_runtime.max_tokens_across_dp = int(sync[1])
+        t1 = time.perf_counter()
+        if so is None or so.is_empty:
+            self.runner.execute_dummy()
+            self.host_times["execute"] += time.perf_counter() - t1
+            return True
+        if self.kv_connector is not None:
+            self.kv_connector.start_load_kv(so)
+        sampled = self.runner.execute(so)
+        t2 = time.perf_counter()
+        now = time.monotonic()
+        for req, _ in so.scheduled:
+            if req.first_token_time is None and req.request_id in sampled:
+                req.first_token_time = now
+        self.scheduler.update_from_output(so, sampled)
+        if self.kv_connector is not None:
+            self.kv_connector.step_finished(so, self.scheduler)
+        self.host_times["schedule"] += t1 - t0
+        self.host_times["execute"] += t2 - t1
+        self.host_times["update"] += time.perf_counter() - t2
+        return True
 
     def check_health(self) -> None:
         if self.device.type == "cuda":
@@ -182,17 +223,26 @@ class LLM:
         if sampling_params is None:
             sampling_params = SamplingParams()
         eng = self.engine
+        dp = eng.dp
         order: list[str] = []
+        mine: list[int] = []
         reqs: dict[str, Request] = {}
         for i, p in enumerate(prompts):
+            if dp.world_size > 1 and i % dp.world_size != dp.rank_in_group:
+                continue            # data parallel: every DP rank serves its own slice
             ids = p["prompt_token_ids"] if isinstance(p, dict) else p
             sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
             ktp = p.get("kv_transfer_params") if isinstance(p, dict) else None
             rid = eng.add_request(ids, sp, kv_transfer_params=ktp)
             order.append(rid)
+            mine.append(i)
             reqs[rid] = eng.scheduler.requests[rid]
-        while eng.has_unfinished():
-            eng.step()
+        if dp.world_size > 1:
+            while eng.step_dp():
+                pass
+        else:
+            while eng.has_unfinished():
+                eng.step()
         eng.check_health()
         outs = []
         for rid in order:
@@ -205,6 +255,13 @@ class LLM:
                 metrics=RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time),
                 kv_transfer_params=r.kv_transfer_params, num_cached_tokens=r.num_cached_tokens))
             eng.scheduler.requests.pop(rid, None)
+        if dp.world_size > 1:
+            # every rank returns the complete, input-ordered list
+            merged: list = [None] * len(prompts)
+            for idxs, part in dp.all_gather_object((mine, outs)):
+                for i, o in zip(idxs, part):
+                    merged[i] = o
+            outs = merged
         return outs
 
     # -- RL / lifecycle passthroughs (implemented by the worker-level mixins) ------

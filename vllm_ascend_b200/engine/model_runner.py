@@ -345,6 +345,14 @@ class ModelRunner:
             out[r.request_id] = [t]
         return out
 
+    @torch.inference_mode()
+    def execute_dummy(self) -> None:
+        """Forward of one padding token that writes nothing to the KV cache; used by idle
+        data-parallel ranks so collectives inside the model still match up."""
+        meta, T, Tp, _, _ = self._dummy_meta(1, 1)
+        meta.slot_mapping.fill_(-1)
+        self._forward(Tp, meta)
+
     def total_launches(self) -> int:
         """Launches of this package's own kernels so far (eager + inside replayed graphs)."""
         return ops.launch_counter[0] + self.stats["graph_kernel_launches"]

@@ -44,7 +44,9 @@ class SparseMoeBlock:
             assert E % ep == 0
             self.E_local = E // ep
             self.expert_start = r * self.E_local
-            self.w13 = pf.normal(f"{prefix}.experts.w13", (E, 2 * I, H), 0, r, ep)
+            g = pf.normal(f"{prefix}.experts.w1", (E, I, H), 0, r, ep)
+            u = pf.normal(f"{prefix}.experts.w3", (E, I, H), 0, r, ep)
+            self.w13 = torch.cat([g, u], dim=1).contiguous()
             self.w2 = pf.normal(f"{prefix}.experts.w2", (E, H, I), 0, r, ep)
             emap = torch.full((E,), -1, dtype=torch.int32)
             emap[self.expert_start:self.expert_start + self.E_local] = torch.arange(self.E_local, dtype=torch.int32)
