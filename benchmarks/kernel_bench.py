@@ -81,7 +81,8 @@ def bench_gemm(a):
 def bench_attn_decode(a):
     from gpu_utils import make_paged_case
     B, ctx = a.batch, a.ctx
-    q, kc, vc, meta = make_paged_case([1] * B, [ctx - 1] * B, a.hq, a.hkv, a.d, a.block_size, seed=0)
+    q, kc, vc, meta = make_paged_case([1] * B, [ctx - 1] * B, a.hq, a.hkv, a.d, a.block_size, seed=0,
+                                      layout=a.kv_layout)
     out = torch.empty_like(q)
     scale = a.d ** -0.5
     meta.tile_seq = meta.tile_qoff = None
@@ -96,7 +97,9 @@ def bench_attn_decode(a):
             continue
         ns = a.splits or ops.choose_num_splits(B, a.hkv, ctx)
         ms = timeit(lambda: fn(ns), a.iters)
-        print(f"attn-decode[{name}] B={B} ctx={ctx} Hq={a.hq} Hkv={a.hkv} D={a.d} splits={ns}: "
+        if name == "cuda-core" and a.kv_layout != "NHD":
+            continue
+        print(f"attn-decode[{name}/{a.kv_layout}] B={B} ctx={ctx} Hq={a.hq} Hkv={a.hkv} D={a.d} splits={ns}: "
               f"{ms:.4f} ms  {bytes_kv / ms / 1e6:.0f} GB/s ({bytes_kv / ms / 1e6 / hbm:.2f} {tag})",
               flush=True)
     _native.check_status(torch.device("cuda"))
@@ -105,7 +108,8 @@ def bench_attn_decode(a):
 def bench_attn_prefill(a):
     from gpu_utils import make_paged_case
     B, S = a.batch, a.seq
-    q, kc, vc, meta = make_paged_case([S] * B, [a.ctx] * B, a.hq, a.hkv, a.d, a.block_size, seed=0)
+    q, kc, vc, meta = make_paged_case([S] * B, [a.ctx] * B, a.hq, a.hkv, a.d, a.block_size, seed=0,
+                                      layout=a.kv_layout)
     out = torch.empty_like(q)
     scale = a.d ** -0.5
     ms = timeit(lambda: ops.paged_attention_tc(q, kc, vc, meta, scale, out, True, 0, 1), a.iters)
@@ -156,6 +160,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--inter", type=int, default=12288)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--kv-layout", default="HND", choices=["NHD", "HND"])
     a = ap.parse_args()
     if a.what in ("gemm", "all"):
         if a.what == "all":

@@ -6,7 +6,7 @@ from vllm_ascend_b200.attention.metadata import AttentionMetadata, build_tile_wo
 
 
 def make_paged_case(q_lens, ctx_lens, Hq, Hkv, D, block_size, device="cuda", seed=0,
-                    dtype=torch.bfloat16, shuffle_blocks=True, tok_per_tile=None):
+                    dtype=torch.bfloat16, shuffle_blocks=True, tok_per_tile=None, layout="NHD"):
     """Random q + paged K/V caches for sequences with `ctx_lens[i]` cached tokens and
     `q_lens[i]` new query tokens (whose K/V are already in the cache)."""
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -43,7 +43,11 @@ def make_paged_case(q_lens, ctx_lens, Hq, Hkv, D, block_size, device="cuda", see
         meta.tile_seq = torch.from_numpy(ts).to(device)
         meta.tile_qoff = torch.from_numpy(tq).to(device)
         meta.num_tiles = len(ts)
-    return q.to(device), k_cache.to(device), v_cache.to(device), meta
+    k_cache, v_cache = k_cache.to(device), v_cache.to(device)
+    if layout == "HND":      # same logical tensor, heads-major physical order
+        k_cache = k_cache.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+        v_cache = v_cache.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    return q.to(device), k_cache, v_cache, meta
 
 
 def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:

@@ -39,10 +39,11 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
 @pytest.mark.parametrize("case", CASES)
-def test_attn_tc_matches_reference(case):
+def test_attn_tc_matches_reference(case, layout):
     q_lens, ctx, Hq, Hkv, D, bs = case
-    q, kc, vc, meta = make_paged_case(q_lens, ctx, Hq, Hkv, D, bs, seed=len(q_lens))
+    q, kc, vc, meta = make_paged_case(q_lens, ctx, Hq, Hkv, D, bs, seed=len(q_lens), layout=layout)
     scale = D ** -0.5
     out = _run_tc(q, kc, vc, meta, scale)
     exp = _ref(q, kc, vc, meta, scale)
@@ -101,11 +102,12 @@ DEC_CASES = [
 ]
 
 
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
 @pytest.mark.parametrize("case", DEC_CASES)
 @pytest.mark.parametrize("ns", [1, 3])
-def test_attn_decode_tc(case, ns):
+def test_attn_decode_tc(case, ns, layout):
     q_lens, ctx, Hq, Hkv, bs = case
-    q, kc, vc, meta = make_paged_case(q_lens, ctx, Hq, Hkv, 128, bs, seed=11)
+    q, kc, vc, meta = make_paged_case(q_lens, ctx, Hq, Hkv, 128, bs, seed=11, layout=layout)
     scale = 128 ** -0.5
     out = torch.full_like(q, float("nan"))
     ops.paged_attention_decode_tc(q, kc, vc, meta, scale, out, 0, ns)

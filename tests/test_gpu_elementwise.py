@@ -52,8 +52,9 @@ def test_embedding_with_vocab_shard():
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,rot", [(32, 8, 128, 128), (4, 2, 64, 64), (8, 8, 128, 64)])
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
 @pytest.mark.parametrize("qk_norm", [True, False])
-def test_qknorm_rope_kvwrite(Hq, Hkv, D, rot, qk_norm):
+def test_qknorm_rope_kvwrite(Hq, Hkv, D, rot, qk_norm, layout):
     torch.manual_seed(1)
     T, bs, nb = 67, 16, 12
     qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
@@ -63,8 +64,8 @@ def test_qknorm_rope_kvwrite(Hq, Hkv, D, rot, qk_norm):
     kn = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16() if qk_norm else None
     slots = torch.randperm(nb * bs, device=DEV)[:T]
     slots[5] = -1
-    kc = torch.zeros(nb, bs, Hkv, D, device=DEV, dtype=torch.bfloat16)
-    vc = torch.zeros_like(kc)
+    kc = ops.alloc_kv_cache(nb, bs, Hkv, D, torch.bfloat16, DEV, layout)
+    vc = ops.alloc_kv_cache(nb, bs, Hkv, D, torch.bfloat16, DEV, layout)
     exp = qkv.clone().float()
     ekc, evc = kc.clone().float(), vc.clone().float()
     ref.qknorm_rope_kvwrite(exp, pos, cs, rot, None if qn is None else qn.float(),
@@ -73,7 +74,7 @@ def test_qknorm_rope_kvwrite(Hq, Hkv, D, rot, qk_norm):
     assert torch.allclose(qkv.float(), exp, atol=6e-2, rtol=3e-2)
     assert torch.allclose(kc.float(), ekc, atol=6e-2, rtol=3e-2)
     assert torch.allclose(vc.float(), evc, atol=1e-6)
-    assert float(kc.view(-1, Hkv, D)[slots[6]].abs().sum()) > 0
+    assert float(kc[slots[6] // bs, slots[6] % bs].abs().sum()) > 0
 
 
 def test_quant_fp8_group128():

@@ -239,6 +239,7 @@ class CacheConfig:
     num_gpu_blocks: Optional[int] = None   # override; else profiled
     enable_prefix_caching: bool = False
     kv_cache_dtype: str = "auto"
+    kv_layout: str = "HND"             # physical order inside a block: HND (per-head pages) | NHD
 
 
 @dataclass

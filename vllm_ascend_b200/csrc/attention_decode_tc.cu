@@ -70,7 +70,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   using Cfg = DecCfg<D>;
   constexpr int NH = Cfg::NH, ST = Cfg::STAGES;
 
-  const int seq = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  // heads of one sequence run side by side so neighbouring KV bytes are fetched together
+  const int h = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
   const int q_start = p.query_start_loc[seq];
   const int q_len = p.query_start_loc[seq + 1] - q_start;
   const int seq_len = p.seq_lens[seq];
@@ -430,8 +431,8 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
                                  const void* query_start_loc, const void* seq_lens,
                                  const void* block_table, int max_blocks, int num_seqs, int Hq,
                                  int Hkv, int D, float scale, int window, int num_splits,
-                                 void* out, long out_stride, void* scratch, int* status,
-                                 cudaStream_t stream) {
+                                 void* out, long out_stride, void* scratch, int kv_layout,
+                                 int* status, cudaStream_t stream) {
   using namespace b200;
   if (num_seqs <= 0 || T <= 0) return 0;
   const int G = Hq / Hkv;
@@ -454,8 +455,13 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
   }
   {
     uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)block_size, (uint64_t)num_blocks};
+    // kv_layout 0: [blocks, tokens, heads, D]; 1: [blocks, heads, tokens, D]
     uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2,
                        (uint64_t)block_size * Hkv * D * 2};
+    if (kv_layout == 1) {
+      str[0] = (uint64_t)block_size * D * 2;
+      str[1] = (uint64_t)D * 2;
+    }
     uint32_t box[4] = {64, 1, (uint32_t)rpl, 1};
     int rc = g_dec_tmaps.get(&tk, k_cache, 4, dims, str, box);
     if (rc) return rc;
@@ -488,7 +494,8 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((unsigned)num_seqs, (unsigned)Hkv, (unsigned)num_splits);
+  if (num_seqs > 65535) return 9125;
+  dim3 grid((unsigned)Hkv, (unsigned)num_seqs, (unsigned)num_splits);
   attn_decode_tc_kernel<128><<<grid, DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   int rc = B200_CHECK_LAUNCH();
   if (rc) return rc;

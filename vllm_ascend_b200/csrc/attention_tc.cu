@@ -72,7 +72,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   constexpr int NH = Cfg::NH, KS = Cfg::KS;
 
   // ---------------- work decode (uniform over the CTA)
-  const int wi = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  const int h = blockIdx.x, wi = blockIdx.y, split = blockIdx.z;
   const int seq = p.tile_seq ? p.tile_seq[wi] : wi;
   const int tok0 = p.tile_qoff ? p.tile_qoff[wi] : 0;
   const int q_start = p.query_start_loc[seq];
@@ -458,7 +458,8 @@ static int launch_attn_tc(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((unsigned)num_tiles, (unsigned)p.Hkv, (unsigned)p.num_splits);
+  if (num_tiles > 65535) return 9125;
+  dim3 grid((unsigned)p.Hkv, (unsigned)num_tiles, (unsigned)p.num_splits);
   attn_fwd_tc_kernel<D><<<grid, ATT_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   return B200_CHECK_LAUNCH();
 }
@@ -484,7 +485,7 @@ B200_API int b200_attn_fwd_tc(const void* q, long q_stride, long T, const void* 
                               const void* tile_qoff, int num_tiles, int Hq, int Hkv, int D,
                               float scale, int causal, int window, int num_splits, void* out,
                               long out_stride, void* scratch, float rescale_threshold,
-                              unsigned v_lbo, unsigned v_sbo, int* status,
+                              unsigned v_lbo, unsigned v_sbo, int kv_layout, int* status,
                               cudaStream_t stream) {
   using namespace b200;
   if (num_tiles <= 0 || T <= 0) return 0;
@@ -512,6 +513,10 @@ B200_API int b200_attn_fwd_tc(const void* q, long q_stride, long T, const void* 
     uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)block_size, (uint64_t)num_blocks};
     uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2,
                        (uint64_t)block_size * Hkv * D * 2};
+    if (kv_layout == 1) {   // [blocks, heads, tokens, D]
+      str[0] = (uint64_t)block_size * D * 2;
+      str[1] = (uint64_t)D * 2;
+    }
     uint32_t box[4] = {64, 1, (uint32_t)rpl, 1};
     int rc = g_att_tmaps.get(&tk, k_cache, 4, dims, str, box);
     if (rc) return rc;

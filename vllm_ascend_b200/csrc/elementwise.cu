@@ -144,7 +144,8 @@ __global__ void qknorm_rope_kvwrite_kernel(__nv_bfloat16* qkv, long qkv_stride,
                                            const __nv_bfloat16* __restrict__ k_norm_w, float eps,
                                            __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                                            const long* __restrict__ slot_mapping, int T, int Hq,
-                                           int Hkv, long num_slots, int* status) {
+                                           int Hkv, long num_slots, int block_size,
+                                           int kv_layout, int* status) {
   constexpr int PER = D / 32;
   const int warps_per_block = blockDim.x >> 5;
   const int heads_total = Hq + 2 * Hkv;
@@ -208,7 +209,12 @@ __global__ void qknorm_rope_kvwrite_kernel(__nv_bfloat16* qkv, long qkv_stride,
       return;
     }
     const int kvh = is_k ? (h - Hq) : (h - Hq - Hkv);
-    __nv_bfloat16* dst = (is_k ? k_cache : v_cache) + (slot * Hkv + kvh) * (long)D;
+    long row = slot * Hkv + kvh;                     // [blocks, tokens, heads, D]
+    if (kv_layout == 1) {                            // [blocks, heads, tokens, D]
+      const long blk = slot / block_size, off = slot - blk * block_size;
+      row = (blk * Hkv + kvh) * block_size + off;
+    }
+    __nv_bfloat16* dst = (is_k ? k_cache : v_cache) + row * (long)D;
 #pragma unroll
     for (int i = 0; i < PER; i++) dst[lane + 32 * i] = __float2bfloat16(v[i]);
   }
@@ -296,8 +302,8 @@ B200_API int b200_qknorm_rope_kvwrite(void* qkv, long qkv_stride, const void* po
                                       const void* cos_sin, int rot_dim, const void* q_norm_w,
                                       const void* k_norm_w, float eps, void* k_cache,
                                       void* v_cache, const void* slot_mapping, int T, int Hq,
-                                      int Hkv, int D, long num_slots, int* status,
-                                      cudaStream_t stream) {
+                                      int Hkv, int D, long num_slots, int block_size,
+                                      int kv_layout, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rot_dim > D || (rot_dim > 0 && ((rot_dim >> 1) & 31))) return 9102;
   const long warps = (long)T * (Hq + 2 * Hkv);
@@ -308,7 +314,7 @@ B200_API int b200_qknorm_rope_kvwrite(void* qkv, long qkv_stride, const void* po
       (__nv_bfloat16*)qkv, qkv_stride, (const long*)positions, (const float*)cos_sin, rot_dim, \
       (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps,                    \
       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const long*)slot_mapping, T, Hq, Hkv, \
-      num_slots, status)
+      num_slots, block_size, kv_layout, status)
   if (D == 128) LAUNCH_ROPE(128);
   else if (D == 64) LAUNCH_ROPE(64);
   else if (D == 256) LAUNCH_ROPE(256);

@@ -60,7 +60,13 @@ class LLMEngine:
             from ..ops.moe_comm import MoERuntime
             moe_runtime = MoERuntime(cfg, self.device)
             self.moe_runtime = moe_runtime
-        self.runner.load_model(moe_runtime=moe_runtime)
+        self.sleep_level = 0
+        if cfg.enable_sleep_mode and cfg.device == "cuda":
+            from ..device_allocator.vmm import VmmAllocator
+            with VmmAllocator.get_instance().use_memory_pool("weights"):
+                self.runner.load_model(moe_runtime=moe_runtime)
+        else:
+            self.runner.load_model(moe_runtime=moe_runtime)
         if world > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM == "fused" \
                 and pc.tensor_parallel_size > 1:
             from ..parallel import fused_linear
@@ -68,7 +74,12 @@ class LLMEngine:
         num_blocks = self.runner.determine_num_blocks()
         if world > 1:   # every rank must agree
             num_blocks = min(pstate.get_world_group().all_gather_object(num_blocks))
-        self.runner.init_kv_cache(num_blocks)
+        if cfg.enable_sleep_mode and cfg.device == "cuda":
+            from ..device_allocator.vmm import VmmAllocator
+            with VmmAllocator.get_instance().use_memory_pool("kv_cache"):
+                self.runner.init_kv_cache(num_blocks)
+        else:
+            self.runner.init_kv_cache(num_blocks)
         self.runner.warmup()
         self.kv_connector = None
         if cfg.kv_transfer_config:

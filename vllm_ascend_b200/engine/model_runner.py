@@ -157,8 +157,10 @@ class ModelRunner:
             else:
                 a = layer.self_attn
                 shapes = [(num_blocks, self.block_size, a.Hkv, a.D)] * 2
-            self.kv_caches.append(tuple(torch.zeros(s, dtype=self.kv_dtype, device=self.device)
-                                        for s in shapes))
+            layout = self.cfg.cache.kv_layout if self.is_cuda else "NHD"
+            self.kv_caches.append(tuple(
+                ops.alloc_kv_cache(s[0], s[1], s[2], s[3], self.kv_dtype, self.device, layout)
+                for s in shapes))
 
     # ------------------------------------------------------------------ persistent batch
     def _sync_rows(self, so: SchedulerOutput) -> None:

@@ -28,6 +28,26 @@ def _use_native(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == _BF16
 
 
+def kv_layout(cache: torch.Tensor) -> int:
+    """Physical layout of a paged cache whose logical shape is [blocks, tokens, heads, D]:
+    0 = stored in that order, 1 = stored as [blocks, heads, tokens, D] (each head's page is
+    one contiguous run, which is what the per-head TMA page loads prefer)."""
+    if cache.is_contiguous():
+        return 0
+    if cache.permute(0, 2, 1, 3).is_contiguous():
+        return 1
+    raise ValueError("unsupported KV-cache strides")
+
+
+def alloc_kv_cache(num_blocks: int, block_size: int, heads: int, dim: int, dtype, device,
+                   layout: str = "HND") -> torch.Tensor:
+    """Zero-filled cache with logical shape [blocks, tokens, heads, dim]."""
+    if layout == "HND" and heads > 1:
+        return torch.zeros((num_blocks, heads, block_size, dim), dtype=dtype,
+                           device=device).permute(0, 2, 1, 3)
+    return torch.zeros((num_blocks, block_size, heads, dim), dtype=dtype, device=device)
+
+
 # ---------------------------------------------------------------- norms / activations
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float,
              residual: Optional[torch.Tensor] = None, gemma: bool = False,
@@ -104,6 +124,7 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: tor
         qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), cos_sin.data_ptr(), rot_dim,
         _native.ptr(q_norm_w), _native.ptr(k_norm_w), eps, _native.ptr(k_cache),
         _native.ptr(v_cache), _native.ptr(slot_mapping), T, Hq, Hkv, D, num_slots,
+        0 if k_cache is None else k_cache.shape[1], 0 if k_cache is None else kv_layout(k_cache),
         _native.status_word(qkv.device).data_ptr(), _native.stream_ptr())
     _native.check(rc, "qknorm_rope_kvwrite")
     launch_counter[0] += 1
@@ -211,7 +232,7 @@ def paged_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         meta.query_start_loc.data_ptr(), meta.seq_lens.data_ptr(), meta.block_table.data_ptr(),
         meta.block_table.stride(0), _native.ptr(meta.tile_seq), _native.ptr(meta.tile_qoff),
         num_tiles, Hq, Hkv, D, scale, int(causal), int(window), num_splits, out.data_ptr(),
-        out.stride(0), _native.ptr(scratch), rescale_threshold, v_lbo, v_sbo,
+        out.stride(0), _native.ptr(scratch), rescale_threshold, v_lbo, v_sbo, kv_layout(k_cache),
         _native.status_word(q.device).data_ptr(), _native.stream_ptr())
     _native.check(rc, "attn_fwd_tc")
     launch_counter[0] += 1 + (1 if num_splits > 1 else 0)
@@ -234,7 +255,7 @@ def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
         q.data_ptr(), q.stride(0), T, k_cache.data_ptr(), v_cache.data_ptr(), NB, BS,
         meta.query_start_loc.data_ptr(), meta.seq_lens.data_ptr(), meta.block_table.data_ptr(),
         meta.block_table.stride(0), num_seqs, Hq, Hkv, D, scale, int(window), num_splits,
-        out.data_ptr(), out.stride(0), _native.ptr(scratch),
+        out.data_ptr(), out.stride(0), _native.ptr(scratch), kv_layout(k_cache),
         _native.status_word(q.device).data_ptr(), _native.stream_ptr())
     _native.check(rc, "attn_decode_tc")
     launch_counter[0] += 1 + (1 if num_splits > 1 else 0)
@@ -247,6 +268,8 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     """CUDA-core flash-decode: one query token per sequence (q [B, Hq, D])."""
     B, Hq, D = q.shape
     NB, BS, Hkv, _ = k_cache.shape
+    if kv_layout(k_cache) != 0:
+        raise ValueError("the CUDA-core decode kernel reads [blocks, tokens, heads, D] caches only")
     scratch = None
     if num_splits > 1:
         scratch = _get_scratch(q.device, B * Hq * num_splits * (D + 1) * 4)
@@ -306,7 +329,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if mode == "tcgen05" and tc_ok:
             return paged_attention_tc(q, k_cache, v_cache, meta, scale, out, causal, window,
                                       num_splits=meta.num_splits)
-        if D in (64, 128) and G in (1, 2, 4, 8):
+        if D in (64, 128) and G in (1, 2, 4, 8) and k_cache.is_contiguous():
             return paged_decode(q, k_cache, v_cache, meta.block_table, meta.seq_lens, scale, out,
                                 window, num_splits=meta.num_splits)
         if tc_ok:

@@ -155,10 +155,10 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: tor
     if k_cache is not None and slot_mapping is not None:
         valid = slot_mapping >= 0
         slots = slot_mapping[valid]
-        kc = k_cache.view(-1, Hkv, D)
-        vc = v_cache.view(-1, Hkv, D)
-        kc[slots] = k[valid].to(kc.dtype)
-        vc[slots] = v[valid].to(vc.dtype)
+        bs = k_cache.shape[1]                      # works for any physical layout of the cache
+        blk, off = slots // bs, slots % bs
+        k_cache[blk, off] = k[valid].to(k_cache.dtype)
+        v_cache[blk, off] = v[valid].to(v_cache.dtype)
 
 
 def gather_kv(cache: torch.Tensor, block_table_row: torch.Tensor, seq_len: int) -> torch.Tensor:
