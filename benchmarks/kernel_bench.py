@@ -95,10 +95,10 @@ def bench_attn_decode(a):
     ):
         if a.impl not in ("both", name):
             continue
+        if name == "cuda-core" and a.kv_layout != "NHD":
+            continue        # that kernel reads [blocks, tokens, heads, D] caches only
         ns = a.splits or ops.choose_num_splits(B, a.hkv, ctx)
         ms = timeit(lambda: fn(ns), a.iters)
-        if name == "cuda-core" and a.kv_layout != "NHD":
-            continue
         print(f"attn-decode[{name}/{a.kv_layout}] B={B} ctx={ctx} Hq={a.hq} Hkv={a.hkv} D={a.d} splits={ns}: "
               f"{ms:.4f} ms  {bytes_kv / ms / 1e6:.0f} GB/s ({bytes_kv / ms / 1e6 / hbm:.2f} {tag})",
               flush=True)

@@ -125,3 +125,15 @@ def test_attn_decode_tc_sliding_window():
     torch.cuda.synchronize()
     exp = _ref(q, kc, vc, meta, scale, window=200)
     assert (out.float().cpu() - exp).abs().max().item() < 2e-2
+
+
+def test_attn_decode_tc_large_score_spread_triggers_rescale():
+    q, kc, vc, meta = make_paged_case([1, 2, 1], [1500, 700, 130], 8, 2, 128, 128, seed=13)
+    q = q * 6          # running max jumps by far more than the lazy-rescale threshold
+    scale = 128 ** -0.5
+    out = torch.full_like(q, float("nan"))
+    ops.paged_attention_decode_tc(q, kc, vc, meta, scale, out, 0, 1)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp = _ref(q, kc, vc, meta, scale)
+    assert (out.float().cpu() - exp).abs().max().item() < 3e-2

@@ -27,7 +27,7 @@ def _check(M, N, K, bn=0, bias=False, residual=False, seed=0):
     assert err < tol, f"M={M} N={N} K={K} bn={bn}: max abs err {err} (tol {tol})"
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (256, 512, 4096),
                                    (1, 256, 128), (77, 1024, 1024), (1000, 768, 2048),
                                    (4096, 6144, 4096)])
@@ -99,3 +99,23 @@ def test_grouped_gemm(swiglu):
         h = a[lo:hi].float() @ w[e].float().t()
         exp = torch.nn.functional.silu(h[:, :N]) * h[:, N:] if swiglu else h
         assert (out[lo:hi].float() - exp).abs().max().item() < 0.05, e
+
+
+def test_gemm_2cta_ragged_and_epilogues():
+    _check(130, 136, 72, bn=512)
+    _check(300, 512, 1024, bn=512, bias=True, residual=True)
+    _check(8192, 4096, 4096, bn=512)
+    _check(1000, 12288, 512, bn=512)
+
+
+@pytest.mark.parametrize("M,I,K", [(256, 128, 64), (300, 768, 2048), (1024, 12288, 4096), (5, 256, 512)])
+def test_gemm_2cta_swiglu(M, I, K):
+    g = torch.Generator(device="cpu").manual_seed(5)
+    a = (torch.randn(M, K, generator=g) * 0.3).bfloat16().to(DEV)
+    w = (torch.randn(2 * I, K, generator=g) * 0.1).bfloat16().to(DEV)
+    out = ops.linear_swiglu(a, w, two_cta=True)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    h = a.float() @ w.float().t()
+    exp = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
+    assert (out.float() - exp).abs().max().item() < 0.02 * exp.abs().max().item() + 0.02

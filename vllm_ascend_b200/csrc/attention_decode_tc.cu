@@ -29,6 +29,7 @@ constexpr int DEC_THREADS = 192;
 constexpr int DEC_NQ = 16;                 // MMA N: query rows per CTA
 constexpr int DEC_HALF = 128 * 128;        // 128 keys x 64 bf16
 constexpr int DEC_QHALF = DEC_NQ * 128;    // 16 rows x 64 bf16
+constexpr float kRescaleLog2 = 8.f;
 
 struct DecParams {
   const int* query_start_loc;
@@ -163,28 +164,37 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       for (int hf = 0; hf < NH; hf++)
         tma_load_4d(Qs + hf * DEC_QHALF, &tmap_q, q_full, hf * 64, 0, h, q_start);
     }
+    // Block ids are fetched one tile ahead (lane p holds the id of part p), so the
+    // dependent global load never sits between a freed stage and the next TMA issue.
+    auto load_blk = [&](int j) -> int {
+      if (j >= n || lane >= parts) return 0;
+      const int key0 = ((t0 + j) << 7) + lane * rpl;
+      return bt[min(key0, seq_len - 1) / p.block_size];
+    };
+    int blk_cur = load_blk(0);
     for (int j = 0; j < n; j++) {
       const int st = j % ST;
       const uint32_t ph = (uint32_t)(j / ST) & 1u;
       const int key_base = (t0 + j) << 7;
+      const int blk_next = load_blk(j + 1);
+      bool bad = blk_cur < 0 || blk_cur >= p.num_blocks_total;
+      bad = __any_sync(0xffffffffu, bad && lane < parts);
 #pragma unroll 1
       for (int kv = 0; kv < 2; kv++) {
         uint64_t* fullb = kv == 0 ? &k_full[st] : &v_full[st];
         uint64_t* emptyb = kv == 0 ? &k_empty[st] : &v_empty[st];
         if (!mbar_wait(emptyb, ph ^ 1u, abort_word)) goto done;
-        if (lane == 0) {
-          uint8_t* dst = (kv == 0 ? Ks : Vs) + st * Cfg::TILE_BYTES;
-          const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
-          mbar_expect_tx(fullb, Cfg::TILE_BYTES);
-          for (int part = 0; part < parts; part++) {
-            const int key0 = key_base + part * rpl;
-            const int kc = min(key0, seq_len - 1);
-            int blk = bt[kc / p.block_size];
-            if (blk < 0 || blk >= p.num_blocks_total) {
-              *abort_word = B200_BAD_INDEX;
-              blk = 0;
-            }
-            const int off = key0 % p.block_size;
+        if (bad) {
+          *abort_word = B200_BAD_INDEX;
+          goto done;
+        }
+        for (int part = 0; part < parts; part++) {
+          const int blk = __shfl_sync(0xffffffffu, blk_cur, part);
+          if (lane == 0) {
+            uint8_t* dst = (kv == 0 ? Ks : Vs) + st * Cfg::TILE_BYTES;
+            const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
+            if (part == 0) mbar_expect_tx(fullb, Cfg::TILE_BYTES);
+            const int off = (key_base + part * rpl) % p.block_size;
 #pragma unroll
             for (int hf = 0; hf < NH; hf++)
               tma_load_4d(dst + hf * DEC_HALF + part * rpl * 128, tm, fullb, hf * 64, h, off, blk);
@@ -192,6 +202,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         __syncwarp();
       }
+      blk_cur = blk_next;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -297,9 +308,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
           const float tm = fmaxf(fmaxf(red[c], red[DEC_NQ + c]),
                                  fmaxf(red[2 * DEC_NQ + c], red[3 * DEC_NQ + c]));
           const float mn = fmaxf(m[c], tm);
-          if (mn > m[c]) {
+          // lazy rescaling: the reference max only moves when it would grow by more than
+          // 2^kRescaleLog2, so probabilities stay below 2^kRescaleLog2 and most tiles never
+          // touch the O^T accumulator (which would serialise softmax behind the previous PV)
+          if (mn > m[c] && (m[c] == -INFINITY || (mn - m[c]) * sl2 > kRescaleLog2)) {
             alpha[c] = (m[c] == -INFINITY) ? 0.f : exp2f((m[c] - mn) * sl2);
-            any_change = true;
+            any_change = any_change || (m[c] != -INFINITY);
             m[c] = mn;
           }
           lsum[c] *= alpha[c];

@@ -57,8 +57,9 @@ struct AttCfg {
   static constexpr int NH = D / 64;
   static constexpr int KS = (D == 64) ? 4 : 2;
   static constexpr int TILE_BYTES = NH * ATT_HALF_BYTES;
-  static constexpr int P_BYTES = 2 * ATT_HALF_BYTES;
-  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KS) + P_BYTES + 1024 + 512;
+  static constexpr int P_BYTES = 2 * ATT_HALF_BYTES;   // one P buffer (two 64-key halves)
+  static constexpr int P_BUFS = 2;                     // P(j+1) is written while PV(j) runs
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KS) + P_BUFS * P_BYTES + 1024 + 512;
   static constexpr int TMEM_COLS = 512;
   static constexpr int O_COL = 256;
 };
@@ -114,7 +115,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint8_t* Ks = Qs + Cfg::TILE_BYTES;
   uint8_t* Vs = Ks + KS * Cfg::TILE_BYTES;
   uint8_t* Ps = Vs + KS * Cfg::TILE_BYTES;
-  uint64_t* bars = (uint64_t*)(Ps + Cfg::P_BYTES);
+  uint64_t* bars = (uint64_t*)(Ps + Cfg::P_BUFS * Cfg::P_BYTES);
   uint64_t* q_full = bars;              // 1
   uint64_t* k_full = bars + 1;          // KS
   uint64_t* k_empty = k_full + KS;      // KS
@@ -122,9 +123,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint64_t* v_empty = v_full + KS;      // KS
   uint64_t* s_ready = v_empty + KS;     // 2
   uint64_t* s_free = s_ready + 2;       // 2
-  uint64_t* p_ready = s_free + 2;       // 1
-  uint64_t* pv_done = p_ready + 1;      // 1
-  uint32_t* tmem_ptr = (uint32_t*)(pv_done + 1);
+  uint64_t* p_ready = s_free + 2;       // 2 (per P buffer)
+  uint64_t* pv_done = p_ready + 2;      // 2 (per P buffer)
+  uint32_t* tmem_ptr = (uint32_t*)(pv_done + 2);
   volatile int* abort_word = (volatile int*)(tmem_ptr + 1);
 
   if (threadIdx.x == 0) {
@@ -138,9 +139,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int b = 0; b < 2; b++) {
       mbar_init(&s_ready[b], 1);
       mbar_init(&s_free[b], 4);
+      mbar_init(&p_ready[b], 4);
+      mbar_init(&pv_done[b], 1);
     }
-    mbar_init(p_ready, 4);
-    mbar_init(pv_done, 1);
     *abort_word = 0;
     mbar_fence_init();
   }
@@ -169,36 +170,45 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       for (int hf = 0; hf < NH; hf++)
         tma_load_4d(Qs + hf * ATT_HALF_BYTES, &tmap_q, q_full, hf * 64, 0, h, q_start + tok0);
     }
+    // Block ids are fetched one tile ahead (lane p holds the id of part p), so the
+    // dependent global load never sits between a freed stage and the next TMA issue.
+    auto load_blk = [&](int j) -> int {
+      if (j >= n || lane >= parts) return 0;
+      const int key0 = ((t0 + j) << 7) + lane * rpl;
+      return bt[min(key0, seq_len - 1) / p.block_size];
+    };
+    int blk_cur = load_blk(0);
     for (int j = 0; j < n; j++) {
       const int ks = j % KS;
       const uint32_t ph = (uint32_t)(j / KS) & 1u;
       const int key_base = (t0 + j) << 7;
+      const int blk_next = load_blk(j + 1);
+      bool bad = blk_cur < 0 || blk_cur >= p.num_blocks_total;
+      bad = __any_sync(0xffffffffu, bad && lane < parts);
 #pragma unroll 1
       for (int kv = 0; kv < 2; kv++) {
         uint64_t* fullb = kv == 0 ? &k_full[ks] : &v_full[ks];
         uint64_t* emptyb = kv == 0 ? &k_empty[ks] : &v_empty[ks];
         if (!mbar_wait(emptyb, ph ^ 1u, abort_word)) goto done;
-        if (lane == 0) {
-          uint8_t* dst = (kv == 0 ? Ks : Vs) + ks * Cfg::TILE_BYTES;
-          const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
-          mbar_expect_tx(fullb, Cfg::TILE_BYTES);
-          for (int part = 0; part < parts; part++) {
-            const int key0 = key_base + part * rpl;
-            const int kc = min(key0, seq_len - 1);
-            int blk = bt[kc / p.block_size];
-            if (blk < 0 || blk >= p.num_blocks_total) {
-              *abort_word = B200_BAD_INDEX;  // reported; the load uses block 0
-              blk = 0;
-            }
-            const int off = key0 % p.block_size;
+        if (bad) {
+          *abort_word = B200_BAD_INDEX;
+          goto done;
+        }
+        for (int part = 0; part < parts; part++) {
+          const int blk = __shfl_sync(0xffffffffu, blk_cur, part);
+          if (lane == 0) {
+            uint8_t* dst = (kv == 0 ? Ks : Vs) + ks * Cfg::TILE_BYTES;
+            const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
+            if (part == 0) mbar_expect_tx(fullb, Cfg::TILE_BYTES);
+            const int off = (key_base + part * rpl) % p.block_size;
 #pragma unroll
             for (int hf = 0; hf < NH; hf++)
-              tma_load_4d(dst + hf * ATT_HALF_BYTES + part * rpl * 128, tm, fullb, hf * 64, h,
-                          off, blk);
+              tma_load_4d(dst + hf * ATT_HALF_BYTES + part * rpl * 128, tm, fullb, hf * 64, h, off, blk);
           }
         }
         __syncwarp();
       }
+      blk_cur = blk_next;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -237,19 +247,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const int vs = j % KS;
       const uint32_t ph = (uint32_t)(j / KS) & 1u;
       if (!mbar_wait(&v_full[vs], ph, abort_word)) goto done;
-      if (!mbar_wait(p_ready, (uint32_t)j & 1u, abort_word)) goto done;
+      const int pb = j & 1;
+      if (!mbar_wait(&p_ready[pb], ((uint32_t)j >> 1) & 1u, abort_word)) goto done;
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
         for (int kk = 0; kk < 8; kk++) {
           const uint32_t po = (kk >> 2) * ATT_HALF_BYTES + (kk & 3) * 32;
-          const uint64_t da = make_smem_desc(p_addr + po, 16, 1024, kLayoutSw128);
+          const uint64_t da =
+              make_smem_desc(p_addr + pb * Cfg::P_BYTES + po, 16, 1024, kLayoutSw128);
           const uint64_t db = make_smem_desc(v_addr + vs * Cfg::TILE_BYTES + kk * 2048, p.v_lbo,
                                              p.v_sbo, kLayoutSw128);
           umma_f16_ss(tmem_base + Cfg::O_COL, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[vs]);
-        umma_commit(pv_done);
+        umma_commit(&pv_done[pb]);
       }
       __syncwarp();
     }
@@ -301,17 +313,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (mx > m) {
         if (j == 0 || m == -INFINITY || (mx - m) * sl2 > p.rescale_threshold) {
           alpha = (m == -INFINITY) ? 0.f : exp2f((m - mx) * sl2);
-          need = (j > 0);
+          need = (j > 0) && (m != -INFINITY);   // an all-masked row has accumulated zeros only
           m = mx;
         }
       }
       l *= alpha;
       const bool warp_need = __any_sync(0xffffffffu, need && row_valid);
-      if (j > 0) {
-        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_word)) goto done;
-        tc_fence_after();
+      // P buffer j&1 was last read by PV(j-2); O must be quiescent only for a rescale
+      if (j >= 2) {
+        if (!mbar_wait(&pv_done[j & 1], (((uint32_t)j - 2) >> 1) & 1u, abort_word)) goto done;
       }
       if (warp_need) {
+        if (!mbar_wait(&pv_done[(j - 1) & 1], (((uint32_t)j - 1) >> 1) & 1u, abort_word)) goto done;
+        tc_fence_after();
         const float a = need ? alpha : 1.f;
 #pragma unroll 1
         for (int c = 0; c < D / 32; c++) {
@@ -345,7 +359,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
           rs += p0 + p1;
           pk[i >> 1] = pack_bf16x2(p0, p1);
         }
-        uint8_t* ph = prow + (c >> 1) * ATT_HALF_BYTES;
+        uint8_t* ph = prow + (j & 1) * Cfg::P_BYTES + (c >> 1) * ATT_HALF_BYTES;
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
           const int chunk = (c & 1) * 4 + q4;
@@ -359,11 +373,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&s_free[b]);
-        mbar_arrive(p_ready);
+        mbar_arrive(&p_ready[j & 1]);
       }
     }
     // ---- epilogue
-    if (!mbar_wait(pv_done, (uint32_t)(n - 1) & 1u, abort_word)) goto done;
+    if (!mbar_wait(&pv_done[(n - 1) & 1], (((uint32_t)n - 1) >> 1) & 1u, abort_word)) goto done;
     tc_fence_after();
     const float inv = l > 0.f ? 1.f / l : 0.f;
     const long tokidx = (long)q_start + tok0 + tok;

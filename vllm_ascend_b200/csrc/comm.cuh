@@ -41,14 +41,17 @@ __device__ __forceinline__ void fence_proxy_async_global() {
 // Bounded wait until *flag >= epoch (wrap-safe signed compare).  Returns false on
 // timeout after recording it in *status.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t epoch, int* status,
-                                             uint64_t budget_ns = B200_WAIT_NS) {
+                                             long long budget_cycles = B200_WAIT_CYCLES) {
   if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
     if ((++spins & 0x3f) == 0) {
-      if (globaltimer_ns() - t0 > budget_ns) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > budget_cycles) {
         if (status) atomicExch(status, B200_TIMEOUT);
         return false;
       }

@@ -73,7 +73,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Budget of a single in-kernel wait (nanoseconds of %globaltimer).
+// Budget of a single in-kernel wait, in SM clock cycles (~2 s at 2 GHz).  The clock is
+// only sampled every 256 failed polls so a wait that is satisfied quickly never pays for it.
+#ifndef B200_WAIT_CYCLES
+#define B200_WAIT_CYCLES 4000000000ll
+#endif
 #ifndef B200_WAIT_NS
 #define B200_WAIT_NS 2000000000ull
 #endif
@@ -83,13 +87,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_word) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0xff) == 0) {
       if (*abort_word != 0) return false;
-      if (globaltimer_ns() - t0 > B200_WAIT_NS) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > B200_WAIT_CYCLES) {
         *abort_word = B200_TIMEOUT;
         return false;
       }

@@ -1,0 +1,388 @@
+// bf16 GEMM with paired-CTA tensor-core instructions (tcgen05 cta_group::2):
+//   C[M,N] = A[M,K] * W[N,K]^T (+bias) (+residual)   or   silu(A Wg^T) * (A Wu^T)
+//
+// Two CTAs of a cluster (two neighbouring SMs) work on one 256 x 256 output tile.
+// Each CTA stages its own 128 rows of A and HALF of the W tile (128 rows), so a
+// stage costs 32 KB per CTA instead of 48 KB and the pipeline is 6 deep.  The
+// leader CTA issues `tcgen05.mma.cta_group::2` (M = 256): the hardware reads A
+// from both CTAs' shared memory and the two halves of W, and writes each CTA's
+// 128 x 256 half of the accumulator into that CTA's own TMEM.  Completion is
+// broadcast to both CTAs with `tcgen05.commit ... multicast::cluster`.
+// TMA loads are plain `cta_group::2` loads (no multicast): each CTA fetches its
+// own tiles and reports the bytes to the leader's barrier.
+//
+//   warp 0      TMA producer (both CTAs)
+//   warp 1      MMA issuer (leader CTA only) + TMEM alloc/dealloc (both)
+//   warps 2..5  epilogue (both CTAs, each for its own 128 rows)
+// All waits are bounded (common.cuh); the cluster barriers at start and end are
+// reached by every thread on every path.
+#include "common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace b200 {
+
+constexpr int G2_BM = 256;          // per CTA pair
+constexpr int G2_BN = 256;
+constexpr int G2_BK = 64;
+constexpr int G2_THREADS = 192;
+constexpr int G2_STAGES = 6;
+constexpr int G2_A_BYTES = 128 * G2_BK * 2;        // 16 KB: this CTA's rows of A
+constexpr int G2_B_BYTES = 128 * G2_BK * 2;        // 16 KB: this CTA's half of the W tile
+constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
+constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared address
+
+struct Gemm2Params {
+  int M, N, K, ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* C;
+  int* status;
+  int tiles_m, tiles_n;
+  int swiglu;          // W = [gate; up]: tile pairs 128 gate + 128 up columns
+  int up_row_offset;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;"
+               ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_2sm(void* dst, const CUtensorMap* map,
+                                                uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2sm() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_2sm(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at the same shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_2sm(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                      const __grid_constant__ CUtensorMap tmap_b, const Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* tiles = smem;
+  uint64_t* full_bar = (uint64_t*)(smem + G2_STAGES * G2_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + G2_STAGES;
+  uint64_t* tmem_full = empty_bar + G2_STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;          // [2] (the leader's copy is the one in use)
+  uint32_t* tmem_ptr = (uint32_t*)(tmem_empty + 2);
+  volatile int* abort_word = (volatile int*)(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G2_STAGES; s++) {
+      mbar_init(&full_bar[s], 1);     // leader's expect_tx arrival; bytes come from both CTAs
+      mbar_init(&empty_bar[s], 1);    // one commit from the leader's MMA warp
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 8);   // 4 epilogue warps of each CTA
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(tmem_ptr, 512);
+    tmem_relinquish_2sm();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // both CTAs' barriers exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = cluster_id; t < num_tiles; t += num_clusters) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const int a_row = tm * G2_BM + (int)rank * 128;
+      // plain: this CTA's 128 of the tile's 256 W rows.  SwiGLU: the leader stages the 128
+      // gate rows, the peer the matching 128 up rows.
+      const int w_row = p.swiglu ? tn * 128 + (int)rank * p.up_row_offset
+                                 : tn * G2_BN + (int)rank * 128;
+      for (int kb = 0; kb < num_kb; kb++) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) goto done;
+        if (lane == 0) {
+          uint8_t* sa = tiles + stage * G2_STAGE_BYTES;
+          uint8_t* sb = sa + G2_A_BYTES;
+          const uint32_t lbar = smem_u32(&full_bar[stage]) & kPeerBitMask;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * G2_STAGE_BYTES);
+          tma_load_2d_2sm(sa, &tmap_a, lbar, kb * G2_BK, a_row);
+          tma_load_2d_2sm(sb, &tmap_b, lbar, kb * G2_BK, w_row);
+        }
+        __syncwarp();
+        if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (leader) {
+      constexpr uint32_t idesc = make_idesc_f16(G2_BM, G2_BN, true, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = cluster_id; t < num_tiles; t += num_clusters, it++) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word)) goto done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * G2_BN;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word)) goto done;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sa = smem_u32(tiles + stage * G2_STAGE_BYTES);
+            const uint32_t sb = sa + G2_A_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < G2_BK / 16; kk++) {
+              const uint64_t da = make_smem_desc(sa + kk * 32, 16, 1024, kLayoutSw128);
+              const uint64_t db = make_smem_desc(sb + kk * 32, 16, 1024, kLayoutSw128);
+              umma_f16_ss_2sm(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit_2sm(&empty_bar[stage]);
+            if (kb == num_kb - 1) umma_commit_2sm(&tmem_full[acc]);
+          }
+          __syncwarp();
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const int out_per_tile = p.swiglu ? 128 : G2_BN;
+    int it = 0;
+    for (int t = cluster_id; t < num_tiles; t += num_clusters, it++) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_word)) goto done;
+      tc_fence_after();
+      const int row = tm * G2_BM + (int)rank * 128 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * G2_BN;
+      __nv_bfloat16* crow = p.C + (size_t)row * p.ldc;
+      const __nv_bfloat16* rrow = p.residual ? p.residual + (size_t)row * p.ldc : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < out_per_tile; c0 += 32) {
+        const int col0 = tn * out_per_tile + c0;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c0, r);
+        if (p.swiglu) {
+          uint32_t u[32];
+          tmem_ld_32x32b_x32(t_row + 128 + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const float g = __uint_as_float(r[j]);
+            r[j] = __float_as_uint(g / (1.f + __expf(-g)) * __uint_as_float(u[j]));
+          }
+        } else {
+          tmem_ld_wait();
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const int col = col0 + g * 8;
+            if (col < p.N) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; j++) v[j] = __uint_as_float(r[g * 8 + j]);
+              if (p.bias) {
+                const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  const float2 f = unpack_bf16x2(bw[j]);
+                  v[2 * j] += f.x;
+                  v[2 * j + 1] += f.y;
+                }
+              }
+              if (rrow) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + col);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  const float2 f = unpack_bf16x2(rw[j]);
+                  v[2 * j] += f.x;
+                  v[2 * j + 1] += f.y;
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]);
+              o.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(crow + col) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      // accumulator buffer drained: tell the leader's MMA warp (local or remote arrive)
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    const uint64_t t_start = globaltimer_ns();
+    while (globaltimer_ns() - t_start < 50000ull) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, *abort_word);
+  }
+  // neither CTA may free TMEM or leave while its partner can still signal it or read its tiles
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------- host
+struct Tmap2Key {
+  const void* ptr;
+  uint64_t rows, cols, ld;
+  bool operator==(const Tmap2Key& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld;
+  }
+};
+struct Tmap2Hash {
+  size_t operator()(const Tmap2Key& k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.cols;
+    h = h * 1000003u ^ k.ld;
+    return h;
+  }
+};
+
+// row-major bf16 [rows, cols], box = 128 rows x 64 columns, 128-byte swizzle
+static int get_tmap_128x64(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
+                           uint64_t ld) {
+  static std::unordered_map<Tmap2Key, CUtensorMap, Tmap2Hash> cache;
+  static std::mutex mu;
+  Tmap2Key key{ptr, rows, cols, ld};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  uint64_t dims[2] = {cols, rows};
+  uint64_t strides[1] = {ld * 2};
+  uint32_t box[2] = {64, 128};
+  int rc = make_tmap(out, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Same contract as b200_gemm_bf16; with swiglu != 0, W is [gate (N rows); up (N rows)]
+// (N a multiple of 128) and C[M, N] = silu(A Wg^T) * (A Wu^T).
+B200_API int b200_gemm_bf16_2cta(const void* A, const void* W, void* C, const void* bias,
+                                 const void* residual, int M, int N, int K, int lda, int ldw,
+                                 int ldc, int swiglu, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
+  if (swiglu && (N % 128)) return 9132;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         G2_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = get_tmap_128x64(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda);
+  if (rc) return rc;
+  rc = get_tmap_128x64(&tb, W, (uint64_t)(swiglu ? 2L * N : N), (uint64_t)K, (uint64_t)ldw);
+  if (rc) return rc;
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.swiglu = swiglu;
+  p.up_row_offset = N;
+  const int out_per_tile = swiglu ? 128 : G2_BN;
+  p.tiles_m = (M + G2_BM - 1) / G2_BM;
+  p.tiles_n = (N + out_per_tile - 1) / out_per_tile;
+  int clusters = p.tiles_m * p.tiles_n;
+  const int max_clusters = num_sms() / 2;
+  if (clusters > max_clusters) clusters = max_clusters;
+  gemm_bf16_2cta_kernel<<<2 * clusters, G2_THREADS, G2_SMEM_BYTES, stream>>>(ta, tb, p);
+  return B200_CHECK_LAUNCH();
+}

@@ -31,6 +31,8 @@ env_variables: dict[str, Callable[[], Any]] = {
     # back to the library path while a kernel is being validated) ----
     # bf16 GEMM: "tcgen05" (hand-written) or "cublas" (plain library GEMM)
     "VLLM_B200_GEMM": _str("VLLM_B200_GEMM", "tcgen05"),
+    # paired-CTA (cta_group::2) GEMM for M >= this many rows; 0 disables it
+    "VLLM_B200_GEMM_2CTA_MIN_M": _int("VLLM_B200_GEMM_2CTA_MIN_M", 256),
     # prefill attention: "tcgen05" or "sdpa" (torch fallback/oracle)
     "VLLM_B200_PREFILL_ATTN": _str("VLLM_B200_PREFILL_ATTN", "tcgen05"),
     "VLLM_B200_DECODE_ATTN": _str("VLLM_B200_DECODE_ATTN", "native"),

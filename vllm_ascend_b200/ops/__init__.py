@@ -159,16 +159,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if residual is not None:
         res2 = residual.view(M, N)
         assert res2.stride(0) == out.stride(0) and res2.stride(1) == 1
-    rc = _native.lib().b200_gemm_bf16(
-        x2.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias), _native.ptr(res2),
-        M, N, K, x2.stride(0), weight.stride(0), out.stride(0), bn,
-        _native.status_word(x.device).data_ptr(), 0, _native.stream_ptr())
+    min2 = envs.VLLM_B200_GEMM_2CTA_MIN_M
+    if bn == 512 or (bn == 0 and min2 > 0 and M >= min2 and N >= 256):
+        # paired-CTA kernel: 256 x 256 tiles issued with tcgen05 cta_group::2
+        rc = _native.lib().b200_gemm_bf16_2cta(
+            x2.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias),
+            _native.ptr(res2), M, N, K, x2.stride(0), weight.stride(0), out.stride(0), 0,
+            _native.status_word(x.device).data_ptr(), _native.stream_ptr())
+    else:
+        rc = _native.lib().b200_gemm_bf16(
+            x2.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias), _native.ptr(res2),
+            M, N, K, x2.stride(0), weight.stride(0), out.stride(0), bn,
+            _native.status_word(x.device).data_ptr(), 0, _native.stream_ptr())
     _native.check(rc, "gemm_bf16")
     launch_counter[0] += 1
     return out.view(*x.shape[:-1], N)
 
 
-def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+                  two_cta: bool = False) -> torch.Tensor:
     """silu(x @ Wg^T) * (x @ Wu^T) with weight = [Wg; Wu] ([2I, K]) in one GEMM: the tile pairs
     128 gate columns with the matching 128 up columns and the epilogue applies SiLU-mul
     (the reference fuses the same pair in its grouped-matmul+swiglu op, csrc/gmm)."""
@@ -183,7 +192,15 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Ten
     M = x2.shape[0]
     if out is None:
         out = torch.empty((M, I), dtype=x.dtype, device=x.device)
-    if M > 0:
+    min2 = envs.VLLM_B200_GEMM_2CTA_MIN_M
+    if M > 0 and (two_cta or (min2 > 0 and M >= min2)):
+        rc = _native.lib().b200_gemm_bf16_2cta(
+            x2.data_ptr(), weight.data_ptr(), out.data_ptr(), None, None, M, I, K, x2.stride(0),
+            weight.stride(0), out.stride(0), 1, _native.status_word(x.device).data_ptr(),
+            _native.stream_ptr())
+        _native.check(rc, "gemm_swiglu_2cta")
+        launch_counter[0] += 1
+    elif M > 0:
         rc = _native.lib().b200_gemm_swiglu_bf16(
             x2.data_ptr(), weight.data_ptr(), out.data_ptr(), M, I, K, x2.stride(0),
             weight.stride(0), out.stride(0), _native.status_word(x.device).data_ptr(),
