@@ -33,7 +33,7 @@ _SIGNATURES = {
     "b200_paged_decode": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, I, P, L, P, L, P, P],
     "b200_attn_fwd_tc": [P, L, L, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P, L, P,
                          F, U, U, I, P, P],
-    "b200_attn_decode_tc": [P, L, L, P, P, L, I, P, P, P, I, I, I, I, I, F, I, I, P, L, P, I, P, P],
+    "b200_attn_decode_tc": [P, L, L, P, P, L, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, P, P],
     "b200_argmax": [P, I, L, I, I, P, P],
     "b200_cast_bf16_f32": [P, L, P, L, I, I, P],
     "b200_apply_penalties": [P, L, I, I, P, I, P, I, P, P, P, P],

@@ -45,6 +45,7 @@ struct DecParams {
   float* partial_lse;
   long num_blocks_total;
   int* status;
+  long long* timeline;   // optional [3 roles][64 tiles][8 stamps] of clock64, CTA (0,0,0) only
 };
 
 template <int D>
@@ -61,9 +62,21 @@ struct DecCfg {
   static constexpr int O_COL = 32;
 };
 
+// Device-side timeline: stamp k of tile j for a role (0 producer, 1 MMA issuer, 2 softmax).
+#define DEC_STAMP(role, j, k)                                                            \
+  do {                                                                                 \
+    if (tl && (j) < 64) tl[((role) * 64 + (j)) * 8 + (k)] = clock64() - tl_t0;          \
+  } while (0)
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int D>
+template <int D, int NVT>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
@@ -89,6 +102,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int t1 = min(tile_hi, t0 + per_split);
   const int n = t1 - t0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long* tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0)
+                      ? p.timeline : nullptr;
+  const long long tl_t0 = clock64();
 
   if (n <= 0) {
     if (p.num_splits > 1) {
@@ -184,6 +200,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         uint64_t* fullb = kv == 0 ? &k_full[st] : &v_full[st];
         uint64_t* emptyb = kv == 0 ? &k_empty[st] : &v_empty[st];
         if (!mbar_wait(emptyb, ph ^ 1u, abort_word)) goto done;
+        DEC_STAMP(0, j, kv);
         if (bad) {
           *abort_word = B200_BAD_INDEX;
           goto done;
@@ -216,6 +233,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const uint32_t ph = (uint32_t)(j / ST) & 1u;
       const int b = j & 1;
       if (!mbar_wait(&k_full[st], ph, abort_word)) return false;
+      DEC_STAMP(1, j, 0);
       if (!mbar_wait(&s_free[b], (((uint32_t)j >> 1) & 1u) ^ 1u, abort_word)) return false;
       tc_fence_after();
       if (lane == 0) {
@@ -243,7 +261,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const uint32_t ph = (uint32_t)(j / ST) & 1u;
       const int pb = j & 1;
       if (!mbar_wait(&v_full[st], ph, abort_word)) goto done;
+      DEC_STAMP(1, j, 1);
       if (!mbar_wait(&p_ready[pb], ((uint32_t)j >> 1) & 1u, abort_word)) goto done;
+      DEC_STAMP(1, j, 2);
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
@@ -263,17 +283,31 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
   } else {
     // ------------------------------------------------------------ softmax / epilogue
+    // NVT = compile-time bound on the valid columns (query rows x heads of the group).
     const int qd = warp & 3;
     const int tid = qd * 32 + lane;                 // key inside the tile; d index for O^T
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
     const float sl2 = p.scale_log2;
-    float m[DEC_NQ], lsum[DEC_NQ];
+    float m[NVT], lsum[NVT];
+    int hi[NVT], lo[NVT];                           // keys [lo, hi) are visible to column c
+    int hi_min = seq_len, lo_max = 0;
 #pragma unroll
-    for (int c = 0; c < DEC_NQ; c++) { m[c] = -INFINITY; lsum[c] = 0.f; }
+    for (int c = 0; c < NVT; c++) {
+      m[c] = -INFINITY;
+      lsum[c] = 0.f;
+      const int q_pos = ctx + min(c / G, q_len - 1);
+      hi[c] = min(seq_len, q_pos + 1);
+      lo[c] = p.window > 0 ? max(0, q_pos - p.window + 1) : 0;
+      hi_min = min(hi_min, hi[c]);
+      lo_max = max(lo_max, lo[c]);
+    }
+    int* redi = reinterpret_cast<int*>(red);        // [2 tiles][4 warps][16]
 
     for (int j = 0; j < n; j++) {
       const int b = j & 1;
+      if (warp == 2) DEC_STAMP(2, j, 0);
       if (!mbar_wait(&s_ready[b], ((uint32_t)j >> 1) & 1u, abort_word)) goto done;
+      if (warp == 2) DEC_STAMP(2, j, 1);
       tc_fence_after();
       uint32_t r[16];
       tmem_ld_32x32b_x16(t_lane + b * DEC_NQ, r);
@@ -281,44 +315,43 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[b]);
-      const int key = ((t0 + j) << 7) + tid;
-      float s[DEC_NQ];
-      float wmax[DEC_NQ];
+      const int tile_base = (t0 + j) << 7;
+      const int key = tile_base + tid;
+      // only tiles that straddle a visibility limit need per-key masking
+      const bool need_mask = (tile_base + 128 > hi_min) || (tile_base < lo_max);
+      float s[NVT];
+      int* rj = redi + (j & 1) * 64 + qd * 16;
 #pragma unroll
-      for (int c = 0; c < DEC_NQ; c++) {
-        if (c < nv) {
-          const int q_pos = ctx + c / G;
-          const bool ok = key < seq_len && key <= q_pos && (p.window <= 0 || key > q_pos - p.window);
-          s[c] = ok ? __uint_as_float(r[c]) : -INFINITY;
-          wmax[c] = warp_reduce_max(s[c]);
-        }
+      for (int c = 0; c < NVT; c++) {
+        s[c] = __uint_as_float(r[c]);
+        if (need_mask && !(key >= lo[c] && key < hi[c])) s[c] = -INFINITY;
+        int ob = __float_as_int(s[c]);
+        ob ^= (ob >> 31) & 0x7fffffff;              // order-preserving float -> int
+        const int wm = __reduce_max_sync(0xffffffffu, ob);
+        if (lane == 0) rj[c] = wm;
       }
-      if (lane == 0) {
-#pragma unroll
-        for (int c = 0; c < DEC_NQ; c++)
-          if (c < nv) red[qd * DEC_NQ + c] = wmax[c];
-      }
+      if (warp == 2) DEC_STAMP(2, j, 5);
       softmax_bar();
+      if (warp == 2) DEC_STAMP(2, j, 6);
+      const int* ra = redi + (j & 1) * 64;
       bool any_change = false;
-      float alpha[DEC_NQ];
+      float alpha[NVT];
 #pragma unroll
-      for (int c = 0; c < DEC_NQ; c++) {
+      for (int c = 0; c < NVT; c++) {
+        int t = max(max(ra[c], ra[16 + c]), max(ra[32 + c], ra[48 + c]));
+        t ^= (t >> 31) & 0x7fffffff;
+        const float mn = fmaxf(m[c], __int_as_float(t));
         alpha[c] = 1.f;
-        if (c < nv) {
-          const float tm = fmaxf(fmaxf(red[c], red[DEC_NQ + c]),
-                                 fmaxf(red[2 * DEC_NQ + c], red[3 * DEC_NQ + c]));
-          const float mn = fmaxf(m[c], tm);
-          // lazy rescaling: the reference max only moves when it would grow by more than
-          // 2^kRescaleLog2, so probabilities stay below 2^kRescaleLog2 and most tiles never
-          // touch the O^T accumulator (which would serialise softmax behind the previous PV)
-          if (mn > m[c] && (m[c] == -INFINITY || (mn - m[c]) * sl2 > kRescaleLog2)) {
-            alpha[c] = (m[c] == -INFINITY) ? 0.f : exp2f((m[c] - mn) * sl2);
-            any_change = any_change || (m[c] != -INFINITY);
-            m[c] = mn;
-          }
-          lsum[c] *= alpha[c];
+        // lazy rescaling: the reference max only moves when it would grow by more than
+        // 2^kRescaleLog2, so most tiles never touch the O^T accumulator
+        if (mn > m[c] && (m[c] == -INFINITY || (mn - m[c]) * sl2 > kRescaleLog2)) {
+          alpha[c] = (m[c] == -INFINITY) ? 0.f : fast_exp2((m[c] - mn) * sl2);
+          any_change = any_change || (m[c] != -INFINITY);
+          m[c] = mn;
         }
+        lsum[c] *= alpha[c];
       }
+      if (warp == 2) DEC_STAMP(2, j, 7);
       // P buffer j&1 was last read by PV(j-2)
       if (j >= 2) {
         if (!mbar_wait(&pv_done[j & 1], (((uint32_t)j - 2) >> 1) & 1u, abort_word)) goto done;
@@ -326,44 +359,41 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (j > 0 && any_change) {    // uniform over the 128 threads: O^T must be quiescent
         if (!mbar_wait(&pv_done[(j - 1) & 1], (((uint32_t)j - 1) >> 1) & 1u, abort_word)) goto done;
         tc_fence_after();
-        {
-          uint32_t o[16];
-          tmem_ld_32x32b_x16(t_lane + Cfg::O_COL, o);
-          tmem_ld_wait();
+        uint32_t o[16];
+        tmem_ld_32x32b_x16(t_lane + Cfg::O_COL, o);
+        tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < DEC_NQ; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c]);
-          tmem_st_32x32b_x16(t_lane + Cfg::O_COL, o);
-          tmem_st_wait();
-        }
+        for (int c = 0; c < NVT; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c]);
+        tmem_st_32x32b_x16(t_lane + Cfg::O_COL, o);
+        tmem_st_wait();
       }
-      // probabilities of this key for every valid column -> P[c][key] (K-major, swizzled)
+      if (warp == 2) DEC_STAMP(2, j, 2);
+      // probabilities of this key for every column -> P[c][key] (K-major, swizzled)
       uint8_t* pbase = Ps + (j & 1) * Cfg::P_BYTES + (tid >> 6) * DEC_QHALF;
       const int kin = tid & 63;
 #pragma unroll
-      for (int c = 0; c < DEC_NQ; c++) {
-        if (c < nv) {
-          const float mb = (m[c] == -INFINITY) ? 0.f : m[c] * sl2;
-          const float pv = exp2f(s[c] * sl2 - mb);
-          lsum[c] += pv;
-          const int chunk = (kin >> 3) ^ (c & 7);
-          *reinterpret_cast<__nv_bfloat16*>(pbase + c * 128 + (chunk << 4) + (kin & 7) * 2) =
-              __float2bfloat16(pv);
-        }
+      for (int c = 0; c < NVT; c++) {
+        const float mb = (m[c] == -INFINITY) ? 0.f : m[c] * sl2;
+        const float pv = fast_exp2(s[c] * sl2 - mb);
+        lsum[c] += pv;
+        const int chunk = (kin >> 3) ^ (c & 7);
+        *reinterpret_cast<__nv_bfloat16*>(pbase + c * 128 + (chunk << 4) + (kin & 7) * 2) =
+            __float2bfloat16(pv);
       }
       tc_fence_before();
       fence_proxy_async_smem();
-      softmax_bar();            // all red[] reads done before the next tile overwrites it
+      __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[j & 1]);
+      if (warp == 2) DEC_STAMP(2, j, 3);
     }
     // ---- epilogue: total row sums, normalise, store
     if (!mbar_wait(&pv_done[(n - 1) & 1], (((uint32_t)n - 1) >> 1) & 1u, abort_word)) goto done;
     tc_fence_after();
+    softmax_bar();          // every thread is past its last read of the reduction scratch
 #pragma unroll
-    for (int c = 0; c < DEC_NQ; c++) {
-      if (c < nv) {
-        const float w = warp_reduce_sum(lsum[c]);
-        if (lane == 0) red[qd * DEC_NQ + c] = w;
-      }
+    for (int c = 0; c < NVT; c++) {
+      const float w = warp_reduce_sum(lsum[c]);
+      if (lane == 0) red[qd * DEC_NQ + c] = w;
     }
     softmax_bar();
     uint32_t o[16];
@@ -371,7 +401,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tmem_ld_wait();
     if (tid < D) {
 #pragma unroll
-      for (int c = 0; c < DEC_NQ; c++) {
+      for (int c = 0; c < NVT; c++) {
         if (c < nv) {
           const float l = red[c] + red[DEC_NQ + c] + red[2 * DEC_NQ + c] + red[3 * DEC_NQ + c];
           const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -445,8 +475,9 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
                                  const void* query_start_loc, const void* seq_lens,
                                  const void* block_table, int max_blocks, int num_seqs, int Hq,
                                  int Hkv, int D, float scale, int window, int num_splits,
-                                 void* out, long out_stride, void* scratch, int kv_layout,
-                                 int* status, cudaStream_t stream) {
+                                 int max_q_len, void* out, long out_stride, void* scratch,
+                                 int kv_layout,
+                                 int* status, void* timeline, cudaStream_t stream) {
   using namespace b200;
   if (num_seqs <= 0 || T <= 0) return 0;
   const int G = Hq / Hkv;
@@ -499,18 +530,32 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
   p.partial_lse = scratch ? (float*)scratch + T * Hq * (long)num_splits * D : nullptr;
   p.num_blocks_total = num_blocks;
   p.status = status;
+  p.timeline = (long long*)timeline;
   using Cfg = DecCfg<128>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<128>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
   if (num_seqs > 65535) return 9125;
   dim3 grid((unsigned)Hkv, (unsigned)num_seqs, (unsigned)num_splits);
-  attn_decode_tc_kernel<128><<<grid, DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  // columns that can be valid: query tokens per sequence x heads per group
+  if (max_q_len < 1) max_q_len = 1;
+  const int ncols = max_q_len * G;
+  if (ncols > DEC_NQ) return 9126;
+#define LAUNCH_DEC_TC(NV)                                                                   \
+  do {                                                                                      \
+    static bool attr_set = false;                                                           \
+    if (!attr_set) {                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<128, NV>,                  \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                           Cfg::SMEM_BYTES);                                \
+      if (e != cudaSuccess) return (int)e;                                                  \
+      attr_set = true;                                                                      \
+    }                                                                                       \
+    attn_decode_tc_kernel<128, NV><<<grid, DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p); \
+  } while (0)
+  if (ncols <= 1) LAUNCH_DEC_TC(1);
+  else if (ncols <= 2) LAUNCH_DEC_TC(2);
+  else if (ncols <= 4) LAUNCH_DEC_TC(4);
+  else if (ncols <= 8) LAUNCH_DEC_TC(8);
+  else LAUNCH_DEC_TC(16);
+#undef LAUNCH_DEC_TC
   int rc = B200_CHECK_LAUNCH();
   if (rc) return rc;
   if (num_splits > 1)

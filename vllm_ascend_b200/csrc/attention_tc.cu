@@ -52,6 +52,12 @@ struct AttnParams {
   float rescale_threshold;
 };
 
+__device__ __forceinline__ float att_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 struct AttCfg {
   static constexpr int NH = D / 64;
@@ -289,30 +295,37 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // mask needed when the tile is not entirely inside every row's window
       const bool need_mask = (tile_base + 128 > min(seq_len, p.causal ? ctx + tok0 + 1 : seq_len)) ||
                              (p.window > 0);
-      // ---- pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_lane + b * 128 + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      // ---- the whole score row lives in registers: one TMEM read, no second pass
+      uint32_t sreg[128];
+      tmem_ld_32x32b_x32(t_lane + b * 128, sreg);
+      tmem_ld_32x32b_x32(t_lane + b * 128 + 32, sreg + 32);
+      tmem_ld_32x32b_x32(t_lane + b * 128 + 64, sreg + 64);
+      tmem_ld_32x32b_x32(t_lane + b * 128 + 96, sreg + 96);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[b]);
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) {
-            const int key = tile_base + c * 32 + i;
-            const float s = __uint_as_float(r[i]);
-            mx = fmaxf(mx, (key >= lo && key < hi) ? s : -INFINITY);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < 128; i++) {
+          const int key = tile_base + i;
+          if (!(key >= lo && key < hi)) sreg[i] = 0xff800000u;   // -inf
         }
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sreg[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sreg[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sreg[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sreg[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       float alpha = 1.f;
       bool need = false;
       if (mx > m) {
         if (j == 0 || m == -INFINITY || (mx - m) * sl2 > p.rescale_threshold) {
-          alpha = (m == -INFINITY) ? 0.f : exp2f((m - mx) * sl2);
+          alpha = (m == -INFINITY) ? 0.f : att_exp2((m - mx) * sl2);
           need = (j > 0) && (m != -INFINITY);   // an all-masked row has accumulated zeros only
           m = mx;
         }
@@ -338,43 +351,31 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         tmem_st_wait();
       }
-      // ---- pass 2: probabilities -> swizzled shared memory (A operand of P V)
-      const float mb = (m == -INFINITY) ? 0.f : m * sl2;
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_lane + b * 128 + c * 32, r);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      // ---- probabilities -> swizzled shared memory (A operand of P V)
+      const float nmb = (m == -INFINITY) ? 0.f : -m * sl2;
+      float rs0 = 0.f, rs1 = 0.f;
+      uint8_t* pbuf = prow + (j & 1) * Cfg::P_BYTES;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-          if (need_mask) {
-            const int key = tile_base + c * 32 + i;
-            if (!(key >= lo && key < hi)) s0 = -INFINITY;
-            if (!(key + 1 >= lo && key + 1 < hi)) s1 = -INFINITY;
-          }
-          const float p0 = exp2f(s0 * sl2 - mb), p1 = exp2f(s1 * sl2 - mb);
-          rs += p0 + p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
-        }
-        uint8_t* ph = prow + (j & 1) * Cfg::P_BYTES + (c >> 1) * ATT_HALF_BYTES;
+      for (int c8 = 0; c8 < 16; c8++) {            // 16 chunks of 8 keys = one 16-byte store
+        uint32_t pk[4];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; q4++) {
-          const int chunk = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(ph + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        for (int q2 = 0; q2 < 4; q2++) {
+          const int i = c8 * 8 + q2 * 2;
+          const float p0 = att_exp2(fmaf(__uint_as_float(sreg[i]), sl2, nmb));
+          const float p1 = att_exp2(fmaf(__uint_as_float(sreg[i + 1]), sl2, nmb));
+          rs0 += p0;
+          rs1 += p1;
+          pk[q2] = pack_bf16x2(p0, p1);
         }
+        const int chunk = c8 & 7;
+        *reinterpret_cast<uint4*>(pbuf + (c8 >> 3) * ATT_HALF_BYTES + ((chunk ^ (row & 7)) << 4)) =
+            make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      l += rs;
+      l += rs0 + rs1;
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_free[b]);
-        mbar_arrive(&p_ready[j & 1]);
-      }
+      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
     }
     // ---- epilogue
     if (!mbar_wait(&pv_done[(n - 1) & 1], (((uint32_t)n - 1) >> 1) & 1u, abort_word)) goto done;

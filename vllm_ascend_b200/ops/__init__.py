@@ -258,7 +258,8 @@ def paged_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
 
 def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
                               scale: float, out: torch.Tensor, window: int = 0,
-                              num_splits: int = 1, num_seqs: Optional[int] = None) -> torch.Tensor:
+                              num_splits: int = 1, num_seqs: Optional[int] = None,
+                              timeline: Optional[torch.Tensor] = None, max_q_len: int = 0) -> torch.Tensor:
     """tcgen05 flash-decode (keys on the MMA M axis): the first ``num_seqs`` sequences of the
     batch, each with at most 16/G query tokens; ``q``/``out`` hold exactly their tokens."""
     T, Hq, D = q.shape
@@ -272,8 +273,9 @@ def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
         q.data_ptr(), q.stride(0), T, k_cache.data_ptr(), v_cache.data_ptr(), NB, BS,
         meta.query_start_loc.data_ptr(), meta.seq_lens.data_ptr(), meta.block_table.data_ptr(),
         meta.block_table.stride(0), num_seqs, Hq, Hkv, D, scale, int(window), num_splits,
-        out.data_ptr(), out.stride(0), _native.ptr(scratch), kv_layout(k_cache),
-        _native.status_word(q.device).data_ptr(), _native.stream_ptr())
+        max_q_len if max_q_len else min(meta.max_query_len, 16 // (Hq // Hkv)), out.data_ptr(),
+        out.stride(0), _native.ptr(scratch), kv_layout(k_cache),
+        _native.status_word(q.device).data_ptr(), _native.ptr(timeline), _native.stream_ptr())
     _native.check(rc, "attn_decode_tc")
     launch_counter[0] += 1 + (1 if num_splits > 1 else 0)
     return out
@@ -338,7 +340,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         # kernel, the work list of the prefill kernel covers the remaining sequences
         nd, ndt = meta.num_decodes, meta.num_decode_tokens
         paged_attention_decode_tc(q[:ndt], k_cache, v_cache, meta, scale, out[:ndt], window,
-                                  num_splits=1, num_seqs=nd)
+                                  num_splits=1, num_seqs=nd, max_q_len=1)
         if meta.num_tiles > 0:
             paged_attention_tc(q, k_cache, v_cache, meta, scale, out, causal, window)
         return out
