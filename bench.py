@@ -285,6 +285,9 @@ def main():
             "preemptions": llm.engine.scheduler.num_preemptions,
             "host_breakdown_s": {**{k: round(v, 3) for k, v in llm.engine.host_times.items()},
                                  **{k: round(runner.stats[k], 3) for k in ("t_prepare", "t_launch", "t_wait")},
+                                 **{k: (round(v, 3) if isinstance(v, float) else v)
+                                    for k, v in runner.stats.items()
+                                    if k[:2] in ("t_", "n_") and k.split("_", 1)[1] in ("decode", "decode_eager", "mixed")},
                                  "note": "cumulative over warm-up and timed passes"},
         }))
     if world > 1:

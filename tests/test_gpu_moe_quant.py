@@ -1,0 +1,84 @@
+"""Native MoE kernels and block-scaled fp8 GEMMs vs PyTorch references."""
+import pytest
+import torch
+
+from vllm_ascend_b200 import _native, ops
+from vllm_ascend_b200.ops import fused_moe, moe_native, reference as ref
+from vllm_ascend_b200.quantization import schemes
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("E,k,scoring,n_group,topk_group,bias", [
+    (128, 8, "softmax", 1, 1, False), (256, 8, "sigmoid", 8, 4, True), (8, 2, "softmax", 1, 1, False),
+    (64, 6, "sigmoid", 4, 2, False), (160, 6, "softmax", 1, 1, True)])
+def test_gating_topk(E, k, scoring, n_group, topk_group, bias):
+    torch.manual_seed(E + k)
+    T = 77
+    logits = torch.randn(T, E, device=DEV) * 2
+    b = torch.randn(E, device=DEV) * 0.1 if bias else None
+    w, ids = moe_native.gating_topk(logits, k, scoring, True, n_group, topk_group, b, 2.5)
+    ew, eids = fused_moe.gating_topk_ref(logits, k, scoring, True, n_group, topk_group, b, 2.5)
+    assert torch.equal(ids.sort(-1).values, eids.sort(-1).values)
+    order = ids.long().argsort(-1)
+    eorder = eids.long().argsort(-1)
+    assert torch.allclose(w.gather(1, order), ew.gather(1, eorder), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("T,E,k,H,I,local", [(64, 8, 2, 256, 128, None), (300, 16, 4, 512, 256, (4, 12)),
+                                             (1, 8, 2, 128, 128, None), (1000, 128, 8, 2048, 768, None)])
+def test_fused_experts_native_matches_reference(T, E, k, H, I, local):
+    torch.manual_seed(T)
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    Elocal = E if local is None else local[1] - local[0]
+    w13 = (torch.randn(Elocal, 2 * I, H, device=DEV) * 0.05).bfloat16()
+    w2 = (torch.randn(Elocal, H, I, device=DEV) * 0.05).bfloat16()
+    logits = torch.randn(T, E, device=DEV)
+    tw, ids = fused_moe.gating_topk_ref(logits, k)
+    emap = None
+    if local is not None:
+        emap = torch.full((E,), -1, dtype=torch.int32, device=DEV)
+        emap[local[0]:local[1]] = torch.arange(Elocal, dtype=torch.int32, device=DEV)
+    got = moe_native.fused_experts(x, w13, w2, tw, ids, emap)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp = fused_moe.fused_experts_ref(x.float(), w13.float(), w2.float(), tw, ids, emap)
+    assert (got.float() - exp).abs().max() < 0.03 * exp.abs().max() + 0.02
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 512, 1024), (4096, 4096, 4096), (5, 1536, 7168), (777, 136, 256)])
+def test_fp8_block_gemm(M, N, K):
+    torch.manual_seed(M)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = torch.randn(N, K, device=DEV) * 0.1
+    w8, ws = schemes.quantize_weight_block_fp8(w)
+    got = schemes.fp8_block_linear(x, w8, ws)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp = ref.block_fp8_linear(x, w8, ws, out_dtype=torch.float32)
+    assert (got.float() - exp).abs().max() < 0.01 * exp.abs().max() + 0.02
+    full = x.float() @ w.t()
+    assert (got.float() - full).abs().max() < 0.08 * full.abs().max()
+
+
+def test_fp8_experts_native_matches_reference():
+    torch.manual_seed(9)
+    T, E, k, H, I = 200, 8, 2, 512, 256
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+
+    class Blk:
+        pass
+    blk = Blk()
+    blk.w13 = torch.randn(E, 2 * I, H, device=DEV) * 0.05
+    blk.w2 = torch.randn(E, H, I, device=DEV) * 0.05
+    sch = schemes.Fp8BlockMoE()
+    sch.convert(blk)
+    tw, ids = fused_moe.gating_topk_ref(torch.randn(T, E, device=DEV), k)
+    got = moe_native.fused_experts_fp8(x, blk.w13, blk.w13_scale, blk.w2, blk.w2_scale, tw, ids, None)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    xc, twc, idc = x.cpu(), tw.cpu(), ids.cpu()
+    blk.w13, blk.w13_scale, blk.w2, blk.w2_scale = (t.cpu() for t in (blk.w13, blk.w13_scale, blk.w2, blk.w2_scale))
+    exp = sch.apply_experts(xc, blk.w13, blk.w2, twc, idc, None)
+    assert (got.float().cpu() - exp.float()).abs().max() < 0.04 * exp.float().abs().max() + 0.02

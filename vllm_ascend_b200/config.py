@@ -251,6 +251,7 @@ class SchedulerConfig:
     policy: str = "fcfs"               # fcfs | short_request_first | batch_job | recompute
     async_scheduling: bool = False
     reserve_full_sequence: bool = True   # admit only what can finish without preemption
+    decode_batch_alignment: int = 1      # rows per decode GEMM tile (256 on GPU, see Scheduler)
 
 
 @dataclass

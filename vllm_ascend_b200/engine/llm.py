@@ -222,6 +222,8 @@ class LLM:
             additional_config=additional_config or {}, device=device, seed=seed,
             kv_transfer_config=kv_transfer_config, speculative_config=speculative_config,
             enable_sleep_mode=enable_sleep_mode)
+        if device == "cuda":
+            cfg.scheduler.decode_batch_alignment = 256
         from ..platform_config import check_and_update_config
         check_and_update_config(cfg)
         self.cfg = cfg

@@ -336,6 +336,9 @@ class ModelRunner:
             toks = tokens.numpy()
         self.stats["d2h_bytes"] += n * 8
         t_sync = time.perf_counter()
+        key = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
+        self.stats["t_" + key] = self.stats.get("t_" + key, 0.0) + (t_sync - t_start)
+        self.stats["n_" + key] = self.stats.get("n_" + key, 0) + 1
         self.stats["t_prepare"] += t_prep - t_start
         self.stats["t_launch"] += t_launch - t_prep
         self.stats["t_wait"] += t_sync - t_launch

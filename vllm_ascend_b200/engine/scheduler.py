@@ -54,6 +54,7 @@ class Scheduler:
         self.reserve_full = getattr(sched_cfg, "reserve_full_sequence", True)
         self._committed_blocks = 0
         self._commit: dict[str, int] = {}
+        self.decode_batch_alignment = getattr(sched_cfg, "decode_batch_alignment", 1)
         self._free_rows = list(range(sched_cfg.max_num_seqs - 1, -1, -1))
         self._hashes: dict[str, list[bytes]] = {}
         # stats
@@ -104,7 +105,19 @@ class Scheduler:
         if not self.pool.can_allocate(num_new_blocks):
             return False
         if self.reserve_full and self.running:
-            return self._committed_blocks + self._final_blocks(req) <= self.pool.num_blocks - 1
+            fb = self._final_blocks(req)
+            room = self.pool.num_blocks - 1 - self._committed_blocks
+            if fb > room:
+                return False
+            # Decode GEMMs work on tiles of `decode_batch_alignment` rows.  When the KV pool
+            # (not max_num_seqs) limits the batch, stopping at a full tile instead of a few
+            # rows into the next one avoids computing a mostly empty tile on every step.
+            a = self.decode_batch_alignment
+            n = len(self.running)
+            if a > 1 and n >= a and n % a == 0:
+                fit = room // max(fb, 1)
+                if fit < a and len(self.waiting) > fit and n + fit < self.cfg.max_num_seqs:
+                    return False
         return True
 
     def _commit_blocks(self, req: Request) -> None:

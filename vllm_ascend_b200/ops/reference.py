@@ -284,14 +284,18 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 # ---------------------------------------------------------------- quantization
 def quant_fp8_group128(x: torch.Tensor, pow2_scale: bool = False):
+    """Per-token groups of 128 columns (the last group may be shorter)."""
     T, H = x.shape
-    xg = x.float().view(T, H // 128, 128)
+    G = (H + 127) // 128
+    xp = torch.zeros(T, G * 128, dtype=torch.float32, device=x.device)
+    xp[:, :H] = x.float()
+    xg = xp.view(T, G, 128)
     amax = xg.abs().amax(dim=-1).clamp_min(1e-10)
     scale = amax / 448.0
     if pow2_scale:
         scale = torch.exp2(torch.ceil(torch.log2(scale)))
     q = (xg / scale.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn)
-    return q.view(T, H), scale
+    return q.view(T, G * 128)[:, :H].contiguous(), scale
 
 
 def dequant_block_fp8_weight(w: torch.Tensor, scale: torch.Tensor, block=(128, 128)):
@@ -304,6 +308,7 @@ def dequant_block_fp8_weight(w: torch.Tensor, scale: torch.Tensor, block=(128, 1
 def block_fp8_linear(x: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, block=(128, 128),
                      out_dtype=torch.bfloat16) -> torch.Tensor:
     xq, xs = quant_fp8_group128(x)
-    xd = xq.float().view(x.shape[0], -1, 128) * xs.unsqueeze(-1)
+    K = x.shape[1]
+    xd = xq.float() * xs.repeat_interleave(128, dim=1)[:, :K]
     wd = dequant_block_fp8_weight(w, w_scale, block)
-    return (xd.view(x.shape[0], -1) @ wd.t()).to(out_dtype)
+    return (xd @ wd.t()).to(out_dtype)

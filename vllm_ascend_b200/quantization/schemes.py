@@ -1,0 +1,301 @@
+"""Quantization schemes.
+
+FP8_BLOCK      128x128 block-scaled e4m3 weights x 1x128 per-token-group e4m3 activations
+               (DeepSeek-V3 / ``quant_method: fp8`` checkpoints load as they are;
+               vllm_ascend/quantization/methods/fp8.py:32-92).  GPU: tcgen05 f8f6f4 kernel
+               with two-level accumulation (csrc/gemm_fp8_block.cu).
+W8A8_DYNAMIC   per-output-channel weight scale x per-token dynamic activation scale, int8
+               (vllm_ascend/quantization/methods/w8a8_dynamic.py:51-399)
+W8A8FP8_DYNAMIC same with e4m3 (methods/w8a8fp8_dynamic.py:27-103)
+W8A8           static per-tensor activation scale (methods/w8a8_static.py:32-141)
+W4A16 / W8A16  weight-only, group-wise scales
+FLOAT          unquantized pass-through (a layer the description lists as "FLOAT")
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native, ops
+from ..ops import reference as ref
+from .registry import register_scheme
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+
+
+def quantize_weight_block_fp8(w: torch.Tensor, block=(128, 128)):
+    """bf16/fp32 [N, K] -> (e4m3 [N, K], scale_inv fp32 [ceil(N/bn), ceil(K/bk)])."""
+    N, K = w.shape
+    bn, bk = block
+    nb, kb = (N + bn - 1) // bn, (K + bk - 1) // bk
+    wp = torch.zeros(nb * bn, kb * bk, dtype=torch.float32, device=w.device)
+    wp[:N, :K] = w.float()
+    blocks = wp.view(nb, bn, kb, bk)
+    amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-10)
+    scale = amax / FP8_MAX
+    q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return q.view(nb * bn, kb * bk)[:N, :K].contiguous(), scale.contiguous()
+
+
+class LinearScheme:
+    """Interface of a linear-layer scheme."""
+    def convert(self, layer) -> None:            # build quantized tensors from layer.weight
+        raise NotImplementedError
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        raise NotImplementedError
+
+    def named_tensors(self, layer):
+        return iter(())
+
+
+@register_scheme("FLOAT", "linear")
+class FloatLinear(LinearScheme):
+    def convert(self, layer) -> None:
+        pass
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        return ops.linear(x, layer.weight, None if skip_bias else layer.bias, residual)
+
+
+@register_scheme("FP8_BLOCK", "linear")
+class Fp8BlockLinear(LinearScheme):
+    block = (128, 128)
+
+    def convert(self, layer) -> None:
+        if layer.weight.dtype != FP8:
+            q, s = quantize_weight_block_fp8(layer.weight, self.block)
+            layer.weight = q
+            layer.weight_scale_inv = s
+        elif not hasattr(layer, "weight_scale_inv"):
+            N, K = layer.weight.shape
+            layer.weight_scale_inv = torch.ones((N + 127) // 128, (K + 127) // 128,
+                                                dtype=torch.float32, device=layer.weight.device)
+
+    def named_tensors(self, layer):
+        yield "weight_scale_inv", layer.weight_scale_inv
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        bias = None if skip_bias else layer.bias
+        K = x.shape[-1]
+        N = layer.weight.shape[0]
+        x2 = x.reshape(-1, K)
+        if x2.is_cuda and x2.dtype == torch.bfloat16 and K % 128 == 0 and N % 8 == 0:
+            y = fp8_block_linear(x2, layer.weight, layer.weight_scale_inv, bias)
+        else:
+            y = ref.block_fp8_linear(x2, layer.weight, layer.weight_scale_inv, self.block, x.dtype)
+            if bias is not None:
+                y = y + bias
+        y = y.view(*x.shape[:-1], N)
+        if residual is not None:
+            y = y + residual
+        return y
+
+
+
+
+def _declare_native():
+    from ctypes import c_int, c_long, c_void_p
+    P, I, L = c_void_p, c_int, c_long
+    _native.register_signature("b200_gemm_fp8_block", [P, P, P, P, P, P, I, I, I, I, I, I, P, P])
+    _native.register_signature("b200_grouped_gemm_fp8_block",
+                               [P, P, P, P, P, P, I, L, I, I, I, I, I, P, P])
+
+
+_declare_native()
+
+
+def fp8_block_linear(x: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
+                     bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 activations [M,K] -> dynamic 1x128 e4m3 quantisation -> block-scaled GEMM."""
+    M, K = x.shape
+    N = w8.shape[0]
+    xq, xs = ops.quant_fp8_group128(x if x.is_contiguous() else x.contiguous())
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if M == 0:
+        return out
+    rc = _native.lib().b200_gemm_fp8_block(
+        xq.data_ptr(), xs.data_ptr(), w8.data_ptr(), w_scale.data_ptr(), out.data_ptr(),
+        _native.ptr(bias), M, N, K, xq.stride(0), w8.stride(0), out.stride(0),
+        _native.status_word(x.device).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "gemm_fp8_block")
+    ops.launch_counter[0] += 1
+    return out
+
+
+class _PerChannelDynamic(LinearScheme):
+    """Per-token dynamic activations x per-output-channel weights."""
+    qdtype = torch.int8
+    qmax = 127.0
+
+    def _q(self, t: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+        v = t.float() / scale
+        if self.qdtype == torch.int8:
+            return v.round().clamp(-self.qmax, self.qmax).to(torch.int8)
+        return v.clamp(-self.qmax, self.qmax).to(self.qdtype)
+
+    def convert(self, layer) -> None:
+        if layer.weight.dtype in (torch.int8, FP8):
+            if not hasattr(layer, "weight_scale"):
+                layer.weight_scale = torch.ones(layer.weight.shape[0], 1, dtype=torch.float32,
+                                                device=layer.weight.device)
+            return
+        w = layer.weight.float()
+        scale = (w.abs().amax(dim=1, keepdim=True) / self.qmax).clamp_min(1e-10)
+        layer.weight = self._q(w, scale)
+        layer.weight_scale = scale
+
+    def named_tensors(self, layer):
+        yield "weight_scale", layer.weight_scale
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K).float()
+        a_scale = (x2.abs().amax(dim=1, keepdim=True) / self.qmax).clamp_min(1e-10)
+        xq = self._q(x2, a_scale).float()
+        y = (xq @ layer.weight.float().t()) * a_scale * layer.weight_scale.view(1, -1)
+        if layer.bias is not None and not skip_bias:
+            y = y + layer.bias.float()
+        y = y.to(x.dtype).view(*x.shape[:-1], layer.weight.shape[0])
+        return y + residual if residual is not None else y
+
+
+@register_scheme("W8A8_DYNAMIC", "linear")
+class W8A8DynamicLinear(_PerChannelDynamic):
+    pass
+
+
+@register_scheme("W8A8FP8_DYNAMIC", "linear")
+class W8A8Fp8DynamicLinear(_PerChannelDynamic):
+    qdtype = FP8
+    qmax = FP8_MAX
+
+
+@register_scheme("W8A8", "linear")
+class W8A8StaticLinear(_PerChannelDynamic):
+    """Static per-tensor activation scale (``input_scale``) instead of per-token."""
+
+    def convert(self, layer) -> None:
+        super().convert(layer)
+        if not hasattr(layer, "input_scale"):
+            layer.input_scale = torch.tensor(1.0 / 16, dtype=torch.float32, device=layer.weight.device)
+
+    def named_tensors(self, layer):
+        yield "weight_scale", layer.weight_scale
+        yield "input_scale", layer.input_scale
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K).float()
+        xq = self._q(x2, layer.input_scale).float()
+        y = (xq @ layer.weight.float().t()) * layer.input_scale * layer.weight_scale.view(1, -1)
+        if layer.bias is not None and not skip_bias:
+            y = y + layer.bias.float()
+        y = y.to(x.dtype).view(*x.shape[:-1], layer.weight.shape[0])
+        return y + residual if residual is not None else y
+
+
+class _WeightOnly(LinearScheme):
+    bits = 8
+    group = 128
+
+    def convert(self, layer) -> None:
+        if hasattr(layer, "weight_scale"):
+            return
+        w = layer.weight.float()
+        N, K = w.shape
+        g = self.group if K % self.group == 0 else K
+        qmax = float(2 ** (self.bits - 1) - 1)
+        wg = w.view(N, K // g, g)
+        scale = (wg.abs().amax(dim=-1, keepdim=True) / qmax).clamp_min(1e-10)
+        layer.weight = (wg / scale).round().clamp(-qmax, qmax).to(torch.int8).view(N, K)
+        layer.weight_scale = scale.squeeze(-1)
+        layer.group_size = g
+
+    def named_tensors(self, layer):
+        yield "weight_scale", layer.weight_scale
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        N, K = layer.weight.shape
+        g = layer.group_size
+        w = (layer.weight.float().view(N, K // g, g) * layer.weight_scale.unsqueeze(-1)).view(N, K)
+        return ops.linear(x, w.to(x.dtype), None if skip_bias else layer.bias, residual)
+
+
+@register_scheme("W8A16", "linear")
+class W8A16Linear(_WeightOnly):
+    bits = 8
+
+
+@register_scheme("W4A16", "linear")
+class W4A16Linear(_WeightOnly):
+    bits = 4
+
+
+# ---------------------------------------------------------------- MoE schemes
+class MoEScheme:
+    def convert(self, block) -> None:
+        raise NotImplementedError
+
+    def apply_experts(self, x, w13, w2, topk_w, topk_ids, expert_map):
+        raise NotImplementedError
+
+
+@register_scheme("FP8_BLOCK", "moe")
+class Fp8BlockMoE(MoEScheme):
+    """Expert weights as block-scaled e4m3; grouped GEMM1 -> SwiGLU -> 1x128 requant -> GEMM2."""
+
+    def convert(self, block) -> None:
+        if block.w13.dtype == FP8:
+            return
+        q13, s13, q2, s2 = [], [], [], []
+        for e in range(block.w13.shape[0]):
+            q, s = quantize_weight_block_fp8(block.w13[e])
+            q13.append(q); s13.append(s)
+            q, s = quantize_weight_block_fp8(block.w2[e])
+            q2.append(q); s2.append(s)
+        block.w13, block.w13_scale = torch.stack(q13), torch.stack(s13)
+        block.w2, block.w2_scale = torch.stack(q2), torch.stack(s2)
+        self.block_ref = block
+
+    def apply_experts(self, x, w13, w2, topk_w, topk_ids, expert_map):
+        from ..ops import moe_native
+        blk = self.block_ref
+        if x.is_cuda and x.dtype == torch.bfloat16 and moe_native.available():
+            return moe_native.fused_experts_fp8(x, w13, blk.w13_scale, w2, blk.w2_scale, topk_w,
+                                                topk_ids, expert_map)
+        # reference: dequantise per expert
+        T, H = x.shape
+        out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+        ids = topk_ids.long()
+        if expert_map is not None:
+            ids = expert_map.long()[ids]
+        for e in range(w13.shape[0]):
+            tok, slot = (ids == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            h = ref.block_fp8_linear(x[tok], w13[e], blk.w13_scale[e], out_dtype=torch.float32)
+            a = ref.silu_and_mul(h).to(x.dtype)
+            y = ref.block_fp8_linear(a, w2[e], blk.w2_scale[e], out_dtype=torch.float32)
+            out.index_add_(0, tok, y * topk_w[tok, slot].unsqueeze(-1).float())
+        return out.to(x.dtype)
+
+
+@register_scheme("W8A8_DYNAMIC", "moe")
+class W8A8DynamicMoE(MoEScheme):
+    def convert(self, block) -> None:
+        def q(w):
+            scale = (w.float().abs().amax(dim=-1, keepdim=True) / 127.0).clamp_min(1e-10)
+            return (w.float() / scale).round().clamp(-127, 127).to(torch.int8), scale
+        block.w13, block.w13_scale = q(block.w13)
+        block.w2, block.w2_scale = q(block.w2)
+        self.block_ref = block
+
+    def apply_experts(self, x, w13, w2, topk_w, topk_ids, expert_map):
+        from ..ops.fused_moe import fused_experts_ref
+        blk = self.block_ref
+        w13f = (w13.float() * blk.w13_scale).to(x.dtype)
+        w2f = (w2.float() * blk.w2_scale).to(x.dtype)
+        return fused_experts_ref(x, w13f, w2f, topk_w, topk_ids, expert_map)
