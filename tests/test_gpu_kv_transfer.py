@@ -1,0 +1,118 @@
+"""KV block movement kernels and disaggregated prefill on GPUs."""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+from vllm_ascend_b200 import _native, ops
+from vllm_ascend_b200.engine.llm import LLM
+from vllm_ascend_b200.engine.request import SamplingParams
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _strides(t):
+    e = t.element_size()
+    return t.stride(0) * e, t.stride(1) * e, t.stride(2) * e
+
+
+@pytest.mark.parametrize("src_layout,dst_layout", [("NHD", "HND"), ("HND", "HND"), ("HND", "NHD")])
+def test_kv_block_copy_reslices_heads(src_layout, dst_layout):
+    import vllm_ascend_b200.distributed.kv_transfer.nvlink_connector  # noqa: F401  (registers signatures)
+    dev = torch.device("cuda")
+    nb_s, nb_d, bs, Hs, Hd, D, L = 24, 17, 128, 8, 4, 128, 6
+    g = torch.Generator(device="cpu").manual_seed(0)
+    src = [ops.alloc_kv_cache(nb_s, bs, Hs, D, torch.bfloat16, dev, src_layout) for _ in range(L)]
+    for t in src:
+        t.copy_(torch.randn(nb_s, bs, Hs, D, generator=g).to(torch.bfloat16))
+    dst = [ops.alloc_kv_cache(nb_d, bs, Hd, D, torch.bfloat16, dev, dst_layout) for _ in range(L)]
+    before = [t.clone() for t in dst]
+    sb = torch.tensor([3, 20, 7, 0, 11], dtype=torch.int32, device=dev)
+    db = torch.tensor([16, 2, 9, 5, 1], dtype=torch.int32, device=dev)
+    sp = torch.tensor([t.data_ptr() for t in src], dtype=torch.int64, device=dev)
+    dp = torch.tensor([t.data_ptr() for t in dst], dtype=torch.int64, device=dev)
+    src_h0, dst_h0, nh = 5, 1, 3
+    status = _native.status_word(dev)
+    rc = _native.lib().b200_kv_block_copy(
+        sp.data_ptr(), dp.data_ptr(), sb.data_ptr(), db.data_ptr(), 5, L, bs, D * 2, nh, src_h0, dst_h0,
+        *_strides(src[0]), *_strides(dst[0]), nb_s, nb_d, status.data_ptr(), _native.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    _native.check_status(dev)
+    for s, d, b in zip(src, dst, before):
+        want = b.clone()
+        want[db.long(), :, dst_h0:dst_h0 + nh] = s[sb.long(), :, src_h0:src_h0 + nh]
+        assert torch.equal(d, want)
+
+
+def test_copy_blocks():
+    import vllm_ascend_b200.distributed.kv_transfer.nvlink_connector  # noqa: F401
+    dev = torch.device("cuda")
+    cache = torch.randn(12, 128, 2, 128, device=dev).to(torch.bfloat16)
+    want = cache.clone()
+    pairs = torch.tensor([[1, 7], [3, 0], [5, 11]], dtype=torch.int64, device=dev)
+    for s, d in pairs.tolist():
+        want[d] = cache[s]
+    rc = _native.lib().b200_copy_blocks(cache.data_ptr(), pairs.data_ptr(), 3,
+                                        cache[0].numel() * 2, _native.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(cache, want)
+
+
+def test_disaggregated_prefill_same_gpu_matches_monolithic():
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import kv_transfer_worker as w
+    sp = SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True)
+    mono = w._llm(None, "M")
+    want = [o.outputs[0].token_ids for o in mono.generate(w._prompts(), sp)]
+    pre, dec = w._llm("kv_producer", "P"), w._llm("kv_consumer", "D")
+    try:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        outs = pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {"do_remote_decode": True}}
+                             for p in w._prompts()], sp1)
+        got = dec.generate([{"prompt_token_ids": p, "kv_transfer_params": o.kv_transfer_params}
+                            for p, o in zip(w._prompts(), outs)], sp)
+        assert [o.outputs[0].token_ids for o in got] == want
+        c = dec.engine.kv_connector
+        assert c.stats["pulled_requests"] == 5 and c.stats["failed"] == 0 and c.stats["bytes"] > 0
+        pre.engine.kv_connector.reap(pre.engine.scheduler)
+        assert pre.engine.kv_connector.num_delayed == 0
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2 if torch.cuda.is_available() else True,
+                    reason="needs 2 GPUs")
+def test_disaggregated_prefill_two_gpus_over_cuda_ipc():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", KV_PORT=str(31000 + os.getpid() % 2000),
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    worker = os.path.join(ROOT, "tests", "kv_transfer_worker.py")
+    with tempfile.TemporaryDirectory() as d:
+        pp = subprocess.Popen([sys.executable, worker, "prefill", d], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True)
+        dp = subprocess.Popen([sys.executable, worker, "decode", d], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True)
+        try:
+            dout, _ = dp.communicate(timeout=300)
+            open(os.path.join(d, "stop"), "w").close()
+            pout, _ = pp.communicate(timeout=60)
+        finally:
+            for p in (pp, dp):
+                if p.poll() is None:
+                    p.kill()
+    assert dp.returncode == 0, dout[-3000:]
+    assert pp.returncode == 0, pout[-3000:]
+    r = json.loads([l for l in dout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    pr = json.loads([l for l in pout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert r["modes"] == ["ipc"]
+    assert r["got"] == r["want"]
+    assert r["stats"]["pulled_requests"] == 5 and r["stats"]["failed"] == 0
+    assert pr["released"] == 5 and pr["delayed"] == 0

@@ -1,0 +1,151 @@
+"""Disaggregated prefill on CPU: a producer engine and a consumer engine in one process talk
+over the ZMQ side channel (tcp transport, fp32 tiny model); failures are injected on the host."""
+import time
+
+import numpy as np
+import pytest
+
+from vllm_ascend_b200 import LLM, SamplingParams
+from vllm_ascend_b200.distributed.kv_transfer import plan_head_slices
+from vllm_ascend_b200.platform_config import clear_b200_config
+
+
+def _mk(role, engine_id, extra=None, additional=None, **kw):
+    ktc = {"kv_connector": "NVLinkConnector", "kv_role": role, "engine_id": engine_id,
+           "kv_connector_extra_config": dict(extra or {})}
+    return LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=8,
+               kv_transfer_config=ktc, additional_config=additional, **kw)
+
+
+def _prompts(n, lo=20, hi=70, seed=1):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(1, 500, size=int(rng.integers(lo, hi))).tolist() for _ in range(n)]
+
+
+def _drain(llm, steps=50):
+    for _ in range(steps):
+        llm.engine.kv_connector.reap(llm.engine.scheduler)
+        if llm.engine.kv_connector.num_delayed == 0:
+            return
+        time.sleep(0.02)
+
+
+@pytest.fixture(autouse=True)
+def _clear():
+    yield
+    clear_b200_config()
+
+
+def test_plan_head_slices():
+    # equal TP: one-to-one
+    assert plan_head_slices(4, 4, 8, 2) == [(2, 0, 0, 2)]
+    # prefill TP4 -> decode TP2: each decode rank pulls from two prefill ranks
+    assert plan_head_slices(4, 2, 8, 1) == [(2, 0, 0, 2), (3, 0, 2, 2)]
+    # prefill TP2 -> decode TP4: half of a prefill rank's heads
+    assert plan_head_slices(2, 4, 8, 3) == [(1, 2, 0, 2)]
+    # replicated heads on the prefill side (TP8, 4 KV heads) -> decode TP2
+    s = plan_head_slices(8, 2, 4, 1)
+    assert [(x[1], x[2], x[3]) for x in s] == [(0, 0, 1), (0, 1, 1)]
+    assert [x[0] for x in s] == [2 * 2 + 1, 3 * 2 + 1]
+    # every head is covered exactly once for a range of shapes
+    for tp_s, tp_d, h in [(1, 8, 8), (8, 1, 8), (2, 8, 4), (8, 4, 2), (4, 4, 1)]:
+        for r in range(tp_d):
+            sl = plan_head_slices(tp_s, tp_d, h, r)
+            n_local = max(h // tp_d, 1)
+            assert sorted(d0 + i for _, _, d0, n in sl for i in range(n)) == list(range(n_local))
+
+
+def test_prefill_then_remote_decode_matches_monolithic():
+    prompts = _prompts(5)
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    mono = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=8)
+    want = [o.outputs[0].token_ids for o in mono.generate(prompts, sp)]
+
+    pre = _mk("kv_producer", "P0")
+    dec = _mk("kv_consumer", "D0")
+    try:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        outs = pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {"do_remote_decode": True}}
+                             for p in prompts], sp1)
+        assert all(o.kv_transfer_params and o.kv_transfer_params["do_remote_prefill"] for o in outs)
+        assert [o.outputs[0].token_ids[0] for o in outs] == [w[0] for w in want]
+        assert pre.engine.kv_connector.num_delayed == len(prompts)
+        free_before = pre.engine.scheduler.pool.num_free_blocks
+
+        got = dec.generate([{"prompt_token_ids": p, "kv_transfer_params": o.kv_transfer_params}
+                            for p, o in zip(prompts, outs)], sp)
+        assert [o.outputs[0].token_ids for o in got] == want
+        c = dec.engine.kv_connector
+        assert c.stats["pulled_requests"] == len(prompts) and c.stats["failed"] == 0
+        # the decode engine computed one prompt token per request, not the whole prompt
+        assert dec.engine.runner.stats["prefill_tokens"] <= len(prompts) \
+            if "prefill_tokens" in dec.engine.runner.stats else True
+        # the producer frees the blocks once the consumer said it is done
+        _drain(pre)
+        assert pre.engine.kv_connector.num_delayed == 0
+        assert pre.engine.scheduler.pool.num_free_blocks > free_before
+        assert pre.engine.kv_connector.stats["released"] == len(prompts)
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()
+
+
+def test_unclaimed_blocks_expire():
+    pre = _mk("kv_producer", "P1", extra={"abort_timeout_s": 0.05})
+    try:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        total = pre.engine.scheduler.pool.num_free_blocks
+        pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {"do_remote_decode": True}}
+                      for p in _prompts(3)], sp1)
+        assert pre.engine.kv_connector.num_delayed == 3
+        assert pre.engine.scheduler.pool.num_free_blocks < total
+        time.sleep(0.1)
+        pre.engine.kv_connector.reap(pre.engine.scheduler)
+        assert pre.engine.kv_connector.num_delayed == 0
+        assert pre.engine.kv_connector.stats["expired"] == 3
+        assert pre.engine.scheduler.pool.num_free_blocks == total
+    finally:
+        pre.engine.kv_connector.close()
+
+
+def test_pull_failure_falls_back_to_local_prefill():
+    """The producer stops answering (dropped messages): the decode engine's recompute
+    scheduler prefills locally and the output is still the monolithic one."""
+    prompts = _prompts(3, seed=3)
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    mono = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=8)
+    want = [o.outputs[0].token_ids for o in mono.generate(prompts, sp)]
+    pre = _mk("kv_producer", "P2")
+    dec = _mk("kv_consumer", "D2", extra={"side_channel_timeout_ms": 200},
+              additional={"scheduler_config": {"recompute_scheduler_enable": True}})
+    try:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        outs = pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {"do_remote_decode": True}}
+                             for p in prompts], sp1)
+        pre.engine.kv_connector.drop_all_messages = True
+        got = dec.generate([{"prompt_token_ids": p, "kv_transfer_params": o.kv_transfer_params}
+                            for p, o in zip(prompts, outs)], sp)
+        assert [o.outputs[0].token_ids for o in got] == want
+        assert dec.engine.kv_connector.stats["failed"] == len(prompts)
+        assert dec.engine.scheduler.num_recomputes == len(prompts)
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()
+
+
+def test_unknown_remote_request_is_a_failure_not_a_crash():
+    dec = _mk("kv_consumer", "D3", extra={"side_channel_timeout_ms": 200},
+              additional={"scheduler_config": {"recompute_scheduler_enable": True}})
+    pre = _mk("kv_producer", "P3")
+    try:
+        p = _prompts(1, seed=5)[0]
+        bogus = {"do_remote_prefill": True, "remote_block_ids": [0, 1, 2, 3, 4], "remote_engine_id": "P3",
+                 "remote_host": "127.0.0.1", "remote_port": pre.engine.kv_connector.base_port,
+                 "remote_tp_size": 1, "remote_block_size": 16, "remote_request_id": "nope"}
+        out = dec.generate([{"prompt_token_ids": p, "kv_transfer_params": bogus}],
+                           SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))
+        assert len(out[0].outputs[0].token_ids) == 4
+        assert dec.engine.kv_connector.stats["failed"] == 1
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()

@@ -285,6 +285,7 @@ class EngineConfig:
     compilation: CompilationConfig = field(default_factory=CompilationConfig)
     additional_config: dict = field(default_factory=dict)
     device: str = "cuda"
+    device_index: Optional[int] = None      # single-process engines only
     seed: int = 0
     kv_transfer_config: Optional[dict] = None
     speculative_config: Optional[dict] = None

@@ -1,0 +1,102 @@
+// KV-cache block movement.
+//   * kv_block_copy: gather/scatter of paged KV blocks between two caches (same GPU, or a
+//     peer GPU's cache mapped through CUDA IPC: the loads then cross NVLink from inside the
+//     kernel).  One launch moves any number of (src block -> dst block) pairs of every
+//     layer, optionally re-slicing KV heads when prefill and decode use different TP sizes.
+//     It is the worker side of the disaggregated-prefill connector: the reference builds
+//     (src, dst, len) lists per layer and hands them to a transfer engine, then fixes the
+//     layout with transpose_kv_cache_by_block
+//     (vllm_ascend/distributed/kv_transfer/kv_p2p/mooncake_connector.py:775-1028, 1271-1296);
+//     here the copy writes straight into the destination block table layout.
+//   * swap/copy blocks inside one cache (attention/attention_v1.py:119-145).
+#include "common.cuh"
+
+namespace b200 {
+
+struct KvCopyParams {
+  const void* const* src_tensors;   // [num_tensors] device array of cache base pointers (K and V of every layer)
+  void* const* dst_tensors;         // [num_tensors]
+  const int* src_blocks;            // [num_pairs]
+  const int* dst_blocks;            // [num_pairs]
+  int num_pairs, num_tensors;
+  int block_size, head_dim_bytes;   // bytes of one (token, head) vector
+  int num_heads;                    // heads to copy
+  int src_head0, dst_head0;         // first head on each side
+  // element strides in bytes: block, token, head
+  long src_sb, src_st, src_sh;
+  long dst_sb, dst_st, dst_sh;
+  long src_num_blocks, dst_num_blocks;
+  int* status;
+};
+
+__global__ void kv_block_copy_kernel(const KvCopyParams p) {
+  const int pair = blockIdx.x, tensor = blockIdx.y;
+  const int sb = p.src_blocks[pair], db = p.dst_blocks[pair];
+  if (sb < 0 || sb >= p.src_num_blocks || db < 0 || db >= p.dst_num_blocks) {
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, B200_BAD_INDEX);
+    return;
+  }
+  const uint8_t* src = (const uint8_t*)p.src_tensors[tensor] + (long)sb * p.src_sb;
+  uint8_t* dst = (uint8_t*)p.dst_tensors[tensor] + (long)db * p.dst_sb;
+  const int vecs = p.head_dim_bytes >> 4;
+  const int total = p.block_size * p.num_heads * vecs;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int v = i % vecs;
+    const int rest = i / vecs;
+    const int tok = rest % p.block_size;
+    const int h = rest / p.block_size;
+    const uint4 val = *reinterpret_cast<const uint4*>(
+        src + (long)tok * p.src_st + (long)(p.src_head0 + h) * p.src_sh + (v << 4));
+    *reinterpret_cast<uint4*>(dst + (long)tok * p.dst_st + (long)(p.dst_head0 + h) * p.dst_sh +
+                              (v << 4)) = val;
+  }
+}
+
+// pairs [n, 2] (src, dst) inside one cache tensor; block_bytes contiguous per block
+__global__ void copy_blocks_kernel(uint8_t* cache, const long* pairs, long block_bytes) {
+  const long s = pairs[2 * blockIdx.x], d = pairs[2 * blockIdx.x + 1];
+  const uint4* src = reinterpret_cast<const uint4*>(cache + s * block_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(cache + d * block_bytes);
+  for (long i = threadIdx.x; i < (block_bytes >> 4); i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// src_tensors / dst_tensors: DEVICE arrays of num_tensors base pointers.
+// strides in bytes (block, token, head).  head_dim_bytes multiple of 16.
+B200_API int b200_kv_block_copy(const void* src_tensors, const void* dst_tensors,
+                                const void* src_blocks, const void* dst_blocks, int num_pairs,
+                                int num_tensors, int block_size, int head_dim_bytes,
+                                int num_heads, int src_head0, int dst_head0, long src_sb,
+                                long src_st, long src_sh, long dst_sb, long dst_st, long dst_sh,
+                                long src_num_blocks, long dst_num_blocks, int* status,
+                                cudaStream_t stream) {
+  if (num_pairs <= 0 || num_tensors <= 0) return 0;
+  if (head_dim_bytes & 15) return 9100;
+  KvCopyParams p;
+  p.src_tensors = (const void* const*)src_tensors;
+  p.dst_tensors = (void* const*)dst_tensors;
+  p.src_blocks = (const int*)src_blocks;
+  p.dst_blocks = (const int*)dst_blocks;
+  p.num_pairs = num_pairs; p.num_tensors = num_tensors;
+  p.block_size = block_size; p.head_dim_bytes = head_dim_bytes;
+  p.num_heads = num_heads; p.src_head0 = src_head0; p.dst_head0 = dst_head0;
+  p.src_sb = src_sb; p.src_st = src_st; p.src_sh = src_sh;
+  p.dst_sb = dst_sb; p.dst_st = dst_st; p.dst_sh = dst_sh;
+  p.src_num_blocks = src_num_blocks; p.dst_num_blocks = dst_num_blocks;
+  p.status = status;
+  dim3 grid((unsigned)num_pairs, (unsigned)num_tensors);
+  kv_block_copy_kernel<<<grid, 256, 0, stream>>>(p);
+  return B200_CHECK_LAUNCH();
+}
+
+B200_API int b200_copy_blocks(void* cache, const void* pairs, int num_pairs, long block_bytes,
+                              cudaStream_t stream) {
+  if (num_pairs <= 0) return 0;
+  if (block_bytes & 15) return 9100;
+  copy_blocks_kernel<<<num_pairs, 256, 0, stream>>>((uint8_t*)cache, (const long*)pairs,
+                                                    block_bytes);
+  return B200_CHECK_LAUNCH();
+}

@@ -38,7 +38,10 @@ class LLMEngine:
         if cfg.device == "cuda":
             if not torch.cuda.is_available():
                 raise RuntimeError("device='cuda' requested but no GPU is visible")
-            self.device = torch.device("cuda", local)
+            # a single-process engine may be pinned to any GPU ("cuda:1"); under torchrun
+            # the local rank decides
+            self.device = torch.device("cuda", cfg.device_index if (world == 1 and cfg.device_index
+                                                                   is not None) else local)
             torch.cuda.set_device(self.device)
             _native.load(required=True)
         else:
@@ -201,6 +204,9 @@ class LLM:
         mcfg.seed = seed
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
+        device_index = None
+        if device.startswith("cuda:"):
+            device, device_index = "cuda", int(device.split(":")[1])
         if block_size is None:
             block_size = 128 if device == "cuda" else 16
         cfg = EngineConfig(
@@ -219,7 +225,7 @@ class LLM:
             compilation=CompilationConfig(
                 cudagraph_mode="NONE" if enforce_eager else "FULL_DECODE_ONLY",
                 cudagraph_capture_sizes=cudagraph_capture_sizes),
-            additional_config=additional_config or {}, device=device, seed=seed,
+            additional_config=additional_config or {}, device=device, device_index=device_index, seed=seed,
             kv_transfer_config=kv_transfer_config, speculative_config=speculative_config,
             enable_sleep_mode=enable_sleep_mode)
         if device == "cuda":

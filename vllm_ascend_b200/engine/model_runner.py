@@ -150,6 +150,7 @@ class ModelRunner:
         self.num_blocks = num_blocks
         c = self.mcfg
         self.kv_caches = []
+        per_layer = []
         for layer in self.model.layers:
             if c.use_mla:
                 shapes = [(num_blocks, self.block_size, 1, c.kv_lora_rank),
@@ -157,9 +158,20 @@ class ModelRunner:
             else:
                 a = layer.self_attn
                 shapes = [(num_blocks, self.block_size, a.Hkv, a.D)] * 2
-            layout = self.cfg.cache.kv_layout if self.is_cuda else "NHD"
+            per_layer.append(shapes)
+        layout = self.cfg.cache.kv_layout if self.is_cuda else "NHD"
+        self.kv_arena = None
+        if self.is_cuda and self.cfg.kv_transfer_config and not self.cfg.enable_sleep_mode:
+            # one exportable allocation, so a decode engine in another process of this node
+            # can map the whole cache through a single CUDA IPC handle
+            from ..distributed.kv_transfer.nvlink_connector import KVArena
+            torch.cuda.empty_cache()
+            self.kv_arena = KVArena(KVArena.bytes_needed([s for sh in per_layer for s in sh],
+                                                         self.kv_dtype), self.device)
+        for shapes in per_layer:
             self.kv_caches.append(tuple(
-                ops.alloc_kv_cache(s[0], s[1], s[2], s[3], self.kv_dtype, self.device, layout)
+                ops.alloc_kv_cache(s[0], s[1], s[2], s[3], self.kv_dtype, self.device, layout,
+                                   arena=self.kv_arena)
                 for s in shapes))
 
     # ------------------------------------------------------------------ persistent batch

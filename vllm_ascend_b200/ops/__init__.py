@@ -40,12 +40,14 @@ def kv_layout(cache: torch.Tensor) -> int:
 
 
 def alloc_kv_cache(num_blocks: int, block_size: int, heads: int, dim: int, dtype, device,
-                   layout: str = "HND") -> torch.Tensor:
-    """Zero-filled cache with logical shape [blocks, tokens, heads, dim]."""
-    if layout == "HND" and heads > 1:
-        return torch.zeros((num_blocks, heads, block_size, dim), dtype=dtype,
-                           device=device).permute(0, 2, 1, 3)
-    return torch.zeros((num_blocks, block_size, heads, dim), dtype=dtype, device=device)
+                   layout: str = "HND", arena=None) -> torch.Tensor:
+    """Zero-filled cache with logical shape [blocks, tokens, heads, dim].  ``arena`` (an
+    object with ``take(shape, dtype)`` returning zeroed storage) replaces the torch
+    allocator, e.g. an IPC-exportable arena for disaggregated prefill."""
+    hnd = layout == "HND" and heads > 1
+    shape = (num_blocks, heads, block_size, dim) if hnd else (num_blocks, block_size, heads, dim)
+    t = arena.take(shape, dtype) if arena is not None else torch.zeros(shape, dtype=dtype, device=device)
+    return t.permute(0, 2, 1, 3) if hnd else t
 
 
 # ---------------------------------------------------------------- norms / activations
