@@ -290,9 +290,16 @@ def main():
                                     if k[:2] in ("t_", "n_") and k.split("_", 1)[1] in ("decode", "decode_eager", "mixed")},
                                  "note": "cumulative over warm-up and timed passes"},
         }))
+    sys.stdout.flush()
+    # Captured graphs that contain NCCL collectives must be gone before the communicators
+    # are torn down; a watchdog ends the process if library teardown stalls anyway.
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        watchdog = threading.Timer(45.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
+    llm.shutdown()
+    if world > 1:
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,171 @@
+"""Platform plugin surface, forward context, CPU binding, health probe, logger, profiling spans."""
+import logging
+import os
+
+import pytest
+import torch
+
+import vllm_ascend_b200 as pkg
+from vllm_ascend_b200 import cpu_binding
+from vllm_ascend_b200.platform_config import clear_b200_config, get_b200_config
+
+
+@pytest.fixture(autouse=True)
+def _clear():
+    yield
+    clear_b200_config()
+
+
+def test_entry_points_and_platform_class_paths():
+    import importlib
+    path = pkg.register()
+    mod, cls = path.rsplit(".", 1)
+    P = getattr(importlib.import_module(mod), cls)
+    assert P.device_type == "cuda" and P.dispatch_key == "CUDA" and P.dist_backend == "nccl"
+    assert "fp8" in P.supported_quantization
+    assert P.is_sleep_mode_available() and P.support_static_graph_mode() and P.opaque_attention_op()
+    # every class path the platform hands out resolves to a real class
+    for getter in (P.get_punica_wrapper, P.get_device_communicator_cls, P.get_static_graph_wrapper_cls,
+                   P.get_pass_manager_cls, P.get_compile_backend):
+        m, c = getter().rsplit(".", 1)
+        assert hasattr(importlib.import_module(m), c), getter
+    for key in [dict(use_mla=False), dict(use_mla=True), dict(use_mla=True, use_sparse=True)]:
+        m, c = P.get_attn_backend_cls(None, **key).rsplit(".", 1)
+        assert hasattr(importlib.import_module(m), c)
+    with pytest.raises(ValueError):
+        P.get_attn_backend_cls(None, use_mla=False, use_sparse=True)
+
+
+def test_platform_check_and_update_config_on_a_host_config():
+    from types import SimpleNamespace as NS
+    from vllm_ascend_b200.platform import B200Platform
+    vc = NS(additional_config={"scheduler_config": {"short_request_first_config": {"enabled": True}}},
+            parallel_config=NS(tensor_parallel_size=2, data_parallel_size=1, enable_expert_parallel=False,
+                               worker_cls="auto", enable_dbo=True, use_sequence_parallel_moe=True,
+                               data_parallel_rank=0),
+            scheduler_config=NS(max_num_seqs=64, scheduler_cls=None),
+            compilation_config=NS(cudagraph_mode="FULL", cudagraph_capture_sizes=[1, 3, 8],
+                                  max_cudagraph_capture_size=None, use_inductor=True),
+            model_config=NS(enforce_eager=False, hf_config=NS(num_experts=0), disable_cascade_attn=False),
+            cache_config=NS(block_size=None), kv_transfer_config=None, speculative_config=None)
+    B200Platform.check_and_update_config(vc)
+    assert vc.parallel_config.worker_cls.endswith("B200Worker")
+    assert vc.parallel_config.enable_dbo is False and vc.compilation_config.use_inductor is False
+    assert vc.compilation_config.cudagraph_capture_sizes == [2, 4, 8]      # TP multiples for SP
+    assert vc.cache_config.block_size == 128
+    assert vc.scheduler_config.scheduler_cls.endswith("ShortRequestFirstScheduler")
+    assert get_b200_config().scheduler_config.short_request_first_config.enabled
+    vc.compilation_config = NS(cudagraph_capture_sizes=None, max_cudagraph_capture_size=None)
+    B200Platform.apply_config_platform_defaults(vc)
+    assert vc.compilation_config.max_cudagraph_capture_size == 64
+
+
+def test_forward_context_extras_and_moe_selection():
+    from vllm_ascend_b200.forward_context import (get_forward_context, has_forward_context,
+                                                  set_forward_context)
+    from vllm_ascend_b200.ops.moe_comm import MoECommType
+    assert not has_forward_context()
+    with set_forward_context(None, num_tokens=5, tp_size=4, sp_enabled=True, is_moe=True, ep_size=8,
+                             num_tokens_across_dp=[5, 300], fused_moe_available=True,
+                             fused_moe_capacity=512) as ctx:
+        assert get_forward_context() is ctx
+        assert ctx.padded_length == 8 and ctx.max_tokens_across_dp == 300
+        assert ctx.moe_comm_type is MoECommType.FUSED
+        assert ctx.fused_moe_mask.sum() == 5 and ctx.fused_moe_mask.numel() == 512
+        with set_forward_context(None, num_tokens=4096, is_moe=True, ep_size=8, fused_moe_available=True) as inner:
+            assert inner.moe_comm_type is MoECommType.ALLTOALL
+        assert get_forward_context() is ctx
+    assert not has_forward_context()
+    with pytest.raises(RuntimeError):
+        get_forward_context()
+
+
+def test_cpu_binding_plan_with_fake_topology():
+    files = {
+        "/sys/devices/system/node/online": "0-1\n",
+        "/sys/devices/system/node/node0/cpulist": "0-15\n",
+        "/sys/devices/system/node/node1/cpulist": "16-31\n",
+        "/sys/bus/pci/devices/0000:1b:00.0/numa_node": "0\n",
+        "/sys/bus/pci/devices/0000:43:00.0/numa_node": "0\n",
+        "/sys/bus/pci/devices/0000:9b:00.0/numa_node": "1\n",
+    }
+    topo = cpu_binding.discover(4, read=files.get, pci_bus_ids=["00000000:1B:00.0", "00000000:43:00.0",
+                                                                 "00000000:9B:00.0", ""])
+    topo.allowed = list(range(32))
+    assert topo.gpu_node == {0: 0, 1: 0, 2: 1, 3: -1}
+    p = cpu_binding.plan(topo, 4)
+    assert p[0] == list(range(2, 9)) and p[1] == list(range(9, 16))      # node 0 minus 2 reserved, halved
+    assert p[2] == list(range(18, 32))
+    assert p[3] == list(range(24, 32))                                   # unknown node: even slice of all
+    got = {}
+    cpus = cpu_binding.bind_cpus(1, 4, topo=topo, setaffinity=lambda pid, s: got.update(pid=pid, cpus=s))
+    assert got["cpus"] == set(range(9, 16)) and cpus == list(range(9, 16))
+    assert cpu_binding.format_cpu_list([0, 1, 2, 5, 7, 8]) == "0-2,5,7-8"
+    assert cpu_binding.parse_cpu_list("0-2,5,7-8") == [0, 1, 2, 5, 7, 8]
+
+
+def test_gpu_health_against_fake_nvml():
+    from vllm_ascend_b200.observability import health
+
+    class Fake:
+        NVML_TEMPERATURE_GPU, NVML_CLOCK_SM = 0, 1
+        NVML_MEMORY_ERROR_TYPE_UNCORRECTED, NVML_VOLATILE_ECC = 1, 0
+        ecc = 0
+        calls = []
+
+        def nvmlInit(self): self.calls.append("init")
+        def nvmlShutdown(self): self.calls.append("shutdown")
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetTemperature(self, h, k): return 55
+        def nvmlDeviceGetPowerUsage(self, h): return 700000
+        def nvmlDeviceGetClockInfo(self, h, k): return 1700
+        def nvmlDeviceGetCurrentClocksEventReasons(self, h): return 0x4 | 0x40
+        def nvmlDeviceGetTotalEccErrors(self, h, a, b): return self.ecc
+
+    fake = Fake()
+    health.set_nvml_for_testing(lambda: fake)
+    try:
+        h = health.gpu_health(0)
+        assert h["ok"] and h["temperature_c"] == 55 and h["power_w"] == 700.0
+        assert sorted(h["throttle"]) == ["hw_thermal_slowdown", "sw_power_cap"]
+        fake.ecc = 3
+        h = health.gpu_health(0)
+        assert not h["ok"] and "ECC" in h["reason"]
+        # only read-only calls were made
+        assert set(fake.calls) == {"init", "shutdown"}
+    finally:
+        health.set_nvml_for_testing(None)
+
+
+def test_file_logging(tmp_path, monkeypatch):
+    from vllm_ascend_b200 import logger as lg
+    monkeypatch.setenv("VLLM_B200_LOG_PATH", str(tmp_path))
+    lg.configure_logging(force=True)
+    lg.logger.warning("hello from the test")
+    for h in lg.logger.handlers:
+        h.flush()
+    files = list(tmp_path.glob("vllm_b200_*.log"))
+    assert files and "hello from the test" in files[0].read_text()
+    monkeypatch.delenv("VLLM_B200_LOG_PATH")
+    for h in list(lg.logger.handlers):
+        if isinstance(h, logging.handlers.RotatingFileHandler):
+            lg.logger.removeHandler(h)
+            h.close()
+
+
+def test_service_profiling_config_and_spans(tmp_path, monkeypatch):
+    from vllm_ascend_b200.profiler import service_profiling as sp
+    monkeypatch.setenv("VLLM_B200_SERVICE_PROFILING_DIR", str(tmp_path))
+    path = sp.generate_service_profiling_config()
+    assert os.path.exists(path) and "engine.step" in open(path).read()
+    names = sp.install_spans(path, nvtx=False)
+    try:
+        assert "scheduler.schedule" in names
+        from vllm_ascend_b200 import LLM, SamplingParams
+        llm = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=64, max_num_seqs=2)
+        llm.generate([[1, 2, 3, 4]], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))
+        assert sp.totals["engine.step"][0] >= 3 and sp.totals["runner.execute"][1] > 0
+        m = llm.get_metrics()
+        assert m["steps"] >= 3 and m["kv_blocks_free"] == m["kv_blocks_total"] or m["kv_usage"] >= 0
+    finally:
+        sp.uninstall_spans()

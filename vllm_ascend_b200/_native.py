@@ -110,6 +110,13 @@ def check(rc: int, what: str) -> None:
 # ---------------------------------------------------------------- status word
 _status_words: dict[int, torch.Tensor] = {}
 
+# launches of this package's own kernels (shared list object: ``ops.launch_counter`` aliases it)
+launch_counter = [0]
+
+
+def count_launch(n: int = 1) -> None:
+    launch_counter[0] += n
+
 
 def status_word(device: torch.device) -> torch.Tensor:
     """Per-device int32 word that kernels set on bounded-wait timeouts or bad

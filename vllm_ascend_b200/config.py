@@ -291,3 +291,5 @@ class EngineConfig:
     speculative_config: Optional[dict] = None
     enable_sleep_mode: bool = False
     enable_lora: bool = False
+    max_loras: int = 4
+    max_lora_rank: int = 64

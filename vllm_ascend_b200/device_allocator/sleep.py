@@ -24,9 +24,7 @@ def sleep(engine, level: int = 1) -> int:
     runner = engine.runner
     torch.cuda.synchronize()
     if get_b200_config().rl_config.sleep_mode_extra_cleanup:
-        runner.graphs.clear()
-        runner.graph_launches.clear()
-        runner.graph_pool = None
+        runner.drop_graphs()
         engine._recapture_on_wake = True
     alloc = VmmAllocator.get_instance()
     freed = alloc.sleep(offload_tags=("weights",) if level == 1 else ())

@@ -31,64 +31,27 @@ _FINISH_REASON = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED
 class LLMEngine:
     def __init__(self, cfg: EngineConfig):
         self.cfg = cfg
-        rank, local, world = pstate.init_distributed(
-            backend=None if cfg.device == "cuda" else "gloo")
+        from ..worker.worker import B200Worker
+        self.worker = B200Worker(cfg)
+        self.worker.init_device()
         pc = cfg.parallel
-        pc.rank, pc.local_rank, pc.world_size = rank, local, world
-        if cfg.device == "cuda":
-            if not torch.cuda.is_available():
-                raise RuntimeError("device='cuda' requested but no GPU is visible")
-            # a single-process engine may be pinned to any GPU ("cuda:1"); under torchrun
-            # the local rank decides
-            self.device = torch.device("cuda", cfg.device_index if (world == 1 and cfg.device_index
-                                                                   is not None) else local)
-            torch.cuda.set_device(self.device)
-            _native.load(required=True)
-        else:
-            self.device = torch.device("cpu")
-        if world > 1:
-            dp = max(1, world // (pc.tensor_parallel_size * pc.pipeline_parallel_size))
-            pc.data_parallel_size = dp
-            from ..platform_config import finegrained_sizes
-            pstate.initialize_model_parallel(pc.tensor_parallel_size, pc.pipeline_parallel_size, dp,
-                                             pc.decode_context_parallel_size,
-                                             finegrained=finegrained_sizes(cfg.additional_config))
-        else:
-            pstate.initialize_model_parallel()
-        self.runner = ModelRunner(cfg, self.device)
+        world = self.worker.world_size
+        self.device = self.worker.device
+        self.runner = self.worker.runner
         self.dp = pstate.get_dp_group()
-        self.moe_runtime = None
-        moe_runtime = None
-        if cfg.model.is_moe and pc.enable_expert_parallel and world > 1:
-            from ..ops.moe_comm import MoERuntime
-            moe_runtime = MoERuntime(cfg, self.device)
-            self.moe_runtime = moe_runtime
         self.sleep_level = 0
-        if cfg.enable_sleep_mode and cfg.device == "cuda":
-            from ..device_allocator.vmm import VmmAllocator
-            with VmmAllocator.get_instance().use_memory_pool("weights"):
-                self.runner.load_model(moe_runtime=moe_runtime)
-        else:
-            self.runner.load_model(moe_runtime=moe_runtime)
-        if world > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM == "fused" \
-                and pc.tensor_parallel_size > 1:
-            from ..parallel import fused_linear
-            fused_linear.attach(self.runner.model, cfg, self.device)
-        num_blocks = self.runner.determine_num_blocks()
-        if world > 1:   # every rank must agree
-            num_blocks = min(pstate.get_world_group().all_gather_object(num_blocks))
-        if cfg.enable_sleep_mode and cfg.device == "cuda":
-            from ..device_allocator.vmm import VmmAllocator
-            with VmmAllocator.get_instance().use_memory_pool("kv_cache"):
-                self.runner.init_kv_cache(num_blocks)
-        else:
-            self.runner.init_kv_cache(num_blocks)
-        self.runner.warmup()
+        self.worker.load_model()
+        self.moe_runtime = self.worker.moe_runtime
+        num_blocks = self.worker.determine_num_blocks()
+        self.worker.initialize_cache(num_blocks)
+        self.worker.compile_or_warm_up_model()
         self.kv_connector = None
         if cfg.kv_transfer_config:
             from ..distributed.kv_transfer import create_connector
             self.kv_connector = create_connector(cfg, self.runner)
         self.scheduler = self._make_scheduler(num_blocks)
+        if cfg.enable_lora:
+            self.scheduler.max_loras = cfg.max_loras
         self.runner.capture_graphs()
         self._req_counter = itertools.count()
         self.eos_token_id: Optional[int] = None
@@ -102,11 +65,13 @@ class LLMEngine:
     # ------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], sampling_params: SamplingParams,
                     request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None,
-                    job_id: Optional[str] = None) -> str:
+                    job_id: Optional[str] = None, lora_request=None) -> str:
         rid = request_id or f"req-{next(self._req_counter)}"
+        if lora_request is not None and self.runner.lora_manager is None:
+            raise ValueError("a LoRA request needs an engine built with enable_lora=True")
         req = Request(rid, np.asarray(prompt_token_ids, dtype=np.int32), sampling_params,
                       eos_token_id=self.eos_token_id, kv_transfer_params=kv_transfer_params,
-                      job_id=job_id)
+                      job_id=job_id, lora_request=lora_request)
         self.scheduler.add_request(req)
         return rid
 
@@ -172,8 +137,7 @@ class LLMEngine:
         return True
 
     def check_health(self) -> None:
-        if self.device.type == "cuda":
-            _native.check_status(self.device)
+        self.worker.check_health()
 
 
 class LLM:
@@ -195,7 +159,8 @@ class LLM:
                  kv_transfer_config: Optional[dict] = None,
                  speculative_config: Optional[dict] = None, enable_sleep_mode: bool = False,
                  cudagraph_capture_sizes: Optional[list] = None,
-                 decode_context_parallel_size: int = 1, **unused):
+                 decode_context_parallel_size: int = 1, enable_lora: bool = False, max_loras: int = 4,
+                 max_lora_rank: int = 64, **unused):
         mcfg = model if isinstance(model, ModelConfig) else get_model_config(model)
         if dtype:
             mcfg.dtype = dtype
@@ -227,7 +192,8 @@ class LLM:
                 cudagraph_capture_sizes=cudagraph_capture_sizes),
             additional_config=additional_config or {}, device=device, device_index=device_index, seed=seed,
             kv_transfer_config=kv_transfer_config, speculative_config=speculative_config,
-            enable_sleep_mode=enable_sleep_mode)
+            enable_sleep_mode=enable_sleep_mode, enable_lora=enable_lora, max_loras=max_loras,
+            max_lora_rank=max_lora_rank)
         if device == "cuda":
             cfg.scheduler.decode_batch_alignment = 256
         from ..platform_config import check_and_update_config
@@ -237,7 +203,7 @@ class LLM:
 
     # ------------------------------------------------------------------
     def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                 use_tqdm: bool = False) -> list[RequestOutput]:
+                 use_tqdm: bool = False, lora_request=None) -> list[RequestOutput]:
         """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``)."""
         if sampling_params is None:
             sampling_params = SamplingParams()
@@ -252,7 +218,8 @@ class LLM:
             ids = p["prompt_token_ids"] if isinstance(p, dict) else p
             sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
             ktp = p.get("kv_transfer_params") if isinstance(p, dict) else None
-            rid = eng.add_request(ids, sp, kv_transfer_params=ktp)
+            lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
+            rid = eng.add_request(ids, sp, kv_transfer_params=ktp, lora_request=lr)
             order.append(rid)
             mine.append(i)
             reqs[rid] = eng.scheduler.requests[rid]
@@ -291,6 +258,22 @@ class LLM:
     def wake_up(self, tags: Optional[list[str]] = None) -> None:
         from ..device_allocator.sleep import wake_up as _wake
         _wake(self.engine, tags)
+
+    def shutdown(self) -> None:
+        """Release device-side state in dependency order: captured graphs first (they may
+        hold collectives), then connectors and peer mappings, then the process groups."""
+        import torch.distributed as dist
+        eng = self.engine
+        if eng.device.type == "cuda":
+            torch.cuda.synchronize()
+        eng.runner.drop_graphs()
+        if eng.kv_connector is not None:
+            eng.kv_connector.close()
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()
+            if eng.device.type == "cuda":
+                torch.cuda.synchronize()
+            dist.destroy_process_group()
 
     def reset_prefix_cache(self) -> bool:
         return self.engine.scheduler.pool.reset_prefix_cache()

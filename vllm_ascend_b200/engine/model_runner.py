@@ -81,13 +81,14 @@ class ModelRunner:
         self._h_tile = torch.zeros((2, max_tiles), dtype=i32, pin_memory=pin)
         self._h_sampled = torch.zeros(B, dtype=i64, pin_memory=pin)
         # ---- CUDA graphs
-        self.graphs: dict[int, tuple] = {}
+        self.graphs: dict[int, object] = {}     # capture size -> BatchDescriptor
+        self.graph_wrapper = None
+        self.lora_manager = None
         self.graph_pool = None
         self.capture_sizes: list[int] = []
         self.stats = {"graph_replays": 0, "eager_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0,
                       "steps": 0, "graph_kernel_launches": 0, "t_prepare": 0.0, "t_launch": 0.0,
                       "t_wait": 0.0}
-        self.graph_launches: dict[int, int] = {}
         self.sm_count = (torch.cuda.get_device_properties(device).multi_processor_count
                          if self.is_cuda else 1)
 
@@ -240,6 +241,8 @@ class ModelRunner:
         self.block_table[:Bp].copy_(h._h_bt[:Bp], non_blocking=nb)
         self.stats["h2d_bytes"] += Tp * 24 + (Bp + 1) * 4 + Bp * 4 + Bp * self.max_blocks_per_seq * 4
 
+        if self.lora_manager is not None:
+            self._update_lora(reqs, q_lens, Tp)
         max_q = int(q_lens.max()) if B else 0
         max_s = int(seq_lens.max()) if B else 0
         nd, npf, ndt, _ = split_decodes_and_prefills(q_lens)
@@ -288,6 +291,26 @@ class ModelRunner:
                 sample_reqs.append(r)
         return meta, T, Tp, sel, sample_reqs
 
+    def init_lora(self) -> None:
+        from ..lora.manager import LoRAManager
+        self.lora_manager = LoRAManager(self.model, self.cfg.max_loras, self.cfg.max_lora_rank,
+                                        self.max_tokens + self.max_seqs, self.max_seqs, self.device,
+                                        next(iter(self.model.named_parameters()))[1].dtype)
+
+    def _update_lora(self, reqs, q_lens, padded_tokens: int) -> None:
+        mgr = self.lora_manager
+        in_use = {r.lora_request.lora_int_id for r in reqs if getattr(r, "lora_request", None) is not None}
+        slots = []
+        for r in reqs:
+            lr = getattr(r, "lora_request", None)
+            if lr is None:
+                slots.append(-1)
+                continue
+            if not mgr.add(lr, in_use):
+                raise RuntimeError(f"no adapter slot for LoRA {lr.lora_int_id}: raise max_loras")
+            slots.append(mgr.slot_of(lr.lora_int_id))
+        mgr.punica.update_metadata(slots, q_lens, padded_tokens)
+
     def _decode_splits(self, batch: int, Hkv: int) -> int:
         """Split factor depends only on the (padded) batch size so that it is a
         compile-time constant of the captured graph."""
@@ -319,10 +342,10 @@ class ModelRunner:
         meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
         t_prep = time.perf_counter()
         if gsize is not None:
-            graph, hidden_out = self.graphs[gsize]
-            graph.replay()
+            desc = self.graphs[gsize]
+            hidden_out = self.graph_wrapper.replay(desc)
             self.stats["graph_replays"] += 1
-            self.stats["graph_kernel_launches"] += self.graph_launches[gsize]
+            self.stats["graph_kernel_launches"] += self.graph_wrapper.entries[desc].num_launches
             logits = self.model.compute_logits(hidden_out[:B])
         else:
             hidden = self._forward(Tp, meta)
@@ -417,6 +440,13 @@ class ModelRunner:
         if self.is_cuda:
             torch.cuda.synchronize()
 
+    def drop_graphs(self) -> None:
+        """Forget every captured graph; decode steps run eagerly until the next capture."""
+        self.graphs.clear()
+        self.capture_sizes = []
+        if self.graph_wrapper is not None:
+            self.graph_wrapper.clear()
+
     @torch.inference_mode()
     def capture_graphs(self) -> None:
         cc = self.cfg.compilation
@@ -435,24 +465,17 @@ class ModelRunner:
                     worst = max(worst, s * a.Hq * ns * (a.D + 1) * 4)
             if worst:
                 ops.reserve_attention_scratch(self.device, worst)
-        self.graph_pool = torch.cuda.graph_pool_handle()
+        from ..compilation.cuda_graph import BatchDescriptor, CUDAGraphWrapper, global_graph_pool
+        self.graph_pool = global_graph_pool()
+
+        def warm(Tp, meta):
+            self.model.compute_logits(self._forward(Tp, meta))
+        self.graph_wrapper = CUDAGraphWrapper(self._forward, cc.cudagraph_mode, self.graph_pool,
+                                              launch_counter=ops.launch_counter)
         for size in sorted(self.capture_sizes, reverse=True):
             meta, T, Tp, _, _ = self._dummy_meta(size, 1)
             meta.slot_mapping.fill_(-1)
-            # warm-up run on the side stream, then capture
-            s = torch.cuda.Stream(device=self.device)
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                h = self._forward(Tp, meta)
-                self.model.compute_logits(h)
-            torch.cuda.current_stream().wait_stream(s)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            c0 = ops.launch_counter[0]
-            with torch.cuda.graph(g, pool=self.graph_pool):
-                hidden = self._forward(Tp, meta)
-            # kernels recorded into the graph run at every replay, not at capture
-            self.graph_launches[size] = ops.launch_counter[0] - c0
-            ops.launch_counter[0] = c0
-            self.graphs[size] = (g, hidden)
+            desc = BatchDescriptor(num_tokens=size)
+            self.graph_wrapper.capture(desc, Tp, meta, warmup=warm)
+            self.graphs[size] = desc
         torch.cuda.synchronize()

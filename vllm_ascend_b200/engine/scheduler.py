@@ -48,6 +48,7 @@ class Scheduler:
         self.requests: dict[str, Request] = {}
         self.finished_since_last: list[str] = []
         self.kv_connector = kv_connector
+        self.max_loras = 0          # set by the engine when LoRA is enabled
         self.step_id = 0
         # blocks promised to admitted requests for their whole life (prompt + max_tokens);
         # admission keeps the sum within the pool so decode never has to preempt
@@ -104,6 +105,11 @@ class Scheduler:
     def _can_admit(self, req: Request, num_new_blocks: int) -> bool:
         if not self.pool.can_allocate(num_new_blocks):
             return False
+        if self.max_loras and req.lora_request is not None:
+            # a batch can address at most max_loras adapter slots
+            active = {r.lora_request.lora_int_id for r in self.running if r.lora_request is not None}
+            if req.lora_request.lora_int_id not in active and len(active) >= self.max_loras:
+                return False
         if self.reserve_full and self.running:
             fb = self._final_blocks(req)
             room = self.pool.num_blocks - 1 - self._committed_blocks
@@ -223,7 +229,8 @@ class Scheduler:
             if self.pool.enable_prefix_caching and req.num_computed_tokens == 0 and not req.block_ids:
                 hashes = self._hashes.get(req.request_id)
                 if hashes is None:
-                    hashes = self.pool.block_hashes(req.prompt_token_ids)
+                    extra = b"" if req.lora_request is None else f"lora{req.lora_request.lora_int_id}".encode()
+                    hashes = self.pool.block_hashes(req.prompt_token_ids, extra)
                     self._hashes[req.request_id] = hashes
                 # never treat the whole prompt as cached: the last token must be computed
                 max_hit = (req.num_prompt_tokens - 1) // self.block_size

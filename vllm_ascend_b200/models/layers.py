@@ -102,11 +102,19 @@ class Linear:
         self.bias = bias
         self.name = name
         self.quant = None           # quantization.LinearMethod or None
+        self.lora = None            # lora.manager.LoRALayerState or None
+
+    def _lora_on(self) -> bool:
+        return self.lora is not None and self.lora.punica.any_active
 
     def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.quant is not None:
-            return self.quant.apply(self, x, residual)
-        return ops.linear(x, self.weight, self.bias, residual)
+            y = self.quant.apply(self, x, residual)
+        else:
+            y = ops.linear(x, self.weight, self.bias, residual)
+        if self._lora_on():
+            y = self.lora.apply(x, y)
+        return y
 
     def named_tensors(self):
         yield "weight", self.weight
@@ -158,6 +166,8 @@ class RowParallelLinear(Linear):
             y = self.quant.apply(self, x, None, skip_bias=self.comm.rank != 0)
         else:
             y = ops.linear(x, self.weight, self.bias if self.comm.rank == 0 else None)
+        if self._lora_on():         # partial delta of this rank's input shard, reduced with y
+            y = self.lora.apply(x, y)
         if self.reduce_results:
             y = self.comm.all_reduce(y)
         if residual is not None:
@@ -281,6 +291,6 @@ class SwiGLUMLP:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         gu = self.gate_up_proj
-        if gu.quant is None and gu.bias is None and not gu.gather_output:
+        if gu.quant is None and gu.bias is None and not gu.gather_output and not gu._lora_on():
             return self.down_proj(ops.linear_swiglu(x, gu.weight))
         return self.down_proj(ops.silu_and_mul(gu(x)))

@@ -21,7 +21,7 @@ from . import reference as ref
 _BF16 = torch.bfloat16
 
 #: number of launches of this package's own kernels (bench.py reports it)
-launch_counter = [0]
+launch_counter = _native.launch_counter
 
 
 def _use_native(t: torch.Tensor) -> bool:
