@@ -71,8 +71,89 @@ def symm_allreduce():
     return {"max_err": max(errs), "status": status}
 
 
+def moe_fused():
+    """Fused dispatch/GEMM/combine over peer memory vs a dense fp32 oracle that holds every
+    expert; uneven token counts per rank, padded (-1) routes, eager and graph replay."""
+    from types import SimpleNamespace
+    from vllm_ascend_b200 import _native
+    from vllm_ascend_b200.config import ModelConfig, EngineConfig
+    from vllm_ascend_b200.ops.moe_fused import FusedMoEComm
+    from vllm_ascend_b200.parallel import state as pstate
+    rank, local, world = pstate.init_distributed()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    _native.load(required=True)
+    st = pstate.initialize_model_parallel(tp=1, dp=world)
+    ep = pstate.get_ep_group() if pstate.get_ep_group().world_size == world else pstate.get_world_group()
+    E, topk, H, I = 8 * world, 4, 512, 256
+    mc = SimpleNamespace(hidden_size=H, moe_intermediate_size=I, num_experts=E, num_experts_per_tok=topk)
+    comm = FusedMoEComm(SimpleNamespace(model=mc), dev, ep, capacity=64)
+    g = torch.Generator(device="cpu").manual_seed(1)
+    w13_full = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16()
+    w2_full = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16()
+    El = E // world
+    block = SimpleNamespace(w13=w13_full[rank * El:(rank + 1) * El].contiguous().to(dev),
+                            w2=w2_full[rank * El:(rank + 1) * El].contiguous().to(dev), quant=None)
+
+    def oracle(x, w, ids):
+        out = torch.zeros(x.shape[0], H)
+        for t in range(x.shape[0]):
+            for k in range(topk):
+                e = int(ids[t, k])
+                if e < 0:
+                    continue
+                h = w13_full[e].float() @ x[t].float()
+                a = (torch.nn.functional.silu(h[:I]) * h[I:]).bfloat16().float()
+                out[t] += float(w[t, k]) * (w2_full[e].float() @ a).bfloat16().float()
+        return out
+
+    errs = []
+    token_counts = [[5, 64], [0, 17], [33, 1], [64, 64]]
+    for it, cnt in enumerate(token_counts):
+        T = cnt[rank % 2]
+        gi = torch.Generator(device="cpu").manual_seed(10 * it + rank)
+        x = (torch.randn(T, H, generator=gi) * 0.5).bfloat16()
+        ids = torch.stack([torch.randperm(E, generator=gi)[:topk] for _ in range(T)]).int() if T else \
+            torch.zeros(0, topk, dtype=torch.int32)
+        if T > 2:
+            ids[1, 2:] = -1            # padded routes
+        w = torch.rand(T, topk, generator=gi)
+        y = comm.forward(block, x.to(dev), w.to(dev), ids.to(dev))
+        torch.cuda.synchronize()
+        ref = oracle(x, w, ids)
+        if T:
+            errs.append(float((y.float().cpu() - ref).abs().max() / (ref.abs().max() + 1e-6)))
+    # graph capture + replay of the four launches
+    T = 16
+    gi = torch.Generator(device="cpu").manual_seed(99 + rank)
+    xs = (torch.randn(T, H, generator=gi) * 0.5).bfloat16().to(dev)
+    ids = torch.stack([torch.randperm(E, generator=gi)[:topk] for _ in range(T)]).int().to(dev)
+    w = torch.rand(T, topk, generator=gi).to(dev)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        comm.forward(block, xs, w, ids)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        yg = comm.forward(block, xs, w, ids)
+    for rep in range(2):
+        xs.copy_((torch.randn(T, H, generator=gi) * 0.5).bfloat16())
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = oracle(xs.cpu(), w.cpu(), ids.cpu())
+        errs.append(float((yg.float().cpu() - ref).abs().max() / (ref.abs().max() + 1e-6)))
+    status = int(_native.status_word(dev).item())
+    torch.distributed.barrier()
+    graph = None
+    all_errs = [None] * world
+    torch.distributed.all_gather_object(all_errs, errs)
+    return {"max_rel_err": max(max(e) for e in all_errs), "status": status, "calls": comm.calls}
+
+
 if __name__ == "__main__":
-    res = {"tp_generate": tp_generate, "symm_allreduce": symm_allreduce}[sys.argv[1]]()
+    res = {"tp_generate": tp_generate, "symm_allreduce": symm_allreduce, "moe_fused": moe_fused}[sys.argv[1]]()
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps(res), flush=True)
     if torch.distributed.is_initialized():

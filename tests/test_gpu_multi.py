@@ -54,3 +54,10 @@ def test_fused_tp2_matches_single_gpu_and_nccl():
     assert agree(nccl["tokens"], single["tokens"]) > 0.8
     assert agree(fused["tokens"], nccl["tokens"]) > 0.8
     assert fused["tokens"] == graph["tokens"]
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_moe_dispatch_gemm_combine_over_peer_memory():
+    r = _run(2, "moe_fused")
+    assert r["status"] == 0
+    assert r["max_rel_err"] < 0.03

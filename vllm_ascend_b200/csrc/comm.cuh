@@ -26,6 +26,20 @@ struct CommCtl {
   uint32_t pad[9];
 };
 
+// Control block of the fused MoE dispatch/GEMM/combine path (lives at the start of the MoE
+// symmetric region of every rank).  All flags are epochs of the same monotonically
+// increasing call counter.
+struct MoeCtl {
+  uint32_t hist_flag[kMaxRanks];   // peer src published its routing histogram for epoch e
+  uint32_t disp_flag[kMaxRanks];   // peer src finished writing its token rows for epoch e
+  uint32_t comb_flag[kMaxRanks];   // peer (expert owner) finished writing my result rows
+  uint32_t epoch;                  // local: calls completed so far
+  uint32_t done_ctr;               // "last block" detection, dispatch kernel
+  uint32_t done_ctr2;              // same, scatter GEMM
+  uint32_t done_ctr3;              // same, reduce kernel
+  uint32_t pad[12];
+};
+
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

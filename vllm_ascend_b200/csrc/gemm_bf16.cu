@@ -35,7 +35,9 @@ constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_MAX_GROUPS = 512;
 
-enum : int { GEMM_AG = 1, GEMM_RS = 2, GEMM_SWIGLU = 4, GEMM_GROUPED = 8 };
+enum : int { GEMM_AG = 1, GEMM_RS = 2, GEMM_SWIGLU = 4, GEMM_GROUPED = 8,
+              GEMM_WAITFLAGS = 16,   // producer waits for every rank's flag before the first load
+              GEMM_SCATTER = 32 };   // epilogue stores row i to peer (row_meta[i] >> 24), row (row_meta[i] & 0xffffff)
 
 template <int BN>
 struct GemmCfg {
@@ -74,6 +76,12 @@ struct GemmParams {
   const int* group_offsets;   // [num_groups + 1] row offsets into A / C
   int num_groups;
   int w_rows_per_group;       // rows of W per group
+  // ---- WAITFLAGS / SCATTER (fused MoE): rs_dst[] = peers' combine buffers
+  const uint32_t* wait_flags;   // [num_ranks] local flags
+  const uint32_t* wait_epoch;   // wait for *wait_epoch + 1
+  const int* row_meta;          // [rows] (dst rank << 24) | dst row
+  MoeCtl* moe_ctl;              // local control block (epoch, done counter)
+  uint32_t* moe_flag_dst[kMaxRanks];   // &moe_ctl(o)->comb_flag[my_rank]
 };
 
 struct TileCoord {
@@ -182,6 +190,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t phase = 0;
     uint32_t ag_epoch = 0;
     if (p.mode & GEMM_AG) ag_epoch = *((volatile const uint32_t*)p.ag_epoch);
+    if ((p.mode & GEMM_WAITFLAGS) && blockIdx.x < num_tiles) {
+      // rows of A are written by peers: wait until every rank has published this call's epoch
+      if (lane == 0) {
+        const uint32_t e = *((volatile const uint32_t*)p.wait_epoch) + 1;
+        for (int s = 0; s < p.num_ranks; s++)
+          if (!wait_flag_ge(&p.wait_flags[s], e, p.status)) { *abort_word = B200_TIMEOUT; break; }
+        fence_proxy_async_global();
+      }
+      __syncwarp();
+      if (*abort_word) goto done;
+    }
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       TileCoord c;
       tile_coord<BN>(p, grp_tiles, t, c);
@@ -271,6 +290,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int owner = row_ok ? row / p.rows_per_owner : 0;
         const int local = row - owner * p.rows_per_owner;
         crow = p.rs_dst[owner] + ((size_t)p.my_rank * p.rows_per_owner + local) * p.ldc;
+      } else if (p.mode & GEMM_SCATTER) {
+        const int meta = row_ok ? p.row_meta[row] : 0;
+        crow = p.rs_dst[(meta >> 24) & (kMaxRanks - 1)] + (size_t)(meta & 0xffffff) * p.ldc;
       } else {
         crow = p.C + (size_t)row * p.ldc;
       }
@@ -335,7 +357,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
-    if (p.mode & GEMM_RS) __threadfence_system();   // partial rows visible to their owners
+    if (p.mode & (GEMM_RS | GEMM_SCATTER)) __threadfence_system();   // rows visible to their owners
   }
 done:
   tc_fence_before();
@@ -354,6 +376,16 @@ done:
       for (int o = 0; o < p.num_ranks; o++) st_release_sys(p.rs_flag_dst[o], epoch);
       p.ctl->rs_epoch = epoch;
       p.ctl->done_ctr = 0;
+      __threadfence();
+    }
+  } else if ((p.mode & GEMM_SCATTER) && threadIdx.x == 0) {
+    // last CTA tells every token owner that this rank's expert outputs are in its buffer
+    const uint32_t prev = atomicAdd(&p.moe_ctl->done_ctr2, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      const uint32_t epoch = *((volatile uint32_t*)&p.moe_ctl->epoch) + 1;
+      for (int o = 0; o < p.num_ranks; o++) st_release_sys(p.moe_flag_dst[o], epoch);
+      p.moe_ctl->done_ctr2 = 0;
       __threadfence();
     }
   }
@@ -575,4 +607,58 @@ B200_API int b200_grouped_gemm_bf16(const void* A, const void* W, void* C, const
   if (swiglu || N % 256 == 0)
     return launch_gemm<256>(A, W, p, lda, ldw, total_rows, w_rows, 0, stream);
   return launch_gemm<128>(A, W, p, lda, ldw, total_rows, w_rows, 0, stream);
+}
+
+// Fused-MoE expert GEMMs over the packed receive pool of this rank.
+//   gemm1: act[r, :I] = silu(X W1g^T) * (X W1u^T) for the rows of every local expert; the
+//          producer first waits until every rank's dispatch flag reached epoch + 1.
+//   gemm2: row r of act W2^T is stored straight into the token owner's combine buffer over
+//          peer memory (owner and row from row_meta), then the owners are flagged.
+// offsets: device int32 [num_groups + 1]; pool_rows: capacity of the pool (rows of X / act).
+B200_API int b200_moe_gemm1_bf16(const void* X, const void* W13, void* act, const void* offsets,
+                                 int num_groups, long pool_rows, int I, int K, void* moe_ctl,
+                                 int num_ranks, int* status, cudaStream_t stream) {
+  if ((K & 7) || (I % 128) || num_groups > GEMM_MAX_GROUPS || num_ranks > kMaxRanks) return 9100;
+  GemmParams p;
+  init_params(p);
+  p.M = (int)pool_rows; p.N = I; p.K = K; p.ldc = I;
+  p.C = (__nv_bfloat16*)act;
+  p.status = status;
+  p.mode = GEMM_GROUPED | GEMM_SWIGLU | GEMM_WAITFLAGS;
+  p.group_offsets = (const int*)offsets;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = 2 * I;
+  p.up_row_offset = I;
+  MoeCtl* c = (MoeCtl*)moe_ctl;
+  p.wait_flags = c->disp_flag;
+  p.wait_epoch = &c->epoch;
+  p.num_ranks = num_ranks;
+  return launch_gemm<256>(X, W13, p, K, K, pool_rows, (long)num_groups * 2 * I, 0, stream);
+}
+
+B200_API int b200_moe_gemm2_scatter_bf16(const void* act, const void* W2, const void* offsets,
+                                         const void* row_meta, int num_groups, long pool_rows,
+                                         int H, int I, void* const* comb_bufs,
+                                         void* const* peer_moe_ctl, int my_rank, int num_ranks,
+                                         int* status, cudaStream_t stream) {
+  if ((I & 7) || (H & 7) || num_groups > GEMM_MAX_GROUPS || num_ranks > kMaxRanks) return 9100;
+  GemmParams p;
+  init_params(p);
+  p.M = (int)pool_rows; p.N = H; p.K = I; p.ldc = H;
+  p.status = status;
+  p.mode = GEMM_GROUPED | GEMM_SCATTER;
+  p.group_offsets = (const int*)offsets;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = H;
+  p.row_meta = (const int*)row_meta;
+  p.my_rank = my_rank;
+  p.num_ranks = num_ranks;
+  for (int o = 0; o < num_ranks; o++) {
+    p.rs_dst[o] = (__nv_bfloat16*)comb_bufs[o];
+    p.moe_flag_dst[o] = &((MoeCtl*)peer_moe_ctl[o])->comb_flag[my_rank];
+  }
+  p.moe_ctl = (MoeCtl*)peer_moe_ctl[my_rank];
+  if (H % 256 == 0)
+    return launch_gemm<256>(act, W2, p, I, I, pool_rows, (long)num_groups * H, 0, stream);
+  return launch_gemm<128>(act, W2, p, I, I, pool_rows, (long)num_groups * H, 0, stream);
 }

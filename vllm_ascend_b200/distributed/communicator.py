@@ -46,7 +46,7 @@ class B200Communicator:
         out = torch.empty_like(x)
         ptrs = self.symm.ptr_array(self._oneshot_off)
         _native.check(_native.lib().b200_allreduce_oneshot(
-            self.symm.ctl_ptrs, ptrs, out.data_ptr(), x.numel(), self.rank, self.world_size,
+            ptrs, self.symm.ctl_ptrs, out.data_ptr(), x.numel(), self.rank, self.world_size,
             _native.stream_ptr()), "allreduce_oneshot")
         return out
 
@@ -71,8 +71,8 @@ class B200Communicator:
     def send(self, x: torch.Tensor, dst: int) -> None:
         dist.send(x, self.group.ranks[dst], group=self.group.device_group)
 
-    def recv(self, shape, dtype, src: int, device=None) -> torch.Tensor:
-        t = torch.empty(shape, dtype=dtype, device=device or self.group.device)
+    def recv(self, shape, dtype, src: int, device) -> torch.Tensor:
+        t = torch.empty(shape, dtype=dtype, device=device)
         dist.recv(t, self.group.ranks[src], group=self.group.device_group)
         return t
 

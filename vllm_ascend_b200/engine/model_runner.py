@@ -81,7 +81,7 @@ class ModelRunner:
         self._h_tile = torch.zeros((2, max_tiles), dtype=i32, pin_memory=pin)
         self._h_sampled = torch.zeros(B, dtype=i64, pin_memory=pin)
         # ---- CUDA graphs
-        self.graphs: dict[int, object] = {}     # capture size -> BatchDescriptor
+        self.graphs: dict[tuple, object] = {}     # (capture size, has_lora) -> BatchDescriptor
         self.graph_wrapper = None
         self.lora_manager = None
         self.graph_pool = None
@@ -342,7 +342,7 @@ class ModelRunner:
         meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
         t_prep = time.perf_counter()
         if gsize is not None:
-            desc = self.graphs[gsize]
+            desc = self.graphs[(gsize, self.lora_manager is not None and self.lora_manager.punica.any_active)]
             hidden_out = self.graph_wrapper.replay(desc)
             self.stats["graph_replays"] += 1
             self.stats["graph_kernel_launches"] += self.graph_wrapper.entries[desc].num_launches
@@ -472,10 +472,18 @@ class ModelRunner:
             self.model.compute_logits(self._forward(Tp, meta))
         self.graph_wrapper = CUDAGraphWrapper(self._forward, cc.cudagraph_mode, self.graph_pool,
                                               launch_counter=ops.launch_counter)
+        # with adapters enabled every size is captured twice: the LoRA kernels are part of the
+        # graph only when some request of the step uses an adapter
+        variants = [False, True] if self.lora_manager is not None else [False]
         for size in sorted(self.capture_sizes, reverse=True):
-            meta, T, Tp, _, _ = self._dummy_meta(size, 1)
-            meta.slot_mapping.fill_(-1)
-            desc = BatchDescriptor(num_tokens=size)
-            self.graph_wrapper.capture(desc, Tp, meta, warmup=warm)
-            self.graphs[size] = desc
+            for has_lora in variants:
+                meta, T, Tp, _, _ = self._dummy_meta(size, 1)
+                meta.slot_mapping.fill_(-1)
+                if self.lora_manager is not None:
+                    self.lora_manager.punica.any_active = has_lora
+                desc = BatchDescriptor(num_tokens=size, has_lora=has_lora)
+                self.graph_wrapper.capture(desc, Tp, meta, warmup=warm)
+                self.graphs[(size, has_lora)] = desc
+        if self.lora_manager is not None:
+            self.lora_manager.punica.any_active = False
         torch.cuda.synchronize()
