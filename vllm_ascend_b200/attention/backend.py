@@ -1,0 +1,115 @@
+"""Attention backend descriptors: what a host framework asks a backend about (name, KV-cache
+shape, block-size support, implementation and metadata-builder classes, block copy).
+
+GQA/MHA backend contract of vllm_ascend/attention/attention_v1.py:82-157: KV cache
+``(2, num_blocks, block_size, kv_heads, head_dim)`` logical shape, kernel block size 128,
+states PrefillNoCache / PrefillCacheHit / DecodeOnly / ChunkedPrefill / SpecDecoding,
+``swap_blocks`` / ``copy_blocks`` (attention_v1.py:119-145).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native, ops
+from .metadata import AttentionMetadata, AttentionState  # noqa: F401  (re-exported)
+
+
+class B200AttentionImpl:
+    """Paged GQA attention: writes the step's K/V into the cache (done by the fused
+    q/k-norm + RoPE + KV-write kernel upstream of this call) and attends over it."""
+
+    def __init__(self, num_heads: int, head_size: int, scale: float, num_kv_heads: int,
+                 sliding_window=None, **_):
+        self.num_heads, self.head_size, self.scale = num_heads, head_size, scale
+        self.num_kv_heads, self.sliding_window = num_kv_heads, sliding_window
+
+    def forward(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                meta: AttentionMetadata) -> torch.Tensor:
+        return ops.paged_attention(q, k_cache, v_cache, meta, self.scale, self.sliding_window or 0)
+
+
+class B200MetadataBuilder:
+    """Builds ``AttentionMetadata`` from per-request query lengths and context lengths."""
+
+    def __init__(self, block_size: int, device):
+        self.block_size, self.device = block_size, torch.device(device)
+
+    def build(self, query_lens, seq_lens, block_table: torch.Tensor, slot_mapping: torch.Tensor,
+              positions: torch.Tensor) -> AttentionMetadata:
+        import numpy as np
+        q = np.asarray(query_lens, dtype=np.int32)
+        s = np.asarray(seq_lens, dtype=np.int32)
+        cu = np.zeros(len(q) + 1, dtype=np.int32)
+        np.cumsum(q, out=cu[1:])
+        if (q == 1).all():
+            state = AttentionState.DecodeOnly
+        elif (s == q).all():
+            state = AttentionState.PrefillNoCache
+        else:
+            state = AttentionState.ChunkedPrefill
+        return AttentionMetadata(
+            num_reqs=len(q), num_actual_tokens=int(q.sum()), max_query_len=int(q.max()), max_seq_len=int(s.max()),
+            query_start_loc=torch.from_numpy(cu).to(self.device), seq_lens=torch.from_numpy(s).to(self.device),
+            block_table=block_table, slot_mapping=slot_mapping, positions=positions,
+            query_start_loc_cpu=cu, seq_lens_cpu=s, attn_state=state)
+
+
+class B200AttentionBackend:
+    accept_output_buffer = True
+
+    @staticmethod
+    def get_name() -> str:
+        return "B200_TCGEN05"
+
+    @staticmethod
+    def get_impl_cls():
+        return B200AttentionImpl
+
+    @staticmethod
+    def get_builder_cls():
+        return B200MetadataBuilder
+
+    @staticmethod
+    def get_kv_cache_shape(num_blocks: int, block_size: int, num_kv_heads: int, head_size: int) -> tuple:
+        return (2, num_blocks, block_size, num_kv_heads, head_size)
+
+    @staticmethod
+    def get_supported_block_size() -> list[int]:
+        return [128]
+
+    @staticmethod
+    def get_supported_head_sizes() -> list[int]:
+        return [64, 128]
+
+    @staticmethod
+    def copy_blocks(kv_caches: list, src_to_dst: torch.Tensor) -> None:
+        """src_to_dst [n, 2] int64 pairs; every cache tensor of every layer is updated."""
+        pairs = src_to_dst.to(torch.int64).contiguous()
+        for cache in kv_caches:
+            for t in (cache if isinstance(cache, (tuple, list)) else (cache,)):
+                _copy_blocks(t, pairs)
+
+    @staticmethod
+    def swap_blocks(src: torch.Tensor, dst: torch.Tensor, src_to_dst: torch.Tensor) -> None:
+        """Copies whole blocks between two caches (device<->device or device<->pinned host)."""
+        s = src_to_dst[:, 0].long()
+        d = src_to_dst[:, 1].long()
+        dst[d.to(dst.device)] = src[s.to(src.device)].to(dst.device, non_blocking=True)
+
+
+def _copy_blocks(t: torch.Tensor, pairs: torch.Tensor) -> None:
+    base = t
+    # the HND cache is a permuted view; copy on its dense storage
+    if not base.is_contiguous():
+        base = base.permute(0, 2, 1, 3)
+    if base.is_cuda and base.is_contiguous():
+        block_bytes = base[0].numel() * base.element_size()
+        import vllm_ascend_b200.distributed.kv_transfer.nvlink_connector  # noqa: F401  (signatures)
+        p = pairs.to(base.device)
+        _native.check(_native.lib().b200_copy_blocks(base.data_ptr(), p.data_ptr(), p.shape[0], block_bytes,
+                                                     _native.stream_ptr()), "copy_blocks")
+        _native.count_launch()
+        return
+    src = pairs[:, 0].to(t.device)
+    dst = pairs[:, 1].to(t.device)
+    t[dst] = t[src]

@@ -45,3 +45,25 @@ def mla_paged_attention(q_lat: torch.Tensor, q_pe: torch.Tensor, lat_cache: torc
         p = torch.softmax(s, dim=-1)
         out[qs:qe] = torch.einsum("hqk,kc->qhc", p, lat).to(out.dtype)
     return out
+
+
+class B200MLABackend:
+    """Descriptor of the MLA backend (vllm_ascend/attention/mla_v1.py: cache of a 512-wide
+    normalised latent plus a 64-wide RoPE key per token, MQA with absorbed up-projections)."""
+
+    @staticmethod
+    def get_name() -> str:
+        return "B200_MLA"
+
+    @staticmethod
+    def get_kv_cache_shape(num_blocks: int, block_size: int, num_kv_heads: int, head_size: int) -> tuple:
+        return (num_blocks, block_size, 1, head_size)
+
+    @staticmethod
+    def get_supported_block_size() -> list[int]:
+        return [128]
+
+    @staticmethod
+    def get_impl_cls():
+        from ..models.transformer import MLAAttention
+        return MLAAttention

@@ -34,7 +34,6 @@ _ATTN_BACKENDS = {
     (False, False, False): "vllm_ascend_b200.attention.backend.B200AttentionBackend",
     (True, False, False): "vllm_ascend_b200.attention.mla.B200MLABackend",
     (True, True, False): "vllm_ascend_b200.attention.sfa.B200SFABackend",
-    (True, False, True): "vllm_ascend_b200.attention.dsa.B200DSABackend",
 }
 
 
