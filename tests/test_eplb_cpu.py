@@ -1,0 +1,120 @@
+"""EPLB: placement policies, expert-map files, move planning, and a two-rank engine run in
+which experts migrate between ranks while generation continues (gloo, CPU)."""
+import json
+import os
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+
+from vllm_ascend_b200.eplb import expert_map as em
+from vllm_ascend_b200.eplb.policy import imbalance, make_policy, rank_loads
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _skewed(L, E, seed=0):
+    rng = np.random.default_rng(seed)
+    load = rng.zipf(1.6, size=(L, E)).astype(np.float64)
+    return np.minimum(load, 200.0)
+
+
+@pytest.mark.parametrize("ptype", [0, 1, 2, 3])
+def test_policies_keep_placements_valid_and_do_not_hurt(ptype):
+    L, E, R, red = 3, 16, 4, 4
+    place = em.initial_placement(L, E, R, red)
+    assert place.shape == (L, R, (E + red) // R)
+    em.validate(place, E)
+    load = _skewed(L, E)
+    new = make_policy(ptype).rebalance(place, load)
+    assert new.shape == place.shape
+    em.validate(new, E)
+    before = np.mean([imbalance(place[l], load[l]) for l in range(L)])
+    after = np.mean([imbalance(new[l], load[l]) for l in range(L)])
+    if ptype in (1, 2, 3):
+        assert after <= before + 1e-9
+    if ptype == 1:
+        assert after < before            # skewed load: greedy packing with replicas must help
+        for l in range(L):               # no rank holds two copies of an expert
+            assert all(len(set(row)) == len(row) for row in new[l])
+    if ptype == 2:                       # bounded number of changed slots
+        assert (new != place).sum() <= L * 2 * 4
+
+
+def test_rank_loads_split_over_replicas():
+    place = np.array([[0, 1], [0, 2]])
+    load = np.array([10.0, 3.0, 5.0])
+    assert rank_loads(place, load).tolist() == [8.0, 10.0]
+
+
+def test_log2phy_moves_and_file_roundtrip(tmp_path):
+    old = np.array([[0, 1, 2], [3, 4, 0]])
+    new = np.array([[0, 1, 4], [3, 2, 0]])
+    table, counts = em.build_log2phy(old, 5, prefer_rank=1)
+    assert counts.tolist() == [2, 1, 1, 1, 1]
+    assert table[0].tolist() == [5, 0]           # the copy on rank 1 (slot 1*3+2) comes first
+    moves = em.plan_moves(old, new)
+    assert sorted((m.expert, m.src_rank, m.dst_rank, m.dst_slot) for m in moves) == [(2, 0, 1, 1), (4, 1, 0, 2)]
+    p = em.initial_placement(2, 8, 2, 2)
+    path = str(tmp_path / "map.json")
+    em.save_placement(path, p)
+    assert (em.load_placement(path) == p).all()
+    doc = json.load(open(path))
+    assert doc["moe_layer_count"] == 2 and doc["layer_list"][0]["device_list"][1]["device_id"] == 1
+    with pytest.raises(ValueError):
+        em.validate(np.array([[[0, 1], [1, 2]]]), 4)
+
+
+WORKER = textwrap.dedent("""
+    import json, os, sys
+    import numpy as np
+    sys.path.insert(0, {root!r})
+    from vllm_ascend_b200.config import get_model_config
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    mode = sys.argv[1]
+    add = {{}}
+    if mode == "eplb":
+        add = {{"eplb_config": {{"dynamic_eplb": True, "num_redundant_experts": 2, "eplb_policy_type": 1,
+                                "expert_heat_collection_interval": 4, "algorithm_execution_interval": 2,
+                                "expert_map_record_path": sys.argv[2]}}}}
+    cfg = get_model_config("tiny-moe")
+    llm = LLM(cfg, device="cpu", tensor_parallel_size=1, enable_expert_parallel=True, additional_config=add,
+              max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(6)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    res = {{"tokens": [o.outputs[0].token_ids for o in outs]}}
+    if llm.engine.eplb is not None:
+        res["stats"] = llm.engine.eplb.stats
+        res["slots"] = int(llm.engine.eplb.a.S)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print("RESULT " + json.dumps(res), flush=True)
+""")
+
+
+def _run(mode, record=""):
+    from test_tp_cpu import _free_port
+    script = WORKER.format(root=ROOT)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="2",
+               OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, "-c", script, mode, record], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, e[-3000:]
+    return json.loads([l for l in outs[0][0].splitlines() if l.startswith("RESULT ")][-1][7:])
+
+
+def test_engine_output_unchanged_while_experts_migrate(tmp_path):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    record = str(tmp_path / "placement.json")
+    base = _run("plain")
+    eplb = _run("eplb", record)
+    assert eplb["tokens"] == base["tokens"]
+    assert eplb["stats"]["updates"] >= 1
+    assert eplb["slots"] > 0 and os.path.exists(record)
+    placement = em.load_placement(record)
+    em.validate(placement, 8) if placement.max() < 8 else None

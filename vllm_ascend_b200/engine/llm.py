@@ -45,6 +45,14 @@ class LLMEngine:
         num_blocks = self.worker.determine_num_blocks()
         self.worker.initialize_cache(num_blocks)
         self.worker.compile_or_warm_up_model()
+        self.eplb = None
+        from ..platform_config import get_b200_config
+        ecfg = get_b200_config().eplb_config
+        if cfg.model.is_moe and pc.enable_expert_parallel and world > 1 and \
+                (ecfg.dynamic_eplb or ecfg.expert_map_path or ecfg.num_redundant_experts):
+            from ..eplb.updater import EplbAdaptor, EplbUpdater
+            self.eplb = EplbUpdater(EplbAdaptor(self.runner.model, pstate.get_ep_group(),
+                                                ecfg.num_redundant_experts), ecfg)
         self.kv_connector = None
         if cfg.kv_transfer_config:
             from ..distributed.kv_transfer import create_connector
@@ -95,6 +103,8 @@ class LLMEngine:
         finished = self.scheduler.update_from_output(so, sampled)
         if self.kv_connector is not None:
             self.kv_connector.step_finished(so, self.scheduler)
+        if self.eplb is not None:
+            self.eplb.step()
         self.host_times["update"] += time.perf_counter() - t2
         return finished
 
@@ -118,6 +128,8 @@ class LLMEngine:
         t1 = time.perf_counter()
         if so is None or so.is_empty:
             self.runner.execute_dummy()
+            if self.eplb is not None:
+                self.eplb.step()
             self.host_times["execute"] += time.perf_counter() - t1
             return True
         if self.kv_connector is not None:
@@ -131,6 +143,8 @@ class LLMEngine:
         self.scheduler.update_from_output(so, sampled)
         if self.kv_connector is not None:
             self.kv_connector.step_finished(so, self.scheduler)
+        if self.eplb is not None:
+            self.eplb.step()
         self.host_times["schedule"] += t1 - t0
         self.host_times["execute"] += t2 - t1
         self.host_times["update"] += time.perf_counter() - t2

@@ -66,7 +66,8 @@ class SparseMoeBlock:
             self.shared = SwiGLUMLP(pf, f"{prefix}.shared_experts", H, I * cfg.n_shared_experts,
                                     comm, reduce_results=False)
         # logical -> physical redirect for redundant experts (EPLB); identity by default
-        self.log2phy: Optional[torch.Tensor] = None
+        self.log2phy: Optional[torch.Tensor] = None          # [E, max_replicas] physical slot ids
+        self.log2phy_count: Optional[torch.Tensor] = None    # [E] replicas per expert
         self.expert_load: Optional[torch.Tensor] = None      # per-physical-expert hit counter
 
     def route(self, x: torch.Tensor):
@@ -75,12 +76,16 @@ class SparseMoeBlock:
         w, ids = fused_moe.gating_topk(logits, cfg.num_experts_per_tok, cfg.scoring_func,
                                        cfg.norm_topk_prob, cfg.n_group, cfg.topk_group,
                                        self.e_bias, cfg.routed_scaling_factor)
-        if self.log2phy is not None:
-            ids = self.log2phy[ids.long()].to(torch.int32)
-        if self.expert_load is not None:
+        if self.expert_load is not None:          # per logical expert, before any redirect
             self.expert_load.scatter_add_(0, ids.flatten().long(),
                                           torch.ones(ids.numel(), dtype=self.expert_load.dtype,
                                                      device=ids.device))
+        if self.log2phy is not None:
+            # logical -> physical slot; tokens spread over an expert's replicas round-robin
+            lid = ids.long()
+            n = self.log2phy_count[lid]
+            pick = torch.arange(ids.shape[0], device=ids.device).unsqueeze(1) % n
+            ids = self.log2phy[lid, pick].to(torch.int32)
         return w, ids
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:

@@ -34,7 +34,9 @@ class FusedMoEComm:
         self.world, self.rank = ep_group.world_size, ep_group.rank_in_group
         self.capacity = capacity or get_b200_config().fused_moe_max_tokens
         self.H, self.I = m.hidden_size, m.moe_intermediate_size
-        self.E, self.topk = m.num_experts, m.num_experts_per_tok
+        # physical expert slots: logical experts plus the redundant replicas of EPLB
+        self.E = m.num_experts + get_b200_config().eplb_config.num_redundant_experts
+        self.topk = m.num_experts_per_tok
         if self.E % self.world:
             raise ImportError("fused MoE path needs num_experts divisible by the EP size")
         if self.I % 128 or self.H % 8 or self.E > 512:
