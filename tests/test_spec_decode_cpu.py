@@ -1,0 +1,143 @@
+"""Speculative decoding on CPU: proposers, rejection sampling rules, and engine equivalence
+(greedy speculative generation must equal plain greedy generation token for token)."""
+import numpy as np
+import pytest
+import torch
+
+from vllm_ascend_b200 import LLM, SamplingParams
+from vllm_ascend_b200.sample.rejection_sampler import (RejectionSampler, block_verify_accept_len,
+                                                       entropy_threshold, rejection_sample_ref)
+from vllm_ascend_b200.spec_decode.ngram import NgramProposer, find_ngram_continuation
+from vllm_ascend_b200.spec_decode.suffix import SuffixProposer
+
+
+def test_ngram_lookup():
+    t = np.array([5, 6, 7, 8, 9, 1, 2, 6, 7, 8], dtype=np.int32)
+    assert find_ngram_continuation(t, 2, 4, 3).tolist() == [9, 1, 2]       # suffix 6 7 8 seen before
+    assert find_ngram_continuation(t, 4, 5, 3).tolist() == []              # no 4-gram repeats
+    assert find_ngram_continuation(np.array([1, 2, 3], dtype=np.int32), 1, 3, 2).tolist() == []
+    # the most recent occurrence wins
+    t2 = np.array([1, 2, 3, 9, 1, 2, 4, 9, 1, 2], dtype=np.int32)
+    assert find_ngram_continuation(t2, 2, 2, 1).tolist() == [4]
+    p = NgramProposer(3, 2, 4, max_model_len=12)
+    table = np.zeros((2, 16), dtype=np.int32)
+    table[1, :10] = t
+    assert [x.tolist() for x in p.propose(table, np.array([10]), np.array([1]))] == [[9]]   # capped by max_model_len
+
+
+def test_suffix_proposer_learns_across_requests():
+    p = SuffixProposer(3, key_len=2)
+    table = np.zeros((2, 32), dtype=np.int32)
+    table[0, :8] = [1, 2, 3, 4, 5, 6, 7, 8]
+    p.propose(table, np.array([8]), np.array([0]))
+    table[1, :4] = [9, 9, 3, 4]
+    out = p.propose(table, np.array([4]), np.array([1]))
+    assert out[0].tolist() == [5, 6, 7]
+
+
+def test_rejection_greedy_and_padding():
+    draft = torch.tensor([4, 5, 6, 7, 8], dtype=torch.int32)
+    cu = torch.tensor([0, 3, 3, 5], dtype=torch.int32)
+    argmax = torch.tensor([4, 5, 9, 7, 8], dtype=torch.int32)
+    bonus = torch.tensor([11, 12, 13], dtype=torch.int32)
+    out, num = rejection_sample_ref(draft, cu, argmax, bonus, None, None, None, None, torch.ones(3, dtype=torch.bool), 3)
+    assert out.tolist() == [[4, 5, 9, -1], [12, -1, -1, -1], [7, 8, 13, -1]]
+    assert num.tolist() == [3, 1, 3]
+
+
+def test_rejection_random_preserves_target_distribution():
+    """One draft position, deterministic proposal (no draft probs): emitted token must be
+    distributed as the target distribution."""
+    torch.manual_seed(0)
+    V, N = 6, 20000
+    pt = torch.tensor([0.05, 0.4, 0.1, 0.25, 0.15, 0.05])
+    x = 1
+    draft = torch.full((N,), x, dtype=torch.int32)
+    cu = torch.arange(N + 1, dtype=torch.int32)
+    probs = pt.expand(N, V).contiguous()
+    bonus = torch.full((N,), -7, dtype=torch.int32)
+    out, num = rejection_sample_ref(draft, cu, probs.argmax(-1).int(), bonus, probs, None, torch.rand(N),
+                                    torch.empty(N, V).exponential_(), torch.zeros(N, dtype=torch.bool), 1)
+    first = out[:, 0]
+    freq = torch.bincount(first.long(), minlength=V).float() / N
+    assert (freq - pt).abs().max() < 0.02
+    accepted = (num == 2)
+    assert abs(float(accepted.float().mean()) - 0.4) < 0.02
+    assert (out[accepted, 1] == -7).all()
+    # with draft probabilities: p_d = one-hot on another token x2 with p_t(x2) = 0.1 < 1
+    pd = torch.zeros(N, V)
+    pd[:, 2] = 1.0
+    draft2 = torch.full((N,), 2, dtype=torch.int32)
+    out2, _ = rejection_sample_ref(draft2, cu, probs.argmax(-1).int(), bonus, probs, pd, torch.rand(N),
+                                   torch.empty(N, V).exponential_(), torch.zeros(N, dtype=torch.bool), 1)
+    freq2 = torch.bincount(out2[:, 0].long(), minlength=V).float() / N
+    assert (freq2 - pt).abs().max() < 0.02
+
+
+def test_block_and_entropy_rules():
+    pt = torch.tensor([0.9, 0.2, 0.9])
+    pd = torch.tensor([1.0, 1.0, 1.0])
+    assert block_verify_accept_len(pt, pd, torch.tensor([0.5, 0.5, 0.1])) == 3     # joint ratio .9*.2*.9=.162 >= .1
+    assert block_verify_accept_len(pt, pd, torch.tensor([0.95, 0.5, 0.5])) == 0
+    conf = torch.tensor([0.97, 0.01, 0.01, 0.01])
+    flat = torch.full((4,), 0.25)
+    assert entropy_threshold(conf, 1.0, 0.9) > entropy_threshold(flat, 1.0, 0.9)
+    assert entropy_threshold(conf, 0.0, 0.6) == 0.6
+    rs = RejectionSampler("entropy_verify", 1.0, 0.5)
+    logits = torch.log(torch.stack([conf, flat]))
+    out, num = rs(torch.tensor([0, 2], dtype=torch.int32), torch.tensor([0, 2], dtype=torch.int32), logits,
+                  torch.tensor([3], dtype=torch.int32), torch.zeros(1, dtype=torch.bool), torch.ones(1), 2)
+    assert out[0, :2].tolist() == [0, 2] and int(num[0]) == 3      # both clear their thresholds
+    with pytest.raises(ValueError):
+        RejectionSampler("nope")
+
+
+@pytest.mark.parametrize("method", ["ngram", "suffix"])
+def test_engine_speculative_greedy_equals_plain_greedy(method):
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=48)
+    rng = np.random.default_rng(0)
+    # repetitive prompts so that lookups hit
+    base = rng.integers(1, 400, size=12).tolist()
+    prompts = [base * 3 + base[:5], rng.integers(1, 400, size=30).tolist(), (base[::-1] * 2)[:20]]
+    sp = SamplingParams(max_tokens=24, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM("tiny-qwen", **kw).generate(prompts, sp)]
+    llm = LLM("tiny-qwen", speculative_config={"method": method, "num_speculative_tokens": 3,
+                                               "prompt_lookup_min": 1, "prompt_lookup_max": 4}, **kw)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    st = llm.engine.runner.spec_stats
+    assert st["verify_steps"] > 0 and st["draft_tokens"] > 0
+    assert llm.engine.scheduler.num_draft_tokens == st["draft_tokens"]
+    # KV bookkeeping survived rejections: a second pass with the same engine is still right
+    got2 = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got2 == want
+
+
+def test_engine_speculative_random_sampling_runs_and_respects_max_tokens():
+    llm = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=128, max_num_seqs=4,
+              speculative_config={"method": "ngram", "num_speculative_tokens": 4, "prompt_lookup_min": 1})
+    prompts = [[7, 8, 9] * 8, [3, 4] * 10]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=17, temperature=0.8, top_k=20, seed=1, ignore_eos=True))
+    assert all(len(o.outputs[0].token_ids) == 17 for o in outs)
+
+
+@pytest.mark.parametrize("method", ["draft_model", "eagle"])
+def test_engine_model_based_proposers_keep_greedy_output(method):
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=40)
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(1, 400, size=n).tolist() for n in (45, 9, 70)]      # 70 > token budget: chunked prefill
+    sp = SamplingParams(max_tokens=14, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM("tiny-qwen", **kw).generate(prompts, sp)]
+    spec = {"method": method, "num_speculative_tokens": 3}
+    if method == "draft_model":
+        spec["model"] = "tiny-qwen"          # same weights as the target: every draft must be accepted
+    llm = LLM("tiny-qwen", speculative_config=spec, **kw)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    st = llm.engine.runner.spec_stats
+    assert st["draft_tokens"] > 0
+    if method == "draft_model":
+        assert st["accepted_tokens"] == st["draft_tokens"]
+        # far fewer target steps than tokens
+        assert st["verify_steps"] <= 5
+    assert llm.engine.runner.proposer.stats["draft_forwards"] > 0

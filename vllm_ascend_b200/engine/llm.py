@@ -60,6 +60,11 @@ class LLMEngine:
         self.scheduler = self._make_scheduler(num_blocks)
         if cfg.enable_lora:
             self.scheduler.max_loras = cfg.max_loras
+        if cfg.speculative_config:
+            from ..spec_decode import get_spec_decode_method
+            self.runner.proposer = get_spec_decode_method(cfg.speculative_config, self.runner)
+            self.scheduler.spec_slack = int(cfg.speculative_config.get("num_speculative_tokens", 3))
+        self._model_proposer = hasattr(self.runner.proposer, "propose_step")
         self.runner.capture_graphs()
         self._req_counter = itertools.count()
         self.eos_token_id: Optional[int] = None
@@ -83,6 +88,16 @@ class LLMEngine:
         self.scheduler.add_request(req)
         return rid
 
+    def _propose(self, so, sampled: dict) -> None:
+        p = self.runner.proposer
+        if p is None:
+            return
+        if self._model_proposer:
+            p.propose_step(so, sampled, self.runner.last_hidden, self.scheduler)
+        else:
+            self.runner.propose_draft_tokens([r for r, _ in so.scheduled
+                                              if r.status == RequestStatus.RUNNING and r.request_id in sampled])
+
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
 
@@ -92,6 +107,8 @@ class LLMEngine:
         t1 = time.perf_counter()
         if self.kv_connector is not None:
             self.kv_connector.start_load_kv(so)
+        if self._model_proposer:
+            self.runner.proposer.note_step_start(so)
         sampled = self.runner.execute(so)
         t2 = time.perf_counter()
         self.host_times["schedule"] += t1 - t0
@@ -101,6 +118,7 @@ class LLMEngine:
             if req.first_token_time is None and req.request_id in sampled:
                 req.first_token_time = now
         finished = self.scheduler.update_from_output(so, sampled)
+        self._propose(so, sampled)
         if self.kv_connector is not None:
             self.kv_connector.step_finished(so, self.scheduler)
         if self.eplb is not None:
@@ -134,6 +152,8 @@ class LLMEngine:
             return True
         if self.kv_connector is not None:
             self.kv_connector.start_load_kv(so)
+        if self._model_proposer:
+            self.runner.proposer.note_step_start(so)
         sampled = self.runner.execute(so)
         t2 = time.perf_counter()
         now = time.monotonic()
@@ -141,6 +161,7 @@ class LLMEngine:
             if req.first_token_time is None and req.request_id in sampled:
                 req.first_token_time = now
         self.scheduler.update_from_output(so, sampled)
+        self._propose(so, sampled)
         if self.kv_connector is not None:
             self.kv_connector.step_finished(so, self.scheduler)
         if self.eplb is not None:

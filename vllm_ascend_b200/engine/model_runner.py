@@ -60,7 +60,9 @@ class ModelRunner:
         self.row_num_blocks = np.zeros(self.max_seqs, dtype=np.int32)
         self.row_num_tokens = np.zeros(self.max_seqs, dtype=np.int32)
         # ---- persistent device inputs
-        T, B = self.max_tokens, self.max_seqs
+        # room for one extra token per sequence: draft-model catch-up passes append the newly
+        # sampled token of every request to a full step
+        T, B = self.max_tokens + self.max_seqs, self.max_seqs
         i64, i32 = torch.int64, torch.int32
         self.input_ids = torch.zeros(T, dtype=i64, device=device)
         self.positions = torch.zeros(T, dtype=i64, device=device)
@@ -84,6 +86,11 @@ class ModelRunner:
         self.graphs: dict[tuple, object] = {}     # (capture size, has_lora) -> BatchDescriptor
         self.graph_wrapper = None
         self.lora_manager = None
+        self.proposer = None
+        self.last_hidden = None      # final hidden states of the latest step, scheduling order
+        self.rejection_sampler = None
+        self.spec_stats = {"draft_tokens": 0, "accepted_tokens": 0, "verify_steps": 0}
+        self._sample_rows: list = []
         self.graph_pool = None
         self.capture_sizes: list[int] = []
         self.stats = {"graph_replays": 0, "eager_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0,
@@ -212,6 +219,10 @@ class ModelRunner:
         pos = np.arange(T, dtype=np.int64) - np.repeat(cu[:-1].astype(np.int64), q_lens) \
             + np.repeat(starts.astype(np.int64), q_lens)
         tok_rows = rows[req_idx]
+        for r in reqs:                      # draft tokens under verification follow the last token
+            sp_ = getattr(r, "spec_token_ids", None)
+            if sp_:
+                self.token_ids_cpu[r.row, r.num_tokens:r.num_tokens + len(sp_)] = sp_
         ids = self.token_ids_cpu[tok_rows, pos]
         blk = self.block_table_cpu[tok_rows, pos // self.block_size].astype(np.int64)
         slots = blk * self.block_size + pos % self.block_size
@@ -285,10 +296,16 @@ class ModelRunner:
         logits_idx = None
         sample_reqs = []
         sel = []
+        rows_per_req = []
         for i, r in enumerate(reqs):
-            if starts[i] + q_lens[i] >= r.num_tokens:
-                sel.append(int(cu[i + 1]) - 1)
+            end = int(starts[i] + q_lens[i])
+            if end >= r.num_tokens:
+                nrow = end - r.num_tokens + 1          # 1 + draft tokens verified in this step
+                base = int(cu[i + 1]) - nrow
+                sel.extend(range(base, base + nrow))
                 sample_reqs.append(r)
+                rows_per_req.append(nrow)
+        self._sample_rows = rows_per_req
         return meta, T, Tp, sel, sample_reqs
 
     def init_lora(self) -> None:
@@ -346,9 +363,11 @@ class ModelRunner:
             hidden_out = self.graph_wrapper.replay(desc)
             self.stats["graph_replays"] += 1
             self.stats["graph_kernel_launches"] += self.graph_wrapper.entries[desc].num_launches
+            self.last_hidden = hidden_out
             logits = self.model.compute_logits(hidden_out[:B])
         else:
             hidden = self._forward(Tp, meta)
+            self.last_hidden = hidden
             self.stats["eager_steps"] += 1
             if not sel:
                 return {}
@@ -357,6 +376,12 @@ class ModelRunner:
             else:
                 h_sel = hidden[torch.tensor(sel, dtype=torch.int64, device=self.device)]
             logits = self.model.compute_logits(h_sel)
+        if any(k > 1 for k in self._sample_rows):
+            out = self._sample_speculative(logits, sample_reqs, self._sample_rows)
+            t_sync = time.perf_counter()
+            self.stats["t_spec"] = self.stats.get("t_spec", 0.0) + (t_sync - t_start)
+            self.stats["n_spec"] = self.stats.get("n_spec", 0) + 1
+            return out
         md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
         if not md.all_greedy and not self.is_cuda:
             md.generator = self._cpu_generator()
@@ -384,6 +409,67 @@ class ModelRunner:
             self.token_ids_cpu[row, r.num_tokens] = t
             out[r.request_id] = [t]
         return out
+
+    def _sample_speculative(self, logits: torch.Tensor, sample_reqs: list, rows: list) -> dict:
+        """Verification step: ``rows[i]`` logits rows belong to request i (its last accepted
+        token followed by rows[i]-1 draft tokens).  Every row is sampled with the request's own
+        parameters (the last row gives the bonus token), then the rejection sampler decides how
+        many draft tokens stand."""
+        from ..sample.rejection_sampler import RejectionSampler
+        if self.rejection_sampler is None:
+            from ..platform_config import get_b200_config
+            rc = get_b200_config().rejection_sampler_config
+            method = "block_verify" if rc.enable_block_verify else (
+                "entropy_verify" if rc.enable_entropy_verify else "standard")
+            self.rejection_sampler = RejectionSampler(method, rc.posterior_alpha, rc.posterior_threshold)
+        dev = self.device
+        expanded = [r for r, k in zip(sample_reqs, rows) for _ in range(k)]
+        md = SamplingMetadata.build(expanded, dev, self.mcfg.vocab_size, self.cfg.seed)
+        if not md.all_greedy:
+            if md.offsets is not None:          # distinct random streams for the rows of one request
+                md.offsets = md.offsets + torch.tensor([j for k in rows for j in range(k)], dtype=torch.int64,
+                                                       device=dev)
+            if not self.is_cuda:
+                md.generator = self._cpu_generator()
+        logits_f = logits.float()
+        tokens_all = self.sampler(logits_f.clone() if not md.all_greedy else logits_f, md).to(torch.int32)
+        cu_rows = np.concatenate([[0], np.cumsum(rows)]).astype(np.int64)
+        last_rows = torch.from_numpy(cu_rows[1:] - 1).to(dev)
+        draft_rows = torch.from_numpy(np.concatenate([np.arange(cu_rows[i], cu_rows[i + 1] - 1)
+                                                      for i in range(len(rows))]).astype(np.int64)).to(dev)
+        draft = np.concatenate([np.asarray(r.spec_token_ids[:k - 1], dtype=np.int32)
+                                for r, k in zip(sample_reqs, rows)]) if draft_rows.numel() else np.zeros(0, np.int32)
+        cu_draft = torch.from_numpy((cu_rows - np.arange(len(rows) + 1)).astype(np.int32)).to(dev)
+        is_greedy = torch.tensor([r.sampling_params.greedy for r in sample_reqs], dtype=torch.bool, device=dev)
+        temp = torch.tensor([max(r.sampling_params.temperature, 1e-5) for r in sample_reqs], dtype=torch.float32,
+                            device=dev)
+        max_spec = max(rows) - 1
+        out, num = self.rejection_sampler(
+            torch.from_numpy(draft).to(dev), cu_draft, logits_f[draft_rows], tokens_all[last_rows].contiguous(),
+            is_greedy, temp, max_spec, generator=None if self.is_cuda else self._cpu_generator())
+        out_h, num_h = out.cpu().numpy(), num.cpu().numpy()
+        self.stats["d2h_bytes"] += out_h.nbytes + num_h.nbytes
+        res = {}
+        for i, r in enumerate(sample_reqs):
+            toks = [int(t) for t in out_h[i, :num_h[i]]]
+            self.token_ids_cpu[r.row, r.num_tokens:r.num_tokens + len(toks)] = toks
+            res[r.request_id] = toks
+        self.spec_stats["draft_tokens"] += int(draft.size)
+        self.spec_stats["accepted_tokens"] += int(np.maximum(num_h - 1, 0).sum())
+        self.spec_stats["verify_steps"] += 1
+        return res
+
+    def propose_draft_tokens(self, reqs: list) -> None:
+        """Fill ``req.spec_token_ids`` for running decode requests (after their tokens of this
+        step were appended)."""
+        if self.proposer is None or not reqs:
+            return
+        rows = np.fromiter((r.row for r in reqs), dtype=np.int64, count=len(reqs))
+        lens = np.fromiter((r.num_tokens for r in reqs), dtype=np.int64, count=len(reqs))
+        props = self.proposer.propose(self.token_ids_cpu, lens, rows)
+        for r, p in zip(reqs, props):
+            left = r.sampling_params.max_tokens - r.num_output_tokens - 1
+            r.spec_token_ids = [int(t) for t in p[:max(left, 0)]]
 
     @torch.inference_mode()
     def execute_dummy(self) -> None:

@@ -48,6 +48,9 @@ class Scheduler:
         self.requests: dict[str, Request] = {}
         self.finished_since_last: list[str] = []
         self.kv_connector = kv_connector
+        self.num_draft_tokens = 0
+        self.spec_slack = 0        # num_speculative_tokens when speculative decoding is on
+        self.num_accepted_tokens = 0
         self.max_loras = 0          # set by the engine when LoRA is enabled
         self.step_id = 0
         # blocks promised to admitted requests for their whole life (prompt + max_tokens);
@@ -99,7 +102,8 @@ class Scheduler:
             self.waiting.remove(req)
 
     def _final_blocks(self, req: Request) -> int:
-        n = min(req.num_prompt_tokens + req.sampling_params.max_tokens, self.cfg.max_model_len)
+        # draft tokens under verification occupy KV slots past the last accepted token
+        n = min(req.num_prompt_tokens + req.sampling_params.max_tokens + self.spec_slack, self.cfg.max_model_len)
         return (n + self.block_size - 1) // self.block_size
 
     def _can_admit(self, req: Request, num_new_blocks: int) -> bool:
@@ -143,6 +147,16 @@ class Scheduler:
         need = (num_tokens_after + self.block_size - 1) // self.block_size
         return max(0, need - len(req.block_ids))
 
+    def try_extend(self, req: Request, num_tokens_after: int) -> bool:
+        """Allocate the blocks ``req`` needs to hold ``num_tokens_after`` tokens if they are
+        free right now (never preempts); used to give draft tokens KV slots ahead of time."""
+        need = self._blocks_needed(req, num_tokens_after)
+        if need > self.pool.num_free_blocks:
+            return False
+        if need:
+            req.block_ids.extend(self.pool.allocate(need))
+        return True
+
     def _preempt(self, req: Request, out: SchedulerOutput) -> None:
         self.running.remove(req)
         self.pool.free(req.block_ids)
@@ -173,8 +187,11 @@ class Scheduler:
         i = 0
         while i < len(self.running) and budget > 0:
             req = self.running[i]
-            remaining = req.num_tokens + len(req.spec_token_ids) - req.num_computed_tokens
+            spec = len(req.spec_token_ids)
+            remaining = req.num_tokens + spec - req.num_computed_tokens
             n = min(remaining, budget)
+            if spec and n < remaining:       # the token budget cuts into the draft tokens
+                del req.spec_token_ids[max(0, spec - (remaining - n)):]
             if n <= 0:
                 i += 1
                 continue
@@ -289,7 +306,15 @@ class Scheduler:
         for req, n in out.scheduled:
             if req.status != RequestStatus.RUNNING:
                 continue
+            # draft tokens verified in this step: only the accepted ones leave valid KV behind
+            n_spec = max(0, req.num_computed_tokens + n - req.num_tokens)
             req.num_computed_tokens += n
+            if n_spec:
+                emitted = len(sampled.get(req.request_id) or ())
+                req.num_computed_tokens -= n_spec - max(emitted - 1, 0)
+                self.num_draft_tokens += n_spec
+                self.num_accepted_tokens += max(emitted - 1, 0)
+            req.spec_token_ids = []
             if self.pool.enable_prefix_caching:
                 hashes = self._hashes.get(req.request_id)
                 if hashes:
