@@ -1,0 +1,89 @@
+"""Kernel time shares of engine steps (torch.profiler / CUPTI), split by step kind.
+
+    python benchmarks/step_profile.py --model qwen3-8b --num-prompts 1024 --skip-steps 40 \
+        --mixed-steps 3 --decode-steps 3 --out gpurun_out/step_profile.txt
+
+Fills the engine with the benchmark workload, lets it reach steady state, then profiles a few
+mixed (prefill chunk + decodes) steps and, once prefill is over, a few decode-only steps.
+Numbers taken under the profiler are for shares only, never for throughput."""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+from collections import defaultdict
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="qwen3-8b")
+    ap.add_argument("--num-prompts", type=int, default=1024)
+    ap.add_argument("--input-len", type=int, default=1024)
+    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--max-num-seqs", type=int, default=1024)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--skip-steps", type=int, default=40)
+    ap.add_argument("--mixed-steps", type=int, default=3)
+    ap.add_argument("--decode-steps", type=int, default=3)
+    ap.add_argument("--out", default="step_profile.txt")
+    args = ap.parse_args()
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    llm = LLM(args.model, max_model_len=args.input_len + args.output_len + 16, max_num_seqs=args.max_num_seqs,
+              max_num_batched_tokens=args.max_num_batched_tokens, device="cuda")
+    eng = llm.engine
+    rng = np.random.default_rng(0)
+    sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
+    for _ in range(args.num_prompts):
+        eng.add_request(rng.integers(0, llm.cfg.model.vocab_size, size=args.input_len).tolist(), sp)
+    for _ in range(args.skip_steps):
+        eng.step()
+    acts = [torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA]
+    lines = []
+
+    def profile(kind: str, n: int, want_decode: bool):
+        # advance until the next step is of the wanted kind
+        guard = 0
+        while eng.has_unfinished() and guard < 100000:
+            waiting_prefill = any(r.num_computed_tokens < r.num_prompt_tokens for r in eng.scheduler.running) \
+                or len(eng.scheduler.waiting) > 0
+            if want_decode != waiting_prefill:
+                break
+            eng.step()
+            guard += 1
+        if not eng.has_unfinished():
+            lines.append(f"== {kind}: workload ended before such a step came up")
+            return
+        torch.cuda.synchronize()
+        with torch.profiler.profile(activities=acts) as prof:
+            for _ in range(n):
+                eng.step()
+            torch.cuda.synchronize()
+        agg = defaultdict(lambda: [0, 0.0])
+        for ev in prof.events():
+            if ev.device_type == torch.autograd.DeviceType.CUDA:
+                a = agg[ev.name[:90]]
+                a[0] += 1
+                a[1] += ev.device_time if hasattr(ev, "device_time") else ev.cuda_time
+        total = sum(v[1] for v in agg.values())
+        lines.append(f"== {kind}: {n} steps, {total / n / 1000:.2f} ms of kernel time per step, "
+                     f"{sum(v[0] for v in agg.values()) // n} launches per step")
+        for name, (cnt, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:18]:
+            lines.append(f"  {us / total * 100:5.1f}%  {us / n / 1000:8.3f} ms/step  {cnt // n:5d}/step  {name}")
+
+    profile("mixed (prefill chunk + decodes)", args.mixed_steps, want_decode=False)
+    profile("decode only", args.decode_steps, want_decode=True)
+    text = "\n".join(lines)
+    print(text)
+    os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
+    with open(args.out, "w") as f:
+        f.write(text + "\n")
+
+
+if __name__ == "__main__":
+    main()

@@ -116,3 +116,27 @@ def test_disaggregated_prefill_two_gpus_over_cuda_ipc():
     assert r["got"] == r["want"]
     assert r["stats"]["pulled_requests"] == 5 and r["stats"]["failed"] == 0
     assert pr["released"] == 5 and pr["delayed"] == 0
+
+
+def test_cpu_offload_connector_on_gpu():
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import kv_transfer_worker as w
+    ktc = {"kv_connector": "CPUOffloadingConnector", "kv_connector_extra_config": {"num_cpu_blocks": 32}}
+    llm = LLM(w._cfg(), device="cuda", seed=0, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=256,
+              num_gpu_blocks_override=40, enforce_eager=True, kv_transfer_config=ktc)
+    c = llm.engine.kv_connector
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    prompts = w._prompts()
+    first = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    c.reap(llm.engine.scheduler)
+    assert c.num_delayed == 0 and c.stats["saved_blocks"] == sum(len(p) // 128 for p in prompts)
+    free = llm.engine.scheduler.pool.num_free_blocks
+    for kc, vc in llm.engine.runner.kv_caches:
+        kc.zero_()
+        vc.zero_()
+    second = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    c.reap(llm.engine.scheduler)
+    assert second == first
+    assert c.stats["loaded_blocks"] == sum((len(p) - 1) // 128 for p in prompts) > 0
+    assert llm.engine.scheduler.pool.num_free_blocks == free
+    _native.check_status(torch.device("cuda"))

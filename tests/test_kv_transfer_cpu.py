@@ -149,3 +149,39 @@ def test_unknown_remote_request_is_a_failure_not_a_crash():
     finally:
         pre.engine.kv_connector.close()
         dec.engine.kv_connector.close()
+
+
+def test_cpu_offload_restores_prefix_after_gpu_cache_is_gone():
+    from vllm_ascend_b200.platform_config import clear_b200_config
+    ktc = {"kv_connector": "CPUOffloadingConnector", "kv_connector_extra_config": {"num_cpu_blocks": 64}}
+    llm = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4,
+              kv_transfer_config=ktc)
+    c = llm.engine.kv_connector
+    prompts = _prompts(3, lo=60, hi=90, seed=9)
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    first = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert c.stats["saved_blocks"] >= sum(len(p) // 16 for p in prompts)
+    # overwrite the device cache: whatever the second pass reuses must come from the host
+    for kc, vc in llm.engine.runner.kv_caches:
+        kc.normal_()
+        vc.normal_()
+    before = llm.engine.runner.stats.get("steps", 0)
+    second = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert second == first
+    assert c.stats["hit_tokens"] == sum((len(p) - 1) // 16 * 16 for p in prompts)
+    assert c.stats["loaded_blocks"] == c.stats["hit_tokens"] // 16
+    mono = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4)
+    assert [o.outputs[0].token_ids for o in mono.generate(prompts, sp)] == first
+
+
+def test_cpu_offload_lru_eviction_and_multi_connector():
+    ktc = {"kv_connector": "MultiConnector", "kv_connector_extra_config": {"connectors": [
+        {"kv_connector": "CPUOffloadingConnector", "kv_connector_extra_config": {"num_cpu_blocks": 4}}]}}
+    llm = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4,
+              kv_transfer_config=ktc)
+    c = llm.engine.kv_connector.connectors[0]
+    sp = SamplingParams(max_tokens=2, temperature=0.0, ignore_eos=True)
+    for seed in range(3):
+        llm.generate(_prompts(1, lo=64, hi=65, seed=20 + seed), sp)
+    assert len(c.lru) <= 4 and c.stats["evicted_blocks"] > 0
+    assert not c.free or len(c.lru) + len(c.free) == 4
