@@ -290,6 +290,8 @@ class EngineConfig:
     kv_transfer_config: Optional[dict] = None
     speculative_config: Optional[dict] = None
     enable_sleep_mode: bool = False
+    load_format: str = "auto"               # auto | netloader | rfork
+    model_loader_extra_config: Optional[dict] = None
     enable_lora: bool = False
     max_loras: int = 4
     max_lora_rank: int = 64

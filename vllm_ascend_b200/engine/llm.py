@@ -195,7 +195,8 @@ class LLM:
                  speculative_config: Optional[dict] = None, enable_sleep_mode: bool = False,
                  cudagraph_capture_sizes: Optional[list] = None,
                  decode_context_parallel_size: int = 1, enable_lora: bool = False, max_loras: int = 4,
-                 max_lora_rank: int = 64, **unused):
+                 max_lora_rank: int = 64, load_format: str = "auto",
+                 model_loader_extra_config: Optional[dict] = None, **unused):
         mcfg = model if isinstance(model, ModelConfig) else get_model_config(model)
         if dtype:
             mcfg.dtype = dtype
@@ -228,7 +229,8 @@ class LLM:
             additional_config=additional_config or {}, device=device, device_index=device_index, seed=seed,
             kv_transfer_config=kv_transfer_config, speculative_config=speculative_config,
             enable_sleep_mode=enable_sleep_mode, enable_lora=enable_lora, max_loras=max_loras,
-            max_lora_rank=max_lora_rank)
+            max_lora_rank=max_lora_rank, load_format=load_format,
+            model_loader_extra_config=model_loader_extra_config)
         if device == "cuda":
             cfg.scheduler.decode_batch_alignment = 256
         from ..platform_config import check_and_update_config
@@ -309,6 +311,14 @@ class LLM:
             if eng.device.type == "cuda":
                 torch.cuda.synchronize()
             dist.destroy_process_group()
+
+    def serve_weights(self, host: str = "127.0.0.1", port: int = 0):
+        """Let starting instances pull this instance's weights (netloader / rfork seed)."""
+        from ..model_loader.netloader import WeightSource
+        tp = pstate.get_tp_group()
+        self._weight_source = WeightSource(self.engine.runner.model, host, port, tp.rank_in_group, tp.world_size,
+                                           self.cfg.model.name)
+        return self._weight_source
 
     def reset_prefix_cache(self) -> bool:
         return self.engine.scheduler.pool.reset_prefix_cache()

@@ -104,7 +104,13 @@ class ModelRunner:
         from ..models import build_model
         t0 = time.time()
         self.model = build_model(self.cfg, self.device, moe_runtime=moe_runtime)
-        if self.mcfg.model_path:
+        from ..model_loader import get_model_loader
+        from ..parallel import state as pstate
+        tp = pstate.get_tp_group()
+        loader = get_model_loader(self.cfg.load_format, self.cfg.model_loader_extra_config, tp.rank_in_group,
+                                  tp.world_size, self.mcfg.name)
+        self.loaded_from_peer = bool(loader is not None and loader.load(self.model))
+        if self.mcfg.model_path and not self.loaded_from_peer:
             from ..models.transformer import iterate_safetensors
             self.model.load_weights(iterate_safetensors(self.mcfg.model_path))
         self.load_time = time.time() - t0
