@@ -18,9 +18,9 @@ WORKER = textwrap.dedent("""
     from vllm_ascend_b200.config import get_model_config
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
-    preset, tp, ep = sys.argv[1], int(sys.argv[2]), sys.argv[3] == "1"
+    preset, tp, ep, pp = sys.argv[1], int(sys.argv[2]), sys.argv[3] == "1", int(sys.argv[4])
     cfg = get_model_config(preset)
-    llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, enable_expert_parallel=ep,
+    llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, enable_expert_parallel=ep, pipeline_parallel_size=pp,
               max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     rng = np.random.default_rng(2)
     prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(3)]
@@ -36,14 +36,14 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(preset, world, tp, ep=False):
+def _run(preset, world, tp, ep=False, pp=1):
     script = WORKER.format(root=ROOT)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()),
                WORLD_SIZE=str(world), OMP_NUM_THREADS="2")
     procs = []
     for r in range(world):
         e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
-        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0"],
+        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0", str(pp)],
                                       env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=300) for p in procs]
     for p, (o, e) in zip(procs, outs):
@@ -60,3 +60,8 @@ def test_tp2_matches_tp1(preset):
 def test_expert_parallel_matches_single_rank():
     # EP over 2 ranks (DP attention: tp=1, experts sharded over the 2 ranks)
     assert _run("tiny-moe", 2, 1, ep=True) == _run("tiny-moe", 1, 1)
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen", "tiny-moe"])
+def test_pipeline_parallel_matches_single_rank(preset):
+    assert _run(preset, 2, 1, pp=2) == _run(preset, 1, 1)

@@ -86,6 +86,8 @@ class ModelRunner:
         self.graphs: dict[tuple, object] = {}     # (capture size, has_lora) -> BatchDescriptor
         self.graph_wrapper = None
         self.lora_manager = None
+        from ..parallel import state as _ps
+        self.pp = _ps.get_pp_group()
         self.proposer = None
         self.last_hidden = None      # final hidden states of the latest step, scheduling order
         self.rejection_sampler = None
@@ -341,7 +343,27 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ execution
     def _forward(self, T: int, meta: AttentionMetadata) -> torch.Tensor:
-        return self.model.forward(self.input_ids[:T], meta, self.kv_caches)
+        pp = self.pp
+        if pp.world_size == 1:
+            return self.model.forward(self.input_ids[:T], meta, self.kv_caches)
+        # Pipeline stage: activations (hidden, residual) arrive from the previous stage and
+        # leave for the next one; only the last stage returns final hidden states
+        # (vllm_ascend/worker/worker.py:634-673 does the same with irecv/isend of a tensor dict).
+        inter = None
+        H, dt = self.mcfg.hidden_size, self.model.dtype
+        if not self.model.is_first:
+            h = torch.empty((T, H), dtype=dt, device=self.device)
+            res = torch.empty((T, H), dtype=dt, device=self.device)
+            pp.recv(h, pp.rank_in_group - 1)
+            pp.recv(res, pp.rank_in_group - 1)
+            inter = (h, res)
+        out = self.model.forward(self.input_ids[:T], meta, self.kv_caches, inter)
+        if self.model.is_last:
+            return out
+        h, res = out
+        pp.send(h.contiguous(), pp.rank_in_group + 1)
+        pp.send((res if res is not None else h).contiguous(), pp.rank_in_group + 1)
+        return h
 
     def _graph_size_for(self, B: int) -> Optional[int]:
         if not self.capture_sizes or B > self.capture_sizes[-1]:
@@ -359,6 +381,8 @@ class ModelRunner:
         t_start = time.perf_counter()
         self.stats["steps"] += 1
         self._sync_rows(so)
+        if self.pp.world_size > 1:
+            return self._execute_pipeline(so)
         B = len(so.scheduled)
         decode_only = all(n == 1 for _, n in so.scheduled)
         gsize = self._graph_size_for(B) if decode_only else None
@@ -414,6 +438,28 @@ class ModelRunner:
             row = r.row
             self.token_ids_cpu[row, r.num_tokens] = t
             out[r.request_id] = [t]
+        return out
+
+    def _execute_pipeline(self, so: SchedulerOutput) -> dict:
+        """One step of a pipeline-parallel engine: every stage runs its layers, the last stage
+        samples and the sampled tokens go back to all stages, whose schedulers advance together."""
+        meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so)
+        hidden = self._forward(Tp, meta)
+        self.stats["eager_steps"] += 1
+        pp = self.pp
+        toks = None
+        if self.model.is_last and sel:
+            h_sel = hidden[:T] if len(sel) == T else hidden[torch.tensor(sel, dtype=torch.int64, device=self.device)]
+            logits = self.model.compute_logits(h_sel)
+            md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
+            if not md.all_greedy and not self.is_cuda:
+                md.generator = self._cpu_generator()
+            toks = self.sampler(logits, md).cpu().tolist()
+        toks = pp.broadcast_object(toks, src=pp.world_size - 1)
+        out = {}
+        for r, t in zip(sample_reqs, toks or []):
+            self.token_ids_cpu[r.row, r.num_tokens] = int(t)
+            out[r.request_id] = [int(t)]
         return out
 
     def _sample_speculative(self, logits: torch.Tensor, sample_reqs: list, rows: list) -> dict:

@@ -300,7 +300,7 @@ def check_and_update_config(engine_cfg) -> B200Config:
     cc.cudagraph_mode = cc.cudagraph_mode.upper()
     if cc.cudagraph_mode not in GRAPH_MODES:
         raise ValueError(f"cudagraph_mode must be one of {GRAPH_MODES}")
-    if engine_cfg.device != "cuda":
+    if engine_cfg.device != "cuda" or pc.pipeline_parallel_size > 1:
         cc.cudagraph_mode = "NONE"
     if cc.max_cudagraph_capture_size is None:
         cc.max_cudagraph_capture_size = min(sc.max_num_seqs, 1024)
