@@ -11,7 +11,57 @@ from __future__ import annotations
 
 import torch
 
+from ctypes import c_float, c_int, c_long, c_void_p
+
+from .. import _native
 from ..ops import reference as ref
+
+_P, _I, _L, _F = c_void_p, c_int, c_long, c_float
+_native.register_signature("b200_mla_decode", [_P, _L, _L, _I, _P, _P, _L, _I, _P, _P, _P, _I, _F, _I, _P, _L, _P,
+                                               _P, _P])
+_scratch: dict = {}
+
+
+def mla_decode_native(q_cat: torch.Tensor, lat_cache: torch.Tensor, pe_cache: torch.Tensor,
+                      row_seq: torch.Tensor, row_kv_len: torch.Tensor, block_table: torch.Tensor,
+                      scale: float, num_splits: int = 0, max_kv_len: int = 0) -> torch.Tensor:
+    """tcgen05 MLA attention over query rows.  q_cat [R, H, 576] = absorbed q_nope ‖ q_pe;
+    every row r attends to the first ``row_kv_len[r]`` tokens of sequence ``row_seq[r]``.
+    Returns o_lat [R, H, 512]."""
+    R, H, dk = q_cat.shape
+    assert dk == 576 and q_cat.dtype == torch.bfloat16 and q_cat.stride(2) == 1 and q_cat.stride(1) == dk
+    dev = q_cat.device
+    out = torch.empty((R, H, 512), dtype=torch.bfloat16, device=dev)
+    if num_splits <= 0:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        nq = 32 if H % 32 == 0 else 16
+        ctas = max(1, R * (H // nq))
+        tiles = max(1, (max_kv_len + 127) // 128) if max_kv_len else 8
+        num_splits = max(1, min(tiles, (2 * sms + ctas - 1) // ctas, 32))
+    scratch = None
+    if num_splits > 1:
+        need = R * H * num_splits * 513
+        key = dev.index
+        scratch = _scratch.get(key)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=dev)
+            _scratch[key] = scratch
+    rc = _native.lib().b200_mla_decode(
+        q_cat.data_ptr(), q_cat.stride(0), R, H, lat_cache.data_ptr(), pe_cache.data_ptr(), lat_cache.shape[0],
+        lat_cache.shape[1], row_seq.data_ptr(), row_kv_len.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), scale, num_splits, out.data_ptr(), out.stride(0), _native.ptr(scratch),
+        _native.status_word(dev).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "mla_decode")
+    _native.count_launch(2 if num_splits > 1 else 1)
+    return out
+
+
+def reserve_mla_scratch(device, rows: int, heads: int, max_splits: int = 32) -> None:
+    """Allocate the split-KV scratch up front (before graph capture)."""
+    need = rows * heads * max_splits * 513
+    cur = _scratch.get(device.index)
+    if cur is None or cur.numel() < need:
+        _scratch[device.index] = torch.empty(need, dtype=torch.float32, device=device)
 
 
 def write_latent_cache(latent: torch.Tensor, k_pe: torch.Tensor, lat_cache: torch.Tensor,
@@ -26,6 +76,23 @@ def mla_paged_attention(q_lat: torch.Tensor, q_pe: torch.Tensor, lat_cache: torc
                         pe_cache: torch.Tensor, meta, scale: float) -> torch.Tensor:
     """q_lat [T,H,dc], q_pe [T,H,dr] -> o_lat [T,H,dc] (softmax over latent‖rope keys)."""
     T, H, dc = q_lat.shape
+    from .. import envs
+    if envs.VLLM_B200_MLA_ATTN == "tcgen05" and q_lat.is_cuda and q_lat.dtype == torch.bfloat16 and dc == 512 and q_pe.shape[-1] == 64 and H % 16 == 0 \
+            and lat_cache.shape[1] in (16, 32, 64, 128, 256, 512) and T <= 65535:
+        q_cat = torch.cat([q_lat, q_pe], dim=-1)
+        B = meta.num_reqs
+        if meta.max_query_len == 1 and T == B:
+            row_seq = torch.arange(T, dtype=torch.int32, device=q_lat.device)
+        else:
+            q_lens = (meta.query_start_loc[1:B + 1] - meta.query_start_loc[:B]).long()
+            row_seq = torch.repeat_interleave(torch.arange(B, device=q_lat.device), q_lens,
+                                              output_size=T).to(torch.int32)
+        row_kv = (meta.positions[:T] + 1).to(torch.int32)
+        # a captured graph must carry a split count that suits any later sequence length
+        max_kv = meta.block_table.shape[1] * lat_cache.shape[1] if torch.cuda.is_current_stream_capturing() \
+            else meta.max_seq_len
+        return mla_decode_native(q_cat, lat_cache, pe_cache, row_seq, row_kv, meta.block_table, scale,
+                                 max_kv_len=max_kv)
     out = torch.empty(T, H, dc, dtype=q_lat.dtype, device=q_lat.device)
     qsl, sls = meta.query_start_loc_cpu, meta.seq_lens_cpu
     for b in range(meta.num_reqs):

@@ -36,6 +36,8 @@ env_variables: dict[str, Callable[[], Any]] = {
     # prefill attention: "tcgen05" or "sdpa" (torch fallback/oracle)
     "VLLM_B200_PREFILL_ATTN": _str("VLLM_B200_PREFILL_ATTN", "tcgen05"),
     "VLLM_B200_DECODE_ATTN": _str("VLLM_B200_DECODE_ATTN", "native"),
+    # MLA attention: "tcgen05" (absorbed-weight kernel) or "torch" (oracle)
+    "VLLM_B200_MLA_ATTN": _str("VLLM_B200_MLA_ATTN", "tcgen05"),
     # fused TP collectives over peer memory: "fused" or "nccl"
     "VLLM_B200_TP_COMM": _str("VLLM_B200_TP_COMM", "fused"),
     # MoE path override: "", "allgather", "alltoall", "fused"
