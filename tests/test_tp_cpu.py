@@ -18,9 +18,10 @@ WORKER = textwrap.dedent("""
     from vllm_ascend_b200.config import get_model_config
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
-    preset, tp, ep, pp = sys.argv[1], int(sys.argv[2]), sys.argv[3] == "1", int(sys.argv[4])
+    preset, tp, ep, pp, dcp = sys.argv[1], int(sys.argv[2]), sys.argv[3] == "1", int(sys.argv[4]), int(sys.argv[5])
     cfg = get_model_config(preset)
-    llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, enable_expert_parallel=ep, pipeline_parallel_size=pp,
+    llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, enable_expert_parallel=ep, pipeline_parallel_size=pp, decode_context_parallel_size=dcp,
+              additional_config=dict(cp_kv_cache_interleave_size=4) if dcp > 1 else None,
               max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     rng = np.random.default_rng(2)
     prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(3)]
@@ -36,14 +37,14 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(preset, world, tp, ep=False, pp=1):
+def _run(preset, world, tp, ep=False, pp=1, dcp=1):
     script = WORKER.format(root=ROOT)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()),
                WORLD_SIZE=str(world), OMP_NUM_THREADS="2")
     procs = []
     for r in range(world):
         e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
-        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0", str(pp)],
+        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0", str(pp), str(dcp)],
                                       env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=300) for p in procs]
     for p, (o, e) in zip(procs, outs):
@@ -65,3 +66,8 @@ def test_expert_parallel_matches_single_rank():
 @pytest.mark.parametrize("preset", ["tiny-qwen", "tiny-moe"])
 def test_pipeline_parallel_matches_single_rank(preset):
     assert _run(preset, 2, 1, pp=2) == _run(preset, 1, 1)
+
+
+def test_decode_context_parallel_matches_single_rank():
+    # MLA latent cache sharded along the sequence over the 2 TP ranks
+    assert _run("tiny-deepseek", 2, 2, dcp=2) == _run("tiny-deepseek", 1, 1)

@@ -23,4 +23,12 @@ def make_scheduler(engine_cfg, num_blocks: int, kv_connector=None):
         raise ValueError(f"unknown scheduler policy {policy!r}")
     if cls is not Scheduler:
         kw["engine_cfg"] = engine_cfg
-    return cls(engine_cfg.scheduler, engine_cfg.cache, num_blocks, kv_connector, **kw)
+    cache_cfg = engine_cfg.cache
+    dcp = engine_cfg.parallel.decode_context_parallel_size
+    if dcp > 1:
+        # the KV of a sequence is spread over the DCP ranks: one block id covers
+        # block_size * dcp tokens, block_size of them on each rank
+        import copy
+        cache_cfg = copy.copy(cache_cfg)
+        cache_cfg.block_size = cache_cfg.block_size * dcp
+    return cls(engine_cfg.scheduler, cache_cfg, num_blocks, kv_connector, **kw)

@@ -88,6 +88,11 @@ class ModelRunner:
         self.lora_manager = None
         from ..parallel import state as _ps
         self.pp = _ps.get_pp_group()
+        dcp = _ps.get_dcp_group()
+        self.dcp_size, self.dcp_rank = dcp.world_size, dcp.rank_in_group
+        self.dcp_interleave = int((cfg.additional_config or {}).get("cp_kv_cache_interleave_size", 1))
+        if self.dcp_size > 1 and not cfg.model.use_mla:
+            raise NotImplementedError("decode context parallelism is implemented for MLA models")
         self.proposer = None
         self.last_hidden = None      # final hidden states of the latest step, scheduling order
         self.rejection_sampler = None
@@ -232,8 +237,16 @@ class ModelRunner:
             if sp_:
                 self.token_ids_cpu[r.row, r.num_tokens:r.num_tokens + len(sp_)] = sp_
         ids = self.token_ids_cpu[tok_rows, pos]
-        blk = self.block_table_cpu[tok_rows, pos // self.block_size].astype(np.int64)
-        slots = blk * self.block_size + pos % self.block_size
+        if self.dcp_size > 1:
+            # sequence-sharded cache: a virtual block of block_size * dcp tokens keeps
+            # block_size of them on this rank
+            from ..attention.dcp import local_slot_mapping
+            blk = self.block_table_cpu[tok_rows, pos // (self.block_size * self.dcp_size)]
+            slots = local_slot_mapping(pos, blk, self.block_size, self.dcp_size, self.dcp_rank,
+                                       self.dcp_interleave)
+        else:
+            blk = self.block_table_cpu[tok_rows, pos // self.block_size].astype(np.int64)
+            slots = blk * self.block_size + pos % self.block_size
         seq_lens = starts + q_lens
         Bp = pad_to or B
         Tp = T + (Bp - B)                       # padded rows carry one dummy token each
@@ -280,6 +293,7 @@ class ModelRunner:
             positions=self.positions[:Tp], query_start_loc_cpu=qsl_cpu, seq_lens_cpu=sl_cpu,
             attn_state=state, num_decodes=nd, num_decode_tokens=ndt, num_prefills=npf,
             num_input_tokens=Tp)
+        meta.dcp_interleave = self.dcp_interleave
         if self.is_cuda and not self.mcfg.use_mla:
             a = self.model.layers[0].self_attn
             G = a.Hq // a.Hkv

@@ -181,7 +181,13 @@ class MLAAttention:
                                    meta.slot_mapping)
         # absorb W_UK into q: [T,H,dn] x [H,dn,dc] -> [T,H,dc]
         q_lat = torch.einsum("thd,hdc->thc", q[..., :self.dn], self.W_UK.to(q.dtype))
-        o_lat = mla_ops.mla_paged_attention(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale)
+        dcp = pstate.get_dcp_group()
+        if dcp.world_size > 1:
+            from ..attention.dcp import mla_attention_dcp
+            o_lat = mla_attention_dcp(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale, dcp,
+                                      getattr(meta, "dcp_interleave", 1))
+        else:
+            o_lat = mla_ops.mla_paged_attention(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale)
         o = torch.einsum("thc,hcv->thv", o_lat, self.W_UV.to(o_lat.dtype))
         return self.o_proj(o.reshape(T, self.H * self.dv))
 

@@ -153,6 +153,7 @@ class B200Config:
     enable_transpose_kv_cache_by_block: bool = True
     enable_cpu_binding: bool = True
     kv_load_failure_policy: str = "recompute"    # recompute | fail
+    cp_kv_cache_interleave_size: int = 1         # tokens per run when the KV of a sequence is spread over DCP ranks
     dump_config: bool = False
     dump_config_path: Optional[str] = None
     log_path: Optional[str] = None
