@@ -105,6 +105,31 @@ def bench_attn_decode(a):
     _native.check_status(torch.device("cuda"))
 
 
+def bench_mla_decode(a):
+    """Absorbed-weight MLA decode: B sequences of ctx tokens, H heads, one query token each."""
+    from vllm_ascend_b200.attention.mla import mla_decode_native
+    dev = torch.device("cuda")
+    B, ctx, H, bs = a.batch, a.ctx, a.heads, a.block_size
+    nblk = (ctx + bs - 1) // bs
+    total = B * nblk + 1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    lat = (torch.randn(total, bs, 512, device=dev, generator=g) * 0.5).bfloat16()
+    pe = (torch.randn(total, bs, 64, device=dev, generator=g) * 0.5).bfloat16()
+    bt = (torch.randperm(total - 1, device=dev, generator=g) + 1).int().view(B, nblk)
+    q = (torch.randn(B, H, 576, device=dev, generator=g) * 0.3).bfloat16()
+    row_seq = torch.arange(B, dtype=torch.int32, device=dev)
+    row_kv = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+    scale = 576 ** -0.5
+    hbm, tf, tag = peaks()
+    ms = timeit(lambda: mla_decode_native(q, lat, pe, row_seq, row_kv, bt, scale, a.splits, ctx), a.iters)
+    kv_bytes = B * ctx * 576 * 2.0
+    flops = 2.0 * B * ctx * H * (576 + 512)
+    print(f"mla-decode B={B} ctx={ctx} H={H}: {ms:.4f} ms  KV {kv_bytes / ms / 1e6:.0f} GB/s "
+          f"({kv_bytes / ms / 1e6 / hbm:.2f} {tag})  {flops / ms / 1e9:.0f} TFLOP/s ({flops / ms / 1e9 / tf:.2f} {tag})",
+          flush=True)
+    _native.check_status(dev)
+
+
 def bench_attn_prefill(a):
     from gpu_utils import make_paged_case
     B, S = a.batch, a.seq
@@ -141,7 +166,7 @@ def bench_norm(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "norm", "all"])
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "mla-decode", "norm", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -153,6 +178,7 @@ def main():
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--heads", type=int, default=128)
     ap.add_argument("--block-size", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--impl", default="both")
@@ -189,6 +215,8 @@ def main():
         else:
             a.ctx = 0 if a.ctx == 1152 else a.ctx
             bench_attn_prefill(a)
+    if a.what == "mla-decode":
+        bench_mla_decode(a)
     if a.what in ("norm", "all"):
         bench_norm(a)
 

@@ -81,7 +81,7 @@ def test_mla_model_on_engine_matches_torch_path(monkeypatch):
     outs = {}
     for mode in ("torch", "tcgen05"):
         monkeypatch.setenv("VLLM_B200_MLA_ATTN", mode)
-        llm = LLM(cfg(), **kw)
+        llm = LLM(cfg(), enforce_eager=(mode == "torch"), **kw)
         c0 = llm.engine.runner.total_launches()
         outs[mode] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
         if mode == "tcgen05":

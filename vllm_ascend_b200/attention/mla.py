@@ -66,10 +66,15 @@ def reserve_mla_scratch(device, rows: int, heads: int, max_splits: int = 32) -> 
 
 def write_latent_cache(latent: torch.Tensor, k_pe: torch.Tensor, lat_cache: torch.Tensor,
                        pe_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
-    valid = slot_mapping >= 0
-    slots = slot_mapping[valid]
-    lat_cache.view(-1, lat_cache.shape[-1])[slots] = latent[valid].to(lat_cache.dtype)
-    pe_cache.view(-1, pe_cache.shape[-1])[slots] = k_pe[valid].to(pe_cache.dtype)
+    """Scatter the step's latents / rope keys into their cache slots; slot -1 = not stored.
+    Written without data-dependent shapes so it can be captured into a CUDA graph: skipped
+    tokens rewrite slot 0 with the value it already holds."""
+    valid = (slot_mapping >= 0).unsqueeze(-1)
+    idx = slot_mapping.clamp(min=0)
+    lat_flat = lat_cache.view(-1, lat_cache.shape[-1])
+    pe_flat = pe_cache.view(-1, pe_cache.shape[-1])
+    lat_flat.index_copy_(0, idx, torch.where(valid, latent.to(lat_cache.dtype), lat_flat[idx]))
+    pe_flat.index_copy_(0, idx, torch.where(valid, k_pe.to(pe_cache.dtype), pe_flat[idx]))
 
 
 def mla_paged_attention(q_lat: torch.Tensor, q_pe: torch.Tensor, lat_cache: torch.Tensor,
