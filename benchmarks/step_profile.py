@@ -2,6 +2,7 @@
 
     python benchmarks/step_profile.py --model qwen3-8b --num-prompts 1024 --skip-steps 40 \
         --mixed-steps 3 --decode-steps 3 --out gpurun_out/step_profile.txt
+    (under torchrun with N ranks it profiles rank 0 of a TP=N engine)
 
 Fills the engine with the benchmark workload, lets it reach steady state, then profiles a few
 mixed (prefill chunk + decodes) steps and, once prefill is over, a few decode-only steps.
@@ -34,8 +35,10 @@ def main():
     args = ap.parse_args()
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
-    llm = LLM(args.model, max_model_len=args.input_len + args.output_len + 16, max_num_seqs=args.max_num_seqs,
-              max_num_batched_tokens=args.max_num_batched_tokens, device="cuda")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    llm = LLM(args.model, tensor_parallel_size=world, max_model_len=args.input_len + args.output_len + 16,
+              max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens, device="cuda")
     eng = llm.engine
     rng = np.random.default_rng(0)
     sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
@@ -79,10 +82,17 @@ def main():
     profile("mixed (prefill chunk + decodes)", args.mixed_steps, want_decode=False)
     profile("decode only", args.decode_steps, want_decode=True)
     text = "\n".join(lines)
+    if rank != 0:
+        llm.shutdown()
+        os._exit(0)
     print(text)
     os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
     with open(args.out, "w") as f:
         f.write(text + "\n")
+    if world > 1:
+        sys.stdout.flush()
+        llm.shutdown()
+        os._exit(0)
 
 
 if __name__ == "__main__":

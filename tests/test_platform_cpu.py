@@ -169,3 +169,40 @@ def test_service_profiling_config_and_spans(tmp_path, monkeypatch):
         assert m["steps"] >= 3 and m["kv_blocks_free"] == m["kv_blocks_total"] or m["kv_usage"] >= 0
     finally:
         sp.uninstall_spans()
+
+
+def test_batch_invariant_mode_pins_split_factor(monkeypatch):
+    from vllm_ascend_b200 import batch_invariant as bi, ops
+    monkeypatch.delenv("VLLM_B200_BATCH_INVARIANT", raising=False)
+    bi.disable_batch_invariant_mode()
+    assert ops.choose_num_splits(4, 8, 8192) > 1
+    bi.enable_batch_invariant_mode()
+    try:
+        assert ops.choose_num_splits(4, 8, 8192) == 1 and bi.is_batch_invariant()
+        assert os.environ["NCCL_ALGO"] == "Ring"
+    finally:
+        bi.disable_batch_invariant_mode()
+    assert ops.choose_num_splits(4, 8, 8192) > 1
+
+
+def test_utils_predicates_and_op_table():
+    import importlib
+    from types import SimpleNamespace as NS
+    from vllm_ascend_b200 import utils
+    cfg = NS(parallel=NS(enable_sequence_parallel=True, tensor_parallel_size=2, data_parallel_size=2,
+                         enable_expert_parallel=True),
+             model=NS(is_moe=True), additional_config={"finegrained_tp_config": {"lmhead_tensor_parallel_size": 2}})
+    assert utils.enable_sp(cfg) and utils.is_moe_model(cfg) and utils.lmhead_tp_enable(cfg)
+    assert not utils.oproj_tp_enable(cfg)
+    assert not utils.should_skip_allreduce_across_dp_group(cfg, True)
+    cfg.model.is_moe = False
+    assert utils.should_skip_allreduce_across_dp_group(cfg, True)
+    for name, path in utils.OOT_OPS.items():
+        m, c = path.rsplit(".", 1)
+        assert hasattr(importlib.import_module(m), c), name
+    from vllm_ascend_b200.ops.host_ops import RMSNorm, SiluAndMul
+    x = torch.randn(3, 8)
+    assert torch.allclose(SiluAndMul()(x), torch.nn.functional.silu(x[:, :4]) * x[:, 4:], atol=1e-6)
+    n = RMSNorm(8, dtype=torch.float32)
+    y = n(x)
+    assert torch.allclose(y, x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6), atol=1e-5)

@@ -306,7 +306,11 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 
 def choose_num_splits(num_seqs: int, Hkv: int, max_seq_len: int, sm_count: int = 148,
                       tile: int = 128) -> int:
-    """Split-KV factor: enough CTAs to fill the GPU, never more splits than KV tiles."""
+    """Split-KV factor: enough CTAs to fill the GPU, never more splits than KV tiles.  In
+    batch-invariant mode the factor is 1: the merge order must not depend on the batch."""
+    from ..batch_invariant import is_batch_invariant
+    if is_batch_invariant():
+        return 1
     ctas = max(1, num_seqs * Hkv)
     if ctas >= 2 * sm_count:
         return 1

@@ -294,6 +294,8 @@ def check_and_update_config(engine_cfg) -> B200Config:
         engine_cfg.enable_sleep_mode = True
         if cfg.rl_config.enable_batch_invariant:
             cc.cudagraph_mode = "NONE"
+            from .batch_invariant import enable_batch_invariant_mode
+            enable_batch_invariant_mode()
     _validate_finegrained(cfg, pc.tensor_parallel_size, max(1, pc.data_parallel_size))
     _validate_eplb(cfg.eplb_config, mc.is_moe, pc.enable_expert_parallel)
     _validate_scheduler_ext(cfg.scheduler_config, engine_cfg)
