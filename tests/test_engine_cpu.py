@@ -168,3 +168,33 @@ def test_random_sampling_is_seeded_and_respects_top_k():
     a = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
     g = [o.outputs[0].token_ids for o in llm.generate(p, greedy)]
     assert a == g          # top_k=1 is greedy whatever the noise
+
+
+@pytest.mark.parametrize("prefix_caching", [False, True])
+def test_async_scheduling_matches_synchronous_engine(prefix_caching):
+    """One-step lookahead: scheduling and input preparation of step N+1 happen before step N's
+    tokens are read; generated tokens, stop handling and block accounting must not change."""
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=96, max_num_seqs=4, max_num_batched_tokens=32,
+              enable_prefix_caching=prefix_caching)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(1, 500, size=n).tolist() for n in (40, 5, 23, 61, 9, 33)]
+    sps = [SamplingParams(max_tokens=m, temperature=0.0, ignore_eos=True) for m in (7, 1, 12, 3, 20, 2)]
+    sync = LLM("tiny-qwen", async_scheduling=False, **kw)
+    want = [o.outputs[0].token_ids for o in sync.generate(prompts, sps)]
+    llm = LLM("tiny-qwen", async_scheduling=True, **kw)
+    assert llm.engine.async_scheduling
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sps)]
+    assert got == want
+    assert [len(g) for g in got] == [7, 1, 12, 3, 20, 2]
+    pool = llm.engine.scheduler.pool
+    assert pool.num_free_blocks == sync.engine.scheduler.pool.num_free_blocks
+    assert not llm.engine.scheduler.running and llm.engine._inflight is None
+    # stop tokens are honoured although the following step was already launched
+    stop = want[2][4]
+    sp = SamplingParams(max_tokens=12, temperature=0.0, stop_token_ids=[stop])
+    a = llm.generate([prompts[2]], sp)[0].outputs[0].token_ids
+    b = sync.generate([prompts[2]], sp)[0].outputs[0].token_ids
+    assert a == b and a[-1] == stop
+    # random sampling with a seed runs through the same path
+    sp = SamplingParams(max_tokens=6, temperature=0.9, top_k=50, seed=11, ignore_eos=True)
+    assert len(llm.generate(prompts[:2], sp)[1].outputs[0].token_ids) == 6

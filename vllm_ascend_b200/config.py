@@ -292,6 +292,7 @@ class EngineConfig:
     enable_sleep_mode: bool = False
     load_format: str = "auto"               # auto | netloader | rfork
     model_loader_extra_config: Optional[dict] = None
+    async_scheduling: Optional[bool] = None     # None: on for single-process CUDA engines
     enable_lora: bool = False
     max_loras: int = 4
     max_lora_rank: int = 64

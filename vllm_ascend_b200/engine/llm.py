@@ -65,6 +65,12 @@ class LLMEngine:
             self.runner.proposer = get_spec_decode_method(cfg.speculative_config, self.runner)
             self.scheduler.spec_slack = int(cfg.speculative_config.get("num_speculative_tokens", 3))
         self._model_proposer = hasattr(self.runner.proposer, "propose_step")
+        # asynchronous scheduling needs nothing between two steps that depends on the sampled
+        # token values: no proposer, no connector bookkeeping, no lock-step groups
+        self._inflight = None
+        want_async = cfg.async_scheduling if cfg.async_scheduling is not None else (cfg.device == "cuda")
+        self.async_scheduling = bool(want_async and self.runner.proposer is None and self.kv_connector is None
+                                     and self.eplb is None and world == 1)
         self.runner.capture_graphs()
         self._req_counter = itertools.count()
         self.eos_token_id: Optional[int] = None
@@ -99,9 +105,40 @@ class LLMEngine:
                                               if r.status == RequestStatus.RUNNING and r.request_id in sampled])
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
+
+    def _step_async(self) -> list[Request]:
+        """One iteration with asynchronous scheduling: plan and enqueue step N+1 while step N
+        runs on the GPU, then read step N's tokens.  The host work of a step (scheduling, input
+        preparation, launches) overlaps the previous step's kernels."""
+        t0 = time.perf_counter()
+        prev = self._inflight
+        so = self.scheduler.schedule()
+        t1 = time.perf_counter()
+        handle = None
+        if not so.is_empty:
+            handle = self.runner.execute_async(so, prev[1] if prev else None)
+            self.scheduler.advance(so)
+        t2 = time.perf_counter()
+        finished: list[Request] = []
+        if prev is not None:
+            so_prev, h_prev = prev
+            sampled = self.runner.collect(h_prev)
+            now = time.monotonic()
+            for req, _ in so_prev.scheduled:
+                if req.first_token_time is None and req.request_id in sampled:
+                    req.first_token_time = now
+            finished = self.scheduler.update_from_output(so_prev, sampled)
+        self._inflight = (so, handle) if handle is not None else None
+        t3 = time.perf_counter()
+        self.host_times["schedule"] += t1 - t0
+        self.host_times["execute"] += t2 - t1
+        self.host_times["update"] += t3 - t2
+        return finished
 
     def step(self) -> list[Request]:
+        if self.async_scheduling:
+            return self._step_async()
         t0 = time.perf_counter()
         so = self.scheduler.schedule()
         t1 = time.perf_counter()
@@ -195,7 +232,7 @@ class LLM:
                  speculative_config: Optional[dict] = None, enable_sleep_mode: bool = False,
                  cudagraph_capture_sizes: Optional[list] = None,
                  decode_context_parallel_size: int = 1, enable_lora: bool = False, max_loras: int = 4,
-                 max_lora_rank: int = 64, load_format: str = "auto",
+                 max_lora_rank: int = 64, async_scheduling: Optional[bool] = None, load_format: str = "auto",
                  model_loader_extra_config: Optional[dict] = None, **unused):
         mcfg = model if isinstance(model, ModelConfig) else get_model_config(model)
         if dtype:
@@ -229,7 +266,7 @@ class LLM:
             additional_config=additional_config or {}, device=device, device_index=device_index, seed=seed,
             kv_transfer_config=kv_transfer_config, speculative_config=speculative_config,
             enable_sleep_mode=enable_sleep_mode, enable_lora=enable_lora, max_loras=max_loras,
-            max_lora_rank=max_lora_rank, load_format=load_format,
+            max_lora_rank=max_lora_rank, async_scheduling=async_scheduling, load_format=load_format,
             model_loader_extra_config=model_loader_extra_config)
         if device == "cuda":
             cfg.scheduler.decode_batch_alignment = 256

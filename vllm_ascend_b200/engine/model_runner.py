@@ -38,6 +38,15 @@ def default_capture_sizes(max_size: int) -> list[int]:
     return [x for x in sizes if x <= max_size]
 
 
+class _StepHandle:
+    """A step that was enqueued but whose sampled tokens have not been read yet."""
+    __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index")
+
+    def __init__(self, tokens, reqs, host, event, kind, t_start):
+        self.tokens, self.reqs, self.host, self.event, self.kind, self.t_start = tokens, reqs, host, event, kind, t_start
+        self.index = {r.request_id: i for i, r in enumerate(reqs)}
+
+
 class ModelRunner:
     def __init__(self, cfg: EngineConfig, device: torch.device):
         self.cfg = cfg
@@ -82,6 +91,8 @@ class ModelRunner:
         self._h_bt = torch.zeros((B, self.max_blocks_per_seq), dtype=i32, pin_memory=pin)
         self._h_tile = torch.zeros((2, max_tiles), dtype=i32, pin_memory=pin)
         self._h_sampled = torch.zeros(B, dtype=i64, pin_memory=pin)
+        self._h_sampled2 = [torch.zeros(B, dtype=i64, pin_memory=pin) for _ in range(2)]   # async steps
+        self._async_flip = 0
         # ---- CUDA graphs
         self.graphs: dict[tuple, object] = {}     # (capture size, has_lora) -> BatchDescriptor
         self.graph_wrapper = None
@@ -321,8 +332,9 @@ class ModelRunner:
         rows_per_req = []
         for i, r in enumerate(reqs):
             end = int(starts[i] + q_lens[i])
-            if end >= r.num_tokens:
-                nrow = end - r.num_tokens + 1          # 1 + draft tokens verified in this step
+            ntok = r.num_tokens + getattr(r, "num_inflight", 0)   # incl. a token still being sampled
+            if end >= ntok:
+                nrow = end - ntok + 1                  # 1 + draft tokens verified in this step
                 base = int(cu[i + 1]) - nrow
                 sel.extend(range(base, base + nrow))
                 sample_reqs.append(r)
@@ -452,6 +464,92 @@ class ModelRunner:
             row = r.row
             self.token_ids_cpu[row, r.num_tokens] = t
             out[r.request_id] = [t]
+        return out
+
+    # ------------------------------------------------------------------ asynchronous stepping
+    @torch.inference_mode()
+    def execute_async(self, so: SchedulerOutput, prev=None):
+        """Enqueue one step without waiting for its result.  Tokens that the previous step
+        (``prev``, still running) is sampling are not known on the host: they are copied on the
+        device from its output into this step's input ids.  Returns a handle for ``collect``."""
+        if so.is_empty:
+            return None
+        t_start = time.perf_counter()
+        self.stats["steps"] += 1
+        self._sync_rows(so)
+        B = len(so.scheduled)
+        decode_only = all(n == 1 for _, n in so.scheduled)
+        gsize = self._graph_size_for(B) if decode_only else None
+        meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
+        if prev is not None:
+            src, dst = [], []
+            off = 0
+            for req, n in so.scheduled:
+                off += n
+                if req.num_inflight > 0:
+                    j = prev.index.get(req.request_id)
+                    if j is not None:
+                        src.append(j)
+                        dst.append(off - 1)          # the pending token is the last one scheduled
+            if src:
+                idx = self._to_dev(torch.tensor([src, dst], dtype=torch.int64))
+                self.input_ids.index_copy_(0, idx[1], prev.tokens.index_select(0, idx[0]))
+        t_prep = time.perf_counter()
+        if gsize is not None:
+            desc = self.graphs[(gsize, self.lora_manager is not None and self.lora_manager.punica.any_active)]
+            hidden_out = self.graph_wrapper.replay(desc)
+            self.stats["graph_replays"] += 1
+            self.stats["graph_kernel_launches"] += self.graph_wrapper.entries[desc].num_launches
+            self.last_hidden = hidden_out
+            logits = self.model.compute_logits(hidden_out[:B])
+        else:
+            hidden = self._forward(Tp, meta)
+            self.last_hidden = hidden
+            self.stats["eager_steps"] += 1
+            if not sel:
+                return _StepHandle(None, [], None, None, "mixed", t_start)
+            h_sel = hidden[:T] if len(sel) == T else hidden[self._to_dev(torch.tensor(sel, dtype=torch.int64))]
+            logits = self.model.compute_logits(h_sel)
+        md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
+        if not md.all_greedy and not self.is_cuda:
+            md.generator = self._cpu_generator()
+        tokens = self.sampler(logits, md)
+        n = tokens.shape[0]
+        buf = self._h_sampled2[self._async_flip]
+        self._async_flip ^= 1
+        buf[:n].copy_(tokens, non_blocking=True)
+        ev = None
+        if self.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+        self.stats["d2h_bytes"] += n * 8
+        self.stats["t_prepare"] += t_prep - t_start
+        self.stats["t_launch"] += time.perf_counter() - t_prep
+        kind = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
+        return _StepHandle(tokens, sample_reqs, buf, ev, kind, t_start)
+
+    def _to_dev(self, t: torch.Tensor) -> torch.Tensor:
+        """Host index tensor to the device without blocking the host on the stream."""
+        return t.pin_memory().to(self.device, non_blocking=True) if self.is_cuda else t
+
+    def collect(self, handle) -> dict:
+        """Wait for a step enqueued by ``execute_async`` and return its sampled tokens."""
+        if handle is None or handle.tokens is None:
+            return {}
+        t0 = time.perf_counter()
+        if handle.event is not None:
+            handle.event.synchronize()
+        toks = handle.host[:len(handle.reqs)].numpy()
+        out = {}
+        for r, t in zip(handle.reqs, toks):
+            t = int(t)
+            if r.row >= 0 and self.row_owner[r.row] == r.request_id:
+                self.token_ids_cpu[r.row, r.num_tokens] = t
+            out[r.request_id] = [t]
+        now = time.perf_counter()
+        self.stats["t_wait"] += now - t0
+        self.stats["t_" + handle.kind] = self.stats.get("t_" + handle.kind, 0.0) + (now - handle.t_start)
+        self.stats["n_" + handle.kind] = self.stats.get("n_" + handle.kind, 0) + 1
         return out
 
     def _execute_pipeline(self, so: SchedulerOutput) -> dict:

@@ -83,6 +83,7 @@ class Request:
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
     spec_token_ids: list = field(default_factory=list)
+    num_inflight: int = 0                 # tokens sampled by steps still running on the GPU (async scheduling)
     job_id: Optional[str] = None
 
     @property

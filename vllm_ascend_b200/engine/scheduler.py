@@ -140,7 +140,11 @@ class Scheduler:
         self._committed_blocks -= self._commit.pop(req.request_id, 0)
 
     def _select_preemption_victim(self) -> Optional[Request]:
-        return self.running[-1] if self.running else None
+        # a request with a token still in flight cannot be rolled back before that step reports
+        for req in reversed(self.running):
+            if req.num_inflight == 0:
+                return req
+        return None
 
     # ------------------------------------------------------------------ core
     def _blocks_needed(self, req: Request, num_tokens_after: int) -> int:
@@ -188,7 +192,10 @@ class Scheduler:
         while i < len(self.running) and budget > 0:
             req = self.running[i]
             spec = len(req.spec_token_ids)
-            remaining = req.num_tokens + spec - req.num_computed_tokens
+            remaining = req.num_tokens + req.num_inflight + spec - req.num_computed_tokens
+            if req.num_inflight and (req.num_output_tokens + req.num_inflight >= req.sampling_params.max_tokens
+                                     or req.num_tokens + req.num_inflight >= self.cfg.max_model_len):
+                remaining = 0           # its last token is already on the way
             n = min(remaining, budget)
             if spec and n < remaining:       # the token budget cuts into the draft tokens
                 del req.spec_token_ids[max(0, spec - (remaining - n)):]
@@ -299,15 +306,32 @@ class Scheduler:
         return out
 
     # ------------------------------------------------------------------ results
+    def advance(self, out: SchedulerOutput) -> None:
+        """Asynchronous scheduling: account for a step at launch time instead of at completion.
+        Every request's computed count moves now, and a request whose step will sample gets one
+        in-flight token, so the next ``schedule()`` can plan the following step while this one
+        is still running."""
+        for req, n in out.scheduled:
+            req.num_computed_tokens += n
+            if req.num_computed_tokens >= req.num_tokens + req.num_inflight:
+                req.num_inflight += 1
+        out.advanced = True
+
     def update_from_output(self, out: SchedulerOutput, sampled: dict) -> list[Request]:
         """``sampled`` maps request_id -> list of new token ids (empty for a partial
         prefill chunk).  Returns the requests that finished in this step."""
         finished: list[Request] = []
+        advanced = getattr(out, "advanced", False)
         for req, n in out.scheduled:
             if req.status != RequestStatus.RUNNING:
                 continue
-            # draft tokens verified in this step: only the accepted ones leave valid KV behind
-            n_spec = max(0, req.num_computed_tokens + n - req.num_tokens)
+            if advanced:
+                if sampled.get(req.request_id):
+                    req.num_inflight = max(0, req.num_inflight - 1)
+                n_spec, n = 0, 0
+            else:
+                # draft tokens verified in this step: only the accepted ones leave valid KV behind
+                n_spec = max(0, req.num_computed_tokens + n - req.num_tokens)
             req.num_computed_tokens += n
             if n_spec:
                 emitted = len(sampled.get(req.request_id) or ())
@@ -346,6 +370,7 @@ class Scheduler:
     def _finish(self, req: Request, status: RequestStatus) -> None:
         import time
         req.status = status
+        req.num_inflight = 0
         req.finish_time = time.monotonic()
         delay_free = False
         if self.kv_connector is not None:
