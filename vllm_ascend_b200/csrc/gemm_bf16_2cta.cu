@@ -16,7 +16,7 @@
 //   warps 2..5  epilogue (both CTAs, each for its own 128 rows)
 // All waits are bounded (common.cuh); the cluster barriers at start and end are
 // reached by every thread on every path.
-#include "common.cuh"
+#include "comm.cuh"
 
 #include <mutex>
 #include <unordered_map>
@@ -43,7 +43,17 @@ struct Gemm2Params {
   int tiles_m, tiles_n;
   int swiglu;          // W = [gate; up]: tile pairs 128 gate + 128 up columns
   int up_row_offset;
+  // ---- fused collectives (same protocol as the single-CTA kernel's AG / RS modes)
+  int mode;                           // 0, G2_AG or G2_RS
+  const uint32_t* ag_flags;           // local CommCtl.ag_flag
+  const uint32_t* ag_epoch;
+  int rows_per_src, my_rank, num_ranks;
+  __nv_bfloat16* rs_dst[kMaxRanks];   // staging on owner o: [num_ranks][rows_per_owner][N]
+  uint32_t* rs_flag_dst[kMaxRanks];
+  CommCtl* ctl;
+  int rows_per_owner;
 };
+enum : int { G2_AG = 1, G2_RS = 2 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -154,9 +164,27 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------ producer (both CTAs)
     int stage = 0;
     uint32_t phase = 0;
+    uint32_t ag_epoch = 0;
+    if (p.mode & G2_AG) ag_epoch = *((volatile const uint32_t*)p.ag_epoch);
     for (int t = cluster_id; t < num_tiles; t += num_clusters) {
-      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      int tm = t % p.tiles_m;
+      const int tn = t / p.tiles_m;
+      if (p.mode & G2_AG) tm = (tm + (p.my_rank * p.rows_per_src) / G2_BM) % p.tiles_m;   // local rows first
       const int a_row = tm * G2_BM + (int)rank * 128;
+      if (p.mode & G2_AG) {
+        // this CTA's 128 rows come from source ranks s0..s1: wait for their pushes
+        if (lane == 0 && a_row < p.M) {
+          const int last_row = min(a_row + 128, p.M) - 1;
+          const int s0 = a_row / p.rows_per_src, s1 = last_row / p.rows_per_src;
+          for (int s = s0; s <= s1; s++) {
+            if (s == p.my_rank) continue;
+            if (!wait_flag_ge(&p.ag_flags[s], ag_epoch, p.status)) *abort_word = B200_TIMEOUT;
+          }
+          fence_proxy_async_global();
+        }
+        __syncwarp();
+        if (*abort_word) goto done;
+      }
       // plain: this CTA's 128 of the tile's 256 W rows.  SwiGLU: the leader stages the 128
       // gate rows, the peer the matching 128 up rows.
       const int w_row = p.swiglu ? tn * 128 + (int)rank * p.up_row_offset
@@ -214,7 +242,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int out_per_tile = p.swiglu ? 128 : G2_BN;
     int it = 0;
     for (int t = cluster_id; t < num_tiles; t += num_clusters, it++) {
-      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      int tm = t % p.tiles_m;
+      const int tn = t / p.tiles_m;
+      if (p.mode & G2_AG) tm = (tm + (p.my_rank * p.rows_per_src) / G2_BM) % p.tiles_m;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_word)) goto done;
@@ -222,7 +252,15 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row = tm * G2_BM + (int)rank * 128 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * G2_BN;
-      __nv_bfloat16* crow = p.C + (size_t)row * p.ldc;
+      __nv_bfloat16* crow;
+      if (p.mode & G2_RS) {
+        // partial-sum row goes straight into its owner's staging buffer over NVLink
+        const int owner = row_ok ? row / p.rows_per_owner : 0;
+        const int local = row - owner * p.rows_per_owner;
+        crow = p.rs_dst[owner] + ((size_t)p.my_rank * p.rows_per_owner + local) * p.ldc;
+      } else {
+        crow = p.C + (size_t)row * p.ldc;
+      }
       const __nv_bfloat16* rrow = p.residual ? p.residual + (size_t)row * p.ldc : nullptr;
 #pragma unroll 1
       for (int c0 = 0; c0 < out_per_tile; c0 += 32) {
@@ -285,6 +323,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // accumulator buffer drained: tell the leader's MMA warp (local or remote arrive)
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));
     }
+    if (p.mode & G2_RS) __threadfence_system();   // partial rows visible to their owners
   }
 done:
   tc_fence_before();
@@ -293,6 +332,17 @@ done:
     const uint64_t t_start = globaltimer_ns();
     while (globaltimer_ns() - t_start < 50000ull) __nanosleep(1000);
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, *abort_word);
+  } else if ((p.mode & G2_RS) && threadIdx.x == 0) {
+    // the last CTA of the grid publishes this rank's reduce-scatter epoch to every owner
+    const uint32_t prev = atomicAdd(&p.ctl->done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      const uint32_t epoch = p.ctl->rs_epoch + 1;
+      for (int o = 0; o < p.num_ranks; o++) st_release_sys(p.rs_flag_dst[o], epoch);
+      p.ctl->rs_epoch = epoch;
+      p.ctl->done_ctr = 0;
+      __threadfence();
+    }
   }
   // neither CTA may free TMEM or leave while its partner can still signal it or read its tiles
   cluster_sync_all();
@@ -346,6 +396,85 @@ static int get_tmap_128x64(CUtensorMap* out, const void* ptr, uint64_t rows, uin
 }  // namespace b200
 
 using namespace b200;
+
+static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, int ldw, long a_rows,
+                       cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         G2_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = get_tmap_128x64(&ta, A, (uint64_t)a_rows, (uint64_t)p.K, (uint64_t)lda);
+  if (rc) return rc;
+  rc = get_tmap_128x64(&tb, W, (uint64_t)(p.swiglu ? 2L * p.N : p.N), (uint64_t)p.K, (uint64_t)ldw);
+  if (rc) return rc;
+  p.up_row_offset = p.N;
+  const int out_per_tile = p.swiglu ? 128 : G2_BN;
+  p.tiles_m = (p.M + G2_BM - 1) / G2_BM;
+  p.tiles_n = (p.N + out_per_tile - 1) / out_per_tile;
+  int clusters = p.tiles_m * p.tiles_n;
+  const int max_clusters = num_sms() / 2;
+  if (clusters > max_clusters) clusters = max_clusters;
+  gemm_bf16_2cta_kernel<<<2 * clusters, G2_THREADS, G2_SMEM_BYTES, stream>>>(ta, tb, p);
+  return B200_CHECK_LAUNCH();
+}
+
+// All-gather -> GEMM with the paired-CTA kernel (contract of b200_gemm_ag_bf16; swiglu != 0
+// additionally fuses silu(gate) * up, W = [gate (N rows); up (N rows)]).
+B200_API int b200_gemm_ag_bf16_2cta(const void* A, const void* W, void* C, const void* bias, int M,
+                                    int N, int K, int lda, int ldw, int ldc, void* ctl,
+                                    int my_rank, int num_ranks, int rows_per_src, int swiglu,
+                                    int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
+  if (num_ranks > kMaxRanks || rows_per_src <= 0) return 9130;
+  if (swiglu && (N % 128)) return 9132;
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.swiglu = swiglu;
+  p.mode = G2_AG;
+  CommCtl* c = (CommCtl*)ctl;
+  p.ag_flags = c->ag_flag;
+  p.ag_epoch = &c->ag_epoch;
+  p.ctl = c;
+  p.rows_per_src = rows_per_src;
+  p.my_rank = my_rank;
+  p.num_ranks = num_ranks;
+  return launch_2cta(A, W, p, lda, ldw, M, stream);
+}
+
+// GEMM -> reduce-scatter with the paired-CTA kernel (contract of b200_gemm_rs_bf16).
+B200_API int b200_gemm_rs_bf16_2cta(const void* A, const void* W, const void* bias, int M, int N,
+                                    int K, int lda, int ldw, void* const* rs_staging,
+                                    void* const* peer_ctl, int my_rank, int num_ranks,
+                                    int rows_per_owner, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7)) return 9100;
+  if (num_ranks > kMaxRanks || (long)rows_per_owner * num_ranks < M) return 9130;
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.ldc = N;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.status = status;
+  p.mode = G2_RS;
+  p.my_rank = my_rank;
+  p.num_ranks = num_ranks;
+  p.rows_per_owner = rows_per_owner;
+  for (int o = 0; o < num_ranks; o++) {
+    p.rs_dst[o] = (__nv_bfloat16*)rs_staging[o];
+    p.rs_flag_dst[o] = &((CommCtl*)peer_ctl[o])->rs_flag[my_rank];
+  }
+  p.ctl = (CommCtl*)peer_ctl[my_rank];
+  return launch_2cta(A, W, p, lda, ldw, M, stream);
+}
 
 // Same contract as b200_gemm_bf16; with swiglu != 0, W is [gate (N rows); up (N rows)]
 // (N a multiple of 128) and C[M, N] = silu(A Wg^T) * (A Wu^T).

@@ -79,10 +79,29 @@ class FusedTPContext:
         _native.check(rc, "reduce_add_norm_push")
         launch_counter[0] += 1
 
-    def ag_gemm(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """[T, N_local] = gathered normalised hidden [T, H] @ weight^T."""
-        N = weight.shape[0]
+    def _two_cta(self, n_cols: int) -> bool:
+        """The paired-CTA kernel (256 x 256 tiles) pays off from a few hundred rows on."""
+        from .. import envs
+        m = envs.VLLM_B200_GEMM_2CTA_MIN_M
+        return m > 0 and self.T >= m and n_cols >= 256
+
+    def ag_gemm(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                swiglu: bool = False) -> torch.Tensor:
+        """[T, N_local] = gathered normalised hidden [T, H] @ weight^T; with ``swiglu`` the weight
+        is [gate; up] and the result is silu(gate) * up ([T, N_local / 2])."""
+        N = weight.shape[0] // 2 if swiglu else weight.shape[0]
         out = torch.empty((self.T, N), dtype=torch.bfloat16, device=self.device)
+        if self._two_cta(N) and (not swiglu or N % 128 == 0):
+            rc = _native.lib().b200_gemm_ag_bf16_2cta(
+                self.ag_local.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias),
+                self.T, N, self.H, self.H, weight.stride(0), N, self.symm.local_ptr, self.rank, self.n,
+                self.rows_local, int(swiglu), self.status.data_ptr(), _native.stream_ptr())
+            _native.check(rc, "gemm_ag_2cta")
+            launch_counter[0] += 1
+            return out
+        if swiglu:
+            from .. import ops
+            return ops.silu_and_mul(self.ag_gemm(weight, bias))
         rc = _native.lib().b200_gemm_ag_bf16(
             self.ag_local.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias),
             self.T, N, self.H, self.H, weight.stride(0), N, self.symm.local_ptr, self.rank, self.n,
@@ -95,11 +114,19 @@ class FusedTPContext:
                 bias: Optional[torch.Tensor] = None) -> None:
         """x [T, K_local] @ weight^T -> partial rows stored into their owners' staging."""
         assert x.shape[0] == self.T and weight.shape[0] == self.H
-        rc = _native.lib().b200_gemm_rs_bf16(
-            x.data_ptr(), weight.data_ptr(), _native.ptr(bias) if self.rank == 0 else None,
-            self.T, self.H, x.shape[1], x.stride(0), weight.stride(0), self.rs_ptrs, self.ctl_ptrs,
-            self.rank, self.n, self.rows_local, 0, self.status.data_ptr(), _native.stream_ptr())
-        _native.check(rc, "gemm_rs")
+        b = _native.ptr(bias) if self.rank == 0 else None
+        if self._two_cta(self.H):
+            rc = _native.lib().b200_gemm_rs_bf16_2cta(
+                x.data_ptr(), weight.data_ptr(), b, self.T, self.H, x.shape[1], x.stride(0), weight.stride(0),
+                self.rs_ptrs, self.ctl_ptrs, self.rank, self.n, self.rows_local, self.status.data_ptr(),
+                _native.stream_ptr())
+            _native.check(rc, "gemm_rs_2cta")
+        else:
+            rc = _native.lib().b200_gemm_rs_bf16(
+                x.data_ptr(), weight.data_ptr(), b, self.T, self.H, x.shape[1], x.stride(0), weight.stride(0),
+                self.rs_ptrs, self.ctl_ptrs, self.rank, self.n, self.rows_local, 0, self.status.data_ptr(),
+                _native.stream_ptr())
+            _native.check(rc, "gemm_rs")
         launch_counter[0] += 1
 
     def gathered(self) -> torch.Tensor:
@@ -148,8 +175,7 @@ def forward_sp(model, ctx: FusedTPContext, input_ids: torch.Tensor, meta, kv_cac
                             causal=True, window=a.window)
         ctx.gemm_rs(attn, a.o_proj.weight, a.o_proj.bias)
         ctx.norm_push(layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
-        gu = ctx.ag_gemm(layer.mlp.gate_up_proj.weight)
-        act = ops.silu_and_mul(gu)
+        act = ctx.ag_gemm(layer.mlp.gate_up_proj.weight, swiglu=True)
         ctx.gemm_rs(act, layer.mlp.down_proj.weight)
         nxt = layers[i + 1].input_layernorm if i + 1 < len(layers) else model.norm
         ctx.norm_push(nxt.weight, nxt.eps)

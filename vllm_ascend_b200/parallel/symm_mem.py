@@ -36,6 +36,8 @@ _native.register_signature("b200_reduce_add_norm_push", [P, I, P, P, P, F, P, P,
 _native.register_signature("b200_ag_wait", [P, I, I, P])
 _native.register_signature("b200_gemm_ag_bf16", [P, P, P, P, I, I, I, I, I, I, P, I, I, I, I, P, P])
 _native.register_signature("b200_gemm_rs_bf16", [P, P, P, I, I, I, I, I, P, P, I, I, I, I, P, P])
+_native.register_signature("b200_gemm_ag_bf16_2cta", [P, P, P, P, I, I, I, I, I, I, P, I, I, I, I, P, P])
+_native.register_signature("b200_gemm_rs_bf16_2cta", [P, P, P, I, I, I, I, I, P, P, I, I, I, P, P])
 _native.register_signature("b200_gemm_swiglu_bf16", [P, P, P, I, I, I, I, I, I, P, P])
 _native.register_signature("b200_grouped_gemm_bf16", [P, P, P, P, I, L, I, I, I, I, I, I, P, P])
 
