@@ -220,6 +220,79 @@ __global__ void qknorm_rope_kvwrite_kernel(__nv_bfloat16* qkv, long qkv_stride,
   }
 }
 
+// Fast path for D = 128 with full rotary (rot_dim = 128): every lane owns 4 consecutive
+// elements (one 8-byte access, 256 contiguous bytes per warp) and gets its rotation partner
+// (element j +- 64) from lane ^ 16 by shuffle.
+__global__ void qknorm_rope_kvwrite_d128_kernel(__nv_bfloat16* qkv, long qkv_stride,
+                                                const long* __restrict__ positions,
+                                                const float* __restrict__ cos_sin,
+                                                const __nv_bfloat16* __restrict__ q_norm_w,
+                                                const __nv_bfloat16* __restrict__ k_norm_w,
+                                                float eps, __nv_bfloat16* k_cache,
+                                                __nv_bfloat16* v_cache,
+                                                const long* __restrict__ slot_mapping, int T,
+                                                int Hq, int Hkv, long num_slots, int block_size,
+                                                int kv_layout, int* status) {
+  constexpr int D = 128;
+  const int warps_per_block = blockDim.x >> 5;
+  const int heads_total = Hq + 2 * Hkv;
+  const long gw = (long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (gw >= (long)T * heads_total) return;
+  const int t = (int)(gw / heads_total);
+  const int h = (int)(gw - (long)t * heads_total);
+  const int lane = threadIdx.x & 31;
+  uint2* src = reinterpret_cast<uint2*>(qkv + (long)t * qkv_stride + (long)h * D) + lane;
+  uint2 raw = *src;
+  const bool is_q = h < Hq;
+  const bool is_k = !is_q && h < Hq + Hkv;
+  if (is_q || is_k) {
+    float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
+    float v[4] = {a.x, a.y, b.x, b.y};
+    const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
+    if (nw) {
+      float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+      ss = warp_reduce_sum(ss);
+      const float inv = rsqrtf(ss / (float)D + eps);
+      const uint2 wr = reinterpret_cast<const uint2*>(nw)[lane];
+      const float2 w0 = unpack_bf16x2(wr.x), w1 = unpack_bf16x2(wr.y);
+      const float w[4] = {w0.x, w0.y, w1.x, w1.y};
+#pragma unroll
+      for (int i = 0; i < 4; i++)      // rounded to bf16 like the unfused norm -> rope sequence
+        v[i] = __bfloat162float(__float2bfloat16(v[i] * inv * w[i]));
+    }
+    const long pos = positions[t];
+    const float* cs = cos_sin + pos * (long)D;
+    const int e = (lane & 15) * 4;                       // index into the 64 cos / sin values
+    const float4 c = *reinterpret_cast<const float4*>(cs + e);
+    const float4 sn = *reinterpret_cast<const float4*>(cs + 64 + e);
+    const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+    const float sign = lane < 16 ? -1.f : 1.f;           // lower half: x1 c - x2 s; upper: x2 c + x1 s
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+      v[i] = v[i] * cc[i] + sign * other * sv[i];
+    }
+    raw.x = pack_bf16x2(v[0], v[1]);
+    raw.y = pack_bf16x2(v[2], v[3]);
+    *src = raw;
+  }
+  if (!is_q && k_cache) {
+    const long slot = slot_mapping[t];
+    if (slot < 0) return;
+    if (slot >= num_slots) {
+      if (lane == 0 && status) atomicExch(status, B200_BAD_INDEX);
+      return;
+    }
+    const int kvh = is_k ? (h - Hq) : (h - Hq - Hkv);
+    long row = slot * Hkv + kvh;
+    if (kv_layout == 1) {
+      const long blk = slot / block_size, off = slot - blk * block_size;
+      row = (blk * Hkv + kvh) * block_size + off;
+    }
+    reinterpret_cast<uint2*>((is_k ? k_cache : v_cache) + row * (long)D)[lane] = raw;
+  }
+}
+
 // ---------------------------------------------------------------- fp8 1x128 group quant
 // x: [T, H] bf16 -> q: [T, H] e4m3, scales: [T, H/128] fp32 (scale = amax/448).
 // One warp per group of 128 elements.
@@ -315,6 +388,14 @@ B200_API int b200_qknorm_rope_kvwrite(void* qkv, long qkv_stride, const void* po
       (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps,                    \
       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const long*)slot_mapping, T, Hq, Hkv, \
       num_slots, block_size, kv_layout, status)
+  if (D == 128 && rot_dim == 128 && (qkv_stride & 3) == 0) {
+    qknorm_rope_kvwrite_d128_kernel<<<blocks, wpb * 32, 0, stream>>>(
+        (__nv_bfloat16*)qkv, qkv_stride, (const long*)positions, (const float*)cos_sin,
+        (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps,
+        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const long*)slot_mapping, T, Hq, Hkv,
+        num_slots, block_size, kv_layout, status);
+    return B200_CHECK_LAUNCH();
+  }
   if (D == 128) LAUNCH_ROPE(128);
   else if (D == 64) LAUNCH_ROPE(64);
   else if (D == 256) LAUNCH_ROPE(256);

@@ -69,8 +69,11 @@ class LLMEngine:
         # token values: no proposer, no connector bookkeeping, no lock-step groups
         self._inflight = None
         want_async = cfg.async_scheduling if cfg.async_scheduling is not None else (cfg.device == "cuda")
+        # (TP ranks take identical decisions from identical tokens, so they stay in lock-step;
+        # DP / PP engines exchange host-side state every step and run synchronously)
         self.async_scheduling = bool(want_async and self.runner.proposer is None and self.kv_connector is None
-                                     and self.eplb is None and world == 1)
+                                     and self.eplb is None and self.dp.world_size == 1
+                                     and pc.pipeline_parallel_size == 1)
         self.runner.capture_graphs()
         self._req_counter = itertools.count()
         self.eos_token_id: Optional[int] = None
