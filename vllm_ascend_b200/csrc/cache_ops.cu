@@ -10,6 +10,8 @@
 //     here the copy writes straight into the destination block table layout.
 //   * swap/copy blocks inside one cache (attention/attention_v1.py:119-145).
 #include "common.cuh"
+#include <cstdio>
+#include <cuda_bf16.h>
 
 namespace b200 {
 
@@ -98,5 +100,50 @@ B200_API int b200_copy_blocks(void* cache, const void* pairs, int num_pairs, lon
   if (block_bytes & 15) return 9100;
   copy_blocks_kernel<<<num_pairs, 256, 0, stream>>>((uint8_t*)cache, (const long*)pairs,
                                                     block_bytes);
+  return B200_CHECK_LAUNCH();
+}
+
+// ---------------------------------------------------------------- block zeroing / debug print
+namespace b200 {
+
+// Zero whole KV blocks of every cache tensor: freshly allocated blocks must not carry bit
+// patterns of earlier requests into masked positions (the reference zeroes new blocks with
+// a small kernel of its own, vllm_ascend/worker/utils.py:15-184).
+__global__ void zero_blocks_kernel(void* const* tensors, const int* blocks, long block_stride_bytes,
+                                   long block_bytes) {
+  uint8_t* base = (uint8_t*)tensors[blockIdx.y] + (long)blocks[blockIdx.x] * block_stride_bytes;
+  uint4* p = reinterpret_cast<uint4*>(base);
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  for (long i = threadIdx.x; i < (block_bytes >> 4); i += blockDim.x) p[i] = z;
+}
+
+// Graph-safe debug print: runs as a kernel in stream order, so it also shows values inside
+// captured graphs (role of the reference's device_print / device_print_tensor ops).
+__global__ void device_print_kernel(const float* f32, const __nv_bfloat16* bf16, long n, int tag) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  printf("[device_print %d]", tag);
+  for (long i = 0; i < n; i++) printf(" %g", f32 ? f32[i] : __bfloat162float(bf16[i]));
+  printf("\n");
+}
+
+}  // namespace b200
+
+// tensors: device array of num_tensors base pointers of DENSE per-block storage (block b of
+// tensor i starts at base + b * block_stride_bytes); blocks: device int32 [num_blocks].
+B200_API int b200_zero_blocks(const void* tensors, int num_tensors, const void* blocks, int num_blocks,
+                              long block_stride_bytes, long block_bytes, cudaStream_t stream) {
+  if (num_blocks <= 0 || num_tensors <= 0) return 0;
+  if ((block_bytes & 15) || (block_stride_bytes & 15)) return 9100;
+  zero_blocks_kernel<<<dim3(num_blocks, num_tensors), 256, 0, stream>>>(
+      (void* const*)tensors, (const int*)blocks, block_stride_bytes, block_bytes);
+  return B200_CHECK_LAUNCH();
+}
+
+// dtype 0: fp32, 1: bf16; prints the first n values
+B200_API int b200_device_print(const void* data, int dtype, long n, int tag, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n > 64) n = 64;
+  device_print_kernel<<<1, 32, 0, stream>>>(dtype == 0 ? (const float*)data : nullptr,
+                                            dtype == 1 ? (const __nv_bfloat16*)data : nullptr, n, tag);
   return B200_CHECK_LAUNCH();
 }

@@ -420,7 +420,7 @@ class ModelRunner:
             self.stats["graph_replays"] += 1
             self.stats["graph_kernel_launches"] += self.graph_wrapper.entries[desc].num_launches
             self.last_hidden = hidden_out
-            logits = self.model.compute_logits(hidden_out[:B])
+            logits = None if self._reduce_sample(sample_reqs) else self.model.compute_logits(hidden_out[:B])
         else:
             hidden = self._forward(Tp, meta)
             self.last_hidden = hidden
@@ -431,17 +431,20 @@ class ModelRunner:
                 h_sel = hidden[:T]
             else:
                 h_sel = hidden[torch.tensor(sel, dtype=torch.int64, device=self.device)]
-            logits = self.model.compute_logits(h_sel)
-        if any(k > 1 for k in self._sample_rows):
+            logits = None if self._reduce_sample(sample_reqs) else self.model.compute_logits(h_sel)
+        if logits is None:
+            tokens = self.model.lm_head.greedy_tokens(h_sel if gsize is None else hidden_out[:B])
+        if logits is not None and any(k > 1 for k in self._sample_rows):
             out = self._sample_speculative(logits, sample_reqs, self._sample_rows)
             t_sync = time.perf_counter()
             self.stats["t_spec"] = self.stats.get("t_spec", 0.0) + (t_sync - t_start)
             self.stats["n_spec"] = self.stats.get("n_spec", 0) + 1
             return out
-        md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
-        if not md.all_greedy and not self.is_cuda:
-            md.generator = self._cpu_generator()
-        tokens = self.sampler(logits, md)
+        if logits is not None:
+            md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
+            if not md.all_greedy and not self.is_cuda:
+                md.generator = self._cpu_generator()
+            tokens = self.sampler(logits, md)
         n = tokens.shape[0]
         t_launch = time.perf_counter()
         if self.is_cuda:
@@ -501,7 +504,7 @@ class ModelRunner:
             self.stats["graph_replays"] += 1
             self.stats["graph_kernel_launches"] += self.graph_wrapper.entries[desc].num_launches
             self.last_hidden = hidden_out
-            logits = self.model.compute_logits(hidden_out[:B])
+            h_sel = hidden_out[:B]
         else:
             hidden = self._forward(Tp, meta)
             self.last_hidden = hidden
@@ -509,11 +512,14 @@ class ModelRunner:
             if not sel:
                 return _StepHandle(None, [], None, None, "mixed", t_start)
             h_sel = hidden[:T] if len(sel) == T else hidden[self._to_dev(torch.tensor(sel, dtype=torch.int64))]
+        if self._reduce_sample(sample_reqs):
+            tokens = self.model.lm_head.greedy_tokens(h_sel)
+        else:
             logits = self.model.compute_logits(h_sel)
-        md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
-        if not md.all_greedy and not self.is_cuda:
-            md.generator = self._cpu_generator()
-        tokens = self.sampler(logits, md)
+            md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
+            if not md.all_greedy and not self.is_cuda:
+                md.generator = self._cpu_generator()
+            tokens = self.sampler(logits, md)
         n = tokens.shape[0]
         buf = self._h_sampled2[self._async_flip]
         self._async_flip ^= 1
@@ -527,6 +533,14 @@ class ModelRunner:
         self.stats["t_launch"] += time.perf_counter() - t_prep
         kind = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
         return _StepHandle(tokens, sample_reqs, buf, ev, kind, t_start)
+
+    def _reduce_sample(self, sample_reqs: list) -> bool:
+        """Greedy batches on a vocabulary-sharded LM head pick their tokens from per-rank
+        (max, index) pairs instead of gathering [B, vocab] logits on every rank."""
+        head = self.model.lm_head
+        if head.comm.size <= 1 or any(k > 1 for k in self._sample_rows):
+            return False
+        return all(r.sampling_params.greedy and not r.sampling_params.has_penalties for r in sample_reqs)
 
     def _to_dev(self, t: torch.Tensor) -> torch.Tensor:
         """Host index tensor to the device without blocking the host on the stream."""

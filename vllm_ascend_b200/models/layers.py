@@ -224,6 +224,29 @@ class ParallelLMHead:
             logits = self.comm.all_gather(logits, dim=-1)
         return logits[..., :self.embed.vocab]
 
+    def greedy_tokens(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Arg-max over the full vocabulary without gathering the logits: every rank reduces its
+        own vocabulary shard to (max value, index) and only those pairs are all-gathered — the
+        "reduce sample" path of vllm_ascend/sample/sampler.py:87-107, 168-204."""
+        logits = ops.linear(hidden, self.weight)                       # [B, V / tp]
+        n, r = self.comm.size, self.comm.rank
+        shard = logits.shape[-1]
+        first = r * shard
+        if first + shard > self.embed.vocab:                           # padded tail of the last shard
+            logits = logits.clone()
+            logits[:, max(self.embed.vocab - first, 0):] = float("-inf")
+        idx = ops.argmax(logits)
+        val = logits.float().gather(1, idx.view(-1, 1)).squeeze(1)
+        if n == 1:
+            return idx
+        pair = torch.stack([val, (idx + first).to(torch.float32)], dim=1)          # ids < 2^24: exact in fp32
+        allp = self.comm.all_gather(pair.contiguous(), dim=0).view(n, -1, 2)       # [tp, B, 2]
+        vals, ids = allp[..., 0], allp[..., 1]
+        best = vals.max(dim=0, keepdim=True).values
+        # ties resolve to the lowest index, as a single arg-max over the whole row would
+        cand = torch.where(vals == best, ids, torch.full_like(ids, float("inf")))
+        return cand.min(dim=0).values.to(torch.int64)
+
 
 # ---------------------------------------------------------------- rotary tables
 _ROPE_CACHE: dict = {}

@@ -90,6 +90,18 @@ class SparseMoeBlock:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         w, ids = self.route(x)
+        overlap = None
+        if self.shared is not None and self.ep is not None and x.is_cuda and self._overlap_shared() \
+                and not torch.cuda.is_current_stream_capturing():
+            # shared experts run on a side stream while the routed tokens travel: the stream
+            # forks after routing and joins before the sum (the reference gates the same overlap
+            # on dispatch / combine events, ops/fused_moe/shared_experts.py:49-349)
+            from ..utils import side_stream
+            side = side_stream("shared_expert", x.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                overlap = self.shared(x)
+                x.record_stream(side)
         if self.runtime is not None and self.ep is not None:
             y = self.runtime.forward(self, x, w, ids)          # EP dispatch/combine paths
         else:
@@ -102,11 +114,20 @@ class SparseMoeBlock:
                 y = self.comm.all_reduce(y)
             return y
         if self.shared is not None:
-            s = self.shared(x)
+            if overlap is not None:
+                torch.cuda.current_stream().wait_stream(side)
+                s = overlap
+            else:
+                s = self.shared(x)
             if self.comm.size > 1:
                 s = self.comm.all_reduce(s)
             y = y + s
         return y
+
+    @staticmethod
+    def _overlap_shared() -> bool:
+        from ..platform_config import get_b200_config
+        return get_b200_config().multistream_overlap_shared_expert
 
 
 # ---------------------------------------------------------------- MLA attention
