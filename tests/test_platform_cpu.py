@@ -206,3 +206,53 @@ def test_utils_predicates_and_op_table():
     n = RMSNorm(8, dtype=torch.float32)
     y = n(x)
     assert torch.allclose(y, x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6), atol=1e-5)
+
+
+def test_dyntra_lb_moves_waiting_requests_to_the_idle_rank():
+    """Two schedulers stand for two DP ranks; the gather function is a shared bus that returns
+    both ranks' contributions (the ranks call it in the same order, like a collective)."""
+    import numpy as np
+    from vllm_ascend_b200.config import CacheConfig, SchedulerConfig
+    from vllm_ascend_b200.core.dyntra_lb import DyntraLBScheduler
+    from vllm_ascend_b200.engine.request import Request, SamplingParams
+    from vllm_ascend_b200.platform_config import init_b200_config
+    init_b200_config({"scheduler_config": {"dyntra_lb_config": {"enabled": True, "imbalance_threshold": 0.1}}},
+                     refresh=True)
+    sc = SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256)
+    cc = CacheConfig(block_size=16)
+    s = [DyntraLBScheduler(sc, cc, 64, rank=r, world=2, gather_fn=lambda v: [v]) for r in range(2)]
+    for i in range(10):                 # everything arrives at rank 0
+        req = Request(f"r{i}", np.arange(100, dtype=np.int32), SamplingParams(max_tokens=4))
+        req.client_index, req.origin_rank = i, 0
+        s[0].add_request(req)
+
+    def lockstep_balance():
+        # phase 1: loads; phase 2: outboxes -- emulate the two all-gathers
+        loads = [(x.pressure(), len(x.waiting), len(x.running)) for x in s]
+        outs = []
+        for r in range(2):
+            phase = {"n": 0}
+
+            def g(v, r=r, phase=phase):
+                phase["n"] += 1
+                if phase["n"] == 1:
+                    return loads
+                outs.append((r, v))
+                return [[], []]         # deliveries happen below
+            s[r]._gather = g
+            s[r].balance()
+        for r, box in outs:
+            for dst, payload in box:
+                from vllm_ascend_b200.core.dyntra_lb import _unpack
+                s[dst].add_request(_unpack(payload))
+                s[dst].migrated_in += 1
+    before = len(s[0].waiting)
+    for _ in range(4):
+        lockstep_balance()
+    assert s[0].migrated_out > 0 and s[1].migrated_in == s[0].migrated_out
+    assert len(s[0].waiting) + len(s[1].waiting) == before
+    assert abs(s[0].pressure() - s[1].pressure()) < before * 7 / 64
+    moved = list(s[1].waiting)
+    assert all(r.origin_rank == 0 and r.client_index is not None for r in moved)
+    # the oldest requests stay where they arrived
+    assert s[0].waiting[0].request_id == "r0"

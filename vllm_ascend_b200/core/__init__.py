@@ -19,6 +19,8 @@ def make_scheduler(engine_cfg, num_blocks: int, kv_connector=None):
         from .profiling_chunk import ProfilingChunkScheduler as cls
     elif policy == "balance":
         from .balance import BalanceScheduler as cls
+    elif policy == "dyntra_lb":
+        from .dyntra_lb import DyntraLBScheduler as cls
     elif policy != "fcfs":
         raise ValueError(f"unknown scheduler policy {policy!r}")
     if cls is not Scheduler:

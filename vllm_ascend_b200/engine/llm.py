@@ -300,6 +300,7 @@ class LLM:
             order.append(rid)
             mine.append(i)
             reqs[rid] = eng.scheduler.requests[rid]
+            reqs[rid].client_index, reqs[rid].origin_rank = i, dp.rank_in_group
         if dp.world_size > 1:
             while eng.step_dp():
                 pass
@@ -307,6 +308,13 @@ class LLM:
             while eng.has_unfinished():
                 eng.step()
         eng.check_health()
+        if dp.world_size > 1:
+            # requests may have moved between DP ranks (load balancing): report what finished here
+            done = [r for r in eng.scheduler.requests.values()
+                    if r.is_finished and getattr(r, "client_index", None) is not None]
+            mine = [r.client_index for r in done]
+            order = [r.request_id for r in done]
+            reqs = {r.request_id: r for r in done}
         outs = []
         for rid in order:
             r = reqs[rid]

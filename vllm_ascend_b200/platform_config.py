@@ -100,6 +100,8 @@ class DyntraLBConfig:
     long_req_block_threshold: int = 64
     dynamic_max_step: int = 0
     enable_diagnostics: bool = False
+    imbalance_threshold: float = 0.15           # pressure gap that triggers a hand-over
+    max_migrations_per_step: int = 4
 
 
 @dataclass
@@ -322,6 +324,8 @@ def check_and_update_config(engine_cfg) -> B200Config:
         sc.policy = "profiling_chunk"
     elif s.enable_balance_scheduling:
         sc.policy = "balance"
+    elif s.dyntra_lb_config.enabled:
+        sc.policy = "dyntra_lb"
     if sc.max_num_batched_tokens < 1 or sc.max_num_seqs < 1:
         raise ValueError("scheduler limits must be positive")
     if not sc.enable_chunked_prefill and sc.max_num_batched_tokens < sc.max_model_len:
