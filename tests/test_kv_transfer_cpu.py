@@ -185,3 +185,42 @@ def test_cpu_offload_lru_eviction_and_multi_connector():
         llm.generate(_prompts(1, lo=64, hi=65, seed=20 + seed), sp)
     assert len(c.lru) <= 4 and c.stats["evicted_blocks"] > 0
     assert not c.free or len(c.lru) + len(c.free) == 4
+
+
+def test_sparse_kv_offload_resident_set():
+    """Native LRU bookkeeping: hits keep their slot, misses evict the least recently used token,
+    tokens needed by the current step are never evicted, copies bring the right rows."""
+    import numpy as np
+    import torch
+    from vllm_ascend_b200.distributed.kv_transfer.sparse_kv_offload import SparseKVOffloadManager
+    m = SparseKVOffloadManager(max_seqs=3, max_tokens_per_seq=64, slots_per_seq=4, width=8,
+                               dtype=torch.float32, device="cpu", num_threads=2)
+    try:
+        for row in range(3):
+            m.append(row, 0, torch.arange(64 * 8, dtype=torch.float32).view(64, 8) + 1000 * row)
+        rows = np.array([0, 2])
+        s1 = m.step(rows, np.array([[5, 9, 1, -1], [7, 7, 3, 2]]))
+        assert (s1[0, 3] == -1) and len(set(s1[0, :3].tolist())) == 3
+        assert s1[1, 0] == s1[1, 1]                                   # same token, same slot
+        for b, row in enumerate(rows):
+            for j, tok in enumerate([[5, 9, 1], [7, 7, 3, 2]][b]):
+                assert torch.equal(m.pool[row, s1[b, j]], m.host[row, tok])
+        st = m.stats()
+        assert st["misses"] == 6 and st["hits"] == 0
+        # second step: 9 and 1 hit, 20 and 21 miss; one free slot is left, then the LRU token 5 goes
+        s2 = m.step(np.array([0]), np.array([[9, 1, 20, 21]]))
+        assert s2[0, 0] == s1[0, 1] and s2[0, 1] == s1[0, 2]
+        assert s2[0, 3] == s1[0, 0]                                   # token 21 took token 5's slot
+        assert torch.equal(m.pool[0, s2[0, 2]], m.host[0, 20])
+        st = m.stats()
+        assert st["hits"] == 2 and st["evictions"] == 1
+        # five distinct tokens cannot be resident in four slots
+        import pytest
+        m.step(np.array([1]), np.array([[1, 2, 3, 4]]))
+        with pytest.raises(RuntimeError):
+            m.step(np.array([1]), np.array([[5, 6, 7, 8, 9]]))
+        m.release(0)
+        s3 = m.step(np.array([0]), np.array([[9, -1, -1, -1]]))
+        assert m.stats()["misses"] > st["misses"]                     # state of the row was dropped
+    finally:
+        m.close()

@@ -43,12 +43,15 @@ _LONG_RET = {"b200_paged_decode_scratch_bytes": [I, I, I, I],
              "b200_attn_scratch_bytes": [L, I, I, I]}
 
 
+_RESTYPES: dict = {}
+
+
 def _declare(lib: ctypes.CDLL) -> None:
     for name, argtypes in _SIGNATURES.items():
         if hasattr(lib, name):
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = c_int
+            fn.restype = _RESTYPES.get(name, c_int)
     for name, argtypes in _LONG_RET.items():
         if hasattr(lib, name):
             fn = getattr(lib, name)
@@ -59,6 +62,8 @@ def _declare(lib: ctypes.CDLL) -> None:
 def register_signature(name: str, argtypes: list, restype=c_int) -> None:
     """Used by sub-modules that own additional entry points (comm, moe, vmm...)."""
     _SIGNATURES[name] = argtypes
+    if restype is not c_int:
+        _RESTYPES[name] = restype
     if _lib is not None and hasattr(_lib, name):
         fn = getattr(_lib, name)
         fn.argtypes = argtypes
