@@ -224,3 +224,35 @@ def test_sparse_kv_offload_resident_set():
         assert m.stats()["misses"] > st["misses"]                     # state of the row was dropped
     finally:
         m.close()
+
+
+def test_kv_pool_shares_prefixes_between_engines():
+    """Engine A publishes the blocks of its finished requests to the store; engine B, which has
+    never seen the prompts, loads them instead of prefilling."""
+    from vllm_ascend_b200.distributed.kv_transfer.kv_pool import KVStoreServer
+    store = KVStoreServer(capacity_bytes=64 << 20)
+    try:
+        def mk():
+            return LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4,
+                       kv_transfer_config={"kv_connector": "KVPoolConnector",
+                                           "kv_connector_extra_config": {"store_port": store.port}})
+        a, b = mk(), mk()
+        prompts = _prompts(3, lo=50, hi=90, seed=31)
+        sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+        want = [o.outputs[0].token_ids for o in a.generate(prompts, sp)]
+        a.engine.kv_connector.flush()
+        assert a.engine.kv_connector.stats["published_blocks"] >= sum(len(p) // 16 for p in prompts)
+        got = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
+        assert got == want
+        cb = b.engine.kv_connector
+        assert cb.stats["hit_tokens"] == sum((len(p) - 1) // 16 * 16 for p in prompts)
+        assert cb.stats["loaded_blocks"] == cb.stats["hit_tokens"] // 16
+        st = store._handle({"op": "stats"})
+        assert st["blocks"] > 0 and st["hits"] == cb.stats["loaded_blocks"]
+        # a tiny store evicts, lookups then simply miss
+        small = KVStoreServer(capacity_bytes=1)
+        small._handle({"op": "put", "hashes": [b"x"], "payloads": [b"123"]})
+        assert small._handle({"op": "exists", "hashes": [b"x"]})["mask"] == [False]
+        small.close()
+    finally:
+        store.close()

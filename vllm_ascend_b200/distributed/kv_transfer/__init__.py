@@ -13,7 +13,11 @@ _CONNECTORS = {
     "MooncakeConnectorV1": ("nvlink_connector", "NVLinkConnector"),
     "MooncakeLayerwiseConnector": ("nvlink_connector", "NVLinkConnector"),
     "CPUOffloadingConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
-    "AscendStoreConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
+    "KVPoolConnector": ("kv_pool", "KVPoolConnector"),
+    "AscendStoreConnector": ("kv_pool", "KVPoolConnector"),
+    "MooncakeConnectorStoreV1": ("kv_pool", "KVPoolConnector"),
+    "SimpleCPUOffloadConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
+    "OffloadingConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
     "MultiConnector": ("multi_connector", "MultiConnector"),
 }
 
