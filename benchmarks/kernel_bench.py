@@ -16,6 +16,7 @@ the fallback 6650 GB/s / 1590 TFLOP/s is used and marked "of fallback".
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -67,6 +68,9 @@ def bench_gemm(a):
     x = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    if a.raster:
+        _native.register_signature("b200_gemm_2cta_set_raster", [ctypes.c_int])
+        _native.lib().b200_gemm_2cta_set_raster(a.raster)
     ms = timeit(lambda: ops.linear(x, w, out=out, bn=a.bn), a.iters)
     ms_lib = timeit(lambda: torch.nn.functional.linear(x, w), a.iters) if a.compare else None
     hbm, tf, tag = peaks()
@@ -171,6 +175,7 @@ def main():
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--raster", type=int, default=0, help="M-tiles per raster group of the paired-CTA GEMM")
     ap.add_argument("--compare", action="store_true")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=1152)

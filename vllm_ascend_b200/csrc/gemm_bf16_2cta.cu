@@ -52,6 +52,7 @@ struct Gemm2Params {
   uint32_t* rs_flag_dst[kMaxRanks];
   CommCtl* ctl;
   int rows_per_owner;
+  int raster;                         // M-tiles per raster group (0/1: column-major order)
 };
 enum : int { G2_AG = 1, G2_RS = 2 };
 
@@ -112,6 +113,24 @@ __device__ __forceinline__ void umma_commit_2sm(uint64_t* bar) {
       : "memory");
 }
 
+// Tile order: groups of `raster` M-tiles are walked column by column, so the clusters that run
+// at the same time share a few A row-blocks and a few W column-blocks (both stay in L2)
+// instead of streaming all of A against one W block.
+__device__ __forceinline__ void tile_of(const Gemm2Params& p, int t, int& tm, int& tn) {
+  const int gm_full = p.raster;
+  if (gm_full <= 1 || gm_full >= p.tiles_m) {
+    tm = t % p.tiles_m;
+    tn = t / p.tiles_m;
+    return;
+  }
+  const int per_group = gm_full * p.tiles_n;
+  const int g = t / per_group, r = t - g * per_group;
+  const int first = g * gm_full;
+  const int gm = min(gm_full, p.tiles_m - first);
+  tm = first + r % gm;
+  tn = r / gm;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b, const Gemm2Params p) {
@@ -167,8 +186,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t ag_epoch = 0;
     if (p.mode & G2_AG) ag_epoch = *((volatile const uint32_t*)p.ag_epoch);
     for (int t = cluster_id; t < num_tiles; t += num_clusters) {
-      int tm = t % p.tiles_m;
-      const int tn = t / p.tiles_m;
+      int tm, tn;
+      tile_of(p, t, tm, tn);
       if (p.mode & G2_AG) tm = (tm + (p.my_rank * p.rows_per_src) / G2_BM) % p.tiles_m;   // local rows first
       const int a_row = tm * G2_BM + (int)rank * 128;
       if (p.mode & G2_AG) {
@@ -242,8 +261,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int out_per_tile = p.swiglu ? 128 : G2_BN;
     int it = 0;
     for (int t = cluster_id; t < num_tiles; t += num_clusters, it++) {
-      int tm = t % p.tiles_m;
-      const int tn = t / p.tiles_m;
+      int tm, tn;
+      tile_of(p, t, tm, tn);
       if (p.mode & G2_AG) tm = (tm + (p.my_rank * p.rows_per_src) / G2_BM) % p.tiles_m;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -397,6 +416,8 @@ static int get_tmap_128x64(CUtensorMap* out, const void* ptr, uint64_t rows, uin
 
 using namespace b200;
 
+static int g_raster = 8;
+
 static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, int ldw, long a_rows,
                        cudaStream_t stream) {
   static bool attr_set = false;
@@ -419,6 +440,7 @@ static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, in
   int clusters = p.tiles_m * p.tiles_n;
   const int max_clusters = num_sms() / 2;
   if (clusters > max_clusters) clusters = max_clusters;
+  p.raster = g_raster;
   gemm_bf16_2cta_kernel<<<2 * clusters, G2_THREADS, G2_SMEM_BYTES, stream>>>(ta, tb, p);
   return B200_CHECK_LAUNCH();
 }
@@ -484,19 +506,6 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* W, void* C, const vo
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
   if (swiglu && (N % 128)) return 9132;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         G2_SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
-  CUtensorMap ta, tb;
-  int rc = get_tmap_128x64(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda);
-  if (rc) return rc;
-  rc = get_tmap_128x64(&tb, W, (uint64_t)(swiglu ? 2L * N : N), (uint64_t)K, (uint64_t)ldw);
-  if (rc) return rc;
   Gemm2Params p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K; p.ldc = ldc;
@@ -505,13 +514,11 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* W, void* C, const vo
   p.C = (__nv_bfloat16*)C;
   p.status = status;
   p.swiglu = swiglu;
-  p.up_row_offset = N;
-  const int out_per_tile = swiglu ? 128 : G2_BN;
-  p.tiles_m = (M + G2_BM - 1) / G2_BM;
-  p.tiles_n = (N + out_per_tile - 1) / out_per_tile;
-  int clusters = p.tiles_m * p.tiles_n;
-  const int max_clusters = num_sms() / 2;
-  if (clusters > max_clusters) clusters = max_clusters;
-  gemm_bf16_2cta_kernel<<<2 * clusters, G2_THREADS, G2_SMEM_BYTES, stream>>>(ta, tb, p);
-  return B200_CHECK_LAUNCH();
+  return launch_2cta(A, W, p, lda, ldw, M, stream);
+}
+
+// Tile order of the paired-CTA kernel: M-tiles per raster group (1 = plain column-major).
+B200_API int b200_gemm_2cta_set_raster(int m_tiles_per_group) {
+  g_raster = m_tiles_per_group < 1 ? 1 : m_tiles_per_group;
+  return 0;
 }

@@ -1,0 +1,174 @@
+"""OpenAI-style completion server on top of the engine (the standalone counterpart of running
+the reference under ``vllm serve``).
+
+    python -m vllm_ascend_b200.entrypoints.api_server --model qwen3-8b --port 8000
+
+One background thread owns the engine and steps it; HTTP handlers enqueue requests and wait
+for their completion.  Prompts are token-id lists (``prompt`` may also be text when a
+tokenizer directory is given).  ``kv_transfer_params`` are accepted and returned, which is
+what a prefill/decode proxy needs.  ``/metrics`` exposes the engine counters in the
+Prometheus text format, ``/health`` runs the worker health check.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import queue
+import threading
+import time
+import uuid
+from typing import Optional
+
+from fastapi import FastAPI, HTTPException
+from fastapi.responses import PlainTextResponse
+
+from ..engine.request import RequestStatus, SamplingParams
+
+_FINISH = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
+           RequestStatus.FINISHED_ABORTED: "abort"}
+
+
+class EngineLoop(threading.Thread):
+    """Owns the engine: drains the submission queue, steps while there is work."""
+
+    def __init__(self, llm):
+        super().__init__(daemon=True, name="engine-loop")
+        self.llm, self.engine = llm, llm.engine
+        self.inbox: "queue.Queue" = queue.Queue()
+        self.waiters: dict[str, tuple] = {}          # request id -> (asyncio future, loop, request)
+        self.stop_flag = threading.Event()
+        self.error: Optional[BaseException] = None
+
+    def submit(self, prompt_ids, sp: SamplingParams, kv_params, fut, loop) -> str:
+        rid = f"cmpl-{uuid.uuid4().hex[:16]}"
+        self.inbox.put((rid, prompt_ids, sp, kv_params, fut, loop))
+        return rid
+
+    def run(self) -> None:
+        eng = self.engine
+        while not self.stop_flag.is_set():
+            try:
+                block = not eng.has_unfinished()
+                while True:
+                    item = self.inbox.get(timeout=0.05) if block else self.inbox.get_nowait()
+                    rid, ids, sp, kvp, fut, loop = item
+                    try:
+                        eng.add_request(ids, sp, request_id=rid, kv_transfer_params=kvp)
+                        self.waiters[rid] = (fut, loop, eng.scheduler.requests[rid])
+                    except Exception as e:
+                        loop.call_soon_threadsafe(fut.set_exception, e)
+                    block = False
+            except queue.Empty:
+                pass
+            if not eng.has_unfinished():
+                continue
+            try:
+                eng.step()
+            except BaseException as e:           # fail every waiter, stop serving
+                self.error = e
+                for fut, loop, _ in self.waiters.values():
+                    loop.call_soon_threadsafe(fut.set_exception, RuntimeError(f"engine failed: {e}"))
+                self.waiters.clear()
+                return
+            for rid in [r for r, (_, _, req) in self.waiters.items() if req.is_finished]:
+                fut, loop, req = self.waiters.pop(rid)
+                eng.scheduler.requests.pop(rid, None)
+                loop.call_soon_threadsafe(fut.set_result, req)
+
+    def stop(self) -> None:
+        self.stop_flag.set()
+
+
+def build_app(llm, tokenizer=None, model_name: str = "model") -> FastAPI:
+    app = FastAPI(title="vllm_ascend_b200")
+    loop_thread = EngineLoop(llm)
+    loop_thread.start()
+    app.state.engine_loop = loop_thread
+
+    @app.get("/health")
+    async def health():
+        if loop_thread.error is not None:
+            raise HTTPException(500, f"engine failed: {loop_thread.error}")
+        try:
+            llm.engine.check_health()
+        except Exception as e:
+            raise HTTPException(500, str(e))
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
+
+    @app.get("/metrics", response_class=PlainTextResponse)
+    async def metrics():
+        from ..observability.metrics import collect
+        lines = []
+        for k, v in collect(llm.engine).items():
+            if isinstance(v, (int, float)):
+                lines.append(f"# TYPE vllm_b200_{k} gauge\nvllm_b200_{k} {float(v)}")
+        return "\n".join(lines) + "\n"
+
+    @app.post("/v1/completions")
+    async def completions(body: dict):
+        prompt = body.get("prompt")
+        if isinstance(prompt, str):
+            if tokenizer is None:
+                raise HTTPException(400, "text prompts need a tokenizer; send token ids")
+            ids = tokenizer.encode(prompt)
+        elif isinstance(prompt, list) and prompt and all(isinstance(t, int) for t in prompt):
+            ids = prompt
+        else:
+            raise HTTPException(400, "prompt must be a string or a list of token ids")
+        sp = SamplingParams(max_tokens=int(body.get("max_tokens", 16)), temperature=float(body.get("temperature", 1.0)),
+                            top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", 0) or 0),
+                            seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
+                            stop_token_ids=list(body.get("stop_token_ids") or []))
+        aloop = asyncio.get_running_loop()
+        fut = aloop.create_future()
+        t0 = time.time()
+        rid = loop_thread.submit(ids, sp, body.get("kv_transfer_params"), fut, aloop)
+        try:
+            req = await fut
+        except Exception as e:
+            raise HTTPException(400 if isinstance(e, ValueError) else 500, str(e))
+        toks = list(req.output_token_ids or [])
+        text = tokenizer.decode(toks) if tokenizer is not None else None
+        return {"id": rid, "object": "text_completion", "created": int(t0), "model": model_name,
+                "choices": [{"index": 0, "text": text, "token_ids": toks,
+                             "finish_reason": _FINISH.get(req.status)}],
+                "usage": {"prompt_tokens": req.num_prompt_tokens, "completion_tokens": len(toks),
+                          "total_tokens": req.num_prompt_tokens + len(toks)},
+                "kv_transfer_params": req.kv_transfer_params}
+
+    return app
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--tokenizer", default=None)
+    ap.add_argument("--max-model-len", type=int, default=4096)
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--kv-transfer-config", default=None, help="JSON")
+    ap.add_argument("--additional-config", default=None, help="JSON")
+    ap.add_argument("--device", default=None)
+    args = ap.parse_args()
+    import json
+
+    import uvicorn
+
+    from ..engine.llm import LLM
+    llm = LLM(args.model, device=args.device, max_model_len=args.max_model_len, max_num_seqs=args.max_num_seqs,
+              kv_transfer_config=json.loads(args.kv_transfer_config) if args.kv_transfer_config else None,
+              additional_config=json.loads(args.additional_config) if args.additional_config else None)
+    tok = None
+    if args.tokenizer:
+        from transformers import AutoTokenizer
+        tok = AutoTokenizer.from_pretrained(args.tokenizer)
+    uvicorn.run(build_app(llm, tok, args.model), host=args.host, port=args.port, log_level="warning")
+
+
+if __name__ == "__main__":
+    main()
