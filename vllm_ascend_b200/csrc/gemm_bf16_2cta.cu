@@ -416,7 +416,7 @@ static int get_tmap_128x64(CUtensorMap* out, const void* ptr, uint64_t rows, uin
 
 using namespace b200;
 
-static int g_raster = 8;
+static int g_raster = 16;
 
 static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, int ldw, long a_rows,
                        cudaStream_t stream) {
