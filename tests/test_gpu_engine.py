@@ -75,3 +75,31 @@ def test_gpu_random_sampling_runs_and_is_seeded():
     a = [o.outputs[0].token_ids for o in gpu.generate(prompts, sp)]
     b = [o.outputs[0].token_ids for o in gpu.generate(prompts, sp)]
     assert a == b
+
+
+def test_sleep_mode_frees_memory_and_restores_weights():
+    """Level-1 sleep offloads weights to the host and drops the KV cache: device memory is
+    returned to the driver while asleep, and after wake-up the engine generates the same tokens."""
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (100, 37)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    llm = LLM(_cfg("bfloat16"), device="cuda", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=256,
+              num_gpu_blocks_override=40, enforce_eager=True, enable_sleep_mode=True)
+    first = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    torch.cuda.synchronize()
+    free_awake, _ = torch.cuda.mem_get_info()
+    llm.sleep(level=1)
+    free_asleep, _ = torch.cuda.mem_get_info()
+    assert llm.engine.sleep_level == 1
+    assert free_asleep - free_awake > 20 << 20, (free_awake, free_asleep)      # weights + KV left the device
+    llm.wake_up()
+    assert llm.engine.sleep_level == 0
+    second = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert second == first
+    # waking up in two stages: weights first (e.g. to receive an update), KV cache later
+    llm.sleep(level=1)
+    llm.wake_up(tags=["weights"])
+    assert llm.engine.sleep_level == 1
+    llm.wake_up(tags=["kv_cache"])
+    assert llm.engine.sleep_level == 0
+    assert [o.outputs[0].token_ids for o in llm.generate(prompts, sp)] == first

@@ -82,3 +82,66 @@ def test_fp8_experts_native_matches_reference():
     blk.w13, blk.w13_scale, blk.w2, blk.w2_scale = (t.cpu() for t in (blk.w13, blk.w13_scale, blk.w2, blk.w2_scale))
     exp = sch.apply_experts(xc, blk.w13, blk.w2, twc, idc, None)
     assert (got.float().cpu() - exp.float()).abs().max() < 0.04 * exp.float().abs().max() + 0.02
+
+
+@pytest.mark.parametrize("H,with_res", [(4096, True), (1024, False), (12288, True)])
+def test_fused_norm_quant_matches_unfused(H, with_res):
+    torch.manual_seed(0)
+    T = 77
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+    res = torch.randn(T, H, device=DEV).bfloat16() if with_res else None
+    r1 = res.clone() if with_res else None
+    r2 = res.clone() if with_res else None
+    y, ro = ops.rms_norm(x.clone(), w, 1e-6, r1)
+    q_ref, s_ref = ops.quant_fp8_group128(y)
+    qa, ro2 = ops.rms_norm_quant_fp8(x.clone(), w, 1e-6, r2)
+    torch.cuda.synchronize()
+    assert torch.equal(qa.scales, s_ref)
+    assert torch.equal(qa.q.view(torch.uint8), q_ref.view(torch.uint8))
+    if with_res:
+        assert torch.equal(ro2, ro)
+
+
+def test_fused_silu_mul_quant_matches_unfused():
+    torch.manual_seed(1)
+    T, I = 65, 3072
+    x = torch.randn(T, 2 * I, device=DEV).bfloat16()
+    q_ref, s_ref = ops.quant_fp8_group128(ops.silu_and_mul(x))
+    qa = ops.silu_and_mul_quant_fp8(x)
+    torch.cuda.synchronize()
+    # the two paths may round silu differently by one bf16 ulp: compare dequantised values
+    a = q_ref.float().view(T, I // 128, 128) * s_ref.unsqueeze(-1)
+    b = qa.q.float().view(T, I // 128, 128) * qa.scales.unsqueeze(-1)
+    assert (a - b).abs().max() <= 0.07 * a.abs().max()
+    assert (a - b).abs().mean() < 2e-3
+
+
+def test_fp8_model_uses_fused_producers_and_matches_unfused(monkeypatch):
+    """A dense model quantised to block fp8: generation with the fused norm/activation
+    producers equals generation with the separate quant kernel."""
+    import numpy as np
+    from vllm_ascend_b200.config import ModelConfig
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    from vllm_ascend_b200.models import layers
+
+    def cfg():
+        return ModelConfig(name="t8", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=512,
+                           intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                           num_key_value_heads=2, head_dim=128, qk_norm=True, rope_theta=1e6,
+                           dtype="bfloat16", init_std=0.05, quantization="fp8")
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (90, 33)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    kw = dict(device="cuda", max_model_len=256, max_num_seqs=4, max_num_batched_tokens=128,
+              num_gpu_blocks_override=16, enforce_eager=True)
+    c0 = ops.launch_counter[0]
+    fused = [o.outputs[0].token_ids for o in LLM(cfg(), **kw).generate(prompts, sp)]
+    n_fused = ops.launch_counter[0] - c0
+    monkeypatch.setattr(layers, "wants_quant_act", lambda linear: False)
+    c0 = ops.launch_counter[0]
+    plain = [o.outputs[0].token_ids for o in LLM(cfg(), **kw).generate(prompts, sp)]
+    n_plain = ops.launch_counter[0] - c0
+    assert fused == plain
+    assert n_fused < n_plain          # fewer launches: the quant passes disappeared

@@ -111,6 +111,8 @@ class Linear:
         if self.quant is not None:
             y = self.quant.apply(self, x, residual)
         else:
+            if isinstance(x, ops.QuantAct):
+                x = x.dequant()
             y = ops.linear(x, self.weight, self.bias, residual)
         if self._lora_on():
             y = self.lora.apply(x, y)
@@ -181,8 +183,19 @@ class RMSNorm:
         self.eps = eps
         self.gemma = gemma
 
-    def __call__(self, x, residual=None):
+    def __call__(self, x, residual=None, quant_out: bool = False):
+        """With ``quant_out`` the normalised activations come back as block-scaled fp8
+        (``ops.QuantAct``) from one fused kernel, for a consumer that is an fp8 GEMM."""
+        if quant_out:
+            return ops.rms_norm_quant_fp8(x, self.weight, self.eps, residual, self.gemma)
         return ops.rms_norm(x, self.weight, self.eps, residual, self.gemma)
+
+
+def wants_quant_act(linear) -> bool:
+    """True when ``linear`` can consume fp8 activations produced by a fused kernel."""
+    q = getattr(linear, "quant", None)
+    return bool(q is not None and getattr(q, "accepts_quant_act", False) and linear.weight.is_cuda
+                and getattr(linear, "lora", None) is None)
 
 
 class VocabParallelEmbedding:
@@ -316,4 +329,6 @@ class SwiGLUMLP:
         gu = self.gate_up_proj
         if gu.quant is None and gu.bias is None and not gu.gather_output and not gu._lora_on():
             return self.down_proj(ops.linear_swiglu(x, gu.weight))
+        if wants_quant_act(self.down_proj):
+            return self.down_proj(ops.silu_and_mul_quant_fp8(gu(x)))
         return self.down_proj(ops.silu_and_mul(gu(x)))

@@ -228,15 +228,29 @@ class DecoderLayer:
             self.mlp = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm)
 
     def __call__(self, h, residual, meta, kv_cache):
+        # a norm whose only consumer is an fp8 GEMM emits fp8 + scales directly
+        qa = self._attn_in_fp8
         if residual is None:
             residual = h
-            x, _ = self.input_layernorm(h)
+            x, _ = self.input_layernorm(h, quant_out=qa)
         else:
-            x, residual = self.input_layernorm(h, residual)
+            x, residual = self.input_layernorm(h, residual, quant_out=qa)
         h = self.self_attn(x, meta, kv_cache)
-        x, residual = self.post_attention_layernorm(h, residual)
+        x, residual = self.post_attention_layernorm(h, residual, quant_out=self._mlp_in_fp8)
         h = self.mlp(x)
         return h, residual
+
+    @property
+    def _attn_in_fp8(self) -> bool:
+        from .layers import wants_quant_act
+        a = self.self_attn
+        return hasattr(a, "qkv_proj") and wants_quant_act(a.qkv_proj)
+
+    @property
+    def _mlp_in_fp8(self) -> bool:
+        from .layers import SwiGLUMLP, wants_quant_act
+        m = self.mlp
+        return isinstance(m, SwiGLUMLP) and wants_quant_act(m.gate_up_proj)
 
 
 class CausalLM:

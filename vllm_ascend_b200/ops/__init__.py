@@ -435,3 +435,53 @@ def quant_fp8_group128(x: torch.Tensor, pow2_scale: bool = False):
     _native.check(rc, "quant_fp8_group128")
     launch_counter[0] += 1
     return q, s
+
+
+class QuantAct:
+    """A block-scaled fp8 activation: values [T, H] e4m3 and scales [T, H / 128] fp32, produced by
+    a fused norm / activation kernel and consumed by the fp8 GEMM without an extra quant pass."""
+    __slots__ = ("q", "scales", "shape", "dtype")
+
+    def __init__(self, q: torch.Tensor, scales: torch.Tensor, dtype=torch.bfloat16):
+        self.q, self.scales, self.shape, self.dtype = q, scales, q.shape, dtype
+
+    def dequant(self) -> torch.Tensor:
+        T, H = self.q.shape
+        return (self.q.float().view(T, H // 128, 128) * self.scales.unsqueeze(-1)).view(T, H).to(self.dtype)
+
+
+def rms_norm_quant_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float,
+                       residual: Optional[torch.Tensor] = None, gemma: bool = False):
+    """Fused (add +) RMSNorm + 1x128 fp8 quantisation.  Returns (QuantAct, residual_out)."""
+    H = x.shape[-1]
+    if not _use_native(x) or H % 128:
+        y, res = rms_norm(x, weight, eps, residual, gemma)
+        return QuantAct(*quant_fp8_group128(y.reshape(-1, H)), dtype=x.dtype), res
+    x2 = x.reshape(-1, H) if x.stride(-1) == 1 else x.contiguous().view(-1, H)
+    T = x2.shape[0]
+    q = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((T, H // 128), dtype=torch.float32, device=x.device)
+    if residual is not None:
+        assert residual.is_contiguous()
+    rc = _native.lib().b200_rms_norm_quant_fp8(x2.data_ptr(), _native.ptr(residual), weight.data_ptr(), q.data_ptr(),
+                                               s.data_ptr(), T, H, eps, int(gemma), x2.stride(0), _native.stream_ptr())
+    _native.check(rc, "rms_norm_quant_fp8")
+    launch_counter[0] += 1
+    return QuantAct(q, s, x.dtype), (residual if residual is not None else x)
+
+
+def silu_and_mul_quant_fp8(x: torch.Tensor, limit: float = 0.0) -> QuantAct:
+    """Fused SiLU(gate) * up + 1x128 fp8 quantisation of [T, 2I] -> QuantAct [T, I]."""
+    I = x.shape[-1] // 2
+    if not _use_native(x) or I % 128 or not x.is_contiguous():
+        y = silu_and_mul(x) if limit <= 0 else ref.silu_and_mul(x, limit)
+        return QuantAct(*quant_fp8_group128(y.reshape(-1, I)), dtype=x.dtype)
+    x2 = x.view(-1, 2 * I)
+    T = x2.shape[0]
+    q = torch.empty((T, I), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((T, I // 128), dtype=torch.float32, device=x.device)
+    rc = _native.lib().b200_silu_mul_quant_fp8(x2.data_ptr(), q.data_ptr(), s.data_ptr(), T, I, limit,
+                                               _native.stream_ptr())
+    _native.check(rc, "silu_mul_quant_fp8")
+    launch_counter[0] += 1
+    return QuantAct(q, s, x.dtype)

@@ -77,8 +77,19 @@ class Fp8BlockLinear(LinearScheme):
     def named_tensors(self, layer):
         yield "weight_scale_inv", layer.weight_scale_inv
 
+    accepts_quant_act = True       # a fused norm / activation kernel may hand over fp8 directly
+
     def apply(self, layer, x, residual=None, skip_bias=False):
         bias = None if skip_bias else layer.bias
+        if isinstance(x, ops.QuantAct):
+            N = layer.weight.shape[0]
+            if x.q.is_cuda and N % 8 == 0:
+                y = fp8_block_linear(None, layer.weight, layer.weight_scale_inv, bias, quant=(x.q, x.scales))
+            else:
+                y = ref.block_fp8_linear(x.dequant(), layer.weight, layer.weight_scale_inv, self.block, x.dtype)
+                if bias is not None:
+                    y = y + bias
+            return y + residual if residual is not None else y
         K = x.shape[-1]
         N = layer.weight.shape[0]
         x2 = x.reshape(-1, K)
@@ -107,19 +118,22 @@ def _declare_native():
 _declare_native()
 
 
-def fp8_block_linear(x: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
-                     bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+def fp8_block_linear(x: Optional[torch.Tensor], w8: torch.Tensor, w_scale: torch.Tensor,
+                     bias: Optional[torch.Tensor] = None, quant: Optional[tuple] = None) -> torch.Tensor:
     """bf16 activations [M,K] -> dynamic 1x128 e4m3 quantisation -> block-scaled GEMM."""
-    M, K = x.shape
+    if quant is not None:
+        xq, xs = quant
+    else:
+        xq, xs = ops.quant_fp8_group128(x if x.is_contiguous() else x.contiguous())
+    M, K = xq.shape
     N = w8.shape[0]
-    xq, xs = ops.quant_fp8_group128(x if x.is_contiguous() else x.contiguous())
-    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
     if M == 0:
         return out
     rc = _native.lib().b200_gemm_fp8_block(
         xq.data_ptr(), xs.data_ptr(), w8.data_ptr(), w_scale.data_ptr(), out.data_ptr(),
         _native.ptr(bias), M, N, K, xq.stride(0), w8.stride(0), out.stride(0),
-        _native.status_word(x.device).data_ptr(), _native.stream_ptr())
+        _native.status_word(xq.device).data_ptr(), _native.stream_ptr())
     _native.check(rc, "gemm_fp8_block")
     ops.launch_counter[0] += 1
     return out
