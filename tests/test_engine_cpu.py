@@ -198,3 +198,20 @@ def test_async_scheduling_matches_synchronous_engine(prefix_caching):
     # random sampling with a seed runs through the same path
     sp = SamplingParams(max_tokens=6, temperature=0.9, top_k=50, seed=11, ignore_eos=True)
     assert len(llm.generate(prompts[:2], sp)[1].outputs[0].token_ids) == 6
+
+
+def test_weight_offload_with_prefetch_keeps_outputs():
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=96, max_num_seqs=4)
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(1, 500, size=n).tolist() for n in (30, 11)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM("tiny-qwen", **kw).generate(prompts, sp)]
+    llm = LLM("tiny-qwen", additional_config={"weight_offload_config": {
+        "enabled": True, "group_size": 2, "num_in_group": 1, "prefetch_step": 1}}, **kw)
+    off = llm.engine.worker.offloader
+    assert off is not None and off.bytes_offloaded > 0 and len(off.layers) >= 1
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    assert off.stats["prefetches"] >= len(off.layers) * 6
+    from vllm_ascend_b200.platform_config import clear_b200_config
+    clear_b200_config()

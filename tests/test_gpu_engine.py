@@ -103,3 +103,24 @@ def test_sleep_mode_frees_memory_and_restores_weights():
     llm.wake_up(tags=["kv_cache"])
     assert llm.engine.sleep_level == 0
     assert [o.outputs[0].token_ids for o in llm.generate(prompts, sp)] == first
+
+
+def test_weight_offload_prefetch_on_gpu():
+    from vllm_ascend_b200.platform_config import clear_b200_config
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (120, 45)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    kw = dict(device="cuda", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=256,
+              num_gpu_blocks_override=40)
+    want = [o.outputs[0].token_ids for o in LLM(_cfg("bfloat16"), enforce_eager=True, **kw).generate(prompts, sp)]
+    llm = LLM(_cfg("bfloat16"), additional_config={"weight_offload_config": {
+        "enabled": True, "group_size": 1, "num_in_group": 1, "prefetch_step": 2}}, **kw)
+    try:
+        off = llm.engine.worker.offloader
+        assert off is not None and len(off.layers) == 3 and off.num_slots == 3
+        got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        assert got == want
+        assert llm.engine.runner.stats["graph_replays"] == 0
+        assert off.stats["bytes"] > 0
+    finally:
+        clear_b200_config()

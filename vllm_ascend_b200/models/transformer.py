@@ -298,7 +298,8 @@ class CausalLM:
         else:
             h, residual = intermediate
         for layer, cache in zip(self.layers, kv_caches):
-            h, residual = layer(h, residual, meta, cache)
+            call = getattr(layer, "offloaded_call", None)      # set by the weight offloader
+            h, residual = call(h, residual, meta, cache) if call is not None else layer(h, residual, meta, cache)
         if not self.is_last:
             return h, residual
         h, _ = self.norm(h, residual)

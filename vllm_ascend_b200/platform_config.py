@@ -137,6 +137,16 @@ class RlConfig:
 
 
 @dataclass
+class WeightOffloadConfig:
+    """Layers i with i % group_size < num_in_group keep their weights on the host and are
+    prefetched ``prefetch_step`` layers ahead."""
+    enabled: bool = False
+    group_size: int = 2
+    num_in_group: int = 1
+    prefetch_step: int = 1
+
+
+@dataclass
 class B200Config:
     finegrained_tp_config: FinegrainedTPConfig = field(default_factory=FinegrainedTPConfig)
     fusion_config: FusionConfig = field(default_factory=FusionConfig)
@@ -145,6 +155,7 @@ class B200Config:
     rejection_sampler_config: RejectionSamplerConfig = field(default_factory=RejectionSamplerConfig)
     dynamic_spec_config: DynamicSpecConfig = field(default_factory=DynamicSpecConfig)
     rl_config: RlConfig = field(default_factory=RlConfig)
+    weight_offload_config: WeightOffloadConfig = field(default_factory=WeightOffloadConfig)
     enable_shared_expert_dp: bool = False
     multistream_overlap_shared_expert: bool = False
     enable_prefill_fused_moe: bool = False       # reference: enable_prefill_mc2
@@ -301,6 +312,8 @@ def check_and_update_config(engine_cfg) -> B200Config:
     _validate_finegrained(cfg, pc.tensor_parallel_size, max(1, pc.data_parallel_size))
     _validate_eplb(cfg.eplb_config, mc.is_moe, pc.enable_expert_parallel)
     _validate_scheduler_ext(cfg.scheduler_config, engine_cfg)
+    if cfg.weight_offload_config.enabled:
+        cc.cudagraph_mode = "NONE"        # offloaded weights rotate through device buffers
     # 4 graph mode normalisation + capture sizes (platform.py:937-1117, 1275-1309)
     cc.cudagraph_mode = cc.cudagraph_mode.upper()
     if cc.cudagraph_mode not in GRAPH_MODES:

@@ -34,6 +34,7 @@ class B200Worker:
         self._weight_update_state = "idle"
         self._profiler = None
         self._mem_before_load = 0
+        self.offloader = None
 
     # ------------------------------------------------------------------ device / groups
     def init_device(self) -> None:
@@ -90,6 +91,11 @@ class B200Worker:
             self.runner.load_model(moe_runtime=self.moe_runtime)
         if cfg.enable_lora:
             self.runner.init_lora()
+        from ..platform_config import get_b200_config
+        oc = get_b200_config().weight_offload_config
+        if oc.enabled:
+            from ..offloader import PrefetchOffloader
+            self.offloader = PrefetchOffloader(self.runner.model, oc.group_size, oc.num_in_group, oc.prefetch_step)
         # the fused sequence-sharded TP path has no adapter hook: LoRA engines use the NCCL path
         if self.world_size > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM == "fused" \
                 and pc.tensor_parallel_size > 1 and not cfg.enable_lora:
