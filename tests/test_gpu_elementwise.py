@@ -84,3 +84,25 @@ def test_quant_fp8_group128():
     assert torch.allclose(s, es, rtol=1e-5)
     deq = q.float().view(65, 8, 128) * s.unsqueeze(-1)
     assert torch.allclose(deq.view(65, 1024), x.float(), atol=0.2, rtol=0.07)
+
+
+@pytest.mark.parametrize("kind,gated", [("gelu", True), ("gelu_tanh", True), ("quick_gelu", False), ("gelu", False),
+                                        ("swiglu_oai", True)])
+def test_activation_family(kind, gated):
+    torch.manual_seed(0)
+    x = (torch.randn(33, 2048, device=DEV) * 2).bfloat16()
+    got = ops.activation(x, kind, gated)
+    want = ref.activation(x.float(), kind, gated)
+    assert got.shape == want.shape
+    assert torch.allclose(got.float(), want, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("group,before", [(0, True), (128, True), (128, False)])
+def test_rms_norm_gated(group, before):
+    torch.manual_seed(1)
+    x = torch.randn(19, 1024, device=DEV).bfloat16()
+    z = torch.randn(19, 1024, device=DEV).bfloat16()
+    w = (1 + 0.1 * torch.randn(group or 1024, device=DEV)).bfloat16()
+    got = ops.rms_norm_gated(x, z, w, 1e-6, group, before)
+    want = ref.rms_norm_gated(x.float(), z.float(), w.float(), 1e-6, group, before)
+    assert torch.allclose(got.float(), want, atol=4e-2, rtol=3e-2)

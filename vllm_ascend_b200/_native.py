@@ -30,6 +30,8 @@ _SIGNATURES = {
     "b200_embedding": [P, P, P, L, I, L, L, P],
     "b200_qknorm_rope_kvwrite": [P, L, P, P, I, P, P, F, P, P, P, I, I, I, I, L, I, I, P, P],
     "b200_quant_fp8_group128": [P, P, P, L, I, I, P],
+    "b200_activation": [P, P, L, I, I, I, F, F, P],
+    "b200_rms_norm_gated": [P, P, P, P, L, I, F, I, P],
     "b200_rms_norm_quant_fp8": [P, P, P, P, P, L, I, F, I, L, P],
     "b200_silu_mul_quant_fp8": [P, P, P, L, I, F, P],
     "b200_paged_decode": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, I, P, L, P, L, P, P],

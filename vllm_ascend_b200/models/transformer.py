@@ -66,13 +66,21 @@ class SparseMoeBlock:
             self.shared = SwiGLUMLP(pf, f"{prefix}.shared_experts", H, I * cfg.n_shared_experts,
                                     comm, reduce_results=False)
         # logical -> physical redirect for redundant experts (EPLB); identity by default
+        self._gate_bf16: Optional[torch.Tensor] = None
         self.log2phy: Optional[torch.Tensor] = None          # [E, max_replicas] physical slot ids
         self.log2phy_count: Optional[torch.Tensor] = None    # [E] replicas per expert
         self.expert_load: Optional[torch.Tensor] = None      # per-physical-expert hit counter
 
     def route(self, x: torch.Tensor):
         cfg = self.cfg
-        logits = torch.nn.functional.linear(x.float(), self.gate_weight)
+        if x.is_cuda and x.dtype == torch.bfloat16 and cfg.scoring_func == "softmax" and not cfg.use_mla:
+            # softmax routers of bf16 checkpoints run their gate in the model dtype (as the
+            # original implementation does): one tensor-core GEMM instead of an fp32 SIMT one
+            if self._gate_bf16 is None:
+                self._gate_bf16 = self.gate_weight.to(torch.bfloat16)
+            logits = ops.linear(x, self._gate_bf16).float()
+        else:
+            logits = torch.nn.functional.linear(x.float(), self.gate_weight)
         w, ids = fused_moe.gating_topk(logits, cfg.num_experts_per_tok, cfg.scoring_func,
                                        cfg.norm_topk_prob, cfg.n_group, cfg.topk_group,
                                        self.e_bias, cfg.routed_scaling_factor)
@@ -413,6 +421,9 @@ class CausalLM:
         for L in self.layers:
             if isinstance(L.self_attn, MLAAttention):
                 L.self_attn.process_weights_after_loading()
+        for L in self.layers:                  # derived copies follow the new values
+            if hasattr(L.mlp, "_gate_bf16"):
+                L.mlp._gate_bf16 = None
         return loaded
 
     def _copy_shard(self, target: str, dst: torch.Tensor, w: torch.Tensor, shard_id, tp: int, r: int):

@@ -485,3 +485,36 @@ def silu_and_mul_quant_fp8(x: torch.Tensor, limit: float = 0.0) -> QuantAct:
     _native.check(rc, "silu_mul_quant_fp8")
     launch_counter[0] += 1
     return QuantAct(q, s, x.dtype)
+
+
+_ACT_KINDS = {"gelu": 1, "gelu_tanh": 2, "quick_gelu": 3, "swiglu_oai": 4}
+
+
+def activation(x: torch.Tensor, kind: str, gated: bool = False, alpha: float = 1.702, limit: float = 7.0):
+    """GELU (erf / tanh), QuickGELU, and the clamped "swiglu-oai" gate; ``gated`` inputs are [gate | up]."""
+    I = x.shape[-1] // 2 if gated else x.shape[-1]
+    if not _use_native(x) or I % 8 or not x.is_contiguous():
+        return ref.activation(x, kind, gated, alpha, limit)
+    x2 = x.view(-1, x.shape[-1])
+    out = torch.empty((x2.shape[0], I), dtype=x.dtype, device=x.device)
+    rc = _native.lib().b200_activation(x2.data_ptr(), out.data_ptr(), x2.shape[0], I, _ACT_KINDS[kind], int(gated),
+                                       alpha, limit, _native.stream_ptr())
+    _native.check(rc, "activation")
+    launch_counter[0] += 1
+    return out.view(*x.shape[:-1], I)
+
+
+def rms_norm_gated(x: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, group: int = 0,
+                   norm_before_gate: bool = True) -> torch.Tensor:
+    """Gated RMSNorm of linear-attention blocks: rmsnorm(x) * w * silu(z), per ``group`` columns."""
+    H = x.shape[-1]
+    g = group or H
+    if not _use_native(x) or not (x.is_contiguous() and z.is_contiguous()) or H % g:
+        return ref.rms_norm_gated(x, z, weight, eps, group, norm_before_gate)
+    out = torch.empty_like(x)
+    rows = x.numel() // g
+    rc = _native.lib().b200_rms_norm_gated(x.data_ptr(), z.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, g,
+                                           eps, int(norm_before_gate), _native.stream_ptr())
+    _native.check(rc, "rms_norm_gated")
+    launch_counter[0] += 1
+    return out

@@ -83,3 +83,13 @@ def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, quant=None):
     if quant is not None:
         return quant.apply_experts(x, w13, w2, topk_w, topk_ids, expert_map)
     return fused_experts_ref(x, w13, w2, topk_w, topk_ids, expert_map)
+
+
+def hash_topk(token_ids: torch.Tensor, table: torch.Tensor):
+    """Hash routing: the experts of a token are a fixed function of its token id
+    (``table`` [vocab, k] of expert ids), all with equal weight — the router of the first
+    layers of some models (vllm_ascend/ops/fused_moe/router/fused_topk_router.py:103-141)."""
+    ids = table[token_ids.long()].to(torch.int32)
+    k = ids.shape[1]
+    w = torch.full(ids.shape, 1.0 / k, dtype=torch.float32, device=ids.device)
+    return w, ids

@@ -312,3 +312,41 @@ def block_fp8_linear(x: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, bl
     xd = xq.float() * xs.repeat_interleave(128, dim=1)[:, :K]
     wd = dequant_block_fp8_weight(w, w_scale, block)
     return (xd @ wd.t()).to(out_dtype)
+
+
+# ---------------------------------------------------------------- more activations / gated norm
+def activation(x: torch.Tensor, kind: str, gated: bool = False, alpha: float = 1.702, limit: float = 7.0):
+    """kind: gelu | gelu_tanh | quick_gelu | swiglu_oai.  gated: x = [gate | up]."""
+    if gated:
+        d = x.shape[-1] // 2
+        g, u = x[..., :d].float(), x[..., d:].float()
+    else:
+        g, u = x.float(), None
+    if kind == "swiglu_oai":
+        g = g.clamp(max=limit)
+        u = u.clamp(min=-limit, max=limit)
+        return (g * torch.sigmoid(alpha * g) * (u + 1)).to(x.dtype)
+    if kind == "gelu":
+        y = F.gelu(g)
+    elif kind == "gelu_tanh":
+        y = F.gelu(g, approximate="tanh")
+    elif kind == "quick_gelu":
+        y = g * torch.sigmoid(1.702 * g)
+    else:
+        raise ValueError(f"unknown activation {kind!r}")
+    return (y * u if u is not None else y).to(x.dtype)
+
+
+def rms_norm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, group: int = 0,
+                   norm_before_gate: bool = True) -> torch.Tensor:
+    """rmsnorm(x) * w * silu(z) (or rmsnorm(x * silu(z)) * w), optionally per group of columns."""
+    H = x.shape[-1]
+    g = group or H
+    xf, zf = x.float().reshape(-1, g), z.float().reshape(-1, g)
+    gate = F.silu(zf)
+    if not norm_before_gate:
+        xf = xf * gate
+    y = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * w.float()[:g]
+    if norm_before_gate:
+        y = y * gate
+    return y.reshape(x.shape).to(x.dtype)

@@ -26,6 +26,8 @@ class LinearMethod:
 
     def __init__(self, scheme):
         self.scheme = scheme
+        # whether fused producers may hand this layer block-scaled fp8 activations
+        self.accepts_quant_act = bool(getattr(scheme, "accepts_quant_act", False))
 
     def apply(self, layer, x, residual=None, skip_bias=False):
         return self.scheme.apply(layer, x, residual, skip_bias)
