@@ -121,7 +121,7 @@ def test_engine_speculative_random_sampling_runs_and_respects_max_tokens():
     assert all(len(o.outputs[0].token_ids) == 17 for o in outs)
 
 
-@pytest.mark.parametrize("method", ["draft_model", "eagle"])
+@pytest.mark.parametrize("method", ["draft_model", "eagle", "medusa"])
 def test_engine_model_based_proposers_keep_greedy_output(method):
     kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=40)
     rng = np.random.default_rng(1)

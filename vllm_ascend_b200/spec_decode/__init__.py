@@ -15,4 +15,7 @@ def get_spec_decode_method(spec_cfg: dict, runner):
     if method in ("draft_model", "eagle", "eagle3", "mtp"):
         from .draft_model import DraftModelProposer
         return DraftModelProposer(method, k, spec_cfg, runner)
+    if method == "medusa":
+        from .medusa import MedusaProposer
+        return MedusaProposer(k, spec_cfg, runner)
     raise ValueError(f"unknown speculative method {method!r}")
