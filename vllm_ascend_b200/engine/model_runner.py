@@ -97,6 +97,7 @@ class ModelRunner:
         self.graphs: dict[tuple, object] = {}     # (capture size, has_lora) -> BatchDescriptor
         self.graph_wrapper = None
         self.lora_manager = None
+        self.moe_runtime = None
         from ..parallel import state as _ps
         self.pp = _ps.get_pp_group()
         dcp = _ps.get_dcp_group()
@@ -121,6 +122,7 @@ class ModelRunner:
     def load_model(self, moe_runtime=None) -> None:
         from ..models import build_model
         t0 = time.time()
+        self.moe_runtime = moe_runtime
         self.model = build_model(self.cfg, self.device, moe_runtime=moe_runtime)
         from ..model_loader import get_model_loader
         from ..parallel import state as pstate
@@ -394,6 +396,8 @@ class ModelRunner:
     def _graph_size_for(self, B: int) -> Optional[int]:
         if not self.capture_sizes or B > self.capture_sizes[-1]:
             return None
+        if self.moe_runtime is not None and not self.moe_runtime.graph_safe(B):
+            return None          # some DP rank has too many tokens for the fused MoE path this step
         for s in self.capture_sizes:
             if s >= B:
                 return s
@@ -719,6 +723,12 @@ class ModelRunner:
         max_size = cc.max_cudagraph_capture_size or min(self.max_seqs, 1024)
         sizes = cc.cudagraph_capture_sizes or default_capture_sizes(max_size)
         self.capture_sizes = sorted(set(int(s) for s in sizes if s <= self.max_seqs))
+        if self.moe_runtime is not None:
+            # expert-parallel steps are only capturable on the fused dispatch/combine path
+            self.moe_runtime.max_tokens_across_dp = 0
+            self.capture_sizes = [s for s in self.capture_sizes if self.moe_runtime.graph_safe(s)]
+            if not self.capture_sizes:
+                return
         # scratch for split-KV partials must exist before capture
         if not self.mcfg.use_mla:
             a = self.model.layers[0].self_attn

@@ -64,10 +64,23 @@ class MoERuntime:
         self.last_method: Optional[MoECommType] = None
         self.counts = {t: 0 for t in MoECommType}
 
+    def select(self, num_tokens: int, is_cuda: bool = True) -> MoECommType:
+        """The method every EP rank uses this step (same inputs on every rank: the largest token
+        count over the DP ranks, agreed by the engine before the forward pass)."""
+        n_max = max(self.max_tokens_across_dp, num_tokens)
+        return select_moe_comm_method(n_max, self.ep.world_size, self.fused is not None,
+                                      self.capacity, is_cuda, envs.VLLM_B200_MOE_COMM)
+
+    def graph_safe(self, num_tokens: int) -> bool:
+        """Only the fused path has no host synchronisation and can live in a captured graph."""
+        return self.select(num_tokens) == MoECommType.FUSED
+
     def forward(self, block, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         n_max = max(self.max_tokens_across_dp, x.shape[0])
-        method = select_moe_comm_method(n_max, self.ep.world_size, self.fused is not None,
-                                        self.capacity, x.is_cuda, envs.VLLM_B200_MOE_COMM)
+        method = self.select(x.shape[0], x.is_cuda)
+        if torch.cuda.is_current_stream_capturing() and method != MoECommType.FUSED:
+            raise RuntimeError(f"MoE path {method.name} cannot be captured into a CUDA graph "
+                               f"({x.shape[0]} tokens, fused capacity {self.capacity})")
         self.last_method = method
         self.counts[method] += 1
         if method == MoECommType.FUSED and self.fused is not None:
