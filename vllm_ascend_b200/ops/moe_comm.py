@@ -78,7 +78,7 @@ class MoERuntime:
     def forward(self, block, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         n_max = max(self.max_tokens_across_dp, x.shape[0])
         method = self.select(x.shape[0], x.is_cuda)
-        if torch.cuda.is_current_stream_capturing() and method != MoECommType.FUSED:
+        if x.is_cuda and method != MoECommType.FUSED and torch.cuda.is_current_stream_capturing():
             raise RuntimeError(f"MoE path {method.name} cannot be captured into a CUDA graph "
                                f"({x.shape[0]} tokens, fused capacity {self.capacity})")
         self.last_method = method
