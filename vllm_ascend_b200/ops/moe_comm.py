@@ -53,12 +53,23 @@ class MoERuntime:
         self.ep = pstate.get_ep_group()
         self.b200 = get_b200_config()
         self.capacity = self.b200.fused_moe_max_tokens
+        if self.b200.enable_prefill_fused_moe:
+            # prefill-sized steps stay on the fused path too when its pools fit comfortably
+            # (the reference caps its device-initiated path at 512 tokens per rank; with 180 GB
+            # per GPU the packed pools of a full step are affordable here)
+            m = engine_cfg.model
+            want = engine_cfg.scheduler.max_num_batched_tokens + engine_cfg.scheduler.max_num_seqs
+            rows = self.ep.world_size * want * m.num_experts_per_tok
+            pool_bytes = rows * (m.hidden_size + m.moe_intermediate_size) * 2 + \
+                want * m.num_experts_per_tok * m.hidden_size * 2
+            if pool_bytes <= int(self.b200.fused_moe_pool_limit_gb * (1 << 30)):
+                self.capacity = max(self.capacity, want)
         self.max_tokens_across_dp = 0          # set per step by the engine's DP sync
         self.fused = None
         if device.type == "cuda" and self.b200.enable_fused_moe_comm and self.ep.world_size > 1:
             try:
                 from .moe_fused import FusedMoEComm
-                self.fused = FusedMoEComm(engine_cfg, device, self.ep)
+                self.fused = FusedMoEComm(engine_cfg, device, self.ep, capacity=self.capacity)
             except ImportError:
                 self.fused = None
         self.last_method: Optional[MoECommType] = None

@@ -158,7 +158,8 @@ class B200Config:
     weight_offload_config: WeightOffloadConfig = field(default_factory=WeightOffloadConfig)
     enable_shared_expert_dp: bool = False
     multistream_overlap_shared_expert: bool = False
-    enable_prefill_fused_moe: bool = False       # reference: enable_prefill_mc2
+    enable_prefill_fused_moe: bool = True        # reference: enable_prefill_mc2
+    fused_moe_pool_limit_gb: float = 12.0        # largest packed receive/combine pools the fused path may allocate
     enable_fused_moe_comm: bool = True           # reference: enable_fused_mc2
     fused_moe_max_tokens: int = 512              # reference: mega_moe_max_tokens / MC2 capacity
     enable_mlapo: bool = True
