@@ -14,10 +14,12 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def _cfg():
     from vllm_ascend_b200.config import ModelConfig
-    return ModelConfig(name="t", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=512,
-                       intermediate_size=1024, num_hidden_layers=3, num_attention_heads=8,
-                       num_key_value_heads=2, head_dim=128, qk_norm=True, rope_theta=1e6,
-                       dtype="bfloat16", init_std=0.05)
+    # WIDE=1: enough heads for 8-way tensor parallelism
+    wide = os.environ.get("WIDE", "0") == "1"
+    return ModelConfig(name="t", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=1024 if wide else 512,
+                       intermediate_size=2048 if wide else 1024, num_hidden_layers=3,
+                       num_attention_heads=16 if wide else 8, num_key_value_heads=8 if wide else 2, head_dim=128,
+                       qk_norm=True, rope_theta=1e6, dtype="bfloat16", init_std=0.05)
 
 
 def tp_generate():
