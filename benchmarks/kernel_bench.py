@@ -82,6 +82,25 @@ def bench_gemm(a):
     print(line, flush=True)
 
 
+def bench_gemm_fp8(a):
+    """Block-scaled fp8 GEMM (1x128 activation scales, 128x128 weight scales) incl. and excl. the
+    activation quantisation pass."""
+    from vllm_ascend_b200.quantization import schemes
+    M, N, K = a.m, a.n, a.k
+    x = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    w8, ws = schemes.quantize_weight_block_fp8(w)
+    xq, xs = ops.quant_fp8_group128(x)
+    ms_all = timeit(lambda: schemes.fp8_block_linear(x, w8, ws), a.iters)
+    ms_gemm = timeit(lambda: schemes.fp8_block_linear(None, w8, ws, quant=(xq, xs)), a.iters)
+    hbm, tf, tag = peaks()
+    fl = 2.0 * M * N * K
+    print(f"gemm-fp8 M={M} N={N} K={K}: quant+gemm {ms_all:.4f} ms {fl / ms_all / 1e9:.0f} TFLOP/s | gemm only "
+          f"{ms_gemm:.4f} ms {fl / ms_gemm / 1e9:.0f} TFLOP/s ({fl / ms_gemm / 1e9 / tf:.2f} of the bf16 {tag} peak)",
+          flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
 def bench_attn_decode(a):
     from gpu_utils import make_paged_case
     B, ctx = a.batch, a.ctx
@@ -170,7 +189,7 @@ def bench_norm(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "mla-decode", "norm", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm-fp8", "attn-decode", "attn-prefill", "mla-decode", "norm", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -220,6 +239,8 @@ def main():
         else:
             a.ctx = 0 if a.ctx == 1152 else a.ctx
             bench_attn_prefill(a)
+    if a.what == "gemm-fp8":
+        bench_gemm_fp8(a)
     if a.what == "mla-decode":
         bench_mla_decode(a)
     if a.what in ("norm", "all"):
