@@ -144,3 +144,40 @@ def test_cpu_offload_connector_on_gpu():
     assert c.stats["loaded_blocks"] == sum((len(p) - 1) // 128 for p in prompts) > 0
     assert llm.engine.scheduler.pool.num_free_blocks == free
     _native.check_status(torch.device("cuda"))
+
+
+def test_layerwise_push_same_gpu():
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import kv_transfer_worker as w
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    mono = w._llm(None, "M")
+    want = [o.outputs[0].token_ids for o in mono.generate(w._prompts(), sp)]
+
+    def mk(role, eid):
+        return LLM(w._cfg(), device="cuda", seed=0, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=256,
+                   num_gpu_blocks_override=40, enforce_eager=True,
+                   kv_transfer_config={"kv_connector": "LayerwiseConnector", "kv_role": role, "engine_id": eid})
+    pre, dec = mk("kv_producer", "PLg"), mk("kv_consumer", "DLg")
+    try:
+        dc = dec.engine.kv_connector
+        rids = [dec.engine.add_request(p, sp, kv_transfer_params={"do_remote_prefill": True, "layerwise": True,
+                                                                   "key": f"k{i}"})
+                for i, p in enumerate(w._prompts())]
+        dec.engine.step()
+        reqs = {r: dec.engine.scheduler.requests[r] for r in rids}
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {
+            "do_remote_decode": True, "layerwise": True,
+            "push_to": {"engine_id": "DLg", "host": "127.0.0.1", "port": dc.base_port, "key": f"k{i}"}}}
+            for i, p in enumerate(w._prompts())], sp1)
+        assert pre.engine.kv_connector.stats["pushed_requests"] == 5
+        while dec.engine.has_unfinished():
+            dec.engine.step()
+        got = [reqs[r].output_token_ids for r in rids]
+        assert [g[0] for g in got] == [x[0] for x in want]
+        agree = sum(a == b for x, y in zip(got, want) for a, b in zip(x, y)) / sum(len(x) for x in want)
+        assert agree > 0.8, (got, want)
+        _native.check_status(torch.device("cuda"))
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()

@@ -256,3 +256,44 @@ def test_kv_pool_shares_prefixes_between_engines():
         small.close()
     finally:
         store.close()
+
+
+def test_layerwise_push_connector():
+    """The decode engine allocates first and waits; the prefill engine pushes every layer's KV
+    into the decode cache while it prefills (chunked), then signals completion."""
+    from vllm_ascend_b200.distributed.kv_transfer.nvlink_connector import _LOCAL_ENGINES
+    prompts = _prompts(3, lo=40, hi=90, seed=13)
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    mono = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=8)
+    want = [o.outputs[0].token_ids for o in mono.generate(prompts, sp)]
+
+    def mk(role, eid):
+        return LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=8,
+                   max_num_batched_tokens=32,        # several prefill chunks per prompt
+                   kv_transfer_config={"kv_connector": "LayerwiseConnector", "kv_role": role, "engine_id": eid})
+    pre, dec = mk("kv_producer", "PL"), mk("kv_consumer", "DL")
+    try:
+        dc, pc = dec.engine.kv_connector, pre.engine.kv_connector
+        rids = []
+        for i, p in enumerate(prompts):
+            rids.append(dec.engine.add_request(p, sp, kv_transfer_params={
+                "do_remote_prefill": True, "layerwise": True, "key": f"k{i}"}))
+        dec.engine.step()                                   # allocates the blocks, then waits
+        assert len(dc._targets) == 3 and not dec.engine.scheduler.running
+        reqs = {r: dec.engine.scheduler.requests[r] for r in rids}
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        outs = pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {
+            "do_remote_decode": True, "layerwise": True,
+            "push_to": {"engine_id": "DL", "host": "127.0.0.1", "port": dc.base_port, "key": f"k{i}"}}}
+            for i, p in enumerate(prompts)], sp1)
+        assert all(o.kv_transfer_params["pushed"] for o in outs)
+        assert pc.stats["pushed_requests"] == 3 and pc.stats["pushed_layers"] >= 2 * 2
+        assert pre.engine.scheduler.pool.num_free_blocks == pre.engine.scheduler.pool.num_blocks - 1
+        while dec.engine.has_unfinished():
+            dec.engine.step()
+        assert [reqs[r].output_token_ids for r in rids] == want
+        assert dc.stats["pulled_requests"] == 3 and not dc._targets
+        # the decode engine computed one prompt token per request itself, the rest was pushed
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()

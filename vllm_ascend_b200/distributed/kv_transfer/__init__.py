@@ -11,7 +11,8 @@ _CONNECTORS = {
     "NVLinkConnector": ("nvlink_connector", "NVLinkConnector"),
     # names the reference registers, mapped to their B200 counterparts
     "MooncakeConnectorV1": ("nvlink_connector", "NVLinkConnector"),
-    "MooncakeLayerwiseConnector": ("nvlink_connector", "NVLinkConnector"),
+    "LayerwiseConnector": ("layerwise_connector", "LayerwiseConnector"),
+    "MooncakeLayerwiseConnector": ("layerwise_connector", "LayerwiseConnector"),
     "CPUOffloadingConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
     "KVPoolConnector": ("kv_pool", "KVPoolConnector"),
     "AscendStoreConnector": ("kv_pool", "KVPoolConnector"),

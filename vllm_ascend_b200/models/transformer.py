@@ -274,6 +274,7 @@ class CausalLM:
         pf = ParamFactory(cfg, self.device, self.dtype)
         self.comm = TPComm(tp_group or pstate.get_tp_group())
         self.sp_ctx = None             # set by parallel.fused_linear.attach()
+        self.layer_hook = None         # callable(local layer index), run after each layer
         self.full_embedding = None
         max_pos = max(max_model_len, 16)
         lo, hi = layer_range or (0, cfg.num_hidden_layers)
@@ -308,6 +309,8 @@ class CausalLM:
         for layer, cache in zip(self.layers, kv_caches):
             call = getattr(layer, "offloaded_call", None)      # set by the weight offloader
             h, residual = call(h, residual, meta, cache) if call is not None else layer(h, residual, meta, cache)
+            if self.layer_hook is not None:
+                self.layer_hook(layer.idx - self.layer_range[0])   # e.g. layer-wise KV push
         if not self.is_last:
             return h, residual
         h, _ = self.norm(h, residual)

@@ -179,6 +179,8 @@ def forward_sp(model, ctx: FusedTPContext, input_ids: torch.Tensor, meta, kv_cac
         ctx.gemm_rs(act, layer.mlp.down_proj.weight)
         nxt = layers[i + 1].input_layernorm if i + 1 < len(layers) else model.norm
         ctx.norm_push(nxt.weight, nxt.eps)
+        if model.layer_hook is not None:
+            model.layer_hook(i)
     return ctx.gathered()[:T]
 
 
