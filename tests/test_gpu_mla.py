@@ -4,6 +4,7 @@ import pytest
 import torch
 
 from vllm_ascend_b200 import _native
+from vllm_ascend_b200.ops import reference as ref
 from vllm_ascend_b200.attention.mla import mla_decode_native
 
 pytestmark = pytest.mark.gpu
@@ -92,3 +93,74 @@ def test_mla_model_on_engine_matches_torch_path(monkeypatch):
     same = sum(a == b for x, y in zip(outs["torch"], outs["tcgen05"]) for a, b in zip(x, y)) / 30
     assert same > 0.6, outs
     _native.check_status(torch.device("cuda"))
+
+
+def _sfa_case(seed=0):
+    from gpu_utils import make_paged_case
+    g = torch.Generator().manual_seed(seed)
+    q_lens, ctx = [1, 1, 3, 1], [700, 129, 260, 1500]
+    bs = 128
+    _, kc, _, meta = make_paged_case(q_lens, ctx, 1, 1, 128, bs, device="cpu", seed=seed)
+    T = sum(q_lens)
+    seq_lens = [c + q for c, q in zip(ctx, q_lens)]
+    pos = torch.tensor(np.concatenate([np.arange(c, c + q) for c, q in zip(ctx, q_lens)]), dtype=torch.int64)
+    meta.positions = pos
+    G = 24
+    q_idx = (torch.randn(T, G, 128, generator=g) * 0.3).bfloat16()
+    w = torch.rand(T, G, generator=g)
+    return q_idx, w, kc, meta, T, seq_lens
+
+
+def _to_cuda_meta(meta):
+    import copy
+    m = copy.copy(meta)
+    for name in ("query_start_loc", "seq_lens", "block_table", "positions", "slot_mapping"):
+        setattr(m, name, getattr(meta, name).cuda())
+    return m
+
+
+def test_lightning_indexer_kernel_matches_definition():
+    from vllm_ascend_b200.attention import sfa
+    q_idx, w, kc, meta, T, seq_lens = _sfa_case()
+    topk = 256
+    want = sfa.lightning_indexer(q_idx.float(), w, kc.float(), meta, topk)           # CPU definition
+    got = sfa.lightning_indexer(q_idx.cuda(), w.cuda(), kc.cuda(), _to_cuda_meta(meta), topk).cpu()
+    _native.check_status(torch.device("cuda"))
+    # reference scores of both selections must agree (ties may order differently)
+    qsl = meta.query_start_loc_cpu
+    for b in range(meta.num_reqs):
+        for t in range(int(qsl[b]), int(qsl[b + 1])):
+            n_vis = int(meta.positions[t]) + 1
+            k = ref.gather_kv(kc, meta.block_table[b], n_vis)[:, 0].float()
+            s = ((q_idx[t].float() @ k.T).relu() * w[t][:, None]).sum(0)
+            for sel in (want[t], got[t]):
+                assert int((sel >= 0).sum()) == min(topk, n_vis)
+                assert int(sel.max()) < n_vis
+            a = torch.sort(s[want[t][want[t] >= 0].long()], descending=True).values
+            b_ = torch.sort(s[got[t][got[t] >= 0].long()], descending=True).values
+            assert torch.allclose(a, b_, atol=0.05, rtol=0.02)
+
+
+def test_sparse_mla_attention_gather_path():
+    from vllm_ascend_b200.attention import sfa
+    q_idx, w, _, meta, T, seq_lens = _sfa_case(seed=2)
+    g = torch.Generator().manual_seed(3)
+    nblk = int(meta.block_table.max()) + 1
+    lat = (torch.randn(nblk, 128, 1, 512, generator=g) * 0.5).bfloat16()
+    pe = (torch.randn(nblk, 128, 1, 64, generator=g) * 0.5).bfloat16()
+    H = 16
+    q_lat = (torch.randn(T, H, 512, generator=g) * 0.3).bfloat16()
+    q_pe = (torch.randn(T, H, 64, generator=g) * 0.3).bfloat16()
+    topk = 200
+    idx = torch.full((T, topk), -1, dtype=torch.int32)
+    for t in range(T):
+        n_vis = int(meta.positions[t]) + 1
+        k = min(topk, n_vis)
+        idx[t, :k] = torch.randperm(n_vis, generator=g)[:k].int()
+    scale = 576 ** -0.5
+    want = sfa.sparse_mla_attention(q_lat.float(), q_pe.float(), lat.float(), pe.float(), meta, idx, scale)
+    got = sfa.sparse_mla_attention(q_lat.cuda(), q_pe.cuda(), lat.cuda(), pe.cuda(), _to_cuda_meta(meta),
+                                   idx.cuda(), scale)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device("cuda"))
+    assert (got.float().cpu() - want).abs().max() < 0.02
