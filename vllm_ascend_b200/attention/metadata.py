@@ -48,6 +48,9 @@ class AttentionMetadata:
     num_tiles: int = 0
     num_splits: int = 1
     num_input_tokens: int = 0              # padded token count (graph replay)
+    # linear-attention layers: per-sequence state row and whether it holds earlier tokens
+    state_slots: Optional[torch.Tensor] = None          # int32 [B] device
+    has_initial_state: Optional[torch.Tensor] = None    # int32 [B] device
     # decode-context-parallel / extras
     dcp_world_size: int = 1
     dcp_rank: int = 0

@@ -47,6 +47,14 @@ class ModelConfig:
     routed_scaling_factor: float = 1.0
     first_k_dense_replace: int = 0   # leading dense layers (DeepSeek)
     e_score_correction_bias: bool = False
+    # ---- linear attention (Gated DeltaNet hybrids: every `full_attention_interval`-th layer is
+    # softmax attention, the others keep a recurrent state instead of a KV cache) ----
+    full_attention_interval: int = 0
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
     # ---- MLA ----
     use_mla: bool = False
     q_lora_rank: Optional[int] = None
@@ -71,6 +79,13 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def is_hybrid(self) -> bool:
+        return self.full_attention_interval > 0
+
+    def is_linear_layer(self, layer_idx: int) -> bool:
+        return self.is_hybrid and (layer_idx + 1) % self.full_attention_interval != 0
 
     def is_moe_layer(self, layer_idx: int) -> bool:
         return self.is_moe and layer_idx >= self.first_k_dense_replace
@@ -209,6 +224,12 @@ PRESETS: dict[str, Any] = {
         intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
         num_key_value_heads=2, head_dim=32, rope_theta=1e6, qk_norm=True, num_experts=8,
         num_experts_per_tok=2, moe_intermediate_size=64, dtype="float32"),
+    "tiny-gdn": lambda: _preset(
+        name="tiny-gdn", architecture="Qwen3NextForCausalLM", vocab_size=512, hidden_size=128,
+        intermediate_size=256, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+        head_dim=32, rope_theta=1e6, qk_norm=True, dtype="float32", full_attention_interval=2,
+        linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+        linear_value_head_dim=32, linear_conv_kernel_dim=4),
     "tiny-deepseek": lambda: _preset(
         name="tiny-deepseek", architecture="DeepseekV3ForCausalLM", vocab_size=512,
         hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,

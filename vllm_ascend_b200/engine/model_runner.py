@@ -91,6 +91,8 @@ class ModelRunner:
         self._h_bt = torch.zeros((B, self.max_blocks_per_seq), dtype=i32, pin_memory=pin)
         self._h_tile = torch.zeros((2, max_tiles), dtype=i32, pin_memory=pin)
         self._h_sampled = torch.zeros(B, dtype=i64, pin_memory=pin)
+        self._h_state = torch.zeros((2, B), dtype=i32, pin_memory=pin)
+        self.state_meta = torch.zeros((2, B), dtype=i32, device=device)     # [slot; has_initial_state]
         self._h_sampled2 = [torch.zeros(B, dtype=i64, pin_memory=pin) for _ in range(2)]   # async steps
         self._async_flip = 0
         # ---- CUDA graphs
@@ -135,9 +137,35 @@ class ModelRunner:
             self.model.load_weights(iterate_safetensors(self.mcfg.model_path))
         self.load_time = time.time() - t0
 
+    def _attn_layer(self):
+        """First layer with a paged KV cache (hybrid models start with recurrent layers)."""
+        for L in self.model.layers:
+            if not getattr(L.self_attn, "is_linear_attention", False):
+                return L.self_attn
+        raise RuntimeError("model has no attention layer with a KV cache")
+
+    def _num_kv_layers(self) -> int:
+        return sum(1 for L in self.model.layers if not getattr(L.self_attn, "is_linear_attention", False))
+
+    def state_bytes(self) -> int:
+        """Memory of the per-sequence recurrent / convolution states of linear-attention layers."""
+        total = 0
+        for L in self.model.layers:
+            a = L.self_attn
+            if getattr(a, "is_linear_attention", False):
+                cs, ss = a.state_shapes(self.max_seqs + 1)
+                n_c = 1
+                for d in cs:
+                    n_c *= d
+                n_s = 1
+                for d in ss:
+                    n_s *= d
+                total += n_c * 2 + n_s * 4
+        return total
+
     def kv_bytes_per_block(self) -> int:
         m = self.model
-        n_layers = len(m.layers)
+        n_layers = self._num_kv_layers()
         itemsize = torch.tensor([], dtype=self.kv_dtype).element_size()
         per_tok = sum(self._cache_widths()) * itemsize
         return n_layers * self.block_size * per_tok
@@ -150,7 +178,7 @@ class ModelRunner:
         c = self.mcfg
         if c.use_mla:
             return (c.kv_lora_rank, c.qk_rope_head_dim)
-        a = self.model.layers[0].self_attn
+        a = self._attn_layer()
         return (a.Hkv * a.D, a.Hkv * a.D)
 
     def activation_bytes_estimate(self) -> int:
@@ -171,7 +199,8 @@ class ModelRunner:
             return max(64, 4 * self.max_seqs)
         torch.cuda.synchronize()
         free, total = torch.cuda.mem_get_info(self.device)
-        budget = total * cc.gpu_memory_utilization - (total - free) - self.activation_bytes_estimate()
+        budget = total * cc.gpu_memory_utilization - (total - free) - self.activation_bytes_estimate() \
+            - self.state_bytes()
         n = int(budget // self.kv_bytes_per_block())
         if n < 8:
             raise RuntimeError(f"not enough memory for the KV cache ({budget / 2**30:.1f} GiB left)")
@@ -186,6 +215,9 @@ class ModelRunner:
         self.kv_caches = []
         per_layer = []
         for layer in self.model.layers:
+            if getattr(layer.self_attn, "is_linear_attention", False):
+                per_layer.append(None)              # recurrent state instead of a paged cache
+                continue
             if c.use_mla:
                 shapes = [(num_blocks, self.block_size, 1, c.kv_lora_rank),
                           (num_blocks, self.block_size, 1, c.qk_rope_head_dim)]
@@ -200,9 +232,15 @@ class ModelRunner:
             # can map the whole cache through a single CUDA IPC handle
             from ..distributed.kv_transfer.nvlink_connector import KVArena
             torch.cuda.empty_cache()
-            self.kv_arena = KVArena(KVArena.bytes_needed([s for sh in per_layer for s in sh],
+            self.kv_arena = KVArena(KVArena.bytes_needed([s for sh in per_layer if sh for s in sh],
                                                          self.kv_dtype), self.device)
-        for shapes in per_layer:
+        for layer, shapes in zip(self.model.layers, per_layer):
+            if shapes is None:
+                # one state row per batch row, plus a scratch row for padded graph entries
+                cs, ss = layer.self_attn.state_shapes(self.max_seqs + 1)
+                self.kv_caches.append((torch.zeros(cs, dtype=self.kv_dtype, device=self.device),
+                                       torch.zeros(ss, dtype=torch.float32, device=self.device)))
+                continue
             self.kv_caches.append(tuple(
                 ops.alloc_kv_cache(s[0], s[1], s[2], s[3], self.kv_dtype, self.device, layout,
                                    arena=self.kv_arena)
@@ -307,8 +345,20 @@ class ModelRunner:
             attn_state=state, num_decodes=nd, num_decode_tokens=ndt, num_prefills=npf,
             num_input_tokens=Tp)
         meta.dcp_interleave = self.dcp_interleave
+        if self.mcfg.is_hybrid:
+            # recurrent layers index their state by the request's batch row; padded rows use the
+            # scratch row
+            hs = self._h_state
+            hs[0, :B] = torch.from_numpy(rows.astype(np.int32))
+            hs[1, :B] = torch.from_numpy((starts > 0).astype(np.int32))
+            if Bp > B:
+                hs[0, B:Bp] = self.max_seqs
+                hs[1, B:Bp] = 0
+            self.state_meta[:, :Bp].copy_(hs[:, :Bp], non_blocking=True)
+            meta.state_slots = self.state_meta[0, :Bp]
+            meta.has_initial_state = self.state_meta[1, :Bp]
         if self.is_cuda and not self.mcfg.use_mla:
-            a = self.model.layers[0].self_attn
+            a = self._attn_layer()
             G = a.Hq // a.Hkv
             tok_per_tile = max(1, 128 // G)
             if max_q > 1:
@@ -731,7 +781,7 @@ class ModelRunner:
                 return
         # scratch for split-KV partials must exist before capture
         if not self.mcfg.use_mla:
-            a = self.model.layers[0].self_attn
+            a = self._attn_layer()
             worst = 0
             for s in self.capture_sizes:
                 ns = self._decode_splits(s, a.Hkv)

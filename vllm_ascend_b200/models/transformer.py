@@ -229,7 +229,11 @@ class DecoderLayer:
         self.idx = idx
         self.input_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
-        self.self_attn = (MLAAttention if cfg.use_mla else GQAAttention)(pf, cfg, idx, comm, max_pos)
+        if cfg.is_linear_layer(idx):
+            from .gdn import GatedDeltaNet
+            self.self_attn = GatedDeltaNet(pf, cfg, idx, comm)
+        else:
+            self.self_attn = (MLAAttention if cfg.use_mla else GQAAttention)(pf, cfg, idx, comm, max_pos)
         if cfg.is_moe_layer(idx):
             self.mlp = SparseMoeBlock(pf, cfg, idx, comm, ep_group, moe_runtime)
         else:

@@ -313,6 +313,9 @@ def check_and_update_config(engine_cfg) -> B200Config:
     _validate_finegrained(cfg, pc.tensor_parallel_size, max(1, pc.data_parallel_size))
     _validate_eplb(cfg.eplb_config, mc.is_moe, pc.enable_expert_parallel)
     _validate_scheduler_ext(cfg.scheduler_config, engine_cfg)
+    if mc.is_hybrid and engine_cfg.cache.enable_prefix_caching:
+        # a recurrent state is not addressable by block: a cached prefix could not restore it
+        engine_cfg.cache.enable_prefix_caching = False
     if cfg.weight_offload_config.enabled:
         cc.cudagraph_mode = "NONE"        # offloaded weights rotate through device buffers
     # 4 graph mode normalisation + capture sizes (platform.py:937-1117, 1275-1309)
