@@ -51,6 +51,8 @@ class AttentionMetadata:
     # linear-attention layers: per-sequence state row and whether it holds earlier tokens
     state_slots: Optional[torch.Tensor] = None          # int32 [B] device
     has_initial_state: Optional[torch.Tensor] = None    # int32 [B] device
+    # multimodal rotary embedding: int64 [3, num_input_tokens] (temporal, height, width)
+    mrope_positions: Optional[torch.Tensor] = None
     # decode-context-parallel / extras
     dcp_world_size: int = 1
     dcp_rank: int = 0

@@ -16,14 +16,24 @@ from typing import Any, Callable, Optional
 
 import torch
 
-_GLOBAL_POOL = None
+_POOLS: dict = {}
 
 
 def global_graph_pool():
-    global _GLOBAL_POOL
-    if _GLOBAL_POOL is None:
-        _GLOBAL_POOL = torch.cuda.graph_pool_handle()
-    return _GLOBAL_POOL
+    """One memory pool per device shared by every captured graph (the reference shares one pool
+    the same way, acl_graph.py:60-75).  The caching allocator retires a pool once its last graph
+    is destroyed and refuses the handle afterwards, so a one-kernel graph captured into the pool
+    here stays alive for the life of the process."""
+    dev = torch.cuda.current_device()
+    ent = _POOLS.get(dev)
+    if ent is None:
+        handle = torch.cuda.graph_pool_handle()
+        keep = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(keep, pool=handle):
+            anchor = torch.zeros(8, device=f"cuda:{dev}")
+        ent = _POOLS[dev] = (handle, keep, anchor)
+    return ent[0]
 
 
 @dataclass(frozen=True)

@@ -55,6 +55,14 @@ class ModelConfig:
     linear_key_head_dim: int = 0
     linear_value_head_dim: int = 0
     linear_conv_kernel_dim: int = 4
+    # multimodal (Qwen2-VL family): rotary sections over (temporal, height, width) positions,
+    # vision-tower config (HF ``vision_config`` dict) and the placeholder token ids
+    mrope_section: Optional[list] = None
+    mrope_interleaved: bool = False
+    vision_config: Optional[dict] = None
+    image_token_id: int = -1
+    video_token_id: int = -1
+    tokens_per_second: float = 2.0
     # ---- MLA ----
     use_mla: bool = False
     q_lora_rank: Optional[int] = None
@@ -79,6 +87,10 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def is_multimodal(self) -> bool:
+        return self.vision_config is not None
 
     @property
     def is_hybrid(self) -> bool:
@@ -110,6 +122,13 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict, **over) -> "ModelConfig":
         arch = (d.get("architectures") or ["LlamaForCausalLM"])[0]
+        top = d
+        if "text_config" in d and "hidden_size" not in d:      # nested multimodal layout
+            d = {**d["text_config"], "architectures": [arch]}
+            for k in ("vision_config", "image_token_id", "video_token_id", "quantization_config",
+                      "tie_word_embeddings"):
+                if k in top and (k not in d or k != "tie_word_embeddings"):
+                    d[k] = top[k]
         hs = d["hidden_size"]
         nh = d["num_attention_heads"]
         kw: dict[str, Any] = dict(
@@ -148,6 +167,19 @@ class ModelConfig:
                       kv_lora_rank=d["kv_lora_rank"],
                       qk_nope_head_dim=d["qk_nope_head_dim"],
                       qk_rope_head_dim=d["qk_rope_head_dim"], v_head_dim=d["v_head_dim"])
+        rs = d.get("rope_scaling") or d.get("rope_parameters") or {}
+        if rs.get("mrope_section"):
+            kw.update(mrope_section=list(rs["mrope_section"]),
+                      mrope_interleaved=bool(rs.get("mrope_interleaved", False)))
+            if rs.get("rope_theta") and "rope_theta" not in d:
+                kw["rope_theta"] = rs["rope_theta"]
+            if (rs.get("rope_type") or rs.get("type")) in ("mrope", "default", None):
+                kw["rope_scaling"] = None
+        if d.get("vision_config"):
+            vc = dict(d["vision_config"])
+            kw.update(vision_config=vc, image_token_id=d.get("image_token_id", -1),
+                      video_token_id=d.get("video_token_id", -1),
+                      tokens_per_second=float(vc.get("tokens_per_second", 2.0)))
         qc = d.get("quantization_config")
         if qc:
             method = qc.get("quant_method", "")
@@ -224,6 +256,13 @@ PRESETS: dict[str, Any] = {
         intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
         num_key_value_heads=2, head_dim=32, rope_theta=1e6, qk_norm=True, num_experts=8,
         num_experts_per_tok=2, moe_intermediate_size=64, dtype="float32"),
+    "tiny-vl": lambda: _preset(
+        name="tiny-vl", architecture="Qwen2_5_VLForConditionalGeneration", vocab_size=512, hidden_size=128,
+        intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+        head_dim=32, rope_theta=1e6, attention_bias=True, dtype="float32", mrope_section=[4, 6, 6],
+        image_token_id=500, video_token_id=501,
+        vision_config=dict(depth=2, hidden_size=64, num_heads=4, intermediate_size=96, out_hidden_size=128,
+                           patch_size=14, window_size=56, fullatt_block_indexes=[1])),
     "tiny-gdn": lambda: _preset(
         name="tiny-gdn", architecture="Qwen3NextForCausalLM", vocab_size=512, hidden_size=128,
         intermediate_size=256, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
@@ -309,6 +348,7 @@ class EngineConfig:
     device_index: Optional[int] = None      # single-process engines only
     seed: int = 0
     kv_transfer_config: Optional[dict] = None
+    ec_transfer_config: Optional[dict] = None      # disaggregated vision encoder (encoder-cache transfer)
     speculative_config: Optional[dict] = None
     enable_sleep_mode: bool = False
     load_format: str = "auto"               # auto | netloader | rfork

@@ -135,7 +135,9 @@ __global__ void embedding_kernel(const long* __restrict__ ids,
 // cos_sin: [max_pos, rot_dim] fp32, first half cos, second half sin (neox layout
 // pairs element j with j + rot_dim/2).  q and k are updated in place; k and v are
 // scattered to the paged caches [num_blocks, block_size, Hkv, D] at
-// slot_mapping[t] (slot < 0: skipped).
+// slot_mapping[t] (slot < 0: skipped).  Multimodal rotary (mrope_axis != null): positions is
+// [3, pos_stride] (temporal, height, width) and rotary pair e takes its angle at the position of
+// axis mrope_axis[e]; text tokens carry the same position on all three axes.
 template <int D>
 __global__ void qknorm_rope_kvwrite_kernel(__nv_bfloat16* qkv, long qkv_stride,
                                            const long* __restrict__ positions,
@@ -145,7 +147,8 @@ __global__ void qknorm_rope_kvwrite_kernel(__nv_bfloat16* qkv, long qkv_stride,
                                            __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                                            const long* __restrict__ slot_mapping, int T, int Hq,
                                            int Hkv, long num_slots, int block_size,
-                                           int kv_layout, int* status) {
+                                           int kv_layout, int* status,
+                                           const int* __restrict__ mrope_axis, long pos_stride) {
   constexpr int PER = D / 32;
   const int warps_per_block = blockDim.x >> 5;
   const int heads_total = Hq + 2 * Hkv;
@@ -189,7 +192,9 @@ __global__ void qknorm_rope_kvwrite_kernel(__nv_bfloat16* qkv, long qkv_stride,
           for (int i = 0; i < hh; i++) {
             if (i + hh < PER) {
               const int e = lane + 32 * i;
-              const float c = cs[e], s = cs[half + e];
+              const float* ce = cs;
+              if (mrope_axis) ce = cos_sin + positions[mrope_axis[e] * pos_stride + t] * (long)rot_dim;
+              const float c = ce[e], s = ce[half + e];
               const float x1 = v[i], x2 = v[i + hh];
               v[i] = x1 * c - x2 * s;
               v[i + hh] = x2 * c + x1 * s;
@@ -293,6 +298,26 @@ __global__ void qknorm_rope_kvwrite_d128_kernel(__nv_bfloat16* qkv, long qkv_str
   }
 }
 
+// Rotary embedding from per-token angle tables (vision encoders: the angle of a pair depends on
+// the patch's row for one half of the pairs and on its column for the other, so the host builds
+// cos / sin [N, half] once per image batch).  x: [N, H, D] with token stride x_stride, pairs
+// (e, e + half) for e < half, in place.  One warp per (token, head).
+__global__ void rope_table_kernel(__nv_bfloat16* x, long x_stride, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, long N, int H, int D, int half) {
+  const long gw = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= N * H) return;
+  const long t = gw / H;
+  const int h = (int)(gw - t * H);
+  __nv_bfloat16* row = x + t * x_stride + (long)h * D;
+  const float* c = cos_t + t * half;
+  const float* sn = sin_t + t * half;
+  for (int e = threadIdx.x & 31; e < half; e += 32) {
+    const float x1 = __bfloat162float(row[e]), x2 = __bfloat162float(row[e + half]);
+    row[e] = __float2bfloat16(x1 * c[e] - x2 * sn[e]);
+    row[e + half] = __float2bfloat16(x2 * c[e] + x1 * sn[e]);
+  }
+}
+
 // ---------------------------------------------------------------- fp8 1x128 group quant
 // x: [T, H] bf16 -> q: [T, H] e4m3, scales: [T, H/128] fp32 (scale = amax/448).
 // One warp per group of 128 elements.
@@ -371,12 +396,13 @@ B200_API int b200_embedding(const void* ids, const void* weight, void* out, long
   return B200_CHECK_LAUNCH();
 }
 
-B200_API int b200_qknorm_rope_kvwrite(void* qkv, long qkv_stride, const void* positions,
-                                      const void* cos_sin, int rot_dim, const void* q_norm_w,
-                                      const void* k_norm_w, float eps, void* k_cache,
-                                      void* v_cache, const void* slot_mapping, int T, int Hq,
-                                      int Hkv, int D, long num_slots, int block_size,
-                                      int kv_layout, int* status, cudaStream_t stream) {
+static int qknorm_rope_impl(void* qkv, long qkv_stride, const void* positions,
+                            const void* cos_sin, int rot_dim, const void* q_norm_w,
+                            const void* k_norm_w, float eps, void* k_cache,
+                            void* v_cache, const void* slot_mapping, int T, int Hq,
+                            int Hkv, int D, long num_slots, int block_size,
+                            int kv_layout, int* status, const void* mrope_axis, long pos_stride,
+                            cudaStream_t stream) {
   if (T <= 0) return 0;
   if (rot_dim > D || (rot_dim > 0 && ((rot_dim >> 1) & 31))) return 9102;
   const long warps = (long)T * (Hq + 2 * Hkv);
@@ -387,8 +413,8 @@ B200_API int b200_qknorm_rope_kvwrite(void* qkv, long qkv_stride, const void* po
       (__nv_bfloat16*)qkv, qkv_stride, (const long*)positions, (const float*)cos_sin, rot_dim, \
       (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps,                    \
       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const long*)slot_mapping, T, Hq, Hkv, \
-      num_slots, block_size, kv_layout, status)
-  if (D == 128 && rot_dim == 128 && (qkv_stride & 3) == 0) {
+      num_slots, block_size, kv_layout, status, (const int*)mrope_axis, pos_stride)
+  if (D == 128 && rot_dim == 128 && (qkv_stride & 3) == 0 && !mrope_axis) {
     qknorm_rope_kvwrite_d128_kernel<<<blocks, wpb * 32, 0, stream>>>(
         (__nv_bfloat16*)qkv, qkv_stride, (const long*)positions, (const float*)cos_sin,
         (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps,
@@ -403,6 +429,41 @@ B200_API int b200_qknorm_rope_kvwrite(void* qkv, long qkv_stride, const void* po
   else if (D == 32) LAUNCH_ROPE(32);
   else return 9103;
 #undef LAUNCH_ROPE
+  return B200_CHECK_LAUNCH();
+}
+
+B200_API int b200_qknorm_rope_kvwrite(void* qkv, long qkv_stride, const void* positions,
+                                      const void* cos_sin, int rot_dim, const void* q_norm_w,
+                                      const void* k_norm_w, float eps, void* k_cache,
+                                      void* v_cache, const void* slot_mapping, int T, int Hq,
+                                      int Hkv, int D, long num_slots, int block_size,
+                                      int kv_layout, int* status, cudaStream_t stream) {
+  return qknorm_rope_impl(qkv, qkv_stride, positions, cos_sin, rot_dim, q_norm_w, k_norm_w, eps,
+                          k_cache, v_cache, slot_mapping, T, Hq, Hkv, D, num_slots, block_size,
+                          kv_layout, status, nullptr, 0, stream);
+}
+
+// positions: int64 [3, pos_stride]; mrope_axis: int32 [rot_dim / 2] with values 0..2.
+B200_API int b200_qknorm_mrope_kvwrite(void* qkv, long qkv_stride, const void* positions,
+                                       long pos_stride, const void* mrope_axis,
+                                       const void* cos_sin, int rot_dim, const void* q_norm_w,
+                                       const void* k_norm_w, float eps, void* k_cache,
+                                       void* v_cache, const void* slot_mapping, int T, int Hq,
+                                       int Hkv, int D, long num_slots, int block_size,
+                                       int kv_layout, int* status, cudaStream_t stream) {
+  if (!mrope_axis) return 9104;
+  return qknorm_rope_impl(qkv, qkv_stride, positions, cos_sin, rot_dim, q_norm_w, k_norm_w, eps,
+                          k_cache, v_cache, slot_mapping, T, Hq, Hkv, D, num_slots, block_size,
+                          kv_layout, status, mrope_axis, pos_stride, stream);
+}
+
+B200_API int b200_rope_table(void* x, long x_stride, const void* cos_t, const void* sin_t, long N,
+                             int H, int D, int half, cudaStream_t stream) {
+  if (N <= 0 || H <= 0) return 0;
+  if (half <= 0 || 2 * half > D) return 9105;
+  const long warps = N * H;
+  rope_table_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(
+      (__nv_bfloat16*)x, x_stride, (const float*)cos_t, (const float*)sin_t, N, H, D, half);
   return B200_CHECK_LAUNCH();
 }
 

@@ -57,6 +57,9 @@ class LLMEngine:
         if cfg.kv_transfer_config:
             from ..distributed.kv_transfer import create_connector
             self.kv_connector = create_connector(cfg, self.runner)
+        if cfg.ec_transfer_config and self.runner.mm is not None:
+            from ..distributed.ec_transfer import create_ec_connector
+            self.runner.mm.ec_connector = create_ec_connector(cfg.ec_transfer_config)
         self.scheduler = self._make_scheduler(num_blocks)
         if cfg.enable_lora:
             self.scheduler.max_loras = cfg.max_loras
@@ -87,13 +90,26 @@ class LLMEngine:
     # ------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], sampling_params: SamplingParams,
                     request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None,
-                    job_id: Optional[str] = None, lora_request=None) -> str:
+                    job_id: Optional[str] = None, lora_request=None,
+                    multi_modal_data: Optional[dict] = None) -> str:
         rid = request_id or f"req-{next(self._req_counter)}"
         if lora_request is not None and self.runner.lora_manager is None:
             raise ValueError("a LoRA request needs an engine built with enable_lora=True")
+        mm_items, mrope, delta = [], None, 0
+        mcfg = self.cfg.model
+        if multi_modal_data:
+            if not mcfg.is_multimodal:
+                raise ValueError(f"{mcfg.architecture} takes no multimodal inputs")
+            from ..multimodal import build_mm_request, mrope_positions
+            from ..models.vision import VisionConfig
+            prompt_token_ids, mm_items = build_mm_request(prompt_token_ids, multi_modal_data, mcfg)
+            mrope, delta = mrope_positions(prompt_token_ids, mm_items,
+                                           VisionConfig.from_hf(mcfg.vision_config).spatial_merge_size,
+                                           mcfg.tokens_per_second)
         req = Request(rid, np.asarray(prompt_token_ids, dtype=np.int32), sampling_params,
                       eos_token_id=self.eos_token_id, kv_transfer_params=kv_transfer_params,
-                      job_id=job_id, lora_request=lora_request)
+                      job_id=job_id, lora_request=lora_request, mm_inputs=mm_items,
+                      mrope_positions=mrope, mrope_delta=delta)
         self.scheduler.add_request(req)
         return rid
 
@@ -106,6 +122,12 @@ class LLMEngine:
         else:
             self.runner.propose_draft_tokens([r for r, _ in so.scheduled
                                               if r.status == RequestStatus.RUNNING and r.request_id in sampled])
+
+    def _release_mm(self, finished) -> None:
+        mm = self.runner.mm
+        if mm is not None:
+            for r in finished:
+                mm.release(r)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or self._inflight is not None
@@ -132,6 +154,7 @@ class LLMEngine:
                 if req.first_token_time is None and req.request_id in sampled:
                     req.first_token_time = now
             finished = self.scheduler.update_from_output(so_prev, sampled)
+            self._release_mm(finished)
         self._inflight = (so, handle) if handle is not None else None
         t3 = time.perf_counter()
         self.host_times["schedule"] += t1 - t0
@@ -158,6 +181,7 @@ class LLMEngine:
             if req.first_token_time is None and req.request_id in sampled:
                 req.first_token_time = now
         finished = self.scheduler.update_from_output(so, sampled)
+        self._release_mm(finished)
         self._propose(so, sampled)
         if self.kv_connector is not None:
             self.kv_connector.step_finished(so, self.scheduler)
@@ -231,7 +255,7 @@ class LLM:
                  enable_prefix_caching: bool = False, enforce_eager: bool = False,
                  enable_chunked_prefill: bool = True, quantization: Optional[str] = None,
                  seed: int = 0, additional_config: Optional[dict] = None,
-                 kv_transfer_config: Optional[dict] = None,
+                 kv_transfer_config: Optional[dict] = None, ec_transfer_config: Optional[dict] = None,
                  speculative_config: Optional[dict] = None, enable_sleep_mode: bool = False,
                  cudagraph_capture_sizes: Optional[list] = None,
                  decode_context_parallel_size: int = 1, enable_lora: bool = False, max_loras: int = 4,
@@ -267,7 +291,8 @@ class LLM:
                 cudagraph_mode="NONE" if enforce_eager else "FULL_DECODE_ONLY",
                 cudagraph_capture_sizes=cudagraph_capture_sizes),
             additional_config=additional_config or {}, device=device, device_index=device_index, seed=seed,
-            kv_transfer_config=kv_transfer_config, speculative_config=speculative_config,
+            kv_transfer_config=kv_transfer_config, ec_transfer_config=ec_transfer_config,
+            speculative_config=speculative_config,
             enable_sleep_mode=enable_sleep_mode, enable_lora=enable_lora, max_loras=max_loras,
             max_lora_rank=max_lora_rank, async_scheduling=async_scheduling, load_format=load_format,
             model_loader_extra_config=model_loader_extra_config)
@@ -279,6 +304,34 @@ class LLM:
         self.engine = LLMEngine(cfg)
 
     # ------------------------------------------------------------------
+    def encode_multimodal(self, multi_modal_data: dict) -> list[dict]:
+        """Encoder-instance entry point of a disaggregated deployment: runs the vision tower over
+        the items, publishes every output through the EC connector and returns
+        ``{"hash", "grid_thw"}`` descriptors a prefill / decode instance accepts in place of pixels."""
+        eng = self.engine
+        mm = eng.runner.mm
+        if mm is None:
+            raise ValueError("the model has no vision tower")
+        from ..multimodal import build_mm_request
+        mcfg = self.cfg.model
+        out = []
+        for modality, tok in (("image", mcfg.image_token_id), ("video", mcfg.video_token_id)):
+            entries = multi_modal_data.get(modality) or []
+            if not entries:
+                continue
+            _, items = build_mm_request([tok] * len(entries), {modality: entries}, mcfg)
+
+            class _Req:
+                request_id = f"_encode-{modality}"
+            with torch.inference_mode():
+                mm._run_encoder([(_Req, k, it) for k, it in enumerate(items)])
+            for k, it in enumerate(items):
+                emb = mm.encoder_cache.pop((_Req.request_id, k))
+                if mm.ec_connector is not None and not mm.ec_connector.is_producer:
+                    mm.ec_connector.save(it.hash, emb)
+                out.append({"modality": modality, "hash": it.hash, "grid_thw": list(it.grid_thw)})
+        return out
+
     def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  use_tqdm: bool = False, lora_request=None) -> list[RequestOutput]:
         """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``)."""
@@ -296,7 +349,8 @@ class LLM:
             sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
             ktp = p.get("kv_transfer_params") if isinstance(p, dict) else None
             lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
-            rid = eng.add_request(ids, sp, kv_transfer_params=ktp, lora_request=lr)
+            mmd = p.get("multi_modal_data") if isinstance(p, dict) else None
+            rid = eng.add_request(ids, sp, kv_transfer_params=ktp, lora_request=lr, multi_modal_data=mmd)
             order.append(rid)
             mine.append(i)
             reqs[rid] = eng.scheduler.requests[rid]

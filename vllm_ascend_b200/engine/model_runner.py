@@ -99,6 +99,7 @@ class ModelRunner:
         self.graphs: dict[tuple, object] = {}     # (capture size, has_lora) -> BatchDescriptor
         self.graph_wrapper = None
         self.lora_manager = None
+        self.mm = None                   # MultimodalState for models with a vision tower
         self.moe_runtime = None
         from ..parallel import state as _ps
         self.pp = _ps.get_pp_group()
@@ -136,6 +137,9 @@ class ModelRunner:
             from ..models.transformer import iterate_safetensors
             self.model.load_weights(iterate_safetensors(self.mcfg.model_path))
         self.load_time = time.time() - t0
+        if self.mcfg.is_multimodal and self.model.is_first:
+            from .mm_runner import MultimodalState
+            self.mm = MultimodalState(self)
 
     def _attn_layer(self):
         """First layer with a paged KV cache (hybrid models start with recurrent layers)."""
@@ -345,6 +349,8 @@ class ModelRunner:
             attn_state=state, num_decodes=nd, num_decode_tokens=ndt, num_prefills=npf,
             num_input_tokens=Tp)
         meta.dcp_interleave = self.dcp_interleave
+        if self.mm is not None:
+            self.mm.prepare(reqs, starts, q_lens, cu, pos, req_idx, T, Tp, meta)
         if self.mcfg.is_hybrid:
             # recurrent layers index their state by the request's batch row; padded rows use the
             # scratch row
@@ -422,7 +428,10 @@ class ModelRunner:
     # ------------------------------------------------------------------ execution
     def _forward(self, T: int, meta: AttentionMetadata) -> torch.Tensor:
         pp = self.pp
+        emb = self.mm.inputs_embeds(self.input_ids[:T]) if self.mm is not None else None
         if pp.world_size == 1:
+            if emb is not None:
+                return self.model.forward(self.input_ids[:T], meta, self.kv_caches, inputs_embeds=emb)
             return self.model.forward(self.input_ids[:T], meta, self.kv_caches)
         # Pipeline stage: activations (hidden, residual) arrive from the previous stage and
         # leave for the next one; only the last stage returns final hidden states
@@ -435,7 +444,7 @@ class ModelRunner:
             pp.recv(h, pp.rank_in_group - 1)
             pp.recv(res, pp.rank_in_group - 1)
             inter = (h, res)
-        out = self.model.forward(self.input_ids[:T], meta, self.kv_caches, inter)
+        out = self.model.forward(self.input_ids[:T], meta, self.kv_caches, inter, inputs_embeds=emb)
         if self.model.is_last:
             return out
         h, res = out

@@ -85,6 +85,11 @@ class Request:
     spec_token_ids: list = field(default_factory=list)
     num_inflight: int = 0                 # tokens sampled by steps still running on the GPU (async scheduling)
     job_id: Optional[str] = None
+    # multimodal: items (placeholder run + pixels), 3-axis rotary positions of the prompt and the
+    # offset decoded tokens continue from (position = index + delta)
+    mm_inputs: list = field(default_factory=list)
+    mrope_positions: Optional[np.ndarray] = None
+    mrope_delta: int = 0
 
     @property
     def num_prompt_tokens(self) -> int:

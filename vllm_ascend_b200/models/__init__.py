@@ -25,6 +25,15 @@ for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwe
     register_model(_arch, _causal_lm)
 
 
+def _qwen_vl(cfg, device, **kw):
+    from .qwen_vl import QwenVLForConditionalGeneration
+    return QwenVLForConditionalGeneration(cfg, device, **kw)
+
+
+for _arch in ("Qwen2_5_VLForConditionalGeneration", "Qwen2VLForConditionalGeneration"):
+    register_model(_arch, _qwen_vl)
+
+
 def supported_architectures() -> list[str]:
     return sorted(_REGISTRY)
 

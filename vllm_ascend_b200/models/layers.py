@@ -303,13 +303,20 @@ class GQAAttention:
         self.cos_sin = get_cos_sin_cache(self.rot_dim, max_pos, cfg.rope_theta, cfg.rope_scaling,
                                          pf.device)
         self.window = cfg.sliding_window or 0
+        self.mrope_axis = None
+        if cfg.mrope_section:
+            assert 2 * sum(cfg.mrope_section) == self.rot_dim, "mrope sections must cover rot_dim / 2 pairs"
+            self.mrope_axis = ref.mrope_axis_table(cfg.mrope_section, cfg.mrope_interleaved).to(pf.device)
 
     def __call__(self, x: torch.Tensor, meta, kv_cache) -> torch.Tensor:
         qkv = self.qkv_proj(x)
         k_cache, v_cache = kv_cache
-        ops.qknorm_rope_kvwrite(qkv, meta.positions, self.cos_sin, self.rot_dim, self.q_norm,
+        mpos = getattr(meta, "mrope_positions", None) if self.mrope_axis is not None else None
+        ops.qknorm_rope_kvwrite(qkv, meta.positions if mpos is None else mpos, self.cos_sin,
+                                self.rot_dim, self.q_norm,
                                 self.k_norm, self.cfg.rms_norm_eps, k_cache, v_cache,
-                                meta.slot_mapping, self.Hq, self.Hkv, self.D)
+                                meta.slot_mapping, self.Hq, self.Hkv, self.D,
+                                mrope_axis=None if mpos is None else self.mrope_axis)
         T = qkv.shape[0]
         q = qkv[:, :self.Hq * self.D].view(T, self.Hq, self.D)
         o = ops.paged_attention(q, k_cache, v_cache, meta, self.scale, causal=True,

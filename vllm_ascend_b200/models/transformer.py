@@ -301,12 +301,13 @@ class CausalLM:
 
     # -- forward ---------------------------------------------------------
     def forward(self, input_ids: torch.Tensor, meta, kv_caches: list,
-                intermediate: Optional[tuple] = None):
-        if self.sp_ctx is not None and input_ids.is_cuda:
+                intermediate: Optional[tuple] = None, inputs_embeds: Optional[torch.Tensor] = None):
+        if self.sp_ctx is not None and input_ids.is_cuda and inputs_embeds is None:
             from ..parallel.fused_linear import forward_sp
             return forward_sp(self, self.sp_ctx, input_ids, meta, kv_caches)
         if self.is_first:
-            h = self.embed_tokens(input_ids)
+            # multimodal steps pass embeddings with the encoder outputs already merged in
+            h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
             residual = None
         else:
             h, residual = intermediate

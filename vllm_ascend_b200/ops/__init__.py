@@ -110,8 +110,11 @@ def embedding(ids: torch.Tensor, weight: torch.Tensor, vocab_start: int = 0,
 def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
                         rot_dim: int, q_norm_w, k_norm_w, eps: float,
                         k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                        slot_mapping: Optional[torch.Tensor], Hq: int, Hkv: int, D: int) -> None:
-    """Split-QKV + per-head q/k RMSNorm + neox RoPE + paged KV-cache write, one pass, in place."""
+                        slot_mapping: Optional[torch.Tensor], Hq: int, Hkv: int, D: int,
+                        mrope_axis: Optional[torch.Tensor] = None) -> None:
+    """Split-QKV + per-head q/k RMSNorm + neox RoPE + paged KV-cache write, one pass, in place.
+    With ``mrope_axis`` (int32 [rot_dim/2]) positions is [3, N] and each rotary pair follows the
+    temporal / height / width position its table entry names (multimodal rotary embedding)."""
     native_ok = (_use_native(qkv) and D in (32, 64, 96, 128, 256) and rot_dim <= D
                  and (rot_dim == 0 or (rot_dim // 2) % 32 == 0)
                  and (k_cache is None or k_cache.dtype == _BF16))
@@ -119,9 +122,20 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: tor
         if qkv.is_cuda and qkv.dtype == _BF16 and D in (64, 128):
             raise RuntimeError("qknorm_rope_kvwrite: unsupported rotary shape for the native kernel")
         return ref.qknorm_rope_kvwrite(qkv, positions, cos_sin, rot_dim, q_norm_w, k_norm_w, eps,
-                                       k_cache, v_cache, slot_mapping, Hq, Hkv, D)
+                                       k_cache, v_cache, slot_mapping, Hq, Hkv, D, mrope_axis)
     T = qkv.shape[0]
     num_slots = 0 if k_cache is None else k_cache.shape[0] * k_cache.shape[1]
+    if mrope_axis is not None:
+        rc = _native.lib().b200_qknorm_mrope_kvwrite(
+            qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), positions.stride(0),
+            mrope_axis.data_ptr(), cos_sin.data_ptr(), rot_dim,
+            _native.ptr(q_norm_w), _native.ptr(k_norm_w), eps, _native.ptr(k_cache),
+            _native.ptr(v_cache), _native.ptr(slot_mapping), T, Hq, Hkv, D, num_slots,
+            0 if k_cache is None else k_cache.shape[1], 0 if k_cache is None else kv_layout(k_cache),
+            _native.status_word(qkv.device).data_ptr(), _native.stream_ptr())
+        _native.check(rc, "qknorm_mrope_kvwrite")
+        launch_counter[0] += 1
+        return
     rc = _native.lib().b200_qknorm_rope_kvwrite(
         qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), cos_sin.data_ptr(), rot_dim,
         _native.ptr(q_norm_w), _native.ptr(k_norm_w), eps, _native.ptr(k_cache),

@@ -120,6 +120,41 @@ def apply_rope_neox(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Ten
     return out.to(x.dtype)
 
 
+def mrope_axis_table(sections, interleaved: bool = False) -> torch.Tensor:
+    """int32 [sum(sections)]: which position axis (0 temporal, 1 height, 2 width) each rotary
+    pair follows.  Sectioned layout: the first sections[0] pairs are temporal, then height, then
+    width (Qwen2-VL); interleaved layout: t h w t h w ... with the temporal axis taking what is
+    left once height / width are used up (Qwen3-VL).  Follows the index arithmetic of
+    vllm_ascend/ops/rotary_embedding.py:582-672 (the mrope paths)."""
+    half = int(sum(sections))
+    axis = torch.zeros(half, dtype=torch.int32)
+    if interleaved:
+        for a in (1, 2):
+            idx = torch.arange(a, sections[a] * 3, 3)
+            axis[idx[idx < half]] = a
+    else:
+        axis[sections[0]:sections[0] + sections[1]] = 1
+        axis[sections[0] + sections[1]:] = 2
+    return axis
+
+
+def apply_mrope_neox(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                     rot_dim: int, axis: torch.Tensor) -> torch.Tensor:
+    """x: [T, H, D]; positions int64 [3, >=T]; pair e rotates by the angle at positions[axis[e]]."""
+    T = x.shape[0]
+    half = rot_dim // 2
+    pos = positions[:, :T][axis.long()]                      # [half, T]
+    e = torch.arange(half, device=x.device).unsqueeze(1)
+    cos = cos_sin[pos, e].t().unsqueeze(1)                   # [T, 1, half]
+    sin = cos_sin[pos, e + half].t().unsqueeze(1)
+    xf = x.float()
+    x1, x2 = xf[..., :half], xf[..., half:rot_dim]
+    out = xf.clone()
+    out[..., :half] = x1 * cos - x2 * sin
+    out[..., half:rot_dim] = x2 * cos + x1 * sin
+    return out.to(x.dtype)
+
+
 def apply_rope_interleaved(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
                            rot_dim: int) -> torch.Tensor:
     """GPT-J style: pairs (2j, 2j+1); used by DeepSeek's rope slice."""
@@ -139,7 +174,8 @@ def apply_rope_interleaved(x: torch.Tensor, positions: torch.Tensor, cos_sin: to
 def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
                         rot_dim: int, q_norm_w, k_norm_w, eps: float,
                         k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                        slot_mapping: Optional[torch.Tensor], Hq: int, Hkv: int, D: int) -> None:
+                        slot_mapping: Optional[torch.Tensor], Hq: int, Hkv: int, D: int,
+                        mrope_axis: Optional[torch.Tensor] = None) -> None:
     """In place on qkv [T, (Hq+2Hkv)*D]; scatters k, v into the paged caches."""
     T = qkv.shape[0]
     q = qkv[:, :Hq * D].view(T, Hq, D)
@@ -149,7 +185,10 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: tor
         q.copy_(rms_norm(q, q_norm_w, eps)[0])
     if k_norm_w is not None:
         k.copy_(rms_norm(k, k_norm_w, eps)[0])
-    if rot_dim > 0:
+    if rot_dim > 0 and mrope_axis is not None:
+        q.copy_(apply_mrope_neox(q, positions, cos_sin, rot_dim, mrope_axis))
+        k.copy_(apply_mrope_neox(k, positions, cos_sin, rot_dim, mrope_axis))
+    elif rot_dim > 0:
         q.copy_(apply_rope_neox(q, positions, cos_sin, rot_dim))
         k.copy_(apply_rope_neox(k, positions, cos_sin, rot_dim))
     if k_cache is not None and slot_mapping is not None:
