@@ -37,6 +37,40 @@ def _llm(role, engine_id, port=0, dev=0):
                kv_transfer_config=ktc)
 
 
+def run_recording(llm, prompts, sp):
+    """generate() that also returns, per prompt, the KV rows of its first len-1 tokens (every layer,
+    K and V) as they sit in the paged cache when the request finishes prefill."""
+    eng = llm.engine
+    rids = [eng.add_request(p["prompt_token_ids"], sp, kv_transfer_params=p.get("kv_transfer_params"))
+            for p in prompts]
+    reqs = {r: eng.scheduler.requests[r] for r in rids}
+    blocks = {r: [] for r in rids}
+    while eng.has_unfinished():
+        eng.step()
+        for r, q in reqs.items():
+            if len(q.block_ids) > len(blocks[r]):
+                blocks[r] = list(q.block_ids)
+    rows = [kv_rows(llm, blocks[r], reqs[r].num_prompt_tokens - 1) for r in rids]
+    return [list(reqs[r].output_token_ids or []) for r in rids], rows, reqs
+
+
+def kv_rows(llm, block_ids, n):
+    """[2 * layers, n, H, D]: the first n token rows of a sequence's K and V in every layer."""
+    torch.cuda.synchronize()
+    runner = llm.engine.runner
+    idx = torch.tensor(list(block_ids), device=runner.device, dtype=torch.long)
+    per_layer = []
+    for pair in runner.kv_caches:
+        for c in pair:
+            g = c[idx]                                     # [nb, bs, H, D] logical
+            per_layer.append(g.reshape(-1, *g.shape[2:])[:n].float().cpu())
+    return torch.stack(per_layer)
+
+
+def kv_equal(a, b) -> bool:
+    return all(x.shape == y.shape and torch.equal(x, y) for x, y in zip(a, b))
+
+
 def prefill(d):
     torch.cuda.set_device(0)
     llm = _llm("kv_producer", "P", int(os.environ.get("KV_PORT", "0")))
@@ -63,7 +97,7 @@ def decode(d):
     torch.cuda.set_device(dev)
     sp = SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True)
     mono = _llm(None, "M", dev=dev)
-    want = [o.outputs[0].token_ids for o in mono.generate(_prompts(), sp)]
+    want, want_kv, _ = run_recording(mono, [{"prompt_token_ids": p} for p in _prompts()], sp)
     del mono
     llm = _llm("kv_consumer", "D", dev=dev)
     path = os.path.join(d, "params.json")
@@ -73,11 +107,11 @@ def decode(d):
             raise TimeoutError("prefill process never wrote its parameters")
         time.sleep(0.05)
     params = json.load(open(path))
-    got = llm.generate([{"prompt_token_ids": p, "kv_transfer_params": k}
-                        for p, k in zip(_prompts(), params)], sp)
+    got, got_kv, _ = run_recording(llm, [{"prompt_token_ids": p, "kv_transfer_params": k}
+                                         for p, k in zip(_prompts(), params)], sp)
     c = llm.engine.kv_connector
     modes = sorted({"ipc" if m.get("_base") else "other" for m in c._remote_meta.values()})
-    res = {"want": want, "got": [o.outputs[0].token_ids for o in got], "stats": c.stats, "modes": modes,
+    res = {"want": want, "got": got, "kv_equal": kv_equal(got_kv, want_kv), "stats": c.stats, "modes": modes,
            "prefill_tokens": int(llm.engine.runner.stats.get("num_prefill_tokens", -1))}
     c.close()
     time.sleep(0.3)          # let the done messages leave before the producer is told to stop

@@ -128,3 +128,23 @@ def test_vision_language_engine_on_gpu():
             assert llm.engine.runner.stats["graph_replays"] > 0
     assert outs[True] == outs[False]
     _native.check_status(torch.device("cuda"))
+
+
+def test_encoder_graph_replay_matches_eager():
+    from vllm_ascend_b200.compilation.encoder_graph import EncoderGraphManager
+    from vllm_ascend_b200.models.vision import VisionConfig, VisionTransformer
+    cfg = VisionConfig(depth=2, hidden_size=256, num_heads=4, intermediate_size=512, out_hidden_size=256,
+                       window_size=112, fullatt_block_indexes=[1], init_std=0.05)
+    tower = VisionTransformer(cfg, DEV, torch.bfloat16)
+    mgr = EncoderGraphManager(tower, bucket_sizes=(512, 2048))
+    g = torch.Generator().manual_seed(5)
+    for grid in ([[1, 16, 20]], [[1, 8, 8], [1, 12, 16]], [[1, 16, 20]], [[2, 24, 28]]):
+        grid = np.array(grid)
+        n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+        px = torch.randn(n, cfg.patch_dim, generator=g).to(DEV).bfloat16()
+        want = tower(px, grid).float()
+        got = mgr.run(px, grid).float()
+        assert got.shape == want.shape
+        assert (got - want).abs().max() < 2e-2 * want.abs().max()
+    assert mgr.stats["captures"] == 2 and mgr.stats["replays"] == 4
+    _native.check_status(torch.device(DEV))

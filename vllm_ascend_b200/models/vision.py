@@ -157,11 +157,11 @@ class VisionTransformer:
         self.inv_freq = 1.0 / (10000.0 ** (np.arange(0, q, dtype=np.float64) * 2 / (cfg.head_dim // 2)))
 
     # -- forward -------------------------------------------------------------
-    def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+    def host_inputs(self, grid_thw) -> dict:
+        """Index math of a batch of images (host): window permutation of the patches, rotary angle
+        tables, the per-frame and per-window sequence boundaries."""
         cfg = self.cfg
         grid = np.asarray(grid_thw, dtype=np.int64).reshape(-1, 3)
-        N = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
-        assert pixel_values.shape[0] == N, "pixel_values rows must equal the patch count of grid_thw"
         unit = cfg.merge_unit
         win_idx, cu_win = window_index(grid, cfg.window_size, cfg.spatial_merge_size, cfg.patch_size)
         pos = rot_pos_ids(grid, cfg.spatial_merge_size)                       # [N, 2]
@@ -169,14 +169,17 @@ class VisionTransformer:
         perm = (win_idx[:, None] * unit + np.arange(unit)[None, :]).reshape(-1)
         pos = pos[perm]
         ang = np.concatenate([pos[:, 0:1] * self.inv_freq[None], pos[:, 1:2] * self.inv_freq[None]], axis=1)
-        cos = torch.from_numpy(np.cos(ang)).float().to(self.device).contiguous()
-        sin = torch.from_numpy(np.sin(ang)).float().to(self.device).contiguous()
         cu_full = np.concatenate([[0], np.cumsum(np.repeat(grid[:, 1] * grid[:, 2], grid[:, 0]))])
-        plan_full = enc.make_plan(cu_full, self.device)
-        plan_win = enc.make_plan(cu_win, self.device)
+        return dict(n=int(perm.shape[0]), perm=perm, inverse=np.argsort(win_idx), cos=np.cos(ang).astype(np.float32),
+                    sin=np.sin(ang).astype(np.float32), cu_full=cu_full, cu_win=cu_win)
 
-        h = self.patch_embed(pixel_values.to(self.device, self.dtype))
-        h = h[torch.from_numpy(perm).to(self.device)]
+    def run(self, pixel_values: torch.Tensor, perm: torch.Tensor, inverse: torch.Tensor, cos: torch.Tensor,
+            sin: torch.Tensor, plan_full, plan_win) -> torch.Tensor:
+        """Device side of the tower (capturable: no host reads)."""
+        cfg = self.cfg
+        N, unit = pixel_values.shape[0], cfg.merge_unit
+        h = self.patch_embed(pixel_values)
+        h = h[perm]
         full = set(cfg.fullatt_block_indexes)
         for i, blk in enumerate(self.blocks):
             h = blk(h, plan_full if i in full else plan_win, cos, sin)
@@ -184,8 +187,16 @@ class VisionTransformer:
         x = self.merger_fc1(x.view(N // unit, -1))
         x = ops.activation(x, "gelu")
         x = self.merger_fc2(x)
-        inverse = np.argsort(win_idx)
-        return x[torch.from_numpy(inverse).to(self.device)]
+        return x[inverse]
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+        hi = self.host_inputs(grid_thw)
+        assert pixel_values.shape[0] == hi["n"], "pixel_values rows must equal the patch count of grid_thw"
+        dev = self.device
+        return self.run(pixel_values.to(dev, self.dtype), torch.from_numpy(hi["perm"]).to(dev),
+                        torch.from_numpy(hi["inverse"]).to(dev), torch.from_numpy(hi["cos"]).to(dev),
+                        torch.from_numpy(hi["sin"]).to(dev), enc.make_plan(hi["cu_full"], dev),
+                        enc.make_plan(hi["cu_win"], dev))
 
     __call__ = forward
 

@@ -67,6 +67,60 @@ def make_plan(cu_seqlens, device) -> EncoderAttnPlan:
     return plan
 
 
+class StaticEncoderPlan(EncoderAttnPlan):
+    """Plan with fixed-capacity device buffers, refreshed in place: what a captured CUDA graph of
+    the vision tower reads.  Unused sequence slots have length 0 and unused tiles point at such a
+    slot, which the kernel leaves at once; the temporary K / V cache has the capacity's block count."""
+
+    def __init__(self, max_tokens: int, max_seqs: int, device):
+        from ..attention.metadata import AttentionMetadata
+        device = torch.device(device)
+        self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        self.max_tiles = max_seqs + (max_tokens + _BLOCK - 1) // _BLOCK
+        self.max_blocks_per_seq = (max_tokens + _BLOCK - 1) // _BLOCK
+        self.cu_seqlens_cpu = np.zeros(max_seqs + 1, dtype=np.int32)
+        self.max_len = max_tokens
+        self.num_blocks = self.max_tiles
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=device)     # noqa: E731
+        self.slots = z((max_tokens,), torch.int64)
+        self._qsl, self._sl = z((max_seqs + 1,), torch.int32), z((max_seqs,), torch.int32)
+        self._bt = z((max_seqs, self.max_blocks_per_seq), torch.int32)
+        self._ts, self._tq = z((self.max_tiles,), torch.int32), z((self.max_tiles,), torch.int32)
+        self.meta = AttentionMetadata(
+            num_reqs=max_seqs, num_actual_tokens=max_tokens, max_query_len=max_tokens, max_seq_len=max_tokens,
+            query_start_loc=self._qsl, seq_lens=self._sl, block_table=self._bt, slot_mapping=self.slots,
+            positions=self.slots, query_start_loc_cpu=self.cu_seqlens_cpu, seq_lens_cpu=np.zeros(max_seqs, np.int32),
+            tile_seq=self._ts, tile_qoff=self._tq, num_tiles=self.max_tiles)
+
+    def update(self, cu_seqlens) -> None:
+        """cu_seqlens must end at max_tokens (the caller appends the padding rows as a sequence)."""
+        from ..attention.metadata import build_tile_worklist
+        cu = np.asarray(cu_seqlens, dtype=np.int64)
+        lens = np.diff(cu)
+        B = len(lens)
+        if B > self.max_seqs - 1 or int(cu[-1]) != self.max_tokens:
+            raise ValueError("sequence list does not fit the static plan")
+        nblk = (lens + _BLOCK - 1) // _BLOCK
+        blk_start = np.concatenate([[0], np.cumsum(nblk)[:-1]])
+        seq_of = np.repeat(np.arange(B), lens)
+        slots = blk_start[seq_of] * _BLOCK + (np.arange(self.max_tokens) - cu[:-1][seq_of])
+        qsl = np.full(self.max_seqs + 1, self.max_tokens, dtype=np.int32)
+        qsl[:B + 1] = cu
+        sl = np.zeros(self.max_seqs, dtype=np.int32)
+        sl[:B] = lens
+        bt = np.zeros((self.max_seqs, self.max_blocks_per_seq), dtype=np.int32)
+        for i, (s, n) in enumerate(zip(blk_start, nblk)):
+            bt[i, :n] = np.arange(s, s + n)
+        ts, tq = build_tile_worklist(lens.astype(np.int64), _BLOCK, lens.astype(np.int64))
+        tile_seq = np.full(self.max_tiles, self.max_seqs - 1, dtype=np.int32)     # an empty slot
+        tile_qoff = np.zeros(self.max_tiles, dtype=np.int32)
+        tile_seq[:len(ts)], tile_qoff[:len(ts)] = ts, tq
+        for dst, a in ((self.slots, slots), (self._qsl, qsl), (self._sl, sl), (self._bt, bt), (self._ts, tile_seq),
+                       (self._tq, tile_qoff)):
+            dst.copy_(torch.from_numpy(np.ascontiguousarray(a)).to(dst.dtype), non_blocking=True)
+        self.cu_seqlens_cpu = qsl
+
+
 def encoder_attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens,
                           scale: float) -> torch.Tensor:
     """fp32 definition: every token attends to all tokens of its own sequence."""
