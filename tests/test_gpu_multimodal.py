@@ -126,6 +126,7 @@ def test_vision_language_engine_on_gpu():
             assert llm.engine.runner.mm.stats["encoder_items"] == 2
         else:
             assert llm.engine.runner.stats["graph_replays"] > 0
+            assert llm.engine.runner.mm.encoder_graphs.stats["replays"] == 1
     assert outs[True] == outs[False]
     _native.check_status(torch.device("cuda"))
 

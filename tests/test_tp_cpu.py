@@ -19,8 +19,10 @@ WORKER = textwrap.dedent("""
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
     preset, tp, ep, pp, dcp = sys.argv[1], int(sys.argv[2]), sys.argv[3] == "1", int(sys.argv[4]), int(sys.argv[5])
+    pcp = int(sys.argv[6])
     cfg = get_model_config(preset)
     llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, enable_expert_parallel=ep, pipeline_parallel_size=pp, decode_context_parallel_size=dcp,
+              prefill_context_parallel_size=pcp,
               additional_config=dict(cp_kv_cache_interleave_size=4) if dcp > 1 else None,
               max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     rng = np.random.default_rng(2)
@@ -37,14 +39,14 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(preset, world, tp, ep=False, pp=1, dcp=1):
+def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1):
     script = WORKER.format(root=ROOT)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()),
                WORLD_SIZE=str(world), OMP_NUM_THREADS="2")
     procs = []
     for r in range(world):
         e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
-        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0", str(pp), str(dcp)],
+        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0", str(pp), str(dcp), str(pcp)],
                                       env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=300) for p in procs]
     for p, (o, e) in zip(procs, outs):
@@ -71,3 +73,25 @@ def test_pipeline_parallel_matches_single_rank(preset):
 def test_decode_context_parallel_matches_single_rank():
     # MLA latent cache sharded along the sequence over the 2 TP ranks
     assert _run("tiny-deepseek", 2, 2, dcp=2) == _run("tiny-deepseek", 1, 1)
+
+
+@pytest.mark.parametrize("preset,world,tp", [("tiny-qwen", 2, 1), ("tiny-moe", 2, 1), ("tiny-qwen", 4, 2)])
+def test_prefill_context_parallel_matches_single_rank(preset, world, tp):
+    # prompt chunks split head-tail over the PCP ranks, K / V all-gathered per layer, rank 0 samples
+    assert _run(preset, world, tp, pcp=2) == _run(preset, 1, 1)
+
+
+def test_pcp_partition_covers_every_token_once_and_balances_work():
+    from vllm_ascend_b200.attention.pcp import build_plan, split_ranges
+    starts, q_lens = np.array([0, 16, 40], dtype=np.int32), np.array([37, 1, 8], dtype=np.int32)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    plan = build_plan(starts, q_lens, cu, 4)
+    cover = np.concatenate(plan.local_idx)
+    split = np.concatenate([np.arange(cu[0], cu[1]), np.arange(cu[2], cu[3])])     # requests 0 and 2 are split
+    for t in split:
+        assert (cover == t).sum() == 1
+    assert (cover == cu[1]).sum() == 4                                             # the decode is replicated
+    # causal cost of a rank = sum over its queries of the key count: head + tail pieces even it out
+    cost = [sum(sum(range(a + 1, b + 1)) for a, b in split_ranges(0, 4096, 4, r)) for r in range(4)]
+    assert max(cost) / min(cost) < 1.01
+    assert any(e[2] == 37 for e in plan.entries[0]) and all(e[2] != 37 or e[0] != 0 for r in (1, 2, 3) for e in plan.entries[r])

@@ -53,6 +53,7 @@ class AttentionMetadata:
     has_initial_state: Optional[torch.Tensor] = None    # int32 [B] device
     # multimodal rotary embedding: int64 [3, num_input_tokens] (temporal, height, width)
     mrope_positions: Optional[torch.Tensor] = None
+    pcp: object = None                      # attention.pcp.PCPMeta on split prefill steps
     # decode-context-parallel / extras
     dcp_world_size: int = 1
     dcp_rank: int = 0

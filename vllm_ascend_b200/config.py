@@ -321,6 +321,7 @@ class ParallelConfig:
     data_parallel_size: int = 1
     enable_expert_parallel: bool = False
     decode_context_parallel_size: int = 1
+    prefill_context_parallel_size: int = 1
     enable_sequence_parallel: bool = False
     rank: int = 0
     local_rank: int = 0

@@ -76,7 +76,8 @@ class LLMEngine:
         # DP / PP engines exchange host-side state every step and run synchronously)
         self.async_scheduling = bool(want_async and self.runner.proposer is None and self.kv_connector is None
                                      and self.eplb is None and self.dp.world_size == 1
-                                     and pc.pipeline_parallel_size == 1)
+                                     and pc.pipeline_parallel_size == 1
+                                     and pc.prefill_context_parallel_size == 1)
         self.runner.capture_graphs()
         self._req_counter = itertools.count()
         self.eos_token_id: Optional[int] = None
@@ -258,7 +259,8 @@ class LLM:
                  kv_transfer_config: Optional[dict] = None, ec_transfer_config: Optional[dict] = None,
                  speculative_config: Optional[dict] = None, enable_sleep_mode: bool = False,
                  cudagraph_capture_sizes: Optional[list] = None,
-                 decode_context_parallel_size: int = 1, enable_lora: bool = False, max_loras: int = 4,
+                 decode_context_parallel_size: int = 1, prefill_context_parallel_size: int = 1,
+                 enable_lora: bool = False, max_loras: int = 4,
                  max_lora_rank: int = 64, async_scheduling: Optional[bool] = None, load_format: str = "auto",
                  model_loader_extra_config: Optional[dict] = None, **unused):
         mcfg = model if isinstance(model, ModelConfig) else get_model_config(model)
@@ -286,7 +288,8 @@ class LLM:
             parallel=ParallelConfig(tensor_parallel_size=tensor_parallel_size,
                                     pipeline_parallel_size=pipeline_parallel_size,
                                     enable_expert_parallel=enable_expert_parallel,
-                                    decode_context_parallel_size=decode_context_parallel_size),
+                                    decode_context_parallel_size=decode_context_parallel_size,
+                                    prefill_context_parallel_size=prefill_context_parallel_size),
             compilation=CompilationConfig(
                 cudagraph_mode="NONE" if enforce_eager else "FULL_DECODE_ONLY",
                 cudagraph_capture_sizes=cudagraph_capture_sizes),

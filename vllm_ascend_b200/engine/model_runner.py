@@ -72,6 +72,9 @@ class ModelRunner:
         # room for one extra token per sequence: draft-model catch-up passes append the newly
         # sampled token of every request to a full step
         T, B = self.max_tokens + self.max_seqs, self.max_seqs
+        from ..parallel import state as _ps0
+        if _ps0.get_pcp_group().world_size > 1:
+            B *= 2            # prefill context parallel: a request contributes up to two batch entries
         i64, i32 = torch.int64, torch.int32
         self.input_ids = torch.zeros(T, dtype=i64, device=device)
         self.positions = torch.zeros(T, dtype=i64, device=device)
@@ -108,6 +111,10 @@ class ModelRunner:
         self.dcp_interleave = int((cfg.additional_config or {}).get("cp_kv_cache_interleave_size", 1))
         if self.dcp_size > 1 and not cfg.model.use_mla:
             raise NotImplementedError("decode context parallelism is implemented for MLA models")
+        self.pcp = _ps.get_pcp_group()
+        if self.pcp.world_size > 1 and (cfg.model.use_mla or cfg.model.is_hybrid or cfg.model.is_multimodal):
+            raise NotImplementedError("prefill context parallelism is implemented for GQA decoder models")
+        self._pcp_bcast = False          # this step's tokens come from PCP rank 0
         self.proposer = None
         self.last_hidden = None      # final hidden states of the latest step, scheduling order
         self.rejection_sampler = None
@@ -140,6 +147,9 @@ class ModelRunner:
         if self.mcfg.is_multimodal and self.model.is_first:
             from .mm_runner import MultimodalState
             self.mm = MultimodalState(self)
+            if self.is_cuda and self.cfg.compilation.cudagraph_mode != "NONE":
+                from ..compilation.encoder_graph import EncoderGraphManager
+                self.mm.encoder_graphs = EncoderGraphManager(self.model.visual)
 
     def _attn_layer(self):
         """First layer with a paged KV cache (hybrid models start with recurrent layers)."""
@@ -302,6 +312,34 @@ class ModelRunner:
         else:
             blk = self.block_table_cpu[tok_rows, pos // self.block_size].astype(np.int64)
             slots = blk * self.block_size + pos % self.block_size
+        pcp_meta = None
+        self._pcp_bcast = False
+        g_cu, g_starts, g_qlens = cu, starts, q_lens       # per request, global token order
+        inv = None
+        P = self.pcp.world_size
+        if P > 1 and pad_to is None and B and int(q_lens.max()) >= 2 * P:
+            # split prefill step: keep this rank's share of the tokens; the attention batch gets one
+            # entry per (request, piece) and K / V of all ranks are gathered inside the layers
+            from ..attention.pcp import PCPMeta, build_plan
+            plan = build_plan(starts, q_lens, cu, P)
+            me = self.pcp.rank_in_group
+            loc = plan.local_idx[me]
+            gslots = np.full(P * plan.t_max, -1, dtype=np.int64)
+            for r_, idx_ in enumerate(plan.local_idx):
+                gslots[r_ * plan.t_max:r_ * plan.t_max + len(idx_)] = slots[idx_]
+            pcp_meta = PCPMeta(self.pcp, plan.t_max, torch.from_numpy(gslots).to(self.device))
+            inv = np.full(T, -1, dtype=np.int64)
+            inv[loc] = np.arange(len(loc))
+            ids, pos, slots = ids[loc], pos[loc], slots[loc]
+            ent = plan.entries[me]
+            e_req = np.fromiter((e[0] for e in ent), dtype=np.int64, count=len(ent))
+            starts = np.fromiter((e[1] for e in ent), dtype=np.int32, count=len(ent))
+            q_lens = np.fromiter((e[2] - e[1] for e in ent), dtype=np.int32, count=len(ent))
+            rows = rows[e_req]
+            B, T = len(ent), len(loc)
+            cu = np.zeros(B + 1, dtype=np.int32)
+            np.cumsum(q_lens, out=cu[1:])
+            self._pcp_bcast = True
         seq_lens = starts + q_lens
         Bp = pad_to or B
         Tp = T + (Bp - B)                       # padded rows carry one dummy token each
@@ -349,6 +387,7 @@ class ModelRunner:
             attn_state=state, num_decodes=nd, num_decode_tokens=ndt, num_prefills=npf,
             num_input_tokens=Tp)
         meta.dcp_interleave = self.dcp_interleave
+        meta.pcp = pcp_meta
         if self.mm is not None:
             self.mm.prepare(reqs, starts, q_lens, cu, pos, req_idx, T, Tp, meta)
         if self.mcfg.is_hybrid:
@@ -389,14 +428,19 @@ class ModelRunner:
         sel = []
         rows_per_req = []
         for i, r in enumerate(reqs):
-            end = int(starts[i] + q_lens[i])
+            end = int(g_starts[i] + g_qlens[i])
             ntok = r.num_tokens + getattr(r, "num_inflight", 0)   # incl. a token still being sampled
             if end >= ntok:
                 nrow = end - ntok + 1                  # 1 + draft tokens verified in this step
-                base = int(cu[i + 1]) - nrow
+                base = int(g_cu[i + 1]) - nrow
                 sel.extend(range(base, base + nrow))
                 sample_reqs.append(r)
                 rows_per_req.append(nrow)
+        if inv is not None:
+            # rows of this rank's hidden states; the last token of every chunk sits on PCP rank 0
+            sel = [int(inv[g]) for g in sel]
+            if self.pcp.rank_in_group != 0:
+                sel = [-1] * len(sel)
         self._sample_rows = rows_per_req
         return meta, T, Tp, sel, sample_reqs
 
@@ -490,6 +534,8 @@ class ModelRunner:
             self.stats["eager_steps"] += 1
             if not sel:
                 return {}
+            if self._pcp_bcast:
+                return self._sample_pcp(hidden, sel, sample_reqs)
             if len(sel) == T:
                 h_sel = hidden[:T]
             else:
@@ -530,6 +576,27 @@ class ModelRunner:
             row = r.row
             self.token_ids_cpu[row, r.num_tokens] = t
             out[r.request_id] = [t]
+        return out
+
+    def _sample_pcp(self, hidden: torch.Tensor, sel: list, sample_reqs: list) -> dict:
+        """Split prefill step: PCP rank 0 holds the last token of every chunk, samples, and sends
+        the token ids to the other ranks of the group."""
+        n = len(sel)
+        if self.pcp.rank_in_group == 0:
+            h_sel = hidden[torch.tensor(sel, dtype=torch.int64, device=self.device)]
+            logits = self.model.compute_logits(h_sel)
+            md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
+            if not md.all_greedy and not self.is_cuda:
+                md.generator = self._cpu_generator()
+            tokens = self.sampler(logits, md).to(torch.int64)
+        else:
+            tokens = torch.zeros(n, dtype=torch.int64, device=self.device)
+        tokens = self.pcp.broadcast(tokens.contiguous(), src=0)
+        toks = tokens.cpu().numpy()
+        out = {}
+        for r, t in zip(sample_reqs, toks):
+            self.token_ids_cpu[r.row, r.num_tokens] = int(t)
+            out[r.request_id] = [int(t)]
         return out
 
     # ------------------------------------------------------------------ asynchronous stepping
@@ -773,6 +840,8 @@ class ModelRunner:
         self.capture_sizes = []
         if self.graph_wrapper is not None:
             self.graph_wrapper.clear()
+        if self.mm is not None and self.mm.encoder_graphs is not None:
+            self.mm.encoder_graphs.buckets.clear()
 
     @torch.inference_mode()
     def capture_graphs(self) -> None:

@@ -312,11 +312,19 @@ class GQAAttention:
         qkv = self.qkv_proj(x)
         k_cache, v_cache = kv_cache
         mpos = getattr(meta, "mrope_positions", None) if self.mrope_axis is not None else None
+        pcp = getattr(meta, "pcp", None)
         ops.qknorm_rope_kvwrite(qkv, meta.positions if mpos is None else mpos, self.cos_sin,
                                 self.rot_dim, self.q_norm,
-                                self.k_norm, self.cfg.rms_norm_eps, k_cache, v_cache,
+                                self.k_norm, self.cfg.rms_norm_eps,
+                                k_cache if pcp is None else None, v_cache if pcp is None else None,
                                 meta.slot_mapping, self.Hq, self.Hkv, self.D,
                                 mrope_axis=None if mpos is None else self.mrope_axis)
+        if pcp is not None:
+            # prefill context parallel: this rank rotated its share of the tokens; the cache gets
+            # the K / V rows of all ranks
+            from ..attention.pcp import gather_kv_into_cache
+            gather_kv_into_cache(qkv[:, self.Hq * self.D:], pcp, k_cache, v_cache, self.Hkv, self.D,
+                                 self.cfg.rms_norm_eps, self.cos_sin)
         T = qkv.shape[0]
         q = qkv[:, :self.Hq * self.D].view(T, self.Hq, self.D)
         o = ops.paged_attention(q, k_cache, v_cache, meta, self.scale, causal=True,

@@ -126,6 +126,7 @@ class ParallelState:
     dp: Optional[GroupCoordinator] = None
     ep: Optional[GroupCoordinator] = None
     dcp: Optional[GroupCoordinator] = None
+    pcp: Optional[GroupCoordinator] = None
     extra: dict = field(default_factory=dict)   # mc2, dynamic_eplb, p_tp, otp, lmtp, embed_tp, mlp_tp
 
 
@@ -133,20 +134,25 @@ _STATE = ParallelState()
 _SINGLE = GroupCoordinator("single", [0], 0)
 
 
-def _layout(world_size: int, tp: int, pp: int, dp: int) -> torch.Tensor:
-    assert world_size == tp * pp * dp, (world_size, tp, pp, dp)
-    return torch.arange(world_size).reshape(dp, pp, tp)
+def _layout(world_size: int, tp: int, pp: int, dp: int, pcp: int = 1) -> torch.Tensor:
+    assert world_size == tp * pp * dp * pcp, (world_size, tp, pp, dp, pcp)
+    return torch.arange(world_size).reshape(dp, pp, pcp * tp)
 
 
-def group_rank_lists(world_size: int, tp: int, pp: int = 1, dp: int = 1) -> dict[str, list[list[int]]]:
-    """Pure function (unit-testable without torch.distributed)."""
-    lay = _layout(world_size, tp, pp, dp)
+def group_rank_lists(world_size: int, tp: int, pp: int = 1, dp: int = 1, pcp: int = 1) -> dict[str, list[list[int]]]:
+    """Pure function (unit-testable without torch.distributed).  Rank order, outermost first:
+    data, pipeline, prefill-context, tensor.  A prefill-context group joins the ranks that hold the
+    same tensor shard of the same replica and stage."""
+    lay = _layout(world_size, tp, pp, dp, pcp)
+    wide = pcp * tp                                   # ranks of one (replica, stage)
+    lay4 = lay.reshape(dp, pp, pcp, tp)
     return {
         "tp": lay.reshape(-1, tp).tolist(),
         "pp": lay.transpose(1, 2).reshape(-1, pp).tolist(),
         "dp": lay.permute(1, 2, 0).reshape(-1, dp).tolist(),
-        # experts are sharded over DP x TP inside one PP stage
-        "ep": lay.transpose(0, 1).reshape(pp, dp * tp).tolist(),
+        "pcp": lay4.transpose(2, 3).reshape(-1, pcp).tolist(),
+        # experts are sharded over DP x PCP x TP inside one PP stage
+        "ep": lay.transpose(0, 1).reshape(pp, dp * wide).tolist(),
     }
 
 
@@ -207,18 +213,18 @@ def init_distributed(backend: Optional[str] = None, timeout_s: Optional[float] =
 def initialize_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, dcp: int = 1,
                               backend: Optional[str] = None,
                               finegrained: Optional[dict] = None,
-                              timeout_s: Optional[float] = None) -> ParallelState:
+                              timeout_s: Optional[float] = None, pcp: int = 1) -> ParallelState:
     global _STATE
     world_size = dist.get_world_size() if dist.is_initialized() else 1
     rank = dist.get_rank() if dist.is_initialized() else 0
     if world_size == 1:
         _STATE = ParallelState(world=_SINGLE, tp=_SINGLE, pp=_SINGLE, dp=_SINGLE, ep=_SINGLE,
-                               dcp=_SINGLE)
+                               dcp=_SINGLE, pcp=_SINGLE)
         return _STATE
     if backend is None:
         backend = dist.get_backend()
     timeout = timedelta(seconds=timeout_s) if timeout_s else None
-    lists = group_rank_lists(world_size, tp, pp, dp)
+    lists = group_rank_lists(world_size, tp, pp, dp, pcp)
     st = ParallelState()
     st.world = _make("world", [list(range(world_size))], rank, backend, timeout)
     st.tp = _make("tp", lists["tp"], rank, backend, timeout)
@@ -231,6 +237,7 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, dcp: int = 
         st.dcp = _make("dcp", dl, rank, backend, timeout)
     else:
         st.dcp = GroupCoordinator("dcp", [rank], 0)
+    st.pcp = _make("pcp", lists["pcp"], rank, backend, timeout) if pcp > 1 else GroupCoordinator("pcp", [rank], 0)
     st.extra["mc2"] = st.ep                      # same ranks as EP, as in the reference
     st.extra["dynamic_eplb"] = _make("dynamic_eplb", lists["ep"], rank, backend, timeout)
     for key, size in (finegrained or {}).items():
@@ -273,6 +280,10 @@ def get_ep_group() -> GroupCoordinator:
 
 def get_dcp_group() -> GroupCoordinator:
     return _get("dcp")
+
+
+def get_pcp_group() -> GroupCoordinator:
+    return _get("pcp")
 
 
 def get_world_group() -> GroupCoordinator:

@@ -298,6 +298,11 @@ def check_and_update_config(engine_cfg) -> B200Config:
     if mc.num_attention_heads % pc.tensor_parallel_size:
         raise ValueError(f"num_attention_heads={mc.num_attention_heads} not divisible by "
                          f"tp={pc.tensor_parallel_size}")
+    if pc.prefill_context_parallel_size > 1:
+        if engine_cfg.speculative_config:
+            raise ValueError("prefill context parallelism cannot be combined with speculative decoding")
+        if pc.pipeline_parallel_size > 1:
+            raise ValueError("prefill context parallelism cannot be combined with pipeline parallelism")
     if pc.decode_context_parallel_size > 1 and pc.tensor_parallel_size % pc.decode_context_parallel_size:
         raise ValueError("decode_context_parallel_size must divide tensor_parallel_size")
     if pc.enable_expert_parallel and not mc.is_moe:

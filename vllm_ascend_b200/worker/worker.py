@@ -63,12 +63,13 @@ class B200Worker:
         else:
             self.device = torch.device("cpu")
         if world > 1:
-            dp = max(1, world // (pc.tensor_parallel_size * pc.pipeline_parallel_size))
+            pcp = max(1, pc.prefill_context_parallel_size)
+            dp = max(1, world // (pc.tensor_parallel_size * pc.pipeline_parallel_size * pcp))
             pc.data_parallel_size = dp
             from ..platform_config import finegrained_sizes
             pstate.initialize_model_parallel(pc.tensor_parallel_size, pc.pipeline_parallel_size, dp,
                                              pc.decode_context_parallel_size,
-                                             finegrained=finegrained_sizes(cfg.additional_config))
+                                             finegrained=finegrained_sizes(cfg.additional_config), pcp=pcp)
         else:
             pstate.initialize_model_parallel()
         from ..engine.model_runner import ModelRunner
@@ -98,7 +99,8 @@ class B200Worker:
             self.offloader = PrefetchOffloader(self.runner.model, oc.group_size, oc.num_in_group, oc.prefetch_step)
         # the fused sequence-sharded TP path has no adapter hook: LoRA engines use the NCCL path
         if self.world_size > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM == "fused" \
-                and pc.tensor_parallel_size > 1 and not cfg.enable_lora:
+                and pc.tensor_parallel_size > 1 and not cfg.enable_lora \
+                and pc.prefill_context_parallel_size == 1:
             from ..parallel import fused_linear
             fused_linear.attach(self.runner.model, cfg, self.device)
 
