@@ -20,14 +20,17 @@ WORKER = textwrap.dedent("""
     from vllm_ascend_b200.engine.request import SamplingParams
     preset, tp, ep, pp, dcp = sys.argv[1], int(sys.argv[2]), sys.argv[3] == "1", int(sys.argv[4]), int(sys.argv[5])
     pcp = int(sys.argv[6])
+    fg = json.loads(sys.argv[7]) if len(sys.argv) > 7 else None
     cfg = get_model_config(preset)
     llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, enable_expert_parallel=ep, pipeline_parallel_size=pp, decode_context_parallel_size=dcp,
               prefill_context_parallel_size=pcp,
-              additional_config=dict(cp_kv_cache_interleave_size=4) if dcp > 1 else None,
+              additional_config=dict(cp_kv_cache_interleave_size=4) if dcp > 1 else (dict(finegrained_tp_config=fg) if fg else None),
               max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     rng = np.random.default_rng(2)
     prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(3)]
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    if fg:                 # data parallel: every rank reports the prompts it served
+        print("PART " + json.dumps(dict((str(o.prompt_token_ids[:3]), o.outputs[0].token_ids) for o in outs)), flush=True)
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps([o.outputs[0].token_ids for o in outs]), flush=True)
 """)
@@ -39,18 +42,25 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1):
+def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1, fg=None):
     script = WORKER.format(root=ROOT)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()),
                WORLD_SIZE=str(world), OMP_NUM_THREADS="2")
     procs = []
     for r in range(world):
         e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
-        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0", str(pp), str(dcp), str(pcp)],
+        procs.append(subprocess.Popen([sys.executable, "-c", script, preset, str(tp), "1" if ep else "0", str(pp), str(dcp), str(pcp)] + ([json.dumps(fg)] if fg else []),
                                       env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     outs = [p.communicate(timeout=300) for p in procs]
     for p, (o, e) in zip(procs, outs):
         assert p.returncode == 0, e[-3000:]
+    if fg:
+        merged = {}
+        for o, _ in outs:
+            for l in o.splitlines():
+                if l.startswith("PART "):
+                    merged.update(json.loads(l[5:]))
+        return merged
     line = [l for l in outs[0][0].splitlines() if l.startswith("RESULT ")][-1]
     return json.loads(line[7:])
 
@@ -95,3 +105,14 @@ def test_pcp_partition_covers_every_token_once_and_balances_work():
     cost = [sum(sum(range(a + 1, b + 1)) for a, b in split_ranges(0, 4096, 4, r)) for r in range(4)]
     assert max(cost) / min(cost) < 1.01
     assert any(e[2] == 37 for e in plan.entries[0]) and all(e[2] != 37 or e[0] != 0 for r in (1, 2, 3) for e in plan.entries[r])
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen", "tiny-llama"])
+def test_finegrained_tp_over_dp_replicas_matches_single_rank(preset):
+    """Two DP replicas (tp=1) share o_proj, MLP, LM head and embedding shards; replicas serve
+    different prompts with different token counts per step."""
+    fg = dict(oproj_tensor_parallel_size=2, mlp_tensor_parallel_size=2, lmhead_tensor_parallel_size=2,
+              embedding_tensor_parallel_size=2)
+    got = _run(preset, 2, 1, fg=fg)
+    want = _run(preset, 1, 1)
+    assert len(got) == 3 and sorted(got.values()) == sorted(want)

@@ -202,12 +202,17 @@ class LLMEngine:
         busy = self.scheduler.has_unfinished()
         so = self.scheduler.schedule() if busy else None
         ntok = so.num_scheduled_tokens if so is not None else 0
-        sync = torch.tensor([int(busy), max(ntok, 1)], dtype=torch.int32)
+        nrows = 0 if so is None else sum(1 for r, n in so.scheduled if r.num_computed_tokens + n >= r.num_tokens)
+        sync = torch.tensor([int(busy), max(ntok, 1), nrows], dtype=torch.int32)
         dist.all_reduce(sync, op=dist.ReduceOp.MAX, group=self.dp.cpu_group)
         if int(sync[0]) == 0:
             return False
         if self.moe_runtime is not None:
             self.moe_runtime.max_tokens_across_dp = int(sync[1])
+        from ..parallel.finegrained import get_fg
+        fg = get_fg()
+        if fg is not None:           # pad targets of the fine-grained TP collectives in this step
+            fg.max_tokens, fg.max_rows = int(sync[1]), int(sync[2])
         t1 = time.perf_counter()
         if so is None or so.is_empty:
             self.runner.execute_dummy()

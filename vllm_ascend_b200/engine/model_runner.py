@@ -533,6 +533,7 @@ class ModelRunner:
             self.last_hidden = hidden
             self.stats["eager_steps"] += 1
             if not sel:
+                self._meet_lm_head(hidden)
                 return {}
             if self._pcp_bcast:
                 return self._sample_pcp(hidden, sel, sample_reqs)
@@ -785,7 +786,16 @@ class ModelRunner:
         data-parallel ranks so collectives inside the model still match up."""
         meta, T, Tp, _, _ = self._dummy_meta(1, 1)
         meta.slot_mapping.fill_(-1)
-        self._forward(Tp, meta)
+        hidden = self._forward(Tp, meta)
+        self._meet_lm_head(hidden)
+
+    def _meet_lm_head(self, hidden: torch.Tensor) -> None:
+        """A rank with nothing to sample still joins the LM head's collectives when the head is
+        sharded over a fine-grained TP group."""
+        from ..parallel.finegrained import get_fg
+        fg = get_fg()
+        if fg is not None and fg.lmtp is not None and self.model.is_last:
+            self.model.compute_logits(hidden[:0])
 
     def total_launches(self) -> int:
         """Launches of this package's own kernels so far (eager + inside replayed graphs)."""
@@ -825,6 +835,9 @@ class ModelRunner:
         B = min(self.max_seqs, 8)
         q = max(1, min(self.max_tokens // B, self.max_model_len - 1, 256))
         meta, T, Tp, _, _ = self._dummy_meta(B, q)
+        from ..parallel.finegrained import get_fg
+        if get_fg() is not None:            # every rank warms up with the same shapes
+            get_fg().max_tokens, get_fg().max_rows = Tp, B
         meta.slot_mapping.fill_(-1)
         h = self._forward(Tp, meta)
         self.model.compute_logits(h[:B])

@@ -234,10 +234,21 @@ class DecoderLayer:
             self.self_attn = GatedDeltaNet(pf, cfg, idx, comm)
         else:
             self.self_attn = (MLAAttention if cfg.use_mla else GQAAttention)(pf, cfg, idx, comm, max_pos)
+        from ..parallel import finegrained as fgm
+        fg = fgm.get_fg()
         if cfg.is_moe_layer(idx):
             self.mlp = SparseMoeBlock(pf, cfg, idx, comm, ep_group, moe_runtime)
+        elif fg is not None and fg.mlp_tp is not None:
+            inner = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, TPComm(fg.mlp_tp),
+                              reduce_results=False)
+            self.mlp = fgm.FGMLP(inner, fg.mlp_tp)
         else:
             self.mlp = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm)
+        if fg is not None and fg.otp is not None and isinstance(self.self_attn, GQAAttention):
+            a = self.self_attn
+            inner = RowParallelLinear(pf, f"{p}.self_attn.o_proj", cfg.num_attention_heads * a.D, cfg.hidden_size,
+                                      TPComm(fg.otp), reduce_results=False)
+            a.o_proj = fgm.FGOProj(inner, fg.otp)
 
     def __call__(self, h, residual, meta, kv_cache):
         # a norm whose only consumer is an fp8 GEMM emits fp8 + scales directly
@@ -285,16 +296,26 @@ class CausalLM:
         self.layer_range = (lo, hi)
         self.is_first = lo == 0
         self.is_last = hi == cfg.num_hidden_layers
-        self.embed_tokens = VocabParallelEmbedding(pf, "model.embed_tokens", cfg.vocab_size,
-                                                   cfg.hidden_size, self.comm)
+        from ..parallel import finegrained as fgm
+        fg = fgm.get_fg()
+        if fg is not None and cfg.tie_word_embeddings and (fg.lmtp is not None or fg.embed_tp is not None) \
+                and getattr(fg.lmtp, "ranks", None) != getattr(fg.embed_tp, "ranks", None):
+            raise ValueError("tied embeddings need the same group for lmhead and embedding tensor parallelism")
+        self.embed_tokens = VocabParallelEmbedding(pf, "model.embed_tokens", cfg.vocab_size, cfg.hidden_size,
+                                                   TPComm(fg.embed_tp) if fg and fg.embed_tp else self.comm)
         self.layers = [DecoderLayer(pf, cfg, i, self.comm, max_pos, ep_group, moe_runtime)
                        for i in range(lo, hi)]
         self.norm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
         if cfg.tie_word_embeddings:
             self.lm_head = ParallelLMHead(self.embed_tokens)
         else:
-            head = VocabParallelEmbedding(pf, "lm_head", cfg.vocab_size, cfg.hidden_size, self.comm)
+            head = VocabParallelEmbedding(pf, "lm_head", cfg.vocab_size, cfg.hidden_size,
+                                          TPComm(fg.lmtp) if fg and fg.lmtp else self.comm)
             self.lm_head = ParallelLMHead(head)
+        if fg is not None and fg.lmtp is not None:
+            self.lm_head = fgm.FGLMHead(self.lm_head, fg.lmtp)
+        if fg is not None and fg.embed_tp is not None:
+            self.embed_tokens = fgm.FGEmbedding(self.embed_tokens, fg.embed_tp)
         if cfg.quantization:
             from ..quantization import apply_quantization
             apply_quantization(self, cfg)
@@ -337,6 +358,7 @@ class CausalLM:
             for attr in ("qkv_proj", "o_proj", "q_a_proj", "q_b_proj", "q_proj", "kv_a_proj",
                          "kv_b_proj"):
                 lin = getattr(a, attr, None)
+                lin = getattr(lin, "inner", lin)            # fine-grained TP wrapper
                 if isinstance(lin, Linear):
                     for n, t in lin.named_tensors():
                         yield f"{p}.self_attn.{attr}.{n}", t
@@ -424,7 +446,8 @@ class CausalLM:
             if target not in params:
                 continue
             dst = params[target]
-            self._copy_shard(target, dst, w, shard_id, tp, r)
+            tp_t, r_t = self._shard_of(target, tp, r)
+            self._copy_shard(target, dst, w, shard_id, tp_t, r_t)
             loaded.add(name)
         for L in self.layers:
             if isinstance(L.self_attn, MLAAttention):
@@ -433,6 +456,24 @@ class CausalLM:
             if hasattr(L.mlp, "_gate_bf16"):
                 L.mlp._gate_bf16 = None
         return loaded
+
+    def _shard_of(self, target: str, tp: int, r: int) -> tuple[int, int]:
+        """(group size, rank) a parameter is sharded over: the TP group unless fine-grained TP
+        gives the module a group of its own."""
+        from ..parallel import finegrained as fgm
+        fg = fgm.get_fg()
+        if fg is None:
+            return tp, r
+        g = None
+        if ".mlp." in target and ".experts." not in target and "shared_experts" not in target:
+            g = fg.mlp_tp
+        elif ".self_attn.o_proj." in target:
+            g = fg.otp
+        elif target.startswith("lm_head"):
+            g = fg.lmtp
+        elif "embed_tokens" in target:
+            g = fg.embed_tp
+        return (g.world_size, g.rank_in_group) if g is not None else (tp, r)
 
     def _copy_shard(self, target: str, dst: torch.Tensor, w: torch.Tensor, shard_id, tp: int, r: int):
         cfg = self.cfg

@@ -315,7 +315,17 @@ def check_and_update_config(engine_cfg) -> B200Config:
             cc.cudagraph_mode = "NONE"
             from .batch_invariant import enable_batch_invariant_mode
             enable_batch_invariant_mode()
-    _validate_finegrained(cfg, pc.tensor_parallel_size, max(1, pc.data_parallel_size))
+    dp_size = max(1, pc.data_parallel_size)
+    if dp_size == 1:      # under a launcher the DP size follows from the world size
+        import os
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        dp_size = max(1, world // (pc.tensor_parallel_size * pc.pipeline_parallel_size
+                                   * max(1, pc.prefill_context_parallel_size)))
+    _validate_finegrained(cfg, pc.tensor_parallel_size, dp_size)
+    if any(finegrained_sizes(engine_cfg.additional_config).values()):
+        if pc.tensor_parallel_size != 1:
+            raise ValueError("fine-grained tensor parallelism shards replicated modules of tp=1 replicas")
+        cc.cudagraph_mode = "NONE"        # token counts differ per replica and are padded per step
     _validate_eplb(cfg.eplb_config, mc.is_moe, pc.enable_expert_parallel)
     _validate_scheduler_ext(cfg.scheduler_config, engine_cfg)
     if mc.is_hybrid and engine_cfg.cache.enable_prefix_caching:

@@ -72,6 +72,8 @@ class B200Worker:
                                              finegrained=finegrained_sizes(cfg.additional_config), pcp=pcp)
         else:
             pstate.initialize_model_parallel()
+        from ..parallel import finegrained
+        finegrained.init_from_groups()
         from ..engine.model_runner import ModelRunner
         self.runner = ModelRunner(cfg, self.device)
 
