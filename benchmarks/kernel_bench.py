@@ -153,6 +153,32 @@ def bench_mla_decode(a):
     _native.check_status(dev)
 
 
+def bench_gdn(a):
+    """Gated delta rule: decode (B sequences, one token each: state traffic bound) and one prefill
+    chunk (sequential over tokens: latency bound)."""
+    from vllm_ascend_b200.ops import linear_attn as la
+    dev = torch.device("cuda")
+    Hk, Hv, DK, DV = 16, 32, 128, 128
+    hbm, tf, tag = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for B, q_len in ((a.batch, 1), (max(1, a.batch // 64), a.seq)):
+        T = B * q_len
+        q = torch.randn(T, Hk, DK, device=dev, generator=g).bfloat16()
+        k = torch.randn(T, Hk, DK, device=dev, generator=g).bfloat16()
+        v = torch.randn(T, Hv, DV, device=dev, generator=g).bfloat16()
+        gg = -torch.rand(T, Hv, device=dev, generator=g) * 0.3
+        beta = torch.rand(T, Hv, device=dev, generator=g)
+        S = torch.randn(B + 1, Hv, DK, DV, device=dev, generator=g) * 0.1
+        cu = torch.arange(0, T + 1, q_len, dtype=torch.int32, device=dev)
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        init = torch.ones(B, dtype=torch.int32, device=dev)
+        ms = timeit(lambda: la.gated_delta_rule(q, k, v, gg, beta, S, cu, slots, init, DK ** -0.5), a.iters)
+        state_bytes = 2.0 * B * Hv * DK * DV * 4
+        print(f"gated-delta-rule B={B} q_len={q_len} Hv={Hv} {DK}x{DV}: {ms:.4f} ms  state {state_bytes / ms / 1e6:.0f} GB/s "
+              f"({state_bytes / ms / 1e6 / hbm:.2f} {tag})  {T / ms * 1e3:.0f} tok/s", flush=True)
+    _native.check_status(dev)
+
+
 def bench_attn_prefill(a):
     from gpu_utils import make_paged_case
     B, S = a.batch, a.seq
@@ -189,7 +215,7 @@ def bench_norm(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-fp8", "attn-decode", "attn-prefill", "mla-decode", "norm", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm-fp8", "attn-decode", "attn-prefill", "mla-decode", "gdn", "norm", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -230,6 +256,8 @@ def main():
                 bench_attn_decode(a)
         else:
             bench_attn_decode(a)
+    if a.what == "gdn":
+        bench_gdn(a)
     if a.what in ("attn-prefill", "all"):
         if a.what == "all":
             a.ctx = 0

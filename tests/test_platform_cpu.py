@@ -256,3 +256,22 @@ def test_dyntra_lb_moves_waiting_requests_to_the_idle_rank():
     assert all(r.origin_rank == 0 and r.client_index is not None for r in moved)
     # the oldest requests stay where they arrived
     assert s[0].waiting[0].request_id == "r0"
+
+
+def test_training_consistent_attention_backend_selection():
+    from vllm_ascend_b200.attention.backend import B200FABackend, training_consistent_attention
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    from vllm_ascend_b200.platform import B200Platform
+    add = {"rl_config": {"enabled": True, "enable_training_consistency": True}}
+    llm = LLM("tiny-qwen", device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32,
+              block_size=16, additional_config=add)
+    assert training_consistent_attention()
+    assert B200Platform.get_attn_backend_cls(use_mla=False).endswith("B200FABackend")
+    with pytest.raises(ValueError):
+        B200Platform.get_attn_backend_cls(use_mla=True)
+    assert B200FABackend.get_name() == "B200_TCGEN05_CONSISTENT"
+    a = [o.outputs[0].token_ids for o in llm.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=4))]
+    plain = LLM("tiny-qwen", device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
+    assert not training_consistent_attention()
+    assert a == [o.outputs[0].token_ids for o in plain.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=4))]

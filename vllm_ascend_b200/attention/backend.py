@@ -97,6 +97,47 @@ class B200AttentionBackend:
         dst[d.to(dst.device)] = src[s.to(src.device)].to(dst.device, non_blocking=True)
 
 
+_TRAINING_CONSISTENT = False
+
+
+def set_training_consistent_attention(on: bool) -> None:
+    global _TRAINING_CONSISTENT
+    _TRAINING_CONSISTENT = bool(on)
+
+
+def training_consistent_attention() -> bool:
+    return _TRAINING_CONSISTENT
+
+
+class B200FAImpl(B200AttentionImpl):
+    """One attention kernel for every batch shape: prefill, chunked prefill, mixed batches and
+    decode all run the tcgen05 tile kernel with a single KV split, so the value computed for a
+    token does not depend on whether it was scheduled alone, in a chunk, or next to decodes — the
+    kernel an RL trainer's forward pass runs (full-sequence causal attention) and the rollout
+    engine then agree.  Role of the reference's FA3 backend for training-inference consistency
+    (vllm_ascend/attention/fa3_v1.py:44-144, selected by platform.py:1247-1272); like it, the
+    mode has no sliding-window support and is slower for decode."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        if self.sliding_window:
+            raise ValueError("the training-consistent attention backend does not support sliding windows")
+
+    def forward(self, q, k_cache, v_cache, meta):
+        out = torch.empty_like(q)
+        return ops.paged_attention_consistent(q, k_cache, v_cache, meta, self.scale, out)
+
+
+class B200FABackend(B200AttentionBackend):
+    @staticmethod
+    def get_name() -> str:
+        return "B200_TCGEN05_CONSISTENT"
+
+    @staticmethod
+    def get_impl_cls():
+        return B200FAImpl
+
+
 def _copy_blocks(t: torch.Tensor, pairs: torch.Tensor) -> None:
     base = t
     # the HND cache is a permuted view; copy on its dense storage

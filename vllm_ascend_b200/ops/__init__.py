@@ -333,6 +333,33 @@ def choose_num_splits(num_seqs: int, Hkv: int, max_seq_len: int, sm_count: int =
     return max(1, min(want, max_tiles, 32))
 
 
+def paged_attention_consistent(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
+                               scale: float, out: torch.Tensor) -> torch.Tensor:
+    """Every batch shape through the tile kernel with one KV split (training-consistent mode)."""
+    if not _use_native(q):
+        return ref.paged_attention(q, k_cache, v_cache, meta.query_start_loc_cpu, meta.seq_lens_cpu,
+                                   meta.block_table, scale, True, 0, out=out)
+    T, Hq, D = q.shape
+    G = Hq // k_cache.shape[2]
+    if D not in (64, 128) or 128 % G:
+        raise RuntimeError("training-consistent attention needs head_dim 64 or 128 and a group size dividing 128")
+    if meta.tile_seq is None and meta.max_query_len > 128 // G:
+        raise RuntimeError("training-consistent attention needs the tile work list for long queries")
+    nd = meta.num_decodes
+    if meta.tile_seq is not None and nd > 0:
+        # the work list of a mixed step covers the prefill sequences; decodes get their own launch of
+        # the same kernel (tile i = sequence i)
+        import copy
+        dm = copy.copy(meta)
+        dm.tile_seq = dm.tile_qoff = None
+        dm.num_reqs, dm.max_query_len = nd, 1
+        paged_attention_tc(q, k_cache, v_cache, dm, scale, out, True, 0, 1)
+        if meta.num_tiles > 0:
+            paged_attention_tc(q, k_cache, v_cache, meta, scale, out, True, 0, 1)
+        return out
+    return paged_attention_tc(q, k_cache, v_cache, meta, scale, out, True, 0, 1)
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
                     scale: float, out: Optional[torch.Tensor] = None, causal: bool = True,
                     window: int = 0) -> torch.Tensor:
@@ -340,6 +367,9 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     T, Hq, D = q.shape
     if out is None:
         out = torch.empty((T, Hq, v_cache.shape[-1]), dtype=q.dtype, device=q.device)
+    from ..attention.backend import training_consistent_attention
+    if training_consistent_attention() and causal and window == 0:
+        return paged_attention_consistent(q, k_cache, v_cache, meta, scale, out)
     if not _use_native(q):
         return ref.paged_attention(q, k_cache, v_cache, meta.query_start_loc_cpu,
                                    meta.seq_lens_cpu, meta.block_table, scale, causal, window,

@@ -131,6 +131,12 @@ class B200Platform(_Base):
         use_sparse = bool(kwargs.get("use_sparse", getattr(cfg, "use_sparse", False)))
         use_compress = bool(kwargs.get("use_compress", getattr(cfg, "use_compress", False)))
         key = (use_mla, use_sparse, use_compress)
+        from .platform_config import get_b200_config
+        rl = get_b200_config().rl_config
+        if rl.enabled and rl.enable_training_consistency:
+            if key != (False, False, False):
+                raise ValueError("the training-consistent attention backend supports neither MLA nor sparse attention")
+            return "vllm_ascend_b200.attention.backend.B200FABackend"
         if key not in _ATTN_BACKENDS:
             raise ValueError(f"no attention backend for use_mla={use_mla} use_sparse={use_sparse} "
                              f"use_compress={use_compress}")

@@ -311,10 +311,14 @@ def check_and_update_config(engine_cfg) -> B200Config:
     # 3 knobs that cannot work together
     if cfg.rl_config.enabled:
         engine_cfg.enable_sleep_mode = True
+        if cfg.rl_config.enable_training_consistency and (mc.use_mla or mc.sliding_window):
+            raise ValueError("training-consistent attention supports neither MLA nor sliding windows")
         if cfg.rl_config.enable_batch_invariant:
             cc.cudagraph_mode = "NONE"
             from .batch_invariant import enable_batch_invariant_mode
             enable_batch_invariant_mode()
+    from .attention.backend import set_training_consistent_attention
+    set_training_consistent_attention(cfg.rl_config.enabled and cfg.rl_config.enable_training_consistency)
     dp_size = max(1, pc.data_parallel_size)
     if dp_size == 1:      # under a launcher the DP size follows from the world size
         import os
