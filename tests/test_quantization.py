@@ -33,7 +33,9 @@ def test_block_fp8_weight_roundtrip(N, K):
 
 
 @pytest.mark.parametrize("name,tol", [("FP8_BLOCK", 0.06), ("W8A8_DYNAMIC", 0.03),
-                                      ("W8A8FP8_DYNAMIC", 0.08), ("W8A16", 0.02), ("W4A16", 0.25)])
+                                      ("W8A8FP8_DYNAMIC", 0.08), ("W8A16", 0.02), ("W4A16", 0.25),
+                                      ("W8A8_MXFP8", 0.08), ("W4A4_MXFP4", 0.5), ("W4A8_MXFP", 0.35),
+                                      ("W4A8_DYNAMIC", 0.25)])
 def test_linear_schemes_approximate_float(name, tol):
     torch.manual_seed(0)
     lin = Linear(torch.randn(96, 256) * 0.1, torch.randn(96) * 0.1)
@@ -79,3 +81,45 @@ def test_description_file_routes_layers(tmp_path):
     assert model.layers[0].self_attn.qkv_proj.quant is not None
     assert model.layers[0].mlp.down_proj.quant is None
     assert model.layers[1].self_attn.qkv_proj.quant is None     # not listed -> FLOAT
+
+
+def test_mx_formats_use_power_of_two_block_scales_and_element_grids():
+    torch.manual_seed(1)
+    x = torch.randn(5, 128) * torch.logspace(-3, 2, 5).unsqueeze(1)
+    for elem, grid_max in (("fp8", 448.0), ("fp4", 6.0)):
+        q, s = schemes.mx_quantize(x, elem)
+        assert s.shape == (5, 4)
+        assert torch.equal(torch.log2(s), torch.log2(s).round())            # e8m0: powers of two only
+        assert q.abs().max() <= grid_max
+        back = schemes.mx_dequantize(q, s)
+        tol = 0.07 if elem == "fp8" else 0.3
+        assert ((back - x).abs() <= tol * x.abs().reshape(5, 4, 32).amax(-1, keepdim=True).expand(5, 4, 32).reshape(5, 128) + 1e-9).all()
+    q4, _ = schemes.mx_quantize(x, "fp4")
+    assert set(q4.abs().unique().tolist()) <= {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0}
+
+
+def test_moe_schemes_for_compressed_expert_weights():
+    from vllm_ascend_b200.ops.fused_moe import fused_experts_ref
+    torch.manual_seed(2)
+    E, I, H, T = 4, 64, 128, 9
+    w13, w2 = torch.randn(E, 2 * I, H) * 0.1, torch.randn(E, H, I) * 0.1
+    x = torch.randn(T, H)
+    ids = torch.randint(0, E, (T, 2))
+    wts = torch.rand(T, 2)
+    want = fused_experts_ref(x, w13, w2, wts, ids, None)
+    for name, tol in (("W8A8_MXFP8", 0.08), ("W4A4_MXFP4", 0.5), ("W4A8_DYNAMIC", 0.3), ("W4A16", 0.3),
+                      ("W4A16_MXFP4", 0.5), ("W4A8_MXFP", 0.5)):
+        blk = type("B", (), {})()
+        blk.w13, blk.w2 = w13.clone(), w2.clone()
+        sch = Q.get_scheme_class(name, "moe")()
+        sch.convert(blk)
+        got = sch.apply_experts(x, blk.w13, blk.w2, wts, ids, None)
+        assert (got - want).abs().max() < tol * want.abs().max() + 1e-3, name
+
+
+def test_kv_cache_fp8_roundtrip():
+    x = torch.randn(6, 4, 32)
+    scale = x.abs().amax(dim=(0, 2)) / 448.0
+    q = schemes.kv_quant_fp8(x, scale)
+    assert q.dtype == torch.float8_e4m3fn
+    assert (schemes.kv_dequant_fp8(q, scale, torch.float32) - x).abs().max() < 0.07 * x.abs().max()

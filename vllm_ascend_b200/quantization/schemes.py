@@ -313,3 +313,200 @@ class W8A8DynamicMoE(MoEScheme):
         w13f = (w13.float() * blk.w13_scale).to(x.dtype)
         w2f = (w2.float() * blk.w2_scale).to(x.dtype)
         return fused_experts_ref(x, w13f, w2f, topk_w, topk_ids, expert_map)
+
+
+# ---------------------------------------------------------------- microscaling (MX) formats
+def _e8m0_scale(amax: torch.Tensor, elem_max_pow2: int) -> torch.Tensor:
+    """Power-of-two block scale of the OCP microscaling formats: 2^(floor(log2 amax) - emax_elem)."""
+    e = torch.floor(torch.log2(amax.clamp_min(2.0 ** -126))) - elem_max_pow2
+    return torch.exp2(e.clamp(-127, 127))
+
+
+_FP4_GRID = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+def _round_fp4(v: torch.Tensor) -> torch.Tensor:
+    """Round to the e2m1 grid (+-{0, .5, 1, 1.5, 2, 3, 4, 6}), saturating."""
+    grid = _FP4_GRID.to(v.device)
+    mag = v.abs().clamp(max=6.0)
+    idx = (mag.unsqueeze(-1) - grid).abs().argmin(dim=-1)
+    return grid[idx] * v.sign()
+
+
+def mx_quantize(t: torch.Tensor, elem: str, block: int = 32):
+    """[..., K] -> (values on the element grid as fp32, e8m0 scales [..., K / block]) with one
+    power-of-two scale per ``block`` consecutive elements of the last dim."""
+    K = t.shape[-1]
+    assert K % block == 0, "the last dimension must be a multiple of the MX block"
+    g = t.float().reshape(*t.shape[:-1], K // block, block)
+    amax = g.abs().amax(dim=-1, keepdim=True)
+    if elem == "fp8":
+        scale = _e8m0_scale(amax, 8)                       # e4m3: largest power of two is 2^8
+        q = (g / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8).float()
+    elif elem == "fp4":
+        scale = _e8m0_scale(amax, 2)                       # e2m1: largest power of two is 2^2
+        q = _round_fp4(g / scale)
+    else:
+        raise ValueError(elem)
+    return q.reshape(t.shape), scale.squeeze(-1)
+
+
+def mx_dequantize(q: torch.Tensor, scale: torch.Tensor, block: int = 32) -> torch.Tensor:
+    K = q.shape[-1]
+    return (q.float().reshape(*q.shape[:-1], K // block, block) * scale.unsqueeze(-1)).reshape(q.shape)
+
+
+class _MXLinear(LinearScheme):
+    """Microscaling linear: weights and (dynamically) activations carry one e8m0 scale per 32
+    elements along K (vllm_ascend/quantization/methods/w8a8_mxfp8.py, w4a4_mxfp4.py,
+    w4a8_mxfp.py).  Checkpoints that ship ``weight`` in the element type with ``weight_scale`` in
+    e8m0 load as they are; float weights are converted.  The product is evaluated on the
+    dequantised operands, which is exact for these formats (block scales are powers of two)."""
+    w_elem = "fp8"
+    a_elem = "fp8"
+
+    def convert(self, layer) -> None:
+        if hasattr(layer, "weight_scale"):
+            return
+        q, s = mx_quantize(layer.weight, self.w_elem)
+        layer.weight = q.to(FP8) if self.w_elem == "fp8" else q.to(torch.bfloat16)
+        layer.weight_scale = s
+
+    def named_tensors(self, layer):
+        yield "weight_scale", layer.weight_scale
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        if isinstance(x, ops.QuantAct):
+            x = x.dequant()
+        K = x.shape[-1]
+        xq, xs = mx_quantize(x.reshape(-1, K), self.a_elem)
+        a = mx_dequantize(xq, xs).to(x.dtype)
+        w = mx_dequantize(layer.weight, layer.weight_scale).to(x.dtype)
+        y = ops.linear(a, w, None if skip_bias else layer.bias)
+        y = y.view(*x.shape[:-1], w.shape[0])
+        return y + residual if residual is not None else y
+
+
+@register_scheme("W8A8_MXFP8", "linear")
+class MXFP8Linear(_MXLinear):
+    pass
+
+
+@register_scheme("W4A4_MXFP4", "linear")
+class MXFP4Linear(_MXLinear):
+    w_elem = a_elem = "fp4"
+
+
+@register_scheme("W4A8_MXFP", "linear")
+class W4A8MXLinear(_MXLinear):
+    w_elem, a_elem = "fp4", "fp8"
+
+
+@register_scheme("W4A8_DYNAMIC", "linear")
+class W4A8DynamicLinear(_PerChannelDynamic):
+    """int4 weights with group-wise scales x per-token dynamic int8 activations
+    (vllm_ascend/quantization/methods/w4a8.py)."""
+    group = 128
+
+    def convert(self, layer) -> None:
+        if hasattr(layer, "weight_scale"):
+            return
+        w = layer.weight.float()
+        N, K = w.shape
+        g = self.group if K % self.group == 0 else K
+        wg = w.view(N, K // g, g)
+        scale = (wg.abs().amax(dim=-1, keepdim=True) / 7.0).clamp_min(1e-10)
+        layer.weight = (wg / scale).round().clamp(-8, 7).to(torch.int8).view(N, K)
+        layer.weight_scale = scale.squeeze(-1)
+        layer.group_size = g
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        N, K = layer.weight.shape
+        g = layer.group_size
+        x2 = x.reshape(-1, K).float()
+        a_scale = (x2.abs().amax(dim=1, keepdim=True) / 127.0).clamp_min(1e-10)
+        xq = (x2 / a_scale).round().clamp(-127, 127)
+        # integer partial sums per group, scaled per (row, group) like the int8 x int4 kernels do
+        part = torch.einsum("tgk,ngk->tng", xq.view(-1, K // g, g), layer.weight.float().view(N, K // g, g))
+        y = (part * layer.weight_scale.unsqueeze(0)).sum(-1) * a_scale
+        if layer.bias is not None and not skip_bias:
+            y = y + layer.bias.float()
+        y = y.to(x.dtype).view(*x.shape[:-1], N)
+        return y + residual if residual is not None else y
+
+
+class _DequantMoE(MoEScheme):
+    """Expert weights in a compressed format, evaluated on dequantised weights."""
+
+    def _q(self, w):
+        raise NotImplementedError
+
+    def _dq(self, q, s, dtype):
+        raise NotImplementedError
+
+    def convert(self, block) -> None:
+        block.w13, block.w13_scale = self._q(block.w13)
+        block.w2, block.w2_scale = self._q(block.w2)
+        self.block_ref = block
+
+    def apply_experts(self, x, w13, w2, topk_w, topk_ids, expert_map):
+        from ..ops.fused_moe import fused_experts_ref
+        blk = self.block_ref
+        return fused_experts_ref(x, self._dq(w13, blk.w13_scale, x.dtype), self._dq(w2, blk.w2_scale, x.dtype),
+                                 topk_w, topk_ids, expert_map)
+
+
+@register_scheme("W8A8_MXFP8", "moe")
+class MXFP8MoE(_DequantMoE):
+    elem = "fp8"
+
+    def _q(self, w):
+        q, s = mx_quantize(w, self.elem)
+        return (q.to(FP8) if self.elem == "fp8" else q.to(torch.bfloat16)), s
+
+    def _dq(self, q, s, dtype):
+        return mx_dequantize(q, s).to(dtype)
+
+
+@register_scheme("W4A4_MXFP4", "moe")
+class MXFP4MoE(MXFP8MoE):
+    elem = "fp4"
+
+
+@register_scheme("W4A8_MXFP", "moe")
+class W4A8MXMoE(MXFP8MoE):
+    elem = "fp4"
+
+
+@register_scheme("W4A16_MXFP4", "moe")
+class W4A16MXMoE(MXFP8MoE):
+    elem = "fp4"
+
+
+@register_scheme("W4A8_DYNAMIC", "moe")
+@register_scheme("W4A16", "moe")
+class W4GroupMoE(_DequantMoE):
+    group = 128
+
+    def _q(self, w):
+        E, N, K = w.shape
+        g = self.group if K % self.group == 0 else K
+        wg = w.float().view(E, N, K // g, g)
+        scale = (wg.abs().amax(dim=-1, keepdim=True) / 7.0).clamp_min(1e-10)
+        return (wg / scale).round().clamp(-8, 7).to(torch.int8).view(E, N, K), scale.squeeze(-1)
+
+    def _dq(self, q, s, dtype):
+        E, N, K = q.shape
+        g = K // s.shape[-1]
+        return (q.float().view(E, N, K // g, g) * s.unsqueeze(-1)).view(E, N, K).to(dtype)
+
+
+# ---------------------------------------------------------------- KV-cache quantization
+def kv_quant_fp8(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """Per-head static scale, e4m3 storage (the C8 KV scheme's role,
+    vllm_ascend/quantization/methods/kv_c8.py): x [T, H, D], scale [H] -> e4m3 [T, H, D]."""
+    return (x.float() / scale.view(1, -1, 1)).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+
+
+def kv_dequant_fp8(q: torch.Tensor, scale: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    return (q.float() * scale.view(1, -1, 1)).to(dtype)
