@@ -191,3 +191,54 @@ def test_layerwise_push_same_gpu():
     finally:
         pre.engine.kv_connector.close()
         dec.engine.kv_connector.close()
+
+
+def test_hybrid_connector_pulls_states_with_the_copy_kernel():
+    from vllm_ascend_b200.config import ModelConfig
+
+    def cfg():
+        return ModelConfig(name="gdn-t", architecture="Qwen3NextForCausalLM", vocab_size=2048, hidden_size=512,
+                           intermediate_size=1024, num_hidden_layers=4, num_attention_heads=8,
+                           num_key_value_heads=2, head_dim=128, qk_norm=True, rope_theta=1e6, dtype="bfloat16",
+                           init_std=0.05, full_attention_interval=2, linear_num_key_heads=2,
+                           linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128)
+
+    def mk(role, eid):
+        return LLM(cfg(), device="cuda", seed=0, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=256,
+                   num_gpu_blocks_override=40, enforce_eager=True,
+                   kv_transfer_config={"kv_connector": "HybridConnector", "kv_role": role, "engine_id": eid})
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 300)]
+    pre, dec = mk("kv_producer", "HPg"), mk("kv_consumer", "HDg")
+    try:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        outs = pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {"do_remote_decode": True}}
+                             for p in prompts], sp1)
+        sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+        eng = dec.engine
+        rids = [eng.add_request(p, sp, kv_transfer_params=o.kv_transfer_params) for p, o in zip(prompts, outs)]
+        reqs = {r: eng.scheduler.requests[r] for r in rids}
+        eng.step()                                   # allocates rows and blocks, starts the pulls
+        c = eng.kv_connector
+        for job in list(c._inflight.values()):
+            for ev in job.events:
+                ev.synchronize()
+        assert c.stats["pulled_states"] == 3
+        p_states, d_states = pre.engine.kv_connector.state_tensors, c.state_tensors
+        assert len(p_states) == len(d_states) == 4   # two linear layers x (conv window, delta-rule matrix)
+        for r, o in zip(rids, outs):
+            src, dst = o.kv_transfer_params["remote_state_row"], reqs[r].row
+            for a, b in zip(p_states, d_states):
+                assert torch.equal(a[src], b[dst]) and a[src].abs().sum() > 0
+        while eng.has_unfinished():
+            eng.step()
+        for r, o in zip(rids, outs):
+            toks = reqs[r].output_token_ids
+            assert len(toks) == 6 and toks[0] == o.outputs[0].token_ids[0]      # adopted first token
+        assert c.stats["failed"] == 0
+        pre.engine.kv_connector.reap(pre.engine.scheduler)
+        assert pre.engine.kv_connector.num_delayed == 0
+        _native.check_status(torch.device("cuda"))
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()

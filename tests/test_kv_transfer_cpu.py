@@ -297,3 +297,36 @@ def test_layerwise_push_connector():
     finally:
         pre.engine.kv_connector.close()
         dec.engine.kv_connector.close()
+
+
+def test_hybrid_connector_moves_kv_and_recurrent_state():
+    """Gated-DeltaNet hybrid: the decode engine gets the attention layers' KV blocks, the linear
+    layers' conv / delta-rule state rows and the first sampled token, and continues exactly as a
+    monolithic engine would; the prefill engine holds the batch row until the pull is acknowledged."""
+    def mk(role, eid):
+        ktc = None if role is None else {"kv_connector": "HybridConnector", "kv_role": role, "engine_id": eid}
+        return LLM("tiny-gdn", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4,
+                   max_num_batched_tokens=48, kv_transfer_config=ktc)
+    prompts = _prompts(3, seed=5)
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in mk(None, "M").generate(prompts, sp)]
+    pre, dec = mk("kv_producer", "HP"), mk("kv_consumer", "HD")
+    try:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        outs = pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {"do_remote_decode": True}}
+                             for p in prompts], sp1)
+        rows = [o.kv_transfer_params["remote_state_row"] for o in outs]
+        assert len(set(rows)) == 3
+        free_rows = pre.engine.scheduler._free_rows
+        assert not set(rows) & set(free_rows)                   # held back with the states in them
+        got = dec.generate([{"prompt_token_ids": p, "kv_transfer_params": o.kv_transfer_params}
+                            for p, o in zip(prompts, outs)], sp)
+        assert [o.outputs[0].token_ids for o in got] == want
+        c = dec.engine.kv_connector
+        assert c.stats["pulled_requests"] == 3 and c.stats["pulled_states"] == 3 and c.stats["failed"] == 0
+        pre.engine.kv_connector.reap(pre.engine.scheduler)
+        assert pre.engine.kv_connector.num_delayed == 0
+        assert set(rows) <= set(pre.engine.scheduler._free_rows)
+    finally:
+        pre.engine.kv_connector.close()
+        dec.engine.kv_connector.close()

@@ -20,6 +20,8 @@ _CONNECTORS = {
     "SimpleCPUOffloadConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
     "OffloadingConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
     "MultiConnector": ("multi_connector", "MultiConnector"),
+    "HybridConnector": ("hybrid_connector", "HybridConnector"),
+    "MooncakeHybridConnector": ("hybrid_connector", "HybridConnector"),
 }
 
 

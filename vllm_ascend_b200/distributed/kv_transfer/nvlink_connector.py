@@ -411,15 +411,7 @@ class NVLinkConnector(KVConnectorBase):
         host, port0 = p.get("remote_host", "127.0.0.1"), int(p.get("remote_port", 0))
         for src_rank, src_h0, dst_h0, nh in self._slices(remote_tp):
             key = (eid, src_rank)
-            local = _LOCAL_ENGINES.get(key)
-            mode = self.transport
-            if mode == "auto":
-                mode = "local" if (local is not None and local.is_cuda == self.is_cuda and self.is_cuda) else None
-            if mode is None:
-                meta = self._get_meta(key, host, port0 + src_rank)
-                same_node = meta.get("hostname") == socket.gethostname()
-                mode = "ipc" if (self.is_cuda and meta.get("cuda") and same_node and meta.get("ipc_handle")
-                                 and local is None) else "tcp"
+            mode, local = self._resolve_mode(key, host, port0 + src_rank)
             job.pulled_from.append(key if local is not None else (host, port0 + src_rank))
             if mode == "local":
                 if local is None:
@@ -432,6 +424,19 @@ class NVLinkConnector(KVConnectorBase):
                 self._copy_kernel(job, srcs, int(meta["num_blocks"]), src_h0, dst_h0, nh)
             else:
                 job.futures.append(self._pool.submit(self._pull_tcp, job, host, port0 + src_rank, src_h0, dst_h0, nh))
+
+    def _resolve_mode(self, key, host, port):
+        """("local" | "ipc" | "tcp", connector of the source when it lives in this process)."""
+        local = _LOCAL_ENGINES.get(key)
+        mode = self.transport
+        if mode == "auto":
+            mode = "local" if (local is not None and local.is_cuda == self.is_cuda and self.is_cuda) else None
+        if mode is None:
+            meta = self._get_meta(key, host, port)
+            same_node = meta.get("hostname") == socket.gethostname()
+            mode = "ipc" if (self.is_cuda and meta.get("cuda") and same_node and meta.get("ipc_handle")
+                             and local is None) else "tcp"
+        return mode, local
 
     def _get_meta(self, key, host, port) -> dict:
         meta = self._remote_meta.get(key)

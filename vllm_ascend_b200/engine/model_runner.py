@@ -246,14 +246,22 @@ class ModelRunner:
             # can map the whole cache through a single CUDA IPC handle
             from ..distributed.kv_transfer.nvlink_connector import KVArena
             torch.cuda.empty_cache()
+            state_bytes = 0
+            for layer, shapes in zip(self.model.layers, per_layer):
+                if shapes is None:         # recurrent state caches travel with the KV (hybrid models)
+                    cs, ss = layer.self_attn.state_shapes(self.max_seqs + 1)
+                    state_bytes += KVArena.bytes_needed([cs], self.kv_dtype) + KVArena.bytes_needed([ss], torch.float32)
             self.kv_arena = KVArena(KVArena.bytes_needed([s for sh in per_layer if sh for s in sh],
-                                                         self.kv_dtype), self.device)
+                                                         self.kv_dtype) + state_bytes, self.device)
         for layer, shapes in zip(self.model.layers, per_layer):
             if shapes is None:
                 # one state row per batch row, plus a scratch row for padded graph entries
                 cs, ss = layer.self_attn.state_shapes(self.max_seqs + 1)
-                self.kv_caches.append((torch.zeros(cs, dtype=self.kv_dtype, device=self.device),
-                                       torch.zeros(ss, dtype=torch.float32, device=self.device)))
+                if self.kv_arena is not None:
+                    self.kv_caches.append((self.kv_arena.take(cs, self.kv_dtype), self.kv_arena.take(ss, torch.float32)))
+                else:
+                    self.kv_caches.append((torch.zeros(cs, dtype=self.kv_dtype, device=self.device),
+                                           torch.zeros(ss, dtype=torch.float32, device=self.device)))
                 continue
             self.kv_caches.append(tuple(
                 ops.alloc_kv_cache(s[0], s[1], s[2], s[3], self.kv_dtype, self.device, layout,

@@ -174,6 +174,11 @@ class Scheduler:
         self.waiting.appendleft(req)
         out.preempted.append(req)
 
+    def release_row_id(self, row: int) -> None:
+        """Return a batch row a connector held back after its request finished."""
+        if row >= 0 and row not in self._free_rows:
+            self._free_rows.append(row)
+
     def _release_row(self, req: Request) -> None:
         if req.row >= 0:
             self._free_rows.append(req.row)
@@ -382,7 +387,10 @@ class Scheduler:
         if not delay_free:
             self.free_blocks(req)
         self._uncommit_blocks(req)
-        self._release_row(req)
+        if delay_free and getattr(self.kv_connector, "holds_state_rows", False):
+            req.row = -1          # the connector keeps the row (recurrent state) until the pull is done
+        else:
+            self._release_row(req)
         self._hashes.pop(req.request_id, None)
         self.finished_since_last.append(req.request_id)
 
