@@ -29,7 +29,9 @@ def tp_generate():
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 333, 129, 7)]
     sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
-    llm = LLM(_cfg(), device="cuda", tensor_parallel_size=world, max_model_len=512, max_num_seqs=8,
+    pcp = int(os.environ.get("PCP", "1"))
+    llm = LLM(_cfg(), device="cuda", tensor_parallel_size=world // pcp, prefill_context_parallel_size=pcp,
+              max_model_len=512, max_num_seqs=8,
               max_num_batched_tokens=256, num_gpu_blocks_override=40,
               enforce_eager=os.environ.get("EAGER", "0") == "1", cudagraph_capture_sizes=[2, 4, 8])
     outs = llm.generate(prompts, sp)

@@ -130,6 +130,8 @@ def test_training_consistent_attention_is_independent_of_batching():
     """With the single-kernel attention backend and split-free decode, a request's tokens do not
     depend on what else is in the batch or on how its prompt was chunked (GEMM kernels accumulate
     every output in one fixed order), which plain mode does not promise."""
+    import os
+    saved_env = dict(os.environ)
     rng = np.random.default_rng(11)
     prompts = [rng.integers(0, 2048, size=n).tolist() for n in (200, 37, 150, 90)]
     sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
@@ -139,13 +141,17 @@ def test_training_consistent_attention_is_independent_of_batching():
         llm = LLM(_cfg("bfloat16"), device="cuda", max_model_len=512, max_num_seqs=8,
                   max_num_batched_tokens=batch_tokens, num_gpu_blocks_override=40, additional_config=add)
         return [o.outputs[0].token_ids for o in llm.generate([prompts[i] for i in which], sp)]
-    together = run(512, [0, 1, 2, 3])
-    chunked = run(64, [0, 1, 2, 3])
-    alone = [run(512, [i])[0] for i in range(4)]
+    try:
+        together = run(512, [0, 1, 2, 3])
+        chunked = run(64, [0, 1, 2, 3])
+        alone = [run(512, [i])[0] for i in range(4)]
+    finally:
+        from vllm_ascend_b200.platform_config import clear_b200_config
+        from vllm_ascend_b200.attention.backend import set_training_consistent_attention
+        from vllm_ascend_b200.batch_invariant import disable_batch_invariant_mode
+        set_training_consistent_attention(False)
+        disable_batch_invariant_mode()
+        clear_b200_config()
+        os.environ.clear()
+        os.environ.update(saved_env)
     assert together == chunked == alone
-    from vllm_ascend_b200.platform_config import clear_b200_config
-    from vllm_ascend_b200.attention.backend import set_training_consistent_attention
-    from vllm_ascend_b200.batch_invariant import disable_batch_invariant_mode
-    set_training_consistent_attention(False)
-    disable_batch_invariant_mode()
-    clear_b200_config()

@@ -61,3 +61,14 @@ def test_fused_moe_dispatch_gemm_combine_over_peer_memory():
     r = _run(2, "moe_fused")
     assert r["status"] == 0
     assert r["max_rel_err"] < 0.03
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_prefill_context_parallel_on_two_gpus():
+    single = _run(1, "tp_generate", {"EAGER": "1"})
+    pcp = _run(2, "tp_generate", {"EAGER": "1", "PCP": "2", "VLLM_B200_TP_COMM": "nccl"})
+    a, b = pcp["tokens"], single["tokens"]
+    assert [len(x) for x in a] == [len(x) for x in b]
+    # the split changes which attention kernel instance sees which query rows, not the math:
+    # first tokens agree, later near-ties of the random-weight model may flip
+    assert sum(x[0] == y[0] for x, y in zip(a, b)) >= len(b) - 1, (a, b)
