@@ -92,6 +92,9 @@ WORKER = textwrap.dedent("""
         res["slots"] = int(llm.engine.eplb.a.S)
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps(res), flush=True)
+    llm.shutdown()
+    sys.stdout.flush()
+    os._exit(0)
 """)
 
 

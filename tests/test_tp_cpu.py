@@ -33,6 +33,11 @@ WORKER = textwrap.dedent("""
         print("PART " + json.dumps(dict((str(o.prompt_token_ids[:3]), o.outputs[0].token_ids) for o in outs)), flush=True)
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps([o.outputs[0].token_ids for o in outs]), flush=True)
+    # orderly teardown: groups destroyed on every rank, then leave without running the
+    # interpreter's atexit handlers against helper threads of the process-group backend
+    llm.shutdown()
+    sys.stdout.flush()
+    os._exit(0)
 """)
 
 
