@@ -240,3 +240,40 @@ def test_hybrid_linear_attention_model_matches_cache_free_recompute():
     # rows are reused by later requests: states must not leak between them
     again = [o.outputs[0].token_ids for o in llm.generate(prompts[::-1], sp)]
     assert again == want[::-1]
+
+
+def test_logit_processors_and_logprobs():
+    """allowed_token_ids, bad words (single- and multi-token), logit_bias, min_tokens and logprobs
+    act on the distribution the way the public API promises."""
+    llm = LLM("tiny-qwen", device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=64, block_size=16)
+    prompt = [5, 6, 7, 8, 9]
+    base = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=3))[0].outputs[0]
+    toks = base.token_ids
+    assert len(base.logprobs) == 6
+    for t, lp in zip(toks, base.logprobs):
+        assert t in lp and len(lp) in (3, 4) and max(lp.values()) == lp[t] <= 0.0       # greedy: the top entry
+    # allowed ids: only these tokens can appear
+    allowed = [11, 12, 13]
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True,
+                                                allowed_token_ids=allowed))[0].outputs[0].token_ids
+    assert set(out) <= set(allowed)
+    # single-token bad word: the greedy first token is replaced by the runner-up
+    second = sorted(base.logprobs[0].items(), key=lambda kv: -kv[1])[1][0]
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True,
+                                                bad_words_token_ids=[[toks[0]]]))[0].outputs[0].token_ids
+    assert out[0] == second and toks[0] not in out
+    # multi-token bad word: banned only after its prefix was generated
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True,
+                                                bad_words_token_ids=[[toks[0], toks[1]]]))[0].outputs[0].token_ids
+    assert out[0] == toks[0] and out[1] != toks[1]
+    # a large bias forces a token
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True,
+                                                logit_bias={77: 1000.0}))[0].outputs[0].token_ids
+    assert out == [77, 77, 77]
+    # min_tokens keeps a stop token away until the minimum is reached
+    stop = toks[1]
+    early = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, stop_token_ids=[stop]))[0].outputs[0].token_ids
+    late = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, stop_token_ids=[stop],
+                                                 min_tokens=4))[0].outputs[0].token_ids
+    assert len(early) == 2 and early[-1] == stop
+    assert len(late) >= 4 and stop not in late[:4]

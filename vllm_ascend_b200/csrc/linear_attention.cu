@@ -85,16 +85,26 @@ gated_delta_rule_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     for (int i = 0; i < DK; i++) S[i] = 0.f;
   }
   const int t0 = cu[b], t1 = cu[b + 1];
+  // inputs of token t + 1 are fetched while token t is processed: the recurrence is sequential,
+  // so the global-load latency would otherwise sit on every step
+  float n_k = 0.f, n_q = 0.f, n_v = 0.f, n_g = 0.f, n_b = 0.f;
+  auto fetch = [&](int t) {
+    if (j < DK) {
+      n_k = __bfloat162float(k[(long)t * qk_stride + (long)hk * DK + j]);
+      n_q = __bfloat162float(q[(long)t * qk_stride + (long)hk * DK + j]);
+    }
+    n_v = __bfloat162float(v[(long)t * v_stride + (long)hv * DV + j]);
+    n_g = g[(long)t * Hv + hv];
+    n_b = beta[(long)t * Hv + hv];
+  };
+  if (t0 < t1) fetch(t0);
   for (int t = t0; t < t1; t++) {
+    float kval = n_k, qval = n_q;
+    const float vt = n_v, decay = __expf(n_g), bt = n_b;
+    if (t + 1 < t1) fetch(t + 1);
     __syncthreads();                    // previous token's reads of ks / qs are done
     // DV >= DK: the first DK threads stage k_t and q_t (optionally L2-normalised)
-    float kq = 0.f, qq = 0.f, kval = 0.f, qval = 0.f;
-    if (j < DK) {
-      kval = __bfloat162float(k[(long)t * qk_stride + (long)hk * DK + j]);
-      qval = __bfloat162float(q[(long)t * qk_stride + (long)hk * DK + j]);
-      kq = kval * kval;
-      qq = qval * qval;
-    }
+    float kq = kval * kval, qq = qval * qval;
     if (l2norm) {
       kq = warp_reduce_sum(kq);
       qq = warp_reduce_sum(qq);
@@ -111,9 +121,6 @@ gated_delta_rule_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       qs[j] = qval * scale;
     }
     __syncthreads();
-    const float decay = __expf(g[(long)t * Hv + hv]);
-    const float bt = beta[(long)t * Hv + hv];
-    const float vt = __bfloat162float(v[(long)t * v_stride + (long)hv * DV + j]);
     float mem = 0.f;
 #pragma unroll
     for (int i = 0; i < DK; i++) {

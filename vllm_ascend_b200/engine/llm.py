@@ -124,6 +124,15 @@ class LLMEngine:
             self.runner.propose_draft_tokens([r for r, _ in so.scheduled
                                               if r.status == RequestStatus.RUNNING and r.request_id in sampled])
 
+    def _attach_logprobs(self) -> None:
+        for rid, entries in self.runner.take_logprobs().items():
+            req = self.scheduler.requests.get(rid)
+            if req is not None:
+                if req.logprobs is None:
+                    req.logprobs = []
+                room = len(req.output_token_ids or []) - len(req.logprobs)
+                req.logprobs.extend(entries[:max(room, 0)])
+
     def _release_mm(self, finished) -> None:
         mm = self.runner.mm
         if mm is not None:
@@ -155,6 +164,7 @@ class LLMEngine:
                 if req.first_token_time is None and req.request_id in sampled:
                     req.first_token_time = now
             finished = self.scheduler.update_from_output(so_prev, sampled)
+            self._attach_logprobs()
             self._release_mm(finished)
         self._inflight = (so, handle) if handle is not None else None
         t3 = time.perf_counter()
@@ -182,6 +192,7 @@ class LLMEngine:
             if req.first_token_time is None and req.request_id in sampled:
                 req.first_token_time = now
         finished = self.scheduler.update_from_output(so, sampled)
+        self._attach_logprobs()
         self._release_mm(finished)
         self._propose(so, sampled)
         if self.kv_connector is not None:
@@ -383,7 +394,7 @@ class LLM:
             outs.append(RequestOutput(
                 request_id=rid, prompt_token_ids=r.prompt_token_ids.tolist(),
                 outputs=[CompletionOutput(0, list(r.output_token_ids or []),
-                                          finish_reason=_FINISH_REASON.get(r.status))],
+                                          finish_reason=_FINISH_REASON.get(r.status), logprobs=r.logprobs)],
                 finished=True,
                 metrics=RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time),
                 kv_transfer_params=r.kv_transfer_params, num_cached_tokens=r.num_cached_tokens))

@@ -40,11 +40,12 @@ def default_capture_sizes(max_size: int) -> list[int]:
 
 class _StepHandle:
     """A step that was enqueued but whose sampled tokens have not been read yet."""
-    __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index")
+    __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index", "logprobs")
 
     def __init__(self, tokens, reqs, host, event, kind, t_start):
         self.tokens, self.reqs, self.host, self.event, self.kind, self.t_start = tokens, reqs, host, event, kind, t_start
         self.index = {r.request_id: i for i, r in enumerate(reqs)}
+        self.logprobs = None
 
 
 class ModelRunner:
@@ -115,6 +116,7 @@ class ModelRunner:
         if self.pcp.world_size > 1 and (cfg.model.use_mla or cfg.model.is_hybrid or cfg.model.is_multimodal):
             raise NotImplementedError("prefill context parallelism is implemented for GQA decoder models")
         self._pcp_bcast = False          # this step's tokens come from PCP rank 0
+        self._logprobs_out: dict = {}
         self.proposer = None
         self.last_hidden = None      # final hidden states of the latest step, scheduling order
         self.rejection_sampler = None
@@ -563,6 +565,7 @@ class ModelRunner:
             if not md.all_greedy and not self.is_cuda:
                 md.generator = self._cpu_generator()
             tokens = self.sampler(logits, md)
+        dev_lp = self._device_logprobs(logits, tokens, sample_reqs)
         n = tokens.shape[0]
         t_launch = time.perf_counter()
         if self.is_cuda:
@@ -571,6 +574,7 @@ class ModelRunner:
             toks = self._h_sampled[:n].numpy()
         else:
             toks = tokens.numpy()
+        self._store_logprobs(dev_lp, sample_reqs, toks)
         self.stats["d2h_bytes"] += n * 8
         t_sync = time.perf_counter()
         key = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
@@ -651,6 +655,7 @@ class ModelRunner:
             if not sel:
                 return _StepHandle(None, [], None, None, "mixed", t_start)
             h_sel = hidden[:T] if len(sel) == T else hidden[self._to_dev(torch.tensor(sel, dtype=torch.int64))]
+        dev_lp = None
         if self._reduce_sample(sample_reqs):
             tokens = self.model.lm_head.greedy_tokens(h_sel)
         else:
@@ -659,6 +664,7 @@ class ModelRunner:
             if not md.all_greedy and not self.is_cuda:
                 md.generator = self._cpu_generator()
             tokens = self.sampler(logits, md)
+            dev_lp = self._device_logprobs(logits, tokens, sample_reqs)
         n = tokens.shape[0]
         buf = self._h_sampled2[self._async_flip]
         self._async_flip ^= 1
@@ -671,7 +677,9 @@ class ModelRunner:
         self.stats["t_prepare"] += t_prep - t_start
         self.stats["t_launch"] += time.perf_counter() - t_prep
         kind = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
-        return _StepHandle(tokens, sample_reqs, buf, ev, kind, t_start)
+        handle = _StepHandle(tokens, sample_reqs, buf, ev, kind, t_start)
+        handle.logprobs = dev_lp
+        return handle
 
     def _reduce_sample(self, sample_reqs: list) -> bool:
         """Greedy batches on a vocabulary-sharded LM head pick their tokens from per-rank
@@ -679,7 +687,34 @@ class ModelRunner:
         head = self.model.lm_head
         if head.comm.size <= 1 or any(k > 1 for k in self._sample_rows):
             return False
-        return all(r.sampling_params.greedy and not r.sampling_params.has_penalties for r in sample_reqs)
+        return all(r.sampling_params.greedy and not r.sampling_params.has_penalties
+                   and not r.sampling_params.has_processors and r.sampling_params.logprobs is None
+                   for r in sample_reqs)
+
+    def _device_logprobs(self, logits, tokens, sample_reqs):
+        """(token logprob, top ids, top values) on the device when a request of the step asked for
+        log-probabilities, else None."""
+        ks = [r.sampling_params.logprobs for r in sample_reqs]
+        if logits is None or all(k is None for k in ks):
+            return None
+        from ..sample.sampler import compute_logprobs
+        return compute_logprobs(logits, tokens, max(int(k or 0) for k in ks))
+
+    def _store_logprobs(self, dev_lp, sample_reqs, toks) -> None:
+        if dev_lp is None:
+            return
+        tok_lp, ids, vals = (t.cpu() for t in dev_lp)
+        for i, r in enumerate(sample_reqs):
+            k = r.sampling_params.logprobs
+            if k is None:
+                continue
+            entry = {int(ids[i, j]): float(vals[i, j]) for j in range(min(int(k), ids.shape[1]))}
+            entry[int(toks[i])] = float(tok_lp[i])
+            self._logprobs_out.setdefault(r.request_id, []).append(entry)
+
+    def take_logprobs(self) -> dict:
+        out, self._logprobs_out = self._logprobs_out, {}
+        return out
 
     def _to_dev(self, t: torch.Tensor) -> torch.Tensor:
         """Host index tensor to the device without blocking the host on the stream."""
@@ -693,6 +728,7 @@ class ModelRunner:
         if handle.event is not None:
             handle.event.synchronize()
         toks = handle.host[:len(handle.reqs)].numpy()
+        self._store_logprobs(handle.logprobs, handle.reqs, toks)
         out = {}
         for r, t in zip(handle.reqs, toks):
             t = int(t)

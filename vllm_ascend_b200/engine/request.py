@@ -24,7 +24,10 @@ class SamplingParams:
     stop_token_ids: Optional[list[int]] = None
     ignore_eos: bool = False
     seed: Optional[int] = None
-    logprobs: Optional[int] = None
+    logprobs: Optional[int] = None             # log-probabilities of the sampled token and the top-N tokens
+    logit_bias: Optional[dict] = None          # token id -> additive bias
+    allowed_token_ids: Optional[list[int]] = None
+    bad_words_token_ids: Optional[list[list[int]]] = None   # token sequences that must not be generated
     extra_args: Optional[dict] = None
 
     def __post_init__(self):
@@ -40,6 +43,10 @@ class SamplingParams:
     @property
     def greedy(self) -> bool:
         return self.temperature < 1e-5
+
+    @property
+    def has_processors(self) -> bool:
+        return bool(self.logit_bias or self.allowed_token_ids or self.bad_words_token_ids or self.min_tokens > 0)
 
     @property
     def has_penalties(self) -> bool:
@@ -87,6 +94,7 @@ class Request:
     job_id: Optional[str] = None
     # multimodal: items (placeholder run + pixels), 3-axis rotary positions of the prompt and the
     # offset decoded tokens continue from (position = index + delta)
+    logprobs: Optional[list] = None       # per generated token: {token id: logprob} (sampled + top-N)
     mm_inputs: list = field(default_factory=list)
     mrope_positions: Optional[np.ndarray] = None
     mrope_delta: int = 0

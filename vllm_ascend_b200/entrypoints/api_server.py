@@ -122,7 +122,15 @@ def build_app(llm, tokenizer=None, model_name: str = "model") -> FastAPI:
         sp = SamplingParams(max_tokens=int(body.get("max_tokens", 16)), temperature=float(body.get("temperature", 1.0)),
                             top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", 0) or 0),
                             seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
-                            stop_token_ids=list(body.get("stop_token_ids") or []))
+                            stop_token_ids=list(body.get("stop_token_ids") or []),
+                            min_p=float(body.get("min_p", 0.0)), min_tokens=int(body.get("min_tokens", 0)),
+                            presence_penalty=float(body.get("presence_penalty", 0.0)),
+                            frequency_penalty=float(body.get("frequency_penalty", 0.0)),
+                            repetition_penalty=float(body.get("repetition_penalty", 1.0)),
+                            logprobs=body.get("logprobs"),
+                            logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()} or None,
+                            allowed_token_ids=body.get("allowed_token_ids"),
+                            bad_words_token_ids=body.get("bad_words_token_ids"))
         aloop = asyncio.get_running_loop()
         fut = aloop.create_future()
         t0 = time.time()
@@ -135,7 +143,9 @@ def build_app(llm, tokenizer=None, model_name: str = "model") -> FastAPI:
         text = tokenizer.decode(toks) if tokenizer is not None else None
         return {"id": rid, "object": "text_completion", "created": int(t0), "model": model_name,
                 "choices": [{"index": 0, "text": text, "token_ids": toks,
-                             "finish_reason": _FINISH.get(req.status)}],
+                             "finish_reason": _FINISH.get(req.status),
+                             "logprobs": ([{str(k): v for k, v in e.items()} for e in req.logprobs]
+                                          if req.logprobs else None)}],
                 "usage": {"prompt_tokens": req.num_prompt_tokens, "completion_tokens": len(toks),
                           "total_tokens": req.num_prompt_tokens + len(toks)},
                 "kv_transfer_params": req.kv_transfer_params}

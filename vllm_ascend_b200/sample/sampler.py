@@ -29,17 +29,21 @@ class SamplingMetadata:
     frequency_penalty: Optional[torch.Tensor] = None
     presence_penalty: Optional[torch.Tensor] = None
     generator: Optional[torch.Generator] = None    # CPU path only
-    allowed_mask: Optional[torch.Tensor] = None    # bool [B, V] (guided decoding / bad words)
+    allowed_mask: Optional[torch.Tensor] = None    # bool [B, V] (allowed_token_ids / guided decoding)
+    bias_index: Optional[torch.Tensor] = None      # int64 [2, n] (row, token) of additive biases
+    bias_values: Optional[torch.Tensor] = None     # fp32 [n]
+    ban_index: Optional[torch.Tensor] = None       # int64 [2, n] (row, token) forced to -inf
 
     @staticmethod
     def build(reqs: list, device, vocab_size: int, base_seed: int = 0) -> "SamplingMetadata":
         sps = [r.sampling_params for r in reqs]
+        proc = _build_processors(reqs, device, vocab_size) if any(sp.has_processors for sp in sps) else {}
         if all(sp.greedy and not sp.has_penalties for sp in sps):
-            return SamplingMetadata(all_greedy=True)
+            return SamplingMetadata(all_greedy=True, **proc)
         B = len(reqs)
         f32 = lambda xs: torch.tensor(xs, dtype=torch.float32, device=device)
         md = SamplingMetadata(
-            all_greedy=False,
+            all_greedy=False, **proc,
             temperature=f32([sp.temperature for sp in sps]),
             top_k=torch.tensor([sp.top_k for sp in sps], dtype=torch.int32, device=device),
             top_p=f32([sp.top_p for sp in sps]),
@@ -67,11 +71,78 @@ class SamplingMetadata:
         return md
 
 
+def _build_processors(reqs: list, device, vocab_size: int) -> dict:
+    """Sparse logit edits of this step: additive biases, banned tokens (bad words whose prefix
+    has just been generated, EOS / stop tokens before min_tokens) and allowed-token masks.  Order of
+    application follows the upstream sampler: allowed ids, bad words, min-tokens, bias, then
+    penalties (the reference's v2 sampler does the same on device, worker/v2/sample/*)."""
+    bias_r, bias_c, bias_v, ban_r, ban_c = [], [], [], [], []
+    allowed = None
+    for i, r in enumerate(reqs):
+        sp = r.sampling_params
+        out = r.output_token_ids or []
+        if sp.allowed_token_ids:
+            if allowed is None:
+                allowed = torch.ones((len(reqs), vocab_size), dtype=torch.bool)
+            allowed[i] = False
+            allowed[i, torch.as_tensor(sp.allowed_token_ids, dtype=torch.long)] = True
+        for seq in sp.bad_words_token_ids or ():
+            seq = list(seq)
+            if not seq or not (0 <= seq[-1] < vocab_size):
+                continue
+            k = len(seq) - 1
+            if k == 0 or (len(out) >= k and list(out[-k:]) == seq[:-1]):
+                ban_r.append(i)
+                ban_c.append(seq[-1])
+        if sp.min_tokens > 0 and r.num_output_tokens < sp.min_tokens:
+            stops = set(sp.stop_token_ids or ())
+            if r.eos_token_id is not None and not sp.ignore_eos:
+                stops.add(r.eos_token_id)
+            for t in stops:
+                if 0 <= t < vocab_size:
+                    ban_r.append(i)
+                    ban_c.append(int(t))
+        for t, b in (sp.logit_bias or {}).items():
+            if 0 <= int(t) < vocab_size:
+                bias_r.append(i)
+                bias_c.append(int(t))
+                bias_v.append(float(b))
+    kw = {}
+    if allowed is not None:
+        kw["allowed_mask"] = allowed.to(device)
+    if bias_r:
+        kw["bias_index"] = torch.tensor([bias_r, bias_c], dtype=torch.int64, device=device)
+        kw["bias_values"] = torch.tensor(bias_v, dtype=torch.float32, device=device)
+    if ban_r:
+        kw["ban_index"] = torch.tensor([ban_r, ban_c], dtype=torch.int64, device=device)
+    return kw
+
+
+def compute_logprobs(logits: torch.Tensor, tokens: torch.Tensor, k: int):
+    """Log-probabilities under the model's raw distribution: (sampled token [B], top-k ids [B, k],
+    top-k values [B, k])."""
+    lp = torch.log_softmax(logits.float(), dim=-1)
+    tok_lp = lp.gather(1, tokens.view(-1, 1).long()).squeeze(1)
+    if k > 0:
+        vals, ids = lp.topk(k, dim=-1)
+    else:
+        vals, ids = lp.new_zeros((lp.shape[0], 0)), tokens.new_zeros((lp.shape[0], 0))
+    return tok_lp, ids, vals
+
+
 class Sampler:
     def __call__(self, logits: torch.Tensor, md: SamplingMetadata) -> torch.Tensor:
         """logits [B, V] (bf16 or fp32) -> token ids int64 [B]."""
-        if md.allowed_mask is not None:
-            logits = logits.float().masked_fill(~md.allowed_mask, float("-inf"))
+        if md.allowed_mask is not None or md.ban_index is not None or md.bias_index is not None:
+            logits = logits.float()
+            if md.allowed_mask is not None:
+                logits = logits.masked_fill(~md.allowed_mask, float("-inf"))
+            else:
+                logits = logits.clone()
+            if md.ban_index is not None:
+                logits[md.ban_index[0], md.ban_index[1]] = float("-inf")
+            if md.bias_index is not None:
+                logits.index_put_((md.bias_index[0], md.bias_index[1]), md.bias_values, accumulate=True)
         if md.all_greedy:
             return ops.argmax(logits)
         lf = ops.to_float_logits(logits)
