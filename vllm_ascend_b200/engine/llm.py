@@ -119,7 +119,8 @@ class LLMEngine:
         if p is None:
             return
         if self._model_proposer:
-            p.propose_step(so, sampled, self.runner.last_hidden, self.scheduler)
+            hidden = self.runner.model.aux_hidden if getattr(p, "method", "") == "eagle3" else self.runner.last_hidden
+            p.propose_step(so, sampled, hidden, self.scheduler)
         else:
             self.runner.propose_draft_tokens([r for r, _ in so.scheduled
                                               if r.status == RequestStatus.RUNNING and r.request_id in sampled])

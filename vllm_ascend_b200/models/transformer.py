@@ -290,6 +290,8 @@ class CausalLM:
         self.comm = TPComm(tp_group or pstate.get_tp_group())
         self.sp_ctx = None             # set by parallel.fused_linear.attach()
         self.layer_hook = None         # callable(local layer index), run after each layer
+        self.aux_layers = None         # layer indices whose residual-stream output EAGLE-3 heads read
+        self.aux_hidden = None         # [T, len(aux_layers) * H] of the latest eager forward
         self.full_embedding = None
         max_pos = max(max_model_len, 16)
         lo, hi = layer_range or (0, cfg.num_hidden_layers)
@@ -332,11 +334,17 @@ class CausalLM:
             residual = None
         else:
             h, residual = intermediate
+        aux = [] if self.aux_layers else None
         for layer, cache in zip(self.layers, kv_caches):
             call = getattr(layer, "offloaded_call", None)      # set by the weight offloader
             h, residual = call(h, residual, meta, cache) if call is not None else layer(h, residual, meta, cache)
+            if aux is not None:
+                for _ in range(self.aux_layers.count(layer.idx)):
+                    aux.append(h + residual)
             if self.layer_hook is not None:
                 self.layer_hook(layer.idx - self.layer_range[0])   # e.g. layer-wise KV push
+        if aux:
+            self.aux_hidden = torch.cat(aux, dim=-1)
         if not self.is_last:
             return h, residual
         h, _ = self.norm(h, residual)

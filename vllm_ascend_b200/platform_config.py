@@ -337,6 +337,8 @@ def check_and_update_config(engine_cfg) -> B200Config:
         engine_cfg.cache.enable_prefix_caching = False
     if cfg.weight_offload_config.enabled:
         cc.cudagraph_mode = "NONE"        # offloaded weights rotate through device buffers
+    if (engine_cfg.speculative_config or {}).get("method") == "eagle3":
+        cc.cudagraph_mode = "NONE"        # the head reads intermediate residual streams of eager forwards
     # 4 graph mode normalisation + capture sizes (platform.py:937-1117, 1275-1309)
     cc.cudagraph_mode = cc.cudagraph_mode.upper()
     if cc.cudagraph_mode not in GRAPH_MODES:

@@ -11,6 +11,7 @@ Draft tokens are argmax picks, i.e. deterministic proposals for the rejection sa
 from __future__ import annotations
 
 import copy
+import os
 from typing import Optional
 
 import numpy as np
@@ -62,6 +63,111 @@ class EagleHead:
         return self.lm_head(hidden)
 
 
+class Eagle3Head:
+    """EAGLE-3 draft head.  Conditioning is the target's residual stream at three depths (low, middle,
+    high), concatenated and projected by ``fc``; the single decoder layer attends over
+    [norm(embed(token_{i+1})); norm(h_i)] (a 2H-wide qkv input) and its pre-norm output is the
+    conditioning of the next draft step.  The head may predict over a reduced draft vocabulary;
+    ``d2t`` maps a draft index to its target token id (index + offset).  Architecture of the
+    eagle3 proposer the reference drives (vllm_ascend/spec_decode/llm_base_proposer.py:354-495 with
+    upstream llama_eagle3)."""
+
+    def __init__(self, target, cfg, device, max_model_len: int, seed_name: str = "eagle3",
+                 draft_vocab_size: Optional[int] = None):
+        from ..models.layers import ColumnParallelLinear, ParallelLMHead, VocabParallelEmbedding
+        from ..models.transformer import DecoderLayer
+        dtype = target.embed_tokens.weight.dtype
+        dcfg = copy.copy(cfg)
+        dcfg.num_experts = 0
+        dcfg.full_attention_interval = 0
+        pf = ParamFactory(dcfg, device, dtype)
+        comm = TPComm(pstate.get_tp_group())
+        H = cfg.hidden_size
+        self.H = H
+        self.embed_tokens = target.embed_tokens
+        self.fc_weight = pf.normal(f"{seed_name}.fc", (H, 3 * H))
+        layer = DecoderLayer(pf, dcfg, 10_000, comm, max_model_len)
+        a = layer.self_attn
+        kv_out = a.total_kv * a.D if a.total_kv >= comm.size else comm.size * a.D
+        a.qkv_proj = ColumnParallelLinear(pf, f"{seed_name}.midlayer.self_attn.qkv_proj", 2 * H,
+                                          [cfg.num_attention_heads * a.D, kv_out, kv_out], comm,
+                                          bias=cfg.attention_bias)
+        self.layers = [layer]
+        self.hidden_norm = RMSNorm(pf, H, cfg.rms_norm_eps)
+        self.norm = RMSNorm(pf, H, cfg.rms_norm_eps)
+        self.d2t = None
+        if draft_vocab_size and draft_vocab_size < cfg.vocab_size:
+            head = VocabParallelEmbedding(pf, f"{seed_name}.lm_head", draft_vocab_size, H, comm)
+            self.lm_head = ParallelLMHead(head)
+            self.d2t = torch.zeros(draft_vocab_size, dtype=torch.int64, device=device)
+        else:
+            self.lm_head = target.lm_head
+
+    def forward(self, input_ids, prev_hidden, meta, kv_caches):
+        """prev_hidden: [T, 3H] target residual streams (first pass) or [T, H] own pre-norm output."""
+        layer = self.layers[0]
+        hs = prev_hidden.to(self.fc_weight.dtype)
+        if hs.shape[-1] == 3 * self.H:
+            hs = ops.linear(hs, self.fc_weight, None, None)
+        emb, _ = layer.input_layernorm(self.embed_tokens(input_ids))
+        hn, _ = self.hidden_norm(hs)
+        attn = layer.self_attn(torch.cat([emb, hn], dim=-1), meta, kv_caches[0])
+        x, residual = layer.post_attention_layernorm(attn, hs.contiguous())
+        return layer.mlp(x) + residual                       # pre-norm: conditions the next draft step
+
+    def compute_logits(self, hidden):
+        out, _ = self.norm(hidden)
+        return self.lm_head(out)
+
+    def draft_tokens(self, hidden) -> torch.Tensor:
+        idx = self.compute_logits(hidden).argmax(-1)
+        return idx if self.d2t is None else idx + self.d2t[idx]
+
+    def named_parameters(self):
+        L = self.layers[0]
+        yield "fc.weight", self.fc_weight
+        yield "midlayer.input_layernorm.weight", L.input_layernorm.weight
+        yield "midlayer.hidden_norm.weight", self.hidden_norm.weight
+        yield "midlayer.post_attention_layernorm.weight", L.post_attention_layernorm.weight
+        for attr in ("qkv_proj", "o_proj"):
+            for n, t in getattr(L.self_attn, attr).named_tensors():
+                yield f"midlayer.self_attn.{attr}.{n}", t
+        for attr in ("gate_up_proj", "down_proj"):
+            for n, t in getattr(L.mlp, attr).named_tensors():
+                yield f"midlayer.mlp.{attr}.{n}", t
+        yield "norm.weight", self.norm.weight
+        if self.d2t is not None:
+            yield "lm_head.weight", self.lm_head.weight
+            yield "d2t", self.d2t
+
+    def load_weights(self, weights) -> set:
+        """HF EAGLE-3 checkpoint names (``fc``, ``midlayer.*`` / ``layers.0.*``, ``norm``, ``lm_head``,
+        ``d2t``); q/k/v and gate/up are merged.  Single-rank layout (draft heads are small: every TP
+        rank would load its slice the same way the target does)."""
+        params = dict(self.named_parameters())
+        L = self.layers[0].self_attn
+        nq, nkv = L.Hq * L.D, L.Hkv * L.D
+        loaded = set()
+        for name, w in weights:
+            n = name.replace("model.", "", 1) if name.startswith("model.") else name
+            n = n.replace("layers.0.", "midlayer.")
+            tgt, rows = n, None
+            for hf, (lo, hi) in (("q_proj", (0, nq)), ("k_proj", (nq, nq + nkv)), ("v_proj", (nq + nkv, nq + 2 * nkv))):
+                if f".{hf}." in n:
+                    tgt, rows = n.replace(hf, "qkv_proj"), (lo, hi)
+            for hf, half in (("gate_proj", 0), ("up_proj", 1)):
+                if f".{hf}." in n:
+                    tgt = n.replace(hf, "gate_up_proj")
+                    I = params[tgt].shape[0] // 2
+                    rows = (half * I, half * I + I)
+            if tgt not in params:
+                continue
+            dst = params[tgt] if rows is None else params[tgt][rows[0]:rows[1]]
+            dst.copy_(w.to(dst.dtype).to(dst.device))
+            loaded.add(name)
+        return loaded
+
+
 class DraftModelProposer:
     name = "draft_model"
 
@@ -69,7 +175,16 @@ class DraftModelProposer:
         self.method, self.k, self.runner = method, num_speculative_tokens, runner
         self.needs_hidden_states = method in ("eagle", "eagle3", "mtp")
         dev = runner.device
-        if self.needs_hidden_states:
+        if method == "eagle3":
+            self.model = Eagle3Head(runner.model, runner.mcfg, dev, runner.max_model_len,
+                                    draft_vocab_size=spec_cfg.get("draft_vocab_size"))
+            N = runner.mcfg.num_hidden_layers
+            runner.model.aux_layers = (min(2, N - 1), N // 2, max(N - 3, 0))
+            path = spec_cfg.get("model")
+            if isinstance(path, str) and os.path.isdir(path):
+                from ..models.transformer import iterate_safetensors
+                self.model.load_weights(iterate_safetensors(path))
+        elif self.needs_hidden_states:
             self.model = EagleHead(runner.model, runner.mcfg, dev, runner.max_model_len, seed_name=method)
         else:
             from ..models import build_model
@@ -179,7 +294,10 @@ class DraftModelProposer:
             if not act:
                 break
             idx = torch.tensor(act, device=h_last.device)
-            tok = self.model.compute_logits(h_last[idx]).argmax(-1).cpu().numpy()
+            if hasattr(self.model, "draft_tokens"):
+                tok = self.model.draft_tokens(h_last[idx]).cpu().numpy()
+            else:
+                tok = self.model.compute_logits(h_last[idx]).argmax(-1).cpu().numpy()
             for i, t in zip(act, tok):
                 q = live[i]
                 drafts[i].append(int(t))
