@@ -62,7 +62,7 @@ def test_expand_draft_inputs_kernel():
     assert cu_out.tolist() == [0, 3, 4, 8]
 
 
-@pytest.mark.parametrize("method", ["ngram", "draft_model", "eagle", "medusa"])
+@pytest.mark.parametrize("method", ["ngram", "draft_model", "eagle", "eagle3", "medusa"])
 def test_engine_speculative_on_gpu(method):
     from test_gpu_engine import _cfg
     from vllm_ascend_b200.engine.llm import LLM

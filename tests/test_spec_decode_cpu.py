@@ -121,7 +121,7 @@ def test_engine_speculative_random_sampling_runs_and_respects_max_tokens():
     assert all(len(o.outputs[0].token_ids) == 17 for o in outs)
 
 
-@pytest.mark.parametrize("method", ["draft_model", "eagle", "medusa"])
+@pytest.mark.parametrize("method", ["draft_model", "eagle", "eagle3", "medusa"])
 def test_engine_model_based_proposers_keep_greedy_output(method):
     kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=40)
     rng = np.random.default_rng(1)
@@ -141,3 +141,36 @@ def test_engine_model_based_proposers_keep_greedy_output(method):
         # far fewer target steps than tokens
         assert st["verify_steps"] <= 5
     assert llm.engine.runner.proposer.stats["draft_forwards"] > 0
+
+
+def test_eagle3_head_reads_three_residual_streams_and_loads_hf_names(tmp_path):
+    from vllm_ascend_b200.spec_decode.draft_model import Eagle3Head
+    llm = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=128, max_num_seqs=4,
+              speculative_config={"method": "eagle3", "num_speculative_tokens": 2, "draft_vocab_size": 128})
+    target = llm.engine.runner.model
+    head = llm.engine.runner.proposer.model
+    assert isinstance(head, Eagle3Head) and len(target.aux_layers) == 3
+    assert head.fc_weight.shape == (target.cfg.hidden_size, 3 * target.cfg.hidden_size)
+    assert head.layers[0].self_attn.qkv_proj.weight.shape[1] == 2 * target.cfg.hidden_size
+    llm.generate([[1, 2, 3, 4, 5, 6]], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))
+    assert target.aux_hidden.shape[-1] == 3 * target.cfg.hidden_size
+    # checkpoint names of the published heads: split q/k/v and gate/up, reduced vocabulary + d2t
+    H, D = target.cfg.hidden_size, target.cfg.head_dim
+    nq, nkv, I = target.cfg.num_attention_heads * D, target.cfg.num_key_value_heads * D, target.cfg.intermediate_size
+    g = torch.Generator().manual_seed(3)
+    ck = {"fc.weight": torch.randn(H, 3 * H, generator=g), "midlayer.self_attn.q_proj.weight": torch.randn(nq, 2 * H, generator=g),
+          "midlayer.self_attn.k_proj.weight": torch.randn(nkv, 2 * H, generator=g),
+          "midlayer.self_attn.v_proj.weight": torch.randn(nkv, 2 * H, generator=g),
+          "midlayer.self_attn.o_proj.weight": torch.randn(H, nq, generator=g),
+          "midlayer.mlp.gate_proj.weight": torch.randn(I, H, generator=g), "midlayer.mlp.up_proj.weight": torch.randn(I, H, generator=g),
+          "midlayer.mlp.down_proj.weight": torch.randn(H, I, generator=g), "midlayer.hidden_norm.weight": torch.rand(H, generator=g),
+          "midlayer.input_layernorm.weight": torch.rand(H, generator=g), "midlayer.post_attention_layernorm.weight": torch.rand(H, generator=g),
+          "norm.weight": torch.rand(H, generator=g), "lm_head.weight": torch.randn(128, H, generator=g),
+          "d2t": torch.arange(128) * 3}
+    loaded = head.load_weights(ck.items())
+    assert loaded == set(ck)
+    qkv = head.layers[0].self_attn.qkv_proj.weight
+    assert torch.equal(qkv[nq:nq + nkv], ck["midlayer.self_attn.k_proj.weight"])
+    assert torch.equal(head.layers[0].mlp.gate_up_proj.weight[I:], ck["midlayer.mlp.up_proj.weight"])
+    toks = head.draft_tokens(torch.randn(5, H, generator=g))
+    assert ((toks % 4) == 0).all() and toks.max() < 128 * 4             # index + d2t[index] = 4 * index
