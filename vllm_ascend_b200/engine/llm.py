@@ -92,7 +92,7 @@ class LLMEngine:
     def add_request(self, prompt_token_ids: Sequence[int], sampling_params: SamplingParams,
                     request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None,
                     job_id: Optional[str] = None, lora_request=None,
-                    multi_modal_data: Optional[dict] = None) -> str:
+                    multi_modal_data: Optional[dict] = None, prompt_embeds=None) -> str:
         rid = request_id or f"req-{next(self._req_counter)}"
         if lora_request is not None and self.runner.lora_manager is None:
             raise ValueError("a LoRA request needs an engine built with enable_lora=True")
@@ -107,6 +107,18 @@ class LLMEngine:
             mrope, delta = mrope_positions(prompt_token_ids, mm_items,
                                            VisionConfig.from_hf(mcfg.vision_config).spatial_merge_size,
                                            mcfg.tokens_per_second)
+        if prompt_embeds is not None:
+            # the caller supplies the input embeddings: the ids are placeholders, the rows are merged in
+            # the way encoder outputs are
+            from ..multimodal.inputs import MMInput
+            pe = torch.as_tensor(prompt_embeds)
+            if pe.dim() != 2 or pe.shape[1] != mcfg.hidden_size:
+                raise ValueError(f"prompt_embeds must be [num_tokens, {mcfg.hidden_size}]")
+            if self.runner.mm is None:
+                from .mm_runner import MultimodalState
+                self.runner.mm = MultimodalState(self.runner)
+            prompt_token_ids = [0] * pe.shape[0]
+            mm_items = [MMInput("embeds", 0, pe.shape[0], (0, 0, 0), None, f"embeds-{rid}", embeds=pe)]
         req = Request(rid, np.asarray(prompt_token_ids, dtype=np.int32), sampling_params,
                       eos_token_id=self.eos_token_id, kv_transfer_params=kv_transfer_params,
                       job_id=job_id, lora_request=lora_request, mm_inputs=mm_items,
@@ -352,6 +364,21 @@ class LLM:
                 out.append({"modality": modality, "hash": it.hash, "grid_thw": list(it.grid_thw)})
         return out
 
+    def embed(self, prompts, normalize: bool = True) -> list:
+        """Sequence embeddings: the final hidden state of every prompt's last token (last-token
+        pooling, the pooling of decoder-only embedding models), L2-normalised by default."""
+        sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, extra_args={"pooling": True})
+        eng = self.engine
+        rids = [eng.add_request(p["prompt_token_ids"] if isinstance(p, dict) else p, sp) for p in prompts]
+        reqs = [eng.scheduler.requests[r] for r in rids]
+        while eng.has_unfinished():
+            eng.step()
+        out = []
+        for r in reqs:
+            v = r.pooled
+            out.append(torch.nn.functional.normalize(v, dim=-1) if normalize else v)
+        return out
+
     def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  use_tqdm: bool = False, lora_request=None) -> list[RequestOutput]:
         """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``)."""
@@ -365,12 +392,16 @@ class LLM:
         for i, p in enumerate(prompts):
             if dp.world_size > 1 and i % dp.world_size != dp.rank_in_group:
                 continue            # data parallel: every DP rank serves its own slice
-            ids = p["prompt_token_ids"] if isinstance(p, dict) else p
+            ids = p.get("prompt_token_ids") if isinstance(p, dict) else p
             sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
             ktp = p.get("kv_transfer_params") if isinstance(p, dict) else None
             lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
             mmd = p.get("multi_modal_data") if isinstance(p, dict) else None
-            rid = eng.add_request(ids, sp, kv_transfer_params=ktp, lora_request=lr, multi_modal_data=mmd)
+            pe = p.get("prompt_embeds") if isinstance(p, dict) else None
+            if pe is not None and ids is None:
+                ids = []
+            rid = eng.add_request(ids, sp, kv_transfer_params=ktp, lora_request=lr, multi_modal_data=mmd,
+                                  prompt_embeds=pe)
             order.append(rid)
             mine.append(i)
             reqs[rid] = eng.scheduler.requests[rid]

@@ -71,6 +71,9 @@ class MultimodalState:
             if key in self.encoder_cache:
                 self.stats["encoder_cache_hits"] += 1
                 continue
+            if it.embeds is not None:
+                self.encoder_cache[key] = it.embeds.to(self.runner.device, self.runner.model.dtype)
+                continue
             if self.ec_connector is not None:
                 got = self.ec_connector.load(it.hash, self.runner.device, self.runner.model.dtype)
                 if got is not None:

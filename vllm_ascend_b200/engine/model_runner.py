@@ -537,6 +537,7 @@ class ModelRunner:
             self.stats["graph_replays"] += 1
             self.stats["graph_kernel_launches"] += self.graph_wrapper.entries[desc].num_launches
             self.last_hidden = hidden_out
+            self._capture_pooled(hidden_out[:B], sample_reqs)
             logits = None if self._reduce_sample(sample_reqs) else self.model.compute_logits(hidden_out[:B])
         else:
             hidden = self._forward(Tp, meta)
@@ -551,6 +552,7 @@ class ModelRunner:
                 h_sel = hidden[:T]
             else:
                 h_sel = hidden[torch.tensor(sel, dtype=torch.int64, device=self.device)]
+            self._capture_pooled(h_sel, sample_reqs)
             logits = None if self._reduce_sample(sample_reqs) else self.model.compute_logits(h_sel)
         if logits is None:
             tokens = self.model.lm_head.greedy_tokens(h_sel if gsize is None else hidden_out[:B])
@@ -655,6 +657,7 @@ class ModelRunner:
             if not sel:
                 return _StepHandle(None, [], None, None, "mixed", t_start)
             h_sel = hidden[:T] if len(sel) == T else hidden[self._to_dev(torch.tensor(sel, dtype=torch.int64))]
+        self._capture_pooled(h_sel, sample_reqs)
         dev_lp = None
         if self._reduce_sample(sample_reqs):
             tokens = self.model.lm_head.greedy_tokens(h_sel)
@@ -711,6 +714,15 @@ class ModelRunner:
             entry = {int(ids[i, j]): float(vals[i, j]) for j in range(min(int(k), ids.shape[1]))}
             entry[int(toks[i])] = float(tok_lp[i])
             self._logprobs_out.setdefault(r.request_id, []).append(entry)
+
+    def _capture_pooled(self, h_sel: torch.Tensor, sample_reqs: list) -> None:
+        """Embedding requests keep the final hidden state of their last prompt token."""
+        if len(self._sample_rows) != len(sample_reqs) or any(k != 1 for k in self._sample_rows):
+            return
+        for i, r in enumerate(sample_reqs):
+            ea = r.sampling_params.extra_args
+            if ea and ea.get("pooling") and r.num_output_tokens == 0:
+                r.pooled = h_sel[i].float().cpu()
 
     def take_logprobs(self) -> dict:
         out, self._logprobs_out = self._logprobs_out, {}

@@ -94,6 +94,7 @@ class Request:
     job_id: Optional[str] = None
     # multimodal: items (placeholder run + pixels), 3-axis rotary positions of the prompt and the
     # offset decoded tokens continue from (position = index + delta)
+    pooled: Optional[Any] = None          # final hidden state of the last prompt token (embedding requests)
     logprobs: Optional[list] = None       # per generated token: {token id: logprob} (sampled + top-N)
     mm_inputs: list = field(default_factory=list)
     mrope_positions: Optional[np.ndarray] = None

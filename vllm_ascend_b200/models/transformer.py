@@ -353,6 +353,9 @@ class CausalLM:
     def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
         return self.lm_head(hidden)
 
+    def embed_input_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return self.embed_tokens(input_ids)
+
     __call__ = forward
 
     # -- parameters --------------------------------------------------------

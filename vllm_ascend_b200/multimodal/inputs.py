@@ -18,6 +18,7 @@ class MMInput:
     pixel_values: Optional[torch.Tensor]   # [t*h*w, patch_dim]; None once the encoder output is cached
     hash: str = ""
     second_per_grid: Optional[float] = None
+    embeds: Optional[torch.Tensor] = None  # rows supplied by the caller (prompt embeddings): no encoder run
 
     @property
     def end(self) -> int:
