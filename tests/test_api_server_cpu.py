@@ -88,3 +88,49 @@ def test_completions_metrics_and_pd_proxy():
             s.stop()
         pre.engine.kv_connector.close()
         dec.engine.kv_connector.close()
+
+
+def test_streaming_chat_and_embeddings_endpoints():
+    import json
+    llm = _llm()
+    prompt = [5, 6, 7, 8, 9, 10]
+    want = llm.generate([prompt], SamplingParams(max_tokens=7, temperature=0.0, ignore_eos=True))[0].outputs[0].token_ids
+    vec = llm.embed([prompt])[0]
+    srv = _Server(build_app(llm, None, "tiny"))
+    try:
+        # server-sent events: the chunks concatenate to the non-streaming answer, then [DONE]
+        r = requests.post(srv.url + "/v1/completions", json={"prompt": prompt, "max_tokens": 7, "temperature": 0.0,
+                                                             "ignore_eos": True, "stream": True}, stream=True, timeout=60)
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+        toks, finish, done = [], None, False
+        for line in r.iter_lines():
+            if not line:
+                continue
+            payload = line.decode()[len("data: "):]
+            if payload == "[DONE]":
+                done = True
+                break
+            ch = json.loads(payload)["choices"][0]
+            toks += ch["token_ids"]
+            finish = ch["finish_reason"] or finish
+        assert done and toks == want and finish == "length"
+        # chat endpoint with a pre-templated prompt (no tokenizer on this server)
+        r = requests.post(srv.url + "/v1/chat/completions", json={
+            "messages": [{"role": "user", "content": "hi"}], "prompt_token_ids": prompt, "max_tokens": 7,
+            "temperature": 0.0, "ignore_eos": True, "logprobs": True, "top_logprobs": 2}, timeout=60)
+        assert r.status_code == 200, r.text
+        body = r.json()
+        assert body["object"] == "chat.completion"
+        ch = body["choices"][0]
+        assert ch["message"]["token_ids"] == want and len(ch["logprobs"]) == 7
+        r = requests.post(srv.url + "/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}]},
+                          timeout=60)
+        assert r.status_code == 400
+        # embeddings
+        r = requests.post(srv.url + "/v1/embeddings", json={"input": [prompt, [1, 2, 3]]}, timeout=60)
+        assert r.status_code == 200, r.text
+        data = r.json()["data"]
+        assert len(data) == 2 and np.allclose(data[0]["embedding"], vec.numpy(), atol=1e-5)
+    finally:
+        srv.stop()
+        srv.server.config.app.state.engine_loop.stop()
