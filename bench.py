@@ -268,6 +268,8 @@ def main():
             "config": {"model": args.model, "global_batch": args.num_prompts,
                        "seq_len": args.input_len, "output_len": args.output_len,
                        "parallelism": (f"ep{world}" if ep else f"tp{world}"),
+                       "tp_comm": os.environ.get("VLLM_B200_TP_COMM", "fused"),
+                       "tp_comm_calibration": getattr(llm.engine.worker, "tp_comm_calibration", None),
                        "max_num_seqs": args.max_num_seqs,
                        "max_num_batched_tokens": args.max_num_batched_tokens,
                        "kv_blocks": runner.num_blocks, "block_size": runner.block_size,

@@ -38,7 +38,8 @@ env_variables: dict[str, Callable[[], Any]] = {
     "VLLM_B200_DECODE_ATTN": _str("VLLM_B200_DECODE_ATTN", "native"),
     # MLA attention: "tcgen05" (absorbed-weight kernel) or "torch" (oracle)
     "VLLM_B200_MLA_ATTN": _str("VLLM_B200_MLA_ATTN", "tcgen05"),
-    # fused TP collectives over peer memory: "fused" or "nccl"
+    # TP collectives of the linear layers: "fused" (inside the GEMM kernels over peer memory),
+    # "nccl" (all-reduce), or "auto" (both are timed at start-up, per step class, the faster one serves)
     "VLLM_B200_TP_COMM": _str("VLLM_B200_TP_COMM", "fused"),
     # MoE path override: "", "allgather", "alltoall", "fused"
     "VLLM_B200_MOE_COMM": _str("VLLM_B200_MOE_COMM", ""),

@@ -289,6 +289,8 @@ class CausalLM:
         pf = ParamFactory(cfg, self.device, self.dtype)
         self.comm = TPComm(tp_group or pstate.get_tp_group())
         self.sp_ctx = None             # set by parallel.fused_linear.attach()
+        self.sp_prefill = self.sp_decode = True     # which step classes use it (auto mode calibrates)
+        self.sp_decode_max_tokens = 2048            # steps up to this many tokens count as decode-like
         self.layer_hook = None         # callable(local layer index), run after each layer
         self.aux_layers = None         # layer indices whose residual-stream output EAGLE-3 heads read
         self.aux_hidden = None         # [T, len(aux_layers) * H] of the latest eager forward
@@ -325,7 +327,8 @@ class CausalLM:
     # -- forward ---------------------------------------------------------
     def forward(self, input_ids: torch.Tensor, meta, kv_caches: list,
                 intermediate: Optional[tuple] = None, inputs_embeds: Optional[torch.Tensor] = None):
-        if self.sp_ctx is not None and input_ids.is_cuda and inputs_embeds is None:
+        if self.sp_ctx is not None and input_ids.is_cuda and inputs_embeds is None \
+                and (self.sp_prefill if input_ids.shape[0] > self.sp_decode_max_tokens else self.sp_decode):
             from ..parallel.fused_linear import forward_sp
             return forward_sp(self, self.sp_ctx, input_ids, meta, kv_caches)
         if self.is_first:

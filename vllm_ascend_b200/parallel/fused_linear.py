@@ -209,3 +209,49 @@ def attach(model, engine_cfg, device: torch.device) -> Optional[FusedTPContext]:
     model.full_embedding = full
     model.sp_ctx = ctx
     return ctx
+
+
+def calibrate(runner, group: GroupCoordinator) -> dict:
+    """``VLLM_B200_TP_COMM=auto``: time one forward pass per step class (a full prefill chunk, a
+    decode batch) with the fused peer-memory dataflow and with the NCCL all-reduce dataflow, take
+    the maximum over the TP ranks, and keep the faster one for that class.  The choice is stored
+    on the model (``sp_prefill`` / ``sp_decode``); a fused pass that raises keeps NCCL."""
+    import torch.distributed as dist
+    model = runner.model
+    ctx = model.sp_ctx
+    out = {}
+    if ctx is None:
+        return out
+    classes = {"prefill": (min(8, runner.max_seqs), max(1, min(runner.max_tokens // min(8, runner.max_seqs),
+                                                             runner.max_model_len - 1))),
+               "decode": (min(256, runner.max_seqs), 1)}
+    for name, (B, q) in classes.items():
+        times = {}
+        for path in ("fused", "nccl"):
+            model.sp_ctx = ctx if path == "fused" else None
+            try:
+                meta, T, Tp, _, _ = runner._dummy_meta(B, q)
+                meta.slot_mapping.fill_(-1)
+                for _ in range(2):
+                    runner._forward(Tp, meta)
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+                for _ in range(3):
+                    runner._forward(Tp, meta)
+                ev1.record()
+                torch.cuda.synchronize()
+                if path == "fused":
+                    ctx.check()
+                t = torch.tensor([ev0.elapsed_time(ev1) / 3], dtype=torch.float64)
+            except Exception as e:                      # keep serving on the NCCL path
+                from ..logger import logger
+                logger.warning("fused TP path failed during calibration (%s): using NCCL", e)
+                t = torch.tensor([float("inf")], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group.cpu_group)
+            times[path] = float(t)
+        model.sp_ctx = ctx
+        out[name] = {"fused_ms": times["fused"], "nccl_ms": times["nccl"],
+                     "choice": "fused" if times["fused"] <= times["nccl"] * 1.02 else "nccl"}
+    model.sp_prefill = out["prefill"]["choice"] == "fused"
+    model.sp_decode = out["decode"]["choice"] == "fused"
+    return out

@@ -100,7 +100,8 @@ class B200Worker:
             from ..offloader import PrefetchOffloader
             self.offloader = PrefetchOffloader(self.runner.model, oc.group_size, oc.num_in_group, oc.prefetch_step)
         # the fused sequence-sharded TP path has no adapter hook: LoRA engines use the NCCL path
-        if self.world_size > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM == "fused" \
+        self.tp_comm_calibration = None
+        if self.world_size > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM in ("fused", "auto") \
                 and pc.tensor_parallel_size > 1 and not cfg.enable_lora \
                 and pc.prefill_context_parallel_size == 1:
             from ..parallel import fused_linear
@@ -123,6 +124,13 @@ class B200Worker:
 
     def compile_or_warm_up_model(self) -> None:
         self.runner.warmup()
+        if envs.VLLM_B200_TP_COMM == "auto" and getattr(self.runner.model, "sp_ctx", None) is not None:
+            from ..parallel import fused_linear
+            try:
+                self.tp_comm_calibration = fused_linear.calibrate(self.runner, pstate.get_tp_group())
+            except Exception as e:          # calibration is an optimisation: keep the fused default
+                logger.warning("TP communication calibration failed: %s", e)
+            logger.info("TP communication path per step class: %s", self.tp_comm_calibration)
 
     def capture_model(self) -> None:
         self.runner.capture_graphs()
