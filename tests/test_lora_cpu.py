@@ -124,3 +124,36 @@ def test_lora_slot_eviction_and_pinning():
     with pytest.raises(ValueError):
         LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=64, max_num_seqs=4) \
             .engine.add_request([1, 2, 3], SamplingParams(max_tokens=1), lora_request=reqs[0])
+
+
+def test_expert_lora_matches_merged_expert_weights():
+    """Adapters on routed experts (gate / up / down of every expert) plus attention projections:
+    mixed batch of adapter and plain requests equals engines with the deltas merged into the weights."""
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=128, max_num_seqs=8)
+    llm = LLM("tiny-moe", enable_lora=True, max_loras=2, max_lora_rank=8, **kw)
+    cfg = llm.cfg.model
+    assert llm.engine.runner.lora_manager.moe_layers and not llm.engine.runner.lora_manager.graph_safe
+    g = torch.Generator().manual_seed(5)
+    rank, alpha = 4, 8.0
+    H, I = cfg.hidden_size, cfg.moe_intermediate_size
+    ad = _adapter(cfg, rank, 9, targets=("q_proj", "o_proj"))
+    for li in range(cfg.num_hidden_layers):
+        for e in range(cfg.num_experts):
+            base = f"base_model.model.model.layers.{li}.mlp.experts.{e}"
+            for name, (k, n) in (("gate_proj", (H, I)), ("up_proj", (H, I)), ("down_proj", (I, H))):
+                ad[f"{base}.{name}.lora_A.weight"] = torch.randn(rank, k, generator=g) * 0.3
+                ad[f"{base}.{name}.lora_B.weight"] = torch.randn(n, rank, generator=g) * 0.3
+    req = LoRARequest("moe", 7, tensors=ad, rank=rank, alpha=alpha)
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(1, 500, size=n).tolist() for n in (23, 9, 31)]
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    toks = [o.outputs[0].token_ids for o in llm.generate(prompts, sp, lora_request=[req, None, req])]
+
+    def oracle(adapter, idx):
+        ref = LLM("tiny-moe", **kw)
+        if adapter is not None:
+            ref.engine.runner.model.load_weights(_merged_state(ref, adapter, rank, alpha).items())
+        return [o.outputs[0].token_ids for o in ref.generate([prompts[i] for i in idx], sp)]
+    assert [toks[0], toks[2]] == oracle(ad, [0, 2])
+    assert [toks[1]] == oracle(None, [1])
+    assert toks[0] != oracle(None, [0])[0]

@@ -506,6 +506,10 @@ class ModelRunner:
         pp.send((res if res is not None else h).contiguous(), pp.rank_in_group + 1)
         return h
 
+    def _lora_step_needs_eager(self, so: SchedulerOutput) -> bool:
+        lm = self.lora_manager
+        return lm is not None and not lm.graph_safe and any(r.lora_request is not None for r, _ in so.scheduled)
+
     def _graph_size_for(self, B: int) -> Optional[int]:
         if not self.capture_sizes or B > self.capture_sizes[-1]:
             return None
@@ -529,6 +533,8 @@ class ModelRunner:
         B = len(so.scheduled)
         decode_only = all(n == 1 for _, n in so.scheduled)
         gsize = self._graph_size_for(B) if decode_only else None
+        if gsize is not None and self._lora_step_needs_eager(so):
+            gsize = None
         meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
         t_prep = time.perf_counter()
         if gsize is not None:
@@ -628,6 +634,8 @@ class ModelRunner:
         B = len(so.scheduled)
         decode_only = all(n == 1 for _, n in so.scheduled)
         gsize = self._graph_size_for(B) if decode_only else None
+        if gsize is not None and self._lora_step_needs_eager(so):
+            gsize = None
         meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
         if prev is not None:
             src, dst = [], []
@@ -945,7 +953,7 @@ class ModelRunner:
                                               launch_counter=ops.launch_counter)
         # with adapters enabled every size is captured twice: the LoRA kernels are part of the
         # graph only when some request of the step uses an adapter
-        variants = [False, True] if self.lora_manager is not None else [False]
+        variants = [False, True] if (self.lora_manager is not None and self.lora_manager.graph_safe) else [False]
         for size in sorted(self.capture_sizes, reverse=True):
             for has_lora in variants:
                 meta, T, Tp, _, _ = self._dummy_meta(size, 1)

@@ -59,6 +59,7 @@ class LoRAManager:
         self.pinned: set[int] = set()
         self.free_slots = list(range(max_loras))
         self.layers: dict[tuple[int, str], LoRALayerState] = {}
+        self.moe_layers: dict[int, object] = {}          # layer index -> lora.moe.MoELoRAState
         self._attach()
 
     def _attach(self) -> None:
@@ -68,6 +69,15 @@ class LoRAManager:
             mlp = getattr(L, "mlp", None)
             if mlp is not None and hasattr(mlp, "gate_up_proj"):
                 mods["gate_up_proj"], mods["down_proj"] = mlp.gate_up_proj, mlp.down_proj
+            if mlp is not None and hasattr(mlp, "w13") and getattr(mlp, "ep", None) is None:
+                from .moe import MoELoRAState
+                E, two_i, H = mlp.w13.shape
+                Il = two_i // 2
+                z = lambda *shape: torch.zeros(shape, dtype=self.dtype, device=self.device)     # noqa: E731
+                n = self.max_loras * E
+                mlp.lora = MoELoRAState(z(n, 2 * r, H), z(n, Il, r), z(n, Il, r), z(n, r, Il), z(n, H, r), E, r,
+                                        self.punica)
+                self.moe_layers[L.idx] = mlp.lora
             for name, lin in mods.items():
                 if lin is None or getattr(lin, "weight", None) is None:
                     continue
@@ -143,7 +153,14 @@ class LoRAManager:
         from safetensors.torch import load_file
         return load_file(path), int(cfg["r"]), float(cfg.get("lora_alpha", cfg["r"]))
 
+    @property
+    def graph_safe(self) -> bool:
+        """Adapter steps of models with expert adapters take a path with host-side routing reads."""
+        return not self.moe_layers
+
     def _zero_slot(self, slot: int) -> None:
+        for ms in self.moe_layers.values():
+            ms.zero_slot(slot)
         for st in self.layers.values():
             st.a[slot].zero_()
             for b in st.b:
@@ -153,6 +170,28 @@ class LoRAManager:
         comm = self.model.comm
         tp, tr = comm.size, comm.rank
         for name, w in tensors.items():
+            me = re.search(r"layers\.(\d+)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.lora_([AB])(?:\.default)?\.weight",
+                           name)
+            if me:
+                ms = self.moe_layers.get(int(me.group(1)))
+                if ms is None:
+                    continue
+                e, proj, which = int(me.group(2)), me.group(3), me.group(4)
+                row = slot * ms.num_experts + e
+                w = w.to(self.device, self.dtype)
+                Il = ms.b_gate.shape[1]
+                if proj in ("gate_proj", "up_proj"):
+                    off = 0 if proj == "gate_proj" else ms.rank
+                    if which == "A":                   # [r, H]
+                        ms.a13[row, off:off + rank] = w
+                    else:                              # [I, r] rows sharded like the expert's weight
+                        dst = ms.b_gate if proj == "gate_proj" else ms.b_up
+                        dst[row, :, :rank] = (w[tr * Il:(tr + 1) * Il].float() * scaling).to(self.dtype)
+                elif which == "A":                     # down: [r, I] columns sharded
+                    ms.a2[row, :rank] = w[:, tr * Il:(tr + 1) * Il]
+                else:                                  # [H, r]
+                    ms.b2[row, :, :rank] = (w.float() * scaling).to(self.dtype)
+                continue
             m = re.search(r"layers\.(\d+)\.(?:self_attn|mlp)\.(\w+)\.lora_([AB])(?:\.default)?\.weight", name)
             if not m or m.group(2) not in _TARGETS:
                 continue

@@ -110,8 +110,12 @@ class SparseMoeBlock:
             with torch.cuda.stream(side):
                 overlap = self.shared(x)
                 x.record_stream(side)
+        moe_lora = getattr(self, "lora", None)
         if self.runtime is not None and self.ep is not None:
             y = self.runtime.forward(self, x, w, ids)          # EP dispatch/combine paths
+        elif moe_lora is not None and moe_lora.punica.any_active and self.quant is None:
+            from ..lora.moe import fused_experts_lora
+            y = fused_experts_lora(x, self.w13, self.w2, w, ids, self.expert_map, moe_lora)
         else:
             y = fused_moe.fused_experts(x, self.w13, self.w2, w, ids, self.expert_map, self.quant)
         if self.ep is None:
