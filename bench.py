@@ -33,7 +33,7 @@ import numpy as np
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
-# reference headline numbers (Ascend NPU, other hardware): BASELINE.md part B
+# reference headline numbers (Ascend NPU, other hardware), as published with the reference
 PUBLISHED = {"qwen3-8b": 349.97}   # Qwen3-8B offline throughput, out tok/s (128 in / 128 out)
 
 

@@ -1,7 +1,7 @@
 """Kernel time shares of engine steps (torch.profiler / CUPTI), split by step kind.
 
     python benchmarks/step_profile.py --model qwen3-8b --num-prompts 1024 --skip-steps 40 \
-        --mixed-steps 3 --decode-steps 3 --out gpurun_out/step_profile.txt
+        --mixed-steps 3 --decode-steps 3 --out step_profile.txt
     (under torchrun with N ranks it profiles rank 0 of a TP=N engine)
 
 Fills the engine with the benchmark workload, lets it reach steady state, then profiles a few
