@@ -188,6 +188,7 @@ def supports(model) -> bool:
     from ..models.layers import GQAAttention, SwiGLUMLP
     cfg = model.cfg
     return (not cfg.use_mla and not cfg.is_moe and model.dtype == torch.bfloat16
+            and not cfg.mrope_section and not cfg.is_hybrid
             and model.is_first and model.is_last
             and all(isinstance(L.self_attn, GQAAttention) and isinstance(L.mlp, SwiGLUMLP)
                     and L.self_attn.qkv_proj.quant is None for L in model.layers))
