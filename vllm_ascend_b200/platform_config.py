@@ -332,6 +332,9 @@ def check_and_update_config(engine_cfg) -> B200Config:
         cc.cudagraph_mode = "NONE"        # token counts differ per replica and are padded per step
     _validate_eplb(cfg.eplb_config, mc.is_moe, pc.enable_expert_parallel)
     _validate_scheduler_ext(cfg.scheduler_config, engine_cfg)
+    if mc.is_hybrid and engine_cfg.speculative_config:
+        # a rejected draft token has already advanced the recurrent state and cannot be taken back
+        raise ValueError("speculative decoding is not supported for models with recurrent (linear-attention) layers")
     if mc.is_hybrid and engine_cfg.cache.enable_prefix_caching:
         # a recurrent state is not addressable by block: a cached prefix could not restore it
         engine_cfg.cache.enable_prefix_caching = False
