@@ -300,3 +300,35 @@ def test_prompt_embeds_and_embedding_api():
     again = llm.embed([prompts[1]], normalize=False)[0]
     assert torch.allclose(torch.nn.functional.normalize(again, dim=-1), vecs[1], atol=1e-5)
     assert not torch.allclose(vecs[0], vecs[1])
+
+
+def test_sparse_mla_model_with_lightning_indexer():
+    """DeepSeek-V3.2 style layers: with index_topk at least the context length the indexer keeps every
+    key and the model equals dense MLA on the same weights; a small top-k changes the continuation,
+    and decoding equals a cache-free recomputation that applies the same selection."""
+    from vllm_ascend_b200.config import get_model_config
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(1, 500, size=n).tolist() for n in (40, 13, 57)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    kw = dict(device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
+
+    def run(topk):
+        cfg = get_model_config("tiny-deepseek-sparse")
+        cfg.index_topk = topk
+        llm = LLM(cfg, **kw)
+        return llm, [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    dense_llm, dense = run(0)
+    full_llm, full = run(128)
+    # the dense model has no indexer parameters: copy the shared ones so both use the same weights
+    shared = dict(dense_llm.engine.runner.model.named_parameters())
+    src = dict(full_llm.engine.runner.model.named_parameters())
+    assert any("indexer" in k for k in src) and not any("indexer" in k for k in shared)
+    assert all(torch.equal(shared[k], src[k]) for k in shared)
+    assert full == dense
+    _, small = run(8)
+    assert small != dense and all(len(t) == 6 for t in small)
+    # chunked prefill + decode of the sparse model equals one-shot prefill of the same engine settings
+    cfg = get_model_config("tiny-deepseek-sparse")
+    cfg.index_topk = 8
+    one = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=128, block_size=16)
+    assert [o.outputs[0].token_ids for o in one.generate(prompts, sp)] == small

@@ -164,3 +164,36 @@ def test_sparse_mla_attention_gather_path():
     torch.cuda.synchronize()
     _native.check_status(torch.device("cuda"))
     assert (got.float().cpu() - want).abs().max() < 0.02
+
+
+def test_sparse_mla_model_on_engine():
+    """DeepSeek-V3.2 style model on the GPU: native indexer + gather + MLA kernel.  With top-k above the
+    context the selection keeps every key and the model follows dense MLA; a small top-k runs and
+    differs."""
+    from vllm_ascend_b200.config import ModelConfig
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+
+    def cfg(topk):
+        return ModelConfig(name="sfa-t", architecture="DeepseekV32ForCausalLM", vocab_size=2048, hidden_size=512,
+                           intermediate_size=1024, num_hidden_layers=2, num_attention_heads=16,
+                           num_key_value_heads=16, head_dim=192, rope_theta=1e4, dtype="bfloat16", init_std=0.05,
+                           use_mla=True, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+                           qk_rope_head_dim=64, v_head_dim=128, index_topk=topk, index_n_heads=8, index_head_dim=128)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 260)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    kw = dict(device="cuda", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=256,
+              num_gpu_blocks_override=40, enforce_eager=True)
+    outs = {}
+    for topk in (0, 512, 32):
+        llm = LLM(cfg(topk), **kw)
+        c0 = llm.engine.runner.total_launches()
+        outs[topk] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        assert llm.engine.runner.total_launches() > c0
+        if topk:
+            assert len(llm.engine.runner.kv_caches[0]) == 3          # latent, rope key, index key
+    assert all(len(t) == 8 for t in outs[32])
+    assert sum(x[0] == y[0] for x, y in zip(outs[512], outs[0])) >= 2, outs
+    assert outs[32] != outs[0]
+    _native.check_status(torch.device("cuda"))

@@ -55,6 +55,10 @@ class ModelConfig:
     linear_key_head_dim: int = 0
     linear_value_head_dim: int = 0
     linear_conv_kernel_dim: int = 4
+    # sparse attention (DeepSeek-V3.2 style lightning indexer over MLA): keys kept per query, indexer heads
+    index_topk: int = 0
+    index_n_heads: int = 0
+    index_head_dim: int = 128
     # multimodal (Qwen2-VL family): rotary sections over (temporal, height, width) positions,
     # vision-tower config (HF ``vision_config`` dict) and the placeholder token ids
     mrope_section: Optional[list] = None
@@ -87,6 +91,10 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def use_sparse(self) -> bool:
+        return self.use_mla and self.index_topk > 0
 
     @property
     def is_multimodal(self) -> bool:
@@ -162,6 +170,9 @@ class ModelConfig:
                 first_k_dense_replace=d.get("first_k_dense_replace", 0),
                 e_score_correction_bias=d.get("topk_method", "") == "noaux_tc",
             )
+        if d.get("index_topk"):
+            kw.update(index_topk=int(d["index_topk"]), index_n_heads=int(d.get("index_n_heads", 64)),
+                      index_head_dim=int(d.get("index_head_dim", 128)))
         if "kv_lora_rank" in d:
             kw.update(use_mla=True, q_lora_rank=d.get("q_lora_rank"),
                       kv_lora_rank=d["kv_lora_rank"],
@@ -256,6 +267,15 @@ PRESETS: dict[str, Any] = {
         intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
         num_key_value_heads=2, head_dim=32, rope_theta=1e6, qk_norm=True, num_experts=8,
         num_experts_per_tok=2, moe_intermediate_size=64, dtype="float32"),
+    "tiny-deepseek-sparse": lambda: _preset(
+        name="tiny-deepseek-sparse", architecture="DeepseekV32ForCausalLM", vocab_size=512,
+        hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+        num_key_value_heads=4, head_dim=48, rope_theta=1e4, num_experts=8,
+        num_experts_per_tok=2, moe_intermediate_size=64, n_shared_experts=1,
+        scoring_func="sigmoid", n_group=4, topk_group=2, routed_scaling_factor=2.5,
+        first_k_dense_replace=1, e_score_correction_bias=True, use_mla=True, q_lora_rank=64,
+        kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, dtype="float32",
+        index_topk=16, index_n_heads=4, index_head_dim=32),
     "tiny-vl": lambda: _preset(
         name="tiny-vl", architecture="Qwen2_5_VLForConditionalGeneration", vocab_size=512, hidden_size=128,
         intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,

@@ -37,9 +37,9 @@ def wake_up(engine, tags: Optional[list[str]] = None) -> int:
     restored = alloc.wake_up(tags)
     if tags is None or "kv_cache" in tags:
         # KV contents were discarded: caches must start from zeros and no prefix survives
-        for kc, vc in engine.runner.kv_caches:
-            kc.zero_()
-            vc.zero_()
+        for caches in engine.runner.kv_caches:
+            for t in caches:
+                t.zero_()
         engine.scheduler.pool.reset_prefix_cache()
     if getattr(engine, "_recapture_on_wake", False) and not alloc.sleeping_tags:
         engine.runner.capture_graphs()

@@ -193,7 +193,7 @@ class ModelRunner:
     def _cache_widths(self) -> tuple[int, int]:
         c = self.mcfg
         if c.use_mla:
-            return (c.kv_lora_rank, c.qk_rope_head_dim)
+            return (c.kv_lora_rank, c.qk_rope_head_dim) + ((c.index_head_dim,) if c.use_sparse else ())
         a = self._attn_layer()
         return (a.Hkv * a.D, a.Hkv * a.D)
 
@@ -237,6 +237,8 @@ class ModelRunner:
             if c.use_mla:
                 shapes = [(num_blocks, self.block_size, 1, c.kv_lora_rank),
                           (num_blocks, self.block_size, 1, c.qk_rope_head_dim)]
+                if c.use_sparse:          # index keys of the lightning indexer
+                    shapes.append((num_blocks, self.block_size, 1, c.index_head_dim))
             else:
                 a = layer.self_attn
                 shapes = [(num_blocks, self.block_size, a.Hkv, a.D)] * 2

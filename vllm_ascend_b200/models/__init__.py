@@ -20,7 +20,7 @@ def _causal_lm(cfg, device, **kw):
 
 for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwen3ForCausalLM",
               "Qwen2MoeForCausalLM", "Qwen3MoeForCausalLM", "DeepseekV2ForCausalLM",
-              "DeepseekV3ForCausalLM", "InternLM2ForCausalLM", "Phi3ForCausalLM",
+              "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM", "InternLM2ForCausalLM", "Phi3ForCausalLM",
               "GemmaForCausalLM", "MiniCPMForCausalLM", "Qwen3NextForCausalLM"):
     register_model(_arch, _causal_lm)
 

@@ -189,6 +189,21 @@ class MLAAttention:
         self.cos_sin = get_cos_sin_cache(self.dr, max_pos, cfg.rope_theta,
                                          dict(sc, rope_type="deepseek_yarn") if sc else None,
                                          pf.device)
+        # lightning indexer (sparse attention): a few small heads score every cached key per query and
+        # attention runs over the index_topk best; weights are replicated over TP (every rank needs
+        # the full selection).  Names follow the published checkpoints (self_attn.indexer.*).
+        self.index_topk = cfg.index_topk if cfg.use_sparse else 0
+        if self.index_topk:
+            if not cfg.q_lora_rank:
+                raise ValueError("the indexer reads the compressed query (q_lora_rank must be set)")
+            Hn, Dh = cfg.index_n_heads, cfg.index_head_dim
+            self.idx_heads, self.idx_dim = Hn, Dh
+            self.idx_wq_b = ColumnParallelLinear(pf, f"{p}.indexer.wq_b", cfg.q_lora_rank, [Hn * Dh], rep)
+            self.idx_wk = ColumnParallelLinear(pf, f"{p}.indexer.wk", hid, [Dh], rep)
+            self.idx_k_norm_w = pf.ones((Dh,))
+            self.idx_k_norm_b = pf.zeros((Dh,))
+            self.idx_weights_proj = ColumnParallelLinear(pf, f"{p}.indexer.weights_proj", hid, [Hn], rep)
+            self.idx_scale = Hn ** -0.5 * Dh ** -0.5
         self.process_weights_after_loading()
 
     def process_weights_after_loading(self) -> None:
@@ -199,23 +214,27 @@ class MLAAttention:
     def __call__(self, x: torch.Tensor, meta, kv_cache) -> torch.Tensor:
         T = x.shape[0]
         if self.q_proj is None:
-            q = self.q_b_proj(self.q_a_norm(self.q_a_proj(x))[0])
+            qr = self.q_a_norm(self.q_a_proj(x))[0]
+            q = self.q_b_proj(qr)
         else:
             q = self.q_proj(x)
+            qr = None
         q = q.view(T, self.H, self.dn + self.dr)
         kv = self.kv_a_proj(x)
         latent = self.kv_a_norm(kv[:, :self.dc].contiguous())[0]
         k_pe = kv[:, self.dc:].reshape(T, 1, self.dr)
         q_pe = ref.apply_rope_interleaved(q[..., self.dn:], meta.positions, self.cos_sin, self.dr)
         k_pe = ref.apply_rope_interleaved(k_pe, meta.positions, self.cos_sin, self.dr)
-        lat_cache, pe_cache = kv_cache
+        lat_cache, pe_cache = kv_cache[0], kv_cache[1]
         from ..attention import mla as mla_ops
         mla_ops.write_latent_cache(latent, k_pe.view(T, self.dr), lat_cache, pe_cache,
                                    meta.slot_mapping)
         # absorb W_UK into q: [T,H,dn] x [H,dn,dc] -> [T,H,dc]
         q_lat = torch.einsum("thd,hdc->thc", q[..., :self.dn], self.W_UK.to(q.dtype))
         dcp = pstate.get_dcp_group()
-        if dcp.world_size > 1:
+        if self.index_topk:
+            o_lat = self._sparse_attention(x, qr, q_lat, q_pe, lat_cache, pe_cache, kv_cache[2], meta)
+        elif dcp.world_size > 1:
             from ..attention.dcp import mla_attention_dcp
             o_lat = mla_attention_dcp(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale, dcp,
                                       getattr(meta, "dcp_interleave", 1))
@@ -223,6 +242,28 @@ class MLAAttention:
             o_lat = mla_ops.mla_paged_attention(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale)
         o = torch.einsum("thc,hcv->thv", o_lat, self.W_UV.to(o_lat.dtype))
         return self.o_proj(o.reshape(T, self.H * self.dv))
+
+    def _sparse_attention(self, x, qr, q_lat, q_pe, lat_cache, pe_cache, idx_cache, meta):
+        """Indexer scores -> top-k key positions per query -> MLA attention over those keys.
+        The rotary part of the indexer's q / k is the leading qk_rope_head_dim slice, rotated in the
+        half-split (neox) pairing; the orthogonal Hadamard rotation the published model applies to
+        both q and k before low-precision scoring leaves the dot products unchanged and is omitted."""
+        from ..attention import sfa
+        T = x.shape[0]
+        Hn, Dh, dr = self.idx_heads, self.idx_dim, self.dr
+        q_idx = self.idx_wq_b(qr).view(T, Hn, Dh)
+        k_idx = torch.nn.functional.layer_norm(self.idx_wk(x).float(), (Dh,), self.idx_k_norm_w.float(),
+                                               self.idx_k_norm_b.float(), 1e-6).to(x.dtype).view(T, 1, Dh)
+        q_idx = ref.apply_rope_neox(q_idx, meta.positions, self.cos_sin, dr)
+        k_idx = ref.apply_rope_neox(k_idx, meta.positions, self.cos_sin, dr)
+        w = self.idx_weights_proj(x).float() * self.idx_scale                       # [T, Hn]
+        # index keys live in their own paged cache, addressed like the latent cache
+        valid = (meta.slot_mapping >= 0).unsqueeze(-1)
+        slot = meta.slot_mapping.clamp(min=0)
+        flat = idx_cache.view(-1, Dh)
+        flat.index_copy_(0, slot, torch.where(valid, k_idx.view(T, Dh).to(flat.dtype), flat[slot]))
+        indices = sfa.lightning_indexer(q_idx.contiguous(), w, idx_cache, meta, self.index_topk)
+        return sfa.sparse_mla_attention(q_lat, q_pe, lat_cache, pe_cache, meta, indices, self.scale)
 
 
 # ---------------------------------------------------------------- decoder layer / model
@@ -388,6 +429,12 @@ class CausalLM:
                 n = getattr(a, attr, None)
                 if n is not None:
                     yield f"{p}.self_attn.{attr}.weight", n.weight
+            if getattr(a, "index_topk", 0):
+                yield f"{p}.self_attn.indexer.wq_b.weight", a.idx_wq_b.weight
+                yield f"{p}.self_attn.indexer.wk.weight", a.idx_wk.weight
+                yield f"{p}.self_attn.indexer.k_norm.weight", a.idx_k_norm_w
+                yield f"{p}.self_attn.indexer.k_norm.bias", a.idx_k_norm_b
+                yield f"{p}.self_attn.indexer.weights_proj.weight", a.idx_weights_proj.weight
             m = L.mlp
             if isinstance(m, SparseMoeBlock):
                 yield f"{p}.mlp.gate.weight", m.gate_weight
