@@ -332,3 +332,30 @@ def test_sparse_mla_model_with_lightning_indexer():
     cfg.index_topk = 8
     one = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=128, block_size=16)
     assert [o.outputs[0].token_ids for o in one.generate(prompts, sp)] == small
+
+
+def test_sparse_attention_with_host_resident_kv():
+    """sparse_kv_offload: latent KV on the host, per-sequence device pools refilled from the indexer's
+    selection; same tokens as the engine that keeps the KV in the paged device cache."""
+    from vllm_ascend_b200.config import get_model_config
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(1, 500, size=n).tolist() for n in (40, 13, 57)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    kw = dict(device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
+
+    def cfg():
+        c = get_model_config("tiny-deepseek-sparse")
+        c.index_topk = 8
+        return c
+    want = [o.outputs[0].token_ids for o in LLM(cfg(), **kw).generate(prompts, sp)]
+    llm = LLM(cfg(), additional_config={"sparse_kv_offload_config": {"enabled": True, "device_slots_per_seq": 12}}, **kw)
+    runner = llm.engine.runner
+    assert runner.sparse_offload is not None and runner.kv_caches[0][0].shape[0] == 1      # placeholders on the device
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    st = runner.sparse_offload[0].mgr.stats()
+    assert st["hits"] > 0 and st["misses"] > 0 and st["evictions"] > 0
+    # rows are reused by later requests: a second batch still matches
+    assert [o.outputs[0].token_ids for o in llm.generate(prompts[::-1], sp)] == want[::-1]
+    from vllm_ascend_b200.platform_config import clear_b200_config
+    clear_b200_config()

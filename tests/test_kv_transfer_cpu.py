@@ -330,3 +330,45 @@ def test_hybrid_connector_moves_kv_and_recurrent_state():
     finally:
         pre.engine.kv_connector.close()
         dec.engine.kv_connector.close()
+
+
+def test_sparse_attention_remote_d2h_connector():
+    """Prefill engine with paged sparse-attention caches -> decode engine whose latent KV is
+    host-resident: the prompt's rows land in the host store, index keys in the paged index cache, and
+    decoding continues as on a monolithic engine."""
+    from vllm_ascend_b200.config import get_model_config
+    from vllm_ascend_b200.platform_config import clear_b200_config
+
+    def cfg():
+        c = get_model_config("tiny-deepseek-sparse")
+        c.index_topk = 8
+        return c
+
+    def mk(role, eid, offload):
+        ktc = None if role is None else {"kv_connector": "SfaRemoteD2HConnector", "kv_role": role, "engine_id": eid}
+        add = {"sparse_kv_offload_config": {"enabled": True, "device_slots_per_seq": 16}} if offload else None
+        return LLM(cfg(), device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4,
+                   max_num_batched_tokens=48, kv_transfer_config=ktc, additional_config=add)
+    prompts = _prompts(3, seed=8)
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in mk(None, "M", False).generate(prompts, sp)]
+    pre = mk("kv_producer", "SP", False)
+    try:
+        sp1 = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+        outs = pre.generate([{"prompt_token_ids": p, "kv_transfer_params": {"do_remote_decode": True}}
+                             for p in prompts], sp1)
+        dec = mk("kv_consumer", "SD", True)          # built last: the offload setting is process-wide config
+        try:
+            got = dec.generate([{"prompt_token_ids": p, "kv_transfer_params": o.kv_transfer_params}
+                                for p, o in zip(prompts, outs)], sp)
+            assert [o.outputs[0].token_ids for o in got] == want
+            c = dec.engine.kv_connector
+            assert c.stats["pulled_requests"] == 3 and c.stats["failed"] == 0
+            assert c.stats["host_rows"] == sum(len(p) - 1 for p in prompts) * dec.cfg.model.num_hidden_layers
+            pre.engine.kv_connector.reap(pre.engine.scheduler)
+            assert pre.engine.kv_connector.num_delayed == 0
+        finally:
+            dec.engine.kv_connector.close()
+    finally:
+        pre.engine.kv_connector.close()
+        clear_b200_config()

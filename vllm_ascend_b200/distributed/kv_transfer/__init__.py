@@ -21,6 +21,7 @@ _CONNECTORS = {
     "OffloadingConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
     "MultiConnector": ("multi_connector", "MultiConnector"),
     "HybridConnector": ("hybrid_connector", "HybridConnector"),
+    "SfaRemoteD2HConnector": ("sfa_remote_d2h", "SfaRemoteD2HConnector"),
     "MooncakeHybridConnector": ("hybrid_connector", "HybridConnector"),
 }
 

@@ -104,6 +104,7 @@ class ModelRunner:
         self.graph_wrapper = None
         self.lora_manager = None
         self.mm = None                   # MultimodalState for models with a vision tower
+        self.sparse_offload = None       # per-layer host-resident KV stores (sparse attention offload)
         self.moe_runtime = None
         from ..parallel import state as _ps
         self.pp = _ps.get_pp_group()
@@ -192,6 +193,8 @@ class ModelRunner:
 
     def _cache_widths(self) -> tuple[int, int]:
         c = self.mcfg
+        if c.use_mla and c.use_sparse and self._offload_cfg().enabled:
+            return (c.index_head_dim,)                    # only the index keys are paged on the device
         if c.use_mla:
             return (c.kv_lora_rank, c.qk_rope_head_dim) + ((c.index_head_dim,) if c.use_sparse else ())
         a = self._attn_layer()
@@ -230,13 +233,15 @@ class ModelRunner:
         c = self.mcfg
         self.kv_caches = []
         per_layer = []
+        self._init_sparse_offload()
         for layer in self.model.layers:
             if getattr(layer.self_attn, "is_linear_attention", False):
                 per_layer.append(None)              # recurrent state instead of a paged cache
                 continue
             if c.use_mla:
-                shapes = [(num_blocks, self.block_size, 1, c.kv_lora_rank),
-                          (num_blocks, self.block_size, 1, c.qk_rope_head_dim)]
+                nb_main = 1 if self._offload_cfg().enabled else num_blocks      # host-resident: placeholders
+                shapes = [(nb_main, self.block_size, 1, c.kv_lora_rank),
+                          (nb_main, self.block_size, 1, c.qk_rope_head_dim)]
                 if c.use_sparse:          # index keys of the lightning indexer
                     shapes.append((num_blocks, self.block_size, 1, c.index_head_dim))
             else:
@@ -273,11 +278,32 @@ class ModelRunner:
                 for s in shapes))
 
     # ------------------------------------------------------------------ persistent batch
+    def _offload_cfg(self):
+        from ..platform_config import get_b200_config
+        return get_b200_config().sparse_kv_offload_config
+
+    def _init_sparse_offload(self) -> None:
+        oc, c = self._offload_cfg(), self.mcfg
+        if not (oc.enabled and c.use_sparse):
+            return
+        from ..attention.sparse_offload import SparseOffloadLayer
+        slots = oc.device_slots_per_seq or 4 * c.index_topk
+        slots = max(slots, c.index_topk)
+        self.sparse_offload = []
+        for layer in self.model.layers:
+            so_ = SparseOffloadLayer(self.max_seqs, self.max_model_len, slots, c.kv_lora_rank, c.qk_rope_head_dim,
+                                     self.kv_dtype, self.device, oc.num_threads)
+            layer.self_attn.offload = so_
+            self.sparse_offload.append(so_)
+
     def _sync_rows(self, so: SchedulerOutput) -> None:
         for req in so.new_block_rows:
             row = req.row
             if row < 0:
                 continue
+            if self.row_owner[row] != req.request_id and self.sparse_offload is not None:
+                for so_ in self.sparse_offload:          # a new sequence starts with an empty resident set
+                    so_.release(row)
             if self.row_owner[row] != req.request_id:
                 self.row_owner[row] = req.request_id
                 self.row_num_blocks[row] = 0
@@ -400,6 +426,12 @@ class ModelRunner:
             num_input_tokens=Tp)
         meta.dcp_interleave = self.dcp_interleave
         meta.pcp = pcp_meta
+        if self.sparse_offload is not None:
+            tr = np.full(Tp, -1, dtype=np.int64)
+            tr[:T] = rows[req_idx] if pcp_meta is None else -1
+            pc_ = np.zeros(Tp, dtype=np.int64)
+            pc_[:T] = pos
+            meta.extra = dict(meta.extra or {}, tok_rows=tr, positions_cpu=pc_)
         if self.mm is not None:
             self.mm.prepare(reqs, starts, q_lens, cu, pos, req_idx, T, Tp, meta)
         if self.mcfg.is_hybrid:

@@ -193,6 +193,7 @@ class MLAAttention:
         # attention runs over the index_topk best; weights are replicated over TP (every rank needs
         # the full selection).  Names follow the published checkpoints (self_attn.indexer.*).
         self.index_topk = cfg.index_topk if cfg.use_sparse else 0
+        self.offload = None            # attention.sparse_offload.SparseOffloadLayer when the KV is host-resident
         if self.index_topk:
             if not cfg.q_lora_rank:
                 raise ValueError("the indexer reads the compressed query (q_lora_rank must be set)")
@@ -227,8 +228,11 @@ class MLAAttention:
         k_pe = ref.apply_rope_interleaved(k_pe, meta.positions, self.cos_sin, self.dr)
         lat_cache, pe_cache = kv_cache[0], kv_cache[1]
         from ..attention import mla as mla_ops
-        mla_ops.write_latent_cache(latent, k_pe.view(T, self.dr), lat_cache, pe_cache,
-                                   meta.slot_mapping)
+        if self.offload is None:
+            mla_ops.write_latent_cache(latent, k_pe.view(T, self.dr), lat_cache, pe_cache,
+                                       meta.slot_mapping)
+        else:       # host-resident KV: the rows of this step's tokens go to the sequence's host store
+            self.offload.append(meta.extra["tok_rows"], meta.extra["positions_cpu"], latent, k_pe.view(T, self.dr))
         # absorb W_UK into q: [T,H,dn] x [H,dn,dc] -> [T,H,dc]
         q_lat = torch.einsum("thd,hdc->thc", q[..., :self.dn], self.W_UK.to(q.dtype))
         dcp = pstate.get_dcp_group()
@@ -263,6 +267,8 @@ class MLAAttention:
         flat = idx_cache.view(-1, Dh)
         flat.index_copy_(0, slot, torch.where(valid, k_idx.view(T, Dh).to(flat.dtype), flat[slot]))
         indices = sfa.lightning_indexer(q_idx.contiguous(), w, idx_cache, meta, self.index_topk)
+        if self.offload is not None:
+            return self.offload.attend(q_lat, q_pe, meta.extra["tok_rows"], indices, self.scale)
         return sfa.sparse_mla_attention(q_lat, q_pe, lat_cache, pe_cache, meta, indices, self.scale)
 
 

@@ -147,6 +147,16 @@ class WeightOffloadConfig:
 
 
 @dataclass
+class SparseKVOffloadConfig:
+    """Sparse-attention models: the latent KV of every sequence lives in pinned host memory, the GPU
+    keeps ``device_slots_per_seq`` recently selected tokens per sequence (0: 4 x index_topk).  Index
+    keys stay on the device (the indexer scores every key each step)."""
+    enabled: bool = False
+    device_slots_per_seq: int = 0
+    num_threads: int = 4
+
+
+@dataclass
 class B200Config:
     finegrained_tp_config: FinegrainedTPConfig = field(default_factory=FinegrainedTPConfig)
     fusion_config: FusionConfig = field(default_factory=FusionConfig)
@@ -156,6 +166,7 @@ class B200Config:
     dynamic_spec_config: DynamicSpecConfig = field(default_factory=DynamicSpecConfig)
     rl_config: RlConfig = field(default_factory=RlConfig)
     weight_offload_config: WeightOffloadConfig = field(default_factory=WeightOffloadConfig)
+    sparse_kv_offload_config: SparseKVOffloadConfig = field(default_factory=SparseKVOffloadConfig)
     enable_shared_expert_dp: bool = False
     multistream_overlap_shared_expert: bool = False
     enable_prefill_fused_moe: bool = True        # reference: enable_prefill_mc2
@@ -340,6 +351,14 @@ def check_and_update_config(engine_cfg) -> B200Config:
         engine_cfg.cache.enable_prefix_caching = False
     if cfg.weight_offload_config.enabled:
         cc.cudagraph_mode = "NONE"        # offloaded weights rotate through device buffers
+    if cfg.sparse_kv_offload_config.enabled:
+        if not mc.use_sparse:
+            raise ValueError("sparse_kv_offload_config needs a sparse-attention (index_topk) model")
+        if pc.tensor_parallel_size > 1 and pc.decode_context_parallel_size > 1:
+            raise ValueError("sparse KV offload cannot be combined with decode context parallelism")
+        cc.cudagraph_mode = "NONE"        # every layer reads the selection back to maintain the host-side LRU
+        engine_cfg.cache.enable_prefix_caching = False
+        engine_cfg.async_scheduling = False
     if (engine_cfg.speculative_config or {}).get("method") == "eagle3":
         cc.cudagraph_mode = "NONE"        # the head reads intermediate residual streams of eager forwards
     # 4 graph mode normalisation + capture sizes (platform.py:937-1117, 1275-1309)
