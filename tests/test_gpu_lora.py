@@ -89,3 +89,42 @@ def test_engine_lora_graph_equals_eager():
         assert base[1] == outs[eager][1]            # the request without adapter is unaffected
         assert base[0] != outs[eager][0]            # the adapter changes the output
     assert outs[True] == outs[False]
+
+
+def test_expert_lora_on_gpu():
+    """Adapters on routed experts through the batched LoRA kernels with (slot, expert) indices; plain
+    requests of the same batch are untouched, graph decode still serves steps without adapters."""
+    from vllm_ascend_b200.config import ModelConfig
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    from vllm_ascend_b200.lora.manager import LoRARequest
+
+    def cfg():
+        return ModelConfig(name="moe-t", architecture="Qwen3MoeForCausalLM", vocab_size=2048, hidden_size=512,
+                           intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+                           head_dim=128, qk_norm=True, rope_theta=1e6, dtype="bfloat16", init_std=0.05,
+                           num_experts=8, num_experts_per_tok=2, moe_intermediate_size=256)
+    c = cfg()
+    g = torch.Generator().manual_seed(0)
+    rank, H, I = 8, c.hidden_size, c.moe_intermediate_size
+    ad = {}
+    for li in range(c.num_hidden_layers):
+        for e in range(c.num_experts):
+            base = f"base_model.model.model.layers.{li}.mlp.experts.{e}"
+            for name, (k, n) in (("gate_proj", (H, I)), ("up_proj", (H, I)), ("down_proj", (I, H))):
+                ad[f"{base}.{name}.lora_A.weight"] = torch.randn(rank, k, generator=g) * 0.1
+                ad[f"{base}.{name}.lora_B.weight"] = torch.randn(n, rank, generator=g) * 0.1
+    req = LoRARequest("moe", 1, tensors=ad, rank=rank, alpha=16.0)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 200)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    llm = LLM(cfg(), device="cuda", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=256,
+              num_gpu_blocks_override=40, cudagraph_capture_sizes=[2, 4], enable_lora=True, max_loras=2, max_lora_rank=8)
+    mixed = [o.outputs[0].token_ids for o in llm.generate(prompts, sp, lora_request=[req, None, req])]
+    replays = llm.engine.runner.stats["graph_replays"]
+    base = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert llm.engine.runner.stats["graph_replays"] > replays       # adapter-free decode steps replay graphs
+    assert base[1][0] == mixed[1][0]
+    assert base[0] != mixed[0] and base[2] != mixed[2]
+    from vllm_ascend_b200 import _native
+    _native.check_status(torch.device("cuda"))
