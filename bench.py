@@ -179,6 +179,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # tensor-parallel runs time the fused peer-memory dataflow against NCCL per step class at start-up
+    # and serve each class with the faster one; the choice is reported under config.tp_comm_calibration
+    os.environ.setdefault("VLLM_B200_TP_COMM", "auto")
     if args.impl == "reference":
         if rank == 0:
             run_reference(args)
