@@ -359,3 +359,18 @@ def test_sparse_attention_with_host_resident_kv():
     assert [o.outputs[0].token_ids for o in llm.generate(prompts[::-1], sp)] == want[::-1]
     from vllm_ascend_b200.platform_config import clear_b200_config
     clear_b200_config()
+
+
+def test_async_engine_steps_synchronously_for_token_dependent_sampling():
+    """Penalties and multi-token bad words read the newest token: an asynchronous engine falls back
+    to synchronous steps while such a request is alive and returns to lookahead afterwards."""
+    kw = dict(device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=64, block_size=16)
+    prompts = [[5, 6, 7, 8, 9], [20, 21, 22]]
+    sps = [SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True, repetition_penalty=1.3, presence_penalty=0.5),
+           SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)]
+    want = [o.outputs[0].token_ids for o in LLM("tiny-qwen", async_scheduling=False, **kw).generate(prompts, sps)]
+    llm = LLM("tiny-qwen", async_scheduling=True, **kw)
+    assert llm.engine.async_scheduling
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sps)]
+    assert got == want
+    assert not llm.engine._needs_sync()

@@ -71,6 +71,7 @@ class LLMEngine:
         # asynchronous scheduling needs nothing between two steps that depends on the sampled
         # token values: no proposer, no connector bookkeeping, no lock-step groups
         self._inflight = None
+        self._sync_reqs: set = set()
         want_async = cfg.async_scheduling if cfg.async_scheduling is not None else (cfg.device == "cuda")
         # (TP ranks take identical decisions from identical tokens, so they stay in lock-step;
         # DP / PP engines exchange host-side state every step and run synchronously)
@@ -123,6 +124,9 @@ class LLMEngine:
                       eos_token_id=self.eos_token_id, kv_transfer_params=kv_transfer_params,
                       job_id=job_id, lora_request=lora_request, mm_inputs=mm_items,
                       mrope_positions=mrope, mrope_delta=delta)
+        sp_ = sampling_params
+        if sp_.has_penalties or any(len(w) > 1 for w in (sp_.bad_words_token_ids or ())):
+            self._sync_reqs.add(rid)
         self.scheduler.add_request(req)
         return rid
 
@@ -186,9 +190,34 @@ class LLMEngine:
         self.host_times["update"] += t3 - t2
         return finished
 
+    def _needs_sync(self) -> bool:
+        """Requests whose next-token distribution depends on the token sampled one step earlier
+        (penalties, multi-token bad words) need that token on the host before the next step is built:
+        while one is alive the engine steps synchronously."""
+        if not self._sync_reqs:
+            return False
+        reqs = self.scheduler.requests
+        self._sync_reqs = {r for r in self._sync_reqs if r in reqs and not reqs[r].is_finished}
+        return bool(self._sync_reqs)
+
+    def _drain_async(self) -> list[Request]:
+        so_prev, h_prev = self._inflight
+        self._inflight = None
+        sampled = self.runner.collect(h_prev)
+        now = time.monotonic()
+        for req, _ in so_prev.scheduled:
+            if req.first_token_time is None and req.request_id in sampled:
+                req.first_token_time = now
+        finished = self.scheduler.update_from_output(so_prev, sampled)
+        self._attach_logprobs()
+        self._release_mm(finished)
+        return finished
+
     def step(self) -> list[Request]:
-        if self.async_scheduling:
+        if self.async_scheduling and not self._needs_sync():
             return self._step_async()
+        if self._inflight is not None:          # switch to synchronous stepping: finish the step in flight
+            return self._drain_async()
         t0 = time.perf_counter()
         so = self.scheduler.schedule()
         t1 = time.perf_counter()
