@@ -174,3 +174,37 @@ def test_eagle3_head_reads_three_residual_streams_and_loads_hf_names(tmp_path):
     assert torch.equal(head.layers[0].mlp.gate_up_proj.weight[I:], ck["midlayer.mlp.up_proj.weight"])
     toks = head.draft_tokens(torch.randn(5, H, generator=g))
     assert ((toks % 4) == 0).all() and toks.max() < 128 * 4             # index + d2t[index] = 4 * index
+
+
+def test_mtp_head_on_mla_moe_target_keeps_greedy_output_and_loads_layer_n(tmp_path):
+    """DeepSeek-style target (MLA + MoE): the MTP module is a full decoder layer of the target's kind
+    with its own latent cache; speculative decoding leaves greedy output unchanged; tensors of layer
+    N in a checkpoint stream go to the module."""
+    from vllm_ascend_b200.spec_decode.draft_model import MTPHead
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=40)
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(1, 400, size=n).tolist() for n in (45, 9, 70)]
+    sp = SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM("tiny-deepseek", **kw).generate(prompts, sp)]
+    llm = LLM("tiny-deepseek", speculative_config={"method": "mtp", "num_speculative_tokens": 2}, **kw)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    head = llm.engine.runner.proposer.model
+    assert isinstance(head, MTPHead) and hasattr(head.layers[0].self_attn, "dc") and hasattr(head.layers[0].mlp, "w13")
+    assert llm.engine.runner.spec_stats["draft_tokens"] > 0
+    N, H = head.idx, llm.cfg.model.hidden_size
+    g = torch.Generator().manual_seed(0)
+    E, I = llm.cfg.model.num_experts, llm.cfg.model.moe_intermediate_size
+    ck = {f"model.layers.{N}.enorm.weight": torch.rand(H, generator=g), f"model.layers.{N}.hnorm.weight": torch.rand(H, generator=g),
+          f"model.layers.{N}.eh_proj.weight": torch.randn(H, 2 * H, generator=g),
+          f"model.layers.{N}.shared_head.norm.weight": torch.rand(H, generator=g),
+          f"model.layers.{N}.shared_head.head.weight": torch.randn(llm.cfg.model.vocab_size, H, generator=g),
+          f"model.layers.{N}.input_layernorm.weight": torch.rand(H, generator=g),
+          f"model.layers.{N}.mlp.experts.3.down_proj.weight": torch.randn(H, I, generator=g),
+          f"model.layers.{N}.self_attn.o_proj.weight": torch.randn(H, head.layers[0].self_attn.o_proj.weight.shape[1], generator=g),
+          "model.layers.0.input_layernorm.weight": torch.rand(H, generator=g)}
+    loaded = head.load_weights(ck.items())
+    assert loaded == {k for k in ck if k.startswith(f"model.layers.{N}.")}
+    assert torch.equal(head.eh_proj_weight, ck[f"model.layers.{N}.eh_proj.weight"])
+    assert torch.equal(head.layers[0].mlp.w2[3], ck[f"model.layers.{N}.mlp.experts.3.down_proj.weight"])
+    assert torch.equal(head.layers[0].input_layernorm.weight, ck[f"model.layers.{N}.input_layernorm.weight"])

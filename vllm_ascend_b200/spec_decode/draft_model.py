@@ -63,6 +63,70 @@ class EagleHead:
         return self.lm_head(hidden)
 
 
+class MTPHead:
+    """Multi-token-prediction module of DeepSeek-V3 style checkpoints: layer N = num_hidden_layers.
+    h_0 = eh_proj([enorm(embed(token_{i+1})); hnorm(hidden_i)]) -> one full decoder layer of the
+    target's own kind (MLA / MoE included) -> shared_head.norm -> LM head shared with the target.
+    Weight names: ``model.layers.N.{enorm,hnorm,eh_proj,shared_head.norm,shared_head.head}`` next to
+    the layer's ordinary ``self_attn`` / ``mlp`` tensors.  Role of the MTP proposer the reference
+    runs through its base proposer (vllm_ascend/spec_decode/llm_base_proposer.py, models/deepseek_mtp)."""
+
+    def __init__(self, target, cfg, device, max_model_len: int, ep_group=None, moe_runtime=None):
+        from ..models.transformer import DecoderLayer
+        dtype = target.embed_tokens.weight.dtype
+        pf = ParamFactory(cfg, device, dtype)
+        comm = TPComm(pstate.get_tp_group())
+        self.cfg = cfg
+        self.comm = comm
+        H, N = cfg.hidden_size, cfg.num_hidden_layers
+        self.idx = N
+        self.embed_tokens = target.embed_tokens
+        self.lm_head = target.lm_head
+        self.enorm = RMSNorm(pf, H, cfg.rms_norm_eps)
+        self.hnorm = RMSNorm(pf, H, cfg.rms_norm_eps)
+        self.eh_proj_weight = pf.normal(f"model.layers.{N}.eh_proj", (H, 2 * H))
+        self.layers = [DecoderLayer(pf, cfg, N, comm, max_model_len, ep_group, moe_runtime)]
+        self.norm = RMSNorm(pf, H, cfg.rms_norm_eps)
+
+    def forward(self, input_ids, prev_hidden, meta, kv_caches):
+        e, _ = self.enorm(self.embed_tokens(input_ids))
+        h, _ = self.hnorm(prev_hidden.to(e.dtype).contiguous())
+        x = ops.linear(torch.cat([e, h], dim=-1), self.eh_proj_weight, None, None)
+        h, residual = self.layers[0](x, None, meta, kv_caches[0])
+        out, _ = self.norm(h, residual)
+        return out
+
+    def compute_logits(self, hidden):
+        return self.lm_head(hidden)
+
+    def load_weights(self, weights) -> set:
+        """Picks the tensors of layer N out of a full checkpoint stream (the target skips them)."""
+        from ..models.transformer import CausalLM
+        N = self.idx
+        pre = f"model.layers.{N}."
+        own = {f"{pre}enorm.weight": self.enorm.weight, f"{pre}hnorm.weight": self.hnorm.weight,
+               f"{pre}eh_proj.weight": self.eh_proj_weight, f"{pre}shared_head.norm.weight": self.norm.weight}
+        loaded, rest = set(), []
+        for name, w in weights:
+            if not name.startswith(pre):
+                continue
+            if name in own:
+                own[name].copy_(w.to(own[name].dtype))
+                loaded.add(name)
+            elif "shared_head.head" in name or "embed_tokens" in name:
+                loaded.add(name)                       # tied to the target's embedding / LM head
+            else:
+                rest.append((name, w))
+        # the decoder layer itself loads through the target's loader (same sharding rules)
+        shell = CausalLM.__new__(CausalLM)
+        shell.cfg, shell.comm, shell.layers = self.cfg, self.comm, self.layers
+        shell.named_parameters = lambda: ((n, t) for n, t in CausalLM.named_parameters(shell)
+                                          if n.startswith(pre))
+        shell.embed_tokens, shell.norm, shell.lm_head = self.embed_tokens, self.norm, self.lm_head
+        loaded |= CausalLM.load_weights(shell, rest)
+        return loaded
+
+
 class Eagle3Head:
     """EAGLE-3 draft head.  Conditioning is the target's residual stream at three depths (low, middle,
     high), concatenated and projected by ``fc``; the single decoder layer attends over
@@ -184,6 +248,15 @@ class DraftModelProposer:
             if isinstance(path, str) and os.path.isdir(path):
                 from ..models.transformer import iterate_safetensors
                 self.model.load_weights(iterate_safetensors(path))
+        elif method == "mtp":
+            from ..parallel import state as _ps
+            st = _ps.get_state()
+            ep = st.ep if (runner.cfg.parallel.enable_expert_parallel and st.ep is not None
+                           and st.ep.world_size > 1) else None
+            self.model = MTPHead(runner.model, runner.mcfg, dev, runner.max_model_len, ep, runner.moe_runtime)
+            if runner.mcfg.model_path:
+                from ..models.transformer import iterate_safetensors
+                self.model.load_weights(iterate_safetensors(runner.mcfg.model_path))
         elif self.needs_hidden_states:
             self.model = EagleHead(runner.model, runner.mcfg, dev, runner.max_model_len, seed_name=method)
         else:
@@ -210,6 +283,11 @@ class DraftModelProposer:
         self.kv_caches = []
         for layer in self.model.layers:
             a = layer.self_attn
+            if hasattr(a, "dc"):                  # MLA draft layer: latent, rope key (and index keys)
+                widths = [a.dc, a.dr] + ([a.idx_dim] if getattr(a, "index_topk", 0) else [])
+                self.kv_caches.append(tuple(ops.alloc_kv_cache(r.num_blocks, r.block_size, 1, w, r.kv_dtype,
+                                                               r.device, "NHD") for w in widths))
+                continue
             self.kv_caches.append(tuple(ops.alloc_kv_cache(r.num_blocks, r.block_size, a.Hkv, a.D, r.kv_dtype,
                                                            r.device, layout) for _ in range(2)))
 
