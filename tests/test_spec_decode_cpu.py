@@ -208,3 +208,32 @@ def test_mtp_head_on_mla_moe_target_keeps_greedy_output_and_loads_layer_n(tmp_pa
     assert torch.equal(head.eh_proj_weight, ck[f"model.layers.{N}.eh_proj.weight"])
     assert torch.equal(head.layers[0].mlp.w2[3], ck[f"model.layers.{N}.mlp.experts.3.down_proj.weight"])
     assert torch.equal(head.layers[0].input_layernorm.weight, ck[f"model.layers.{N}.input_layernorm.weight"])
+
+
+def test_dynamic_speculation_length_follows_acceptance():
+    from vllm_ascend_b200.platform_config import clear_b200_config
+    from vllm_ascend_b200.spec_decode.dynamic import DynamicSpecController
+    c = DynamicSpecController(6, {"budget_threshold": 0.3, "ema_alpha": 0.5, "initial_acceptance": 0.7})
+    assert c.budget("a") == 3                              # 0.7^3 = 0.34 >= 0.3 > 0.7^4
+    for _ in range(6):
+        c.update("a", 4, 4)
+    assert c.budget("a") == 6
+    for _ in range(8):
+        c.update("a", 4, 0)
+    assert c.budget("a") == 1
+    c.forget("a")
+    assert c.budget("a") == 3
+    # engine: a random EAGLE head is almost never right, so its budget collapses to the minimum while
+    # greedy output stays exact
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=40)
+    prompts = [[7, 8, 9, 10, 11, 12] * 3, [3, 4, 5] * 4]
+    sp = SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM("tiny-qwen", **kw).generate(prompts, sp)]
+    spec = {"method": "eagle", "num_speculative_tokens": 4}
+    fixed = LLM("tiny-qwen", speculative_config=spec, **kw)
+    assert [o.outputs[0].token_ids for o in fixed.generate(prompts, sp)] == want
+    dyn = LLM("tiny-qwen", speculative_config=spec, additional_config={
+        "dynamic_spec_config": {"method": "acceptance", "method_params": {"ema_alpha": 0.6}}}, **kw)
+    assert [o.outputs[0].token_ids for o in dyn.generate(prompts, sp)] == want
+    assert dyn.engine.runner.spec_stats["draft_tokens"] < fixed.engine.runner.spec_stats["draft_tokens"]
+    clear_b200_config()

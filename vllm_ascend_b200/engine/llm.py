@@ -67,6 +67,10 @@ class LLMEngine:
             from ..spec_decode import get_spec_decode_method
             self.runner.proposer = get_spec_decode_method(cfg.speculative_config, self.runner)
             self.scheduler.spec_slack = int(cfg.speculative_config.get("num_speculative_tokens", 3))
+            dsc = get_b200_config().dynamic_spec_config
+            if dsc.method:
+                from ..spec_decode.dynamic import DynamicSpecController
+                self.runner.dynamic_spec = DynamicSpecController(self.scheduler.spec_slack, dsc.method_params)
         self._model_proposer = hasattr(self.runner.proposer, "propose_step")
         # asynchronous scheduling needs nothing between two steps that depends on the sampled
         # token values: no proposer, no connector bookkeeping, no lock-step groups
@@ -151,6 +155,9 @@ class LLMEngine:
                 req.logprobs.extend(entries[:max(room, 0)])
 
     def _release_mm(self, finished) -> None:
+        if self.runner.dynamic_spec is not None:
+            for r in finished:
+                self.runner.dynamic_spec.forget(r.request_id)
         mm = self.runner.mm
         if mm is not None:
             for r in finished:

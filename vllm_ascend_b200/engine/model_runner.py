@@ -121,6 +121,7 @@ class ModelRunner:
         self.proposer = None
         self.last_hidden = None      # final hidden states of the latest step, scheduling order
         self.rejection_sampler = None
+        self.dynamic_spec = None         # spec_decode.dynamic.DynamicSpecController when configured
         self.spec_stats = {"draft_tokens": 0, "accepted_tokens": 0, "verify_steps": 0}
         self._sample_rows: list = []
         self.graph_pool = None
@@ -861,6 +862,8 @@ class ModelRunner:
             toks = [int(t) for t in out_h[i, :num_h[i]]]
             self.token_ids_cpu[r.row, r.num_tokens:r.num_tokens + len(toks)] = toks
             res[r.request_id] = toks
+            if self.dynamic_spec is not None:
+                self.dynamic_spec.update(r.request_id, rows[i] - 1, max(int(num_h[i]) - 1, 0))
         self.spec_stats["draft_tokens"] += int(draft.size)
         self.spec_stats["accepted_tokens"] += int(np.maximum(num_h - 1, 0).sum())
         self.spec_stats["verify_steps"] += 1
@@ -876,6 +879,8 @@ class ModelRunner:
         props = self.proposer.propose(self.token_ids_cpu, lens, rows)
         for r, p in zip(reqs, props):
             left = r.sampling_params.max_tokens - r.num_output_tokens - 1
+            if self.dynamic_spec is not None:
+                left = min(left, self.dynamic_spec.budget(r.request_id))
             r.spec_token_ids = [int(t) for t in p[:max(left, 0)]]
 
     @torch.inference_mode()

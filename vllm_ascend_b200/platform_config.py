@@ -124,8 +124,16 @@ class RejectionSamplerConfig:
 
 @dataclass
 class DynamicSpecConfig:
+    """``method``: None (fixed speculation length) or "acceptance" (per-request length from the measured
+    acceptance rate; the reference's "dspark" / "dflash" names select the same controller here, their
+    confidence heads are not part of this build).  ``method_params``: min_tokens, budget_threshold,
+    ema_alpha, initial_acceptance."""
     method: Optional[str] = None
     method_params: dict = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.method is not None and self.method not in ("acceptance", "dspark", "dflash"):
+            raise ValueError("dynamic_spec_config.method must be one of acceptance, dspark, dflash or None")
 
 
 @dataclass

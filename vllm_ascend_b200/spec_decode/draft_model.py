@@ -363,6 +363,8 @@ class DraftModelProposer:
         for q in live:
             room = min(self.k, r.max_model_len - q.num_tokens - 1,
                        q.sampling_params.max_tokens - q.num_output_tokens - 1)
+            if r.dynamic_spec is not None:
+                room = min(room, r.dynamic_spec.budget(q.request_id))
             if room > 0 and not scheduler.try_extend(q, q.num_tokens + room):
                 room = 0
             budget.append(max(room, 0))
