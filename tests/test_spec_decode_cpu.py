@@ -237,3 +237,23 @@ def test_dynamic_speculation_length_follows_acceptance():
     assert [o.outputs[0].token_ids for o in dyn.generate(prompts, sp)] == want
     assert dyn.engine.runner.spec_stats["draft_tokens"] < fixed.engine.runner.spec_stats["draft_tokens"]
     clear_b200_config()
+
+
+def test_extract_hidden_states_records_every_position(tmp_path):
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=24)
+    prompts = [[7, 8, 9, 10, 11, 12] * 6, [3, 4, 5] * 4]
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM("tiny-qwen", **kw).generate(prompts, sp)]
+    llm = LLM("tiny-qwen", speculative_config={"method": "extract_hidden_states", "layers": [0, 1],
+                                               "output_dir": str(tmp_path)}, **kw)
+    outs = llm.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want                  # nothing is drafted
+    H = llm.cfg.model.hidden_size
+    for o, p in zip(outs, prompts):
+        rec = torch.load(tmp_path / f"{o.request_id}.pt")
+        # every computed position: the prompt and all generated tokens but the last one
+        assert rec["hidden_states"].shape == (len(p) + 5 - 1, 2 * H)
+        assert rec["token_ids"] == p + o.outputs[0].token_ids
+    mem = LLM("tiny-qwen", speculative_config={"method": "extract_hidden_states"}, **kw)
+    o = mem.generate(prompts[:1], sp)[0]
+    assert mem.engine.runner.proposer.results[o.request_id].shape == (len(prompts[0]) + 4, H)

@@ -367,7 +367,7 @@ def check_and_update_config(engine_cfg) -> B200Config:
         cc.cudagraph_mode = "NONE"        # every layer reads the selection back to maintain the host-side LRU
         engine_cfg.cache.enable_prefix_caching = False
         engine_cfg.async_scheduling = False
-    if (engine_cfg.speculative_config or {}).get("method") == "eagle3":
+    if (engine_cfg.speculative_config or {}).get("method") in ("eagle3", "extract_hidden_states"):
         cc.cudagraph_mode = "NONE"        # the head reads intermediate residual streams of eager forwards
     # 4 graph mode normalisation + capture sizes (platform.py:937-1117, 1275-1309)
     cc.cudagraph_mode = cc.cudagraph_mode.upper()

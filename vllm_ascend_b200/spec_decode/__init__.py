@@ -18,4 +18,7 @@ def get_spec_decode_method(spec_cfg: dict, runner):
     if method == "medusa":
         from .medusa import MedusaProposer
         return MedusaProposer(k, spec_cfg, runner)
+    if method == "extract_hidden_states":
+        from .extract_hidden import ExtractHiddenStatesProposer
+        return ExtractHiddenStatesProposer(spec_cfg, runner)
     raise ValueError(f"unknown speculative method {method!r}")
