@@ -2,6 +2,7 @@
 import threading
 
 import numpy as np
+import pytest
 import torch
 
 from vllm_ascend_b200 import LLM, SamplingParams
@@ -104,3 +105,37 @@ def test_rl_weight_transfer_updates_a_live_engine():
     assert n == len(params) and res["sent"]["buckets"] == eng.stats["buckets"] > 1
     worker.reset_prefix_cache()
     assert _tokens(worker) == _tokens(trainer_model)
+
+
+def test_sharded_state_roundtrip_and_reload_weights(tmp_path):
+    import torch
+    from safetensors.torch import save_file
+    from vllm_ascend_b200 import LLM, SamplingParams
+    from vllm_ascend_b200.models.transformer import export_hf_state_dict
+    kw = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=4)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompt = [[5, 6, 7, 8, 9, 10]]
+    a = LLM("tiny-moe", seed=0, **kw)
+    want = a.generate(prompt, sp)[0].outputs[0].token_ids
+    files = a.save_sharded_state(str(tmp_path / "sharded"), max_bytes=1 << 18)
+    assert len(files) > 1                                         # split into parts
+    from vllm_ascend_b200.config import get_model_config
+    cfg = get_model_config("tiny-moe")
+    cfg.seed = 123                                                # other random weights, then overwritten
+    b = LLM(cfg, load_format="sharded_state", model_loader_extra_config={"path": str(tmp_path / "sharded")}, **kw)
+    assert b.engine.runner.loaded_from_peer
+    assert b.generate(prompt, sp)[0].outputs[0].token_ids == want
+    # in-place reload from an HF-layout checkpoint directory
+    c = LLM(get_model_config("tiny-moe"), **kw)
+    ck = tmp_path / "hf"
+    ck.mkdir()
+    sd = {k: v.contiguous() for k, v in export_hf_state_dict(a.engine.runner.model).items()}
+    save_file(sd, str(ck / "model.safetensors"))
+    for _, t in c.engine.runner.model.named_parameters():
+        t.zero_()
+    ptrs = [t.data_ptr() for _, t in c.engine.runner.model.named_parameters()]
+    assert c.reload_weights(str(ck)) == len(sd)
+    assert ptrs == [t.data_ptr() for _, t in c.engine.runner.model.named_parameters()]
+    assert c.generate(prompt, sp)[0].outputs[0].token_ids == want
+    with pytest.raises(FileNotFoundError):
+        LLM("tiny-moe", load_format="sharded_state", model_loader_extra_config={"path": str(tmp_path / "none")}, **kw)

@@ -501,6 +501,28 @@ class LLM:
                 torch.cuda.synchronize()
             dist.destroy_process_group()
 
+    def save_sharded_state(self, path: str, max_bytes: int = 5 << 30) -> list:
+        """Every rank writes the tensors it holds; load them back with
+        ``load_format="sharded_state", model_loader_extra_config={"path": path}``."""
+        import os
+        from ..model_loader.sharded_state import save_sharded_state
+        return save_sharded_state(self.engine.runner.model, path, int(os.environ.get("RANK", "0")), max_bytes)
+
+    def reload_weights(self, path: Optional[str] = None) -> int:
+        """Re-read the weights in place (same tensors, same addresses: captured graphs and peer
+        mappings stay valid) from ``path`` or from the directory the model was loaded from; the KV
+        cache of earlier weights is dropped.  Returns the number of tensors loaded."""
+        from ..models.transformer import iterate_safetensors
+        src = path or self.cfg.model.model_path
+        if not src:
+            raise ValueError("reload_weights needs a checkpoint directory")
+        if self.engine.has_unfinished():
+            raise RuntimeError("reload_weights with requests in flight")
+        n = len(self.engine.runner.model.load_weights(iterate_safetensors(src)))
+        self.cfg.model.model_path = src
+        self.engine.scheduler.pool.reset_prefix_cache()
+        return n
+
     def serve_weights(self, host: str = "127.0.0.1", port: int = 0):
         """Let starting instances pull this instance's weights (netloader / rfork seed)."""
         from ..model_loader.netloader import WeightSource

@@ -324,6 +324,11 @@ class ModelRunner:
                 self.row_num_blocks[row] = nb
 
     def _prepare_inputs(self, so: SchedulerOutput, pad_to: Optional[int] = None):
+        from ..profiler import nvtx_range
+        with nvtx_range("prepare_inputs"):
+            return self._prepare_inputs_impl(so, pad_to)
+
+    def _prepare_inputs_impl(self, so: SchedulerOutput, pad_to: Optional[int] = None):
         reqs = [r for r, _ in so.scheduled]
         B = len(reqs)
         q_lens = np.fromiter((n for _, n in so.scheduled), dtype=np.int32, count=B)
@@ -516,6 +521,11 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ execution
     def _forward(self, T: int, meta: AttentionMetadata) -> torch.Tensor:
+        from ..profiler import nvtx_range
+        with nvtx_range(f"forward[{T}]"):
+            return self._forward_impl(T, meta)
+
+    def _forward_impl(self, T: int, meta: AttentionMetadata) -> torch.Tensor:
         pp = self.pp
         emb = self.mm.inputs_embeds(self.input_ids[:T]) if self.mm is not None else None
         if pp.world_size == 1:

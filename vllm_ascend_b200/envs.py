@@ -57,6 +57,9 @@ env_variables: dict[str, Callable[[], Any]] = {
     "VLLM_B200_LOG_PATH": _str("VLLM_B200_LOG_PATH", None),
     "VLLM_B200_ENABLE_CPU_BINDING": _bool("VLLM_B200_ENABLE_CPU_BINDING", "1"),
     "VLLM_B200_CUDA_GRAPH": _bool("VLLM_B200_CUDA_GRAPH", "1"),
+    # NVTX ranges around the engine's hook points: 0 off, 1 step level (prepare / forward / sample),
+    # 2 also one range per decoder layer
+    "VLLM_B200_NVTX": _int("VLLM_B200_NVTX", 0),
 }
 
 

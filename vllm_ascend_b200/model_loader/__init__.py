@@ -7,7 +7,7 @@ from __future__ import annotations
 
 from typing import Optional
 
-LOAD_FORMATS = ("auto", "netloader", "rfork")
+LOAD_FORMATS = ("auto", "netloader", "rfork", "sharded_state")
 
 
 def get_model_loader(load_format: str, extra: Optional[dict], tp_rank: int = 0, tp_size: int = 1, model_id: str = ""):
@@ -22,6 +22,10 @@ def get_model_loader(load_format: str, extra: Optional[dict], tp_rank: int = 0, 
         from .rfork import RForkLoader
         return RForkLoader(extra.get("planner_host", "127.0.0.1"), int(extra["planner_port"]),
                            extra.get("model_id", model_id), tp_rank, tp_size, backend=extra.get("backend"))
+    if load_format == "sharded_state":
+        import os
+        from .sharded_state import ShardedStateLoader
+        return ShardedStateLoader(extra["path"], int(os.environ.get("RANK", "0")))
     raise ValueError(f"unknown load_format {load_format!r}; known: {LOAD_FORMATS}")
 
 

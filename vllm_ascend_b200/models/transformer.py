@@ -389,9 +389,15 @@ class CausalLM:
         else:
             h, residual = intermediate
         aux = [] if self.aux_layers else None
+        from .. import envs
+        per_layer_nvtx = envs.VLLM_B200_NVTX >= 2 and h.is_cuda
         for layer, cache in zip(self.layers, kv_caches):
             call = getattr(layer, "offloaded_call", None)      # set by the weight offloader
+            if per_layer_nvtx:
+                torch.cuda.nvtx.range_push(f"layer{layer.idx}")
             h, residual = call(h, residual, meta, cache) if call is not None else layer(h, residual, meta, cache)
+            if per_layer_nvtx:
+                torch.cuda.nvtx.range_pop()
             if aux is not None:
                 for _ in range(self.aux_layers.count(layer.idx)):
                     aux.append(h + residual)
