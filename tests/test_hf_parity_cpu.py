@@ -1,0 +1,78 @@
+"""Checkpoint compatibility: random-weight transformers models saved as safetensors, loaded by this
+framework from the directory, greedy tokens compared with transformers' own generate()."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from vllm_ascend_b200 import LLM, SamplingParams
+
+
+def _save(model, cfg, path):
+    from safetensors.torch import save_file
+    path.mkdir()
+    sd = {k: v.contiguous() for k, v in model.state_dict().items()}
+    save_file(sd, str(path / "model.safetensors"))
+    d = cfg.to_dict()
+    d["architectures"] = [type(model).__name__]
+    (path / "config.json").write_text(json.dumps(d, default=str))
+
+
+def _cases():
+    from transformers import LlamaConfig, LlamaForCausalLM, Qwen2Config, Qwen2ForCausalLM, Qwen3Config, \
+        Qwen3ForCausalLM, Qwen3MoeConfig, Qwen3MoeForCausalLM
+    common = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=256, rope_theta=10000.0, tie_word_embeddings=False)
+    yield "llama", LlamaConfig(**common, rms_norm_eps=1e-5), LlamaForCausalLM
+    yield "qwen2", Qwen2Config(**common, rms_norm_eps=1e-6), Qwen2ForCausalLM
+    yield "qwen3", Qwen3Config(**common, head_dim=32, rms_norm_eps=1e-6), Qwen3ForCausalLM
+    yield "qwen3_moe", Qwen3MoeConfig(**common, head_dim=32, rms_norm_eps=1e-6, num_experts=4, num_experts_per_tok=2,
+                                      moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
+                                      mlp_only_layers=[]), Qwen3MoeForCausalLM
+    try:
+        from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+        yield "deepseek_v3", DeepseekV3Config(
+            vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+            num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8,
+            routed_scaling_factor=2.5, kv_lora_rank=32, q_lora_rank=48, qk_rope_head_dim=16, v_head_dim=32,
+            qk_nope_head_dim=32, n_group=4, topk_group=2, num_experts_per_tok=2, first_k_dense_replace=1,
+            norm_topk_prob=True, max_position_embeddings=256, rope_theta=10000.0, tie_word_embeddings=False,
+            rms_norm_eps=1e-6), DeepseekV3ForCausalLM
+    except ImportError:
+        pass
+    try:
+        from transformers import MixtralConfig, MixtralForCausalLM
+        yield "mixtral", MixtralConfig(**common, rms_norm_eps=1e-5, num_local_experts=4, num_experts_per_tok=2,
+                                       sliding_window=None), MixtralForCausalLM
+    except ImportError:
+        pass
+
+
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3"])
+def test_greedy_tokens_match_transformers(name, tmp_path):
+    case = {n: (c, m) for n, c, m in _cases()}.get(name)
+    if case is None:
+        pytest.skip(f"transformers has no {name}")
+    cfg, cls = case
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = cls(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.uniform_(0.5, 1.5)
+            else:
+                p.normal_(0, 0.08)
+    _save(hf, cfg, tmp_path / name)
+    llm = LLM(str(tmp_path / name), device="cpu", dtype="float32", max_model_len=128, max_num_seqs=4,
+              max_num_batched_tokens=24, block_size=16)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(1, 300, size=n).tolist() for n in (33, 7)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        t = torch.tensor([p])
+        with torch.no_grad():
+            ref = hf.generate(t, attention_mask=torch.ones_like(t), max_new_tokens=8, do_sample=False,
+                              pad_token_id=0)[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == ref, name

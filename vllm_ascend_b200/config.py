@@ -157,18 +157,22 @@ class ModelConfig:
             hidden_act=d.get("hidden_act", "silu"),
             dtype=str(d.get("torch_dtype", "bfloat16")).replace("torch.", ""),
         )
-        if "num_experts" in d or "n_routed_experts" in d:
+        n_exp = d.get("num_experts") or d.get("n_routed_experts") or d.get("num_local_experts") or 0
+        if n_exp:
             kw.update(
-                num_experts=d.get("num_experts", d.get("n_routed_experts", 0)),
+                num_experts=n_exp,
                 num_experts_per_tok=d.get("num_experts_per_tok", 0),
-                moe_intermediate_size=d.get("moe_intermediate_size", 0),
+                # Mixtral-style configs size their experts with intermediate_size
+                moe_intermediate_size=d.get("moe_intermediate_size") or d.get("intermediate_size", 0),
                 n_shared_experts=d.get("n_shared_experts", 0) or 0,
                 norm_topk_prob=d.get("norm_topk_prob", True),
-                scoring_func=d.get("scoring_func", "softmax"),
+                # DeepSeek-V3 family routers are sigmoid + bias-corrected top-k even when the config omits it
+                scoring_func=d.get("scoring_func", "sigmoid" if arch.startswith("DeepseekV3") else "softmax"),
                 n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1,
                 routed_scaling_factor=d.get("routed_scaling_factor", 1.0),
                 first_k_dense_replace=d.get("first_k_dense_replace", 0),
-                e_score_correction_bias=d.get("topk_method", "") == "noaux_tc",
+                e_score_correction_bias=d.get("topk_method", "noaux_tc" if arch.startswith("DeepseekV3") else "")
+                == "noaux_tc",
             )
         if d.get("index_topk"):
             kw.update(index_topk=int(d["index_topk"]), index_n_heads=int(d.get("index_n_heads", 64)),

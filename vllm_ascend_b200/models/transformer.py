@@ -484,6 +484,30 @@ class CausalLM:
         for name, w in weights:
             if name.endswith("rotary_emb.inv_freq"):
                 continue
+            orig_name = name
+            if "block_sparse_moe" in name:             # Mixtral's original tensor names
+                name = name.replace("block_sparse_moe", "mlp").replace(".w1.", ".gate_proj.") \
+                           .replace(".w3.", ".up_proj.").replace(".w2.", ".down_proj.")
+            mf = re.match(r"model\.layers\.(\d+)\.mlp\.experts\.(gate_up_proj|down_proj)$", name)
+            if mf and int(mf.group(1)) in layers and hasattr(layers[int(mf.group(1))].mlp, "w13"):
+                # all experts of a layer in one tensor: [E, 2I, H] (gate rows, then up rows) / [E, H, I]
+                L = layers[int(mf.group(1))].mlp
+                I = self.cfg.moe_intermediate_size
+                if L.ep is not None:
+                    w = w[L.expert_start:L.expert_start + L.E_local]
+                    if mf.group(2) == "gate_up_proj":
+                        L.w13.copy_(w)
+                    else:
+                        L.w2.copy_(w)
+                else:
+                    Il = I // tp
+                    if mf.group(2) == "gate_up_proj":
+                        L.w13[:, :Il].copy_(w[:, r * Il:(r + 1) * Il])
+                        L.w13[:, Il:].copy_(w[:, I + r * Il:I + (r + 1) * Il])
+                    else:
+                        L.w2.copy_(w[:, :, r * Il:(r + 1) * Il])
+                loaded.add(orig_name)
+                continue
             m = re.match(r"model\.layers\.(\d+)\.(.*)", name)
             if m and int(m.group(1)) not in layers:
                 continue
@@ -511,7 +535,7 @@ class CausalLM:
                         L.w13[e, Il:].copy_(w[r * Il:(r + 1) * Il])
                     else:
                         L.w2[e].copy_(w[:, r * Il:(r + 1) * Il])
-                loaded.add(name)
+                loaded.add(orig_name)
                 continue
             target, shard_id = name, None
             for hf, (merged, sid) in self._STACKED.items():
@@ -525,7 +549,7 @@ class CausalLM:
             dst = params[target]
             tp_t, r_t = self._shard_of(target, tp, r)
             self._copy_shard(target, dst, w, shard_id, tp_t, r_t)
-            loaded.add(name)
+            loaded.add(orig_name)
         for L in self.layers:
             if isinstance(L.self_attn, MLAAttention):
                 L.self_attn.process_weights_after_loading()
