@@ -31,6 +31,17 @@ def _cases():
                                       moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
                                       mlp_only_layers=[]), Qwen3MoeForCausalLM
     try:
+        from transformers import Qwen3NextConfig, Qwen3NextForCausalLM
+        yield "qwen3_next", Qwen3NextConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=32, max_position_embeddings=256, rope_theta=10000.0,
+            tie_word_embeddings=False, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16,
+            linear_num_key_heads=2, linear_num_value_heads=4, num_experts=4, num_experts_per_tok=2,
+            moe_intermediate_size=32, shared_expert_intermediate_size=32, decoder_sparse_step=1, mlp_only_layers=[],
+            full_attention_interval=2, partial_rotary_factor=0.25, rms_norm_eps=1e-6), Qwen3NextForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
         yield "deepseek_v3", DeepseekV3Config(
             vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
@@ -49,7 +60,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3"])
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:
@@ -60,7 +71,9 @@ def test_greedy_tokens_match_transformers(name, tmp_path):
     hf = cls(cfg).eval().float()
     with torch.no_grad():
         for n, p in hf.named_parameters():
-            if "norm" in n:
+            if n.endswith("A_log") or n.endswith("dt_bias"):
+                p.uniform_(-1.0, 1.0)
+            elif "norm" in n:
                 p.uniform_(0.5, 1.5)
             else:
                 p.normal_(0, 0.08)

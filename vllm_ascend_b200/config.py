@@ -55,6 +55,13 @@ class ModelConfig:
     linear_key_head_dim: int = 0
     linear_value_head_dim: int = 0
     linear_conv_kernel_dim: int = 4
+    layer_types: Optional[list] = None       # per layer "linear_attention" | "full_attention" (overrides the interval)
+    # Qwen3-Next attention / norm variants
+    gemma_norm: bool = False                 # RMSNorm scales by (1 + weight)
+    partial_rotary_factor: float = 1.0       # fraction of head_dim that is rotated
+    attn_output_gate: bool = False           # q_proj also produces a per-head sigmoid gate of the attention output
+    shared_expert_gate: bool = False         # shared expert output scaled by sigmoid(x . w)
+    shared_expert_intermediate_size: int = 0
     # sparse attention (DeepSeek-V3.2 style lightning indexer over MLA): keys kept per query, indexer heads
     index_topk: int = 0
     index_n_heads: int = 0
@@ -105,6 +112,8 @@ class ModelConfig:
         return self.full_attention_interval > 0
 
     def is_linear_layer(self, layer_idx: int) -> bool:
+        if self.layer_types and layer_idx < len(self.layer_types):
+            return self.layer_types[layer_idx] == "linear_attention"
         return self.is_hybrid and (layer_idx + 1) % self.full_attention_interval != 0
 
     def is_moe_layer(self, layer_idx: int) -> bool:
@@ -182,6 +191,20 @@ class ModelConfig:
                       kv_lora_rank=d["kv_lora_rank"],
                       qk_nope_head_dim=d["qk_nope_head_dim"],
                       qk_rope_head_dim=d["qk_rope_head_dim"], v_head_dim=d["v_head_dim"])
+        if d.get("full_attention_interval") or "linear_num_value_heads" in d:
+            rp = d.get("rope_parameters") or {}
+            lt = d.get("layer_types")
+            interval = d.get("full_attention_interval") or ((lt.index("full_attention") + 1) if lt and "full_attention" in lt else 4)
+            kw.update(full_attention_interval=int(interval), layer_types=list(lt) if lt else None,
+                      linear_num_key_heads=d["linear_num_key_heads"], linear_num_value_heads=d["linear_num_value_heads"],
+                      linear_key_head_dim=d["linear_key_head_dim"], linear_value_head_dim=d["linear_value_head_dim"],
+                      linear_conv_kernel_dim=d.get("linear_conv_kernel_dim", 4),
+                      gemma_norm=True, attn_output_gate=True, qk_norm=True,
+                      partial_rotary_factor=float(d.get("partial_rotary_factor", rp.get("partial_rotary_factor", 1.0))),
+                      shared_expert_intermediate_size=int(d.get("shared_expert_intermediate_size", 0) or 0),
+                      shared_expert_gate=bool(d.get("shared_expert_intermediate_size")))
+            if rp.get("rope_theta") and "rope_theta" not in d:
+                kw["rope_theta"] = rp["rope_theta"]
         rs = d.get("rope_scaling") or d.get("rope_parameters") or {}
         if rs.get("mrope_section"):
             kw.update(mrope_section=list(rs["mrope_section"]),

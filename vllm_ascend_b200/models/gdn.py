@@ -70,6 +70,40 @@ class GatedDeltaNet:
                                group=self.Dv, norm_before_gate=True)
         return self.out_proj(o)
 
+    def load_hf(self, suffix: str, w: torch.Tensor, tp: int, r: int) -> bool:
+        """One tensor of a published checkpoint (name relative to ``linear_attn.``).  The checkpoint
+        groups the projection rows by key head ([q, k, v-heads of the group, z-heads of the group] and
+        [b, a] per group); here the layout is [q | k | v | z] and [b | a], sliced per TP rank."""
+        cfg = self.cfg
+        Hk, Hv, Dk, Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, self.Dk, self.Dv
+        ratio = Hv // Hk
+
+        def shard(parts):          # every part is split over TP along dim 0
+            return torch.cat([p_[r * p_.shape[0] // tp:(r + 1) * p_.shape[0] // tp] for p_ in parts], dim=0)
+        if suffix == "in_proj_qkvz.weight":
+            g = w.view(Hk, 2 * Dk + 2 * ratio * Dv, -1)
+            q, k = g[:, :Dk].reshape(Hk * Dk, -1), g[:, Dk:2 * Dk].reshape(Hk * Dk, -1)
+            v = g[:, 2 * Dk:2 * Dk + ratio * Dv].reshape(Hv * Dv, -1)
+            z = g[:, 2 * Dk + ratio * Dv:].reshape(Hv * Dv, -1)
+            self.in_proj_qkvz.weight.copy_(shard([q, k, v, z]))
+        elif suffix == "in_proj_ba.weight":
+            g = w.view(Hk, 2 * ratio, -1)
+            self.in_proj_ba.weight.copy_(shard([g[:, :ratio].reshape(Hv, -1), g[:, ratio:].reshape(Hv, -1)]))
+        elif suffix == "conv1d.weight":
+            c = w.reshape(w.shape[0], -1)                                   # [conv_dim, K]
+            kd, vd = Hk * Dk, Hv * Dv
+            self.conv_weight.copy_(shard([c[:kd], c[kd:2 * kd], c[2 * kd:2 * kd + vd]]))
+        elif suffix in ("dt_bias", "A_log"):
+            getattr(self, suffix).copy_(w[r * Hv // tp:(r + 1) * Hv // tp].to(torch.float32))
+        elif suffix == "norm.weight":
+            self.norm_weight.copy_(w)
+        elif suffix == "out_proj.weight":
+            n = w.shape[1] // tp
+            self.out_proj.weight.copy_(w[:, r * n:(r + 1) * n])
+        else:
+            return False
+        return True
+
     def named_tensors(self):
         yield "conv1d.weight", self.conv_weight
         yield "dt_bias", self.dt_bias

@@ -291,15 +291,18 @@ class GQAAttention:
         prefix = f"model.layers.{layer_idx}.self_attn"
         kv_out = self.total_kv * self.D if self.total_kv >= tp else tp * self.D
         self.kv_replicas = 1 if self.total_kv >= tp else tp // self.total_kv
-        self.qkv_proj = ColumnParallelLinear(
-            pf, f"{prefix}.qkv_proj", cfg.hidden_size,
-            [cfg.num_attention_heads * self.D, kv_out, kv_out], comm, bias=cfg.attention_bias)
+        self.out_gate = bool(cfg.attn_output_gate)
+        sizes = [cfg.num_attention_heads * self.D, kv_out, kv_out]
+        if self.out_gate:       # [q | k | v | gate]: the fused rope / cache-write kernel still sees q, k, v first
+            sizes.append(cfg.num_attention_heads * self.D)
+        self.qkv_proj = ColumnParallelLinear(pf, f"{prefix}.qkv_proj", cfg.hidden_size, sizes, comm,
+                                             bias=cfg.attention_bias)
         self.o_proj = RowParallelLinear(pf, f"{prefix}.o_proj", cfg.num_attention_heads * self.D,
                                         cfg.hidden_size, comm)
         self.q_norm = pf.ones((self.D,)) if cfg.qk_norm else None
         self.k_norm = pf.ones((self.D,)) if cfg.qk_norm else None
         self.scale = self.D ** -0.5
-        self.rot_dim = self.D
+        self.rot_dim = int(self.D * cfg.partial_rotary_factor) // 2 * 2
         self.cos_sin = get_cos_sin_cache(self.rot_dim, max_pos, cfg.rope_theta, cfg.rope_scaling,
                                          pf.device)
         self.window = cfg.sliding_window or 0
@@ -313,6 +316,9 @@ class GQAAttention:
         k_cache, v_cache = kv_cache
         mpos = getattr(meta, "mrope_positions", None) if self.mrope_axis is not None else None
         pcp = getattr(meta, "pcp", None)
+        qkv_in = qkv
+        if self.out_gate:          # the kernel walks (Hq + 2 Hkv) heads per row; the gate columns follow them
+            qkv = qkv[:, :(self.Hq + 2 * self.Hkv) * self.D]
         ops.qknorm_rope_kvwrite(qkv, meta.positions if mpos is None else mpos, self.cos_sin,
                                 self.rot_dim, self.q_norm,
                                 self.k_norm, self.cfg.rms_norm_eps,
@@ -325,11 +331,15 @@ class GQAAttention:
             from ..attention.pcp import gather_kv_into_cache
             gather_kv_into_cache(qkv[:, self.Hq * self.D:], pcp, k_cache, v_cache, self.Hkv, self.D,
                                  self.cfg.rms_norm_eps, self.cos_sin)
+        qkv = qkv_in
         T = qkv.shape[0]
         q = qkv[:, :self.Hq * self.D].view(T, self.Hq, self.D)
         o = ops.paged_attention(q, k_cache, v_cache, meta, self.scale, causal=True,
                                 window=self.window)
-        return self.o_proj(o.view(T, self.Hq * self.D))
+        o = o.view(T, self.Hq * self.D)
+        if self.out_gate:
+            o = o * torch.sigmoid(qkv[:, (self.Hq + 2 * self.Hkv) * self.D:].float()).to(o.dtype)
+        return self.o_proj(o)
 
 
 class SwiGLUMLP:

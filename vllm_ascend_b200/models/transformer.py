@@ -62,14 +62,23 @@ class SparseMoeBlock:
             self.expert_map = None
         self.quant = None
         self.shared = None
-        if cfg.n_shared_experts > 0:
-            self.shared = SwiGLUMLP(pf, f"{prefix}.shared_experts", H, I * cfg.n_shared_experts,
-                                    comm, reduce_results=False)
+        self.shared_gate_weight = None
+        shared_inter = cfg.shared_expert_intermediate_size or I * cfg.n_shared_experts
+        if shared_inter > 0:
+            self.shared = SwiGLUMLP(pf, f"{prefix}.shared_experts", H, shared_inter, comm, reduce_results=False)
+            if cfg.shared_expert_gate:           # Qwen2-MoE / Qwen3-Next: sigmoid(x . w) scales the shared expert
+                self.shared_gate_weight = pf.normal(f"{prefix}.shared_expert_gate", (1, H))
         # logical -> physical redirect for redundant experts (EPLB); identity by default
         self._gate_bf16: Optional[torch.Tensor] = None
         self.log2phy: Optional[torch.Tensor] = None          # [E, max_replicas] physical slot ids
         self.log2phy_count: Optional[torch.Tensor] = None    # [E] replicas per expert
         self.expert_load: Optional[torch.Tensor] = None      # per-physical-expert hit counter
+
+    def _shared_out(self, x: torch.Tensor) -> torch.Tensor:
+        s = self.shared(x)
+        if self.shared_gate_weight is not None:
+            s = s * torch.sigmoid(torch.nn.functional.linear(x.float(), self.shared_gate_weight.float())).to(s.dtype)
+        return s
 
     def route(self, x: torch.Tensor):
         cfg = self.cfg
@@ -108,7 +117,7 @@ class SparseMoeBlock:
             side = side_stream("shared_expert", x.device)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                overlap = self.shared(x)
+                overlap = self._shared_out(x)
                 x.record_stream(side)
         moe_lora = getattr(self, "lora", None)
         if self.runtime is not None and self.ep is not None:
@@ -121,7 +130,7 @@ class SparseMoeBlock:
         if self.ep is None:
             # TP-sharded experts (and shared experts) hold partial sums: one reduction
             if self.shared is not None:
-                y = y + self.shared(x)
+                y = y + self._shared_out(x)
             if self.comm.size > 1:
                 y = self.comm.all_reduce(y)
             return y
@@ -130,7 +139,7 @@ class SparseMoeBlock:
                 torch.cuda.current_stream().wait_stream(side)
                 s = overlap
             else:
-                s = self.shared(x)
+                s = self._shared_out(x)
             if self.comm.size > 1:
                 s = self.comm.all_reduce(s)
             y = y + s
@@ -278,8 +287,8 @@ class DecoderLayer:
                  ep_group=None, moe_runtime=None):
         p = f"model.layers.{idx}"
         self.idx = idx
-        self.input_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
-        self.post_attention_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
+        self.input_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
+        self.post_attention_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
         if cfg.is_linear_layer(idx):
             from .gdn import GatedDeltaNet
             self.self_attn = GatedDeltaNet(pf, cfg, idx, comm)
@@ -360,7 +369,7 @@ class CausalLM:
                                                    TPComm(fg.embed_tp) if fg and fg.embed_tp else self.comm)
         self.layers = [DecoderLayer(pf, cfg, i, self.comm, max_pos, ep_group, moe_runtime)
                        for i in range(lo, hi)]
-        self.norm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps)
+        self.norm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
         if cfg.tie_word_embeddings:
             self.lm_head = ParallelLMHead(self.embed_tokens)
         else:
@@ -426,6 +435,12 @@ class CausalLM:
             yield f"{p}.input_layernorm.weight", L.input_layernorm.weight
             yield f"{p}.post_attention_layernorm.weight", L.post_attention_layernorm.weight
             a = L.self_attn
+            if getattr(a, "is_linear_attention", False):
+                for attr in ("in_proj_qkvz", "in_proj_ba", "out_proj"):
+                    for n, t in getattr(a, attr).named_tensors():
+                        yield f"{p}.linear_attn.{attr}.{n}", t
+                for n, t in a.named_tensors():
+                    yield f"{p}.linear_attn.{n}", t
             for attr in ("qkv_proj", "o_proj", "q_a_proj", "q_b_proj", "q_proj", "kv_a_proj",
                          "kv_b_proj"):
                 lin = getattr(a, attr, None)
@@ -454,6 +469,8 @@ class CausalLM:
                     yield f"{p}.mlp.gate.e_score_correction_bias", m.e_bias
                 yield f"{p}.mlp.experts.w13", m.w13
                 yield f"{p}.mlp.experts.w2", m.w2
+                if m.shared_gate_weight is not None:
+                    yield f"{p}.mlp.shared_expert_gate.weight", m.shared_gate_weight
                 if m.shared is not None:
                     for n, t in m.shared.gate_up_proj.named_tensors():
                         yield f"{p}.mlp.shared_experts.gate_up_proj.{n}", t
@@ -537,6 +554,23 @@ class CausalLM:
                         L.w2[e].copy_(w[:, r * Il:(r + 1) * Il])
                 loaded.add(orig_name)
                 continue
+            ml = re.match(r"model\.layers\.(\d+)\.linear_attn\.(.*)", name)
+            if ml:
+                a = layers[int(ml.group(1))].self_attn
+                if getattr(a, "is_linear_attention", False) and a.load_hf(ml.group(2), w, tp, r):
+                    loaded.add(orig_name)
+                continue
+            name = name.replace(".mlp.shared_expert.", ".mlp.shared_experts.")
+            if self.cfg.attn_output_gate and name.endswith("self_attn.q_proj.weight"):
+                # rows per head: [q (D) | gate (D)] -> q rows into slice 0, gate rows into slice 3 of the merged projection
+                D = self.cfg.head_dim
+                w4 = w.view(self.cfg.num_attention_heads, 2, D, -1)
+                tgt = name.replace("q_proj", "qkv_proj")
+                if tgt in params:
+                    self._copy_shard(tgt, params[tgt], w4[:, 0].reshape(-1, w.shape[-1]), 0, tp, r)
+                    self._copy_shard(tgt, params[tgt], w4[:, 1].reshape(-1, w.shape[-1]), 3, tp, r)
+                    loaded.add(orig_name)
+                continue
             target, shard_id = name, None
             for hf, (merged, sid) in self._STACKED.items():
                 if f".{hf}." in name:
@@ -549,6 +583,8 @@ class CausalLM:
             dst = params[target]
             tp_t, r_t = self._shard_of(target, tp, r)
             self._copy_shard(target, dst, w, shard_id, tp_t, r_t)
+            if self.cfg.gemma_norm and (target.endswith("self_attn.q_norm.weight") or target.endswith("self_attn.k_norm.weight")):
+                dst.add_(1.0)          # stored as the effective scale (1 + weight) the fused kernel multiplies by
             loaded.add(orig_name)
         for L in self.layers:
             if isinstance(L.self_attn, MLAAttention):
@@ -585,6 +621,10 @@ class CausalLM:
             Hkv_l = max(1, Hkv // tp)
             if shard_id == 0:
                 rows = slice(0, Hq_l * D)
+                src = w[r * Hq_l * D:(r + 1) * Hq_l * D]
+            elif shard_id == 3:        # output gate rows follow q, k, v
+                base = (Hq_l + 2 * Hkv_l) * D
+                rows = slice(base, base + Hq_l * D)
                 src = w[r * Hq_l * D:(r + 1) * Hq_l * D]
             else:
                 kv_rank = r if Hkv >= tp else r // (tp // Hkv)
