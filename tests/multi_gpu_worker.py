@@ -42,6 +42,48 @@ def tp_generate():
     return {"tokens": toks, "fused": fused, "replays": llm.engine.runner.stats["graph_replays"]}
 
 
+def fused_linear_ops():
+    """AG->GEMM and GEMM->RS (+ reduce / norm / push) of the fused TP dataflow against fp32 math, at
+    row counts that take the paired-CTA kernels (ragged last tile, columns not a multiple of 64)."""
+    from vllm_ascend_b200 import _native
+    from vllm_ascend_b200.parallel import state as pstate
+    from vllm_ascend_b200.parallel.fused_linear import FusedTPContext
+    rank, local, world = pstate.init_distributed()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    st = pstate.initialize_model_parallel(tp=world)
+    errs = []
+    for T, H, K in ((1000, 1024, 512), (4096, 2048 + 32, 768), (300, 512, 256)):
+        ctx = FusedTPContext(st.tp, dev, T + world, H)
+        Tp, rl = ctx.begin(T)
+        g = torch.Generator(device="cpu").manual_seed(7)
+        x_full = (torch.randn(Tp, K * world, generator=g) * 0.5).bfloat16()      # [T, K_total], this rank holds a K slice
+        w_full = (torch.randn(H, K * world, generator=g) * 0.05).bfloat16()
+        res_full = (torch.randn(Tp, H, generator=g) * 0.5).bfloat16()
+        norm_w = (torch.rand(H, generator=g) + 0.5).bfloat16()
+        x = x_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
+        w = w_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
+        ctx.residual[:rl].copy_(res_full[rank * rl:(rank + 1) * rl].to(dev))
+        for _ in range(2):                                   # epochs advance: run twice
+            ctx.residual[:rl].copy_(res_full[rank * rl:(rank + 1) * rl].to(dev))
+            ctx.gemm_rs(x, w)
+            ctx.norm_push(norm_w.to(dev), 1e-6)
+            got = ctx.gathered().float().cpu()
+        ctx.check()
+        y = (x_full.float() @ w_full.float().t()).bfloat16().float() + res_full.float()
+        y = y.bfloat16().float()
+        want = (y * torch.rsqrt((y * y).mean(-1, keepdim=True) + 1e-6) * norm_w.float()).bfloat16().float()
+        errs.append(float((got[:T] - want[:T]).abs().max() / want[:T].abs().max()))
+        # all-gather -> GEMM on the gathered rows
+        w2 = (torch.randn(384, H, generator=g) * 0.05).bfloat16()
+        out = ctx.ag_gemm(w2.to(dev)).float().cpu()
+        ctx.check()
+        want2 = got @ w2.float().t()
+        errs.append(float((out[:T] - want2[:T]).abs().max() / want2[:T].abs().max()))
+    torch.cuda.synchronize()
+    return {"max_rel_err": max(errs), "errs": errs}
+
+
 def symm_allreduce():
     """One-shot all-reduce and barrier over peer memory vs NCCL."""
     import ctypes
@@ -157,7 +199,7 @@ def moe_fused():
 
 
 if __name__ == "__main__":
-    res = {"tp_generate": tp_generate, "symm_allreduce": symm_allreduce, "moe_fused": moe_fused}[sys.argv[1]]()
+    res = {"tp_generate": tp_generate, "symm_allreduce": symm_allreduce, "fused_linear_ops": fused_linear_ops, "moe_fused": moe_fused}[sys.argv[1]]()
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps(res), flush=True)
     if torch.distributed.is_initialized():

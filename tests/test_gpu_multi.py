@@ -72,3 +72,9 @@ def test_prefill_context_parallel_on_two_gpus():
     # the split changes which attention kernel instance sees which query rows, not the math:
     # first tokens agree, later near-ties of the random-weight model may flip
     assert sum(x[0] == y[0] for x, y in zip(a, b)) >= len(b) - 1, (a, b)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_linear_ops_match_fp32_math():
+    r = _run(2, "fused_linear_ops")
+    assert r["max_rel_err"] < 0.03, r

@@ -31,7 +31,11 @@ constexpr int G2_STAGES = 6;
 constexpr int G2_A_BYTES = 128 * G2_BK * 2;        // 16 KB: this CTA's rows of A
 constexpr int G2_B_BYTES = 128 * G2_BK * 2;        // 16 KB: this CTA's half of the W tile
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
-constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+// reduce-scatter epilogue: every epilogue warp stages 32 rows x 64 columns (128 B per row, 16 B pad)
+// so that rows leave for their owner's GPU as 128-byte segments instead of one 16-byte store per row
+constexpr int G2_RS_ROW_BYTES = 144;
+constexpr int G2_RS_STAGE_BYTES = 4 * 32 * G2_RS_ROW_BYTES;
+constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256 + G2_RS_STAGE_BYTES;
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared address
 
 struct Gemm2Params {
@@ -259,6 +263,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
     const int out_per_tile = p.swiglu ? 128 : G2_BN;
+    uint8_t* rs_stage = smem + G2_STAGES * G2_STAGE_BYTES + 256 + q * (32 * G2_RS_ROW_BYTES);
     int it = 0;
     for (int t = cluster_id; t < num_tiles; t += num_clusters, it++) {
       int tm, tn;
@@ -332,8 +337,34 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
               o.y = pack_bf16x2(v[2], v[3]);
               o.z = pack_bf16x2(v[4], v[5]);
               o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(crow + col) = o;
+              if (p.mode & G2_RS)
+                *reinterpret_cast<uint4*>(rs_stage + lane * G2_RS_ROW_BYTES + ((c0 & 32) + g * 8) * 2) = o;
+              else
+                *reinterpret_cast<uint4*>(crow + col) = o;
             }
+          }
+        }
+        if (p.mode & G2_RS) {
+          // flush after two 32-column chunks (or at the tile's / matrix's last chunk): lanes regroup so
+          // one store instruction covers 4 rows x 128 contiguous bytes (8 rows x 64 bytes for a lone chunk)
+          const bool last = (col0 + 32 >= p.N) || (c0 + 32 >= out_per_tile);
+          if ((c0 & 32) || last) {
+            __syncwarp();
+            const int staged = (c0 & 32) ? 64 : 32;
+            const int colbase = col0 - (c0 & 32);
+            const int segs = staged >> 3;                 // 16-byte segments per row: 8 or 4
+            const int rows_per_inst = 32 / segs;
+            const unsigned long long my_ptr = (unsigned long long)crow;
+            for (int r0 = 0; r0 < 32; r0 += rows_per_inst) {
+              const int rr = r0 + lane / segs, sg = lane % segs;
+              const unsigned long long ptr = __shfl_sync(0xffffffffu, my_ptr, rr);
+              const int ok = __shfl_sync(0xffffffffu, (int)row_ok, rr);
+              const int col = colbase + sg * 8;
+              if (ok && col < p.N)
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)ptr + col) =
+                    *reinterpret_cast<const uint4*>(rs_stage + rr * G2_RS_ROW_BYTES + sg * 16);
+            }
+            __syncwarp();
           }
         }
       }
