@@ -47,8 +47,11 @@ struct GemmCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // 256 or 512 (power of two)
   // tiles + barriers + tmem pointer + abort word + group table, plus alignment slack
-  static constexpr int kSmemBytes =
-      kStages * kStageBytes + 1024 + 256 + (GEMM_MAX_GROUPS + 1) * 4;
+  // epilogues that store rows into another GPU's memory (reduce-scatter, MoE scatter) stage 32 rows x
+  // 64 columns per warp (128 B per row + 16 B pad) and send 128-byte row segments
+  static constexpr int kRsRowBytes = 144;
+  static constexpr int kRsStageOff = (kStages * kStageBytes + 256 + (GEMM_MAX_GROUPS + 1) * 4 + 15) / 16 * 16;
+  static constexpr int kSmemBytes = kRsStageOff + 4 * 32 * kRsRowBytes + 1024;
 };
 
 struct GemmParams {
@@ -273,6 +276,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     constexpr int OUT_COLS = BN;             // accumulator columns per tile
+    const bool remote_rows = (p.mode & (GEMM_RS | GEMM_SCATTER)) != 0;
+    uint8_t* rs_stage = smem + Cfg::kRsStageOff + q * (32 * Cfg::kRsRowBytes);
     const int out_per_tile = swiglu ? OUT_COLS / 2 : OUT_COLS;
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, it++) {
@@ -348,8 +353,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
               o.y = pack_bf16x2(v[2], v[3]);
               o.z = pack_bf16x2(v[4], v[5]);
               o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(crow + col) = o;
+              if (remote_rows)
+                *reinterpret_cast<uint4*>(rs_stage + lane * Cfg::kRsRowBytes + ((c0 & 32) + g * 8) * 2) = o;
+              else
+                *reinterpret_cast<uint4*>(crow + col) = o;
             }
+          }
+        }
+        if (remote_rows) {
+          // flush after two 32-column chunks (or at the last chunk): lanes regroup so one store
+          // instruction covers 4 rows x 128 contiguous bytes (8 rows x 64 bytes for a lone chunk)
+          const bool last = (col0 + 32 >= p.N) || (c0 + 32 >= out_per_tile);
+          if ((c0 & 32) || last) {
+            __syncwarp();
+            const int staged = (c0 & 32) ? 64 : 32;
+            const int colbase = col0 - (c0 & 32);
+            const int segs = staged >> 3;
+            const int rows_per_inst = 32 / segs;
+            const unsigned long long my_ptr = (unsigned long long)crow;
+            for (int r0 = 0; r0 < 32; r0 += rows_per_inst) {
+              const int rr = r0 + lane / segs, sg = lane % segs;
+              const unsigned long long ptr = __shfl_sync(0xffffffffu, my_ptr, rr);
+              const int ok = __shfl_sync(0xffffffffu, (int)row_ok, rr);
+              const int col = colbase + sg * 8;
+              if (ok && col < p.N)
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)ptr + col) =
+                    *reinterpret_cast<const uint4*>(rs_stage + rr * Cfg::kRsRowBytes + sg * 16);
+            }
+            __syncwarp();
           }
         }
       }
