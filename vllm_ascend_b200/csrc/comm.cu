@@ -99,7 +99,9 @@ __global__ void allreduce_oneshot_kernel(PeerPtrs bufs, PeerFlags bar_flags, Com
 }
 
 // ---------------------------------------------------------------- reduce + add + norm + push
-// One CTA per local row (rows_local rows of H columns).
+// CTAs walk the local rows (rows_local rows of H columns) with a grid stride: the peers' flags are
+// checked, and the system-scope fence after the remote stores is paid, once per CTA instead of once
+// per row.
 //   staging : [num_src][rows_local][H] bf16 partial sums written by the peers' GEMM
 //             epilogues (num_src = 0: no reduction, `x_local` is the input instead)
 //   residual: [rows_local][H] bf16, updated in place (may be null when num_src == 0
@@ -115,7 +117,6 @@ __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int nu
                                             int skip_norm) {
   __shared__ float red[32];
   __shared__ int s_ok;
-  const int row = blockIdx.x;
   const int nvec = H >> 3;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -127,8 +128,9 @@ __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int nu
     __syncthreads();
   }
   float vals[VEC_PER_THREAD][8];
-  float ss = 0.f;
   if (s_ok) {
+   for (int row = blockIdx.x; row < rows_local; row += gridDim.x) {
+    float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VEC_PER_THREAD; i++) {
       const int v = threadIdx.x + i * blockDim.x;
@@ -221,6 +223,8 @@ __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int nu
         }
       }
     }
+    __syncthreads();          // red[] is reused by the next row
+   }
     __threadfence_system();
   }
   __syncthreads();
@@ -346,8 +350,9 @@ B200_API int b200_reduce_add_norm_push(const void* staging, int num_src, const v
   if (threads < 32 * ((num_ranks + 31) / 32)) threads = 32 * ((num_ranks + 31) / 32);
   const int per = (nvec + threads - 1) / threads;
   CommCtl* ctl = (CommCtl*)peer_ctl[my_rank];
+  const int grid = rows_local < 148 * 4 ? rows_local : 148 * 4;
 #define LAUNCH_RANP(V)                                                                       \
-  reduce_add_norm_push_kernel<V><<<rows_local, threads, 0, stream>>>(                        \
+  reduce_add_norm_push_kernel<V><<<grid, threads, 0, stream>>>(                              \
       (const __nv_bfloat16*)staging, num_src, (const __nv_bfloat16*)x_local,                 \
       (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, a, f, ctl, rows_local, H, \
       my_rank, num_ranks, skip_norm)
