@@ -79,8 +79,10 @@ def main():
         for name, (cnt, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:18]:
             lines.append(f"  {us / total * 100:5.1f}%  {us / n / 1000:8.3f} ms/step  {cnt // n:5d}/step  {name}")
 
-    profile("mixed (prefill chunk + decodes)", args.mixed_steps, want_decode=False)
-    profile("decode only", args.decode_steps, want_decode=True)
+    if args.mixed_steps > 0:
+        profile("mixed (prefill chunk + decodes)", args.mixed_steps, want_decode=False)
+    if args.decode_steps > 0:
+        profile("decode only", args.decode_steps, want_decode=True)
     text = "\n".join(lines)
     if rank != 0:
         llm.shutdown()
