@@ -12,7 +12,9 @@ from vllm_ascend_b200 import LLM, SamplingParams
 def _save(model, cfg, path):
     from safetensors.torch import save_file
     path.mkdir()
-    sd = {k: v.contiguous() for k, v in model.state_dict().items()}
+    sd = {k: v.contiguous().clone() for k, v in model.state_dict().items()}
+    if getattr(cfg, "tie_word_embeddings", False):
+        sd.pop("lm_head.weight", None)           # tied checkpoints store the embedding only
     save_file(sd, str(path / "model.safetensors"))
     d = cfg.to_dict()
     d["architectures"] = [type(model).__name__]
@@ -30,6 +32,21 @@ def _cases():
     yield "qwen3_moe", Qwen3MoeConfig(**common, head_dim=32, rms_norm_eps=1e-6, num_experts=4, num_experts_per_tok=2,
                                       moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
                                       mlp_only_layers=[]), Qwen3MoeForCausalLM
+    try:
+        from transformers import MistralConfig, MistralForCausalLM
+        yield "mistral", MistralConfig(**common, rms_norm_eps=1e-5, sliding_window=None), MistralForCausalLM
+    except ImportError:
+        pass
+    try:
+        from transformers import Phi3Config, Phi3ForCausalLM
+        yield "phi3", Phi3Config(**{**common, "pad_token_id": 0}, rms_norm_eps=1e-5, sliding_window=None), Phi3ForCausalLM
+    except ImportError:
+        pass
+    try:
+        from transformers import GemmaConfig, GemmaForCausalLM
+        yield "gemma", GemmaConfig(**{**common, "tie_word_embeddings": True}, head_dim=32, rms_norm_eps=1e-6), GemmaForCausalLM
+    except ImportError:
+        pass
     try:
         from transformers import Qwen3NextConfig, Qwen3NextForCausalLM
         yield "qwen3_next", Qwen3NextConfig(
@@ -60,7 +77,8 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next"])
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
+                                  "mistral", "phi3", "gemma"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:
@@ -89,3 +107,42 @@ def test_greedy_tokens_match_transformers(name, tmp_path):
             ref = hf.generate(t, attention_mask=torch.ones_like(t), max_new_tokens=8, do_sample=False,
                               pad_token_id=0)[0, len(p):].tolist()
         assert o.outputs[0].token_ids == ref, name
+
+
+def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
+    """InternLM2 checkpoints (tok_embeddings / attention.wqkv grouped per KV head / feed_forward.w1,w3,w2 /
+    output) give the same model as the Llama-named tensors they were built from."""
+    from vllm_ascend_b200.config import ModelConfig
+    kw = dict(device="cpu", max_model_len=64, max_num_seqs=2, block_size=16)
+    base = dict(vocab_size=256, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=16, dtype="float32")
+    g = torch.Generator().manual_seed(0)
+    Hq, Hkv, D, H, I = 4, 2, 16, 64, 96
+    llama, intern = {}, {}
+    emb, head = torch.randn(256, H, generator=g) * 0.1, torch.randn(256, H, generator=g) * 0.1
+    llama["model.embed_tokens.weight"], intern["model.tok_embeddings.weight"] = emb, emb
+    llama["lm_head.weight"], intern["output.weight"] = head, head
+    nw = torch.rand(H, generator=g) + 0.5
+    llama["model.norm.weight"], intern["model.norm.weight"] = nw, nw
+    for i in range(2):
+        q, k, v = (torch.randn(n, H, generator=g) * 0.1 for n in (Hq * D, Hkv * D, Hkv * D))
+        wqkv = torch.cat([q.view(Hkv, Hq // Hkv, D, H), k.view(Hkv, 1, D, H), v.view(Hkv, 1, D, H)], dim=1).reshape(-1, H)
+        o = torch.randn(H, Hq * D, generator=g) * 0.1
+        w1, w3, w2 = torch.randn(I, H, generator=g) * 0.1, torch.randn(I, H, generator=g) * 0.1, torch.randn(H, I, generator=g) * 0.1
+        n1, n2 = torch.rand(H, generator=g) + 0.5, torch.rand(H, generator=g) + 0.5
+        L, N = f"model.layers.{i}.", f"model.layers.{i}."
+        llama.update({L + "self_attn.q_proj.weight": q, L + "self_attn.k_proj.weight": k, L + "self_attn.v_proj.weight": v,
+                      L + "self_attn.o_proj.weight": o, L + "mlp.gate_proj.weight": w1, L + "mlp.up_proj.weight": w3,
+                      L + "mlp.down_proj.weight": w2, L + "input_layernorm.weight": n1, L + "post_attention_layernorm.weight": n2})
+        intern.update({N + "attention.wqkv.weight": wqkv, N + "attention.wo.weight": o, N + "feed_forward.w1.weight": w1,
+                       N + "feed_forward.w3.weight": w3, N + "feed_forward.w2.weight": w2, N + "attention_norm.weight": n1,
+                       N + "ffn_norm.weight": n2})
+    a = LLM(ModelConfig(name="a", architecture="LlamaForCausalLM", **base), **kw)
+    b = LLM(ModelConfig(name="b", architecture="InternLM2ForCausalLM", **base), **kw)
+    assert len(a.engine.runner.model.load_weights(llama.items())) == len(llama)
+    assert len(b.engine.runner.model.load_weights(intern.items())) == len(intern)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    p = [[3, 9, 27, 81, 5, 15]]
+    assert a.generate(p, sp)[0].outputs[0].token_ids == b.generate(p, sp)[0].outputs[0].token_ids
+    pa, pb = dict(a.engine.runner.model.named_parameters()), dict(b.engine.runner.model.named_parameters())
+    assert all(torch.equal(pa[k], pb[k]) for k in pa)

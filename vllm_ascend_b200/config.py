@@ -58,6 +58,7 @@ class ModelConfig:
     layer_types: Optional[list] = None       # per layer "linear_attention" | "full_attention" (overrides the interval)
     # Qwen3-Next attention / norm variants
     gemma_norm: bool = False                 # RMSNorm scales by (1 + weight)
+    embed_scale: float = 1.0                 # token embeddings are multiplied by this (Gemma: sqrt(hidden))
     partial_rotary_factor: float = 1.0       # fraction of head_dim that is rotated
     attn_output_gate: bool = False           # q_proj also produces a per-head sigmoid gate of the attention output
     shared_expert_gate: bool = False         # shared expert output scaled by sigmoid(x . w)
@@ -163,9 +164,12 @@ class ModelConfig:
             qk_norm=arch.startswith("Qwen3"),
             attention_bias=d.get("attention_bias", arch.startswith("Qwen2")),
             sliding_window=d.get("sliding_window") if d.get("use_sliding_window", False) else None,
-            hidden_act=d.get("hidden_act", "silu"),
+            hidden_act=d.get("hidden_activation") or d.get("hidden_act", "silu"),
             dtype=str(d.get("torch_dtype", "bfloat16")).replace("torch.", ""),
         )
+        if arch.startswith("Gemma"):
+            kw.update(gemma_norm=True, embed_scale=float(hs) ** 0.5,
+                      tie_word_embeddings=d.get("tie_word_embeddings", True))
         n_exp = d.get("num_experts") or d.get("n_routed_experts") or d.get("num_local_experts") or 0
         if n_exp:
             kw.update(

@@ -342,9 +342,18 @@ class GQAAttention:
         return self.o_proj(o)
 
 
+_GATED_ACTS = {"silu": None, "swish": None, "gelu_pytorch_tanh": "gelu_tanh", "gelu_tanh": "gelu_tanh",
+               "gelu_new": "gelu_tanh", "gelu": "gelu"}
+
+
 class SwiGLUMLP:
+    """Gated MLP: act(x W_gate) * (x W_up) -> W_down; SiLU (fused into the GEMM epilogue) or GELU gates."""
+
     def __init__(self, pf: ParamFactory, prefix: str, hidden: int, inter: int, comm: TPComm,
-                 reduce_results: bool = True):
+                 reduce_results: bool = True, act: str = "silu"):
+        if act not in _GATED_ACTS:
+            raise ValueError(f"unsupported MLP activation {act!r}")
+        self.act = _GATED_ACTS[act]
         self.gate_up_proj = ColumnParallelLinear(pf, f"{prefix}.gate_up_proj", hidden,
                                                  [inter, inter], comm)
         self.down_proj = RowParallelLinear(pf, f"{prefix}.down_proj", inter, hidden, comm,
@@ -352,6 +361,8 @@ class SwiGLUMLP:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         gu = self.gate_up_proj
+        if self.act is not None:
+            return self.down_proj(ops.activation(gu(x).contiguous(), self.act, gated=True))
         if gu.quant is None and gu.bias is None and not gu.gather_output and not gu._lora_on():
             return self.down_proj(ops.linear_swiglu(x, gu.weight))
         if wants_quant_act(self.down_proj):

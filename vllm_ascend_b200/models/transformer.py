@@ -303,7 +303,7 @@ class DecoderLayer:
                               reduce_results=False)
             self.mlp = fgm.FGMLP(inner, fg.mlp_tp)
         else:
-            self.mlp = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm)
+            self.mlp = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm, act=cfg.hidden_act)
         if fg is not None and fg.otp is not None and isinstance(self.self_attn, GQAAttention):
             a = self.self_attn
             inner = RowParallelLinear(pf, f"{p}.self_attn.o_proj", cfg.num_attention_heads * a.D, cfg.hidden_size,
@@ -394,6 +394,8 @@ class CausalLM:
         if self.is_first:
             # multimodal steps pass embeddings with the encoder outputs already merged in
             h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+            if self.cfg.embed_scale != 1.0 and inputs_embeds is None:
+                h = h * torch.tensor(self.cfg.embed_scale, dtype=h.dtype)      # rounded to the model dtype first
             residual = None
         else:
             h, residual = intermediate
@@ -498,10 +500,25 @@ class CausalLM:
         params = dict(self.named_parameters())
         layers = {L.idx: L for L in self.layers}
         tp, r = self.comm.size, self.comm.rank
+        arch_internlm2 = self.cfg.architecture.startswith("InternLM2")
         for name, w in weights:
             if name.endswith("rotary_emb.inv_freq"):
                 continue
             orig_name = name
+            if arch_internlm2:
+                name = _internlm2_name(name)
+                if name.endswith("attention.wqkv.weight"):
+                    # rows grouped per KV head: [q heads of the group..., k, v] x head_dim
+                    D, Hkv = self.cfg.head_dim, self.cfg.num_key_value_heads
+                    G = self.cfg.num_attention_heads // Hkv
+                    w5 = w.view(Hkv, G + 2, D, -1)
+                    base = name.replace("attention.wqkv", "self_attn.qkv_proj")
+                    if base in params:
+                        for sid, part in ((0, w5[:, :G].reshape(Hkv * G * D, -1)), (1, w5[:, G].reshape(Hkv * D, -1)),
+                                          (2, w5[:, G + 1].reshape(Hkv * D, -1))):
+                            self._copy_shard(base, params[base], part, sid, tp, r)
+                        loaded.add(orig_name)
+                    continue
             if "block_sparse_moe" in name:             # Mixtral's original tensor names
                 name = name.replace("block_sparse_moe", "mlp").replace(".w1.", ".gate_proj.") \
                            .replace(".w3.", ".up_proj.").replace(".w2.", ".down_proj.")
@@ -652,6 +669,14 @@ class CausalLM:
                     dst.copy_(w.narrow(d, r * n, n))
                 return
         raise ValueError(f"cannot place {target}: {tuple(w.shape)} -> {tuple(dst.shape)}")
+
+
+def _internlm2_name(name: str) -> str:
+    """InternLM2 tensor names -> the Llama-style names the loader works with."""
+    return (name.replace("model.tok_embeddings.", "model.embed_tokens.").replace("output.weight", "lm_head.weight")
+            .replace(".attention.wo.", ".self_attn.o_proj.").replace(".attention_norm.", ".input_layernorm.")
+            .replace(".ffn_norm.", ".post_attention_layernorm.").replace(".feed_forward.w1.", ".mlp.gate_proj.")
+            .replace(".feed_forward.w3.", ".mlp.up_proj.").replace(".feed_forward.w2.", ".mlp.down_proj."))
 
 
 def iterate_safetensors(path: str):
