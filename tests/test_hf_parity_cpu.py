@@ -33,6 +33,13 @@ def _cases():
                                       moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
                                       mlp_only_layers=[]), Qwen3MoeForCausalLM
     try:
+        from transformers import Qwen2MoeConfig, Qwen2MoeForCausalLM
+        yield "qwen2_moe", Qwen2MoeConfig(**common, rms_norm_eps=1e-6, num_experts=4, num_experts_per_tok=2,
+                                          moe_intermediate_size=48, shared_expert_intermediate_size=64,
+                                          norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[]), Qwen2MoeForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MistralConfig, MistralForCausalLM
         yield "mistral", MistralConfig(**common, rms_norm_eps=1e-5, sliding_window=None), MistralForCausalLM
     except ImportError:
@@ -78,7 +85,7 @@ def _cases():
 
 
 @pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
-                                  "mistral", "phi3", "gemma"])
+                                  "mistral", "phi3", "gemma", "qwen2_moe"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:

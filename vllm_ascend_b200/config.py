@@ -167,6 +167,8 @@ class ModelConfig:
             hidden_act=d.get("hidden_activation") or d.get("hidden_act", "silu"),
             dtype=str(d.get("torch_dtype", "bfloat16")).replace("torch.", ""),
         )
+        if d.get("shared_expert_intermediate_size"):       # Qwen2-MoE / Qwen3-Next: one gated shared expert
+            kw.update(shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]), shared_expert_gate=True)
         if arch.startswith("Gemma"):
             kw.update(gemma_norm=True, embed_scale=float(hs) ** 0.5,
                       tie_word_embeddings=d.get("tie_word_embeddings", True))
