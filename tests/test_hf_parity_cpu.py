@@ -40,6 +40,17 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import DeepseekV2Config, DeepseekV2ForCausalLM
+        yield "deepseek_v2", DeepseekV2Config(
+            vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+            num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8,
+            routed_scaling_factor=1.0, kv_lora_rank=32, q_lora_rank=None, qk_rope_head_dim=16, v_head_dim=32,
+            qk_nope_head_dim=32, n_group=1, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
+            norm_topk_prob=False, topk_method="greedy", max_position_embeddings=256, rope_theta=10000.0,
+            tie_word_embeddings=False, rms_norm_eps=1e-6), DeepseekV2ForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MistralConfig, MistralForCausalLM
         yield "mistral", MistralConfig(**common, rms_norm_eps=1e-5, sliding_window=None), MistralForCausalLM
     except ImportError:
@@ -85,7 +96,8 @@ def _cases():
 
 
 @pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
-                                  "mistral", "phi3", "gemma", "qwen2_moe"])
+                                  "mistral", "phi3", "gemma", "qwen2_moe",
+                                  "deepseek_v2"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:

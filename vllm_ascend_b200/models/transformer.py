@@ -595,6 +595,8 @@ class CausalLM:
                     break
             target = target.replace("kv_a_proj_with_mqa", "kv_a_proj") \
                            .replace("q_a_layernorm", "q_a_norm").replace("kv_a_layernorm", "kv_a_norm")
+            if target not in params and name in params:
+                target, shard_id = name, None          # e.g. the un-merged q_proj of MLA layers without q_lora
             if target not in params:
                 continue
             dst = params[target]
