@@ -25,9 +25,15 @@ def _cases():
     from transformers import LlamaConfig, LlamaForCausalLM, Qwen2Config, Qwen2ForCausalLM, Qwen3Config, \
         Qwen3ForCausalLM, Qwen3MoeConfig, Qwen3MoeForCausalLM
     common = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                  num_key_value_heads=2, max_position_embeddings=256, rope_theta=10000.0, tie_word_embeddings=False)
+                  num_key_value_heads=2, max_position_embeddings=256, rope_theta=50000.0, tie_word_embeddings=False)
     yield "llama", LlamaConfig(**common, rms_norm_eps=1e-5), LlamaForCausalLM
     yield "qwen2", Qwen2Config(**common, rms_norm_eps=1e-6), Qwen2ForCausalLM
+    l3 = dict(common, max_position_embeddings=512)
+    yield "llama31_rope", LlamaConfig(**l3, rms_norm_eps=1e-5, rope_scaling={
+        "rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 64}), LlamaForCausalLM
+    yield "qwen2_yarn", Qwen2Config(**l3, rms_norm_eps=1e-6, rope_scaling={
+        "rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64}), Qwen2ForCausalLM
     yield "qwen3", Qwen3Config(**common, head_dim=32, rms_norm_eps=1e-6), Qwen3ForCausalLM
     yield "qwen3_moe", Qwen3MoeConfig(**common, head_dim=32, rms_norm_eps=1e-6, num_experts=4, num_experts_per_tok=2,
                                       moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
@@ -88,6 +94,18 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+        yield "deepseek_v3_yarn", DeepseekV3Config(
+            vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=2,
+            num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8,
+            routed_scaling_factor=2.5, kv_lora_rank=32, q_lora_rank=48, qk_rope_head_dim=16, v_head_dim=32,
+            qk_nope_head_dim=32, n_group=4, topk_group=2, num_experts_per_tok=2, first_k_dense_replace=1,
+            norm_topk_prob=True, max_position_embeddings=512, rope_theta=10000.0, tie_word_embeddings=False,
+            rms_norm_eps=1e-6, rope_scaling={"rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 64,
+                                             "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0}),             DeepseekV3ForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MixtralConfig, MixtralForCausalLM
         yield "mixtral", MixtralConfig(**common, rms_norm_eps=1e-5, num_local_experts=4, num_experts_per_tok=2,
                                        sliding_window=None), MixtralForCausalLM
@@ -97,7 +115,8 @@ def _cases():
 
 @pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
-                                  "deepseek_v2"])
+                                  "deepseek_v2", "llama31_rope", "qwen2_yarn",
+                                  "deepseek_v3_yarn"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:
@@ -118,7 +137,7 @@ def test_greedy_tokens_match_transformers(name, tmp_path):
     llm = LLM(str(tmp_path / name), device="cpu", dtype="float32", max_model_len=128, max_num_seqs=4,
               max_num_batched_tokens=24, block_size=16)
     rng = np.random.default_rng(0)
-    prompts = [rng.integers(1, 300, size=n).tolist() for n in (33, 7)]
+    prompts = [rng.integers(1, 300, size=n).tolist() for n in ((100, 7) if "rope" in name or "yarn" in name else (33, 7))]
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     for p, o in zip(prompts, outs):
         t = torch.tensor([p])

@@ -149,6 +149,11 @@ class ModelConfig:
                     d[k] = top[k]
         hs = d["hidden_size"]
         nh = d["num_attention_heads"]
+        rp_ = d.get("rope_parameters") or {}
+        if not d.get("rope_scaling") and (rp_.get("rope_type") or rp_.get("type")) not in (None, "default", "mrope"):
+            d = dict(d, rope_scaling={k: v for k, v in rp_.items() if k != "rope_theta"})   # newer config layout
+        if "rope_theta" not in d and rp_.get("rope_theta"):
+            d = dict(d, rope_theta=rp_["rope_theta"])
         kw: dict[str, Any] = dict(
             architecture=arch,
             vocab_size=d["vocab_size"], hidden_size=hs,
