@@ -59,6 +59,7 @@ def _cases():
     try:
         from transformers import MistralConfig, MistralForCausalLM
         yield "mistral", MistralConfig(**common, rms_norm_eps=1e-5, sliding_window=None), MistralForCausalLM
+        yield "mistral_window", MistralConfig(**common, rms_norm_eps=1e-5, sliding_window=16), MistralForCausalLM
     except ImportError:
         pass
     try:
@@ -116,7 +117,7 @@ def _cases():
 @pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
-                                  "deepseek_v3_yarn"])
+                                  "deepseek_v3_yarn", "mistral_window"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:

@@ -168,7 +168,9 @@ class ModelConfig:
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             qk_norm=arch.startswith("Qwen3"),
             attention_bias=d.get("attention_bias", arch.startswith("Qwen2")),
-            sliding_window=d.get("sliding_window") if d.get("use_sliding_window", False) else None,
+            # Qwen2 gates its window with use_sliding_window; Mistral-style configs apply it whenever it is set
+            sliding_window=(d.get("sliding_window") if d.get("use_sliding_window", not arch.startswith("Qwen"))
+                            else None),
             hidden_act=d.get("hidden_activation") or d.get("hidden_act", "silu"),
             dtype=str(d.get("torch_dtype", "bfloat16")).replace("torch.", ""),
         )
