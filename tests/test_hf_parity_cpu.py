@@ -185,3 +185,33 @@ def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
     assert a.generate(p, sp)[0].outputs[0].token_ids == b.generate(p, sp)[0].outputs[0].token_ids
     pa, pb = dict(a.engine.runner.model.named_parameters()), dict(b.engine.runner.model.named_parameters())
     assert all(torch.equal(pa[k], pb[k]) for k in pa)
+
+
+@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe"])
+def test_checkpoint_sharding_tp2_matches_tp1(name, tmp_path):
+    """The same checkpoint directory loaded by two tensor-parallel ranks (gloo) gives the single-rank
+    tokens: per-rank slicing of grouped GDN projections, gated q_proj, fused expert tensors, MLA."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_tp_cpu import _run
+    case = {n: (c, m) for n, c, m in _cases()}.get(name)
+    if case is None:
+        pytest.skip(f"transformers has no {name}")
+    cfg, cls = case
+    torch.manual_seed(0)
+    hf = cls(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("A_log") or n.endswith("dt_bias"):
+                p.uniform_(-1.0, 1.0)
+            elif "norm" in n:
+                p.uniform_(0.5, 1.5)
+            else:
+                p.normal_(0, 0.08)
+    cfg.dtype = torch.float32
+    _save(hf, cfg, tmp_path / name)
+    path = str(tmp_path / name)
+    want = _run(path, 1, 1)
+    assert _run(path, 2, 2) == want
+    if name == "qwen2_moe":          # experts sharded over the two ranks instead (expert parallel, DP attention)
+        assert _run(path, 2, 1, ep=True) == want

@@ -172,7 +172,7 @@ class ModelConfig:
             sliding_window=(d.get("sliding_window") if d.get("use_sliding_window", not arch.startswith("Qwen"))
                             else None),
             hidden_act=d.get("hidden_activation") or d.get("hidden_act", "silu"),
-            dtype=str(d.get("torch_dtype", "bfloat16")).replace("torch.", ""),
+            dtype=str(d.get("torch_dtype") or d.get("dtype") or "bfloat16").replace("torch.", ""),
         )
         if d.get("shared_expert_intermediate_size"):       # Qwen2-MoE / Qwen3-Next: one gated shared expert
             kw.update(shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]), shared_expert_gate=True)
