@@ -374,3 +374,19 @@ def test_async_engine_steps_synchronously_for_token_dependent_sampling():
     got = [o.outputs[0].token_ids for o in llm.generate(prompts, sps)]
     assert got == want
     assert not llm.engine._needs_sync()
+
+
+def test_n_samples_per_prompt():
+    llm = LLM("tiny-qwen", device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=64, block_size=16,
+              enable_prefix_caching=True)
+    prompt = list(range(5, 45))
+    out = llm.generate([prompt, [7, 8, 9]], [SamplingParams(n=3, temperature=1.0, top_k=50, seed=11, max_tokens=8, ignore_eos=True),
+                                             SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)])
+    assert [len(o.outputs) for o in out] == [3, 1]
+    assert [c.index for c in out[0].outputs] == [0, 1, 2]
+    toks = [tuple(c.token_ids) for c in out[0].outputs]
+    assert len(set(toks)) > 1 and all(len(t) == 8 for t in toks)                # independent random streams
+    again = llm.generate([prompt], SamplingParams(n=3, temperature=1.0, top_k=50, seed=11, max_tokens=8, ignore_eos=True))
+    assert [tuple(c.token_ids) for c in again[0].outputs] == toks               # reproducible with the seed
+    assert again[0].num_cached_tokens > 0 or llm.engine.scheduler.pool.hits > 0  # siblings share the cached prompt
+    assert not llm.engine.scheduler.requests

@@ -415,6 +415,19 @@ class LLM:
             out.append(torch.nn.functional.normalize(v, dim=-1) if normalize else v)
         return out
 
+    @staticmethod
+    def _child_params(sp: SamplingParams, j: int) -> SamplingParams:
+        """Sampling parameters of the j-th of ``sp.n`` samples: independent random streams (seed + j
+        when a seed is given), everything else shared."""
+        if sp.n <= 1:
+            return sp
+        import copy
+        c = copy.copy(sp)
+        c.n = 1
+        if sp.seed is not None:
+            c.seed = sp.seed + j
+        return c
+
     def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  use_tqdm: bool = False, lora_request=None) -> list[RequestOutput]:
         """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``)."""
@@ -436,12 +449,17 @@ class LLM:
             pe = p.get("prompt_embeds") if isinstance(p, dict) else None
             if pe is not None and ids is None:
                 ids = []
-            rid = eng.add_request(ids, sp, kv_transfer_params=ktp, lora_request=lr, multi_modal_data=mmd,
-                                  prompt_embeds=pe)
+            rid = eng.add_request(ids, self._child_params(sp, 0), kv_transfer_params=ktp, lora_request=lr,
+                                  multi_modal_data=mmd, prompt_embeds=pe)
             order.append(rid)
             mine.append(i)
             reqs[rid] = eng.scheduler.requests[rid]
             reqs[rid].client_index, reqs[rid].origin_rank = i, dp.rank_in_group
+            reqs[rid].siblings = []
+            for j in range(1, max(1, sp.n)):          # n > 1: sibling requests over the same prompt
+                sid = eng.add_request(ids, self._child_params(sp, j), kv_transfer_params=ktp, lora_request=lr,
+                                      multi_modal_data=mmd, prompt_embeds=pe)
+                reqs[rid].siblings.append(eng.scheduler.requests[sid])
         if dp.world_size > 1:
             while eng.step_dp():
                 pass
@@ -453,20 +471,26 @@ class LLM:
             # requests may have moved between DP ranks (load balancing): report what finished here
             done = [r for r in eng.scheduler.requests.values()
                     if r.is_finished and getattr(r, "client_index", None) is not None]
+            for r in done:
+                if getattr(r, "siblings", None) and not all(s_.is_finished for s_ in r.siblings):
+                    raise RuntimeError("n > 1 is not supported together with cross-replica request migration")
             mine = [r.client_index for r in done]
             order = [r.request_id for r in done]
             reqs = {r.request_id: r for r in done}
         outs = []
         for rid in order:
             r = reqs[rid]
+            family = [r] + list(getattr(r, "siblings", None) or [])
             outs.append(RequestOutput(
                 request_id=rid, prompt_token_ids=r.prompt_token_ids.tolist(),
-                outputs=[CompletionOutput(0, list(r.output_token_ids or []),
-                                          finish_reason=_FINISH_REASON.get(r.status), logprobs=r.logprobs)],
+                outputs=[CompletionOutput(j, list(c.output_token_ids or []),
+                                          finish_reason=_FINISH_REASON.get(c.status), logprobs=c.logprobs)
+                         for j, c in enumerate(family)],
                 finished=True,
                 metrics=RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time),
                 kv_transfer_params=r.kv_transfer_params, num_cached_tokens=r.num_cached_tokens))
-            eng.scheduler.requests.pop(rid, None)
+            for c in family:
+                eng.scheduler.requests.pop(c.request_id, None)
         if dp.world_size > 1:
             # every rank returns the complete, input-ordered list
             merged: list = [None] * len(prompts)

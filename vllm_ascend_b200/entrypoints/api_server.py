@@ -96,6 +96,8 @@ def _sampling_params(body: dict) -> SamplingParams:
     lp = body.get("logprobs")
     if isinstance(lp, bool):                       # chat API: boolean + top_logprobs
         lp = int(body.get("top_logprobs") or 0) if lp else None
+    if int(body.get("n") or 1) != 1:
+        raise HTTPException(400, "n > 1 is served by LLM.generate; the HTTP server returns one choice per request")
     return SamplingParams(
         max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
         temperature=float(body.get("temperature", 1.0)),

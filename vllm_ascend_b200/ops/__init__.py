@@ -456,7 +456,7 @@ def sample(logits_f32: torch.Tensor, temperature, top_k, top_p, min_p=None, seed
            offsets=None, generator=None) -> torch.Tensor:
     """Top-k/top-p/min-p + exponential-race sampling (destroys ``logits_f32`` on CUDA)."""
     if not logits_f32.is_cuda:
-        return ref.sample(logits_f32, temperature, top_k.to(torch.int64), top_p, min_p, generator)
+        return ref.sample(logits_f32, temperature, top_k.to(torch.int64), top_p, min_p, generator, seeds, offsets)
     B, V = logits_f32.shape
     out = torch.empty(B, dtype=torch.int64, device=logits_f32.device)
     rc = _native.lib().b200_sample(

@@ -310,13 +310,23 @@ def top_k_top_p_filter(probs: torch.Tensor, top_k: torch.Tensor, top_p: torch.Te
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, min_p: Optional[torch.Tensor] = None,
-           generator: Optional[torch.Generator] = None) -> torch.Tensor:
-    """Greedy rows (temperature < 1e-5) take argmax; others the exponential race."""
+           generator: Optional[torch.Generator] = None, seeds: Optional[torch.Tensor] = None,
+           offsets: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy rows (temperature < 1e-5) take argmax; others the exponential race.  With ``seeds`` /
+    ``offsets`` every row draws from its own stream (request seed, number of tokens generated so
+    far), so a request's samples do not depend on what else is in the batch."""
     greedy = temperature < 1e-5
     t = torch.where(greedy, torch.ones_like(temperature), temperature).unsqueeze(1)
     probs = torch.softmax(logits.float() / t, dim=-1)
     probs = top_k_top_p_filter(probs, top_k, top_p, min_p)
-    e = torch.empty_like(probs).exponential_(1.0, generator=generator)
+    if seeds is not None:
+        e = torch.empty_like(probs)
+        off = offsets if offsets is not None else torch.zeros_like(seeds)
+        for i in range(probs.shape[0]):
+            g = torch.Generator(device="cpu").manual_seed((int(seeds[i]) * 1000003 + int(off[i])) & ((1 << 63) - 1))
+            e[i].exponential_(1.0, generator=g)
+    else:
+        e = torch.empty_like(probs).exponential_(1.0, generator=generator)
     sampled = (probs / e).argmax(dim=-1)
     return torch.where(greedy, logits.argmax(dim=-1), sampled)
 
