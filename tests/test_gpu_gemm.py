@@ -30,7 +30,7 @@ def _check(M, N, K, bn=0, bias=False, residual=False, seed=0):
 @pytest.mark.parametrize("bn", [128, 256, 512])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (256, 512, 4096),
                                    (1, 256, 128), (77, 1024, 1024), (1000, 768, 2048),
-                                   (4096, 6144, 4096)])
+                                   (4096, 6144, 4096), (300, 768, 288), (64, 256, 3424)])
 def test_gemm_shapes(M, N, K, bn):
     _check(M, N, K, bn)
 

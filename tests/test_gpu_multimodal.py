@@ -149,3 +149,78 @@ def test_encoder_graph_replay_matches_eager():
         assert (got - want).abs().max() < 2e-2 * want.abs().max()
     assert mgr.stats["captures"] == 2 and mgr.stats["replays"] == 4
     _native.check_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("H,T", [(1152, 300), (4608, 77), (64, 5), (10240, 3)])
+def test_layer_norm_kernel(H, T):
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(T, H, generator=g) * 2 + 0.7).bfloat16()
+    w, b = (torch.rand(H, generator=g) + 0.5).bfloat16(), torch.randn(H, generator=g).bfloat16()
+    want = torch.nn.functional.layer_norm(x.float(), (H,), w.float(), b.float(), 1e-6)
+    c0 = _native.launch_counter[0]
+    got = ops.layer_norm(x.to(DEV), w.to(DEV), b.to(DEV), 1e-6)
+    assert _native.launch_counter[0] == c0 + 1
+    assert (got.float().cpu() - want).abs().max() < 4e-2
+    nob = ops.layer_norm(x.to(DEV), w.to(DEV), None, 1e-6)
+    want0 = torch.nn.functional.layer_norm(x.float(), (H,), w.float(), None, 1e-6)
+    assert (nob.float().cpu() - want0).abs().max() < 4e-2
+
+
+def test_qwen3_vl_tower_on_gpu_matches_fp32():
+    from vllm_ascend_b200.models.vision import Qwen3VisionTransformer, VisionConfig
+    cfg = VisionConfig(depth=3, hidden_size=288, num_heads=4, intermediate_size=512, out_hidden_size=256,
+                       patch_size=16, num_position_embeddings=64, deepstack_visual_indexes=[0, 2], init_std=0.05)
+    cpu = Qwen3VisionTransformer(cfg, "cpu", torch.float32)
+    gpu = Qwen3VisionTransformer(cfg, DEV, torch.bfloat16)
+    gpu.load_weights([(n, t) for n, t in cpu.named_parameters()])
+    grid = np.array([[1, 16, 20], [2, 8, 8]])
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, cfg.patch_dim, generator=torch.Generator().manual_seed(3))
+    want = cpu(px, grid)
+    c0 = _native.launch_counter[0]
+    got = gpu(px.to(DEV), grid).float().cpu()
+    assert _native.launch_counter[0] - c0 >= 10 * cfg.depth
+    _native.check_status(torch.device(DEV))
+    assert got.shape == want.shape == (n // 4, 3 * 256)
+    for i in range(3):
+        a, b = got[:, 256 * i:256 * (i + 1)], want[:, 256 * i:256 * (i + 1)]
+        assert (a - b).norm() / b.norm() < 3e-2, i
+
+
+def test_qwen3_vl_engine_on_gpu():
+    """Deepstack rows under CUDA-graph decode and chunked prefill: graph output equals eager, and the
+    image changes the continuation."""
+    from vllm_ascend_b200.config import ModelConfig
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+
+    def cfg():
+        return ModelConfig(name="vl3-t", architecture="Qwen3VLForConditionalGeneration", vocab_size=2048,
+                           hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=8,
+                           num_key_value_heads=2, head_dim=128, qk_norm=True, rope_theta=1e6,
+                           dtype="bfloat16", init_std=0.05, mrope_section=[24, 20, 20], mrope_interleaved=True,
+                           image_token_id=2000, video_token_id=2001,
+                           vision_config=dict(depth=2, hidden_size=256, num_heads=4, intermediate_size=512,
+                                              out_hidden_size=512, patch_size=16, num_position_embeddings=64,
+                                              deepstack_visual_indexes=[0, 1], init_std=0.05))
+    g = torch.Generator().manual_seed(0)
+    grid = (1, 16, 12)
+    img_a = torch.randn(16 * 12, 3 * 2 * 16 * 16, generator=g)
+    img_b = torch.randn(16 * 12, 3 * 2 * 16 * 16, generator=g)
+    rng = np.random.default_rng(0)
+    text = rng.integers(0, 1900, size=40).tolist()
+    ids = text[:10] + [2000] + text[10:]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = {}
+    for eager in (True, False):
+        llm = LLM(cfg(), device="cuda", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=64,
+                  num_gpu_blocks_override=40, enforce_eager=eager, cudagraph_capture_sizes=[2, 4])
+        assert llm.engine.runner.model.num_deepstack == 2
+        outs[eager] = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": [(img_a, grid)]}}],
+                                   sp)[0].outputs[0].token_ids
+        if eager:
+            other = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": [(img_b, grid)]}}],
+                                 sp)[0].outputs[0].token_ids
+            assert other != outs[eager]
+    assert outs[True] == outs[False]
+    _native.check_status(torch.device("cuda"))

@@ -201,3 +201,83 @@ def test_patchify_layout_and_resize():
     assert np.allclose(pv[1].reshape(3, 2, 14, 14)[:, 0], x[:14, 14:28].transpose(2, 0, 1), atol=1e-6)
     assert np.allclose(pv[2].reshape(3, 2, 14, 14)[:, 0], x[14:28, :14].transpose(2, 0, 1), atol=1e-6)
     assert np.allclose(pv[4].reshape(3, 2, 14, 14)[:, 0], x[:14, 28:42].transpose(2, 0, 1), atol=1e-6)
+
+
+# ---------------------------------------------------------------- Qwen3-VL (deepstack, learned positions)
+def _hf_qwen3_vl():
+    from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+    cfg = Qwen3VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                         rope_parameters={"rope_type": "default", "rope_theta": 1e6, "mrope_section": [4, 6, 6],
+                                          "mrope_interleaved": True},
+                         max_position_embeddings=2048, tie_word_embeddings=False),
+        vision_config=dict(depth=3, hidden_size=64, num_heads=4, intermediate_size=96, out_hidden_size=128,
+                           patch_size=14, num_position_embeddings=36, deepstack_visual_indexes=[0, 1]),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
+    cfg._attn_implementation = "eager"
+    cfg.architectures = ["Qwen3VLForConditionalGeneration"]
+    torch.manual_seed(0)
+    m = Qwen3VLForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.normal_(0, 0.05)
+            if "norm" in n and n.endswith("weight"):
+                p.add_(1.0)
+    return cfg, m
+
+
+def test_qwen3_vl_tower_matches_transformers():
+    from vllm_ascend_b200.models.vision import Qwen3VisionTransformer
+    cfg, hf = _hf_qwen3_vl()
+    vc = VisionConfig.from_hf(cfg.vision_config.to_dict())
+    assert vc.num_position_embeddings == 36 and vc.deepstack_visual_indexes == [0, 1]
+    ours = Qwen3VisionTransformer(vc, "cpu", torch.float32)
+    sd = hf.model.visual.state_dict()
+    assert len(ours.load_weights(sd.items())) == len(sd)
+    grid = np.array([[1, 6, 8], [2, 4, 4], [1, 10, 6]])
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, vc.patch_dim, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf.model.visual(px, grid_thw=torch.from_numpy(grid))
+    main = ref.pooler_output if hasattr(ref, "pooler_output") else ref[0]
+    deep = ref.deepstack_features if hasattr(ref, "deepstack_features") else ref[1]
+    got = ours(px, grid)
+    assert got.shape == (n // 4, 3 * 128)
+    assert torch.allclose(got[:, :128], main, atol=2e-4, rtol=2e-4), (got[:, :128] - main).abs().max()
+    for i, d in enumerate(deep):
+        assert torch.allclose(got[:, 128 * (i + 1):128 * (i + 2)], d, atol=2e-4, rtol=2e-4)
+
+
+def test_qwen3_vl_engine_matches_transformers_greedy():
+    """Deepstack features join the residual stream after the first decoder layers, positions use the
+    interleaved 3-axis rotary layout: greedy tokens equal transformers' under chunked prefill."""
+    from vllm_ascend_b200.config import ModelConfig
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    from vllm_ascend_b200.multimodal import build_mm_request, mrope_positions
+    cfg, hf = _hf_qwen3_vl()
+    mcfg = ModelConfig.from_hf_dict(cfg.to_dict(), dtype="float32", architecture="Qwen3VLForConditionalGeneration")
+    assert mcfg.mrope_section == [4, 6, 6] and mcfg.mrope_interleaved and mcfg.qk_norm
+    llm = LLM(mcfg, device="cpu", max_model_len=256, max_num_seqs=4, max_num_batched_tokens=16,
+              num_gpu_blocks_override=64, block_size=16)
+    loaded = llm.engine.runner.model.load_weights(hf.state_dict().items())
+    assert len(loaded) == len(hf.state_dict())
+    ids, px, grids = _mm_prompt(torch.Generator().manual_seed(0))
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": list(zip(px, grids))}},
+                         {"prompt_token_ids": [9, 8, 7, 6, 5]}], sp)
+    full = outs[0].prompt_token_ids
+    _, items = build_mm_request(ids, {"image": list(zip(px, grids))}, mcfg)
+    pos, delta = mrope_positions(full, items, 2, 2.0)
+    seq, want = list(full), []
+    for _ in range(6):
+        L = len(seq)
+        p3 = np.concatenate([pos, np.arange(pos.shape[1], L)[None].repeat(3, 0) + delta], axis=1)
+        t = torch.tensor([seq])
+        with torch.no_grad():
+            lg = hf(input_ids=t, position_ids=torch.from_numpy(p3)[:, None, :], attention_mask=torch.ones_like(t),
+                    pixel_values=torch.cat(px), image_grid_thw=torch.tensor(grids)).logits
+        seq.append(int(lg[0, -1].argmax()))
+        want.append(seq[-1])
+    assert outs[0].outputs[0].token_ids == want

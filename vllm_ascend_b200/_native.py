@@ -30,6 +30,7 @@ _SIGNATURES = {
     "b200_embedding": [P, P, P, L, I, L, L, P],
     "b200_qknorm_rope_kvwrite": [P, L, P, P, I, P, P, F, P, P, P, I, I, I, I, L, I, I, P, P],
     "b200_rope_table": [P, L, P, P, L, I, I, I, P],
+    "b200_layer_norm": [P, P, P, P, L, I, F, L, L, P],
     "b200_qknorm_mrope_kvwrite": [P, L, P, L, P, P, I, P, P, F, P, P, P, I, I, I, I, L, I, I, P, P],
     "b200_quant_fp8_group128": [P, P, P, L, I, I, P],
     "b200_activation": [P, P, L, I, I, I, F, F, P],

@@ -54,6 +54,7 @@ class AttentionMetadata:
     # multimodal rotary embedding: int64 [3, num_input_tokens] (temporal, height, width)
     mrope_positions: Optional[torch.Tensor] = None
     pcp: object = None                      # attention.pcp.PCPMeta on split prefill steps
+    deepstack: object = None                # (rows [n], features [L, n, H]) added after the first L layers
     # decode-context-parallel / extras
     dcp_world_size: int = 1
     dcp_rank: int = 0

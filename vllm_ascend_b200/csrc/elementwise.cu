@@ -341,6 +341,87 @@ __global__ void quant_fp8_group128_kernel(const __nv_bfloat16* __restrict__ x,
   if (lane == 0) scales[g] = scale;
 }
 
+
+// ---------------------------------------------------------------- LayerNorm
+// One CTA per row, row held in registers: mean, then the variance around it, then
+// out <- (x - mean) * rstd * w + b.  Used by vision-tower blocks and mergers.
+template <int VEC_PER_THREAD>
+__global__ void layer_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                  const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ out,
+                                  int H, float eps, long x_stride, long out_stride) {
+  const long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * x_stride);
+  uint4* orow = reinterpret_cast<uint4*>(out + row * out_stride);
+  const int nvec = H >> 3;
+  float vals[VEC_PER_THREAD][8];
+  __shared__ float red[33];
+  auto block_sum = [&](float v) {
+    v = warp_reduce_sum(v);
+    __syncthreads();                       // previous use of red is over
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+      t = warp_reduce_sum(t);
+      if (threadIdx.x == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+  };
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC_PER_THREAD; i++) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      uint4 a = xr[v];
+      uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float2 f = unpack_bf16x2(aw[j]);
+        vals[i][2 * j] = f.x;
+        vals[i][2 * j + 1] = f.y;
+        s += f.x + f.y;
+      }
+    }
+  }
+  const float mean = block_sum(s) / (float)H;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC_PER_THREAD; i++) {
+    if (threadIdx.x + i * blockDim.x < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const float d = vals[i][j] - mean;
+        ss = fmaf(d, d, ss);
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss) / (float)H + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const uint4* br = reinterpret_cast<const uint4*>(b);
+#pragma unroll
+  for (int i = 0; i < VEC_PER_THREAD; i++) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      uint4 ww = wr[v];
+      uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
+      uint32_t b4[4] = {0u, 0u, 0u, 0u};
+      if (b) {
+        uint4 bb = br[v];
+        b4[0] = bb.x; b4[1] = bb.y; b4[2] = bb.z; b4[3] = bb.w;
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float2 fw = unpack_bf16x2(w4[j]), fb = unpack_bf16x2(b4[j]);
+        o[j] = pack_bf16x2(fmaf((vals[i][2 * j] - mean) * rstd, fw.x, fb.x),
+                           fmaf((vals[i][2 * j + 1] - mean) * rstd, fw.y, fb.y));
+      }
+      orow[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -369,6 +450,29 @@ B200_API int b200_rms_norm(const void* x, void* residual, const void* w, void* o
                                                             out_stride);
   else
     return 9101;  // hidden size above 32768 not supported
+  return B200_CHECK_LAUNCH();
+}
+
+B200_API int b200_layer_norm(const void* x, const void* w, const void* b, void* out, long T, int H,
+                             float eps, long x_stride, long out_stride, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((H & 7) || (x_stride & 7) || (out_stride & 7)) return 9110;
+  const int nvec = H >> 3;
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  const int per = (nvec + threads - 1) / threads;
+  auto X = (const __nv_bfloat16*)x;
+  auto W = (const __nv_bfloat16*)w;
+  auto Bp = (const __nv_bfloat16*)b;
+  auto O = (__nv_bfloat16*)out;
+  if (per <= 1)
+    layer_norm_kernel<1><<<(unsigned)T, threads, 0, stream>>>(X, W, Bp, O, H, eps, x_stride, out_stride);
+  else if (per <= 2)
+    layer_norm_kernel<2><<<(unsigned)T, threads, 0, stream>>>(X, W, Bp, O, H, eps, x_stride, out_stride);
+  else if (per <= 4)
+    layer_norm_kernel<4><<<(unsigned)T, threads, 0, stream>>>(X, W, Bp, O, H, eps, x_stride, out_stride);
+  else
+    return 9111;
   return B200_CHECK_LAUNCH();
 }
 

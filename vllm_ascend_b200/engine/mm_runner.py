@@ -28,6 +28,7 @@ class MultimodalState:
         self.ec_connector = ec_connector
         self.encoder_graphs = None                 # optional EncoderGraphManager
         self._patches: list[tuple[int, int, torch.Tensor]] = []
+        self.deepstack = None                      # set by inputs_embeds for models with deepstack features
         self.stats = {"encoder_runs": 0, "encoder_items": 0, "encoder_cache_hits": 0, "remote_items": 0}
 
     # -- per-step preparation -------------------------------------------------
@@ -104,11 +105,21 @@ class MultimodalState:
     # -- forward-time merge -------------------------------------------------------
     def inputs_embeds(self, input_ids: torch.Tensor) -> Optional[torch.Tensor]:
         """Token embeddings with this step's encoder rows written in; None for text-only steps."""
+        self.deepstack = None
         if not self._patches:
             return None
         h = self.runner.model.embed_input_ids(input_ids)
+        H = h.shape[-1]
+        L = getattr(self.runner.model, "num_deepstack", 0)
+        rows, feats = [], []
         for a, b, emb in self._patches:
-            h[a:b] = emb.to(h.dtype)
+            h[a:b] = emb[:, :H].to(h.dtype)
+            if L and emb.shape[-1] == (1 + L) * H:
+                rows.append(torch.arange(a, b, device=h.device))
+                feats.append(emb[:, H:].to(h.dtype).view(b - a, L, H))
+        if rows:
+            # (token rows [n], features [L, n, H]) the decoder adds after its first L layers
+            self.deepstack = (torch.cat(rows), torch.cat(feats).transpose(0, 1).contiguous())
         self._patches = []
         return h
 

@@ -151,7 +151,9 @@ class ModelRunner:
         if self.mcfg.is_multimodal and self.model.is_first:
             from .mm_runner import MultimodalState
             self.mm = MultimodalState(self)
-            if self.is_cuda and self.cfg.compilation.cudagraph_mode != "NONE":
+            # towers that split host index math from a capturable device part replay from graphs
+            if self.is_cuda and self.cfg.compilation.cudagraph_mode != "NONE" \
+                    and hasattr(self.model.visual, "host_inputs"):
                 from ..compilation.encoder_graph import EncoderGraphManager
                 self.mm.encoder_graphs = EncoderGraphManager(self.model.visual)
 
@@ -528,6 +530,8 @@ class ModelRunner:
     def _forward_impl(self, T: int, meta: AttentionMetadata) -> torch.Tensor:
         pp = self.pp
         emb = self.mm.inputs_embeds(self.input_ids[:T]) if self.mm is not None else None
+        if emb is not None:
+            meta.deepstack = self.mm.deepstack
         if pp.world_size == 1:
             if emb is not None:
                 return self.model.forward(self.input_ids[:T], meta, self.kv_caches, inputs_embeds=emb)

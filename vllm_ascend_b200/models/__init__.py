@@ -30,7 +30,8 @@ def _qwen_vl(cfg, device, **kw):
     return QwenVLForConditionalGeneration(cfg, device, **kw)
 
 
-for _arch in ("Qwen2_5_VLForConditionalGeneration", "Qwen2VLForConditionalGeneration"):
+for _arch in ("Qwen2_5_VLForConditionalGeneration", "Qwen2VLForConditionalGeneration",
+              "Qwen3VLForConditionalGeneration"):
     register_model(_arch, _qwen_vl)
 
 

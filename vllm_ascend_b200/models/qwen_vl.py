@@ -24,7 +24,14 @@ class QwenVLForConditionalGeneration(CausalLM):
         self.vision_cfg = VisionConfig.from_hf(cfg.vision_config or {})
         if self.vision_cfg.out_hidden_size != cfg.hidden_size:
             raise ValueError("vision tower output width must equal the decoder's hidden size")
-        self.visual = VisionTransformer(self.vision_cfg, self.device, self.dtype) if self.is_first else None
+        self.num_deepstack = len(self.vision_cfg.deepstack_visual_indexes)
+        if not self.is_first:
+            self.visual = None
+        elif self.vision_cfg.num_position_embeddings:
+            from .vision import Qwen3VisionTransformer
+            self.visual = Qwen3VisionTransformer(self.vision_cfg, self.device, self.dtype)
+        else:
+            self.visual = VisionTransformer(self.vision_cfg, self.device, self.dtype)
 
     # -- multimodal interface ------------------------------------------------
     def embed_multimodal(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:

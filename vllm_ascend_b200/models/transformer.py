@@ -400,6 +400,7 @@ class CausalLM:
         else:
             h, residual = intermediate
         aux = [] if self.aux_layers else None
+        deepstack = getattr(meta, "deepstack", None)
         from .. import envs
         per_layer_nvtx = envs.VLLM_B200_NVTX >= 2 and h.is_cuda
         for layer, cache in zip(self.layers, kv_caches):
@@ -409,6 +410,9 @@ class CausalLM:
             h, residual = call(h, residual, meta, cache) if call is not None else layer(h, residual, meta, cache)
             if per_layer_nvtx:
                 torch.cuda.nvtx.range_pop()
+            if deepstack is not None and layer.idx < deepstack[1].shape[0]:
+                # visual features join the residual stream (h + residual) at the image-token rows
+                h.index_add_(0, deepstack[0], deepstack[1][layer.idx].to(h.dtype))
             if aux is not None:
                 for _ in range(self.aux_layers.count(layer.idx)):
                     aux.append(h + residual)

@@ -39,6 +39,10 @@ class VisionConfig:
     fullatt_block_indexes: list = field(default_factory=lambda: [7, 15, 23, 31])
     rms_norm_eps: float = 1e-6
     init_std: float = 0.02
+    # Qwen3-VL tower: learned position table (bilinearly interpolated to the image grid), LayerNorm
+    # blocks with a plain GELU MLP, no windows, extra "deepstack" mergers after the listed blocks
+    num_position_embeddings: int = 0
+    deepstack_visual_indexes: list = field(default_factory=list)
 
     @property
     def head_dim(self) -> int:
@@ -233,4 +237,145 @@ class VisionTransformer:
             dst = params[tgt] if rows is None else params[tgt][rows[0]:rows[1]]
             dst.copy_(w.to(dst.dtype))
             loaded.add(name)
+        return loaded
+
+
+# ---------------------------------------------------------------- Qwen3-VL tower
+def pos_embed_interpolation(grid_thw: np.ndarray, side: int, merge: int):
+    """Bilinear sampling of a side x side position table on every image's h x w patch grid, in the
+    merge-group patch order: (indices [4, N], weights [4, N])."""
+    idx, wts = [[] for _ in range(4)], [[] for _ in range(4)]
+    for t, h, w in grid_thw:
+        hs = torch.linspace(0, side - 1, int(h))
+        ws = torch.linspace(0, side - 1, int(w))
+        hf, wf = hs.int(), ws.int()
+        hc, wc = (hf + 1).clip(max=side - 1), (wf + 1).clip(max=side - 1)
+        dh, dw = hs - hf, ws - wf
+        combos = [(hf, wf, (1 - dh)[:, None] * (1 - dw)[None]), (hf, wc, (1 - dh)[:, None] * dw[None]),
+                  (hc, wf, dh[:, None] * (1 - dw)[None]), (hc, wc, dh[:, None] * dw[None])]
+
+        def regroup(a):          # [h, w] -> merge-group order, repeated over the t frame groups
+            a = a.reshape(int(h) // merge, merge, int(w) // merge, merge).permute(0, 2, 1, 3).reshape(-1)
+            return a.repeat(int(t))
+        for k, (hi, wi, wt) in enumerate(combos):
+            idx[k].append(regroup((hi[:, None] * side + wi[None]).long()))
+            wts[k].append(regroup(wt))
+    return torch.stack([torch.cat(x) for x in idx]), torch.stack([torch.cat(x) for x in wts])
+
+
+class _LN:
+    def __init__(self, mk, size):
+        self.weight, self.bias = mk.ones((size,)), mk.zeros((size,))
+
+    def __call__(self, x):
+        return ops.layer_norm(x, self.weight, self.bias, 1e-6)
+
+
+class Qwen3VisionBlock:
+    def __init__(self, cfg: VisionConfig, mk, idx: int):
+        H, I = cfg.hidden_size, cfg.intermediate_size
+        self.cfg = cfg
+        self.norm1, self.norm2 = _LN(mk, H), _LN(mk, H)
+        self.qkv = Linear(mk.normal((3 * H, H)), mk.zeros((3 * H,)), f"blocks.{idx}.attn.qkv")
+        self.proj = Linear(mk.normal((H, H)), mk.zeros((H,)), f"blocks.{idx}.attn.proj")
+        self.fc1 = Linear(mk.normal((I, H)), mk.zeros((I,)), f"blocks.{idx}.mlp.linear_fc1")
+        self.fc2 = Linear(mk.normal((H, I)), mk.zeros((H,)), f"blocks.{idx}.mlp.linear_fc2")
+
+    def __call__(self, h, plan, cos, sin):
+        cfg = self.cfg
+        N, nh, D = h.shape[0], cfg.num_heads, cfg.head_dim
+        qkv = self.qkv(self.norm1(h))
+        qk = qkv[:, :2 * nh * D].view(N, 2 * nh, D)
+        if qkv.is_cuda:
+            enc.rope_table_(qkv.view(N, 3 * nh, D)[:, :2 * nh], cos, sin)
+        else:
+            qk.copy_(enc.rope_table_ref(qk, cos, sin))
+        q, k, v = (qkv[:, i * nh * D:(i + 1) * nh * D].view(N, nh, D) for i in range(3))
+        o = enc.encoder_attention(q, k, v, plan, D ** -0.5)
+        h = self.proj(o.reshape(N, nh * D), residual=h)
+        return self.fc2(ops.activation(self.fc1(self.norm2(h)).contiguous(), "gelu_tanh"), residual=h)
+
+
+class _Qwen3Merger:
+    def __init__(self, cfg: VisionConfig, mk, name: str, postshuffle: bool):
+        Hm = cfg.hidden_size * cfg.merge_unit
+        self.postshuffle, self.Hm = postshuffle, Hm
+        self.norm = _LN(mk, Hm if postshuffle else cfg.hidden_size)
+        self.fc1 = Linear(mk.normal((Hm, Hm)), mk.zeros((Hm,)), f"{name}.linear_fc1")
+        self.fc2 = Linear(mk.normal((cfg.out_hidden_size, Hm)), mk.zeros((cfg.out_hidden_size,)), f"{name}.linear_fc2")
+
+    def __call__(self, x):
+        x = self.norm(x.view(-1, self.Hm)) if self.postshuffle else self.norm(x).view(-1, self.Hm)
+        return self.fc2(ops.activation(self.fc1(x).contiguous(), "gelu"))
+
+
+class Qwen3VisionTransformer:
+    """``forward(pixel_values, grid_thw)`` -> [N / merge_unit, (1 + len(deepstack)) * out_hidden]: the merged
+    image tokens followed, along the feature axis, by the deepstack features the decoder adds to the
+    residual stream after its first layers."""
+
+    def __init__(self, cfg: VisionConfig, device, dtype=torch.bfloat16):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        mk = _Maker(self.device, dtype, cfg.init_std)
+        self.patch_embed = Linear(mk.normal((cfg.hidden_size, cfg.patch_dim)), mk.zeros((cfg.hidden_size,)),
+                                  "patch_embed.proj")
+        self.pos_embed = mk.normal((cfg.num_position_embeddings, cfg.hidden_size))
+        self.side = int(round(cfg.num_position_embeddings ** 0.5))
+        self.blocks = [Qwen3VisionBlock(cfg, mk, i) for i in range(cfg.depth)]
+        self.merger = _Qwen3Merger(cfg, mk, "merger", False)
+        self.deepstack = [_Qwen3Merger(cfg, mk, f"deepstack_merger_list.{i}", True)
+                          for i in range(len(cfg.deepstack_visual_indexes))]
+        q = cfg.head_dim // 4
+        self.inv_freq = 1.0 / (10000.0 ** (np.arange(0, q, dtype=np.float64) * 2 / (cfg.head_dim // 2)))
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+        cfg = self.cfg
+        grid = np.asarray(grid_thw, dtype=np.int64).reshape(-1, 3)
+        dev = self.device
+        idx, wts = pos_embed_interpolation(grid, self.side, cfg.spatial_merge_size)
+        pos = (self.pos_embed[idx.to(dev)] * wts.to(dev, self.dtype).unsqueeze(-1)).sum(0)
+        h = self.patch_embed(pixel_values.to(dev, self.dtype)) + pos
+        ids = rot_pos_ids(grid, cfg.spatial_merge_size)
+        ang = np.concatenate([ids[:, 0:1] * self.inv_freq[None], ids[:, 1:2] * self.inv_freq[None]], axis=1)
+        cos = torch.from_numpy(np.cos(ang)).float().to(dev).contiguous()
+        sin = torch.from_numpy(np.sin(ang)).float().to(dev).contiguous()
+        cu = np.concatenate([[0], np.cumsum(np.repeat(grid[:, 1] * grid[:, 2], grid[:, 0]))])
+        plan = enc.make_plan(cu, dev)
+        feats = []
+        for i, blk in enumerate(self.blocks):
+            h = blk(h, plan, cos, sin)
+            if i in cfg.deepstack_visual_indexes:
+                feats.append(self.deepstack[cfg.deepstack_visual_indexes.index(i)](h))
+        return torch.cat([self.merger(h)] + feats, dim=-1)
+
+    __call__ = forward
+
+    def named_parameters(self):
+        yield "patch_embed.proj.weight", self.patch_embed.weight
+        yield "patch_embed.proj.bias", self.patch_embed.bias
+        yield "pos_embed.weight", self.pos_embed
+        for i, b in enumerate(self.blocks):
+            p = f"blocks.{i}"
+            for nm, ln in (("norm1", b.norm1), ("norm2", b.norm2)):
+                yield f"{p}.{nm}.weight", ln.weight
+                yield f"{p}.{nm}.bias", ln.bias
+            for nm, lin in (("attn.qkv", b.qkv), ("attn.proj", b.proj), ("mlp.linear_fc1", b.fc1), ("mlp.linear_fc2", b.fc2)):
+                yield f"{p}.{nm}.weight", lin.weight
+                yield f"{p}.{nm}.bias", lin.bias
+        for nm, mg in [("merger", self.merger)] + [(f"deepstack_merger_list.{i}", m) for i, m in enumerate(self.deepstack)]:
+            yield f"{nm}.norm.weight", mg.norm.weight
+            yield f"{nm}.norm.bias", mg.norm.bias
+            for sub, lin in (("linear_fc1", mg.fc1), ("linear_fc2", mg.fc2)):
+                yield f"{nm}.{sub}.weight", lin.weight
+                yield f"{nm}.{sub}.bias", lin.bias
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        params = dict(self.named_parameters())
+        loaded = set()
+        for name, w in weights:
+            if name == "patch_embed.proj.weight":
+                w = w.reshape(w.shape[0], -1)
+            if name in params:
+                params[name].copy_(w.to(params[name].dtype))
+                loaded.add(name)
         return loaded

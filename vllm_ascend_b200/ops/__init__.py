@@ -74,6 +74,22 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float,
     return out.view(x.shape), residual
 
 
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """LayerNorm over the last dimension (vision-tower blocks and mergers)."""
+    H = x.shape[-1]
+    if not _use_native(x) or H % 8 or H > 32768:
+        return ref.layer_norm(x, weight, bias, eps)
+    x2 = x.reshape(-1, H) if x.stride(-1) == 1 else x.contiguous().view(-1, H)
+    if x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], H), dtype=x.dtype, device=x.device)
+    rc = _native.lib().b200_layer_norm(x2.data_ptr(), weight.data_ptr(), _native.ptr(bias), out.data_ptr(),
+                                       x2.shape[0], H, eps, x2.stride(0), out.stride(0), _native.stream_ptr())
+    _native.check(rc, "layer_norm")
+    launch_counter[0] += 1
+    return out.view(x.shape)
+
+
 def silu_and_mul(x: torch.Tensor, limit: float = 0.0,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if not _use_native(x):

@@ -364,6 +364,11 @@ def block_fp8_linear(x: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, bl
 
 
 # ---------------------------------------------------------------- more activations / gated norm
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float) -> torch.Tensor:
+    return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), None if bias is None else bias.float(),
+                        eps).to(x.dtype)
+
+
 def activation(x: torch.Tensor, kind: str, gated: bool = False, alpha: float = 1.702, limit: float = 7.0):
     """kind: gelu | gelu_tanh | quick_gelu | swiglu_oai.  gated: x = [gate | up]."""
     if gated:
