@@ -121,3 +121,47 @@ def test_finegrained_tp_over_dp_replicas_matches_single_rank(preset):
     got = _run(preset, 2, 1, fg=fg)
     want = _run(preset, 1, 1)
     assert len(got) == 3 and sorted(got.values()) == sorted(want)
+
+
+SUSPEND_WORKER = textwrap.dedent("""
+    import json, os, sys
+    import numpy as np
+    sys.path.insert(0, {root!r})
+    from vllm_ascend_b200.config import get_model_config
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    from vllm_ascend_b200.parallel import state as pstate
+    cfg = get_model_config("tiny-moe")
+    llm = LLM(cfg, device="cpu", tensor_parallel_size=2, enable_expert_parallel=True, max_model_len=128, max_num_seqs=4,
+              max_num_batched_tokens=32, block_size=16)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(3)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    before = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    tp = pstate.get_tp_group()
+    destroyed = pstate.suspend_groups()
+    assert destroyed >= 2 and tp.device_group is None and pstate.groups_suspended()
+    assert pstate.suspend_groups() == 0
+    restored = pstate.restore_groups()
+    assert restored == destroyed and tp.device_group is not None and pstate.get_tp_group() is tp
+    after = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    if int(os.environ.get("RANK", "0")) == 0:
+        print("RESULT " + json.dumps([before, after, destroyed]), flush=True)
+    llm.shutdown()
+    sys.stdout.flush()
+    os._exit(0)
+""")
+
+
+def test_groups_destroyed_for_sleep_come_back_in_the_same_coordinators():
+    """The sleep path with extra cleanup destroys every model-parallel communicator and wake-up
+    re-creates them inside the coordinator objects the layers already hold."""
+    script = SUSPEND_WORKER.format(root=ROOT)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="2", OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, "-c", script], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, e[-3000:]
+    before, after, destroyed = json.loads([l for l in outs[0][0].splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert before == after and destroyed >= 2

@@ -3,8 +3,9 @@
 level 1: weights are offloaded to pinned host memory, the KV cache is discarded;
 level 2: everything is discarded, only module buffers (rotary tables, norm-free
 state) are kept on the host — the two levels of vllm_ascend/worker/worker.py:221-273.
-With ``rl_config.sleep_mode_extra_cleanup`` the captured graphs are dropped before
-sleeping and re-captured on wake-up (vllm_ascend/device_allocator/sleep_mem_optimized.py:34-186).
+With ``rl_config.sleep_mode_extra_cleanup`` the captured graphs are dropped and the model-parallel
+communicators destroyed before sleeping; wake-up re-creates the communicators and re-captures the
+graphs (vllm_ascend/device_allocator/sleep_mem_optimized.py:34-186).
 """
 from __future__ import annotations
 
@@ -26,6 +27,8 @@ def sleep(engine, level: int = 1) -> int:
     if get_b200_config().rl_config.sleep_mode_extra_cleanup:
         runner.drop_graphs()
         engine._recapture_on_wake = True
+        from ..parallel import state as pstate
+        pstate.suspend_groups()
     alloc = VmmAllocator.get_instance()
     freed = alloc.sleep(offload_tags=("weights",) if level == 1 else ())
     engine.sleep_level = level
@@ -42,6 +45,8 @@ def wake_up(engine, tags: Optional[list[str]] = None) -> int:
                 t.zero_()
         engine.scheduler.pool.reset_prefix_cache()
     if getattr(engine, "_recapture_on_wake", False) and not alloc.sleeping_tags:
+        from ..parallel import state as pstate
+        pstate.restore_groups()
         engine.runner.capture_graphs()
         engine._recapture_on_wake = False
     if not alloc.sleeping_tags:

@@ -173,6 +173,11 @@ def finegrained_rank_lists(world_size: int, tp: int, pp: int, dp: int, size: int
     return out
 
 
+# every multi-rank group this process created, in creation order: what suspend / restore replays
+_RECORDS: list = []
+_SUSPENDED = False
+
+
 def _make(name: str, lists: Sequence[Sequence[int]], rank: int, backend: str,
           timeout: Optional[timedelta]) -> GroupCoordinator:
     mine = None
@@ -187,7 +192,59 @@ def _make(name: str, lists: Sequence[Sequence[int]], rank: int, backend: str,
         if rank in ranks:
             mine = GroupCoordinator(name, ranks, ranks.index(rank), dg, cg)
     assert mine is not None, f"rank {rank} not in any {name} group"
+    _RECORDS.append((mine, [list(r) for r in lists], rank, backend, timeout))
     return mine
+
+
+def suspend_groups() -> int:
+    """Destroys the device communicators of all model-parallel groups (their buffers are device
+    memory a sleeping engine gives back); the coordinators stay and are refilled by
+    ``restore_groups``.  Collective: every rank calls it at the same point, with no collective in
+    flight.  The host-side (gloo) companions of NCCL groups are kept.  Returns how many
+    communicators this rank destroyed.  Same step as the reference's optimised sleep
+    (vllm_ascend/device_allocator/sleep_mem_optimized.py:34-186 destroys the process groups before
+    the allocator releases memory and re-creates them on wake-up)."""
+    global _SUSPENDED
+    if _SUSPENDED:
+        return 0
+    n = 0
+    for mine, _, _, _, _ in _RECORDS:
+        dg = mine.device_group
+        if dg is None:
+            continue
+        same = mine.cpu_group is dg
+        dist.destroy_process_group(dg)
+        mine.device_group = None
+        if same:
+            mine.cpu_group = None
+        n += 1
+    _SUSPENDED = True
+    return n
+
+
+def restore_groups() -> int:
+    """Re-creates the communicators destroyed by ``suspend_groups`` in their original order and
+    puts them back into the same coordinator objects (layers keep their references)."""
+    global _SUSPENDED
+    if not _SUSPENDED:
+        return 0
+    n = 0
+    for mine, lists, rank, backend, timeout in _RECORDS:
+        for ranks in lists:
+            if len(ranks) == 1:
+                continue
+            dg = dist.new_group(ranks, backend=backend, timeout=timeout)
+            if rank in ranks:
+                mine.device_group = dg
+                if mine.cpu_group is None:
+                    mine.cpu_group = dg
+                n += 1
+    _SUSPENDED = False
+    return n
+
+
+def groups_suspended() -> bool:
+    return _SUSPENDED
 
 
 def init_distributed(backend: Optional[str] = None, timeout_s: Optional[float] = None) -> tuple[int, int, int]:
@@ -224,6 +281,7 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, dcp: int = 
     if backend is None:
         backend = dist.get_backend()
     timeout = timedelta(seconds=timeout_s) if timeout_s else None
+    _RECORDS.clear()
     lists = group_rank_lists(world_size, tp, pp, dp, pcp)
     st = ParallelState()
     st.world = _make("world", [list(range(world_size))], rank, backend, timeout)
@@ -249,8 +307,10 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, dcp: int = 
 
 
 def destroy_model_parallel() -> None:
-    global _STATE
+    global _STATE, _SUSPENDED
     _STATE = ParallelState()
+    _RECORDS.clear()
+    _SUSPENDED = False
 
 
 def get_state() -> ParallelState:
