@@ -157,3 +157,72 @@ def test_expert_lora_matches_merged_expert_weights():
     assert [toks[0], toks[2]] == oracle(ad, [0, 2])
     assert [toks[1]] == oracle(None, [1])
     assert toks[0] != oracle(None, [0])[0]
+
+
+_EP_WORKER = """
+import json, os, sys
+import numpy as np, torch
+sys.path.insert(0, {root!r})
+from vllm_ascend_b200 import LLM, SamplingParams
+from vllm_ascend_b200.lora.manager import LoRARequest
+ep = int(os.environ.get("WORLD_SIZE", "1")) > 1
+llm = LLM("tiny-moe", device="cpu", seed=0, block_size=16, max_model_len=128, max_num_seqs=8, enable_lora=True,
+          max_loras=2, max_lora_rank=8, tensor_parallel_size=2 if ep else 1, enable_expert_parallel=ep)
+cfg = llm.cfg.model
+mgr = llm.engine.runner.lora_manager
+assert mgr.moe_layers
+if ep:
+    ms = next(iter(mgr.moe_layers.values()))
+    assert ms.num_experts == cfg.num_experts // 2 and not ms.sharded and ms.expert_map.count(-1) == cfg.num_experts // 2
+g = torch.Generator().manual_seed(5)
+rank, alpha = 4, 8.0
+H, I = cfg.hidden_size, cfg.moe_intermediate_size
+ad = dict()
+for li in range(cfg.num_hidden_layers):
+    for e in range(cfg.num_experts):
+        base = "base_model.model.model.layers.%d.mlp.experts.%d" % (li, e)
+        for name, (k, n) in (("gate_proj", (H, I)), ("up_proj", (H, I)), ("down_proj", (I, H))):
+            ad[base + "." + name + ".lora_A.weight"] = torch.randn(rank, k, generator=g) * 0.3
+            ad[base + "." + name + ".lora_B.weight"] = torch.randn(n, rank, generator=g) * 0.3
+req = LoRARequest("moe", 7, tensors=ad, rank=rank, alpha=alpha)
+rng = np.random.default_rng(1)
+prompts = [rng.integers(1, 500, size=n).tolist() for n in (23, 9, 31)]
+sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+toks = [o.outputs[0].token_ids for o in llm.generate(prompts, sp, lora_request=[req, None, req])]
+if int(os.environ.get("RANK", "0")) == 0:
+    rt = llm.engine.runner.moe_runtime
+    print("RESULT " + json.dumps([toks, dict((k.name, v) for k, v in rt.counts.items()) if rt else None]), flush=True)
+llm.shutdown()
+sys.stdout.flush()
+os._exit(0)
+"""
+
+
+@pytest.mark.parametrize("method", ["allgather", "alltoall"])
+def test_expert_lora_under_expert_parallelism_matches_single_rank(method):
+    """Each EP rank keeps the adapters of its own experts; the adapter slot travels with the token on
+    both the all-gather and the all-to-all path."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = _EP_WORKER.format(root=root)
+
+    def run(world):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
+                   OMP_NUM_THREADS="2", VLLM_B200_MOE_COMM=method)
+        procs = [subprocess.Popen([sys.executable, "-c", script], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(world)]
+        outs = [p.communicate(timeout=300) for p in procs]
+        for p, (o, e) in zip(procs, outs):
+            assert p.returncode == 0, e[-3000:]
+        return json.loads([l for l in outs[0][0].splitlines() if l.startswith("RESULT ")][-1][7:])
+    single, _ = run(1)
+    ep, counts = run(2)
+    assert ep == single
+    assert counts[method.upper()] > 0

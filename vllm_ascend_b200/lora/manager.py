@@ -69,14 +69,16 @@ class LoRAManager:
             mlp = getattr(L, "mlp", None)
             if mlp is not None and hasattr(mlp, "gate_up_proj"):
                 mods["gate_up_proj"], mods["down_proj"] = mlp.gate_up_proj, mlp.down_proj
-            if mlp is not None and hasattr(mlp, "w13") and getattr(mlp, "ep", None) is None:
+            if mlp is not None and hasattr(mlp, "w13") and self._experts_supported(mlp):
                 from .moe import MoELoRAState
                 E, two_i, H = mlp.w13.shape
                 Il = two_i // 2
                 z = lambda *shape: torch.zeros(shape, dtype=self.dtype, device=self.device)     # noqa: E731
                 n = self.max_loras * E
+                ep = getattr(mlp, "ep", None) is not None
+                emap = mlp.expert_map.tolist() if ep and getattr(mlp, "expert_map", None) is not None else None
                 mlp.lora = MoELoRAState(z(n, 2 * r, H), z(n, Il, r), z(n, Il, r), z(n, r, Il), z(n, H, r), E, r,
-                                        self.punica)
+                                        self.punica, expert_map=emap, sharded=not ep)
                 self.moe_layers[L.idx] = mlp.lora
             for name, lin in mods.items():
                 if lin is None or getattr(lin, "weight", None) is None:
@@ -89,6 +91,16 @@ class LoRAManager:
                     output_slices=slices, rank=r, punica=self.punica)
                 lin.lora = st
                 self.layers[(L.idx, name)] = st
+
+    @staticmethod
+    def _experts_supported(mlp) -> bool:
+        """Expert adapters under expert parallelism need every EP rank to see the same batch (the
+        slot vector travels with the tokens and all ranks must agree on the path): engines without
+        data parallelism and without redundant expert replicas."""
+        if getattr(mlp, "ep", None) is None:
+            return True
+        from ..parallel import state as pstate
+        return pstate.get_dp_group().world_size == 1 and getattr(mlp, "log2phy", None) is None
 
     # ------------------------------------------------------------------ registry
     def list(self) -> set:
@@ -177,9 +189,14 @@ class LoRAManager:
                 if ms is None:
                     continue
                 e, proj, which = int(me.group(2)), me.group(3), me.group(4)
+                if ms.expert_map is not None:
+                    e = ms.expert_map[e] if e < len(ms.expert_map) else -1
+                    if e < 0:
+                        continue                       # another rank's expert
                 row = slot * ms.num_experts + e
                 w = w.to(self.device, self.dtype)
                 Il = ms.b_gate.shape[1]
+                tr = comm.rank if ms.sharded else 0
                 if proj in ("gate_proj", "up_proj"):
                     off = 0 if proj == "gate_proj" else ms.rank
                     if which == "A":                   # [r, H]

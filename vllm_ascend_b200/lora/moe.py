@@ -7,8 +7,12 @@ adapter on a MoE layer take the expert-by-expert path: GEMM1 (unfused, the delta
 before SiLU-mul), delta, SiLU-mul, GEMM2, delta, weighted sum.  Tensor-parallel experts shard
 B of gate / up by rows and A of down by columns like the base weights, so the partial sums the
 all-reduce adds up include the adapter's contribution.  Role of the reference's MoE LoRA for its
-all-gather / all-to-all MoE paths (vllm_ascend/lora/fused_moe.py, lora/quant_moe.py); expert
-parallel engines do not take expert adapters here.
+all-gather / all-to-all MoE paths (vllm_ascend/lora/fused_moe.py, lora/quant_moe.py).
+
+Under expert parallelism each rank stores the adapters of its own experts only (whole, not
+sliced), and the adapter slot of every token travels with the token: the all-gather path gathers
+the slot vector next to the activations, the all-to-all path sends it with the rows.  Steps that
+carry an adapter leave the fused dispatch kernel for those two paths.
 """
 from __future__ import annotations
 
@@ -27,9 +31,11 @@ class MoELoRAState:
     b_up: torch.Tensor         # [slots * E, I_local, r]
     a2: torch.Tensor           # [slots * E, r, I_local]
     b2: torch.Tensor           # [slots * E, H, r]
-    num_experts: int
+    num_experts: int           # experts stored here (the local ones under expert parallelism)
     rank: int
     punica: object
+    expert_map: object = None  # global expert id -> local row (list, -1 = elsewhere); None = identity
+    sharded: bool = True       # expert weights are TP-sliced along I (False under expert parallelism)
 
     def zero_slot(self, slot: int) -> None:
         E = self.num_experts
@@ -38,7 +44,8 @@ class MoELoRAState:
 
 
 def fused_experts_lora(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
-                       topk_ids: torch.Tensor, expert_map, st: MoELoRAState) -> torch.Tensor:
+                       topk_ids: torch.Tensor, expert_map, st: MoELoRAState, slots=None) -> torch.Tensor:
+    """slots: adapter slot of every row of x (defaults to this step's local token slots)."""
     T, H = x.shape
     E, r = st.num_experts, st.rank
     I = w13.shape[1] // 2
@@ -46,7 +53,8 @@ def fused_experts_lora(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, top
     ids = topk_ids.long()
     if expert_map is not None:
         ids = expert_map.long()[ids]
-    slots = st.punica.token_slots[:T]
+    if slots is None:
+        slots = st.punica.token_slots[:T]
     for e in range(w13.shape[0]):
         tok, k = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:

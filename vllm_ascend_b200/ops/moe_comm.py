@@ -92,6 +92,18 @@ class MoERuntime:
         if x.is_cuda and method != MoECommType.FUSED and torch.cuda.is_current_stream_capturing():
             raise RuntimeError(f"MoE path {method.name} cannot be captured into a CUDA graph "
                                f"({x.shape[0]} tokens, fused capacity {self.capacity})")
+        lora = getattr(block, "lora", None)
+        if lora is not None and lora.punica.any_active and block.quant is None:
+            # adapter steps: the slot of every token travels with it, which the fused kernel's
+            # packed pools do not carry
+            if method == MoECommType.FUSED:
+                method = MoECommType.ALLGATHER
+            self.last_method = method
+            self.counts[method] += 1
+            slots = lora.punica.token_slots[:x.shape[0]]
+            if method == MoECommType.ALLGATHER:
+                return self._allgather(block, x, topk_w, topk_ids, n_max, lora, slots)
+            return self._alltoall(block, x, topk_w, topk_ids, lora, slots)
         self.last_method = method
         self.counts[method] += 1
         if method == MoECommType.FUSED and self.fused is not None:
@@ -101,10 +113,12 @@ class MoERuntime:
         return self._alltoall(block, x, topk_w, topk_ids)
 
     # ------------------------------------------------------------------ all-gather path
-    def _allgather(self, block, x, topk_w, topk_ids, n_max: int) -> torch.Tensor:
+    def _allgather(self, block, x, topk_w, topk_ids, n_max: int, lora=None, slots=None) -> torch.Tensor:
         ep = self.ep
         T, H = x.shape
         pad = n_max - T
+        if lora is not None:
+            slots = torch.cat([slots, slots.new_full((pad,), -1)]) if pad else slots
         if pad:
             x = torch.cat([x, x.new_zeros(pad, H)])
             topk_w = torch.cat([topk_w, topk_w.new_zeros(pad, topk_w.shape[1])])
@@ -113,7 +127,12 @@ class MoERuntime:
         xg = ep.all_gather(x, 0)
         wg = ep.all_gather(topk_w, 0)
         ig = ep.all_gather(topk_ids, 0)
-        y = fused_moe.fused_experts(xg, block.w13, block.w2, wg, ig, block.expert_map, block.quant)
+        if lora is not None:
+            from ..lora.moe import fused_experts_lora
+            y = fused_experts_lora(xg, block.w13, block.w2, wg, ig, block.expert_map, lora,
+                                   slots=ep.all_gather(slots.contiguous(), 0))
+        else:
+            y = fused_moe.fused_experts(xg, block.w13, block.w2, wg, ig, block.expert_map, block.quant)
         if x.is_cuda:
             y = ep.reduce_scatter(y, 0)
         else:   # gloo has no reduce-scatter
@@ -121,7 +140,7 @@ class MoERuntime:
         return y[:T]
 
     # ------------------------------------------------------------------ all-to-all-v path
-    def _alltoall(self, block, x, topk_w, topk_ids) -> torch.Tensor:
+    def _alltoall(self, block, x, topk_w, topk_ids, lora=None, slots=None) -> torch.Tensor:
         ep = self.ep
         n, E_local = ep.world_size, block.E_local
         T, H = x.shape
@@ -142,7 +161,13 @@ class MoERuntime:
         recv_e = ep.all_to_all_single(send_e, out_splits, in_splits)
         # local experts on the received rows (each row is one (token, expert) pair, weight 1)
         R = recv_x.shape[0]
-        if R > 0:
+        recv_s = ep.all_to_all_single(slots[send_tok].contiguous(), out_splits, in_splits) if lora is not None else None
+        if R > 0 and lora is not None:
+            from ..lora.moe import fused_experts_lora
+            ones = torch.ones(R, 1, dtype=topk_w.dtype, device=x.device)
+            y = fused_experts_lora(recv_x, block.w13, block.w2, ones, recv_e.view(R, 1).to(torch.int32),
+                                   block.expert_map, lora, slots=recv_s)
+        elif R > 0:
             ones = torch.ones(R, 1, dtype=topk_w.dtype, device=x.device)
             y = fused_moe.fused_experts(recv_x, block.w13, block.w2, ones,
                                         recv_e.view(R, 1).to(torch.int32), block.expert_map,
