@@ -145,3 +145,80 @@ def test_fp8_model_uses_fused_producers_and_matches_unfused(monkeypatch):
     n_plain = ops.launch_counter[0] - c0
     assert fused == plain
     assert n_fused < n_plain          # fewer launches: the quant passes disappeared
+
+
+@pytest.mark.parametrize("T,H", [(300, 4096), (5, 128), (64, 12288)])
+def test_quant_fp8_per_token_kernel(T, H):
+    torch.manual_seed(T)
+    x = (torch.randn(T, H, device=DEV) * torch.rand(T, 1, device=DEV) * 3).bfloat16()
+    c0 = _native.launch_counter[0]
+    q, s = ops.quant_fp8_per_token(x)
+    assert _native.launch_counter[0] == c0 + 1
+    eq, es = ref.quant_fp8_per_token(x.cpu())
+    assert torch.allclose(s.cpu(), es, rtol=1e-6)
+    # identical except where the product lands on a rounding boundary of e4m3
+    diff = (q.float().cpu() - eq.float()).abs()
+    assert (diff > 0).float().mean() < 1e-3 and (diff <= 0.13 * eq.float().abs() + 1e-3).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 512, 1024), (4096, 4096, 4096), (5, 1536, 7168), (777, 136, 256)])
+def test_fp8_channel_gemm(M, N, K):
+    torch.manual_seed(M)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = torch.randn(N, K, device=DEV) * 0.1 * (torch.rand(N, 1, device=DEV) + 0.2)
+    bias = torch.randn(N, device=DEV).bfloat16()
+    ws = (w.abs().amax(dim=1) / 448.0).clamp_min(1e-10)
+    w8 = (w / ws.unsqueeze(1)).to(torch.float8_e4m3fn)
+    got = schemes.fp8_channel_linear(x, w8, ws, bias)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    xq, xs = ref.quant_fp8_per_token(x)
+    exp = (xq.float() @ w8.float().t()) * xs.unsqueeze(1) * ws.unsqueeze(0) + bias.float()
+    assert (got.float() - exp).abs().max() < 0.01 * exp.abs().max() + 0.02
+    full = x.float() @ w.t() + bias.float()
+    assert (got.float() - full).abs().max() < 0.08 * full.abs().max()
+
+
+def test_fp8_channel_linear_scheme_and_experts_on_gpu():
+    from vllm_ascend_b200 import quantization as Q
+    from vllm_ascend_b200.models.layers import Linear
+    torch.manual_seed(3)
+    lin = Linear((torch.randn(384, 512, device=DEV) * 0.1).bfloat16(), (torch.randn(384, device=DEV) * 0.1).bfloat16())
+    x = torch.randn(2, 33, 512, device=DEV).bfloat16()
+    exp = x.float() @ lin.weight.float().t() + lin.bias.float()
+    sch = Q.get_scheme_class("W8A8FP8_DYNAMIC", "linear")()
+    sch.convert(lin)
+    lin.quant = Q.LinearMethod(sch)
+    c0 = _native.launch_counter[0]
+    got = lin(x)
+    assert _native.launch_counter[0] == c0 + 2            # per-token quant + GEMM, no fallback
+    assert got.shape == exp.shape and (got.float() - exp).abs().max() < 0.08 * exp.abs().max()
+
+    T, E, k, H, I = 200, 8, 2, 512, 256
+    xt = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    blk = type("B", (), {})()
+    blk.w13 = torch.randn(E, 2 * I, H, device=DEV) * 0.05
+    blk.w2 = torch.randn(E, H, I, device=DEV) * 0.05
+    tw, ids = fused_moe.gating_topk_ref(torch.randn(T, E, device=DEV), k)
+    want = fused_moe.fused_experts_ref(xt.float(), blk.w13, blk.w2, tw, ids, None)
+    ms = Q.get_scheme_class("W8A8FP8_DYNAMIC", "moe")()
+    ms.convert(blk)
+    assert blk.w13.dtype == torch.float8_e4m3fn and blk.w13_scale.shape == (E, 2 * I)
+    got = ms.apply_experts(xt, blk.w13, blk.w2, tw, ids, None)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    assert (got.float() - want).abs().max() < 0.1 * want.abs().max() + 0.02
+    # local-expert subset (expert parallel layout): experts 2..5 live here
+    emap = torch.full((E,), -1, dtype=torch.int32, device=DEV)
+    emap[2:6] = torch.arange(4, dtype=torch.int32, device=DEV)
+    sub = type("B", (), {})()
+    sub.w13, sub.w2, sub.w13_scale, sub.w2_scale = blk.w13[2:6].contiguous(), blk.w2[2:6].contiguous(), \
+        blk.w13_scale[2:6].contiguous(), blk.w2_scale[2:6].contiguous()
+    ms2 = Q.get_scheme_class("W8A8FP8_DYNAMIC", "moe")()
+    ms2.block_ref = sub
+    part = ms2.apply_experts(xt, sub.w13, sub.w2, tw, ids, emap)
+    mask = ((ids >= 2) & (ids < 6)).to(tw.dtype)
+    want_part = fused_moe.fused_experts_ref(xt.float(), (blk.w13[2:6].float() * blk.w13_scale[2:6].unsqueeze(-1)),
+                                            (blk.w2[2:6].float() * blk.w2_scale[2:6].unsqueeze(-1)), tw * mask,
+                                            (ids - 2).clamp(0, 3), None)
+    assert (part.float() - want_part).abs().max() < 0.1 * want_part.abs().max() + 0.02

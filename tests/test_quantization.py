@@ -15,7 +15,7 @@ def test_registry_has_linear_and_moe_schemes():
     have = Q.registered()
     for key in [("FP8_BLOCK", "linear"), ("W8A8_DYNAMIC", "linear"), ("W8A8", "linear"),
                 ("W8A8FP8_DYNAMIC", "linear"), ("W4A16", "linear"), ("W8A16", "linear"),
-                ("FP8_BLOCK", "moe"), ("W8A8_DYNAMIC", "moe")]:
+                ("FP8_BLOCK", "moe"), ("W8A8_DYNAMIC", "moe"), ("W8A8FP8_DYNAMIC", "moe")]:
         assert key in have
     with pytest.raises(ValueError):
         Q.get_scheme_class("W3A3", "linear")
@@ -107,7 +107,7 @@ def test_moe_schemes_for_compressed_expert_weights():
     ids = torch.randint(0, E, (T, 2))
     wts = torch.rand(T, 2)
     want = fused_experts_ref(x, w13, w2, wts, ids, None)
-    for name, tol in (("W8A8_MXFP8", 0.08), ("W4A4_MXFP4", 0.5), ("W4A8_DYNAMIC", 0.3), ("W4A16", 0.3),
+    for name, tol in (("W8A8FP8_DYNAMIC", 0.08), ("W8A8_MXFP8", 0.08), ("W4A4_MXFP4", 0.5), ("W4A8_DYNAMIC", 0.3), ("W4A16", 0.3),
                       ("W4A16_MXFP4", 0.5), ("W4A8_MXFP", 0.5)):
         blk = type("B", (), {})()
         blk.w13, blk.w2 = w13.clone(), w2.clone()

@@ -33,6 +33,7 @@ _SIGNATURES = {
     "b200_layer_norm": [P, P, P, P, L, I, F, L, L, P],
     "b200_qknorm_mrope_kvwrite": [P, L, P, L, P, P, I, P, P, F, P, P, P, I, I, I, I, L, I, I, P, P],
     "b200_quant_fp8_group128": [P, P, P, L, I, I, P],
+    "b200_quant_fp8_per_token": [P, L, P, P, L, I, P],
     "b200_activation": [P, P, L, I, I, I, F, F, P],
     "b200_rms_norm_gated": [P, P, P, P, L, I, F, I, P],
     "b200_rms_norm_quant_fp8": [P, P, P, P, P, L, I, F, I, L, P],

@@ -342,6 +342,58 @@ __global__ void quant_fp8_group128_kernel(const __nv_bfloat16* __restrict__ x,
 }
 
 
+// ---------------------------------------------------------------- fp8 per-token quant
+// x: [T, H] bf16 (row stride x_stride) -> q: [T, H] e4m3, scales: [T] fp32 (amax / 448).
+// One CTA per row, the row stays in registers between the amax pass and the store.
+template <int VEC_PER_THREAD>
+__global__ void quant_fp8_per_token_kernel(const __nv_bfloat16* __restrict__ x, long x_stride,
+                                           __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scales,
+                                           int H) {
+  const long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * x_stride);
+  const int nvec = H >> 3;
+  float vals[VEC_PER_THREAD][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC_PER_THREAD; i++) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      const uint4 a = xr[v];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float2 f = unpack_bf16x2(aw[j]);
+        vals[i][2 * j] = f.x;
+        vals[i][2 * j + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+  }
+  __shared__ float red[33];
+  amax = warp_reduce_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+    t = warp_reduce_max(t);
+    if (threadIdx.x == 0) red[32] = fmaxf(t, 1e-10f) / 448.f;
+  }
+  __syncthreads();
+  const float scale = red[32];
+  if (threadIdx.x == 0) scales[row] = scale;
+  uint2* qr = reinterpret_cast<uint2*>(q + row * (long)H);
+#pragma unroll
+  for (int i = 0; i < VEC_PER_THREAD; i++) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      __nv_fp8_e4m3 o[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) o[j] = __nv_fp8_e4m3(__fdiv_rn(vals[i][j], scale));   // as x / scale in fp32
+      qr[v] = *reinterpret_cast<uint2*>(o);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- LayerNorm
 // One CTA per row, row held in registers: mean, then the variance around it, then
 // out <- (x - mean) * rstd * w + b.  Used by vision-tower blocks and mergers.
@@ -568,6 +620,24 @@ B200_API int b200_rope_table(void* x, long x_stride, const void* cos_t, const vo
   const long warps = N * H;
   rope_table_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(
       (__nv_bfloat16*)x, x_stride, (const float*)cos_t, (const float*)sin_t, N, H, D, half);
+  return B200_CHECK_LAUNCH();
+}
+
+B200_API int b200_quant_fp8_per_token(const void* x, long x_stride, void* q, void* scales, long T,
+                                      int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((H & 7) || (x_stride & 7)) return 9120;
+  const int nvec = H >> 3;
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  const int per = (nvec + threads - 1) / threads;
+  auto X = (const __nv_bfloat16*)x;
+  auto Q = (__nv_fp8_e4m3*)q;
+  auto S = (float*)scales;
+  if (per <= 1) quant_fp8_per_token_kernel<1><<<(unsigned)T, threads, 0, stream>>>(X, x_stride, Q, S, H);
+  else if (per <= 2) quant_fp8_per_token_kernel<2><<<(unsigned)T, threads, 0, stream>>>(X, x_stride, Q, S, H);
+  else if (per <= 4) quant_fp8_per_token_kernel<4><<<(unsigned)T, threads, 0, stream>>>(X, x_stride, Q, S, H);
+  else return 9121;
   return B200_CHECK_LAUNCH();
 }
 

@@ -38,6 +38,11 @@ struct Fp8Params {
   int* status;
   int tiles_m, tiles_n;
   int num_kb;
+  // per-channel mode (dynamic per-token x per-output-channel scales, constant along K):
+  // row_scale [M], col_scale [groups][N]; the K blocks are summed unscaled and the product of
+  // the two scales is applied once in the epilogue
+  const float* row_scale;
+  const float* col_scale;
   // grouped
   const int* group_offsets;
   int num_groups;
@@ -181,16 +186,17 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
       f8_tile(p, grp_tiles, t, c);
       const int row = c.row0 + q * 32 + lane;
       const bool row_ok = row < c.row_end;
-      const float* as_row = p.a_scale + (size_t)(row_ok ? row : 0) * kblocks;
-      const float* ws_row = p.w_scale + ((size_t)c.group * n_blocks + c.tn) * kblocks;
+      const bool per_channel = p.row_scale != nullptr;
+      const float* as_row = per_channel ? nullptr : p.a_scale + (size_t)(row_ok ? row : 0) * kblocks;
+      const float* ws_row = per_channel ? nullptr : p.w_scale + ((size_t)c.group * n_blocks + c.tn) * kblocks;
       float acc[F8_BN];
 #pragma unroll
       for (int i = 0; i < F8_BN; i++) acc[i] = 0.f;
-      float sc_next = as_row[0] * ws_row[0];
+      float sc_next = per_channel ? 1.f : as_row[0] * ws_row[0];
       for (int kb = 0; kb < num_kb; kb++, it++) {
         const int b = it & 1;
         const float sc = sc_next;
-        if (kb + 1 < num_kb) sc_next = as_row[kb + 1] * ws_row[kb + 1];
+        if (!per_channel && kb + 1 < num_kb) sc_next = as_row[kb + 1] * ws_row[kb + 1];
         if (!mbar_wait(&part_full[b], (it >> 1) & 1u, abort_word)) goto done;
         tc_fence_after();
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * F8_BN;
@@ -208,6 +214,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       if (row_ok) {
         __nv_bfloat16* crow = p.C + (size_t)row * p.ldc;
+        const float rs = per_channel ? p.row_scale[row] : 1.f;
+        const float* cs = per_channel ? p.col_scale + (size_t)c.group * p.N : nullptr;
 #pragma unroll
         for (int g = 0; g < F8_BN / 8; g++) {
           const int col = c.tn * F8_BN + g * 8;
@@ -215,6 +223,13 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
             float v[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) v[j] = acc[g * 8 + j];
+            if (per_channel) {
+              const float4 c0 = *reinterpret_cast<const float4*>(cs + col);
+              const float4 c1 = *reinterpret_cast<const float4*>(cs + col + 4);
+              const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+              for (int j = 0; j < 8; j++) v[j] *= rs * cv[j];
+            }
             if (p.bias) {
               const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -350,6 +365,48 @@ B200_API int b200_grouped_gemm_fp8_block(const void* A8, const void* a_scale, co
   p.M = (int)total_rows; p.N = N; p.K = K; p.ldc = ldc;
   p.a_scale = (const float*)a_scale;
   p.w_scale = (const float*)w_scale;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.group_offsets = (const int*)offsets;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = N;
+  return launch_fp8(A8, W8, p, lda, ldw, total_rows, (long)num_groups * N, stream);
+}
+
+// Per-token x per-channel form (dynamic W8A8 in e4m3): C = row_scale[m] * col_scale[n] * (A8 . W8^T).
+// row_scale [M] fp32, col_scale [N] fp32 (16-byte aligned, N multiple of 8).
+B200_API int b200_gemm_fp8_channel(const void* A8, const void* row_scale, const void* W8,
+                                   const void* col_scale, void* C, const void* bias, int M, int N,
+                                   int K, int lda, int ldw, int ldc, int* status,
+                                   cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 128) || (N & 7) || (lda & 15) || (ldw & 15) || (ldc & 7) || ((uintptr_t)col_scale & 15))
+    return 9100;
+  Fp8Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.row_scale = (const float*)row_scale;
+  p.col_scale = (const float*)col_scale;
+  p.C = (__nv_bfloat16*)C;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.status = status;
+  return launch_fp8(A8, W8, p, lda, ldw, M, N, stream);
+}
+
+// Grouped per-channel form: expert e's W8[e] [N,K] with col_scale[e] [N].
+B200_API int b200_grouped_gemm_fp8_channel(const void* A8, const void* row_scale, const void* W8,
+                                           const void* col_scale, void* C, const void* offsets,
+                                           int num_groups, long total_rows, int N, int K, int lda,
+                                           int ldw, int ldc, int* status, cudaStream_t stream) {
+  if (total_rows <= 0 || N <= 0 || num_groups <= 0) return 0;
+  if ((K % 128) || (N & 7) || (lda & 15) || (ldw & 15) || (ldc & 7) || ((uintptr_t)col_scale & 15))
+    return 9100;
+  if (num_groups > F8_MAX_GROUPS) return 9131;
+  Fp8Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = (int)total_rows; p.N = N; p.K = K; p.ldc = ldc;
+  p.row_scale = (const float*)row_scale;
+  p.col_scale = (const float*)col_scale;
   p.C = (__nv_bfloat16*)C;
   p.status = status;
   p.group_offsets = (const int*)offsets;

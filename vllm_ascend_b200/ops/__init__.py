@@ -497,6 +497,23 @@ def quant_fp8_group128(x: torch.Tensor, pow2_scale: bool = False):
     return q, s
 
 
+def quant_fp8_per_token(x: torch.Tensor):
+    """[T, H] -> (e4m3 [T, H], scale [T] fp32 = row amax / 448): the dynamic per-token activation
+    quantisation of the per-channel W8A8 schemes."""
+    if not _use_native(x) or x.shape[-1] % 8:
+        return ref.quant_fp8_per_token(x)
+    if x.stride(-1) != 1 or x.stride(0) % 8:
+        x = x.contiguous()
+    T, H = x.shape
+    q = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((T,), dtype=torch.float32, device=x.device)
+    rc = _native.lib().b200_quant_fp8_per_token(x.data_ptr(), x.stride(0), q.data_ptr(), s.data_ptr(), T, H,
+                                                _native.stream_ptr())
+    _native.check(rc, "quant_fp8_per_token")
+    launch_counter[0] += 1
+    return q, s
+
+
 class QuantAct:
     """A block-scaled fp8 activation: values [T, H] e4m3 and scales [T, H / 128] fp32, produced by
     a fused norm / activation kernel and consumed by the fp8 GEMM without an extra quant pass."""

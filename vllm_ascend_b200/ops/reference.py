@@ -364,6 +364,12 @@ def block_fp8_linear(x: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, bl
 
 
 # ---------------------------------------------------------------- more activations / gated norm
+def quant_fp8_per_token(x: torch.Tensor):
+    xf = x.float()
+    scale = (xf.abs().amax(dim=-1) / 448.0).clamp_min(1e-10)
+    return (xf / scale.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn), scale
+
+
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float) -> torch.Tensor:
     return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), None if bias is None else bias.float(),
                         eps).to(x.dtype)

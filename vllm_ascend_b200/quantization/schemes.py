@@ -113,6 +113,9 @@ def _declare_native():
     _native.register_signature("b200_gemm_fp8_block", [P, P, P, P, P, P, I, I, I, I, I, I, P, P])
     _native.register_signature("b200_grouped_gemm_fp8_block",
                                [P, P, P, P, P, P, I, L, I, I, I, I, I, P, P])
+    _native.register_signature("b200_gemm_fp8_channel", [P, P, P, P, P, P, I, I, I, I, I, I, P, P])
+    _native.register_signature("b200_grouped_gemm_fp8_channel",
+                               [P, P, P, P, P, P, I, L, I, I, I, I, I, P, P])
 
 
 _declare_native()
@@ -135,6 +138,40 @@ def fp8_block_linear(x: Optional[torch.Tensor], w8: torch.Tensor, w_scale: torch
         _native.ptr(bias), M, N, K, xq.stride(0), w8.stride(0), out.stride(0),
         _native.status_word(xq.device).data_ptr(), _native.stream_ptr())
     _native.check(rc, "gemm_fp8_block")
+    ops.launch_counter[0] += 1
+    return out
+
+
+def fp8_channel_linear(x: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
+                       bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 activations [M, K] -> dynamic per-token e4m3 quantisation -> tcgen05 GEMM whose epilogue
+    applies row scale x column scale.  w8 [N, K] e4m3, w_scale [N] fp32."""
+    xq, xs = ops.quant_fp8_per_token(x)
+    M, K = xq.shape
+    N = w8.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
+    if M == 0:
+        return out
+    rc = _native.lib().b200_gemm_fp8_channel(
+        xq.data_ptr(), xs.data_ptr(), w8.data_ptr(), w_scale.data_ptr(), out.data_ptr(), _native.ptr(bias),
+        M, N, K, xq.stride(0), w8.stride(0), out.stride(0), _native.status_word(xq.device).data_ptr(),
+        _native.stream_ptr())
+    _native.check(rc, "gemm_fp8_channel")
+    ops.launch_counter[0] += 1
+    return out
+
+
+def grouped_fp8_channel(a8: torch.Tensor, a_scale: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
+                        offsets: torch.Tensor) -> torch.Tensor:
+    """Rows of a8 grouped by expert (offsets [E + 1] int32); w8 [E, N, K] e4m3, w_scale [E, N] fp32."""
+    rows, K = a8.shape
+    E, N = w8.shape[0], w8.shape[1]
+    out = torch.empty((rows, N), dtype=torch.bfloat16, device=a8.device)
+    rc = _native.lib().b200_grouped_gemm_fp8_channel(
+        a8.data_ptr(), a_scale.data_ptr(), w8.data_ptr(), w_scale.data_ptr(), out.data_ptr(), offsets.data_ptr(),
+        E, rows, N, K, a8.stride(0), w8.stride(1), out.stride(0), _native.status_word(a8.device).data_ptr(),
+        _native.stream_ptr())
+    _native.check(rc, "grouped_gemm_fp8_channel")
     ops.launch_counter[0] += 1
     return out
 
@@ -183,8 +220,25 @@ class W8A8DynamicLinear(_PerChannelDynamic):
 
 @register_scheme("W8A8FP8_DYNAMIC", "linear")
 class W8A8Fp8DynamicLinear(_PerChannelDynamic):
+    """e4m3 weights with one scale per output channel, activations quantised per token at run
+    time; on the GPU both steps are native (per-token quant kernel, tcgen05 GEMM with the scale
+    product in its epilogue)."""
     qdtype = FP8
     qmax = FP8_MAX
+
+    def apply(self, layer, x, residual=None, skip_bias=False):
+        K, N = x.shape[-1], layer.weight.shape[0]
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and layer.weight.dtype == FP8 and K % 128 == 0
+                and N % 8 == 0):
+            return super().apply(layer, x, residual, skip_bias)
+        ws = getattr(layer, "_ws_flat", None)
+        if ws is None or ws.data_ptr() != layer.weight_scale.data_ptr():
+            ws = layer._ws_flat = layer.weight_scale.view(-1)
+            if not ws.is_contiguous() or ws.dtype != torch.float32:
+                ws = layer._ws_flat = ws.float().contiguous()
+        y = fp8_channel_linear(x.reshape(-1, K), layer.weight, ws, None if skip_bias else layer.bias)
+        y = y.view(*x.shape[:-1], N)
+        return y + residual if residual is not None else y
 
 
 @register_scheme("W8A8", "linear")
@@ -313,6 +367,60 @@ class W8A8DynamicMoE(MoEScheme):
         w13f = (w13.float() * blk.w13_scale).to(x.dtype)
         w2f = (w2.float() * blk.w2_scale).to(x.dtype)
         return fused_experts_ref(x, w13f, w2f, topk_w, topk_ids, expert_map)
+
+
+@register_scheme("W8A8FP8_DYNAMIC", "moe")
+class W8A8Fp8DynamicMoE(MoEScheme):
+    """Experts in e4m3 with per-channel scales: permute -> per-token quant -> grouped GEMM1 ->
+    SiLU-mul -> per-token quant -> grouped GEMM2 -> weighted combine."""
+
+    def convert(self, block) -> None:
+        def q(w):
+            if w.dtype == FP8:
+                return w, None
+            scale = (w.float().abs().amax(dim=-1, keepdim=True) / FP8_MAX).clamp_min(1e-10)
+            return (w.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8), scale.squeeze(-1).contiguous()
+        w13, s13 = q(block.w13)
+        w2, s2 = q(block.w2)
+        block.w13, block.w2 = w13, w2
+        if s13 is not None:
+            block.w13_scale = s13                    # [E, 2I]
+        if s2 is not None:
+            block.w2_scale = s2                      # [E, H]
+        self.block_ref = block
+
+    def apply_experts(self, x, w13, w2, topk_w, topk_ids, expert_map):
+        blk = self.block_ref
+        E, two_i, H = w13.shape
+        if x.is_cuda and x.dtype == torch.bfloat16 and H % 128 == 0 and (two_i // 2) % 128 == 0 and E <= 512 \
+                and x.shape[0] > 0:
+            from ..ops import moe_native
+            perm = moe_native.Permutation(topk_ids, expert_map, E)
+            xs = perm.gather(x)
+            a8, a_s = ops.quant_fp8_per_token(xs)
+            h = grouped_fp8_channel(a8, a_s, w13, blk.w13_scale, perm.offsets)
+            a = ops.silu_and_mul(h)
+            b8, b_s = ops.quant_fp8_per_token(a)
+            y = grouped_fp8_channel(b8, b_s, w2, blk.w2_scale, perm.offsets)
+            return perm.combine(y, topk_w)
+        T = x.shape[0]
+        out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+        ids = topk_ids.long()
+        if expert_map is not None:
+            ids = expert_map.long()[ids]
+
+        def lin(a, w, ws):
+            q, s = ref.quant_fp8_per_token(a)
+            return (q.float() @ w.float().t()) * s.unsqueeze(-1) * ws.view(1, -1)
+        for e in range(E):
+            tok, slot = (ids == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            h = lin(x[tok], w13[e], blk.w13_scale[e])
+            a = ref.silu_and_mul(h).to(x.dtype)
+            y = lin(a, w2[e], blk.w2_scale[e])
+            out.index_add_(0, tok, y * topk_w[tok, slot].unsqueeze(-1).float())
+        return out.to(x.dtype)
 
 
 # ---------------------------------------------------------------- microscaling (MX) formats
