@@ -224,3 +224,23 @@ def test_qwen3_vl_engine_on_gpu():
             assert other != outs[eager]
     assert outs[True] == outs[False]
     _native.check_status(torch.device("cuda"))
+
+
+def test_audio_tower_on_gpu_matches_fp32():
+    from vllm_ascend_b200.models.audio import AudioConfig, AudioEncoder, audio_output_lengths
+    cfg = AudioConfig(num_mel_bins=128, d_model=256, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=512,
+                      max_source_positions=300, init_std=0.05, output_dim=384)
+    cpu = AudioEncoder(cfg, "cpu", torch.float32)
+    gpu = AudioEncoder(cfg, DEV, torch.bfloat16)
+    for (n, a), (_, b) in zip(cpu.named_parameters(), gpu.named_parameters()):
+        b.copy_(a)
+    g = torch.Generator().manual_seed(5)
+    feats = [torch.randn(128, 600, generator=g), torch.randn(128, 600, generator=g)]
+    valid = [600, 333]
+    want = cpu(feats, valid)
+    c0 = _native.launch_counter[0]
+    got = gpu([f.to(DEV) for f in feats], valid).float().cpu()
+    assert _native.launch_counter[0] - c0 >= 9 * cfg.encoder_layers + 8
+    _native.check_status(torch.device(DEV))
+    assert got.shape == want.shape == (int(audio_output_lengths(valid)[1].sum()), 384)
+    assert (got - want).norm() / want.norm() < 3e-2

@@ -281,3 +281,65 @@ def test_qwen3_vl_engine_matches_transformers_greedy():
         seq.append(int(lg[0, -1].argmax()))
         want.append(seq[-1])
     assert outs[0].outputs[0].token_ids == want
+
+
+# ---------------------------------------------------------------- audio-language model (Qwen2-Audio layout)
+def _hf_audio_lm():
+    from transformers import Qwen2AudioConfig, Qwen2AudioForConditionalGeneration
+    cfg = Qwen2AudioConfig(
+        audio_config=dict(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128,
+                          max_source_positions=50),
+        text_config=dict(model_type="qwen2", vocab_size=512, hidden_size=128, intermediate_size=256,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6,
+                         max_position_embeddings=2048, tie_word_embeddings=False),
+        audio_token_index=500)
+    cfg._attn_implementation = "eager"
+    cfg.architectures = ["Qwen2AudioForConditionalGeneration"]
+    torch.manual_seed(0)
+    m = Qwen2AudioForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.normal_(0, 0.05)
+            if "norm" in n and n.endswith("weight"):
+                p.add_(1.0)
+    return cfg, m
+
+
+def test_audio_language_engine_matches_transformers_greedy():
+    """Two padded clips of different valid lengths: conv front end as GEMMs, attention over the
+    valid frames only, pair pooling, projector, merge into the prompt; greedy tokens equal
+    transformers' under chunked prefill."""
+    from vllm_ascend_b200.config import ModelConfig
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    from vllm_ascend_b200.models.audio import audio_output_lengths
+    cfg, hf = _hf_audio_lm()
+    mcfg = ModelConfig.from_hf_dict(cfg.to_dict(), dtype="float32", architecture="Qwen2AudioForConditionalGeneration")
+    assert mcfg.is_multimodal and mcfg.audio_token_id == 500 and mcfg.audio_config["d_model"] == 64
+    llm = LLM(mcfg, device="cpu", max_model_len=256, max_num_seqs=4, max_num_batched_tokens=16,
+              num_gpu_blocks_override=64, block_size=16)
+    loaded = llm.engine.runner.model.load_weights(hf.state_dict().items())
+    assert len(loaded) == len(hf.state_dict())
+    g = torch.Generator().manual_seed(0)
+    feats = [torch.randn(16, 100, generator=g), torch.randn(16, 100, generator=g)]
+    valid = [100, 57]
+    n_tok = [int(x) for x in audio_output_lengths(valid)[1]]
+    assert n_tok == [25, 14]
+    ids = [3, 4, 500, 7, 8, 9, 500, 11, 12]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"audio": list(zip(feats, valid))}},
+                         {"prompt_token_ids": [9, 8, 7, 6, 5]}], sp)
+    full = outs[0].prompt_token_ids
+    assert len(full) == len(ids) - 2 + sum(n_tok)
+    mask = torch.zeros(2, 100, dtype=torch.long)
+    mask[0, :100], mask[1, :57] = 1, 1
+    seq, want = list(full), []
+    for _ in range(6):
+        t = torch.tensor([seq])
+        with torch.no_grad():
+            lg = hf(input_ids=t, attention_mask=torch.ones_like(t), input_features=torch.stack(feats),
+                    feature_attention_mask=mask).logits
+        seq.append(int(lg[0, -1].argmax()))
+        want.append(seq[-1])
+    assert outs[0].outputs[0].token_ids == want
+    assert llm.engine.runner.mm.stats["encoder_items"] == 2

@@ -72,6 +72,8 @@ class ModelConfig:
     mrope_section: Optional[list] = None
     mrope_interleaved: bool = False
     vision_config: Optional[dict] = None
+    audio_config: Optional[dict] = None     # HF ``audio_config`` of audio-language models
+    audio_token_id: int = -1
     image_token_id: int = -1
     video_token_id: int = -1
     tokens_per_second: float = 2.0
@@ -106,7 +108,7 @@ class ModelConfig:
 
     @property
     def is_multimodal(self) -> bool:
-        return self.vision_config is not None
+        return self.vision_config is not None or self.audio_config is not None
 
     @property
     def is_hybrid(self) -> bool:
@@ -144,7 +146,7 @@ class ModelConfig:
         if "text_config" in d and "hidden_size" not in d:      # nested multimodal layout
             d = {**d["text_config"], "architectures": [arch]}
             for k in ("vision_config", "image_token_id", "video_token_id", "quantization_config",
-                      "tie_word_embeddings"):
+                      "tie_word_embeddings", "audio_config", "audio_token_id", "audio_token_index"):
                 if k in top and (k not in d or k != "tie_word_embeddings"):
                     d[k] = top[k]
         hs = d["hidden_size"]
@@ -231,6 +233,9 @@ class ModelConfig:
             kw.update(vision_config=vc, image_token_id=d.get("image_token_id", -1),
                       video_token_id=d.get("video_token_id", -1),
                       tokens_per_second=float(vc.get("tokens_per_second", 2.0)))
+        if d.get("audio_config"):
+            kw.update(audio_config=dict(d["audio_config"]),
+                      audio_token_id=int(d.get("audio_token_id", d.get("audio_token_index", -1))))
         qc = d.get("quantization_config")
         if qc:
             method = qc.get("quant_method", "")

@@ -109,9 +109,10 @@ class LLMEngine:
             from ..multimodal import build_mm_request, mrope_positions
             from ..models.vision import VisionConfig
             prompt_token_ids, mm_items = build_mm_request(prompt_token_ids, multi_modal_data, mcfg)
-            mrope, delta = mrope_positions(prompt_token_ids, mm_items,
-                                           VisionConfig.from_hf(mcfg.vision_config).spatial_merge_size,
-                                           mcfg.tokens_per_second)
+            if mcfg.mrope_section:
+                mrope, delta = mrope_positions(prompt_token_ids, mm_items,
+                                               VisionConfig.from_hf(mcfg.vision_config).spatial_merge_size,
+                                               mcfg.tokens_per_second)
         if prompt_embeds is not None:
             # the caller supplies the input embeddings: the ids are placeholders, the rows are merged in
             # the way encoder outputs are

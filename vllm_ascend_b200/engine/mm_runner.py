@@ -87,16 +87,26 @@ class MultimodalState:
         if not missing:
             return
         model = self.runner.model
+        audio = [(key, it) for key, it in missing if it.modality == "audio"]
+        missing = [(key, it) for key, it in missing if it.modality != "audio"]
+        if audio:
+            out = model.embed_audio([it.pixel_values for _, it in audio], [it.grid_thw[0] for _, it in audio])
+            self._store(audio, out)
+        if not missing:
+            return
         px = torch.cat([it.pixel_values for _, it in missing]).to(self.runner.device, model.dtype)
         grid = np.array([it.grid_thw for _, it in missing], dtype=np.int64)
         if self.encoder_graphs is not None:
             out = self.encoder_graphs.run(px, grid)
         else:
             out = model.embed_multimodal(px, grid)
+        self._store(missing, out)
+
+    def _store(self, items: list, out: torch.Tensor) -> None:
         self.stats["encoder_runs"] += 1
-        self.stats["encoder_items"] += len(missing)
+        self.stats["encoder_items"] += len(items)
         off = 0
-        for key, it in missing:
+        for key, it in items:
             self.encoder_cache[key] = out[off:off + it.length]
             off += it.length
             if self.ec_connector is not None and self.ec_connector.is_producer:

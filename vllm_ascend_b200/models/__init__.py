@@ -35,6 +35,14 @@ for _arch in ("Qwen2_5_VLForConditionalGeneration", "Qwen2VLForConditionalGenera
     register_model(_arch, _qwen_vl)
 
 
+def _audio_lm(cfg, device, **kw):
+    from .audio import AudioLMForConditionalGeneration
+    return AudioLMForConditionalGeneration(cfg, device, **kw)
+
+
+register_model("Qwen2AudioForConditionalGeneration", _audio_lm)
+
+
 def supported_architectures() -> list[str]:
     return sorted(_REGISTRY)
 

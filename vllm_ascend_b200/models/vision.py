@@ -264,11 +264,11 @@ def pos_embed_interpolation(grid_thw: np.ndarray, side: int, merge: int):
 
 
 class _LN:
-    def __init__(self, mk, size):
-        self.weight, self.bias = mk.ones((size,)), mk.zeros((size,))
+    def __init__(self, mk, size, eps: float = 1e-6):
+        self.weight, self.bias, self.eps = mk.ones((size,)), mk.zeros((size,)), eps
 
     def __call__(self, x):
-        return ops.layer_norm(x, self.weight, self.bias, 1e-6)
+        return ops.layer_norm(x, self.weight, self.bias, self.eps)
 
 
 class Qwen3VisionBlock:

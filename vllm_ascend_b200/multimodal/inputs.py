@@ -11,7 +11,7 @@ import torch
 
 @dataclass
 class MMInput:
-    modality: str                      # "image" | "video"
+    modality: str                      # "image" | "video" | "audio" (grid_thw = (valid mel frames,), pixel_values = [mel, frames])
     offset: int                        # first placeholder token in the (expanded) prompt
     length: int                        # number of placeholder tokens = t * h * w / merge^2
     grid_thw: tuple
@@ -68,12 +68,16 @@ def build_mm_request(token_ids: Sequence[int], mm_data: dict, mcfg) -> tuple[lis
     """``mm_data``: {"image": [...], "video": [...]}; every entry is an array of pixels
     ([H, W, 3] / [T, H, W, 3]) or an already patchified ``(pixel_values, grid_thw)`` pair.
     Returns (expanded prompt ids, MMInput list sorted by offset)."""
+    ids = list(token_ids)
+    items: list[MMInput] = []
+    if mcfg.audio_config is not None and mm_data.get("audio") is not None:
+        ids, items = _build_audio(ids, mm_data["audio"], mcfg)
+    if mcfg.vision_config is None:
+        return ids, items
     from ..models.vision import VisionConfig
     from .processor import patchify
     vc = VisionConfig.from_hf(mcfg.vision_config)
     m2 = vc.merge_unit
-    ids = list(token_ids)
-    items: list[MMInput] = []
     for modality, tok in (("image", mcfg.image_token_id), ("video", mcfg.video_token_id)):
         entries = mm_data.get(modality) or []
         if not isinstance(entries, (list, tuple)):
@@ -107,7 +111,8 @@ def build_mm_request(token_ids: Sequence[int], mm_data: dict, mcfg) -> tuple[lis
                                  second_per_grid=(1.0 if modality == "video" else None)))
     # recompute offsets of items invalidated above
     if any(it.offset < 0 for it in items):
-        for modality, tok in (("image", mcfg.image_token_id), ("video", mcfg.video_token_id)):
+        for modality, tok in (("audio", mcfg.audio_token_id), ("image", mcfg.image_token_id),
+                              ("video", mcfg.video_token_id)):
             group = [it for it in items if it.modality == modality]
             if group:
                 _, offs = expand_placeholders(ids, tok, [it.length for it in group])
@@ -115,3 +120,29 @@ def build_mm_request(token_ids: Sequence[int], mm_data: dict, mcfg) -> tuple[lis
                     it.offset = o
     items.sort(key=lambda m: m.offset)
     return ids, items
+
+
+def _build_audio(ids: list, entries, mcfg) -> tuple[list, list]:
+    """Audio entries: log-mel features [mel bins, frames] (all frames valid), a ``(features,
+    valid_frames)`` pair for padded clips, or a dict with ``hash`` / ``valid_frames`` (and optionally
+    ``features``) for outputs produced elsewhere."""
+    from ..models.audio import audio_output_lengths
+    if not isinstance(entries, (list, tuple)) or (len(entries) == 2 and isinstance(entries[1], (int, np.integer))):
+        entries = [entries]
+    prepared = []
+    for e in entries:
+        if isinstance(e, dict):
+            f = e.get("features")
+            f = None if f is None else torch.as_tensor(f)
+            n = int(e["valid_frames"])
+            prepared.append((f, n, e.get("hash") or mm_hash(f, (n,))))
+            continue
+        if isinstance(e, (tuple, list)) and len(e) == 2:
+            f, n = torch.as_tensor(np.asarray(e[0]) if not isinstance(e[0], torch.Tensor) else e[0]), int(e[1])
+        else:
+            f = torch.as_tensor(np.asarray(e) if not isinstance(e, torch.Tensor) else e)
+            n = int(f.shape[-1])
+        prepared.append((f, n, mm_hash(f, (n,))))
+    lengths = [int(audio_output_lengths(n)[1]) for _, n, _ in prepared]
+    ids, offsets = expand_placeholders(ids, mcfg.audio_token_id, lengths)
+    return ids, [MMInput("audio", off, ln, (n,), f, hsh) for (f, n, hsh), off, ln in zip(prepared, offsets, lengths)]
