@@ -68,6 +68,9 @@ def test_completions_metrics_and_pd_proxy():
         assert r["choices"][0]["token_ids"] == want[0] and r["choices"][0]["finish_reason"] == "length"
         assert r["usage"] == {"prompt_tokens": 40, "completion_tokens": 6, "total_tokens": 46}
         assert requests.post(servers[0].url + "/v1/completions", json={"prompt": "text"}, timeout=10).status_code == 400
+        r = requests.post(servers[0].url + "/v1/completions", json=dict(body, prompt_logprobs=1), timeout=60).json()
+        plp = r["choices"][0]["prompt_logprobs"]
+        assert len(plp) == 40 and plp[0] is None and str(prompts[0][5]) in plp[5]
         m = requests.get(servers[0].url + "/metrics", timeout=10).text
         assert "vllm_b200_steps" in m and "vllm_b200_kv_blocks_free" in m
         assert requests.get(servers[0].url + "/v1/models", timeout=10).json()["data"][0]["id"] == "tiny-qwen"

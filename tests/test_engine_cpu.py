@@ -390,3 +390,53 @@ def test_n_samples_per_prompt():
     assert [tuple(c.token_ids) for c in again[0].outputs] == toks               # reproducible with the seed
     assert again[0].num_cached_tokens > 0 or llm.engine.scheduler.pool.hits > 0  # siblings share the cached prompt
     assert not llm.engine.scheduler.requests
+
+
+def test_beam_search_keeps_best_cumulative_logprob():
+    """Width 1 is greedy decoding; wider beams never score below it; the reported cumulative
+    log-probability equals the teacher-forced sum of the chosen tokens' log-probabilities."""
+    from vllm_ascend_b200 import LLM, SamplingParams
+    llm = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=128, max_num_seqs=16)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(1, 500, size=n).tolist() for n in (11, 7)]
+    greedy = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True, logprobs=1))
+    one = llm.beam_search(prompts, beam_width=1, max_tokens=5, ignore_eos=True)
+    wide = llm.beam_search(prompts, beam_width=3, max_tokens=5, ignore_eos=True)
+    for g, b1, b3, p in zip(greedy, one, wide, prompts):
+        toks = g.outputs[0].token_ids
+        g_cum = sum(lp[t] for lp, t in zip(g.outputs[0].logprobs, toks))
+        assert b1[0]["tokens"] == toks and abs(b1[0]["cum_logprob"] - g_cum) < 1e-4
+        assert len(b3) == 3 and b3[0]["cum_logprob"] >= g_cum - 1e-5
+        assert [b["score"] for b in b3] == sorted((b["score"] for b in b3), reverse=True)
+        assert len({tuple(b["tokens"]) for b in b3}) == 3
+        # teacher-forced rescoring of the best beam
+        best, cum = b3[0]["tokens"], 0.0
+        for j, t in enumerate(best):
+            o = llm.generate([p + best[:j]], SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, logprobs=500))
+            cum += o[0].outputs[0].logprobs[0][t]
+        assert abs(cum - b3[0]["cum_logprob"]) < 1e-3
+
+
+def test_prompt_logprobs_match_teacher_forcing_across_chunks():
+    """Prompt log-probabilities computed chunk by chunk during prefill equal the generation
+    log-probabilities of the same tokens given the same prefixes."""
+    from vllm_ascend_b200 import LLM, SamplingParams
+    llm = LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=128, max_num_seqs=8,
+              max_num_batched_tokens=16)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(1, 500, size=37).tolist()
+    # warm the prefix cache with the same prompt: the logprob request must not reuse it
+    llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=1))
+    out = llm.generate([prompt, prompt[:9]], SamplingParams(temperature=0.0, max_tokens=2, prompt_logprobs=2))
+    plp = out[0].prompt_logprobs
+    assert len(plp) == 37 and plp[0] is None and all(e is not None for e in plp[1:])
+    assert out[0].num_cached_tokens == 0 and len(out[1].prompt_logprobs) == 9
+    for pos in (1, 15, 16, 17, 31, 36):
+        o = llm.generate([prompt[:pos]], SamplingParams(temperature=0.0, max_tokens=1, logprobs=llm.cfg.model.vocab_size))
+        ref_lp = o[0].outputs[0].logprobs[0]
+        assert abs(plp[pos][prompt[pos]] - ref_lp[prompt[pos]]) < 1e-4
+        top = sorted(ref_lp.items(), key=lambda kv: -kv[1])[:2]
+        for t, v in top:
+            assert abs(plp[pos][t] - v) < 1e-4
+    plain = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=2))
+    assert plain[0].prompt_logprobs is None and plain[0].outputs[0].token_ids == out[0].outputs[0].token_ids

@@ -147,6 +147,13 @@ class LLMEngine:
                                               if r.status == RequestStatus.RUNNING and r.request_id in sampled])
 
     def _attach_logprobs(self) -> None:
+        for rid, entries in self.runner.take_prompt_logprobs().items():
+            req = self.scheduler.requests.get(rid)
+            if req is not None:
+                if getattr(req, "prompt_logprobs", None) is None:
+                    req.prompt_logprobs = [None] * req.num_prompt_tokens
+                for pos, entry in entries:
+                    req.prompt_logprobs[pos] = entry
         for rid, entries in self.runner.take_logprobs().items():
             req = self.scheduler.requests.get(rid)
             if req is not None:
@@ -401,6 +408,57 @@ class LLM:
                 out.append({"modality": modality, "hash": it.hash, "grid_thw": list(it.grid_thw)})
         return out
 
+    def beam_search(self, prompts, beam_width: int = 4, max_tokens: int = 16, length_penalty: float = 1.0,
+                    ignore_eos: bool = False, temperature: float = 0.0) -> list[list[dict]]:
+        """Beam search over the engine: every round extends all live beams of all prompts by one
+        token in ONE batch (``logprobs = 2 * beam_width`` candidates each; automatic prefix caching
+        makes a round cost one decode step per beam), keeps the ``beam_width`` best continuations
+        per prompt by cumulative log-probability and retires beams that emit the end token.
+        Returns, per prompt, the ``beam_width`` best sequences as dicts ``{"tokens",
+        "cum_logprob", "score"}`` with score = cum_logprob / len ** length_penalty."""
+        del temperature
+        eos = self.engine.eos_token_id
+        width = int(beam_width)
+        plist = [list(p["prompt_token_ids"]) if isinstance(p, dict) else list(p) for p in prompts]
+        live = [[(p, 0.0)] for p in plist]              # per prompt: (tokens, cum_logprob)
+        done: list[list[tuple]] = [[] for _ in plist]
+        sp = SamplingParams(temperature=0.0, max_tokens=1, logprobs=2 * width, ignore_eos=True)
+
+        def score(tokens, cum, n_prompt):
+            return cum / (max(len(tokens) - n_prompt, 1) ** length_penalty)
+        for _ in range(max_tokens):
+            flat = [(i, b) for i, beams in enumerate(live) for b in beams]
+            if not flat:
+                break
+            outs = self.generate([b[0] for _, b in flat], sp)
+            cands: list[list[tuple]] = [[] for _ in plist]
+            for (i, (toks, cum)), o in zip(flat, outs):
+                for tok, lp in o.outputs[0].logprobs[0].items():
+                    cands[i].append((toks + [int(tok)], cum + float(lp)))
+            for i, cs in enumerate(cands):
+                cs.sort(key=lambda c: c[1], reverse=True)
+                nxt = []
+                for toks, cum in cs:
+                    if not ignore_eos and eos is not None and toks[-1] == eos:
+                        done[i].append((toks, cum))
+                    else:
+                        nxt.append((toks, cum))
+                    if len(nxt) >= width:
+                        break
+                # a prompt stops once it holds `width` finished beams that beat every live one
+                if len(done[i]) >= width:
+                    n0 = len(plist[i])
+                    worst_done = sorted((score(t, c, n0) for t, c in done[i]), reverse=True)[width - 1]
+                    if not nxt or worst_done >= max(score(t, c, n0) for t, c in nxt):
+                        nxt = []
+                live[i] = nxt
+        result = []
+        for i, n0 in enumerate(len(p) for p in plist):
+            allb = done[i] + live[i]
+            allb.sort(key=lambda b: score(b[0], b[1], n0), reverse=True)
+            result.append([{"tokens": t[n0:], "cum_logprob": c, "score": score(t, c, n0)} for t, c in allb[:width]])
+        return result
+
     def embed(self, prompts, normalize: bool = True) -> list:
         """Sequence embeddings: the final hidden state of every prompt's last token (last-token
         pooling, the pooling of decoder-only embedding models), L2-normalised by default."""
@@ -489,7 +547,8 @@ class LLM:
                          for j, c in enumerate(family)],
                 finished=True,
                 metrics=RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time),
-                kv_transfer_params=r.kv_transfer_params, num_cached_tokens=r.num_cached_tokens))
+                kv_transfer_params=r.kv_transfer_params, num_cached_tokens=r.num_cached_tokens,
+                prompt_logprobs=r.prompt_logprobs))
             for c in family:
                 eng.scheduler.requests.pop(c.request_id, None)
         if dp.world_size > 1:

@@ -117,6 +117,8 @@ class ModelRunner:
         if self.pcp.world_size > 1 and (cfg.model.use_mla or cfg.model.is_hybrid or cfg.model.is_multimodal):
             raise NotImplementedError("prefill context parallelism is implemented for GQA decoder models")
         self._pcp_bcast = False          # this step's tokens come from PCP rank 0
+        self._prompt_lp_out: dict = {}
+        self._plp_chunks: list = []
         self._logprobs_out: dict = {}
         self.proposer = None
         self.last_hidden = None      # final hidden states of the latest step, scheduling order
@@ -494,7 +496,40 @@ class ModelRunner:
             if self.pcp.rank_in_group != 0:
                 sel = [-1] * len(sel)
         self._sample_rows = rows_per_req
+        # chunk geometry of requests that asked for prompt log-probabilities
+        self._plp_chunks = [(r, int(g_starts[i]), int(g_qlens[i]), int(g_cu[i])) for i, r in enumerate(reqs)
+                            if getattr(getattr(r, "sampling_params", None), "prompt_logprobs", None) is not None
+                            and int(g_starts[i]) < r.num_prompt_tokens - 1] if inv is None else []
         return meta, T, Tp, sel, sample_reqs
+
+    def _prompt_logprobs(self, hidden: torch.Tensor) -> None:
+        """Log-probability of every prompt token given its prefix (plus the top-N alternatives) for
+        the prompt chunks computed in this step: row p of a chunk predicts prompt token p + 1."""
+        for r, s, n, cu in self._plp_chunks:
+            P = r.num_prompt_tokens
+            hi = min(s + n, P - 1)                     # positions s .. hi-1 predict tokens s+1 .. hi
+            if hi <= s:
+                continue
+            k = int(r.sampling_params.prompt_logprobs)
+            targets = torch.from_numpy(np.asarray(r.prompt_token_ids[s + 1:hi + 1], dtype=np.int64)).to(self.device)
+            for a in range(0, hi - s, 1024):           # bounded logits footprint
+                b = min(a + 1024, hi - s)
+                lp = torch.log_softmax(self.model.compute_logits(hidden[cu + a:cu + b]).float(), dim=-1)
+                tgt = targets[a:b]
+                tok_lp = lp.gather(1, tgt.unsqueeze(1)).squeeze(1).cpu()
+                if k > 0:
+                    vals, ids = lp.topk(min(k, lp.shape[-1]), dim=-1)
+                    vals, ids = vals.cpu(), ids.cpu()
+                out = self._prompt_lp_out.setdefault(r.request_id, [])
+                for j in range(b - a):
+                    entry = {int(ids[j, q]): float(vals[j, q]) for q in range(ids.shape[1])} if k > 0 else {}
+                    entry[int(tgt[j])] = float(tok_lp[j])
+                    out.append((s + a + j + 1, entry))
+        self._plp_chunks = []
+
+    def take_prompt_logprobs(self) -> dict:
+        out, self._prompt_lp_out = self._prompt_lp_out, {}
+        return out
 
     def init_lora(self) -> None:
         from ..lora.manager import LoRAManager
@@ -598,6 +633,8 @@ class ModelRunner:
             hidden = self._forward(Tp, meta)
             self.last_hidden = hidden
             self.stats["eager_steps"] += 1
+            if self._plp_chunks:
+                self._prompt_logprobs(hidden)
             if not sel:
                 self._meet_lm_head(hidden)
                 return {}
@@ -711,6 +748,8 @@ class ModelRunner:
             hidden = self._forward(Tp, meta)
             self.last_hidden = hidden
             self.stats["eager_steps"] += 1
+            if self._plp_chunks:
+                self._prompt_logprobs(hidden)
             if not sel:
                 return _StepHandle(None, [], None, None, "mixed", t_start)
             h_sel = hidden[:T] if len(sel) == T else hidden[self._to_dev(torch.tensor(sel, dtype=torch.int64))]

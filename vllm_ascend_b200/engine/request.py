@@ -25,6 +25,7 @@ class SamplingParams:
     ignore_eos: bool = False
     seed: Optional[int] = None
     logprobs: Optional[int] = None             # log-probabilities of the sampled token and the top-N tokens
+    prompt_logprobs: Optional[int] = None      # log-probabilities of the prompt tokens (+ top-N); disables prefix reuse
     logit_bias: Optional[dict] = None          # token id -> additive bias
     allowed_token_ids: Optional[list[int]] = None
     bad_words_token_ids: Optional[list[list[int]]] = None   # token sequences that must not be generated
@@ -96,6 +97,7 @@ class Request:
     # offset decoded tokens continue from (position = index + delta)
     pooled: Optional[Any] = None          # final hidden state of the last prompt token (embedding requests)
     logprobs: Optional[list] = None       # per generated token: {token id: logprob} (sampled + top-N)
+    prompt_logprobs: Optional[list] = None    # per prompt token (None for the first): {token id: logprob}
     mm_inputs: list = field(default_factory=list)
     mrope_positions: Optional[np.ndarray] = None
     mrope_delta: int = 0
@@ -146,3 +148,4 @@ class RequestOutput:
     metrics: Optional[RequestMetrics] = None
     kv_transfer_params: Optional[dict] = None
     num_cached_tokens: int = 0
+    prompt_logprobs: Optional[list] = None     # [None, {token: logprob, ...}, ...] one entry per prompt token

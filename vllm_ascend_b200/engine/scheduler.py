@@ -255,7 +255,8 @@ class Scheduler:
                 req.status = RequestStatus.WAITING
             # prefix cache
             cached_blocks: list[int] = []
-            if self.pool.enable_prefix_caching and req.num_computed_tokens == 0 and not req.block_ids:
+            if self.pool.enable_prefix_caching and req.num_computed_tokens == 0 and not req.block_ids \
+                    and req.sampling_params.prompt_logprobs is None:      # every prompt position must be computed
                 hashes = self._hashes.get(req.request_id)
                 if hashes is None:
                     extra = b"" if req.lora_request is None else f"lora{req.lora_request.lora_int_id}".encode()

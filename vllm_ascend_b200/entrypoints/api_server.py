@@ -109,6 +109,7 @@ def _sampling_params(body: dict) -> SamplingParams:
         frequency_penalty=float(body.get("frequency_penalty", 0.0)),
         repetition_penalty=float(body.get("repetition_penalty", 1.0)),
         logprobs=lp,
+        prompt_logprobs=(int(body["prompt_logprobs"]) if body.get("prompt_logprobs") is not None else None),
         logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()} or None,
         allowed_token_ids=body.get("allowed_token_ids"),
         bad_words_token_ids=body.get("bad_words_token_ids"))
@@ -171,7 +172,10 @@ def build_app(llm, tokenizer=None, model_name: str = "model") -> FastAPI:
                 "choices": [{"index": 0, "text": text, "token_ids": toks,
                              "finish_reason": _FINISH.get(req.status),
                              "logprobs": ([{str(k): v for k, v in e.items()} for e in req.logprobs]
-                                          if req.logprobs else None)}],
+                                          if req.logprobs else None),
+                             "prompt_logprobs": ([None if e is None else {str(k): v for k, v in e.items()}
+                                                  for e in req.prompt_logprobs]
+                                                 if getattr(req, "prompt_logprobs", None) else None)}],
                 "usage": {"prompt_tokens": req.num_prompt_tokens, "completion_tokens": len(toks),
                           "total_tokens": req.num_prompt_tokens + len(toks)},
                 "kv_transfer_params": req.kv_transfer_params}
