@@ -68,6 +68,12 @@ def test_completions_metrics_and_pd_proxy():
         assert r["choices"][0]["token_ids"] == want[0] and r["choices"][0]["finish_reason"] == "length"
         assert r["usage"] == {"prompt_tokens": 40, "completion_tokens": 6, "total_tokens": 46}
         assert requests.post(servers[0].url + "/v1/completions", json={"prompt": "text"}, timeout=10).status_code == 400
+        mono.set_guided_vocabulary([None] + [chr(97 + i % 26) * (1 + i // 26) for i in range(mono.cfg.model.vocab_size - 1)],
+                                   eos_token_id=0)
+        r = requests.post(servers[0].url + "/v1/completions",
+                          json=dict(body, guided_choice=["abba", "cc"], max_tokens=12, ignore_eos=False), timeout=60).json()
+        vocab = [""] + [chr(97 + i % 26) * (1 + i // 26) for i in range(mono.cfg.model.vocab_size - 1)]
+        assert "".join(vocab[t] for t in r["choices"][0]["token_ids"]) in ("abba", "cc")
         r = requests.post(servers[0].url + "/v1/completions", json=dict(body, prompt_logprobs=1), timeout=60).json()
         plp = r["choices"][0]["prompt_logprobs"]
         assert len(plp) == 40 and plp[0] is None and str(prompts[0][5]) in plp[5]

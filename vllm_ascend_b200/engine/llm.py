@@ -76,6 +76,7 @@ class LLMEngine:
         # token values: no proposer, no connector bookkeeping, no lock-step groups
         self._inflight = None
         self._sync_reqs: set = set()
+        self.guided = None                 # sample.guided.GuidedDecodingManager once a vocabulary is set
         want_async = cfg.async_scheduling if cfg.async_scheduling is not None else (cfg.device == "cuda")
         # (TP ranks take identical decisions from identical tokens, so they stay in lock-step;
         # DP / PP engines exchange host-side state every step and run synchronously)
@@ -130,7 +131,14 @@ class LLMEngine:
                       job_id=job_id, lora_request=lora_request, mm_inputs=mm_items,
                       mrope_positions=mrope, mrope_delta=delta)
         sp_ = sampling_params
-        if sp_.has_penalties or any(len(w) > 1 for w in (sp_.bad_words_token_ids or ())):
+        if sp_.guided_decoding is not None:
+            if self.guided is None:
+                raise ValueError("guided decoding needs the token strings: call set_guided_vocabulary() first")
+            if self.cfg.speculative_config:
+                raise ValueError("guided decoding and speculative decoding cannot be combined")
+            req.guided = self.guided.new_state(sp_.guided_decoding)
+        if sp_.guided_decoding is not None or sp_.has_penalties \
+                or any(len(w) > 1 for w in (sp_.bad_words_token_ids or ())):
             self._sync_reqs.add(rid)
         self.scheduler.add_request(req)
         return rid
@@ -145,6 +153,20 @@ class LLMEngine:
         else:
             self.runner.propose_draft_tokens([r for r, _ in so.scheduled
                                               if r.status == RequestStatus.RUNNING and r.request_id in sampled])
+
+    def set_guided_vocabulary(self, tokens, eos_token_id: Optional[int] = None) -> None:
+        """``tokens``: the string of every token id (list), or a tokenizer with ``decode``.  Needed
+        once before requests with ``guided_decoding`` are accepted."""
+        from ..sample.guided import GuidedDecodingManager, TokenVocabulary
+        if hasattr(tokens, "decode"):
+            vocab = TokenVocabulary.from_tokenizer(tokens, self.cfg.model.vocab_size)
+            if eos_token_id is not None:
+                vocab.eos_token_id = eos_token_id
+        else:
+            vocab = TokenVocabulary(list(tokens), eos_token_id if eos_token_id is not None else self.eos_token_id)
+        if self.eos_token_id is None and vocab.eos_token_id is not None:
+            self.eos_token_id = vocab.eos_token_id
+        self.guided = GuidedDecodingManager(vocab)
 
     def _attach_logprobs(self) -> None:
         for rid, entries in self.runner.take_prompt_logprobs().items():
@@ -407,6 +429,9 @@ class LLM:
                     mm.ec_connector.save(it.hash, emb)
                 out.append({"modality": modality, "hash": it.hash, "grid_thw": list(it.grid_thw)})
         return out
+
+    def set_guided_vocabulary(self, tokens, eos_token_id: Optional[int] = None) -> None:
+        self.engine.set_guided_vocabulary(tokens, eos_token_id)
 
     def beam_search(self, prompts, beam_width: int = 4, max_tokens: int = 16, length_penalty: float = 1.0,
                     ignore_eos: bool = False, temperature: float = 0.0) -> list[list[dict]]:

@@ -29,9 +29,13 @@ class SamplingParams:
     logit_bias: Optional[dict] = None          # token id -> additive bias
     allowed_token_ids: Optional[list[int]] = None
     bad_words_token_ids: Optional[list[list[int]]] = None   # token sequences that must not be generated
+    guided_decoding: Optional[Any] = None      # sample.guided.GuidedDecodingParams (or a dict of its fields)
     extra_args: Optional[dict] = None
 
     def __post_init__(self):
+        if isinstance(self.guided_decoding, dict):
+            from ..sample.guided import GuidedDecodingParams
+            self.guided_decoding = GuidedDecodingParams(**self.guided_decoding)
         if self.top_k is None or self.top_k < 0:
             self.top_k = 0
         if self.temperature < 0:
@@ -47,7 +51,8 @@ class SamplingParams:
 
     @property
     def has_processors(self) -> bool:
-        return bool(self.logit_bias or self.allowed_token_ids or self.bad_words_token_ids or self.min_tokens > 0)
+        return bool(self.logit_bias or self.allowed_token_ids or self.bad_words_token_ids or self.min_tokens > 0
+                    or self.guided_decoding is not None)
 
     @property
     def has_penalties(self) -> bool:
@@ -96,6 +101,7 @@ class Request:
     # multimodal: items (placeholder run + pixels), 3-axis rotary positions of the prompt and the
     # offset decoded tokens continue from (position = index + delta)
     pooled: Optional[Any] = None          # final hidden state of the last prompt token (embedding requests)
+    guided: Optional[Any] = None          # sample.guided.GuidedState of structured-output requests
     logprobs: Optional[list] = None       # per generated token: {token id: logprob} (sampled + top-N)
     prompt_logprobs: Optional[list] = None    # per prompt token (None for the first): {token id: logprob}
     mm_inputs: list = field(default_factory=list)

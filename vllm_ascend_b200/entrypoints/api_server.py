@@ -92,6 +92,23 @@ class EngineLoop(threading.Thread):
         self.stop_flag.set()
 
 
+def _guided(body: dict):
+    """``guided_regex`` / ``guided_choice`` / ``guided_json`` (or an OpenAI ``response_format`` with a
+    JSON schema) -> GuidedDecodingParams."""
+    from ..sample.guided import GuidedDecodingParams
+    if body.get("guided_regex") is not None:
+        return GuidedDecodingParams(regex=str(body["guided_regex"]))
+    if body.get("guided_choice") is not None:
+        return GuidedDecodingParams(choice=list(body["guided_choice"]))
+    if body.get("guided_json") is not None:
+        return GuidedDecodingParams(json=body["guided_json"])
+    rf = body.get("response_format") or {}
+    if rf.get("type") == "json_schema":
+        js = rf.get("json_schema") or {}
+        return GuidedDecodingParams(json=js.get("schema", js))
+    return None
+
+
 def _sampling_params(body: dict) -> SamplingParams:
     lp = body.get("logprobs")
     if isinstance(lp, bool):                       # chat API: boolean + top_logprobs
@@ -112,11 +129,17 @@ def _sampling_params(body: dict) -> SamplingParams:
         prompt_logprobs=(int(body["prompt_logprobs"]) if body.get("prompt_logprobs") is not None else None),
         logit_bias={int(k): float(v) for k, v in (body.get("logit_bias") or {}).items()} or None,
         allowed_token_ids=body.get("allowed_token_ids"),
-        bad_words_token_ids=body.get("bad_words_token_ids"))
+        bad_words_token_ids=body.get("bad_words_token_ids"),
+        guided_decoding=_guided(body))
 
 
 def build_app(llm, tokenizer=None, model_name: str = "model") -> FastAPI:
     app = FastAPI(title="vllm_ascend_b200")
+    if tokenizer is not None and llm.engine.guided is None and hasattr(tokenizer, "decode"):
+        try:
+            llm.set_guided_vocabulary(tokenizer)
+        except Exception:                          # a tokenizer that cannot decode single ids: guided requests are refused
+            pass
     loop_thread = EngineLoop(llm)
     loop_thread.start()
     app.state.engine_loop = loop_thread

@@ -86,6 +86,13 @@ def _build_processors(reqs: list, device, vocab_size: int) -> dict:
                 allowed = torch.ones((len(reqs), vocab_size), dtype=torch.bool)
             allowed[i] = False
             allowed[i, torch.as_tensor(sp.allowed_token_ids, dtype=torch.long)] = True
+        g = getattr(r, "guided", None)
+        if g is not None:
+            # structured output: tokens that keep the text inside the request's language
+            g.sync(out)
+            if allowed is None:
+                allowed = torch.ones((len(reqs), vocab_size), dtype=torch.bool)
+            allowed[i] &= g.mask(vocab_size, "cpu")
         for seq in sp.bad_words_token_ids or ():
             seq = list(seq)
             if not seq or not (0 <= seq[-1] < vocab_size):
