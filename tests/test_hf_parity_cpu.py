@@ -107,6 +107,13 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import Glm4Config, Glm4ForCausalLM, GlmConfig, GlmForCausalLM
+        glm = dict(common, head_dim=16, rms_norm_eps=1e-5, attention_bias=True, pad_token_id=0)
+        yield "glm", GlmConfig(**glm), GlmForCausalLM
+        yield "glm4", Glm4Config(**glm), Glm4ForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MixtralConfig, MixtralForCausalLM
         yield "mixtral", MixtralConfig(**common, rms_norm_eps=1e-5, num_local_experts=4, num_experts_per_tok=2,
                                        sliding_window=None), MixtralForCausalLM
@@ -117,7 +124,7 @@ def _cases():
 @pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
-                                  "deepseek_v3_yarn", "mistral_window"])
+                                  "deepseek_v3_yarn", "mistral_window", "glm", "glm4"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:

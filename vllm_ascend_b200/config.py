@@ -60,6 +60,9 @@ class ModelConfig:
     gemma_norm: bool = False                 # RMSNorm scales by (1 + weight)
     embed_scale: float = 1.0                 # token embeddings are multiplied by this (Gemma: sqrt(hidden))
     partial_rotary_factor: float = 1.0       # fraction of head_dim that is rotated
+    rope_interleaved: bool = False           # checkpoint rotates pairs (2i, 2i+1); q / k rows are re-ordered at load
+    sandwich_norm: bool = False              # extra RMSNorm on every sub-layer output (GLM-4)
+    split_fused_gate_up: bool = False        # checkpoint stores mlp.gate_up_proj as one [gate; up] tensor
     attn_output_gate: bool = False           # q_proj also produces a per-head sigmoid gate of the attention output
     shared_expert_gate: bool = False         # shared expert output scaled by sigmoid(x . w)
     shared_expert_intermediate_size: int = 0
@@ -178,6 +181,11 @@ class ModelConfig:
         )
         if d.get("shared_expert_intermediate_size"):       # Qwen2-MoE / Qwen3-Next: one gated shared expert
             kw.update(shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]), shared_expert_gate=True)
+        if arch.startswith("Glm"):
+            kw.update(rope_interleaved=True, split_fused_gate_up=True, sandwich_norm=arch.startswith("Glm4"),
+                      partial_rotary_factor=float(d.get("partial_rotary_factor",
+                                                        (d.get("rope_parameters") or {}).get("partial_rotary_factor", 0.5))),
+                      attention_bias=bool(d.get("attention_bias", True)))
         if arch.startswith("Gemma"):
             kw.update(gemma_norm=True, embed_scale=float(hs) ** 0.5,
                       tie_word_embeddings=d.get("tie_word_embeddings", True))

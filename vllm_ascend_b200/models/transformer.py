@@ -289,6 +289,11 @@ class DecoderLayer:
         self.idx = idx
         self.input_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
         self.post_attention_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
+        # sandwich norms (GLM-4): each sub-layer's output is normalised before it joins the residual stream
+        self.post_self_attn_layernorm = self.post_mlp_layernorm = None
+        if cfg.sandwich_norm:
+            self.post_self_attn_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
+            self.post_mlp_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
         if cfg.is_linear_layer(idx):
             from .gdn import GatedDeltaNet
             self.self_attn = GatedDeltaNet(pf, cfg, idx, comm)
@@ -319,8 +324,12 @@ class DecoderLayer:
         else:
             x, residual = self.input_layernorm(h, residual, quant_out=qa)
         h = self.self_attn(x, meta, kv_cache)
+        if self.post_self_attn_layernorm is not None:
+            h, _ = self.post_self_attn_layernorm(h)
         x, residual = self.post_attention_layernorm(h, residual, quant_out=self._mlp_in_fp8)
         h = self.mlp(x)
+        if self.post_mlp_layernorm is not None:
+            h, _ = self.post_mlp_layernorm(h)
         return h, residual
 
     @property
@@ -440,6 +449,9 @@ class CausalLM:
             p = f"model.layers.{L.idx}"
             yield f"{p}.input_layernorm.weight", L.input_layernorm.weight
             yield f"{p}.post_attention_layernorm.weight", L.post_attention_layernorm.weight
+            if L.post_self_attn_layernorm is not None:
+                yield f"{p}.post_self_attn_layernorm.weight", L.post_self_attn_layernorm.weight
+                yield f"{p}.post_mlp_layernorm.weight", L.post_mlp_layernorm.weight
             a = L.self_attn
             if getattr(a, "is_linear_attention", False):
                 for attr in ("in_proj_qkvz", "in_proj_ba", "out_proj"):
@@ -505,10 +517,28 @@ class CausalLM:
         layers = {L.idx: L for L in self.layers}
         tp, r = self.comm.size, self.comm.rank
         arch_internlm2 = self.cfg.architecture.startswith("InternLM2")
+        cfg = self.cfg
         for name, w in weights:
             if name.endswith("rotary_emb.inv_freq"):
                 continue
             orig_name = name
+            if cfg.rope_interleaved and re.search(r"self_attn\.(q|k)_proj\.(weight|bias)$", name):
+                # checkpoints whose rotary pairs are (2i, 2i + 1): move every head's rotated rows into
+                # the half-split order the kernels rotate; q.k is unchanged by a common permutation
+                D = cfg.head_dim
+                rot = int(D * cfg.partial_rotary_factor) // 2 * 2
+                idx = torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2), torch.arange(rot, D)])
+                w = w.view(-1, D, *w.shape[1:])[:, idx].reshape(w.shape)
+            if name.endswith(".mlp.gate_up_proj.weight") and ".experts." not in name and cfg.split_fused_gate_up:
+                # [gate rows; up rows] stored as one tensor: place the halves like separate projections
+                tgt = name
+                if tgt in params:
+                    half = w.shape[0] // 2
+                    tp_t, r_t = self._shard_of(tgt, tp, r)
+                    self._copy_shard(tgt, params[tgt], w[:half], 0, tp_t, r_t)
+                    self._copy_shard(tgt, params[tgt], w[half:], 1, tp_t, r_t)
+                    loaded.add(orig_name)
+                continue
             if arch_internlm2:
                 name = _internlm2_name(name)
                 if name.endswith("attention.wqkv.weight"):

@@ -189,7 +189,8 @@ def supports(model) -> bool:
     cfg = model.cfg
     return (not cfg.use_mla and not cfg.is_moe and model.dtype == torch.bfloat16
             and not cfg.mrope_section and not cfg.is_hybrid and cfg.embed_scale == 1.0
-            and cfg.hidden_act in ("silu", "swish") and not cfg.attn_output_gate
+            and cfg.hidden_act in ("silu", "swish") and not cfg.attn_output_gate and not cfg.sandwich_norm
+            and cfg.partial_rotary_factor == 1.0
             and model.is_first and model.is_last
             and all(isinstance(L.self_attn, GQAAttention) and isinstance(L.mlp, SwiGLUMLP)
                     and L.self_attn.qkv_proj.quant is None for L in model.layers))
