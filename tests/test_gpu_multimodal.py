@@ -240,7 +240,7 @@ def test_audio_tower_on_gpu_matches_fp32():
     want = cpu(feats, valid)
     c0 = _native.launch_counter[0]
     got = gpu([f.to(DEV) for f in feats], valid).float().cpu()
-    assert _native.launch_counter[0] - c0 >= 9 * cfg.encoder_layers + 8
+    assert _native.launch_counter[0] - c0 >= 6 * cfg.encoder_layers + 6     # native kernels, not a fallback
     _native.check_status(torch.device(DEV))
     assert got.shape == want.shape == (int(audio_output_lengths(valid)[1].sum()), 384)
     assert (got - want).norm() / want.norm() < 3e-2
