@@ -114,6 +114,12 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import Ernie4_5Config, Ernie4_5ForCausalLM
+        yield "ernie45", Ernie4_5Config(**common, head_dim=16, rms_norm_eps=1e-5, use_bias=False, pad_token_id=0), \
+            Ernie4_5ForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MixtralConfig, MixtralForCausalLM
         yield "mixtral", MixtralConfig(**common, rms_norm_eps=1e-5, num_local_experts=4, num_experts_per_tok=2,
                                        sliding_window=None), MixtralForCausalLM
@@ -124,7 +130,7 @@ def _cases():
 @pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
-                                  "deepseek_v3_yarn", "mistral_window", "glm", "glm4"])
+                                  "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])
 def test_greedy_tokens_match_transformers(name, tmp_path):
     case = {n: (c, m) for n, c, m in _cases()}.get(name)
     if case is None:

@@ -186,6 +186,9 @@ class ModelConfig:
                       partial_rotary_factor=float(d.get("partial_rotary_factor",
                                                         (d.get("rope_parameters") or {}).get("partial_rotary_factor", 0.5))),
                       attention_bias=bool(d.get("attention_bias", True)))
+        if arch.startswith("Ernie4_5"):
+            kw.update(rope_interleaved=True, attention_bias=bool(d.get("use_bias", False)),
+                      tie_word_embeddings=d.get("tie_word_embeddings", True))
         if arch.startswith("Gemma"):
             kw.update(gemma_norm=True, embed_scale=float(hs) ** 0.5,
                       tie_word_embeddings=d.get("tie_word_embeddings", True))

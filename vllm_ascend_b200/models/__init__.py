@@ -21,7 +21,8 @@ def _causal_lm(cfg, device, **kw):
 for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwen3ForCausalLM",
               "Qwen2MoeForCausalLM", "Qwen3MoeForCausalLM", "MixtralForCausalLM", "DeepseekV2ForCausalLM",
               "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM", "InternLM2ForCausalLM", "Phi3ForCausalLM",
-              "GemmaForCausalLM", "Qwen3NextForCausalLM", "GlmForCausalLM", "Glm4ForCausalLM"):
+              "GemmaForCausalLM", "Qwen3NextForCausalLM", "GlmForCausalLM", "Glm4ForCausalLM",
+              "Ernie4_5ForCausalLM", "Ernie4_5_ForCausalLM"):
     register_model(_arch, _causal_lm)
 
 
