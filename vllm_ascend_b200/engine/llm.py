@@ -131,6 +131,8 @@ class LLMEngine:
                       job_id=job_id, lora_request=lora_request, mm_inputs=mm_items,
                       mrope_positions=mrope, mrope_delta=delta)
         sp_ = sampling_params
+        if sp_.prompt_logprobs is not None:
+            self.runner.plp_enabled = True
         if sp_.guided_decoding is not None:
             if self.guided is None:
                 raise ValueError("guided decoding needs the token strings: call set_guided_vocabulary() first")

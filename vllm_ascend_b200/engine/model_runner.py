@@ -118,6 +118,7 @@ class ModelRunner:
             raise NotImplementedError("prefill context parallelism is implemented for GQA decoder models")
         self._pcp_bcast = False          # this step's tokens come from PCP rank 0
         self._prompt_lp_out: dict = {}
+        self.plp_enabled = False     # set once a request asks for prompt log-probabilities
         self._plp_chunks: list = []
         self._logprobs_out: dict = {}
         self.proposer = None
@@ -499,7 +500,7 @@ class ModelRunner:
         # chunk geometry of requests that asked for prompt log-probabilities
         self._plp_chunks = [(r, int(g_starts[i]), int(g_qlens[i]), int(g_cu[i])) for i, r in enumerate(reqs)
                             if getattr(getattr(r, "sampling_params", None), "prompt_logprobs", None) is not None
-                            and int(g_starts[i]) < r.num_prompt_tokens - 1] if inv is None else []
+                            and int(g_starts[i]) < r.num_prompt_tokens - 1] if (inv is None and self.plp_enabled) else []
         return meta, T, Tp, sel, sample_reqs
 
     def _prompt_logprobs(self, hidden: torch.Tensor) -> None:
