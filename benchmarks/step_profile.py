@@ -32,6 +32,8 @@ def main():
     ap.add_argument("--mixed-steps", type=int, default=3)
     ap.add_argument("--decode-steps", type=int, default=3)
     ap.add_argument("--out", default="step_profile.txt")
+    ap.add_argument("--whole-pass", action="store_true",
+                    help="profile one complete pass of the workload (device activity only) after a warm pass")
     args = ap.parse_args()
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
@@ -42,6 +44,43 @@ def main():
     eng = llm.engine
     rng = np.random.default_rng(0)
     sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
+    if args.whole_pass:
+        import time
+        mk = lambda: [rng.integers(0, llm.cfg.model.vocab_size, size=args.input_len).tolist()
+                      for _ in range(args.num_prompts)]
+        llm.generate(mk(), sp)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+            llm.generate(mk(), sp)
+            torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        agg = defaultdict(lambda: [0, 0.0])
+        first, last = None, 0.0
+        for ev in prof.events():
+            if ev.device_type == torch.autograd.DeviceType.CUDA:
+                a = agg[ev.name[:90]]
+                a[0] += 1
+                a[1] += ev.device_time
+                tr = ev.time_range
+                first = tr.start if first is None else min(first, tr.start)
+                last = max(last, tr.end)
+        total = sum(v[1] for v in agg.values())
+        span = (last - first) if first is not None else 0.0
+        out = [f"== whole pass under the profiler: wall {wall:.2f} s, device span {span / 1e6:.2f} s, "
+               f"sum of kernel time {total / 1e6:.2f} s ({100 * total / max(span, 1):.1f}% of the span), "
+               f"{sum(v[0] for v in agg.values())} launches"]
+        for name, (cnt, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:20]:
+            out.append(f"  {us / total * 100:5.1f}%  {us / 1e6:8.3f} s  {cnt:7d}  {name}")
+        text = "\n".join(out)
+        if rank == 0:
+            print(text)
+            os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
+            with open(args.out, "w") as f:
+                f.write(text + "\n")
+        sys.stdout.flush()
+        llm.shutdown()
+        os._exit(0)
     for _ in range(args.num_prompts):
         eng.add_request(rng.integers(0, llm.cfg.model.vocab_size, size=args.input_len).tolist(), sp)
     for _ in range(args.skip_steps):

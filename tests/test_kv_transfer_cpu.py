@@ -372,3 +372,47 @@ def test_sparse_attention_remote_d2h_connector():
     finally:
         pre.engine.kv_connector.close()
         clear_b200_config()
+
+
+def test_block_keys_separate_multimodal_content_adapters_and_engines():
+    """Blocks are shared only between requests whose KV really is the same: equal placeholder ids with
+    other pixels, another adapter, or another model / cache layout give other keys; prompt-embedding
+    requests (ids are placeholders, no content hash) are never looked up nor published."""
+    from types import SimpleNamespace as NS
+    import numpy as np
+    from vllm_ascend_b200.engine.block_pool import BlockPool
+    ids = np.arange(64, dtype=np.int32)
+    mm = lambda h, modality="image": NS(hash=h, modality=modality)
+    req = lambda **kw: NS(prompt_token_ids=ids, output_token_ids=[], lora_request=None, mm_inputs=[], **kw)
+    base = BlockPool.request_key_extra(req())
+    a, b = req(), req()
+    a.mm_inputs, b.mm_inputs = [mm("img-a")], [mm("img-b")]
+    ka, kb = BlockPool.request_key_extra(a), BlockPool.request_key_extra(b)
+    assert len({base, ka, kb}) == 3
+    c = req()
+    c.lora_request = NS(lora_int_id=3)
+    assert BlockPool.request_key_extra(c) not in (base, ka, kb)
+    e = req()
+    e.mm_inputs = [mm("embeds-req-1", "embeds")]
+    assert BlockPool.request_key_extra(e) is None
+    # a store shared by engines: another model or cache dtype changes every key
+    import torch
+    cfg = lambda name, bs=16: NS(model=NS(architecture="Qwen3ForCausalLM", name=name, model_path=None,
+                                         num_hidden_layers=2, hidden_size=64, num_attention_heads=4,
+                                         num_key_value_heads=2, head_dim=16, vocab_size=100, seed=0,
+                                         quantization=None), cache=NS(block_size=bs))
+    t16 = [torch.zeros(4, 16, 2, 16, dtype=torch.bfloat16)]
+    t8 = [torch.zeros(4, 16, 2, 16, dtype=torch.float8_e4m3fn)]
+    f = BlockPool.store_fingerprint
+    assert f(cfg("a"), t16) == f(cfg("a"), t16)
+    assert len({f(cfg("a"), t16), f(cfg("b"), t16), f(cfg("a"), t8)}) == 3
+    # the connectors route through the same helper
+    from vllm_ascend_b200.distributed.kv_transfer.kv_pool import KVPoolConnector
+    conn = KVPoolConnector.__new__(KVPoolConnector)
+    conn.block_size, conn._fingerprint = 16, f(cfg("a"), t16)
+    assert conn._hashes(e, 64) == []
+    ha, hb = conn._hashes(a, 64), conn._hashes(b, 64)
+    assert len(ha) == 4 and ha[0] != hb[0]
+    conn2 = KVPoolConnector.__new__(KVPoolConnector)
+    conn2.block_size, conn2._fingerprint = 16, f(cfg("b"), t16)
+    assert conn2._hashes(a, 64)[0] != ha[0]

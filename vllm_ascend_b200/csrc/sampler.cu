@@ -261,7 +261,7 @@ sample_kernel(float* logits, long ld, int V, const float* __restrict__ temperatu
   int besti = bi;
   for (int i0 = threadIdx.x * 4; i0 < V; i0 += blockDim.x * 4) {
     const uint4 rnd = philox4x32(
-        make_uint4((uint32_t)i0, (uint32_t)offset, (uint32_t)((unsigned long long)offset >> 32), (uint32_t)b), key);
+        make_uint4((uint32_t)i0, (uint32_t)offset, (uint32_t)((unsigned long long)offset >> 32), 0u), key);
     const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
 #pragma unroll
     for (int j = 0; j < 4; j++) {

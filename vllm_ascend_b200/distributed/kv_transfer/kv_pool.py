@@ -81,6 +81,7 @@ class KVPoolConnector(KVConnectorBase):
         self.timeout_ms = int(extra.get("timeout_ms", 3000))
         self.block_size = engine_cfg.cache.block_size
         self.tensors = [t for pair in runner.kv_caches for t in pair]
+        self._fingerprint = BlockPool.store_fingerprint(engine_cfg, self.tensors)
         self.is_cuda = self.tensors[0].is_cuda
         self.role = ktc.get("kv_role", "kv_both")
         self._pending_load: list[tuple[list, list]] = []        # (hashes, gpu blocks)
@@ -91,7 +92,9 @@ class KVPoolConnector(KVConnectorBase):
     # ------------------------------------------------------------------ helpers
     def _hashes(self, req, num_tokens: int) -> list[bytes]:
         toks = np.concatenate([req.prompt_token_ids, np.asarray(req.output_token_ids or [], dtype=np.int32)])
-        extra = b"" if req.lora_request is None else f"lora{req.lora_request.lora_int_id}".encode()
+        extra = BlockPool.request_key_extra(req, self._fingerprint)
+        if extra is None:               # nothing of this request may be looked up or published
+            return []
         out, parent = [], None
         for i in range(num_tokens // self.block_size):
             parent = BlockPool.hash_block(parent, toks[i * self.block_size:(i + 1) * self.block_size], extra)

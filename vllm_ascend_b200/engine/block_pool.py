@@ -70,6 +70,36 @@ class BlockPool:
 
     # ------------------------------------------------------------------ prefix cache
     @staticmethod
+    def request_key_extra(req, store_fingerprint: bytes = b"") -> Optional[bytes]:
+        """Everything besides the token ids that decides what a request's KV blocks hold: the
+        adapter, the content hash of every multimodal item (equal placeholder ids, other pixels or
+        audio) and, for stores shared between engines, a fingerprint of the model and the cache
+        layout.  One helper for the scheduler's prefix cache and every connector, so that they can
+        never disagree.  ``None``: the request's blocks must not be shared at all (caller-supplied
+        embeddings have placeholder ids and no content hash)."""
+        extra = store_fingerprint
+        if req.lora_request is not None:
+            extra += f"lora{req.lora_request.lora_int_id}".encode()
+        for it in getattr(req, "mm_inputs", None) or ():
+            if getattr(it, "modality", "") == "embeds" or not getattr(it, "hash", None) \
+                    or str(it.hash).startswith("embeds-"):
+                return None
+            extra += b"mm" + str(it.hash).encode()
+        return extra
+
+    @staticmethod
+    def store_fingerprint(engine_cfg, tensors) -> bytes:
+        """Identity of what a KV block of this engine means: architecture and shape of the model, its
+        weights' origin, and the cache tensors' dtype / per-block shape (which carry the TP sharding)."""
+        m = engine_cfg.model
+        desc = [m.architecture, m.name, str(m.model_path), m.num_hidden_layers, m.hidden_size,
+                m.num_attention_heads, m.num_key_value_heads, m.head_dim, m.vocab_size, m.seed,
+                str(m.quantization), engine_cfg.cache.block_size]
+        for t in tensors:
+            desc.append((str(t.dtype), tuple(t.shape[1:])))
+        return hashlib.blake2b(repr(desc).encode(), digest_size=8).digest()
+
+    @staticmethod
     def hash_block(parent: Optional[bytes], tokens: np.ndarray, extra: bytes = b"") -> bytes:
         h = hashlib.blake2b(digest_size=16)
         if parent:

@@ -100,6 +100,7 @@ class LLMEngine:
                     job_id: Optional[str] = None, lora_request=None,
                     multi_modal_data: Optional[dict] = None, prompt_embeds=None) -> str:
         rid = request_id or f"req-{next(self._req_counter)}"
+        sampling_params.validate_for_vocab(self.cfg.model.vocab_size)
         if lora_request is not None and self.runner.lora_manager is None:
             raise ValueError("a LoRA request needs an engine built with enable_lora=True")
         mm_items, mrope, delta = [], None, 0
@@ -515,8 +516,15 @@ class LLM:
         return c
 
     def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                 use_tqdm: bool = False, lora_request=None) -> list[RequestOutput]:
-        """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``)."""
+                 use_tqdm: bool = False, lora_request=None,
+                 max_concurrency: Optional[int] = None) -> list[RequestOutput]:
+        """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``).
+
+        ``max_concurrency``: closed-loop admission.  At most that many requests are in flight (per
+        data-parallel replica: its share of the total); the next prompt enters when one finishes.
+        This is the fixed-concurrency serving workload of the reference's benchmark cases
+        (benchmarks/tests/serving-tests.json, ``max_concurrency``); ``None`` submits everything at once.
+        A request's ``arrival_time`` is the moment it is admitted."""
         if sampling_params is None:
             sampling_params = SamplingParams()
         eng = self.engine
@@ -524,34 +532,45 @@ class LLM:
         order: list[str] = []
         mine: list[int] = []
         reqs: dict[str, Request] = {}
-        for i, p in enumerate(prompts):
-            if dp.world_size > 1 and i % dp.world_size != dp.rank_in_group:
-                continue            # data parallel: every DP rank serves its own slice
-            ids = p.get("prompt_token_ids") if isinstance(p, dict) else p
-            sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
-            ktp = p.get("kv_transfer_params") if isinstance(p, dict) else None
-            lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
-            mmd = p.get("multi_modal_data") if isinstance(p, dict) else None
-            pe = p.get("prompt_embeds") if isinstance(p, dict) else None
-            if pe is not None and ids is None:
-                ids = []
-            rid = eng.add_request(ids, self._child_params(sp, 0), kv_transfer_params=ktp, lora_request=lr,
-                                  multi_modal_data=mmd, prompt_embeds=pe)
-            order.append(rid)
-            mine.append(i)
-            reqs[rid] = eng.scheduler.requests[rid]
-            reqs[rid].client_index, reqs[rid].origin_rank = i, dp.rank_in_group
-            reqs[rid].siblings = []
-            for j in range(1, max(1, sp.n)):          # n > 1: sibling requests over the same prompt
-                sid = eng.add_request(ids, self._child_params(sp, j), kv_transfer_params=ktp, lora_request=lr,
+        pending = [i for i in range(len(prompts))
+                   if dp.world_size == 1 or i % dp.world_size == dp.rank_in_group]
+        pending.reverse()             # data parallel: every DP rank serves its own slice
+        limit = None
+        if max_concurrency is not None:
+            limit = max(1, int(max_concurrency) // max(dp.world_size, 1))
+
+        def admit() -> None:
+            while pending and (limit is None or eng.scheduler.num_unfinished() < limit):
+                i = pending.pop()
+                p = prompts[i]
+                ids = p.get("prompt_token_ids") if isinstance(p, dict) else p
+                sp = sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
+                ktp = p.get("kv_transfer_params") if isinstance(p, dict) else None
+                lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
+                mmd = p.get("multi_modal_data") if isinstance(p, dict) else None
+                pe = p.get("prompt_embeds") if isinstance(p, dict) else None
+                if pe is not None and ids is None:
+                    ids = []
+                rid = eng.add_request(ids, self._child_params(sp, 0), kv_transfer_params=ktp, lora_request=lr,
                                       multi_modal_data=mmd, prompt_embeds=pe)
-                reqs[rid].siblings.append(eng.scheduler.requests[sid])
+                order.append(rid)
+                mine.append(i)
+                reqs[rid] = eng.scheduler.requests[rid]
+                reqs[rid].client_index, reqs[rid].origin_rank = i, dp.rank_in_group
+                reqs[rid].siblings = []
+                for j in range(1, max(1, sp.n)):          # n > 1: sibling requests over the same prompt
+                    sid = eng.add_request(ids, self._child_params(sp, j), kv_transfer_params=ktp, lora_request=lr,
+                                          multi_modal_data=mmd, prompt_embeds=pe)
+                    reqs[rid].siblings.append(eng.scheduler.requests[sid])
+
+        admit()
         if dp.world_size > 1:
             while eng.step_dp():
-                pass
+                admit()
         else:
-            while eng.has_unfinished():
+            while eng.has_unfinished() or pending:
                 eng.step()
+                admit()
         eng.check_health()
         if dp.world_size > 1:
             # requests may have moved between DP ranks (load balancing): report what finished here

@@ -10,6 +10,7 @@ persistent buffers so graph replay needs no host-side argument refresh.
 from __future__ import annotations
 
 import math
+import os
 import time
 from typing import Optional
 
@@ -38,6 +39,22 @@ def default_capture_sizes(max_size: int) -> list[int]:
     return [x for x in sizes if x <= max_size]
 
 
+class _SpecRow:
+    """One logits row of a speculative verification step seen as a request: the request itself with
+    its first ``j`` draft tokens appended to the generated history."""
+    __slots__ = ("_r", "_j", "output_token_ids", "num_output_tokens", "num_inflight", "guided")
+
+    def __init__(self, req, j: int):
+        self._r, self._j = req, j
+        self.output_token_ids = list(req.output_token_ids or []) + [int(t) for t in req.spec_token_ids[:j]]
+        self.num_output_tokens = req.num_output_tokens + j
+        self.num_inflight = getattr(req, "num_inflight", 0)
+        self.guided = None
+
+    def __getattr__(self, name):
+        return getattr(self._r, name)
+
+
 class _StepHandle:
     """A step that was enqueued but whose sampled tokens have not been read yet."""
     __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index", "logprobs")
@@ -50,6 +67,8 @@ class _StepHandle:
 
 class ModelRunner:
     def __init__(self, cfg: EngineConfig, device: torch.device):
+        self._step_timing = device.type == "cuda" and os.environ.get("VLLM_B200_STEP_TIMING", "0") == "1"
+        self._last_step_end = None
         self.cfg = cfg
         self.device = device
         self.mcfg = cfg.model
@@ -723,6 +742,12 @@ class ModelRunner:
         gsize = self._graph_size_for(B) if decode_only else None
         if gsize is not None and self._lora_step_needs_eager(so):
             gsize = None
+        ev_start = None
+        if self._step_timing:
+            # device-side account of the step: time between the first and the last GPU operation of
+            # the step, and the idle gap since the previous step's last one
+            ev_start = torch.cuda.Event(enable_timing=True)
+            ev_start.record()
         meta, T, Tp, sel, sample_reqs = self._prepare_inputs(so, pad_to=gsize)
         if prev is not None:
             src, dst = [], []
@@ -771,7 +796,7 @@ class ModelRunner:
         buf[:n].copy_(tokens, non_blocking=True)
         ev = None
         if self.is_cuda:
-            ev = torch.cuda.Event()
+            ev = torch.cuda.Event(enable_timing=self._step_timing)
             ev.record()
         self.stats["d2h_bytes"] += n * 8
         self.stats["t_prepare"] += t_prep - t_start
@@ -779,6 +804,8 @@ class ModelRunner:
         kind = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
         handle = _StepHandle(tokens, sample_reqs, buf, ev, kind, t_start)
         handle.logprobs = dev_lp
+        handle.ev_start = ev_start
+        handle.num_tokens = T
         return handle
 
     def _reduce_sample(self, sample_reqs: list) -> bool:
@@ -836,6 +863,12 @@ class ModelRunner:
         t0 = time.perf_counter()
         if handle.event is not None:
             handle.event.synchronize()
+            if getattr(handle, "ev_start", None) is not None:
+                st = self.stats
+                st["gpu_ms_" + handle.kind] = st.get("gpu_ms_" + handle.kind, 0.0) + handle.ev_start.elapsed_time(handle.event)
+                if self._last_step_end is not None:
+                    st["gpu_idle_ms"] = st.get("gpu_idle_ms", 0.0) + max(0.0, self._last_step_end.elapsed_time(handle.ev_start))
+                self._last_step_end = handle.event
         toks = handle.host[:len(handle.reqs)].numpy()
         self._store_logprobs(handle.logprobs, handle.reqs, toks)
         out = {}
@@ -885,20 +918,24 @@ class ModelRunner:
                 "entropy_verify" if rc.enable_entropy_verify else "standard")
             self.rejection_sampler = RejectionSampler(method, rc.posterior_alpha, rc.posterior_threshold)
         dev = self.device
-        expanded = [r for r, k in zip(sample_reqs, rows) for _ in range(k)]
+        # row j of a request sees the request's history extended by its first j draft tokens: logit
+        # processors, penalties and the position in the random stream are those of a step that
+        # had really generated them
+        expanded = [_SpecRow(r, j) for r, k in zip(sample_reqs, rows) for j in range(k)]
         md = SamplingMetadata.build(expanded, dev, self.mcfg.vocab_size, self.cfg.seed)
-        if not md.all_greedy:
-            if md.offsets is not None:          # distinct random streams for the rows of one request
-                md.offsets = md.offsets + torch.tensor([j for k in rows for j in range(k)], dtype=torch.int64,
-                                                       device=dev)
-            if not self.is_cuda:
-                md.generator = self._cpu_generator()
-        logits_f = logits.float()
-        tokens_all = self.sampler(logits_f.clone() if not md.all_greedy else logits_f, md).to(torch.int32)
+        if not md.all_greedy and not self.is_cuda:
+            md.generator = self._cpu_generator()
+        processed = self.sampler.apply_processors(logits.float(), md)
         cu_rows = np.concatenate([[0], np.cumsum(rows)]).astype(np.int64)
         last_rows = torch.from_numpy(cu_rows[1:] - 1).to(dev)
         draft_rows = torch.from_numpy(np.concatenate([np.arange(cu_rows[i], cu_rows[i + 1] - 1)
                                                       for i in range(len(rows))]).astype(np.int64)).to(dev)
+        target_logits = processed[draft_rows]
+        target_probs = None
+        if not md.all_greedy and draft_rows.numel():
+            target_probs = self.sampler.filtered_probs(target_logits, md, draft_rows)
+        tokens_all = self.sampler.sample_processed(processed.clone() if not md.all_greedy else processed,
+                                                   md).to(torch.int32)
         draft = np.concatenate([np.asarray(r.spec_token_ids[:k - 1], dtype=np.int32)
                                 for r, k in zip(sample_reqs, rows)]) if draft_rows.numel() else np.zeros(0, np.int32)
         cu_draft = torch.from_numpy((cu_rows - np.arange(len(rows) + 1)).astype(np.int32)).to(dev)
@@ -906,9 +943,12 @@ class ModelRunner:
         temp = torch.tensor([max(r.sampling_params.temperature, 1e-5) for r in sample_reqs], dtype=torch.float32,
                             device=dev)
         max_spec = max(rows) - 1
+        first_rows = torch.from_numpy(cu_rows[:-1]).to(dev)
         out, num = self.rejection_sampler(
-            torch.from_numpy(draft).to(dev), cu_draft, logits_f[draft_rows], tokens_all[last_rows].contiguous(),
-            is_greedy, temp, max_spec, generator=None if self.is_cuda else self._cpu_generator())
+            torch.from_numpy(draft).to(dev), cu_draft, target_logits, tokens_all[last_rows].contiguous(),
+            is_greedy, temp, max_spec, target_probs=target_probs,
+            seeds=None if md.seeds is None else md.seeds[first_rows],
+            offsets=None if md.offsets is None else md.offsets[first_rows])
         out_h, num_h = out.cpu().numpy(), num.cpu().numpy()
         self.stats["d2h_bytes"] += out_h.nbytes + num_h.nbytes
         res = {}

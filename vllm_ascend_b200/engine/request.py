@@ -44,6 +44,36 @@ class SamplingParams:
             raise ValueError("top_p must be in (0, 1]")
         if self.max_tokens is not None and self.max_tokens < 1:
             raise ValueError("max_tokens must be at least 1")
+        if not (self.repetition_penalty > 0.0):
+            raise ValueError("repetition_penalty must be positive")
+        if not (0.0 <= self.min_p <= 1.0):
+            raise ValueError("min_p must be in [0, 1]")
+        if self.min_tokens < 0:
+            raise ValueError("min_tokens must be non-negative")
+        if self.n < 1:
+            raise ValueError("n must be at least 1")
+        for name in ("logprobs", "prompt_logprobs"):
+            v = getattr(self, name)
+            if v is not None and int(v) < 0:
+                raise ValueError(f"{name} must be non-negative")
+        if self.allowed_token_ids is not None:
+            ids = [int(t) for t in self.allowed_token_ids]
+            if not ids:
+                raise ValueError("allowed_token_ids must not be empty")
+            if min(ids) < 0:
+                raise ValueError("allowed_token_ids must be non-negative")
+            self.allowed_token_ids = ids
+
+    def validate_for_vocab(self, vocab_size: int) -> None:
+        """Checks that need the model: token ids named by the request exist.  Raises ``ValueError``
+        (the HTTP server answers 400) instead of letting an index fault stop the engine later."""
+        if self.allowed_token_ids is not None and max(self.allowed_token_ids) >= vocab_size:
+            raise ValueError(f"allowed_token_ids holds an id >= vocab size {vocab_size}")
+        if self.top_k and self.top_k > vocab_size:
+            self.top_k = 0
+        for t in self.stop_token_ids or ():
+            if not (0 <= int(t) < vocab_size):
+                raise ValueError(f"stop_token_ids holds an id outside [0, {vocab_size})")
 
     @property
     def greedy(self) -> bool:
@@ -58,6 +88,15 @@ class SamplingParams:
     def has_penalties(self) -> bool:
         return (self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
                 or self.repetition_penalty != 1.0)
+
+
+class RequestError(RuntimeError):
+    """A failure that belongs to one request (malformed parameters discovered while a step is
+    built): the serving loop aborts that request and keeps serving the others."""
+
+    def __init__(self, request_id: str, message: str):
+        super().__init__(f"request {request_id}: {message}")
+        self.request_id = request_id
 
 
 class RequestStatus(enum.IntEnum):

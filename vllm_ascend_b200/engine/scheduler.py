@@ -259,10 +259,8 @@ class Scheduler:
                     and req.sampling_params.prompt_logprobs is None:      # every prompt position must be computed
                 hashes = self._hashes.get(req.request_id)
                 if hashes is None:
-                    extra = b"" if req.lora_request is None else f"lora{req.lora_request.lora_int_id}".encode()
-                    for it in getattr(req, "mm_inputs", None) or ():     # same placeholders, other pixels
-                        extra += it.hash.encode()
-                    hashes = self.pool.block_hashes(req.prompt_token_ids, extra)
+                    extra = BlockPool.request_key_extra(req)
+                    hashes = [] if extra is None else self.pool.block_hashes(req.prompt_token_ids, extra)
                     self._hashes[req.request_id] = hashes
                 # never treat the whole prompt as cached: the last token must be computed
                 max_hit = (req.num_prompt_tokens - 1) // self.block_size

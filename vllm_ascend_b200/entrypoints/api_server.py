@@ -25,7 +25,7 @@ from typing import Optional
 from fastapi import FastAPI, HTTPException
 from fastapi.responses import PlainTextResponse
 
-from ..engine.request import RequestStatus, SamplingParams
+from ..engine.request import RequestError, RequestStatus, SamplingParams
 
 _FINISH = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
            RequestStatus.FINISHED_ABORTED: "abort"}
@@ -70,6 +70,14 @@ class EngineLoop(threading.Thread):
                 continue
             try:
                 eng.step()
+            except RequestError as e:            # one request's fault: abort it, keep serving the others
+                eng.scheduler.abort_request(e.request_id)
+                self.streams.pop(e.request_id, None)
+                w = self.waiters.pop(e.request_id, None)
+                eng.scheduler.requests.pop(e.request_id, None)
+                if w is not None:
+                    w[1].call_soon_threadsafe(w[0].set_exception, ValueError(str(e)))
+                continue
             except BaseException as e:           # fail every waiter, stop serving
                 self.error = e
                 for fut, loop, _ in self.waiters.values():
@@ -115,6 +123,13 @@ def _sampling_params(body: dict) -> SamplingParams:
         lp = int(body.get("top_logprobs") or 0) if lp else None
     if int(body.get("n") or 1) != 1:
         raise HTTPException(400, "n > 1 is served by LLM.generate; the HTTP server returns one choice per request")
+    try:
+        return _sampling_params_unchecked(body, lp)
+    except (ValueError, TypeError) as e:
+        raise HTTPException(400, f"bad sampling parameters: {e}")
+
+
+def _sampling_params_unchecked(body: dict, lp) -> SamplingParams:
     return SamplingParams(
         max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
         temperature=float(body.get("temperature", 1.0)),

@@ -116,8 +116,13 @@ class RejectionSampler:
         self.stats = {"drafted": 0, "accepted": 0, "steps": 0}
 
     def __call__(self, draft_ids, cu_draft, target_logits, bonus_ids, is_greedy, temperature, max_spec,
-                 draft_probs=None, generator=None):
-        """target_logits: [N, V] rows of the draft positions (fp32)."""
+                 draft_probs=None, generator=None, target_probs=None, seeds=None, offsets=None):
+        """target_logits: [N, V] rows of the draft positions (fp32), after the request's logit
+        processors and penalties.  ``target_probs``: the distribution the sampler would draw from at
+        those rows (temperature, top-k / top-p / min-p applied); softmax(logits / T) when absent.
+        ``seeds`` / ``offsets`` (int64 [B]: request seed, tokens sampled so far): the acceptance
+        uniforms and the recovered-token race come from the request's own counter-based stream, the
+        same in every tensor-parallel process; otherwise from ``generator``."""
         target_argmax = target_logits.argmax(-1).to(torch.int32)
         all_greedy = bool(is_greedy.all())
         probs = uniform = noise = None
@@ -125,10 +130,22 @@ class RejectionSampler:
             N, V = target_logits.shape
             B = bonus_ids.shape[0]
             counts = (cu_draft[1:] - cu_draft[:-1]).long()
-            t_rows = torch.repeat_interleave(temperature.float().clamp(min=1e-5), counts)
-            probs = torch.softmax(target_logits.float() / t_rows[:, None], dim=-1).contiguous()
-            uniform = torch.rand(N, device=probs.device, generator=generator)
-            noise = torch.empty(B, V, device=probs.device).exponential_(generator=generator)
+            if target_probs is not None:
+                probs = target_probs.float().contiguous()
+            else:
+                t_rows = torch.repeat_interleave(temperature.float().clamp(min=1e-5), counts)
+                probs = torch.softmax(target_logits.float() / t_rows[:, None], dim=-1).contiguous()
+            if seeds is not None:
+                from . import rng
+                off = offsets if offsets is not None else torch.zeros_like(seeds)
+                row_seed = torch.repeat_interleave(seeds, counts)
+                within = torch.arange(N, device=probs.device) - torch.repeat_interleave(cu_draft[:-1].long(), counts)
+                row_off = torch.repeat_interleave(off, counts) + within
+                uniform = rng.uniform(rng.stream_keys(row_seed, row_off, rng.TAG_ACCEPT)).contiguous()
+                noise = rng.exponential(rng.stream_keys(seeds, off, rng.TAG_RECOVER), V).contiguous()
+            else:
+                uniform = torch.rand(N, device=probs.device, generator=generator)
+                noise = torch.empty(B, V, device=probs.device).exponential_(generator=generator)
             if self.method != "standard":
                 uniform = self._reshape_uniform(draft_ids, cu_draft, probs, draft_probs, uniform, is_greedy)
         out, num = rejection_sample(draft_ids, cu_draft, target_argmax, bonus_ids, probs, draft_probs, uniform,

@@ -7,10 +7,38 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional
 
+import hashlib
+
 import numpy as np
 import torch
 
 from .. import ops
+
+
+def request_seed(req, base_seed: int = 0) -> int:
+    """Seed of a request's random stream.  A request that names a seed uses it; otherwise the seed is
+    a digest of (engine seed, request id) that is the same in every process: tensor- and
+    expert-parallel ranks sample independently from identical logits and must draw identical tokens
+    (Python's ``hash`` of a string differs from process to process)."""
+    sp = req.sampling_params
+    if sp.seed is not None:
+        return int(sp.seed) & ((1 << 62) - 1)
+    s = getattr(req, "_sample_seed", None)
+    if s is None:
+        h = hashlib.blake2b(f"{int(base_seed)}/{req.request_id}".encode(), digest_size=8).digest()
+        s = int.from_bytes(h, "little") & ((1 << 62) - 1)
+        try:
+            req._sample_seed = s
+        except AttributeError:
+            pass
+    return s
+
+
+def tokens_sampled_so_far(req) -> int:
+    """Position of the next token in the request's random stream: tokens already received plus the
+    ones sampled by steps still running on the GPU (asynchronous scheduling builds step N+1 before
+    step N's token is read back)."""
+    return int(req.num_output_tokens) + int(getattr(req, "num_inflight", 0))
 
 
 @dataclass
@@ -49,10 +77,8 @@ class SamplingMetadata:
             top_p=f32([sp.top_p for sp in sps]),
             min_p=f32([sp.min_p for sp in sps]) if any(sp.min_p > 0 for sp in sps) else None,
         )
-        seeds = [(sp.seed if sp.seed is not None else (base_seed * 1000003 + hash(r.request_id)) & ((1 << 62) - 1))
-                 for sp, r in zip(sps, reqs)]
-        md.seeds = torch.tensor(seeds, dtype=torch.int64, device=device)
-        md.offsets = torch.tensor([r.num_output_tokens for r in reqs], dtype=torch.int64, device=device)
+        md.seeds = torch.tensor([request_seed(r, base_seed) for r in reqs], dtype=torch.int64, device=device)
+        md.offsets = torch.tensor([tokens_sampled_so_far(r) for r in reqs], dtype=torch.int64, device=device)
         if any(sp.has_penalties for sp in sps):
             md.has_penalties = True
             Lp = max(r.num_prompt_tokens for r in reqs)
@@ -84,8 +110,12 @@ def _build_processors(reqs: list, device, vocab_size: int) -> dict:
         if sp.allowed_token_ids:
             if allowed is None:
                 allowed = torch.ones((len(reqs), vocab_size), dtype=torch.bool)
+            ids = torch.as_tensor(sp.allowed_token_ids, dtype=torch.long)
+            if int(ids.min()) < 0 or int(ids.max()) >= vocab_size:
+                from ..engine.request import RequestError
+                raise RequestError(r.request_id, f"allowed_token_ids outside [0, {vocab_size})")
             allowed[i] = False
-            allowed[i, torch.as_tensor(sp.allowed_token_ids, dtype=torch.long)] = True
+            allowed[i, ids] = True
         g = getattr(r, "guided", None)
         if g is not None:
             # structured output: tokens that keep the text inside the request's language
@@ -101,7 +131,7 @@ def _build_processors(reqs: list, device, vocab_size: int) -> dict:
             if k == 0 or (len(out) >= k and list(out[-k:]) == seq[:-1]):
                 ban_r.append(i)
                 ban_c.append(seq[-1])
-        if sp.min_tokens > 0 and r.num_output_tokens < sp.min_tokens:
+        if sp.min_tokens > 0 and tokens_sampled_so_far(r) < sp.min_tokens:
             stops = set(sp.stop_token_ids or ())
             if r.eos_token_id is not None and not sp.ignore_eos:
                 stops.add(r.eos_token_id)
@@ -138,8 +168,10 @@ def compute_logprobs(logits: torch.Tensor, tokens: torch.Tensor, k: int):
 
 
 class Sampler:
-    def __call__(self, logits: torch.Tensor, md: SamplingMetadata) -> torch.Tensor:
-        """logits [B, V] (bf16 or fp32) -> token ids int64 [B]."""
+    def apply_processors(self, logits: torch.Tensor, md: SamplingMetadata) -> torch.Tensor:
+        """Allowed-token masks, banned tokens, additive biases and the repetition / frequency /
+        presence penalties.  Returns ``logits`` itself when the step has none of them, otherwise a
+        new fp32 tensor."""
         if md.allowed_mask is not None or md.ban_index is not None or md.bias_index is not None:
             logits = logits.float()
             if md.allowed_mask is not None:
@@ -150,13 +182,41 @@ class Sampler:
                 logits[md.ban_index[0], md.ban_index[1]] = float("-inf")
             if md.bias_index is not None:
                 logits.index_put_((md.bias_index[0], md.bias_index[1]), md.bias_values, accumulate=True)
+        if md.has_penalties and not md.all_greedy:
+            lf = ops.to_float_logits(logits)
+            if lf is logits:
+                lf = logits.clone()
+            logits = ops.apply_penalties(lf, md.prompt_ids, md.output_ids, md.repetition_penalty,
+                                         md.frequency_penalty, md.presence_penalty)
+        return logits
+
+    def filtered_probs(self, processed_logits: torch.Tensor, md: SamplingMetadata, rows: torch.Tensor) -> torch.Tensor:
+        """Distribution the sampler draws from at the given rows (after temperature and
+        top-k / top-p / min-p) of already processed logits: the target distribution of speculative
+        verification (vllm_ascend/sample/rejection_sampler.py:232 filters the target logits the same
+        way before rejection)."""
+        from ..ops import reference as ref
+        t = md.temperature[rows].clamp(min=1e-5).unsqueeze(1)
+        probs = torch.softmax(processed_logits.float() / t, dim=-1)
+        probs = ref.top_k_top_p_filter(probs, md.top_k[rows].to(torch.int64), md.top_p[rows],
+                                       None if md.min_p is None else md.min_p[rows])
+        return (probs / probs.sum(dim=-1, keepdim=True).clamp(min=1e-30)).contiguous()
+
+    def sample_processed(self, logits: torch.Tensor, md: SamplingMetadata) -> torch.Tensor:
+        """Draw from logits that already went through ``apply_processors`` (destroys them on CUDA)."""
         if md.all_greedy:
             return ops.argmax(logits)
         lf = ops.to_float_logits(logits)
+        return ops.sample(lf, md.temperature, md.top_k, md.top_p, md.min_p, md.seeds, md.offsets,
+                          md.generator)
+
+    def __call__(self, logits: torch.Tensor, md: SamplingMetadata) -> torch.Tensor:
+        """logits [B, V] (bf16 or fp32) -> token ids int64 [B]."""
+        processed = self.apply_processors(logits, md)
+        if md.all_greedy:
+            return ops.argmax(processed)
+        lf = ops.to_float_logits(processed)
         if lf is logits:
             lf = logits.clone()
-        if md.has_penalties:
-            lf = ops.apply_penalties(lf, md.prompt_ids, md.output_ids, md.repetition_penalty,
-                                     md.frequency_penalty, md.presence_penalty)
         return ops.sample(lf, md.temperature, md.top_k, md.top_p, md.min_p, md.seeds, md.offsets,
                           md.generator)
