@@ -63,6 +63,25 @@ def timeit(fn, iters=20, warm=5, flush=True):
     return ts[len(ts) // 2]
 
 
+def timeit_between(fn, between, iters=20, warm=5):
+    """Median device time of ``fn`` when ``between`` (untimed) runs before every timed launch."""
+    for _ in range(warm):
+        between()
+        fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(iters):
+        between()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        evs.append((e0, e1))
+    torch.cuda.synchronize()
+    ts = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
+    return ts[len(ts) // 2]
+
+
 def bench_gemm(a):
     M, N, K = a.m, a.n, a.k
     x = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
@@ -104,12 +123,27 @@ def bench_gemm_fp8(a):
 def bench_attn_decode(a):
     from gpu_utils import make_paged_case
     B, ctx = a.batch, a.ctx
-    q, kc, vc, meta = make_paged_case([1] * B, [ctx - 1] * B, a.hq, a.hkv, a.d, a.block_size, seed=0,
+    if a.ragged:
+        # serving-like batch: context lengths spread over +-ragged tokens around ctx
+        import numpy as np
+        lens = np.random.default_rng(0).integers(ctx - a.ragged, ctx + a.ragged, size=B)
+        ctxs = [int(x) - 1 for x in lens]
+    else:
+        ctxs = [ctx - 1] * B
+    q, kc, vc, meta = make_paged_case([1] * B, ctxs, a.hq, a.hkv, a.d, a.block_size, seed=0,
                                       layout=a.kv_layout)
     out = torch.empty_like(q)
     scale = a.d ** -0.5
     meta.tile_seq = meta.tile_qoff = None
-    bytes_kv = 2.0 * B * ctx * a.hkv * a.d * 2
+    bytes_kv = 2.0 * float(sum(c + 1 for c in ctxs)) * a.hkv * a.d * 2
+    between = None
+    if a.interleave_gemm:
+        # a compute-bound GEMM between the timed launches keeps the GPU at its power cap, the
+        # clock regime the kernel meets inside a serving step
+        ga = torch.randn(8192, 4096, device="cuda", dtype=torch.bfloat16)
+        gb = torch.randn(12288, 4096, device="cuda", dtype=torch.bfloat16)
+        gout = torch.empty(8192, 12288, device="cuda", dtype=torch.bfloat16)
+        between = lambda: [ops.linear(ga, gb, out=gout) for _ in range(a.interleave_gemm)]
     hbm, tf, tag = peaks()
     for name, fn in (
         ("cuda-core", lambda ns: ops.paged_decode(q, kc, vc, meta.block_table, meta.seq_lens, scale, out, 0, ns)),
@@ -121,8 +155,9 @@ def bench_attn_decode(a):
         if name == "cuda-core" and a.kv_layout != "NHD":
             continue        # that kernel reads [blocks, tokens, heads, D] caches only
         ns = a.splits or ops.choose_num_splits(B, a.hkv, ctx)
-        ms = timeit(lambda: fn(ns), a.iters)
-        print(f"attn-decode[{name}/{a.kv_layout}] B={B} ctx={ctx} Hq={a.hq} Hkv={a.hkv} D={a.d} splits={ns}: "
+        ms = timeit(lambda: fn(ns), a.iters) if between is None else timeit_between(lambda: fn(ns), between, a.iters)
+        print(f"attn-decode[{name}/{a.kv_layout}] B={B} ctx={ctx}{' ragged' if a.ragged else ''}"
+              f"{' between GEMMs' if between else ''} Hq={a.hq} Hkv={a.hkv} D={a.d} splits={ns}: "
               f"{ms:.4f} ms  {bytes_kv / ms / 1e6:.0f} GB/s ({bytes_kv / ms / 1e6 / hbm:.2f} {tag})",
               flush=True)
     _native.check_status(torch.device("cuda"))
@@ -237,6 +272,9 @@ def main():
     ap.add_argument("--inter", type=int, default=12288)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--kv-layout", default="HND", choices=["NHD", "HND"])
+    ap.add_argument("--ragged", type=int, default=0, help="attn-decode: spread of the context lengths (+-tokens)")
+    ap.add_argument("--interleave-gemm", type=int, default=0,
+                    help="attn-decode: run this many large GEMMs (untimed) between the timed launches")
     a = ap.parse_args()
     if a.what in ("gemm", "all"):
         if a.what == "all":

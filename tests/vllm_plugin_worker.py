@@ -1,0 +1,64 @@
+"""Child process of tests/test_vllm_plugin.py: runs upstream ``vllm.LLM`` with this package as the
+platform plugin and prints what the test checks as one JSON line.
+
+argv: <site dir with the installed distribution or ''> <model dir> <dtype> <mode>
+mode: 'sync' | 'async' | 'preempt'"""
+import json
+import os
+import sys
+
+site_dir, model_dir, dtype, mode = sys.argv[1:5]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+os.environ["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"
+os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
+if site_dir:
+    import site
+    site.addsitedir(site_dir)            # processes the editable install's .pth file
+else:
+    sys.path.insert(0, ROOT)
+    from vllm_ascend_b200.vllm_plugin import ensure_entry_points
+    ensure_entry_points()
+
+import numpy as np
+import torch
+from vllm import LLM, SamplingParams
+from vllm.platforms import current_platform
+
+kw = dict(model=model_dir, load_format="dummy", skip_tokenizer_init=True, dtype=dtype, max_model_len=256,
+          max_num_seqs=8, max_num_batched_tokens=64, enable_prefix_caching=False, seed=0,
+          async_scheduling=(mode == "async"))
+if mode == "preempt":
+    kw["num_gpu_blocks_override"] = 4 if torch.cuda.is_available() else 20     # too few for every request to finish
+llm = LLM(**kw)
+rng = np.random.default_rng(0)
+lens = (20, 70, 33, 5) if mode != "preempt" else (40, 44, 36, 48)
+prompts = [rng.integers(0, 1024, size=n).tolist() for n in lens]
+n_out = 8 if mode != "preempt" else 40
+outs = llm.generate([{"prompt_token_ids": p} for p in prompts],
+                    SamplingParams(temperature=0.0, max_tokens=n_out, ignore_eos=True), use_tqdm=False)
+got = [list(o.outputs[0].token_ids) for o in outs]
+
+# the worker vLLM constructed
+core = llm.llm_engine.engine_core.engine_core
+worker = core.model_executor.driver_worker.worker
+stats = dict(worker.stats)
+
+# the same prompts through this package's own engine: same architecture, same seed, same weights
+from vllm_ascend_b200 import _native
+from vllm_ascend_b200.config import ModelConfig
+from vllm_ascend_b200.engine.llm import LLM as OwnLLM
+from vllm_ascend_b200.engine.request import SamplingParams as OwnSP
+launches_under_vllm = int(_native.launch_counter[0]) + int(worker.runner.stats.get("graph_kernel_launches", 0))
+cfg = ModelConfig.from_hf_dict(json.load(open(os.path.join(model_dir, "config.json"))), dtype=dtype)
+cfg.name = os.path.basename(os.path.normpath(model_dir))
+own = OwnLLM(cfg, max_model_len=256, max_num_seqs=8, max_num_batched_tokens=64, seed=0,
+             block_size=worker.cfg.cache.block_size)
+want = [o.outputs[0].token_ids for o in own.generate(prompts, OwnSP(temperature=0.0, max_tokens=n_out,
+                                                                    ignore_eos=True))]
+maps = open("/proc/self/maps").read()
+print("RESULT " + json.dumps({
+    "platform": type(current_platform).__name__, "worker": type(worker).__name__, "got": got, "want": want,
+    "stats": stats, "native_mapped": "vllm_ascend_b200/_C.so" in maps, "launches": launches_under_vllm,
+    "device": str(worker.device), "async": bool(worker._async),
+    "installed": bool(site_dir)}), flush=True)
+os._exit(0)

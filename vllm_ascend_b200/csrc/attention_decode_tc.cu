@@ -44,8 +44,9 @@ struct DecParams {
   float* partial_o;
   float* partial_lse;
   long num_blocks_total;
+  int num_seqs, num_items;   // items = Hkv x sequences x splits
   int* status;
-  long long* timeline;   // optional [3 roles][64 tiles][8 stamps] of clock64, CTA (0,0,0) only
+  long long* timeline;   // optional [3 roles][64 tiles][8 stamps] of clock64, CTA 0 only
 };
 
 template <int D>
@@ -57,15 +58,15 @@ struct DecCfg {
   static constexpr int P_BYTES = 2 * DEC_QHALF;     // one P buffer (two 64-key halves)
   static constexpr int P_BUFS = 2;                  // double-buffered so P(j+1) overlaps PV(j)
   static constexpr int SMEM_BYTES =
-      2 * STAGES * TILE_BYTES + Q_BYTES + P_BUFS * P_BYTES + 1024 + 1024;
+      2 * STAGES * TILE_BYTES + 2 * Q_BYTES + P_BUFS * P_BYTES + 1024 + 1024;
   static constexpr int TMEM_COLS = 64;
-  static constexpr int O_COL = 32;
+  static constexpr int O_COL = 32;                  // two O^T accumulators: columns 32..47, 48..63
 };
 
 // Device-side timeline: stamp k of tile j for a role (0 producer, 1 MMA issuer, 2 softmax).
 #define DEC_STAMP(role, j, k)                                                            \
   do {                                                                                 \
-    if (tl && (j) < 64) tl[((role) * 64 + (j)) * 8 + (k)] = clock64() - tl_t0;          \
+    if (tl && (j) < 64u) tl[((role) * 64 + (j)) * 8 + (k)] = clock64() - tl_t0;         \
   } while (0)
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -76,6 +77,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// One work item = (KV head, sequence, KV split).  The kernel is persistent: CTA b serves items
+// b, b + gridDim.x, ... and the three roles keep running tile / item counters, so barrier
+// initialisation, the TMEM allocation and the pipeline fill are paid once per CTA, the K/V
+// stream of the next item is already in flight while the current item's epilogue runs, and
+// a short item (a few tiles) costs no more than its bytes.
+struct DecItem {
+  int h, seq, split;
+  int q_start, q_len, seq_len, ctx, t0, n;
+};
+
+__device__ __forceinline__ DecItem dec_item(const DecParams& p, int item) {
+  DecItem w;
+  w.h = item % p.Hkv;
+  const int r = item / p.Hkv;
+  w.seq = r % p.num_seqs;
+  w.split = r / p.num_seqs;
+  w.q_start = p.query_start_loc[w.seq];
+  w.q_len = p.query_start_loc[w.seq + 1] - w.q_start;
+  w.seq_len = p.seq_lens[w.seq];
+  w.ctx = w.seq_len - w.q_len;
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, w.ctx - p.window + 1);
+  const int tile_lo = kv_lo >> 7, tile_hi = (w.seq_len + 127) >> 7;
+  const int n_all = tile_hi - tile_lo;
+  const int per_split = (n_all + p.num_splits - 1) / p.num_splits;
+  w.t0 = tile_lo + w.split * per_split;
+  w.n = w.q_len > 0 ? max(0, min(tile_hi, w.t0 + per_split) - w.t0) : 0;
+  return w;
+}
+
 template <int D, int NVT>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -83,50 +114,21 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_v, const DecParams p) {
   using Cfg = DecCfg<D>;
   constexpr int NH = Cfg::NH, ST = Cfg::STAGES;
-
-  // heads of one sequence run side by side so neighbouring KV bytes are fetched together
-  const int h = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
-  const int q_start = p.query_start_loc[seq];
-  const int q_len = p.query_start_loc[seq + 1] - q_start;
-  const int seq_len = p.seq_lens[seq];
-  const int ctx = seq_len - q_len;
   const int G = p.G;
-  const int nv = q_len * G;                 // valid columns (<= 16)
-  if (q_len <= 0) return;
-  int kv_lo = 0;
-  if (p.window > 0) kv_lo = max(0, ctx - p.window + 1);
-  const int tile_lo = kv_lo >> 7, tile_hi = (seq_len + 127) >> 7;
-  const int n_all = tile_hi - tile_lo;
-  const int per_split = (n_all + p.num_splits - 1) / p.num_splits;
-  const int t0 = tile_lo + split * per_split;
-  const int t1 = min(tile_hi, t0 + per_split);
-  const int n = t1 - t0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  long long* tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0)
-                      ? p.timeline : nullptr;
+  long long* tl = (p.timeline && blockIdx.x == 0 && lane == 0) ? p.timeline : nullptr;
   const long long tl_t0 = clock64();
-
-  if (n <= 0) {
-    if (p.num_splits > 1) {
-      for (int c = threadIdx.x; c < nv; c += blockDim.x) {
-        const long pidx =
-            ((long)(q_start + c / G) * p.Hq + (h * G + c % G)) * p.num_splits + split;
-        p.partial_lse[pidx] = -INFINITY;
-        for (int d = 0; d < D; d++) p.partial_o[pidx * D + d] = 0.f;
-      }
-    }
-    return;
-  }
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* Ks = smem;
   uint8_t* Vs = Ks + ST * Cfg::TILE_BYTES;
-  uint8_t* Qs = Vs + ST * Cfg::TILE_BYTES;
-  uint8_t* Ps = Qs + Cfg::Q_BYTES;
+  uint8_t* Qs = Vs + ST * Cfg::TILE_BYTES;          // two Q buffers
+  uint8_t* Ps = Qs + 2 * Cfg::Q_BYTES;
   uint64_t* bars = (uint64_t*)(Ps + Cfg::P_BUFS * Cfg::P_BYTES);
-  uint64_t* q_full = bars;            // 1
-  uint64_t* k_full = bars + 1;        // ST
+  uint64_t* q_full = bars;            // 2
+  uint64_t* q_empty = q_full + 2;     // 2
+  uint64_t* k_full = q_empty + 2;     // ST
   uint64_t* k_empty = k_full + ST;    // ST
   uint64_t* v_full = k_empty + ST;    // ST
   uint64_t* v_empty = v_full + ST;    // ST
@@ -134,23 +136,27 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint64_t* s_free = s_ready + 2;     // 2
   uint64_t* p_ready = s_free + 2;     // 2 (per P buffer)
   uint64_t* pv_done = p_ready + 2;    // 2 (per P buffer)
-  uint32_t* tmem_ptr = (uint32_t*)(pv_done + 2);
+  uint64_t* o_free = pv_done + 2;     // 2 (per O accumulator)
+  uint32_t* tmem_ptr = (uint32_t*)(o_free + 2);
   volatile int* abort_word = (volatile int*)(tmem_ptr + 1);
-  float* red = (float*)(tmem_ptr + 2);            // [4 warps][16]
+  float* red = (float*)(tmem_ptr + 2);            // [2 tiles][4 warps][16] maxima
+  float* red_sum = red + 128;                     // [4 warps][16] row sums of the epilogue
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int b = 0; b < 2; b++) {
+      mbar_init(&q_full[b], 1);
+      mbar_init(&q_empty[b], 1);
+      mbar_init(&s_ready[b], 1);
+      mbar_init(&s_free[b], 4);
+      mbar_init(&p_ready[b], 4);
+      mbar_init(&pv_done[b], 1);
+      mbar_init(&o_free[b], 4);
+    }
     for (int s = 0; s < ST; s++) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
-    }
-    for (int b = 0; b < 2; b++) {
-      mbar_init(&s_ready[b], 1);
-      mbar_init(&s_free[b], 4);
-      mbar_init(&p_ready[b], 4);
-      mbar_init(&pv_done[b], 1);
     }
     *abort_word = 0;
     mbar_fence_init();
@@ -168,118 +174,143 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
+  const int num_items = p.num_items;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    const int* bt = p.block_table + (long)seq * p.max_blocks;
     const int rpl = p.rows_per_load;
     const int parts = 128 / rpl;
-    if (lane == 0) {
-      mbar_expect_tx(q_full, Cfg::Q_BYTES);
+    uint32_t gt = 0, it = 0;             // tiles / items issued so far by this CTA
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const DecItem w = dec_item(p, item);
+      if (w.n <= 0) continue;
+      const int* bt = p.block_table + (long)w.seq * p.max_blocks;
+      const int qb = it & 1;
+      if (!mbar_wait(&q_empty[qb], ((it >> 1) & 1u) ^ 1u, abort_word)) goto done;
+      if (lane == 0) {
+        mbar_expect_tx(&q_full[qb], Cfg::Q_BYTES);
 #pragma unroll
-      for (int hf = 0; hf < NH; hf++)
-        tma_load_4d(Qs + hf * DEC_QHALF, &tmap_q, q_full, hf * 64, 0, h, q_start);
-    }
-    // Block ids are fetched one tile ahead (lane p holds the id of part p), so the
-    // dependent global load never sits between a freed stage and the next TMA issue.
-    auto load_blk = [&](int j) -> int {
-      if (j >= n || lane >= parts) return 0;
-      const int key0 = ((t0 + j) << 7) + lane * rpl;
-      return bt[min(key0, seq_len - 1) / p.block_size];
-    };
-    int blk_cur = load_blk(0);
-    for (int j = 0; j < n; j++) {
-      const int st = j % ST;
-      const uint32_t ph = (uint32_t)(j / ST) & 1u;
-      const int key_base = (t0 + j) << 7;
-      const int blk_next = load_blk(j + 1);
-      bool bad = blk_cur < 0 || blk_cur >= p.num_blocks_total;
-      bad = __any_sync(0xffffffffu, bad && lane < parts);
-#pragma unroll 1
-      for (int kv = 0; kv < 2; kv++) {
-        uint64_t* fullb = kv == 0 ? &k_full[st] : &v_full[st];
-        uint64_t* emptyb = kv == 0 ? &k_empty[st] : &v_empty[st];
-        if (!mbar_wait(emptyb, ph ^ 1u, abort_word)) goto done;
-        DEC_STAMP(0, j, kv);
-        if (bad) {
-          *abort_word = B200_BAD_INDEX;
-          goto done;
-        }
-        for (int part = 0; part < parts; part++) {
-          const int blk = __shfl_sync(0xffffffffu, blk_cur, part);
-          if (lane == 0) {
-            uint8_t* dst = (kv == 0 ? Ks : Vs) + st * Cfg::TILE_BYTES;
-            const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
-            if (part == 0) mbar_expect_tx(fullb, Cfg::TILE_BYTES);
-            const int off = (key_base + part * rpl) % p.block_size;
-#pragma unroll
-            for (int hf = 0; hf < NH; hf++)
-              tma_load_4d(dst + hf * DEC_HALF + part * rpl * 128, tm, fullb, hf * 64, h, off, blk);
-          }
-        }
-        __syncwarp();
+        for (int hf = 0; hf < NH; hf++)
+          tma_load_4d(Qs + qb * Cfg::Q_BYTES + hf * DEC_QHALF, &tmap_q, &q_full[qb], hf * 64, 0, w.h,
+                      w.q_start);
       }
-      blk_cur = blk_next;
+      // Block ids are fetched one tile ahead (lane p holds the id of part p), so the
+      // dependent global load never sits between a freed stage and the next TMA issue.
+      auto load_blk = [&](int j) -> int {
+        if (j >= w.n || lane >= parts) return 0;
+        const int key0 = ((w.t0 + j) << 7) + lane * rpl;
+        return bt[min(key0, w.seq_len - 1) / p.block_size];
+      };
+      int blk_cur = load_blk(0);
+      for (int j = 0; j < w.n; j++, gt++) {
+        const int st = gt % ST;
+        const uint32_t ph = (gt / ST) & 1u;
+        const int key_base = (w.t0 + j) << 7;
+        const int blk_next = load_blk(j + 1);
+        bool bad = blk_cur < 0 || blk_cur >= p.num_blocks_total;
+        bad = __any_sync(0xffffffffu, bad && lane < parts);
+#pragma unroll 1
+        for (int kv = 0; kv < 2; kv++) {
+          uint64_t* fullb = kv == 0 ? &k_full[st] : &v_full[st];
+          uint64_t* emptyb = kv == 0 ? &k_empty[st] : &v_empty[st];
+          if (!mbar_wait(emptyb, ph ^ 1u, abort_word)) goto done;
+          DEC_STAMP(0, gt, kv);
+          if (bad) {
+            *abort_word = B200_BAD_INDEX;
+            goto done;
+          }
+          for (int part = 0; part < parts; part++) {
+            const int blk = __shfl_sync(0xffffffffu, blk_cur, part);
+            if (lane == 0) {
+              uint8_t* dst = (kv == 0 ? Ks : Vs) + st * Cfg::TILE_BYTES;
+              const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
+              if (part == 0) mbar_expect_tx(fullb, Cfg::TILE_BYTES);
+              const int off = (key_base + part * rpl) % p.block_size;
+#pragma unroll
+              for (int hf = 0; hf < NH; hf++)
+                tma_load_4d(dst + hf * DEC_HALF + part * rpl * 128, tm, fullb, hf * 64, w.h, off, blk);
+            }
+          }
+          __syncwarp();
+        }
+        blk_cur = blk_next;
+      }
+      it++;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_s = make_idesc_f16(128, DEC_NQ, true, false, false);
     constexpr uint32_t idesc_o = make_idesc_f16(D, DEC_NQ, true, true, false);   // A = V, MN-major
-    const uint32_t q_addr = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
+    const uint32_t q_addr0 = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
                    p_addr = smem_u32(Ps);
-    if (!mbar_wait(q_full, 0, abort_word)) goto done;
-    auto issue_s = [&](int j) -> bool {
-      const int st = j % ST;
-      const uint32_t ph = (uint32_t)(j / ST) & 1u;
-      const int b = j & 1;
-      if (!mbar_wait(&k_full[st], ph, abort_word)) return false;
-      DEC_STAMP(1, j, 0);
-      if (!mbar_wait(&s_free[b], (((uint32_t)j >> 1) & 1u) ^ 1u, abort_word)) return false;
-      tc_fence_after();
-      if (lane == 0) {
+    uint32_t gt = 0, it = 0;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const DecItem w = dec_item(p, item);
+      if (w.n <= 0) continue;
+      const int qb = it & 1;
+      const uint32_t q_addr = q_addr0 + qb * Cfg::Q_BYTES;
+      const uint32_t o_col = Cfg::O_COL + qb * DEC_NQ;
+      if (!mbar_wait(&q_full[qb], (it >> 1) & 1u, abort_word)) goto done;
+      // the accumulator of two items ago has been read out by its epilogue
+      if (!mbar_wait(&o_free[qb], ((it >> 1) & 1u) ^ 1u, abort_word)) goto done;
+      auto issue_s = [&](int j) -> bool {
+        const uint32_t g = gt + (uint32_t)j;
+        const int st = g % ST;
+        const uint32_t ph = (g / ST) & 1u;
+        const int b = g & 1;
+        if (!mbar_wait(&k_full[st], ph, abort_word)) return false;
+        DEC_STAMP(1, g, 0);
+        if (!mbar_wait(&s_free[b], ((g >> 1) & 1u) ^ 1u, abort_word)) return false;
+        tc_fence_after();
+        if (lane == 0) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; kk++) {
-          const uint64_t da = make_smem_desc(
-              k_addr + st * Cfg::TILE_BYTES + (kk >> 2) * DEC_HALF + (kk & 3) * 32, 16, 1024,
-              kLayoutSw128);
-          const uint64_t db = make_smem_desc(q_addr + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16,
-                                             1024, kLayoutSw128);
-          umma_f16_ss(tmem_base + b * DEC_NQ, da, db, idesc_s, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < D / 16; kk++) {
+            const uint64_t da = make_smem_desc(
+                k_addr + st * Cfg::TILE_BYTES + (kk >> 2) * DEC_HALF + (kk & 3) * 32, 16, 1024,
+                kLayoutSw128);
+            const uint64_t db = make_smem_desc(q_addr + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16,
+                                               1024, kLayoutSw128);
+            umma_f16_ss(tmem_base + b * DEC_NQ, da, db, idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&k_empty[st]);
+          umma_commit(&s_ready[b]);
+          if (j == w.n - 1) umma_commit(&q_empty[qb]);     // last read of this item's Q
         }
-        umma_commit(&k_empty[st]);
-        umma_commit(&s_ready[b]);
-      }
-      __syncwarp();
-      return true;
-    };
-    if (!issue_s(0)) goto done;
-    for (int j = 0; j < n; j++) {
-      if (j + 1 < n) {
-        if (!issue_s(j + 1)) goto done;
-      }
-      const int st = j % ST;
-      const uint32_t ph = (uint32_t)(j / ST) & 1u;
-      const int pb = j & 1;
-      if (!mbar_wait(&v_full[st], ph, abort_word)) goto done;
-      DEC_STAMP(1, j, 1);
-      if (!mbar_wait(&p_ready[pb], ((uint32_t)j >> 1) & 1u, abort_word)) goto done;
-      DEC_STAMP(1, j, 2);
-      tc_fence_after();
-      if (lane == 0) {
+        __syncwarp();
+        return true;
+      };
+      if (!issue_s(0)) goto done;
+      for (int j = 0; j < w.n; j++) {
+        if (j + 1 < w.n) {
+          if (!issue_s(j + 1)) goto done;
+        }
+        const uint32_t g = gt + (uint32_t)j;
+        const int st = g % ST;
+        const uint32_t ph = (g / ST) & 1u;
+        const int pb = g & 1;
+        if (!mbar_wait(&v_full[st], ph, abort_word)) goto done;
+        DEC_STAMP(1, g, 1);
+        if (!mbar_wait(&p_ready[pb], (g >> 1) & 1u, abort_word)) goto done;
+        DEC_STAMP(1, g, 2);
+        tc_fence_after();
+        if (lane == 0) {
 #pragma unroll
-        for (int kk = 0; kk < 8; kk++) {
-          // A: 16 keys of V^T (two 64-wide d atoms DEC_HALF apart, 8-key groups 1024 B apart)
-          const uint64_t da = make_smem_desc(v_addr + st * Cfg::TILE_BYTES + kk * 2048, DEC_HALF,
-                                             1024, kLayoutSw128);
-          const uint64_t db = make_smem_desc(
-              p_addr + pb * Cfg::P_BYTES + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16, 1024,
-              kLayoutSw128);
-          umma_f16_ss(tmem_base + Cfg::O_COL, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 8; kk++) {
+            // A: 16 keys of V^T (two 64-wide d atoms DEC_HALF apart, 8-key groups 1024 B apart)
+            const uint64_t da = make_smem_desc(v_addr + st * Cfg::TILE_BYTES + kk * 2048, DEC_HALF,
+                                               1024, kLayoutSw128);
+            const uint64_t db = make_smem_desc(
+                p_addr + pb * Cfg::P_BYTES + (kk >> 2) * DEC_QHALF + (kk & 3) * 32, 16, 1024,
+                kLayoutSw128);
+            umma_f16_ss(tmem_base + o_col, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&v_empty[st]);
+          umma_commit(&pv_done[pb]);
         }
-        umma_commit(&v_empty[st]);
-        umma_commit(&pv_done[pb]);
+        __syncwarp();
       }
-      __syncwarp();
+      gt += (uint32_t)w.n;
+      it++;
     }
   } else {
     // ------------------------------------------------------------ softmax / epilogue
@@ -288,137 +319,163 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int tid = qd * 32 + lane;                 // key inside the tile; d index for O^T
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
     const float sl2 = p.scale_log2;
-    float m[NVT], lsum[NVT];
-    int hi[NVT], lo[NVT];                           // keys [lo, hi) are visible to column c
-    int hi_min = seq_len, lo_max = 0;
-#pragma unroll
-    for (int c = 0; c < NVT; c++) {
-      m[c] = -INFINITY;
-      lsum[c] = 0.f;
-      const int q_pos = ctx + min(c / G, q_len - 1);
-      hi[c] = min(seq_len, q_pos + 1);
-      lo[c] = p.window > 0 ? max(0, q_pos - p.window + 1) : 0;
-      hi_min = min(hi_min, hi[c]);
-      lo_max = max(lo_max, lo[c]);
-    }
     int* redi = reinterpret_cast<int*>(red);        // [2 tiles][4 warps][16]
+    uint32_t gt = 0, it = 0;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const DecItem w = dec_item(p, item);
+      const int nv = w.q_len * G;                   // valid columns (<= 16)
+      if (w.n <= 0) {
+        if (p.num_splits > 1 && w.q_len > 0) {      // an empty split still owns its partial slots
+          for (int c = tid; c < nv; c += 128) {
+            const long pidx =
+                ((long)(w.q_start + c / G) * p.Hq + (w.h * G + c % G)) * p.num_splits + w.split;
+            p.partial_lse[pidx] = -INFINITY;
+            for (int d = 0; d < D; d++) p.partial_o[pidx * D + d] = 0.f;
+          }
+        }
+        continue;
+      }
+      const uint32_t o_col = Cfg::O_COL + (it & 1) * DEC_NQ;
+      float m[NVT], lsum[NVT];
+      int hi[NVT], lo[NVT];                           // keys [lo, hi) are visible to column c
+      int hi_min = w.seq_len, lo_max = 0;
+#pragma unroll
+      for (int c = 0; c < NVT; c++) {
+        m[c] = -INFINITY;
+        lsum[c] = 0.f;
+        const int q_pos = w.ctx + min(c / G, w.q_len - 1);
+        hi[c] = min(w.seq_len, q_pos + 1);
+        lo[c] = p.window > 0 ? max(0, q_pos - p.window + 1) : 0;
+        hi_min = min(hi_min, hi[c]);
+        lo_max = max(lo_max, lo[c]);
+      }
 
-    for (int j = 0; j < n; j++) {
-      const int b = j & 1;
-      if (warp == 2) DEC_STAMP(2, j, 0);
-      if (!mbar_wait(&s_ready[b], ((uint32_t)j >> 1) & 1u, abort_word)) goto done;
-      if (warp == 2) DEC_STAMP(2, j, 1);
+      for (int j = 0; j < w.n; j++) {
+        const uint32_t g = gt + (uint32_t)j;
+        const int b = g & 1;
+        if (warp == 2) DEC_STAMP(2, g, 0);
+        if (!mbar_wait(&s_ready[b], (g >> 1) & 1u, abort_word)) goto done;
+        if (warp == 2) DEC_STAMP(2, g, 1);
+        tc_fence_after();
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(t_lane + b * DEC_NQ, r);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[b]);
+        const int tile_base = (w.t0 + j) << 7;
+        const int key = tile_base + tid;
+        // only tiles that straddle a visibility limit need per-key masking
+        const bool need_mask = (tile_base + 128 > hi_min) || (tile_base < lo_max);
+        float s[NVT];
+        int* rj = redi + b * 64 + qd * 16;
+#pragma unroll
+        for (int c = 0; c < NVT; c++) {
+          s[c] = __uint_as_float(r[c]);
+          if (need_mask && !(key >= lo[c] && key < hi[c])) s[c] = -INFINITY;
+          int ob = __float_as_int(s[c]);
+          ob ^= (ob >> 31) & 0x7fffffff;              // order-preserving float -> int
+          const int wm = __reduce_max_sync(0xffffffffu, ob);
+          if (lane == 0) rj[c] = wm;
+        }
+        if (warp == 2) DEC_STAMP(2, g, 5);
+        softmax_bar();
+        if (warp == 2) DEC_STAMP(2, g, 6);
+        const int* ra = redi + b * 64;
+        bool any_change = false;
+        float alpha[NVT];
+#pragma unroll
+        for (int c = 0; c < NVT; c++) {
+          int t = max(max(ra[c], ra[16 + c]), max(ra[32 + c], ra[48 + c]));
+          t ^= (t >> 31) & 0x7fffffff;
+          const float mn = fmaxf(m[c], __int_as_float(t));
+          alpha[c] = 1.f;
+          // lazy rescaling: the reference max only moves when it would grow by more than
+          // 2^kRescaleLog2, so most tiles never touch the O^T accumulator
+          if (mn > m[c] && (m[c] == -INFINITY || (mn - m[c]) * sl2 > kRescaleLog2)) {
+            alpha[c] = (m[c] == -INFINITY) ? 0.f : fast_exp2((m[c] - mn) * sl2);
+            any_change = any_change || (m[c] != -INFINITY);
+            m[c] = mn;
+          }
+          lsum[c] *= alpha[c];
+        }
+        if (warp == 2) DEC_STAMP(2, g, 7);
+        // P buffer g&1 was last read by PV(g-2) (possibly of the previous item)
+        if (g >= 2) {
+          if (!mbar_wait(&pv_done[b], ((g - 2) >> 1) & 1u, abort_word)) goto done;
+        }
+        if (j > 0 && any_change) {    // uniform over the 128 threads: O^T must be quiescent
+          if (!mbar_wait(&pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1u, abort_word)) goto done;
+          tc_fence_after();
+          uint32_t o[16];
+          tmem_ld_32x32b_x16(t_lane + o_col, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < NVT; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c]);
+          tmem_st_32x32b_x16(t_lane + o_col, o);
+          tmem_st_wait();
+        }
+        if (warp == 2) DEC_STAMP(2, g, 2);
+        // probabilities of this key for every column -> P[c][key] (K-major, swizzled)
+        uint8_t* pbase = Ps + b * Cfg::P_BYTES + (tid >> 6) * DEC_QHALF;
+        const int kin = tid & 63;
+#pragma unroll
+        for (int c = 0; c < NVT; c++) {
+          const float mb = (m[c] == -INFINITY) ? 0.f : m[c] * sl2;
+          const float pv = fast_exp2(s[c] * sl2 - mb);
+          lsum[c] += pv;
+          const int chunk = (kin >> 3) ^ (c & 7);
+          *reinterpret_cast<__nv_bfloat16*>(pbase + c * 128 + (chunk << 4) + (kin & 7) * 2) =
+              __float2bfloat16(pv);
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[b]);
+        if (warp == 2) DEC_STAMP(2, g, 3);
+      }
+      gt += (uint32_t)w.n;
+      // ---- epilogue of the item: total row sums, normalise, store
+      {
+        const uint32_t gl = gt - 1;
+        if (!mbar_wait(&pv_done[gl & 1], (gl >> 1) & 1u, abort_word)) goto done;
+      }
       tc_fence_after();
-      uint32_t r[16];
-      tmem_ld_32x32b_x16(t_lane + b * DEC_NQ, r);
+#pragma unroll
+      for (int c = 0; c < NVT; c++) {
+        const float ws = warp_reduce_sum(lsum[c]);
+        if (lane == 0) red_sum[qd * DEC_NQ + c] = ws;
+      }
+      uint32_t o[16];
+      tmem_ld_32x32b_x16(t_lane + o_col, o);
       tmem_ld_wait();
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[b]);
-      const int tile_base = (t0 + j) << 7;
-      const int key = tile_base + tid;
-      // only tiles that straddle a visibility limit need per-key masking
-      const bool need_mask = (tile_base + 128 > hi_min) || (tile_base < lo_max);
-      float s[NVT];
-      int* rj = redi + (j & 1) * 64 + qd * 16;
+      softmax_bar();            // row sums visible; every thread holds its O^T row
+      if (lane == 0) mbar_arrive(&o_free[it & 1]);
+      if (tid < D) {
 #pragma unroll
-      for (int c = 0; c < NVT; c++) {
-        s[c] = __uint_as_float(r[c]);
-        if (need_mask && !(key >= lo[c] && key < hi[c])) s[c] = -INFINITY;
-        int ob = __float_as_int(s[c]);
-        ob ^= (ob >> 31) & 0x7fffffff;              // order-preserving float -> int
-        const int wm = __reduce_max_sync(0xffffffffu, ob);
-        if (lane == 0) rj[c] = wm;
-      }
-      if (warp == 2) DEC_STAMP(2, j, 5);
-      softmax_bar();
-      if (warp == 2) DEC_STAMP(2, j, 6);
-      const int* ra = redi + (j & 1) * 64;
-      bool any_change = false;
-      float alpha[NVT];
-#pragma unroll
-      for (int c = 0; c < NVT; c++) {
-        int t = max(max(ra[c], ra[16 + c]), max(ra[32 + c], ra[48 + c]));
-        t ^= (t >> 31) & 0x7fffffff;
-        const float mn = fmaxf(m[c], __int_as_float(t));
-        alpha[c] = 1.f;
-        // lazy rescaling: the reference max only moves when it would grow by more than
-        // 2^kRescaleLog2, so most tiles never touch the O^T accumulator
-        if (mn > m[c] && (m[c] == -INFINITY || (mn - m[c]) * sl2 > kRescaleLog2)) {
-          alpha[c] = (m[c] == -INFINITY) ? 0.f : fast_exp2((m[c] - mn) * sl2);
-          any_change = any_change || (m[c] != -INFINITY);
-          m[c] = mn;
-        }
-        lsum[c] *= alpha[c];
-      }
-      if (warp == 2) DEC_STAMP(2, j, 7);
-      // P buffer j&1 was last read by PV(j-2)
-      if (j >= 2) {
-        if (!mbar_wait(&pv_done[j & 1], (((uint32_t)j - 2) >> 1) & 1u, abort_word)) goto done;
-      }
-      if (j > 0 && any_change) {    // uniform over the 128 threads: O^T must be quiescent
-        if (!mbar_wait(&pv_done[(j - 1) & 1], (((uint32_t)j - 1) >> 1) & 1u, abort_word)) goto done;
-        tc_fence_after();
-        uint32_t o[16];
-        tmem_ld_32x32b_x16(t_lane + Cfg::O_COL, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < NVT; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c]);
-        tmem_st_32x32b_x16(t_lane + Cfg::O_COL, o);
-        tmem_st_wait();
-      }
-      if (warp == 2) DEC_STAMP(2, j, 2);
-      // probabilities of this key for every column -> P[c][key] (K-major, swizzled)
-      uint8_t* pbase = Ps + (j & 1) * Cfg::P_BYTES + (tid >> 6) * DEC_QHALF;
-      const int kin = tid & 63;
-#pragma unroll
-      for (int c = 0; c < NVT; c++) {
-        const float mb = (m[c] == -INFINITY) ? 0.f : m[c] * sl2;
-        const float pv = fast_exp2(s[c] * sl2 - mb);
-        lsum[c] += pv;
-        const int chunk = (kin >> 3) ^ (c & 7);
-        *reinterpret_cast<__nv_bfloat16*>(pbase + c * 128 + (chunk << 4) + (kin & 7) * 2) =
-            __float2bfloat16(pv);
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
-      if (warp == 2) DEC_STAMP(2, j, 3);
-    }
-    // ---- epilogue: total row sums, normalise, store
-    if (!mbar_wait(&pv_done[(n - 1) & 1], (((uint32_t)n - 1) >> 1) & 1u, abort_word)) goto done;
-    tc_fence_after();
-    softmax_bar();          // every thread is past its last read of the reduction scratch
-#pragma unroll
-    for (int c = 0; c < NVT; c++) {
-      const float w = warp_reduce_sum(lsum[c]);
-      if (lane == 0) red[qd * DEC_NQ + c] = w;
-    }
-    softmax_bar();
-    uint32_t o[16];
-    tmem_ld_32x32b_x16(t_lane + Cfg::O_COL, o);
-    tmem_ld_wait();
-    if (tid < D) {
-#pragma unroll
-      for (int c = 0; c < NVT; c++) {
-        if (c < nv) {
-          const float l = red[c] + red[DEC_NQ + c] + red[2 * DEC_NQ + c] + red[3 * DEC_NQ + c];
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          const long tok = q_start + c / G;
-          const int hq = h * G + c % G;
-          const float val = __uint_as_float(o[c]) * inv;
-          if (p.num_splits == 1) {
-            p.out[tok * p.out_stride + (long)hq * D + tid] = __float2bfloat16(val);
-          } else {
-            const long pidx = (tok * p.Hq + hq) * p.num_splits + split;
-            p.partial_o[pidx * D + tid] = val;
-            if (tid == 0)
-              p.partial_lse[pidx] =
-                  (l > 0.f) ? (m[c] * sl2 * 0.6931471805599453f + logf(l)) : -INFINITY;
+        for (int c = 0; c < NVT; c++) {
+          if (c < nv) {
+            const float l = red_sum[c] + red_sum[DEC_NQ + c] + red_sum[2 * DEC_NQ + c] +
+                            red_sum[3 * DEC_NQ + c];
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const long tok = w.q_start + c / G;
+            const int hq = w.h * G + c % G;
+            const float val = __uint_as_float(o[c]) * inv;
+            if (p.num_splits == 1) {
+              p.out[tok * p.out_stride + (long)hq * D + tid] = __float2bfloat16(val);
+            } else {
+              const long pidx = (tok * p.Hq + hq) * p.num_splits + w.split;
+              p.partial_o[pidx * D + tid] = val;
+              if (tid == 0)
+                p.partial_lse[pidx] =
+                    (l > 0.f) ? (m[c] * sl2 * 0.6931471805599453f + logf(l)) : -INFINITY;
+            }
           }
         }
       }
+      // the next item's epilogue overwrites red_sum only after a softmax_bar of its tile loop
+      it++;
     }
   }
 done:
@@ -532,8 +589,20 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
   p.status = status;
   p.timeline = (long long*)timeline;
   using Cfg = DecCfg<128>;
-  if (num_seqs > 65535) return 9125;
-  dim3 grid((unsigned)Hkv, (unsigned)num_seqs, (unsigned)num_splits);
+  const long items = (long)Hkv * num_seqs * num_splits;
+  if (items > 0x7fffffffL) return 9125;
+  p.num_seqs = num_seqs;
+  p.num_items = (int)items;
+  static int sm_count[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 9127;
+  if (sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      return 9127;
+    sm_count[dev] = n;
+  }
+  dim3 grid((unsigned)(items < sm_count[dev] ? items : sm_count[dev]));
   // columns that can be valid: query tokens per sequence x heads per group
   if (max_q_len < 1) max_q_len = 1;
   const int ncols = max_q_len * G;

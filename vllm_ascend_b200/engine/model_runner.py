@@ -57,12 +57,14 @@ class _SpecRow:
 
 class _StepHandle:
     """A step that was enqueued but whose sampled tokens have not been read yet."""
-    __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index", "logprobs")
+    __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index", "logprobs", "ev_start", "num_tokens")
 
     def __init__(self, tokens, reqs, host, event, kind, t_start):
         self.tokens, self.reqs, self.host, self.event, self.kind, self.t_start = tokens, reqs, host, event, kind, t_start
         self.index = {r.request_id: i for i, r in enumerate(reqs)}
         self.logprobs = None
+        self.ev_start = None
+        self.num_tokens = 0
 
 
 class ModelRunner:

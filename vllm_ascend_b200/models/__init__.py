@@ -65,3 +65,22 @@ def build_model(engine_cfg, device, moe_runtime=None):
     return ctor(cfg, device, max_model_len=engine_cfg.scheduler.max_model_len,
                 tp_group=st.tp, ep_group=ep_group, moe_runtime=moe_runtime,
                 layer_range=layer_range)
+
+
+def register_with_vllm() -> list[str]:
+    """General-plugin hook: architectures this package serves that the installed vLLM's registry does
+    not know are registered with a description-only class (``host_stub.HostModelStub``), so that
+    vLLM's config validation accepts them; the worker builds the real model from this package's
+    registry.  Architectures vLLM already knows keep vLLM's own entry (only its metadata is read).
+    Returns the names it added."""
+    try:
+        from vllm import ModelRegistry
+    except Exception:
+        return []
+    known = set(ModelRegistry.get_supported_archs())
+    added = []
+    for arch in supported_architectures():
+        if arch not in known:
+            ModelRegistry.register_model(arch, "vllm_ascend_b200.models.host_stub:HostModelStub")
+            added.append(arch)
+    return added

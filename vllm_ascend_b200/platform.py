@@ -37,13 +37,21 @@ _ATTN_BACKENDS = {
 }
 
 
+_HAS_GPU = torch.cuda.is_available()
+
+#: the worker class a host vLLM's executor constructs (a ``WorkerBase`` subclass)
+WORKER_CLS = "vllm_ascend_b200.worker.vllm_worker.B200VllmWorker"
+
+
 class B200Platform(_Base):
     _enum = _OOT
-    device_name: str = "cuda"
-    device_type: str = "cuda"
-    dispatch_key: str = "CUDA"
+    # without a visible GPU the platform still loads (CPU runs of the whole stack, used by the
+    # tests of the plugin path): tensors then live on the host and the ops take their PyTorch path
+    device_name: str = "cuda" if _HAS_GPU else "cpu"
+    device_type: str = "cuda" if _HAS_GPU else "cpu"
+    dispatch_key: str = "CUDA" if _HAS_GPU else "CPU"
     ray_device_key: str = "GPU"
-    dist_backend: str = "nccl"
+    dist_backend: str = "nccl" if _HAS_GPU else "gloo"
     device_control_env_var: str = "CUDA_VISIBLE_DEVICES"
     simple_compile_backend: str = "eager"
     supported_quantization: list = SUPPORTED_QUANTIZATION
@@ -67,16 +75,22 @@ class B200Platform(_Base):
 
     @classmethod
     def get_device_total_memory(cls, device_id: int = 0) -> int:
+        if not _HAS_GPU:
+            import psutil
+            return int(psutil.virtual_memory().total)
         return torch.cuda.get_device_properties(device_id).total_memory
 
     @classmethod
     def get_current_memory_usage(cls, device=None) -> float:
+        if not _HAS_GPU:
+            return 0.0
         torch.cuda.reset_peak_memory_stats(device)
         return torch.cuda.max_memory_allocated(device)
 
     @classmethod
     def set_device(cls, device: torch.device) -> None:
-        torch.cuda.set_device(device)
+        if _HAS_GPU:
+            torch.cuda.set_device(device)
 
     @classmethod
     def inference_mode(cls):
@@ -84,7 +98,7 @@ class B200Platform(_Base):
 
     @classmethod
     def is_pin_memory_available(cls) -> bool:
-        return True
+        return _HAS_GPU
 
     @classmethod
     def is_sleep_mode_available(cls) -> bool:
@@ -211,7 +225,7 @@ class B200Platform(_Base):
                           or getattr(getattr(mc, "hf_config", None), "n_routed_experts", 0))
             _validate_eplb(cfg.eplb_config, is_moe, getattr(pc, "enable_expert_parallel", False))
             if getattr(pc, "worker_cls", "auto") == "auto":
-                pc.worker_cls = "vllm_ascend_b200.worker.worker.B200Worker"
+                pc.worker_cls = WORKER_CLS
         if cc is not None:
             mode = getattr(cc, "cudagraph_mode", None)
             name = getattr(mode, "name", mode)
@@ -227,8 +241,17 @@ class B200Platform(_Base):
                 tp = pc.tensor_parallel_size
                 cc.cudagraph_capture_sizes = sorted({((s + tp - 1) // tp) * tp
                                                      for s in cc.cudagraph_capture_sizes})
-        if cache is not None and getattr(cache, "block_size", None) in (None, 0):
-            cache.block_size = 128
+        if cache is not None and (getattr(cache, "block_size", None) in (None, 0)
+                                  or not getattr(cache, "user_specified_block_size", True)):
+            cache.block_size = 128 if _HAS_GPU else 16      # 128-token pages: one TMA box per KV head
+        if cc is not None:
+            # the worker runs this package's own model code and CUDA graphs: the host's tracing
+            # compiler has nothing to compile
+            try:
+                from vllm.config import CompilationMode
+                cc.mode = CompilationMode.NONE
+            except Exception:
+                pass
         if sc is not None:
             s = cfg.scheduler_config
             if s.recompute_scheduler_enable:
