@@ -409,7 +409,7 @@ def run_ours_under_vllm(args, rank: int, world: int, local: int):
             "dtype": "bf16", "data": "synthetic",
             "config": config_block(args, world, {"engine": "vllm.LLM with this package as platform plugin",
                                                  "timing": "host clock between device synchronisations"}),
-            "clocks": clocks, "gpu_launches": _native.launch_count(),
+            "clocks": clocks, "gpu_launches": int(_native.launch_counter[0]),
         }))
 
 

@@ -39,7 +39,8 @@ def tp_generate():
     fused = llm.engine.runner.model.sp_ctx is not None
     if fused:
         llm.engine.runner.model.sp_ctx.check()
-    return {"tokens": toks, "fused": fused, "replays": llm.engine.runner.stats["graph_replays"]}
+    nvls = bool(fused and llm.engine.runner.model.sp_ctx.nvls)
+    return {"tokens": toks, "fused": fused, "nvls": nvls, "replays": llm.engine.runner.stats["graph_replays"]}
 
 
 def fused_linear_ops():
@@ -81,7 +82,9 @@ def fused_linear_ops():
         want2 = got @ w2.float().t()
         errs.append(float((out[:T] - want2[:T]).abs().max() / want2[:T].abs().max()))
     torch.cuda.synchronize()
-    return {"max_rel_err": max(errs), "errs": errs}
+    all_errs = [None] * world
+    torch.distributed.all_gather_object(all_errs, errs)        # every rank checked its own copy
+    return {"max_rel_err": max(max(e) for e in all_errs), "errs": errs, "nvls": bool(ctx.nvls)}
 
 
 def symm_allreduce():

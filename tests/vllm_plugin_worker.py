@@ -27,13 +27,19 @@ from vllm.platforms import current_platform
 kw = dict(model=model_dir, load_format="dummy", skip_tokenizer_init=True, dtype=dtype, max_model_len=256,
           max_num_seqs=8, max_num_batched_tokens=64, enable_prefix_caching=False, seed=0,
           async_scheduling=(mode == "async"))
+on_gpu = torch.cuda.is_available()
 if mode == "preempt":
-    kw["num_gpu_blocks_override"] = 4 if torch.cuda.is_available() else 20     # too few for every request to finish
+    # too few blocks for every request to finish (pages: 128 tokens on a GPU, 16 on the host)
+    kw["num_gpu_blocks_override"] = 6 if on_gpu else 20
 llm = LLM(**kw)
 rng = np.random.default_rng(0)
-lens = (20, 70, 33, 5) if mode != "preempt" else (40, 44, 36, 48)
+if mode != "preempt":
+    lens, n_out = (20, 70, 33, 5), 8
+elif on_gpu:
+    lens, n_out = (100, 110, 90, 120), 60
+else:
+    lens, n_out = (40, 44, 36, 48), 40
 prompts = [rng.integers(0, 1024, size=n).tolist() for n in lens]
-n_out = 8 if mode != "preempt" else 40
 outs = llm.generate([{"prompt_token_ids": p} for p in prompts],
                     SamplingParams(temperature=0.0, max_tokens=n_out, ignore_eos=True), use_tqdm=False)
 got = [list(o.outputs[0].token_ids) for o in outs]

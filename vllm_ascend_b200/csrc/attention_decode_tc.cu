@@ -45,6 +45,7 @@ struct DecParams {
   float* partial_lse;
   long num_blocks_total;
   int num_seqs, num_items;   // items = Hkv x sequences x splits
+  int tail_loads;            // 1: the last tile of a sequence is loaded in 32-key pieces (pages >= 128 keys)
   int* status;
   long long* timeline;   // optional [3 roles][64 tiles][8 stamps] of clock64, CTA 0 only
 };
@@ -111,7 +112,9 @@ template <int D, int NVT>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
-                      const __grid_constant__ CUtensorMap tmap_v, const DecParams p) {
+                      const __grid_constant__ CUtensorMap tmap_v,
+                      const __grid_constant__ CUtensorMap tmap_k32,
+                      const __grid_constant__ CUtensorMap tmap_v32, const DecParams p) {
   using Cfg = DecCfg<D>;
   constexpr int NH = Cfg::NH, ST = Cfg::STAGES;
   const int G = p.G;
@@ -142,6 +145,16 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   float* red = (float*)(tmem_ptr + 2);            // [2 tiles][4 warps][16] maxima
   float* red_sum = red + 128;                     // [4 warps][16] row sums of the epilogue
 
+  if (p.tail_loads) {
+    // The last tile of a sequence is fetched in 32-key pieces up to its length; the rest of the
+    // stage keeps what an earlier tile left there.  Those keys are masked (P = 0), so all that is
+    // asked of the stale rows is that they are finite: start from zeros instead of whatever the
+    // shared memory held.
+    uint4* z = reinterpret_cast<uint4*>(Ks);
+    for (int i = threadIdx.x; i < 2 * ST * Cfg::TILE_BYTES / 16; i += DEC_THREADS)
+      z[i] = make_uint4(0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
+  }
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; b++) {
       mbar_init(&q_full[b], 1);
@@ -169,6 +182,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
+    if (p.tail_loads) {
+      tma_prefetch_desc(&tmap_k32);
+      tma_prefetch_desc(&tmap_v32);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -218,6 +235,29 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
           if (bad) {
             *abort_word = B200_BAD_INDEX;
             goto done;
+          }
+          // 32-key pieces of the tile that hold keys of the sequence (4 = the whole tile)
+          int nsub = 4;
+          if (p.tail_loads) {
+            const int valid = w.seq_len - key_base;
+            if (valid < 128) nsub = (valid + 31) >> 5;
+          }
+          if (nsub < 4) {
+            const int blk = __shfl_sync(0xffffffffu, blk_cur, 0);
+            if (lane == 0) {
+              uint8_t* dst = (kv == 0 ? Ks : Vs) + st * Cfg::TILE_BYTES;
+              const CUtensorMap* tm = kv == 0 ? &tmap_k32 : &tmap_v32;
+              mbar_expect_tx(fullb, nsub * NH * 32 * 128);
+              const int off = key_base % p.block_size;
+              for (int sub = 0; sub < nsub; sub++) {
+#pragma unroll
+                for (int hf = 0; hf < NH; hf++)
+                  tma_load_4d(dst + hf * DEC_HALF + sub * 32 * 128, tm, fullb, hf * 64, w.h,
+                              off + sub * 32, blk);
+              }
+            }
+            __syncwarp();
+            continue;
           }
           for (int part = 0; part < parts; part++) {
             const int blk = __shfl_sync(0xffffffffu, blk_cur, part);
@@ -547,7 +587,7 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
   if (num_splits < 1) num_splits = 1;
   if (num_splits > 1 && !scratch) return 9124;
   const int rpl = block_size < 128 ? block_size : 128;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, tk32, tv32;
   {
     uint64_t dims[4] = {(uint64_t)D, (uint64_t)G, (uint64_t)Hkv, (uint64_t)T};
     uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)G * D * 2, (uint64_t)q_stride * 2};
@@ -569,6 +609,15 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
     if (rc) return rc;
     rc = g_dec_tmaps.get(&tv, v_cache, 4, dims, str, box);
     if (rc) return rc;
+    tk32 = tk;
+    tv32 = tv;
+    if (rpl == 128) {
+      uint32_t box32[4] = {64, 1, 32, 1};
+      rc = g_dec_tmaps.get(&tk32, k_cache, 4, dims, str, box32);
+      if (rc) return rc;
+      rc = g_dec_tmaps.get(&tv32, v_cache, 4, dims, str, box32);
+      if (rc) return rc;
+    }
   }
   DecParams p;
   p.query_start_loc = (const int*)query_start_loc;
@@ -592,6 +641,7 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
   const long items = (long)Hkv * num_seqs * num_splits;
   if (items > 0x7fffffffL) return 9125;
   p.num_seqs = num_seqs;
+  p.tail_loads = rpl == 128 ? 1 : 0;
   p.num_items = (int)items;
   static int sm_count[64] = {};
   int dev = 0;
@@ -617,7 +667,8 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
       if (e != cudaSuccess) return (int)e;                                                  \
       attr_set = true;                                                                      \
     }                                                                                       \
-    attn_decode_tc_kernel<128, NV><<<grid, DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p); \
+    attn_decode_tc_kernel<128, NV><<<grid, DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tk32,  \
+                                                                                    tv32, p); \
   } while (0)
   if (ncols <= 1) LAUNCH_DEC_TC(1);
   else if (ncols <= 2) LAUNCH_DEC_TC(2);

@@ -242,6 +242,133 @@ __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int nu
   }
 }
 
+// ---------------------------------------------------------------- NVLS (multimem) variant
+// The same step through NVSwitch multicast memory: every rank's GEMM wrote its bf16 partial
+// [T, H] into ITS OWN copy of a multicast-bound buffer; the owner of a row shard fetches the sum
+// over all ranks with one `multimem.ld_reduce` per 16 bytes (the switch adds the N copies in
+// fp32, 1/N of the bytes arrive here) and publishes the normalised rows with `multimem.st`
+// (one store leaves this GPU, the switch replicates it into every rank's gather buffer).
+// Flags and epochs are the ones of the peer-store variant.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile(
+      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(mc)
+      : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_b128(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <int VEC_PER_THREAD>
+__global__ void nvls_reduce_add_norm_push_kernel(const __nv_bfloat16* mc_partial, int reduce,
+                                                 const __nv_bfloat16* x_local,
+                                                 __nv_bfloat16* residual,
+                                                 const __nv_bfloat16* __restrict__ weight, float eps,
+                                                 __nv_bfloat16* mc_gather, PeerFlags ag_flag_dst,
+                                                 CommCtl* ctl, int rows_local, int H, int my_rank,
+                                                 int num_ranks, int skip_norm) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const int nvec = H >> 3;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (reduce) {
+    const uint32_t epoch = ctl->rs_epoch;      // published by this rank's own GEMM launch
+    if (threadIdx.x < num_ranks && threadIdx.x != my_rank) {
+      if (!wait_flag_ge(&ctl->rs_flag[threadIdx.x], epoch, &ctl->status)) s_ok = 0;
+    }
+    __syncthreads();
+  }
+  float vals[VEC_PER_THREAD][8];
+  if (s_ok) {
+    for (int row = blockIdx.x; row < rows_local; row += gridDim.x) {
+      const size_t grow = (size_t)my_rank * rows_local + row;
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC_PER_THREAD; i++) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+          uint32_t zw[4];
+          if (reduce) {
+            const uint4 pv = multimem_ld_reduce_bf16x8(mc_partial + grow * H + (size_t)v * 8);
+            const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
+            uint4* rr = reinterpret_cast<uint4*>(residual + (size_t)row * H) + v;
+            const uint4 rv = *rr;
+            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const float2 f = unpack_bf16x2(rw[j]);
+              const float2 g = unpack_bf16x2(pw[j]);     // the reduced GEMM output, rounded to bf16
+              zw[j] = pack_bf16x2(g.x + f.x, g.y + f.y);
+            }
+            *rr = make_uint4(zw[0], zw[1], zw[2], zw[3]);
+          } else {
+            const uint4 pv = reinterpret_cast<const uint4*>(x_local + (size_t)row * H)[v];
+            zw[0] = pv.x; zw[1] = pv.y; zw[2] = pv.z; zw[3] = pv.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const float2 f = unpack_bf16x2(zw[j]);
+            vals[i][2 * j] = f.x;
+            vals[i][2 * j + 1] = f.y;
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+      }
+      ss = warp_reduce_sum(ss);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+        t = warp_reduce_sum(t);
+        if (threadIdx.x == 0) red[0] = skip_norm ? 1.f : rsqrtf(t / (float)H + eps);
+      }
+      __syncthreads();
+      const float inv = red[0];
+#pragma unroll
+      for (int i = 0; i < VEC_PER_THREAD; i++) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+          uint32_t o[4];
+          if (skip_norm) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) o[j] = pack_bf16x2(vals[i][2 * j], vals[i][2 * j + 1]);
+          } else {
+            const uint4 ww = reinterpret_cast<const uint4*>(weight)[v];
+            const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const float2 fw = unpack_bf16x2(w4[j]);
+              o[j] = pack_bf16x2(vals[i][2 * j] * inv * fw.x, vals[i][2 * j + 1] * inv * fw.y);
+            }
+          }
+          multimem_st_b128(mc_gather + grow * H + (size_t)v * 8, make_uint4(o[0], o[1], o[2], o[3]));
+        }
+      }
+      __syncthreads();          // red[] is reused by the next row
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(&ctl->done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      const uint32_t epoch = ctl->ag_epoch + 1;
+      if (ctl->status == 0)
+        for (int r = 0; r < num_ranks; r++) st_release_sys(ag_flag_dst.p[r], epoch);
+      ctl->ag_epoch = epoch;
+      ctl->done_ctr = 0;
+      __threadfence();
+    }
+  }
+}
+
 // Wait until every source rank's all-gather rows of the current epoch have landed.
 __global__ void ag_wait_kernel(CommCtl* ctl, int my_rank, int num_ranks) {
   if (threadIdx.x < num_ranks && threadIdx.x != my_rank)
@@ -361,6 +488,39 @@ B200_API int b200_reduce_add_norm_push(const void* staging, int num_src, const v
   else if (per <= 4) LAUNCH_RANP(4);
   else return 9101;
 #undef LAUNCH_RANP
+  return B200_CHECK_LAUNCH();
+}
+
+// NVLS form of b200_reduce_add_norm_push.  mc_partial / mc_gather: multicast addresses of the
+// partial-sum buffer [T, H] and of the gather buffer [T, H] (T = num_ranks * rows_local);
+// reduce = 0 normalises x_local (first layer) instead of summing partials.
+B200_API int b200_nvls_reduce_add_norm_push(const void* mc_partial, int reduce, const void* x_local,
+                                            void* residual, const void* weight, float eps,
+                                            void* mc_gather, void* const* peer_ctl, int rows_local,
+                                            int H, int my_rank, int num_ranks, int skip_norm,
+                                            cudaStream_t stream) {
+  if (rows_local <= 0) return 0;
+  if (H & 7) return 9100;
+  if (!mc_gather || (reduce && (!mc_partial || !residual))) return 9141;
+  PeerFlags f;
+  for (int r = 0; r < num_ranks; r++) f.p[r] = &((CommCtl*)peer_ctl[r])->ag_flag[my_rank];
+  const int nvec = H >> 3;
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32 * ((num_ranks + 31) / 32)) threads = 32 * ((num_ranks + 31) / 32);
+  const int per = (nvec + threads - 1) / threads;
+  CommCtl* ctl = (CommCtl*)peer_ctl[my_rank];
+  const int grid = rows_local < 148 * 4 ? rows_local : 148 * 4;
+#define LAUNCH_NVLS(V)                                                                          \
+  nvls_reduce_add_norm_push_kernel<V><<<grid, threads, 0, stream>>>(                            \
+      (const __nv_bfloat16*)mc_partial, reduce, (const __nv_bfloat16*)x_local,                  \
+      (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, (__nv_bfloat16*)mc_gather, f, \
+      ctl, rows_local, H, my_rank, num_ranks, skip_norm)
+  if (per <= 1) LAUNCH_NVLS(1);
+  else if (per <= 2) LAUNCH_NVLS(2);
+  else if (per <= 4) LAUNCH_NVLS(4);
+  else return 9101;
+#undef LAUNCH_NVLS
   return B200_CHECK_LAUNCH();
 }
 

@@ -225,76 +225,128 @@ __global__ void qknorm_rope_kvwrite_kernel(__nv_bfloat16* qkv, long qkv_stride,
   }
 }
 
-// Fast path for D = 128 with full rotary (rot_dim = 128): every lane owns 4 consecutive
-// elements (one 8-byte access, 256 contiguous bytes per warp) and gets its rotation partner
-// (element j +- 64) from lane ^ 16 by shuffle.
-__global__ void qknorm_rope_kvwrite_d128_kernel(__nv_bfloat16* qkv, long qkv_stride,
-                                                const long* __restrict__ positions,
-                                                const float* __restrict__ cos_sin,
-                                                const __nv_bfloat16* __restrict__ q_norm_w,
-                                                const __nv_bfloat16* __restrict__ k_norm_w,
-                                                float eps, __nv_bfloat16* k_cache,
-                                                __nv_bfloat16* v_cache,
-                                                const long* __restrict__ slot_mapping, int T,
-                                                int Hq, int Hkv, long num_slots, int block_size,
-                                                int kv_layout, int* status) {
+// Fast path for D = 128 with full rotary (rot_dim = 128).  The op moves ~27 KB per token and is
+// limited by instruction issue as much as by bytes, so: a half-warp owns one (token, head) row and
+// lane l holds elements [4l, 4l+4) AND their rotation partners [64+4l, 64+4l+4) (two 8-byte
+// accesses, each half-warp access covers 128 contiguous bytes), which makes the rotation
+// shuffle-free; a warp walks QKN_ROWS_PER_WARP rows and issues all row loads up front.
+constexpr int QKN_ROWS_PER_WARP = 8;     // 4 rows per half-warp
+
+__global__ void __launch_bounds__(256)
+qknorm_rope_kvwrite_d128_kernel(__nv_bfloat16* qkv, long qkv_stride,
+                                const long* __restrict__ positions,
+                                const float* __restrict__ cos_sin,
+                                const __nv_bfloat16* __restrict__ q_norm_w,
+                                const __nv_bfloat16* __restrict__ k_norm_w, float eps,
+                                __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                                const long* __restrict__ slot_mapping, int T, int Hq, int Hkv,
+                                long num_slots, int block_size, int kv_layout, int* status) {
   constexpr int D = 128;
-  const int warps_per_block = blockDim.x >> 5;
+  constexpr int RPT = QKN_ROWS_PER_WARP / 2;          // rows per thread
   const int heads_total = Hq + 2 * Hkv;
-  const long gw = (long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  if (gw >= (long)T * heads_total) return;
-  const int t = (int)(gw / heads_total);
-  const int h = (int)(gw - (long)t * heads_total);
+  const long total_rows = (long)T * heads_total;
+  const long gw = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  uint2* src = reinterpret_cast<uint2*>(qkv + (long)t * qkv_stride + (long)h * D) + lane;
-  uint2 raw = *src;
-  const bool is_q = h < Hq;
-  const bool is_k = !is_q && h < Hq + Hkv;
-  if (is_q || is_k) {
-    float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
-    float v[4] = {a.x, a.y, b.x, b.y};
-    const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
-    if (nw) {
-      float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-      ss = warp_reduce_sum(ss);
-      const float inv = rsqrtf(ss / (float)D + eps);
-      const uint2 wr = reinterpret_cast<const uint2*>(nw)[lane];
-      const float2 w0 = unpack_bf16x2(wr.x), w1 = unpack_bf16x2(wr.y);
-      const float w[4] = {w0.x, w0.y, w1.x, w1.y};
+  const int hl = lane & 15;                            // lane inside the half-warp
+  const long row0 = gw * QKN_ROWS_PER_WARP + (lane >> 4);
+  if (gw * QKN_ROWS_PER_WARP >= total_rows) return;
+
+  uint2 lo[RPT], hi[RPT];                              // elements 4hl.. and 64+4hl..
+  int tt[RPT], hh[RPT];
+  bool ok[RPT];
 #pragma unroll
-      for (int i = 0; i < 4; i++)      // rounded to bf16 like the unfused norm -> rope sequence
-        v[i] = __bfloat162float(__float2bfloat16(v[i] * inv * w[i]));
-    }
-    const long pos = positions[t];
-    const float* cs = cos_sin + pos * (long)D;
-    const int e = (lane & 15) * 4;                       // index into the 64 cos / sin values
-    const float4 c = *reinterpret_cast<const float4*>(cs + e);
-    const float4 sn = *reinterpret_cast<const float4*>(cs + 64 + e);
-    const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
-    const float sign = lane < 16 ? -1.f : 1.f;           // lower half: x1 c - x2 s; upper: x2 c + x1 s
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-      v[i] = v[i] * cc[i] + sign * other * sv[i];
-    }
-    raw.x = pack_bf16x2(v[0], v[1]);
-    raw.y = pack_bf16x2(v[2], v[3]);
-    *src = raw;
+  for (int i = 0; i < RPT; i++) {
+    const long r = row0 + 2 * i;
+    ok[i] = r < total_rows;
+    const long rc = ok[i] ? r : 0;
+    tt[i] = (int)(rc / heads_total);
+    hh[i] = (int)(rc - (long)tt[i] * heads_total);
+    const uint2* src = reinterpret_cast<const uint2*>(qkv + (long)tt[i] * qkv_stride + (long)hh[i] * D);
+    lo[i] = ok[i] ? src[hl] : make_uint2(0u, 0u);
+    hi[i] = ok[i] ? src[16 + hl] : make_uint2(0u, 0u);
   }
-  if (!is_q && k_cache) {
-    const long slot = slot_mapping[t];
-    if (slot < 0) return;
-    if (slot >= num_slots) {
-      if (lane == 0 && status) atomicExch(status, B200_BAD_INDEX);
-      return;
+  // norm weights of this thread's 8 columns (q and k), shared by all of its rows
+  float wq[8], wk[8];
+  {
+    const uint2 z = make_uint2(0u, 0u);
+    const uint2 a0 = q_norm_w ? reinterpret_cast<const uint2*>(q_norm_w)[hl] : z;
+    const uint2 a1 = q_norm_w ? reinterpret_cast<const uint2*>(q_norm_w)[16 + hl] : z;
+    const uint2 b0 = k_norm_w ? reinterpret_cast<const uint2*>(k_norm_w)[hl] : z;
+    const uint2 b1 = k_norm_w ? reinterpret_cast<const uint2*>(k_norm_w)[16 + hl] : z;
+    const uint32_t aw[4] = {a0.x, a0.y, a1.x, a1.y}, bw[4] = {b0.x, b0.y, b1.x, b1.y};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float2 fa = unpack_bf16x2(aw[j]), fb = unpack_bf16x2(bw[j]);
+      wq[2 * j] = fa.x; wq[2 * j + 1] = fa.y;
+      wk[2 * j] = fb.x; wk[2 * j + 1] = fb.y;
     }
-    const int kvh = is_k ? (h - Hq) : (h - Hq - Hkv);
-    long row = slot * Hkv + kvh;
-    if (kv_layout == 1) {
-      const long blk = slot / block_size, off = slot - blk * block_size;
-      row = (blk * Hkv + kvh) * block_size + off;
+  }
+#pragma unroll
+  for (int i = 0; i < RPT; i++) {
+    const int t = tt[i], h = hh[i];
+    const bool is_q = h < Hq;
+    const bool is_k = !is_q && h < Hq + Hkv;
+    const bool rot = is_q || is_k;
+    uint2 olo = lo[i], ohi = hi[i];
+    // every lane takes part in the reduction shuffles; rows past the end carry zeros
+    float v[8];                                          // v[0..3] first half, v[4..7] partners
+    {
+      const uint32_t w32[4] = {lo[i].x, lo[i].y, hi[i].x, hi[i].y};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float2 f = unpack_bf16x2(w32[j]);
+        v[2 * j] = f.x; v[2 * j + 1] = f.y;
+      }
     }
-    reinterpret_cast<uint2*>((is_k ? k_cache : v_cache) + row * (long)D)[lane] = raw;
+    const bool has_norm = is_q ? (q_norm_w != nullptr) : (is_k && k_norm_w != nullptr);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) ss += v[j] * v[j];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (rot) {
+      if (has_norm) {
+        const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int j = 0; j < 8; j++)      // rounded to bf16 like the unfused norm -> rope sequence
+          v[j] = __bfloat162float(__float2bfloat16(v[j] * inv * (is_q ? wq[j] : wk[j])));
+      }
+      const float* cs = cos_sin + positions[t] * (long)D + hl * 4;
+      const float4 c = *reinterpret_cast<const float4*>(cs);
+      const float4 sn = *reinterpret_cast<const float4*>(cs + 64);
+      const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+      float x1[4], x2[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        x1[j] = v[j] * cc[j] - v[4 + j] * sv[j];
+        x2[j] = v[4 + j] * cc[j] + v[j] * sv[j];
+      }
+      olo = make_uint2(pack_bf16x2(x1[0], x1[1]), pack_bf16x2(x1[2], x1[3]));
+      ohi = make_uint2(pack_bf16x2(x2[0], x2[1]), pack_bf16x2(x2[2], x2[3]));
+    }
+    if (!ok[i]) continue;
+    if (rot) {
+      uint2* dst = reinterpret_cast<uint2*>(qkv + (long)t * qkv_stride + (long)h * D);
+      dst[hl] = olo;
+      dst[16 + hl] = ohi;
+    }
+    if (!is_q && k_cache) {
+      const long slot = slot_mapping[t];
+      if (slot < 0) continue;
+      if (slot >= num_slots) {
+        if (hl == 0 && status) atomicExch(status, B200_BAD_INDEX);
+        continue;
+      }
+      const int kvh = is_k ? (h - Hq) : (h - Hq - Hkv);
+      long row = slot * Hkv + kvh;
+      if (kv_layout == 1) {
+        const long blk = slot / block_size, off = slot - blk * block_size;
+        row = (blk * Hkv + kvh) * block_size + off;
+      }
+      uint2* dst = reinterpret_cast<uint2*>((is_k ? k_cache : v_cache) + row * (long)D);
+      dst[hl] = olo;
+      dst[16 + hl] = ohi;
+    }
   }
 }
 
@@ -570,8 +622,12 @@ static int qknorm_rope_impl(void* qkv, long qkv_stride, const void* positions,
       (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps,                    \
       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const long*)slot_mapping, T, Hq, Hkv, \
       num_slots, block_size, kv_layout, status, (const int*)mrope_axis, pos_stride)
-  if (D == 128 && rot_dim == 128 && (qkv_stride & 3) == 0 && !mrope_axis) {
-    qknorm_rope_kvwrite_d128_kernel<<<blocks, wpb * 32, 0, stream>>>(
+  if (D == 128 && rot_dim == 128 && (qkv_stride & 3) == 0 && !mrope_axis &&
+      (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q_norm_w |
+        (uintptr_t)k_norm_w) & 7) == 0) {
+    const long w8 = (warps + QKN_ROWS_PER_WARP - 1) / QKN_ROWS_PER_WARP;
+    const unsigned blocks8 = (unsigned)((w8 + wpb - 1) / wpb);
+    qknorm_rope_kvwrite_d128_kernel<<<blocks8, wpb * 32, 0, stream>>>(
         (__nv_bfloat16*)qkv, qkv_stride, (const long*)positions, (const float*)cos_sin,
         (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps,
         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const long*)slot_mapping, T, Hq, Hkv,

@@ -37,7 +37,8 @@ constexpr int GEMM_MAX_GROUPS = 512;
 
 enum : int { GEMM_AG = 1, GEMM_RS = 2, GEMM_SWIGLU = 4, GEMM_GROUPED = 8,
               GEMM_WAITFLAGS = 16,   // producer waits for every rank's flag before the first load
-              GEMM_SCATTER = 32 };   // epilogue stores row i to peer (row_meta[i] >> 24), row (row_meta[i] & 0xffffff)
+              GEMM_SCATTER = 32,     // epilogue stores row i to peer (row_meta[i] >> 24), row (row_meta[i] & 0xffffff)
+              GEMM_PUB = 64 };       // last CTA publishes the reduce-scatter epoch (with GEMM_RS, or alone: rows stay local)
 
 template <int BN>
 struct GemmCfg {
@@ -388,7 +389,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
-    if (p.mode & (GEMM_RS | GEMM_SCATTER)) __threadfence_system();   // rows visible to their owners
+    if (p.mode & (GEMM_RS | GEMM_SCATTER | GEMM_PUB)) __threadfence_system();   // rows visible to their owners
   }
 done:
   tc_fence_before();
@@ -398,7 +399,7 @@ done:
     while (globaltimer_ns() - t_start < 50000ull) __nanosleep(1000);
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, *abort_word);
     __syncthreads();
-  } else if ((p.mode & GEMM_RS) && threadIdx.x == 0) {
+  } else if ((p.mode & GEMM_PUB) && threadIdx.x == 0) {
     // last CTA of the grid publishes this rank's reduce-scatter epoch to every owner
     const uint32_t prev = atomicAdd(&p.ctl->done_ctr, 1u);
     if (prev == gridDim.x - 1) {
@@ -600,7 +601,7 @@ B200_API int b200_gemm_rs_bf16(const void* A, const void* W, const void* bias, i
   p.M = M; p.N = N; p.K = K; p.ldc = N;
   p.bias = (const __nv_bfloat16*)bias;
   p.status = status;
-  p.mode = GEMM_RS;
+  p.mode = GEMM_RS | GEMM_PUB;
   p.my_rank = my_rank;
   p.num_ranks = num_ranks;
   p.rows_per_owner = rows_per_owner;
@@ -608,6 +609,29 @@ B200_API int b200_gemm_rs_bf16(const void* A, const void* W, const void* bias, i
     p.rs_dst[o] = (__nv_bfloat16*)rs_staging[o];
     p.rs_flag_dst[o] = &((CommCtl*)peer_ctl[o])->rs_flag[my_rank];
   }
+  p.ctl = (CommCtl*)peer_ctl[my_rank];
+  if (pick_bn(M, N, bn) == 256) return launch_gemm<256>(A, W, p, lda, ldw, M, N, 0, stream);
+  return launch_gemm<128>(A, W, p, lda, ldw, M, N, 0, stream);
+}
+
+// GEMM into this rank's own buffer C (a multicast-bound partial-sum buffer) that publishes its
+// completion to every peer's rs_flag: producer side of b200_nvls_reduce_add_norm_push.
+B200_API int b200_gemm_pub_bf16(const void* A, const void* W, void* C, const void* bias, int M, int N,
+                                int K, int lda, int ldw, int ldc, void* const* peer_ctl, int my_rank,
+                                int num_ranks, int bn, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
+  if (num_ranks > kMaxRanks) return 9130;
+  GemmParams p;
+  init_params(p);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.mode = GEMM_PUB;
+  p.my_rank = my_rank;
+  p.num_ranks = num_ranks;
+  for (int o = 0; o < num_ranks; o++) p.rs_flag_dst[o] = &((CommCtl*)peer_ctl[o])->rs_flag[my_rank];
   p.ctl = (CommCtl*)peer_ctl[my_rank];
   if (pick_bn(M, N, bn) == 256) return launch_gemm<256>(A, W, p, lda, ldw, M, N, 0, stream);
   return launch_gemm<128>(A, W, p, lda, ldw, M, N, 0, stream);

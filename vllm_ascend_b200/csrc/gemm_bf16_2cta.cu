@@ -58,7 +58,9 @@ struct Gemm2Params {
   int rows_per_owner;
   int raster;                         // M-tiles per raster group (0/1: column-major order)
 };
-enum : int { G2_AG = 1, G2_RS = 2 };
+// G2_PUB: the last CTA publishes this rank's reduce-scatter epoch to every peer (set with G2_RS;
+// alone it is the NVLS form: rows stay in the local multicast-bound buffer C)
+enum : int { G2_AG = 1, G2_RS = 2, G2_PUB = 4 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -373,7 +375,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // accumulator buffer drained: tell the leader's MMA warp (local or remote arrive)
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));
     }
-    if (p.mode & G2_RS) __threadfence_system();   // partial rows visible to their owners
+    if (p.mode & G2_PUB) __threadfence_system();   // partial rows visible to their owners
   }
 done:
   tc_fence_before();
@@ -382,7 +384,7 @@ done:
     const uint64_t t_start = globaltimer_ns();
     while (globaltimer_ns() - t_start < 50000ull) __nanosleep(1000);
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, *abort_word);
-  } else if ((p.mode & G2_RS) && threadIdx.x == 0) {
+  } else if ((p.mode & G2_PUB) && threadIdx.x == 0) {
     // the last CTA of the grid publishes this rank's reduce-scatter epoch to every owner
     const uint32_t prev = atomicAdd(&p.ctl->done_ctr, 1u);
     if (prev == gridDim.x - 1) {
@@ -517,7 +519,7 @@ B200_API int b200_gemm_rs_bf16_2cta(const void* A, const void* W, const void* bi
   p.M = M; p.N = N; p.K = K; p.ldc = N;
   p.bias = (const __nv_bfloat16*)bias;
   p.status = status;
-  p.mode = G2_RS;
+  p.mode = G2_RS | G2_PUB;
   p.my_rank = my_rank;
   p.num_ranks = num_ranks;
   p.rows_per_owner = rows_per_owner;
@@ -525,6 +527,29 @@ B200_API int b200_gemm_rs_bf16_2cta(const void* A, const void* W, const void* bi
     p.rs_dst[o] = (__nv_bfloat16*)rs_staging[o];
     p.rs_flag_dst[o] = &((CommCtl*)peer_ctl[o])->rs_flag[my_rank];
   }
+  p.ctl = (CommCtl*)peer_ctl[my_rank];
+  return launch_2cta(A, W, p, lda, ldw, M, stream);
+}
+
+// GEMM whose output stays in this rank's own buffer C [M, N] (a multicast-bound partial-sum buffer)
+// and whose completion is published to every peer's rs_flag: the producer side of the NVLS
+// reduce (b200_nvls_reduce_add_norm_push sums the ranks' buffers inside the switch).
+B200_API int b200_gemm_pub_bf16_2cta(const void* A, const void* W, void* C, const void* bias, int M,
+                                     int N, int K, int lda, int ldw, int ldc, void* const* peer_ctl,
+                                     int my_rank, int num_ranks, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
+  if (num_ranks > kMaxRanks) return 9130;
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.mode = G2_PUB;
+  p.my_rank = my_rank;
+  p.num_ranks = num_ranks;
+  for (int o = 0; o < num_ranks; o++) p.rs_flag_dst[o] = &((CommCtl*)peer_ctl[o])->rs_flag[my_rank];
   p.ctl = (CommCtl*)peer_ctl[my_rank];
   return launch_2cta(A, W, p, lda, ldw, M, stream);
 }

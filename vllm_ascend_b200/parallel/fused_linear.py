@@ -39,9 +39,15 @@ class FusedTPContext:
         self.max_rows_local = (max_tokens + self.n - 1) // self.n
         self.max_tokens = self.max_rows_local * self.n
         nbytes = self.max_tokens * hidden * 2
-        self.symm = SymmetricMemory(group, device, 2 * nbytes + 4096)
+        from .. import envs
+        self.symm = SymmetricMemory(group, device, 2 * nbytes + 4096, multicast=envs.VLLM_B200_NVLS != "0")
         self.off_ag = self.symm.region(nbytes)
         self.off_rs = self.symm.region(nbytes)
+        # NVSwitch multicast (NVLS): the reduce-scatter region holds THIS rank's partial sums of all
+        # T rows and the reduction / the all-gather push go through multimem instructions
+        self.nvls = self.symm.mc_ptr != 0
+        self.mc_ag = self.symm.mc_ptr + self.off_ag if self.nvls else 0
+        self.mc_rs = self.symm.mc_ptr + self.off_rs if self.nvls else 0
         self.ag_ptrs = self.symm.ptr_array(self.off_ag)
         self.rs_ptrs = self.symm.ptr_array(self.off_rs)
         self.ctl_ptrs = self.symm.ctl_ptrs
@@ -66,6 +72,14 @@ class FusedTPContext:
         first=False: sum the peers' GEMM partials, add the residual shard, normalise, push."""
         lib = _native.lib()
         rl = self.rows_local
+        if self.nvls:
+            rc = lib.b200_nvls_reduce_add_norm_push(
+                None if first else self.mc_rs, 0 if first else 1, self.residual.data_ptr() if first else None,
+                None if first else self.residual.data_ptr(), weight.data_ptr(), eps, self.mc_ag, self.ctl_ptrs,
+                rl, self.H, self.rank, self.n, int(skip_norm), _native.stream_ptr())
+            _native.check(rc, "nvls_reduce_add_norm_push")
+            launch_counter[0] += 1
+            return
         if first:
             rc = lib.b200_reduce_add_norm_push(None, 0, self.residual.data_ptr(), None,
                                                weight.data_ptr(), eps, self.ag_ptrs, self.ctl_ptrs,
@@ -115,6 +129,22 @@ class FusedTPContext:
         """x [T, K_local] @ weight^T -> partial rows stored into their owners' staging."""
         assert x.shape[0] == self.T and weight.shape[0] == self.H
         b = _native.ptr(bias) if self.rank == 0 else None
+        if self.nvls:
+            # the partial rows stay in this rank's own (multicast-bound) buffer; peers learn that
+            # they are complete and sum them inside the switch
+            if self._two_cta(self.H):
+                rc = _native.lib().b200_gemm_pub_bf16_2cta(
+                    x.data_ptr(), weight.data_ptr(), self.rs_local_ptr, b, self.T, self.H, x.shape[1], x.stride(0),
+                    weight.stride(0), self.H, self.ctl_ptrs, self.rank, self.n, self.status.data_ptr(),
+                    _native.stream_ptr())
+            else:
+                rc = _native.lib().b200_gemm_pub_bf16(
+                    x.data_ptr(), weight.data_ptr(), self.rs_local_ptr, b, self.T, self.H, x.shape[1], x.stride(0),
+                    weight.stride(0), self.H, self.ctl_ptrs, self.rank, self.n, 0, self.status.data_ptr(),
+                    _native.stream_ptr())
+            _native.check(rc, "gemm_pub")
+            launch_counter[0] += 1
+            return
         if self._two_cta(self.H):
             rc = _native.lib().b200_gemm_rs_bf16_2cta(
                 x.data_ptr(), weight.data_ptr(), b, self.T, self.H, x.shape[1], x.stride(0), weight.stride(0),
