@@ -57,6 +57,12 @@ UPSTREAM_VLLM_B200 = {
 
 #: HF ``config.json`` contents of the benchmark architectures (random-init weights of these shapes).
 HF_SHAPES = {
+    # plumbing case (CPU, fp32): exercises every mode of this script in the tests
+    "tiny-qwen": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=1024, hidden_size=256,
+        intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+        head_dim=64, rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=4096,
+        tie_word_embeddings=False, torch_dtype="float32", hidden_act="silu", attention_bias=False),
     "qwen3-8b": dict(
         architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
         intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,

@@ -75,7 +75,7 @@ def test_prefill_context_parallel_on_two_gpus():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("nvls", ["0", "auto"])
+@pytest.mark.parametrize("nvls", ["0", "auto", "full"])
 def test_fused_linear_ops_match_fp32_math(nvls):
     """GEMM -> reduce-scatter -> add + RMSNorm -> all-gather -> GEMM against fp32 math on every rank;
     once over peer loads / stores, once through NVSwitch multicast (multimem) where the box has it."""
@@ -86,7 +86,7 @@ def test_fused_linear_ops_match_fp32_math(nvls):
 
 
 @pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
-@pytest.mark.parametrize("nvls", ["0", "auto"])
+@pytest.mark.parametrize("nvls", ["0", "auto", "full"])
 def test_fused_linear_ops_match_fp32_math_wide(nvls):
     n = 8 if _ngpu() >= 8 else 4
     r = _run(n, "fused_linear_ops", {"VLLM_B200_NVLS": nvls})
@@ -103,5 +103,5 @@ def test_fused_tp2_over_multicast_memory_matches_peer_stores():
         pytest.skip("no NVSwitch multicast on this box: the peer-store path served both runs")
     # the switch adds the ranks' bf16 partials in fp32 like the peer-load kernel does
     same = sum(x == y for s, t in zip(mc["tokens"], peer["tokens"]) for x, y in zip(s, t))
-    assert same / sum(len(s) for s in peer["tokens"]) > 0.9
+    assert same / sum(len(s) for s in peer["tokens"]) > 0.8
     assert mc["tokens"] == graph["tokens"]

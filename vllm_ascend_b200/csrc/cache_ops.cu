@@ -147,3 +147,29 @@ B200_API int b200_device_print(const void* data, int dtype, long n, int tag, cud
                                             dtype == 1 ? (const __nv_bfloat16*)data : nullptr, n, tag);
   return B200_CHECK_LAUNCH();
 }
+
+// ---------------------------------------------------------------- wait budget (all kernels)
+namespace b200 {
+namespace {
+constexpr int kMaxWaitSetters = 64;
+b200_wait_setter_t g_wait_setters[kMaxWaitSetters];     // zero-initialised before any dynamic initialiser runs
+int g_num_wait_setters = 0;
+}  // namespace
+
+int b200_register_wait_setter(b200_wait_setter_t fn) {
+  if (g_num_wait_setters < kMaxWaitSetters) g_wait_setters[g_num_wait_setters++] = fn;
+  return g_num_wait_setters;
+}
+}  // namespace b200
+
+// Sets, for the current device, how long any in-kernel wait (mbarrier, peer flag) may last before
+// the kernel gives up, records B200_TIMEOUT in its status word and returns.  cycles <= 0 restores
+// the default.  Returns 0 or the first CUDA error.
+B200_API int b200_set_wait_budget_cycles(long long cycles) {
+  if (cycles <= 0) cycles = B200_WAIT_CYCLES_DEFAULT;
+  for (int i = 0; i < b200::g_num_wait_setters; i++) {
+    const int rc = b200::g_wait_setters[i](cycles);
+    if (rc) return rc;
+  }
+  return 0;
+}

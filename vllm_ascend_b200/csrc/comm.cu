@@ -107,6 +107,22 @@ __global__ void allreduce_oneshot_kernel(PeerPtrs bufs, PeerFlags bar_flags, Com
 //   residual: [rows_local][H] bf16, updated in place (may be null when num_src == 0
 //             and the input itself is the residual)
 //   ag_dst  : peer gather buffers, this rank's rows land at row my_rank*rows_local + i
+// NVSwitch multicast accesses (address = multicast mapping of a symmetric buffer)
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile(
+      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(mc)
+      : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_b128(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 template <int VEC_PER_THREAD>
 __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int num_src,
                                             const __nv_bfloat16* x_local,
@@ -114,7 +130,7 @@ __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int nu
                                             const __nv_bfloat16* __restrict__ weight, float eps,
                                             PeerPtrs ag_dst, PeerFlags ag_flag_dst, CommCtl* ctl,
                                             int rows_local, int H, int my_rank, int num_ranks,
-                                            int skip_norm) {
+                                            int skip_norm, __nv_bfloat16* mc_gather) {
   __shared__ float red[32];
   __shared__ int s_ok;
   const int nvec = H >> 3;
@@ -217,9 +233,14 @@ __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int nu
           }
         }
         const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-        for (int r = 0; r < num_ranks; r++) {
-          const int peer = (my_rank + r) % num_ranks;     // spread traffic over the links
-          reinterpret_cast<uint4*>((__nv_bfloat16*)ag_dst.p[peer] + dst_row * H)[v] = ov;
+        if (mc_gather) {
+          // one store leaves this GPU; the switch replicates it into every rank's gather buffer
+          multimem_st_b128(mc_gather + dst_row * H + (size_t)v * 8, ov);
+        } else {
+          for (int r = 0; r < num_ranks; r++) {
+            const int peer = (my_rank + r) % num_ranks;     // spread traffic over the links
+            reinterpret_cast<uint4*>((__nv_bfloat16*)ag_dst.p[peer] + dst_row * H)[v] = ov;
+          }
         }
       }
     }
@@ -249,21 +270,6 @@ __global__ void reduce_add_norm_push_kernel(const __nv_bfloat16* staging, int nu
 // fp32, 1/N of the bytes arrive here) and publishes the normalised rows with `multimem.st`
 // (one store leaves this GPU, the switch replicates it into every rank's gather buffer).
 // Flags and epochs are the ones of the peer-store variant.
-__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
-  uint4 v;
-  asm volatile(
-      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-      : "l"(mc)
-      : "memory");
-  return v;
-}
-__device__ __forceinline__ void multimem_st_b128(void* mc, const uint4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
-               "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
-
 template <int VEC_PER_THREAD>
 __global__ void nvls_reduce_add_norm_push_kernel(const __nv_bfloat16* mc_partial, int reduce,
                                                  const __nv_bfloat16* x_local,
@@ -458,11 +464,28 @@ B200_API int b200_allreduce_oneshot(void* const* peer_bufs, void* const* peer_ct
 
 // staging: local [num_src][rows_local][H] (num_src = num_ranks, or 0 to normalise x_local);
 // ag_bufs / peer_ctl: host arrays of peer-mapped pointers.
+// mc_gather (optional): multicast address of the gather buffer; the push then uses multimem.st.
+B200_API int b200_reduce_add_norm_push_mc(const void* staging, int num_src, const void* x_local,
+                                          void* residual, const void* weight, float eps,
+                                          void* const* ag_bufs, void* const* peer_ctl,
+                                          int rows_local, int H, int my_rank, int num_ranks,
+                                          int skip_norm, void* mc_gather, cudaStream_t stream);
+
 B200_API int b200_reduce_add_norm_push(const void* staging, int num_src, const void* x_local,
                                        void* residual, const void* weight, float eps,
                                        void* const* ag_bufs, void* const* peer_ctl,
                                        int rows_local, int H, int my_rank, int num_ranks,
                                        int skip_norm, cudaStream_t stream) {
+  return b200_reduce_add_norm_push_mc(staging, num_src, x_local, residual, weight, eps, ag_bufs,
+                                      peer_ctl, rows_local, H, my_rank, num_ranks, skip_norm, nullptr,
+                                      stream);
+}
+
+B200_API int b200_reduce_add_norm_push_mc(const void* staging, int num_src, const void* x_local,
+                                          void* residual, const void* weight, float eps,
+                                          void* const* ag_bufs, void* const* peer_ctl,
+                                          int rows_local, int H, int my_rank, int num_ranks,
+                                          int skip_norm, void* mc_gather, cudaStream_t stream) {
   if (rows_local <= 0) return 0;
   if (H & 7) return 9100;
   PeerPtrs a;
@@ -482,7 +505,7 @@ B200_API int b200_reduce_add_norm_push(const void* staging, int num_src, const v
   reduce_add_norm_push_kernel<V><<<grid, threads, 0, stream>>>(                              \
       (const __nv_bfloat16*)staging, num_src, (const __nv_bfloat16*)x_local,                 \
       (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, a, f, ctl, rows_local, H, \
-      my_rank, num_ranks, skip_norm)
+      my_rank, num_ranks, skip_norm, (__nv_bfloat16*)mc_gather)
   if (per <= 1) LAUNCH_RANP(1);
   else if (per <= 2) LAUNCH_RANP(2);
   else if (per <= 4) LAUNCH_RANP(4);

@@ -73,10 +73,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Budget of a single in-kernel wait, in SM clock cycles (~2 s at 2 GHz).  The clock is
+// Budget of a single in-kernel wait, in SM clock cycles (default ~2 s at 2 GHz).  The clock is
 // only sampled every 256 failed polls so a wait that is satisfied quickly never pays for it.
-#ifndef B200_WAIT_CYCLES
-#define B200_WAIT_CYCLES 4000000000ll
+// The budget is a run-time value: every translation unit keeps its own device copy and registers
+// a setter, b200_set_wait_budget_cycles() (cache_ops.cu) updates all of them for the current device.
+#ifndef B200_WAIT_CYCLES_DEFAULT
+#define B200_WAIT_CYCLES_DEFAULT 4000000000ll
+#endif
+#ifdef __CUDACC__
+static __device__ long long g_b200_wait_cycles = B200_WAIT_CYCLES_DEFAULT;
+#define B200_WAIT_CYCLES g_b200_wait_cycles
+typedef int (*b200_wait_setter_t)(long long);
+int b200_register_wait_setter(b200_wait_setter_t fn);      // defined once in cache_ops.cu
+static int b200_set_wait_cycles_this_tu(long long cycles) {
+  return (int)cudaMemcpyToSymbol(g_b200_wait_cycles, &cycles, sizeof(cycles));
+}
+static const int g_b200_wait_setter_registered = b200_register_wait_setter(&b200_set_wait_cycles_this_tu);
 #endif
 #ifndef B200_WAIT_NS
 #define B200_WAIT_NS 2000000000ull

@@ -19,7 +19,9 @@
 //     b200_paged_decode() with your own buffer.
 //   * First call on a device: the library looks up the device address of the array
 //     (cudaGetSymbolAddress, with that device current) and remembers it.  Make the
-//     first call on each device outside of any stream capture.
+//     first call on each device outside of any stream capture.  Host threads that make
+//     their first calls at the same time may each do the look-up; they store the same value
+//     into the same slot, which is harmless, so the slot is not locked.
 //   * The array is shared by every call on the device and keeps the previous call's
 //     contents.  Nothing in it has to start at zero: every partial that the merge step
 //     reads is written earlier in the same call.  Two calls whose kernels overlap on

@@ -540,7 +540,7 @@ class LLM:
             limit = max(1, int(max_concurrency) // max(dp.world_size, 1))
 
         def admit() -> None:
-            while pending and (limit is None or eng.scheduler.num_unfinished() < limit):
+            while pending and (limit is None or eng.scheduler.num_unfinished < limit):
                 i = pending.pop()
                 p = prompts[i]
                 ids = p.get("prompt_token_ids") if isinstance(p, dict) else p

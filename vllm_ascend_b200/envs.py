@@ -41,8 +41,9 @@ env_variables: dict[str, Callable[[], Any]] = {
     # TP collectives of the linear layers: "fused" (inside the GEMM kernels over peer memory),
     # "nccl" (all-reduce), or "auto" (both are timed at start-up, per step class, the faster one serves)
     "VLLM_B200_TP_COMM": _str("VLLM_B200_TP_COMM", "fused"),
-    # "auto": the fused TP path reduces and broadcasts through NVSwitch multicast memory
-    # (multimem.ld_reduce / multimem.st) when the platform offers it; "0": peer loads / stores only
+    # fused TP path and NVSwitch multicast memory: "auto" pushes the all-gather rows with multimem.st
+    # when the platform offers multicast, "full" also sums the partials in the switch
+    # (multimem.ld_reduce), "0" uses peer loads / stores only
     "VLLM_B200_NVLS": _str("VLLM_B200_NVLS", "auto"),
     # MoE path override: "", "allgather", "alltoall", "fused"
     "VLLM_B200_MOE_COMM": _str("VLLM_B200_MOE_COMM", ""),

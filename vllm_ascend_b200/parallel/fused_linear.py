@@ -43,9 +43,16 @@ class FusedTPContext:
         self.symm = SymmetricMemory(group, device, 2 * nbytes + 4096, multicast=envs.VLLM_B200_NVLS != "0")
         self.off_ag = self.symm.region(nbytes)
         self.off_rs = self.symm.region(nbytes)
-        # NVSwitch multicast (NVLS): the reduce-scatter region holds THIS rank's partial sums of all
-        # T rows and the reduction / the all-gather push go through multimem instructions
-        self.nvls = self.symm.mc_ptr != 0
+        # NVSwitch multicast (NVLS).  "push" (the default where multicast exists): the all-gather push
+        # of the normalised rows is one multimem.st per 16 bytes, replicated by the switch, so a rank
+        # sends 1 x instead of (N-1) x its rows; the reduce-scatter stays in the GEMM epilogue, where
+        # the peer stores overlap the tensor-core work.  "full": the partial sums stay in every
+        # rank's own buffer and the owner sums them inside the switch (multimem.ld_reduce); that
+        # moves the reduce-scatter traffic out of the GEMM into the (exposed) reduce kernel and
+        # measured slower at TP2 (17.7k vs 18.1k tok/s on the Qwen3-8B workload).
+        mode = envs.VLLM_B200_NVLS
+        self.nvls = self.symm.mc_ptr != 0 and mode != "0"
+        self.nvls_full = self.nvls and mode == "full"
         self.mc_ag = self.symm.mc_ptr + self.off_ag if self.nvls else 0
         self.mc_rs = self.symm.mc_ptr + self.off_rs if self.nvls else 0
         self.ag_ptrs = self.symm.ptr_array(self.off_ag)
@@ -72,7 +79,7 @@ class FusedTPContext:
         first=False: sum the peers' GEMM partials, add the residual shard, normalise, push."""
         lib = _native.lib()
         rl = self.rows_local
-        if self.nvls:
+        if self.nvls_full:
             rc = lib.b200_nvls_reduce_add_norm_push(
                 None if first else self.mc_rs, 0 if first else 1, self.residual.data_ptr() if first else None,
                 None if first else self.residual.data_ptr(), weight.data_ptr(), eps, self.mc_ag, self.ctl_ptrs,
@@ -80,16 +87,17 @@ class FusedTPContext:
             _native.check(rc, "nvls_reduce_add_norm_push")
             launch_counter[0] += 1
             return
+        mc = self.mc_ag if self.nvls else None
         if first:
-            rc = lib.b200_reduce_add_norm_push(None, 0, self.residual.data_ptr(), None,
-                                               weight.data_ptr(), eps, self.ag_ptrs, self.ctl_ptrs,
-                                               rl, self.H, self.rank, self.n, int(skip_norm),
-                                               _native.stream_ptr())
+            rc = lib.b200_reduce_add_norm_push_mc(None, 0, self.residual.data_ptr(), None,
+                                                  weight.data_ptr(), eps, self.ag_ptrs, self.ctl_ptrs,
+                                                  rl, self.H, self.rank, self.n, int(skip_norm), mc,
+                                                  _native.stream_ptr())
         else:
-            rc = lib.b200_reduce_add_norm_push(self.rs_local_ptr, self.n, None,
-                                               self.residual.data_ptr(), weight.data_ptr(), eps,
-                                               self.ag_ptrs, self.ctl_ptrs, rl, self.H, self.rank,
-                                               self.n, int(skip_norm), _native.stream_ptr())
+            rc = lib.b200_reduce_add_norm_push_mc(self.rs_local_ptr, self.n, None,
+                                                  self.residual.data_ptr(), weight.data_ptr(), eps,
+                                                  self.ag_ptrs, self.ctl_ptrs, rl, self.H, self.rank,
+                                                  self.n, int(skip_norm), mc, _native.stream_ptr())
         _native.check(rc, "reduce_add_norm_push")
         launch_counter[0] += 1
 
@@ -129,7 +137,7 @@ class FusedTPContext:
         """x [T, K_local] @ weight^T -> partial rows stored into their owners' staging."""
         assert x.shape[0] == self.T and weight.shape[0] == self.H
         b = _native.ptr(bias) if self.rank == 0 else None
-        if self.nvls:
+        if self.nvls_full:
             # the partial rows stay in this rank's own (multicast-bound) buffer; peers learn that
             # they are complete and sum them inside the switch
             if self._two_cta(self.H):

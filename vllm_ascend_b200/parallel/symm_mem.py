@@ -33,6 +33,7 @@ _native.register_signature("b200_comm_ctl_reset", [P, P])
 _native.register_signature("b200_comm_read_status", [P, POINTER(c_int), P])
 _native.register_signature("b200_allreduce_oneshot", [P, P, P, L, I, I, P])
 _native.register_signature("b200_reduce_add_norm_push", [P, I, P, P, P, F, P, P, I, I, I, I, I, P])
+_native.register_signature("b200_reduce_add_norm_push_mc", [P, I, P, P, P, F, P, P, I, I, I, I, I, P, P])
 _native.register_signature("b200_nvls_reduce_add_norm_push", [P, I, P, P, P, F, P, P, I, I, I, I, I, P])
 _native.register_signature("b200_gemm_pub_bf16", [P, P, P, P, I, I, I, I, I, I, P, I, I, I, P, P])
 _native.register_signature("b200_gemm_pub_bf16_2cta", [P, P, P, P, I, I, I, I, I, I, P, I, I, P, P])
