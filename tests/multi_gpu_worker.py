@@ -40,7 +40,13 @@ def tp_generate():
     if fused:
         llm.engine.runner.model.sp_ctx.check()
     nvls = bool(fused and llm.engine.runner.model.sp_ctx.nvls)
-    return {"tokens": toks, "fused": fused, "nvls": nvls, "replays": llm.engine.runner.stats["graph_replays"]}
+    # log-probabilities of the first generated token (top 8): compared across the communication paths
+    lp = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, logprobs=8))
+    first_lp = [{str(k): float(v) for k, v in o.outputs[0].logprobs[0].items()} for o in lp]
+    if fused:
+        llm.engine.runner.model.sp_ctx.check()
+    return {"tokens": toks, "fused": fused, "nvls": nvls, "replays": llm.engine.runner.stats["graph_replays"],
+            "first_logprobs": first_lp}
 
 
 def fused_linear_ops():

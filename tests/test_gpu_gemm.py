@@ -119,3 +119,27 @@ def test_gemm_2cta_swiglu(M, I, K):
     h = a.float() @ w.float().t()
     exp = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
     assert (out.float() - exp).abs().max().item() < 0.02 * exp.abs().max().item() + 0.02
+
+
+@pytest.mark.parametrize("width", [128, 160, 192, 224, 256])
+def test_gemm_2cta_every_tile_width(width):
+    """The paired-CTA kernel picks its tile width (128..256 columns) per problem so that the tiles fill
+    whole waves of CTA pairs; every width is forced here on shapes with ragged last tiles in M and N,
+    with bias and residual, and on the decode shape that motivated it (768 x 4096)."""
+    import ctypes
+    lib = _native.lib()
+    _native.register_signature("b200_gemm_2cta_set_bn", [ctypes.c_int])
+    assert lib.b200_gemm_2cta_set_bn(width) == 0
+    try:
+        _check(768, 4096, 4096, bn=512)
+        _check(300, 520, 1024, bn=512, bias=True, residual=True, seed=3)
+        _check(1000, 776, 512, bn=512, seed=4)
+        _check(130, 136, 72, bn=512, seed=5)
+    finally:
+        lib.b200_gemm_2cta_set_bn(0)
+
+
+def test_gemm_2cta_chooses_narrow_tiles_for_few_tiles():
+    # automatic choice: same answers as the fixed widths on the shapes where it departs from 256
+    for M, N, K in ((768, 4096, 4096), (1024, 3072, 4096), (512, 6144, 4096), (8192, 768, 4096)):
+        _check(M, N, K, bn=512, seed=M)

@@ -24,8 +24,10 @@ class B200AttentionImpl:
         self.num_kv_heads, self.sliding_window = num_kv_heads, sliding_window
 
     def forward(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                meta: AttentionMetadata) -> torch.Tensor:
-        return ops.paged_attention(q, k_cache, v_cache, meta, self.scale, self.sliding_window or 0)
+                meta: AttentionMetadata, out: torch.Tensor = None) -> torch.Tensor:
+        """q [T, Hq, D] -> [T, Hq, D]; ``out`` (optional) receives the result."""
+        return ops.paged_attention(q, k_cache, v_cache, meta, self.scale, out=out, causal=True,
+                                   window=self.sliding_window or 0)
 
 
 class B200MetadataBuilder:
@@ -123,8 +125,11 @@ class B200FAImpl(B200AttentionImpl):
         if self.sliding_window:
             raise ValueError("the training-consistent attention backend does not support sliding windows")
 
-    def forward(self, q, k_cache, v_cache, meta):
-        out = torch.empty_like(q)
+    def forward(self, q, k_cache, v_cache, meta, out=None):
+        if out is None:
+            out = torch.empty_like(q)
+        if not q.is_cuda:
+            return super().forward(q, k_cache, v_cache, meta, out)
         return ops.paged_attention_consistent(q, k_cache, v_cache, meta, self.scale, out)
 
 
@@ -154,3 +159,33 @@ def _copy_blocks(t: torch.Tensor, pairs: torch.Tensor) -> None:
     src = pairs[:, 0].to(t.device)
     dst = pairs[:, 1].to(t.device)
     t[dst] = t[src]
+
+
+_ATTN_BACKENDS = {
+    # (use_mla, use_sparse, use_compress) -> backend class path (the reference's table:
+    # vllm_ascend/platform.py:216-242)
+    (False, False, False): "vllm_ascend_b200.attention.backend.B200AttentionBackend",
+    (True, False, False): "vllm_ascend_b200.attention.mla.B200MLABackend",
+    (True, True, False): "vllm_ascend_b200.attention.sfa.B200SFABackend",
+}
+
+
+def attn_backend_path(use_mla: bool = False, use_sparse: bool = False, use_compress: bool = False) -> str:
+    """Dotted path of the backend class for a layer kind.  One table for the platform hook a host
+    vLLM queries (``B200Platform.get_attn_backend_cls``) and for this package's own model code."""
+    key = (bool(use_mla), bool(use_sparse), bool(use_compress))
+    from ..platform_config import get_b200_config
+    rl = get_b200_config().rl_config
+    if rl.enabled and rl.enable_training_consistency:
+        if key != (False, False, False):
+            raise ValueError("the training-consistent attention backend supports neither MLA nor sparse attention")
+        return "vllm_ascend_b200.attention.backend.B200FABackend"
+    if key not in _ATTN_BACKENDS:
+        raise ValueError(f"no attention backend for use_mla={key[0]} use_sparse={key[1]} use_compress={key[2]}")
+    return _ATTN_BACKENDS[key]
+
+
+def get_attn_backend(use_mla: bool = False, use_sparse: bool = False, use_compress: bool = False):
+    import importlib
+    mod, cls = attn_backend_path(use_mla, use_sparse, use_compress).rsplit(".", 1)
+    return getattr(importlib.import_module(mod), cls)

@@ -57,6 +57,7 @@ struct Gemm2Params {
   CommCtl* ctl;
   int rows_per_owner;
   int raster;                         // M-tiles per raster group (0/1: column-major order)
+  int bn;                             // tile width: 128..256 in steps of 32 (SwiGLU tiles: 256)
 };
 // G2_PUB: the last CTA publishes this rank's reduce-scatter epoch to every peer (set with G2_RS;
 // alone it is the NVLS form: rows stay in the local multicast-bound buffer C)
@@ -213,14 +214,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // plain: this CTA's 128 of the tile's 256 W rows.  SwiGLU: the leader stages the 128
       // gate rows, the peer the matching 128 up rows.
       const int w_row = p.swiglu ? tn * 128 + (int)rank * p.up_row_offset
-                                 : tn * G2_BN + (int)rank * 128;
+                                 : tn * p.bn + (int)rank * (p.bn >> 1);
       for (int kb = 0; kb < num_kb; kb++) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) goto done;
         if (lane == 0) {
           uint8_t* sa = tiles + stage * G2_STAGE_BYTES;
           uint8_t* sb = sa + G2_A_BYTES;
           const uint32_t lbar = smem_u32(&full_bar[stage]) & kPeerBitMask;
-          if (leader) mbar_expect_tx(&full_bar[stage], 2 * G2_STAGE_BYTES);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * (G2_A_BYTES + (p.bn >> 1) * G2_BK * 2));
           tma_load_2d_2sm(sa, &tmap_a, lbar, kb * G2_BK, a_row);
           tma_load_2d_2sm(sb, &tmap_b, lbar, kb * G2_BK, w_row);
         }
@@ -231,7 +232,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (leader) {
-      constexpr uint32_t idesc = make_idesc_f16(G2_BM, G2_BN, true, false, false);
+      const uint32_t idesc = make_idesc_f16(G2_BM, p.bn, true, false, false);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -264,7 +265,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
-    const int out_per_tile = p.swiglu ? 128 : G2_BN;
+    const int out_per_tile = p.swiglu ? 128 : p.bn;
     uint8_t* rs_stage = smem + G2_STAGES * G2_STAGE_BYTES + 256 + q * (32 * G2_RS_ROW_BYTES);
     int it = 0;
     for (int t = cluster_id; t < num_tiles; t += num_clusters, it++) {
@@ -424,10 +425,10 @@ struct Tmap2Hash {
 
 // row-major bf16 [rows, cols], box = 128 rows x 64 columns, 128-byte swizzle
 static int get_tmap_128x64(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
-                           uint64_t ld) {
+                           uint64_t ld, uint32_t box_rows = 128) {
   static std::unordered_map<Tmap2Key, CUtensorMap, Tmap2Hash> cache;
   static std::mutex mu;
-  Tmap2Key key{ptr, rows, cols, ld};
+  Tmap2Key key{ptr, rows, cols, ld | ((uint64_t)box_rows << 48)};
   std::lock_guard<std::mutex> g(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -436,7 +437,7 @@ static int get_tmap_128x64(CUtensorMap* out, const void* ptr, uint64_t rows, uin
   }
   uint64_t dims[2] = {cols, rows};
   uint64_t strides[1] = {ld * 2};
-  uint32_t box[2] = {64, 128};
+  uint32_t box[2] = {64, box_rows};
   int rc = make_tmap(out, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
@@ -450,6 +451,7 @@ static int get_tmap_128x64(CUtensorMap* out, const void* ptr, uint64_t rows, uin
 using namespace b200;
 
 static int g_raster = 16;
+static int g_force_bn = 0;      // 0: choose per problem; 128..256: fixed tile width (benchmarks)
 
 static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, int ldw, long a_rows,
                        cudaStream_t stream) {
@@ -461,17 +463,42 @@ static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, in
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
+  const int max_clusters = num_sms() / 2;
+  p.tiles_m = (p.M + G2_BM - 1) / G2_BM;
+  // Tile width.  256 columns make the best use of the tensor cores, but whole waves of tiles
+  // over the CTA pairs matter more when there are only a few tiles: a decode batch of 768 rows
+  // against N = 4096 is 48 tiles of 256 columns on 74 pairs (35% of the GPU idle), or 66 tiles
+  // of 192 columns in the same single wave.  Cost model: waves x tile width; a narrower tile
+  // must win by 8% to be taken.
+  if (p.swiglu) {
+    p.bn = G2_BN;
+  } else if (g_force_bn >= 128 && g_force_bn <= 256 && (g_force_bn % 32) == 0) {
+    p.bn = g_force_bn;
+  } else {
+    auto cost = [&](int bn) {
+      const long tiles = (long)p.tiles_m * ((p.N + bn - 1) / bn);
+      return ((tiles + max_clusters - 1) / max_clusters) * bn;
+    };
+    p.bn = G2_BN;
+    long best = cost(G2_BN);
+    for (int bn = 224; bn >= 128; bn -= 32) {
+      const long c = cost(bn);
+      if (c * 100 < best * 92) {
+        best = c;
+        p.bn = bn;
+      }
+    }
+  }
   CUtensorMap ta, tb;
   int rc = get_tmap_128x64(&ta, A, (uint64_t)a_rows, (uint64_t)p.K, (uint64_t)lda);
   if (rc) return rc;
-  rc = get_tmap_128x64(&tb, W, (uint64_t)(p.swiglu ? 2L * p.N : p.N), (uint64_t)p.K, (uint64_t)ldw);
+  rc = get_tmap_128x64(&tb, W, (uint64_t)(p.swiglu ? 2L * p.N : p.N), (uint64_t)p.K, (uint64_t)ldw,
+                       p.swiglu ? 128u : (uint32_t)(p.bn >> 1));
   if (rc) return rc;
   p.up_row_offset = p.N;
-  const int out_per_tile = p.swiglu ? 128 : G2_BN;
-  p.tiles_m = (p.M + G2_BM - 1) / G2_BM;
+  const int out_per_tile = p.swiglu ? 128 : p.bn;
   p.tiles_n = (p.N + out_per_tile - 1) / out_per_tile;
   int clusters = p.tiles_m * p.tiles_n;
-  const int max_clusters = num_sms() / 2;
   if (clusters > max_clusters) clusters = max_clusters;
   p.raster = g_raster;
   gemm_bf16_2cta_kernel<<<2 * clusters, G2_THREADS, G2_SMEM_BYTES, stream>>>(ta, tb, p);
@@ -571,6 +598,12 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* W, void* C, const vo
   p.status = status;
   p.swiglu = swiglu;
   return launch_2cta(A, W, p, lda, ldw, M, stream);
+}
+
+// Fixed tile width of the paired-CTA kernel for every following call (0 = choose per problem).
+B200_API int b200_gemm_2cta_set_bn(int bn) {
+  g_force_bn = bn;
+  return 0;
 }
 
 // Tile order of the paired-CTA kernel: M-tiles per raster group (1 = plain column-major).

@@ -306,6 +306,12 @@ class GQAAttention:
         self.cos_sin = get_cos_sin_cache(self.rot_dim, max_pos, cfg.rope_theta, cfg.rope_scaling,
                                          pf.device)
         self.window = cfg.sliding_window or 0
+        # the attention implementation comes from the platform's backend table (paged tcgen05
+        # kernels, or the training-consistent single-kernel backend when the RL config asks for it)
+        from ..attention.backend import get_attn_backend
+        self.backend = get_attn_backend()
+        self.impl = self.backend.get_impl_cls()(self.Hq, self.D, self.scale, self.Hkv,
+                                                sliding_window=self.window or None)
         self.mrope_axis = None
         if cfg.mrope_section:
             assert 2 * sum(cfg.mrope_section) == self.rot_dim, "mrope sections must cover rot_dim / 2 pairs"
@@ -334,8 +340,7 @@ class GQAAttention:
         qkv = qkv_in
         T = qkv.shape[0]
         q = qkv[:, :self.Hq * self.D].view(T, self.Hq, self.D)
-        o = ops.paged_attention(q, k_cache, v_cache, meta, self.scale, causal=True,
-                                window=self.window)
+        o = self.impl.forward(q, k_cache, v_cache, meta)
         o = o.view(T, self.Hq * self.D)
         if self.out_gate:
             o = o * torch.sigmoid(qkv[:, (self.Hq + 2 * self.Hkv) * self.D:].float()).to(o.dtype)

@@ -29,14 +29,6 @@ except Exception:  # pragma: no cover - exercised only without vLLM
 
 SUPPORTED_QUANTIZATION = ["fp8", "compressed-tensors", "b200", "w8a8_dynamic", "modelopt"]
 
-_ATTN_BACKENDS = {
-    # (use_mla, use_sparse, use_compress) -> backend class path (platform.py:216-242)
-    (False, False, False): "vllm_ascend_b200.attention.backend.B200AttentionBackend",
-    (True, False, False): "vllm_ascend_b200.attention.mla.B200MLABackend",
-    (True, True, False): "vllm_ascend_b200.attention.sfa.B200SFABackend",
-}
-
-
 _HAS_GPU = torch.cuda.is_available()
 
 #: the worker class a host vLLM's executor constructs (a ``WorkerBase`` subclass)
@@ -144,17 +136,8 @@ class B200Platform(_Base):
         use_mla = bool(kwargs.get("use_mla", getattr(cfg, "use_mla", False)))
         use_sparse = bool(kwargs.get("use_sparse", getattr(cfg, "use_sparse", False)))
         use_compress = bool(kwargs.get("use_compress", getattr(cfg, "use_compress", False)))
-        key = (use_mla, use_sparse, use_compress)
-        from .platform_config import get_b200_config
-        rl = get_b200_config().rl_config
-        if rl.enabled and rl.enable_training_consistency:
-            if key != (False, False, False):
-                raise ValueError("the training-consistent attention backend supports neither MLA nor sparse attention")
-            return "vllm_ascend_b200.attention.backend.B200FABackend"
-        if key not in _ATTN_BACKENDS:
-            raise ValueError(f"no attention backend for use_mla={use_mla} use_sparse={use_sparse} "
-                             f"use_compress={use_compress}")
-        return _ATTN_BACKENDS[key]
+        from .attention.backend import attn_backend_path
+        return attn_backend_path(use_mla, use_sparse, use_compress)
 
     @classmethod
     def get_punica_wrapper(cls) -> str:

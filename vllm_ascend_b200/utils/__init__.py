@@ -74,47 +74,6 @@ def should_skip_allreduce_across_dp_group(engine_cfg, is_decode_only: bool) -> b
     return not (engine_cfg.model.is_moe and pc.enable_expert_parallel)
 
 
-# ---------------------------------------------------------------- OOT op table
-#: op name a host vLLM looks up  ->  class of this package that implements it
-OOT_OPS = {
-    "SiluAndMul": "vllm_ascend_b200.ops.host_ops.SiluAndMul",
-    "RMSNorm": "vllm_ascend_b200.ops.host_ops.RMSNorm",
-    "GemmaRMSNorm": "vllm_ascend_b200.ops.host_ops.GemmaRMSNorm",
-    "RotaryEmbedding": "vllm_ascend_b200.ops.host_ops.RotaryEmbedding",
-    "ColumnParallelLinear": "vllm_ascend_b200.models.layers.ColumnParallelLinear",
-    "RowParallelLinear": "vllm_ascend_b200.models.layers.RowParallelLinear",
-    "MergedColumnParallelLinear": "vllm_ascend_b200.models.layers.ColumnParallelLinear",
-    "QKVParallelLinear": "vllm_ascend_b200.models.layers.ColumnParallelLinear",
-    "VocabParallelEmbedding": "vllm_ascend_b200.models.layers.VocabParallelEmbedding",
-    "ParallelLMHead": "vllm_ascend_b200.models.layers.ParallelLMHead",
-    "FusedMoE": "vllm_ascend_b200.models.transformer.SparseMoeBlock",
-    "MultiHeadLatentAttentionWrapper": "vllm_ascend_b200.models.transformer.MLAAttention",
-}
-_registered = False
-
-
-def register_oot_ops() -> list[str]:
-    """Register the table with a host vLLM's ``CustomOp`` registry (once per process)."""
-    global _registered
-    if _registered:
-        return []
-    try:
-        from vllm.model_executor.custom_op import CustomOp
-    except Exception:
-        return []
-    import importlib
-    done = []
-    for name, path in OOT_OPS.items():
-        mod, cls = path.rsplit(".", 1)
-        try:
-            CustomOp.register_oot(_decorated_cls=getattr(importlib.import_module(mod), cls), name=name)
-            done.append(name)
-        except Exception:
-            continue
-    _registered = True
-    return done
-
-
 # ---------------------------------------------------------------- weak tensor references
 def weak_ref_tensor(t: Any) -> Any:
     """A view that does not keep the storage's allocation alive in the caching allocator's
