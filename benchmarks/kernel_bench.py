@@ -92,8 +92,8 @@ def bench_gemm(a):
         _native.lib().b200_gemm_2cta_set_raster(a.raster)
     _native.register_signature("b200_gemm_2cta_set_bn", [ctypes.c_int])
     _native.lib().b200_gemm_2cta_set_bn(a.tile_n)       # 0: the kernel chooses its tile width
-    ms = timeit(lambda: ops.linear(x, w, out=out, bn=a.bn), a.iters)
-    ms_lib = timeit(lambda: torch.nn.functional.linear(x, w), a.iters) if a.compare else None
+    ms = timeit(lambda: ops.linear(x, w, out=out, bn=a.bn), a.iters, flush=not a.no_flush)
+    ms_lib = timeit(lambda: torch.nn.functional.linear(x, w), a.iters, flush=not a.no_flush) if a.compare else None
     hbm, tf, tag = peaks()
     fl = 2.0 * M * N * K
     line = (f"gemm M={M} N={N} K={K} bn={a.bn or 'auto'} tile_n={a.tile_n or 'auto'}: {ms:.4f} ms  {fl / ms / 1e9:.0f} TFLOP/s "
@@ -259,6 +259,7 @@ def main():
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--raster", type=int, default=0, help="M-tiles per raster group of the paired-CTA GEMM")
     ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--no-flush", action="store_true", help="gemm: leave the operands in L2 between timed launches")
     ap.add_argument("--tile-n", type=int, default=0, help="paired-CTA GEMM: fixed tile width (128..256 step 32)")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=1152)

@@ -88,15 +88,31 @@ struct DecItem {
   int q_start, q_len, seq_len, ctx, t0, n;
 };
 
-__device__ __forceinline__ DecItem dec_item(const DecParams& p, int item) {
+// The three words of an item that live in global memory.  They are loaded one item ahead
+// (dec_load) and turned into a DecItem (dec_make, arithmetic only) when the item starts, so no
+// role waits for a dependent global load at an item boundary.
+struct DecRaw {
+  int q0, q1, seq_len;
+};
+
+__device__ __forceinline__ DecRaw dec_load(const DecParams& p, int item) {
+  const int seq = (item / p.Hkv) % p.num_seqs;
+  DecRaw r;
+  r.q0 = p.query_start_loc[seq];
+  r.q1 = p.query_start_loc[seq + 1];
+  r.seq_len = p.seq_lens[seq];
+  return r;
+}
+
+__device__ __forceinline__ DecItem dec_make(const DecParams& p, int item, const DecRaw& r) {
   DecItem w;
   w.h = item % p.Hkv;
-  const int r = item / p.Hkv;
-  w.seq = r % p.num_seqs;
-  w.split = r / p.num_seqs;
-  w.q_start = p.query_start_loc[w.seq];
-  w.q_len = p.query_start_loc[w.seq + 1] - w.q_start;
-  w.seq_len = p.seq_lens[w.seq];
+  const int q = item / p.Hkv;
+  w.seq = q % p.num_seqs;
+  w.split = q / p.num_seqs;
+  w.q_start = r.q0;
+  w.q_len = r.q1 - r.q0;
+  w.seq_len = r.seq_len;
   w.ctx = w.seq_len - w.q_len;
   int kv_lo = 0;
   if (p.window > 0) kv_lo = max(0, w.ctx - p.window + 1);
@@ -106,6 +122,10 @@ __device__ __forceinline__ DecItem dec_item(const DecParams& p, int item) {
   w.t0 = tile_lo + w.split * per_split;
   w.n = w.q_len > 0 ? max(0, min(tile_hi, w.t0 + per_split) - w.t0) : 0;
   return w;
+}
+
+__device__ __forceinline__ DecItem dec_item(const DecParams& p, int item) {
+  return dec_make(p, item, dec_load(p, item));
 }
 
 template <int D, int NVT>
@@ -198,19 +218,60 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int rpl = p.rows_per_load;
     const int parts = 128 / rpl;
     uint32_t gt = 0, it = 0;             // tiles / items issued so far by this CTA
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      const DecItem w = dec_item(p, item);
-      if (w.n <= 0) continue;
-      const int* bt = p.block_table + (long)w.seq * p.max_blocks;
-      const int qb = it & 1;
-      if (!mbar_wait(&q_empty[qb], ((it >> 1) & 1u) ^ 1u, abort_word)) goto done;
+    // The description of an item (two dependent global loads) and the block ids of its first tile
+    // (a third) are fetched while the previous item streams, so that the first TMA of an item
+    // can follow the last TMA of its predecessor without a gap and the K/V pipeline stays full
+    // across item boundaries.
+    auto first_blk = [&](const DecItem& d) -> int {
+      if (d.n <= 0 || lane >= parts) return 0;
+      const int key0 = (d.t0 << 7) + lane * rpl;
+      return p.block_table[(long)d.seq * p.max_blocks + min(key0, d.seq_len - 1) / p.block_size];
+    };
+    DecItem w_next;
+    DecRaw raw_next = {0, 0, 0};          // words of the item after the next one
+    int blk_first_next = 0;
+    w_next.n = 0;
+    if ((int)blockIdx.x < num_items) {
+      w_next = dec_item(p, blockIdx.x);
+      blk_first_next = first_blk(w_next);
+      if ((int)(blockIdx.x + gridDim.x) < num_items) raw_next = dec_load(p, blockIdx.x + gridDim.x);
+    }
+    auto advance = [&](int item_after) {
+      if (item_after < num_items) {
+        w_next = dec_make(p, item_after, raw_next);
+        blk_first_next = first_blk(w_next);
+        if (item_after + (int)gridDim.x < num_items) raw_next = dec_load(p, item_after + gridDim.x);
+      }
+    };
+    // The query rows of an item go into Q buffer (its index among the non-empty items) & 1; the
+    // buffer of the item after the current one is free (its last reader was two items ago), so
+    // that load is issued one item early as well and never sits in front of an item's first MMA.
+    auto load_q = [&](uint32_t idx, const DecItem& d) -> bool {
+      const int b = idx & 1;
+      if (!mbar_wait(&q_empty[b], ((idx >> 1) & 1u) ^ 1u, abort_word)) return false;
       if (lane == 0) {
-        mbar_expect_tx(&q_full[qb], Cfg::Q_BYTES);
+        mbar_expect_tx(&q_full[b], Cfg::Q_BYTES);
 #pragma unroll
         for (int hf = 0; hf < NH; hf++)
-          tma_load_4d(Qs + qb * Cfg::Q_BYTES + hf * DEC_QHALF, &tmap_q, &q_full[qb], hf * 64, 0, w.h,
-                      w.q_start);
+          tma_load_4d(Qs + b * Cfg::Q_BYTES + hf * DEC_QHALF, &tmap_q, &q_full[b], hf * 64, 0, d.h, d.q_start);
       }
+      __syncwarp();
+      return true;
+    };
+    bool q_ahead = false;                // the next non-empty item's Q load was already issued
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const DecItem w = w_next;
+      int blk_cur = blk_first_next;
+      const int item_after = item + gridDim.x;
+      if (w.n <= 0) {
+        advance(item_after);
+        continue;
+      }
+      const int* bt = p.block_table + (long)w.seq * p.max_blocks;
+      if (!q_ahead) {
+        if (!load_q(it, w)) goto done;
+      }
+      q_ahead = false;
       // Block ids are fetched one tile ahead (lane p holds the id of part p), so the
       // dependent global load never sits between a freed stage and the next TMA issue.
       auto load_blk = [&](int j) -> int {
@@ -218,7 +279,6 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int key0 = ((w.t0 + j) << 7) + lane * rpl;
         return bt[min(key0, w.seq_len - 1) / p.block_size];
       };
-      int blk_cur = load_blk(0);
       for (int j = 0; j < w.n; j++, gt++) {
         const int st = gt % ST;
         const uint32_t ph = (gt / ST) & 1u;
@@ -274,6 +334,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
           __syncwarp();
         }
         blk_cur = blk_next;
+        if (j == 0) advance(item_after);       // after this item's first tile is on its way
+        // third tile: its stage was freed by the last S MMA of the previous item, so the Q buffer
+        // of the next item (last read by that MMA) is free as well and load_q does not wait
+        if (j == min(2, w.n - 1) && item_after < num_items && w_next.n > 0) {
+          if (!load_q(it + 1, w_next)) goto done;
+          q_ahead = true;
+        }
       }
       it++;
     }
@@ -284,8 +351,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t q_addr0 = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs),
                    p_addr = smem_u32(Ps);
     uint32_t gt = 0, it = 0;
+    DecRaw raw_next = {0, 0, 0};
+    if ((int)blockIdx.x < num_items) raw_next = dec_load(p, blockIdx.x);
     for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      const DecItem w = dec_item(p, item);
+      const DecItem w = dec_make(p, item, raw_next);
+      if (item + (int)gridDim.x < num_items) raw_next = dec_load(p, item + gridDim.x);
       if (w.n <= 0) continue;
       const int qb = it & 1;
       const uint32_t q_addr = q_addr0 + qb * Cfg::Q_BYTES;
@@ -361,8 +431,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const float sl2 = p.scale_log2;
     int* redi = reinterpret_cast<int*>(red);        // [2 tiles][4 warps][16]
     uint32_t gt = 0, it = 0;
+    DecRaw raw_next = {0, 0, 0};
+    if ((int)blockIdx.x < num_items) raw_next = dec_load(p, blockIdx.x);
     for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      const DecItem w = dec_item(p, item);
+      const DecItem w = dec_make(p, item, raw_next);
+      if (item + (int)gridDim.x < num_items) raw_next = dec_load(p, item + gridDim.x);
       const int nv = w.q_len * G;                   // valid columns (<= 16)
       if (w.n <= 0) {
         if (p.num_splits > 1 && w.q_len > 0) {      // an empty split still owns its partial slots
