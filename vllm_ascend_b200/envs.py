@@ -48,7 +48,6 @@ env_variables: dict[str, Callable[[], Any]] = {
     # MoE path override: "", "allgather", "alltoall", "fused"
     "VLLM_B200_MOE_COMM": _str("VLLM_B200_MOE_COMM", ""),
     "VLLM_B200_ENABLE_NVLS": _bool("VLLM_B200_ENABLE_NVLS", "0"),
-    "VLLM_B200_DEBUG_BOUNDS": _bool("VLLM_B200_DEBUG_BOUNDS", "0"),
     # device-side bounded wait, in microseconds of globaltimer
     "VLLM_B200_WAIT_TIMEOUT_US": _int("VLLM_B200_WAIT_TIMEOUT_US", 1_000_000),
     # ---- runtime features (names follow the reference where they make sense) ----
