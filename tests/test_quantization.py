@@ -123,3 +123,24 @@ def test_kv_cache_fp8_roundtrip():
     q = schemes.kv_quant_fp8(x, scale)
     assert q.dtype == torch.float8_e4m3fn
     assert (schemes.kv_dequant_fp8(q, scale, torch.float32) - x).abs().max() < 0.07 * x.abs().max()
+
+
+def test_description_of_fused_layers_and_modelopt_detection():
+    """A per-weight description names checkpoint projections; the fused qkv / gate_up layers take the
+    type of their parts and refuse parts that disagree.  ModelOpt exports select a scheme by algorithm."""
+    import pytest
+    from vllm_ascend_b200.quantization import description_quant_type, detect_modelopt
+    d = {"model.layers.0.self_attn.q_proj.weight": "W8A8_DYNAMIC", "model.layers.0.self_attn.k_proj.weight": "W8A8_DYNAMIC",
+         "model.layers.0.self_attn.v_proj.weight": "W8A8_DYNAMIC", "model.layers.0.mlp.gate_proj.weight": "W8A8",
+         "model.layers.0.mlp.up_proj.weight": "FLOAT", "model.layers.0.mlp.down_proj.weight": "w8a8",
+         "model.layers.1.self_attn.q_proj.weight": "W4A16", "model.layers.1.self_attn.k_proj.weight": "W4A16"}
+    assert description_quant_type(d, "model.layers.0.self_attn.qkv_proj") == "W8A8_DYNAMIC"
+    assert description_quant_type(d, "model.layers.0.mlp.down_proj") == "W8A8"
+    assert description_quant_type(d, "model.layers.1.self_attn.qkv_proj") == "W4A16"      # k == v checkpoints: no v_proj
+    assert description_quant_type(d, "model.layers.2.self_attn.qkv_proj") == "FLOAT"
+    with pytest.raises(ValueError, match="quantized differently"):
+        description_quant_type(d, "model.layers.0.mlp.gate_up_proj")
+    assert detect_modelopt({"quantization": {"quant_algo": "MXFP8"}}) == "W8A8_MXFP8"
+    assert detect_modelopt({"quant_algo": "FP8"}) == "W8A8FP8_DYNAMIC"
+    with pytest.raises(ValueError):
+        detect_modelopt({"quant_algo": "INT3"})

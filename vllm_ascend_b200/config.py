@@ -90,6 +90,7 @@ class ModelConfig:
     # ---- numerics / quantization ----
     dtype: str = "bfloat16"
     quantization: Optional[str] = None   # None | "fp8" (128x128 block) | "w8a8_dynamic"
+    quantization_config: Optional[dict] = None   # the checkpoint's own description (compressed-tensors, ModelOpt)
     weight_block_size: tuple = (128, 128)
     init_std: float = 0.02
     seed: int = 0
@@ -253,9 +254,9 @@ class ModelConfig:
             if method == "fp8" and qc.get("weight_block_size"):
                 kw.update(quantization="fp8", weight_block_size=tuple(qc["weight_block_size"]))
             elif method == "compressed-tensors":
-                kw.update(quantization="compressed-tensors")
+                kw.update(quantization="compressed-tensors", quantization_config=dict(qc))
             elif method:
-                kw.update(quantization=method)
+                kw.update(quantization=method, quantization_config=dict(qc))
         kw.update(over)
         return cls(**kw)
 
@@ -263,6 +264,10 @@ class ModelConfig:
     def from_pretrained(cls, path: str, **over) -> "ModelConfig":
         with open(os.path.join(path, "config.json")) as f:
             d = json.load(f)
+        mo = os.path.join(path, "hf_quant_config.json")       # ModelOpt exports keep their description here
+        if "quantization_config" not in d and os.path.exists(mo):
+            with open(mo) as f:
+                d = dict(d, quantization_config=dict(json.load(f), quant_method="modelopt"))
         cfg = cls.from_hf_dict(d, **over)
         cfg.model_path = path
         cfg.name = os.path.basename(os.path.normpath(path))

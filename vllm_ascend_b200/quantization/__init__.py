@@ -18,7 +18,8 @@ from .registry import get_scheme_class, register_scheme, registered  # noqa: F40
 _ALIASES = {"fp8": "FP8_BLOCK", "fp8_block": "FP8_BLOCK", "w8a8_dynamic": "W8A8_DYNAMIC",
             "w8a8": "W8A8", "w8a8fp8_dynamic": "W8A8FP8_DYNAMIC", "w4a16": "W4A16",
             "w8a16": "W8A16", "float": "FLOAT", "ascend": "DESCRIPTION",
-            "compressed-tensors": "COMPRESSED_TENSORS"}
+            "compressed-tensors": "COMPRESSED_TENSORS", "modelopt": "MODELOPT", "modelopt_mxfp8": "MODELOPT_MXFP8",
+            "mxfp8": "MXFP8"}
 
 
 class LinearMethod:
@@ -64,14 +65,65 @@ def load_description(model_path: Optional[str]) -> Optional[dict]:
     return None
 
 
+#: fused modules of this package -> the checkpoint projections packed into them: a description file
+#: names the checkpoint projections, and all parts of one fused GEMM must share a quant type
+#: (vllm_ascend/quantization/modelslim_config.py:105-402 keeps this table per model type).
+PACKED_MODULES = {
+    "qkv_proj": ["q_proj", "k_proj", "v_proj"],
+    "gate_up_proj": ["gate_proj", "up_proj"],
+    "kv_a_proj": ["kv_a_proj_with_mqa"],
+}
+
+
+def description_quant_type(description: dict, prefix: str) -> str:
+    """Quant type of a (possibly fused) linear layer from a per-weight description.  A fused layer
+    takes the type of its parts and raises when they disagree
+    (vllm_ascend/quantization/modelslim_config.py:431-470).  A part that the checkpoint does not
+    have at all (v_proj of k == v attention) is skipped; a layer without any entry is FLOAT."""
+    proj = prefix.rsplit(".", 1)[-1]
+    direct = description.get(prefix + ".weight")
+    if direct is not None:
+        return str(direct).upper()
+    parts = PACKED_MODULES.get(proj)
+    if not parts:
+        return "FLOAT"
+    found: dict[str, str] = {}
+    for part in parts:
+        key = prefix[:-len(proj)] + part + ".weight"
+        if key in description:
+            found[part] = str(description[key]).upper()
+    if not found:
+        return "FLOAT"
+    kinds = set(found.values())
+    if len(kinds) > 1:
+        raise ValueError(f"the parts of {prefix} are quantized differently ({found}): a fused GEMM needs "
+                         "one quant type for all of them")
+    return kinds.pop()
+
+
+def detect_modelopt(qc: dict) -> str:
+    """ModelOpt export (``quant_method: modelopt`` / ``hf_quant_config.json``): the algorithm name
+    decides the scheme (vllm_ascend/quantization/modelopt_mxfp8_config.py:28-41 registers the MXFP8
+    form)."""
+    algo = str((qc.get("quantization") or qc).get("quant_algo", "")).upper()
+    table = {"MXFP8": "W8A8_MXFP8", "FP8": "W8A8FP8_DYNAMIC", "FP8_PER_CHANNEL_PER_TOKEN": "W8A8FP8_DYNAMIC",
+             "FP8_PB_WO": "FP8_BLOCK", "W4A16_AWQ": "W4A16", "NVFP4": "W4A4_MXFP4"}
+    if algo not in table:
+        raise ValueError(f"unsupported ModelOpt quant_algo {algo!r}; known: {sorted(table)}")
+    return table[algo]
+
+
 def resolve_quant_type(cfg, prefix: str, description: Optional[dict]) -> str:
     q = _ALIASES.get(str(cfg.quantization).lower(), str(cfg.quantization).upper())
     if q == "DESCRIPTION":
         if description is None:
             raise ValueError("--quantization ascend needs quant_model_description.json")
-        return str(description.get(prefix + ".weight", "FLOAT")).upper()
+        return description_quant_type(description, prefix)
+    qc = getattr(cfg, "quantization_config", None)
+    if q in ("MODELOPT", "MODELOPT_MXFP8", "MXFP8"):
+        return detect_modelopt(qc) if qc and q == "MODELOPT" else "W8A8_MXFP8"
     if q == "COMPRESSED_TENSORS":
-        return getattr(cfg, "_ct_scheme", "W8A8_DYNAMIC")
+        return detect_compressed_tensors(qc) if qc else "W8A8_DYNAMIC"
     return q
 
 
