@@ -20,6 +20,68 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def _aggregate(prof, wall: float, title: str) -> str:
+    agg = defaultdict(lambda: [0, 0.0])
+    first, last = None, 0.0
+    for ev in prof.events():
+        if ev.device_type == torch.autograd.DeviceType.CUDA:
+            a = agg[ev.name[:90]]
+            a[0] += 1
+            a[1] += ev.device_time
+            tr = ev.time_range
+            first = tr.start if first is None else min(first, tr.start)
+            last = max(last, tr.end)
+    total = sum(v[1] for v in agg.values())
+    span = (last - first) if first is not None else 0.0
+    out = [f"== {title}: wall {wall:.2f} s, device span {span / 1e6:.2f} s, "
+           f"sum of kernel time {total / 1e6:.2f} s ({100 * total / max(span, 1):.1f}% of the span), "
+           f"{sum(v[0] for v in agg.values())} launches"]
+    for name, (cnt, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:24]:
+        out.append(f"  {us / total * 100:5.1f}%  {us / 1e6:8.3f} s  {cnt:7d}  {name}")
+    return "\n".join(out)
+
+
+def reference_whole_pass(args) -> None:
+    """Kernel shares of one whole pass of the same workload through upstream vLLM (the benchmark's
+    reference arm): in-process engine core so that CUPTI sees its kernels, no out-of-tree plugin."""
+    import importlib.util
+    import json
+    import tempfile
+    import time
+    os.environ["VLLM_PLUGINS"] = ""
+    os.environ["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"
+    os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
+    spec = importlib.util.spec_from_file_location(
+        "bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    from vllm import LLM, SamplingParams
+    hf = dict(bench.HF_SHAPES[args.model])
+    d = tempfile.mkdtemp(prefix="profile_cfg_")
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(hf, f)
+    llm = LLM(model=d, load_format="dummy", skip_tokenizer_init=True, dtype="bfloat16",
+              max_model_len=args.input_len + args.output_len + 16, max_num_seqs=args.max_num_seqs,
+              max_num_batched_tokens=args.max_num_batched_tokens, gpu_memory_utilization=0.92,
+              enable_prefix_caching=False, seed=0)
+    sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
+    mk = lambda seed: [{"prompt_token_ids": p} for p in
+                       bench.make_prompts(args.num_prompts, args.input_len, hf["vocab_size"], seed)]
+    llm.generate(mk(1), sp, use_tqdm=False)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        llm.generate(mk(2), sp, use_tqdm=False)
+        torch.cuda.synchronize()
+    text = _aggregate(prof, time.perf_counter() - t0, "upstream vLLM, whole pass under the profiler")
+    print(text)
+    os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
+    with open(args.out, "w") as f:
+        f.write(text + "\n")
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen3-8b")
@@ -34,7 +96,11 @@ def main():
     ap.add_argument("--out", default="step_profile.txt")
     ap.add_argument("--whole-pass", action="store_true",
                     help="profile one complete pass of the workload (device activity only) after a warm pass")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
+                    help="reference: upstream vLLM (in-process, plugins off); whole-pass mode only")
     args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_whole_pass(args)
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -55,24 +121,7 @@ def main():
             llm.generate(mk(), sp)
             torch.cuda.synchronize()
         wall = time.perf_counter() - t0
-        agg = defaultdict(lambda: [0, 0.0])
-        first, last = None, 0.0
-        for ev in prof.events():
-            if ev.device_type == torch.autograd.DeviceType.CUDA:
-                a = agg[ev.name[:90]]
-                a[0] += 1
-                a[1] += ev.device_time
-                tr = ev.time_range
-                first = tr.start if first is None else min(first, tr.start)
-                last = max(last, tr.end)
-        total = sum(v[1] for v in agg.values())
-        span = (last - first) if first is not None else 0.0
-        out = [f"== whole pass under the profiler: wall {wall:.2f} s, device span {span / 1e6:.2f} s, "
-               f"sum of kernel time {total / 1e6:.2f} s ({100 * total / max(span, 1):.1f}% of the span), "
-               f"{sum(v[0] for v in agg.values())} launches"]
-        for name, (cnt, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:20]:
-            out.append(f"  {us / total * 100:5.1f}%  {us / 1e6:8.3f} s  {cnt:7d}  {name}")
-        text = "\n".join(out)
+        text = _aggregate(prof, wall, "whole pass under the profiler")
         if rank == 0:
             print(text)
             os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)

@@ -23,6 +23,7 @@ P, I, L, F, U = c_void_p, c_int, c_long, c_float, c_uint
 _SIGNATURES = {
     "b200_gemm_bf16": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, P],
     "b200_gemm_bf16_2cta": [P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+    "b200_gemm_bf16_2cta_norm": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, ctypes.c_float, P, P, P, P],
     "b200_gemm_swiglu_bf16": [P, P, P, I, I, I, I, I, I, P, P],
     "b200_grouped_gemm_bf16": [P, P, P, P, I, L, I, I, I, I, I, I, P, P],
     "b200_rms_norm": [P, P, P, P, L, I, F, I, L, L, P],

@@ -58,6 +58,11 @@ struct Gemm2Params {
   int rows_per_owner;
   int raster;                         // M-tiles per raster group (0/1: column-major order)
   int bn;                             // tile width: 128..256 in steps of 32 (SwiGLU tiles: 256)
+  // ---- RMSNorm folded into the GEMMs around it (the norm weight lives in W of the consumer)
+  const float* row_ss_in;             // [M] sum of squares of the rows of A: accumulators are scaled by
+  float inv_dim, eps;                 //     rsqrt(row_ss_in[row] * inv_dim + eps) before bias / SwiGLU
+  float* row_ss_out;                  // [M] += sum of squares of the bf16 output row (producer side)
+  float* row_zero;                    // [M] cleared by the tiles of column block 0 (the buffer a later GEMM accumulates)
 };
 // G2_PUB: the last CTA publishes this rank's reduce-scatter epoch to every peer (set with G2_RS;
 // alone it is the NVLS form: rows stay in the local multicast-bound buffer C)
@@ -289,6 +294,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
         crow = p.C + (size_t)row * p.ldc;
       }
       const __nv_bfloat16* rrow = p.residual ? p.residual + (size_t)row * p.ldc : nullptr;
+      float rstd = 1.f, ss_acc = 0.f;
+      if (p.row_ss_in && row_ok) rstd = rsqrtf(p.row_ss_in[row] * p.inv_dim + p.eps);
+      if (p.row_zero && tn == 0 && row_ok) p.row_zero[row] = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < out_per_tile; c0 += 32) {
         const int col0 = tn * out_per_tile + c0;
@@ -301,8 +309,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; j++) {
-            const float g = __uint_as_float(r[j]);
-            r[j] = __float_as_uint(g / (1.f + __expf(-g)) * __uint_as_float(u[j]));
+            const float g = __uint_as_float(r[j]) * rstd;
+            r[j] = __float_as_uint(g / (1.f + __expf(-g)) * (__uint_as_float(u[j]) * rstd));
           }
         } else {
           tmem_ld_wait();
@@ -315,6 +323,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
               float v[8];
 #pragma unroll
               for (int j = 0; j < 8; j++) v[j] = __uint_as_float(r[g * 8 + j]);
+              if (p.row_ss_in && !p.swiglu) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] *= rstd;
+              }
               if (p.bias) {
                 const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
                 const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -340,6 +352,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
               o.y = pack_bf16x2(v[2], v[3]);
               o.z = pack_bf16x2(v[4], v[5]);
               o.w = pack_bf16x2(v[6], v[7]);
+              if (p.row_ss_out) {       // of the values as stored (bf16), like a norm that reads them back
+                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  const float2 f = unpack_bf16x2(ow[j]);
+                  ss_acc += f.x * f.x + f.y * f.y;
+                }
+              }
               if (p.mode & G2_RS)
                 *reinterpret_cast<uint4*>(rs_stage + lane * G2_RS_ROW_BYTES + ((c0 & 32) + g * 8) * 2) = o;
               else
@@ -371,6 +391,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      if (p.row_ss_out && row_ok) atomicAdd(p.row_ss_out + row, ss_acc);
       tc_fence_before();
       __syncwarp();
       // accumulator buffer drained: tell the leader's MMA warp (local or remote arrive)
@@ -604,6 +625,36 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* W, void* C, const vo
 B200_API int b200_gemm_2cta_set_bn(int bn) {
   g_force_bn = bn;
   return 0;
+}
+
+// b200_gemm_bf16_2cta with the RMSNorm around it folded in (either side optional):
+//   row_ss_in  [M] fp32: accumulators are scaled by rsqrt(row_ss_in[row] / norm_dim + eps) (the
+//              normalisation of A's rows; the norm weight is expected inside W),
+//   row_ss_out [M] fp32: += sum of squares of every stored output row (+bias +residual, bf16),
+//   row_zero   [M] fp32: set to 0 (the accumulator a later GEMM of the chain adds into).
+B200_API int b200_gemm_bf16_2cta_norm(const void* A, const void* W, void* C, const void* bias,
+                                      const void* residual, int M, int N, int K, int lda, int ldw,
+                                      int ldc, int swiglu, const void* row_ss_in, int norm_dim,
+                                      float eps, void* row_ss_out, void* row_zero, int* status,
+                                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
+  if (swiglu && (N % 128)) return 9132;
+  if (row_ss_in && norm_dim <= 0) return 9133;
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.C = (__nv_bfloat16*)C;
+  p.status = status;
+  p.swiglu = swiglu;
+  p.row_ss_in = (const float*)row_ss_in;
+  p.inv_dim = norm_dim > 0 ? 1.f / (float)norm_dim : 0.f;
+  p.eps = eps;
+  p.row_ss_out = (float*)row_ss_out;
+  p.row_zero = (float*)row_zero;
+  return launch_2cta(A, W, p, lda, ldw, M, stream);
 }
 
 // Tile order of the paired-CTA kernel: M-tiles per raster group (1 = plain column-major).

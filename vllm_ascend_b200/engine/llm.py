@@ -648,7 +648,11 @@ class LLM:
             raise ValueError("reload_weights needs a checkpoint directory")
         if self.engine.has_unfinished():
             raise RuntimeError("reload_weights with requests in flight")
-        n = len(self.engine.runner.model.load_weights(iterate_safetensors(src)))
+        model = self.engine.runner.model
+        n = len(model.load_weights(iterate_safetensors(src)))
+        if getattr(model, "norm_folded", False):        # the norm weights just came back: fold them again
+            from ..models.folded import fold_norms
+            fold_norms(model)
         self.cfg.model.model_path = src
         self.engine.scheduler.pool.reset_prefix_cache()
         return n

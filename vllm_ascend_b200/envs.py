@@ -41,6 +41,8 @@ env_variables: dict[str, Callable[[], Any]] = {
     # TP collectives of the linear layers: "fused" (inside the GEMM kernels over peer memory),
     # "nccl" (all-reduce), or "auto" (both are timed at start-up, per step class, the faster one serves)
     "VLLM_B200_TP_COMM": _str("VLLM_B200_TP_COMM", "fused"),
+    # "1" (default): dense bf16 decoders on one GPU fold RMSNorm into the neighbouring GEMMs; "0": off
+    "VLLM_B200_FOLD_NORM": _str("VLLM_B200_FOLD_NORM", "1"),
     # fused TP path and NVSwitch multicast memory: "auto" pushes the all-gather rows with multimem.st
     # when the platform offers multicast, "full" also sums the partials in the switch
     # (multimem.ld_reduce), "0" uses peer loads / stores only

@@ -318,7 +318,11 @@ class GQAAttention:
             self.mrope_axis = ref.mrope_axis_table(cfg.mrope_section, cfg.mrope_interleaved).to(pf.device)
 
     def __call__(self, x: torch.Tensor, meta, kv_cache) -> torch.Tensor:
-        qkv = self.qkv_proj(x)
+        return self.o_proj(self.attend(self.qkv_proj(x), meta, kv_cache))
+
+    def attend(self, qkv: torch.Tensor, meta, kv_cache) -> torch.Tensor:
+        """Everything between the two projections: q/k norm + rotary + KV write, paged attention,
+        output gate.  qkv [T, (Hq + 2 Hkv) D (+ gate)] -> [T, Hq D]."""
         k_cache, v_cache = kv_cache
         mpos = getattr(meta, "mrope_positions", None) if self.mrope_axis is not None else None
         pcp = getattr(meta, "pcp", None)
@@ -344,7 +348,7 @@ class GQAAttention:
         o = o.view(T, self.Hq * self.D)
         if self.out_gate:
             o = o * torch.sigmoid(qkv[:, (self.Hq + 2 * self.Hkv) * self.D:].float()).to(o.dtype)
-        return self.o_proj(o)
+        return o
 
 
 _GATED_ACTS = {"silu": None, "swish": None, "gelu_pytorch_tanh": "gelu_tanh", "gelu_tanh": "gelu_tanh",

@@ -400,6 +400,11 @@ class CausalLM:
                 and (self.sp_prefill if input_ids.shape[0] > self.sp_decode_max_tokens else self.sp_decode):
             from ..parallel.fused_linear import forward_sp
             return forward_sp(self, self.sp_ctx, input_ids, meta, kv_caches)
+        if getattr(self, "norm_folded", False) and input_ids.is_cuda and inputs_embeds is None \
+                and intermediate is None and not self.aux_layers and getattr(meta, "deepstack", None) is None:
+            from . import folded
+            if input_ids.shape[0] >= folded.min_rows():
+                return folded.forward_folded(self, input_ids, meta, kv_caches)
         if self.is_first:
             # multimodal steps pass embeddings with the encoder outputs already merged in
             h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds

@@ -208,6 +208,31 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return out.view(*x.shape[:-1], N)
 
 
+def linear_norm_folded(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                       residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                       swiglu: bool = False, ss_in: Optional[torch.Tensor] = None, norm_dim: int = 0,
+                       eps: float = 1e-6, ss_out: Optional[torch.Tensor] = None,
+                       zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paired-CTA GEMM with the RMSNorm around it folded in (CUDA, bf16, x [M, K] with M >= 1).
+
+    ``ss_in`` (fp32 [>= M], sum of squares of x's rows): the result rows are scaled by
+    rsqrt(ss_in / norm_dim + eps), i.e. the GEMM runs on the un-normalised rows and ``weight``
+    already carries the norm weight.  ``ss_out``: the sum of squares of every stored output row is
+    added to it (the statistics of the NEXT norm).  ``zero``: cleared (the buffer a later GEMM of the
+    chain accumulates into).  ``residual`` may alias ``out``."""
+    M, K = x.shape
+    N = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    rc = _native.lib().b200_gemm_bf16_2cta_norm(
+        x.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias), _native.ptr(residual), M, N, K,
+        x.stride(0), weight.stride(0), out.stride(0), int(swiglu), _native.ptr(ss_in), int(norm_dim), float(eps),
+        _native.ptr(ss_out), _native.ptr(zero), _native.status_word(x.device).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "gemm_2cta_norm")
+    launch_counter[0] += 1
+    return out
+
+
 def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
                   two_cta: bool = False) -> torch.Tensor:
     """silu(x @ Wg^T) * (x @ Wu^T) with weight = [Wg; Wu] ([2I, K]) in one GEMM: the tile pairs

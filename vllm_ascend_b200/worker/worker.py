@@ -94,6 +94,10 @@ class B200Worker:
             self.runner.load_model(moe_runtime=self.moe_runtime)
         if cfg.enable_lora:
             self.runner.init_lora()
+        if self.world_size == 1 and cfg.device == "cuda":
+            from ..models import folded
+            if folded.attach(self.runner.model, cfg):
+                logger.info("RMSNorm folded into the neighbouring GEMMs (%d layers)", len(self.runner.model.layers))
         from ..platform_config import get_b200_config
         oc = get_b200_config().weight_offload_config
         if oc.enabled:
@@ -173,12 +177,28 @@ class B200Worker:
         """Copy new values into the live parameters (same shapes, any device)."""
         if self._weight_update_state != "updating":
             raise RuntimeError("call start_weight_update() first")
-        return len(self.runner.model.load_weights(named_tensors))
+        loaded = self.runner.model.load_weights(named_tensors)
+        self._updated_names = getattr(self, "_updated_names", set()) | set(loaded)
+        return len(loaded)
 
     def finish_weight_update(self) -> None:
         if self._weight_update_state != "updating":
             raise RuntimeError("no weight update in progress")
         self._weight_update_state = "idle"
+        names, self._updated_names = getattr(self, "_updated_names", set()), set()
+        model = self.runner.model
+        if getattr(model, "norm_folded", False):
+            # a norm weight lives inside the GEMM weight that follows it: both must arrive together
+            for L in model.layers:
+                p = f"model.layers.{L.idx}"
+                for norm, parts in ((f"{p}.input_layernorm.weight", ("q_proj", "k_proj", "v_proj", "qkv_proj")),
+                                    (f"{p}.post_attention_layernorm.weight", ("gate_proj", "up_proj", "gate_up_proj"))):
+                    got_w = any(f".{x}.weight" in n and n.startswith(p + ".") for n in names for x in parts)
+                    if got_w != (norm in names):
+                        raise RuntimeError(f"weight update of layer {L.idx} replaced a projection without its "
+                                           "norm weight (or the reverse); with folded norms send both")
+            from ..models.folded import fold_norms
+            fold_norms(model)
         if self.device.type == "cuda":
             torch.cuda.synchronize()
 
