@@ -271,3 +271,52 @@ def test_training_consistent_attention_backend_selection():
     plain = LLM("tiny-qwen", device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     assert not training_consistent_attention()
     assert a == [o.outputs[0].token_ids for o in plain.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=4))]
+
+
+def _ns(**kw):
+    from types import SimpleNamespace as NS
+    return NS(**kw)
+
+
+def test_pipeline_refuses_unrunnable_parallel_layouts():
+    from vllm_ascend_b200 import platform as P
+    with pytest.raises(ValueError, match="prefill context parallelism"):
+        P._validate_parallel_config(_ns(parallel_config=_ns(tensor_parallel_size=4, prefill_context_parallel_size=2,
+                                                            decode_context_parallel_size=1)))
+    with pytest.raises(ValueError, match="must divide"):
+        P._validate_parallel_config(_ns(parallel_config=_ns(tensor_parallel_size=4, prefill_context_parallel_size=1,
+                                                            decode_context_parallel_size=3)))
+    with pytest.raises(ValueError, match="speculative"):
+        P._validate_parallel_config(_ns(
+            parallel_config=_ns(tensor_parallel_size=4, prefill_context_parallel_size=1, decode_context_parallel_size=2),
+            speculative_config=_ns(num_speculative_tokens_per_batch_size={1: 3})))
+    P._validate_parallel_config(_ns(parallel_config=_ns(tensor_parallel_size=4, prefill_context_parallel_size=1,
+                                                        decode_context_parallel_size=2), speculative_config=None))
+
+
+def test_pipeline_detects_quantization_from_the_checkpoint_dir(tmp_path):
+    import json
+    from vllm_ascend_b200 import platform as P
+    (tmp_path / "quant_model_description.json").write_text(json.dumps({"model.layers.0.mlp.down_proj.weight": "FLOAT"}))
+    mc = _ns(model=str(tmp_path), quantization=None, hf_config=None)
+    P._auto_detect_quantization(_ns(model_config=mc))
+    assert mc.quantization == "ascend"
+    mc2 = _ns(model=str(tmp_path), quantization="fp8", hf_config=None)
+    P._auto_detect_quantization(_ns(model_config=mc2))
+    assert mc2.quantization == "fp8"                      # an explicit choice is kept
+    other = tmp_path / "plain"
+    other.mkdir()
+    mc3 = _ns(model=str(other), quantization=None, hf_config=_ns(quantization_config={"quant_method": "compressed-tensors"}))
+    P._auto_detect_quantization(_ns(model_config=mc3))
+    assert mc3.quantization == "compressed-tensors"
+
+
+def test_pipeline_ties_cp_interleave_to_block_size_under_kv_transfer():
+    from vllm_ascend_b200 import platform as P
+    bad = _ns(parallel_config=_ns(prefill_context_parallel_size=1, decode_context_parallel_size=2,
+                                  cp_kv_cache_interleave_size=1),
+              cache_config=_ns(block_size=128), kv_transfer_config=_ns())
+    with pytest.raises(ValueError, match="interleave"):
+        P._validate_cp_kv(bad)
+    bad.kv_transfer_config = None
+    P._validate_cp_kv(bad)

@@ -93,10 +93,39 @@ class B200AttentionBackend:
 
     @staticmethod
     def swap_blocks(src: torch.Tensor, dst: torch.Tensor, src_to_dst: torch.Tensor) -> None:
-        """Copies whole blocks between two caches (device<->device or device<->pinned host)."""
+        """Copies whole blocks between two caches (device<->device or device<->pinned host) with one
+        launch of the block copy kernel on the current stream; caches the kernel cannot address
+        (pageable host memory, other layouts) take the indexing form."""
+        _swap_blocks(src, dst, src_to_dst)
+
+
+def _swap_blocks(src: torch.Tensor, dst: torch.Tensor, src_to_dst: torch.Tensor) -> None:
+    def addressable(t):
+        return t.is_cuda or t.is_pinned()
+
+    dev = src.device if src.is_cuda else dst.device
+    ok = (dev.type == "cuda" and addressable(src) and addressable(dst) and src.dim() == 4 and dst.dim() == 4
+          and src.shape[1:] == dst.shape[1:] and src.dtype == dst.dtype and src.stride(3) == 1 and dst.stride(3) == 1
+          and (src.shape[3] * src.element_size()) % 16 == 0 and src_to_dst.numel() > 0)
+    if not ok:
         s = src_to_dst[:, 0].long()
         d = src_to_dst[:, 1].long()
         dst[d.to(dst.device)] = src[s.to(src.device)].to(dst.device, non_blocking=True)
+        return
+    import vllm_ascend_b200.distributed.kv_transfer.nvlink_connector  # noqa: F401  (signatures)
+    e = src.element_size()
+    pairs = src_to_dst.to(torch.int32)
+    sb = pairs[:, 0].contiguous().to(dev, non_blocking=True)
+    db = pairs[:, 1].contiguous().to(dev, non_blocking=True)
+    ptrs = torch.tensor([src.data_ptr(), dst.data_ptr()], dtype=torch.int64).to(dev, non_blocking=True)
+    rc = _native.lib().b200_kv_block_copy(
+        ptrs[0:1].data_ptr(), ptrs[1:2].data_ptr(), sb.data_ptr(), db.data_ptr(), pairs.shape[0], 1,
+        src.shape[1], src.shape[3] * e, src.shape[2], 0, 0,
+        src.stride(0) * e, src.stride(1) * e, src.stride(2) * e,
+        dst.stride(0) * e, dst.stride(1) * e, dst.stride(2) * e,
+        src.shape[0], dst.shape[0], _native.status_word(dev).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "swap_blocks")
+    _native.count_launch()
 
 
 _TRAINING_CONSISTENT = False

@@ -92,3 +92,34 @@ def build_tile_worklist(query_lens: np.ndarray, tok_per_tile: int,
         order = np.argsort(-work, kind="stable")
         tile_seq, tile_qoff = tile_seq[order], tile_qoff[order]
     return np.ascontiguousarray(tile_seq), np.ascontiguousarray(tile_qoff)
+
+
+def metadata_from_tensors(query_start_loc: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
+                          max_query_len: int, max_seq_len: int, num_q_heads: int, num_kv_heads: int,
+                          head_dim: int, decode_kernel: bool = True) -> AttentionMetadata:
+    """Metadata for one attention call from device tensors alone (callers that reach the attention op
+    through its dispatcher schema have no runner to prepare the host-side views): copies the two
+    length vectors to the host once, orders nothing (the batch must already be decodes-first) and
+    builds the tile work list of the tensor-core kernel."""
+    qsl = query_start_loc.detach().cpu().numpy().astype(np.int32)
+    sl = seq_lens.detach().cpu().numpy().astype(np.int32)
+    q_lens = qsl[1:] - qsl[:-1]
+    B = int(sl.shape[0])
+    nd, npf, ndt, _ = split_decodes_and_prefills(q_lens)
+    T = int(qsl[-1])
+    meta = AttentionMetadata(
+        num_reqs=B, num_actual_tokens=T, max_query_len=int(max_query_len), max_seq_len=int(max_seq_len),
+        query_start_loc=query_start_loc, seq_lens=seq_lens, block_table=block_table, slot_mapping=None,
+        positions=None, query_start_loc_cpu=qsl, seq_lens_cpu=sl, num_decodes=nd, num_decode_tokens=ndt,
+        num_prefills=npf, num_input_tokens=T)
+    if query_start_loc.is_cuda and max_query_len > 1:
+        G = max(1, num_q_heads // num_kv_heads)
+        skip = nd if (decode_kernel and head_dim == 128 and 16 % G == 0) else 0
+        ts, tq = build_tile_worklist(q_lens[skip:], max(1, 128 // G), sl[skip:])
+        if skip == 0:
+            meta.num_decodes = meta.num_decode_tokens = 0
+        dev = query_start_loc.device
+        meta.tile_seq = torch.from_numpy(ts + np.int32(skip)).to(dev)
+        meta.tile_qoff = torch.from_numpy(tq).to(dev)
+        meta.num_tiles = len(ts)
+    return meta

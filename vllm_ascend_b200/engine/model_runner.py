@@ -111,6 +111,8 @@ class ModelRunner:
         self._h_ids = torch.zeros(T, dtype=i64, pin_memory=pin)
         self._h_pos = torch.zeros(T, dtype=i64, pin_memory=pin)
         self._h_slot = torch.zeros(T, dtype=i64, pin_memory=pin)
+        self._h_req = torch.zeros(T, dtype=torch.int32, pin_memory=pin)
+        self._req_rows = torch.zeros(T, dtype=torch.int32, device=device)
         self._h_qsl = torch.zeros(B + 1, dtype=i32, pin_memory=pin)
         self._h_sl = torch.zeros(B, dtype=i32, pin_memory=pin)
         self._h_bt = torch.zeros((B, self.max_blocks_per_seq), dtype=i32, pin_memory=pin)
@@ -349,6 +351,10 @@ class ModelRunner:
                 self.block_table_cpu[row, :nb] = req.block_ids
                 self.row_num_blocks[row] = nb
 
+    def _use_device_slots(self) -> bool:
+        from .. import envs
+        return envs.VLLM_B200_DEVICE_SLOT_MAPPING == "1" and self.device.type == "cuda"
+
     def _prepare_inputs(self, so: SchedulerOutput, pad_to: Optional[int] = None):
         from ..profiler import nvtx_range
         with nvtx_range("prepare_inputs"):
@@ -430,10 +436,20 @@ class ModelRunner:
         nb = True
         self.input_ids[:Tp].copy_(h._h_ids[:Tp], non_blocking=nb)
         self.positions[:Tp].copy_(h._h_pos[:Tp], non_blocking=nb)
-        self.slot_mapping[:Tp].copy_(h._h_slot[:Tp], non_blocking=nb)
         self.query_start_loc[:Bp + 1].copy_(h._h_qsl[:Bp + 1], non_blocking=nb)
         self.seq_lens[:Bp].copy_(h._h_sl[:Bp], non_blocking=nb)
         self.block_table[:Bp].copy_(h._h_bt[:Bp], non_blocking=nb)
+        if self._use_device_slots() and pcp_meta is None and self.dcp_size == 1:
+            # slots from the block table on the device: the request row of every token travels
+            # (4 bytes per token) instead of the slot (8 bytes), padding rows carry -1
+            from ..ops.bookkeeping import slot_mapping as device_slot_mapping
+            h._h_req[:T] = torch.from_numpy(req_idx.astype(np.int32))
+            h._h_req[T:Tp] = -1
+            self._req_rows[:Tp].copy_(h._h_req[:Tp], non_blocking=nb)
+            device_slot_mapping(self.block_table[:Bp], self._req_rows[:Tp], self.positions[:Tp], self.block_size,
+                                self.num_blocks, out=self.slot_mapping[:Tp])
+        else:
+            self.slot_mapping[:Tp].copy_(h._h_slot[:Tp], non_blocking=nb)
         self.stats["h2d_bytes"] += Tp * 24 + (Bp + 1) * 4 + Bp * 4 + Bp * self.max_blocks_per_seq * 4
 
         if self.lora_manager is not None:

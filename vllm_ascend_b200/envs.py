@@ -43,6 +43,9 @@ env_variables: dict[str, Callable[[], Any]] = {
     "VLLM_B200_TP_COMM": _str("VLLM_B200_TP_COMM", "fused"),
     # "1" (default): dense bf16 decoders on one GPU fold RMSNorm into the neighbouring GEMMs; "0": off
     "VLLM_B200_FOLD_NORM": _str("VLLM_B200_FOLD_NORM", "1"),
+    # "1": the slot of every token is computed on the device from the block table (one small kernel per
+    # step) instead of on the host; "0" (default): host numpy + copy
+    "VLLM_B200_DEVICE_SLOT_MAPPING": _str("VLLM_B200_DEVICE_SLOT_MAPPING", "0"),
     # fused TP path and NVSwitch multicast memory: "auto" pushes the all-gather rows with multimem.st
     # when the platform offers multicast, "full" also sums the partials in the switch
     # (multimem.ld_reduce), "0" uses peer loads / stores only

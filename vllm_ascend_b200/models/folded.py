@@ -32,6 +32,9 @@ def supports(model, engine_cfg) -> bool:
         return False
     if model.comm.size != 1 or engine_cfg.enable_lora or engine_cfg.enable_sleep_mode:
         return False
+    from ..platform_config import get_b200_config
+    if get_b200_config().weight_offload_config.enabled:
+        return False          # offloaded layers hold their weights on the host between their turns
     if engine_cfg.speculative_config or engine_cfg.kv_transfer_config and \
             (engine_cfg.kv_transfer_config.get("kv_connector") == "LayerwiseConnector"):
         return False

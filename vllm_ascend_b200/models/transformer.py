@@ -403,7 +403,8 @@ class CausalLM:
         if getattr(self, "norm_folded", False) and input_ids.is_cuda and inputs_embeds is None \
                 and intermediate is None and not self.aux_layers and getattr(meta, "deepstack", None) is None:
             from . import folded
-            if input_ids.shape[0] >= folded.min_rows():
+            if input_ids.shape[0] >= folded.min_rows() and \
+                    not any(getattr(L, "offloaded_call", None) is not None for L in self.layers):
                 return folded.forward_folded(self, input_ids, meta, kv_caches)
         if self.is_first:
             # multimodal steps pass embeddings with the encoder outputs already merged in

@@ -222,6 +222,12 @@ def linear_norm_folded(x: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
     chain accumulates into).  ``residual`` may alias ``out``."""
     M, K = x.shape
     N = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    if weight.dim() != 2 or weight.shape[1] != K or N == 0 or not weight.is_cuda:
+        raise ValueError(f"weight {tuple(weight.shape)} on {weight.device} does not fit rows of {K} columns "
+                         "(offloaded or unloaded layer?)")
+    for name, t in (("ss_in", ss_in), ("ss_out", ss_out), ("zero", zero)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() < M):
+            raise ValueError(f"{name} must hold at least {M} fp32 values")
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     rc = _native.lib().b200_gemm_bf16_2cta_norm(

@@ -201,6 +201,8 @@ class B200Platform(_Base):
         cc = getattr(vllm_config, "compilation_config", None)
         mc = getattr(vllm_config, "model_config", None)
         cache = getattr(vllm_config, "cache_config", None)
+        _validate_parallel_config(vllm_config)
+        _auto_detect_quantization(vllm_config)
         _fix_incompatible_config(vllm_config)
         if pc is not None:
             _validate_finegrained(cfg, pc.tensor_parallel_size, max(1, getattr(pc, "data_parallel_size", 1)))
@@ -247,6 +249,7 @@ class B200Platform(_Base):
                 sc.scheduler_cls = "vllm_ascend_b200.core.profiling_chunk.ProfilingChunkScheduler"
             elif s.enable_balance_scheduling:
                 sc.scheduler_cls = "vllm_ascend_b200.core.balance.BalanceScheduler"
+        _validate_cp_kv(vllm_config)
         _set_allocator_env()
         logger.debug("B200 platform config finalised: %s", cfg)
 
@@ -258,8 +261,13 @@ class B200Platform(_Base):
 
     @classmethod
     def import_kernels(cls) -> None:
+        """Loads the native library and defines the ``torch.ops.b200`` dispatcher ops with their meta
+        functions (the reference imports its compiled op library and the meta registrations here,
+        platform.py import_kernels)."""
         from . import _native
         _native.load(required=torch.cuda.is_available())
+        from .ops.torch_bindings import register as register_torch_ops
+        register_torch_ops()
 
 
 # GPU-side knobs of a host config that this runtime does not honour are reset so they can
@@ -290,6 +298,63 @@ def _fix_incompatible_config(vllm_config: Any) -> None:
         dp = getattr(getattr(vllm_config, "parallel_config", None), "data_parallel_rank", 0) or 0
         if not str(ktc.engine_id).endswith(f"-dp{dp}") and dp:
             ktc.engine_id = f"{ktc.engine_id}-dp{dp}"
+
+
+def _validate_parallel_config(vllm_config: Any) -> None:
+    """Parallel layouts the worker behind a host engine cannot run are refused before any process
+    starts (the reference refuses prefill context parallelism on its first-generation runner and
+    ties sparse-attention DCP to the TP size, platform.py:1381-1398; dynamic speculative lengths
+    with DCP, platform.py:1401-1418)."""
+    pc = getattr(vllm_config, "parallel_config", None)
+    if pc is None:
+        return
+    tp = getattr(pc, "tensor_parallel_size", 1) or 1
+    pcp = getattr(pc, "prefill_context_parallel_size", 1) or 1
+    dcp = getattr(pc, "decode_context_parallel_size", 1) or 1
+    if pcp > 1:
+        raise ValueError("prefill context parallelism is offered by this package's own engine "
+                         "(LLM(prefill_context_parallel_size=...)), not behind a host engine: "
+                         f"set --prefill-context-parallel-size 1 (got {pcp})")
+    if dcp > 1 and tp % dcp:
+        raise ValueError(f"decode_context_parallel_size ({dcp}) must divide tensor_parallel_size ({tp})")
+    spec = getattr(vllm_config, "speculative_config", None)
+    if spec is not None and dcp > 1 and getattr(spec, "num_speculative_tokens_per_batch_size", None):
+        raise ValueError("per-batch-size speculative lengths cannot be combined with decode context "
+                         "parallelism: set --decode-context-parallel-size 1 or drop "
+                         "num_speculative_tokens_per_batch_size")
+
+
+def _auto_detect_quantization(vllm_config: Any) -> None:
+    """A checkpoint directory that carries a quantization description selects the quantization
+    method when the user gave none (platform.py:365-366, utils.py maybe_auto_detect_quantization)."""
+    mc = getattr(vllm_config, "model_config", None)
+    if mc is None or getattr(mc, "quantization", None):
+        return
+    path = getattr(mc, "model", None)
+    if not isinstance(path, str) or not os.path.isdir(path):
+        return
+    from .quantization import detect_quantization
+    found = detect_quantization(path, getattr(mc, "hf_config", None))
+    if found:
+        logger.info("quantization method %r detected from %s", found, path)
+        try:
+            mc.quantization = found
+        except Exception:
+            pass
+
+
+def _validate_cp_kv(vllm_config: Any) -> None:
+    """Context parallelism with KV transfer moves whole pages between instances: the interleave
+    granule of the context-parallel KV layout has to be the page size (platform.py:1167-1184)."""
+    pc = getattr(vllm_config, "parallel_config", None)
+    cache = getattr(vllm_config, "cache_config", None)
+    if pc is None or cache is None or getattr(vllm_config, "kv_transfer_config", None) is None:
+        return
+    cp = (getattr(pc, "prefill_context_parallel_size", 1) or 1) * (getattr(pc, "decode_context_parallel_size", 1) or 1)
+    inter = getattr(pc, "cp_kv_cache_interleave_size", None)
+    if cp > 1 and inter is not None and inter != getattr(cache, "block_size", inter):
+        raise ValueError(f"cp_kv_cache_interleave_size ({inter}) must equal block_size ({cache.block_size}) "
+                         "when context parallelism is combined with KV transfer or a KV pool")
 
 
 def _set_allocator_env() -> None:

@@ -65,6 +65,22 @@ def load_description(model_path: Optional[str]) -> Optional[dict]:
     return None
 
 
+def detect_quantization(model_path: Optional[str], hf_config=None) -> Optional[str]:
+    """Quantization method a checkpoint directory implies when the user named none: a per-weight
+    description file selects ``ascend``; a ModelOpt export its own method; otherwise the
+    ``quantization_config.quant_method`` of the HF config (the reference detects the description
+    file the same way before the engine starts, vllm_ascend/quantization/utils.py
+    maybe_auto_detect_quantization)."""
+    if model_path and os.path.exists(os.path.join(model_path, "quant_model_description.json")):
+        return "ascend"
+    if model_path and os.path.exists(os.path.join(model_path, "hf_quant_config.json")):
+        return "modelopt"
+    qc = getattr(hf_config, "quantization_config", None) if hf_config is not None else None
+    if isinstance(qc, dict) and qc.get("quant_method"):
+        return str(qc["quant_method"])
+    return None
+
+
 #: fused modules of this package -> the checkpoint projections packed into them: a description file
 #: names the checkpoint projections, and all parts of one fused GEMM must share a quant type
 #: (vllm_ascend/quantization/modelslim_config.py:105-402 keeps this table per model type).
