@@ -16,6 +16,10 @@ def _cfg():
     from vllm_ascend_b200.config import ModelConfig
     # WIDE=1: enough heads for 8-way tensor parallelism
     wide = os.environ.get("WIDE", "0") == "1"
+    if os.environ.get("MQA", "0") == "1":       # one KV head, replicated over the TP ranks
+        return ModelConfig(name="t", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=512,
+                           intermediate_size=1024, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=1,
+                           head_dim=128, qk_norm=True, rope_theta=1e6, dtype="bfloat16", init_std=0.05)
     return ModelConfig(name="t", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=1024 if wide else 512,
                        intermediate_size=2048 if wide else 1024, num_hidden_layers=3,
                        num_attention_heads=16 if wide else 8, num_key_value_heads=8 if wide else 2, head_dim=128,
@@ -30,7 +34,9 @@ def tp_generate():
     prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 333, 129, 7)]
     sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
     pcp = int(os.environ.get("PCP", "1"))
+    dcp = int(os.environ.get("DCP", "1"))
     llm = LLM(_cfg(), device="cuda", tensor_parallel_size=world // pcp, prefill_context_parallel_size=pcp,
+              decode_context_parallel_size=dcp,
               max_model_len=512, max_num_seqs=8,
               max_num_batched_tokens=256, num_gpu_blocks_override=40,
               enforce_eager=os.environ.get("EAGER", "0") == "1", cudagraph_capture_sizes=[2, 4, 8])
@@ -207,8 +213,93 @@ def moe_fused():
     return {"max_rel_err": max(max(e) for e in all_errs), "status": status, "calls": comm.calls}
 
 
+def pp_generate():
+    """Two pipeline stages on two GPUs (NCCL send / recv of hidden + residual, token broadcast)."""
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    world = int(os.environ["WORLD_SIZE"])
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 333, 129, 7)]
+    llm = LLM(_cfg(), device="cuda", tensor_parallel_size=1, pipeline_parallel_size=world, max_model_len=512,
+              max_num_seqs=8, max_num_batched_tokens=256, num_gpu_blocks_override=40, enforce_eager=True)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    lp = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, logprobs=8))
+    return {"tokens": [o.outputs[0].token_ids for o in outs],
+            "first_logprobs": [{str(k): float(v) for k, v in o.outputs[0].logprobs[0].items()} for o in lp]}
+
+
+def sleep_wake():
+    """Sleep mode on NCCL ranks with the extra cleanup: graphs dropped and the model-parallel
+    communicators destroyed on sleep, re-created into the same coordinators on wake-up."""
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    world = int(os.environ["WORLD_SIZE"])
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 129)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    llm = LLM(_cfg(), device="cuda", tensor_parallel_size=world, max_model_len=512, max_num_seqs=8,
+              max_num_batched_tokens=256, num_gpu_blocks_override=40, enable_sleep_mode=True,
+              cudagraph_capture_sizes=[2, 4], additional_config={"rl_config": {"sleep_mode_extra_cleanup": True}})
+    before = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    torch.cuda.synchronize()
+    used0 = torch.cuda.mem_get_info()[0]
+    llm.sleep(level=1)
+    free_asleep = torch.cuda.mem_get_info()[0]
+    llm.wake_up()
+    after = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    return {"before": before, "after": after, "freed_bytes": int(free_asleep - used0),
+            "replays": llm.engine.runner.stats["graph_replays"]}
+
+
+def weight_transfer():
+    """RL weight update over NCCL: rank 0 is the trainer (holds other weights, serves no requests),
+    rank 1 a live single-GPU engine that receives the buckets and applies them in place."""
+    from vllm_ascend_b200.distributed.weight_transfer import NCCLWeightTransferEngine
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    rank = int(os.environ["RANK"])
+    port = int(os.environ["MASTER_PORT"]) + 17
+    # each process is a world of its own for the engine; the transfer group spans both
+    os.environ["WORLD_SIZE"], os.environ["RANK"] = "1", "0"
+    os.environ["MASTER_PORT"] = str(int(os.environ["MASTER_PORT"]) + 31 + rank)
+    torch.cuda.set_device(rank)
+    cfg = _cfg()
+    cfg.seed = 42 if rank == 0 else 1
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    prompts = [list(range(10, 90)), list(range(300, 340))]
+    llm = LLM(cfg, device=f"cuda:{rank}", max_model_len=256, max_num_seqs=4, max_num_batched_tokens=128,
+              num_gpu_blocks_override=16, enforce_eager=True)
+    mine = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    eng = NCCLWeightTransferEngine("127.0.0.1", port, rank, 2, backend="nccl", bucket_bytes=4 << 20)
+    if rank == 0:
+        eng.send_weights(llm.engine.runner.model.named_parameters())
+        out = {"trainer": mine, "buckets": eng.stats["buckets"]}
+    else:
+        w = llm.engine.worker
+        w.start_weight_update()
+        params = dict(w.runner.model.named_parameters())
+
+        def apply(pairs):
+            n = 0
+            for name, tensor in pairs:
+                params[name].copy_(tensor)
+                n += 1
+            return n
+        n = eng.receive_weights(apply)
+        w.finish_weight_update()
+        llm.reset_prefix_cache()
+        out = {"before": mine, "after": [o.outputs[0].token_ids for o in llm.generate(prompts, sp)], "applied": n,
+               "params": len(params)}
+    torch.cuda.synchronize()
+    eng.close()
+    # both sides report through files-free stdout lines; the test reads them per rank
+    print("PART%d " % rank + json.dumps(out), flush=True)
+    return out
+
+
 if __name__ == "__main__":
-    res = {"tp_generate": tp_generate, "symm_allreduce": symm_allreduce, "fused_linear_ops": fused_linear_ops, "moe_fused": moe_fused}[sys.argv[1]]()
+    res = {"pp_generate": pp_generate, "sleep_wake": sleep_wake, "weight_transfer": weight_transfer,
+           "tp_generate": tp_generate, "symm_allreduce": symm_allreduce, "fused_linear_ops": fused_linear_ops, "moe_fused": moe_fused}[sys.argv[1]]()
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps(res), flush=True)
     if torch.distributed.is_initialized():

@@ -137,3 +137,91 @@ def test_attn_decode_tc_large_score_spread_triggers_rescale():
     _native.check_status(torch.device(DEV))
     exp = _ref(q, kc, vc, meta, scale)
     assert (out.float().cpu() - exp).abs().max().item() < 3e-2
+
+
+def _lse_ref(q, kc, vc, meta, scale, lens):
+    """fp32 log-sum-exp of the scaled scores of every (query token, head) over the first ``lens[b]``
+    keys of its sequence, and the attention output over those keys."""
+    T, Hq, D = q.shape
+    Hkv = kc.shape[2]
+    G = Hq // Hkv
+    bs = kc.shape[1]
+    lse = torch.full((T, Hq), float("-inf"))
+    out = torch.zeros(T, Hq, D)
+    kcf, vcf, bt = kc.float().cpu(), vc.float().cpu(), meta.block_table.cpu()
+    for b in range(meta.num_reqs):
+        n = int(lens[b])
+        qs, qe = int(meta.query_start_loc_cpu[b]), int(meta.query_start_loc_cpu[b + 1])
+        if n == 0 or qe == qs:
+            continue
+        nb = (n + bs - 1) // bs
+        k = torch.cat([kcf[int(i)] for i in bt[b, :nb]])[:n].repeat_interleave(G, dim=1)
+        v = torch.cat([vcf[int(i)] for i in bt[b, :nb]])[:n].repeat_interleave(G, dim=1)
+        s = torch.einsum("qhd,khd->qhk", q[qs:qe].float().cpu(), k) * scale
+        lse[qs:qe] = torch.logsumexp(s, -1)
+        out[qs:qe] = torch.einsum("qhk,khd->qhd", s.softmax(-1), v)
+    return out, lse
+
+
+@pytest.mark.parametrize("ns", [1, 3])
+def test_attn_decode_tc_returns_log_sum_exp_and_takes_local_lengths(ns):
+    q, kc, vc, meta = make_paged_case([1, 1, 1, 1], [640, 5, 300, 1290], 16, 2, 128, 128, seed=21)
+    scale = 128 ** -0.5
+    # a context-parallel rank sees fewer keys than the sequence holds; one sequence has none here
+    local = np.array([333, 0, 128, 700], dtype=np.int32)
+    lens = torch.from_numpy(local).to(DEV)
+    out = torch.full_like(q, float("nan"))
+    lse = torch.full((q.shape[0], q.shape[1]), float("nan"), dtype=torch.float32, device=DEV)
+    ops.paged_attention_decode_tc(q, kc, vc, meta, scale, out, 0, ns, max_q_len=1, lse_out=lse, seq_lens=lens)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp_o, exp_l = _lse_ref(q, kc, vc, meta, scale, local)
+    assert torch.isinf(lse[1]).all() and (lse[1] < 0).all() and (out[1] == 0).all()
+    keep = [0, 2, 3]
+    assert (lse[keep].cpu() - exp_l[keep]).abs().max().item() < 2e-2
+    assert (out.float().cpu() - exp_o).abs().max().item() < 2e-2
+
+
+def test_partials_of_two_key_shards_merge_to_full_attention():
+    """Two 'ranks' hold the even / odd keys of every sequence densely under the same block table
+    (interleave 1): their decode results merged by log-sum-exp equal attention over all keys."""
+    q, kc, vc, meta = make_paged_case([1, 1, 1], [1023, 37, 300], 8, 1, 128, 128, seed=22)
+    scale = 128 ** -0.5
+    T, Hq, D = q.shape
+    bs = kc.shape[1]
+    full = meta.seq_lens_cpu
+    po = torch.empty(T, Hq, 2, D, dtype=torch.float32, device=DEV)
+    pl = torch.empty(T, Hq, 2, dtype=torch.float32, device=DEV)
+    bt = meta.block_table.cpu()
+    for r in range(2):
+        kr, vr = torch.zeros_like(kc), torch.zeros_like(vc)
+        local = np.zeros(len(full), dtype=np.int32)
+        for b, n in enumerate(full):
+            nb = (int(n) + bs - 1) // bs
+            ids = bt[b, :nb].long().to(DEV)
+            ks = kc[ids].reshape(-1, *kc.shape[2:])[:int(n)][r::2]
+            vs = vc[ids].reshape(-1, *vc.shape[2:])[:int(n)][r::2]
+            local[b] = ks.shape[0]
+            flat_k = kr[ids].reshape(-1, *kc.shape[2:])
+            flat_v = vr[ids].reshape(-1, *vc.shape[2:])
+            flat_k[:ks.shape[0]] = ks
+            flat_v[:vs.shape[0]] = vs
+            kr[ids] = flat_k.view(nb, bs, *kc.shape[2:])
+            vr[ids] = flat_v.view(nb, bs, *vc.shape[2:])
+        o = torch.empty_like(q)
+        l = torch.empty(T, Hq, dtype=torch.float32, device=DEV)
+        ops.paged_attention_decode_tc(q, kr, vr, meta, scale, o, 0, 1, max_q_len=1, lse_out=l,
+                                      seq_lens=torch.from_numpy(local).to(DEV))
+        po[:, :, r] = o.float()
+        pl[:, :, r] = l
+    merged_lse = torch.empty(T, Hq, dtype=torch.float32, device=DEV)
+    merged = ops.merge_attn_partials(po, pl, lse_out=merged_lse)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    exp = _ref(q, kc, vc, meta, scale)
+    assert (merged.float().cpu() - exp).abs().max().item() < 2e-2
+    _, exp_l = _lse_ref(q, kc, vc, meta, scale, full)
+    assert (merged_lse.cpu() - exp_l).abs().max().item() < 2e-2
+    # the PyTorch definition of the merge agrees with the kernel
+    host = ops.merge_attn_partials(po.cpu(), pl.cpu())
+    assert (host - merged.float().cpu()).abs().max().item() < 1e-2

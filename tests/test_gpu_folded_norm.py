@@ -9,24 +9,47 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def test_gemm_scales_rows_and_accumulates_sum_of_squares():
+def _stats(rows, feats, per_row):
+    """Row-statistics buffer holding ``per_row`` as two unequal partials."""
+    buf = ops.alloc_row_stats(rows, feats, DEV)
+    n = per_row.numel()
+    view = buf[:buf.stats_rows * buf.stats_parts].view(buf.stats_parts, buf.stats_rows)
+    view[0, :n] = per_row * 0.25
+    view[1, :n] = per_row * 0.75
+    view[2, :n] = 1e9                                   # beyond the part count: must not be read
+    buf[buf.stats_rows * buf.stats_parts:].view(torch.int32)[0] = 2
+    return buf
+
+
+def test_gemm_scales_rows_and_writes_sum_of_squares_partials():
     g = torch.Generator(device="cpu").manual_seed(0)
     M, K, N, H = 520, 512, 768, 512
     x = (torch.randn(M, K, generator=g) * 2.0).bfloat16().to(DEV)
     w = (torch.randn(N, K, generator=g) * 0.1).bfloat16().to(DEV)
     res = torch.randn(M, N, generator=g).bfloat16().to(DEV)
-    ss_in = (x.float() ** 2).sum(-1).contiguous()
-    ss_out = torch.full((M + 8,), 3.0, dtype=torch.float32, device=DEV)        # keeps what was there and adds
-    zero = torch.full((M + 8,), 7.0, dtype=torch.float32, device=DEV)
-    out = ops.linear_norm_folded(x, w, residual=res, ss_in=ss_in, norm_dim=H, eps=1e-6, ss_out=ss_out, zero=zero)
+    ss_rows = (x.float() ** 2).sum(-1).contiguous()
+    ss_in = _stats(M + 8, N, ss_rows)
+    ss_out = ops.alloc_row_stats(M + 8, N, DEV)
+    ss_out.fill_(5.0)                                     # stale values of an earlier step
+    out = ops.linear_norm_folded(x, w, residual=res, ss_in=ss_in, norm_dim=H, eps=1e-6, ss_out=ss_out)
     torch.cuda.synchronize()
     _native.check_status(torch.device(DEV))
-    rstd = torch.rsqrt(ss_in / H + 1e-6)
+    rstd = torch.rsqrt(ss_rows / H + 1e-6)
     want = (x.float() @ w.float().t()) * rstd[:, None] + res.float()
     assert float((out.float() - want).abs().max() / want.abs().max()) < 2e-2
-    want_ss = 3.0 + (out.float() ** 2).sum(-1)
-    assert float(((ss_out[:M] - want_ss) / want_ss).abs().max()) < 1e-3
-    assert float(ss_out[M:].min()) == 3.0 and float(zero[:M].abs().max()) == 0.0 and float(zero[M:].min()) == 7.0
+    R, P = ss_out.stats_rows, ss_out.stats_parts
+    parts = int(ss_out[R * P:].view(torch.int32)[0])
+    assert 1 <= parts <= P
+    got_ss = ss_out[:R * P].view(P, R)[:parts, :M].sum(0)
+    want_ss = (out.float() ** 2).sum(-1)
+    assert float(((got_ss - want_ss) / want_ss).abs().max()) < 1e-3
+    # bit-for-bit repeatable: the statistics are stores summed in a fixed order, not atomics
+    ss_again = ops.alloc_row_stats(M + 8, N, DEV)
+    out2 = ops.linear_norm_folded(x, w, residual=res, ss_in=ss_in, norm_dim=H, eps=1e-6, ss_out=ss_again)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    assert torch.equal(ss_again[:R * P].view(P, R)[:parts, :M], ss_out[:R * P].view(P, R)[:parts, :M])
+    ss_in = _stats(M + 8, N, ss_rows)
     # SwiGLU epilogue: both halves are scaled before the activation
     I = 256
     w2 = (torch.randn(2 * I, K, generator=g) * 0.1).bfloat16().to(DEV)
@@ -79,3 +102,8 @@ def test_engine_with_folded_norms_matches_the_unfolded_engine(monkeypatch):
         assert len(common) >= 3 and max(abs(la[t] - lb[t]) for t in common) < 0.1, (la, lb)
     same = sum(x == y for a, b in zip(got, want) for x, y in zip(a.outputs[0].token_ids, b.outputs[0].token_ids))
     assert same >= 0.8 * 18
+    # the folded engine repeats itself exactly
+    folded.reset_prefix_cache()             # same step shapes as the first pass
+    again = folded.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in again] == [o.outputs[0].token_ids for o in got]
+    assert [o.outputs[0].logprobs[0] for o in again] == [o.outputs[0].logprobs[0] for o in got]

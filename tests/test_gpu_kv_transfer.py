@@ -66,6 +66,15 @@ def test_copy_blocks():
     assert torch.equal(cache, want)
 
 
+@pytest.fixture(autouse=True)
+def _same_rounding_in_every_engine(monkeypatch):
+    """The tests below compare transferred KV bit for bit with what a monolithic engine computes.  That
+    needs every engine to round the same way at every step size, so the norm-in-GEMM fold (used from a
+    minimum row count on, and not by engines with layer-wise transfer) is off here; child processes
+    inherit the setting."""
+    monkeypatch.setenv("VLLM_B200_FOLD_NORM", "0")
+
+
 def _tokens_agree(got, want):
     assert sum(g[0] == x[0] for g, x in zip(got, want)) >= len(want) - 1, (got, want)
     assert all(len(g) == len(x) for g, x in zip(got, want))

@@ -26,6 +26,8 @@ def _run(n, what, env=None, timeout=600):
            os.path.join(ROOT, "tests", "multi_gpu_worker.py"), what]
     p = subprocess.run(cmd, capture_output=True, text=True, env=e, timeout=timeout)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    if what == "weight_transfer":          # one line per rank
+        return {l[:5]: json.loads(l[6:]) for l in p.stdout.splitlines() if l.startswith("PART")}
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
     return json.loads(line[len("RESULT "):])
 
@@ -88,6 +90,49 @@ def test_prefill_context_parallel_on_two_gpus():
     # the split changes which attention kernel instance sees which query rows, not the math:
     # first tokens agree, later near-ties of the random-weight model may flip
     assert sum(x[0] == y[0] for x, y in zip(a, b)) >= len(b) - 1, (a, b)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pipeline_parallel_on_two_gpus():
+    single = _run(1, "tp_generate", {"EAGER": "1"})
+    pp = _run(2, "pp_generate")
+    a, b = pp["tokens"], single["tokens"]
+    assert [len(x) for x in a] == [len(x) for x in b]
+    # the stages run the kernels of the single-GPU engine on the same rows: same tokens
+    assert sum(x == y for s, t in zip(a, b) for x, y in zip(s, t)) / sum(len(s) for s in a) > 0.9, (a, b)
+    _close_logprobs(single["first_logprobs"], pp["first_logprobs"])
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_sleep_and_wake_up_rebuild_nccl_communicators():
+    r = _run(2, "sleep_wake", {"VLLM_B200_TP_COMM": "nccl"})
+    assert r["before"] == r["after"]
+    assert r["freed_bytes"] > 0 and r["replays"] > 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_rl_weight_transfer_over_nccl_updates_a_live_engine():
+    r = _run(2, "weight_transfer")
+    t, w = r["PART0"], r["PART1"]
+    assert w["applied"] == w["params"] and t["buckets"] >= 1
+    assert w["before"] != t["trainer"]
+    assert w["after"] == t["trainer"]
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_gqa_decode_context_parallel_on_two_gpus():
+    """One KV head replicated over 2 TP ranks, its cache sharded along the sequence between them: decode
+    steps run the tcgen05 decode kernel on the local keys and merge by log-sum-exp."""
+    env = {"EAGER": "1", "MQA": "1", "VLLM_B200_TP_COMM": "nccl"}
+    single = _run(1, "tp_generate", env)
+    tp = _run(2, "tp_generate", env)
+    dcp = _run(2, "tp_generate", dict(env, DCP="2"))
+    a, b = dcp["tokens"], tp["tokens"]
+    assert [len(x) for x in a] == [len(x) for x in b]
+    same = sum(x == y for s, t in zip(a, b) for x, y in zip(s, t)) / sum(len(s) for s in a)
+    assert same > 0.8, (a, b)
+    _close_logprobs(single["first_logprobs"], dcp["first_logprobs"])
+    _close_logprobs(tp["first_logprobs"], dcp["first_logprobs"])
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")

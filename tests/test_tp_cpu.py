@@ -70,7 +70,7 @@ def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1, fg=None):
     return json.loads(line[7:])
 
 
-@pytest.mark.parametrize("preset", ["tiny-qwen", "tiny-moe", "tiny-deepseek"])
+@pytest.mark.parametrize("preset", ["tiny-qwen", "tiny-moe", "tiny-deepseek", "tiny-mqa"])
 def test_tp2_matches_tp1(preset):
     assert _run(preset, 2, 2) == _run(preset, 1, 1)
 
@@ -88,6 +88,26 @@ def test_pipeline_parallel_matches_single_rank(preset):
 def test_decode_context_parallel_matches_single_rank():
     # MLA latent cache sharded along the sequence over the 2 TP ranks
     assert _run("tiny-deepseek", 2, 2, dcp=2) == _run("tiny-deepseek", 1, 1)
+
+
+def test_gqa_decode_context_parallel_matches_single_rank():
+    # one KV head replicated over the 2 TP ranks; its cache sharded along the sequence between them
+    assert _run("tiny-mqa", 2, 2, dcp=2) == _run("tiny-mqa", 1, 1)
+
+
+def test_dcp_local_lengths_count_the_tokens_a_rank_stores():
+    from vllm_ascend_b200.attention.dcp import local_seq_lens, owner_and_offset
+    for bs, d, inter in ((16, 2, 1), (16, 2, 4), (8, 4, 2), (16, 4, 16)):
+        for sl in (0, 1, 5, 16, 31, 32, 33, 100, 257):
+            pos = np.arange(sl)
+            owner, local = owner_and_offset(pos % (bs * d), bs, d, inter)
+            for r in range(d):
+                n = int(local_seq_lens(np.array([sl]), bs, d, r, inter)[0])
+                assert n == int((owner == r).sum()), (bs, d, inter, sl, r)
+                # the rank's tokens fill its blocks densely: local index == running count
+                mine = np.nonzero(owner == r)[0]
+                idx = (mine // (bs * d)) * bs + local[mine]
+                assert (idx == np.arange(n)).all()
 
 
 @pytest.mark.parametrize("preset,world,tp", [("tiny-qwen", 2, 1), ("tiny-moe", 2, 1), ("tiny-qwen", 4, 2)])

@@ -23,7 +23,7 @@ P, I, L, F, U = c_void_p, c_int, c_long, c_float, c_uint
 _SIGNATURES = {
     "b200_gemm_bf16": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, P],
     "b200_gemm_bf16_2cta": [P, P, P, P, P, I, I, I, I, I, I, I, P, P],
-    "b200_gemm_bf16_2cta_norm": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, ctypes.c_float, P, P, P, P],
+    "b200_gemm_bf16_2cta_norm": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, ctypes.c_float, P, L, I, P, P],
     "b200_gemm_swiglu_bf16": [P, P, P, I, I, I, I, I, I, P, P],
     "b200_grouped_gemm_bf16": [P, P, P, P, I, L, I, I, I, I, I, I, P, P],
     "b200_rms_norm": [P, P, P, P, L, I, F, I, L, L, P],
@@ -43,6 +43,8 @@ _SIGNATURES = {
     "b200_attn_fwd_tc": [P, L, L, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P, L, P,
                          F, U, U, I, P, P],
     "b200_attn_decode_tc": [P, L, L, P, P, L, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, P, P],
+    "b200_attn_decode_tc_lse": [P, L, L, P, P, L, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, P, P, P],
+    "b200_merge_attn_partials": [P, P, L, I, I, I, P, L, P, P],
     "b200_argmax": [P, I, L, I, I, P, P],
     "b200_cast_bf16_f32": [P, L, P, L, I, I, P],
     "b200_apply_penalties": [P, L, I, I, P, I, P, I, P, P, P, P],

@@ -91,3 +91,87 @@ def mla_attention_dcp(q_lat: torch.Tensor, q_pe: torch.Tensor, lat_cache: torch.
     recv = group.all_to_all_single(packed.view(d * T, H, dc + 1))                      # [d(src) * T, H, dc+1]
     recv = recv.view(d, T, H, dc + 1)
     return merge_partials(recv[..., :dc], recv[..., dc]).to(q_lat.dtype)
+
+
+def local_seq_lens(seq_lens: np.ndarray, block_size: int, dcp: int, rank: int, interleave: int) -> np.ndarray:
+    """Number of tokens of each sequence that ``rank`` stores.  A rank's tokens of one sequence
+    fill its blocks densely and in global order, so the local cache of a sequence is an ordinary
+    paged sequence of this length under the same block table."""
+    sl = np.asarray(seq_lens, dtype=np.int64)
+    vb = block_size * dcp
+    rem = sl % vb
+    cyc = interleave * dcp
+    cnt = (rem // cyc) * interleave + np.clip(rem % cyc - rank * interleave, 0, interleave)
+    return ((sl // vb) * block_size + cnt).astype(np.int32)
+
+
+def _gqa_local_partials(q_all: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta, scale: float,
+                        d: int, rank: int, interleave: int):
+    """PyTorch definition of one rank's partial attention: (out fp32 [T, HH, D] normalised over the local
+    keys, lse fp32 [T, HH]).  Serves prefill / mixed steps and the host tests."""
+    T, HH, D = q_all.shape
+    bs, Hkv = k_cache.shape[1], k_cache.shape[2]
+    G = HH // Hkv
+    out = torch.zeros(T, HH, D, dtype=torch.float32, device=q_all.device)
+    lse = torch.full((T, HH), float("-inf"), dtype=torch.float32, device=q_all.device)
+    k_flat = k_cache.reshape(-1, Hkv, D)
+    v_flat = v_cache.reshape(-1, Hkv, D)
+    qsl, sls = meta.query_start_loc_cpu, meta.seq_lens_cpu
+    for b in range(meta.num_reqs):
+        qs, qe = int(qsl[b]), int(qsl[b + 1])
+        ql, sl = qe - qs, int(sls[b])
+        if ql <= 0:
+            continue
+        slots, gpos = local_tokens(sl, meta.block_table[b], bs, d, rank, interleave)
+        if len(slots) == 0:
+            continue
+        st = torch.from_numpy(slots).to(q_all.device)
+        k = k_flat[st].float().repeat_interleave(G, dim=1)          # [n, HH, D]
+        v = v_flat[st].float().repeat_interleave(G, dim=1)
+        s = torch.einsum("qhd,khd->qhk", q_all[qs:qe].float(), k) * scale
+        qpos = (sl - ql) + torch.arange(ql, device=q_all.device)
+        vis = torch.from_numpy(gpos).to(q_all.device)[None, :] <= qpos[:, None]
+        s = s.masked_fill(~vis[:, None, :], float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l.clamp(min=-1e30).unsqueeze(-1))
+        p = torch.where(torch.isfinite(s), p, torch.zeros_like(p))
+        out[qs:qe] = torch.einsum("qhk,khd->qhd", p, v)
+        lse[qs:qe] = l
+    return out, lse
+
+
+def gqa_attention_dcp(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta, scale: float,
+                      group, interleave: int) -> torch.Tensor:
+    """Grouped-query attention with the KV cache sharded along the sequence over ``group`` (ranks that
+    hold the same KV heads).  q [T, H, D] holds this rank's query heads; returns [T, H, D].
+
+    Every rank gathers the group's query heads, attends over the keys it stores and keeps the
+    log-sum-exp; an all-to-all returns each head's partial results to the rank that owns the head,
+    which merges them (vllm_ascend/attention/context_parallel/attention_cp.py:173-393).  Decode steps
+    run the tcgen05 flash-decode kernel on the local cache (the rank's tokens of a sequence form an
+    ordinary paged sequence of ``local_seq_lens`` keys, all of them visible to the new token) and the
+    merge kernel; steps with longer queries take the PyTorch definition."""
+    from .. import ops
+    d, rank = group.world_size, group.rank_in_group
+    T, H, D = q.shape
+    q_all = group.all_gather(q.contiguous(), dim=1)                  # [T, d*H, D]
+    HH = q_all.shape[1]
+    Hkv = k_cache.shape[2]
+    G = HH // Hkv
+    local_sl = getattr(meta, "dcp_seq_lens", None)
+    kernel_ok = (q.is_cuda and q.dtype == torch.bfloat16 and D == 128 and v_cache.shape[-1] == D
+                 and meta.max_query_len == 1 and G <= 16 and 16 % G == 0 and local_sl is not None)
+    if kernel_ok:
+        out = torch.empty((T, HH, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((T, HH), dtype=torch.float32, device=q.device)
+        ops.paged_attention_decode_tc(q_all, k_cache, v_cache, meta, scale, out, 0, num_splits=1, max_q_len=1,
+                                      lse_out=lse, seq_lens=local_sl)
+        out = out.float()
+    else:
+        out, lse = _gqa_local_partials(q_all, k_cache, v_cache, meta, scale, d, rank, interleave)
+    # head block j of every rank's partials goes to rank j
+    packed = torch.cat([out, lse.unsqueeze(-1)], dim=-1).view(T, d, H, D + 1).permute(1, 0, 2, 3).contiguous()
+    recv = group.all_to_all_single(packed.view(d * T, H, D + 1)).view(d, T, H, D + 1)
+    po = recv[..., :D].permute(1, 2, 0, 3).contiguous()              # [T, H, d, D]
+    pl = recv[..., D].permute(1, 2, 0).contiguous()                  # [T, H, d]
+    return ops.merge_attn_partials(po, pl, out_dtype=q.dtype).to(q.dtype)

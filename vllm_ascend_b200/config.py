@@ -323,6 +323,10 @@ PRESETS: dict[str, Any] = {
         name="tiny-llama", architecture="LlamaForCausalLM", vocab_size=512, hidden_size=128,
         intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
         num_key_value_heads=2, head_dim=32, rope_theta=1e4, dtype="float32"),
+    "tiny-mqa": lambda: _preset(          # one KV head: replicated over TP ranks (decode context parallelism)
+        name="tiny-mqa", architecture="Qwen3ForCausalLM", vocab_size=512, hidden_size=128,
+        intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=1, head_dim=32, rope_theta=1e6, qk_norm=True, dtype="float32"),
     "tiny-moe": lambda: _preset(
         name="tiny-moe", architecture="Qwen3MoeForCausalLM", vocab_size=512, hidden_size=128,
         intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,

@@ -4,8 +4,10 @@
 
 namespace b200 {
 
+// lse_out (optional, [T, Hq]): log-sum-exp of the merged result
 int launch_merge_splits(const float* partial_o, const float* partial_lse, long T, int Hq,
-                        int num_splits, int D, void* out, long out_stride, cudaStream_t stream);
+                        int num_splits, int D, void* out, long out_stride, cudaStream_t stream,
+                        float* lse_out = nullptr);
 
 int launch_paged_decode(const void* q, long q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int max_blocks, const int* seq_lens, int B,

@@ -149,12 +149,19 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
 // out[t, hq, :] = sum_s softmax_s(lse)[s] * partial_o[t, hq, s, :]
 __global__ void merge_splits_kernel(const float* __restrict__ partial_o,
                                     const float* __restrict__ partial_lse, int num_splits, int D,
-                                    int Hq, __nv_bfloat16* __restrict__ out, long out_stride) {
+                                    int Hq, __nv_bfloat16* __restrict__ out, long out_stride,
+                                    float* __restrict__ lse_out) {
   const long t = blockIdx.x;
   const int hq = blockIdx.y;
   const long base = (t * Hq + hq) * num_splits;
   float M = -INFINITY;
   for (int s = 0; s < num_splits; s++) M = fmaxf(M, partial_lse[base + s]);
+  if (lse_out && threadIdx.x == 0) {
+    float L = 0.f;
+    if (M != -INFINITY)
+      for (int s = 0; s < num_splits; s++) L += __expf(partial_lse[base + s] - M);
+    lse_out[t * Hq + hq] = L > 0.f ? M + logf(L) : -INFINITY;
+  }
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f, L = 0.f;
     if (M != -INFINITY) {
@@ -169,11 +176,12 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o,
 }
 
 int launch_merge_splits(const float* partial_o, const float* partial_lse, long T, int Hq,
-                        int num_splits, int D, void* out, long out_stride, cudaStream_t stream) {
+                        int num_splits, int D, void* out, long out_stride, cudaStream_t stream,
+                        float* lse_out) {
   if (T <= 0) return 0;
   dim3 grid((unsigned)T, (unsigned)Hq);
   merge_splits_kernel<<<grid, D >= 128 ? 128 : 64, 0, stream>>>(
-      partial_o, partial_lse, num_splits, D, Hq, (__nv_bfloat16*)out, out_stride);
+      partial_o, partial_lse, num_splits, D, Hq, (__nv_bfloat16*)out, out_stride, lse_out);
   return B200_CHECK_LAUNCH();
 }
 
@@ -240,4 +248,16 @@ B200_API int b200_paged_decode(const void* q, long q_stride, const void* k_cache
                                    max_blocks, (const int*)seq_lens, B, Hq, Hkv, D, block_size,
                                    scale, window, num_splits, out, out_stride, po, pl,
                                    num_blocks_total, status, stream);
+}
+
+// Merge attention results computed over disjoint key sets (KV splits of one call, or the ranks of
+// a context-parallel group): partial_o fp32 [T, Hq, S, D] (each normalised by its own denominator),
+// partial_lse fp32 [T, Hq, S] -> out bf16 [T, Hq, D] (row stride out_stride elements), optional
+// merged lse_out [T, Hq].
+B200_API int b200_merge_attn_partials(const void* partial_o, const void* partial_lse, long T, int Hq,
+                                      int S, int D, void* out, long out_stride, void* lse_out,
+                                      cudaStream_t stream) {
+  if (S < 1 || D < 1 || Hq < 1) return 9114;
+  return b200::launch_merge_splits((const float*)partial_o, (const float*)partial_lse, T, Hq, S, D,
+                                   out, out_stride, stream, (float*)lse_out);
 }

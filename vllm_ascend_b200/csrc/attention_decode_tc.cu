@@ -43,6 +43,7 @@ struct DecParams {
   long out_stride;
   float* partial_o;
   float* partial_lse;
+  float* lse_out;            // optional [T, Hq] natural-log sum-exp of the scaled scores (-inf: no key)
   long num_blocks_total;
   int num_seqs, num_items;   // items = Hkv x sequences x splits
   int tail_loads;            // 1: the last tile of a sequence is loaded in 32-key pieces (pages >= 128 keys)
@@ -445,6 +446,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
             p.partial_lse[pidx] = -INFINITY;
             for (int d = 0; d < D; d++) p.partial_o[pidx * D + d] = 0.f;
           }
+        } else if (p.num_splits == 1 && p.lse_out && w.q_len > 0) {
+          // a caller that merges partial results of several ranks needs a defined (zero-weight)
+          // result for a sequence none of whose keys live here
+          for (int c = 0; c < nv; c++) {
+            const long tok = w.q_start + c / G;
+            const int hq = w.h * G + c % G;
+            if (tid == 0) p.lse_out[tok * p.Hq + hq] = -INFINITY;
+            if (tid < D) p.out[tok * p.out_stride + (long)hq * D + tid] = __float2bfloat16(0.f);
+          }
         }
         continue;
       }
@@ -577,6 +587,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const float val = __uint_as_float(o[c]) * inv;
             if (p.num_splits == 1) {
               p.out[tok * p.out_stride + (long)hq * D + tid] = __float2bfloat16(val);
+              if (tid == 0 && p.lse_out)
+                p.lse_out[tok * p.Hq + hq] =
+                    (l > 0.f) ? (m[c] * sl2 * 0.6931471805599453f + logf(l)) : -INFINITY;
             } else {
               const long pidx = (tok * p.Hq + hq) * p.num_splits + w.split;
               p.partial_o[pidx * D + tid] = val;
@@ -640,14 +653,16 @@ static DecTmapCache g_dec_tmaps;
 // Decode / short-query attention: every sequence has q_len <= 16 / (Hq/Hkv) query
 // tokens (query_start_loc gives their positions in q).  Arguments as b200_attn_fwd_tc;
 // scratch needs b200_attn_scratch_bytes(T, Hq, D, num_splits) bytes when num_splits > 1.
-B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const void* k_cache,
-                                 const void* v_cache, long num_blocks, int block_size,
-                                 const void* query_start_loc, const void* seq_lens,
-                                 const void* block_table, int max_blocks, int num_seqs, int Hq,
-                                 int Hkv, int D, float scale, int window, int num_splits,
-                                 int max_q_len, void* out, long out_stride, void* scratch,
-                                 int kv_layout,
-                                 int* status, void* timeline, cudaStream_t stream) {
+// lse_out (optional, fp32 [T, Hq]): log-sum-exp of every (token, head) over the keys this call saw,
+// for callers that merge the results of several calls (context-parallel ranks).
+B200_API int b200_attn_decode_tc_lse(const void* q, long q_stride, long T, const void* k_cache,
+                                     const void* v_cache, long num_blocks, int block_size,
+                                     const void* query_start_loc, const void* seq_lens,
+                                     const void* block_table, int max_blocks, int num_seqs, int Hq,
+                                     int Hkv, int D, float scale, int window, int num_splits,
+                                     int max_q_len, void* out, long out_stride, void* scratch,
+                                     int kv_layout, void* lse_out,
+                                     int* status, void* timeline, cudaStream_t stream) {
   using namespace b200;
   if (num_seqs <= 0 || T <= 0) return 0;
   const int G = Hq / Hkv;
@@ -707,6 +722,7 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
   p.out_stride = out_stride;
   p.partial_o = (float*)scratch;
   p.partial_lse = scratch ? (float*)scratch + T * Hq * (long)num_splits * D : nullptr;
+  p.lse_out = (float*)lse_out;
   p.num_blocks_total = num_blocks;
   p.status = status;
   p.timeline = (long long*)timeline;
@@ -753,6 +769,20 @@ B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const voi
   if (rc) return rc;
   if (num_splits > 1)
     return launch_merge_splits(p.partial_o, p.partial_lse, T, Hq, num_splits, D, out,
-                               out_stride, stream);
+                               out_stride, stream, (float*)lse_out);
   return 0;
+}
+
+B200_API int b200_attn_decode_tc(const void* q, long q_stride, long T, const void* k_cache,
+                                 const void* v_cache, long num_blocks, int block_size,
+                                 const void* query_start_loc, const void* seq_lens,
+                                 const void* block_table, int max_blocks, int num_seqs, int Hq,
+                                 int Hkv, int D, float scale, int window, int num_splits,
+                                 int max_q_len, void* out, long out_stride, void* scratch,
+                                 int kv_layout,
+                                 int* status, void* timeline, cudaStream_t stream) {
+  return b200_attn_decode_tc_lse(q, q_stride, T, k_cache, v_cache, num_blocks, block_size,
+                                 query_start_loc, seq_lens, block_table, max_blocks, num_seqs, Hq,
+                                 Hkv, D, scale, window, num_splits, max_q_len, out, out_stride,
+                                 scratch, kv_layout, nullptr, status, timeline, stream);
 }

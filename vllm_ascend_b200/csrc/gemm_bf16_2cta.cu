@@ -59,10 +59,14 @@ struct Gemm2Params {
   int raster;                         // M-tiles per raster group (0/1: column-major order)
   int bn;                             // tile width: 128..256 in steps of 32 (SwiGLU tiles: 256)
   // ---- RMSNorm folded into the GEMMs around it (the norm weight lives in W of the consumer)
-  const float* row_ss_in;             // [M] sum of squares of the rows of A: accumulators are scaled by
-  float inv_dim, eps;                 //     rsqrt(row_ss_in[row] * inv_dim + eps) before bias / SwiGLU
-  float* row_ss_out;                  // [M] += sum of squares of the bf16 output row (producer side)
-  float* row_zero;                    // [M] cleared by the tiles of column block 0 (the buffer a later GEMM accumulates)
+  // Row statistics travel as per-column-tile partial sums so that their total does not depend on
+  // the order in which tiles finish: buffer [ss_parts_max][ss_stride] fp32 followed by one int32
+  // (the number of partials the producer wrote).
+  const float* row_ss_in;             // sum of squares of the rows of A: accumulators are scaled by
+  float inv_dim, eps;                 //     rsqrt(sum_i row_ss_in[i][row] * inv_dim + eps) before bias / SwiGLU
+  float* row_ss_out;                  // [tile_n][row] = sum of squares of the bf16 output row within that column tile
+  long ss_stride;
+  int ss_parts_max;
 };
 // G2_PUB: the last CTA publishes this rank's reduce-scatter epoch to every peer (set with G2_RS;
 // alone it is the NVLS form: rows stay in the local multicast-bound buffer C)
@@ -295,8 +299,15 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       const __nv_bfloat16* rrow = p.residual ? p.residual + (size_t)row * p.ldc : nullptr;
       float rstd = 1.f, ss_acc = 0.f;
-      if (p.row_ss_in && row_ok) rstd = rsqrtf(p.row_ss_in[row] * p.inv_dim + p.eps);
-      if (p.row_zero && tn == 0 && row_ok) p.row_zero[row] = 0.f;
+      if (p.row_ss_in && row_ok) {
+        int parts = *reinterpret_cast<const int*>(p.row_ss_in + (long)p.ss_parts_max * p.ss_stride);
+        parts = parts < 0 ? 0 : (parts > p.ss_parts_max ? p.ss_parts_max : parts);
+        float ss = 0.f;
+        for (int i = 0; i < parts; i++) ss += p.row_ss_in[(long)i * p.ss_stride + row];   // fixed order
+        rstd = rsqrtf(ss * p.inv_dim + p.eps);
+      }
+      if (p.row_ss_out && t == 0 && rank == 0 && q == 0 && lane == 0)
+        *reinterpret_cast<int*>(p.row_ss_out + (long)p.ss_parts_max * p.ss_stride) = p.tiles_n;
 #pragma unroll 1
       for (int c0 = 0; c0 < out_per_tile; c0 += 32) {
         const int col0 = tn * out_per_tile + c0;
@@ -391,7 +402,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
-      if (p.row_ss_out && row_ok) atomicAdd(p.row_ss_out + row, ss_acc);
+      if (p.row_ss_out && row_ok) p.row_ss_out[(long)tn * p.ss_stride + row] = ss_acc;
       tc_fence_before();
       __syncwarp();
       // accumulator buffer drained: tell the leader's MMA warp (local or remote arrive)
@@ -628,19 +639,25 @@ B200_API int b200_gemm_2cta_set_bn(int bn) {
 }
 
 // b200_gemm_bf16_2cta with the RMSNorm around it folded in (either side optional):
-//   row_ss_in  [M] fp32: accumulators are scaled by rsqrt(row_ss_in[row] / norm_dim + eps) (the
-//              normalisation of A's rows; the norm weight is expected inside W),
-//   row_ss_out [M] fp32: += sum of squares of every stored output row (+bias +residual, bf16),
-//   row_zero   [M] fp32: set to 0 (the accumulator a later GEMM of the chain adds into).
+// Statistics buffers: fp32 [ss_parts_max][ss_stride] (ss_stride >= M) followed by one int32.
+//   row_ss_in : accumulators are scaled by rsqrt(sum of the row's partials / norm_dim + eps) (the
+//               normalisation of A's rows; the norm weight is expected inside W); the trailing int
+//               says how many partials the producer wrote,
+//   row_ss_out: partial [column tile][row] = sum of squares of the stored output row (+bias
+//               +residual, bf16) inside that column tile, and the tile count in the trailing int.
+// Partials instead of atomic adds: the total is summed in a fixed order, so a step repeats bit for
+// bit.  The output must have at most ss_parts_max column tiles of the narrowest tile width (128).
 B200_API int b200_gemm_bf16_2cta_norm(const void* A, const void* W, void* C, const void* bias,
                                       const void* residual, int M, int N, int K, int lda, int ldw,
                                       int ldc, int swiglu, const void* row_ss_in, int norm_dim,
-                                      float eps, void* row_ss_out, void* row_zero, int* status,
-                                      cudaStream_t stream) {
+                                      float eps, void* row_ss_out, long ss_stride, int ss_parts_max,
+                                      int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7)) return 9100;
   if (swiglu && (N % 128)) return 9132;
   if (row_ss_in && norm_dim <= 0) return 9133;
+  if ((row_ss_in || row_ss_out) && (ss_stride < M || ss_parts_max < 1)) return 9134;
+  if (row_ss_out && (long)ss_parts_max * 128 < N) return 9135;
   Gemm2Params p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K; p.ldc = ldc;
@@ -653,7 +670,8 @@ B200_API int b200_gemm_bf16_2cta_norm(const void* A, const void* W, void* C, con
   p.inv_dim = norm_dim > 0 ? 1.f / (float)norm_dim : 0.f;
   p.eps = eps;
   p.row_ss_out = (float*)row_ss_out;
-  p.row_zero = (float*)row_zero;
+  p.ss_stride = ss_stride;
+  p.ss_parts_max = ss_parts_max;
   return launch_2cta(A, W, p, lda, ldw, M, stream);
 }
 

@@ -135,7 +135,14 @@ class ModelRunner:
         self.dcp_size, self.dcp_rank = dcp.world_size, dcp.rank_in_group
         self.dcp_interleave = int((cfg.additional_config or {}).get("cp_kv_cache_interleave_size", 1))
         if self.dcp_size > 1 and not cfg.model.use_mla:
-            raise NotImplementedError("decode context parallelism is implemented for MLA models")
+            # the ranks of a DCP group shard one sequence of keys: they must hold the same KV heads
+            tp_ = _ps.get_tp_group().world_size
+            rep = max(1, tp_ // max(1, cfg.model.num_key_value_heads))
+            if cfg.model.is_hybrid or cfg.model.sliding_window or rep % self.dcp_size:
+                raise NotImplementedError(
+                    "decode context parallelism for grouped-query attention needs KV heads replicated over the "
+                    f"DCP ranks (tensor_parallel_size / num_key_value_heads = {rep} must be a multiple of "
+                    f"{self.dcp_size}), no sliding window and no recurrent layers")
         self.pcp = _ps.get_pcp_group()
         if self.pcp.world_size > 1 and (cfg.model.use_mla or cfg.model.is_hybrid or cfg.model.is_multimodal):
             raise NotImplementedError("prefill context parallelism is implemented for GQA decoder models")
@@ -473,6 +480,14 @@ class ModelRunner:
             attn_state=state, num_decodes=nd, num_decode_tokens=ndt, num_prefills=npf,
             num_input_tokens=Tp)
         meta.dcp_interleave = self.dcp_interleave
+        if self.dcp_size > 1:
+            from ..attention.dcp import local_seq_lens
+            lsl = np.ones(Bp, dtype=np.int32)
+            lsl[:B] = local_seq_lens(seq_lens, self.block_size, self.dcp_size, self.dcp_rank, self.dcp_interleave)
+            if not hasattr(self, "_dcp_sl"):
+                self._dcp_sl = torch.zeros(self.max_seqs + 8, dtype=torch.int32, device=self.device)
+            self._dcp_sl[:Bp].copy_(torch.from_numpy(lsl), non_blocking=False)
+            meta.dcp_seq_lens = self._dcp_sl[:Bp]
         meta.pcp = pcp_meta
         if self.sparse_offload is not None:
             tr = np.full(Tp, -1, dtype=np.int64)
@@ -1076,6 +1091,8 @@ class ModelRunner:
         cc = self.cfg.compilation
         if not self.is_cuda or cc.cudagraph_mode == "NONE" or not envs.VLLM_B200_CUDA_GRAPH:
             return
+        if self.dcp_size > 1:
+            return          # context-parallel steps read per-step host metadata: not captured
         max_size = cc.max_cudagraph_capture_size or min(self.max_seqs, 1024)
         sizes = cc.cudagraph_capture_sizes or default_capture_sizes(max_size)
         self.capture_sizes = sorted(set(int(s) for s in sizes if s <= self.max_seqs))

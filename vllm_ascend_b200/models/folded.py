@@ -11,9 +11,11 @@ two full passes over the residual stream in HBM per norm.  Here it disappears fr
 * the consumer GEMM reads the un-normalised residual rows and scales its accumulators by
   ``rsqrt(ss / H + eps)`` in the epilogue (before the bias / SiLU-mul).
 
-Two fp32 row-statistics buffers rotate: each GEMM that consumes one clears the other (its tiles of
-column block 0 do), so no memset kernel is needed either.  Steps with fewer rows than the
-paired-CTA kernel takes run the ordinary layer code (which sees norm weights of 1).
+Two fp32 row-statistics buffers alternate.  A producer writes one partial sum per column tile and
+row (plain stores, no atomics) and the consumer adds a row's partials in tile order, so the
+statistics, and with them the whole step, repeat bit for bit; nothing has to be cleared between
+GEMMs.  Steps with fewer rows than the paired-CTA kernel takes run the ordinary layer code (which
+sees norm weights of 1).
 
 The reference fuses add + RMSNorm (+ quant) as one kernel behind its compiler passes
 (vllm_ascend/compilation/passes/norm_quant_fusion_pass.py:29-403); it has no GEMM-epilogue form.
@@ -32,6 +34,9 @@ def supports(model, engine_cfg) -> bool:
         return False
     if model.comm.size != 1 or engine_cfg.enable_lora or engine_cfg.enable_sleep_mode:
         return False
+    from ..batch_invariant import is_batch_invariant
+    if is_batch_invariant():
+        return False          # the folded and the ordinary path round differently; which one runs depends on the step size
     from ..platform_config import get_b200_config
     if get_b200_config().weight_offload_config.enabled:
         return False          # offloaded layers hold their weights on the host between their turns
@@ -67,7 +72,7 @@ def attach(model, engine_cfg) -> bool:
         return False
     fold_norms(model)
     n = max(engine_cfg.scheduler.max_num_batched_tokens, engine_cfg.scheduler.max_num_seqs) + 8
-    model.fold_ss = torch.zeros((2, n), dtype=torch.float32, device=model.device)
+    model.fold_ss = [ops.alloc_row_stats(n, model.cfg.hidden_size, model.device) for _ in range(2)]
     model.fold_ones = torch.ones(model.cfg.hidden_size, dtype=model.dtype, device=model.device)
     return True
 
@@ -88,14 +93,12 @@ def forward_folded(model, input_ids: torch.Tensor, meta, kv_caches: list) -> tor
     for i, (layer, cache) in enumerate(zip(model.layers, kv_caches)):
         a, m = layer.self_attn, layer.mlp
         if i == 0:
-            qkv = ops.linear_norm_folded(x0, a.qkv_proj.weight, a.qkv_proj.bias, zero=ss_b)
+            qkv = ops.linear_norm_folded(x0, a.qkv_proj.weight, a.qkv_proj.bias)
         else:
-            qkv = ops.linear_norm_folded(r, a.qkv_proj.weight, a.qkv_proj.bias, ss_in=ss_a, norm_dim=H, eps=eps,
-                                         zero=ss_b)
+            qkv = ops.linear_norm_folded(r, a.qkv_proj.weight, a.qkv_proj.bias, ss_in=ss_a, norm_dim=H, eps=eps)
         o = a.attend(qkv, meta, cache)
         ops.linear_norm_folded(o, a.o_proj.weight, a.o_proj.bias, residual=r, out=r, ss_out=ss_b)
-        act = ops.linear_norm_folded(r, m.gate_up_proj.weight, swiglu=True, ss_in=ss_b, norm_dim=H, eps=eps,
-                                     zero=ss_a)
+        act = ops.linear_norm_folded(r, m.gate_up_proj.weight, swiglu=True, ss_in=ss_b, norm_dim=H, eps=eps)
         ops.linear_norm_folded(act, m.down_proj.weight, m.down_proj.bias, residual=r, out=r, ss_out=ss_a)
         if model.layer_hook is not None:
             model.layer_hook(layer.idx)

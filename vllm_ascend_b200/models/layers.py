@@ -297,6 +297,16 @@ class GQAAttention:
             sizes.append(cfg.num_attention_heads * self.D)
         self.qkv_proj = ColumnParallelLinear(pf, f"{prefix}.qkv_proj", cfg.hidden_size, sizes, comm,
                                              bias=cfg.attention_bias)
+        if self.kv_replicas > 1 and self.qkv_proj.weight.device.type != "meta":
+            # random init: ranks that replicate a KV head must hold the same rows (those of the
+            # unsharded model), as they do after loading a checkpoint
+            kv_rank = comm.rank // self.kv_replicas
+            with torch.no_grad():
+                for i in (1, 2):
+                    rows = pf.normal(f"{prefix}.qkv_proj.{i}", (self.total_kv * self.D, cfg.hidden_size), 0, kv_rank,
+                                     self.total_kv)
+                    at = self.Hq * self.D + (i - 1) * self.D
+                    self.qkv_proj.weight[at:at + self.D].copy_(rows)
         self.o_proj = RowParallelLinear(pf, f"{prefix}.o_proj", cfg.num_attention_heads * self.D,
                                         cfg.hidden_size, comm)
         self.q_norm = pf.ones((self.D,)) if cfg.qk_norm else None
@@ -344,7 +354,14 @@ class GQAAttention:
         qkv = qkv_in
         T = qkv.shape[0]
         q = qkv[:, :self.Hq * self.D].view(T, self.Hq, self.D)
-        o = self.impl.forward(q, k_cache, v_cache, meta)
+        from ..parallel import state as pstate
+        dcp = pstate.get_dcp_group()
+        if dcp.world_size > 1:
+            # the KV cache holds this rank's share of every sequence
+            from ..attention.dcp import gqa_attention_dcp
+            o = gqa_attention_dcp(q, k_cache, v_cache, meta, self.scale, dcp, getattr(meta, "dcp_interleave", 1))
+        else:
+            o = self.impl.forward(q, k_cache, v_cache, meta)
         o = o.view(T, self.Hq * self.D)
         if self.out_gate:
             o = o * torch.sigmoid(qkv[:, (self.Hq + 2 * self.Hkv) * self.D:].float()).to(o.dtype)

@@ -208,32 +208,48 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return out.view(*x.shape[:-1], N)
 
 
+def alloc_row_stats(rows: int, max_out_features: int, device) -> torch.Tensor:
+    """Row-statistics buffer of the folded-norm GEMMs: fp32 [parts][rows] partial sums of squares
+    (one part per 128 output columns at most) followed by the int32 part count."""
+    parts = (max_out_features + 127) // 128
+    buf = torch.zeros(parts * rows + 4, dtype=torch.float32, device=device)
+    buf.stats_rows, buf.stats_parts = rows, parts          # geometry travels with the tensor
+    return buf
+
+
 def linear_norm_folded(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                        residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                        swiglu: bool = False, ss_in: Optional[torch.Tensor] = None, norm_dim: int = 0,
-                       eps: float = 1e-6, ss_out: Optional[torch.Tensor] = None,
-                       zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       eps: float = 1e-6, ss_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paired-CTA GEMM with the RMSNorm around it folded in (CUDA, bf16, x [M, K] with M >= 1).
 
-    ``ss_in`` (fp32 [>= M], sum of squares of x's rows): the result rows are scaled by
-    rsqrt(ss_in / norm_dim + eps), i.e. the GEMM runs on the un-normalised rows and ``weight``
-    already carries the norm weight.  ``ss_out``: the sum of squares of every stored output row is
-    added to it (the statistics of the NEXT norm).  ``zero``: cleared (the buffer a later GEMM of the
-    chain accumulates into).  ``residual`` may alias ``out``."""
+    ``ss_in`` / ``ss_out`` are buffers of ``alloc_row_stats`` (same geometry).  ``ss_in`` holds the
+    partial sums of squares of x's rows: the result rows are scaled by rsqrt(sum / norm_dim + eps),
+    i.e. the GEMM runs on the un-normalised rows and ``weight`` already carries the norm weight.
+    ``ss_out`` receives, per column tile, the sum of squares of every stored output row (the
+    statistics of the NEXT norm).  Partials are summed in a fixed order: a step repeats bit for bit.
+    ``residual`` may alias ``out``."""
     M, K = x.shape
     N = weight.shape[0] // 2 if swiglu else weight.shape[0]
     if weight.dim() != 2 or weight.shape[1] != K or N == 0 or not weight.is_cuda:
         raise ValueError(f"weight {tuple(weight.shape)} on {weight.device} does not fit rows of {K} columns "
                          "(offloaded or unloaded layer?)")
-    for name, t in (("ss_in", ss_in), ("ss_out", ss_out), ("zero", zero)):
-        if t is not None and (t.dtype != torch.float32 or t.numel() < M):
-            raise ValueError(f"{name} must hold at least {M} fp32 values")
+    rows = parts = 0
+    for name, t in (("ss_in", ss_in), ("ss_out", ss_out)):
+        if t is None:
+            continue
+        r_, p_ = getattr(t, "stats_rows", 0), getattr(t, "stats_parts", 0)
+        if t.dtype != torch.float32 or r_ < M or p_ < 1 or t.numel() < r_ * p_ + 1 or (rows and (r_, p_) != (rows, parts)):
+            raise ValueError(f"{name} must be a row-statistics buffer (alloc_row_stats) of at least {M} rows")
+        rows, parts = r_, p_
+    if ss_out is not None and parts * 128 < N:
+        raise ValueError(f"row-statistics buffer has {parts} parts; {N} output columns need {(N + 127) // 128}")
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     rc = _native.lib().b200_gemm_bf16_2cta_norm(
         x.data_ptr(), weight.data_ptr(), out.data_ptr(), _native.ptr(bias), _native.ptr(residual), M, N, K,
         x.stride(0), weight.stride(0), out.stride(0), int(swiglu), _native.ptr(ss_in), int(norm_dim), float(eps),
-        _native.ptr(ss_out), _native.ptr(zero), _native.status_word(x.device).data_ptr(), _native.stream_ptr())
+        _native.ptr(ss_out), rows, parts, _native.status_word(x.device).data_ptr(), _native.stream_ptr())
     _native.check(rc, "gemm_2cta_norm")
     launch_counter[0] += 1
     return out
@@ -322,9 +338,13 @@ def paged_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
 def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
                               scale: float, out: torch.Tensor, window: int = 0,
                               num_splits: int = 1, num_seqs: Optional[int] = None,
-                              timeline: Optional[torch.Tensor] = None, max_q_len: int = 0) -> torch.Tensor:
+                              timeline: Optional[torch.Tensor] = None, max_q_len: int = 0,
+                              lse_out: Optional[torch.Tensor] = None,
+                              seq_lens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """tcgen05 flash-decode (keys on the MMA M axis): the first ``num_seqs`` sequences of the
-    batch, each with at most 16/G query tokens; ``q``/``out`` hold exactly their tokens."""
+    batch, each with at most 16/G query tokens; ``q``/``out`` hold exactly their tokens.
+    ``lse_out`` (fp32 [T, Hq]) receives the log-sum-exp over the keys seen, ``seq_lens`` replaces
+    the metadata's lengths (a context-parallel rank attends over the keys it stores)."""
     T, Hq, D = q.shape
     if num_seqs is None:
         num_seqs = meta.num_reqs
@@ -332,15 +352,51 @@ def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
     scratch = None
     if num_splits > 1:
         scratch = _get_scratch(q.device, T * Hq * num_splits * (D + 1) * 4)
-    rc = _native.lib().b200_attn_decode_tc(
+    if lse_out is not None and (lse_out.dtype != torch.float32 or lse_out.numel() < T * Hq
+                                or not lse_out.is_contiguous()):
+        raise ValueError("lse_out must be a contiguous fp32 tensor of T x Hq elements")
+    sl = meta.seq_lens if seq_lens is None else seq_lens
+    rc = _native.lib().b200_attn_decode_tc_lse(
         q.data_ptr(), q.stride(0), T, k_cache.data_ptr(), v_cache.data_ptr(), NB, BS,
-        meta.query_start_loc.data_ptr(), meta.seq_lens.data_ptr(), meta.block_table.data_ptr(),
+        meta.query_start_loc.data_ptr(), sl.data_ptr(), meta.block_table.data_ptr(),
         meta.block_table.stride(0), num_seqs, Hq, Hkv, D, scale, int(window), num_splits,
         max_q_len if max_q_len else min(meta.max_query_len, 16 // (Hq // Hkv)), out.data_ptr(),
-        out.stride(0), _native.ptr(scratch), kv_layout(k_cache),
+        out.stride(0), _native.ptr(scratch), kv_layout(k_cache), _native.ptr(lse_out),
         _native.status_word(q.device).data_ptr(), _native.ptr(timeline), _native.stream_ptr())
     _native.check(rc, "attn_decode_tc")
     launch_counter[0] += 1 + (1 if num_splits > 1 else 0)
+    return out
+
+
+def merge_attn_partials(partial_o: torch.Tensor, partial_lse: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        lse_out: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:
+    """partial_o fp32 [T, H, S, D] (each normalised over its own keys), partial_lse fp32 [T, H, S] ->
+    [T, H, D]: the attention result over the union of the S key sets."""
+    T, H, S, D = partial_o.shape
+    if not partial_o.is_cuda:
+        m = partial_lse.max(dim=-1, keepdim=True).values.clamp(min=-1e30)
+        w = torch.exp(partial_lse - m)
+        w = torch.where(torch.isfinite(partial_lse), w, torch.zeros_like(w))
+        den = w.sum(-1)
+        res = (partial_o * w.unsqueeze(-1)).sum(2) / den.clamp(min=1e-30).unsqueeze(-1)
+        if lse_out is not None:
+            lse_out.copy_(torch.where(den > 0, m.squeeze(-1) + torch.log(den.clamp(min=1e-30)),
+                                      torch.full_like(den, float("-inf"))))
+        res = res.to(out_dtype or partial_o.dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    if out is None:
+        out = torch.empty((T, H, D), dtype=_BF16, device=partial_o.device)
+    if not (partial_o.is_contiguous() and partial_lse.is_contiguous() and partial_lse.dtype == torch.float32
+            and out.dtype == _BF16 and out.stride(2) == 1 and out.stride(1) == D):
+        raise ValueError("merge_attn_partials takes contiguous fp32 partials and a bf16 [T, H, D] output")
+    rc = _native.lib().b200_merge_attn_partials(partial_o.data_ptr(), partial_lse.data_ptr(), T, H, S, D,
+                                                out.data_ptr(), out.stride(0), _native.ptr(lse_out),
+                                                _native.stream_ptr())
+    _native.check(rc, "merge_attn_partials")
+    launch_counter[0] += 1
     return out
 
 
