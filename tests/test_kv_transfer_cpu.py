@@ -258,6 +258,55 @@ def test_kv_pool_shares_prefixes_between_engines():
         store.close()
 
 
+@pytest.mark.parametrize("backend,layerwise", [("memory", False), ("file", False), ("file", True), ("memory", True)])
+def test_kv_pool_backends_and_layerwise_keys(backend, layerwise, tmp_path):
+    """The same sharing through the other built-in stores, block-wise and layer-wise."""
+    extra = {"backend": backend, "layerwise": layerwise, "name": f"t-{backend}-{layerwise}", "path": str(tmp_path / "kv")}
+
+    def mk():
+        return LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4,
+                   kv_transfer_config={"kv_connector": "KVPoolConnector", "kv_connector_extra_config": extra})
+    a, b = mk(), mk()
+    prompts = _prompts(2, lo=50, hi=90, seed=33)
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in a.generate(prompts, sp)]
+    a.engine.kv_connector.flush()
+    got = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
+    assert got == want
+    cb = b.engine.kv_connector
+    assert cb.stats["hit_tokens"] == sum((len(p) - 1) // 16 * 16 for p in prompts) > 0
+    st = cb.backend.stats()
+    layers = len(cb.layers)
+    per_block = layers if layerwise else 1
+    assert st["blocks"] >= a.engine.kv_connector.stats["published_blocks"] * per_block > 0
+    assert st["hits"] == cb.stats["loaded_blocks"] * per_block
+    a.engine.kv_connector.close()
+    cb.close()
+
+
+def test_kv_store_backend_registry_and_file_eviction(tmp_path):
+    from vllm_ascend_b200.distributed.kv_transfer import kv_store_backends as kb
+    with pytest.raises(ValueError, match="unknown KV store backend"):
+        kb.create_kv_store_backend({"backend": "nope"})
+    made = []
+    kb.register_kv_store_backend("mine", lambda e: made.append(e) or kb.MemoryBackend("mine-store", 1 << 20))
+    be = kb.create_kv_store_backend({"backend": "mine", "x": 1})
+    assert made == [{"backend": "mine", "x": 1}] and be.put([b"k"], [b"v"]) and be.get([b"k"]) == [b"v"]
+    assert be.get([b"k", b"missing"]) is None
+    # file store: capacity of three payloads, the least recently used file goes first
+    fb = kb.FileBackend(str(tmp_path / "s"), capacity_bytes=300)
+    for i in range(3):
+        fb.put([b"k%d" % i], [bytes([i]) * 100])
+        time.sleep(0.02)
+    assert fb.get([b"k0"]) == [b"\x00" * 100]            # touch k0: k1 is now the oldest
+    time.sleep(0.02)
+    fb.put([b"k3"], [b"\x03" * 100])
+    assert fb.exists([b"k0", b"k1", b"k2", b"k3"]) == [True, False, True, True]
+    assert fb.stats()["evictions"] == 1 and fb.stats()["used"] == 300
+    # a second process-like client on the same directory sees the same blocks
+    assert kb.FileBackend(str(tmp_path / "s")).get([b"k3"]) == [b"\x03" * 100]
+
+
 def test_layerwise_push_connector():
     """The decode engine allocates first and waits; the prefill engine pushes every layer's KV
     into the decode cache while it prefills (chunked), then signals completion."""
@@ -416,3 +465,42 @@ def test_block_keys_separate_multimodal_content_adapters_and_engines():
     conn2 = KVPoolConnector.__new__(KVPoolConnector)
     conn2.block_size, conn2._fingerprint = 16, f(cfg("b"), t16)
     assert conn2._hashes(a, 64)[0] != ha[0]
+
+
+@pytest.mark.parametrize("keep", [False, True])
+def test_recompute_cpu_offload_keeps_preempted_requests_kv_on_the_host(keep):
+    """A pool too small for the batch forces recompute preemption; with the connector the preempted
+    requests' blocks come back from the host instead of being prefilled again, and outputs do not
+    change."""
+    from vllm_ascend_b200.config import get_model_config
+    cfg = get_model_config("tiny-qwen")
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg.vocab_size, size=40).tolist() for _ in range(6)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    big = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=512, block_size=16)
+    ref = [o.outputs[0].token_ids for o in big.generate(prompts, sp)]
+
+    def small(ktc):
+        llm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=16, block_size=16,
+                  num_gpu_blocks_override=14, kv_transfer_config=ktc, enable_prefix_caching=False)
+        llm.engine.scheduler.reserve_full = False          # over-admit so decode must preempt
+        return llm
+    plain = small(None)
+    assert [o.outputs[0].token_ids for o in plain.generate(prompts, sp)] == ref
+    assert plain.engine.scheduler.num_preemptions > 0
+    steps_plain = plain.engine.runner.stats.get("steps", 0)
+    llm = small({"kv_connector": "RecomputeCPUOffloadConnector",
+                 "kv_connector_extra_config": {"cpu_bytes_to_use": 8 << 20, "enable_offload_prefix_caching": keep}})
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == ref
+    c = llm.engine.kv_connector
+    assert llm.engine.scheduler.num_preemptions > 0
+    assert c.stats["preempted_saved"] > 0 and c.stats["resumed_hits"] > 0 and c.stats["loaded_blocks"] > 0
+    if not keep:
+        # host blocks of finished requests went back to the free list
+        assert len(c.free) == c.num_cpu_blocks and not c.lru and not c._owned
+    else:
+        assert c.lru
+    with pytest.raises(ValueError, match="boolean"):
+        small({"kv_connector": "RecomputeCPUOffloadConnector",
+               "kv_connector_extra_config": {"enable_offload_prefix_caching": "yes"}})

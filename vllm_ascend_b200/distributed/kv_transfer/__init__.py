@@ -19,6 +19,8 @@ _CONNECTORS = {
     "MooncakeConnectorStoreV1": ("kv_pool", "KVPoolConnector"),
     "SimpleCPUOffloadConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
     "OffloadingConnector": ("cpu_offload_connector", "CPUOffloadConnector"),
+    "RecomputeCPUOffloadConnector": ("cpu_offload_connector", "RecomputeCPUOffloadConnector"),
+    "RecomputeCPUOffloadConnectorV1": ("cpu_offload_connector", "RecomputeCPUOffloadConnector"),
     "MultiConnector": ("multi_connector", "MultiConnector"),
     "HybridConnector": ("hybrid_connector", "HybridConnector"),
     "SfaRemoteD2HConnector": ("sfa_remote_d2h", "SfaRemoteD2HConnector"),

@@ -119,7 +119,7 @@ class CPUOffloadConnector(KVConnectorBase):
     # ------------------------------------------------------------------ scheduler side
     def get_num_new_matched_tokens(self, req, num_computed_tokens: int) -> tuple[int, bool]:
         bs = self.block_size
-        hashes = self._hashes(req, req.num_prompt_tokens - 1)      # the last token is always computed
+        hashes = self._hashes(req, self._lookup_tokens(req))       # the last token is always computed
         first = num_computed_tokens // bs
         n = 0
         for h in hashes[first:]:
@@ -145,12 +145,21 @@ class CPUOffloadConnector(KVConnectorBase):
     def build_connector_meta(self, scheduler_output) -> ConnectorMetadata:
         return ConnectorMetadata(reqs_to_recv={i: j for i, j in enumerate(self._pending_load)})
 
+    def _lookup_tokens(self, req) -> int:
+        return req.num_prompt_tokens - 1
+
     def request_finished(self, req, block_ids: list) -> tuple[bool, Optional[dict]]:
         """Offload the request's full blocks that the host does not hold yet."""
+        return self._save_blocks(req, block_ids), None
+
+    def _save_blocks(self, req, block_ids: list) -> bool:
+        """Copy the request's full blocks the host does not hold yet; True when the GPU blocks must
+        stay allocated until the copy has finished (the connector frees them then)."""
         n_full = min(req.num_computed_tokens, req.num_tokens) // self.block_size
         if n_full == 0 or not block_ids:
-            return False, None
+            return False
         hashes = self._hashes(req, n_full * self.block_size)
+        self._note_owner(req, hashes)
         src, dst, hs = [], [], []
         for h, b in zip(hashes, block_ids):
             if h in self.lru:
@@ -163,20 +172,23 @@ class CPUOffloadConnector(KVConnectorBase):
             dst.append(hb)
             hs.append(h)
         if not src:
-            return False, None
+            return False
         if not self.is_cuda:
             self._copy(src, dst, True, None)
             for h, hb in zip(hs, dst):
                 self.lru[h] = hb
             self.stats["saved_blocks"] += len(src)
-            return False, None
+            return False
         # the blocks were written on the compute stream: order the copy after it
         self.stream.wait_stream(torch.cuda.current_stream())
         self._copy(src, dst, True, self.stream)
         ev = torch.cuda.Event()
         ev.record(self.stream)
         self._saving.append((ev, list(block_ids), hs, dst))
-        return True, None          # free after the copy finished
+        return True                # free after the copy finished
+
+    def _note_owner(self, req, hashes: list) -> None:
+        pass
 
     # ------------------------------------------------------------------ worker side
     def start_load_kv(self, scheduler_output) -> None:
@@ -213,3 +225,69 @@ class CPUOffloadConnector(KVConnectorBase):
             self.stream.synchronize()
             if self._scheduler is not None:
                 self.step_finished(None, self._scheduler)
+
+
+
+class RecomputeCPUOffloadConnector(CPUOffloadConnector):
+    """Host copies of the KV of *preempted* requests.
+
+    When the scheduler preempts a request for lack of GPU blocks, everything it computed would be
+    recomputed on resume.  This connector copies the request's full blocks (prompt and generated
+    tokens) to pinned host memory before they are freed and copies them back when the request is
+    scheduled again, so a resume costs a host-to-device copy instead of a prefill.  Host blocks of a
+    request are released when it finishes; with ``enable_offload_prefix_caching`` they stay in the
+    LRU pool (and finished requests are offloaded too), which adds the prefix-sharing behaviour of the
+    plain offload connector.
+
+    Behaviour of the reference's ``RecomputeCPUOffloadConnectorV1``
+    (vllm_ascend/distributed/kv_transfer/kv_pool/recompute_cpu_offload/recompute_cpu_offload_connector.py:
+    "CPU KV cache preservation for recompute-preempted requests", ``cpu_bytes_to_use`` and
+    ``enable_offload_prefix_caching`` options)."""
+
+    def __init__(self, engine_cfg, runner):
+        ktc = dict(engine_cfg.kv_transfer_config or {})
+        extra = dict(ktc.get("kv_connector_extra_config") or {})
+        if "cpu_bytes_to_use" in extra and "cpu_bytes" not in extra:
+            extra["cpu_bytes"] = extra["cpu_bytes_to_use"]
+            engine_cfg.kv_transfer_config = dict(ktc, kv_connector_extra_config=extra)
+        super().__init__(engine_cfg, runner)
+        keep = extra.get("enable_offload_prefix_caching", False)
+        if not isinstance(keep, bool):
+            raise ValueError(f"enable_offload_prefix_caching must be a boolean, got {keep!r}")
+        self.keep_finished = keep
+        self._owned: dict[str, set] = {}
+        self.stats.update(preempted_saved=0, resumed_hits=0)
+
+    def _lookup_tokens(self, req) -> int:
+        return req.num_tokens - 1                   # a resumed request also finds its generated tokens
+
+    def _note_owner(self, req, hashes: list) -> None:
+        self._owned.setdefault(req.request_id, set()).update(hashes)
+
+    def request_preempted(self, req, block_ids: list) -> bool:
+        """Called by the scheduler before it frees a preempted request's blocks.  Returns True when
+        the blocks must stay allocated until the copy has finished."""
+        before = self.stats["saved_blocks"] + sum(len(hs) for _, _, hs, _ in self._saving)
+        delay = self._save_blocks(req, block_ids)
+        after = self.stats["saved_blocks"] + sum(len(hs) for _, _, hs, _ in self._saving)
+        self.stats["preempted_saved"] += after - before
+        return delay
+
+    def update_state_after_alloc(self, req, block_ids: list, num_external_tokens: int) -> None:
+        if num_external_tokens > 0 and req.request_id in self._owned:
+            self.stats["resumed_hits"] += num_external_tokens // self.block_size
+        super().update_state_after_alloc(req, block_ids, num_external_tokens)
+
+    def request_finished(self, req, block_ids: list) -> tuple[bool, Optional[dict]]:
+        if self.keep_finished:
+            return super().request_finished(req, block_ids)
+        # copies still in flight for this request land in the pool first
+        if self.is_cuda and any(h in self._owned.get(req.request_id, ()) for _, _, hs, _ in self._saving for h in hs):
+            self.stream.synchronize()
+            if self._scheduler is not None:
+                self.step_finished(None, self._scheduler)
+        for h in self._owned.pop(req.request_id, ()):
+            hb = self.lru.pop(h, None)
+            if hb is not None:
+                self.free.append(hb)
+        return False, None

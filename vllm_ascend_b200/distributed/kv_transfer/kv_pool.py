@@ -5,13 +5,14 @@ requests under their prefix hashes and looks blocks up before prefilling, so a p
 once is reused across the fleet.  ``KVStoreServer`` is the store (LRU by bytes) with a lookup
 endpoint; ``KVPoolConnector`` is the engine side.  Roles of the reference's store connector
 (vllm_ascend/distributed/kv_transfer/kv_pool/ascend_store/: pool_scheduler.py lookup client,
-pool_worker.py put/get, backend/* stores); the backend here is an in-memory server reached over
-ZMQ, payloads are staged through pinned host memory.
+pool_worker.py put/get, backend/* stores).  Where the blocks live is a backend chosen by name
+(``kv_store_backends``: the in-tree server, a process-local store, a directory on a shared
+filesystem, or one a deployment registers).  With ``layerwise: true`` a block travels as one
+payload per layer under ``<prefix hash>/L<layer>`` keys, so that stores see smaller objects, pipeline
+stages publish only the layers they hold, and a load can proceed layer by layer.
 """
 from __future__ import annotations
 
-import threading
-from collections import OrderedDict
 from concurrent.futures import ThreadPoolExecutor
 from typing import Optional
 
@@ -21,52 +22,45 @@ import torch
 from ...engine.block_pool import BlockPool
 from ...logger import logger
 from .base import ConnectorMetadata, KVConnectorBase
-from .side_channel import SideChannelError, SideChannelServer, request
+from .kv_store_backends import LRUBytes, create_kv_store_backend
+from .side_channel import SideChannelServer
 
 
 class KVStoreServer:
+    """The in-tree store: a byte-capacity LRU map behind the side-channel protocol."""
+
     def __init__(self, host: str = "127.0.0.1", port: int = 0, capacity_bytes: int = 1 << 30):
-        self.capacity = capacity_bytes
-        self.used = 0
-        self.blocks: "OrderedDict[bytes, bytes]" = OrderedDict()
-        self.lock = threading.Lock()
-        self.stats = {"puts": 0, "gets": 0, "hits": 0, "evictions": 0}
+        self.lru = LRUBytes(capacity_bytes)
         self.server = SideChannelServer(host, port, self._handle)
         self.port = self.server.port
         self.server.start()
 
+    @property
+    def stats(self) -> dict:
+        return self.lru.counters
+
+    @property
+    def blocks(self):
+        return self.lru.blocks
+
+    @property
+    def used(self) -> int:
+        return self.lru.used
+
     def _handle(self, msg: dict) -> dict:
         op = msg.get("op")
-        with self.lock:
-            if op == "exists":
-                return {"ok": True, "mask": [h in self.blocks for h in msg["hashes"]]}
-            if op == "put":
-                for h, payload in zip(msg["hashes"], msg["payloads"]):
-                    if h in self.blocks:
-                        self.blocks.move_to_end(h)
-                        continue
-                    while self.used + len(payload) > self.capacity and self.blocks:
-                        _, old = self.blocks.popitem(last=False)
-                        self.used -= len(old)
-                        self.stats["evictions"] += 1
-                    if len(payload) <= self.capacity:
-                        self.blocks[h] = payload
-                        self.used += len(payload)
-                        self.stats["puts"] += 1
-                return {"ok": True}
-            if op == "get":
-                out = []
-                for h in msg["hashes"]:
-                    p = self.blocks.get(h)
-                    if p is None:
-                        return {"ok": False, "error": "block evicted"}
-                    self.blocks.move_to_end(h)
-                    out.append(p)
-                self.stats["gets"] += 1
-                self.stats["hits"] += len(out)
-                return {"ok": True, "payloads": out}
-            if op == "stats":
-                return {"ok": True, "used": self.used, "blocks": len(self.blocks), **self.stats}
+        if op == "exists":
+            return {"ok": True, "mask": self.lru.exists(msg["hashes"])}
+        if op == "put":
+            self.lru.put(msg["hashes"], msg["payloads"])
+            return {"ok": True}
+        if op == "get":
+            out = self.lru.get(msg["hashes"])
+            if out is None:
+                return {"ok": False, "error": "block evicted"}
+            return {"ok": True, "payloads": out}
+        if op == "stats":
+            return {"ok": True, **self.lru.stats()}
         return {"ok": False, "error": f"unknown op {op!r}"}
 
     def close(self) -> None:
@@ -77,10 +71,12 @@ class KVPoolConnector(KVConnectorBase):
     def __init__(self, engine_cfg, runner):
         ktc = dict(engine_cfg.kv_transfer_config or {})
         extra = dict(ktc.get("kv_connector_extra_config") or {})
-        self.store = (extra.get("store_host", "127.0.0.1"), int(extra["store_port"]))
-        self.timeout_ms = int(extra.get("timeout_ms", 3000))
+        self.backend = create_kv_store_backend(extra)
+        self.layerwise = bool(extra.get("layerwise", False))
         self.block_size = engine_cfg.cache.block_size
         self.tensors = [t for pair in runner.kv_caches for t in pair]
+        # tensors of one layer travel together in layer-wise mode
+        self.layers = [[t for t in pair] for pair in runner.kv_caches]
         self._fingerprint = BlockPool.store_fingerprint(engine_cfg, self.tensors)
         self.is_cuda = self.tensors[0].is_cuda
         self.role = ktc.get("kv_role", "kv_both")
@@ -101,24 +97,48 @@ class KVPoolConnector(KVConnectorBase):
             out.append(parent)
         return out
 
-    def _ask(self, msg: dict) -> Optional[dict]:
-        try:
-            return request(*self.store, msg, self.timeout_ms)
-        except SideChannelError as e:
+    def _keys(self, hashes: list[bytes]) -> list[bytes]:
+        """Store keys of the given blocks: the hash itself, or one key per (block, layer)."""
+        if not self.layerwise:
+            return list(hashes)
+        return [h + b"/L%d" % li for h in hashes for li in range(len(self.layers))]
+
+    def _exists(self, hashes: list[bytes]) -> Optional[list[bool]]:
+        """Per block: is it (every layer of it) in the store?"""
+        mask = self.backend.exists(self._keys(hashes))
+        if mask is None:
             self.stats["lookup_failures"] += 1
-            logger.warning("KV pool: %s", e)
             return None
+        if not self.layerwise:
+            return mask
+        n = len(self.layers)
+        return [all(mask[i * n:(i + 1) * n]) for i in range(len(hashes))]
 
-    def _serialize(self, block: int) -> bytes:
-        return b"".join(t[block].contiguous().view(torch.uint8).cpu().numpy().tobytes() for t in self.tensors)
+    @staticmethod
+    def _pack(tensors, block: int) -> bytes:
+        return b"".join(t[block].contiguous().view(torch.uint8).cpu().numpy().tobytes() for t in tensors)
 
-    def _deserialize(self, payload: bytes, block: int) -> None:
+    @staticmethod
+    def _unpack(tensors, payload: bytes, block: int) -> None:
         off = 0
-        for t in self.tensors:
+        for t in tensors:
             n = t[block].numel() * t.element_size()
             src = torch.frombuffer(bytearray(payload[off:off + n]), dtype=torch.uint8).view(t.dtype).view(t[block].shape)
             t[block].copy_(src.to(t.device, non_blocking=False))
             off += n
+
+    def _serialize(self, block: int) -> list[bytes]:
+        """Payloads of one block in key order."""
+        if not self.layerwise:
+            return [self._pack(self.tensors, block)]
+        return [self._pack(layer, block) for layer in self.layers]
+
+    def _deserialize(self, payloads: list[bytes], block: int) -> None:
+        if not self.layerwise:
+            self._unpack(self.tensors, payloads[0], block)
+            return
+        for layer, payload in zip(self.layers, payloads):
+            self._unpack(layer, payload, block)
 
     # ------------------------------------------------------------------ scheduler side
     def get_num_new_matched_tokens(self, req, num_computed_tokens: int) -> tuple[int, bool]:
@@ -127,11 +147,11 @@ class KVPoolConnector(KVConnectorBase):
         hashes = self._hashes(req, req.num_prompt_tokens - 1)[num_computed_tokens // self.block_size:]
         if not hashes:
             return 0, False
-        r = self._ask({"op": "exists", "hashes": hashes})
-        if r is None:
+        mask = self._exists(hashes)
+        if mask is None:
             return 0, False
         n = 0
-        for hit in r["mask"]:
+        for hit in mask:
             if not hit:
                 break
             n += 1
@@ -156,18 +176,17 @@ class KVPoolConnector(KVConnectorBase):
         if n_full == 0 or not block_ids:
             return False, None
         hashes = self._hashes(req, n_full * self.block_size)
-        r = self._ask({"op": "exists", "hashes": hashes})
-        if r is None:
+        mask = self._exists(hashes)
+        if mask is None:
             return False, None
-        todo = [(h, b) for h, b, hit in zip(hashes, block_ids, r["mask"]) if not hit]
+        todo = [(h, b) for h, b, hit in zip(hashes, block_ids, mask) if not hit]
         if not todo:
             return False, None
         if self.is_cuda:
             torch.cuda.current_stream().synchronize()       # the blocks' last writes are complete
         # serialise now (the blocks go back to the pool right after), publish in the background
-        payloads = [self._serialize(b) for _, b in todo]
-        self._puts.append(self._pool.submit(self._ask, {"op": "put", "hashes": [h for h, _ in todo],
-                                                        "payloads": payloads}))
+        payloads = [p for _, b in todo for p in self._serialize(b)]
+        self._puts.append(self._pool.submit(self.backend.put, self._keys([h for h, _ in todo]), payloads))
         self.stats["published_blocks"] += len(todo)
         return False, None
 
@@ -175,11 +194,12 @@ class KVPoolConnector(KVConnectorBase):
     def start_load_kv(self, scheduler_output) -> None:
         jobs, self._pending_load = self._pending_load, []
         for hashes, blocks in jobs:
-            r = self._ask({"op": "get", "hashes": hashes})
-            if r is None:
+            payloads = self.backend.get(self._keys(hashes))
+            if payloads is None:
                 raise RuntimeError("KV pool lost blocks between lookup and load")
-            for payload, b in zip(r["payloads"], blocks):
-                self._deserialize(payload, b)
+            per = len(self.layers) if self.layerwise else 1
+            for i, b in enumerate(blocks):
+                self._deserialize(payloads[i * per:(i + 1) * per], b)
             self.stats["loaded_blocks"] += len(blocks)
 
     def flush(self) -> None:
@@ -193,3 +213,4 @@ class KVPoolConnector(KVConnectorBase):
     def close(self) -> None:
         self.flush()
         self._pool.shutdown(wait=True)
+        self.backend.close()

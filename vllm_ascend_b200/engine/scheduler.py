@@ -163,7 +163,11 @@ class Scheduler:
 
     def _preempt(self, req: Request, out: SchedulerOutput) -> None:
         self.running.remove(req)
-        self.pool.free(req.block_ids)
+        # a connector may keep a host copy of what the request computed: it then frees the blocks
+        # itself once the copy has finished
+        hook = getattr(self.kv_connector, "request_preempted", None)
+        if hook is None or not hook(req, req.block_ids):
+            self.pool.free(req.block_ids)
         req.block_ids = []
         req.num_computed_tokens = 0
         req.status = RequestStatus.PREEMPTED
