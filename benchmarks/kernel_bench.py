@@ -250,9 +250,117 @@ def bench_norm(a):
           flush=True)
 
 
+def bench_rope(a):
+    """Split-QKV + q/k RMSNorm + RoPE + paged KV write (one pass over the fused QKV rows)."""
+    from vllm_ascend_b200.models.layers import get_cos_sin_cache
+    T, Hq, Hkv, D = a.tokens, a.hq, a.hkv, a.d
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    pos = torch.arange(T, device="cuda", dtype=torch.int64) % 4096
+    cs = get_cos_sin_cache(D, 8192, 1e6, None, torch.device("cuda"))
+    nb = (T + 127) // 128 + 1
+    kc = ops.alloc_kv_cache(nb, 128, Hkv, D, torch.bfloat16, "cuda")
+    vc = ops.alloc_kv_cache(nb, 128, Hkv, D, torch.bfloat16, "cuda")
+    slots = torch.arange(T, device="cuda", dtype=torch.int64) + 128
+    w = torch.ones(D, device="cuda").bfloat16()
+    hbm, tf, tag = peaks()
+    ms = timeit(lambda: ops.qknorm_rope_kvwrite(qkv, pos, cs, D, w, w, 1e-6, kc, vc, slots, Hq, Hkv, D), a.iters)
+    by = T * D * 2.0 * (2 * (Hq + Hkv) + 3 * Hkv)       # q, k read + written in place; v read; k, v cache written
+    print(f"qknorm+rope+kvwrite T={T} Hq={Hq} Hkv={Hkv} D={D}: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s "
+          f"({by / ms / 1e6 / hbm:.2f} {tag})", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
+def bench_sampler(a):
+    """Greedy argmax over the vocabulary, and temperature / top-k / top-p sampling (radix select)."""
+    B, V = a.batch, a.vocab
+    logits = torch.randn(B, V, device="cuda").bfloat16()
+    hbm, tf, tag = peaks()
+    ms = timeit(lambda: ops.argmax(logits), a.iters)
+    print(f"argmax B={B} V={V}: {ms:.4f} ms  {B * V * 2 / ms / 1e6:.0f} GB/s ({B * V * 2 / ms / 1e6 / hbm:.2f} {tag})")
+    temp = torch.full((B,), 0.8, device="cuda")
+    tk = torch.full((B,), 50, device="cuda", dtype=torch.int32)
+    tp = torch.full((B,), 0.9, device="cuda")
+    seeds = torch.arange(B, device="cuda", dtype=torch.int64)
+    offs = torch.zeros(B, device="cuda", dtype=torch.int64)
+    lf = logits.float()
+
+    def run():
+        ops.sample(lf.clone(), temp, tk, tp, None, seeds, offs)
+    ms_clone = timeit(lambda: lf.clone(), a.iters)
+    ms = timeit(run, a.iters) - ms_clone
+    print(f"sample top-k/top-p B={B} V={V}: {ms:.4f} ms (clone of the logits subtracted)  "
+          f"{B * V * 4 / ms / 1e6:.0f} GB/s of fp32 logits per pass", flush=True)
+
+
+def bench_moe(a):
+    """Grouped GEMM + SwiGLU over experts (rows already sorted by expert)."""
+    from vllm_ascend_b200.ops import moe_native
+    E, K, I, rows = a.experts, a.k, a.inter, a.m
+    w13 = (torch.randn(E, 2 * I, K, device="cuda") * 0.05).bfloat16()
+    w2 = (torch.randn(E, K, I, device="cuda") * 0.05).bfloat16()
+    x = (torch.randn(rows, K, device="cuda") * 0.1).bfloat16()
+    per = rows // E
+    offsets = torch.arange(0, E + 1, device="cuda", dtype=torch.int32) * per
+    offsets[-1] = rows
+    hbm, tf, tag = peaks()
+    h = moe_native.grouped_gemm(x, w13, offsets, True)
+    ms1 = timeit(lambda: moe_native.grouped_gemm(x, w13, offsets, True), a.iters)
+    ms2 = timeit(lambda: moe_native.grouped_gemm(h, w2, offsets, False), a.iters)
+    f1, f2 = 2.0 * rows * 2 * I * K, 2.0 * rows * K * I
+    b1 = (w13.numel() + x.numel() + h.numel()) * 2.0
+    print(f"moe grouped gemm1+swiglu E={E} rows={rows} K={K} I={I}: {ms1:.4f} ms {f1 / ms1 / 1e9:.0f} TFLOP/s "
+          f"({f1 / ms1 / 1e9 / tf:.2f} {tag}), weights+acts {b1 / ms1 / 1e6:.0f} GB/s ({b1 / ms1 / 1e6 / hbm:.2f} {tag})")
+    print(f"moe grouped gemm2 : {ms2:.4f} ms {f2 / ms2 / 1e9:.0f} TFLOP/s ({f2 / ms2 / 1e9 / tf:.2f} {tag})", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
+def bench_kv_copy(a):
+    """Paged KV block gather/scatter between two caches (all layers in one launch)."""
+    from vllm_ascend_b200.attention.backend import B200AttentionBackend
+    nb, bs, H, D = a.blocks, 128, a.hkv, a.d
+    src = torch.randn(nb, bs, H, D, device="cuda").bfloat16()
+    dst = torch.zeros_like(src)
+    perm = torch.randperm(nb)
+    pairs = torch.stack([torch.arange(nb), perm], dim=1)
+    hbm, tf, tag = peaks()
+    ms = timeit(lambda: B200AttentionBackend.swap_blocks(src, dst, pairs), a.iters)
+    by = 2.0 * src.numel() * 2
+    print(f"kv block copy blocks={nb} x {bs * H * D * 2 >> 10} KiB: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s "
+          f"({by / ms / 1e6 / hbm:.2f} {tag})", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
+def bench_gemm_folded(a):
+    """Paired-CTA GEMM with the RMSNorm fold: consumer (row scale from partial statistics) and producer
+    (residual add + per-tile sum of squares) forms against the plain kernel."""
+    M, N, K = a.m, a.n, a.k
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ss_in = ops.alloc_row_stats(M + 8, max(N, K), "cuda")
+    ss_out = ops.alloc_row_stats(M + 8, max(N, K), "cuda")
+    R, P = ss_in.stats_rows, ss_in.stats_parts
+    ss_in[:R * P].view(P, R)[:8, :M] = (x.float() ** 2).sum(-1) / 8
+    ss_in[R * P:].view(torch.int32)[0] = 8
+    hbm, tf, tag = peaks()
+    fl = 2.0 * M * N * K
+    ms0 = timeit(lambda: ops.linear_norm_folded(x, w, out=out), a.iters)
+    ms1 = timeit(lambda: ops.linear_norm_folded(x, w, out=out, ss_in=ss_in, norm_dim=K, eps=1e-6), a.iters)
+    ms2 = timeit(lambda: ops.linear_norm_folded(x, w, residual=res, out=out, ss_out=ss_out), a.iters)
+    print(f"gemm-folded M={M} N={N} K={K}: plain {ms0:.4f} ms {fl / ms0 / 1e9:.0f} TFLOP/s | row-scaled "
+          f"{ms1:.4f} ms {fl / ms1 / 1e9:.0f} | +residual+statistics {ms2:.4f} ms {fl / ms2 / 1e9:.0f} "
+          f"({fl / ms2 / 1e9 / tf:.2f} {tag})", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-fp8", "attn-decode", "attn-prefill", "mla-decode", "gdn", "norm", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm-fp8", "gemm-folded", "attn-decode", "attn-prefill", "mla-decode", "gdn",
+                                     "norm", "rope", "sampler", "moe", "kv-copy", "all"])
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--blocks", type=int, default=2048)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -290,6 +398,16 @@ def main():
                 bench_gemm(a)
         else:
             bench_gemm(a)
+    if a.what == "rope":
+        bench_rope(a)
+    if a.what == "sampler":
+        bench_sampler(a)
+    if a.what == "moe":
+        bench_moe(a)
+    if a.what == "kv-copy":
+        bench_kv_copy(a)
+    if a.what == "gemm-folded":
+        bench_gemm_folded(a)
     if a.what in ("attn-decode", "all"):
         if a.what == "all":
             for b, c in [(768, 1152), (256, 1152), (32, 4096), (4, 32768)]:

@@ -24,7 +24,7 @@ WORKER = textwrap.dedent("""
     cfg = get_model_config(preset)
     llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, enable_expert_parallel=ep, pipeline_parallel_size=pp, decode_context_parallel_size=dcp,
               prefill_context_parallel_size=pcp,
-              additional_config=dict(cp_kv_cache_interleave_size=4) if dcp > 1 else (dict(finegrained_tp_config=fg) if fg else None),
+              additional_config=json.loads(os.environ["ADDCFG"]) if os.environ.get("ADDCFG") else (dict(cp_kv_cache_interleave_size=4) if dcp > 1 else (dict(finegrained_tp_config=fg) if fg else None)),
               max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     rng = np.random.default_rng(2)
     prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(3)]
@@ -47,10 +47,12 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1, fg=None):
+def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1, fg=None, addcfg=None):
     script = WORKER.format(root=ROOT)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()),
                WORLD_SIZE=str(world), OMP_NUM_THREADS="2")
+    if addcfg:
+        env["ADDCFG"] = json.dumps(addcfg)
     procs = []
     for r in range(world):
         e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
@@ -88,6 +90,73 @@ def test_pipeline_parallel_matches_single_rank(preset):
 def test_decode_context_parallel_matches_single_rank():
     # MLA latent cache sharded along the sequence over the 2 TP ranks
     assert _run("tiny-deepseek", 2, 2, dcp=2) == _run("tiny-deepseek", 1, 1)
+
+
+def test_replicated_shared_experts_match_single_rank():
+    # whole shared expert on every TP rank, each runs half of the rows, rows all-gathered
+    assert _run("tiny-deepseek", 2, 2, addcfg={"enable_shared_expert_dp": True}) == _run("tiny-deepseek", 1, 1)
+
+
+SHARED_WORKER = textwrap.dedent("""
+    import json, os, sys
+    import torch, torch.distributed as dist
+    sys.path.insert(0, {root!r})
+    from vllm_ascend_b200.config import get_model_config
+    from vllm_ascend_b200.models.layers import ParamFactory, SwiGLUMLP, TPComm
+    from vllm_ascend_b200.ops.shared_experts import SharedExpertParallelMode as M, SharedExperts
+    from vllm_ascend_b200.parallel import state as pstate
+    dist.init_process_group("gloo")
+    rank, tp = dist.get_rank(), dist.get_world_size()
+    pstate.initialize_model_parallel(tp=tp)
+    cfg = get_model_config("tiny-qwen")
+    pf = ParamFactory(cfg, torch.device("cpu"), torch.float32)
+    H, I, T = 64, 96, 10
+    comm = TPComm(pstate.get_tp_group())
+    one = TPComm(pstate.single_rank_group())
+    full = SwiGLUMLP(pf, "shared", H, I, one, reduce_results=False)                 # whole weights
+    shard = SwiGLUMLP(pf, "shared", H, I, comm, reduce_results=False)              # this rank's shard
+    gate = pf.normal("shared_gate", (1, H))
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(T, H, generator=g)
+    want = SharedExperts(full, one, True, gate).forward(x)
+    rows = T // tp
+    mine = x[rank * rows:(rank + 1) * rows]
+    out = {{}}
+    ex_tp, ex_dp = SharedExperts(shard, comm, False, gate), SharedExperts(full, comm, True, gate)
+    out["modes"] = [ex_tp.mode(False).name, ex_dp.mode(False).name, ex_tp.mode(True).name, ex_dp.mode(True).name]
+    out["tp"] = float((ex_tp.forward(x) - want).abs().max())
+    part = ex_tp.forward(x, reduce=False)
+    out["tp_partial_differs"] = float((part - want).abs().max()) > 1e-3
+    out["dp"] = float((ex_dp.forward(x) - want).abs().max())
+    out["dp_odd"] = float((ex_dp.forward(x[:7]) - want[:7]).abs().max())            # rows not divisible by tp
+    out["sp"] = float((ex_tp.forward(mine, activations_sharded=True) - want[rank * rows:(rank + 1) * rows]).abs().max())
+    out["sp_sedp"] = float((ex_dp.forward(mine, activations_sharded=True) - want[rank * rows:(rank + 1) * rows]).abs().max())
+    ex_tp.validate_split(torch.device("cpu"), torch.float32, H)
+    res = [None] * tp
+    dist.all_gather_object(res, out)
+    if rank == 0:
+        print("RESULT " + json.dumps(res), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.stdout.flush()
+    os._exit(0)
+""")
+
+
+def test_shared_experts_four_parallel_modes_agree():
+    script = SHARED_WORKER.format(root=ROOT)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE="2", OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, "-c", script], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, e[-3000:]
+    res = json.loads([l for l in outs[0][0].splitlines() if l.startswith("RESULT ")][-1][7:])
+    for r in res:
+        assert r["modes"] == ["TENSOR_PARALLEL", "DATA_PARALLEL_ONLY", "SEQUENCE_PARALLEL_ONLY", "SEQUENCE_PARALLEL_SEDP"]
+        assert r["tp_partial_differs"]
+        for k in ("tp", "dp", "dp_odd", "sp", "sp_sedp"):
+            assert r[k] < 1e-4, (k, r)
 
 
 def test_gqa_decode_context_parallel_matches_single_rank():

@@ -64,10 +64,17 @@ class SparseMoeBlock:
         self.shared = None
         self.shared_gate_weight = None
         shared_inter = cfg.shared_expert_intermediate_size or I * cfg.n_shared_experts
+        self.shared_exec = None
         if shared_inter > 0:
-            self.shared = SwiGLUMLP(pf, f"{prefix}.shared_experts", H, shared_inter, comm, reduce_results=False)
+            from ..ops.shared_experts import SharedExperts
+            from ..platform_config import get_b200_config
+            # replicated shared-expert weights: every rank holds the whole MLP and runs part of the rows
+            self.shared_replicated = bool(get_b200_config().enable_shared_expert_dp) and comm.size > 1
+            s_comm = TPComm(pstate.single_rank_group()) if self.shared_replicated else comm
+            self.shared = SwiGLUMLP(pf, f"{prefix}.shared_experts", H, shared_inter, s_comm, reduce_results=False)
             if cfg.shared_expert_gate:           # Qwen2-MoE / Qwen3-Next: sigmoid(x . w) scales the shared expert
                 self.shared_gate_weight = pf.normal(f"{prefix}.shared_expert_gate", (1, H))
+            self.shared_exec = SharedExperts(self.shared, comm, self.shared_replicated, self.shared_gate_weight)
         # logical -> physical redirect for redundant experts (EPLB); identity by default
         self._gate_bf16: Optional[torch.Tensor] = None
         self.log2phy: Optional[torch.Tensor] = None          # [E, max_replicas] physical slot ids
@@ -75,10 +82,10 @@ class SparseMoeBlock:
         self.expert_load: Optional[torch.Tensor] = None      # per-physical-expert hit counter
 
     def _shared_out(self, x: torch.Tensor) -> torch.Tensor:
-        s = self.shared(x)
-        if self.shared_gate_weight is not None:
-            s = s * torch.sigmoid(torch.nn.functional.linear(x.float(), self.shared_gate_weight.float())).to(s.dtype)
-        return s
+        """This rank's shared-expert result for the rows of ``x``: a partial sum when the weights are
+        TP shards, the complete result of the given rows when they are replicated."""
+        self.shared_exec.gate_weight = self.shared_gate_weight      # may have been reloaded
+        return self.shared_exec.local(x)
 
     def route(self, x: torch.Tensor):
         cfg = self.cfg
@@ -127,21 +134,27 @@ class SparseMoeBlock:
             y = fused_experts_lora(x, self.w13, self.w2, w, ids, self.expert_map, moe_lora)
         else:
             y = fused_moe.fused_experts(x, self.w13, self.w2, w, ids, self.expert_map, self.quant)
+        replicated = self.shared is not None and self.shared_replicated
         if self.ep is None:
             # TP-sharded experts (and shared experts) hold partial sums: one reduction
-            if self.shared is not None:
+            if self.shared is not None and not replicated:
                 y = y + self._shared_out(x)
             if self.comm.size > 1:
                 y = self.comm.all_reduce(y)
+            if replicated:
+                # whole shared expert on every rank: each runs its part of the rows, rows gathered
+                self.shared_exec.gate_weight = self.shared_gate_weight
+                y = y + self.shared_exec.forward(x)
             return y
         if self.shared is not None:
             if overlap is not None:
                 torch.cuda.current_stream().wait_stream(side)
                 s = overlap
+                if self.comm.size > 1 and not replicated:
+                    s = self.comm.all_reduce(s)
             else:
-                s = self._shared_out(x)
-            if self.comm.size > 1:
-                s = self.comm.all_reduce(s)
+                self.shared_exec.gate_weight = self.shared_gate_weight
+                s = self.shared_exec.forward(x)
             y = y + s
         return y
 
@@ -657,6 +670,10 @@ class CausalLM:
         """(group size, rank) a parameter is sharded over: the TP group unless fine-grained TP
         gives the module a group of its own."""
         from ..parallel import finegrained as fgm
+        if "shared_experts" in target and tp > 1:
+            from ..platform_config import get_b200_config
+            if get_b200_config().enable_shared_expert_dp:
+                return 1, 0                     # replicated: every rank loads the whole tensor
         fg = fgm.get_fg()
         if fg is None:
             return tp, r

@@ -134,6 +134,11 @@ _STATE = ParallelState()
 _SINGLE = GroupCoordinator("single", [0], 0)
 
 
+def single_rank_group() -> GroupCoordinator:
+    """A group of this rank alone (modules that hold whole, replicated weights)."""
+    return _SINGLE
+
+
 def _layout(world_size: int, tp: int, pp: int, dp: int, pcp: int = 1) -> torch.Tensor:
     assert world_size == tp * pp * dp * pcp, (world_size, tp, pp, dp, pcp)
     return torch.arange(world_size).reshape(dp, pp, pcp * tp)
