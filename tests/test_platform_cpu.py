@@ -204,47 +204,76 @@ def test_utils_predicates_and_op_table():
     assert utils.should_skip_allreduce_across_dp_group(cfg, True)
 
 
-def test_dyntra_lb_moves_waiting_requests_to_the_idle_rank():
-    """Two schedulers stand for two DP ranks; the gather function is a shared bus that returns
-    both ranks' contributions (the ranks call it in the same order, like a collective)."""
-    import numpy as np
+def _dyntra_pair(threshold=0.1, **cfg):
+    import numpy as np  # noqa: F401
     from vllm_ascend_b200.config import CacheConfig, SchedulerConfig
     from vllm_ascend_b200.core.dyntra_lb import DyntraLBScheduler
-    from vllm_ascend_b200.engine.request import Request, SamplingParams
     from vllm_ascend_b200.platform_config import init_b200_config
-    init_b200_config({"scheduler_config": {"dyntra_lb_config": {"enabled": True, "imbalance_threshold": 0.1}}},
-                     refresh=True)
+    init_b200_config({"scheduler_config": {"dyntra_lb_config": dict({"enabled": True, "imbalance_threshold": threshold},
+                                                                      **cfg)}}, refresh=True)
     sc = SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=64, max_model_len=256)
     cc = CacheConfig(block_size=16)
-    s = [DyntraLBScheduler(sc, cc, 64, rank=r, world=2, gather_fn=lambda v: [v]) for r in range(2)]
+    return [DyntraLBScheduler(sc, cc, 64, rank=r, world=2, gather_fn=lambda v: [v]) for r in range(2)]
+
+
+def _dyntra_lockstep(s):
+    """Emulates the two all-gathers of a balancing step for schedulers living in one process: the ranks
+    are run one after the other against a bus that returns all contributions of the phase."""
+    reports = [x.report() for x in s]
+    boxes = []
+    for r, x in enumerate(s):
+        phase = {"n": 0}
+
+        def g(v, phase=phase):
+            phase["n"] += 1
+            if phase["n"] == 1:
+                return reports
+            boxes.append(v)
+            return []                       # deliveries happen below, once every rank has posted
+        x._gather = g
+        x.balance()
+    from vllm_ascend_b200.core.dyntra_lb import _unpack
+    for box in boxes:
+        for dst, payload in box:
+            s[dst]._adopt(_unpack(payload))
+
+
+def test_dyntra_lb_plan_is_deterministic_and_narrows_the_gap():
+    from vllm_ascend_b200.core.dyntra_lb import RankReport, plan_balance
+    reps = [RankReport(running=[10, 10, 10], movable_running=[10, 10], waiting=[4, 6, 8], pool_blocks=100),
+            RankReport(running=[5], movable_running=[5], waiting=[], pool_blocks=100),
+            RankReport(running=[20, 4], movable_running=[4], waiting=[2], pool_blocks=100)]
+    a = plan_balance(reps, 0.05, 4)
+    b = plan_balance(reps, 0.05, 4)
+    assert [(m.out_blk, m.out_to, m.in_blk, m.freeze) for m in a] == [(m.out_blk, m.out_to, m.in_blk, m.freeze) for m in b]
+    loads = [r.load for r in reps]
+    after = list(loads)
+    for i, m in enumerate(a):
+        after[i] += sum(m.in_blk) - sum(m.out_blk)
+    assert sum(after) == sum(loads) and max(after) - min(after) < max(loads) - min(loads)
+    assert sum(len(m.out_blk) for m in a) == sum(len(m.in_blk) for m in a) > 0
+    assert a[0].out_blk and all(d != 0 for d in a[0].out_to)
+    assert len(a[0].out_blk) <= 4
+    # waiting requests go before running ones
+    assert set(a[0].out_blk) <= {4, 6, 8} or set([4, 6, 8]) <= set(a[0].out_blk)
+    # inside the threshold nothing moves
+    calm = plan_balance([RankReport(running=[10], waiting=[], pool_blocks=100),
+                         RankReport(running=[8], waiting=[], pool_blocks=100)], 0.05, 4)
+    assert not any(m.out_blk or m.freeze for m in calm)
+
+
+def test_dyntra_lb_moves_waiting_requests_to_the_idle_rank():
+    """Two schedulers stand for two DP ranks."""
+    import numpy as np
+    from vllm_ascend_b200.engine.request import Request, SamplingParams
+    s = _dyntra_pair()
     for i in range(10):                 # everything arrives at rank 0
         req = Request(f"r{i}", np.arange(100, dtype=np.int32), SamplingParams(max_tokens=4))
         req.client_index, req.origin_rank = i, 0
         s[0].add_request(req)
-
-    def lockstep_balance():
-        # phase 1: loads; phase 2: outboxes -- emulate the two all-gathers
-        loads = [(x.pressure(), len(x.waiting), len(x.running)) for x in s]
-        outs = []
-        for r in range(2):
-            phase = {"n": 0}
-
-            def g(v, r=r, phase=phase):
-                phase["n"] += 1
-                if phase["n"] == 1:
-                    return loads
-                outs.append((r, v))
-                return [[], []]         # deliveries happen below
-            s[r]._gather = g
-            s[r].balance()
-        for r, box in outs:
-            for dst, payload in box:
-                from vllm_ascend_b200.core.dyntra_lb import _unpack
-                s[dst].add_request(_unpack(payload))
-                s[dst].migrated_in += 1
     before = len(s[0].waiting)
     for _ in range(4):
-        lockstep_balance()
+        _dyntra_lockstep(s)
     assert s[0].migrated_out > 0 and s[1].migrated_in == s[0].migrated_out
     assert len(s[0].waiting) + len(s[1].waiting) == before
     assert abs(s[0].pressure() - s[1].pressure()) < before * 7 / 64
@@ -252,6 +281,49 @@ def test_dyntra_lb_moves_waiting_requests_to_the_idle_rank():
     assert all(r.origin_rank == 0 and r.client_index is not None for r in moved)
     # the oldest requests stay where they arrived
     assert s[0].waiting[0].request_id == "r0"
+
+
+def test_dyntra_lb_pauses_running_requests_and_the_receiver_resumes_them():
+    import numpy as np
+    from vllm_ascend_b200.engine.request import Request, RequestStatus, SamplingParams
+    s = _dyntra_pair(threshold=0.05, long_req_block_threshold=5)
+    lens = [40, 40, 40, 40, 120]                      # the last one is long (8 blocks > 5): it stays
+    for i, n in enumerate(lens):
+        req = Request(f"r{i}", np.arange(n, dtype=np.int32), SamplingParams(max_tokens=16))
+        req.client_index, req.origin_rank = i, 0
+        s[0].add_request(req)
+    s[0].world = 1                                     # admit everything without balancing first
+    for _ in range(8):
+        out = s[0].schedule()
+        for req, n in out.scheduled:
+            req.num_computed_tokens += n
+            if req.num_computed_tokens >= req.num_tokens:
+                req.output_token_ids = (req.output_token_ids or []) + [7]
+                req.num_output_tokens += 1
+    s[0].world = 2
+    assert len(s[0].running) == 5 and not s[0].waiting
+    assert all(r.num_output_tokens > 0 for r in s[0].running)
+    free_before = s[0].pool.num_free_blocks
+    _dyntra_lockstep(s)
+    assert s[0].paused_running > 0 and s[0].migrated_out == s[0].paused_running == s[1].migrated_in
+    assert s[0].pool.num_free_blocks > free_before                       # the paused requests' blocks came back
+    assert "r4" in s[0].requests and all(r.request_id != "r4" for r in s[1].waiting)
+    got = list(s[1].waiting)
+    assert all(r.status == RequestStatus.PREEMPTED and r.num_output_tokens > 0 and r.output_token_ids for r in got)
+    assert all(r.request_id not in s[0].requests for r in got)
+    # the receiver schedules prompt + generated tokens of a resumed request
+    out = s[1].schedule.__wrapped__(s[1]) if hasattr(s[1].schedule, "__wrapped__") else None
+    s[1].world = 1
+    out = s[1].schedule()
+    first = out.scheduled[0]
+    assert first[0].request_id == got[0].request_id and first[1] == min(64, got[0].num_tokens)
+    # a frozen rank admits nothing new
+    s[0].lb_freeze = True
+    fresh = Request("new", np.arange(20, dtype=np.int32), SamplingParams(max_tokens=4))
+    s[0].add_request(fresh)
+    s[0].world = 1
+    s[0].schedule()
+    assert fresh.status == RequestStatus.WAITING and fresh not in s[0].running
 
 
 def test_training_consistent_attention_backend_selection():

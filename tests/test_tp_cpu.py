@@ -254,3 +254,56 @@ def test_groups_destroyed_for_sleep_come_back_in_the_same_coordinators():
         assert p.returncode == 0, e[-3000:]
     before, after, destroyed = json.loads([l for l in outs[0][0].splitlines() if l.startswith("RESULT ")][-1][7:])
     assert before == after and destroyed >= 2
+
+
+DYNTRA_WORKER = textwrap.dedent("""
+    import json, os, sys
+    import numpy as np
+    sys.path.insert(0, {root!r})
+    from vllm_ascend_b200.config import get_model_config
+    from vllm_ascend_b200.engine.llm import LLM
+    from vllm_ascend_b200.engine.request import SamplingParams
+    dp = int(sys.argv[1])
+    add = {{"scheduler_config": {{"dyntra_lb_config": {{"enabled": True, "imbalance_threshold": 0.02,
+                                                        "max_migrations_per_step": 2}}}}}} if dp > 1 else None
+    cfg = get_model_config("tiny-qwen")
+    llm = LLM(cfg, device="cpu", data_parallel_size=dp, additional_config=add, max_model_len=256, max_num_seqs=4,
+              max_num_batched_tokens=64, block_size=16, num_gpu_blocks_override=64)
+    rng = np.random.default_rng(5)
+    # even prompts (rank 0's share) are long, odd ones short: rank 0 is the loaded one
+    prompts = [rng.integers(0, cfg.vocab_size, size=(90 if i % 2 == 0 else 8)).tolist() for i in range(12)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    s = llm.engine.scheduler
+    stats = [getattr(s, "migrated_out", 0), getattr(s, "migrated_in", 0), getattr(s, "paused_running", 0)]
+    print("STATS%s " % os.environ.get("RANK", "0") + json.dumps(stats), flush=True)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print("RESULT " + json.dumps([o.outputs[0].token_ids for o in outs]), flush=True)
+    llm.shutdown()
+    sys.stdout.flush()
+    os._exit(0)
+""")
+
+
+def _run_dyntra(dp):
+    script = DYNTRA_WORKER.format(root=ROOT)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE=str(dp), OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, "-c", script, str(dp)], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(dp)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, e[-3000:]
+    res = json.loads([l for l in outs[0][0].splitlines() if l.startswith("RESULT ")][-1][7:])
+    stats = {}
+    for o, _ in outs:
+        for l in o.splitlines():
+            if l.startswith("STATS"):
+                stats[int(l[5])] = json.loads(l[7:])
+    return res, stats
+
+
+def test_dyntra_lb_balances_data_parallel_engines_without_changing_outputs():
+    want, _ = _run_dyntra(1)
+    got, stats = _run_dyntra(2)
+    assert got == want
+    # the loaded rank handed requests to the other one (waiting or paused running ones)
+    assert stats[0][0] > 0 and stats[1][1] == stats[0][0] + stats[1][0] - stats[0][1]

@@ -99,7 +99,13 @@ class LLMEngine:
                     request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None,
                     job_id: Optional[str] = None, lora_request=None,
                     multi_modal_data: Optional[dict] = None, prompt_embeds=None) -> str:
-        rid = request_id or f"req-{next(self._req_counter)}"
+        if request_id:
+            rid = request_id
+        elif self.dp.world_size > 1:
+            # unique across replicas: a request may move to another replica (load balancing)
+            rid = f"req-d{self.dp.rank_in_group}-{next(self._req_counter)}"
+        else:
+            rid = f"req-{next(self._req_counter)}"
         sampling_params.validate_for_vocab(self.cfg.model.vocab_size)
         if lora_request is not None and self.runner.lora_manager is None:
             raise ValueError("a LoRA request needs an engine built with enable_lora=True")
@@ -293,7 +299,11 @@ class LLMEngine:
         import torch.distributed as dist
         t0 = time.perf_counter()
         busy = self.scheduler.has_unfinished()
-        so = self.scheduler.schedule() if busy else None
+        # a scheduler that talks to its peers inside schedule() (cross-replica load balancing) must be
+        # called on every rank every step, and may have received work there
+        collective = getattr(self.scheduler, "collective_schedule", False)
+        so = self.scheduler.schedule() if (busy or collective) else None
+        busy = busy or (collective and self.scheduler.has_unfinished())
         ntok = so.num_scheduled_tokens if so is not None else 0
         nrows = 0 if so is None else sum(1 for r, n in so.scheduled if r.num_computed_tokens + n >= r.num_tokens)
         sync = torch.tensor([int(busy), max(ntok, 1), nrows], dtype=torch.int32)

@@ -282,7 +282,7 @@ def _validate_eplb(e: EplbConfig, is_moe: bool, ep: bool) -> None:
         raise ValueError("dynamic_eplb and a static expert_map_path are mutually exclusive")
 
 
-def _validate_scheduler_ext(s: SchedulerExtConfig, engine_cfg) -> None:
+def _validate_scheduler_ext(s: SchedulerExtConfig, engine_cfg, dp_size: int = 1) -> None:
     """vllm_ascend/platform.py:798-925: at most one queue policy; option sanity."""
     chosen = [n for n, on in (("short_request_first", s.short_request_first_config.enabled),
                               ("batch_job", s.batch_job_sched_config.enabled),
@@ -300,7 +300,7 @@ def _validate_scheduler_ext(s: SchedulerExtConfig, engine_cfg) -> None:
             raise ValueError("profiling_chunk_config requires chunked prefill")
     if s.recompute_scheduler_enable and not engine_cfg.kv_transfer_config:
         raise ValueError("recompute_scheduler_enable requires a kv_transfer_config (decode node)")
-    if s.dyntra_lb_config.enabled and engine_cfg.parallel.data_parallel_size <= 1:
+    if s.dyntra_lb_config.enabled and max(dp_size, engine_cfg.parallel.data_parallel_size) <= 1:
         raise ValueError("dyntra_lb_config requires data parallelism")
 
 
@@ -350,7 +350,7 @@ def check_and_update_config(engine_cfg) -> B200Config:
             raise ValueError("fine-grained tensor parallelism shards replicated modules of tp=1 replicas")
         cc.cudagraph_mode = "NONE"        # token counts differ per replica and are padded per step
     _validate_eplb(cfg.eplb_config, mc.is_moe, pc.enable_expert_parallel)
-    _validate_scheduler_ext(cfg.scheduler_config, engine_cfg)
+    _validate_scheduler_ext(cfg.scheduler_config, engine_cfg, dp_size)
     if mc.is_hybrid and engine_cfg.speculative_config:
         # a rejected draft token has already advanced the recurrent state and cannot be taken back
         raise ValueError("speculative decoding is not supported for models with recurrent (linear-attention) layers")
