@@ -264,10 +264,9 @@ def weight_transfer():
     os.environ["MASTER_PORT"] = str(int(os.environ["MASTER_PORT"]) + 31 + rank)
     torch.cuda.set_device(rank)
     cfg = _cfg()
-    cfg.seed = 42 if rank == 0 else 1
     sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
     prompts = [list(range(10, 90)), list(range(300, 340))]
-    llm = LLM(cfg, device=f"cuda:{rank}", max_model_len=256, max_num_seqs=4, max_num_batched_tokens=128,
+    llm = LLM(cfg, device=f"cuda:{rank}", seed=42 if rank == 0 else 1, max_model_len=256, max_num_seqs=4, max_num_batched_tokens=128,
               num_gpu_blocks_override=16, enforce_eager=True)
     mine = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
     eng = NCCLWeightTransferEngine("127.0.0.1", port, rank, 2, backend="nccl", bucket_bytes=4 << 20)

@@ -105,7 +105,7 @@ def test_pipeline_parallel_on_two_gpus():
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_sleep_and_wake_up_rebuild_nccl_communicators():
-    r = _run(2, "sleep_wake", {"VLLM_B200_TP_COMM": "nccl"})
+    r = _run(2, "sleep_wake", {"VLLM_B200_TP_COMM": "nccl"}, timeout=180)
     assert r["before"] == r["after"]
     assert r["freed_bytes"] > 0 and r["replays"] > 0
 

@@ -28,7 +28,12 @@ WORKER = textwrap.dedent("""
               max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     rng = np.random.default_rng(2)
     prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(3)]
-    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    want_lp = os.environ.get("LOGPROBS") == "1"
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True,
+                                                logprobs=2 if want_lp else None))
+    if want_lp and int(os.environ.get("RANK", "0")) == 0:
+        print("LOGPROBS " + json.dumps([[sorted((int(k), round(float(v), 4)) for k, v in d.items())
+                                         for d in o.outputs[0].logprobs] for o in outs]), flush=True)
     if fg:                 # data parallel: every rank reports the prompts it served
         print("PART " + json.dumps(dict((str(o.prompt_token_ids[:3]), o.outputs[0].token_ids) for o in outs)), flush=True)
     if int(os.environ.get("RANK", "0")) == 0:
@@ -75,6 +80,40 @@ def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1, fg=None, addcfg=None):
 @pytest.mark.parametrize("preset", ["tiny-qwen", "tiny-moe", "tiny-deepseek", "tiny-mqa"])
 def test_tp2_matches_tp1(preset):
     assert _run(preset, 2, 2) == _run(preset, 1, 1)
+
+
+def _run_logprobs(preset, world, tp, **kw):
+    os.environ["LOGPROBS"] = "1"
+    try:
+        script_out = {}
+        orig = subprocess.Popen
+
+        class Capture(orig):
+            def communicate(self, *a, **k):
+                o, e = super().communicate(*a, **k)
+                for l in o.splitlines():
+                    if l.startswith("LOGPROBS "):
+                        script_out["lp"] = json.loads(l[9:])
+                return o, e
+        subprocess.Popen = Capture
+        toks = _run(preset, world, tp, **kw)
+        return toks, script_out.get("lp")
+    finally:
+        subprocess.Popen = orig
+        os.environ.pop("LOGPROBS", None)
+
+
+@pytest.mark.parametrize("kw", [dict(pp=2), dict(pcp=2)])
+def test_logprobs_reach_every_rank_under_pipeline_and_prefill_context_parallelism(kw):
+    tp = 1
+    want_t, want_lp = _run_logprobs("tiny-qwen", 1, 1)
+    got_t, got_lp = _run_logprobs("tiny-qwen", 2, tp, **kw)
+    assert got_t == want_t and got_lp is not None and len(got_lp) == len(want_lp)
+    for a, b in zip(got_lp, want_lp):
+        assert len(a) == len(b) == 6
+        for da, db in zip(a, b):
+            assert [k for k, _ in da] == [k for k, _ in db]
+            assert max(abs(x[1] - y[1]) for x, y in zip(da, db)) < 1e-3
 
 
 def test_expert_parallel_matches_single_rank():

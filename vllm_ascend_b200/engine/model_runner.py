@@ -749,10 +749,17 @@ class ModelRunner:
             if not md.all_greedy and not self.is_cuda:
                 md.generator = self._cpu_generator()
             tokens = self.sampler(logits, md).to(torch.int64)
+            dev_lp = self._device_logprobs(logits, tokens, sample_reqs)
         else:
             tokens = torch.zeros(n, dtype=torch.int64, device=self.device)
+            dev_lp = None
         tokens = self.pcp.broadcast(tokens.contiguous(), src=0)
         toks = tokens.cpu().numpy()
+        if any(r.sampling_params.logprobs is not None for r in sample_reqs):
+            # every rank of the group reports the same log-probabilities
+            host_lp = None if dev_lp is None else tuple(t.cpu() for t in dev_lp)
+            host_lp = self.pcp.broadcast_object(host_lp, src=0)
+            self._store_logprobs(host_lp, sample_reqs, toks)
         out = {}
         for r, t in zip(sample_reqs, toks):
             self.token_ids_cpu[r.row, r.num_tokens] = int(t)
@@ -930,8 +937,13 @@ class ModelRunner:
             md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
             if not md.all_greedy and not self.is_cuda:
                 md.generator = self._cpu_generator()
-            toks = self.sampler(logits, md).cpu().tolist()
+            tokens = self.sampler(logits, md)
+            dev_lp = self._device_logprobs(logits, tokens, sample_reqs)
+            toks = (tokens.cpu().tolist(), None if dev_lp is None else tuple(t.cpu() for t in dev_lp))
         toks = pp.broadcast_object(toks, src=pp.world_size - 1)
+        if toks is not None:
+            toks, host_lp = toks
+            self._store_logprobs(host_lp, sample_reqs, toks)
         out = {}
         for r, t in zip(sample_reqs, toks or []):
             self.token_ids_cpu[r.row, r.num_tokens] = int(t)

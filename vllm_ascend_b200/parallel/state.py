@@ -244,6 +244,13 @@ def restore_groups() -> int:
                 if mine.cpu_group is None:
                     mine.cpu_group = dg
                 n += 1
+                if backend == "nccl" and torch.cuda.is_available():
+                    # a device communicator is built by its first collective: do that here, outside
+                    # any stream capture (graphs are re-captured right after wake-up)
+                    t = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()))
+                    dist.all_reduce(t, group=dg)
+    if n and torch.cuda.is_available():
+        torch.cuda.synchronize()
     _SUSPENDED = False
     return n
 
