@@ -197,3 +197,86 @@ def test_sparse_mla_model_on_engine():
     assert sum(x[0] == y[0] for x, y in zip(outs[512], outs[0])) >= 2, outs
     assert outs[32] != outs[0]
     _native.check_status(torch.device("cuda"))
+
+
+@pytest.mark.parametrize("H,dn,dr,dc", [(16, 128, 64, 512), (4, 32, 16, 32)])
+def test_mla_preprocess_kernel_matches_separate_steps(H, dn, dr, dc):
+    """Latent RMSNorm + rope-key RoPE + cache scatter + query RoPE in one kernel against the norm / rope /
+    index_copy steps it replaces."""
+    from vllm_ascend_b200 import ops
+    dev = "cuda"
+    g = torch.Generator().manual_seed(3)
+    T, bs, nblk = 37, 16, 6
+    q = (torch.randn(T, H, dn + dr, generator=g) * 0.5).bfloat16().to(dev)
+    kv = (torch.randn(T, dc + dr + 8, generator=g) * 0.5).bfloat16().to(dev)[:, :dc + dr]     # strided rows
+    w = (torch.rand(dc, generator=g) + 0.5).bfloat16().to(dev)
+    pos = torch.randint(0, 500, (T,), generator=g).to(dev)
+    cos_sin = ref.build_cos_sin_cache(dr, 512, 1e4, None, torch.device(dev))
+    slots = torch.randperm(nblk * bs, generator=g)[:T].to(dev)
+    slots[5] = -1
+    slots[20] = -1
+    lat_cache = torch.full((nblk, bs, 1, dc), 7.0, dtype=torch.bfloat16, device=dev)
+    pe_cache = torch.full((nblk, bs, 1, dr), 7.0, dtype=torch.bfloat16, device=dev)
+    # the separate steps
+    want_lat = ref.rms_norm(kv[:, :dc].contiguous(), w, 1e-6)[0]
+    want_kpe = ref.apply_rope_interleaved(kv[:, dc:].reshape(T, 1, dr), pos, cos_sin, dr).view(T, dr)
+    want_q = q.clone()
+    want_q[..., dn:] = ref.apply_rope_interleaved(q[..., dn:], pos, cos_sin, dr)
+    want_lc, want_pc = lat_cache.clone(), pe_cache.clone()
+    keep = slots >= 0
+    want_lc.view(-1, dc)[slots[keep]] = want_lat[keep]
+    want_pc.view(-1, dr)[slots[keep]] = want_kpe[keep]
+    got_lat, got_kpe = ops.mla_preprocess(q, kv, w, 1e-6, pos, cos_sin, slots, lat_cache, pe_cache, dn, dr,
+                                          want_outputs=True)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(dev))
+    assert torch.equal(q[..., :dn], want_q[..., :dn])
+    # fp32 math rounded once on both sides; the fused multiply-adds may differ by one bf16 ulp
+    assert float((q.float() - want_q.float()).abs().max()) <= 2e-2
+    assert float((got_lat.float() - want_lat.float()).abs().max()) <= 3e-2
+    assert float((got_kpe.float() - want_kpe.float()).abs().max()) <= 2e-2
+    assert torch.equal(lat_cache.view(-1, dc)[slots[keep]], got_lat[keep])
+    assert torch.equal(pe_cache.view(-1, dr)[slots[keep]], got_kpe[keep])
+    # untouched slots keep their contents; skipped tokens wrote nothing
+    untouched = torch.ones(nblk * bs, dtype=torch.bool, device=dev)
+    untouched[slots[keep]] = False
+    assert bool((lat_cache.view(-1, dc)[untouched] == 7.0).all()) and bool((pe_cache.view(-1, dr)[untouched] == 7.0).all())
+    # without caches (host-resident KV): outputs only, query still rotated
+    q2 = want_q.clone()
+    q2[..., dn:] = (torch.randn(T, H, dr, generator=g) * 0.5).bfloat16().to(dev)
+    exp2 = q2.clone()
+    exp2[..., dn:] = ref.apply_rope_interleaved(q2[..., dn:], pos, cos_sin, dr)
+    lat2, kpe2 = ops.mla_preprocess(q2, kv, w, 1e-6, pos, cos_sin, None, None, None, dn, dr, want_outputs=True)
+    torch.cuda.synchronize()
+    assert torch.equal(lat2, got_lat) and torch.equal(kpe2, got_kpe)
+    assert float((q2.float() - exp2.float()).abs().max()) <= 2e-2
+
+
+def test_weight_absorption_through_the_grouped_gemm_matches_einsum():
+    """[T, H, K] x per-head [K, N] with the heads as groups of the grouped tcgen05 GEMM."""
+    from vllm_ascend_b200.config import get_model_config
+    from vllm_ascend_b200.models.layers import ParamFactory, TPComm
+    from vllm_ascend_b200.models.transformer import MLAAttention
+    from vllm_ascend_b200.parallel import state as pstate
+    cfg = get_model_config("deepseek-v3")
+    cfg.num_attention_heads = 16
+    cfg.hidden_size = 1024
+    cfg.q_lora_rank = 256
+    cfg.quantization = None
+    dev = torch.device("cuda")
+    pstate.initialize_model_parallel()
+    pf = ParamFactory(cfg, dev, torch.bfloat16)
+    a = MLAAttention(pf, cfg, 0, TPComm(pstate.single_rank_group()), 1024)
+    g = torch.Generator().manual_seed(0)
+    for T in (1, 37, 300):
+        q_nope = (torch.randn(T, a.H, a.dn, generator=g) * 0.5).bfloat16().to(dev)
+        got = a._per_head_matmul(q_nope, a.W_UK, a.W_UK_nk)
+        want = torch.einsum("thd,hdc->thc", q_nope.float(), a.W_UK.float())
+        assert got.shape == (T, a.H, a.dc)
+        assert float((got.float() - want).abs().max()) <= 0.02 * float(want.abs().max()) + 1e-3
+        o_lat = (torch.randn(T, a.H, a.dc, generator=g) * 0.5).bfloat16().to(dev)
+        got2 = a._per_head_matmul(o_lat, a.W_UV, a.W_UV_nk)
+        want2 = torch.einsum("thc,hcv->thv", o_lat.float(), a.W_UV.float())
+        assert float((got2.float() - want2).abs().max()) <= 0.02 * float(want2.abs().max()) + 1e-3
+    torch.cuda.synchronize()
+    _native.check_status(dev)

@@ -15,6 +15,21 @@ def test_argmax(dtype):
     assert torch.equal(ops.argmax(x), x.float().argmax(-1))
 
 
+def test_argmax_ties_odd_widths_and_unaligned_rows():
+    """The first maximum wins, whatever mix of vector and scalar loads reads the row."""
+    g = torch.Generator(device="cpu").manual_seed(0)
+    for V in (8, 9, 1000, 1003, 4099):
+        x = torch.randint(-3, 4, (5, V), generator=g).to(torch.bfloat16).to(DEV)       # many ties
+        assert torch.equal(ops.argmax(x), x.float().argmax(-1)), V
+    wide = torch.randint(-3, 4, (6, 2051), generator=g).to(torch.bfloat16).to(DEV)
+    view = wide[:, 3:]                       # rows start 6 bytes off a 16-byte boundary
+    assert torch.equal(ops.argmax(view), view.float().argmax(-1))
+    top = torch.zeros(2, 4096, dtype=torch.bfloat16, device=DEV)
+    top[0, 4095] = 1.0
+    top[1, 0] = 1.0
+    assert ops.argmax(top).tolist() == [4095, 0]
+
+
 def test_penalties_match_reference():
     torch.manual_seed(0)
     B, V = 9, 5000

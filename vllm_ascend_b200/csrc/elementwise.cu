@@ -281,6 +281,10 @@ qknorm_rope_kvwrite_d128_kernel(__nv_bfloat16* qkv, long qkv_stride,
       wk[2 * j] = fb.x; wk[2 * j + 1] = fb.y;
     }
   }
+  // rotary angles of the token the previous row belonged to: a thread's rows are heads of one token
+  // most of the time, so the table is read once per token instead of once per (token, head)
+  int t_cs = -1;
+  float cc[4] = {1.f, 1.f, 1.f, 1.f}, sv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int i = 0; i < RPT; i++) {
     const int t = tt[i], h = hh[i];
@@ -311,10 +315,14 @@ qknorm_rope_kvwrite_d128_kernel(__nv_bfloat16* qkv, long qkv_stride,
         for (int j = 0; j < 8; j++)      // rounded to bf16 like the unfused norm -> rope sequence
           v[j] = __bfloat162float(__float2bfloat16(v[j] * inv * (is_q ? wq[j] : wk[j])));
       }
-      const float* cs = cos_sin + positions[t] * (long)D + hl * 4;
-      const float4 c = *reinterpret_cast<const float4*>(cs);
-      const float4 sn = *reinterpret_cast<const float4*>(cs + 64);
-      const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+      if (t != t_cs) {
+        const float* cs = cos_sin + positions[t] * (long)D + hl * 4;
+        const float4 c = *reinterpret_cast<const float4*>(cs);
+        const float4 sn = *reinterpret_cast<const float4*>(cs + 64);
+        cc[0] = c.x; cc[1] = c.y; cc[2] = c.z; cc[3] = c.w;
+        sv[0] = sn.x; sv[1] = sn.y; sv[2] = sn.z; sv[3] = sn.w;
+        t_cs = t;
+      }
       float x1[4], x2[4];
 #pragma unroll
       for (int j = 0; j < 4; j++) {

@@ -67,6 +67,7 @@ struct Gemm2Params {
   float* row_ss_out;                  // [tile_n][row] = sum of squares of the bf16 output row within that column tile
   long ss_stride;
   int ss_parts_max;
+  int l2_prefetch;                    // k-blocks the L2 prefetch of W (and A) runs ahead of the staged loads; 0 = off
 };
 // G2_PUB: the last CTA publishes this rank's reduce-scatter epoch to every peer (set with G2_RS;
 // alone it is the NVLS form: rows stay in the local multicast-bound buffer C)
@@ -224,9 +225,25 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // gate rows, the peer the matching 128 up rows.
       const int w_row = p.swiglu ? tn * 128 + (int)rank * p.up_row_offset
                                  : tn * p.bn + (int)rank * (p.bn >> 1);
+      // Few row tiles (decode batches): every weight byte is read from DRAM once and nothing else
+      // hides that latency but the depth of the stage ring, so the boxes of later k-blocks are
+      // requested into L2 ahead of time.  One row tile asks for W, one column tile for A.
+      const bool pf_w = p.l2_prefetch > 0 && tm == 0;
+      const bool pf_a = p.l2_prefetch > 0 && p.mode == 0 && tn == 0 && a_row < p.M;
+      if (lane == 0 && (pf_w || pf_a)) {
+        for (int kb = 0; kb < p.l2_prefetch && kb < num_kb; kb++) {
+          if (pf_w) tma_prefetch_l2_2d(&tmap_b, kb * G2_BK, w_row);
+          if (pf_a) tma_prefetch_l2_2d(&tmap_a, kb * G2_BK, a_row);
+        }
+      }
       for (int kb = 0; kb < num_kb; kb++) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word)) goto done;
         if (lane == 0) {
+          const int kpf = kb + p.l2_prefetch;
+          if (kpf < num_kb) {
+            if (pf_w) tma_prefetch_l2_2d(&tmap_b, kpf * G2_BK, w_row);
+            if (pf_a) tma_prefetch_l2_2d(&tmap_a, kpf * G2_BK, a_row);
+          }
           uint8_t* sa = tiles + stage * G2_STAGE_BYTES;
           uint8_t* sb = sa + G2_A_BYTES;
           const uint32_t lbar = smem_u32(&full_bar[stage]) & kPeerBitMask;
@@ -484,6 +501,7 @@ using namespace b200;
 
 static int g_raster = 16;
 static int g_force_bn = 0;      // 0: choose per problem; 128..256: fixed tile width (benchmarks)
+static int g_l2_prefetch = -1;  // -1: per problem; otherwise the prefetch distance in k-blocks (0 = off)
 
 static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, int ldw, long a_rows,
                        cudaStream_t stream) {
@@ -533,6 +551,8 @@ static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, in
   int clusters = p.tiles_m * p.tiles_n;
   if (clusters > max_clusters) clusters = max_clusters;
   p.raster = g_raster;
+  // decode-sized problems stream the weights from DRAM once: request them into L2 ahead of the loads
+  p.l2_prefetch = g_l2_prefetch >= 0 ? g_l2_prefetch : (p.tiles_m <= 4 ? 16 : 0);
   gemm_bf16_2cta_kernel<<<2 * clusters, G2_THREADS, G2_SMEM_BYTES, stream>>>(ta, tb, p);
   return B200_CHECK_LAUNCH();
 }
@@ -630,6 +650,12 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* W, void* C, const vo
   p.status = status;
   p.swiglu = swiglu;
   return launch_2cta(A, W, p, lda, ldw, M, stream);
+}
+
+// Distance (k-blocks) of the L2 prefetch for every following call; -1 = choose per problem, 0 = off.
+B200_API int b200_gemm_2cta_set_l2_prefetch(int kblocks) {
+  g_l2_prefetch = kblocks;
+  return 0;
 }
 
 // Fixed tile width of the paired-CTA kernel for every following call (0 = choose per problem).

@@ -74,9 +74,30 @@ __global__ void argmax_kernel(const T* __restrict__ logits, long ld, int V,
   const T* row = logits + (long)blockIdx.x * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  int done = 0;                        // elements [0, done) are covered by the vector loop
+  if constexpr (sizeof(T) == 2) {
+    // 16-byte loads (8 logits) when the row starts on a 16-byte boundary; a thread walks its
+    // chunks in ascending index order, so "first maximum wins" still holds per thread
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const int nvec = V >> 3;
+      const uint4* rv = reinterpret_cast<const uint4*>(row);
+      for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+        const uint4 q = rv[c];
+        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const float lo = __uint_as_float(w4[k] << 16);
+          const float hi = __uint_as_float(w4[k] & 0xffff0000u);
+          if (lo > best) { best = lo; bi = c * 8 + 2 * k; }
+          if (hi > best) { best = hi; bi = c * 8 + 2 * k + 1; }
+        }
+      }
+      done = nvec << 3;
+    }
+  }
+  for (int i = done + threadIdx.x; i < V; i += blockDim.x) {
     const float v = ld_logit<T>(row, i);
-    if (v > best) { best = v; bi = i; }
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
   }
   block_argmax(best, bi, sv, si);
   if (threadIdx.x == 0) out[blockIdx.x] = bi;

@@ -233,6 +233,10 @@ class MLAAttention:
         w = self.kv_b_proj.weight.view(self.H, self.dn + self.dv, self.dc)
         self.W_UK = w[:, :self.dn, :].contiguous()                        # [H, dn, dc]
         self.W_UV = w[:, self.dn:, :].transpose(1, 2).contiguous()        # [H, dc, dv]
+        # the same matrices as [out, in] per head: operands of the grouped (one group per head) GEMM
+        self.W_UK_nk = self.W_UK.transpose(1, 2).contiguous()             # [H, dc, dn]
+        self.W_UV_nk = w[:, self.dn:, :].contiguous()                     # [H, dv, dc]
+        self._head_offsets = None
 
     def __call__(self, x: torch.Tensor, meta, kv_cache) -> torch.Tensor:
         T = x.shape[0]
@@ -244,30 +248,56 @@ class MLAAttention:
             qr = None
         q = q.view(T, self.H, self.dn + self.dr)
         kv = self.kv_a_proj(x)
-        latent = self.kv_a_norm(kv[:, :self.dc].contiguous())[0]
-        k_pe = kv[:, self.dc:].reshape(T, 1, self.dr)
-        q_pe = ref.apply_rope_interleaved(q[..., self.dn:], meta.positions, self.cos_sin, self.dr)
-        k_pe = ref.apply_rope_interleaved(k_pe, meta.positions, self.cos_sin, self.dr)
         lat_cache, pe_cache = kv_cache[0], kv_cache[1]
         from ..attention import mla as mla_ops
-        if self.offload is None:
-            mla_ops.write_latent_cache(latent, k_pe.view(T, self.dr), lat_cache, pe_cache,
-                                       meta.slot_mapping)
-        else:       # host-resident KV: the rows of this step's tokens go to the sequence's host store
-            self.offload.append(meta.extra["tok_rows"], meta.extra["positions_cpu"], latent, k_pe.view(T, self.dr))
+        if self.offload is None and not self.kv_a_norm.gemma:
+            # one pass: latent RMSNorm + rope of the shared key -> their cache slots, rope of every
+            # query head in place
+            ops.mla_preprocess(q, kv, self.kv_a_norm.weight, self.kv_a_norm.eps, meta.positions, self.cos_sin,
+                               meta.slot_mapping, lat_cache, pe_cache, self.dn, self.dr)
+            q_pe = q[..., self.dn:]
+        else:
+            latent = self.kv_a_norm(kv[:, :self.dc].contiguous())[0]
+            k_pe = kv[:, self.dc:].reshape(T, 1, self.dr)
+            q_pe = ref.apply_rope_interleaved(q[..., self.dn:], meta.positions, self.cos_sin, self.dr)
+            k_pe = ref.apply_rope_interleaved(k_pe, meta.positions, self.cos_sin, self.dr)
+            if self.offload is None:
+                mla_ops.write_latent_cache(latent, k_pe.view(T, self.dr), lat_cache, pe_cache, meta.slot_mapping)
+            else:   # host-resident KV: the rows of this step's tokens go to the sequence's host store
+                self.offload.append(meta.extra["tok_rows"], meta.extra["positions_cpu"], latent,
+                                    k_pe.view(T, self.dr))
         # absorb W_UK into q: [T,H,dn] x [H,dn,dc] -> [T,H,dc]
-        q_lat = torch.einsum("thd,hdc->thc", q[..., :self.dn], self.W_UK.to(q.dtype))
+        q_lat = self._per_head_matmul(q[..., :self.dn], self.W_UK, self.W_UK_nk)
         dcp = pstate.get_dcp_group()
         if self.index_topk:
-            o_lat = self._sparse_attention(x, qr, q_lat, q_pe, lat_cache, pe_cache, kv_cache[2], meta)
+            o_lat = self._sparse_attention(x, qr, q_lat.contiguous(), q_pe.contiguous(), lat_cache, pe_cache,
+                                           kv_cache[2], meta)
         elif dcp.world_size > 1:
             from ..attention.dcp import mla_attention_dcp
             o_lat = mla_attention_dcp(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale, dcp,
                                       getattr(meta, "dcp_interleave", 1))
         else:
             o_lat = mla_ops.mla_paged_attention(q_lat, q_pe, lat_cache, pe_cache, meta, self.scale)
-        o = torch.einsum("thc,hcv->thv", o_lat, self.W_UV.to(o_lat.dtype))
+        o = self._per_head_matmul(o_lat, self.W_UV, self.W_UV_nk)
         return self.o_proj(o.reshape(T, self.H * self.dv))
+
+    def _per_head_matmul(self, x: torch.Tensor, w_kn: torch.Tensor, w_nk: torch.Tensor) -> torch.Tensor:
+        """x [T, H, K] times one [K, N] matrix per head -> [T, H, N] (the two weight absorptions of MLA:
+        W_UK into the query, W_UV out of the latent result).  On the GPU the heads are the groups of the
+        grouped tcgen05 GEMM: rows are laid out head-major, every head's T rows meet that head's matrix
+        (the reference has a dedicated op for this product, csrc/batch_matmul_transpose/)."""
+        T, H, K = x.shape
+        N = w_nk.shape[1]
+        from ..ops import moe_native
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and moe_native.available()
+                and K % 8 == 0 and N % 8 == 0 and H <= 256 and T > 0):
+            return torch.einsum("thk,hkn->thn", x, w_kn.to(x.dtype))
+        if self._head_offsets is None or self._head_offsets[0] != T:
+            off = torch.arange(0, H + 1, dtype=torch.int32, device=x.device) * T
+            self._head_offsets = (T, off)
+        rows = x.transpose(0, 1).contiguous().view(H * T, K)             # head-major rows
+        out = moe_native.grouped_gemm(rows, w_nk, self._head_offsets[1], False)      # [H * T, N]
+        return out.view(H, T, N).transpose(0, 1)
 
     def _sparse_attention(self, x, qr, q_lat, q_pe, lat_cache, pe_cache, idx_cache, meta):
         """Indexer scores -> top-k key positions per query -> MLA attention over those keys.

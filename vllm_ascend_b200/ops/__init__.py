@@ -514,6 +514,45 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                meta.block_table, scale, causal, window, out=out)
 
 
+def mla_preprocess(q: torch.Tensor, kv: torch.Tensor, norm_w: torch.Tensor, eps: float, positions: torch.Tensor,
+                   cos_sin: torch.Tensor, slot_mapping: Optional[torch.Tensor], lat_cache: Optional[torch.Tensor],
+                   pe_cache: Optional[torch.Tensor], dn: int, dr: int, want_outputs: bool = False):
+    """Fused MLA pre-processing: RMSNorm of the latent part of ``kv`` [T, dc + dr] and interleaved RoPE
+    of its rope part, both scattered into their paged caches at ``slot_mapping`` (slot < 0: skipped);
+    interleaved RoPE of the last ``dr`` columns of every head of ``q`` [T, H, dn + dr] in place.
+    Returns (latent [T, dc], k_pe [T, dr]) when ``want_outputs`` else None."""
+    T, H, D = q.shape
+    dc = kv.shape[1] - dr
+    native = (_use_native(q) and kv.dtype == _BF16 and q.stride(2) == 1 and q.stride(1) == D and kv.stride(1) == 1
+              and cos_sin.dtype == torch.float32 and cos_sin.shape[1] == dr and dn % 2 == 0 and dr % 2 == 0
+              and q.stride(0) % 2 == 0
+              and (lat_cache is None or (lat_cache.dtype == _BF16 and lat_cache.is_contiguous()
+                                         and pe_cache.is_contiguous())))
+    if not native:
+        latent = ref.rms_norm(kv[:, :dc].contiguous(), norm_w, eps)[0]
+        k_pe = ref.apply_rope_interleaved(kv[:, dc:].reshape(T, 1, dr), positions, cos_sin, dr).view(T, dr)
+        q[..., dn:] = ref.apply_rope_interleaved(q[..., dn:], positions, cos_sin, dr)
+        if slot_mapping is not None and lat_cache is not None:
+            valid = (slot_mapping >= 0).unsqueeze(-1)
+            idx = slot_mapping.clamp(min=0)
+            lf, pf_ = lat_cache.view(-1, dc), pe_cache.view(-1, dr)
+            lf.index_copy_(0, idx, torch.where(valid, latent.to(lf.dtype), lf[idx]))
+            pf_.index_copy_(0, idx, torch.where(valid, k_pe.to(pf_.dtype), pf_[idx]))
+        return (latent, k_pe) if want_outputs else None
+    latent = torch.empty((T, dc), dtype=q.dtype, device=q.device) if want_outputs else None
+    k_pe = torch.empty((T, dr), dtype=q.dtype, device=q.device) if want_outputs else None
+    num_slots = 0 if lat_cache is None else lat_cache.numel() // dc
+    use_slots = slot_mapping is not None and lat_cache is not None
+    rc = _native.lib().b200_mla_preprocess(
+        q.data_ptr(), q.stride(0), T, H, dn, dr, kv.data_ptr(), kv.stride(0), dc, norm_w.data_ptr(), float(eps),
+        positions.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[0], _native.ptr(slot_mapping) if use_slots else None,
+        _native.ptr(lat_cache), _native.ptr(pe_cache), num_slots, _native.ptr(latent), _native.ptr(k_pe),
+        _native.status_word(q.device).data_ptr(), _native.stream_ptr())
+    _native.check(rc, "mla_preprocess")
+    launch_counter[0] += 1
+    return (latent, k_pe) if want_outputs else None
+
+
 # ---------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     if not logits.is_cuda or logits.dtype not in (_BF16, torch.float32):
