@@ -52,7 +52,7 @@ REFERENCE_CLASS = "upstream vLLM 0.22 CUDA build (the reference project itself r
 #: output tok/s of upstream vLLM 0.22 on one B200 box, same workload (``--impl reference``);
 #: keyed by (model, mode, n_gpus).  ``vs_baseline`` divides by these; None where nothing was measured.
 UPSTREAM_VLLM_B200 = {
-    ("qwen3-8b", "offline", 1): 10287.2,
+    ("qwen3-8b", "offline", 1): 10622.2,
 }
 
 #: HF ``config.json`` contents of the benchmark architectures (random-init weights of these shapes).

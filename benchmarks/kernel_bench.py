@@ -93,7 +93,7 @@ def bench_gemm(a):
     _native.register_signature("b200_gemm_2cta_set_bn", [ctypes.c_int])
     _native.lib().b200_gemm_2cta_set_bn(a.tile_n)       # 0: the kernel chooses its tile width
     _native.register_signature("b200_gemm_2cta_set_l2_prefetch", [ctypes.c_int])
-    _native.lib().b200_gemm_2cta_set_l2_prefetch(a.l2_prefetch)      # -1: per problem
+    _native.lib().b200_gemm_2cta_set_l2_prefetch(a.l2_prefetch)      # 0: off
     ms = timeit(lambda: ops.linear(x, w, out=out, bn=a.bn), a.iters, flush=not a.no_flush)
     ms_lib = timeit(lambda: torch.nn.functional.linear(x, w), a.iters, flush=not a.no_flush) if a.compare else None
     hbm, tf, tag = peaks()
@@ -360,8 +360,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "gemm-fp8", "gemm-folded", "attn-decode", "attn-prefill", "mla-decode", "gdn",
                                      "norm", "rope", "sampler", "moe", "kv-copy", "all"])
-    ap.add_argument("--l2-prefetch", type=int, default=-1,
-                    help="paired-CTA GEMM: k-blocks the L2 prefetch runs ahead (-1 per problem, 0 off)")
+    ap.add_argument("--l2-prefetch", type=int, default=0,
+                    help="paired-CTA GEMM: k-blocks the L2 prefetch runs ahead (0 = off)")
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--blocks", type=int, default=2048)

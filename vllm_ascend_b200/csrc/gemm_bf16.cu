@@ -164,11 +164,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     *abort_word = 0;
     mbar_fence_init();
     if (p.mode & GEMM_GROUPED) {
+      // offsets come from device memory the caller filled: a table that is not ascending inside
+      // [0, M] (stale or overwritten) is reported and yields no tiles instead of addresses
       int acc = 0;
+      bool ok = p.group_offsets[0] >= 0;
       for (int e = 0; e < p.num_groups; e++) {
         grp_tiles[e] = acc;
-        const int cnt = p.group_offsets[e + 1] - p.group_offsets[e];
+        const int g0 = p.group_offsets[e], g1 = p.group_offsets[e + 1];
+        if (g1 < g0 || g1 > p.M) ok = false;
+        const int cnt = ok ? g1 - g0 : 0;
         acc += (cnt + GEMM_BM - 1) / GEMM_BM;
+      }
+      if (!ok) {
+        for (int e = 0; e <= p.num_groups; e++) grp_tiles[e] = 0;
+        acc = 0;
+        if (p.status) atomicCAS(p.status, 0, B200_BAD_INDEX);
       }
       grp_tiles[p.num_groups] = acc;
     }

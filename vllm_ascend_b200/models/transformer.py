@@ -165,6 +165,9 @@ class SparseMoeBlock:
 
 
 # ---------------------------------------------------------------- MLA attention
+_HEAD_OFFSETS: dict = {}       # (device, heads, tokens) -> int32 group offsets of the per-head grouped GEMM
+
+
 class MLAAttention:
     """Multi-head latent attention with absorbed weights.
 
@@ -236,7 +239,6 @@ class MLAAttention:
         # the same matrices as [out, in] per head: operands of the grouped (one group per head) GEMM
         self.W_UK_nk = self.W_UK.transpose(1, 2).contiguous()             # [H, dc, dn]
         self.W_UV_nk = w[:, self.dn:, :].contiguous()                     # [H, dv, dc]
-        self._head_offsets = None
 
     def __call__(self, x: torch.Tensor, meta, kv_cache) -> torch.Tensor:
         T = x.shape[0]
@@ -292,11 +294,15 @@ class MLAAttention:
         if not (x.is_cuda and x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and moe_native.available()
                 and K % 8 == 0 and N % 8 == 0 and H <= 256 and T > 0):
             return torch.einsum("thk,hkn->thn", x, w_kn.to(x.dtype))
-        if self._head_offsets is None or self._head_offsets[0] != T:
+        # group offsets per token count, kept for the life of the process: a captured graph keeps
+        # reading the tensor it was recorded with
+        key = (x.device, H, T)
+        off = _HEAD_OFFSETS.get(key)
+        if off is None:
             off = torch.arange(0, H + 1, dtype=torch.int32, device=x.device) * T
-            self._head_offsets = (T, off)
+            _HEAD_OFFSETS[key] = off
         rows = x.transpose(0, 1).contiguous().view(H * T, K)             # head-major rows
-        out = moe_native.grouped_gemm(rows, w_nk, self._head_offsets[1], False)      # [H * T, N]
+        out = moe_native.grouped_gemm(rows, w_nk, off, False)            # [H * T, N]
         return out.view(H, T, N).transpose(0, 1)
 
     def _sparse_attention(self, x, qr, q_lat, q_pe, lat_cache, pe_cache, idx_cache, meta):
