@@ -229,8 +229,9 @@ def pp_generate():
 
 
 def sleep_wake():
-    """Sleep mode on NCCL ranks with the extra cleanup: graphs dropped and the model-parallel
-    communicators destroyed on sleep, re-created into the same coordinators on wake-up."""
+    """Sleep mode on NCCL ranks with the extra cleanup asked for: graphs are dropped and re-captured
+    around the sleep; NCCL communicators stay (destroy / re-create is done for host-side groups only,
+    tested on gloo ranks)."""
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
     world = int(os.environ["WORLD_SIZE"])

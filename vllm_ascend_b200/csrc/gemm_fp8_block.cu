@@ -10,8 +10,11 @@
 //   warp 0      TMA producer: 128 x 128 e4m3 tiles of A and W (one 128-byte swizzle row each)
 //   warp 1      tcgen05.mma kind::f8f6f4 (M=128, N=128, K=32 x 4) per K block into one of two
 //               TMEM partial buffers (fresh accumulator every block)
-//   warps 2..5  read the partial with tcgen05.ld, scale it by a_scale * w_scale and add it to
-//               fp32 accumulators held in registers (128 per thread); store bf16 at the end
+//   warps 2..9  read the partial with tcgen05.ld, scale it by a_scale * w_scale and add it to
+//               fp32 accumulators held in registers; store bf16 at the end.  Two warpgroups
+//               split the tile's 128 columns (64 accumulators per thread, both TMEM loads of a
+//               K block in flight before the one wait): the promotion of a block has to keep up
+//               with its MMA, which four warps with 128 accumulators each did not
 // The MMA of block kb+1 overlaps the promotion of block kb.  Grouped mode (MoE experts)
 // uses per-group row offsets and per-expert weight / scale matrices.  Bounded waits.
 #include "common.cuh"
@@ -22,7 +25,8 @@
 namespace b200 {
 
 constexpr int F8_BM = 128, F8_BN = 128, F8_BK = 128;
-constexpr int F8_THREADS = 192;
+constexpr int F8_THREADS = 320;            // producer, MMA issuer, 2 x 4 promotion warps
+constexpr int F8_HALF = F8_BN / 2;         // columns per promotion warpgroup
 constexpr int F8_STAGES = 6;
 constexpr int F8_TILE_BYTES = 128 * 128;                 // 16 KB per operand tile
 constexpr int F8_STAGE_BYTES = 2 * F8_TILE_BYTES;
@@ -101,15 +105,24 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&part_full[b], 1);
-      mbar_init(&part_empty[b], 4);
+      mbar_init(&part_empty[b], 8);
     }
     *abort_word = 0;
     mbar_fence_init();
     if (p.num_groups > 0) {
+      // a table that is not ascending inside [0, M] is reported and yields no tiles
       int acc = 0;
+      bool ok = p.group_offsets[0] >= 0;
       for (int e = 0; e < p.num_groups; e++) {
         grp_tiles[e] = acc;
-        acc += (p.group_offsets[e + 1] - p.group_offsets[e] + F8_BM - 1) / F8_BM;
+        const int g0 = p.group_offsets[e], g1 = p.group_offsets[e + 1];
+        if (g1 < g0 || g1 > p.M) ok = false;
+        acc += ok ? (g1 - g0 + F8_BM - 1) / F8_BM : 0;
+      }
+      if (!ok) {
+        for (int e = 0; e <= p.num_groups; e++) grp_tiles[e] = 0;
+        acc = 0;
+        if (p.status) atomicCAS(p.status, 0, B200_BAD_INDEX);
       }
       grp_tiles[p.num_groups] = acc;
     }
@@ -177,7 +190,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------------------------------------------ promotion + epilogue
-    const int q = warp & 3;
+    const int q = warp & 3;                              // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;                    // which 64 columns of the tile
     const int kblocks = p.K / F8_BK;                     // columns of the scale matrices
     const int n_blocks = (p.N + F8_BN - 1) / F8_BN;
     uint32_t it = 0;
@@ -189,9 +203,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool per_channel = p.row_scale != nullptr;
       const float* as_row = per_channel ? nullptr : p.a_scale + (size_t)(row_ok ? row : 0) * kblocks;
       const float* ws_row = per_channel ? nullptr : p.w_scale + ((size_t)c.group * n_blocks + c.tn) * kblocks;
-      float acc[F8_BN];
+      float acc[F8_HALF];
 #pragma unroll
-      for (int i = 0; i < F8_BN; i++) acc[i] = 0.f;
+      for (int i = 0; i < F8_HALF; i++) acc[i] = 0.f;
       float sc_next = per_channel ? 1.f : as_row[0] * ws_row[0];
       for (int kb = 0; kb < num_kb; kb++, it++) {
         const int b = it & 1;
@@ -199,26 +213,27 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!per_channel && kb + 1 < num_kb) sc_next = as_row[kb + 1] * ws_row[kb + 1];
         if (!mbar_wait(&part_full[b], (it >> 1) & 1u, abort_word)) goto done;
         tc_fence_after();
-        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * F8_BN;
-#pragma unroll
-        for (int c0 = 0; c0 < F8_BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_row + c0, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; i++) acc[c0 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c0 + i]);
-        }
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * F8_BN + half * F8_HALF;
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(t_row, r0);
+        tmem_ld_32x32b_x32(t_row + 32, r1);
+        tmem_ld_wait();
+        // the partial is in registers: the MMA warp may overwrite the buffer
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&part_empty[b]);
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[i] = fmaf(__uint_as_float(r0[i]), sc, acc[i]);
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[32 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[32 + i]);
       }
       if (row_ok) {
         __nv_bfloat16* crow = p.C + (size_t)row * p.ldc;
         const float rs = per_channel ? p.row_scale[row] : 1.f;
         const float* cs = per_channel ? p.col_scale + (size_t)c.group * p.N : nullptr;
 #pragma unroll
-        for (int g = 0; g < F8_BN / 8; g++) {
-          const int col = c.tn * F8_BN + g * 8;
+        for (int g = 0; g < F8_HALF / 8; g++) {
+          const int col = c.tn * F8_BN + half * F8_HALF + g * 8;
           if (col < p.N) {
             float v[8];
 #pragma unroll

@@ -19,6 +19,8 @@ from typing import Optional, Sequence
 import torch
 import torch.distributed as dist
 
+from ..logger import logger
+
 
 @dataclass
 class GroupCoordinator:
@@ -211,6 +213,11 @@ def suspend_groups() -> int:
     the allocator releases memory and re-creates them on wake-up)."""
     global _SUSPENDED
     if _SUSPENDED:
+        return 0
+    if any(b == "nccl" for _, _, _, b, _ in _RECORDS):
+        # NCCL communicators are kept: on two B200s a wake-up after destroying and re-creating them
+        # did not return (twice, cause not found); their buffers are small next to weights and KV
+        logger.warning("sleep: NCCL communicators are kept (destroy / re-create is limited to host-side groups)")
         return 0
     n = 0
     for mine, _, _, _, _ in _RECORDS:
