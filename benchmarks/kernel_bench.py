@@ -356,10 +356,61 @@ def bench_gemm_folded(a):
     _native.check_status(torch.device("cuda"))
 
 
+def bench_quant(a):
+    """Producers of the fp8 GEMM's activation operand: add + RMSNorm + 1x128 quant, SiLU-mul + quant."""
+    T, H, I = a.tokens, a.hidden, a.inter
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    r = torch.randn(T, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda").bfloat16()
+    hbm, tf, tag = peaks()
+    ms = timeit(lambda: ops.rms_norm_quant_fp8(x, w, 1e-6, r), a.iters)
+    by = T * H * (2 + 2 + 2 + 1) + T * (H // 128) * 4.0          # x, residual in / residual out, fp8 out, scales
+    print(f"add+rmsnorm+quant T={T} H={H}: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s ({by / ms / 1e6 / hbm:.2f} {tag})")
+    g = torch.randn(T, 2 * I, device="cuda").bfloat16()
+    ms = timeit(lambda: ops.silu_and_mul_quant_fp8(g), a.iters)
+    by = T * I * (4 + 1) + T * (I // 128) * 4.0
+    print(f"silu_mul+quant T={T} I={I}: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s ({by / ms / 1e6 / hbm:.2f} {tag})")
+    ms = timeit(lambda: ops.quant_fp8_group128(x), a.iters)
+    by = T * H * 3 + T * (H // 128) * 4.0
+    print(f"quant 1x128 T={T} H={H}: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s ({by / ms / 1e6 / hbm:.2f} {tag})", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
+def bench_moe_route(a):
+    """Router top-k (softmax scoring, renormalised) over the expert logits."""
+    from vllm_ascend_b200.ops import moe_native
+    T, E, k = a.tokens, a.experts, a.topk
+    logits = torch.randn(T, E, device="cuda")
+    ms = timeit(lambda: moe_native.gating_topk(logits, k, "softmax", True, 1, 1, None, 1.0), a.iters)
+    print(f"moe gating top-{k} T={T} E={E}: {ms:.4f} ms  {T * E * 4 / ms / 1e6:.0f} GB/s of logits", flush=True)
+
+
+def bench_mla_pre(a):
+    """Fused MLA pre-process (latent norm + rope key + cache scatter + query rope), DeepSeek-V3 head geometry."""
+    from vllm_ascend_b200.ops import reference as ref
+    T, H, dn, dr, dc = a.tokens, a.heads, 128, 64, 512
+    q = torch.randn(T, H, dn + dr, device="cuda").bfloat16()
+    kv = torch.randn(T, dc + dr, device="cuda").bfloat16()
+    w = torch.ones(dc, device="cuda").bfloat16()
+    pos = torch.arange(T, device="cuda") % 4096
+    cs = ref.build_cos_sin_cache(dr, 8192, 1e4, None, torch.device("cuda"))
+    nb = (T + 127) // 128 + 1
+    lat = torch.zeros(nb, 128, 1, dc, device="cuda", dtype=torch.bfloat16)
+    pe = torch.zeros(nb, 128, 1, dr, device="cuda", dtype=torch.bfloat16)
+    slots = torch.arange(T, device="cuda") + 128
+    hbm, tf, tag = peaks()
+    ms = timeit(lambda: ops.mla_preprocess(q, kv, w, 1e-6, pos, cs, slots, lat, pe, dn, dr), a.iters)
+    by = T * (2.0 * H * dr * 2 + (dc + dr) * 2 * 2)
+    print(f"mla preprocess T={T} H={H}: {ms:.4f} ms  {by / ms / 1e6:.0f} GB/s of touched bytes "
+          f"({by / ms / 1e6 / hbm:.2f} {tag})", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "gemm-fp8", "gemm-folded", "attn-decode", "attn-prefill", "mla-decode", "gdn",
-                                     "norm", "rope", "sampler", "moe", "kv-copy", "all"])
+                                     "norm", "rope", "sampler", "moe", "kv-copy", "quant", "moe-route", "mla-pre", "all"])
+    ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--l2-prefetch", type=int, default=0,
                     help="paired-CTA GEMM: k-blocks the L2 prefetch runs ahead (0 = off)")
     ap.add_argument("--vocab", type=int, default=151936)
@@ -402,6 +453,12 @@ def main():
                 bench_gemm(a)
         else:
             bench_gemm(a)
+    if a.what == "quant":
+        bench_quant(a)
+    if a.what == "moe-route":
+        bench_moe_route(a)
+    if a.what == "mla-pre":
+        bench_mla_pre(a)
     if a.what == "rope":
         bench_rope(a)
     if a.what == "sampler":

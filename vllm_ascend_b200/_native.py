@@ -45,6 +45,7 @@ _SIGNATURES = {
     "b200_attn_decode_tc": [P, L, L, P, P, L, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, P, P],
     "b200_attn_decode_tc_lse": [P, L, L, P, P, L, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, P, P, P],
     "b200_merge_attn_partials": [P, P, L, I, I, I, P, L, P, P],
+    "b200_attn_decode_set_l2_prefetch": [I],
     "b200_mla_preprocess": [P, L, I, I, I, I, P, L, I, P, F, P, P, L, P, P, P, L, P, P, P, P],
     "b200_argmax": [P, I, L, I, I, P, P],
     "b200_cast_bf16_f32": [P, L, P, L, I, I, P],

@@ -47,6 +47,7 @@ struct DecParams {
   long num_blocks_total;
   int num_seqs, num_items;   // items = Hkv x sequences x splits
   int tail_loads;            // 1: the last tile of a sequence is loaded in 32-key pieces (pages >= 128 keys)
+  int l2_prefetch;           // tiles the L2 prefetch of K / V runs ahead of the staged loads (0 = off)
   int* status;
   long long* timeline;   // optional [3 roles][64 tiles][8 stamps] of clock64, CTA 0 only
 };
@@ -285,6 +286,20 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t ph = (gt / ST) & 1u;
         const int key_base = (w.t0 + j) << 7;
         const int blk_next = load_blk(j + 1);
+        if (p.l2_prefetch > 0 && j + p.l2_prefetch < w.n) {
+          // ask for a later tile's pages in L2 now: the bytes in flight towards shared memory are
+          // bounded by the stage ring, requests towards L2 are not
+          const int jp = j + p.l2_prefetch;
+          const int blk_pf = load_blk(jp);
+          if (lane < parts && blk_pf >= 0 && blk_pf < p.num_blocks_total) {
+            const int off = (((w.t0 + jp) << 7) + lane * rpl) % p.block_size;
+#pragma unroll
+            for (int hf = 0; hf < NH; hf++) {
+              tma_prefetch_l2_4d(&tmap_k, hf * 64, w.h, off, blk_pf);
+              tma_prefetch_l2_4d(&tmap_v, hf * 64, w.h, off, blk_pf);
+            }
+          }
+        }
         bool bad = blk_cur < 0 || blk_cur >= p.num_blocks_total;
         bad = __any_sync(0xffffffffu, bad && lane < parts);
 #pragma unroll 1
@@ -647,8 +662,15 @@ struct DecTmapCache {
   }
 };
 static DecTmapCache g_dec_tmaps;
+static int g_dec_l2_prefetch = 0;      // tiles of L2 prefetch ahead of the staged K / V loads (0 = off)
 
 }  // namespace b200
+
+// Distance (128-key tiles) of the L2 prefetch of K / V pages for every following call; 0 = off.
+B200_API int b200_attn_decode_set_l2_prefetch(int tiles) {
+  b200::g_dec_l2_prefetch = tiles < 0 ? 0 : (tiles > 16 ? 16 : tiles);
+  return 0;
+}
 
 // Decode / short-query attention: every sequence has q_len <= 16 / (Hq/Hkv) query
 // tokens (query_start_loc gives their positions in q).  Arguments as b200_attn_fwd_tc;
@@ -731,6 +753,7 @@ B200_API int b200_attn_decode_tc_lse(const void* q, long q_stride, long T, const
   if (items > 0x7fffffffL) return 9125;
   p.num_seqs = num_seqs;
   p.tail_loads = rpl == 128 ? 1 : 0;
+  p.l2_prefetch = g_dec_l2_prefetch;
   p.num_items = (int)items;
   static int sm_count[64] = {};
   int dev = 0;

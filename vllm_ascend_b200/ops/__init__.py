@@ -335,6 +335,9 @@ def paged_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     return out
 
 
+_dec_prefetch_set = None
+
+
 def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta,
                               scale: float, out: torch.Tensor, window: int = 0,
                               num_splits: int = 1, num_seqs: Optional[int] = None,
@@ -349,6 +352,10 @@ def paged_attention_decode_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
     if num_seqs is None:
         num_seqs = meta.num_reqs
     NB, BS, Hkv, _ = k_cache.shape
+    global _dec_prefetch_set
+    if _dec_prefetch_set != envs.VLLM_B200_DECODE_L2_PREFETCH:
+        _dec_prefetch_set = envs.VLLM_B200_DECODE_L2_PREFETCH
+        _native.lib().b200_attn_decode_set_l2_prefetch(int(_dec_prefetch_set))
     scratch = None
     if num_splits > 1:
         scratch = _get_scratch(q.device, T * Hq * num_splits * (D + 1) * 4)
