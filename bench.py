@@ -556,7 +556,18 @@ def main():
                str(29500 + os.getpid() % 400), os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
     if args.impl in ("reference", "vllm"):
-        run_reference(args, rank, world, local)
+        try:
+            run_reference(args, rank, world, local)
+        except SystemExit:
+            raise
+        except BaseException as e:  # noqa: BLE001 - the arm must leave a line behind, whatever failed
+            import traceback
+            traceback.print_exc()
+            print(json.dumps({"impl": "reference", "reference_class": REFERENCE_CLASS, "n_gpus": world,
+                              "unavailable": f"upstream vLLM failed at run time on rank {rank}: "
+                                             f"{type(e).__name__}: {e}"[:400]}), flush=True)
+            # a non-zero status lets the launcher stop the other ranks instead of leaving them in a collective
+            os._exit(0 if world == 1 else 3)
     elif args.mode == "pd":
         sys.path.insert(0, REPO)
         from benchmarks.pd_bench import run_pd

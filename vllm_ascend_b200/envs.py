@@ -50,8 +50,11 @@ env_variables: dict[str, Callable[[], Any]] = {
     "VLLM_B200_DEVICE_SLOT_MAPPING": _str("VLLM_B200_DEVICE_SLOT_MAPPING", "0"),
     # fused TP path and NVSwitch multicast memory: "auto" pushes the all-gather rows with multimem.st
     # when the platform offers multicast, "full" also sums the partials in the switch
-    # (multimem.ld_reduce), "0" uses peer loads / stores only
+    # (multimem.ld_reduce), "push" forces the multicast push at any group size, "0" uses peer loads /
+    # stores only
     "VLLM_B200_NVLS": _str("VLLM_B200_NVLS", "auto"),
+    # "auto" uses multicast up to this many ranks per TP group ("push" / "full" force it at any size)
+    "VLLM_B200_NVLS_AUTO_MAX_RANKS": _int("VLLM_B200_NVLS_AUTO_MAX_RANKS", 2),
     # MoE path override: "", "allgather", "alltoall", "fused"
     "VLLM_B200_MOE_COMM": _str("VLLM_B200_MOE_COMM", ""),
     "VLLM_B200_ENABLE_NVLS": _bool("VLLM_B200_ENABLE_NVLS", "0"),

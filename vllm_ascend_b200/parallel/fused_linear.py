@@ -40,7 +40,10 @@ class FusedTPContext:
         self.max_tokens = self.max_rows_local * self.n
         nbytes = self.max_tokens * hidden * 2
         from .. import envs
-        self.symm = SymmetricMemory(group, device, 2 * nbytes + 4096, multicast=envs.VLLM_B200_NVLS != "0")
+        mode = envs.VLLM_B200_NVLS
+        if mode == "auto" and self.n > envs.VLLM_B200_NVLS_AUTO_MAX_RANKS:
+            mode = "0"          # group sizes the multicast path has not been validated on use peer stores
+        self.symm = SymmetricMemory(group, device, 2 * nbytes + 4096, multicast=mode != "0")
         self.off_ag = self.symm.region(nbytes)
         self.off_rs = self.symm.region(nbytes)
         # NVSwitch multicast (NVLS).  "push" (the default where multicast exists): the all-gather push
@@ -50,7 +53,6 @@ class FusedTPContext:
         # rank's own buffer and the owner sums them inside the switch (multimem.ld_reduce); that
         # moves the reduce-scatter traffic out of the GEMM into the (exposed) reduce kernel and
         # measured slower at TP2 (17.7k vs 18.1k tok/s on the Qwen3-8B workload).
-        mode = envs.VLLM_B200_NVLS
         self.nvls = self.symm.mc_ptr != 0 and mode != "0"
         self.nvls_full = self.nvls and mode == "full"
         self.mc_ag = self.symm.mc_ptr + self.off_ag if self.nvls else 0
