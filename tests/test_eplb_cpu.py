@@ -121,3 +121,46 @@ def test_engine_output_unchanged_while_experts_migrate(tmp_path):
     assert eplb["slots"] > 0 and os.path.exists(record)
     placement = em.load_placement(record)
     em.validate(placement, 8) if placement.max() < 8 else None
+
+
+def test_flash_policy_plans_for_the_window_not_the_last_sample_and_moves_little():
+    from vllm_ascend_b200.eplb.policy import FlashPolicy, lpt_deploy, minimize_redeploy, replica_counts
+    E, R, red = 16, 4, 4
+    place = em.initial_placement(1, E, R, red)
+    rng = np.random.default_rng(1)
+    base = np.ones(E) * 10
+    base[[2, 9]] = 120.0                               # two persistently hot experts
+    pol = FlashPolicy(threshold=1.05, fluctuation=0.01, window=6)
+    for _ in range(5):                                 # noisy samples around the same profile
+        pol.register_hotness(0, base * rng.uniform(0.8, 1.2, size=E))
+    spike = base.copy()
+    spike[5] = 400.0                                   # one outlier sample of a cold expert
+    new = pol.rebalance(place, spike[None])
+    em.validate(new, E)
+    counts = np.bincount(new[0].reshape(-1), minlength=E)
+    assert counts[2] >= 2 and counts[9] >= 2           # the persistently hot experts got the replicas
+    mu, var = pol.statistics(0, spike)
+    assert imbalance(new[0], mu) < imbalance(place[0], mu)
+    # replicas: spare slots go where the risk-adjusted unit load is largest, one copy per rank at most
+    r = replica_counts(np.array([100.0, 10.0, 10.0]), np.zeros(3), 6, 2, 0.674)
+    assert r.tolist() == [2, 2, 2] or r[0] == 2
+    assert replica_counts(np.array([100.0, 1.0, 1.0, 1.0]), np.zeros(4), 6, 3, 0.0).tolist() == [3, 1, 1, 1]
+    # LPT packing balances and never puts two copies on one rank
+    rows = lpt_deploy(np.array([50.0, 50.0, 10.0, 10.0, 10.0, 10.0]), np.array([2, 2, 1, 1, 1, 1]), 4, 2)
+    assert all(len(set(x)) == len(x) == 2 for x in rows)
+    # renaming keeps what can stay: the same sets in another rank order / slot order move nothing
+    old = np.array([[0, 1], [2, 3], [4, 5]])
+    same_sets = [[3, 2], [5, 4], [1, 0]]
+    assert (minimize_redeploy(old, same_sets) == old).all()
+    one_change = minimize_redeploy(old, [[4, 5], [0, 6], [2, 3]])
+    assert (one_change != old).sum() == 1 and one_change[0].tolist() == [0, 6]
+    # a balanced layer is left alone; the per-call layer limit holds
+    calm = FlashPolicy(threshold=1.5)
+    flat = np.ones((2, E))
+    p2 = em.initial_placement(2, E, R, red)
+    assert (calm.rebalance(p2, flat) == p2).all()
+    lim = FlashPolicy(threshold=1.01, fluctuation=0.0, max_layers_per_call=1)
+    skew = _skewed(3, E, seed=2)
+    p3 = em.initial_placement(3, E, R, red)
+    out = lim.rebalance(p3, skew)
+    assert sum(bool((out[l] != p3[l]).any()) for l in range(3)) <= 1

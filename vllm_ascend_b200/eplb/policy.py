@@ -11,8 +11,9 @@ same shape.  Policies (numbering of vllm_ascend/eplb/core/policy/policy_factory.
   2  swift           keep the current placement and apply at most ``max_swaps`` pairwise
                      swaps between the heaviest and lightest rank, so little weight moves
                      (policy_swift_balancer.py:510-751)
-  3  flash           per layer, re-plan only when the imbalance exceeds a threshold or moved
-                     by more than a fluctuation margin since the last plan (policy_flashlb.py)
+  3  flash           statistical: sliding-window mean / variance of the expert loads, replicas by
+                     risk-adjusted load per replica, longest-first packing, renaming that minimises
+                     weight movement, per-layer gating by predicted imbalance (policy_flashlb.py)
 """
 from __future__ import annotations
 
@@ -124,33 +125,154 @@ class SwiftPolicy(EplbPolicy):
         return p
 
 
-class FlashPolicy(EplbPolicy):
-    """Greedy re-plan gated per layer: skip layers that are balanced enough or whose imbalance
-    did not move since the last plan; limit how many layers change per call."""
+def replica_counts(mu: np.ndarray, var: np.ndarray, slots: int, max_per_expert: int, z: float) -> np.ndarray:
+    """Replicas per expert: every expert gets one, each spare slot goes to the expert whose
+    risk-adjusted load per replica ``(mu + z * sigma / sqrt(r)) / r`` is largest (a replica takes
+    1/r of the mean; tokens spread over replicas independently, so the spread of one replica's
+    share falls faster than the mean)."""
+    E = mu.shape[0]
+    r = np.ones(E, dtype=np.int64)
+    sd = np.sqrt(np.maximum(var, 0.0))
+    for _ in range(max(0, slots - E)):
+        unit = (mu + z * sd / np.sqrt(r)) / r
+        unit[r >= max_per_expert] = -np.inf
+        e = int(unit.argmax())
+        if not np.isfinite(unit[e]):
+            break
+        r[e] += 1
+    return r
 
-    def __init__(self, threshold: float = 1.15, fluctuation: float = 0.05, max_layers_per_call: Optional[int] = None):
+
+def lpt_deploy(unit: np.ndarray, replicas: np.ndarray, R: int, S: int) -> list[list[int]]:
+    """Longest-processing-time-first: replicas in descending unit load go to the least loaded
+    rank that has a free slot and no copy of the expert."""
+    items = sorted(((unit[e], e) for e in range(unit.shape[0]) for _ in range(int(replicas[e]))),
+                   key=lambda x: (-x[0], x[1]))
+    load = np.zeros(R)
+    rows: list[list[int]] = [[] for _ in range(R)]
+    for w, e in items:
+        order = np.argsort(load, kind="stable")
+        pick = next((r for r in order if len(rows[r]) < S and e not in rows[r]), None)
+        if pick is None:
+            pick = next(r for r in order if len(rows[r]) < S)
+        rows[pick].append(e)
+        load[pick] += w
+    return rows
+
+
+def minimize_redeploy(old: np.ndarray, rows: list[list[int]]) -> np.ndarray:
+    """Name the new rank-sets and order their slots so that as few expert weights as possible
+    move: ranks are matched to the new sets by maximum overlap (assignment problem), and inside a
+    rank an expert that stays keeps its slot (the reference solves the same matching before it
+    transfers weights, policy_flashlb.py:761-845)."""
+    R, S = old.shape
+    overlap = np.zeros((R, R), dtype=np.int64)
+    old_sets = [set(int(x) for x in old[r]) for r in range(R)]
+    for i in range(R):
+        for j in range(R):
+            overlap[i, j] = len(old_sets[i] & set(rows[j]))
+    try:
+        from scipy.optimize import linear_sum_assignment
+        ri, cj = linear_sum_assignment(-overlap)
+        match = dict(zip(ri.tolist(), cj.tolist()))
+    except Exception:                                    # greedy matching without scipy
+        match, used = {}, set()
+        for i in np.argsort(-overlap.max(axis=1)):
+            j = next(j for j in np.argsort(-overlap[i]) if j not in used)
+            match[int(i)] = int(j)
+            used.add(int(j))
+    out = np.full((R, S), -1, dtype=old.dtype)
+    for i in range(R):
+        want = list(rows[match[i]])
+        for s_ in range(S):                              # experts that stay keep their slot
+            e = int(old[i, s_])
+            if e in want:
+                out[i, s_] = e
+                want.remove(e)
+        for s_ in range(S):
+            if out[i, s_] < 0:
+                out[i, s_] = want.pop(0)
+    return out
+
+
+class FlashPolicy(EplbPolicy):
+    """Statistical re-planning, gated per layer.
+
+    Loads fluctuate from step to step, so a plan made for the last sample chases noise.  This
+    policy keeps a sliding window of load samples per layer and plans for the risk-adjusted load
+    ``mu + z * sigma`` of every expert: replicas go to the experts with the largest risk-adjusted
+    load per replica, replicas are packed longest-first onto the least loaded rank, and the result
+    is renamed to overlap the current placement as far as possible so that few weights move.  A
+    layer is re-planned only when its predicted imbalance exceeds ``threshold`` and the new plan
+    improves it by more than ``fluctuation``; at most ``max_layers_per_call`` layers change per
+    call (weight movement is paid for in serving time).
+
+    Approach of the reference's FlashLB (policy_flashlb.py:515-965: windowed hotness statistics,
+    z-score replica allocation, LPT deployment, redeploy minimisation, update gating)."""
+
+    def __init__(self, threshold: float = 1.15, fluctuation: float = 0.05, max_layers_per_call: Optional[int] = None,
+                 window: int = 8, z_score: float = 0.674):
         self.threshold, self.fluctuation = threshold, fluctuation
         self.max_layers = max_layers_per_call
-        self.inner = GreedyPolicy()
+        self.window, self.z = max(1, int(window)), float(z_score)
+        self.samples: dict[int, list] = {}
         self.last: dict[int, float] = {}
+        self.moved_slots = 0
+
+    # ---- statistics
+    def register_hotness(self, layer: int, load: np.ndarray) -> None:
+        buf = self.samples.setdefault(int(layer), [])
+        buf.append(np.asarray(load, dtype=np.float64))
+        if len(buf) > self.window:
+            del buf[0]
+
+    def statistics(self, layer: int, load: np.ndarray):
+        """(mean, variance) per expert over the window (the current sample alone when the window is empty)."""
+        buf = self.samples.get(int(layer))
+        if not buf:
+            x = np.asarray(load, dtype=np.float64)
+            return x, np.zeros_like(x)
+        X = np.stack(buf)
+        return X.mean(axis=0), X.var(axis=0)
+
+    def risk_load(self, layer: int, load: np.ndarray) -> np.ndarray:
+        mu, var = self.statistics(layer, load)
+        return mu + self.z * np.sqrt(var)
+
+    # ---- planning
+    def plan_layer(self, placement: np.ndarray, load: np.ndarray, layer: int = 0) -> np.ndarray:
+        R, S = placement.shape
+        mu, var = self.statistics(layer, load)
+        if R * S < mu.shape[0]:
+            raise ValueError("fewer expert slots than experts")
+        r = replica_counts(mu, var, R * S, R, self.z)
+        unit = (mu + self.z * np.sqrt(var) / np.sqrt(r)) / r
+        return minimize_redeploy(placement, lpt_deploy(unit, r, R, S))
 
     def rebalance(self, placement, load):
         L = placement.shape[0]
-        imb = np.array([imbalance(placement[l], load[l]) for l in range(L)])
-        todo = [l for l in np.argsort(-imb)
-                if imb[l] > self.threshold and abs(imb[l] - self.last.get(int(l), 0.0)) > self.fluctuation]
-        if self.max_layers is not None:
-            todo = todo[:self.max_layers]
+        for l in range(L):
+            self.register_hotness(l, load[l])
+        risk = [self.risk_load(l, load[l]) for l in range(L)]
+        imb = np.array([imbalance(placement[l], risk[l]) for l in range(L)])
+        todo = [int(l) for l in np.argsort(-imb) if imb[l] > self.threshold]
         out = placement.copy()
+        changed = 0
         for l in todo:
-            cand = self.inner.rebalance_layer(placement[l], load[l], int(l))
-            if imbalance(cand, load[l]) < imb[l]:
+            if self.max_layers is not None and changed >= self.max_layers:
+                break
+            cand = self.plan_layer(placement[l], load[l], l)
+            new_imb = imbalance(cand, risk[l])
+            if imb[l] - new_imb > self.fluctuation:
                 out[l] = cand
-            self.last[int(l)] = float(imbalance(out[l], load[l]))
+                self.moved_slots += int((cand != placement[l]).sum())
+                changed += 1
+            self.last[l] = float(imbalance(out[l], risk[l]))
         return out
 
     def rebalance_layer(self, placement, load, layer=0):
-        return self.rebalance(placement[None], load[None])[0]
+        self.register_hotness(layer, load)
+        return self.plan_layer(placement, load, layer)
 
 
 def make_policy(policy_type: int, **kw) -> EplbPolicy:
