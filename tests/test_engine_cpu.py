@@ -440,3 +440,51 @@ def test_prompt_logprobs_match_teacher_forcing_across_chunks():
             assert abs(plp[pos][t] - v) < 1e-4
     plain = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=2))
     assert plain[0].prompt_logprobs is None and plain[0].outputs[0].token_ids == out[0].outputs[0].token_ids
+
+
+def test_deferred_sampling_applies_an_allowed_token_mask():
+    """The forward pass and the sampling of a step can be separated: a constraint on the logits that
+    arrives after the forward was launched (a host engine's grammar bitmask) is applied before sampling."""
+    import torch
+    cfg = get_model_config("tiny-qwen")
+    llm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=64, block_size=16)
+    eng = llm.engine
+    prompts = _prompts(2, 12, cfg.vocab_size, seed=5)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    rids = [eng.add_request(p, sp) for p in prompts]
+    so = eng.scheduler.schedule()
+    h = eng.runner.execute_async(so, None, defer_sampling=True)
+    assert h.tokens is None and h.h_sel is not None
+    allowed = torch.zeros(cfg.vocab_size, dtype=torch.bool)
+    allowed[[5, 7, 300]] = True
+    logits = eng.runner.model.compute_logits(h.h_sel).float()
+    eng.runner.finish_sampling(h, {rids[0]: allowed})
+    assert h.h_sel is None and h.tokens is not None
+    sampled = eng.runner.collect(h)
+    i0 = h.index[rids[0]]
+    want0 = max((5, 7, 300), key=lambda t: float(logits[i0, t]))
+    assert sampled[rids[0]] == [want0]
+    assert sampled[rids[1]] == [int(logits[h.index[rids[1]]].argmax())]           # unconstrained row untouched
+    eng.scheduler.update_from_output(so, sampled)
+    # the engine carries on normally from there
+    while eng.has_unfinished():
+        eng.step()
+    assert all(len(eng.scheduler.requests[r].output_token_ids) == 4 for r in rids)
+
+
+def test_grammar_bitmask_rows_unpack_to_token_masks():
+    import numpy as np
+    import torch
+    from types import SimpleNamespace as NS
+    from vllm_ascend_b200.worker.vllm_worker import B200VllmWorker
+    w = B200VllmWorker.__new__(B200VllmWorker)
+    w.runner = NS(mcfg=NS(vocab_size=70))
+    w.device = torch.device("cpu")
+    bm = np.zeros((2, 3), dtype=np.int32)
+    bm[0, 0] = np.array([(1 << 3) | (1 << 31)], dtype=np.uint32).view(np.int32)[0]       # tokens 3 and 31
+    bm[0, 2] = 1 << 5                          # token 69
+    bm[1, 1] = -1                              # tokens 32..63
+    out = w._unpack_bitmask(["a", "b"], bm)
+    assert torch.nonzero(out["a"]).flatten().tolist() == [3, 31, 69]
+    assert torch.nonzero(out["b"]).flatten().tolist() == list(range(32, 64))
+    assert out["a"].shape == (70,)

@@ -52,6 +52,16 @@ def _check_common(r):
     assert all(len(t) > 0 for t in r["got"])
 
 
+def test_vllm_structured_outputs_reach_the_plugin_sampler_cpu(tmp_path):
+    """vLLM compiles the grammar and hands the worker one token bitmask per step; the worker runs the
+    forward pass, applies the bitmask to the rows of the constrained requests and samples."""
+    r = _run("", _model_dir(tmp_path, "float32"), "float32", "structured")
+    _check_common(r)
+    assert r["texts"][0] in r["choices"] and r["texts"][2] in r["choices"]
+    assert len(r["got"][1]) == 6 and len(r["got"][3]) == 6
+    assert [r["got"][1], r["got"][3]] == r["free_alone"]
+
+
 @pytest.mark.parametrize("mode", ["sync", "async"])
 def test_vllm_llm_runs_on_the_plugin_and_matches_the_own_engine_cpu(tmp_path, mode):
     r = _run("", _model_dir(tmp_path, "float32"), "float32", mode)

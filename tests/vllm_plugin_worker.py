@@ -2,7 +2,8 @@
 platform plugin and prints what the test checks as one JSON line.
 
 argv: <site dir with the installed distribution or ''> <model dir> <dtype> <mode>
-mode: 'sync' | 'async' | 'preempt'"""
+mode: 'sync' | 'async' | 'preempt' | 'structured' (vLLM's structured outputs: a character-level
+tokenizer is written next to the model and requests constrained to a choice run next to free ones)"""
 import json
 import os
 import sys
@@ -23,6 +24,46 @@ import numpy as np
 import torch
 from vllm import LLM, SamplingParams
 from vllm.platforms import current_platform
+
+if mode == "structured":
+    import string
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    from vllm.sampling_params import StructuredOutputsParams
+    vocab = {"<pad>": 0, "<eos>": 1, "<unk>": 2}
+    for ch in string.ascii_letters + string.digits + string.punctuation + " ":
+        vocab.setdefault(ch, len(vocab))
+    i = 0
+    while len(vocab) < 1024:
+        vocab[f"w{i}x"] = len(vocab)
+        i += 1
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", "isolated")
+    tok.decoder = decoders.Fuse()
+    PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<eos>", pad_token="<pad>",
+                            unk_token="<unk>").save_pretrained(model_dir)
+    cfg_path = os.path.join(model_dir, "config.json")
+    hf = json.load(open(cfg_path))
+    hf.update(eos_token_id=1, pad_token_id=0)
+    json.dump(hf, open(cfg_path, "w"))
+    llm = LLM(model=model_dir, tokenizer=model_dir, load_format="dummy", dtype=dtype, max_model_len=256, max_num_seqs=8,
+              max_num_batched_tokens=64, enable_prefix_caching=False, seed=0)
+    choices = ["yes", "no", "maybe"]
+    constrained = SamplingParams(temperature=0.0, max_tokens=12,
+                                 structured_outputs=StructuredOutputsParams(choice=choices))
+    free = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(3, 1024, size=n).tolist() for n in (9, 20, 5, 33)]
+    outs = llm.generate([{"prompt_token_ids": p} for p in prompts], [constrained, free, constrained, free], use_tqdm=False)
+    worker = llm.llm_engine.engine_core.engine_core.model_executor.driver_worker.worker
+    # the free requests alone: their tokens must not depend on sharing steps with constrained ones
+    alone = llm.generate([{"prompt_token_ids": prompts[1]}, {"prompt_token_ids": prompts[3]}], free, use_tqdm=False)
+    print("RESULT " + json.dumps({
+        "platform": type(current_platform).__name__, "worker": type(worker).__name__,
+        "texts": [o.outputs[0].text for o in outs], "choices": choices,
+        "got": [list(o.outputs[0].token_ids) for o in outs],
+        "free_alone": [list(o.outputs[0].token_ids) for o in alone]}), flush=True)
+    os._exit(0)
 
 kw = dict(model=model_dir, load_format="dummy", skip_tokenizer_init=True, dtype=dtype, max_model_len=256,
           max_num_seqs=8, max_num_batched_tokens=64, enable_prefix_caching=False, seed=0,

@@ -57,7 +57,8 @@ class _SpecRow:
 
 class _StepHandle:
     """A step that was enqueued but whose sampled tokens have not been read yet."""
-    __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index", "logprobs", "ev_start", "num_tokens")
+    __slots__ = ("tokens", "reqs", "host", "event", "kind", "t_start", "index", "logprobs", "ev_start", "num_tokens",
+                 "h_sel")
 
     def __init__(self, tokens, reqs, host, event, kind, t_start):
         self.tokens, self.reqs, self.host, self.event, self.kind, self.t_start = tokens, reqs, host, event, kind, t_start
@@ -65,6 +66,7 @@ class _StepHandle:
         self.logprobs = None
         self.ev_start = None
         self.num_tokens = 0
+        self.h_sel = None          # hidden rows awaiting a deferred sampling (finish_sampling)
 
 
 class ModelRunner:
@@ -768,10 +770,15 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ asynchronous stepping
     @torch.inference_mode()
-    def execute_async(self, so: SchedulerOutput, prev=None):
+    def execute_async(self, so: SchedulerOutput, prev=None, defer_sampling: bool = False):
         """Enqueue one step without waiting for its result.  Tokens that the previous step
         (``prev``, still running) is sampling are not known on the host: they are copied on the
-        device from its output into this step's input ids.  Returns a handle for ``collect``."""
+        device from its output into this step's input ids.  Returns a handle for ``collect``.
+
+        ``defer_sampling``: stop after the forward pass and keep the hidden rows of the sampling
+        positions in the handle; ``finish_sampling`` computes the logits and samples later, when a
+        caller-side constraint on the logits (a host engine's grammar bitmask for this very step)
+        has arrived."""
         if so.is_empty:
             return None
         t_start = time.perf_counter()
@@ -820,11 +827,42 @@ class ModelRunner:
                 return _StepHandle(None, [], None, None, "mixed", t_start)
             h_sel = hidden[:T] if len(sel) == T else hidden[self._to_dev(torch.tensor(sel, dtype=torch.int64))]
         self._capture_pooled(h_sel, sample_reqs)
+        kind = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
+        handle = _StepHandle(None, sample_reqs, None, None, kind, t_start)
+        handle.ev_start = ev_start
+        handle.num_tokens = T
+        self.stats["t_prepare"] += t_prep - t_start
+        if defer_sampling:
+            handle.h_sel = h_sel
+            self.stats["t_launch"] += time.perf_counter() - t_prep
+            return handle
+        self._sample_into(handle, h_sel, None)
+        self.stats["t_launch"] += time.perf_counter() - t_prep
+        return handle
+
+    def finish_sampling(self, handle, allowed: Optional[dict] = None):
+        """Second half of a step enqueued with ``defer_sampling``.  ``allowed``: request id -> bool
+        tensor [vocab] (True = token may be sampled) for the requests whose logits are constrained."""
+        if handle is None or handle.h_sel is None:
+            return handle
+        h_sel, handle.h_sel = handle.h_sel, None
+        self._sample_into(handle, h_sel, allowed)
+        return handle
+
+    def _sample_into(self, handle, h_sel: torch.Tensor, allowed: Optional[dict]) -> None:
+        sample_reqs = handle.reqs
         dev_lp = None
-        if self._reduce_sample(sample_reqs):
+        if not allowed and self._reduce_sample(sample_reqs):
             tokens = self.model.lm_head.greedy_tokens(h_sel)
         else:
             logits = self.model.compute_logits(h_sel)
+            if allowed:
+                rows = [i for i, r in enumerate(sample_reqs) if r.request_id in allowed]
+                if rows:
+                    mask = torch.stack([allowed[sample_reqs[i].request_id] for i in rows]).to(logits.device)
+                    idx = torch.tensor(rows, dtype=torch.int64, device=logits.device)
+                    sub = logits.index_select(0, idx)
+                    logits.index_copy_(0, idx, sub.masked_fill(~mask[:, :sub.shape[1]], float("-inf")))
             md = SamplingMetadata.build(sample_reqs, self.device, self.mcfg.vocab_size, self.cfg.seed)
             if not md.all_greedy and not self.is_cuda:
                 md.generator = self._cpu_generator()
@@ -839,14 +877,8 @@ class ModelRunner:
             ev = torch.cuda.Event(enable_timing=self._step_timing)
             ev.record()
         self.stats["d2h_bytes"] += n * 8
-        self.stats["t_prepare"] += t_prep - t_start
-        self.stats["t_launch"] += time.perf_counter() - t_prep
-        kind = "decode" if gsize is not None else ("decode_eager" if decode_only else "mixed")
-        handle = _StepHandle(tokens, sample_reqs, buf, ev, kind, t_start)
+        handle.tokens, handle.host, handle.event = tokens, buf, ev
         handle.logprobs = dev_lp
-        handle.ev_start = ev_start
-        handle.num_tokens = T
-        return handle
 
     def _reduce_sample(self, sample_reqs: list) -> bool:
         """Greedy batches on a vocabulary-sharded LM head pick their tokens from per-rank

@@ -275,6 +275,11 @@ class B200VllmWorker(_WorkerBase):
                 req.row = old.row
                 self.runner.row_owner[req.row] = None      # the row's cached ids are rebuilt
                 self.stats["resumed"] += 1
+            vsp = nr.sampling_params
+            # structured outputs: the host computes a token bitmask per step after scheduling; steps of
+            # such requests sample only once the bitmask has arrived (sample_tokens)
+            req.structured = vsp is not None and (getattr(vsp, "structured_outputs", None) is not None
+                                                   or getattr(vsp, "guided_decoding", None) is not None)
             req.status = RequestStatus.RUNNING
             req.block_ids = list(nr.block_ids[0])
             req.num_computed_tokens = int(nr.num_computed_tokens)
@@ -338,7 +343,8 @@ class B200VllmWorker(_WorkerBase):
             from vllm.v1.outputs import EMPTY_MODEL_RUNNER_OUTPUT
             return EMPTY_MODEL_RUNNER_OUTPUT
         plan, order = self._plan(so)
-        handle = self.runner.execute_async(plan, self._uncollected)
+        defer = any(getattr(r, "structured", False) for r, _ in plan.scheduled)
+        handle = self.runner.execute_async(plan, self._uncollected, defer_sampling=defer)
         # account for the step at launch (the runner's own scheduler does the same): a request whose
         # step samples has one more token in flight until the step is collected
         for req, n in plan.scheduled:
@@ -350,14 +356,36 @@ class B200VllmWorker(_WorkerBase):
         return None
 
     def sample_tokens(self, grammar_output=None):
-        if grammar_output is not None and getattr(grammar_output, "grammar_bitmask", None) is not None:
-            raise NotImplementedError("structured outputs under a host vLLM: use this package's guided decoding")
         pending, self._pending = self._pending, None
         if pending is None:
             return None
+        handle = pending[0]
+        bitmask = getattr(grammar_output, "grammar_bitmask", None) if grammar_output is not None else None
+        if handle is not None and handle.h_sel is not None:
+            # the forward pass ran without sampling: apply the host's grammar bitmask (bit t of word
+            # t // 32 set = token t allowed) to the rows of the structured requests, then sample
+            allowed = None
+            if bitmask is not None:
+                allowed = self._unpack_bitmask(grammar_output.structured_output_request_ids, bitmask)
+            self.runner.finish_sampling(handle, allowed)
+            if handle.tokens is not None:
+                self._uncollected = handle
+        elif bitmask is not None and len(grammar_output.structured_output_request_ids):
+            raise RuntimeError("a grammar bitmask arrived for a step that was sampled without it")
         if self._async:
             return _AsyncStepOutput(self, pending)
         return self._finish(pending)
+
+    def _unpack_bitmask(self, req_ids, bitmask) -> dict:
+        vocab = self.runner.mcfg.vocab_size
+        bm = torch.from_numpy(np.ascontiguousarray(bitmask)).to(torch.int32)
+        if self.device is not None and self.device.type == "cuda":
+            bm = bm.to(self.device, non_blocking=True)
+        shifts = torch.arange(32, dtype=torch.int32, device=bm.device)
+        bits = ((bm.unsqueeze(-1) >> shifts) & 1).bool().reshape(bm.shape[0], -1)
+        if bits.shape[1] < vocab:                # tokens beyond the grammar's vocabulary are not allowed
+            bits = torch.nn.functional.pad(bits, (0, vocab - bits.shape[1]))
+        return {rid: bits[i, :vocab] for i, rid in enumerate(req_ids)}
 
     def _finish(self, pending):
         from vllm.v1.outputs import ModelRunnerOutput
