@@ -52,6 +52,12 @@ def _check_common(r):
     assert all(len(t) > 0 for t in r["got"])
 
 
+def test_vllm_prompt_embedding_requests_on_the_plugin_cpu(tmp_path):
+    r = _run("", _model_dir(tmp_path, "float32"), "float32", "embeds")
+    _check_common(r)
+    assert r["got"] == r["want"]
+
+
 def test_vllm_structured_outputs_reach_the_plugin_sampler_cpu(tmp_path):
     """vLLM compiles the grammar and hands the worker one token bitmask per step; the worker runs the
     forward pass, applies the bitmask to the rows of the constrained requests and samples."""

@@ -2,7 +2,7 @@
 platform plugin and prints what the test checks as one JSON line.
 
 argv: <site dir with the installed distribution or ''> <model dir> <dtype> <mode>
-mode: 'sync' | 'async' | 'preempt' | 'structured' (vLLM's structured outputs: a character-level
+mode: 'sync' | 'async' | 'preempt' | 'embeds' (a prompt-embedding request) | 'structured' (vLLM's structured outputs: a character-level
 tokenizer is written next to the model and requests constrained to a choice run next to free ones)"""
 import json
 import os
@@ -24,6 +24,27 @@ import numpy as np
 import torch
 from vllm import LLM, SamplingParams
 from vllm.platforms import current_platform
+
+if mode == "embeds":
+    # a request that brings its input embeddings next to a request with token ids
+    llm = LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True, dtype=dtype, max_model_len=256,
+              max_num_seqs=8, max_num_batched_tokens=64, enable_prefix_caching=False, seed=0, enable_prompt_embeds=True)
+    hidden = json.load(open(os.path.join(model_dir, "config.json")))["hidden_size"]
+    pe = torch.randn(11, hidden, generator=torch.Generator().manual_seed(0)) * 0.05
+    reqs = [{"prompt_embeds": pe}, {"prompt_token_ids": [5, 6, 7, 8, 9]}]
+    outs = llm.generate(reqs, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True), use_tqdm=False)
+    worker = llm.llm_engine.engine_core.engine_core.model_executor.driver_worker.worker
+    from vllm_ascend_b200.config import ModelConfig
+    from vllm_ascend_b200.engine.llm import LLM as OwnLLM
+    from vllm_ascend_b200.engine.request import SamplingParams as OwnSP
+    cfg = ModelConfig.from_hf_dict(json.load(open(os.path.join(model_dir, "config.json"))), dtype=dtype)
+    cfg.name = os.path.basename(os.path.normpath(model_dir))
+    own = OwnLLM(cfg, max_model_len=256, max_num_seqs=8, max_num_batched_tokens=64, seed=0,
+                 block_size=worker.cfg.cache.block_size)
+    want = [o.outputs[0].token_ids for o in own.generate(reqs, OwnSP(temperature=0.0, max_tokens=6, ignore_eos=True))]
+    print("RESULT " + json.dumps({"platform": type(current_platform).__name__, "worker": type(worker).__name__,
+                                  "got": [list(o.outputs[0].token_ids) for o in outs], "want": want}), flush=True)
+    os._exit(0)
 
 if mode == "structured":
     import string

@@ -264,13 +264,29 @@ class B200VllmWorker(_WorkerBase):
             # (``prefill_token_ids`` = prompt + generated so far)
             every = getattr(nr, "prefill_token_ids", None) or nr.prompt_token_ids
             prompt = nr.prompt_token_ids if nr.prompt_token_ids is not None else every
-            if every is None:
-                raise NotImplementedError("prompt-embedding requests run on the standalone engine")
             if getattr(nr, "mm_features", None):
                 raise NotImplementedError("multimodal requests run on the standalone engine")
+            mm_items = []
+            embeds = getattr(nr, "prompt_embeds", None)
+            if embeds is not None:
+                # the caller supplied input embeddings: placeholder ids, rows merged in like encoder outputs
+                from ..multimodal.inputs import MMInput
+                pe = torch.as_tensor(embeds)
+                if pe.dim() != 2 or pe.shape[1] != self.runner.mcfg.hidden_size:
+                    raise ValueError(f"prompt_embeds must be [num_tokens, {self.runner.mcfg.hidden_size}]")
+                if self.runner.mm is None:
+                    from ..engine.mm_runner import MultimodalState
+                    self.runner.mm = MultimodalState(self.runner)
+                n_emb = pe.shape[0]
+                mm_items = [MMInput("embeds", 0, n_emb, (0, 0, 0), None, f"embeds-{nr.req_id}", embeds=pe)]
+                tail = [int(t) for t in (every[n_emb:] if every is not None else [])]
+                prompt = [0] * n_emb
+                every = prompt + tail
+            if every is None:
+                raise ValueError(f"request {nr.req_id} carries neither token ids nor embeddings")
             old = self.reqs.pop(nr.req_id, None)
             req = Request(nr.req_id, np.asarray(prompt, dtype=np.int32), to_sampling_params(nr.sampling_params),
-                          lora_request=nr.lora_request)
+                          lora_request=nr.lora_request, mm_inputs=mm_items)
             if old is not None:
                 req.row = old.row
                 self.runner.row_owner[req.row] = None      # the row's cached ids are rebuilt
