@@ -280,3 +280,44 @@ def test_weight_absorption_through_the_grouped_gemm_matches_einsum():
         assert float((got2.float() - want2).abs().max()) <= 0.02 * float(want2.abs().max()) + 1e-3
     torch.cuda.synchronize()
     _native.check_status(dev)
+
+
+def test_mla_partials_of_two_key_shards_merge_to_full_attention():
+    """Two 'ranks' hold the even / odd tokens of every sequence densely under the same block table; each
+    runs the MLA kernel over its share with the log-sum-exp output, and the merged result equals
+    attention over all tokens (one row also has no token on the second rank)."""
+    from vllm_ascend_b200 import ops
+    dev = torch.device("cuda")
+    H, bs = 16, 128
+    kv_lens, q_lens = [1, 130, 517, 999], [1, 1, 1, 1]
+    q, lat, pe, bt, row_seq, row_kv = _case(kv_lens, q_lens, H, bs, seed=5)
+    scale = 576 ** -0.5
+    R = q.shape[0]
+    po = torch.empty(R, H, 2, 512, dtype=torch.float32, device=dev)
+    pl = torch.empty(R, H, 2, dtype=torch.float32, device=dev)
+    for r in range(2):
+        lat_r, pe_r = torch.zeros_like(lat), torch.zeros_like(pe)
+        local = []
+        for b, n in enumerate(kv_lens):
+            nb = (n + bs - 1) // bs
+            ids = bt[b, :nb].long()
+            ls = lat[ids].reshape(-1, 512)[:n][r::2]
+            ps = pe[ids].reshape(-1, 64)[:n][r::2]
+            local.append(ls.shape[0])
+            fl, fp = lat_r[ids].reshape(-1, 512), pe_r[ids].reshape(-1, 64)
+            fl[:ls.shape[0]] = ls
+            fp[:ps.shape[0]] = ps
+            lat_r[ids] = fl.view(nb, bs, 512)
+            pe_r[ids] = fp.view(nb, bs, 64)
+        lse = torch.empty(R, H, dtype=torch.float32, device=dev)
+        out = mla_decode_native(q.to(dev), lat_r.to(dev), pe_r.to(dev), row_seq.to(dev),
+                                torch.tensor(local, dtype=torch.int32, device=dev), bt.to(dev), scale,
+                                max_kv_len=max(local), lse_out=lse)
+        po[:, :, r] = out.float()
+        pl[:, :, r] = lse
+    torch.cuda.synchronize()
+    _native.check_status(dev)
+    assert bool(torch.isinf(pl[0, :, 1]).all())              # the one-token sequence lives on rank 0 only
+    merged = ops.merge_attn_partials(po, pl)
+    want = _oracle(q, lat, pe, bt, row_seq, row_kv, scale, bs)
+    assert float((merged.float().cpu() - want).abs().max()) < 0.02

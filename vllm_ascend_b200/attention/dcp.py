@@ -51,18 +51,13 @@ def merge_partials(outs: torch.Tensor, lses: torch.Tensor) -> torch.Tensor:
     return (outs * w.unsqueeze(-1)).sum(0) / den.unsqueeze(-1)
 
 
-def mla_attention_dcp(q_lat: torch.Tensor, q_pe: torch.Tensor, lat_cache: torch.Tensor, pe_cache: torch.Tensor,
-                      meta, scale: float, group, interleave: int) -> torch.Tensor:
-    """MLA attention with the latent cache sharded over ``group``.  q_* hold this rank's heads."""
-    d, rank = group.world_size, group.rank_in_group
-    T, H, dc = q_lat.shape
+def _mla_local_partials(q_all, lat_cache, pe_cache, meta, scale, d, rank, interleave, dc):
+    """PyTorch definition of one rank's partial MLA attention: (out fp32 [T, HH, dc] normalised over the
+    local keys, lse fp32 [T, HH]).  Serves prefill / mixed steps and the host tests."""
+    T, HH, _ = q_all.shape
     bs = lat_cache.shape[1]
-    # every rank needs every head of the group to attend over its slice of the sequence
-    q = torch.cat([q_lat, q_pe], dim=-1)
-    q_all = group.all_gather(q.contiguous(), dim=1)                        # [T, d*H, dc+dr]
-    HH = q_all.shape[1]
-    out = torch.zeros(T, HH, dc, dtype=torch.float32, device=q.device)
-    lse = torch.full((T, HH), float("-inf"), dtype=torch.float32, device=q.device)
+    out = torch.zeros(T, HH, dc, dtype=torch.float32, device=q_all.device)
+    lse = torch.full((T, HH), float("-inf"), dtype=torch.float32, device=q_all.device)
     lat_flat = lat_cache.reshape(-1, lat_cache.shape[-1])
     pe_flat = pe_cache.reshape(-1, pe_cache.shape[-1])
     qsl, sls = meta.query_start_loc_cpu, meta.seq_lens_cpu
@@ -74,18 +69,47 @@ def mla_attention_dcp(q_lat: torch.Tensor, q_pe: torch.Tensor, lat_cache: torch.
         slots, gpos = local_tokens(sl, meta.block_table[b], bs, d, rank, interleave)
         if len(slots) == 0:
             continue
-        st = torch.from_numpy(slots).to(q.device)
+        st = torch.from_numpy(slots).to(q_all.device)
         kl, kp = lat_flat[st].float(), pe_flat[st].float()
         s = (torch.einsum("qhc,kc->qhk", q_all[qs:qe, :, :dc].float(), kl) +
              torch.einsum("qhr,kr->qhk", q_all[qs:qe, :, dc:].float(), kp)) * scale
-        qpos = (sl - ql) + torch.arange(ql, device=q.device)
-        vis = torch.from_numpy(gpos).to(q.device)[None, :] <= qpos[:, None]           # [ql, n]
+        qpos = (sl - ql) + torch.arange(ql, device=q_all.device)
+        vis = torch.from_numpy(gpos).to(q_all.device)[None, :] <= qpos[:, None]           # [ql, n]
         s = s.masked_fill(~vis[:, None, :], float("-inf"))
         l = torch.logsumexp(s, dim=-1)                                                 # [ql, HH]
         p = torch.exp(s - l.clamp(min=-1e30).unsqueeze(-1))
         p = torch.where(torch.isfinite(s), p, torch.zeros_like(p))
         out[qs:qe] = torch.einsum("qhk,kc->qhc", p, kl)
         lse[qs:qe] = l
+    return out, lse
+
+
+def mla_attention_dcp(q_lat: torch.Tensor, q_pe: torch.Tensor, lat_cache: torch.Tensor, pe_cache: torch.Tensor,
+                      meta, scale: float, group, interleave: int) -> torch.Tensor:
+    """MLA attention with the latent cache sharded over ``group``.  q_* hold this rank's heads."""
+    d, rank = group.world_size, group.rank_in_group
+    T, H, dc = q_lat.shape
+    bs = lat_cache.shape[1]
+    # every rank needs every head of the group to attend over its slice of the sequence
+    q = torch.cat([q_lat, q_pe], dim=-1)
+    q_all = group.all_gather(q.contiguous(), dim=1)                        # [T, d*H, dc+dr]
+    HH = q_all.shape[1]
+    local_sl = getattr(meta, "dcp_seq_lens", None)
+    from .. import envs
+    kernel_ok = (q.is_cuda and q.dtype == torch.bfloat16 and dc == 512 and q_pe.shape[-1] == 64 and HH % 16 == 0
+                 and meta.max_query_len == 1 and T == meta.num_reqs and local_sl is not None
+                 and envs.VLLM_B200_MLA_ATTN == "tcgen05" and bs in (16, 32, 64, 128, 256, 512) and T <= 65535)
+    if kernel_ok:
+        # decode step: a rank's tokens of a sequence are an ordinary paged sequence of local_seq_lens keys,
+        # all visible to the new token: the tcgen05 MLA kernel runs on it and its split merge returns
+        # the log-sum-exp
+        from .mla import mla_decode_native
+        row_seq = torch.arange(T, dtype=torch.int32, device=q.device)
+        lse = torch.empty((T, HH), dtype=torch.float32, device=q.device)
+        out = mla_decode_native(q_all, lat_cache, pe_cache, row_seq, local_sl, meta.block_table, scale,
+                                max_kv_len=max(1, (meta.max_seq_len + d - 1) // d), lse_out=lse).float()
+    else:
+        out, lse = _mla_local_partials(q_all, lat_cache, pe_cache, meta, scale, d, rank, interleave, dc)
     # partial results of head block j go to rank j: all-to-all of (out ‖ lse)
     packed = torch.cat([out, lse.unsqueeze(-1)], dim=-1).view(T, d, H, dc + 1).permute(1, 0, 2, 3).contiguous()
     recv = group.all_to_all_single(packed.view(d * T, H, dc + 1))                      # [d(src) * T, H, dc+1]

@@ -9,6 +9,8 @@ Cache layout contract: two paged tensors per layer, latent
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from ctypes import c_float, c_int, c_long, c_void_p
@@ -19,15 +21,19 @@ from ..ops import reference as ref
 _P, _I, _L, _F = c_void_p, c_int, c_long, c_float
 _native.register_signature("b200_mla_decode", [_P, _L, _L, _I, _P, _P, _L, _I, _P, _P, _P, _I, _F, _I, _P, _L, _P,
                                                _P, _P])
+_native.register_signature("b200_mla_decode_lse", [_P, _L, _L, _I, _P, _P, _L, _I, _P, _P, _P, _I, _F, _I, _P, _L, _P,
+                                                   _P, _P, _P])
 _scratch: dict = {}
 
 
 def mla_decode_native(q_cat: torch.Tensor, lat_cache: torch.Tensor, pe_cache: torch.Tensor,
                       row_seq: torch.Tensor, row_kv_len: torch.Tensor, block_table: torch.Tensor,
-                      scale: float, num_splits: int = 0, max_kv_len: int = 0) -> torch.Tensor:
+                      scale: float, num_splits: int = 0, max_kv_len: int = 0,
+                      lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """tcgen05 MLA attention over query rows.  q_cat [R, H, 576] = absorbed q_nope ‖ q_pe;
     every row r attends to the first ``row_kv_len[r]`` tokens of sequence ``row_seq[r]``.
-    Returns o_lat [R, H, 512]."""
+    Returns o_lat [R, H, 512].  ``lse_out`` (fp32 [R, H]) receives the log-sum-exp over the keys
+    seen (-inf for a row without keys), for merging the results of context-parallel ranks."""
     R, H, dk = q_cat.shape
     assert dk == 576 and q_cat.dtype == torch.bfloat16 and q_cat.stride(2) == 1 and q_cat.stride(1) == dk
     dev = q_cat.device
@@ -38,6 +44,8 @@ def mla_decode_native(q_cat: torch.Tensor, lat_cache: torch.Tensor, pe_cache: to
         ctas = max(1, R * (H // nq))
         tiles = max(1, (max_kv_len + 127) // 128) if max_kv_len else 8
         num_splits = max(1, min(tiles, (2 * sms + ctas - 1) // ctas, 32))
+    if lse_out is not None:
+        num_splits = max(2, num_splits)          # the split merge produces the log-sum-exp
     scratch = None
     if num_splits > 1:
         need = R * H * num_splits * 513
@@ -46,11 +54,11 @@ def mla_decode_native(q_cat: torch.Tensor, lat_cache: torch.Tensor, pe_cache: to
         if scratch is None or scratch.numel() < need:
             scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=dev)
             _scratch[key] = scratch
-    rc = _native.lib().b200_mla_decode(
+    rc = _native.lib().b200_mla_decode_lse(
         q_cat.data_ptr(), q_cat.stride(0), R, H, lat_cache.data_ptr(), pe_cache.data_ptr(), lat_cache.shape[0],
         lat_cache.shape[1], row_seq.data_ptr(), row_kv_len.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), scale, num_splits, out.data_ptr(), out.stride(0), _native.ptr(scratch),
-        _native.status_word(dev).data_ptr(), _native.stream_ptr())
+        _native.ptr(lse_out), _native.status_word(dev).data_ptr(), _native.stream_ptr())
     _native.check(rc, "mla_decode")
     _native.count_launch(2 if num_splits > 1 else 1)
     return out

@@ -432,13 +432,18 @@ static int launch_mla(const CUtensorMap& tq, const CUtensorMap& tl, const CUtens
 // row_seq / row_kv_len: int32 [R]: block-table row and visible key count of every query row
 // (a decode token sees all of its sequence; row t of a multi-token query sees ctx + t + 1).
 // out: [R, H, 512].  scratch: R * H * num_splits * 513 floats when num_splits > 1.
-B200_API int b200_mla_decode(const void* q, long q_stride, long R, int H, const void* lat_cache,
-                             const void* pe_cache, long num_blocks, int block_size,
-                             const void* row_seq, const void* row_kv_len, const void* block_table,
-                             int max_blocks, float scale, int num_splits, void* out,
-                             long out_stride, void* scratch, int* status, cudaStream_t stream) {
+// lse_out (optional, fp32 [R, H]): log-sum-exp of every (row, head) over the keys the row saw, for
+// callers that merge the results of several calls (context-parallel ranks).  It is produced by the
+// split merge, so a call that wants it runs with at least two KV splits.
+B200_API int b200_mla_decode_lse(const void* q, long q_stride, long R, int H, const void* lat_cache,
+                                 const void* pe_cache, long num_blocks, int block_size,
+                                 const void* row_seq, const void* row_kv_len,
+                                 const void* block_table, int max_blocks, float scale,
+                                 int num_splits, void* out, long out_stride, void* scratch,
+                                 void* lse_out, int* status, cudaStream_t stream) {
   using namespace b200;
   if (R <= 0) return 0;
+  if (lse_out && num_splits < 2) num_splits = 2;
   if (H % 16) return 9500;
   if (block_size < 8 || (block_size < 128 && (128 % block_size) != 0) ||
       (block_size > 128 && (block_size % 128) != 0))
@@ -493,6 +498,16 @@ B200_API int b200_mla_decode(const void* q, long q_stride, long R, int H, const 
   if (rc) return rc;
   if (num_splits > 1)
     return launch_merge_splits(p.partial_o, p.partial_lse, R, H, num_splits, MLA_DC, out,
-                               out_stride, stream);
+                               out_stride, stream, (float*)lse_out);
   return 0;
+}
+
+B200_API int b200_mla_decode(const void* q, long q_stride, long R, int H, const void* lat_cache,
+                             const void* pe_cache, long num_blocks, int block_size,
+                             const void* row_seq, const void* row_kv_len, const void* block_table,
+                             int max_blocks, float scale, int num_splits, void* out,
+                             long out_stride, void* scratch, int* status, cudaStream_t stream) {
+  return b200_mla_decode_lse(q, q_stride, R, H, lat_cache, pe_cache, num_blocks, block_size, row_seq,
+                             row_kv_len, block_table, max_blocks, scale, num_splits, out,
+                             out_stride, scratch, nullptr, status, stream);
 }
