@@ -215,6 +215,12 @@ def bench_gdn(a):
         state_bytes = 2.0 * B * Hv * DK * DV * 4
         print(f"gated-delta-rule B={B} q_len={q_len} Hv={Hv} {DK}x{DV}: {ms:.4f} ms  state {state_bytes / ms / 1e6:.0f} GB/s "
               f"({state_bytes / ms / 1e6 / hbm:.2f} {tag})  {T / ms * 1e3:.0f} tok/s", flush=True)
+        if q_len >= 64:
+            cu_h = cu.cpu().numpy()
+            ms_c = timeit(lambda: la.gated_delta_rule_chunked(q, k, v, gg, beta, S, cu_h, slots, init, DK ** -0.5),
+                          max(3, a.iters // 4))
+            print(f"gated-delta-rule chunk-parallel form, same case: {ms_c:.4f} ms  {T / ms_c * 1e3:.0f} tok/s "
+                  f"({ms / ms_c:.1f}x the recurrence)", flush=True)
     _native.check_status(dev)
 
 
@@ -423,7 +429,7 @@ def main():
     ap.add_argument("--raster", type=int, default=0, help="M-tiles per raster group of the paired-CTA GEMM")
     ap.add_argument("--compare", action="store_true")
     ap.add_argument("--no-flush", action="store_true", help="gemm: leave the operands in L2 between timed launches")
-    ap.add_argument("--tile-n", type=int, default=0, help="paired-CTA GEMM: fixed tile width (128..256 step 32)")
+    ap.add_argument("--tile-n", type=int, default=0, help="paired-CTA GEMM: fixed tile width (128..256 step 16)")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=1152)
     ap.add_argument("--seq", type=int, default=1024)

@@ -121,7 +121,7 @@ def test_gemm_2cta_swiglu(M, I, K):
     assert (out.float() - exp).abs().max().item() < 0.02 * exp.abs().max().item() + 0.02
 
 
-@pytest.mark.parametrize("width", [128, 160, 192, 224, 256])
+@pytest.mark.parametrize("width", [128, 144, 160, 176, 192, 208, 224, 240, 256])
 def test_gemm_2cta_every_tile_width(width):
     """The paired-CTA kernel picks its tile width (128..256 columns) per problem so that the tiles fill
     whole waves of CTA pairs; every width is forced here on shapes with ragged last tiles in M and N,

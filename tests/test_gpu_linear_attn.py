@@ -59,6 +59,34 @@ def test_gated_delta_rule_kernel(Hk, Hv, DK, DV):
     assert (S_dev.cpu() - S_ref).abs().max() < 2e-2
 
 
+def test_chunk_parallel_delta_rule_on_device():
+    """bf16 inputs on the device: the chunked form (fp32 matrix products) and the recurrence kernel
+    both against the fp32 definition, mixed step routed by sequence length."""
+    g = torch.Generator().manual_seed(4)
+    lens = [300, 1, 64, 130, 2]
+    cu_h = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    cu = torch.tensor(cu_h, dtype=torch.int32)
+    slots = torch.tensor([3, 0, 5, 1, 2], dtype=torch.int32)
+    has_init = torch.tensor([1, 1, 0, 1, 0], dtype=torch.int32)
+    Hk, Hv, DK, DV = 2, 4, 128, 128
+    T = sum(lens)
+    q = torch.randn(T, Hk, DK, generator=g).bfloat16()
+    k = torch.randn(T, Hk, DK, generator=g).bfloat16()
+    v = torch.randn(T, Hv, DV, generator=g).bfloat16()
+    gg = -torch.rand(T, Hv, generator=g) * 0.3
+    beta = torch.rand(T, Hv, generator=g)
+    S = torch.randn(6, Hv, DK, DV, generator=g) * 0.1
+    S_ref = S.clone()
+    want = la.gated_delta_rule_ref(q.float(), k.float(), v.float(), gg, beta, S_ref, cu, slots, has_init, DK ** -0.5)
+    S_dev = S.to(DEV)
+    got = la.gated_delta_rule(q.to(DEV), k.to(DEV), v.to(DEV), gg.to(DEV), beta.to(DEV), S_dev, cu.to(DEV),
+                              slots.to(DEV), has_init.to(DEV), DK ** -0.5, cu_cpu=cu_h)
+    torch.cuda.synchronize()
+    _native.check_status(torch.device(DEV))
+    assert (got.float().cpu() - want).abs().max() < 3e-2
+    assert (S_dev.cpu() - S_ref).abs().max() < 2e-2
+
+
 def test_hybrid_model_on_engine_graph_equals_eager():
     from vllm_ascend_b200.config import ModelConfig
     from vllm_ascend_b200.engine.llm import LLM

@@ -57,7 +57,8 @@ struct Gemm2Params {
   CommCtl* ctl;
   int rows_per_owner;
   int raster;                         // M-tiles per raster group (0/1: column-major order)
-  int bn;                             // tile width: 128..256 in steps of 32 (SwiGLU tiles: 256)
+  int bn;                             // tile width: 128..256 in steps of 16 (32 with the reduce-scatter
+                                      // epilogue, whose staging flushes 64-column pairs; SwiGLU tiles: 256)
   // ---- RMSNorm folded into the GEMMs around it (the norm weight lives in W of the consumer)
   // Row statistics travel as per-column-tile partial sums so that their total does not depend on
   // the order in which tiles finish: buffer [ss_parts_max][ss_stride] fp32 followed by one int32
@@ -347,7 +348,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int g = 0; g < 4; g++) {
             const int col = col0 + g * 8;
-            if (col < p.N) {
+            if (col < p.N && c0 + g * 8 < out_per_tile) {     // tile widths are multiples of 16
               float v[8];
 #pragma unroll
               for (int j = 0; j < 8; j++) v[j] = __uint_as_float(r[g * 8 + j]);
@@ -519,10 +520,11 @@ static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, in
   // over the CTA pairs matter more when there are only a few tiles: a decode batch of 768 rows
   // against N = 4096 is 48 tiles of 256 columns on 74 pairs (35% of the GPU idle), or 66 tiles
   // of 192 columns in the same single wave.  Cost model: waves x tile width; a narrower tile
-  // must win by 8% to be taken.
+  // must win by 8% to be taken.  M = 768, N = 4096 ends at 176 columns: 72 tiles on 74 pairs.
+  const int bn_step = (p.mode & G2_RS) ? 32 : 16;
   if (p.swiglu) {
     p.bn = G2_BN;
-  } else if (g_force_bn >= 128 && g_force_bn <= 256 && (g_force_bn % 32) == 0) {
+  } else if (g_force_bn >= 128 && g_force_bn <= 256 && (g_force_bn % bn_step) == 0) {
     p.bn = g_force_bn;
   } else {
     auto cost = [&](int bn) {
@@ -531,7 +533,7 @@ static int launch_2cta(const void* A, const void* W, Gemm2Params& p, int lda, in
     };
     p.bn = G2_BN;
     long best = cost(G2_BN);
-    for (int bn = 224; bn >= 128; bn -= 32) {
+    for (int bn = G2_BN - bn_step; bn >= 128; bn -= bn_step) {
       const long c = cost(bn);
       if (c * 100 < best * 92) {
         best = c;

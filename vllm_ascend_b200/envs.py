@@ -45,6 +45,9 @@ env_variables: dict[str, Callable[[], Any]] = {
     "VLLM_B200_FOLD_NORM": _str("VLLM_B200_FOLD_NORM", "1"),
     # 128-key tiles the decode-attention kernel requests into L2 ahead of its staged K / V loads (0 = off)
     "VLLM_B200_DECODE_L2_PREFETCH": _int("VLLM_B200_DECODE_L2_PREFETCH", 0),
+    # gated delta rule: sequences with at least this many new tokens in a step (prefill chunks) take the
+    # chunk-parallel form (matrix products per 64-token chunk) instead of the per-token recurrence; 0 = never
+    "VLLM_B200_GDN_CHUNK_MIN": _int("VLLM_B200_GDN_CHUNK_MIN", 64),
     # "1": the slot of every token is computed on the device from the block table (one small kernel per
     # step) instead of on the host; "0" (default): host numpy + copy
     "VLLM_B200_DEVICE_SLOT_MAPPING": _str("VLLM_B200_DEVICE_SLOT_MAPPING", "0"),

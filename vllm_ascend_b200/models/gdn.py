@@ -65,7 +65,8 @@ class GatedDeltaNet:
         v = mixed[:, 2 * kd:].reshape(T, self.Hv, self.Dv)
         beta = torch.sigmoid(ba[:, :self.Hv].float())
         g = -torch.exp(self.A_log) * F.softplus(ba[:, self.Hv:].float() + self.dt_bias)
-        o = la.gated_delta_rule(q, k, v, g, beta, ssm_state, cu, slots, has_init, self.scale, l2norm=True)
+        o = la.gated_delta_rule(q, k, v, g, beta, ssm_state, cu, slots, has_init, self.scale, l2norm=True,
+                                cu_cpu=None if meta.max_query_len <= 1 else meta.query_start_loc_cpu)
         o = ops.rms_norm_gated(o.reshape(T, vd), z.contiguous(), self.norm_weight, self.cfg.rms_norm_eps,
                                group=self.Dv, norm_before_gate=True)
         return self.out_proj(o)

@@ -76,7 +76,133 @@ def gated_delta_rule_ref(q, k, v, g, beta, state, cu, slots, has_init, scale, l2
     return out
 
 
-def gated_delta_rule(q, k, v, g, beta, state, cu, slots, has_init, scale, l2norm=True):
+def gated_delta_rule_chunked(q, k, v, g, beta, state, cu_cpu, slots, has_init, scale, l2norm=True,
+                             chunk=64, seqs=None, out=None):
+    """The gated delta rule in its chunk-parallel form (same contract as ``gated_delta_rule_ref``;
+    ``cu_cpu``: host sequence boundaries, ``seqs``: indices of the sequences to process, default all;
+    rows of other sequences in ``out`` are left alone).
+
+    A chunk of C tokens with log-decays g, cumulative gamma_i = sum_{j<=i} g_j, entered with state S0:
+
+        u_j = beta_j (v_j - e^{gamma_j} S0^T k_j - sum_{m<j} e^{gamma_j - gamma_m} (k_m . k_j) u_m)
+        o_i = e^{gamma_i} S0^T q_i + sum_{j<=i} e^{gamma_i - gamma_j} (k_j . q_i) u_j
+        S_C = e^{gamma_C} S0 + sum_j e^{gamma_C - gamma_j} k_j u_j^T
+
+    The first line is a unit-lower-triangular system (I + A) U = beta (V - e^gamma K S0) with
+    A = strict_lower(beta (K K^T) * Gamma), so U = U' - W S0 with U' and W solved once per chunk,
+    for every chunk of every sequence at once.  What stays sequential is three small matrix
+    products per chunk position (all sequences that have such a chunk batched together), instead
+    of one state update per token: the form the reference uses for prefill
+    (vllm_ascend/ops/triton/fla/chunk.py:259, chunk_gated_delta_rule)."""
+    import numpy as np
+    T, Hv, DV = v.shape
+    Hk, DK = q.shape[1], q.shape[2]
+    rep = Hv // Hk
+    dev = q.device
+    cu_cpu = np.asarray(cu_cpu, dtype=np.int64)
+    seqs = np.arange(len(cu_cpu) - 1) if seqs is None else np.asarray(seqs, dtype=np.int64)
+    if out is None:
+        out = torch.empty((T, Hv, DV), dtype=v.dtype, device=dev)
+    lens = cu_cpu[seqs + 1] - cu_cpu[seqs]
+    keep = lens > 0
+    seqs, lens = seqs[keep], lens[keep]
+    if seqs.size == 0:
+        return out
+    order = np.argsort(-lens, kind="stable")          # longest first: the scan's live set is a prefix
+    seqs, lens = seqs[order], lens[order]
+    C = int(chunk)
+    nch = (lens + C - 1) // C
+    first = np.concatenate([[0], np.cumsum(nch)[:-1]])           # first chunk id of each sequence
+    Nc = int(nch.sum())
+    tok = np.full((Nc, C), -1, dtype=np.int64)
+    for b, (sq, n) in enumerate(zip(seqs, lens)):
+        ids = np.arange(cu_cpu[sq], cu_cpu[sq] + n)
+        flat = tok[first[b]:first[b] + nch[b]].reshape(-1)
+        flat[:n] = ids
+    tok_t = torch.from_numpy(tok).to(dev)
+    valid = tok_t >= 0
+    gather = tok_t.clamp(min=0).reshape(-1)
+    vmask = valid.reshape(-1, 1, 1).float()
+
+    qf, kf = q.float(), k.float()
+    if l2norm:
+        qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6)
+        kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+
+    def chunks(x, heads, dim):          # [T, heads, dim] -> [Nc, heads, C, dim], padding rows zero
+        return (x[gather] * vmask).reshape(Nc, C, heads, dim).permute(0, 2, 1, 3)
+    Qc = chunks(qf * scale, Hk, DK)
+    Kc = chunks(kf, Hk, DK)
+    Vc = chunks(v.float(), Hv, DV)
+    vm2 = valid.reshape(-1, 1).float()
+    gc = (g.float()[gather] * vm2).reshape(Nc, C, Hv).permute(0, 2, 1)          # [Nc, Hv, C]
+    bc = (beta.float()[gather] * vm2).reshape(Nc, C, Hv).permute(0, 2, 1)
+    gamma = gc.cumsum(-1)
+    tri = torch.ones(C, C, dtype=torch.bool, device=dev).tril()                 # j >= m
+    diff = gamma.unsqueeze(-1) - gamma.unsqueeze(-2)                            # gamma_j - gamma_m
+    Gam = torch.where(tri, diff, torch.full_like(diff, float("-inf"))).exp()    # 0 above the diagonal
+    KK = (Kc @ Kc.transpose(-1, -2)).repeat_interleave(rep, dim=1)              # [Nc, Hv, C, C]
+    QK = (Qc @ Kc.transpose(-1, -2)).repeat_interleave(rep, dim=1)
+    A = (bc.unsqueeze(-1) * KK * Gam).tril(-1)
+    Kv = Kc.repeat_interleave(rep, dim=1)                                       # [Nc, Hv, C, DK]
+    eg = gamma.exp().unsqueeze(-1)
+    rhs = torch.cat([bc.unsqueeze(-1) * Vc, (bc.unsqueeze(-1) * eg) * Kv], dim=-1)
+    eye = torch.eye(C, device=dev, dtype=torch.float32)
+    sol = torch.linalg.solve_triangular(A + eye, rhs, upper=False, unitriangular=True)
+    Up, W = sol[..., :DV], sol[..., DV:]                                        # U', W
+    Aqk = QK * Gam                                                              # lower incl. diagonal
+    Qg = Qc.repeat_interleave(rep, dim=1) * eg
+    g_last = gamma[..., -1:]
+    Kd = Kv * (g_last - gamma).exp().unsqueeze(-1)
+    decay = g_last.exp().unsqueeze(-1)                                          # [Nc, Hv, 1, 1]
+
+    sl = slots[torch.from_numpy(seqs).to(dev)].long()
+    init = has_init[torch.from_numpy(seqs).to(dev)].reshape(-1, 1, 1, 1).to(torch.float32)
+    S = state[sl].float() * (init != 0).float()                                 # [ns, Hv, DK, DV]
+    O = torch.empty((Nc, Hv, C, DV), dtype=torch.float32, device=dev)
+    first_t = torch.from_numpy(first).to(dev)
+    for i in range(int(nch.max())):
+        live = int((nch > i).sum())                 # sequences 0..live-1 have an i-th chunk
+        ids = first_t[:live] + i
+        Si = S[:live]
+        U = Up[ids] - W[ids] @ Si
+        O[ids] = Qg[ids] @ Si + Aqk[ids] @ U
+        S[:live] = decay[ids] * Si + Kd[ids].transpose(-1, -2) @ U
+    state[sl] = S.to(state.dtype)
+    rows = O.permute(0, 2, 1, 3).reshape(Nc * C, Hv, DV)
+    sel = valid.reshape(-1)
+    out[gather[sel]] = rows[sel].to(out.dtype)
+    return out
+
+
+def _chunk_min() -> int:
+    from .. import envs
+    return int(envs.VLLM_B200_GDN_CHUNK_MIN)
+
+
+def gated_delta_rule(q, k, v, g, beta, state, cu, slots, has_init, scale, l2norm=True, cu_cpu=None):
+    """``cu_cpu`` (host copy of ``cu``) lets long sequences (>= ``VLLM_B200_GDN_CHUNK_MIN`` new tokens:
+    prefill chunks) take the chunk-parallel form while decode and verification rows stay on the
+    per-token recurrence."""
+    if cu_cpu is not None and _chunk_min() > 0:
+        import numpy as np
+        cu_h = np.asarray(cu_cpu, dtype=np.int64)[:cu.numel()]
+        lens = np.diff(cu_h)
+        long_ = np.nonzero(lens >= _chunk_min())[0]
+        if long_.size:
+            out = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+            gated_delta_rule_chunked(q, k, v, g, beta, state, cu_h, slots, has_init, scale, l2norm,
+                                     seqs=long_, out=out)
+            short = np.nonzero((lens < _chunk_min()) & (lens > 0))[0]
+            if short.size:
+                rows = np.concatenate([np.arange(cu_h[b], cu_h[b + 1]) for b in short])
+                rows_t = torch.from_numpy(rows).to(q.device)
+                sel = torch.from_numpy(short).to(q.device)
+                cu_s = torch.from_numpy(np.concatenate([[0], np.cumsum(lens[short])]).astype(np.int32)).to(q.device)
+                out[rows_t] = gated_delta_rule(q[rows_t].contiguous(), k[rows_t].contiguous(), v[rows_t].contiguous(),
+                                               g[rows_t], beta[rows_t], state, cu_s, slots[sel].contiguous(),
+                                               has_init[sel].contiguous(), scale, l2norm)
+            return out
     if not (q.is_cuda and q.dtype == torch.bfloat16):
         return gated_delta_rule_ref(q, k, v, g, beta, state, cu, slots, has_init, scale, l2norm)
     T, Hv, DV = v.shape
