@@ -504,3 +504,54 @@ def test_recompute_cpu_offload_keeps_preempted_requests_kv_on_the_host(keep):
     with pytest.raises(ValueError, match="boolean"):
         small({"kv_connector": "RecomputeCPUOffloadConnector",
                "kv_connector_extra_config": {"enable_offload_prefix_caching": "yes"}})
+
+
+def test_ucm_connector_delegates_to_an_external_cache_manager(monkeypatch):
+    """A stand-in for the external package: a dispatcher class that declares only ``stats`` itself and
+    keeps the real connector (the pool over a process-local store) as ``.connector``.  Every hook of
+    the contract must reach the inner connector: the second engine loads what the first published."""
+    import sys
+    import types
+
+    from vllm_ascend_b200.distributed.kv_transfer.kv_pool import KVPoolConnector
+    from vllm_ascend_b200.distributed.kv_transfer.ucm_connector import UCMConnector
+    calls = []
+
+    class Dispatcher:
+        def __init__(self, engine_cfg, runner):
+            import copy
+            cfg = copy.copy(engine_cfg)
+            cfg.kv_transfer_config = {"kv_connector": "KVPoolConnector",
+                                      "kv_connector_extra_config": {"backend": "memory", "name": "ucm-fake"}}
+            self.connector = KVPoolConnector(cfg, runner)
+
+        def stats(self):
+            calls.append("stats")
+            return dict(self.connector.stats, manager="fake")
+
+    mod = types.ModuleType("fake_ucm")
+    mod.Manager = Dispatcher
+    monkeypatch.setitem(sys.modules, "fake_ucm", mod)
+    extra = {"ucm_connector_module": "fake_ucm", "ucm_connector_class": "Manager"}
+
+    def mk():
+        return LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=256, max_num_seqs=4,
+                   kv_transfer_config={"kv_connector": "UCMConnectorV1", "kv_connector_extra_config": extra})
+    a, b = mk(), mk()
+    assert isinstance(b.engine.kv_connector, UCMConnector)
+    prompts = _prompts(2, lo=50, hi=90, seed=41)
+    sp = SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in a.generate(prompts, sp)]
+    a.engine.kv_connector._engine.connector.flush()
+    got = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
+    assert got == want
+    st = b.engine.kv_connector.stats()
+    assert calls == ["stats"] and st["manager"] == "fake"
+    assert st["hit_tokens"] == sum((len(p) - 1) // 16 * 16 for p in prompts) > 0
+    a.engine.kv_connector.close()
+    b.engine.kv_connector.close()
+    # a missing package is reported with the names that were tried
+    with pytest.raises(ImportError, match="no_such_ucm.UCMConnector"):
+        LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=64, max_num_seqs=2,
+            kv_transfer_config={"kv_connector": "UCMConnector",
+                                "kv_connector_extra_config": {"ucm_connector_module": "no_such_ucm"}})

@@ -25,6 +25,8 @@ _CONNECTORS = {
     "HybridConnector": ("hybrid_connector", "HybridConnector"),
     "SfaRemoteD2HConnector": ("sfa_remote_d2h", "SfaRemoteD2HConnector"),
     "MooncakeHybridConnector": ("hybrid_connector", "HybridConnector"),
+    "UCMConnector": ("ucm_connector", "UCMConnector"),
+    "UCMConnectorV1": ("ucm_connector", "UCMConnector"),
 }
 
 
