@@ -528,7 +528,9 @@ class LLM:
     def generate(self, prompts, sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  use_tqdm: bool = False, lora_request=None,
                  max_concurrency: Optional[int] = None) -> list[RequestOutput]:
-        """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids``).
+        """``prompts``: list of token-id lists (or dicts with ``prompt_token_ids`` and optionally
+        ``request_id``, ``job_id`` (the batch-job scheduler groups requests by it), ``multi_modal_data``,
+        ``prompt_embeds``, ``kv_transfer_params``).
 
         ``max_concurrency``: closed-loop admission.  At most that many requests are in flight (per
         data-parallel replica: its share of the total); the next prompt enters when one finishes.
@@ -559,18 +561,20 @@ class LLM:
                 lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
                 mmd = p.get("multi_modal_data") if isinstance(p, dict) else None
                 pe = p.get("prompt_embeds") if isinstance(p, dict) else None
+                job = p.get("job_id") if isinstance(p, dict) else None       # batch-job scheduling
+                given_id = p.get("request_id") if isinstance(p, dict) else None
                 if pe is not None and ids is None:
                     ids = []
-                rid = eng.add_request(ids, self._child_params(sp, 0), kv_transfer_params=ktp, lora_request=lr,
-                                      multi_modal_data=mmd, prompt_embeds=pe)
+                rid = eng.add_request(ids, self._child_params(sp, 0), request_id=given_id, kv_transfer_params=ktp,
+                                      job_id=job, lora_request=lr, multi_modal_data=mmd, prompt_embeds=pe)
                 order.append(rid)
                 mine.append(i)
                 reqs[rid] = eng.scheduler.requests[rid]
                 reqs[rid].client_index, reqs[rid].origin_rank = i, dp.rank_in_group
                 reqs[rid].siblings = []
                 for j in range(1, max(1, sp.n)):          # n > 1: sibling requests over the same prompt
-                    sid = eng.add_request(ids, self._child_params(sp, j), kv_transfer_params=ktp, lora_request=lr,
-                                          multi_modal_data=mmd, prompt_embeds=pe)
+                    sid = eng.add_request(ids, self._child_params(sp, j), kv_transfer_params=ktp, job_id=job,
+                                          lora_request=lr, multi_modal_data=mmd, prompt_embeds=pe)
                     reqs[rid].siblings.append(eng.scheduler.requests[sid])
 
         admit()

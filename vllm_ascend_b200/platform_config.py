@@ -85,9 +85,13 @@ class ProfilingChunkConfig:
 @dataclass
 class BatchJobSchedConfig:
     enabled: bool = False
-    max_jobs: int = 8
-    reserve_margin_blocks: int = 0
-    reserve_max_blocks: int = 0
+    max_jobs: int = 20                          # 0 = no limit
+    reserve_margin_blocks: int = 2
+    reserve_max_blocks: int = 8                 # 0 = no cap
+    low_available_tokens_threshold: int = 4096  # above: long-decode jobs first; at or below: short ones
+    short_decode_token_threshold: int = 32      # predicted decode length that separates short from long jobs
+    max_samples_per_job: int = 10               # the estimate of a job is frozen after this many samples (0 = never)
+    cold_start_requests: int = 3                # first requests of a job admitted ahead of the job ordering
 
 
 @dataclass
@@ -290,6 +294,13 @@ def _validate_scheduler_ext(s: SchedulerExtConfig, engine_cfg, dp_size: int = 1)
                               ("dyntra_lb", s.dyntra_lb_config.enabled)) if on]
     if len(chosen) > 1:
         raise ValueError(f"scheduler extensions are mutually exclusive, got {chosen}")
+    b = s.batch_job_sched_config
+    for name in ("max_jobs", "reserve_margin_blocks", "reserve_max_blocks", "max_samples_per_job",
+                 "cold_start_requests"):
+        if getattr(b, name) < 0:
+            raise ValueError(f"batch_job_sched_config.{name} must be non-negative, got {getattr(b, name)}")
+    if b.low_available_tokens_threshold <= 0 or b.short_decode_token_threshold <= 0:
+        raise ValueError("batch_job_sched_config thresholds must be positive")
     if s.short_request_first_config.enabled and s.short_request_first_config.threshold <= 0:
         raise ValueError("short_request_first_config.threshold must be positive")
     if s.profiling_chunk_config.enabled:
