@@ -4,7 +4,10 @@ Behaviour of vllm_ascend/core/short_request_first_scheduler.py:37-384: three lan
 (immediate / short / long).  Requests whose prompt is at most ``threshold`` tokens
 go to the short lane and are admitted before long ones; a long request that has
 waited ``long_max_wait_ms`` is promoted ahead of the short lane so it cannot
-starve.  Preempted requests re-enter the immediate lane.
+starve.  Preempted requests re-enter the immediate lane, and so does whatever an optional
+predicate names.  The head chosen by a peek stays the head until it is popped; a run of aged
+long requests overtaking waiting short ones is reported once per run; lane sizes and dispatch
+counts are logged every few seconds.
 """
 from __future__ import annotations
 
@@ -14,26 +17,39 @@ from typing import Optional
 
 from ..engine.request import Request, RequestStatus
 from ..engine.scheduler import Scheduler
+from ..logger import logger
 from ..platform_config import get_b200_config
 
 
 class ShortRequestFirstScheduler(Scheduler):
+    AGED_STREAK_WARNING = 8        # aged long requests dispatched in a row, with short ones waiting
+    STATS_INTERVAL_S = 5.0
+
     def __init__(self, sched_cfg, cache_cfg, num_blocks, kv_connector=None, engine_cfg=None,
-                 clock=time.monotonic):
+                 clock=time.monotonic, immediate_predicate=None):
         super().__init__(sched_cfg, cache_cfg, num_blocks, kv_connector)
         c = get_b200_config().scheduler_config.short_request_first_config
         self.threshold = c.threshold
         self.long_max_wait_ms = c.long_max_wait_ms
         self.clock = clock
+        # requests that bypass both lanes: preempted ones always, plus whatever the deployment names
+        # (e.g. requests whose KV is already on the device after a remote prefill)
+        self.immediate_predicate = immediate_predicate
         self.immediate: deque[Request] = deque()
         self.short: deque[Request] = deque()
         self.long: deque[Request] = deque()
         self._long_enqueued: dict[str, float] = {}
+        self._pinned: Optional[tuple[deque, Request, bool]] = None     # (lane, head, aged) chosen by the last peek
+        self.dispatched = {"immediate": 0, "short": 0, "long": 0, "aged_long": 0}
         self.aged_long_promotions = 0
+        self.aged_streak = 0
+        self._last_stats = clock()
         self.waiting = _LaneView(self)      # keeps the base-class bookkeeping working
 
     def _classify(self, req: Request) -> deque:
-        if req.status == RequestStatus.PREEMPTED or req.num_preemptions > 0:
+        if req.status == RequestStatus.PREEMPTED or req.num_preemptions > 0 or req.block_ids:
+            return self.immediate
+        if self.immediate_predicate is not None and self.immediate_predicate(req):
             return self.immediate
         return self.short if req.num_prompt_tokens <= self.threshold else self.long
 
@@ -42,30 +58,66 @@ class ShortRequestFirstScheduler(Scheduler):
         (lane.appendleft if front else lane.append)(req)
         if lane is self.long:
             self._long_enqueued.setdefault(req.request_id, self.clock())
+        self._pinned = None
 
     def _pick_waiting(self) -> Optional[Request]:
+        """The head to admit next.  The choice is pinned until that request is popped: the admission
+        loop peeks, checks the budget and pops, and the answer must not flip in between because a long
+        request crossed its waiting limit meanwhile."""
+        pin = self._pinned
+        if pin is not None and pin[0] and pin[0][0] is pin[1]:
+            return pin[1]
+        self._maybe_log_stats()
+        lane, aged = None, False
         if self.immediate:
-            return self.immediate[0]
-        if self.long and self.short and self.long_max_wait_ms > 0:
-            waited = (self.clock() - self._long_enqueued.get(self.long[0].request_id, self.clock())) * 1e3
-            if waited >= self.long_max_wait_ms:
-                self.aged_long_promotions += 1
-                return self.long[0]
-        if self.short:
-            return self.short[0]
-        return self.long[0] if self.long else None
+            lane = self.immediate
+        elif self.long and self.short and self.long_max_wait_ms > 0 and \
+                (self.clock() - self._long_enqueued.get(self.long[0].request_id, self.clock())) * 1e3 \
+                >= self.long_max_wait_ms:
+            lane, aged = self.long, True
+        elif self.short:
+            lane = self.short
+        elif self.long:
+            lane = self.long
+        if lane is None:
+            self._pinned = None
+            return None
+        self._pinned = (lane, lane[0], aged)
+        return lane[0]
 
-    def _pop_waiting(self, req: Request) -> None:
-        for lane in (self.immediate, self.short, self.long):
+    def _pop_waiting(self, req: Request, dispatched: bool = True) -> None:
+        pin, self._pinned = self._pinned, None
+        for name, lane in (("immediate", self.immediate), ("short", self.short), ("long", self.long)):
             if lane and lane[0] is req:
                 lane.popleft()
-                break
-        else:
-            for lane in (self.immediate, self.short, self.long):
-                if req in lane:
-                    lane.remove(req)
-                    break
+            elif req in lane:
+                lane.remove(req)
+            else:
+                continue
+            if dispatched:
+                self._account(name, pin is not None and pin[1] is req and pin[2])
+            break
         self._long_enqueued.pop(req.request_id, None)
+
+    def _account(self, lane: str, aged: bool) -> None:
+        self.dispatched[lane] += 1
+        if aged:
+            self.dispatched["aged_long"] += 1
+            self.aged_long_promotions += 1
+            self.aged_streak += 1
+            if self.aged_streak == self.AGED_STREAK_WARNING:
+                logger.warning("short-request-first: %d long requests in a row overtook %d waiting short ones "
+                               "after long_max_wait_ms=%.0f; the long lane is backlogged",
+                               self.aged_streak, len(self.short), self.long_max_wait_ms)
+        elif lane == "short":
+            self.aged_streak = 0
+
+    def _maybe_log_stats(self) -> None:
+        now = self.clock()
+        if now - self._last_stats >= self.STATS_INTERVAL_S:
+            self._last_stats = now
+            logger.info("short-request-first: waiting immediate=%d short=%d long=%d; dispatched %s",
+                        len(self.immediate), len(self.short), len(self.long), self.dispatched)
 
 
 class _LaneView:
@@ -84,7 +136,7 @@ class _LaneView:
         self.s._enqueue(req, front=True)
 
     def remove(self, req):
-        self.s._pop_waiting(req)
+        self.s._pop_waiting(req, dispatched=False)      # aborts and rotations are not dispatches
 
     def popleft(self):
         req = self.s._pick_waiting()
