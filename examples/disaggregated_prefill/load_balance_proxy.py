@@ -169,10 +169,12 @@ def _prompt_len(body: dict) -> int:
 
 
 def build_proxy(prefill_urls: list[str], decode_urls: list[str], timeout: float = 600.0, max_retries: int = 2,
-                probe_interval: float = 1.0, max_probes: int = 0) -> FastAPI:
+                probe_interval: float = 1.0, max_probes: int = 0, max_recompute_hops: int = 4) -> FastAPI:
     app = FastAPI(title="pd-load-balance-proxy")
     pools = Pools(prefill_urls, decode_urls)
     app.state.pools = pools
+    stats = {"recomputed": 0}
+    app.state.stats = stats
     stop = threading.Event()
 
     def prober():
@@ -249,7 +251,41 @@ def build_proxy(prefill_urls: list[str], decode_urls: list[str], timeout: float 
     def handle(body: dict, path: str):
         n_prompt = _prompt_len(body)
         ktp = run_prefill(body, n_prompt, path)
-        return run_decode(body, ktp, n_prompt, path)
+        out = run_decode(body, ktp, n_prompt, path)
+        # A decode instance under KV pressure hands a request back (stop_reason "recomputed") with the
+        # tokens it produced: continue from prompt + those tokens through a fresh prefill, and join
+        # the pieces.  (Streaming responses are relayed as they are: the client sees the stop reason.)
+        done_ids: list = []
+        done_text = ""
+        hops = 0
+        while isinstance(out, dict) and path == "/v1/completions" and hops < max_recompute_hops:
+            ch = (out.get("choices") or [{}])[0]
+            if ch.get("stop_reason") != "recomputed" or "prompt_token_ids" not in out:
+                break
+            hops += 1
+            stats["recomputed"] += 1
+            done_ids += list(ch.get("token_ids") or [])
+            done_text += ch.get("text") or ""
+            left = int(body.get("max_tokens") or 16) - len(done_ids)
+            if left <= 0:
+                ch["finish_reason"], ch["stop_reason"] = "length", None
+                break
+            again = dict(body, prompt=list(out["prompt_token_ids"]) + list(ch.get("token_ids") or []), max_tokens=left)
+            again.pop("kv_transfer_params", None)
+            n2 = _prompt_len(again)
+            out = run_decode(again, run_prefill(again, n2, path), n2, path)
+            body = dict(again, max_tokens=int(body.get("max_tokens") or 16))
+        if done_ids and isinstance(out, dict):
+            ch = (out.get("choices") or [{}])[0]
+            ch["token_ids"] = done_ids + list(ch.get("token_ids") or [])
+            if ch.get("text") is not None:
+                ch["text"] = done_text + ch["text"]
+            u = out.get("usage") or {}
+            u["prompt_tokens"] = n_prompt
+            u["completion_tokens"] = len(ch["token_ids"])
+            u["total_tokens"] = n_prompt + len(ch["token_ids"])
+            out["usage"] = u
+        return out
 
     @app.post("/v1/completions")
     def completions(body: dict):

@@ -555,3 +555,48 @@ def test_ucm_connector_delegates_to_an_external_cache_manager(monkeypatch):
         LLM("tiny-qwen", device="cpu", seed=0, block_size=16, max_model_len=64, max_num_seqs=2,
             kv_transfer_config={"kv_connector": "UCMConnector",
                                 "kv_connector_extra_config": {"ucm_connector_module": "no_such_ucm"}})
+
+
+def test_recompute_scheduler_hands_requests_back_under_kv_pressure():
+    """Decode node, pool too small for the batch, no host copy to park the victim on: the victim finishes
+    with stop reason "recomputed" and the tokens it produced (a prefix of the full answer), ahead of the
+    regular outputs of its step; continuing from prompt + those tokens gives the full answer."""
+    from vllm_ascend_b200.config import get_model_config
+    from vllm_ascend_b200.core.recompute import RecomputeScheduler
+    cfg = get_model_config("tiny-qwen")
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg.vocab_size, size=40).tolist() for _ in range(6)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    big = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=512, block_size=16)
+    ref = [o.outputs[0].token_ids for o in big.generate(prompts, sp)]
+    llm = LLM(cfg, device="cpu", max_model_len=128, max_num_seqs=8, max_num_batched_tokens=16, block_size=16,
+              num_gpu_blocks_override=14, enable_prefix_caching=False,
+              kv_transfer_config={"kv_connector": "NVLinkConnector", "kv_role": "kv_consumer", "engine_id": "dec-hb",
+                                  "kv_connector_extra_config": {"recompute_hand_back": True}},
+              additional_config={"scheduler_config": {"recompute_scheduler_enable": True}})
+    s = llm.engine.scheduler
+    assert isinstance(s, RecomputeScheduler) and s.hand_back
+    s.reserve_full = False
+    rids = [llm.engine.add_request(p, sp) for p in prompts]
+    finished_order = []
+    while llm.engine.has_unfinished():
+        step_done = llm.engine.step()
+        # hand-backs lead the step's list
+        kinds = [r.stop_reason == "recomputed" for r in step_done]
+        assert kinds == sorted(kinds, reverse=True)
+        finished_order += step_done
+    assert len(finished_order) == len(prompts) and s.pool.num_free_blocks == s.pool.num_blocks - 1
+    handed = [r for r in finished_order if r.stop_reason == "recomputed"]
+    assert handed and set(s.recomputed_requests) == {r.request_id for r in handed}
+    for r in finished_order:
+        want = ref[rids.index(r.request_id)]
+        got = list(r.output_token_ids or [])
+        if r.stop_reason == "recomputed":
+            assert r.status.name == "FINISHED_STOPPED" and len(got) < len(want) and got == want[:len(got)]
+            # what the proxy does next: the rest from prompt + produced tokens
+            rest = big.generate([prompts[rids.index(r.request_id)] + got],
+                                SamplingParams(temperature=0.0, max_tokens=12 - len(got), ignore_eos=True))
+            assert got + rest[0].outputs[0].token_ids == want
+        else:
+            assert got == want
+    llm.engine.kv_connector.close()

@@ -146,3 +146,49 @@ def test_proxy_routes_retries_and_grows():
     finally:
         for s in (p0, p1, d0, d1, proxy):
             s.stop()
+
+
+def test_proxy_continues_a_request_a_decode_instance_handed_back():
+    """First decode answer: three tokens and stop_reason "recomputed"; the proxy prefills prompt + those
+    tokens again, asks for the remaining tokens and joins the pieces."""
+    lb = _load()
+    seen = []
+
+    def engine(role):
+        app = FastAPI()
+
+        @app.get("/health")
+        def health():
+            return {"status": "ok"}
+
+        @app.post("/v1/completions")
+        def completions(body: dict):
+            seen.append((role, list(body["prompt"]), body["max_tokens"]))
+            if body.get("kv_transfer_params", {}).get("do_remote_decode"):
+                return {"choices": [{"token_ids": [0]}], "kv_transfer_params": {"n": len(body["prompt"])}}
+            first = sum(1 for r, _, _ in seen if r == "decode") == 1
+            if first:
+                return {"choices": [{"token_ids": [11, 12, 13], "text": "abc", "finish_reason": "stop",
+                                     "stop_reason": "recomputed"}],
+                        "prompt_token_ids": list(body["prompt"]),
+                        "usage": {"prompt_tokens": 4, "completion_tokens": 3, "total_tokens": 7}}
+            return {"choices": [{"token_ids": [14, 15], "text": "de", "finish_reason": "length", "stop_reason": None}],
+                    "usage": {"prompt_tokens": 7, "completion_tokens": 2, "total_tokens": 9}}
+        return app
+    p, d = _Server(engine("prefill")), _Server(engine("decode"))
+    proxy = lb.build_proxy([p.url], [d.url], probe_interval=0.05)
+    px = _Server(proxy)
+    try:
+        r = requests.post(px.url + "/v1/completions", json={"prompt": [1, 2, 3, 4], "max_tokens": 5}, timeout=30)
+        assert r.status_code == 200, r.text
+        out = r.json()
+    finally:
+        proxy.state.stop.set()
+        for srv in (px, p, d):
+            srv.stop()
+    ch = out["choices"][0]
+    assert ch["token_ids"] == [11, 12, 13, 14, 15] and ch["text"] == "abcde" and ch["finish_reason"] == "length"
+    assert out["usage"] == {"prompt_tokens": 4, "completion_tokens": 5, "total_tokens": 9}
+    assert seen == [("prefill", [1, 2, 3, 4], 1), ("decode", [1, 2, 3, 4], 5),
+                    ("prefill", [1, 2, 3, 4, 11, 12, 13], 1), ("decode", [1, 2, 3, 4, 11, 12, 13], 2)]
+    assert proxy.state.stats["recomputed"] == 1

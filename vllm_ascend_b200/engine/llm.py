@@ -603,7 +603,8 @@ class LLM:
             outs.append(RequestOutput(
                 request_id=rid, prompt_token_ids=r.prompt_token_ids.tolist(),
                 outputs=[CompletionOutput(j, list(c.output_token_ids or []),
-                                          finish_reason=_FINISH_REASON.get(c.status), logprobs=c.logprobs)
+                                          finish_reason=_FINISH_REASON.get(c.status), logprobs=c.logprobs,
+                                          stop_reason=c.stop_reason)
                          for j, c in enumerate(family)],
                 finished=True,
                 metrics=RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time),

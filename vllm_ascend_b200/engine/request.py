@@ -137,6 +137,7 @@ class Request:
     spec_token_ids: list = field(default_factory=list)
     num_inflight: int = 0                 # tokens sampled by steps still running on the GPU (async scheduling)
     job_id: Optional[str] = None
+    stop_reason: Optional[str] = None      # why a stopped request stopped when it was not a stop token ("recomputed")
     # multimodal: items (placeholder run + pixels), 3-axis rotary positions of the prompt and the
     # offset decoded tokens continue from (position = index + delta)
     pooled: Optional[Any] = None          # final hidden state of the last prompt token (embedding requests)
@@ -167,6 +168,7 @@ class CompletionOutput:
     text: str = ""
     finish_reason: Optional[str] = None
     logprobs: Optional[list] = None
+    stop_reason: Optional[str] = None
 
 
 @dataclass

@@ -161,12 +161,14 @@ class Scheduler:
             req.block_ids.extend(self.pool.allocate(need))
         return True
 
-    def _preempt(self, req: Request, out: SchedulerOutput) -> None:
+    def _preempt(self, req: Request, out: SchedulerOutput, parked: Optional[bool] = None) -> None:
         self.running.remove(req)
         # a connector may keep a host copy of what the request computed: it then frees the blocks
-        # itself once the copy has finished
-        hook = getattr(self.kv_connector, "request_preempted", None)
-        if hook is None or not hook(req, req.block_ids):
+        # itself once the copy has finished (``parked``: a subclass already asked it)
+        if parked is None:
+            hook = getattr(self.kv_connector, "request_preempted", None)
+            parked = hook is not None and bool(hook(req, req.block_ids))
+        if not parked:
             self.pool.free(req.block_ids)
         req.block_ids = []
         req.num_computed_tokens = 0

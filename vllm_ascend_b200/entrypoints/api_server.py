@@ -208,7 +208,7 @@ def build_app(llm, tokenizer=None, model_name: str = "model") -> FastAPI:
         text = tokenizer.decode(toks) if tokenizer is not None else None
         return {"id": rid, "object": "text_completion", "created": int(t0), "model": model_name,
                 "choices": [{"index": 0, "text": text, "token_ids": toks,
-                             "finish_reason": _FINISH.get(req.status),
+                             "finish_reason": _FINISH.get(req.status), "stop_reason": req.stop_reason,
                              "logprobs": ([{str(k): v for k, v in e.items()} for e in req.logprobs]
                                           if req.logprobs else None),
                              "prompt_logprobs": ([None if e is None else {str(k): v for k, v in e.items()}
@@ -216,7 +216,10 @@ def build_app(llm, tokenizer=None, model_name: str = "model") -> FastAPI:
                                                  if getattr(req, "prompt_logprobs", None) else None)}],
                 "usage": {"prompt_tokens": req.num_prompt_tokens, "completion_tokens": len(toks),
                           "total_tokens": req.num_prompt_tokens + len(toks)},
-                "kv_transfer_params": req.kv_transfer_params}
+                "kv_transfer_params": req.kv_transfer_params,
+                # a request handed back under KV pressure: the proxy continues it elsewhere from these
+                **({"prompt_token_ids": [int(t) for t in req.prompt_token_ids]}
+                   if req.stop_reason == "recomputed" else {})}
 
     async def _stream(ids, sp, body, chat: bool):
         """Server-sent events: one chunk per engine step that produced tokens, then ``[DONE]``."""
