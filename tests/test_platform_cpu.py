@@ -392,3 +392,34 @@ def test_pipeline_ties_cp_interleave_to_block_size_under_kv_transfer():
         P._validate_cp_kv(bad)
     bad.kv_transfer_config = None
     P._validate_cp_kv(bad)
+
+
+def test_balance_scheduler_freezes_admission_while_any_replica_is_full():
+    from vllm_ascend_b200.config import CacheConfig, SchedulerConfig
+    from vllm_ascend_b200.core.balance import BalanceScheduler
+    from vllm_ascend_b200.engine.request import Request, SamplingParams
+    peers = {"v": [0, 0]}
+    sc = SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64, max_model_len=256)
+    s = BalanceScheduler(sc, CacheConfig(block_size=16), 64, gather_fn=lambda v: [v] + peers["v"][1:], world=2)
+    assert s.collective_schedule
+
+    def add(i):
+        s.add_request(Request(request_id=f"r{i}", prompt_token_ids=list(range(1, 9)),
+                              sampling_params=SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)))
+    add(0)
+    add(1)
+    peers["v"] = [0, 4]                      # the other replica ended its last step at the cap
+    out = s.schedule()
+    assert not out.scheduled and len(s.waiting) == 2 and s.frozen_steps == 1 and s.peer_running == [0, 4]
+    peers["v"] = [0, 3]                      # it finished one: admission resumes
+    out = s.schedule()
+    assert len(out.scheduled) == 2 and not s.waiting and s.frozen_steps == 1
+    # optional lead rule: two ahead of the least loaded replica, which still has room -> wait
+    lead = BalanceScheduler(sc, CacheConfig(block_size=16), 64, gather_fn=lambda v: [v, 0], world=2, max_lead=2)
+    for i in range(3):
+        lead.add_request(Request(request_id=f"q{i}", prompt_token_ids=list(range(1, 9)),
+                                 sampling_params=SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)))
+    assert len(lead.schedule().scheduled) == 2 and len(lead.waiting) == 1
+    # a single replica never gathers
+    solo = BalanceScheduler(sc, CacheConfig(block_size=16), 64, gather_fn=lambda v: 1 / 0, world=1)
+    assert not solo.collective_schedule and solo.schedule() is not None

@@ -303,8 +303,13 @@ DYNTRA_WORKER = textwrap.dedent("""
     from vllm_ascend_b200.engine.llm import LLM
     from vllm_ascend_b200.engine.request import SamplingParams
     dp = int(sys.argv[1])
-    add = {{"scheduler_config": {{"dyntra_lb_config": {{"enabled": True, "imbalance_threshold": 0.02,
-                                                        "max_migrations_per_step": 2}}}}}} if dp > 1 else None
+    policy = sys.argv[2] if len(sys.argv) > 2 else "dyntra"
+    add = None
+    if dp > 1 and policy == "dyntra":
+        add = {{"scheduler_config": {{"dyntra_lb_config": {{"enabled": True, "imbalance_threshold": 0.02,
+                                                            "max_migrations_per_step": 2}}}}}}
+    elif dp > 1:
+        add = {{"scheduler_config": {{"enable_balance_scheduling": True}}}}
     cfg = get_model_config("tiny-qwen")
     llm = LLM(cfg, device="cpu", data_parallel_size=dp, additional_config=add, max_model_len=256, max_num_seqs=4,
               max_num_batched_tokens=64, block_size=16, num_gpu_blocks_override=64)
@@ -313,7 +318,8 @@ DYNTRA_WORKER = textwrap.dedent("""
     prompts = [rng.integers(0, cfg.vocab_size, size=(90 if i % 2 == 0 else 8)).tolist() for i in range(12)]
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
     s = llm.engine.scheduler
-    stats = [getattr(s, "migrated_out", 0), getattr(s, "migrated_in", 0), getattr(s, "paused_running", 0)]
+    stats = [getattr(s, "migrated_out", 0), getattr(s, "migrated_in", 0), getattr(s, "paused_running", 0),
+             getattr(s, "frozen_steps", -1), type(s).__name__]
     print("STATS%s " % os.environ.get("RANK", "0") + json.dumps(stats), flush=True)
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps([o.outputs[0].token_ids for o in outs]), flush=True)
@@ -323,10 +329,11 @@ DYNTRA_WORKER = textwrap.dedent("""
 """)
 
 
-def _run_dyntra(dp):
+def _run_dyntra(dp, policy="dyntra"):
     script = DYNTRA_WORKER.format(root=ROOT)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE=str(dp), OMP_NUM_THREADS="2")
-    procs = [subprocess.Popen([sys.executable, "-c", script, str(dp)], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+    procs = [subprocess.Popen([sys.executable, "-c", script, str(dp), policy],
+                              env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(dp)]
     outs = [p.communicate(timeout=300) for p in procs]
     for p, (o, e) in zip(procs, outs):
@@ -346,3 +353,14 @@ def test_dyntra_lb_balances_data_parallel_engines_without_changing_outputs():
     assert got == want
     # the loaded rank handed requests to the other one (waiting or paused running ones)
     assert stats[0][0] > 0 and stats[1][1] == stats[0][0] + stats[1][0] - stats[0][1]
+
+
+def test_balance_scheduling_on_two_data_parallel_engines():
+    """Two replicas with different loads (one finishes its share early and keeps stepping with nothing to
+    do): the per-step gather never blocks, admission freezes while a replica is full, tokens are those of a
+    single engine."""
+    want, _ = _run_dyntra(1)
+    got, stats = _run_dyntra(2, "balance")
+    assert got == want
+    assert stats[0][4] == stats[1][4] == "BalanceScheduler"
+    assert stats[0][3] > 0 or stats[1][3] > 0
