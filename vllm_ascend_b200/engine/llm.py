@@ -89,6 +89,13 @@ class LLMEngine:
         self.eos_token_id: Optional[int] = None
         self.step_times: list[float] = []
         self.host_times = {"schedule": 0.0, "execute": 0.0, "update": 0.0}
+        # schedulers that learn from step durations (profiling chunk): start-up profile + online samples
+        self._record_step = None
+        if hasattr(self.scheduler, "run_profiling"):
+            if getattr(self.scheduler, "need_timing", True):
+                self._record_step = self.scheduler.record_step
+            if cfg.parallel.pipeline_parallel_size == 1 and cfg.parallel.data_parallel_size == 1:
+                self.scheduler.run_profiling(self.runner.profile_prefill_latency)
 
     def _make_scheduler(self, num_blocks: int) -> Scheduler:
         from ..core import make_scheduler
@@ -280,6 +287,8 @@ class LLMEngine:
             if req.first_token_time is None and req.request_id in sampled:
                 req.first_token_time = now
         finished = self.scheduler.update_from_output(so, sampled)
+        if self._record_step is not None and so.scheduled:
+            self._record_step(so, t2 - t1)              # chunk-size predictor: duration of this step
         self._attach_logprobs()
         self._release_mm(finished)
         self._propose(so, sampled)

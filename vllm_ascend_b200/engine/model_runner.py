@@ -1063,6 +1063,23 @@ class ModelRunner:
         hidden = self._forward(Tp, meta)
         self._meet_lm_head(hidden)
 
+    @torch.inference_mode()
+    def profile_prefill_latency(self, num_tokens: int) -> float:
+        """Seconds of one prefill-shaped forward of ``num_tokens`` tokens of a single sequence that
+        writes nothing to the KV cache (the start-up profiling of the chunk-size predictor,
+        vllm_ascend/worker/worker.py profile_prefill_latency)."""
+        import time
+        n = int(max(1, min(num_tokens, self.max_tokens, self.max_model_len - 1)))
+        meta, T, Tp, _, _ = self._dummy_meta(1, n)
+        meta.slot_mapping.fill_(-1)
+        if self.is_cuda:
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        self._forward(Tp, meta)
+        if self.is_cuda:
+            torch.cuda.synchronize()
+        return time.perf_counter() - t0
+
     def _meet_lm_head(self, hidden: torch.Tensor) -> None:
         """A rank with nothing to sample still joins the LM head's collectives when the head is
         sharded over a fine-grained TP group."""
