@@ -120,6 +120,16 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import MiniMaxM2Config, MiniMaxM2ForCausalLM
+        yield "minimax_m2", MiniMaxM2Config(
+            vocab_size=320, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=32, num_local_experts=4, num_experts_per_tok=2,
+            max_position_embeddings=256, rms_norm_eps=1e-6, tie_word_embeddings=False,
+            rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5}), \
+            MiniMaxM2ForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MixtralConfig, MixtralForCausalLM
         yield "mixtral", MixtralConfig(**common, rms_norm_eps=1e-5, num_local_experts=4, num_experts_per_tok=2,
                                        sliding_window=None), MixtralForCausalLM
@@ -127,7 +137,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])
@@ -147,6 +157,9 @@ def test_greedy_tokens_match_transformers(name, tmp_path):
                 p.uniform_(0.5, 1.5)
             else:
                 p.normal_(0, 0.08)
+        for n, b in hf.named_buffers():
+            if n.endswith("e_score_correction_bias"):       # the selection bias must matter
+                b.uniform_(-0.3, 0.3)
     _save(hf, cfg, tmp_path / name)
     llm = LLM(str(tmp_path / name), device="cpu", dtype="float32", max_model_len=128, max_num_seqs=4,
               max_num_batched_tokens=24, block_size=16)
@@ -200,7 +213,7 @@ def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
     assert all(torch.equal(pa[k], pb[k]) for k in pa)
 
 
-@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe"])
+@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2"])
 def test_checkpoint_sharding_tp2_matches_tp1(name, tmp_path):
     """The same checkpoint directory loaded by two tensor-parallel ranks (gloo) gives the single-rank
     tokens: per-rank slicing of grouped GDN projections, gated q_proj, fused expert tensors, MLA."""

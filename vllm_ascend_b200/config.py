@@ -32,6 +32,7 @@ class ModelConfig:
     max_position_embeddings: int = 32768
     tie_word_embeddings: bool = False
     qk_norm: bool = False            # Qwen3 per-head q/k RMSNorm
+    qk_norm_full: bool = False       # MiniMax-M2: RMSNorm over the whole projected q (and k) vector, all heads together
     attention_bias: bool = False     # Qwen2 style qkv bias
     sliding_window: Optional[int] = None
     hidden_act: str = "silu"
@@ -190,6 +191,14 @@ class ModelConfig:
         if arch.startswith("Ernie4_5"):
             kw.update(rope_interleaved=True, attention_bias=bool(d.get("use_bias", False)),
                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if arch.startswith("MiniMaxM2"):
+            # sigmoid router with a selection bias and renormalised weights, rotary on the first rotary_dim
+            # channels of a head, q / k normalised over all heads at once
+            prf = rp_.get("partial_rotary_factor", d.get("partial_rotary_factor"))
+            if prf is None:                     # the published config names the rotated width instead
+                prf = float(d.get("rotary_dim", kw["head_dim"])) / kw["head_dim"]
+            kw.update(qk_norm_full=True, partial_rotary_factor=float(prf))
+            d = dict(d, scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True)
         if arch.startswith("Gemma"):
             kw.update(gemma_norm=True, embed_scale=float(hs) ** 0.5,
                       tie_word_embeddings=d.get("tie_word_embeddings", True))

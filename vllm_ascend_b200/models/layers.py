@@ -311,6 +311,11 @@ class GQAAttention:
                                         cfg.hidden_size, comm)
         self.q_norm = pf.ones((self.D,)) if cfg.qk_norm else None
         self.k_norm = pf.ones((self.D,)) if cfg.qk_norm else None
+        self.comm = comm
+        self.qk_norm_full = bool(cfg.qk_norm_full)
+        if self.qk_norm_full:      # this rank's slice of the [all heads x D] weights
+            self.q_norm = pf.ones((self.Hq * self.D,))
+            self.k_norm = pf.ones((self.Hkv * self.D,))
         self.scale = self.D ** -0.5
         self.rot_dim = int(self.D * cfg.partial_rotary_factor) // 2 * 2
         self.cos_sin = get_cos_sin_cache(self.rot_dim, max_pos, cfg.rope_theta, cfg.rope_scaling,
@@ -339,9 +344,11 @@ class GQAAttention:
         qkv_in = qkv
         if self.out_gate:          # the kernel walks (Hq + 2 Hkv) heads per row; the gate columns follow them
             qkv = qkv[:, :(self.Hq + 2 * self.Hkv) * self.D]
+        if self.qk_norm_full:
+            self._norm_over_all_heads(qkv)
         ops.qknorm_rope_kvwrite(qkv, meta.positions if mpos is None else mpos, self.cos_sin,
-                                self.rot_dim, self.q_norm,
-                                self.k_norm, self.cfg.rms_norm_eps,
+                                self.rot_dim, None if self.qk_norm_full else self.q_norm,
+                                None if self.qk_norm_full else self.k_norm, self.cfg.rms_norm_eps,
                                 k_cache if pcp is None else None, v_cache if pcp is None else None,
                                 meta.slot_mapping, self.Hq, self.Hkv, self.D,
                                 mrope_axis=None if mpos is None else self.mrope_axis)
@@ -366,6 +373,26 @@ class GQAAttention:
         if self.out_gate:
             o = o * torch.sigmoid(qkv[:, (self.Hq + 2 * self.Hkv) * self.D:].float()).to(o.dtype)
         return o
+
+
+def _norm_over_all_heads(self, qkv: torch.Tensor) -> None:
+    """RMSNorm of q over all query heads together, and of k over all KV heads (MiniMax-M2), in place.
+    Under TP a rank holds some of the heads: the sums of squares of both vectors travel in one
+    all-reduce ([T, 2] fp32); replicated KV heads count once."""
+    cfg = self.cfg
+    nq, nk = self.Hq * self.D, self.Hkv * self.D
+    q, k = qkv[:, :nq], qkv[:, nq:nq + nk]
+    qf, kf = q.float(), k.float()
+    ss = torch.stack([(qf * qf).sum(-1), (kf * kf).sum(-1) / self.kv_replicas], dim=-1)
+    if self.comm.size > 1:
+        ss = self.comm.group.all_reduce(ss)
+    inv_q = torch.rsqrt(ss[:, :1] / (cfg.num_attention_heads * self.D) + cfg.rms_norm_eps)
+    inv_k = torch.rsqrt(ss[:, 1:] / (self.total_kv * self.D) + cfg.rms_norm_eps)
+    q.copy_((qf * inv_q).to(q.dtype) * self.q_norm)
+    k.copy_((kf * inv_k).to(k.dtype) * self.k_norm)
+
+
+GQAAttention._norm_over_all_heads = _norm_over_all_heads
 
 
 _GATED_ACTS = {"silu": None, "swish": None, "gelu_pytorch_tanh": "gelu_tanh", "gelu_tanh": "gelu_tanh",

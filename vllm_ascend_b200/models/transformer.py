@@ -608,6 +608,15 @@ class CausalLM:
                             self._copy_shard(base, params[base], part, sid, tp, r)
                         loaded.add(orig_name)
                     continue
+            if name.endswith(".mlp.e_score_correction_bias"):       # MiniMax-M2 keeps the bias beside the gate
+                name = name.replace(".mlp.e_score_correction_bias", ".mlp.gate.e_score_correction_bias")
+            if self.cfg.qk_norm_full and name.endswith("self_attn.k_norm.weight") and name in params:
+                # [all KV heads x D]; ranks that replicate a KV head take the same slice
+                Hkv, n = self.cfg.num_key_value_heads, params[name].shape[0]
+                kv_rank = r if Hkv >= tp else r // (tp // Hkv)
+                params[name].copy_(w[kv_rank * n:(kv_rank + 1) * n])
+                loaded.add(orig_name)
+                continue
             if "block_sparse_moe" in name:             # Mixtral's original tensor names
                 name = name.replace("block_sparse_moe", "mlp").replace(".w1.", ".gate_proj.") \
                            .replace(".w3.", ".up_proj.").replace(".w2.", ".down_proj.")
