@@ -120,6 +120,17 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import MiniMaxConfig, MiniMaxForCausalLM
+        yield "minimax_text01", MiniMaxConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=32, num_hidden_layers=4, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
+            max_position_embeddings=256, rms_norm_eps=1e-5, tie_word_embeddings=False, block_size=16,
+            full_attn_alpha_factor=1.5, full_attn_beta_factor=0.9, linear_attn_alpha_factor=1.4,
+            linear_attn_beta_factor=1.1, mlp_alpha_factor=1.3, mlp_beta_factor=0.8,
+            rope_parameters={"rope_type": "default", "rope_theta": 10000.0}), MiniMaxForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MiniMaxM2Config, MiniMaxM2ForCausalLM
         yield "minimax_m2", MiniMaxM2Config(
             vocab_size=320, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
@@ -137,7 +148,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])
@@ -213,7 +224,7 @@ def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
     assert all(torch.equal(pa[k], pb[k]) for k in pa)
 
 
-@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2"])
+@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01"])
 def test_checkpoint_sharding_tp2_matches_tp1(name, tmp_path):
     """The same checkpoint directory loaded by two tensor-parallel ranks (gloo) gives the single-rank
     tokens: per-rank slicing of grouped GDN projections, gated q_proj, fused expert tensors, MLA."""

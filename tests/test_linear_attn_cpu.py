@@ -98,3 +98,25 @@ def test_hybrid_engine_tokens_do_not_depend_on_the_form(monkeypatch):
                   max_num_batched_tokens=32)
         outs[chunk_min] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
     assert outs["0"] == outs["8"]
+
+
+@pytest.mark.parametrize("lens", [[1, 70, 3, 200, 64, 1, 129], [1, 1, 1], [65]])
+def test_lightning_attention_batched_forms_equal_the_recurrence(lens):
+    g = torch.Generator().manual_seed(11)
+    H, D = 4, 16
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    T, B = int(cu[-1]), len(lens)
+    q, k, v = (torch.randn(T, H, D, generator=g) * 0.5 for _ in range(3))
+    log_decay = -torch.tensor([0.5, 0.1, 0.02, 1.5])
+    slots = torch.randperm(B + 2, generator=g)[:B].to(torch.int32)
+    has_init = (torch.rand(B, generator=g) > 0.4).to(torch.int32)
+    state = torch.randn(B + 2, H, D, D, generator=g) * 0.5
+    s_ref, s_got = state.clone(), state.clone()
+    cu_t = torch.tensor(cu, dtype=torch.int32)
+    want = la.lightning_attention_ref(q, k, v, log_decay, s_ref, cu_t, slots, has_init)
+    got = la.lightning_attention(q, k, v, log_decay, s_got, cu_t, slots, has_init, cu_cpu=cu, chunk=64)
+    assert (want - got).abs().max() < 1e-4
+    assert (s_ref - s_got).abs().max() < 1e-4
+    small = state.clone()
+    got16 = la.lightning_attention(q, k, v, log_decay, small, cu_t, slots, has_init, cu_cpu=cu, chunk=16)
+    assert (want - got16).abs().max() < 1e-4 and (s_ref - small).abs().max() < 1e-4

@@ -63,6 +63,11 @@ class ModelConfig:
     partial_rotary_factor: float = 1.0       # fraction of head_dim that is rotated
     rope_interleaved: bool = False           # checkpoint rotates pairs (2i, 2i+1); q / k rows are re-ordered at load
     sandwich_norm: bool = False              # extra RMSNorm on every sub-layer output (GLM-4)
+    # MiniMax-Text-01: a sub-layer reads the *normalised* stream and the stream continues from it,
+    # x = norm(s); s' = alpha * x + beta * f(x); (attention alpha, beta of full layers, of linear layers, MLP)
+    deepnorm_factors: Optional[dict] = None
+    linear_attn_kind: str = "gdn"            # "gdn" (Gated DeltaNet) | "lightning" (fixed decay per head)
+    lightning_block_size: int = 0
     split_fused_gate_up: bool = False        # checkpoint stores mlp.gate_up_proj as one [gate; up] tensor
     attn_output_gate: bool = False           # q_proj also produces a per-head sigmoid gate of the attention output
     shared_expert_gate: bool = False         # shared expert output scaled by sigmoid(x . w)
@@ -191,6 +196,14 @@ class ModelConfig:
         if arch.startswith("Ernie4_5"):
             kw.update(rope_interleaved=True, attention_bias=bool(d.get("use_bias", False)),
                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if arch == "MiniMaxForCausalLM" or arch.startswith("MiniMaxText01"):
+            lt = d.get("layer_types") or ["full_attention" if (i + 1) % 2 else "linear_attention"
+                                          for i in range(d["num_hidden_layers"])]
+            kw.update(linear_attn_kind="lightning", layer_types=list(lt), full_attention_interval=2,
+                      lightning_block_size=min(int(d.get("block_size", 256)), 64),
+                      deepnorm_factors={"full": (float(d.get("full_attn_alpha_factor", 1)), float(d.get("full_attn_beta_factor", 1))),
+                                        "linear": (float(d.get("linear_attn_alpha_factor", 1)), float(d.get("linear_attn_beta_factor", 1))),
+                                        "mlp": (float(d.get("mlp_alpha_factor", 1)), float(d.get("mlp_beta_factor", 1)))})
         if arch.startswith("MiniMaxM2"):
             # sigmoid router with a selection bias and renormalised weights, rotary on the first rotary_dim
             # channels of a head, q / k normalised over all heads at once

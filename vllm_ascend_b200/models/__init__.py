@@ -22,7 +22,8 @@ for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwe
               "Qwen2MoeForCausalLM", "Qwen3MoeForCausalLM", "MixtralForCausalLM", "DeepseekV2ForCausalLM",
               "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM", "InternLM2ForCausalLM", "Phi3ForCausalLM",
               "GemmaForCausalLM", "Qwen3NextForCausalLM", "GlmForCausalLM", "Glm4ForCausalLM",
-              "Ernie4_5ForCausalLM", "Ernie4_5_ForCausalLM", "MiniMaxM2ForCausalLM"):
+              "Ernie4_5ForCausalLM", "Ernie4_5_ForCausalLM", "MiniMaxM2ForCausalLM", "MiniMaxForCausalLM",
+              "MiniMaxText01ForCausalLM"):
     register_model(_arch, _causal_lm)
 
 

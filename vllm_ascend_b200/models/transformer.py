@@ -343,7 +343,14 @@ class DecoderLayer:
         if cfg.sandwich_norm:
             self.post_self_attn_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
             self.post_mlp_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
-        if cfg.is_linear_layer(idx):
+        self.deepnorm = None
+        if cfg.deepnorm_factors:
+            f = cfg.deepnorm_factors
+            self.deepnorm = (tuple(f["linear" if cfg.is_linear_layer(idx) else "full"]), tuple(f["mlp"]))
+        if cfg.is_linear_layer(idx) and cfg.linear_attn_kind == "lightning":
+            from .lightning import LightningAttention
+            self.self_attn = LightningAttention(pf, cfg, idx, comm)
+        elif cfg.is_linear_layer(idx):
             from .gdn import GatedDeltaNet
             self.self_attn = GatedDeltaNet(pf, cfg, idx, comm)
         else:
@@ -365,6 +372,13 @@ class DecoderLayer:
             a.o_proj = fgm.FGOProj(inner, fg.otp)
 
     def __call__(self, h, residual, meta, kv_cache):
+        if self.deepnorm is not None:
+            # the stream continues from the normalised value: s = norm(s); s = alpha s + beta f(s)
+            (aa, ab), (ma, mb) = self.deepnorm
+            x, _ = self.input_layernorm(h if residual is None else h + residual)
+            s = x * aa + self.self_attn(x, meta, kv_cache) * ab
+            y, _ = self.post_attention_layernorm(s)
+            return y * ma + self.mlp(y) * mb, None
         # a norm whose only consumer is an fp8 GEMM emits fp8 + scales directly
         qa = self._attn_in_fp8
         if residual is None:
@@ -508,7 +522,10 @@ class CausalLM:
                 yield f"{p}.post_self_attn_layernorm.weight", L.post_self_attn_layernorm.weight
                 yield f"{p}.post_mlp_layernorm.weight", L.post_mlp_layernorm.weight
             a = L.self_attn
-            if getattr(a, "is_linear_attention", False):
+            if getattr(a, "kind", "") == "lightning":
+                for n, t in a.named_tensors():
+                    yield f"{p}.self_attn.{n}", t
+            elif getattr(a, "is_linear_attention", False):
                 for attr in ("in_proj_qkvz", "in_proj_ba", "out_proj"):
                     for n, t in getattr(a, attr).named_tensors():
                         yield f"{p}.linear_attn.{attr}.{n}", t
@@ -516,6 +533,8 @@ class CausalLM:
                     yield f"{p}.linear_attn.{n}", t
             for attr in ("qkv_proj", "o_proj", "q_a_proj", "q_b_proj", "q_proj", "kv_a_proj",
                          "kv_b_proj"):
+                if getattr(a, "kind", "") == "lightning":       # yielded above under its own names
+                    break
                 lin = getattr(a, attr, None)
                 lin = getattr(lin, "inner", lin)            # fine-grained TP wrapper
                 if isinstance(lin, Linear):

@@ -219,3 +219,105 @@ def gated_delta_rule(q, k, v, g, beta, state, cu, slots, has_init, scale, l2norm
     _native.check(rc, "gated_delta_rule")
     _native.count_launch()
     return out
+
+
+# ---------------------------------------------------------------------------- lightning attention
+def lightning_attention_ref(q, k, v, log_decay, state, cu, slots, has_init):
+    """Linear attention with a fixed per-head decay (MiniMax-Text-01, Bailing linear layers):
+
+        S_t = e^{-lambda_h} S_{t-1} + k_t v_t^T          o_t = S_t^T q_t
+
+    q, k, v [T, H, D]; ``log_decay`` [H] = -lambda_h; state [slots, H, D, D] fp32 (in place).
+    Token by token: the definition the other forms are tested against."""
+    T, H, D = q.shape
+    out = torch.empty((T, H, v.shape[-1]), dtype=v.dtype, device=v.device)
+    ratio = torch.exp(log_decay.float()).view(H, 1, 1)
+    cu_l = cu.tolist()
+    for b in range(len(cu_l) - 1):
+        s = int(slots[b])
+        S = state[s].clone() if bool(has_init[b]) else torch.zeros_like(state[s])
+        for t in range(cu_l[b], cu_l[b + 1]):
+            S = ratio * S + k[t].float()[:, :, None] * v[t].float()[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, q[t].float()).to(out.dtype)
+        if cu_l[b + 1] > cu_l[b]:
+            state[s] = S
+    return out
+
+
+def lightning_attention(q, k, v, log_decay, state, cu, slots, has_init, cu_cpu, chunk=64):
+    """Same contract, two batched forms chosen per sequence from the host copy of ``cu``:
+
+    * one new token (decode): every such sequence in one batched update
+      S = r S + k v^T, o = S^T q (no per-sequence work on the host);
+    * more tokens (prefill chunks, verification): chunks of ``chunk`` tokens,
+      O = (Q K^T * decay mask) V + diag(r^i) Q S0 and S_C = r^C S0 + (r^{C-i} K)^T V,
+      all chunks' local products at once and one small update per chunk position.
+
+    The reference's kernels for this layer are its Triton lightning-attention prefill / decode
+    pair (vllm_ascend/ops/triton/mamba/lightning_attn.py)."""
+    import numpy as np
+    T, H, D = q.shape
+    DV = v.shape[-1]
+    dev = q.device
+    cu_h = np.asarray(cu_cpu, dtype=np.int64)[:cu.numel()]
+    lens = np.diff(cu_h)
+    out = torch.empty((T, H, DV), dtype=v.dtype, device=dev)
+    ld = log_decay.float().to(dev)
+    ones = np.nonzero(lens == 1)[0]
+    if ones.size:
+        rows = torch.from_numpy(cu_h[ones]).to(dev)
+        sel = torch.from_numpy(ones).to(dev)
+        sl = slots[sel].long()
+        init = (has_init[sel] != 0).float().view(-1, 1, 1, 1)
+        S = state[sl].float() * init
+        S = torch.exp(ld).view(1, H, 1, 1) * S + k[rows].float().unsqueeze(-1) * v[rows].float().unsqueeze(-2)
+        out[rows] = torch.einsum("bhkv,bhk->bhv", S, q[rows].float()).to(out.dtype)
+        state[sl] = S.to(state.dtype)
+    many = np.nonzero(lens > 1)[0]
+    if many.size == 0:
+        return out
+    order = np.argsort(-lens[many], kind="stable")
+    seqs, ln = many[order], lens[many][order]
+    C = int(chunk)
+    nch = (ln + C - 1) // C
+    first = np.concatenate([[0], np.cumsum(nch)[:-1]])
+    Nc = int(nch.sum())
+    tok = np.full((Nc, C), -1, dtype=np.int64)
+    for b, (sq, n) in enumerate(zip(seqs, ln)):
+        tok[first[b]:first[b] + nch[b]].reshape(-1)[:n] = np.arange(cu_h[sq], cu_h[sq] + n)
+    tok_t = torch.from_numpy(tok).to(dev)
+    valid = tok_t >= 0
+    gather = tok_t.clamp(min=0).reshape(-1)
+    vmask = valid.reshape(-1, 1, 1).float()
+
+    def chunks(x, dim):
+        return (x.float()[gather] * vmask).reshape(Nc, C, H, dim).permute(0, 2, 1, 3)      # [Nc, H, C, dim]
+    Qc, Kc, Vc = chunks(q, D), chunks(k, D), chunks(v, DV)
+    n_valid = valid.sum(-1).view(Nc, 1, 1).float()                      # tokens in each chunk
+    pos = torch.arange(1, C + 1, device=dev, dtype=torch.float32)       # 1-based position in the chunk
+    ldh = ld.view(1, H, 1)
+    diff = pos.view(C, 1) - pos.view(1, C)                               # i - j
+    Dm = torch.where(diff >= 0, torch.exp(ld.view(H, 1, 1) * diff.clamp(min=0)),
+                     torch.zeros((), device=dev))                       # r^(i-j) on and below the diagonal, else 0
+    intra = ((Qc @ Kc.transpose(-1, -2)) * Dm) @ Vc                      # [Nc, H, C, DV]
+    Qd = Qc * torch.exp(ldh * pos.view(1, 1, C)).unsqueeze(-1)           # r^i q_i
+    Kd = Kc * torch.exp(ldh * (n_valid - pos.view(1, 1, C)).clamp(min=0)).unsqueeze(-1)   # r^(n-j) k_j (padding rows are 0)
+    KV = Kd.transpose(-1, -2) @ Vc                                       # [Nc, H, D, DV]
+    block = torch.exp(ldh * n_valid).unsqueeze(-1)                       # r^n, [Nc, H, 1, 1]
+
+    sel = torch.from_numpy(seqs).to(dev)
+    sl = slots[sel].long()
+    S = state[sl].float() * (has_init[sel] != 0).float().view(-1, 1, 1, 1)
+    O = torch.empty((Nc, H, C, DV), dtype=torch.float32, device=dev)
+    first_t = torch.from_numpy(first).to(dev)
+    for i in range(int(nch.max())):
+        live = int((nch > i).sum())
+        ids = first_t[:live] + i
+        Si = S[:live]
+        O[ids] = intra[ids] + Qd[ids] @ Si
+        S[:live] = block[ids] * Si + KV[ids]
+    state[sl] = S.to(state.dtype)
+    rows = O.permute(0, 2, 1, 3).reshape(Nc * C, H, DV)
+    keep = valid.reshape(-1)
+    out[gather[keep]] = rows[keep].to(out.dtype)
+    return out
