@@ -120,3 +120,24 @@ def test_lightning_attention_batched_forms_equal_the_recurrence(lens):
     small = state.clone()
     got16 = la.lightning_attention(q, k, v, log_decay, small, cu_t, slots, has_init, cu_cpu=cu, chunk=16)
     assert (want - got16).abs().max() < 1e-4 and (s_ref - small).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize("Hk", [4, 1, 2])
+def test_gated_linear_attention_with_per_token_decay_and_grouped_keys(Hk):
+    """The Mamba-2 shape of the op: scalar decay per token and head, keys / queries shared by groups of heads."""
+    g_ = torch.Generator().manual_seed(21)
+    lens = [1, 40, 130, 1, 2]
+    H, N, P = 4, 8, 12
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    T, B = int(cu[-1]), len(lens)
+    q, k = torch.randn(T, Hk, N, generator=g_) * 0.5, torch.randn(T, Hk, N, generator=g_) * 0.5
+    v = torch.randn(T, H, P, generator=g_)
+    gate = -torch.rand(T, H, generator=g_) * 2.0
+    slots = torch.randperm(B + 1, generator=g_)[:B].to(torch.int32)
+    has_init = torch.tensor([1, 0, 1, 0, 1], dtype=torch.int32)
+    state = torch.randn(B + 1, H, N, P, generator=g_) * 0.5
+    s_ref, s_got = state.clone(), state.clone()
+    cu_t = torch.tensor(cu, dtype=torch.int32)
+    want = la.gated_linear_attention_ref(q, k, v, gate, s_ref, cu_t, slots, has_init)
+    got = la.gated_linear_attention(q, k, v, gate, s_got, cu_t, slots, has_init, cu_cpu=cu, chunk=32)
+    assert (want - got).abs().max() < 1e-4 and (s_ref - s_got).abs().max() < 1e-4

@@ -244,25 +244,52 @@ def lightning_attention_ref(q, k, v, log_decay, state, cu, slots, has_init):
     return out
 
 
-def lightning_attention(q, k, v, log_decay, state, cu, slots, has_init, cu_cpu, chunk=64):
-    """Same contract, two batched forms chosen per sequence from the host copy of ``cu``:
+def gated_linear_attention_ref(q, k, v, g, state, cu, slots, has_init):
+    """S_t = e^{g_t} S_{t-1} + k_t v_t^T, o_t = S_t^T q_t with a scalar log-decay per token and head.
+    q, k [T, Hk, N] (Hk divides H: grouped keys / queries), v [T, H, P], g [T, H];
+    state [slots, H, N, P] fp32 (in place).  Token by token."""
+    T, H, P = v.shape
+    rep = H // q.shape[1]
+    out = torch.empty((T, H, P), dtype=v.dtype, device=v.device)
+    qf = q.float().repeat_interleave(rep, dim=1)
+    kf = k.float().repeat_interleave(rep, dim=1)
+    cu_l = cu.tolist()
+    for b in range(len(cu_l) - 1):
+        s = int(slots[b])
+        S = state[s].clone() if bool(has_init[b]) else torch.zeros_like(state[s])
+        for t in range(cu_l[b], cu_l[b + 1]):
+            S = torch.exp(g[t].float()).view(H, 1, 1) * S + kf[t][:, :, None] * v[t].float()[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, qf[t]).to(out.dtype)
+        if cu_l[b + 1] > cu_l[b]:
+            state[s] = S
+    return out
+
+
+def gated_linear_attention(q, k, v, g, state, cu, slots, has_init, cu_cpu, chunk=64):
+    """Same contract as ``gated_linear_attention_ref``, two batched forms chosen per sequence from
+    the host copy of ``cu``:
 
     * one new token (decode): every such sequence in one batched update
-      S = r S + k v^T, o = S^T q (no per-sequence work on the host);
-    * more tokens (prefill chunks, verification): chunks of ``chunk`` tokens,
-      O = (Q K^T * decay mask) V + diag(r^i) Q S0 and S_C = r^C S0 + (r^{C-i} K)^T V,
+      S = e^g S + k v^T, o = S^T q (no per-sequence work on the host);
+    * more tokens (prefill chunks, verification): chunks of ``chunk`` tokens with cumulative
+      log-decay gamma_i inside the chunk,
+      O = (Q K^T * e^{gamma_i - gamma_j} [j <= i]) V + diag(e^{gamma_i}) Q S0 and
+      S_C = e^{gamma_C} S0 + (e^{gamma_C - gamma_j} K)^T V,
       all chunks' local products at once and one small update per chunk position.
 
-    The reference's kernels for this layer are its Triton lightning-attention prefill / decode
-    pair (vllm_ascend/ops/triton/mamba/lightning_attn.py)."""
+    This is the state-space-duality form of Mamba-2 (q = C, k = B, v = dt x, g = dt A) and, with a
+    constant g per head, lightning attention.  The reference's kernels for these layers are its
+    Triton lightning-attention prefill / decode pair and vLLM's Mamba-2 kernels
+    (vllm_ascend/ops/triton/mamba/lightning_attn.py, vllm_ascend/ops/triton/mamba/causal_conv1d.py)."""
     import numpy as np
-    T, H, D = q.shape
-    DV = v.shape[-1]
+    T, H, DV = v.shape
+    Hk, D = q.shape[1], q.shape[2]
+    rep = H // Hk
     dev = q.device
     cu_h = np.asarray(cu_cpu, dtype=np.int64)[:cu.numel()]
     lens = np.diff(cu_h)
     out = torch.empty((T, H, DV), dtype=v.dtype, device=dev)
-    ld = log_decay.float().to(dev)
+    gf = g.float()
     ones = np.nonzero(lens == 1)[0]
     if ones.size:
         rows = torch.from_numpy(cu_h[ones]).to(dev)
@@ -270,8 +297,9 @@ def lightning_attention(q, k, v, log_decay, state, cu, slots, has_init, cu_cpu, 
         sl = slots[sel].long()
         init = (has_init[sel] != 0).float().view(-1, 1, 1, 1)
         S = state[sl].float() * init
-        S = torch.exp(ld).view(1, H, 1, 1) * S + k[rows].float().unsqueeze(-1) * v[rows].float().unsqueeze(-2)
-        out[rows] = torch.einsum("bhkv,bhk->bhv", S, q[rows].float()).to(out.dtype)
+        kr = k[rows].float().repeat_interleave(rep, dim=1)
+        S = torch.exp(gf[rows]).view(-1, H, 1, 1) * S + kr.unsqueeze(-1) * v[rows].float().unsqueeze(-2)
+        out[rows] = torch.einsum("bhkv,bhk->bhv", S, q[rows].float().repeat_interleave(rep, dim=1)).to(out.dtype)
         state[sl] = S.to(state.dtype)
     many = np.nonzero(lens > 1)[0]
     if many.size == 0:
@@ -290,20 +318,21 @@ def lightning_attention(q, k, v, log_decay, state, cu, slots, has_init, cu_cpu, 
     gather = tok_t.clamp(min=0).reshape(-1)
     vmask = valid.reshape(-1, 1, 1).float()
 
-    def chunks(x, dim):
-        return (x.float()[gather] * vmask).reshape(Nc, C, H, dim).permute(0, 2, 1, 3)      # [Nc, H, C, dim]
-    Qc, Kc, Vc = chunks(q, D), chunks(k, D), chunks(v, DV)
-    n_valid = valid.sum(-1).view(Nc, 1, 1).float()                      # tokens in each chunk
-    pos = torch.arange(1, C + 1, device=dev, dtype=torch.float32)       # 1-based position in the chunk
-    ldh = ld.view(1, H, 1)
-    diff = pos.view(C, 1) - pos.view(1, C)                               # i - j
-    Dm = torch.where(diff >= 0, torch.exp(ld.view(H, 1, 1) * diff.clamp(min=0)),
-                     torch.zeros((), device=dev))                       # r^(i-j) on and below the diagonal, else 0
-    intra = ((Qc @ Kc.transpose(-1, -2)) * Dm) @ Vc                      # [Nc, H, C, DV]
-    Qd = Qc * torch.exp(ldh * pos.view(1, 1, C)).unsqueeze(-1)           # r^i q_i
-    Kd = Kc * torch.exp(ldh * (n_valid - pos.view(1, 1, C)).clamp(min=0)).unsqueeze(-1)   # r^(n-j) k_j (padding rows are 0)
-    KV = Kd.transpose(-1, -2) @ Vc                                       # [Nc, H, D, DV]
-    block = torch.exp(ldh * n_valid).unsqueeze(-1)                       # r^n, [Nc, H, 1, 1]
+    def chunks(x, heads, dim):
+        return (x.float()[gather] * vmask).reshape(Nc, C, heads, dim).permute(0, 2, 1, 3)      # [Nc, heads, C, dim]
+    Qc, Kc, Vc = chunks(q, Hk, D), chunks(k, Hk, D), chunks(v, H, DV)
+    gc = (gf[gather] * valid.reshape(-1, 1).float()).reshape(Nc, C, H).permute(0, 2, 1)         # padding: no decay
+    gamma = gc.cumsum(-1)                                                                       # [Nc, H, C]
+    tri = torch.ones(C, C, dtype=torch.bool, device=dev).tril()
+    diff = gamma.unsqueeze(-1) - gamma.unsqueeze(-2)
+    Gam = torch.where(tri, diff, torch.full_like(diff, float("-inf"))).exp()                    # 0 above the diagonal
+    QK = (Qc @ Kc.transpose(-1, -2)).repeat_interleave(rep, dim=1)                              # [Nc, H, C, C]
+    intra = (QK * Gam) @ Vc
+    Qd = Qc.repeat_interleave(rep, dim=1) * gamma.exp().unsqueeze(-1)
+    g_last = gamma[..., -1:]
+    Kd = Kc.repeat_interleave(rep, dim=1) * (g_last - gamma).exp().unsqueeze(-1)
+    KV = Kd.transpose(-1, -2) @ Vc                                                              # [Nc, H, D, DV]
+    block = g_last.exp().unsqueeze(-1)                                                          # [Nc, H, 1, 1]
 
     sel = torch.from_numpy(seqs).to(dev)
     sl = slots[sel].long()
@@ -321,3 +350,10 @@ def lightning_attention(q, k, v, log_decay, state, cu, slots, has_init, cu_cpu, 
     keep = valid.reshape(-1)
     out[gather[keep]] = rows[keep].to(out.dtype)
     return out
+
+
+def lightning_attention(q, k, v, log_decay, state, cu, slots, has_init, cu_cpu, chunk=64):
+    """Lightning attention through the batched forms of ``gated_linear_attention``: the log-decay
+    of a token is its head's constant."""
+    g = log_decay.float().to(q.device).view(1, -1).expand(q.shape[0], -1)
+    return gated_linear_attention(q, k, v, g, state, cu, slots, has_init, cu_cpu, chunk)
