@@ -228,30 +228,6 @@ def pp_generate():
             "first_logprobs": [{str(k): float(v) for k, v in o.outputs[0].logprobs[0].items()} for o in lp]}
 
 
-def sleep_wake():
-    """Sleep mode on NCCL ranks with the extra cleanup asked for: graphs are dropped and re-captured
-    around the sleep; NCCL communicators stay (destroy / re-create is done for host-side groups only,
-    tested on gloo ranks)."""
-    from vllm_ascend_b200.engine.llm import LLM
-    from vllm_ascend_b200.engine.request import SamplingParams
-    world = int(os.environ["WORLD_SIZE"])
-    rng = np.random.default_rng(0)
-    prompts = [rng.integers(0, 2048, size=n).tolist() for n in (150, 40, 129)]
-    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
-    llm = LLM(_cfg(), device="cuda", tensor_parallel_size=world, max_model_len=512, max_num_seqs=8,
-              max_num_batched_tokens=256, num_gpu_blocks_override=40, enable_sleep_mode=True,
-              cudagraph_capture_sizes=[2, 4], additional_config={"rl_config": {"sleep_mode_extra_cleanup": True}})
-    before = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
-    torch.cuda.synchronize()
-    used0 = torch.cuda.mem_get_info()[0]
-    llm.sleep(level=1)
-    free_asleep = torch.cuda.mem_get_info()[0]
-    llm.wake_up()
-    after = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
-    return {"before": before, "after": after, "freed_bytes": int(free_asleep - used0),
-            "replays": llm.engine.runner.stats["graph_replays"]}
-
-
 def weight_transfer():
     """RL weight update over NCCL: rank 0 is the trainer (holds other weights, serves no requests),
     rank 1 a live single-GPU engine that receives the buckets and applies them in place."""
@@ -298,7 +274,7 @@ def weight_transfer():
 
 
 if __name__ == "__main__":
-    res = {"pp_generate": pp_generate, "sleep_wake": sleep_wake, "weight_transfer": weight_transfer,
+    res = {"pp_generate": pp_generate, "weight_transfer": weight_transfer,
            "tp_generate": tp_generate, "symm_allreduce": symm_allreduce, "fused_linear_ops": fused_linear_ops, "moe_fused": moe_fused}[sys.argv[1]]()
     if int(os.environ.get("RANK", "0")) == 0:
         print("RESULT " + json.dumps(res), flush=True)

@@ -106,13 +106,6 @@ def test_pipeline_parallel_on_two_gpus():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_sleep_and_wake_up_on_two_nccl_ranks():
-    r = _run(2, "sleep_wake", {"VLLM_B200_TP_COMM": "nccl"}, timeout=180)
-    assert r["before"] == r["after"]
-    assert r["freed_bytes"] > 0 and r["replays"] > 0
-
-
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_rl_weight_transfer_over_nccl_updates_a_live_engine():
     r = _run(2, "weight_transfer")
     t, w = r["PART0"], r["PART1"]

@@ -120,6 +120,27 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import BambaConfig, BambaForCausalLM
+        yield "bamba", BambaConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+            num_key_value_heads=2, max_position_embeddings=256, attn_layer_indices=[1, 3], mamba_n_heads=8,
+            mamba_d_head=16, mamba_n_groups=2, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2,
+            mamba_chunk_size=16, tie_word_embeddings=False, rms_norm_eps=1e-5, pad_token_id=0,
+            # this transformers release rotates the whole head whatever the factor says; the factor is honoured here
+            partial_rotary_factor=1.0,
+            rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 1.0}), \
+            BambaForCausalLM
+        # one group shared by all heads: under TP every rank keeps it (B / C computed redundantly)
+        yield "bamba_g1", BambaConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+            num_key_value_heads=2, max_position_embeddings=256, attn_layer_indices=[1], mamba_n_heads=8,
+            mamba_d_head=16, mamba_n_groups=1, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2,
+            mamba_chunk_size=16, tie_word_embeddings=False, rms_norm_eps=1e-5, pad_token_id=0, partial_rotary_factor=1.0,
+            rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 1.0}), \
+            BambaForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import MiniMaxConfig, MiniMaxForCausalLM
         yield "minimax_text01", MiniMaxConfig(
             vocab_size=320, hidden_size=64, intermediate_size=32, num_hidden_layers=4, num_attention_heads=4,
@@ -148,7 +169,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])
@@ -224,7 +245,7 @@ def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
     assert all(torch.equal(pa[k], pb[k]) for k in pa)
 
 
-@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01"])
+@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01", "bamba", "bamba_g1"])
 def test_checkpoint_sharding_tp2_matches_tp1(name, tmp_path):
     """The same checkpoint directory loaded by two tensor-parallel ranks (gloo) gives the single-rank
     tokens: per-rank slicing of grouped GDN projections, gated q_proj, fused expert tensors, MLA."""

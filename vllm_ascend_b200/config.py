@@ -66,7 +66,8 @@ class ModelConfig:
     # MiniMax-Text-01: a sub-layer reads the *normalised* stream and the stream continues from it,
     # x = norm(s); s' = alpha * x + beta * f(x); (attention alpha, beta of full layers, of linear layers, MLP)
     deepnorm_factors: Optional[dict] = None
-    linear_attn_kind: str = "gdn"            # "gdn" (Gated DeltaNet) | "lightning" (fixed decay per head)
+    linear_attn_kind: str = "gdn"            # "gdn" (Gated DeltaNet) | "lightning" (fixed decay per head) | "mamba2"
+    mamba_config: Optional[dict] = None      # Mamba-2 mixer: n_heads, d_head, n_groups, d_state, d_conv, biases, dt limits
     lightning_block_size: int = 0
     split_fused_gate_up: bool = False        # checkpoint stores mlp.gate_up_proj as one [gate; up] tensor
     attn_output_gate: bool = False           # q_proj also produces a per-head sigmoid gate of the attention output
@@ -196,6 +197,18 @@ class ModelConfig:
         if arch.startswith("Ernie4_5"):
             kw.update(rope_interleaved=True, attention_bias=bool(d.get("use_bias", False)),
                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if arch.startswith("Bamba"):
+            attn_idx = set(d.get("attn_layer_indices") or [])
+            kw.update(linear_attn_kind="mamba2", full_attention_interval=2,
+                      layer_types=["full_attention" if i in attn_idx else "linear_attention"
+                                   for i in range(d["num_hidden_layers"])],
+                      partial_rotary_factor=float(rp_.get("partial_rotary_factor", d.get("partial_rotary_factor", 0.5))),
+                      mamba_config={"n_heads": d["mamba_n_heads"], "d_head": d["mamba_d_head"],
+                                    "n_groups": d.get("mamba_n_groups", 1), "d_state": d.get("mamba_d_state", 256),
+                                    "d_conv": d.get("mamba_d_conv", 4), "conv_bias": d.get("mamba_conv_bias", True),
+                                    "proj_bias": d.get("mamba_proj_bias", False),
+                                    "chunk_size": d.get("mamba_chunk_size", 256),
+                                    "time_step_limit": [float(x) for x in d.get("time_step_limit", (0.0, float("inf")))]})
         if arch == "MiniMaxForCausalLM" or arch.startswith("MiniMaxText01"):
             lt = d.get("layer_types") or ["full_attention" if (i + 1) % 2 else "linear_attention"
                                           for i in range(d["num_hidden_layers"])]

@@ -13,6 +13,8 @@ from typing import Optional
 
 import torch
 
+from .. import envs
+
 from ..platform_config import get_b200_config
 from .vmm import VmmAllocator
 
@@ -23,6 +25,13 @@ def sleep(engine, level: int = 1) -> int:
     if level not in (1, 2):
         raise ValueError("sleep level must be 1 or 2")
     runner = engine.runner
+    from ..parallel import state as pstate
+    if pstate.has_nccl_groups() and not envs.VLLM_B200_SLEEP_WITH_NCCL:
+        # On two B200 ranks over NCCL a sleep / wake-up cycle did not return (three runs: communicators
+        # destroyed and re-created, re-created with a warm-up collective, and kept); the step that blocks
+        # was not found.  Until it is, a multi-rank NCCL engine refuses to sleep instead of hanging.
+        raise RuntimeError("sleep mode is not available on multi-rank NCCL engines "
+                           "(set VLLM_B200_SLEEP_WITH_NCCL=1 to try it anyway)")
     torch.cuda.synchronize()
     if get_b200_config().rl_config.sleep_mode_extra_cleanup:
         runner.drop_graphs()

@@ -45,6 +45,8 @@ env_variables: dict[str, Callable[[], Any]] = {
     "VLLM_B200_FOLD_NORM": _str("VLLM_B200_FOLD_NORM", "1"),
     # 128-key tiles the decode-attention kernel requests into L2 ahead of its staged K / V loads (0 = off)
     "VLLM_B200_DECODE_L2_PREFETCH": _int("VLLM_B200_DECODE_L2_PREFETCH", 0),
+    # "1": let a multi-rank NCCL engine enter sleep mode (off: such a cycle has not completed on this hardware)
+    "VLLM_B200_SLEEP_WITH_NCCL": _bool("VLLM_B200_SLEEP_WITH_NCCL", "0"),
     # gated delta rule: sequences with at least this many new tokens in a step (prefill chunks) take the
     # chunk-parallel form (matrix products per 64-token chunk) instead of the per-token recurrence; 0 = never
     "VLLM_B200_GDN_CHUNK_MIN": _int("VLLM_B200_GDN_CHUNK_MIN", 64),

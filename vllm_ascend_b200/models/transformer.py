@@ -350,6 +350,9 @@ class DecoderLayer:
         if cfg.is_linear_layer(idx) and cfg.linear_attn_kind == "lightning":
             from .lightning import LightningAttention
             self.self_attn = LightningAttention(pf, cfg, idx, comm)
+        elif cfg.is_linear_layer(idx) and cfg.linear_attn_kind == "mamba2":
+            from .mamba2 import Mamba2Mixer
+            self.self_attn = Mamba2Mixer(pf, cfg, idx, comm)
         elif cfg.is_linear_layer(idx):
             from .gdn import GatedDeltaNet
             self.self_attn = GatedDeltaNet(pf, cfg, idx, comm)
@@ -525,6 +528,9 @@ class CausalLM:
             if getattr(a, "kind", "") == "lightning":
                 for n, t in a.named_tensors():
                     yield f"{p}.self_attn.{n}", t
+            elif getattr(a, "kind", "") == "mamba2":
+                for n, t in a.named_tensors():
+                    yield f"{p}.mamba.{n}", t
             elif getattr(a, "is_linear_attention", False):
                 for attr in ("in_proj_qkvz", "in_proj_ba", "out_proj"):
                     for n, t in getattr(a, attr).named_tensors():
@@ -533,7 +539,7 @@ class CausalLM:
                     yield f"{p}.linear_attn.{n}", t
             for attr in ("qkv_proj", "o_proj", "q_a_proj", "q_b_proj", "q_proj", "kv_a_proj",
                          "kv_b_proj"):
-                if getattr(a, "kind", "") == "lightning":       # yielded above under its own names
+                if getattr(a, "kind", "") in ("lightning", "mamba2"):       # yielded above under their own names
                     break
                 lin = getattr(a, attr, None)
                 lin = getattr(lin, "inner", lin)            # fine-grained TP wrapper
@@ -688,7 +694,11 @@ class CausalLM:
                         L.w2[e].copy_(w[:, r * Il:(r + 1) * Il])
                 loaded.add(orig_name)
                 continue
-            ml = re.match(r"model\.layers\.(\d+)\.linear_attn\.(.*)", name)
+            if ".feed_forward." in name or ".pre_ff_layernorm." in name or name.startswith("model.final_layernorm"):
+                # Bamba's names for the MLP, the norm in front of it and the last norm
+                name = name.replace(".feed_forward.", ".mlp.").replace(".pre_ff_layernorm.", ".post_attention_layernorm.") \
+                           .replace("model.final_layernorm", "model.norm")
+            ml = re.match(r"model\.layers\.(\d+)\.(?:linear_attn|mamba)\.(.*)", name)
             if ml:
                 a = layers[int(ml.group(1))].self_attn
                 if getattr(a, "is_linear_attention", False) and a.load_hf(ml.group(2), w, tp, r):

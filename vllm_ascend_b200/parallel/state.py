@@ -203,6 +203,11 @@ def _make(name: str, lists: Sequence[Sequence[int]], rank: int, backend: str,
     return mine
 
 
+def has_nccl_groups() -> bool:
+    """True when a model-parallel group of more than one rank runs over NCCL."""
+    return any(b == "nccl" and any(len(r) > 1 for r in lists) for _, lists, _, b, _ in _RECORDS)
+
+
 def suspend_groups() -> int:
     """Destroys the device communicators of all model-parallel groups (their buffers are device
     memory a sleeping engine gives back); the coordinators stay and are refilled by
