@@ -391,6 +391,26 @@ def bench_moe_route(a):
     print(f"moe gating top-{k} T={T} E={E}: {ms:.4f} ms  {T * E * 4 / ms / 1e6:.0f} GB/s of logits", flush=True)
 
 
+def bench_indexer(a):
+    """Lightning indexer (scores of every query token against its sequence's index keys + top-k), decode rows."""
+    from gpu_utils import make_paged_case
+    from vllm_ascend_b200.attention import sfa
+    B, ctx, G = a.batch, a.ctx, a.heads
+    _, kc, _, meta = make_paged_case([1] * B, [ctx] * B, 1, 1, 128, 128, device="cuda", seed=0)
+    kc = kc.cuda()
+    meta.positions = torch.full((B,), ctx, dtype=torch.int64, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q_idx = (torch.randn(B, G, 128, device="cuda", generator=g) * 0.3).bfloat16()
+    w = torch.rand(B, G, device="cuda", generator=g)
+    ms = timeit(lambda: sfa.lightning_indexer_native(q_idx, w, kc, meta, a.topk), a.iters)
+    hbm, tf, tag = peaks()
+    key_bytes = float(B) * (ctx + 1) * 128 * 2
+    fl = 2.0 * B * G * (ctx + 1) * 128
+    print(f"indexer B={B} ctx={ctx} G={G} topk={a.topk}: {ms:.4f} ms (scores + top-k)  keys {key_bytes / ms / 1e6:.0f} GB/s "
+          f"({key_bytes / ms / 1e6 / hbm:.2f} {tag})  {fl / ms / 1e9:.1f} TFLOP/s", flush=True)
+    _native.check_status(torch.device("cuda"))
+
+
 def bench_mla_pre(a):
     """Fused MLA pre-process (latent norm + rope key + cache scatter + query rope), DeepSeek-V3 head geometry."""
     from vllm_ascend_b200.ops import reference as ref
@@ -415,7 +435,7 @@ def bench_mla_pre(a):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "gemm-fp8", "gemm-folded", "attn-decode", "attn-prefill", "mla-decode", "gdn",
-                                     "norm", "rope", "sampler", "moe", "kv-copy", "quant", "moe-route", "mla-pre", "all"])
+                                     "norm", "rope", "sampler", "moe", "kv-copy", "quant", "moe-route", "mla-pre", "indexer", "all"])
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--l2-prefetch", type=int, default=0,
                     help="paired-CTA GEMM: k-blocks the L2 prefetch runs ahead (0 = off)")
@@ -483,6 +503,8 @@ def main():
                 bench_attn_decode(a)
         else:
             bench_attn_decode(a)
+    if a.what == "indexer":
+        bench_indexer(a)
     if a.what == "gdn":
         bench_gdn(a)
     if a.what in ("attn-prefill", "all"):

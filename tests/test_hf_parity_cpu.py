@@ -120,6 +120,16 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import Glm4MoeConfig, Glm4MoeForCausalLM
+        yield "glm4_moe", Glm4MoeConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+            num_attention_heads=4, num_key_value_heads=2, head_dim=16, n_routed_experts=8, n_shared_experts=1,
+            num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, max_position_embeddings=256,
+            use_qk_norm=True, attention_bias=True, tie_word_embeddings=False, routed_scaling_factor=1.5,
+            norm_topk_prob=True, rms_norm_eps=1e-5, pad_token_id=0), Glm4MoeForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import BambaConfig, BambaForCausalLM
         yield "bamba", BambaConfig(
             vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
@@ -169,7 +179,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])
@@ -245,7 +255,7 @@ def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
     assert all(torch.equal(pa[k], pb[k]) for k in pa)
 
 
-@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01", "bamba", "bamba_g1"])
+@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01", "bamba", "bamba_g1", "glm4_moe"])
 def test_checkpoint_sharding_tp2_matches_tp1(name, tmp_path):
     """The same checkpoint directory loaded by two tensor-parallel ranks (gloo) gives the single-rank
     tokens: per-rank slicing of grouped GDN projections, gated q_proj, fused expert tensors, MLA."""

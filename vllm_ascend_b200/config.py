@@ -189,7 +189,13 @@ class ModelConfig:
         )
         if d.get("shared_expert_intermediate_size"):       # Qwen2-MoE / Qwen3-Next: one gated shared expert
             kw.update(shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]), shared_expert_gate=True)
-        if arch.startswith("Glm"):
+        if arch.startswith("Glm4Moe"):
+            # GLM-4.5 / 4.6: Llama-style attention with optional per-head q / k norms, half of every head
+            # rotated (rotate-half pairing), DeepSeek-V3 style router (sigmoid, selection bias, expert groups)
+            kw.update(qk_norm=bool(d.get("use_qk_norm", False)), attention_bias=bool(d.get("attention_bias", False)),
+                      partial_rotary_factor=float(rp_.get("partial_rotary_factor", d.get("partial_rotary_factor", 0.5))))
+            d = dict(d, scoring_func="sigmoid", topk_method="noaux_tc")
+        elif arch.startswith("Glm"):
             kw.update(rope_interleaved=True, split_fused_gate_up=True, sandwich_norm=arch.startswith("Glm4"),
                       partial_rotary_factor=float(d.get("partial_rotary_factor",
                                                         (d.get("rope_parameters") or {}).get("partial_rotary_factor", 0.5))),
