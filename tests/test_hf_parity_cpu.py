@@ -130,6 +130,15 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import Ernie4_5_MoeConfig, Ernie4_5_MoeForCausalLM
+        yield "ernie45_moe", Ernie4_5_MoeConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=4,
+            num_attention_heads=4, num_key_value_heads=2, moe_num_experts=8, moe_num_shared_experts=1, moe_k=2,
+            moe_layer_start_index=1, moe_layer_end_index=2, max_position_embeddings=256, tie_word_embeddings=False,
+            use_bias=False, rms_norm_eps=1e-5, pad_token_id=0), Ernie4_5_MoeForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import BambaConfig, BambaForCausalLM
         yield "bamba", BambaConfig(
             vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
@@ -179,7 +188,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])

@@ -47,6 +47,8 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     first_k_dense_replace: int = 0   # leading dense layers (DeepSeek)
+    moe_layer_end_index: int = -1            # last MoE layer (-1: the last layer); Ernie 4.5 MoE
+    moe_layer_interval: int = 1              # every n-th layer inside [first_k_dense_replace, end] is MoE
     e_score_correction_bias: bool = False
     # ---- linear attention (Gated DeltaNet hybrids: every `full_attention_interval`-th layer is
     # softmax attention, the others keep a recurrent state instead of a KV cache) ----
@@ -131,7 +133,11 @@ class ModelConfig:
         return self.is_hybrid and (layer_idx + 1) % self.full_attention_interval != 0
 
     def is_moe_layer(self, layer_idx: int) -> bool:
-        return self.is_moe and layer_idx >= self.first_k_dense_replace
+        if not self.is_moe or layer_idx < self.first_k_dense_replace:
+            return False
+        if self.moe_layer_end_index >= 0 and layer_idx > self.moe_layer_end_index:
+            return False
+        return (layer_idx + 1) % max(self.moe_layer_interval, 1) == 0
 
     @property
     def q_head_dim(self) -> int:
@@ -234,6 +240,17 @@ class ModelConfig:
         if arch.startswith("Gemma"):
             kw.update(gemma_norm=True, embed_scale=float(hs) ** 0.5,
                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if arch.startswith("Ernie4_5_Moe"):
+            # softmax router whose selection (not the weights) is shifted by a learned bias; MoE layers from
+            # moe_layer_start_index to moe_layer_end_index, every moe_layer_interval-th
+            start = d.get("moe_layer_start_index", 0)
+            end = d.get("moe_layer_end_index", -1)
+            d = dict(d, num_experts=d.get("moe_num_experts", 0), num_experts_per_tok=d.get("moe_k", 2),
+                     n_shared_experts=d.get("moe_num_shared_experts", 0), scoring_func="softmax",
+                     topk_method="noaux_tc", norm_topk_prob=True,
+                     first_k_dense_replace=int(start if isinstance(start, int) else min(start)))
+            kw.update(moe_layer_end_index=int(end if isinstance(end, int) else max(end)),
+                      moe_layer_interval=int(d.get("moe_layer_interval", 1)))
         n_exp = d.get("num_experts") or d.get("n_routed_experts") or d.get("num_local_experts") or 0
         if n_exp:
             kw.update(

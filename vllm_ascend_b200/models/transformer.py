@@ -633,6 +633,9 @@ class CausalLM:
                             self._copy_shard(base, params[base], part, sid, tp, r)
                         loaded.add(orig_name)
                     continue
+            if name.endswith(".mlp.gate.moe_statics.e_score_correction_bias"):      # Ernie 4.5 MoE: [1, E]
+                name = name.replace(".moe_statics.", ".")
+                w = w.reshape(-1)
             if name.endswith(".mlp.e_score_correction_bias"):       # MiniMax-M2 keeps the bias beside the gate
                 name = name.replace(".mlp.e_score_correction_bias", ".mlp.gate.e_score_correction_bias")
             if self.cfg.qk_norm_full and name.endswith("self_attn.k_norm.weight") and name in params:
