@@ -139,6 +139,14 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import OlmoeConfig, OlmoeForCausalLM
+        yield "olmoe", OlmoeConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, num_experts=8, num_experts_per_tok=2, max_position_embeddings=256,
+            tie_word_embeddings=False, rms_norm_eps=1e-5, pad_token_id=0), OlmoeForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import BambaConfig, BambaForCausalLM
         yield "bamba", BambaConfig(
             vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
@@ -188,7 +196,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])

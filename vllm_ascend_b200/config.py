@@ -229,6 +229,10 @@ class ModelConfig:
                       deepnorm_factors={"full": (float(d.get("full_attn_alpha_factor", 1)), float(d.get("full_attn_beta_factor", 1))),
                                         "linear": (float(d.get("linear_attn_alpha_factor", 1)), float(d.get("linear_attn_beta_factor", 1))),
                                         "mlp": (float(d.get("mlp_alpha_factor", 1)), float(d.get("mlp_beta_factor", 1)))})
+        if arch.startswith("Olmoe"):
+            # OLMoE: q / k normalised over all heads at once, softmax router without renormalisation by default
+            kw.update(qk_norm_full=True)
+            d = dict(d, norm_topk_prob=bool(d.get("norm_topk_prob", False)))
         if arch.startswith("MiniMaxM2"):
             # sigmoid router with a selection bias and renormalised weights, rotary on the first rotary_dim
             # channels of a head, q / k normalised over all heads at once
