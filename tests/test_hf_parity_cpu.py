@@ -147,6 +147,12 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import GraniteConfig, GraniteForCausalLM
+        yield "granite", GraniteConfig(**common, rms_norm_eps=1e-5, embedding_multiplier=6.0, attention_multiplier=0.2,
+                                       residual_multiplier=0.4, logits_scaling=4.0, pad_token_id=0), GraniteForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import BambaConfig, BambaForCausalLM
         yield "bamba", BambaConfig(
             vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
@@ -196,7 +202,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])

@@ -65,6 +65,11 @@ class ModelConfig:
     partial_rotary_factor: float = 1.0       # fraction of head_dim that is rotated
     rope_interleaved: bool = False           # checkpoint rotates pairs (2i, 2i+1); q / k rows are re-ordered at load
     sandwich_norm: bool = False              # extra RMSNorm on every sub-layer output (GLM-4)
+    # Granite: fixed multipliers on the embeddings (embed_scale), the attention scores, every sub-layer output
+    # before it joins the residual stream, and the logits (divided by logits_scaling)
+    attention_multiplier: Optional[float] = None
+    residual_multiplier: float = 1.0
+    logits_scaling: float = 1.0
     # MiniMax-Text-01: a sub-layer reads the *normalised* stream and the stream continues from it,
     # x = norm(s); s' = alpha * x + beta * f(x); (attention alpha, beta of full layers, of linear layers, MLP)
     deepnorm_factors: Optional[dict] = None
@@ -229,6 +234,12 @@ class ModelConfig:
                       deepnorm_factors={"full": (float(d.get("full_attn_alpha_factor", 1)), float(d.get("full_attn_beta_factor", 1))),
                                         "linear": (float(d.get("linear_attn_alpha_factor", 1)), float(d.get("linear_attn_beta_factor", 1))),
                                         "mlp": (float(d.get("mlp_alpha_factor", 1)), float(d.get("mlp_beta_factor", 1)))})
+        if arch.startswith("Granite"):
+            kw.update(embed_scale=float(d.get("embedding_multiplier", 1.0)),
+                      attention_multiplier=float(d["attention_multiplier"]) if d.get("attention_multiplier") else None,
+                      residual_multiplier=float(d.get("residual_multiplier", 1.0)),
+                      logits_scaling=float(d.get("logits_scaling", 1.0)),
+                      tie_word_embeddings=d.get("tie_word_embeddings", True))
         if arch.startswith("Olmoe"):
             # OLMoE: q / k normalised over all heads at once, softmax router without renormalisation by default
             kw.update(qk_norm_full=True)

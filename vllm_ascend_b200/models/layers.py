@@ -316,7 +316,7 @@ class GQAAttention:
         if self.qk_norm_full:      # this rank's slice of the [all heads x D] weights
             self.q_norm = pf.ones((self.Hq * self.D,))
             self.k_norm = pf.ones((self.Hkv * self.D,))
-        self.scale = self.D ** -0.5
+        self.scale = self.D ** -0.5 if cfg.attention_multiplier is None else float(cfg.attention_multiplier)
         self.rot_dim = int(self.D * cfg.partial_rotary_factor) // 2 * 2
         self.cos_sin = get_cos_sin_cache(self.rot_dim, max_pos, cfg.rope_theta, cfg.rope_scaling,
                                          pf.device)

@@ -343,6 +343,7 @@ class DecoderLayer:
         if cfg.sandwich_norm:
             self.post_self_attn_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
             self.post_mlp_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
+        self.residual_multiplier = float(cfg.residual_multiplier)
         self.deepnorm = None
         if cfg.deepnorm_factors:
             f = cfg.deepnorm_factors
@@ -390,10 +391,14 @@ class DecoderLayer:
         else:
             x, residual = self.input_layernorm(h, residual, quant_out=qa)
         h = self.self_attn(x, meta, kv_cache)
+        if self.residual_multiplier != 1.0:
+            h = h * self.residual_multiplier
         if self.post_self_attn_layernorm is not None:
             h, _ = self.post_self_attn_layernorm(h)
         x, residual = self.post_attention_layernorm(h, residual, quant_out=self._mlp_in_fp8)
         h = self.mlp(x)
+        if self.residual_multiplier != 1.0:
+            h = h * self.residual_multiplier
         if self.post_mlp_layernorm is not None:
             h, _ = self.post_mlp_layernorm(h)
         return h, residual
@@ -507,7 +512,10 @@ class CausalLM:
         return h
 
     def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
-        return self.lm_head(hidden)
+        logits = self.lm_head(hidden)
+        if self.cfg.logits_scaling != 1.0:
+            logits = logits / self.cfg.logits_scaling
+        return logits
 
     def embed_input_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
         return self.embed_tokens(input_ids)
