@@ -5,8 +5,10 @@ The reference rewrites FX graphs with pattern-matching passes
 qknorm_rope_fusion_pass.py:31-244, muls_add_pass.py, manager
 graph_fusion_pass_manager.py:25-67).  Here there is no tracing compiler on the hot path:
 every fusion is a CUDA kernel the model code calls directly, and this table only records
-which of them are switched on (``additional_config["fusion_config"]``) so a layer can ask
-``plan.enabled("qknorm_rope")`` and tests can run the unfused op sequence as an oracle.
+which of them are switched on (``additional_config["fusion_config"]``).  The layers ask
+``get_plan().enabled(...)``: with a fusion off they run the op sequence it replaces (residual add then
+RMSNorm; q/k norm, rotary and cache write as three passes; gate_up GEMM then SiLU-mul; NCCL
+collectives around plain GEMMs), which is what tests use as the oracle of the fused kernels.
 """
 from __future__ import annotations
 
@@ -55,6 +57,19 @@ class FusionPlan:
     # pass-manager call shape: a graph goes in, the same graph comes out
     def __call__(self, graph):
         return graph
+
+
+_PLAN = None
+
+
+def get_plan() -> FusionPlan:
+    """The process-wide plan, built from the configuration on first use."""
+    global _PLAN
+    cfg = get_b200_config().fusion_config
+    if _PLAN is None or _PLAN._cfg is not cfg:
+        _PLAN = FusionPlan()
+        _PLAN._cfg = cfg
+    return _PLAN
 
 
 class EagerFusedBackend:

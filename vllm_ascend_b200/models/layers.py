@@ -186,6 +186,11 @@ class RMSNorm:
     def __call__(self, x, residual=None, quant_out: bool = False):
         """With ``quant_out`` the normalised activations come back as block-scaled fp8
         (``ops.QuantAct``) from one fused kernel, for a consumer that is an fp8 GEMM."""
+        if residual is not None and not _plan().enabled("add_rmsnorm"):
+            # the sequence the fused kernel replaces: add, then normalise
+            residual = x + residual
+            x, _ = (ops.rms_norm_quant_fp8 if quant_out else ops.rms_norm)(residual, self.weight, self.eps, None, self.gemma)
+            return x, residual
         if quant_out:
             return ops.rms_norm_quant_fp8(x, self.weight, self.eps, residual, self.gemma)
         return ops.rms_norm(x, self.weight, self.eps, residual, self.gemma)
@@ -275,6 +280,11 @@ def get_cos_sin_cache(rot_dim: int, max_pos: int, theta: float, scaling, device)
 
 
 # ---------------------------------------------------------------- attention + MLP
+def _plan():
+    from ..compilation.fusion import get_plan
+    return get_plan()
+
+
 class GQAAttention:
     """qkv proj -> fused (q/k RMSNorm + RoPE + paged KV write) -> paged attention -> o proj."""
 
@@ -346,6 +356,17 @@ class GQAAttention:
             qkv = qkv[:, :(self.Hq + 2 * self.Hkv) * self.D]
         if self.qk_norm_full:
             self._norm_over_all_heads(qkv)
+        elif not _plan().enabled("qknorm_rope") and mpos is None and pcp is None:
+            # the three passes the fused kernel replaces: q / k norm, rotary, cache write
+            eps = self.cfg.rms_norm_eps
+            if self.q_norm is not None:
+                ops.qknorm_rope_kvwrite(qkv, meta.positions, self.cos_sin, 0, self.q_norm, self.k_norm, eps,
+                                        None, None, None, self.Hq, self.Hkv, self.D)
+            ops.qknorm_rope_kvwrite(qkv, meta.positions, self.cos_sin, self.rot_dim, None, None, eps,
+                                    None, None, None, self.Hq, self.Hkv, self.D)
+            ops.qknorm_rope_kvwrite(qkv, meta.positions, self.cos_sin, 0, None, None, eps,
+                                    k_cache, v_cache, meta.slot_mapping, self.Hq, self.Hkv, self.D)
+            return self._after_kv_write(qkv_in, meta, kv_cache)
         ops.qknorm_rope_kvwrite(qkv, meta.positions if mpos is None else mpos, self.cos_sin,
                                 self.rot_dim, None if self.qk_norm_full else self.q_norm,
                                 None if self.qk_norm_full else self.k_norm, self.cfg.rms_norm_eps,
@@ -358,7 +379,10 @@ class GQAAttention:
             from ..attention.pcp import gather_kv_into_cache
             gather_kv_into_cache(qkv[:, self.Hq * self.D:], pcp, k_cache, v_cache, self.Hkv, self.D,
                                  self.cfg.rms_norm_eps, self.cos_sin)
-        qkv = qkv_in
+        return self._after_kv_write(qkv_in, meta, kv_cache)
+
+    def _after_kv_write(self, qkv: torch.Tensor, meta, kv_cache) -> torch.Tensor:
+        k_cache, v_cache = kv_cache
         T = qkv.shape[0]
         q = qkv[:, :self.Hq * self.D].view(T, self.Hq, self.D)
         from ..parallel import state as pstate
@@ -416,7 +440,8 @@ class SwiGLUMLP:
         gu = self.gate_up_proj
         if self.act is not None:
             return self.down_proj(ops.activation(gu(x).contiguous(), self.act, gated=True))
-        if gu.quant is None and gu.bias is None and not gu.gather_output and not gu._lora_on():
+        if gu.quant is None and gu.bias is None and not gu.gather_output and not gu._lora_on() \
+                and _plan().enabled("gemm_swiglu"):
             return self.down_proj(ops.linear_swiglu(x, gu.weight))
         if wants_quant_act(self.down_proj):
             return self.down_proj(ops.silu_and_mul_quant_fp8(gu(x)))

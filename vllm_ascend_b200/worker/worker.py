@@ -105,7 +105,9 @@ class B200Worker:
             self.offloader = PrefetchOffloader(self.runner.model, oc.group_size, oc.num_in_group, oc.prefetch_step)
         # the fused sequence-sharded TP path has no adapter hook: LoRA engines use the NCCL path
         self.tp_comm_calibration = None
+        from ..compilation.fusion import get_plan
         if self.world_size > 1 and cfg.device == "cuda" and envs.VLLM_B200_TP_COMM in ("fused", "auto") \
+                and get_plan().enabled("gemm_reduce_scatter") \
                 and pc.tensor_parallel_size > 1 and not cfg.enable_lora \
                 and pc.prefill_context_parallel_size == 1:
             from ..parallel import fused_linear
