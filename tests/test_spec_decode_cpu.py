@@ -239,6 +239,45 @@ def test_dynamic_speculation_length_follows_acceptance():
     clear_b200_config()
 
 
+def test_shared_verify_budget_goes_to_the_most_promising_draft_prefixes():
+    from vllm_ascend_b200.platform_config import clear_b200_config
+    from vllm_ascend_b200.spec_decode.dynamic import DynamicSpecController, VerifyBudgetAllocator
+    a = VerifyBudgetAllocator(6, {"initial_verify_budget_per_req": 3, "budget_update_interval": 2,
+                                  "budget_threshold": 0.3, "min_verify_tokens": 1})
+    probs = np.array([[0.99] * 6,            # drafts that almost surely pass
+                      [0.2] * 6,             # hopeless ones
+                      [0.9, 0.9, 0.1, 0.9, 0.9, 0.9]])
+    lens = a.allocate(probs)
+    # 3 requests x budget 3 = 9 verify tokens: everyone gets one, the other six go where survival is highest
+    assert lens.sum() == 9 and lens.tolist() == [6, 1, 2]
+    # second step: the budget is re-estimated: positions with survival >= 0.3 are 6 + 0 + 2 -> mean 2.67 -> 3 (odd)
+    lens = a.allocate(probs)
+    assert a.budget_k == 3 and lens.tolist() == [6, 1, 2]
+    good = np.full((2, 6), 0.95)
+    a.allocate(good)
+    a.allocate(good)                           # update step: 6 positions each -> 6 (the maximum; no odd bump past it)
+    assert a.budget_k == 6 and a.allocate(good).tolist() == [6, 6]
+    even = VerifyBudgetAllocator(6, {"budget_update_interval": 1, "budget_threshold": 0.5})
+    even.allocate(np.array([[0.9, 0.9, 0.9, 0.9, 0.1, 0.1]]))      # 4 positions above 0.5 -> bumped to 5
+    assert even.budget_k == 5
+    # controller: the per-request estimates stand in when the proposer has no confidences
+    c = DynamicSpecController(4, {"shared_budget": True, "initial_verify_budget_per_req": 2, "ema_alpha": 1.0})
+    c.update("hot", 4, 4)
+    c.update("cold", 4, 0)
+    assert c.budgets(["hot", "cold"]) == [3, 1]
+    assert DynamicSpecController(4, {}).budgets(["x"]) == [DynamicSpecController(4, {}).budget("x")]
+    # engine run on the shared budget: exact greedy output
+    kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=40)
+    prompts = [[7, 8, 9, 10, 11, 12] * 3, [3, 4, 5] * 4]
+    sp = SamplingParams(max_tokens=16, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM("tiny-qwen", **kw).generate(prompts, sp)]
+    dyn = LLM("tiny-qwen", speculative_config={"method": "ngram", "num_speculative_tokens": 4}, additional_config={
+        "dynamic_spec_config": {"method": "acceptance", "method_params": {"shared_budget": True}}}, **kw)
+    assert [o.outputs[0].token_ids for o in dyn.generate(prompts, sp)] == want
+    assert dyn.engine.runner.dynamic_spec.allocator is not None
+    clear_b200_config()
+
+
 def test_extract_hidden_states_records_every_position(tmp_path):
     kw = dict(device="cpu", seed=0, block_size=16, max_model_len=160, max_num_seqs=4, max_num_batched_tokens=24)
     prompts = [[7, 8, 9, 10, 11, 12] * 6, [3, 4, 5] * 4]

@@ -1048,10 +1048,15 @@ class ModelRunner:
         rows = np.fromiter((r.row for r in reqs), dtype=np.int64, count=len(reqs))
         lens = np.fromiter((r.num_tokens for r in reqs), dtype=np.int64, count=len(reqs))
         props = self.proposer.propose(self.token_ids_cpu, lens, rows)
-        for r, p in zip(reqs, props):
+        budgets = None
+        if self.dynamic_spec is not None:
+            # confidences of this step's draft tokens, when the proposer has them ([B, k], padded with 0)
+            budgets = self.dynamic_spec.budgets([r.request_id for r in reqs],
+                                                getattr(self.proposer, "last_token_probs", None))
+        for i, (r, p) in enumerate(zip(reqs, props)):
             left = r.sampling_params.max_tokens - r.num_output_tokens - 1
-            if self.dynamic_spec is not None:
-                left = min(left, self.dynamic_spec.budget(r.request_id))
+            if budgets is not None:
+                left = min(left, budgets[i])
             r.spec_token_ids = [int(t) for t in p[:max(left, 0)]]
 
     @torch.inference_mode()
