@@ -59,9 +59,10 @@ def test_gated_delta_rule_kernel(Hk, Hv, DK, DV):
     assert (S_dev.cpu() - S_ref).abs().max() < 2e-2
 
 
-def test_chunk_parallel_delta_rule_on_device():
-    """bf16 inputs on the device: the chunked form (fp32 matrix products) and the recurrence kernel
+def test_chunk_parallel_delta_rule_on_device(monkeypatch):
+    """bf16 inputs on the device (the form is opt-in there): the chunked form (fp32 matrix products) and the recurrence kernel
     both against the fp32 definition, mixed step routed by sequence length."""
+    monkeypatch.setenv("VLLM_B200_GDN_CHUNK_MIN", "64")
     g = torch.Generator().manual_seed(4)
     lens = [300, 1, 64, 130, 2]
     cu_h = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)

@@ -48,7 +48,8 @@ env_variables: dict[str, Callable[[], Any]] = {
     # "1": let a multi-rank NCCL engine enter sleep mode (off: such a cycle has not completed on this hardware)
     "VLLM_B200_SLEEP_WITH_NCCL": _bool("VLLM_B200_SLEEP_WITH_NCCL", "0"),
     # gated delta rule: sequences with at least this many new tokens in a step (prefill chunks) take the
-    # chunk-parallel form (matrix products per 64-token chunk) instead of the per-token recurrence; 0 = never
+    # chunk-parallel form (matrix products per 64-token chunk) instead of the per-token recurrence; 0 = never.
+    # Unset: 64 for host tensors, never on the GPU (the recurrence kernel is faster there)
     "VLLM_B200_GDN_CHUNK_MIN": _int("VLLM_B200_GDN_CHUNK_MIN", 64),
     # "1": the slot of every token is computed on the device from the block table (one small kernel per
     # step) instead of on the host; "0" (default): host numpy + copy
