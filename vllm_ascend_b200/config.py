@@ -73,6 +73,9 @@ class ModelConfig:
     # MiniMax-Text-01: a sub-layer reads the *normalised* stream and the stream continues from it,
     # x = norm(s); s' = alpha * x + beta * f(x); (attention alpha, beta of full layers, of linear layers, MLP)
     deepnorm_factors: Optional[dict] = None
+    # hyper-connections: the residual stream is hc_mult parallel streams mixed by learned weights (0 / 1 = plain residual)
+    hc_mult: int = 0
+    hc_sinkhorn_iters: int = 20
     linear_attn_kind: str = "gdn"            # "gdn" (Gated DeltaNet) | "lightning" (fixed decay per head) | "mamba2"
     mamba_config: Optional[dict] = None      # Mamba-2 mixer: n_heads, d_head, n_groups, d_state, d_conv, biases, dt limits
     lightning_block_size: int = 0
@@ -234,6 +237,8 @@ class ModelConfig:
                       deepnorm_factors={"full": (float(d.get("full_attn_alpha_factor", 1)), float(d.get("full_attn_beta_factor", 1))),
                                         "linear": (float(d.get("linear_attn_alpha_factor", 1)), float(d.get("linear_attn_beta_factor", 1))),
                                         "mlp": (float(d.get("mlp_alpha_factor", 1)), float(d.get("mlp_beta_factor", 1)))})
+        if d.get("hc_mult"):
+            kw.update(hc_mult=int(d["hc_mult"]), hc_sinkhorn_iters=int(d.get("hc_sinkhorn_iters", 20)))
         if arch.startswith("Granite"):
             kw.update(embed_scale=float(d.get("embedding_multiplier", 1.0)),
                       attention_multiplier=float(d["attention_multiplier"]) if d.get("attention_multiplier") else None,

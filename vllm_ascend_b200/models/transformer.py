@@ -344,6 +344,13 @@ class DecoderLayer:
             self.post_self_attn_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
             self.post_mlp_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
         self.residual_multiplier = float(cfg.residual_multiplier)
+        self.hc_attn = self.hc_ffn = None
+        if cfg.hc_mult > 1:
+            from ..ops.hyper_connection import HyperConnection
+            self.hc_attn = HyperConnection(pf, f"{p}.hc_attn", cfg.hidden_size, cfg.hc_mult, cfg.hc_sinkhorn_iters,
+                                           cfg.rms_norm_eps)
+            self.hc_ffn = HyperConnection(pf, f"{p}.hc_ffn", cfg.hidden_size, cfg.hc_mult, cfg.hc_sinkhorn_iters,
+                                          cfg.rms_norm_eps)
         self.deepnorm = None
         if cfg.deepnorm_factors:
             f = cfg.deepnorm_factors
@@ -376,6 +383,16 @@ class DecoderLayer:
             a.o_proj = fgm.FGOProj(inner, fg.otp)
 
     def __call__(self, h, residual, meta, kv_cache):
+        if self.hc_attn is not None:
+            # h: the widened residual streams [T, m, H]; each sub-layer reads a mixture and writes back
+            from ..ops.hyper_connection import hc_post
+            streams = h
+            x, post, comb = self.hc_attn.pre(streams)
+            x, _ = self.input_layernorm(x)
+            streams = hc_post(self.self_attn(x, meta, kv_cache), streams, post, comb)
+            x, post, comb = self.hc_ffn.pre(streams)
+            x, _ = self.post_attention_layernorm(x)
+            return hc_post(self.mlp(x), streams, post, comb), None
         if self.deepnorm is not None:
             # the stream continues from the normalised value: s = norm(s); s = alpha s + beta f(s)
             (aa, ab), (ma, mb) = self.deepnorm
@@ -450,6 +467,14 @@ class CausalLM:
         self.layers = [DecoderLayer(pf, cfg, i, self.comm, max_pos, ep_group, moe_runtime)
                        for i in range(lo, hi)]
         self.norm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
+        self.hc_head = None
+        if cfg.hc_mult > 1:
+            if not (self.is_first and self.is_last):
+                raise ValueError("hyper-connections: the widened residual streams are not carried between pipeline stages")
+            m = cfg.hc_mult
+            self.hc_head = (pf.normal("model.hc_head_fn", (m, m * cfg.hidden_size), std=1.0 / (m * cfg.hidden_size) ** 0.5,
+                                      dtype=torch.float32),
+                            pf.ones((1,), dtype=torch.float32), pf.zeros((m,), dtype=torch.float32))
         if cfg.tie_word_embeddings:
             self.lm_head = ParallelLMHead(self.embed_tokens)
         else:
@@ -482,6 +507,8 @@ class CausalLM:
             h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
             if self.cfg.embed_scale != 1.0 and inputs_embeds is None:
                 h = h * torch.tensor(self.cfg.embed_scale, dtype=h.dtype)      # rounded to the model dtype first
+            if self.hc_head is not None:
+                h = h.unsqueeze(1).repeat(1, self.cfg.hc_mult, 1)              # [T, H] -> [T, m, H]
             residual = None
         else:
             h, residual = intermediate
@@ -501,13 +528,16 @@ class CausalLM:
                 h.index_add_(0, deepstack[0], deepstack[1][layer.idx].to(h.dtype))
             if aux is not None:
                 for _ in range(self.aux_layers.count(layer.idx)):
-                    aux.append(h + residual)
+                    aux.append(h if residual is None else h + residual)
             if self.layer_hook is not None:
                 self.layer_hook(layer.idx - self.layer_range[0])   # e.g. layer-wise KV push
         if aux:
             self.aux_hidden = torch.cat(aux, dim=-1)
         if not self.is_last:
             return h, residual
+        if self.hc_head is not None:
+            from ..ops.hyper_connection import hc_head
+            h = hc_head(h, self.hc_head[0], self.hc_head[1], self.hc_head[2], self.cfg.rms_norm_eps)
         h, _ = self.norm(h, residual)
         return h
 
@@ -529,6 +559,9 @@ class CausalLM:
             p = f"model.layers.{L.idx}"
             yield f"{p}.input_layernorm.weight", L.input_layernorm.weight
             yield f"{p}.post_attention_layernorm.weight", L.post_attention_layernorm.weight
+            if L.hc_attn is not None:
+                yield from L.hc_attn.named_tensors(f"{p}.hc_attn")
+                yield from L.hc_ffn.named_tensors(f"{p}.hc_ffn")
             if L.post_self_attn_layernorm is not None:
                 yield f"{p}.post_self_attn_layernorm.weight", L.post_self_attn_layernorm.weight
                 yield f"{p}.post_mlp_layernorm.weight", L.post_mlp_layernorm.weight
@@ -588,6 +621,10 @@ class CausalLM:
                 for n, t in m.down_proj.named_tensors():
                     yield f"{p}.mlp.down_proj.{n}", t
         yield "model.norm.weight", self.norm.weight
+        if self.hc_head is not None:
+            yield "model.hc_head_fn", self.hc_head[0]
+            yield "model.hc_head_scale", self.hc_head[1]
+            yield "model.hc_head_base", self.hc_head[2]
         if not self.cfg.tie_word_embeddings:
             yield "lm_head.weight", self.lm_head.weight
 
