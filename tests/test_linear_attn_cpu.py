@@ -141,3 +141,30 @@ def test_gated_linear_attention_with_per_token_decay_and_grouped_keys(Hk):
     want = la.gated_linear_attention_ref(q, k, v, gate, s_ref, cu_t, slots, has_init)
     got = la.gated_linear_attention(q, k, v, gate, s_got, cu_t, slots, has_init, cu_cpu=cu, chunk=32)
     assert (want - got).abs().max() < 1e-4 and (s_ref - s_got).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize("chunk", [8, 16])
+def test_kda_chunked_form_equals_the_per_channel_recurrence(chunk):
+    g_ = torch.Generator().manual_seed(31)
+    lens = [1, 21, 40, 16]
+    H, DK, DV = 3, 8, 12
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    T, B = int(cu[-1]), len(lens)
+    q, k = torch.randn(T, H, DK, generator=g_), torch.randn(T, H, DK, generator=g_)
+    v = torch.randn(T, H, DV, generator=g_)
+    gate = -torch.rand(T, H, DK, generator=g_) * 3.0                    # a different decay for every key channel
+    beta = torch.rand(T, H, generator=g_)
+    slots = torch.tensor([2, 0, 4, 1], dtype=torch.int32)
+    has_init = torch.tensor([1, 0, 1, 1], dtype=torch.int32)
+    state = torch.randn(5, H, DK, DV, generator=g_) * 0.5
+    s_ref, s_got = state.clone(), state.clone()
+    want = la.kda_recurrent_ref(q, k, v, gate, beta, s_ref, torch.tensor(cu, dtype=torch.int32), slots, has_init, 0.3)
+    got = la.kda_chunked(q, k, v, gate, beta, s_got, cu, slots, has_init, 0.3, chunk=chunk)
+    assert (want - got).abs().max() < 1e-4 and (s_ref - s_got).abs().max() < 1e-4
+    assert torch.equal(s_got[3], state[3])                              # the unused slot
+    # with the same decay on every channel it is the scalar-gated delta rule
+    flat = gate[:, :, :1].expand(-1, -1, DK).contiguous()
+    a, b = state.clone(), state.clone()
+    x = la.kda_recurrent_ref(q, k, v, flat, beta, a, torch.tensor(cu, dtype=torch.int32), slots, has_init, 0.3)
+    y = la.gated_delta_rule_ref(q, k, v, flat[:, :, 0], beta, b, torch.tensor(cu, dtype=torch.int32), slots, has_init, 0.3)
+    assert (x - y).abs().max() < 1e-5 and (a - b).abs().max() < 1e-5

@@ -364,3 +364,83 @@ def lightning_attention(q, k, v, log_decay, state, cu, slots, has_init, cu_cpu, 
     of a token is its head's constant."""
     g = log_decay.float().to(q.device).view(1, -1).expand(q.shape[0], -1)
     return gated_linear_attention(q, k, v, g, state, cu, slots, has_init, cu_cpu, chunk)
+
+
+# ---------------------------------------------------------------------------- KDA (delta rule, per-channel decay)
+def kda_recurrent_ref(q, k, v, g, beta, state, cu, slots, has_init, scale, l2norm=True):
+    """Delta rule whose decay is a vector over the key channels (Kimi delta attention):
+
+        S_t = diag(e^{g_t}) S_{t-1};  u_t = beta_t (v_t - S_t^T k_t);  S_t += k_t u_t^T;  o_t = S_t^T q_t
+
+    q, k [T, H, DK]; v [T, H, DV]; g [T, H, DK] (log-decay per key channel); beta [T, H];
+    state [slots, H, DK, DV] fp32 (in place).  Token by token
+    (vllm_ascend/ops/triton/kda/fused_recurrent_kda.py:98-136 is the same recurrence as a kernel)."""
+    T, H, DV = v.shape
+    out = torch.empty((T, H, DV), dtype=v.dtype, device=v.device)
+    qf, kf = q.float(), k.float()
+    if l2norm:
+        qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6)
+        kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+    qf = qf * scale
+    cu_l = cu.tolist()
+    for b in range(len(cu_l) - 1):
+        s = int(slots[b])
+        S = state[s].clone() if bool(has_init[b]) else torch.zeros_like(state[s])
+        for t in range(cu_l[b], cu_l[b + 1]):
+            S = S * torch.exp(g[t].float())[:, :, None]
+            u = (v[t].float() - torch.einsum("hkv,hk->hv", S, kf[t])) * beta[t].float()[:, None]
+            S = S + kf[t][:, :, None] * u[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, qf[t]).to(out.dtype)
+        if cu_l[b + 1] > cu_l[b]:
+            state[s] = S
+    return out
+
+
+def kda_chunked(q, k, v, g, beta, state, cu_cpu, slots, has_init, scale, l2norm=True, chunk=16):
+    """Chunk-parallel form of ``kda_recurrent_ref`` for one step's sequences (host boundaries
+    ``cu_cpu``).  As for the scalar-gated rule, U solves a unit-lower-triangular system per chunk; the
+    pairwise decays e^{gamma_j - gamma_m} differ per key channel, so the chunk-local products are
+    contractions over (channel) of k_j k_m e^{gamma_j - gamma_m}, formed exactly (only non-positive
+    exponents are ever exponentiated) for a short chunk
+    (vllm_ascend/ops/triton/kda/kda.py, chunk_delta_h.py, solve_tril.py are the reference's kernels)."""
+    import numpy as np
+    T, H, DV = v.shape
+    DK = q.shape[2]
+    dev = q.device
+    cu_h = np.asarray(cu_cpu, dtype=np.int64)
+    out = torch.empty((T, H, DV), dtype=v.dtype, device=dev)
+    qf, kf = q.float(), k.float()
+    if l2norm:
+        qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6)
+        kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+    qf = qf * scale
+    C = int(chunk)
+    tri = torch.ones(C, C, dtype=torch.bool, device=dev).tril()
+    eye = torch.eye(C, device=dev)
+    for b in range(len(cu_h) - 1):
+        t0, t1 = int(cu_h[b]), int(cu_h[b + 1])
+        if t1 <= t0:
+            continue
+        s = int(slots[b])
+        S = state[s].float().clone() if bool(has_init[b]) else torch.zeros_like(state[s], dtype=torch.float32)
+        for c0 in range(t0, t1, C):
+            c1 = min(c0 + C, t1)
+            n = c1 - c0
+            Q, K, V = (x[c0:c1].permute(1, 0, 2) for x in (qf, kf, v.float()))            # [H, n, *]
+            G = g[c0:c1].float().permute(1, 0, 2).cumsum(1)                               # gamma [H, n, DK]
+            Bt = beta[c0:c1].float().t()                                                  # [H, n]
+            diff = G.unsqueeze(2) - G.unsqueeze(1)                                        # gamma_j - gamma_m [H, n, n, DK]
+            dec = torch.where(tri[:n, :n, None], diff, torch.full_like(diff, float("-inf"))).exp()
+            KK = torch.einsum("hjd,hmd,hjmd->hjm", K, K, dec)
+            QK = torch.einsum("hjd,hmd,hjmd->hjm", Q, K, dec)
+            A = (Bt.unsqueeze(-1) * KK).tril(-1)
+            eG = G.exp()                                                                   # e^{gamma_j}, per channel
+            rhs = torch.cat([Bt.unsqueeze(-1) * V, Bt.unsqueeze(-1) * (K * eG)], dim=-1)
+            sol = torch.linalg.solve_triangular(A + eye[:n, :n], rhs, upper=False, unitriangular=True)
+            U = sol[..., :DV] - sol[..., DV:] @ S                                          # [H, n, DV]
+            O = (Q * eG) @ S + QK @ U
+            out[c0:c1] = O.permute(1, 0, 2).to(out.dtype)
+            last = G[:, -1:, :]
+            S = last.transpose(1, 2).exp() * S + (K * (last - G).exp()).transpose(1, 2) @ U
+        state[s] = S.to(state.dtype)
+    return out
