@@ -153,6 +153,17 @@ def _cases():
     except ImportError:
         pass
     try:
+        from transformers import GraniteMoeHybridConfig, GraniteMoeHybridForCausalLM
+        yield "granite4_hybrid", GraniteMoeHybridConfig(
+            vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+            num_key_value_heads=2, max_position_embeddings=256, layer_types=["mamba", "attention", "mamba"],
+            mamba_n_heads=8, mamba_d_head=16, mamba_n_groups=2, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2,
+            mamba_chunk_size=16, num_local_experts=0, shared_intermediate_size=96, position_embedding_type="nope",
+            tie_word_embeddings=False, embedding_multiplier=3.0, attention_multiplier=0.2, residual_multiplier=0.5,
+            logits_scaling=2.0, rms_norm_eps=1e-5, pad_token_id=0), GraniteMoeHybridForCausalLM
+    except ImportError:
+        pass
+    try:
         from transformers import BambaConfig, BambaForCausalLM
         yield "bamba", BambaConfig(
             vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
@@ -202,7 +213,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "granite4_hybrid", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])
@@ -278,7 +289,7 @@ def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
     assert all(torch.equal(pa[k], pb[k]) for k in pa)
 
 
-@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01", "bamba", "bamba_g1", "glm4_moe"])
+@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01", "bamba", "bamba_g1", "glm4_moe", "granite4_hybrid"])
 def test_checkpoint_sharding_tp2_matches_tp1(name, tmp_path):
     """The same checkpoint directory loaded by two tensor-parallel ranks (gloo) gives the single-rank
     tokens: per-rank slicing of grouped GDN projections, gated q_proj, fused expert tensors, MLA."""

@@ -217,6 +217,22 @@ class ModelConfig:
         if arch.startswith("Ernie4_5"):
             kw.update(rope_interleaved=True, attention_bias=bool(d.get("use_bias", False)),
                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if arch.startswith("GraniteMoeHybrid"):
+            # Granite 4 hybrids: Mamba-2 / attention layers by layer_types, attention without rotary
+            # ("nope"), a gated MLP stored as one fused input projection (dense form: no routed experts)
+            if d.get("num_local_experts"):
+                raise ValueError("GraniteMoeHybrid with routed experts is not supported (dense shared MLP only)")
+            lt = [("full_attention" if t == "attention" else "linear_attention") for t in d["layer_types"]]
+            kw.update(linear_attn_kind="mamba2", full_attention_interval=2, layer_types=lt, split_fused_gate_up=True,
+                      intermediate_size=int(d.get("shared_intermediate_size", kw["intermediate_size"])),
+                      partial_rotary_factor=0.0 if d.get("position_embedding_type", "rope") == "nope" else 1.0,
+                      mamba_config={"n_heads": d["mamba_n_heads"], "d_head": d["mamba_d_head"],
+                                    "n_groups": d.get("mamba_n_groups", 1), "d_state": d.get("mamba_d_state", 256),
+                                    "d_conv": d.get("mamba_d_conv", 4), "conv_bias": d.get("mamba_conv_bias", True),
+                                    "proj_bias": d.get("mamba_proj_bias", False),
+                                    "chunk_size": d.get("mamba_chunk_size", 256),
+                                    "time_step_limit": [float(x) for x in d.get("time_step_limit", (0.0, float("inf")))]})
+            d = dict(d, num_local_experts=0)
         if arch.startswith("Bamba"):
             attn_idx = set(d.get("attn_layer_indices") or [])
             kw.update(linear_attn_kind="mamba2", full_attention_interval=2,

@@ -23,7 +23,7 @@ for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwe
               "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM", "InternLM2ForCausalLM", "Phi3ForCausalLM",
               "GemmaForCausalLM", "Qwen3NextForCausalLM", "GlmForCausalLM", "Glm4ForCausalLM",
               "Ernie4_5ForCausalLM", "Ernie4_5_ForCausalLM", "MiniMaxM2ForCausalLM", "MiniMaxForCausalLM",
-              "MiniMaxText01ForCausalLM", "BambaForCausalLM", "Glm4MoeForCausalLM", "Ernie4_5_MoeForCausalLM", "OlmoeForCausalLM", "GraniteForCausalLM"):
+              "MiniMaxText01ForCausalLM", "BambaForCausalLM", "Glm4MoeForCausalLM", "Ernie4_5_MoeForCausalLM", "OlmoeForCausalLM", "GraniteForCausalLM", "GraniteMoeHybridForCausalLM"):
     register_model(_arch, _causal_lm)
 
 

@@ -742,6 +742,10 @@ class CausalLM:
                         L.w2[e].copy_(w[:, r * Il:(r + 1) * Il])
                 loaded.add(orig_name)
                 continue
+            if ".shared_mlp." in name and not self.cfg.is_moe:
+                # Granite 4 dense hybrids: the gated MLP under its own names, gate and up rows in one tensor
+                name = name.replace(".shared_mlp.input_linear.", ".mlp.gate_up_proj.") \
+                           .replace(".shared_mlp.output_linear.", ".mlp.down_proj.")
             if ".feed_forward." in name or ".pre_ff_layernorm." in name or name.startswith("model.final_layernorm"):
                 # Bamba's names for the MLP, the norm in front of it and the last norm
                 name = name.replace(".feed_forward.", ".mlp.").replace(".pre_ff_layernorm.", ".post_attention_layernorm.") \
