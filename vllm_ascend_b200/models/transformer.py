@@ -647,6 +647,10 @@ class CausalLM:
             if name.endswith("rotary_emb.inv_freq"):
                 continue
             orig_name = name
+            if ".shared_mlp." in name and not self.cfg.is_moe:
+                # Granite 4 dense hybrids: the gated MLP under its own names, gate and up rows in one tensor
+                name = name.replace(".shared_mlp.input_linear.", ".mlp.gate_up_proj.") \
+                           .replace(".shared_mlp.output_linear.", ".mlp.down_proj.")
             if cfg.rope_interleaved and re.search(r"self_attn\.(q|k)_proj\.(weight|bias)$", name):
                 # checkpoints whose rotary pairs are (2i, 2i + 1): move every head's rotated rows into
                 # the half-split order the kernels rotate; q.k is unchanged by a common permutation
@@ -742,10 +746,6 @@ class CausalLM:
                         L.w2[e].copy_(w[:, r * Il:(r + 1) * Il])
                 loaded.add(orig_name)
                 continue
-            if ".shared_mlp." in name and not self.cfg.is_moe:
-                # Granite 4 dense hybrids: the gated MLP under its own names, gate and up rows in one tensor
-                name = name.replace(".shared_mlp.input_linear.", ".mlp.gate_up_proj.") \
-                           .replace(".shared_mlp.output_linear.", ".mlp.down_proj.")
             if ".feed_forward." in name or ".pre_ff_layernorm." in name or name.startswith("model.final_layernorm"):
                 # Bamba's names for the MLP, the norm in front of it and the last norm
                 name = name.replace(".feed_forward.", ".mlp.").replace(".pre_ff_layernorm.", ".post_attention_layernorm.") \
