@@ -164,6 +164,18 @@ def _cases():
     except ImportError:
         pass
     try:
+        import transformers as _tf
+        yield "seed_oss", _tf.SeedOssConfig(**common, head_dim=16, pad_token_id=0), _tf.SeedOssForCausalLM
+        yield "smollm3", _tf.SmolLM3Config(**{**common, "num_hidden_layers": 4}, no_rope_layer_interval=2, pad_token_id=0), \
+            _tf.SmolLM3ForCausalLM                                      # every second layer attends without rotary
+        yield "ministral", _tf.MinistralConfig(**common, head_dim=16, pad_token_id=0), _tf.MinistralForCausalLM
+        yield "helium", _tf.HeliumConfig(**common, head_dim=16, pad_token_id=0), _tf.HeliumForCausalLM
+        yield "dots1", _tf.Dots1Config(**common, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1,
+                                       num_experts_per_tok=2, first_k_dense_replace=1, n_group=2, topk_group=1,
+                                       pad_token_id=0), _tf.Dots1ForCausalLM
+    except (ImportError, AttributeError):
+        pass
+    try:
         from transformers import BambaConfig, BambaForCausalLM
         yield "bamba", BambaConfig(
             vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
@@ -213,7 +225,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "granite4_hybrid", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "granite4_hybrid", "seed_oss", "smollm3", "ministral", "helium", "dots1", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])

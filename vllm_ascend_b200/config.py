@@ -63,6 +63,7 @@ class ModelConfig:
     gemma_norm: bool = False                 # RMSNorm scales by (1 + weight)
     embed_scale: float = 1.0                 # token embeddings are multiplied by this (Gemma: sqrt(hidden))
     partial_rotary_factor: float = 1.0       # fraction of head_dim that is rotated
+    no_rope_layers: Optional[list] = None    # per layer: 0 = this layer's attention uses no rotary embedding (SmolLM3)
     rope_interleaved: bool = False           # checkpoint rotates pairs (2i, 2i+1); q / k rows are re-ordered at load
     sandwich_norm: bool = False              # extra RMSNorm on every sub-layer output (GLM-4)
     # Granite: fixed multipliers on the embeddings (embed_scale), the attention scores, every sub-layer output
@@ -255,6 +256,14 @@ class ModelConfig:
                                         "mlp": (float(d.get("mlp_alpha_factor", 1)), float(d.get("mlp_beta_factor", 1)))})
         if d.get("hc_mult"):
             kw.update(hc_mult=int(d["hc_mult"]), hc_sinkhorn_iters=int(d.get("hc_sinkhorn_iters", 20)))
+        if d.get("no_rope_layers"):
+            kw.update(no_rope_layers=[int(x) for x in d["no_rope_layers"]])
+        if arch.startswith("Dots1"):
+            # dots.llm1: Qwen3-style per-head q / k norms on a DeepSeek-V3 style MoE (sigmoid router, selection bias)
+            kw.update(qk_norm=True)
+            d = dict(d, scoring_func="sigmoid", topk_method="noaux_tc")
+        if arch.startswith("Helium"):
+            kw.update(rope_interleaved=True)
         if arch.startswith("Granite"):
             kw.update(embed_scale=float(d.get("embedding_multiplier", 1.0)),
                       attention_multiplier=float(d["attention_multiplier"]) if d.get("attention_multiplier") else None,

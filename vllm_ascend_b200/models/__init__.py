@@ -23,7 +23,8 @@ for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwe
               "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM", "InternLM2ForCausalLM", "Phi3ForCausalLM",
               "GemmaForCausalLM", "Qwen3NextForCausalLM", "GlmForCausalLM", "Glm4ForCausalLM",
               "Ernie4_5ForCausalLM", "Ernie4_5_ForCausalLM", "MiniMaxM2ForCausalLM", "MiniMaxForCausalLM",
-              "MiniMaxText01ForCausalLM", "BambaForCausalLM", "Glm4MoeForCausalLM", "Ernie4_5_MoeForCausalLM", "OlmoeForCausalLM", "GraniteForCausalLM", "GraniteMoeHybridForCausalLM"):
+              "MiniMaxText01ForCausalLM", "BambaForCausalLM", "Glm4MoeForCausalLM", "Ernie4_5_MoeForCausalLM", "OlmoeForCausalLM", "GraniteForCausalLM", "GraniteMoeHybridForCausalLM", "SeedOssForCausalLM", "SmolLM3ForCausalLM",
+              "MinistralForCausalLM", "Dots1ForCausalLM", "HeliumForCausalLM"):
     register_model(_arch, _causal_lm)
 
 

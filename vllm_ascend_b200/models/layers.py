@@ -328,6 +328,8 @@ class GQAAttention:
             self.k_norm = pf.ones((self.Hkv * self.D,))
         self.scale = self.D ** -0.5 if cfg.attention_multiplier is None else float(cfg.attention_multiplier)
         self.rot_dim = int(self.D * cfg.partial_rotary_factor) // 2 * 2
+        if cfg.no_rope_layers and layer_idx < len(cfg.no_rope_layers) and not cfg.no_rope_layers[layer_idx]:
+            self.rot_dim = 0
         self.cos_sin = get_cos_sin_cache(self.rot_dim, max_pos, cfg.rope_theta, cfg.rope_scaling,
                                          pf.device)
         self.window = cfg.sliding_window or 0
