@@ -621,7 +621,7 @@ class CausalLM:
                 for n, t in m.down_proj.named_tensors():
                     yield f"{p}.mlp.down_proj.{n}", t
         yield "model.norm.weight", self.norm.weight
-        if self.hc_head is not None:
+        if getattr(self, "hc_head", None) is not None:
             yield "model.hc_head_fn", self.hc_head[0]
             yield "model.hc_head_scale", self.hc_head[1]
             yield "model.hc_head_base", self.hc_head[2]
