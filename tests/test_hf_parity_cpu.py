@@ -168,6 +168,7 @@ def _cases():
         yield "seed_oss", _tf.SeedOssConfig(**common, head_dim=16, pad_token_id=0), _tf.SeedOssForCausalLM
         yield "smollm3", _tf.SmolLM3Config(**{**common, "num_hidden_layers": 4}, no_rope_layer_interval=2, pad_token_id=0), \
             _tf.SmolLM3ForCausalLM                                      # every second layer attends without rotary
+        yield "olmo2", _tf.Olmo2Config(**common, pad_token_id=0), _tf.Olmo2ForCausalLM
         yield "ministral", _tf.MinistralConfig(**common, head_dim=16, pad_token_id=0), _tf.MinistralForCausalLM
         yield "helium", _tf.HeliumConfig(**common, head_dim=16, pad_token_id=0), _tf.HeliumForCausalLM
         yield "dots1", _tf.Dots1Config(**common, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1,
@@ -225,7 +226,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "granite4_hybrid", "seed_oss", "smollm3", "ministral", "helium", "dots1", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "granite4_hybrid", "seed_oss", "smollm3", "olmo2", "ministral", "helium", "dots1", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])

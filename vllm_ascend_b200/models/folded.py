@@ -46,7 +46,7 @@ def supports(model, engine_cfg) -> bool:
     return (not cfg.use_mla and not cfg.is_moe and model.dtype == torch.bfloat16 and not cfg.is_hybrid
             and not cfg.gemma_norm and not cfg.sandwich_norm and cfg.embed_scale == 1.0
             and cfg.residual_multiplier == 1.0 and cfg.logits_scaling == 1.0 and not cfg.qk_norm_full
-            and not cfg.deepnorm_factors and cfg.hc_mult <= 1
+            and not cfg.deepnorm_factors and cfg.hc_mult <= 1 and cfg.pre_norm
             and cfg.hidden_act in ("silu", "swish") and not cfg.is_multimodal and not cfg.quantization
             and cfg.hidden_size % 8 == 0 and model.is_first and model.is_last
             and all(isinstance(L.self_attn, GQAAttention) and isinstance(L.mlp, SwiGLUMLP)

@@ -344,6 +344,7 @@ class DecoderLayer:
             self.post_self_attn_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
             self.post_mlp_layernorm = RMSNorm(pf, cfg.hidden_size, cfg.rms_norm_eps, gemma=cfg.gemma_norm)
         self.residual_multiplier = float(cfg.residual_multiplier)
+        self.pre_norm = bool(cfg.pre_norm)
         self.hc_attn = self.hc_ffn = None
         if cfg.hc_mult > 1:
             from ..ops.hyper_connection import HyperConnection
@@ -383,6 +384,13 @@ class DecoderLayer:
             a.o_proj = fgm.FGOProj(inner, fg.otp)
 
     def __call__(self, h, residual, meta, kv_cache):
+        if not self.pre_norm:
+            # sub-layers read the stream as it is; their outputs are normalised before they join it
+            s = h if residual is None else h + residual
+            a, _ = self.post_self_attn_layernorm(self.self_attn(s, meta, kv_cache))
+            s = s + a
+            f, _ = self.post_mlp_layernorm(self.mlp(s))
+            return s + f, None
         if self.hc_attn is not None:
             # h: the widened residual streams [T, m, H]; each sub-layer reads a mixture and writes back
             from ..ops.hyper_connection import hc_post
@@ -647,6 +655,9 @@ class CausalLM:
             if name.endswith("rotary_emb.inv_freq"):
                 continue
             orig_name = name
+            if not cfg.pre_norm:            # OLMo-2 names its two output norms like other models' pre-norms
+                name = name.replace(".post_attention_layernorm.", ".post_self_attn_layernorm.") \
+                           .replace(".post_feedforward_layernorm.", ".post_mlp_layernorm.")
             if ".shared_mlp." in name and not self.cfg.is_moe:
                 # Granite 4 dense hybrids: the gated MLP under its own names, gate and up rows in one tensor
                 name = name.replace(".shared_mlp.input_linear.", ".mlp.gate_up_proj.") \

@@ -230,7 +230,7 @@ def supports(model) -> bool:
     return (not cfg.use_mla and not cfg.is_moe and model.dtype == torch.bfloat16
             and not cfg.mrope_section and not cfg.is_hybrid and cfg.embed_scale == 1.0
             and cfg.residual_multiplier == 1.0 and cfg.logits_scaling == 1.0 and not cfg.qk_norm_full
-            and not cfg.deepnorm_factors and cfg.hc_mult <= 1
+            and not cfg.deepnorm_factors and cfg.hc_mult <= 1 and cfg.pre_norm
             and cfg.hidden_act in ("silu", "swish") and not cfg.attn_output_gate and not cfg.sandwich_norm
             and cfg.partial_rotary_factor == 1.0
             and model.is_first and model.is_last
