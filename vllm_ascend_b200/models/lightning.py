@@ -9,8 +9,8 @@ Instead of a KV cache the layer keeps one [D x D] fp32 state per head and sequen
 
 Heads are sharded over TP (the checkpoint's projection rows are grouped per head, so a rank's
 heads are contiguous rows); the norm's mean square is all-reduced.  Role of the reference's
-linear-attention layer op for this family (SURVEY of the reference: ``BailingMoELinearAttention`` in
-the out-of-tree op table, vllm_ascend/utils.py:703-732, kernels in
+linear-attention layer op for this family (``BailingMoELinearAttention`` in its
+out-of-tree op table, vllm_ascend/utils.py:703-732, kernels in
 vllm_ascend/ops/triton/mamba/lightning_attn.py).
 """
 from __future__ import annotations
