@@ -169,6 +169,7 @@ def _cases():
         yield "smollm3", _tf.SmolLM3Config(**{**common, "num_hidden_layers": 4}, no_rope_layer_interval=2, pad_token_id=0), \
             _tf.SmolLM3ForCausalLM                                      # every second layer attends without rotary
         yield "olmo2", _tf.Olmo2Config(**common, pad_token_id=0), _tf.Olmo2ForCausalLM
+        yield "arcee", _tf.ArceeConfig(**common, pad_token_id=0), _tf.ArceeForCausalLM          # ReLU^2 MLP without a gate
         yield "ministral", _tf.MinistralConfig(**common, head_dim=16, pad_token_id=0), _tf.MinistralForCausalLM
         yield "helium", _tf.HeliumConfig(**common, head_dim=16, pad_token_id=0), _tf.HeliumForCausalLM
         yield "dots1", _tf.Dots1Config(**common, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1,
@@ -226,7 +227,7 @@ def _cases():
         pass
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "granite4_hybrid", "seed_oss", "smollm3", "olmo2", "ministral", "helium", "dots1", "deepseek_v3", "qwen3_next",
+@pytest.mark.parametrize("name", ["llama", "qwen2", "qwen3", "qwen3_moe", "mixtral", "minimax_m2", "minimax_text01", "bamba", "glm4_moe", "ernie45_moe", "olmoe", "granite", "granite4_hybrid", "seed_oss", "smollm3", "olmo2", "arcee", "ministral", "helium", "dots1", "deepseek_v3", "qwen3_next",
                                   "mistral", "phi3", "gemma", "qwen2_moe",
                                   "deepseek_v2", "llama31_rope", "qwen2_yarn",
                                   "deepseek_v3_yarn", "mistral_window", "glm", "glm4", "ernie45"])
@@ -302,7 +303,7 @@ def test_internlm2_names_and_grouped_wqkv_load_like_llama(tmp_path):
     assert all(torch.equal(pa[k], pb[k]) for k in pa)
 
 
-@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01", "bamba", "bamba_g1", "glm4_moe", "granite4_hybrid"])
+@pytest.mark.parametrize("name", ["qwen3_next", "deepseek_v3", "gemma", "qwen2_moe", "minimax_m2", "minimax_text01", "bamba", "bamba_g1", "glm4_moe", "granite4_hybrid", "arcee"])
 def test_checkpoint_sharding_tp2_matches_tp1(name, tmp_path):
     """The same checkpoint directory loaded by two tensor-parallel ranks (gloo) gives the single-rank
     tokens: per-rank slicing of grouped GDN projections, gated q_proj, fused expert tensors, MLA."""

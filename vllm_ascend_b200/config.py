@@ -66,6 +66,7 @@ class ModelConfig:
     no_rope_layers: Optional[list] = None    # per layer: 0 = this layer's attention uses no rotary embedding (SmolLM3)
     rope_interleaved: bool = False           # checkpoint rotates pairs (2i, 2i+1); q / k rows are re-ordered at load
     sandwich_norm: bool = False              # extra RMSNorm on every sub-layer output (GLM-4)
+    mlp_gated: bool = True                   # False (Arcee): act(x W_up) W_down without a gate projection
     pre_norm: bool = True                    # False (OLMo-2): sub-layers read the raw stream, only their outputs are normalised
     # Granite: fixed multipliers on the embeddings (embed_scale), the attention scores, every sub-layer output
     # before it joins the residual stream, and the logits (divided by logits_scaling)
@@ -271,6 +272,8 @@ class ModelConfig:
                       residual_multiplier=float(d.get("residual_multiplier", 1.0)),
                       logits_scaling=float(d.get("logits_scaling", 1.0)),
                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if arch.startswith("Arcee"):
+            kw.update(mlp_gated=False)
         if arch.startswith("Olmo2"):
             # OLMo-2: no norm in front of a sub-layer, RMSNorm on its output; q / k normalised over all heads
             kw.update(pre_norm=False, sandwich_norm=True, qk_norm_full=True)

@@ -24,7 +24,7 @@ for _arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwe
               "GemmaForCausalLM", "Qwen3NextForCausalLM", "GlmForCausalLM", "Glm4ForCausalLM",
               "Ernie4_5ForCausalLM", "Ernie4_5_ForCausalLM", "MiniMaxM2ForCausalLM", "MiniMaxForCausalLM",
               "MiniMaxText01ForCausalLM", "BambaForCausalLM", "Glm4MoeForCausalLM", "Ernie4_5_MoeForCausalLM", "OlmoeForCausalLM", "GraniteForCausalLM", "GraniteMoeHybridForCausalLM", "SeedOssForCausalLM", "SmolLM3ForCausalLM",
-              "MinistralForCausalLM", "Dots1ForCausalLM", "HeliumForCausalLM", "Olmo2ForCausalLM"):
+              "MinistralForCausalLM", "Dots1ForCausalLM", "HeliumForCausalLM", "Olmo2ForCausalLM", "ArceeForCausalLM"):
     register_model(_arch, _causal_lm)
 
 

@@ -425,6 +425,24 @@ _GATED_ACTS = {"silu": None, "swish": None, "gelu_pytorch_tanh": "gelu_tanh", "g
                "gelu_new": "gelu_tanh", "gelu": "gelu"}
 
 
+class PlainMLP:
+    """Ungated MLP: act(x W_up) -> W_down, with ReLU^2 (Arcee), GELU, SiLU or ReLU."""
+
+    _ACTS = {"relu2": lambda t: torch.relu(t).square(), "relu": torch.relu, "silu": torch.nn.functional.silu,
+             "gelu": torch.nn.functional.gelu,
+             "gelu_pytorch_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}
+
+    def __init__(self, pf: ParamFactory, prefix: str, hidden: int, inter: int, comm: TPComm, act: str = "relu2"):
+        if act not in self._ACTS:
+            raise ValueError(f"unsupported MLP activation {act!r}")
+        self.fn = self._ACTS[act]
+        self.up_proj = ColumnParallelLinear(pf, f"{prefix}.up_proj", hidden, [inter], comm)
+        self.down_proj = RowParallelLinear(pf, f"{prefix}.down_proj", inter, hidden, comm)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(self.fn(self.up_proj(x)))
+
+
 class SwiGLUMLP:
     """Gated MLP: act(x W_gate) * (x W_up) -> W_down; SiLU (fused into the GEMM epilogue) or GELU gates."""
 

@@ -376,7 +376,11 @@ class DecoderLayer:
                               reduce_results=False)
             self.mlp = fgm.FGMLP(inner, fg.mlp_tp)
         else:
-            self.mlp = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm, act=cfg.hidden_act)
+            if cfg.mlp_gated:
+                self.mlp = SwiGLUMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm, act=cfg.hidden_act)
+            else:
+                from .layers import PlainMLP
+                self.mlp = PlainMLP(pf, f"{p}.mlp", cfg.hidden_size, cfg.intermediate_size, comm, act=cfg.hidden_act)
         if fg is not None and fg.otp is not None and isinstance(self.self_attn, GQAAttention):
             a = self.self_attn
             inner = RowParallelLinear(pf, f"{p}.self_attn.o_proj", cfg.num_attention_heads * a.D, cfg.hidden_size,
@@ -623,6 +627,11 @@ class CausalLM:
                         yield f"{p}.mlp.shared_experts.gate_up_proj.{n}", t
                     for n, t in m.shared.down_proj.named_tensors():
                         yield f"{p}.mlp.shared_experts.down_proj.{n}", t
+            elif hasattr(m, "up_proj"):            # ungated MLP
+                for n, t in m.up_proj.named_tensors():
+                    yield f"{p}.mlp.up_proj.{n}", t
+                for n, t in m.down_proj.named_tensors():
+                    yield f"{p}.mlp.down_proj.{n}", t
             else:
                 for n, t in m.gate_up_proj.named_tensors():
                     yield f"{p}.mlp.gate_up_proj.{n}", t
