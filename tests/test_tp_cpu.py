@@ -126,6 +126,15 @@ def test_pipeline_parallel_matches_single_rank(preset):
     assert _run(preset, 2, 1, pp=2) == _run(preset, 1, 1)
 
 
+@pytest.mark.parametrize("tp,pp", [(1, 2), (2, 1)])
+def test_profiling_chunk_scheduler_decides_alike_on_every_rank(tp, pp):
+    """Chunk sizes come from measured durations, and every rank has its own scheduler copy: the ranks agree
+    on each duration (start-up profile and online samples), so pipeline stages / TP ranks stay in step and the
+    tokens are those of one rank."""
+    add = {"scheduler_config": {"profiling_chunk_config": {"enabled": True, "min_chunk": 8}}}
+    assert _run("tiny-qwen", 2, tp, pp=pp, addcfg=add) == _run("tiny-qwen", 1, 1)
+
+
 def test_decode_context_parallel_matches_single_rank():
     # MLA latent cache sharded along the sequence over the 2 TP ranks
     assert _run("tiny-deepseek", 2, 2, dcp=2) == _run("tiny-deepseek", 1, 1)

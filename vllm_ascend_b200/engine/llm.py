@@ -92,10 +92,20 @@ class LLMEngine:
         # schedulers that learn from step durations (profiling chunk): start-up profile + online samples
         self._record_step = None
         if hasattr(self.scheduler, "run_profiling"):
+            # Every rank of a replica runs its own copy of the scheduler and all copies must decide alike, so
+            # a duration is agreed on (the slowest rank's) before the predictor sees it.
+            from ..parallel import state as _ps
+            groups = [g for g in (_ps.get_tp_group(), _ps.get_pp_group()) if g.world_size > 1]
+
+            def agreed(seconds: float) -> float:
+                for g in groups:
+                    seconds = max(g.all_gather_object(float(seconds)))
+                return seconds
             if getattr(self.scheduler, "need_timing", True):
-                self._record_step = self.scheduler.record_step
-            if cfg.parallel.pipeline_parallel_size == 1 and cfg.parallel.data_parallel_size == 1:
-                self.scheduler.run_profiling(self.runner.profile_prefill_latency)
+                self._record_step = lambda so, sec: self.scheduler.record_step(so, agreed(sec))
+            if cfg.parallel.data_parallel_size == 1:
+                # pipeline stages take part too: the dummy forward passes activations from stage to stage
+                self.scheduler.run_profiling(lambda n: agreed(self.runner.profile_prefill_latency(n)))
 
     def _make_scheduler(self, num_blocks: int) -> Scheduler:
         from ..core import make_scheduler
