@@ -27,7 +27,8 @@ WORKER = textwrap.dedent("""
               additional_config=json.loads(os.environ["ADDCFG"]) if os.environ.get("ADDCFG") else (dict(cp_kv_cache_interleave_size=4) if dcp > 1 else (dict(finegrained_tp_config=fg) if fg else None)),
               max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, block_size=16)
     rng = np.random.default_rng(2)
-    prompts = [rng.integers(0, cfg.vocab_size, size=24).tolist() for _ in range(3)]
+    lens = [int(x) for x in os.environ["PROMPT_LENS"].split(",")] if os.environ.get("PROMPT_LENS") else [24] * 3
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lens]
     want_lp = os.environ.get("LOGPROBS") == "1"
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True,
                                                 logprobs=2 if want_lp else None))
@@ -52,10 +53,12 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1, fg=None, addcfg=None):
+def _run(preset, world, tp, ep=False, pp=1, dcp=1, pcp=1, fg=None, addcfg=None, prompt_lens=None):
     script = WORKER.format(root=ROOT)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()),
                WORLD_SIZE=str(world), OMP_NUM_THREADS="2")
+    if prompt_lens:
+        env["PROMPT_LENS"] = ",".join(str(n) for n in prompt_lens)
     if addcfg:
         env["ADDCFG"] = json.dumps(addcfg)
     procs = []
@@ -133,6 +136,15 @@ def test_profiling_chunk_scheduler_decides_alike_on_every_rank(tp, pp):
     tokens are those of one rank."""
     add = {"scheduler_config": {"profiling_chunk_config": {"enabled": True, "min_chunk": 8}}}
     assert _run("tiny-qwen", 2, tp, pp=pp, addcfg=add) == _run("tiny-qwen", 1, 1)
+
+
+def test_short_request_first_aging_is_decided_once_for_all_ranks():
+    """A waiting limit of a few microseconds makes the aging decision depend on each rank's clock; the ranks
+    share rank 0's answer, so two TP ranks stay in step (the run ends, with the single-rank tokens)."""
+    add = {"scheduler_config": {"short_request_first_config": {"enabled": True, "threshold": 16,
+                                                               "long_max_wait_ms": 0.005}}}
+    lens = [40, 8, 30, 6, 50, 10, 12, 44]          # long and short prompts, more requests than batch rows
+    assert _run("tiny-qwen", 2, 2, addcfg=add, prompt_lens=lens) == _run("tiny-qwen", 1, 1, prompt_lens=lens)
 
 
 def test_decode_context_parallel_matches_single_rank():

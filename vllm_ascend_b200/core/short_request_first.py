@@ -32,6 +32,17 @@ class ShortRequestFirstScheduler(Scheduler):
         self.threshold = c.threshold
         self.long_max_wait_ms = c.long_max_wait_ms
         self.clock = clock
+        # Every rank of a replica runs its own copy of this queue and all copies must pick alike, but their
+        # clocks differ: whether the oldest long request has aged is decided by the first rank and shared.
+        self._agree = None
+        from ..parallel import state as pstate
+        groups = [g for g in (pstate.get_tp_group(), pstate.get_pp_group()) if g.world_size > 1]
+        if groups:
+            def agree(flag: bool) -> bool:
+                for g in groups:
+                    flag = bool(g.broadcast_object(bool(flag), src=0))
+                return flag
+            self._agree = agree
         # requests that bypass both lanes: preempted ones always, plus whatever the deployment names
         # (e.g. requests whose KV is already on the device after a remote prefill)
         self.immediate_predicate = immediate_predicate
@@ -71,9 +82,7 @@ class ShortRequestFirstScheduler(Scheduler):
         lane, aged = None, False
         if self.immediate:
             lane = self.immediate
-        elif self.long and self.short and self.long_max_wait_ms > 0 and \
-                (self.clock() - self._long_enqueued.get(self.long[0].request_id, self.clock())) * 1e3 \
-                >= self.long_max_wait_ms:
+        elif self.long and self.short and self.long_max_wait_ms > 0 and self._aged():
             lane, aged = self.long, True
         elif self.short:
             lane = self.short
@@ -84,6 +93,11 @@ class ShortRequestFirstScheduler(Scheduler):
             return None
         self._pinned = (lane, lane[0], aged)
         return lane[0]
+
+    def _aged(self) -> bool:
+        waited_ms = (self.clock() - self._long_enqueued.get(self.long[0].request_id, self.clock())) * 1e3
+        flag = waited_ms >= self.long_max_wait_ms
+        return self._agree(flag) if self._agree is not None else flag
 
     def _pop_waiting(self, req: Request, dispatched: bool = True) -> None:
         pin, self._pinned = self._pinned, None
